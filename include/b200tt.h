@@ -1,0 +1,228 @@
+/*
+ * b200tt.h -- C ABI of the B200 compute engine that stands in for an
+ * implementation of metalium-rs's `burn_tt::Engine` trait
+ * (crates/burn-tt/src/server.rs:42-786).
+ *
+ * Every function mirrors one trait method: same argument meaning, same result
+ * dims, same refusal behaviour.  A Rust `impl Engine for CudaEngine` binds these
+ * one to one (see the `rust/` sources beside the package and INTEGRATION.md).
+ *
+ * Conventions
+ *  - Tensors are opaque `b200_buffer` ids numbered by the engine
+ *    (`BufferId = u64`, server.rs:862).  A tensor is a row-major `[rows, cols]`
+ *    matrix; rank-N tensors are stored `[prod(leading), last]`
+ *    (crates/burn-tt/src/tensor.rs:905).  F32, I32 and Bool are 32-bit words,
+ *    BF16 is 16-bit.  Device layout is plain row-major, leading dimension =
+ *    cols, base 256-byte aligned.
+ *  - Every producing call returns the new id in `*out` and the stored dims in
+ *    `out_dims[2]` (`Result<(BufferId, [usize; 2]), TtError>`).
+ *  - Every call returns a status: 0 ok, else one of `b200_status` mapping onto
+ *    `TtError` (crates/burn-tt/src/error.rs:26-67).  `b200_last_error` gives
+ *    the cause text.  Unsupported shapes or dtypes are refused, never computed
+ *    on the host.
+ *  - Calls are asynchronous: they launch on the engine's stream and return.
+ *    `b200_download*` and `b200_sync` are the waits and report any earlier
+ *    device-side failure (server.rs:2392-2405).
+ *  - One engine is driven by one thread at a time (the reference's server
+ *    thread, server.rs:2801-2820); different engines may be driven
+ *    concurrently.
+ */
+#ifndef B200TT_H
+#define B200TT_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct b200_engine b200_engine;
+typedef uint64_t b200_buffer; /* server.rs:862 `BufferId` */
+
+/* error.rs:26-67 */
+enum b200_status {
+  B200_OK = 0,
+  B200_OUT_OF_MEMORY = 1, /* TtError::OutOfMemory{slots,free,largest} */
+  B200_UNSUPPORTED = 2,   /* TtError::Unsupported */
+  B200_DEVICE = 3,        /* TtError::Device */
+  B200_TIMEOUT = 4,       /* TtError::Timeout */
+  B200_STALE = 5,         /* TtError::StaleTensor */
+  B200_DOMAIN = 6,        /* TtError::Device("... DOMAIN ..."): bad index, /0 */
+  B200_NO_DEVICE = 7      /* TtError::NoDriver / NoSuchCard */
+};
+
+/* tt-kernels/src/tensor.rs:751 `Elem` (+ Elem::BF16) */
+enum b200_elem { B200_F32 = 0, B200_I32 = 1, B200_BOOL = 2, B200_BF16 = 3 };
+
+/* tt-kernels/src/sfpu/reduce.rs:56 `ReduceOp`, :117 `Axis` */
+enum b200_reduce_op {
+  B200_SUM = 0, B200_MAX = 1, B200_PROD = 2, B200_ALL = 3, B200_ANY = 4,
+  B200_BITOR = 5, B200_SUM_I32 = 6, B200_PROD_I32 = 7, B200_MIN_I32 = 8,
+  B200_MAX_I32 = 9
+};
+enum b200_axis { B200_ROWS = 0 /* -> [1,cols] */, B200_COLS = 1 /* -> [rows,1] */ };
+
+/* tt-kernels/src/tensor.rs:3785 `Eltwise{kind, scalar, scalar2}`; kinds are the
+ * reference's numbers (tt-kernels/src/kind.rs:12-26, sfpu/ops.rs:24-251). */
+typedef struct { uint32_t kind; float scalar; float scalar2; } b200_eltwise_op;
+/* tt-kernels/src/tensor.rs:3479 `Block{at, transposed}` */
+typedef struct { uint64_t at[2]; int32_t transposed; int32_t _pad; } b200_block;
+/* tt-kernels/src/tensor.rs:6659 `BlockMove` */
+typedef struct { uint64_t from[2]; uint64_t to[2]; uint64_t extent[2];
+                 int32_t transposed; int32_t _pad; } b200_block_move;
+/* burn-tt/src/server.rs:3449 `BlockArg{id, at, dims}` */
+typedef struct { b200_buffer id; uint64_t at[2]; uint64_t dims[2]; } b200_block_arg;
+/* tt-kernels/src/session.rs:802 `BatchedLayout{lhs_padded, stacked}` */
+typedef struct { int32_t lhs_padded; int32_t stacked; } b200_batched_layout;
+/* tt-device/src/device.rs:133 `Traffic`, re-read as host<->device copies */
+typedef struct {
+  uint64_t bytes_h2d, bytes_d2h, h2d_calls, d2h_calls;
+  uint64_t launches;        /* kernels this engine launched */
+  uint64_t pool_reserved;   /* bytes held from the driver */
+  uint64_t pool_in_use;     /* bytes in live buffers */
+  uint64_t pool_high_water; /* max of pool_in_use */
+} b200_traffic;
+
+/* registry.rs:31 `TtConfig`, reduced to what a GPU engine needs. */
+typedef struct {
+  int32_t f32_matmul_mode;   /* 0 auto, 1 FFMA only, 2 split-precision tensor cores */
+  int32_t bf16_matmul_mode;  /* 0 auto, 1 SIMT only, 2 tcgen05 only (refuse otherwise) */
+  uint64_t pool_limit_bytes; /* 0 = no limit beyond the device's */
+  int32_t fail_alloc_at;     /* host fault hook: the Nth allocation reports OOM; 0 off */
+  int32_t _pad;
+} b200_config;
+
+/* --- attach / detach: server.rs:2738 `attach`, :2711 `AttachGuard::drop` --- */
+int32_t b200_engine_create(int32_t device_ordinal, const b200_config* cfg, b200_engine** out);
+void b200_engine_destroy(b200_engine* eng);
+/* server.rs:75 `supports_dram`, :240 `supports_batched_layout`, :53 */
+int32_t b200_supports_dram(const b200_engine* eng);
+int32_t b200_supports_batched_layout(const b200_engine* eng);
+int32_t b200_supports_exact_matmul(const b200_engine* eng);
+/* Text of the last failure on this engine (or of a failed create when eng is NULL). */
+size_t b200_last_error(const b200_engine* eng, char* buf, size_t len);
+/* OutOfMemory's fields for the last B200_OUT_OF_MEMORY: need, free, largest. */
+void b200_last_oom(const b200_engine* eng, uint64_t out[3]);
+
+/* --- storage: server.rs:91,104,107,115,160,170,174,285 --- */
+int32_t b200_upload_f32(b200_engine*, const float* values, uint64_t rows, uint64_t cols, b200_buffer* out);
+int32_t b200_upload_bf16(b200_engine*, const uint16_t* values, uint64_t rows, uint64_t cols, b200_buffer* out);
+int32_t b200_upload_bits(b200_engine*, const uint32_t* bits, uint64_t rows, uint64_t cols, int32_t elem, b200_buffer* out);
+int32_t b200_download_f32(b200_engine*, b200_buffer id, float* out, uint64_t capacity_elems);
+int32_t b200_download_bf16(b200_engine*, b200_buffer id, uint16_t* out, uint64_t capacity_elems);
+int32_t b200_download_bits(b200_engine*, b200_buffer id, uint32_t* out, uint64_t capacity_elems);
+void    b200_free(b200_engine*, b200_buffer id); /* unknown id: no-op */
+int32_t b200_zeros(b200_engine*, uint64_t rows, uint64_t cols, int32_t elem, b200_buffer* out, uint64_t out_dims[2]);
+/* dims and elem of a live buffer (the server's `dims_of`, server.rs:2427) */
+int32_t b200_dims(const b200_engine*, b200_buffer id, uint64_t out_dims[2], int32_t* elem);
+/* Device address of a live buffer, for a collective library that shares the process. */
+int32_t b200_device_ptr(const b200_engine*, b200_buffer id, void** ptr, uint64_t* bytes);
+/* Register caller-owned device memory as a buffer (never freed by the engine). */
+int32_t b200_adopt(b200_engine*, void* device_ptr, uint64_t rows, uint64_t cols, int32_t elem, b200_buffer* out);
+/* server.rs:742 `copy_into` */
+int32_t b200_copy_into(b200_engine*, b200_buffer src, b200_buffer dst);
+/* Overwrite a live buffer from host memory (same dims): steady-state input refresh. */
+int32_t b200_write_f32(b200_engine*, b200_buffer id, const float* values, uint64_t n);
+int32_t b200_write_bf16(b200_engine*, b200_buffer id, const uint16_t* values, uint64_t n);
+
+/* --- products: server.rs:70,178,191,229,245 --- */
+/* `matmul` (host-staged, required by the trait): upload, matmul_dram, download. */
+int32_t b200_matmul_host(b200_engine*, const float* a, const float* b, const uint64_t mkn[3], float* out);
+/* `matmul_dram` / `matmul_dram_bf16`: C = op(A) op(B).  F32 operands give an F32
+ * result; with out_bf16 the F32 accumulator is rounded once to BF16.  BF16
+ * operands accumulate in F32. */
+int32_t b200_matmul(b200_engine*, b200_buffer a, int32_t a_transposed, b200_buffer b, int32_t b_transposed,
+                    int32_t out_bf16, b200_buffer* out, uint64_t out_dims[2]);
+/* `matmul_dram_batched(_layout)`: one [m,k]x[k,n] product per (Block,Block) pair,
+ * read where it lies; output [items*m, n] stacked, or with layout.stacked == 0
+ * product i at row i*ceil(m/32)*32 (server.rs:3749-3754).  layout NULL = STACKED. */
+int32_t b200_matmul_batched(b200_engine*, b200_buffer a, b200_buffer b, const b200_block* a_blocks,
+                            const b200_block* b_blocks, uint64_t items, const uint64_t mkn[3],
+                            const b200_batched_layout* layout, int32_t out_bf16,
+                            b200_buffer* out, uint64_t out_dims[2]);
+
+/* --- element-wise: server.rs:492,504,519,536,555 --- */
+/* `eltwise_op_as`: out = a (kind) b [, c]; b/c may be 0 (absent).  b may be a's
+ * shape, [1,cols], [rows,1] or whole rows repeated down a (tensor.rs:3799-3859). */
+int32_t b200_eltwise(b200_engine*, const b200_eltwise_op* op, b200_buffer a, b200_buffer b, b200_buffer c,
+                     int32_t out_bf16, b200_buffer* out, uint64_t out_dims[2]);
+/* `eltwise_blocks_as`: the same over blocks of buffers; b, c may be NULL. */
+int32_t b200_eltwise_blocks(b200_engine*, const b200_eltwise_op* op, const b200_block_arg* a,
+                            const b200_block_arg* b, const b200_block_arg* c, int32_t out_bf16,
+                            b200_buffer* out, uint64_t out_dims[2]);
+/* server.rs:128 `cast_float`: F32 <-> BF16. */
+int32_t b200_cast_float(b200_engine*, b200_buffer a, int32_t to_bf16, b200_buffer* out, uint64_t out_dims[2]);
+/* server.rs:566 `rope_blocks` */
+int32_t b200_rope_blocks(b200_engine*, const b200_block_arg* x, const b200_block_arg* cos_,
+                         const b200_block_arg* sin_, uint64_t head, int32_t out_bf16,
+                         b200_buffer* out, uint64_t out_dims[2]);
+
+/* --- reductions: server.rs:80,399,404,423,428,438,449,466,477 --- */
+/* `reduce(a, op, axis, then)`: then_kind 0 = none, else an exact unary kind
+ * applied to the result with scalar bits then_bits (tensor.rs:6038). */
+int32_t b200_reduce(b200_engine*, b200_buffer a, int32_t op, int32_t axis, uint32_t then_kind,
+                    uint32_t then_bits, b200_buffer* out, uint64_t out_dims[2]);
+int32_t b200_sum_rows(b200_engine*, b200_buffer a, b200_buffer* out, uint64_t out_dims[2]);
+/* Burn's `float_sum` / `float_mean` of a resident tensor (ops.rs:3246-3398): [1,1]. */
+int32_t b200_full_sum(b200_engine*, b200_buffer a, int32_t mean, b200_buffer* out, uint64_t out_dims[2]);
+/* `full_reduce(values, dims, mean)`: host values in, scalar out, device arithmetic. */
+int32_t b200_full_reduce(b200_engine*, const float* values, const uint64_t dims[2], int32_t mean, float* out);
+/* `softmax_rows(x, mask, scale)`: mask 0 = none; Bool words, read for rows r % mask_rows. */
+int32_t b200_softmax_rows(b200_engine*, b200_buffer x, b200_buffer mask, float scale,
+                          b200_buffer* out, uint64_t out_dims[2]);
+/* Burn's `activation::log_softmax` over the last dim (ops.rs:5153-5158). */
+int32_t b200_log_softmax_rows(b200_engine*, b200_buffer x, b200_buffer* out, uint64_t out_dims[2]);
+int32_t b200_rms(b200_engine*, b200_buffer a, float eps, b200_buffer* out, uint64_t out_dims[2]);
+int32_t b200_rms_norm(b200_engine*, b200_buffer a, b200_buffer gamma, float eps, int32_t out_bf16,
+                      b200_buffer* out, uint64_t out_dims[2]);
+/* `add_rms_norm`: s = a + b and s's RMSNorm: (s, norm). */
+int32_t b200_add_rms_norm(b200_engine*, b200_buffer a, b200_buffer b, b200_buffer gamma, float eps,
+                          b200_buffer out[2], uint64_t out_dims[2]);
+/* `argmax_row`: a [rows, cols] -> [rows, 1] I32 (the trait passes one row). */
+int32_t b200_argmax_row(b200_engine*, b200_buffer a, b200_buffer* out, uint64_t out_dims[2]);
+
+/* --- indexing: server.rs:269,277,293,300,329,339,349,358,368,379,482 --- */
+int32_t b200_select_rows(b200_engine*, b200_buffer table, b200_buffer indices, b200_buffer* out, uint64_t out_dims[2]);
+int32_t b200_pick_columns(b200_engine*, b200_buffer input, b200_buffer indices, b200_buffer* out, uint64_t out_dims[2]);
+/* Burn's scatter-add of a [rows,1] value at (r, idx[r]) into a copy of t (ops.rs:1043). */
+int32_t b200_scatter_add_columns(b200_engine*, b200_buffer t, b200_buffer indices, b200_buffer value,
+                                 b200_buffer* out, uint64_t out_dims[2]);
+int32_t b200_select_add_rows(b200_engine*, b200_buffer t, b200_buffer indices, b200_buffer value,
+                             b200_buffer* out, uint64_t out_dims[2]);
+int32_t b200_rows_add(b200_engine*, b200_buffer t, const uint64_t* indices, uint64_t n, b200_buffer value,
+                      b200_buffer* out, uint64_t out_dims[2]);
+int32_t b200_assign_rows(b200_engine*, b200_buffer t, b200_buffer value, const uint64_t* dst_src_pairs,
+                         uint64_t n, b200_buffer* out, uint64_t out_dims[2]);
+int32_t b200_scatter_rows(b200_engine*, b200_buffer table, b200_buffer indices, b200_buffer values,
+                          int32_t column, b200_buffer* out, uint64_t out_dims[2]);
+int32_t b200_gather_indexed(b200_engine*, b200_buffer input, b200_buffer indices, b200_buffer* out, uint64_t out_dims[2]);
+/* `gather_rows(sources, rows:[(source, row)], cols)` */
+int32_t b200_gather_rows(b200_engine*, const b200_buffer* sources, uint64_t n_sources,
+                         const uint64_t* source_row_pairs, uint64_t n_rows, uint64_t cols,
+                         b200_buffer* out, uint64_t out_dims[2]);
+/* `slice_rows`: a view, no copy; the parent stays alive while a view is. */
+int32_t b200_slice_rows(b200_engine*, b200_buffer a, uint64_t first, uint64_t rows, b200_buffer* out, uint64_t out_dims[2]);
+int32_t b200_copy_blocks(b200_engine*, b200_buffer a, const b200_block_move* moves, uint64_t n,
+                         const uint64_t dims[2], b200_buffer* out, uint64_t out_dims[2]);
+/* `repack(a, sources:[[row,col]] in output order, dims)` */
+int32_t b200_repack(b200_engine*, b200_buffer a, const uint64_t* row_col_pairs, const uint64_t dims[2],
+                    b200_buffer* out, uint64_t out_dims[2]);
+
+/* --- waits and observability: lib.rs:218 `sync`, server.rs:584,663 --- */
+int32_t b200_sync(b200_engine*);
+void    b200_set_op_label(b200_engine*, const char* label);
+void    b200_traffic_get(const b200_engine*, b200_traffic* out);
+/* Device time of the ops launched between the two marks, in milliseconds
+ * (CUDA events on the engine's stream).  `b200_timer_stop` is a wait. */
+int32_t b200_timer_start(b200_engine*);
+int32_t b200_timer_stop(b200_engine*, float* ms);
+/* The engine's stream as a `cudaStream_t`, for a caller that shares the process. */
+void*   b200_stream(const b200_engine*);
+/* Name of the kernel path the last product took ("tcgen05", "simt", ...). */
+const char* b200_last_matmul_path(const b200_engine*);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200TT_H */

@@ -1,0 +1,49 @@
+// Scalar device helpers shared by the kernel files.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+// "positive and not NaN" on raw bits: the test the reference's relu family uses
+// (crates/tt-kernels/src/sfpu/ops.rs:3877-3906): relu(NaN) = 0, relu(-0) = +0.
+__device__ __forceinline__ bool positive_not_nan(uint32_t u) {
+  return u != 0u && u <= 0x7f800000u;
+}
+__device__ __forceinline__ uint32_t relu_bits(uint32_t u) { return positive_not_nan(u) ? u : 0u; }
+
+// BF16 narrowing as the reference defines it (crates/tt-kernels/src/bf16.rs:1-4;
+// model at crates/tt-tests/tests/step270_native_bf16.rs:244-255): ties to even,
+// NaNs quieted keeping sign and high payload, results below 2^-126 to signed zero.
+__device__ __forceinline__ uint16_t f32_to_bf16_bits(uint32_t x) {
+  uint32_t r;
+  if ((x & 0x7fffffffu) > 0x7f800000u) r = x | 0x00400000u;
+  else r = x + 0x7fffu + ((x >> 16) & 1u);
+  r &= 0xffff0000u;
+  if ((r & 0x7fffffffu) < 0x00800000u) r &= 0x80000000u;
+  return (uint16_t)(r >> 16);
+}
+__device__ __forceinline__ float bf16_bits_to_f32(uint16_t h) {
+  return __uint_as_float((uint32_t)h << 16);
+}
+
+// burn-flex's sigmoid: two branches on the sign, one exp(-|x|)
+// (crates/tt-kernels/src/sfpu/ops.rs:772-775).
+__device__ __forceinline__ float sigmoid_flex(float x) {
+  const float e = expf(-fabsf(x));
+  const float d = 1.0f + e;
+  return (x >= 0.f) ? (1.0f / d) : (e / d);
+}
+
+// 0.5 x (1 + erf(x / sqrt 2))  (crates/tt-kernels/src/sfpu/ops.rs:135)
+__device__ __forceinline__ float gelu_erf(float x) {
+  return (0.5f * x) * (1.0f + erff(x * 0.70710678118654752440f));
+}
+// 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float x3 = x * x * x;
+  const float inner = 0.7978845608028654f * (x + 0.044715f * x3);
+  return (0.5f * x) * (1.0f + tanhf(inner));
+}
+
+}  // namespace b200

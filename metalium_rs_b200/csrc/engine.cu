@@ -1,0 +1,1177 @@
+// The engine behind include/b200tt.h: host-side state and routing for one GPU.
+//
+// It plays the part of an `impl burn_tt::Engine` (crates/burn-tt/src/server.rs:42-786)
+// with the reference's `Session`, GDDR allocator, L1 planner and data movers
+// (crates/tt-kernels/src/session.rs:824) replaced by
+//   - a device-memory pool (cached blocks, reuse in stream order),
+//   - a buffer table `id -> {ptr, rows, cols, elem}` with views that keep their parent alive,
+//   - one CUDA stream on which every op is launched in call order,
+//   - a device error word read at the waits (an index out of its table, a division by
+//     zero), so a failed op never traps the GPU.
+// No op falls back to host arithmetic: what the kernels cannot do is refused.
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <map>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/b200tt.h"
+#include "kernels.h"
+#include "kinds.h"
+
+using namespace b200;
+
+namespace {
+
+std::string g_create_error;
+
+struct Buf {
+  void* ptr = nullptr;
+  uint64_t rows = 0, cols = 0;
+  int elem = B200_F32;
+  uint64_t bytes = 0;       // bytes of the pool block (0 for views / adopted memory)
+  b200_buffer parent = 0;   // view of another buffer
+  int views = 0;            // live views of this buffer
+  bool freed = false;       // free() called while views are alive
+  bool adopted = false;
+};
+
+inline uint64_t elem_bytes(int elem) { return elem == B200_BF16 ? 2 : 4; }
+
+}  // namespace
+
+struct b200_engine {
+  int device = 0;
+  b200_config cfg{};
+  cudaStream_t stream = nullptr;
+  cudaEvent_t t0 = nullptr, t1 = nullptr;
+  int* d_err = nullptr;
+  int* h_err = nullptr;  // pinned
+  std::string last_error;
+  uint64_t oom[3] = {0, 0, 0};
+  int sticky = 0;  // first asynchronous failure, reported at every later wait
+  std::string sticky_text;
+  std::string label;
+  const char* matmul_path = "none";
+  b200_traffic traffic{};
+  uint64_t next_id = 1;
+  uint64_t alloc_calls = 0;
+  std::unordered_map<b200_buffer, Buf> bufs;
+  std::multimap<uint64_t, void*> cache;  // free blocks by size
+  float* full_scratch = nullptr;
+
+  int fail(int code, const char* fmt, ...) {
+    char tmp[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(tmp, sizeof tmp, fmt, ap);
+    va_end(ap);
+    last_error = label.empty() ? std::string(tmp) : (label + ": " + tmp);
+    return code;
+  }
+  int cuda_fail(cudaError_t e, const char* what) {
+    return fail(B200_DEVICE, "%s: %s", what, cudaGetErrorString(e));
+  }
+
+  // ---- pool ---------------------------------------------------------------------
+  static uint64_t round_size(uint64_t n) {
+    if (n == 0) n = 1;
+    if (n <= 4096) return (n + 255) & ~255ull;
+    if (n <= (1ull << 20)) {
+      uint64_t p = 4096;
+      while (p < n) p <<= 1;
+      return p;
+    }
+    return (n + (2ull << 20) - 1) & ~((2ull << 20) - 1);
+  }
+  void release_cache() {
+    for (auto& kv : cache) {
+      cudaFree(kv.second);
+      traffic.pool_reserved -= kv.first;
+    }
+    cache.clear();
+  }
+  int alloc(uint64_t bytes, void** out, uint64_t* got) {
+    ++alloc_calls;
+    const uint64_t sz = round_size(bytes);
+    if (cfg.fail_alloc_at > 0 && alloc_calls == (uint64_t)cfg.fail_alloc_at) {
+      oom[0] = sz; oom[1] = 0; oom[2] = 0;
+      return fail(B200_OUT_OF_MEMORY, "out of device memory: need %llu bytes (injected)", (unsigned long long)sz);
+    }
+    auto it = cache.lower_bound(sz);
+    if (it != cache.end() && it->first <= sz + sz / 4) {
+      *out = it->second;
+      *got = it->first;
+      cache.erase(it);
+    } else {
+      if (cfg.pool_limit_bytes && traffic.pool_reserved + sz > cfg.pool_limit_bytes) release_cache();
+      if (cfg.pool_limit_bytes && traffic.pool_reserved + sz > cfg.pool_limit_bytes) {
+        oom[0] = sz; oom[1] = cfg.pool_limit_bytes - traffic.pool_reserved; oom[2] = oom[1];
+        return fail(B200_OUT_OF_MEMORY, "out of device memory: need %llu bytes, pool limit leaves %llu",
+                    (unsigned long long)sz, (unsigned long long)oom[1]);
+      }
+      void* p = nullptr;
+      cudaError_t e = cudaMalloc(&p, sz);
+      if (e != cudaSuccess) {
+        cudaGetLastError();
+        cudaStreamSynchronize(stream);
+        release_cache();
+        e = cudaMalloc(&p, sz);
+      }
+      if (e != cudaSuccess) {
+        cudaGetLastError();
+        size_t fr = 0, tot = 0;
+        cudaMemGetInfo(&fr, &tot);
+        oom[0] = sz; oom[1] = fr; oom[2] = fr;
+        return fail(B200_OUT_OF_MEMORY, "out of device memory: need %llu bytes, %llu free",
+                    (unsigned long long)sz, (unsigned long long)fr);
+      }
+      *out = p;
+      *got = sz;
+      traffic.pool_reserved += sz;
+    }
+    traffic.pool_in_use += *got;
+    traffic.pool_high_water = std::max(traffic.pool_high_water, traffic.pool_in_use);
+    return B200_OK;
+  }
+  // The block returns to the cache at once: every user of it was enqueued on the one
+  // stream before this call, and so is every later user.
+  void release(void* p, uint64_t sz) {
+    traffic.pool_in_use -= sz;
+    cache.emplace(sz, p);
+  }
+
+  // ---- buffer table ------------------------------------------------------------
+  int new_buffer(uint64_t rows, uint64_t cols, int elem, b200_buffer* id, Buf** out) {
+    void* p = nullptr;
+    uint64_t got = 0;
+    const uint64_t bytes = rows * cols * elem_bytes(elem);
+    int st = alloc(bytes, &p, &got);
+    if (st) return st;
+    Buf b;
+    b.ptr = p; b.rows = rows; b.cols = cols; b.elem = elem; b.bytes = got;
+    *id = next_id++;
+    auto ins = bufs.emplace(*id, b);
+    if (out) *out = &ins.first->second;
+    return B200_OK;
+  }
+  Buf* get(b200_buffer id) {
+    auto it = bufs.find(id);
+    if (it == bufs.end() || it->second.freed) return nullptr;
+    return &it->second;
+  }
+  int need(b200_buffer id, Buf** out, const char* what) {
+    Buf* b = get(id);
+    if (!b) return fail(B200_STALE, "%s: buffer %llu is not live on this engine", what, (unsigned long long)id);
+    *out = b;
+    return B200_OK;
+  }
+  void drop(b200_buffer id) {
+    auto it = bufs.find(id);
+    if (it == bufs.end()) return;
+    Buf& b = it->second;
+    if (b.views > 0) { b.freed = true; return; }
+    const b200_buffer parent = b.parent;
+    if (!b.parent && !b.adopted && b.ptr) release(b.ptr, b.bytes);
+    bufs.erase(it);
+    if (parent) {
+      auto pit = bufs.find(parent);
+      if (pit != bufs.end()) {
+        pit->second.views--;
+        if (pit->second.views == 0 && pit->second.freed) { pit->second.freed = false; drop(parent); }
+      }
+    }
+  }
+  // Host metadata (block lists, index lists) to a temporary device block.
+  int to_device(const void* host, uint64_t bytes, void** dev, uint64_t* got) {
+    int st = alloc(bytes, dev, got);
+    if (st) return st;
+    cudaError_t e = cudaMemcpyAsync(*dev, host, bytes, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) { release(*dev, *got); return cuda_fail(e, "metadata upload"); }
+    traffic.bytes_h2d += bytes;
+    return B200_OK;
+  }
+  int launched(cudaError_t e, const char* what, int n = 1) {
+    if (e == cudaErrorNotSupported) return fail(B200_UNSUPPORTED, "%s: unsupported", what);
+    if (e != cudaSuccess) return cuda_fail(e, what);
+    traffic.launches += n;
+    return B200_OK;
+  }
+  int wait() {
+    cudaError_t e = cudaMemcpyAsync(h_err, d_err, sizeof(int), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) {
+      sticky = B200_DEVICE;
+      sticky_text = std::string("device failure: ") + cudaGetErrorString(e);
+    } else if (*h_err != 0 && !sticky) {
+      sticky = *h_err;
+      sticky_text = sticky == B200_DOMAIN ? "DOMAIN: an index outside its table or a division by zero in an earlier op"
+                                          : (sticky == B200_TIMEOUT ? "TIMEOUT: a bounded device wait ran out in an earlier op"
+                                                                    : "an earlier op failed on the device");
+    }
+    if (sticky) { last_error = sticky_text; return sticky; }
+    return B200_OK;
+  }
+};
+
+namespace {
+
+bool host_is_pinned(const void* p) {
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, p) != cudaSuccess) { cudaGetLastError(); return false; }
+  return at.type == cudaMemoryTypeHost;
+}
+
+int upload_any(b200_engine* e, const void* src, uint64_t rows, uint64_t cols, int elem, b200_buffer* out) {
+  cudaSetDevice(e->device);
+  Buf* b = nullptr;
+  int st = e->new_buffer(rows, cols, elem, out, &b);
+  if (st) return st;
+  const uint64_t bytes = rows * cols * elem_bytes(elem);
+  if (bytes) {
+    cudaError_t ce = cudaMemcpyAsync(b->ptr, src, bytes, cudaMemcpyHostToDevice, e->stream);
+    if (ce != cudaSuccess) { e->drop(*out); return e->cuda_fail(ce, "upload"); }
+    // A pinned source is read by DMA after the call returns; the trait lends the slice
+    // only for the call, so wait for the copy.
+    if (host_is_pinned(src)) cudaStreamSynchronize(e->stream);
+  }
+  e->traffic.bytes_h2d += bytes;
+  e->traffic.h2d_calls++;
+  return B200_OK;
+}
+
+int download_any(b200_engine* e, b200_buffer id, void* dst, uint64_t cap, int want_bytes, const char* what) {
+  cudaSetDevice(e->device);
+  Buf* b = nullptr;
+  int st = e->need(id, &b, what);
+  if (st) return st;
+  if ((int)elem_bytes(b->elem) != want_bytes)
+    return e->fail(B200_UNSUPPORTED, "%s: buffer %llu holds %d-byte elements", what, (unsigned long long)id, (int)elem_bytes(b->elem));
+  const uint64_t n = b->rows * b->cols;
+  if (cap < n) return e->fail(B200_UNSUPPORTED, "%s: %llu elements into room for %llu", what, (unsigned long long)n, (unsigned long long)cap);
+  if (n) {
+    cudaError_t ce = cudaMemcpyAsync(dst, b->ptr, n * want_bytes, cudaMemcpyDeviceToHost, e->stream);
+    if (ce != cudaSuccess) return e->cuda_fail(ce, what);
+  }
+  e->traffic.bytes_d2h += n * want_bytes;
+  e->traffic.d2h_calls++;
+  return e->wait();
+}
+
+inline void set_dims(uint64_t d[2], uint64_t r, uint64_t c) { if (d) { d[0] = r; d[1] = c; } }
+
+Mat mat_of(const Buf* b) {
+  Mat m;
+  m.p = b->ptr; m.ld = b->cols; m.rows = b->rows; m.cols = b->cols; m.bf16 = b->elem == B200_BF16;
+  return m;
+}
+// A block of a buffer.
+int mat_of_block(b200_engine* e, const b200_block_arg* a, Mat* m, const char* what) {
+  Buf* b = nullptr;
+  int st = e->need(a->id, &b, what);
+  if (st) return st;
+  if (a->at[0] + a->dims[0] > b->rows || a->at[1] + a->dims[1] > b->cols)
+    return e->fail(B200_UNSUPPORTED, "%s: block [%llu,%llu]+[%llu,%llu] outside [%llu,%llu]", what,
+                   (unsigned long long)a->at[0], (unsigned long long)a->at[1], (unsigned long long)a->dims[0],
+                   (unsigned long long)a->dims[1], (unsigned long long)b->rows, (unsigned long long)b->cols);
+  m->bf16 = b->elem == B200_BF16;
+  m->p = (const char*)b->ptr + (a->at[0] * b->cols + a->at[1]) * elem_bytes(b->elem);
+  m->ld = b->cols; m->rows = a->dims[0]; m->cols = a->dims[1];
+  return B200_OK;
+}
+
+// How b meets a: the same shape, one row, one column, or whole rows repeated
+// (crates/tt-kernels/src/tensor.rs:3799-3859).
+bool broadcast_ok(uint32_t k, uint64_t rows, uint64_t cols, const Mat& b) {
+  if (b.rows == rows && b.cols == cols) return true;
+  if (!kind::broadcasts(k)) return false;
+  if (b.rows == 1 && b.cols == cols) return true;
+  if (b.cols == 1 && b.rows == rows) return true;
+  if (b.cols == 1 && b.rows == 1) return true;
+  if (b.cols == cols && b.rows > 0 && rows % b.rows == 0) return true;
+  return false;
+}
+
+int run_eltwise(b200_engine* e, const b200_eltwise_op* op, Mat a, const Mat* b, const Mat* c, int out_bf16,
+                b200_buffer* out, uint64_t out_dims[2]) {
+  const uint32_t k = op->kind;
+  const int ar = kind::arity(k);
+  if (ar == 0) return e->fail(B200_UNSUPPORTED, "eltwise: kind %#x is not an element-wise op of this engine", k);
+  if ((ar >= 2) != (b != nullptr) || (ar == 3) != (c != nullptr))
+    return e->fail(B200_UNSUPPORTED, "eltwise %s: takes %d operand(s)", kind::name(k), ar);
+  Mat bb, cc;
+  if (b) bb = *b;
+  if (c) cc = *c;
+  // ADD and MUL take the broadcast operand on either side (crates/burn-tt/src/ops.rs:1850).
+  if (b && (k == kind::ADD || k == kind::MUL) && (a.rows < bb.rows || a.cols < bb.cols)) std::swap(a, bb);
+  const uint64_t rows = a.rows, cols = a.cols;
+  if (b && !broadcast_ok(k, rows, cols, bb))
+    return e->fail(B200_UNSUPPORTED, "eltwise %s: [%llu,%llu] with [%llu,%llu]", kind::name(k),
+                   (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)bb.rows, (unsigned long long)bb.cols);
+  if (c && (cc.rows != rows || cc.cols != cols))
+    return e->fail(B200_UNSUPPORTED, "eltwise %s: third operand [%llu,%llu] is not [%llu,%llu]", kind::name(k),
+                   (unsigned long long)cc.rows, (unsigned long long)cc.cols, (unsigned long long)rows, (unsigned long long)cols);
+  if (k == kind::CLAMP && !(op->scalar <= op->scalar2))
+    return e->fail(B200_UNSUPPORTED, "eltwise CLAMP: bounds %g, %g are crossed or NaN", op->scalar, op->scalar2);
+  const int relem = kind::result_elem(k);
+  if (out_bf16 && relem != 0) return e->fail(B200_UNSUPPORTED, "eltwise %s: a BF16 result of a non-float kind", kind::name(k));
+  const int oelem = relem == 0 ? (out_bf16 ? B200_BF16 : B200_F32) : (relem == 1 ? B200_I32 : B200_BOOL);
+  Buf* ob = nullptr;
+  int st = e->new_buffer(rows, cols, oelem, out, &ob);
+  if (st) return st;
+  EltwiseArgs g{};
+  g.kind = k; g.s1 = op->scalar; g.s2 = op->scalar2;
+  g.a = a; g.b = bb; g.c = cc;
+  g.out = ob->ptr; g.out_ld = cols; g.out_bf16 = out_bf16; g.rows = rows; g.cols = cols; g.err = e->d_err;
+  st = e->launched(launch_eltwise(g, e->stream), "eltwise");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
+}
+
+int copy_of(b200_engine* e, const Buf* src, b200_buffer* out, Buf** ob) {
+  int st = e->new_buffer(src->rows, src->cols, src->elem, out, ob);
+  if (st) return st;
+  const uint64_t bytes = src->rows * src->cols * elem_bytes(src->elem);
+  if (bytes) {
+    cudaError_t ce = cudaMemcpyAsync((*ob)->ptr, src->ptr, bytes, cudaMemcpyDeviceToDevice, e->stream);
+    if (ce != cudaSuccess) { e->drop(*out); return e->cuda_fail(ce, "copy"); }
+  }
+  return B200_OK;
+}
+
+int index_buf(b200_engine* e, b200_buffer id, Buf** b, const char* what) {
+  int st = e->need(id, b, what);
+  if (st) return st;
+  if ((*b)->elem != B200_I32) return e->fail(B200_UNSUPPORTED, "%s: indices must be I32", what);
+  return B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t b200_engine_create(int32_t device_ordinal, const b200_config* cfg, b200_engine** out) {
+  *out = nullptr;
+  int count = 0;
+  cudaError_t ce = cudaGetDeviceCount(&count);
+  if (ce != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    g_create_error = std::string("no CUDA device: ") + (ce != cudaSuccess ? cudaGetErrorString(ce) : "device count is 0");
+    return B200_NO_DEVICE;
+  }
+  if (device_ordinal < 0 || device_ordinal >= count) {
+    g_create_error = "no such device " + std::to_string(device_ordinal) + " (present: 0.." + std::to_string(count - 1) + ")";
+    return B200_NO_DEVICE;
+  }
+  cudaDeviceProp prop;
+  cudaGetDeviceProperties(&prop, device_ordinal);
+  if (prop.major != 10) {
+    g_create_error = std::string("device ") + prop.name + " is sm_" + std::to_string(prop.major) + std::to_string(prop.minor) +
+                     "; this engine's kernels are built for sm_100a only";
+    return B200_UNSUPPORTED;
+  }
+  if (cfg && (cfg->f32_matmul_mode < 0 || cfg->f32_matmul_mode > 2 || cfg->bf16_matmul_mode < 0 || cfg->bf16_matmul_mode > 2)) {
+    g_create_error = "config: unknown matmul mode";
+    return B200_UNSUPPORTED;
+  }
+  b200_engine* e = new b200_engine();
+  e->device = device_ordinal;
+  if (cfg) e->cfg = *cfg;
+  cudaSetDevice(device_ordinal);
+  ce = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking);
+  if (ce == cudaSuccess) ce = cudaEventCreate(&e->t0);
+  if (ce == cudaSuccess) ce = cudaEventCreate(&e->t1);
+  if (ce == cudaSuccess) ce = cudaMalloc(&e->d_err, 256);
+  if (ce == cudaSuccess) ce = cudaMemsetAsync(e->d_err, 0, 256, e->stream);
+  if (ce == cudaSuccess) ce = cudaMallocHost(&e->h_err, sizeof(int));
+  if (ce == cudaSuccess) ce = cudaMalloc(&e->full_scratch, full_sum_scratch_floats() * sizeof(float));
+  if (ce != cudaSuccess) {
+    g_create_error = std::string("engine set-up: ") + cudaGetErrorString(ce);
+    delete e;
+    return B200_DEVICE;
+  }
+  *e->h_err = 0;
+  *out = e;
+  return B200_OK;
+}
+
+void b200_engine_destroy(b200_engine* e) {
+  if (!e) return;
+  cudaSetDevice(e->device);
+  cudaStreamSynchronize(e->stream);
+  for (auto& kv : e->bufs)
+    if (!kv.second.parent && !kv.second.adopted && kv.second.ptr) cudaFree(kv.second.ptr);
+  for (auto& kv : e->cache) cudaFree(kv.second);
+  cudaFree(e->d_err);
+  cudaFree(e->full_scratch);
+  cudaFreeHost(e->h_err);
+  cudaEventDestroy(e->t0);
+  cudaEventDestroy(e->t1);
+  cudaStreamDestroy(e->stream);
+  delete e;
+}
+
+int32_t b200_supports_dram(const b200_engine*) { return 1; }
+int32_t b200_supports_batched_layout(const b200_engine*) { return 1; }
+int32_t b200_supports_exact_matmul(const b200_engine*) { return 0; }
+
+size_t b200_last_error(const b200_engine* e, char* buf, size_t len) {
+  const std::string& s = e ? e->last_error : g_create_error;
+  if (buf && len) {
+    const size_t n = std::min(len - 1, s.size());
+    memcpy(buf, s.data(), n);
+    buf[n] = 0;
+  }
+  return s.size();
+}
+void b200_last_oom(const b200_engine* e, uint64_t out[3]) { out[0] = e->oom[0]; out[1] = e->oom[1]; out[2] = e->oom[2]; }
+
+// ---- storage -------------------------------------------------------------------
+int32_t b200_upload_f32(b200_engine* e, const float* v, uint64_t rows, uint64_t cols, b200_buffer* out) {
+  return upload_any(e, v, rows, cols, B200_F32, out);
+}
+int32_t b200_upload_bf16(b200_engine* e, const uint16_t* v, uint64_t rows, uint64_t cols, b200_buffer* out) {
+  return upload_any(e, v, rows, cols, B200_BF16, out);
+}
+int32_t b200_upload_bits(b200_engine* e, const uint32_t* v, uint64_t rows, uint64_t cols, int32_t elem, b200_buffer* out) {
+  if (elem != B200_F32 && elem != B200_I32 && elem != B200_BOOL)
+    return e->fail(B200_UNSUPPORTED, "upload_bits: elem %d is not a 32-bit element", elem);
+  return upload_any(e, v, rows, cols, elem, out);
+}
+int32_t b200_download_f32(b200_engine* e, b200_buffer id, float* out, uint64_t cap) {
+  Buf* b = e->get(id);
+  if (b && b->elem != B200_F32) return e->fail(B200_UNSUPPORTED, "download: buffer %llu is not F32", (unsigned long long)id);
+  return download_any(e, id, out, cap, 4, "download");
+}
+int32_t b200_download_bf16(b200_engine* e, b200_buffer id, uint16_t* out, uint64_t cap) {
+  return download_any(e, id, out, cap, 2, "download_bf16");
+}
+int32_t b200_download_bits(b200_engine* e, b200_buffer id, uint32_t* out, uint64_t cap) {
+  return download_any(e, id, out, cap, 4, "download_bits");
+}
+void b200_free(b200_engine* e, b200_buffer id) { e->drop(id); }
+
+int32_t b200_zeros(b200_engine* e, uint64_t rows, uint64_t cols, int32_t elem, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  if (elem < 0 || elem > B200_BF16) return e->fail(B200_UNSUPPORTED, "zeros: unknown elem %d", elem);
+  Buf* b = nullptr;
+  int st = e->new_buffer(rows, cols, elem, out, &b);
+  if (st) return st;
+  const uint64_t bytes = rows * cols * elem_bytes(elem);
+  if (bytes) {
+    cudaError_t ce = cudaMemsetAsync(b->ptr, 0, bytes, e->stream);
+    if (ce != cudaSuccess) { e->drop(*out); return e->cuda_fail(ce, "zeros"); }
+  }
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
+}
+
+int32_t b200_dims(const b200_engine* e, b200_buffer id, uint64_t out_dims[2], int32_t* elem) {
+  auto it = e->bufs.find(id);
+  if (it == e->bufs.end() || it->second.freed) return B200_STALE;
+  set_dims(out_dims, it->second.rows, it->second.cols);
+  if (elem) *elem = it->second.elem;
+  return B200_OK;
+}
+int32_t b200_device_ptr(const b200_engine* e, b200_buffer id, void** ptr, uint64_t* bytes) {
+  auto it = e->bufs.find(id);
+  if (it == e->bufs.end() || it->second.freed) return B200_STALE;
+  *ptr = it->second.ptr;
+  if (bytes) *bytes = it->second.rows * it->second.cols * elem_bytes(it->second.elem);
+  return B200_OK;
+}
+int32_t b200_adopt(b200_engine* e, void* p, uint64_t rows, uint64_t cols, int32_t elem, b200_buffer* out) {
+  if (elem < 0 || elem > B200_BF16) return e->fail(B200_UNSUPPORTED, "adopt: unknown elem %d", elem);
+  if (reinterpret_cast<uintptr_t>(p) & 15) return e->fail(B200_UNSUPPORTED, "adopt: address is not 16-byte aligned");
+  Buf b;
+  b.ptr = p; b.rows = rows; b.cols = cols; b.elem = elem; b.adopted = true;
+  *out = e->next_id++;
+  e->bufs.emplace(*out, b);
+  return B200_OK;
+}
+int32_t b200_copy_into(b200_engine* e, b200_buffer src, b200_buffer dst) {
+  cudaSetDevice(e->device);
+  Buf *s = nullptr, *d = nullptr;
+  int st = e->need(src, &s, "copy_into");
+  if (!st) st = e->need(dst, &d, "copy_into");
+  if (st) return st;
+  if (s->rows != d->rows || s->cols != d->cols || s->elem != d->elem)
+    return e->fail(B200_UNSUPPORTED, "copy_into: [%llu,%llu] into [%llu,%llu]", (unsigned long long)s->rows,
+                   (unsigned long long)s->cols, (unsigned long long)d->rows, (unsigned long long)d->cols);
+  cudaError_t ce = cudaMemcpyAsync(d->ptr, s->ptr, s->rows * s->cols * elem_bytes(s->elem), cudaMemcpyDeviceToDevice, e->stream);
+  return ce == cudaSuccess ? B200_OK : e->cuda_fail(ce, "copy_into");
+}
+static int write_any(b200_engine* e, b200_buffer id, const void* v, uint64_t n, int eb) {
+  cudaSetDevice(e->device);
+  Buf* b = nullptr;
+  int st = e->need(id, &b, "write");
+  if (st) return st;
+  if (b->rows * b->cols != n || (int)elem_bytes(b->elem) != eb)
+    return e->fail(B200_UNSUPPORTED, "write: %llu elements of %d bytes into [%llu,%llu]", (unsigned long long)n, eb,
+                   (unsigned long long)b->rows, (unsigned long long)b->cols);
+  cudaError_t ce = cudaMemcpyAsync(b->ptr, v, n * eb, cudaMemcpyHostToDevice, e->stream);
+  if (ce != cudaSuccess) return e->cuda_fail(ce, "write");
+  e->traffic.bytes_h2d += n * eb;
+  e->traffic.h2d_calls++;
+  return B200_OK;
+}
+int32_t b200_write_f32(b200_engine* e, b200_buffer id, const float* v, uint64_t n) { return write_any(e, id, v, n, 4); }
+int32_t b200_write_bf16(b200_engine* e, b200_buffer id, const uint16_t* v, uint64_t n) { return write_any(e, id, v, n, 2); }
+
+// ---- products -------------------------------------------------------------------
+static int run_gemm(b200_engine* e, GemmArgs& g, const GemmBatch* batches_host, const char* what) {
+  const char* why = "";
+  const bool want_tc = g.in_bf16 ? e->cfg.bf16_matmul_mode != 1 : e->cfg.f32_matmul_mode == 2;
+  if (want_tc && gemm_tc_supported(g, &why)) {
+    e->matmul_path = "tcgen05";
+    return e->launched(launch_gemm_tc(g, batches_host, e->d_err, e->stream), what);
+  }
+  if (g.in_bf16 && e->cfg.bf16_matmul_mode == 2)
+    return e->fail(B200_UNSUPPORTED, "%s: the tcgen05 path refuses this product (%s) and the engine is set to use no other", what, why);
+  e->matmul_path = "simt";
+  return e->launched(launch_gemm_simt(g, e->stream), what);
+}
+
+int32_t b200_matmul(b200_engine* e, b200_buffer a, int32_t ta, b200_buffer b, int32_t tb, int32_t out_bf16,
+                    b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *A = nullptr, *B = nullptr;
+  int st = e->need(a, &A, "matmul");
+  if (!st) st = e->need(b, &B, "matmul");
+  if (st) return st;
+  const bool abf = A->elem == B200_BF16, bbf = B->elem == B200_BF16;
+  if ((A->elem != B200_F32 && !abf) || (B->elem != B200_F32 && !bbf) || abf != bbf)
+    return e->fail(B200_UNSUPPORTED, "matmul: operands must both be F32 or both BF16 (got elem %d, %d)", A->elem, B->elem);
+  const uint64_t m = ta ? A->cols : A->rows, k = ta ? A->rows : A->cols;
+  const uint64_t k2 = tb ? B->cols : B->rows, n = tb ? B->rows : B->cols;
+  if (k != k2)
+    return e->fail(B200_UNSUPPORTED, "matmul: [%llu,%llu] x [%llu,%llu]", (unsigned long long)m, (unsigned long long)k,
+                   (unsigned long long)k2, (unsigned long long)n);
+  Buf* C = nullptr;
+  st = e->new_buffer(m, n, out_bf16 ? B200_BF16 : B200_F32, out, &C);
+  if (st) return st;
+  // new_buffer may rehash the table
+  A = e->get(a); B = e->get(b);
+  GemmArgs g{};
+  g.a = A->ptr; g.b = B->ptr; g.c = C->ptr;
+  g.in_bf16 = abf; g.out_bf16 = out_bf16;
+  g.m = m; g.n = n; g.k = k;
+  g.lda = A->cols; g.ldb = B->cols; g.ldc = n;
+  g.a_trans = ta; g.b_trans = tb;
+  g.batch = 1; g.batches_dev = nullptr;
+  if (k == 0) {
+    cudaMemsetAsync(C->ptr, 0, m * n * elem_bytes(C->elem), e->stream);
+  } else {
+    st = run_gemm(e, g, nullptr, "matmul");
+    if (st) { e->drop(*out); return st; }
+  }
+  set_dims(out_dims, m, n);
+  return B200_OK;
+}
+
+int32_t b200_matmul_host(b200_engine* e, const float* a, const float* b, const uint64_t mkn[3], float* out) {
+  b200_buffer ia = 0, ib = 0, ic = 0;
+  uint64_t d[2];
+  int st = b200_upload_f32(e, a, mkn[0], mkn[1], &ia);
+  if (!st) st = b200_upload_f32(e, b, mkn[1], mkn[2], &ib);
+  if (!st) st = b200_matmul(e, ia, 0, ib, 0, 0, &ic, d);
+  if (!st) st = b200_download_f32(e, ic, out, mkn[0] * mkn[2]);
+  b200_free(e, ia); b200_free(e, ib); b200_free(e, ic);
+  return st;
+}
+
+int32_t b200_matmul_batched(b200_engine* e, b200_buffer a, b200_buffer b, const b200_block* ab, const b200_block* bb,
+                            uint64_t items, const uint64_t mkn[3], const b200_batched_layout* layout,
+                            int32_t out_bf16, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *A = nullptr, *B = nullptr;
+  int st = e->need(a, &A, "matmul_batched");
+  if (!st) st = e->need(b, &B, "matmul_batched");
+  if (st) return st;
+  const bool abf = A->elem == B200_BF16, bbf = B->elem == B200_BF16;
+  if ((A->elem != B200_F32 && !abf) || (B->elem != B200_F32 && !bbf) || abf != bbf)
+    return e->fail(B200_UNSUPPORTED, "matmul_batched: operands must both be F32 or both BF16");
+  const uint64_t m = mkn[0], k = mkn[1], n = mkn[2];
+  const bool stacked = !layout || layout->stacked;
+  const uint64_t step = stacked ? m : ((m + 31) / 32) * 32;  // server.rs:3749-3754
+  std::vector<GemmBatch> bt(items);
+  for (uint64_t i = 0; i < items; ++i) {
+    const b200_block &x = ab[i], &y = bb[i];
+    const uint64_t ar = x.transposed ? k : m, ac = x.transposed ? m : k;
+    const uint64_t br = y.transposed ? n : k, bc = y.transposed ? k : n;
+    if (x.at[0] + ar > A->rows || x.at[1] + ac > A->cols || y.at[0] + br > B->rows || y.at[1] + bc > B->cols)
+      return e->fail(B200_UNSUPPORTED, "matmul_batched: item %llu's block lies outside its buffer", (unsigned long long)i);
+    bt[i].a_off = x.at[0] * A->cols + x.at[1];
+    bt[i].b_off = y.at[0] * B->cols + y.at[1];
+    bt[i].c_off = i * step * n;
+    bt[i].a_trans = x.transposed; bt[i].b_trans = y.transposed;
+  }
+  Buf* C = nullptr;
+  st = e->new_buffer(items * step, n, out_bf16 ? B200_BF16 : B200_F32, out, &C);
+  if (st) return st;
+  A = e->get(a); B = e->get(b);
+  if ((!stacked && step != m) || k == 0) cudaMemsetAsync(C->ptr, 0, items * step * n * elem_bytes(C->elem), e->stream);
+  if (items && k) {
+    void* dev = nullptr;
+    uint64_t got = 0;
+    st = e->to_device(bt.data(), items * sizeof(GemmBatch), &dev, &got);
+    if (st) { e->drop(*out); return st; }
+    GemmArgs g{};
+    g.a = A->ptr; g.b = B->ptr; g.c = C->ptr;
+    g.in_bf16 = abf; g.out_bf16 = out_bf16;
+    g.m = m; g.n = n; g.k = k;
+    g.lda = A->cols; g.ldb = B->cols; g.ldc = n;
+    g.batch = items; g.batches_dev = (const GemmBatch*)dev;
+    st = run_gemm(e, g, bt.data(), "matmul_batched");
+    e->release(dev, got);
+    if (st) { e->drop(*out); return st; }
+  }
+  set_dims(out_dims, items * step, n);
+  return B200_OK;
+}
+
+// ---- element-wise ----------------------------------------------------------------
+int32_t b200_eltwise(b200_engine* e, const b200_eltwise_op* op, b200_buffer a, b200_buffer b, b200_buffer c,
+                     int32_t out_bf16, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *A = nullptr, *B = nullptr, *C = nullptr;
+  int st = e->need(a, &A, "eltwise");
+  if (!st && b) st = e->need(b, &B, "eltwise");
+  if (!st && c) st = e->need(c, &C, "eltwise");
+  if (st) return st;
+  Mat ma = mat_of(A), mb, mc;
+  if (B) mb = mat_of(B);
+  if (C) mc = mat_of(C);
+  return run_eltwise(e, op, ma, B ? &mb : nullptr, C ? &mc : nullptr, out_bf16, out, out_dims);
+}
+
+int32_t b200_eltwise_blocks(b200_engine* e, const b200_eltwise_op* op, const b200_block_arg* a, const b200_block_arg* b,
+                            const b200_block_arg* c, int32_t out_bf16, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Mat ma, mb, mc;
+  int st = mat_of_block(e, a, &ma, "eltwise_blocks");
+  if (!st && b) st = mat_of_block(e, b, &mb, "eltwise_blocks");
+  if (!st && c) st = mat_of_block(e, c, &mc, "eltwise_blocks");
+  if (st) return st;
+  return run_eltwise(e, op, ma, b ? &mb : nullptr, c ? &mc : nullptr, out_bf16, out, out_dims);
+}
+
+int32_t b200_cast_float(b200_engine* e, b200_buffer a, int32_t to_bf16, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf* A = nullptr;
+  int st = e->need(a, &A, "cast_float");
+  if (st) return st;
+  const int want_in = to_bf16 ? B200_F32 : B200_BF16;
+  if (A->elem != want_in) return e->fail(B200_UNSUPPORTED, "cast_float: source elem %d", A->elem);
+  const uint64_t rows = A->rows, cols = A->cols;
+  const void* src = A->ptr;
+  Buf* O = nullptr;
+  st = e->new_buffer(rows, cols, to_bf16 ? B200_BF16 : B200_F32, out, &O);
+  if (st) return st;
+  st = e->launched(launch_cast(src, O->ptr, rows * cols, to_bf16, e->stream), "cast_float");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
+}
+
+int32_t b200_rope_blocks(b200_engine* e, const b200_block_arg* x, const b200_block_arg* cs, const b200_block_arg* sn,
+                         uint64_t head, int32_t out_bf16, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Mat mx, mc, ms;
+  int st = mat_of_block(e, x, &mx, "rope");
+  if (!st) st = mat_of_block(e, cs, &mc, "rope");
+  if (!st) st = mat_of_block(e, sn, &ms, "rope");
+  if (st) return st;
+  if (head == 0 || head % 2 || mx.cols % head)
+    return e->fail(B200_UNSUPPORTED, "rope: %llu columns are not heads of %llu", (unsigned long long)mx.cols, (unsigned long long)head);
+  auto table_ok = [&](const Mat& t) {
+    return (t.cols == head || t.cols == mx.cols) && t.rows > 0 && mx.rows % t.rows == 0;
+  };
+  if (!table_ok(mc) || !table_ok(ms)) return e->fail(B200_UNSUPPORTED, "rope: a table's shape does not meet x's");
+  Buf* O = nullptr;
+  st = e->new_buffer(mx.rows, mx.cols, out_bf16 ? B200_BF16 : B200_F32, out, &O);
+  if (st) return st;
+  st = e->launched(launch_rope(mx, mc, ms, head, O->ptr, mx.cols, out_bf16, mx.rows, mx.cols, e->stream), "rope");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, mx.rows, mx.cols);
+  return B200_OK;
+}
+
+// ---- reductions ------------------------------------------------------------------
+int32_t b200_reduce(b200_engine* e, b200_buffer a, int32_t op, int32_t axis, uint32_t then_kind, uint32_t then_bits,
+                    b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf* A = nullptr;
+  int st = e->need(a, &A, "reduce");
+  if (st) return st;
+  if (op < 0 || op > B200_MAX_I32 || (axis != 0 && axis != 1)) return e->fail(B200_UNSUPPORTED, "reduce: op %d axis %d", op, axis);
+  switch (then_kind) {
+    case 0: case kind::NEG: case kind::ABS: case kind::SIGN: case kind::RELU: case kind::CLAMP_MIN:
+    case kind::CLAMP_MAX: case kind::INT_ABS: break;
+    default: return e->fail(B200_UNSUPPORTED, "reduce: kind %#x is not an exact unary finishing kind", then_kind);
+  }
+  const int oelem = (op == B200_ALL || op == B200_ANY) ? B200_BOOL : (op >= B200_SUM_I32 ? B200_I32 : B200_F32);
+  if (A->elem == B200_BF16 && oelem != B200_F32) return e->fail(B200_UNSUPPORTED, "reduce: an integer fold of a BF16 tensor");
+  const uint64_t rows = A->rows, cols = A->cols;
+  const void* src = A->ptr;
+  const int bf = A->elem == B200_BF16;
+  const uint64_t orows = axis == 0 ? 1 : rows, ocols = axis == 0 ? cols : 1;
+  Buf* O = nullptr;
+  st = e->new_buffer(orows, ocols, oelem, out, &O);
+  if (st) return st;
+  st = e->launched(launch_reduce(src, bf, rows, cols, op, axis, then_kind, then_bits, O->ptr, e->stream), "reduce");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, orows, ocols);
+  return B200_OK;
+}
+int32_t b200_sum_rows(b200_engine* e, b200_buffer a, b200_buffer* out, uint64_t out_dims[2]) {
+  return b200_reduce(e, a, B200_SUM, B200_ROWS, 0, 0, out, out_dims);
+}
+int32_t b200_full_sum(b200_engine* e, b200_buffer a, int32_t mean, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf* A = nullptr;
+  int st = e->need(a, &A, "full_sum");
+  if (st) return st;
+  if (A->elem != B200_F32) return e->fail(B200_UNSUPPORTED, "full_sum: F32 only");
+  const float* src = (const float*)A->ptr;
+  const uint64_t n = A->rows * A->cols;
+  Buf* O = nullptr;
+  st = e->new_buffer(1, 1, B200_F32, out, &O);
+  if (st) return st;
+  st = e->launched(launch_full_sum(src, n, mean, e->full_scratch, (float*)O->ptr, e->stream), "full_sum", 2);
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, 1, 1);
+  return B200_OK;
+}
+int32_t b200_full_reduce(b200_engine* e, const float* values, const uint64_t dims[2], int32_t mean, float* out) {
+  b200_buffer ia = 0, io = 0;
+  uint64_t d[2];
+  int st = b200_upload_f32(e, values, dims[0], dims[1], &ia);
+  if (!st) st = b200_full_sum(e, ia, mean, &io, d);
+  if (!st) st = b200_download_f32(e, io, out, 1);
+  b200_free(e, ia); b200_free(e, io);
+  return st;
+}
+
+static int softmax_any(b200_engine* e, b200_buffer x, b200_buffer mask, float scale, int log_form, b200_buffer* out,
+                       uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *X = nullptr, *M = nullptr;
+  int st = e->need(x, &X, "softmax_rows");
+  if (!st && mask) st = e->need(mask, &M, "softmax_rows");
+  if (st) return st;
+  if (X->elem != B200_F32) return e->fail(B200_UNSUPPORTED, "softmax_rows: F32 scores only");
+  if (M && (M->elem != B200_BOOL || M->cols != X->cols || M->rows == 0 || X->rows % M->rows))
+    return e->fail(B200_UNSUPPORTED, "softmax_rows: mask [%llu,%llu] does not meet [%llu,%llu]", (unsigned long long)M->rows,
+                   (unsigned long long)M->cols, (unsigned long long)X->rows, (unsigned long long)X->cols);
+  const uint64_t rows = X->rows, cols = X->cols;
+  const float* xs = (const float*)X->ptr;
+  const uint32_t* ms = M ? (const uint32_t*)M->ptr : nullptr;
+  const uint64_t mrows = M ? M->rows : 1;
+  Buf* O = nullptr;
+  st = e->new_buffer(rows, cols, B200_F32, out, &O);
+  if (st) return st;
+  st = e->launched(launch_softmax_rows(xs, ms, mrows, scale, log_form, (float*)O->ptr, rows, cols, e->stream), "softmax_rows");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
+}
+int32_t b200_softmax_rows(b200_engine* e, b200_buffer x, b200_buffer mask, float scale, b200_buffer* out, uint64_t out_dims[2]) {
+  return softmax_any(e, x, mask, scale, 0, out, out_dims);
+}
+int32_t b200_log_softmax_rows(b200_engine* e, b200_buffer x, b200_buffer* out, uint64_t out_dims[2]) {
+  return softmax_any(e, x, 0, 1.0f, 1, out, out_dims);
+}
+
+int32_t b200_rms(b200_engine* e, b200_buffer a, float eps, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf* A = nullptr;
+  int st = e->need(a, &A, "rms");
+  if (st) return st;
+  if (A->elem != B200_F32) return e->fail(B200_UNSUPPORTED, "rms: F32 only");
+  const uint64_t rows = A->rows, cols = A->cols;
+  const float* src = (const float*)A->ptr;
+  Buf* O = nullptr;
+  st = e->new_buffer(rows, 1, B200_F32, out, &O);
+  if (st) return st;
+  st = e->launched(launch_rms(src, rows, cols, eps, (float*)O->ptr, e->stream), "rms");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, rows, 1);
+  return B200_OK;
+}
+
+static bool is_float(const Buf* b) { return b->elem == B200_F32 || b->elem == B200_BF16; }
+
+int32_t b200_rms_norm(b200_engine* e, b200_buffer a, b200_buffer gamma, float eps, int32_t out_bf16, b200_buffer* out,
+                      uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *A = nullptr, *G = nullptr;
+  int st = e->need(a, &A, "rms_norm");
+  if (!st && gamma) st = e->need(gamma, &G, "rms_norm");
+  if (st) return st;
+  if (!is_float(A) || (G && (!is_float(G) || G->rows != 1 || G->cols != A->cols)))
+    return e->fail(B200_UNSUPPORTED, "rms_norm: gamma must be [1, cols] floats");
+  const uint64_t rows = A->rows, cols = A->cols;
+  const void* src = A->ptr; const int abf = A->elem == B200_BF16;
+  const void* gp = G ? G->ptr : nullptr; const int gbf = G ? G->elem == B200_BF16 : 0;
+  Buf* O = nullptr;
+  st = e->new_buffer(rows, cols, out_bf16 ? B200_BF16 : B200_F32, out, &O);
+  if (st) return st;
+  st = e->launched(launch_rms_norm(src, abf, nullptr, 0, gp, gbf, eps, nullptr, 0, O->ptr, out_bf16, rows, cols, e->stream), "rms_norm");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
+}
+
+int32_t b200_add_rms_norm(b200_engine* e, b200_buffer a, b200_buffer b, b200_buffer gamma, float eps, b200_buffer out[2],
+                          uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *A = nullptr, *B = nullptr, *G = nullptr;
+  int st = e->need(a, &A, "add_rms_norm");
+  if (!st) st = e->need(b, &B, "add_rms_norm");
+  if (!st && gamma) st = e->need(gamma, &G, "add_rms_norm");
+  if (st) return st;
+  if (!is_float(A) || !is_float(B) || A->rows != B->rows || A->cols != B->cols ||
+      (G && (!is_float(G) || G->rows != 1 || G->cols != A->cols)))
+    return e->fail(B200_UNSUPPORTED, "add_rms_norm: operand shapes do not meet");
+  const uint64_t rows = A->rows, cols = A->cols;
+  const int abf = A->elem == B200_BF16, bbf = B->elem == B200_BF16;
+  const int obf = abf && bbf;  // results in the operands' type
+  const void *ap = A->ptr, *bp = B->ptr, *gp = G ? G->ptr : nullptr;
+  const int gbf = G ? G->elem == B200_BF16 : 0;
+  Buf *S = nullptr, *N = nullptr;
+  st = e->new_buffer(rows, cols, obf ? B200_BF16 : B200_F32, &out[0], &S);
+  if (st) return st;
+  void* sp = S->ptr;
+  st = e->new_buffer(rows, cols, obf ? B200_BF16 : B200_F32, &out[1], &N);
+  if (st) { e->drop(out[0]); return st; }
+  st = e->launched(launch_rms_norm(ap, abf, bp, bbf, gp, gbf, eps, sp, obf, N->ptr, obf, rows, cols, e->stream), "add_rms_norm");
+  if (st) { e->drop(out[0]); e->drop(out[1]); return st; }
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
+}
+
+int32_t b200_argmax_row(b200_engine* e, b200_buffer a, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf* A = nullptr;
+  int st = e->need(a, &A, "argmax_row");
+  if (st) return st;
+  if (A->elem != B200_F32) return e->fail(B200_UNSUPPORTED, "argmax_row: F32 only");
+  if (A->cols == 0 || A->cols > (1ull << 31)) return e->fail(B200_UNSUPPORTED, "argmax_row: %llu columns", (unsigned long long)A->cols);
+  const uint64_t rows = A->rows, cols = A->cols;
+  const float* src = (const float*)A->ptr;
+  Buf* O = nullptr;
+  st = e->new_buffer(rows, 1, B200_I32, out, &O);
+  if (st) return st;
+  st = e->launched(launch_argmax_rows(src, rows, cols, (int32_t*)O->ptr, e->stream), "argmax_row");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, rows, 1);
+  return B200_OK;
+}
+
+// ---- indexing ----------------------------------------------------------------------
+int32_t b200_select_rows(b200_engine* e, b200_buffer table, b200_buffer indices, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *T = nullptr, *I = nullptr;
+  int st = e->need(table, &T, "select_rows");
+  if (!st) st = index_buf(e, indices, &I, "select_rows");
+  if (st) return st;
+  const uint64_t n = I->rows * I->cols, cols = T->cols, trows = T->rows;
+  const int elem = T->elem;
+  const void* tp = T->ptr; const int32_t* ip = (const int32_t*)I->ptr;
+  Buf* O = nullptr;
+  st = e->new_buffer(n, cols, elem, out, &O);
+  if (st) return st;
+  st = e->launched(launch_select_rows(tp, trows, cols, (int)elem_bytes(elem), ip, n, O->ptr, e->d_err, e->stream), "select_rows");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, n, cols);
+  return B200_OK;
+}
+
+int32_t b200_pick_columns(b200_engine* e, b200_buffer input, b200_buffer indices, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *X = nullptr, *I = nullptr;
+  int st = e->need(input, &X, "pick_columns");
+  if (!st) st = index_buf(e, indices, &I, "pick_columns");
+  if (st) return st;
+  if (elem_bytes(X->elem) != 4 || I->rows * I->cols != X->rows)
+    return e->fail(B200_UNSUPPORTED, "pick_columns: [%llu,%llu] with %llu indices", (unsigned long long)X->rows,
+                   (unsigned long long)X->cols, (unsigned long long)(I->rows * I->cols));
+  const uint64_t rows = X->rows, cols = X->cols;
+  const int elem = X->elem;
+  const uint32_t* xp = (const uint32_t*)X->ptr; const int32_t* ip = (const int32_t*)I->ptr;
+  Buf* O = nullptr;
+  st = e->new_buffer(rows, 1, elem, out, &O);
+  if (st) return st;
+  st = e->launched(launch_pick_columns(xp, rows, cols, ip, (uint32_t*)O->ptr, e->d_err, e->stream), "pick_columns");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, rows, 1);
+  return B200_OK;
+}
+
+int32_t b200_scatter_add_columns(b200_engine* e, b200_buffer t, b200_buffer indices, b200_buffer value, b200_buffer* out,
+                                 uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *T = nullptr, *I = nullptr, *V = nullptr;
+  int st = e->need(t, &T, "scatter_add_columns");
+  if (!st) st = index_buf(e, indices, &I, "scatter_add_columns");
+  if (!st) st = e->need(value, &V, "scatter_add_columns");
+  if (st) return st;
+  if (T->elem != B200_F32 || V->elem != B200_F32 || I->rows * I->cols != T->rows || V->rows * V->cols != T->rows)
+    return e->fail(B200_UNSUPPORTED, "scatter_add_columns: shapes do not meet");
+  const uint64_t rows = T->rows, cols = T->cols;
+  Buf* O = nullptr;
+  st = copy_of(e, T, out, &O);
+  if (st) return st;
+  I = e->get(indices); V = e->get(value);
+  st = e->launched(launch_scatter_add_columns((float*)O->ptr, rows, cols, (const int32_t*)I->ptr, (const float*)V->ptr, e->d_err, e->stream),
+                   "scatter_add_columns");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
+}
+
+int32_t b200_select_add_rows(b200_engine* e, b200_buffer t, b200_buffer indices, b200_buffer value, b200_buffer* out,
+                             uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *T = nullptr, *I = nullptr, *V = nullptr;
+  int st = e->need(t, &T, "select_add_rows");
+  if (!st) st = index_buf(e, indices, &I, "select_add_rows");
+  if (!st) st = e->need(value, &V, "select_add_rows");
+  if (st) return st;
+  const uint64_t n = I->rows * I->cols;
+  if (T->elem != B200_F32 || V->elem != B200_F32 || V->rows != n || V->cols != T->cols)
+    return e->fail(B200_UNSUPPORTED, "select_add_rows: shapes do not meet");
+  const uint64_t rows = T->rows, cols = T->cols;
+  Buf* O = nullptr;
+  st = copy_of(e, T, out, &O);
+  if (st) return st;
+  I = e->get(indices); V = e->get(value);
+  st = e->launched(launch_select_add_rows((float*)O->ptr, rows, cols, (const int32_t*)I->ptr, n, (const float*)V->ptr, e->d_err, e->stream),
+                   "select_add_rows");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
+}
+
+int32_t b200_rows_add(b200_engine* e, b200_buffer t, const uint64_t* indices, uint64_t n, b200_buffer value, b200_buffer* out,
+                      uint64_t out_dims[2]) {
+  std::vector<uint32_t> idx(n);
+  for (uint64_t i = 0; i < n; ++i) idx[i] = (uint32_t)indices[i];
+  b200_buffer ii = 0;
+  int st = b200_upload_bits(e, idx.data(), 1, n, B200_I32, &ii);
+  if (st) return st;
+  st = b200_select_add_rows(e, t, ii, value, out, out_dims);
+  b200_free(e, ii);
+  return st;
+}
+
+int32_t b200_assign_rows(b200_engine* e, b200_buffer t, b200_buffer value, const uint64_t* pairs, uint64_t n, b200_buffer* out,
+                         uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *T = nullptr, *V = nullptr;
+  int st = e->need(t, &T, "assign_rows");
+  if (!st) st = e->need(value, &V, "assign_rows");
+  if (st) return st;
+  if (T->elem != V->elem || T->cols != V->cols) return e->fail(B200_UNSUPPORTED, "assign_rows: value does not meet the table");
+  for (uint64_t i = 0; i < n; ++i)
+    if (pairs[2 * i] >= T->rows || pairs[2 * i + 1] >= V->rows) return e->fail(B200_DOMAIN, "assign_rows: DOMAIN: pair %llu names a row outside", (unsigned long long)i);
+  const uint64_t rows = T->rows, cols = T->cols;
+  const int eb = (int)elem_bytes(T->elem);
+  Buf* O = nullptr;
+  st = copy_of(e, T, out, &O);
+  if (st) return st;
+  void* op = O->ptr;
+  V = e->get(value);
+  const void* vp = V->ptr;
+  if (n) {
+    void* dev = nullptr; uint64_t got = 0;
+    st = e->to_device(pairs, n * 16, &dev, &got);
+    if (st) { e->drop(*out); return st; }
+    st = e->launched(launch_assign_rows(op, vp, cols, eb, (const uint64_t*)dev, n, e->stream), "assign_rows");
+    e->release(dev, got);
+    if (st) { e->drop(*out); return st; }
+  }
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
+}
+
+int32_t b200_scatter_rows(b200_engine* e, b200_buffer table, b200_buffer indices, b200_buffer values, int32_t column,
+                          b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *T = nullptr, *I = nullptr, *V = nullptr;
+  int st = e->need(table, &T, "scatter_rows");
+  if (!st) st = index_buf(e, indices, &I, "scatter_rows");
+  if (!st) st = e->need(values, &V, "scatter_rows");
+  if (st) return st;
+  const uint64_t n = I->rows * I->cols;
+  if ((column ? I->cols : I->rows) != 1 || elem_bytes(T->elem) != 4 || V->elem != T->elem || V->rows != n || V->cols != T->cols)
+    return e->fail(B200_UNSUPPORTED, "scatter_rows: shapes do not meet");
+  const uint64_t rows = T->rows, cols = T->cols;
+  Buf* O = nullptr;
+  st = copy_of(e, T, out, &O);
+  if (st) return st;
+  I = e->get(indices); V = e->get(values);
+  st = e->launched(launch_scatter_rows((uint32_t*)O->ptr, rows, cols, (const int32_t*)I->ptr, n, (const uint32_t*)V->ptr, e->d_err, e->stream),
+                   "scatter_rows");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
+}
+
+int32_t b200_gather_indexed(b200_engine* e, b200_buffer input, b200_buffer indices, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *X = nullptr, *I = nullptr;
+  int st = e->need(input, &X, "gather_indexed");
+  if (!st) st = index_buf(e, indices, &I, "gather_indexed");
+  if (st) return st;
+  if (elem_bytes(X->elem) != 4 || I->rows != X->rows) return e->fail(B200_UNSUPPORTED, "gather_indexed: shapes do not meet");
+  const uint64_t rows = X->rows, cols = X->cols, icols = I->cols;
+  const int elem = X->elem;
+  const uint32_t* xp = (const uint32_t*)X->ptr; const int32_t* ip = (const int32_t*)I->ptr;
+  Buf* O = nullptr;
+  st = e->new_buffer(rows, icols, elem, out, &O);
+  if (st) return st;
+  st = e->launched(launch_gather_indexed(xp, rows, cols, ip, icols, (uint32_t*)O->ptr, e->d_err, e->stream), "gather_indexed");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, rows, icols);
+  return B200_OK;
+}
+
+int32_t b200_gather_rows(b200_engine* e, const b200_buffer* sources, uint64_t n_sources, const uint64_t* pairs, uint64_t n_rows,
+                         uint64_t cols, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  if (n_sources == 0) return e->fail(B200_UNSUPPORTED, "gather_rows: no source");
+  std::vector<Buf*> src(n_sources);
+  for (uint64_t i = 0; i < n_sources; ++i) {
+    int st = e->need(sources[i], &src[i], "gather_rows");
+    if (st) return st;
+    if (src[i]->cols != cols || src[i]->elem != src[0]->elem) return e->fail(B200_UNSUPPORTED, "gather_rows: source %llu does not have %llu columns of the first's type", (unsigned long long)i, (unsigned long long)cols);
+  }
+  const int elem = src[0]->elem;
+  const uint64_t eb = elem_bytes(elem);
+  std::vector<const void*> ptrs(n_rows);
+  for (uint64_t i = 0; i < n_rows; ++i) {
+    const uint64_t s = pairs[2 * i], r = pairs[2 * i + 1];
+    if (s >= n_sources || r >= src[s]->rows) return e->fail(B200_DOMAIN, "gather_rows: DOMAIN: row %llu names (%llu, %llu)", (unsigned long long)i, (unsigned long long)s, (unsigned long long)r);
+    ptrs[i] = (const char*)src[s]->ptr + r * cols * eb;
+  }
+  Buf* O = nullptr;
+  int st = e->new_buffer(n_rows, cols, elem, out, &O);
+  if (st) return st;
+  void* op = O->ptr;
+  if (n_rows) {
+    void* dev = nullptr; uint64_t got = 0;
+    st = e->to_device(ptrs.data(), n_rows * sizeof(void*), &dev, &got);
+    if (st) { e->drop(*out); return st; }
+    st = e->launched(launch_gather_row_ptrs((const void* const*)dev, n_rows, cols, (int)eb, op, e->stream), "gather_rows");
+    e->release(dev, got);
+    if (st) { e->drop(*out); return st; }
+  }
+  set_dims(out_dims, n_rows, cols);
+  return B200_OK;
+}
+
+int32_t b200_slice_rows(b200_engine* e, b200_buffer a, uint64_t first, uint64_t rows, b200_buffer* out, uint64_t out_dims[2]) {
+  Buf* A = nullptr;
+  int st = e->need(a, &A, "slice_rows");
+  if (st) return st;
+  if (first + rows > A->rows) return e->fail(B200_UNSUPPORTED, "slice_rows: rows %llu..%llu of %llu", (unsigned long long)first, (unsigned long long)(first + rows), (unsigned long long)A->rows);
+  Buf v;
+  v.ptr = (char*)A->ptr + first * A->cols * elem_bytes(A->elem);
+  v.rows = rows; v.cols = A->cols; v.elem = A->elem; v.parent = a;
+  A->views++;
+  *out = e->next_id++;
+  e->bufs.emplace(*out, v);
+  set_dims(out_dims, rows, v.cols);
+  return B200_OK;
+}
+
+int32_t b200_copy_blocks(b200_engine* e, b200_buffer a, const b200_block_move* moves, uint64_t n, const uint64_t dims[2],
+                         b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf* A = nullptr;
+  int st = e->need(a, &A, "copy_blocks");
+  if (st) return st;
+  std::vector<MoveDev> mv(n);
+  uint64_t area = 0, max_r = 0, max_c = 0;
+  for (uint64_t i = 0; i < n; ++i) {
+    const b200_block_move& m = moves[i];
+    const uint64_t sr = m.transposed ? m.extent[1] : m.extent[0], sc = m.transposed ? m.extent[0] : m.extent[1];
+    if (m.from[0] + sr > A->rows || m.from[1] + sc > A->cols || m.to[0] + m.extent[0] > dims[0] || m.to[1] + m.extent[1] > dims[1])
+      return e->fail(B200_UNSUPPORTED, "copy_blocks: move %llu lies outside a tensor", (unsigned long long)i);
+    mv[i] = MoveDev{m.from[0], m.from[1], m.to[0], m.to[1], m.extent[0], m.extent[1], m.transposed, 0};
+    area += m.extent[0] * m.extent[1];
+    max_r = std::max(max_r, m.extent[0]); max_c = std::max(max_c, m.extent[1]);
+  }
+  if (area != dims[0] * dims[1]) return e->fail(B200_UNSUPPORTED, "copy_blocks: the blocks do not cover the output exactly once");
+  const int elem = A->elem;
+  const uint64_t src_ld = A->cols;
+  const void* sp = A->ptr;
+  Buf* O = nullptr;
+  st = e->new_buffer(dims[0], dims[1], elem, out, &O);
+  if (st) return st;
+  void* op = O->ptr;
+  if (n) {
+    void* dev = nullptr; uint64_t got = 0;
+    st = e->to_device(mv.data(), n * sizeof(MoveDev), &dev, &got);
+    if (st) { e->drop(*out); return st; }
+    st = e->launched(launch_copy_blocks(sp, src_ld, op, dims[1], (int)elem_bytes(elem), (const MoveDev*)dev, n, max_r, max_c, e->stream), "copy_blocks");
+    e->release(dev, got);
+    if (st) { e->drop(*out); return st; }
+  }
+  set_dims(out_dims, dims[0], dims[1]);
+  return B200_OK;
+}
+
+int32_t b200_repack(b200_engine* e, b200_buffer a, const uint64_t* pairs, const uint64_t dims[2], b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf* A = nullptr;
+  int st = e->need(a, &A, "repack");
+  if (st) return st;
+  const uint64_t n = dims[0] * dims[1];
+  for (uint64_t i = 0; i < n; ++i)
+    if (pairs[2 * i] >= A->rows || pairs[2 * i + 1] >= A->cols) return e->fail(B200_DOMAIN, "repack: DOMAIN: source %llu lies outside", (unsigned long long)i);
+  const int elem = A->elem; const uint64_t ld = A->cols; const void* sp = A->ptr;
+  Buf* O = nullptr;
+  st = e->new_buffer(dims[0], dims[1], elem, out, &O);
+  if (st) return st;
+  void* op = O->ptr;
+  if (n) {
+    void* dev = nullptr; uint64_t got = 0;
+    st = e->to_device(pairs, n * 16, &dev, &got);
+    if (st) { e->drop(*out); return st; }
+    st = e->launched(launch_repack(sp, ld, (int)elem_bytes(elem), (const uint64_t*)dev, n, op, e->stream), "repack");
+    e->release(dev, got);
+    if (st) { e->drop(*out); return st; }
+  }
+  set_dims(out_dims, dims[0], dims[1]);
+  return B200_OK;
+}
+
+// ---- waits and observability ---------------------------------------------------
+int32_t b200_sync(b200_engine* e) { cudaSetDevice(e->device); return e->wait(); }
+void b200_set_op_label(b200_engine* e, const char* label) { e->label = label ? label : ""; }
+void b200_traffic_get(const b200_engine* e, b200_traffic* out) { *out = e->traffic; }
+int32_t b200_timer_start(b200_engine* e) {
+  cudaSetDevice(e->device);
+  cudaError_t ce = cudaEventRecord(e->t0, e->stream);
+  return ce == cudaSuccess ? B200_OK : e->cuda_fail(ce, "timer_start");
+}
+int32_t b200_timer_stop(b200_engine* e, float* ms) {
+  cudaSetDevice(e->device);
+  cudaError_t ce = cudaEventRecord(e->t1, e->stream);
+  if (ce == cudaSuccess) ce = cudaEventSynchronize(e->t1);
+  if (ce == cudaSuccess) ce = cudaEventElapsedTime(ms, e->t0, e->t1);
+  return ce == cudaSuccess ? B200_OK : e->cuda_fail(ce, "timer_stop");
+}
+void* b200_stream(const b200_engine* e) { return (void*)e->stream; }
+const char* b200_last_matmul_path(const b200_engine* e) { return e->matmul_path; }
+
+}  // extern "C"

@@ -1,0 +1,212 @@
+// Element-wise kernels: every `Eltwise` kind of the reference
+// (crates/tt-kernels/src/sfpu/ops.rs:24-251, crates/tt-kernels/src/kind.rs:12-26)
+// over 32-bit words (F32 / I32 / Bool) or BF16 storage, with the reference's
+// broadcast forms (crates/tt-kernels/src/tensor.rs:3799-3859).
+//
+// Memory-bound: the fast path moves 128-bit vectors, four per thread in flight,
+// coalesced; the generic path handles blocks of buffers, BF16 and odd widths.
+// Compiled with -fmad=false: every kind that the reference defines as separate
+// roundings (MUL_ADD, HARD_SIGMOID, SILU_MUL ...) keeps them.
+#include "eltwise_ev.cuh"
+#include "kernels.h"
+
+namespace b200 {
+namespace {
+
+// ---- fast path: contiguous 32-bit words, cols % 4 == 0 -------------------------
+// BM: 0 no b, 1 b of a's shape, 2 b one row, 3 b one column.
+template <uint32_t K, int BM>
+__global__ void __launch_bounds__(256)
+elt_vec4(const uint4* __restrict__ a, const uint32_t* __restrict__ b, uint4* __restrict__ out,
+         uint64_t n4, uint32_t cols4, float s1, float s2, int* err, int streaming) {
+  constexpr int U = 4;
+  const uint64_t base = (uint64_t)blockIdx.x * (256 * U) + threadIdx.x;
+  uint4 va[U], vb[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const uint64_t i = base + (uint64_t)u * 256;
+    if (i < n4) {
+      va[u] = streaming ? __ldcs(a + i) : a[i];
+      if constexpr (BM == 1) {
+        vb[u] = streaming ? __ldcs(reinterpret_cast<const uint4*>(b) + i)
+                          : reinterpret_cast<const uint4*>(b)[i];
+      } else if constexpr (BM == 2) {
+        vb[u] = __ldg(reinterpret_cast<const uint4*>(b) + (i % cols4));
+      } else if constexpr (BM == 3) {
+        uint32_t w = __ldg(b + (i / cols4));
+        vb[u] = make_uint4(w, w, w, w);
+      } else {
+        vb[u] = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const uint64_t i = base + (uint64_t)u * 256;
+    if (i < n4) {
+      uint4 r;
+      r.x = ev<K>(va[u].x, vb[u].x, 0u, s1, s2, err);
+      r.y = ev<K>(va[u].y, vb[u].y, 0u, s1, s2, err);
+      r.z = ev<K>(va[u].z, vb[u].z, 0u, s1, s2, err);
+      r.w = ev<K>(va[u].w, vb[u].w, 0u, s1, s2, err);
+      if (streaming) __stcs(out + i, r); else out[i] = r;
+    }
+  }
+}
+
+// ---- generic path ------------------------------------------------------------
+__device__ __forceinline__ uint32_t load_word(const Mat& m, uint64_t r, uint64_t c) {
+  const uint64_t rr = (m.rows == 1) ? 0 : (r % m.rows);
+  const uint64_t cc = (m.cols == 1) ? 0 : (c % m.cols);
+  const uint64_t off = rr * m.ld + cc;
+  if (m.bf16) return (uint32_t)reinterpret_cast<const uint16_t*>(m.p)[off] << 16;
+  return reinterpret_cast<const uint32_t*>(m.p)[off];
+}
+
+template <uint32_t K>
+__global__ void __launch_bounds__(256) elt_generic(EltwiseArgs g) {
+  const uint64_t n = g.rows * g.cols;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    uint64_t r, c;
+    if (n <= 0xffffffffull) {
+      r = (uint32_t)i / (uint32_t)g.cols;
+      c = (uint32_t)i - (uint32_t)r * (uint32_t)g.cols;
+    } else {
+      r = i / g.cols;
+      c = i - r * g.cols;
+    }
+    const uint32_t ua = load_word(g.a, r, c);
+    const uint32_t ub = g.b.p ? load_word(g.b, r, c) : 0u;
+    const uint32_t uc = g.c.p ? load_word(g.c, r, c) : 0u;
+    const uint32_t res = ev<K>(ua, ub, uc, g.s1, g.s2, g.err);
+    const uint64_t o = r * g.out_ld + c;
+    if (g.out_bf16) reinterpret_cast<uint16_t*>(g.out)[o] = f32_to_bf16_bits(res);
+    else reinterpret_cast<uint32_t*>(g.out)[o] = res;
+  }
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <uint32_t K>
+cudaError_t launch_kind(const EltwiseArgs& g, cudaStream_t stream) {
+  const uint64_t n = g.rows * g.cols;
+  if (n == 0) return cudaSuccess;
+  // Which broadcast form b takes, if the fast path can serve it.
+  int bm = -1;
+  const bool plain = !g.a.bf16 && !g.out_bf16 && !g.c.p && g.a.ld == g.cols && g.out_ld == g.cols &&
+                     g.a.rows == g.rows && g.a.cols == g.cols && (g.cols % 4 == 0) &&
+                     aligned16(g.a.p) && aligned16(g.out) && (g.cols / 4) <= 0xffffffffull;
+  if (plain) {
+    if (!g.b.p) bm = 0;
+    else if (!g.b.bf16 && g.b.rows == g.rows && g.b.cols == g.cols && g.b.ld == g.cols && aligned16(g.b.p)) bm = 1;
+    else if (!g.b.bf16 && g.b.rows == 1 && g.b.cols == g.cols && aligned16(g.b.p)) bm = 2;
+    else if (!g.b.bf16 && g.b.cols == 1 && g.b.rows == g.rows && g.b.ld == 1) bm = 3;
+  }
+  if (bm >= 0) {
+    const uint64_t n4 = n / 4;
+    const uint32_t cols4 = (uint32_t)(g.cols / 4);
+    const unsigned grid = (unsigned)((n4 + 1023) / 1024);
+    const int streaming = n * 4 > (64ull << 20);
+    auto a = reinterpret_cast<const uint4*>(g.a.p);
+    auto b = reinterpret_cast<const uint32_t*>(g.b.p);
+    auto o = reinterpret_cast<uint4*>(g.out);
+    switch (bm) {
+      case 0: elt_vec4<K, 0><<<grid, 256, 0, stream>>>(a, b, o, n4, cols4, g.s1, g.s2, g.err, streaming); break;
+      case 1: elt_vec4<K, 1><<<grid, 256, 0, stream>>>(a, b, o, n4, cols4, g.s1, g.s2, g.err, streaming); break;
+      case 2: elt_vec4<K, 2><<<grid, 256, 0, stream>>>(a, b, o, n4, cols4, g.s1, g.s2, g.err, streaming); break;
+      default: elt_vec4<K, 3><<<grid, 256, 0, stream>>>(a, b, o, n4, cols4, g.s1, g.s2, g.err, streaming); break;
+    }
+    return cudaGetLastError();
+  }
+  uint64_t blocks = (n + 255) / 256;
+  if (blocks > 148ull * 32) blocks = 148ull * 32;
+  elt_generic<K><<<(unsigned)blocks, 256, 0, stream>>>(g);
+  return cudaGetLastError();
+}
+
+// ---- RoPE -------------------------------------------------------------------
+// out = fl(fl(x cos) + fl(swap(x) sin)): the product, the product and the sum
+// (crates/tt-kernels/src/tensor.rs:5545-5552).
+__global__ void __launch_bounds__(256)
+rope_kernel(Mat x, Mat cs, Mat sn, uint64_t head, void* out, uint64_t out_ld, int out_bf16,
+            uint64_t rows, uint64_t cols) {
+  const uint64_t n = rows * cols;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  const uint64_t half = head / 2;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const uint64_t r = i / cols, c = i - r * cols;
+    const uint64_t h = c / head, j = c - h * head;
+    const uint64_t cswap = h * head + (j < half ? j + half : j - half);
+    const float xv = __uint_as_float(load_word(x, r, c));
+    const float xs = __uint_as_float(load_word(x, r, cswap));
+    const float co = __uint_as_float(load_word(cs, r, cs.cols == head ? j : c));
+    const float si = __uint_as_float(load_word(sn, r, sn.cols == head ? j : c));
+    const float p1 = xv * co;
+    const float p2 = xs * si;
+    const uint32_t res = __float_as_uint(p1 + p2);
+    const uint64_t o = r * out_ld + c;
+    if (out_bf16) reinterpret_cast<uint16_t*>(out)[o] = f32_to_bf16_bits(res);
+    else reinterpret_cast<uint32_t*>(out)[o] = res;
+  }
+}
+
+// ---- casts ---------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+cast_to_bf16(const uint32_t* __restrict__ in, uint16_t* __restrict__ out, uint64_t n) {
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x * 4;
+  for (uint64_t i = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
+    if (i + 3 < n && ((reinterpret_cast<uintptr_t>(in) & 15) == 0) && ((reinterpret_cast<uintptr_t>(out) & 7) == 0)) {
+      const uint4 v = *reinterpret_cast<const uint4*>(in + i);
+      uint2 o;
+      o.x = (uint32_t)f32_to_bf16_bits(v.x) | ((uint32_t)f32_to_bf16_bits(v.y) << 16);
+      o.y = (uint32_t)f32_to_bf16_bits(v.z) | ((uint32_t)f32_to_bf16_bits(v.w) << 16);
+      *reinterpret_cast<uint2*>(out + i) = o;
+    } else {
+      for (uint64_t j = i; j < n && j < i + 4; ++j) out[j] = f32_to_bf16_bits(in[j]);
+    }
+  }
+}
+__global__ void __launch_bounds__(256)
+cast_from_bf16(const uint16_t* __restrict__ in, uint32_t* __restrict__ out, uint64_t n) {
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    out[i] = (uint32_t)in[i] << 16;
+}
+
+}  // namespace
+
+bool eltwise_kind_known(uint32_t k) { return kind::arity(k) != 0; }
+
+cudaError_t launch_eltwise(const EltwiseArgs& g, cudaStream_t stream) {
+  switch (g.kind) {
+#define B200_CASE(name, value, ar) case value: return launch_kind<value>(g, stream);
+    B200_KINDS(B200_CASE)
+#undef B200_CASE
+    default: return cudaErrorNotSupported;
+  }
+}
+
+cudaError_t launch_rope(const Mat& x, const Mat& cs, const Mat& sn, uint64_t head, void* out,
+                        uint64_t out_ld, int out_bf16, uint64_t rows, uint64_t cols,
+                        cudaStream_t stream) {
+  const uint64_t n = rows * cols;
+  if (n == 0) return cudaSuccess;
+  uint64_t blocks = (n + 255) / 256;
+  if (blocks > 148ull * 32) blocks = 148ull * 32;
+  rope_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, cs, sn, head, out, out_ld, out_bf16, rows, cols);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_cast(const void* in, void* out, uint64_t n, int to_bf16, cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  uint64_t blocks = to_bf16 ? (n / 4 + 255) / 256 + 1 : (n + 255) / 256;
+  if (blocks > 148ull * 64) blocks = 148ull * 64;
+  if (to_bf16)
+    cast_to_bf16<<<(unsigned)blocks, 256, 0, stream>>>((const uint32_t*)in, (uint16_t*)out, n);
+  else
+    cast_from_bf16<<<(unsigned)blocks, 256, 0, stream>>>((const uint16_t*)in, (uint32_t*)out, n);
+  return cudaGetLastError();
+}
+
+}  // namespace b200

@@ -1,0 +1,455 @@
+// Tensor-core product for sm_100a: C = op(A) op(B), BF16 operands, FP32 accumulation in
+// tensor memory, the accumulator rounded once to BF16 (or stored F32).
+// Boundary: `Engine::matmul_dram_bf16`, `matmul_dram_batched` on BF16 buffers
+// (crates/burn-tt/src/server.rs:191,229); arithmetic contract "the F32 product, rounded
+// once" (crates/tt-tests/tests/step270_native_bf16.rs:462).
+//
+// One persistent CTA per SM walks output tiles of 128 x BN.  Warp roles:
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of the A and B k-blocks into a
+//               ring of shared-memory stages (128-byte swizzle), one mbarrier a stage;
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) from
+//               shared-memory descriptors into one of two TMEM accumulators, and
+//               tcgen05.commit hands each stage back to the producer;
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (a warp owns the 32 TMEM
+//               lanes of its quadrant), round, store; overlaps the next tile's mainloop.
+// No load uses cluster multicast: operand reuse comes from L2 through the tile order.
+// Either operand may be K-major or MN-major (the stored matrix transposed or not): the
+// TMA box and the shared-memory descriptor change, the instruction stays.
+// Every wait on an mbarrier is bounded; a wait that runs out sets the engine's error
+// word to TIMEOUT and the kernel drains and frees its tensor memory before it returns.
+#include <cuda.h>
+#include <stdlib.h>
+
+#include "device_math.cuh"
+#include "kernels.h"
+
+namespace b200 {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;            // bf16 elements: one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;  // 6 warps
+constexpr int TIMEOUT_CODE = 4;
+constexpr long long WAIT_CYCLES = 4000000000ll;  // ~2 s: far beyond any healthy wait
+
+struct TcParams {
+  uint64_t m, n, k;
+  uint64_t lda, ldb, ldc;
+  uint32_t tiles_m, tiles_n;
+  uint64_t batch;
+  const GemmBatch* batches;  // device, or nullptr
+  void* c;
+  int out_bf16;
+  int* err;
+  uint32_t mn_lbo, mn_sbo;   // byte offsets of an MN-major operand's descriptor
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when it ran out (the caller abandons its role).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > WAIT_CYCLES) return false;
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int32_t c0, int32_t c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100 UMMA): start address, leading / stride byte
+// offsets (all >> 4), version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3fff);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= 1ull << 46;  // descriptor version
+  d |= 2ull << 61;  // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+}
+
+// Tile order: groups of 16 tile rows walked column by column, so the CTAs running at one
+// time share A rows and B columns in L2.
+__device__ __forceinline__ void tile_coords(uint64_t t, uint32_t tiles_m, uint32_t tiles_n, uint64_t* batch,
+                                            uint32_t* tm, uint32_t* tn) {
+  const uint64_t per = (uint64_t)tiles_m * tiles_n;
+  *batch = t / per;
+  const uint32_t r = (uint32_t)(t - *batch * per);
+  constexpr uint32_t G = 16;
+  const uint32_t group = r / (G * tiles_n);
+  const uint32_t first = group * G;
+  const uint32_t rows = (tiles_m - first < G) ? (tiles_m - first) : G;
+  const uint32_t in = r - group * G * tiles_n;
+  *tm = first + in % rows;
+  *tn = in / rows;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
+  constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  const uint64_t total_tiles = (uint64_t)p.tiles_m * p.tiles_n * p.batch;
+  const uint32_t num_kb = (uint32_t)((p.k + BK - 1) / BK);
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (uint64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        uint64_t b; uint32_t tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, &b, &tm, &tn);
+        uint64_t a_off = 0, b_off = 0;
+        if (p.batches) { a_off = p.batches[b].a_off; b_off = p.batches[b].b_off; }
+        const int32_t a_r0 = (int32_t)(a_off / p.lda), a_c0 = (int32_t)(a_off % p.lda);
+        const int32_t b_r0 = (int32_t)(b_off / p.ldb), b_c0 = (int32_t)(b_off % p.ldb);
+        const int32_t m0 = (int32_t)(tm * BM), n0 = (int32_t)(tn * BN);
+        for (uint32_t kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          mbar_expect_tx(&full[stage], STAGE_BYTES);
+          const int32_t k0 = (int32_t)(kb * BK);
+          if constexpr (!A_MN) {
+            tma_load_2d(sa, &map_a, &full[stage], a_c0 + k0, a_r0 + m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sa + j * 8192, &map_a, &full[stage], a_c0 + m0 + j * 64, a_r0 + k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(sb, &map_b, &full[stage], b_c0 + k0, b_r0 + n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * 8192, &map_b, &full[stage], b_c0 + n0 + j * 64, b_r0 + k0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        atomicCAS(p.err, 0, TIMEOUT_CODE);
+        *abort_flag = 1;
+      }
+      // Drain: every stage armed above either was consumed (its empty barrier fired) or
+      // still has its copy in flight; wait (bounded) until the last armed phase of each
+      // stage has landed so no copy outlives the CTA.
+      for (int s = 0; s < STAGES; ++s) {
+        const uint32_t ph = (s < (int)stage) ? phase : (phase ^ 1);
+        // stages before `stage` were armed in the current phase, the rest in the previous
+        const long long t0 = clock64();
+        while (!mbar_try(&full[s], ph)) {
+          if (clock64() - t0 > WAIT_CYCLES) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                                 ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      uint32_t stage = 0, phase = 0, local = 0;
+      bool ok = true;
+      for (uint64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+        const uint32_t acc = local & 1, acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (uint32_t kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t adesc = A_MN ? make_desc(sa + kk * 2048, p.mn_lbo, p.mn_sbo) : make_desc(sa + kk * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_desc(sb + kk * 2048, p.mn_lbo, p.mn_sbo) : make_desc(sb + kk * 32, 16, 1024);
+            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb | (uint32_t)kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);  // the stage is free once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[acc]);
+      }
+      if (!ok) {
+        atomicCAS(p.err, 0, TIMEOUT_CODE);
+        *abort_flag = 1;
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const uint32_t quad = warp & 3;  // the TMEM lanes this warp may read
+    uint32_t local = 0;
+    bool ok = true;
+    for (uint64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+      uint64_t b; uint32_t tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, &b, &tm, &tn);
+      const uint32_t acc = local & 1, acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint64_t c_off = p.batches ? p.batches[b].c_off : 0;
+      const uint64_t row = (uint64_t)tm * BM + quad * 32 + lane;
+      const uint64_t n0 = (uint64_t)tn * BN;
+      const bool row_ok = row < p.m;
+#pragma unroll 1
+      for (int cb = 0; cb < BN / 32; ++cb) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((quad * 32u) << 16) + acc * BN + cb * 32, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const uint64_t col = n0 + cb * 32;
+        if (row_ok && col < p.n) {
+          const uint64_t o = c_off + row * p.ldc + col;
+          if (p.out_bf16) {
+            uint16_t* dst = (uint16_t*)p.c + o;
+            if (col + 32 <= p.n && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 w;
+                w.x = (uint32_t)f32_to_bf16_bits(v[q * 8 + 0]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 1]) << 16);
+                w.y = (uint32_t)f32_to_bf16_bits(v[q * 8 + 2]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 3]) << 16);
+                w.z = (uint32_t)f32_to_bf16_bits(v[q * 8 + 4]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 5]) << 16);
+                w.w = (uint32_t)f32_to_bf16_bits(v[q * 8 + 6]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 7]) << 16);
+                *reinterpret_cast<uint4*>(dst + q * 8) = w;
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < p.n; ++j) dst[j] = f32_to_bf16_bits(v[j]);
+            }
+          } else {
+            uint32_t* dst = (uint32_t*)p.c + o;
+            if (col + 32 <= p.n && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<uint4*>(dst + q * 4) = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+            } else {
+              for (int j = 0; j < 32 && col + j < p.n; ++j) dst[j] = v[j];
+            }
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+    if (!ok && lane == 0) {
+      atomicCAS(p.err, 0, TIMEOUT_CODE);
+      *abort_flag = 1;
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// ---- host side -----------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  }
+  return fn;
+}
+
+// A 2-D BF16 tensor map over a stored [rows, cols] matrix, box [box_rows, 64 columns].
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {ld * 2};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES>
+cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, bool a_mn, bool b_mn,
+                           unsigned grid, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+#define TC_LAUNCH(AM, BMJ)                                                                              \
+  do {                                                                                                  \
+    static bool attr_set = false;                                                                       \
+    if (!attr_set) {                                                                                    \
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, AM, BMJ>,                          \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+      if (e != cudaSuccess) return e;                                                                   \
+      attr_set = true;                                                                                  \
+    }                                                                                                   \
+    gemm_tc_kernel<BN, STAGES, AM, BMJ><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p);                \
+  } while (0)
+  if (!a_mn && !b_mn) TC_LAUNCH(false, false);
+  else if (!a_mn && b_mn) TC_LAUNCH(false, true);
+  else if (a_mn && !b_mn) TC_LAUNCH(true, false);
+  else TC_LAUNCH(true, true);
+#undef TC_LAUNCH
+  return cudaGetLastError();
+}
+
+uint32_t env_u32(const char* name, uint32_t dflt) {
+  const char* s = getenv(name);
+  return s ? (uint32_t)strtoul(s, nullptr, 0) : dflt;
+}
+
+}  // namespace
+
+bool gemm_tc_supported(const GemmArgs& g, const char** why) {
+  *why = "";
+  if (!g.in_bf16) { *why = "operands are not BF16"; return false; }
+  if (!encode_fn()) { *why = "the driver offers no tensor-map encoder"; return false; }
+  if (g.m < 64 || g.n < 64 || g.k < 64) { *why = "a dimension is below 64"; return false; }
+  if (g.lda % 8 || g.ldb % 8) { *why = "a row pitch is not a multiple of 16 bytes"; return false; }
+  if (((uintptr_t)g.a | (uintptr_t)g.b) & 15) { *why = "an operand is not 16-byte aligned"; return false; }
+  if (g.m > 0x7fffffffull || g.n > 0x7fffffffull || g.k > 0x7fffffffull) { *why = "a dimension exceeds 2^31"; return false; }
+  if (g.batch > 1 && g.k % BK) { *why = "a batched product's k is not a multiple of 64"; return false; }
+  return true;
+}
+
+cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int* err_word, cudaStream_t stream) {
+  bool a_mn = g.a_trans != 0, b_mn = g.b_trans == 0;
+  if (g.batch > 1) {
+    a_mn = batches_host[0].a_trans != 0;
+    b_mn = batches_host[0].b_trans == 0;
+    for (uint64_t i = 0; i < g.batch; ++i) {
+      if ((batches_host[i].a_trans != 0) != a_mn || (batches_host[i].b_trans == 0) != b_mn) return cudaErrorNotSupported;
+      if (batches_host[i].a_off % 8 || batches_host[i].b_off % 8) return cudaErrorNotSupported;
+    }
+  }
+  // The stored matrices.  For one product they are exactly the operands; for a batched
+  // call the maps span the whole buffers and each item adds its block's coordinates.
+  uint64_t a_rows, a_cols, b_rows, b_cols;
+  if (g.batch > 1) {
+    // The engine checked that every block lies inside; rows are not known here beyond
+    // that, so cover the blocks' farthest row.
+    uint64_t a_last = 0, b_last = 0;
+    const uint64_t ar = a_mn ? g.k : g.m, br = b_mn ? g.k : g.n;
+    for (uint64_t i = 0; i < g.batch; ++i) {
+      a_last = a_last > batches_host[i].a_off / g.lda + ar ? a_last : batches_host[i].a_off / g.lda + ar;
+      b_last = b_last > batches_host[i].b_off / g.ldb + br ? b_last : batches_host[i].b_off / g.ldb + br;
+    }
+    a_rows = a_last; a_cols = g.lda; b_rows = b_last; b_cols = g.ldb;
+  } else {
+    a_rows = a_mn ? g.k : g.m; a_cols = a_mn ? g.m : g.k;
+    b_rows = b_mn ? g.k : g.n; b_cols = b_mn ? g.n : g.k;
+  }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+
+  const uint32_t tiles_m = (uint32_t)((g.m + BM - 1) / BM);
+  // Narrow tiles when wide ones would leave SMs idle or waste most of a tile.
+  const uint64_t wide_tiles = (uint64_t)tiles_m * ((g.n + 255) / 256) * g.batch;
+  const bool narrow = g.n <= 128 || wide_tiles < (uint64_t)sms;
+  const int bn = narrow ? 128 : 256;
+  const uint32_t tiles_n = (uint32_t)((g.n + bn - 1) / bn);
+
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, g.a, a_rows, a_cols, g.lda, a_mn ? 64 : BM)) return cudaErrorInvalidValue;
+  if (!make_map(&mb, g.b, b_rows, b_cols, g.ldb, b_mn ? 64 : (uint32_t)bn)) return cudaErrorInvalidValue;
+
+  TcParams p{};
+  p.m = g.m; p.n = g.n; p.k = g.k;
+  p.lda = g.lda; p.ldb = g.ldb; p.ldc = g.ldc;
+  p.tiles_m = tiles_m; p.tiles_n = tiles_n;
+  p.batch = g.batch ? g.batch : 1;
+  p.batches = g.batch > 1 ? g.batches_dev : nullptr;
+  p.c = g.c; p.out_bf16 = g.out_bf16; p.err = err_word;
+  p.mn_lbo = env_u32("B200TT_MN_LBO", 8192);
+  p.mn_sbo = env_u32("B200TT_MN_SBO", 1024);
+  if (g.batch == 1 && g.batches_dev) p.batches = g.batches_dev;
+
+  const uint64_t total = (uint64_t)tiles_m * tiles_n * p.batch;
+  const unsigned grid = (unsigned)(total < (uint64_t)sms ? total : (uint64_t)sms);
+  if (bn == 256) return launch_variant<256, 4>(ma, mb, p, a_mn, b_mn, grid, stream);
+  return launch_variant<128, 6>(ma, mb, p, a_mn, b_mn, grid, stream);
+}
+
+}  // namespace b200

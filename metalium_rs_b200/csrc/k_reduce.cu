@@ -1,0 +1,533 @@
+// Reductions, row softmax, RMS statistics / RMSNorm and row argmax.
+//
+//  - reduce: crates/tt-kernels/src/sfpu/reduce.rs:56 (`ReduceOp`), :117 (`Axis`).
+//    Sum over rows is a left fold from +0.0, top to bottom, one thread a column
+//    (reduce.rs:31-38, :296): bit for bit a sequential sum.  Sums over columns use a
+//    fixed tree, so a result never depends on the launch.
+//  - full sum / mean: crates/burn-tt/src/ops.rs:3246-3398.  Two stages in a fixed order.
+//  - softmax rows: crates/tt-kernels/src/sfpu/softmax.rs:1-45; one read and one write of
+//    the scores, the row held in registers between the three phases.
+//  - rms / rms_norm: crates/tt-kernels/src/sfpu/norm.rs:1-25.
+//  - argmax: first maximum, first NaN wins (crates/tt-tests/tests/step211_argmax_row.rs:8-10).
+//
+// Compiled with -fmad=false so every rounding the reference names is kept.
+#include <float.h>
+
+#include "eltwise_ev.cuh"
+#include "kernels.h"
+
+namespace b200 {
+namespace {
+
+enum { SUM = 0, MAX = 1, PROD = 2, ALL = 3, ANY = 4, BITOR = 5, SUM_I32 = 6, PROD_I32 = 7, MIN_I32 = 8, MAX_I32 = 9 };
+
+template <int OP> __device__ __forceinline__ uint32_t identity() {
+  if constexpr (OP == MAX) return 0xff800000u;
+  else if constexpr (OP == PROD) return 0x3f800000u;
+  else if constexpr (OP == ALL || OP == PROD_I32) return 1u;
+  else if constexpr (OP == MIN_I32) return 0x7fffffffu;
+  else if constexpr (OP == MAX_I32) return 0x80000000u;
+  else return 0u;
+}
+// Total order on float bits in which a positive NaN is above everything (reduce.rs:24-26).
+__device__ __forceinline__ uint32_t order_key(uint32_t u) {
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+template <int OP> __device__ __forceinline__ uint32_t combine(uint32_t acc, uint32_t x) {
+  if constexpr (OP == SUM) return __float_as_uint(__uint_as_float(acc) + __uint_as_float(x));
+  else if constexpr (OP == MAX) return order_key(acc) < order_key(x) ? x : acc;
+  else if constexpr (OP == PROD) return __float_as_uint(__uint_as_float(acc) * __uint_as_float(x));
+  else if constexpr (OP == ALL) return (acc != 0 && x != 0) ? 1u : 0u;
+  else if constexpr (OP == ANY) return (acc != 0 || x != 0) ? 1u : 0u;
+  else if constexpr (OP == BITOR) return acc | x;
+  else if constexpr (OP == SUM_I32) return acc + x;
+  else if constexpr (OP == PROD_I32) return acc * x;
+  else if constexpr (OP == MIN_I32) return (int32_t)x < (int32_t)acc ? x : acc;
+  else return (int32_t)x > (int32_t)acc ? x : acc;
+}
+
+// The finishing kind of a reduction (tensor.rs:6038 `ReduceThen`): exact unary kinds only.
+__device__ __forceinline__ uint32_t apply_then(uint32_t v, uint32_t then_kind, uint32_t then_bits) {
+  const float s = __uint_as_float(then_bits);
+  switch (then_kind) {
+    case 0: return v;
+    case kind::NEG: return ev<kind::NEG>(v, 0, 0, s, 0.f, nullptr);
+    case kind::ABS: return ev<kind::ABS>(v, 0, 0, s, 0.f, nullptr);
+    case kind::SIGN: return ev<kind::SIGN>(v, 0, 0, s, 0.f, nullptr);
+    case kind::RELU: return ev<kind::RELU>(v, 0, 0, s, 0.f, nullptr);
+    case kind::CLAMP_MIN: return ev<kind::CLAMP_MIN>(v, 0, 0, s, 0.f, nullptr);
+    case kind::CLAMP_MAX: return ev<kind::CLAMP_MAX>(v, 0, 0, s, 0.f, nullptr);
+    case kind::INT_ABS: return ev<kind::INT_ABS>(v, 0, 0, s, 0.f, nullptr);
+    default: return v;
+  }
+}
+
+__device__ __forceinline__ uint32_t ld_word(const void* p, int bf16, uint64_t i) {
+  if (bf16) return (uint32_t)reinterpret_cast<const uint16_t*>(p)[i] << 16;
+  return reinterpret_cast<const uint32_t*>(p)[i];
+}
+
+// ---- over rows: [rows, cols] -> [1, cols]; in order, one thread a column ----------
+template <int OP>
+__global__ void __launch_bounds__(128)
+reduce_rows_kernel(const void* a, int bf16, uint64_t rows, uint64_t cols, uint32_t then_kind,
+                   uint32_t then_bits, uint32_t* out) {
+  const uint64_t c = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  uint32_t acc = identity<OP>();
+  uint64_t r = 0;
+  constexpr int U = 16;
+  for (; r + U <= rows; r += U) {
+    uint32_t v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = ld_word(a, bf16, (r + u) * cols + c);
+#pragma unroll
+    for (int u = 0; u < U; ++u) acc = combine<OP>(acc, v[u]);
+  }
+  for (; r < rows; ++r) acc = combine<OP>(acc, ld_word(a, bf16, r * cols + c));
+  out[c] = apply_then(acc, then_kind, then_bits);
+}
+
+// ---- over columns: [rows, cols] -> [rows, 1] ----------------------------------
+template <int OP> __device__ __forceinline__ uint32_t warp_reduce(uint32_t v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = combine<OP>(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// THREADS threads a row (32: a warp a row, several rows a block).
+template <int OP, int THREADS>
+__global__ void __launch_bounds__(256)
+reduce_cols_kernel(const void* a, int bf16, uint64_t rows, uint64_t cols, uint32_t then_kind,
+                   uint32_t then_bits, uint32_t* out) {
+  constexpr int ROWS_PER_BLOCK = 256 / THREADS;
+  __shared__ uint32_t part[8];
+  const int lane_in_row = threadIdx.x % THREADS;
+  const int sub = threadIdx.x / THREADS;
+  for (uint64_t row0 = (uint64_t)blockIdx.x * ROWS_PER_BLOCK; row0 < rows;
+       row0 += (uint64_t)gridDim.x * ROWS_PER_BLOCK) {
+    const uint64_t row = row0 + sub;
+    uint32_t acc = identity<OP>();
+    if (row < rows) {
+      const uint64_t base = row * cols;
+      const bool vec = !bf16 && (cols % 4 == 0) &&
+                       ((reinterpret_cast<uintptr_t>(a) & 15) == 0);
+      if (vec) {
+        const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const uint32_t*>(a) + base);
+        const uint64_t n4 = cols / 4;
+        uint32_t a0 = identity<OP>(), a1 = a0, a2 = a0, a3 = a0;
+        for (uint64_t i = lane_in_row; i < n4; i += THREADS) {
+          const uint4 v = __ldcs(p + i);
+          a0 = combine<OP>(a0, v.x); a1 = combine<OP>(a1, v.y);
+          a2 = combine<OP>(a2, v.z); a3 = combine<OP>(a3, v.w);
+        }
+        acc = combine<OP>(combine<OP>(a0, a1), combine<OP>(a2, a3));
+      } else {
+        for (uint64_t i = lane_in_row; i < cols; i += THREADS)
+          acc = combine<OP>(acc, ld_word(a, bf16, base + i));
+      }
+    }
+    acc = warp_reduce<OP>(acc);
+    if constexpr (THREADS == 32) {
+      if (lane_in_row == 0 && row < rows) out[row] = apply_then(acc, then_kind, then_bits);
+    } else {
+      if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        uint32_t t = part[0];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) t = combine<OP>(t, part[w]);
+        out[row] = apply_then(t, then_kind, then_bits);
+      }
+      __syncthreads();
+    }
+  }
+}
+
+template <int OP>
+cudaError_t launch_reduce_op(const void* a, int bf16, uint64_t rows, uint64_t cols, int axis,
+                             uint32_t tk, uint32_t tb, void* out, cudaStream_t s) {
+  uint32_t* o = reinterpret_cast<uint32_t*>(out);
+  if (axis == 0) {
+    reduce_rows_kernel<OP><<<(unsigned)((cols + 127) / 128), 128, 0, s>>>(a, bf16, rows, cols, tk, tb, o);
+  } else if (cols >= 2048) {
+    uint64_t grid = rows < 148ull * 16 ? rows : 148ull * 16;
+    reduce_cols_kernel<OP, 256><<<(unsigned)grid, 256, 0, s>>>(a, bf16, rows, cols, tk, tb, o);
+  } else {
+    uint64_t grid = (rows + 7) / 8;
+    if (grid > 148ull * 16) grid = 148ull * 16;
+    reduce_cols_kernel<OP, 32><<<(unsigned)grid, 256, 0, s>>>(a, bf16, rows, cols, tk, tb, o);
+  }
+  return cudaGetLastError();
+}
+
+// ---- full sum -----------------------------------------------------------------
+constexpr int FULL_BLOCKS = 148 * 8;
+constexpr int FULL_THREADS = 256;
+
+__device__ __forceinline__ float block_sum_256(float v, float* sm) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = v + __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+  if (threadIdx.x == 0) {
+    t = sm[0];
+    for (int w = 1; w < FULL_THREADS / 32; ++w) t = t + sm[w];
+  }
+  __syncthreads();
+  return t;  // valid in thread 0
+}
+
+__global__ void __launch_bounds__(FULL_THREADS)
+full_sum_stage1(const float* __restrict__ a, uint64_t n, float* __restrict__ partial) {
+  __shared__ float sm[FULL_THREADS / 32];
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  const bool vec = (reinterpret_cast<uintptr_t>(a) & 15) == 0;
+  const uint64_t n4 = vec ? n / 4 : 0;
+  const float4* p = reinterpret_cast<const float4*>(a);
+  const uint64_t stride = (uint64_t)gridDim.x * FULL_THREADS;
+  uint64_t i = (uint64_t)blockIdx.x * FULL_THREADS + threadIdx.x;
+  for (; i + 3 * stride < n4; i += 4 * stride) {
+    const float4 v0 = __ldcs(p + i), v1 = __ldcs(p + i + stride), v2 = __ldcs(p + i + 2 * stride),
+                 v3 = __ldcs(p + i + 3 * stride);
+    s0 = s0 + ((v0.x + v0.y) + (v0.z + v0.w));
+    s1 = s1 + ((v1.x + v1.y) + (v1.z + v1.w));
+    s2 = s2 + ((v2.x + v2.y) + (v2.z + v2.w));
+    s3 = s3 + ((v3.x + v3.y) + (v3.z + v3.w));
+  }
+  for (; i < n4; i += stride) {
+    const float4 v0 = __ldcs(p + i);
+    s0 = s0 + ((v0.x + v0.y) + (v0.z + v0.w));
+  }
+  // tail (and the whole array when it is not 16-byte aligned)
+  for (uint64_t j = n4 * 4 + (uint64_t)blockIdx.x * FULL_THREADS + threadIdx.x; j < n; j += stride)
+    s1 = s1 + a[j];
+  const float t = block_sum_256((s0 + s1) + (s2 + s3), sm);
+  if (threadIdx.x == 0) partial[blockIdx.x] = t;
+}
+
+__global__ void __launch_bounds__(FULL_THREADS)
+full_sum_stage2(const float* __restrict__ partial, int count, uint64_t n, int mean,
+                float* __restrict__ out) {
+  __shared__ float sm[FULL_THREADS / 32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < count; i += FULL_THREADS) s = s + partial[i];
+  const float t = block_sum_256(s, sm);
+  if (threadIdx.x == 0) out[0] = mean ? t / (float)n : t;  // sum DIV_SCALAR n (ops.rs:3260-3270)
+}
+
+// ---- softmax rows -----------------------------------------------------------------
+__device__ __forceinline__ float nan_max(float a, float b) {
+  return (a != a) ? a : ((b != b) ? b : fmaxf(a, b));
+}
+template <int THREADS> __device__ __forceinline__ float block_max(float v, float* sm) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = nan_max(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if constexpr (THREADS == 32) return v;
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = sm[0];
+  for (int w = 1; w < THREADS / 32; ++w) t = nan_max(t, sm[w]);
+  __syncthreads();
+  return t;
+}
+template <int THREADS> __device__ __forceinline__ float block_add(float v, float* sm) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = v + __shfl_xor_sync(0xffffffffu, v, o);
+  if constexpr (THREADS == 32) return v;
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = sm[0];
+  for (int w = 1; w < THREADS / 32; ++w) t = t + sm[w];
+  __syncthreads();
+  return t;
+}
+
+__device__ __forceinline__ float scaled_masked(float x, uint32_t m, float scale, bool has_scale) {
+  const float s = has_scale ? x * scale : x;
+  return m ? -INFINITY : s;
+}
+
+// One block a row; the row lives in registers: VPT float4 per thread.
+template <int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+softmax_block_kernel(const float* __restrict__ x, const uint32_t* __restrict__ mask, uint64_t mask_rows,
+                     float scale, int log_form, float* __restrict__ out, uint64_t rows, uint32_t cols) {
+  __shared__ float sm[32];
+  const uint32_t n4 = cols / 4;
+  const bool has_scale = scale != 1.0f;
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float4* xr = reinterpret_cast<const float4*>(x + row * cols);
+    const uint4* mr = mask ? reinterpret_cast<const uint4*>(mask + (row % mask_rows) * cols) : nullptr;
+    float4 v[VPT];
+    float m = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      const uint32_t i = threadIdx.x + u * THREADS;
+      if (i < n4) {
+        float4 t = __ldcs(xr + i);
+        uint4 k = mr ? __ldg(mr + i) : make_uint4(0, 0, 0, 0);
+        t.x = scaled_masked(t.x, k.x, scale, has_scale);
+        t.y = scaled_masked(t.y, k.y, scale, has_scale);
+        t.z = scaled_masked(t.z, k.z, scale, has_scale);
+        t.w = scaled_masked(t.w, k.w, scale, has_scale);
+        v[u] = t;
+        m = nan_max(m, nan_max(nan_max(t.x, t.y), nan_max(t.z, t.w)));
+      }
+    }
+    m = block_max<THREADS>(m, sm);
+    m = (m < -FLT_MAX) ? -FLT_MAX : m;  // clamp: a fully masked row (sfpu/softmax.rs:37-43)
+    float s = 0.f;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      const uint32_t i = threadIdx.x + u * THREADS;
+      if (i < n4) {
+        float4 t = v[u];
+        if (log_form) {
+          t.x = t.x - m; t.y = t.y - m; t.z = t.z - m; t.w = t.w - m;
+          v[u] = t;
+          s = s + ((expf(t.x) + expf(t.y)) + (expf(t.z) + expf(t.w)));
+        } else {
+          t.x = expf(t.x - m); t.y = expf(t.y - m); t.z = expf(t.z - m); t.w = expf(t.w - m);
+          v[u] = t;
+          s = s + ((t.x + t.y) + (t.z + t.w));
+        }
+      }
+    }
+    s = block_add<THREADS>(s, sm);
+    float4* orow = reinterpret_cast<float4*>(out + row * cols);
+    if (log_form) {
+      const float l = logf(s);
+#pragma unroll
+      for (int u = 0; u < VPT; ++u) {
+        const uint32_t i = threadIdx.x + u * THREADS;
+        if (i < n4) {
+          float4 t = v[u];
+          t.x = t.x - l; t.y = t.y - l; t.z = t.z - l; t.w = t.w - l;
+          __stcs(orow + i, t);
+        }
+      }
+    } else {
+      s = (s < FLT_MIN) ? FLT_MIN : s;
+#pragma unroll
+      for (int u = 0; u < VPT; ++u) {
+        const uint32_t i = threadIdx.x + u * THREADS;
+        if (i < n4) {
+          float4 t = v[u];
+          t.x = t.x / s; t.y = t.y / s; t.z = t.z / s; t.w = t.w / s;
+          __stcs(orow + i, t);
+        }
+      }
+    }
+  }
+}
+
+// Any width: a block a row, three passes over global memory (the second and third
+// mostly from L2).  Rows too short or ragged for the register kernel, or too long.
+__global__ void __launch_bounds__(256)
+softmax_stream_kernel(const float* __restrict__ x, const uint32_t* __restrict__ mask, uint64_t mask_rows,
+                      float scale, int log_form, float* __restrict__ out, uint64_t rows, uint64_t cols) {
+  __shared__ float sm[32];
+  const bool has_scale = scale != 1.0f;
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* xr = x + row * cols;
+    const uint32_t* mr = mask ? mask + (row % mask_rows) * cols : nullptr;
+    float m = -INFINITY;
+    for (uint64_t i = threadIdx.x; i < cols; i += 256)
+      m = nan_max(m, scaled_masked(xr[i], mr ? mr[i] : 0u, scale, has_scale));
+    m = block_max<256>(m, sm);
+    m = (m < -FLT_MAX) ? -FLT_MAX : m;
+    float s = 0.f;
+    for (uint64_t i = threadIdx.x; i < cols; i += 256)
+      s = s + expf(scaled_masked(xr[i], mr ? mr[i] : 0u, scale, has_scale) - m);
+    s = block_add<256>(s, sm);
+    float* orow = out + row * cols;
+    if (log_form) {
+      const float l = logf(s);
+      for (uint64_t i = threadIdx.x; i < cols; i += 256)
+        orow[i] = (scaled_masked(xr[i], mr ? mr[i] : 0u, scale, has_scale) - m) - l;
+    } else {
+      s = (s < FLT_MIN) ? FLT_MIN : s;
+      for (uint64_t i = threadIdx.x; i < cols; i += 256)
+        orow[i] = expf(scaled_masked(xr[i], mr ? mr[i] : 0u, scale, has_scale) - m) / s;
+    }
+  }
+}
+
+// ---- rms / rms_norm -------------------------------------------------------------
+__device__ __forceinline__ float ld_f(const void* p, int bf16, uint64_t i) {
+  return __uint_as_float(ld_word(p, bf16, i));
+}
+
+// One warp a row.  stat = sqrt(sumsq * (1/n) + eps): MUL_SCALAR, ADD_SCALAR, SQRT (norm.rs:45-60).
+__global__ void __launch_bounds__(256)
+rms_norm_kernel(const void* a, int a_bf16, const void* b, int b_bf16, const void* gamma, int g_bf16,
+                float eps, void* sum_out, int sum_bf16, void* norm_out, int norm_bf16, float* stat_out,
+                uint64_t rows, uint64_t cols) {
+  const int lane = threadIdx.x & 31;
+  const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+  const float inv = 1.0f / (float)cols;
+  for (uint64_t row = warp; row < rows; row += nwarps) {
+    const uint64_t base = row * cols;
+    float ss = 0.f;
+    for (uint64_t i = lane; i < cols; i += 32) {
+      float v = ld_f(a, a_bf16, base + i);
+      if (b) {
+        v = v + ld_f(b, b_bf16, base + i);
+        if (sum_out) {
+          if (sum_bf16) {
+            const uint16_t h = f32_to_bf16_bits(__float_as_uint(v));
+            reinterpret_cast<uint16_t*>(sum_out)[base + i] = h;
+            v = bf16_bits_to_f32(h);  // the norm reads the sum as it was stored
+          } else {
+            reinterpret_cast<float*>(sum_out)[base + i] = v;
+          }
+        }
+      }
+      ss = ss + v * v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss = ss + __shfl_xor_sync(0xffffffffu, ss, o);
+    const float stat = sqrtf(ss * inv + eps);
+    if (stat_out) { if (lane == 0) stat_out[row] = stat; }
+    if (norm_out) {
+      for (uint64_t i = lane; i < cols; i += 32) {
+        float v;
+        if (b && sum_out) v = ld_f(sum_out, sum_bf16, base + i);
+        else if (b) v = ld_f(a, a_bf16, base + i) + ld_f(b, b_bf16, base + i);
+        else v = ld_f(a, a_bf16, base + i);
+        float r = v / stat;
+        if (gamma) r = r * ld_f(gamma, g_bf16, i);
+        if (norm_bf16) reinterpret_cast<uint16_t*>(norm_out)[base + i] = f32_to_bf16_bits(__float_as_uint(r));
+        else reinterpret_cast<float*>(norm_out)[base + i] = r;
+      }
+    }
+  }
+}
+
+// ---- argmax ---------------------------------------------------------------------
+struct Best { float v; uint32_t i; };
+__device__ __forceinline__ bool better(float v, uint32_t i, float bv, uint32_t bi) {
+  const bool vn = v != v, bn = bv != bv;
+  if (vn || bn) return vn && (!bn || i < bi);
+  return v > bv || (v == bv && i < bi);
+}
+__global__ void __launch_bounds__(1024)
+argmax_rows_kernel(const float* __restrict__ a, uint64_t rows, uint64_t cols, int32_t* __restrict__ out) {
+  __shared__ float sv[32];
+  __shared__ uint32_t si[32];
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* p = a + row * cols;
+    float bv = -INFINITY;
+    uint32_t bi = 0xffffffffu;
+    for (uint64_t i = threadIdx.x; i < cols; i += blockDim.x) {
+      const float v = p[i];
+      if (better(v, (uint32_t)i, bv, bi)) { bv = v; bi = (uint32_t)i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int nw = (blockDim.x + 31) / 32;
+      for (int w = 1; w < nw; ++w)
+        if (better(sv[w], si[w], bv, bi)) { bv = sv[w]; bi = si[w]; }
+      out[row] = (int32_t)bi;
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_reduce(const void* a, int a_bf16, uint64_t rows, uint64_t cols, int op, int axis,
+                          uint32_t tk, uint32_t tb, void* out, cudaStream_t s) {
+  if (rows == 0 || cols == 0) return cudaSuccess;
+  switch (op) {
+    case SUM: return launch_reduce_op<SUM>(a, a_bf16, rows, cols, axis, tk, tb, out, s);
+    case MAX: return launch_reduce_op<MAX>(a, a_bf16, rows, cols, axis, tk, tb, out, s);
+    case PROD: return launch_reduce_op<PROD>(a, a_bf16, rows, cols, axis, tk, tb, out, s);
+    case ALL: return launch_reduce_op<ALL>(a, a_bf16, rows, cols, axis, tk, tb, out, s);
+    case ANY: return launch_reduce_op<ANY>(a, a_bf16, rows, cols, axis, tk, tb, out, s);
+    case BITOR: return launch_reduce_op<BITOR>(a, a_bf16, rows, cols, axis, tk, tb, out, s);
+    case SUM_I32: return launch_reduce_op<SUM_I32>(a, a_bf16, rows, cols, axis, tk, tb, out, s);
+    case PROD_I32: return launch_reduce_op<PROD_I32>(a, a_bf16, rows, cols, axis, tk, tb, out, s);
+    case MIN_I32: return launch_reduce_op<MIN_I32>(a, a_bf16, rows, cols, axis, tk, tb, out, s);
+    case MAX_I32: return launch_reduce_op<MAX_I32>(a, a_bf16, rows, cols, axis, tk, tb, out, s);
+    default: return cudaErrorNotSupported;
+  }
+}
+
+uint64_t full_sum_scratch_floats() { return FULL_BLOCKS; }
+
+cudaError_t launch_full_sum(const float* a, uint64_t n, int mean, float* scratch, float* out,
+                            cudaStream_t s) {
+  full_sum_stage1<<<FULL_BLOCKS, FULL_THREADS, 0, s>>>(a, n, scratch);
+  full_sum_stage2<<<1, FULL_THREADS, 0, s>>>(scratch, FULL_BLOCKS, n, mean, out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t mask_rows, float scale,
+                                int log_form, float* out, uint64_t rows, uint64_t cols,
+                                cudaStream_t s) {
+  if (rows == 0 || cols == 0) return cudaSuccess;
+  const bool al = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) |
+                    reinterpret_cast<uintptr_t>(mask)) & 15) == 0;
+  const uint64_t n4 = cols / 4;
+  const uint64_t grid = rows < 148ull * 64 ? rows : 148ull * 64;
+#define SM_LAUNCH(T, V)                                                                         \
+  softmax_block_kernel<T, V><<<(unsigned)(rows < (148ull * (2048 / T)) ? rows : 148ull * (2048 / T)), \
+                               T, 0, s>>>(x, mask, mask_rows, scale, log_form, out, rows, (uint32_t)cols)
+  if (al && cols % 4 == 0 && cols >= 128 && n4 <= 1024 * 8) {
+    if (n4 <= 32) SM_LAUNCH(32, 1);
+    else if (n4 <= 64) SM_LAUNCH(64, 1);
+    else if (n4 <= 128) SM_LAUNCH(128, 1);
+    else if (n4 <= 256) SM_LAUNCH(128, 2);
+    else if (n4 <= 512) SM_LAUNCH(256, 2);
+    else if (n4 <= 1024) SM_LAUNCH(256, 4);
+    else if (n4 <= 2048) SM_LAUNCH(512, 4);
+    else if (n4 <= 4096) SM_LAUNCH(1024, 4);
+    else SM_LAUNCH(1024, 8);
+  } else {
+    softmax_stream_kernel<<<(unsigned)grid, 256, 0, s>>>(x, mask, mask_rows, scale, log_form, out, rows, cols);
+  }
+#undef SM_LAUNCH
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rms(const float* a, uint64_t rows, uint64_t cols, float eps, float* out,
+                       cudaStream_t s) {
+  if (rows == 0) return cudaSuccess;
+  uint64_t grid = (rows + 7) / 8;
+  if (grid > 148ull * 16) grid = 148ull * 16;
+  rms_norm_kernel<<<(unsigned)grid, 256, 0, s>>>(a, 0, nullptr, 0, nullptr, 0, eps, nullptr, 0, nullptr, 0,
+                                                 out, rows, cols);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rms_norm(const void* a, int a_bf16, const void* b, int b_bf16, const void* gamma,
+                            int gamma_bf16, float eps, void* sum_out, int sum_bf16, void* norm_out,
+                            int norm_bf16, uint64_t rows, uint64_t cols, cudaStream_t s) {
+  if (rows == 0) return cudaSuccess;
+  uint64_t grid = (rows + 7) / 8;
+  if (grid > 148ull * 16) grid = 148ull * 16;
+  rms_norm_kernel<<<(unsigned)grid, 256, 0, s>>>(a, a_bf16, b, b_bf16, gamma, gamma_bf16, eps, sum_out,
+                                                 sum_bf16, norm_out, norm_bf16, nullptr, rows, cols);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_argmax_rows(const float* a, uint64_t rows, uint64_t cols, int32_t* out,
+                               cudaStream_t s) {
+  if (rows == 0) return cudaSuccess;
+  const unsigned threads = cols >= 4096 ? 1024 : (cols >= 512 ? 256 : 64);
+  argmax_rows_kernel<<<(unsigned)(rows < 65535 ? rows : 65535), threads, 0, s>>>(a, rows, cols, out);
+  return cudaGetLastError();
+}
+
+}  // namespace b200

@@ -1,0 +1,110 @@
+// Launch interface between the engine (host logic, engine.cu) and the kernel
+// translation units.  Every function enqueues on `stream` and returns the launch
+// status; none allocates or synchronises.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+// A matrix operand as a kernel sees it: base already moved to the block's
+// first element, leading dimension in elements.
+struct Mat {
+  const void* p = nullptr;
+  uint64_t ld = 0;
+  uint64_t rows = 0, cols = 0;  // extent of the operand (for broadcast: r % rows, c % cols)
+  int bf16 = 0;                 // 0: 32-bit words, 1: bf16
+};
+
+struct EltwiseArgs {
+  uint32_t kind;
+  float s1, s2;
+  Mat a, b, c;
+  void* out;
+  uint64_t out_ld;
+  int out_bf16;
+  uint64_t rows, cols;  // output extent
+  int* err;             // device error word (first failure wins)
+};
+cudaError_t launch_eltwise(const EltwiseArgs& args, cudaStream_t stream);
+bool eltwise_kind_known(uint32_t kind);
+
+// x cos + swap_halves(x) sin, heads of `head` columns (tt-kernels/src/tensor.rs:5545).
+cudaError_t launch_rope(const Mat& x, const Mat& cs, const Mat& sn, uint64_t head, void* out,
+                        uint64_t out_ld, int out_bf16, uint64_t rows, uint64_t cols,
+                        cudaStream_t stream);
+cudaError_t launch_cast(const void* in, void* out, uint64_t n, int to_bf16, cudaStream_t stream);
+
+// ---- reductions ------------------------------------------------------------
+cudaError_t launch_reduce(const void* a, int a_bf16, uint64_t rows, uint64_t cols, int op, int axis,
+                          uint32_t then_kind, uint32_t then_bits, void* out, cudaStream_t stream);
+// Full sum (mean): two stages, fixed order.  `scratch` holds >= full_sum_scratch_floats() floats.
+uint64_t full_sum_scratch_floats();
+cudaError_t launch_full_sum(const float* a, uint64_t n, int mean, float* scratch, float* out,
+                            cudaStream_t stream);
+cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t mask_rows, float scale,
+                                int log_form, float* out, uint64_t rows, uint64_t cols,
+                                cudaStream_t stream);
+cudaError_t launch_rms(const float* a, uint64_t rows, uint64_t cols, float eps, float* out,
+                       cudaStream_t stream);
+// a (+ b) -> optional sum_out, norm_out (f32 or bf16); a/b may be bf16.
+cudaError_t launch_rms_norm(const void* a, int a_bf16, const void* b, int b_bf16, const void* gamma,
+                            int gamma_bf16, float eps, void* sum_out, int sum_bf16, void* norm_out,
+                            int norm_bf16, uint64_t rows, uint64_t cols, cudaStream_t stream);
+cudaError_t launch_argmax_rows(const float* a, uint64_t rows, uint64_t cols, int32_t* out,
+                               cudaStream_t stream);
+
+// ---- indexing and copies (bit moves; elem_bytes 2 or 4) -----------------------
+cudaError_t launch_select_rows(const void* table, uint64_t t_rows, uint64_t cols, int elem_bytes,
+                               const int32_t* idx, uint64_t n, void* out, int* err, cudaStream_t);
+cudaError_t launch_pick_columns(const uint32_t* x, uint64_t rows, uint64_t cols, const int32_t* idx,
+                                uint32_t* out, int* err, cudaStream_t);
+cudaError_t launch_scatter_add_columns(float* t_copy, uint64_t rows, uint64_t cols, const int32_t* idx,
+                                       const float* v, int* err, cudaStream_t);
+// out (already a copy of t) += value rows at idx, duplicates in index order.
+cudaError_t launch_select_add_rows(float* out, uint64_t t_rows, uint64_t cols, const int32_t* idx,
+                                   uint64_t n, const float* value, int* err, cudaStream_t);
+// out (already a copy of table) row idx[i] = values row i; later i wins.
+cudaError_t launch_scatter_rows(uint32_t* out, uint64_t t_rows, uint64_t cols, const int32_t* idx,
+                                uint64_t n, const uint32_t* values, int* err, cudaStream_t);
+cudaError_t launch_gather_indexed(const uint32_t* x, uint64_t rows, uint64_t cols, const int32_t* idx,
+                                  uint64_t i_cols, uint32_t* out, int* err, cudaStream_t);
+// out[i,:] = *(row_ptrs[i]) for cols elements.
+cudaError_t launch_gather_row_ptrs(const void* const* row_ptrs, uint64_t n_rows, uint64_t cols,
+                                   int elem_bytes, void* out, cudaStream_t);
+// out[dst_row(i), :] = src[src_row(i), :], pairs (dst, src) on the device.
+cudaError_t launch_assign_rows(void* out, const void* value, uint64_t cols, int elem_bytes,
+                               const uint64_t* pairs, uint64_t n, cudaStream_t);
+struct MoveDev { uint64_t from_r, from_c, to_r, to_c, rows, cols; int32_t transposed; int32_t pad; };
+cudaError_t launch_copy_blocks(const void* src, uint64_t src_ld, void* dst, uint64_t dst_ld,
+                               int elem_bytes, const MoveDev* moves_dev, uint64_t n_moves,
+                               uint64_t max_rows, uint64_t max_cols, cudaStream_t);
+// out[i] = src[pairs[2i] * src_ld + pairs[2i+1]]
+cudaError_t launch_repack(const void* src, uint64_t src_ld, int elem_bytes, const uint64_t* pairs_dev,
+                          uint64_t n, void* out, cudaStream_t);
+
+// ---- products ---------------------------------------------------------------
+struct GemmBatch {       // one product of a batched call, element offsets into a / b / c
+  uint64_t a_off, b_off, c_off;
+  int32_t a_trans, b_trans;
+};
+struct GemmArgs {
+  const void* a; const void* b; void* c;
+  int in_bf16;           // operands bf16 (else f32)
+  int out_bf16;          // result bf16 (else f32)
+  uint64_t m, n, k;
+  uint64_t lda, ldb, ldc;  // leading dims of the stored matrices
+  int a_trans, b_trans;    // stored matrix is the transpose of the logical operand
+  uint64_t batch;          // 1, or number of products
+  const GemmBatch* batches_dev;  // device array when batch > 1 (or nullptr for batch 1)
+};
+// SIMT (FFMA) path: any shape, any transposes, f32 or bf16 operands, f32 accumulate.
+cudaError_t launch_gemm_simt(const GemmArgs& g, cudaStream_t stream);
+
+// tcgen05 path.  Returns cudaErrorNotSupported when the shape cannot take it.
+struct TcPlan;  // opaque: tensor maps + grid
+bool gemm_tc_supported(const GemmArgs& g, const char** why);
+cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int* err_word,
+                           cudaStream_t stream);
+
+}  // namespace b200
