@@ -1,0 +1,345 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: BF16 GEMM TFLOP/s through the engine's C ABI.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--extras]
+
+N = 1: one step is one 8192^3 BF16 product (FP32 accumulate, BF16 result) on operands
+resident in HBM, launched through `matmul_dram_bf16`; `value` is 2*8192^3*K / device time.
+N > 1 (under torchrun, one rank a GPU): the 16384^3 product split along N with K whole
+(crates/tt-kernels/src/shard.rs:348-458), every rank computing its column slice and an
+NCCL all-gather leaving the full C on every rank; time is the max over ranks.
+`e2e` is the same product called with HOST operands: upload of A and B from pinned host
+memory, the product, and the download of C, all inside the timed region.
+`--impl reference` times the CPU restatement of the reference's comparison backend (the
+reference itself is Rust for Tenstorrent cards and cannot run here) on the host cores.
+One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "bf16_gemm_tflops"
+UNIT = "TFLOP/s"
+N1_SIZE = 8192
+NN_SIZE = 16384
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return d, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.idx = gpu_index
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-i", str(gpu_index), "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cheap_bf16(shape, seed):
+    """Fast synthetic BF16 operand in [-1,1) for the big benchmark shapes."""
+    rng = np.random.default_rng(seed)
+    f = rng.random(shape, dtype=np.float32) * 2.0 - 1.0
+    return (f.view(np.uint32) >> 16).astype(np.uint16)
+
+
+# ---------------------------------------------------------------------- CPU baseline
+def cpu_gemm_baseline(target_seconds=12.0):
+    """The CPU restatement's F32 product of BF16-rounded operands on all host cores, on a
+    bounded sample (the same product at a smaller size), as TFLOP/s."""
+    from oracle import oracle as orc
+    cores = orc.clib().orc_threads()
+    n = 1024
+    a = orc.from_bf16(cheap_bf16((n, n), 1))
+    b = orc.from_bf16(cheap_bf16((n, n), 2))
+    t0 = time.perf_counter()
+    orc.gemm_f32(a, b)
+    dt = time.perf_counter() - t0
+    rate = 2.0 * n ** 3 / dt
+    # grow the sample towards the target time (cubic cost), capped at 4096
+    n2 = int(min(4096, max(1024, (rate * target_seconds / 2.0) ** (1.0 / 3.0)) // 256 * 256))
+    if n2 > n:
+        a = orc.from_bf16(cheap_bf16((n2, n2), 1))
+        b = orc.from_bf16(cheap_bf16((n2, n2), 2))
+        t0 = time.perf_counter()
+        orc.gemm_f32(a, b)
+        dt = time.perf_counter() - t0
+        n = n2
+    return {"value": 2.0 * n ** 3 / dt / 1e12, "unit": UNIT, "cores": int(cores), "kind": "port",
+            "sample": f"{n}^3 F32 product of BF16-rounded operands (C/OpenMP restatement), {dt:.2f} s"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    base = None
+    for _ in range(max(1, min(args.steps, 3))):
+        base = cpu_gemm_baseline(target_seconds=8.0)
+        vals.append(base["value"])
+    v = float(np.mean(vals))
+    base["value"] = v
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+            "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": workload_name(args.gpus), "note": "CPU restatement of the reference's comparison backend "
+                       "(burn-flex is not in the reference tree); bounded sample, see cpu_baseline.sample"},
+            "cpu_baseline": base,
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload_name(n_gpus):
+    if n_gpus == 1:
+        return f"bf16 gemm {N1_SIZE}^3 (A [M,K], B [K,N] row-major, FP32 accumulate, bf16 out)"
+    return f"bf16 gemm {NN_SIZE}^3 column-sharded over {n_gpus} GPUs, NCCL all-gather of C"
+
+
+# ---------------------------------------------------------------------- GPU arm
+def run_single(args):
+    import torch
+    from metalium_rs_b200 import CudaEngine, build
+    build.build()
+    eng = CudaEngine(0, bf16_matmul_mode=2)  # tcgen05 or refuse: never a slower path silently
+    n = args.size or N1_SIZE
+    a_host = torch.from_numpy(cheap_bf16((n, n), 11).view(np.int16)).pin_memory()
+    b_host = torch.from_numpy(cheap_bf16((n, n), 12).view(np.int16)).pin_memory()
+    c_host = torch.empty((n, n), dtype=torch.int16).pin_memory()
+    ia = eng.upload_ptr(a_host.data_ptr(), n, n, 3)
+    ib = eng.upload_ptr(b_host.data_ptr(), n, n, 3)
+    flops = 2.0 * n ** 3
+
+    def step():
+        out, _ = eng.matmul_dram_bf16(ia, False, ib, False)
+        eng.free(out)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    eng.sync()
+    # a quick validity check of the timed kernel's output (64 samples against F64 dots)
+    out, _ = eng.matmul_dram(ia, False, ib, False)
+    c = eng.download(out)
+    eng.free(out)
+    af = (a_host.numpy().view(np.uint16).astype(np.uint32) << 16).view(np.float32)
+    bf = (b_host.numpy().view(np.uint16).astype(np.uint32) << 16).view(np.float32)
+    rng = np.random.default_rng(0)
+    worst = 0.0
+    for i, j in zip(rng.integers(0, n, 64), rng.integers(0, n, 64)):
+        t = af[i].astype(np.float64) @ bf[:, j].astype(np.float64)
+        s = np.abs(af[i]).astype(np.float64) @ np.abs(bf[:, j]).astype(np.float64)
+        worst = max(worst, abs(float(c[i, j]) - t) / s)
+    if worst > 1e-5:
+        raise SystemExit(f"bench: the timed kernel's output is wrong (error / S = {worst:.3e})")
+    del c
+
+    launches0 = eng.device_traffic().launches
+    sampler = ClockSampler(0)
+    eng.sync()
+    eng.timer_start()
+    for _ in range(args.steps):
+        step()
+    ms = eng.timer_stop()
+    clocks = sampler.stop()
+    launches = eng.device_traffic().launches - launches0
+    ms_per_step = ms / args.steps
+    value = flops / (ms_per_step * 1e-3) / 1e12
+
+    # end to end through the C ABI with host buffers
+    e2e_steps = max(1, min(args.steps, 5))
+    for _ in range(2):
+        x, y = eng.upload_ptr(a_host.data_ptr(), n, n, 3), eng.upload_ptr(b_host.data_ptr(), n, n, 3)
+        o, _ = eng.matmul_dram_bf16(x, False, y, False)
+        eng.download_into(o, c_host.data_ptr(), n * n, 2)
+        for i in (x, y, o):
+            eng.free(i)
+    t0 = time.perf_counter()
+    eng.timer_start()
+    for _ in range(e2e_steps):
+        x, y = eng.upload_ptr(a_host.data_ptr(), n, n, 3), eng.upload_ptr(b_host.data_ptr(), n, n, 3)
+        o, _ = eng.matmul_dram_bf16(x, False, y, False)
+        eng.download_into(o, c_host.data_ptr(), n * n, 2)
+        for i in (x, y, o):
+            eng.free(i)
+    e2e_ms = eng.timer_stop() / e2e_steps
+    wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    e2e_ms = max(e2e_ms, wall_ms)
+    e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": 2 * n * n * 2,
+           "d2h_bytes_per_step": n * n * 2, "ms_per_step": e2e_ms}
+
+    pk, which = peaks()
+    peak = float(pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel<256,4,K-major A,MN-major B>", "achieved": value, "peak": peak,
+                "unit": UNIT, "frac": value / peak, "peak_source": f"{which} cuBLAS bf16 burst",
+                "frac_of_nominal_2250": value / 2250.0, "traffic": None}
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": workload_name(1) if n == N1_SIZE else f"bf16 gemm {n}^3", "m": n, "n": n, "k": n,
+                       "l2": "operands and result (403 MB at 8192^3) exceed the 126 MB L2; no flush needed",
+                       "path": eng.last_matmul_path()},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
+            "validated": {"samples": 64, "max_err_over_S": worst}}
+    if args.extras:
+        line["extras"] = extras(eng)
+    if not args.no_cpu:
+        line["cpu_baseline"] = cpu_gemm_baseline()
+    print(json.dumps(line))
+    eng.close()
+
+
+def extras(eng):
+    """The other sizes of the sweep and the memory-bound suite, timed the same way."""
+    from metalium_rs_b200 import COLS, SUM, EltwiseOp, kinds
+    pk, _ = peaks()
+    hbm = float(pk.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+    out = {"gemm_bf16": {}, "gemm_f32": {}, "suite": {}}
+
+    def timed(fn, reps=20, warm=3):
+        for _ in range(warm):
+            fn()
+        eng.sync()
+        eng.timer_start()
+        for _ in range(reps):
+            fn()
+        return eng.timer_stop() / reps
+
+    for n in (512, 1024, 2048, 4096, 8192):
+        ia = eng.upload_bf16(cheap_bf16((n, n), 1), n, n)
+        ib = eng.upload_bf16(cheap_bf16((n, n), 2), n, n)
+
+        def f():
+            o, _ = eng.matmul_dram_bf16(ia, False, ib, False)
+            eng.free(o)
+        ms = timed(f)
+        out["gemm_bf16"][str(n)] = {"ms": ms, "tflops": 2.0 * n ** 3 / ms / 1e9}
+        eng.free(ia); eng.free(ib)
+    for n in (512, 1024, 2048, 4096):
+        rng = np.random.default_rng(n)
+        ia = eng.upload(rng.random((n, n), dtype=np.float32) * 2 - 1, n, n)
+        ib = eng.upload(rng.random((n, n), dtype=np.float32) * 2 - 1, n, n)
+
+        def f():
+            o, _ = eng.matmul_dram(ia, False, ib, False)
+            eng.free(o)
+        ms = timed(f, reps=5 if n >= 2048 else 20)
+        out["gemm_f32"][str(n)] = {"ms": ms, "tflops": 2.0 * n ** 3 / ms / 1e9, "path": eng.last_matmul_path()}
+        eng.free(ia); eng.free(ib)
+
+    rows = cols = 8192
+    rng = np.random.default_rng(3)
+    x = eng.upload(rng.random((rows, cols), dtype=np.float32) * 3.99 + 0.01, rows, cols)
+    row = eng.upload(rng.random((1, cols), dtype=np.float32) + 0.5, 1, cols)
+    nbytes = rows * cols * 4
+    for name, k, b in (("exp", kinds.EXP, None), ("log", kinds.LOG, None), ("recip", kinds.RECIP, None),
+                       ("sqrt", kinds.SQRT, None), ("relu", kinds.RELU, None), ("gelu_tanh", kinds.GELU_TANH, None),
+                       ("silu", kinds.SILU, None), ("add_row", kinds.ADD, row), ("mul_row", kinds.MUL, row),
+                       ("div_row", kinds.DIV, row)):
+        def f():
+            o, _ = eng.eltwise_op(EltwiseOp(k, 0, 0), x, b)
+            eng.free(o)
+        ms = timed(f)
+        gbs = 2 * nbytes / ms / 1e6
+        out["suite"][name] = {"ms": ms, "gbs": gbs, "frac_of_measured_hbm": gbs / hbm, "frac_of_nominal_8000": gbs / 8000.0}
+
+    def fs():
+        o, _ = eng.full_sum(x)
+        eng.free(o)
+    ms = timed(fs)
+    out["suite"]["full_sum"] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm}
+
+    def fr():
+        o, _ = eng.reduce(x, SUM, COLS)
+        eng.free(o)
+    ms = timed(fr)
+    out["suite"]["row_sum"] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm}
+    eng.free(x); eng.free(row)
+    sx = eng.upload(rng.random((4096, 32768), dtype=np.float32) * 8 - 4, 4096, 32768)
+
+    def fm():
+        o, _ = eng.softmax_rows(sx, None, 1.0)
+        eng.free(o)
+    ms = timed(fm)
+    sb = 2 * 4096 * 32768 * 4
+    out["suite"]["softmax_4096x32768"] = {"ms": ms, "gbs": sb / ms / 1e6, "frac_of_measured_hbm": sb / ms / 1e6 / hbm}
+    eng.free(sx)
+    return out
+
+
+def run_multi(args):
+    from metalium_rs_b200 import sharded
+    sharded.bench_main(args, METRIC, UNIT, NN_SIZE, workload_name, peaks, ClockSampler, cheap_bf16)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--extras", action="store_true", help="also time the rest of the sweep and the memory-bound suite")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--size", type=int, default=0, help="override the N=1 problem size (profiling on a small case)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus > 1 or world > 1:
+        return run_multi(args)
+    return run_single(args)
+
+
+if __name__ == "__main__":
+    main()

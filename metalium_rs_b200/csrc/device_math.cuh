@@ -36,14 +36,17 @@ __device__ __forceinline__ float sigmoid_flex(float x) {
 }
 
 // 0.5 x (1 + erf(x / sqrt 2))  (crates/tt-kernels/src/sfpu/ops.rs:135)
+// 1 + erf(z) is taken as erfc(-z): for x well below zero the sum would cancel and lose
+// the relative accuracy the contract asks for.
 __device__ __forceinline__ float gelu_erf(float x) {
-  return (0.5f * x) * (1.0f + erff(x * 0.70710678118654752440f));
+  return (0.5f * x) * erfcf(-x * 0.70710678118654752440f);
 }
 // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
+// 0.5 (1 + tanh y) = sigmoid(2y), which keeps its relative accuracy for y << 0.
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float x3 = x * x * x;
   const float inner = 0.7978845608028654f * (x + 0.044715f * x3);
-  return (0.5f * x) * (1.0f + tanhf(inner));
+  return x * sigmoid_flex(2.0f * inner);
 }
 
 }  // namespace b200

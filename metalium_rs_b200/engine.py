@@ -1,0 +1,460 @@
+"""Host-side mirror of the reference's `Engine` trait over the C ABI.
+
+`CudaEngine` has the method names, argument meaning and failure behaviour of
+`burn_tt::Engine` (crates/burn-tt/src/server.rs:42-786): tensors are opaque buffer ids,
+every producing method returns `(id, [rows, cols])`, failures raise `TtError` with the
+variant the reference would return (crates/burn-tt/src/error.rs:26-67).  It is a thin
+ctypes binding of include/b200tt.h: no arithmetic happens here, and there is no
+fallback -- without the built library, or without a B200, construction fails.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Optional, Sequence, Tuple
+
+import numpy as np
+
+from . import kinds
+
+_LIB_PATH = Path(__file__).resolve().parent / "libb200tt.so"
+_lib = None
+
+OK, OUT_OF_MEMORY, UNSUPPORTED, DEVICE, TIMEOUT, STALE, DOMAIN, NO_DEVICE = range(8)
+F32, I32, BOOL, BF16 = range(4)
+SUM, MAX, PROD, ALL, ANY, BITOR, SUM_I32, PROD_I32, MIN_I32, MAX_I32 = range(10)
+ROWS, COLS = 0, 1
+
+_STATUS_NAMES = {1: "OutOfMemory", 2: "Unsupported", 3: "Device", 4: "Timeout", 5: "StaleTensor",
+                 6: "Device(DOMAIN)", 7: "NoDriver"}
+
+
+class TtError(RuntimeError):
+    """A failed engine call: `status` is the b200_status code, `variant` the reference's name."""
+
+    def __init__(self, status: int, text: str):
+        self.status = status
+        self.variant = _STATUS_NAMES.get(status, str(status))
+        super().__init__(f"{self.variant}: {text}")
+
+
+class EltwiseOp(C.Structure):  # tt-kernels/src/tensor.rs:3785
+    _fields_ = [("kind", C.c_uint32), ("scalar", C.c_float), ("scalar2", C.c_float)]
+
+
+class Block(C.Structure):  # tt-kernels/src/tensor.rs:3479
+    _fields_ = [("at", C.c_uint64 * 2), ("transposed", C.c_int32), ("_pad", C.c_int32)]
+
+
+class BlockMove(C.Structure):  # tt-kernels/src/tensor.rs:6659
+    _fields_ = [("from_", C.c_uint64 * 2), ("to", C.c_uint64 * 2), ("extent", C.c_uint64 * 2),
+                ("transposed", C.c_int32), ("_pad", C.c_int32)]
+
+
+class BlockArg(C.Structure):  # burn-tt/src/server.rs:3449
+    _fields_ = [("id", C.c_uint64), ("at", C.c_uint64 * 2), ("dims", C.c_uint64 * 2)]
+
+
+class BatchedLayout(C.Structure):  # tt-kernels/src/session.rs:802
+    _fields_ = [("lhs_padded", C.c_int32), ("stacked", C.c_int32)]
+
+
+class Traffic(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("bytes_h2d", "bytes_d2h", "h2d_calls", "d2h_calls", "launches",
+                                          "pool_reserved", "pool_in_use", "pool_high_water")]
+
+
+class Config(C.Structure):
+    _fields_ = [("f32_matmul_mode", C.c_int32), ("bf16_matmul_mode", C.c_int32), ("pool_limit_bytes", C.c_uint64),
+                ("fail_alloc_at", C.c_int32), ("_pad", C.c_int32)]
+
+
+def library_path() -> Path:
+    return _LIB_PATH
+
+
+def load_library() -> C.CDLL:
+    """dlopen the engine.  Raises if it was not built: there is no other implementation."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise ImportError(f"{_LIB_PATH} is missing: run `python -m metalium_rs_b200.build` "
+                              "(the engine has no CPU or PyTorch fallback)")
+        _lib = C.CDLL(str(_LIB_PATH))
+        _lib.b200_last_error.restype = C.c_size_t
+        _lib.b200_last_error.argtypes = [C.c_void_p, C.c_char_p, C.c_size_t]
+        _lib.b200_stream.restype = C.c_void_p
+        _lib.b200_stream.argtypes = [C.c_void_p]
+        _lib.b200_last_matmul_path.restype = C.c_char_p
+        _lib.b200_last_matmul_path.argtypes = [C.c_void_p]
+        _lib.b200_engine_destroy.restype = None
+        _lib.b200_free.restype = None
+        _lib.b200_set_op_label.restype = None
+        _lib.b200_traffic_get.restype = None
+        _lib.b200_last_oom.restype = None
+    return _lib
+
+
+def _ptr(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _block(b) -> "BlockArg":
+    if isinstance(b, BlockArg):
+        return b
+    bid, at, dims = b
+    return BlockArg(bid, (C.c_uint64 * 2)(*at), (C.c_uint64 * 2)(*dims))
+
+
+Out = Tuple[int, Tuple[int, int]]
+
+
+class CudaEngine:
+    """One GPU's engine; the B200 counterpart of `KmdEngine` (server.rs:4071)."""
+
+    def __init__(self, device: int = 0, *, f32_matmul_mode: int = 0, bf16_matmul_mode: int = 0,
+                 pool_limit_bytes: int = 0, fail_alloc_at: int = 0):
+        self._lib = load_library()
+        self._e = C.c_void_p()
+        cfg = Config(f32_matmul_mode, bf16_matmul_mode, pool_limit_bytes, fail_alloc_at, 0)
+        st = self._lib.b200_engine_create(C.c_int32(device), C.byref(cfg), C.byref(self._e))
+        if st:
+            buf = C.create_string_buffer(1024)
+            self._lib.b200_last_error(None, buf, 1024)
+            self._e = None
+            raise TtError(st, buf.value.decode())
+        self.device = device
+
+    # -- plumbing ------------------------------------------------------------
+    def close(self):
+        if getattr(self, "_e", None):
+            self._lib.b200_engine_destroy(self._e)
+            self._e = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def _check(self, st: int):
+        if st:
+            buf = C.create_string_buffer(2048)
+            self._lib.b200_last_error(self._e, buf, 2048)
+            raise TtError(st, buf.value.decode())
+
+    def _call(self, fn, *args) -> Out:
+        out = C.c_uint64()
+        dims = (C.c_uint64 * 2)()
+        self._check(fn(self._e, *args, C.byref(out), dims))
+        return out.value, (dims[0], dims[1])
+
+    # -- capabilities (server.rs:53,75,240) --------------------------------------
+    def supports_dram(self) -> bool:
+        return bool(self._lib.b200_supports_dram(self._e))
+
+    def supports_batched_layout(self) -> bool:
+        return bool(self._lib.b200_supports_batched_layout(self._e))
+
+    def supports_exact_matmul(self) -> bool:
+        return bool(self._lib.b200_supports_exact_matmul(self._e))
+
+    # -- storage (server.rs:91-174, 285) -----------------------------------------
+    def upload(self, values, rows: int, cols: int) -> int:
+        a = np.ascontiguousarray(values, dtype=np.float32)
+        assert a.size == rows * cols
+        out = C.c_uint64()
+        self._check(self._lib.b200_upload_f32(self._e, _ptr(a), C.c_uint64(rows), C.c_uint64(cols), C.byref(out)))
+        return out.value
+
+    def upload_bf16(self, values, rows: int, cols: int) -> int:
+        a = np.ascontiguousarray(values, dtype=np.uint16)
+        assert a.size == rows * cols
+        out = C.c_uint64()
+        self._check(self._lib.b200_upload_bf16(self._e, _ptr(a), C.c_uint64(rows), C.c_uint64(cols), C.byref(out)))
+        return out.value
+
+    def upload_bits(self, bits, rows: int, cols: int, elem: int) -> int:
+        a = np.ascontiguousarray(bits).view(np.uint32) if np.asarray(bits).dtype.itemsize == 4 \
+            else np.ascontiguousarray(bits, dtype=np.uint32)
+        assert a.size == rows * cols
+        out = C.c_uint64()
+        self._check(self._lib.b200_upload_bits(self._e, _ptr(a), C.c_uint64(rows), C.c_uint64(cols), C.c_int32(elem),
+                                               C.byref(out)))
+        return out.value
+
+    def upload_ptr(self, host_ptr: int, rows: int, cols: int, elem: int = F32) -> int:
+        """Upload from a raw host address (e.g. pinned memory another library owns)."""
+        out = C.c_uint64()
+        fn = {F32: self._lib.b200_upload_f32, BF16: self._lib.b200_upload_bf16}.get(elem)
+        if fn is None:
+            self._check(self._lib.b200_upload_bits(self._e, C.c_void_p(host_ptr), C.c_uint64(rows), C.c_uint64(cols),
+                                                   C.c_int32(elem), C.byref(out)))
+        else:
+            self._check(fn(self._e, C.c_void_p(host_ptr), C.c_uint64(rows), C.c_uint64(cols), C.byref(out)))
+        return out.value
+
+    def dims_of(self, buf: int) -> Tuple[Tuple[int, int], int]:
+        dims = (C.c_uint64 * 2)()
+        elem = C.c_int32()
+        st = self._lib.b200_dims(self._e, C.c_uint64(buf), dims, C.byref(elem))
+        if st:
+            raise TtError(st, f"buffer {buf} is not live on this engine")
+        return (dims[0], dims[1]), elem.value
+
+    def download(self, buf: int) -> np.ndarray:
+        (r, c), _ = self.dims_of(buf)
+        out = np.empty((r, c), dtype=np.float32)
+        self._check(self._lib.b200_download_f32(self._e, C.c_uint64(buf), _ptr(out), C.c_uint64(out.size)))
+        return out
+
+    def download_bf16(self, buf: int) -> np.ndarray:
+        (r, c), _ = self.dims_of(buf)
+        out = np.empty((r, c), dtype=np.uint16)
+        self._check(self._lib.b200_download_bf16(self._e, C.c_uint64(buf), _ptr(out), C.c_uint64(out.size)))
+        return out
+
+    def download_bits(self, buf: int) -> np.ndarray:
+        (r, c), _ = self.dims_of(buf)
+        out = np.empty((r, c), dtype=np.uint32)
+        self._check(self._lib.b200_download_bits(self._e, C.c_uint64(buf), _ptr(out), C.c_uint64(out.size)))
+        return out
+
+    def download_into(self, buf: int, host_ptr: int, capacity_elems: int, elem_bytes: int = 4):
+        fn = self._lib.b200_download_bits if elem_bytes == 4 else self._lib.b200_download_bf16
+        self._check(fn(self._e, C.c_uint64(buf), C.c_void_p(host_ptr), C.c_uint64(capacity_elems)))
+
+    def free(self, buf: int):
+        self._lib.b200_free(self._e, C.c_uint64(buf))
+
+    def zeros_dram(self, dims, elem: int = F32, bf16: bool = False) -> Out:
+        return self._call(self._lib.b200_zeros, C.c_uint64(dims[0]), C.c_uint64(dims[1]),
+                          C.c_int32(BF16 if bf16 else elem))
+
+    def device_ptr(self, buf: int) -> Tuple[int, int]:
+        p = C.c_void_p()
+        n = C.c_uint64()
+        st = self._lib.b200_device_ptr(self._e, C.c_uint64(buf), C.byref(p), C.byref(n))
+        if st:
+            raise TtError(st, f"buffer {buf} is not live on this engine")
+        return p.value, n.value
+
+    def adopt(self, device_ptr: int, rows: int, cols: int, elem: int) -> int:
+        out = C.c_uint64()
+        self._check(self._lib.b200_adopt(self._e, C.c_void_p(device_ptr), C.c_uint64(rows), C.c_uint64(cols),
+                                         C.c_int32(elem), C.byref(out)))
+        return out.value
+
+    def copy_into(self, src: int, dst: int):
+        self._check(self._lib.b200_copy_into(self._e, C.c_uint64(src), C.c_uint64(dst)))
+
+    def write_ptr(self, buf: int, host_ptr: int, n: int, elem_bytes: int = 4):
+        fn = self._lib.b200_write_f32 if elem_bytes == 4 else self._lib.b200_write_bf16
+        self._check(fn(self._e, C.c_uint64(buf), C.c_void_p(host_ptr), C.c_uint64(n)))
+
+    # -- products (server.rs:70,178,191,229,245) -----------------------------------
+    def matmul(self, a, b, mkn) -> np.ndarray:
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        b = np.ascontiguousarray(b, dtype=np.float32)
+        out = np.empty((mkn[0], mkn[2]), dtype=np.float32)
+        self._check(self._lib.b200_matmul_host(self._e, _ptr(a), _ptr(b), (C.c_uint64 * 3)(*mkn), _ptr(out)))
+        return out
+
+    def matmul_dram(self, a: int, a_transposed: bool, b: int, b_transposed: bool) -> Out:
+        return self._call(self._lib.b200_matmul, C.c_uint64(a), C.c_int32(a_transposed), C.c_uint64(b),
+                          C.c_int32(b_transposed), C.c_int32(0))
+
+    def matmul_dram_bf16(self, a: int, a_transposed: bool, b: int, b_transposed: bool) -> Out:
+        return self._call(self._lib.b200_matmul, C.c_uint64(a), C.c_int32(a_transposed), C.c_uint64(b),
+                          C.c_int32(b_transposed), C.c_int32(1))
+
+    def matmul_dram_batched_layout(self, a: int, b: int, items, mkn, layout: Optional[BatchedLayout] = None,
+                                   bf16: bool = False) -> Out:
+        n = len(items)
+        ab = (Block * max(n, 1))()
+        bb = (Block * max(n, 1))()
+        for i, (x, y) in enumerate(items):
+            ab[i] = Block((C.c_uint64 * 2)(*x[0]), int(x[1]), 0)
+            bb[i] = Block((C.c_uint64 * 2)(*y[0]), int(y[1]), 0)
+        lay = C.byref(layout) if layout is not None else None
+        return self._call(self._lib.b200_matmul_batched, C.c_uint64(a), C.c_uint64(b), ab, bb, C.c_uint64(n),
+                          (C.c_uint64 * 3)(*mkn), lay, C.c_int32(bf16))
+
+    def matmul_dram_batched(self, a: int, b: int, items, mkn, bf16: bool = False) -> Out:
+        return self.matmul_dram_batched_layout(a, b, items, mkn, None, bf16)
+
+    def last_matmul_path(self) -> str:
+        return self._lib.b200_last_matmul_path(self._e).decode()
+
+    # -- element-wise (server.rs:492-566) --------------------------------------------
+    def eltwise_op_as(self, op, a: int, b: Optional[int] = None, c: Optional[int] = None, bf16: bool = False) -> Out:
+        if not isinstance(op, EltwiseOp):
+            op = EltwiseOp(*op)
+        return self._call(self._lib.b200_eltwise, C.byref(op), C.c_uint64(a), C.c_uint64(b or 0), C.c_uint64(c or 0),
+                          C.c_int32(bf16))
+
+    def eltwise_op(self, op, a, b=None, c=None) -> Out:
+        return self.eltwise_op_as(op, a, b, c, False)
+
+    def eltwise(self, kind: int, scalar: float, a: int, b: Optional[int] = None) -> Out:
+        return self.eltwise_op_as(EltwiseOp(kind, scalar, 0.0), a, b, None, False)
+
+    def eltwise_blocks_as(self, op, a, b=None, c=None, bf16: bool = False) -> Out:
+        if not isinstance(op, EltwiseOp):
+            op = EltwiseOp(*op)
+        ba = _block(a)
+        bb = _block(b) if b is not None else None
+        bc = _block(c) if c is not None else None
+        return self._call(self._lib.b200_eltwise_blocks, C.byref(op), C.byref(ba),
+                          C.byref(bb) if bb is not None else None, C.byref(bc) if bc is not None else None,
+                          C.c_int32(bf16))
+
+    def eltwise_blocks(self, op, a, b=None, c=None) -> Out:
+        return self.eltwise_blocks_as(op, a, b, c, False)
+
+    def cast_float(self, a: int, bf16: bool) -> Out:
+        return self._call(self._lib.b200_cast_float, C.c_uint64(a), C.c_int32(bf16))
+
+    def rope_blocks(self, x, cos, sin, head: int, bf16: bool = False) -> Out:
+        bx, bc, bs = _block(x), _block(cos), _block(sin)
+        return self._call(self._lib.b200_rope_blocks, C.byref(bx), C.byref(bc), C.byref(bs), C.c_uint64(head),
+                          C.c_int32(bf16))
+
+    # -- reductions (server.rs:80,399-477) ---------------------------------------------
+    def reduce(self, a: int, op: int, axis: int, then: Optional[Tuple[int, int]] = None) -> Out:
+        tk, tb = then if then else (0, 0)
+        return self._call(self._lib.b200_reduce, C.c_uint64(a), C.c_int32(op), C.c_int32(axis), C.c_uint32(tk),
+                          C.c_uint32(tb))
+
+    def sum_rows(self, a: int) -> Out:
+        return self._call(self._lib.b200_sum_rows, C.c_uint64(a))
+
+    def full_sum(self, a: int, mean: bool = False) -> Out:
+        return self._call(self._lib.b200_full_sum, C.c_uint64(a), C.c_int32(mean))
+
+    def full_reduce(self, values, dims, mean: bool) -> float:
+        a = np.ascontiguousarray(values, dtype=np.float32)
+        out = C.c_float()
+        self._check(self._lib.b200_full_reduce(self._e, _ptr(a), (C.c_uint64 * 2)(*dims), C.c_int32(mean),
+                                               C.byref(out)))
+        return out.value
+
+    def softmax_rows(self, x: int, mask: Optional[int], scale: float) -> Out:
+        return self._call(self._lib.b200_softmax_rows, C.c_uint64(x), C.c_uint64(mask or 0), C.c_float(scale))
+
+    def log_softmax_rows(self, x: int) -> Out:
+        return self._call(self._lib.b200_log_softmax_rows, C.c_uint64(x))
+
+    def rms(self, a: int, eps: float) -> Out:
+        return self._call(self._lib.b200_rms, C.c_uint64(a), C.c_float(eps))
+
+    def rms_norm_as(self, a: int, gamma: Optional[int], eps: float, bf16: bool) -> Out:
+        return self._call(self._lib.b200_rms_norm, C.c_uint64(a), C.c_uint64(gamma or 0), C.c_float(eps),
+                          C.c_int32(bf16))
+
+    def rms_norm(self, a: int, gamma: Optional[int], eps: float) -> Out:
+        return self.rms_norm_as(a, gamma, eps, False)
+
+    def add_rms_norm(self, a: int, b: int, gamma: Optional[int], eps: float):
+        out = (C.c_uint64 * 2)()
+        dims = (C.c_uint64 * 2)()
+        self._check(self._lib.b200_add_rms_norm(self._e, C.c_uint64(a), C.c_uint64(b), C.c_uint64(gamma or 0),
+                                                C.c_float(eps), out, dims))
+        d = (dims[0], dims[1])
+        return [(out[0], d), (out[1], d)]
+
+    def argmax_row(self, a: int) -> Out:
+        return self._call(self._lib.b200_argmax_row, C.c_uint64(a))
+
+    # -- indexing (server.rs:269-379,482) -----------------------------------------------
+    def select_rows(self, table: int, indices: int) -> Out:
+        return self._call(self._lib.b200_select_rows, C.c_uint64(table), C.c_uint64(indices))
+
+    def pick_columns(self, input: int, indices: int) -> Out:
+        return self._call(self._lib.b200_pick_columns, C.c_uint64(input), C.c_uint64(indices))
+
+    def scatter_add_columns(self, t: int, indices: int, value: int) -> Out:
+        return self._call(self._lib.b200_scatter_add_columns, C.c_uint64(t), C.c_uint64(indices), C.c_uint64(value))
+
+    def select_add_rows(self, t: int, indices: int, value: int) -> Out:
+        return self._call(self._lib.b200_select_add_rows, C.c_uint64(t), C.c_uint64(indices), C.c_uint64(value))
+
+    def rows_add(self, t: int, indices: Sequence[int], value: int) -> Out:
+        idx = (C.c_uint64 * max(len(indices), 1))(*indices)
+        return self._call(self._lib.b200_rows_add, C.c_uint64(t), idx, C.c_uint64(len(indices)), C.c_uint64(value))
+
+    def assign_rows(self, t: int, value: int, rows: Sequence[Tuple[int, int]]) -> Out:
+        flat = [x for p in rows for x in p]
+        arr = (C.c_uint64 * max(len(flat), 1))(*flat)
+        return self._call(self._lib.b200_assign_rows, C.c_uint64(t), C.c_uint64(value), arr, C.c_uint64(len(rows)))
+
+    def scatter_rows(self, table: int, indices: int, values: int, column: bool) -> Out:
+        return self._call(self._lib.b200_scatter_rows, C.c_uint64(table), C.c_uint64(indices), C.c_uint64(values),
+                          C.c_int32(column))
+
+    def gather_indexed(self, input: int, indices: int) -> Out:
+        return self._call(self._lib.b200_gather_indexed, C.c_uint64(input), C.c_uint64(indices))
+
+    def gather_rows(self, sources: Sequence[int], rows: Sequence[Tuple[int, int]], cols: int) -> Out:
+        src = (C.c_uint64 * max(len(sources), 1))(*sources)
+        flat = [x for p in rows for x in p]
+        arr = (C.c_uint64 * max(len(flat), 1))(*flat)
+        return self._call(self._lib.b200_gather_rows, src, C.c_uint64(len(sources)), arr, C.c_uint64(len(rows)),
+                          C.c_uint64(cols))
+
+    def slice_rows(self, a: int, first: int, rows: int) -> Out:
+        return self._call(self._lib.b200_slice_rows, C.c_uint64(a), C.c_uint64(first), C.c_uint64(rows))
+
+    def copy_blocks(self, a: int, moves, dims) -> Out:
+        n = len(moves)
+        arr = (BlockMove * max(n, 1))()
+        for i, m in enumerate(moves):
+            frm, to, ext, tr = m
+            arr[i] = BlockMove((C.c_uint64 * 2)(*frm), (C.c_uint64 * 2)(*to), (C.c_uint64 * 2)(*ext), int(tr), 0)
+        return self._call(self._lib.b200_copy_blocks, C.c_uint64(a), arr, C.c_uint64(n), (C.c_uint64 * 2)(*dims))
+
+    def repack(self, a: int, sources, dims) -> Out:
+        src = np.ascontiguousarray(sources, dtype=np.uint64).reshape(-1)
+        assert src.size == 2 * dims[0] * dims[1]
+        return self._call(self._lib.b200_repack, C.c_uint64(a), _ptr(src), (C.c_uint64 * 2)(*dims))
+
+    # -- waits and observability (lib.rs:218, server.rs:584,663) ---------------------------
+    def sync(self):
+        self._check(self._lib.b200_sync(self._e))
+
+    def set_op_label(self, label: str):
+        self._lib.b200_set_op_label(self._e, label.encode())
+
+    def device_traffic(self) -> Traffic:
+        t = Traffic()
+        self._lib.b200_traffic_get(self._e, C.byref(t))
+        return t
+
+    def last_oom(self) -> Tuple[int, int, int]:
+        o = (C.c_uint64 * 3)()
+        self._lib.b200_last_oom(self._e, o)
+        return o[0], o[1], o[2]
+
+    def timer_start(self):
+        self._check(self._lib.b200_timer_start(self._e))
+
+    def timer_stop(self) -> float:
+        ms = C.c_float()
+        self._check(self._lib.b200_timer_stop(self._e, C.byref(ms)))
+        return ms.value
+
+    def stream(self) -> int:
+        return self._lib.b200_stream(self._e)
+
+
+__all__ = ["CudaEngine", "TtError", "EltwiseOp", "Block", "BlockMove", "BlockArg", "BatchedLayout", "Traffic",
+           "load_library", "library_path", "kinds",
+           "F32", "I32", "BOOL", "BF16", "SUM", "MAX", "PROD", "ALL", "ANY", "BITOR", "SUM_I32", "PROD_I32",
+           "MIN_I32", "MAX_I32", "ROWS", "COLS"]

@@ -1,0 +1,541 @@
+"""TEST INFRASTRUCTURE, not product code: the CPU oracle.
+
+A NumPy (plus C, oracle.c) restatement of what the reference's device path is held to by
+its CPU comparison backend.  That backend (burn-flex `=0.21.0`, Cargo.toml:46) and the
+reference itself (Rust; crates.io dependencies not vendored) cannot be built or run where
+this was written, so parity against burn-flex's own output bits is UNPINNED.  What pins
+this oracle are the closed-form known-answer cases the reference's tests hold for the
+path (tests/test_oracle_kats.py lists them with file:line).
+
+Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline leg may import this.
+
+Arithmetic: IEEE-754 binary32, round to nearest even, denormals kept (what burn-flex
+does; the reference's own device flushes them and records that as its difference,
+crates/tt-tests/tests/step19_eltwise.rs:215).  Exact kinds are computed in float32 with
+separate roundings; transcendental kinds are computed in float64 and rounded once, and
+compared within the bound the reference derives for the kind (`ULP_BOUND`).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+_clib = None
+
+f32 = np.float32
+u32 = np.uint32
+
+
+# ------------------------------------------------------------------ C twin
+def build_c() -> Path:
+    out = HERE / "_build" / "liboracle.so"
+    src = HERE / "oracle.c"
+    if not out.exists() or out.stat().st_mtime < src.stat().st_mtime:
+        subprocess.run(["make", "-C", str(HERE)], check=True, capture_output=True)
+    return out
+
+
+def clib() -> C.CDLL:
+    global _clib
+    if _clib is None:
+        lib = C.CDLL(str(build_c()))
+        lib.orc_full_sum.restype = C.c_float
+        lib.orc_full_sum_f64.restype = C.c_double
+        lib.orc_bf16_round.restype = C.c_uint16
+        lib.orc_argmax.restype = C.c_int32
+        _clib = lib
+    return _clib
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+# ------------------------------------------------------------------ seeded inputs
+_GOLD = np.uint64(0x9E3779B97F4A7C15)
+
+
+def splitmix64(seed: int, tag: int, n: int) -> np.ndarray:
+    """n draws of splitmix64 started at seed ^ tag."""
+    with np.errstate(over="ignore"):
+        s0 = np.uint64((seed ^ tag) & 0xFFFFFFFFFFFFFFFF)
+        z = s0 + _GOLD * np.arange(1, n + 1, dtype=np.uint64)
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        z = z ^ (z >> np.uint64(31))
+    return z
+
+
+def uniform(seed: int, tag: int, shape, lo: float, hi: float) -> np.ndarray:
+    n = int(np.prod(shape))
+    u = (splitmix64(seed, tag, n) >> np.uint64(40)).astype(np.float32) / f32(16777216.0)
+    return (f32(lo) + (f32(hi) - f32(lo)) * u).astype(np.float32).reshape(shape)
+
+
+def normal(seed: int, tag: int, shape, sigma: float = 1.0) -> np.ndarray:
+    n = int(np.prod(shape))
+    z = splitmix64(seed, tag, 2 * n)
+    u1 = ((z[:n] >> np.uint64(40)).astype(np.float64) + 1.0) / 16777216.0
+    u2 = (z[n:] >> np.uint64(40)).astype(np.float64) / 16777216.0
+    g = np.sqrt(-2.0 * np.log(u1)) * np.cos(2.0 * np.pi * u2)
+    return (g * sigma).astype(np.float32).reshape(shape)
+
+
+def integers(seed: int, tag: int, shape, high: int) -> np.ndarray:
+    n = int(np.prod(shape))
+    return (splitmix64(seed, tag, n) % np.uint64(high)).astype(np.int32).reshape(shape)
+
+
+# ------------------------------------------------------------------ bf16
+def bf16_round_bits(x_bits: np.ndarray) -> np.ndarray:
+    """F32 bits -> BF16 bits (crates/tt-tests/tests/step270_native_bf16.rs:244-255)."""
+    x = np.asarray(x_bits, dtype=np.uint32)
+    nan = (x & u32(0x7FFFFFFF)) > u32(0x7F800000)
+    with np.errstate(over="ignore"):
+        r = np.where(nan, x | u32(0x00400000), x + u32(0x7FFF) + ((x >> u32(16)) & u32(1)))
+    r = r & u32(0xFFFF0000)
+    r = np.where((r & u32(0x7FFFFFFF)) < u32(0x00800000), r & u32(0x80000000), r)
+    return (r >> u32(16)).astype(np.uint16)
+
+
+def to_bf16(x: np.ndarray) -> np.ndarray:
+    return bf16_round_bits(np.ascontiguousarray(x, dtype=np.float32).view(np.uint32))
+
+
+def from_bf16(h: np.ndarray) -> np.ndarray:
+    return (np.asarray(h, dtype=np.uint16).astype(np.uint32) << u32(16)).view(np.float32)
+
+
+# ------------------------------------------------------------------ element-wise kinds
+# The bound, in units of u = 2^-24 relative to the true value, within which a device's
+# result of a transcendental kind must lie (crates/tt-kernels/src/sfpu/ops.rs:356-380,
+# 473-2021: exp 1.3e-7 relative = 2.2u, log 7.12u, sigmoid exp+4u, gelu 12.5u, tanh 7.5u).
+# Kinds not listed are exact: bit for bit.
+ULP_BOUND = {
+    "EXP": 2.2, "LOG": 7.12, "SIGMOID": 6.2, "SILU": 8.2, "SILU_MUL": 10.2, "SUB_EXP": 2.2, "GELU": 12.5,
+    "GELU_TANH": 12.5, "TANH": 7.5, "ERF": 8.0, "RSQRT": 4.1, "LOG1P": 8.0, "EXPM1": 8.0, "SINH": 8.0,
+    "COSH": 8.0, "ASINH": 8.0, "ACOSH": 8.0, "ATANH": 8.0, "LOG_SIGMOID": 8.0, "SIN": 8.0, "COS": 8.0, "TAN": 12.0,
+    "ATAN": 8.0, "ATAN2": 8.0, "ASIN": 8.0, "ACOS": 8.0, "POW": 16.0, "POW_S": 16.0, "POW_I": 16.0,
+    "GELU_BACKWARD": 16.0, "LOG_SIGMOID_BACKWARD": 8.2, "SIGMOID_BACKWARD": 0.0,
+}
+
+
+def _bits(x):
+    return np.ascontiguousarray(x).view(np.uint32)
+
+
+def _f(x):
+    return np.ascontiguousarray(x).view(np.float32)
+
+
+def _bool(x):
+    return x.astype(np.uint32)
+
+
+def _pos_not_nan(ub):
+    return (ub != 0) & (ub <= u32(0x7F800000))
+
+
+def _sigmoid64(x64):
+    e = np.exp(-np.abs(x64))
+    return np.where(x64 >= 0, 1.0 / (1.0 + e), e / (1.0 + e))
+
+
+def _erf64(x64):
+    from math import erf
+    return np.vectorize(erf, otypes=[np.float64])(x64)
+
+
+def eltwise(kind_name: str, a, b=None, c=None, s1: float = 0.0, s2: float = 0.0) -> np.ndarray:
+    """One element-wise kind on raw 32-bit words (any of F32 / I32 / Bool), broadcasting b
+    as NumPy does for [1,cols] / [rows,1] / a's shape.  Returns uint32 words.
+    Semantics: crates/tt-kernels/src/kind.rs:12-26, crates/tt-kernels/src/sfpu/ops.rs:24-251."""
+    ua = _bits(a)
+    ub = _bits(b) if b is not None else None
+    uc = _bits(c) if c is not None else None
+    if ub is not None and ub.shape != ua.shape:
+        if ub.ndim == 2 and ua.ndim == 2 and ub.shape[1] == ua.shape[1] and ub.shape[0] not in (1, ua.shape[0]):
+            ub = np.tile(ub, (ua.shape[0] // ub.shape[0], 1))  # whole rows repeated
+        else:
+            ub = np.broadcast_to(ub, ua.shape)
+    fa = ua.view(np.float32)
+    fb = np.ascontiguousarray(ub).view(np.float32) if ub is not None else None
+    fc = uc.view(np.float32) if uc is not None else None
+    ia = ua.view(np.int32)
+    ib = np.ascontiguousarray(ub).view(np.int32) if ub is not None else None
+    s1f, s2f = f32(s1), f32(s2)
+    s_bits = np.array([s1], dtype=np.float32).view(np.int32)[0]
+    k = kind_name
+    a64 = fa.astype(np.float64)
+    with np.errstate(all="ignore"):
+        if k in ("ADD", "ADD_ROW"): r = fa + fb
+        elif k == "SUB": r = fa - fb
+        elif k == "MUL": r = fa * fb
+        elif k == "MUL_SCALAR": r = fa * s1f
+        elif k == "ADD_SCALAR": r = fa + s1f
+        elif k == "RELU": return np.where(_pos_not_nan(ua), ua, u32(0))
+        elif k == "RELU_BACKWARD": return np.where(_pos_not_nan(ua), ub, u32(0))
+        elif k == "RECIP": r = f32(1.0) / fa
+        elif k == "DIV": r = fa / fb
+        elif k == "DIV_SCALAR": r = fa / s1f
+        elif k == "EXP": r = np.exp(a64).astype(np.float32)
+        elif k == "LOG": r = np.log(a64).astype(np.float32)
+        elif k == "BOOL_NOT": return _bool(ua == 0)
+        elif k == "BOOL_AND": return _bool((ua != 0) & (ub != 0))
+        elif k == "BOOL_OR": return _bool((ua != 0) | (ub != 0))
+        elif k == "BOOL_XOR": return _bool((ua != 0) != (ub != 0))
+        elif k == "NEG": return ua ^ u32(0x80000000)
+        elif k == "ABS": return ua & u32(0x7FFFFFFF)
+        elif k == "SIGN":
+            r = np.where(np.isnan(fa), fa, np.where(fa > 0, f32(1), np.where(fa < 0, f32(-1), f32(0))))
+        elif k == "CLAMP": r = np.where(fa < s1f, s1f, np.where(fa > s2f, s2f, fa))
+        elif k == "CLAMP_MIN": r = np.where(np.isnan(fa), s1f, np.where(np.isnan(s1f), fa, np.where(fa > s1f, fa, s1f)))
+        elif k == "CLAMP_MAX": r = np.where(np.isnan(fa), s1f, np.where(np.isnan(s1f), fa, np.where(fa < s1f, fa, s1f)))
+        elif k == "LEAKY_RELU": r = np.where(fa >= 0, fa, s1f * fa)
+        elif k == "HARD_SIGMOID":
+            t = (s1f * fa).astype(np.float32) + s2f
+            r = np.where(t < 0, f32(0), np.where(t > 1, f32(1), t))
+        elif k in ("EQ", "NE", "GT", "GE", "LT", "LE"):
+            op = {"EQ": np.equal, "NE": np.not_equal, "GT": np.greater, "GE": np.greater_equal, "LT": np.less, "LE": np.less_equal}[k]
+            return _bool(op(fa, fb))
+        elif k in ("EQ_S", "NE_S", "GT_S", "GE_S", "LT_S", "LE_S"):
+            op = {"EQ_S": np.equal, "NE_S": np.not_equal, "GT_S": np.greater, "GE_S": np.greater_equal, "LT_S": np.less, "LE_S": np.less_equal}[k]
+            return _bool(op(fa, s1f))
+        elif k == "IS_NAN": return _bool(np.isnan(fa))
+        elif k == "IS_INF": return _bool(np.isinf(fa))
+        elif k in ("MASK_FILL", "INT_MASK_FILL", "BOOL_MASK_FILL"):
+            return np.where(ub != 0, np.array([s1], dtype=np.float32).view(np.uint32)[0], ua)
+        elif k in ("MASK_WHERE", "INT_MASK_WHERE", "BOOL_MASK_WHERE"): return np.where(ub != 0, uc, ua)
+        elif k == "PRELU": r = np.where(fa >= 0, fa, fb * fa)
+        elif k == "FILL": r = np.full(fa.shape, s1f, dtype=np.float32)
+        elif k == "SQRT": r = np.sqrt(fa)
+        elif k == "RSQRT": r = (1.0 / np.sqrt(a64)).astype(np.float32)
+        elif k == "LOG1P": r = np.log1p(a64).astype(np.float32)
+        elif k == "POW": r = np.power(a64, fb.astype(np.float64)).astype(np.float32)
+        elif k == "POW_S": r = np.power(a64, float(s1f)).astype(np.float32)
+        elif k == "POW_I": r = np.power(a64, ib.astype(np.float32).astype(np.float64)).astype(np.float32)
+        elif k in ("I32_TO_F32", "BOOL_TO_F32"): r = ia.astype(np.float32)
+        elif k == "BOOL_TO_I32": return ua.copy()
+        elif k in ("INDEX_TO_I32", "F32_TO_I32"):
+            t = np.trunc(a64)
+            t = np.where(np.isnan(t), 0.0, np.clip(t, -2147483648.0, 2147483647.0))
+            return t.astype(np.int64).astype(np.int32).view(np.uint32)
+        elif k == "INT_ABS": return np.where(ia < 0, (u32(0) - ua), ua)
+        elif k == "EXPM1": r = np.expm1(a64).astype(np.float32)
+        elif k == "SIGMOID": r = _sigmoid64(a64).astype(np.float32)
+        elif k == "SIGMOID_BACKWARD": r = ((fb * fa).astype(np.float32) * (f32(1) - fa).astype(np.float32)).astype(np.float32)
+        elif k == "TANH": r = np.tanh(a64).astype(np.float32)
+        elif k == "ERF": r = _erf64(a64).astype(np.float32)
+        elif k == "GELU": r = (0.5 * a64 * (1.0 + _erf64(a64 / np.sqrt(2.0)))).astype(np.float32)
+        elif k == "GELU_TANH":
+            r = (0.5 * a64 * (1.0 + np.tanh(np.sqrt(2.0 / np.pi) * (a64 + 0.044715 * a64 ** 3)))).astype(np.float32)
+        elif k == "GELU_BACKWARD":
+            cdf = 0.5 * (1.0 + _erf64(a64 / np.sqrt(2.0)))
+            pdf = np.exp(-0.5 * a64 * a64) / np.sqrt(2.0 * np.pi)
+            r = (fb.astype(np.float64) * (cdf + a64 * pdf)).astype(np.float32)
+        elif k == "SINH": r = np.sinh(a64).astype(np.float32)
+        elif k == "COSH": r = np.cosh(a64).astype(np.float32)
+        elif k == "ASINH": r = np.arcsinh(a64).astype(np.float32)
+        elif k == "ACOSH": r = np.arccosh(a64).astype(np.float32)
+        elif k == "ATANH": r = np.arctanh(a64).astype(np.float32)
+        elif k == "LOG_SIGMOID": r = (-(np.maximum(-a64, 0.0) + np.log1p(np.exp(-np.abs(a64))))).astype(np.float32)
+        elif k == "LOG_SIGMOID_BACKWARD": r = (fb.astype(np.float64) * _sigmoid64(-a64)).astype(np.float32)
+        elif k == "SIN": r = np.sin(a64).astype(np.float32)
+        elif k == "COS": r = np.cos(a64).astype(np.float32)
+        elif k == "TAN": r = np.tan(a64).astype(np.float32)
+        elif k == "ATAN": r = np.arctan(a64).astype(np.float32)
+        elif k == "ATAN2": r = np.arctan2(a64, fb.astype(np.float64)).astype(np.float32)
+        elif k == "ASIN": r = np.arcsin(a64).astype(np.float32)
+        elif k == "ACOS": r = np.arccos(a64).astype(np.float32)
+        elif k == "REM": r = np.fmod((np.fmod(fa, fb) + fb).astype(np.float32), fb)
+        elif k == "REM_S": r = np.fmod((np.fmod(fa, s1f) + s1f).astype(np.float32), s1f)
+        elif k == "ROUND": r = np.rint(fa)
+        elif k == "FLOOR": r = np.floor(fa)
+        elif k == "CEIL": r = np.ceil(fa)
+        elif k == "TRUNC": r = np.trunc(fa)
+        elif k == "POW2_FLOOR": return ua & u32(0x7F800000)
+        elif k == "POW2_FLOOR_INV":
+            e = ua & u32(0x7F800000)
+            return np.where(e >= u32(0x7F000000), u32(0x00800000), u32(0x7F000000) - e)
+        elif k == "INT_ADD": return ua + ub
+        elif k == "INT_SUB": return ua - ub
+        elif k == "INT_MUL": return ua * ub
+        elif k == "INT_AND": return ua & ub
+        elif k == "INT_OR": return ua | ub
+        elif k == "INT_XOR": return ua ^ ub
+        elif k == "INT_SHL": return ua << (ub & u32(31))
+        elif k == "INT_SHR": return (ia >> (ub & u32(31)).astype(np.int32)).view(np.uint32)
+        elif k in ("INT_EQ", "INT_NE", "INT_GT", "INT_GE", "INT_LT", "INT_LE"):
+            op = {"INT_EQ": np.equal, "INT_NE": np.not_equal, "INT_GT": np.greater, "INT_GE": np.greater_equal, "INT_LT": np.less, "INT_LE": np.less_equal}[k]
+            return _bool(op(ia, ib))
+        elif k == "INT_NOT": return ~ua
+        elif k in ("INT_ADD_S", "INT_SUB_S", "INT_MUL_S", "INT_AND_S", "INT_OR_S", "INT_XOR_S", "INT_SHL_S", "INT_SHR_S",
+                   "INT_EQ_S", "INT_NE_S", "INT_GT_S", "INT_GE_S", "INT_LT_S", "INT_LE_S", "INT_DIV_S", "INT_REM_S"):
+            sb = np.full(ua.shape, s_bits, dtype=np.int32).view(np.uint32)
+            return eltwise(k[:-2], ua, sb)
+        elif k in ("INT_DIV", "INT_REM"):
+            d = ib.astype(np.int64)
+            safe = np.where(d == 0, 1, d)
+            q = np.trunc(ia.astype(np.int64) / safe).astype(np.int64)  # truncating division
+            q = (np.abs(ia.astype(np.int64)) // np.abs(safe)) * np.sign(ia.astype(np.int64)) * np.sign(safe)
+            rem = ia.astype(np.int64) - q * safe
+            res = q if k == "INT_DIV" else rem
+            return np.where(d == 0, 0, res).astype(np.int64).astype(np.uint32)
+        elif k == "ADD_RELU":
+            t = (fa + fb).astype(np.float32).view(np.uint32)
+            return np.where(_pos_not_nan(t), t, u32(0))
+        elif k == "SILU": r = (a64 * _sigmoid64(a64)).astype(np.float32)
+        elif k == "SILU_MUL": r = ((a64 * _sigmoid64(a64)).astype(np.float32) * fb).astype(np.float32)
+        elif k == "SUB_EXP": r = np.exp((fa - fb).astype(np.float32).astype(np.float64)).astype(np.float32)
+        elif k == "MUL_ADD": r = (fc + (fa * fb).astype(np.float32)).astype(np.float32)
+        elif k == "SCALE_MASK_FILL":
+            return np.where(ub != 0, np.array([s2], dtype=np.float32).view(np.uint32)[0], (fa * s1f).astype(np.float32).view(np.uint32))
+        else:
+            raise KeyError(k)
+    return np.ascontiguousarray(r, dtype=np.float32).view(np.uint32)
+
+
+def ulp_error(got_bits: np.ndarray, want_bits: np.ndarray) -> float:
+    """Largest |got - want| in units of 2^-24 |want| (the reference's `u`), NaN == NaN,
+    infinities equal when identical."""
+    g = got_bits.view(np.float32).astype(np.float64).ravel()
+    w = want_bits.view(np.float32).astype(np.float64).ravel()
+    same = (got_bits.ravel() == want_bits.ravel()) | (np.isnan(g) & np.isnan(w))
+    with np.errstate(all="ignore"):
+        scale = np.maximum(np.abs(w), 2.0 ** -125) * 2.0 ** -24
+        err = np.where(same, 0.0, np.abs(g - w) / scale)
+    err = np.where(np.isfinite(err), err, np.inf)
+    return float(err.max()) if err.size else 0.0
+
+
+# ------------------------------------------------------------------ products
+def gemm_f32(a: np.ndarray, b: np.ndarray, a_t=False, b_t=False) -> np.ndarray:
+    """F32 product, k ascending per element (C, OpenMP).  a, b are the STORED matrices."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    b = np.ascontiguousarray(b, dtype=np.float32)
+    m, k = (a.shape[1], a.shape[0]) if a_t else a.shape
+    k2, n = (b.shape[1], b.shape[0]) if b_t else b.shape
+    assert k == k2
+    c = np.empty((m, n), dtype=np.float32)
+    clib().orc_gemm_f32(_p(a), C.c_int(a_t), _p(b), C.c_int(b_t), _p(c), C.c_uint64(m), C.c_uint64(k), C.c_uint64(n))
+    return c
+
+
+def gemm_truth(a: np.ndarray, b: np.ndarray, a_t=False, b_t=False):
+    """(truth, S): the F64-accumulated product of the exact inputs and S = |A| |B|
+    (crates/tt-tests/tests/step11_burn.rs:15-17,101-111)."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    b = np.ascontiguousarray(b, dtype=np.float32)
+    A = a.T.astype(np.float64) if a_t else a.astype(np.float64)
+    B = b.T.astype(np.float64) if b_t else b.astype(np.float64)
+    return A @ B, np.abs(A) @ np.abs(B)
+
+
+def gemm_rel_error(c: np.ndarray, truth: np.ndarray, s: np.ndarray):
+    """(max |C - truth| / S, max |C - truth| / |truth| over |truth| > 1e-3 S)."""
+    d = np.abs(c.astype(np.float64) - truth)
+    with np.errstate(all="ignore"):
+        e_s = np.where(s > 0, d / s, d)
+        big = np.abs(truth) > 1e-3 * s
+        e_t = np.where(big, d / np.abs(truth), 0.0)
+    return float(e_s.max()) if e_s.size else 0.0, float(e_t.max()) if e_t.size else 0.0
+
+
+def gemm_bf16(a_bits: np.ndarray, b_bits: np.ndarray, a_t=False, b_t=False, out_bf16=True):
+    """BF16 product: the F32-or-better product of the exact BF16 inputs, rounded once
+    (crates/tt-tests/tests/step270_native_bf16.rs:462).  Returns (bits or f32, truth, S)."""
+    a = from_bf16(a_bits)
+    b = from_bf16(b_bits)
+    truth, s = gemm_truth(a, b, a_t, b_t)
+    c32 = truth.astype(np.float32)
+    return (to_bf16(c32) if out_bf16 else c32), truth, s
+
+
+# ------------------------------------------------------------------ reductions
+def sum_rows_in_order(a: np.ndarray) -> np.ndarray:
+    """[rows, cols] -> [1, cols]: a left fold from +0.0 (crates/tt-kernels/src/sfpu/reduce.rs:31-38)."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    acc = np.zeros(a.shape[1], dtype=np.float32)
+    for r in range(a.shape[0]):
+        acc = (acc + a[r]).astype(np.float32)
+    return acc.reshape(1, -1)
+
+
+def _order_key(u):
+    return np.where(u & u32(0x80000000), ~u, u | u32(0x80000000))
+
+
+def reduce(a_bits: np.ndarray, op: str, axis: int) -> np.ndarray:
+    """`ReduceOp` over `Axis` (crates/tt-kernels/src/sfpu/reduce.rs:56,117) on raw words.
+    axis 0: over rows -> [1, cols]; axis 1: over columns -> [rows, 1].  Sum over columns and
+    Prod are returned as the F64-accumulated value rounded once (compare with a bound)."""
+    u = _bits(a_bits)
+    fa = u.view(np.float32)
+    ia = u.view(np.int32)
+    keep = dict(axis=axis, keepdims=True)
+    if op == "SUM":
+        if axis == 0:
+            return sum_rows_in_order(fa).view(np.uint32)
+        return fa.astype(np.float64).sum(**keep).astype(np.float32).view(np.uint32)
+    if op == "MAX":
+        k = _order_key(u)
+        idx = np.expand_dims(np.argmax(k, axis=axis), axis)
+        return np.take_along_axis(u, idx, axis)
+    if op == "PROD":
+        return fa.astype(np.float64).prod(**keep).astype(np.float32).view(np.uint32)
+    if op == "ALL": return (u != 0).all(**keep).astype(np.uint32)
+    if op == "ANY": return (u != 0).any(**keep).astype(np.uint32)
+    if op == "BITOR": return np.bitwise_or.reduce(u, **keep)
+    if op == "SUM_I32": return ia.astype(np.int64).sum(**keep).astype(np.uint32)
+    if op == "PROD_I32":
+        out = np.ones(1, dtype=np.uint64)
+        p = np.ones([1 if i == axis else s for i, s in enumerate(u.shape)], dtype=np.uint64)
+        for i in range(u.shape[axis]):
+            p = (p * np.take(u, [i], axis=axis).astype(np.uint64)) & np.uint64(0xFFFFFFFF)
+        return p.astype(np.uint32)
+    if op == "MIN_I32": return ia.min(**keep).view(np.uint32)
+    if op == "MAX_I32": return ia.max(**keep).view(np.uint32)
+    raise KeyError(op)
+
+
+def sum_bound(a: np.ndarray, axis=None) -> np.ndarray:
+    """2 gamma_{n-1} sum|x| (crates/tt-tests/tests/step63_burn_full_reduce.rs:104-122; for one
+    axis crates/tt-tests/tests/step31_reduce.rs header: 2 (n-1) u sum|x|)."""
+    a64 = np.abs(np.asarray(a, dtype=np.float64))
+    n = a64.size if axis is None else a64.shape[axis]
+    u = 2.0 ** -24
+    g = (n - 1) * u / (1 - (n - 1) * u) if n > 1 else 0.0
+    s = a64.sum() if axis is None else a64.sum(axis=axis, keepdims=True)
+    return 2 * g * s + 2.0 ** -149
+
+
+def full_sum(a: np.ndarray, mean=False):
+    """(F64 truth rounded once, bound) of Burn's float_sum / float_mean
+    (crates/burn-tt/src/ops.rs:3246-3398)."""
+    a = np.asarray(a, dtype=np.float32)
+    t = a.astype(np.float64).sum()
+    b = sum_bound(a)
+    if mean:
+        n = f32(a.size)
+        return f32(f32(t) / n), b / a.size + abs(t / a.size) * 2.0 ** -23
+    return f32(t), b
+
+
+def full_sum_reference_order(a: np.ndarray) -> np.float32:
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return f32(clib().orc_full_sum(_p(a), C.c_uint64(a.shape[0]), C.c_uint64(a.shape[1])))
+
+
+def softmax_rows(x: np.ndarray, mask=None, scale: float = 1.0, log_form=False) -> np.ndarray:
+    """softmax(scale x, masked) per row (crates/tt-kernels/src/sfpu/softmax.rs:1-45; the unfused
+    composition crates/burn-tt/src/ops.rs:5133-5165).  C, OpenMP."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty_like(x)
+    if mask is not None:
+        mask = np.ascontiguousarray(mask, dtype=np.uint32)
+    clib().orc_softmax_rows(_p(x), _p(mask) if mask is not None else None, C.c_uint64(mask.shape[0] if mask is not None else 1),
+                            C.c_float(scale), C.c_int(log_form), _p(out), C.c_uint64(x.shape[0]), C.c_uint64(x.shape[1]))
+    return out
+
+
+def softmax_bound(n: int) -> float:
+    """Relative bound of a softmax entry: 2 EXP_BOUND + (n-1) u + 2u, doubled for the
+    oracle's own rounding (crates/tt-tests/tests/step32_burn_softmax.rs:94-95)."""
+    u = 2.0 ** -24
+    return 2 * (2 * 1.3e-7 + (n - 1) * u + 2 * u)
+
+
+def argmax_rows(a: np.ndarray) -> np.ndarray:
+    """First maximum, first NaN wins (crates/tt-tests/tests/step211_argmax_row.rs:8-10)."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    out = np.empty((a.shape[0], 1), dtype=np.int32)
+    for r in range(a.shape[0]):
+        out[r, 0] = clib().orc_argmax(_p(a[r]), C.c_uint64(a.shape[1]))
+    return out
+
+
+def rms(a: np.ndarray, eps: float) -> np.ndarray:
+    """sqrt(mean(x x) + eps): MUL, sum, MUL_SCALAR(1/n), ADD_SCALAR(eps), SQRT
+    (crates/tt-kernels/src/sfpu/norm.rs:1-25,45-60).  The sum in F64, rounded once."""
+    a = np.asarray(a, dtype=np.float32)
+    sq = (a * a).astype(np.float32)
+    ss = sq.astype(np.float64).sum(axis=1, keepdims=True).astype(np.float32)
+    inv = f32(1.0) / f32(a.shape[1])
+    return np.sqrt(((ss * inv).astype(np.float32) + f32(eps)).astype(np.float32))
+
+
+def rms_norm(a: np.ndarray, gamma, eps: float) -> np.ndarray:
+    """x / stat [* gamma]: DIV by the statistic's column, then MUL by gamma's row
+    (crates/tt-kernels/src/session.rs:8676-8682)."""
+    a = np.asarray(a, dtype=np.float32)
+    r = (a / rms(a, eps)).astype(np.float32)
+    if gamma is not None:
+        r = (r * np.asarray(gamma, dtype=np.float32).reshape(1, -1)).astype(np.float32)
+    return r
+
+
+def rope(x: np.ndarray, cos: np.ndarray, sin: np.ndarray, head: int) -> np.ndarray:
+    """x cos + swap_halves(x) sin per head, the product, the product and the sum
+    (crates/tt-kernels/src/tensor.rs:5545-5552; crates/tt-models/src/rope.rs:151-161)."""
+    x = np.asarray(x, dtype=np.float32)
+    rows, cols = x.shape
+    xs = x.reshape(rows, cols // head, head)
+    sw = np.concatenate([xs[..., head // 2:], xs[..., :head // 2]], axis=-1).reshape(rows, cols)
+    def table(t):
+        t = np.asarray(t, dtype=np.float32)
+        if t.shape[1] == head:
+            t = np.tile(t, (1, cols // head))
+        if t.shape[0] != rows:
+            t = np.tile(t, (rows // t.shape[0], 1))
+        return t
+    p1 = (x * table(cos)).astype(np.float32)
+    p2 = (sw * table(sin)).astype(np.float32)
+    return (p1 + p2).astype(np.float32)
+
+
+def rope_tables(positions: int, head: int, theta: float):
+    """cos, sin' = [-sin, sin] tables [positions, head] (crates/tt-models/src/rope.rs:19-60)."""
+    i = np.arange(head // 2, dtype=np.float64)
+    freq = (theta ** (-2.0 * i / head)).astype(np.float32)
+    ang = (np.arange(positions, dtype=np.float32)[:, None] * freq[None, :]).astype(np.float32)
+    cos = np.cos(ang.astype(np.float64)).astype(np.float32)
+    sin = np.sin(ang.astype(np.float64)).astype(np.float32)
+    return np.concatenate([cos, cos], axis=1), np.concatenate([-sin, sin], axis=1)
+
+
+# ------------------------------------------------------------------ indexing (bit moves)
+def select_rows(table: np.ndarray, idx: np.ndarray) -> np.ndarray:
+    return np.ascontiguousarray(table)[np.asarray(idx).ravel()]
+
+
+def pick_columns(x: np.ndarray, idx: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x)
+    return x[np.arange(x.shape[0]), np.asarray(idx).ravel()].reshape(-1, 1)
+
+
+def scatter_add_columns(t: np.ndarray, idx: np.ndarray, v: np.ndarray) -> np.ndarray:
+    out = np.array(t, dtype=np.float32, copy=True)
+    r = np.arange(out.shape[0])
+    c = np.asarray(idx).ravel()
+    out[r, c] = (out[r, c] + np.asarray(v, dtype=np.float32).ravel()).astype(np.float32)
+    return out
+
+
+def select_add_rows(t: np.ndarray, idx: np.ndarray, value: np.ndarray) -> np.ndarray:
+    """Rows added in index order, duplicates in order (crates/burn-tt/src/server.rs:358)."""
+    out = np.array(t, dtype=np.float32, copy=True)
+    value = np.asarray(value, dtype=np.float32)
+    for i, r in enumerate(np.asarray(idx).ravel()):
+        out[r] = (out[r] + value[i]).astype(np.float32)
+    return out
+
+
+def scatter_rows(table: np.ndarray, idx: np.ndarray, values: np.ndarray) -> np.ndarray:
+    out = np.array(table, copy=True)
+    for i, r in enumerate(np.asarray(idx).ravel()):
+        out[r] = values[i]
+    return out

@@ -1,0 +1,219 @@
+"""Products through the C ABI against the oracle, in the shape of
+crates/tt-tests/tests/step11_burn.rs (exact on small integers :131-168, a bound on random
+floats :101-111, a negative control :197-220) and step270_native_bf16.rs:462 (a BF16 product
+is the F32 product rounded once)."""
+import numpy as np
+import pytest
+
+from metalium_rs_b200 import BatchedLayout, CudaEngine, TtError
+from oracle import oracle as orc
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-5   # north star: F32 ops within 1e-5 relative (normalised by S = |A||B|)
+BF16_TOL = 1e-2  # north star: BF16 GEMM within 1e-2 relative, FP32 accumulate
+
+
+def up(eng, x, bf16=False):
+    return eng.upload_bf16(orc.to_bf16(x), *x.shape) if bf16 else eng.upload(x, *x.shape)
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+@pytest.mark.parametrize("sa,sb", [((32, 32), (32, 32)), ((13, 47), (47, 29)), ((1, 64), (64, 96)), ((128, 256), (256, 384)),
+                                   ((200, 136), (136, 328))])
+def test_small_integer_products_are_bit_exact(eng, sa, sb, bf16):
+    rng = np.random.default_rng(0xB11)
+    a, b = H.small_ints(rng, sa), H.small_ints(rng, sb)
+    ia, ib = up(eng, a, bf16), up(eng, b, bf16)
+    out, dims = (eng.matmul_dram_bf16 if bf16 else eng.matmul_dram)(ia, False, ib, False)
+    assert dims == (sa[0], sb[1])
+    want = (a.astype(np.int64) @ b.astype(np.int64)).astype(np.float32)
+    got = orc.from_bf16(eng.download_bf16(out)) if bf16 else eng.download(out)
+    if bf16:
+        want = orc.from_bf16(orc.to_bf16(want))
+    assert np.array_equal(got, want)
+    for i in (ia, ib, out):
+        eng.free(i)
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("mkn", [(64, 784, 128), (64, 128, 10), (784, 64, 128), (300, 200, 100), (512, 512, 512)])
+def test_f32_products_hold_f32_accuracy(eng, mkn, ta, tb):
+    m, k, n = mkn
+    a = orc.uniform(0xC0F2, 1, (k, m) if ta else (m, k), -1, 1)
+    b = orc.uniform(0xC0F2, 2, (n, k) if tb else (k, n), -1, 1)
+    ia, ib = up(eng, a), up(eng, b)
+    out, dims = eng.matmul_dram(ia, ta, ib, tb)
+    assert dims == (m, n)
+    got = eng.download(out)
+    truth, s = orc.gemm_truth(a, b, ta, tb)
+    e_s, e_t = orc.gemm_rel_error(got, truth, s)
+    cpu = orc.gemm_f32(a, b, ta, tb)
+    c_s, _ = orc.gemm_rel_error(cpu, truth, s)
+    assert e_s <= F32_TOL, (e_s, c_s)
+    assert e_s <= 4 * c_s + 2 ** -22  # never far from the CPU restatement's own rounding
+    for i in (ia, ib, out):
+        eng.free(i)
+
+
+def test_f32_negative_control(eng):  # step11_burn.rs:197-220: a BF16-grade product must fail the F32 bound
+    a = orc.uniform(0xC0F2, 3, (256, 256), -1, 1)
+    b = orc.uniform(0xC0F2, 4, (256, 256), -1, 1)
+    truth, s = orc.gemm_truth(a, b)
+    lo = orc.from_bf16(orc.to_bf16(a)).astype(np.float64) @ orc.from_bf16(orc.to_bf16(b)).astype(np.float64)
+    e_s, _ = orc.gemm_rel_error(lo, truth, s)
+    assert e_s > F32_TOL
+
+
+TC_SHAPES = [(128, 64, 128), (256, 512, 384), (384, 192, 640), (200, 136, 328), (1024, 1024, 1024), (64, 64, 64), (4096, 576, 576),
+             (130, 72, 1536)]
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("mkn", TC_SHAPES)
+def test_bf16_products_take_the_tensor_cores_and_round_once(eng, mkn, ta, tb):
+    m, k, n = mkn
+    a = orc.to_bf16(orc.uniform(0xC0F2, 5, (k, m) if ta else (m, k), -1, 1))
+    b = orc.to_bf16(orc.uniform(0xC0F2, 6, (n, k) if tb else (k, n), -1, 1))
+    ia = eng.upload_bf16(a, *a.shape)
+    ib = eng.upload_bf16(b, *b.shape)
+    out, dims = eng.matmul_dram_bf16(ia, ta, ib, tb)
+    assert dims == (m, n)
+    aligned = (a.shape[1] % 8 == 0) and (b.shape[1] % 8 == 0)
+    assert eng.last_matmul_path() == ("tcgen05" if aligned else "simt")
+    got_bits = eng.download_bf16(out)
+    want_bits, truth, s = orc.gemm_bf16(a, b, ta, tb)
+    got = orc.from_bf16(got_bits)
+    e_s, e_t = orc.gemm_rel_error(got, truth, s)
+    assert e_s <= BF16_TOL and e_t <= BF16_TOL, (e_s, e_t)
+    # the F32 product rounded once: at most one BF16 step from the F64 truth rounded once
+    step = np.abs(got_bits.astype(np.int32) - want_bits.astype(np.int32))
+    assert step.max() <= 1, f"{int((step > 1).sum())} elements are more than one BF16 step off"
+    assert (step == 0).mean() > 0.95
+    # F32 result of BF16 operands
+    o32, _ = eng.matmul_dram(ia, ta, ib, tb)
+    e32, _ = orc.gemm_rel_error(eng.download(o32), truth, s)
+    assert e32 <= 1e-5
+    for i in (ia, ib, out, o32):
+        eng.free(i)
+
+
+def test_tensor_core_and_simt_paths_agree(lib):
+    a = orc.to_bf16(orc.normal(0xC0F5, 1, (512, 256)))
+    b = orc.to_bf16(orc.normal(0xC0F5, 2, (256, 320)))
+    res = []
+    for mode in (1, 2):
+        with CudaEngine(0, bf16_matmul_mode=mode) as e:
+            ia, ib = e.upload_bf16(a, 512, 256), e.upload_bf16(b, 256, 320)
+            out, _ = e.matmul_dram(ia, False, ib, False)
+            res.append(e.download(out))
+            assert e.last_matmul_path() == ("simt" if mode == 1 else "tcgen05")
+    truth, s = orc.gemm_truth(orc.from_bf16(a), orc.from_bf16(b))
+    for r in res:
+        assert orc.gemm_rel_error(r, truth, s)[0] <= 1e-6
+
+
+def test_the_tensor_core_only_mode_refuses_what_it_cannot_take(lib):
+    with CudaEngine(0, bf16_matmul_mode=2) as e:
+        a = e.upload_bf16(np.zeros((13, 47), np.uint16), 13, 47)
+        b = e.upload_bf16(np.zeros((47, 29), np.uint16), 47, 29)
+        with pytest.raises(TtError) as ei:
+            e.matmul_dram_bf16(a, False, b, False)
+        assert ei.value.status == 2
+
+
+def test_mismatched_inner_dimensions_are_refused(eng):
+    a, b = eng.upload(np.zeros((4, 5), np.float32), 4, 5), eng.upload(np.zeros((6, 4), np.float32), 6, 4)
+    with pytest.raises(TtError):
+        eng.matmul_dram(a, False, b, False)
+    out, dims = eng.matmul_dram(a, True, b, True)  # [5,4] x [4,6]
+    assert dims == (5, 6)
+    for i in (a, b, out):
+        eng.free(i)
+
+
+def test_host_staged_matmul(eng):  # server.rs:70
+    a, b = orc.uniform(1, 1, (33, 65), -1, 1), orc.uniform(1, 2, (65, 17), -1, 1)
+    got = eng.matmul(a, b, (33, 65, 17))
+    truth, s = orc.gemm_truth(a, b)
+    assert orc.gemm_rel_error(got, truth, s)[0] <= F32_TOL
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_batched_products_read_blocks_where_they_lie(eng, bf16):
+    # heads side by side in one buffer: Q [t, heads*hd] blocks at column h*hd; K^T read as a
+    # transposed block (server.rs:229; ops.rs:3008-3081)
+    t, heads, hd = 128, 4, 64
+    q = orc.normal(0xC0F5, 3, (t, heads * hd))
+    kx = orc.normal(0xC0F5, 4, (t, heads * hd))
+    if bf16:
+        q, kx = orc.from_bf16(orc.to_bf16(q)), orc.from_bf16(orc.to_bf16(kx))
+    iq, ik = up(eng, q, bf16), up(eng, kx, bf16)
+    items = [(((0, h * hd), False), ((0, h * hd), True)) for h in range(heads)]
+    out, dims = eng.matmul_dram_batched(iq, ik, items, (t, hd, t), bf16=False)
+    assert dims == (heads * t, t)
+    got = eng.download(out)
+    for h in range(heads):
+        truth, s = orc.gemm_truth(q[:, h * hd:(h + 1) * hd], kx[:, h * hd:(h + 1) * hd], False, True)
+        assert orc.gemm_rel_error(got[h * t:(h + 1) * t], truth, s)[0] <= F32_TOL, h
+    if bf16:
+        assert eng.last_matmul_path() == "tcgen05"
+    # P.V: [t,t] blocks stacked in rows x V blocks by column
+    p = eng.download(out)
+    if bf16:
+        p = orc.from_bf16(orc.to_bf16(p))
+    ip = up(eng, p, bf16)
+    items2 = [(((h * t, 0), False), ((0, h * hd), False)) for h in range(heads)]
+    o2, dims2 = eng.matmul_dram_batched(ip, ik, items2, (t, t, hd), bf16=False)
+    assert dims2 == (heads * t, hd)
+    g2 = eng.download(o2)
+    for h in range(heads):
+        truth, s = orc.gemm_truth(p[h * t:(h + 1) * t], kx[:, h * hd:(h + 1) * hd])
+        assert orc.gemm_rel_error(g2[h * t:(h + 1) * t], truth, s)[0] <= F32_TOL, h
+    for i in (iq, ik, out, ip, o2):
+        eng.free(i)
+
+
+def test_unstacked_layout_places_each_product_on_a_tile_row(eng):  # server.rs:3749-3754
+    m, k, n, items_n = 20, 40, 33, 3
+    a = orc.uniform(2, 1, (items_n * 32, k), -1, 1)
+    b = orc.uniform(2, 2, (k, items_n * n), -1, 1)
+    ia, ib = up(eng, a), up(eng, b)
+    items = [(((i * 32, 0), False), ((0, i * n), False)) for i in range(items_n)]
+    out, dims = eng.matmul_dram_batched_layout(ia, ib, items, (m, k, n), BatchedLayout(1, 0))
+    assert dims == (items_n * 32, n)
+    got = eng.download(out)
+    for i in range(items_n):
+        truth, s = orc.gemm_truth(a[i * 32:i * 32 + m], b[:, i * n:(i + 1) * n])
+        assert orc.gemm_rel_error(got[i * 32:i * 32 + m], truth, s)[0] <= F32_TOL
+    st, dims = eng.matmul_dram_batched(ia, ib, items, (m, k, n))
+    assert dims == (items_n * m, n)
+    assert np.array_equal(eng.download(st), np.concatenate([got[i * 32:i * 32 + m] for i in range(items_n)]))
+    for i in (ia, ib, out, st):
+        eng.free(i)
+
+
+def test_bf16_product_at_4096_by_properties(eng):
+    # Too large for the F64 oracle in seconds: check the row-sum identity C 1 = A (B 1) and
+    # 64 sampled elements against F64 dot products.
+    n = 4096
+    a = orc.to_bf16(orc.uniform(0xC0F2, 7, (n, n), -1, 1))
+    b = orc.to_bf16(orc.uniform(0xC0F2, 8, (n, n), -1, 1))
+    ia, ib = eng.upload_bf16(a, n, n), eng.upload_bf16(b, n, n)
+    out, _ = eng.matmul_dram(ia, False, ib, False)  # F32 result keeps the identity tight
+    assert eng.last_matmul_path() == "tcgen05"
+    c = eng.download(out).astype(np.float64)
+    af, bf = orc.from_bf16(a).astype(np.float64), orc.from_bf16(b).astype(np.float64)
+    rows = af @ bf.sum(1)
+    s_rows = np.abs(af) @ np.abs(bf).sum(1)
+    assert np.max(np.abs(c.sum(1) - rows) / s_rows) <= 1e-6
+    rng = np.random.default_rng(5)
+    for i, j in zip(rng.integers(0, n, 64), rng.integers(0, n, 64)):
+        t = af[i] @ bf[:, j]
+        s = np.abs(af[i]) @ np.abs(bf[:, j])
+        assert abs(c[i, j] - t) <= 1e-6 * s
+    ob, _ = eng.matmul_dram_bf16(ia, False, ib, False)
+    assert np.array_equal(eng.download_bf16(ob), orc.to_bf16(c.astype(np.float32)))
+    for i in (ia, ib, out, ob):
+        eng.free(i)
