@@ -70,7 +70,7 @@ def test_float_kind_against_oracle(eng, name, shape):
     assert dims == shape
     bound = orc.ULP_BOUND.get(name)
     if bound is None or bound == 0.0:
-        nan_both = np.isnan(got.view(np.float32)) & np.isnan(want.view(np.float32)) if name not in ("NEG", "ABS") else False
+        nan_both = (np.isnan(got.view(np.float32)) & np.isnan(want.view(np.float32))) if name not in ("NEG", "ABS") else np.zeros(got.shape, bool)
         bad = (got != want) & ~nan_both
         assert not bad.any(), f"{name}: {int(bad.sum())} words differ, first at {np.argwhere(bad)[0]}: " \
                               f"{got[bad][0]:#x} vs {want[bad][0]:#x} (a={a[bad][0]!r})"

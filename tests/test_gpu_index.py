@@ -13,8 +13,8 @@ def special_table(rows, cols, seed):
     t = orc.normal(seed, 1, (rows, cols))
     bits = t.view(np.uint32)
     bits[0, 0] = 0x80000000      # -0.0 survives a gather (the GPU moves bits; burn-flex's answer)
-    bits[1, 1] = 0x7FC0BEEF      # a NaN payload
-    bits[2, 2] = 0x00000001      # a denormal
+    bits[1, min(1, cols - 1)] = 0x7FC0BEEF      # a NaN payload
+    bits[2, min(2, cols - 1)] = 0x00000001      # a denormal
     return t
 
 
@@ -64,7 +64,9 @@ def test_pick_columns_and_its_backward(eng):  # burn-tt/src/ops.rs:1001,1043
     sc, _ = eng.scatter_add_columns(z, ii, ig)
     assert np.array_equal(eng.download_bits(sc), orc.scatter_add_columns(np.zeros((64, 10), np.float32), idx, g).view(np.uint32))
     sc2, _ = eng.scatter_add_columns(ix, ii, ig)
-    assert np.array_equal(eng.download_bits(sc2), orc.scatter_add_columns(x, idx, g).view(np.uint32))
+    got2, want2 = eng.download_bits(sc2), orc.scatter_add_columns(x, idx, g).view(np.uint32)
+    both_nan = np.isnan(got2.view(np.float32)) & np.isnan(want2.view(np.float32))  # NaN + g: the payload is the adder's
+    assert np.array_equal(got2[~both_nan], want2[~both_nan])
     gi, _ = eng.gather_indexed(ix, ii)
     assert np.array_equal(eng.download_bits(gi), eng.download_bits(out))
     for i in (ix, ii, ig, out, z, sc, sc2, gi):

@@ -87,10 +87,11 @@ def test_bf16_products_take_the_tensor_cores_and_round_once(eng, mkn, ta, tb):
     got = orc.from_bf16(got_bits)
     e_s, e_t = orc.gemm_rel_error(got, truth, s)
     assert e_s <= BF16_TOL and e_t <= BF16_TOL, (e_s, e_t)
-    # the F32 product rounded once: at most one BF16 step from the F64 truth rounded once
+    # the F32 product rounded once: within one BF16 step of the truth plus the F32 sum's own
+    # rounding (which matters only where the sum cancels), and the same bits almost everywhere
     step = np.abs(got_bits.astype(np.int32) - want_bits.astype(np.int32))
-    assert step.max() <= 1, f"{int((step > 1).sum())} elements are more than one BF16 step off"
-    assert (step == 0).mean() > 0.95
+    assert np.all(np.abs(got.astype(np.float64) - truth) <= 2.0 ** -8 * np.abs(truth) + 1e-6 * s)
+    assert (step == 0).mean() > 0.95 and (step <= 1).mean() > 0.999
     # F32 result of BF16 operands
     o32, _ = eng.matmul_dram(ia, ta, ib, tb)
     e32, _ = orc.gemm_rel_error(eng.download(o32), truth, s)
