@@ -198,8 +198,8 @@ def run_single(args):
     value = flops / (ms_per_step * 1e-3) / 1e12
 
     # end to end through the C ABI with host buffers
-    e2e_steps = max(1, min(args.steps, 5))
-    for _ in range(2):
+    e2e_steps = 0 if args.no_e2e else max(1, min(args.steps, 5))
+    for _ in range(2 if e2e_steps else 0):
         x, y = eng.upload_ptr(a_host.data_ptr(), n, n, 3), eng.upload_ptr(b_host.data_ptr(), n, n, 3)
         o, _ = eng.matmul_dram_bf16(x, False, y, False)
         eng.download_into(o, c_host.data_ptr(), n * n, 2)
@@ -213,11 +213,13 @@ def run_single(args):
         eng.download_into(o, c_host.data_ptr(), n * n, 2)
         for i in (x, y, o):
             eng.free(i)
-    e2e_ms = eng.timer_stop() / e2e_steps
-    wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    e2e_ms = max(e2e_ms, wall_ms)
-    e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": 2 * n * n * 2,
-           "d2h_bytes_per_step": n * n * 2, "ms_per_step": e2e_ms}
+    e2e = None
+    if e2e_steps:
+        e2e_ms = eng.timer_stop() / e2e_steps
+        wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+        e2e_ms = max(e2e_ms, wall_ms)
+        e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": 2 * n * n * 2,
+               "d2h_bytes_per_step": n * n * 2, "ms_per_step": e2e_ms}
 
     pk, which = peaks()
     peak = float(pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
@@ -331,6 +333,7 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--extras", action="store_true", help="also time the rest of the sweep and the memory-bound suite")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--size", type=int, default=0, help="override the N=1 problem size (profiling on a small case)")
     args = ap.parse_args()
     if args.impl == "reference":
