@@ -166,6 +166,23 @@ int32_t b200_reduce(b200_engine*, b200_buffer a, int32_t op, int32_t axis, uint3
 int32_t b200_sum_rows(b200_engine*, b200_buffer a, b200_buffer* out, uint64_t out_dims[2]);
 /* Burn's `float_sum` / `float_mean` of a resident tensor (ops.rs:3246-3398): [1,1]. */
 int32_t b200_full_sum(b200_engine*, b200_buffer a, int32_t mean, b200_buffer* out, uint64_t out_dims[2]);
+/* No counterpart in the reference.  The full sum (or mean) of `n` F32 values for a caller
+ * that must not allocate device memory -- a host whose GPU memory belongs to another
+ * runtime's fixed arenas, or code on a path where an allocation would stall the device.
+ * `device_values` and `device_out` (one float) are the caller's device memory; the call
+ * launches on `cuda_stream` (a cudaStream_t; NULL is the default stream) of the current
+ * device and returns without waiting.  It calls no cudaMalloc or cudaFree: the per-block
+ * partial sums go to a fixed 4,736-byte array inside the library image, which every GPU
+ * that loads the library holds until exit.
+ *  - n may not exceed 2^31 (B200_UNSUPPORTED, text through b200_last_error(NULL, ..)).
+ *  - The first call on each device looks the array's address up; make that call before
+ *    any stream capture begins.
+ *  - All calls share the array.  Nothing in it needs clearing between calls (every
+ *    partial is rewritten before it is read), but two calls that overlap on one GPU --
+ *    different streams, or different threads -- race on it: order them.
+ *  - The result has the same bits as b200_full_sum's on the same values. */
+int32_t b200_full_sum_noalloc(const float* device_values, uint64_t n, int32_t mean, float* device_out,
+                              void* cuda_stream);
 /* `full_reduce(values, dims, mean)`: host values in, scalar out, device arithmetic. */
 int32_t b200_full_reduce(b200_engine*, const float* values, const uint64_t dims[2], int32_t mean, float* out);
 /* `softmax_rows(x, mask, scale)`: mask 0 = none; Bool words, read for rows r % mask_rows. */

@@ -354,6 +354,10 @@ int index_buf(b200_engine* e, b200_buffer id, Buf** b, const char* what) {
 
 }  // namespace
 
+namespace b200 {
+void set_global_error(const char* text) { g_create_error = text ? text : ""; }
+}  // namespace b200
+
 extern "C" {
 
 int32_t b200_engine_create(int32_t device_ordinal, const b200_config* cfg, b200_engine** out) {

@@ -12,6 +12,10 @@
 //
 // Compiled with -fmad=false so every rounding the reference names is kept.
 #include <float.h>
+#include <stdio.h>
+
+#include <mutex>
+#include <string>
 
 #include "eltwise_ev.cuh"
 #include "kernels.h"
@@ -472,6 +476,76 @@ cudaError_t launch_full_sum(const float* a, uint64_t n, int mean, float* scratch
   full_sum_stage2<<<1, FULL_THREADS, 0, s>>>(scratch, FULL_BLOCKS, n, mean, out);
   return cudaGetLastError();
 }
+
+}  // namespace b200
+
+// ---- full sum for callers that cannot allocate -------------------------------------
+// Some hosts of this library must not call cudaMalloc at all: a process whose device memory
+// is owned and budgeted by another runtime (a serving stack that hands out fixed arenas and
+// treats any allocation of its own as a leak), or code that runs where allocating would
+// synchronise the device at the wrong moment.  For them the two-stage sum's per-block
+// partials live in a fixed array inside the library image instead of in a buffer the
+// engine allocates.  Every GPU that loads the library holds these 4,736 bytes until exit.
+namespace {
+constexpr uint64_t NOALLOC_MAX_ELEMS = 1ull << 31;  // the largest input accepted (8 GiB of F32)
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static __device__ __align__(256) float g_full_sum_partials[b200::FULL_BLOCKS];
+float* g_partials_addr[NOALLOC_MAX_DEVICES] = {};
+std::mutex g_partials_lock;
+}  // namespace
+
+// No counterpart in the reference.  See include/b200tt.h for the contract.
+extern "C" __attribute__((visibility("default")))
+int32_t b200_full_sum_noalloc(const float* device_values, uint64_t n, int32_t mean, float* device_out,
+                              void* cuda_stream) {
+  if (!device_values || !device_out) {
+    b200::set_global_error("full_sum_noalloc: a null device pointer");
+    return 2;
+  }
+  if (n > NOALLOC_MAX_ELEMS) {
+    char msg[160];
+    snprintf(msg, sizeof msg, "full_sum_noalloc: %llu elements exceed the limit of %llu",
+             (unsigned long long)n, (unsigned long long)NOALLOC_MAX_ELEMS);
+    b200::set_global_error(msg);
+    return 2;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
+    b200::set_global_error("full_sum_noalloc: no current CUDA device");
+    return 3;
+  }
+  float* partials = nullptr;
+  {
+    // Set-up, once per device, with that device current: in host code the array's name is
+    // only a stand-in, so ask the runtime for the address the kernels must be given.
+    std::lock_guard<std::mutex> hold(g_partials_lock);
+    if (!g_partials_addr[dev]) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_full_sum_partials);
+      if (e != cudaSuccess || !p) {
+        cudaGetLastError();
+        b200::set_global_error((std::string("full_sum_noalloc: cudaGetSymbolAddress: ") + cudaGetErrorString(e)).c_str());
+        return 3;
+      }
+      g_partials_addr[dev] = static_cast<float*>(p);
+    }
+    partials = g_partials_addr[dev];
+  }
+  // Stage 1 writes every one of the partials before stage 2 reads them, so nothing has to
+  // start at zero and the last call's contents do not matter.
+  cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+  b200::full_sum_stage1<<<b200::FULL_BLOCKS, b200::FULL_THREADS, 0, s>>>(device_values, n, partials);
+  b200::full_sum_stage2<<<1, b200::FULL_THREADS, 0, s>>>(partials, b200::FULL_BLOCKS, n, mean, device_out);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    b200::set_global_error((std::string("full_sum_noalloc: launch: ") + cudaGetErrorString(e)).c_str());
+    return 3;
+  }
+  return 0;
+}
+
+namespace b200 {
 
 cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t mask_rows, float scale,
                                 int log_form, float* out, uint64_t rows, uint64_t cols,

@@ -107,4 +107,7 @@ bool gemm_tc_supported(const GemmArgs& g, const char** why);
 cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int* err_word,
                            cudaStream_t stream);
 
+// Text for `b200_last_error(NULL, ...)`: failures of calls that take no engine.
+void set_global_error(const char* text);
+
 }  // namespace b200
