@@ -11,6 +11,7 @@
 //  - argmax: first maximum, first NaN wins (crates/tt-tests/tests/step211_argmax_row.rs:8-10).
 //
 // Compiled with -fmad=false so every rounding the reference names is kept.
+#include <cooperative_groups.h>
 #include <float.h>
 #include <stdio.h>
 
@@ -327,6 +328,107 @@ softmax_block_kernel(const float* __restrict__ x, const uint32_t* __restrict__ m
   }
 }
 
+// Wide rows: a thread-block cluster a row.  Each of the C CTAs (256 threads) keeps its
+// share of the row in registers and the CTAs exchange their partial maximum and sum through
+// distributed shared memory, combined in rank order so every CTA holds the same bits.
+// Several clusters are resident per SM at different phases, so one row's loads overlap
+// another's exponentials and stores; a single 1024-thread block a row cannot do that.
+template <int VPT>
+__global__ void __launch_bounds__(256, 4)
+softmax_cluster_kernel(const float* __restrict__ x, const uint32_t* __restrict__ mask, uint64_t mask_rows,
+                       float scale, int log_form, float* __restrict__ out, uint64_t rows, uint32_t cols) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned csize = cluster.num_blocks();
+  const unsigned crank = cluster.block_rank();
+  __shared__ float sm[32];
+  __shared__ float xchg[2][2];  // [row parity][0 max, 1 sum], read by the peers
+  const uint32_t n4 = cols / 4;
+  const uint32_t share = (n4 + csize - 1) / csize;
+  const uint32_t first = crank * share;
+  const uint32_t last = (first + share < n4) ? first + share : n4;
+  const bool has_scale = scale != 1.0f;
+  const uint64_t n_clusters = gridDim.x / csize;
+  int par = 0;
+  for (uint64_t row = blockIdx.x / csize; row < rows; row += n_clusters, par ^= 1) {
+    const float4* xr = reinterpret_cast<const float4*>(x + row * cols);
+    const uint4* mr = mask ? reinterpret_cast<const uint4*>(mask + (row % mask_rows) * cols) : nullptr;
+    float4 v[VPT];
+    float m = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      const uint32_t i = first + threadIdx.x + u * 256;
+      if (i < last) {
+        float4 t = __ldcs(xr + i);
+        uint4 k = mr ? __ldg(mr + i) : make_uint4(0, 0, 0, 0);
+        t.x = scaled_masked(t.x, k.x, scale, has_scale);
+        t.y = scaled_masked(t.y, k.y, scale, has_scale);
+        t.z = scaled_masked(t.z, k.z, scale, has_scale);
+        t.w = scaled_masked(t.w, k.w, scale, has_scale);
+        v[u] = t;
+        m = nan_max(m, nan_max(nan_max(t.x, t.y), nan_max(t.z, t.w)));
+      }
+    }
+    m = block_max<256>(m, sm);
+    if (csize > 1) {
+      if (threadIdx.x == 0) xchg[par][0] = m;
+      cluster.sync();
+      m = *cluster.map_shared_rank(&xchg[par][0], 0);
+      for (unsigned r = 1; r < csize; ++r) m = nan_max(m, *cluster.map_shared_rank(&xchg[par][0], r));
+    }
+    m = (m < -FLT_MAX) ? -FLT_MAX : m;
+    float s = 0.f;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      const uint32_t i = first + threadIdx.x + u * 256;
+      if (i < last) {
+        float4 t = v[u];
+        if (log_form) {
+          t.x = t.x - m; t.y = t.y - m; t.z = t.z - m; t.w = t.w - m;
+          v[u] = t;
+          s = s + ((expf(t.x) + expf(t.y)) + (expf(t.z) + expf(t.w)));
+        } else {
+          t.x = expf(t.x - m); t.y = expf(t.y - m); t.z = expf(t.z - m); t.w = expf(t.w - m);
+          v[u] = t;
+          s = s + ((t.x + t.y) + (t.z + t.w));
+        }
+      }
+    }
+    s = block_add<256>(s, sm);
+    if (csize > 1) {
+      if (threadIdx.x == 0) xchg[par][1] = s;
+      cluster.sync();
+      s = *cluster.map_shared_rank(&xchg[par][1], 0);
+      for (unsigned r = 1; r < csize; ++r) s = s + *cluster.map_shared_rank(&xchg[par][1], r);
+    }
+    float4* orow = reinterpret_cast<float4*>(out + row * cols);
+    if (log_form) {
+      const float l = logf(s);
+#pragma unroll
+      for (int u = 0; u < VPT; ++u) {
+        const uint32_t i = first + threadIdx.x + u * 256;
+        if (i < last) {
+          float4 t = v[u];
+          t.x = t.x - l; t.y = t.y - l; t.z = t.z - l; t.w = t.w - l;
+          __stcs(orow + i, t);
+        }
+      }
+    } else {
+      s = (s < FLT_MIN) ? FLT_MIN : s;
+#pragma unroll
+      for (int u = 0; u < VPT; ++u) {
+        const uint32_t i = first + threadIdx.x + u * 256;
+        if (i < last) {
+          float4 t = v[u];
+          t.x = t.x / s; t.y = t.y / s; t.z = t.z / s; t.w = t.w / s;
+          __stcs(orow + i, t);
+        }
+      }
+    }
+  }
+  if (csize > 1) cluster.sync();  // no CTA leaves while a peer may still read its exchange slots
+}
+
 // Any width: a block a row, three passes over global memory (the second and third
 // mostly from L2).  Rows too short or ragged for the register kernel, or too long.
 __global__ void __launch_bounds__(256)
@@ -558,16 +660,31 @@ cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t m
 #define SM_LAUNCH(T, V)                                                                         \
   softmax_block_kernel<T, V><<<(unsigned)(rows < (148ull * (2048 / T)) ? rows : 148ull * (2048 / T)), \
                                T, 0, s>>>(x, mask, mask_rows, scale, log_form, out, rows, (uint32_t)cols)
-  if (al && cols % 4 == 0 && cols >= 128 && n4 <= 1024 * 8) {
+  if (al && cols % 4 == 0 && cols >= 128 && n4 <= 1024) {
     if (n4 <= 32) SM_LAUNCH(32, 1);
     else if (n4 <= 64) SM_LAUNCH(64, 1);
     else if (n4 <= 128) SM_LAUNCH(128, 1);
     else if (n4 <= 256) SM_LAUNCH(128, 2);
     else if (n4 <= 512) SM_LAUNCH(256, 2);
     else if (n4 <= 1024) SM_LAUNCH(256, 4);
-    else if (n4 <= 2048) SM_LAUNCH(512, 4);
-    else if (n4 <= 4096) SM_LAUNCH(1024, 4);
-    else SM_LAUNCH(1024, 8);
+  } else if (al && cols % 4 == 0 && n4 <= 2048ull * 8) {
+    unsigned csize = 1;
+    while ((n4 + csize - 1) / csize > 2048) csize <<= 1;
+    const uint32_t share = (uint32_t)((n4 + csize - 1) / csize);
+    uint64_t clusters = rows < (148ull * 4) / csize ? rows : (148ull * 4) / csize;
+    if (clusters == 0) clusters = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(clusters * csize), 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    const uint32_t cols32 = (uint32_t)cols;
+    if (share <= 1024) return cudaLaunchKernelEx(&cfg, softmax_cluster_kernel<4>, x, mask, mask_rows, scale, log_form, out, rows, cols32);
+    return cudaLaunchKernelEx(&cfg, softmax_cluster_kernel<8>, x, mask, mask_rows, scale, log_form, out, rows, cols32);
   } else {
     softmax_stream_kernel<<<(unsigned)grid, 256, 0, s>>>(x, mask, mask_rows, scale, log_form, out, rows, cols);
   }

@@ -1,0 +1,71 @@
+"""The column-sharded product's host logic on two CPU ranks (gloo): the partition is the
+reference's (crates/tt-kernels/src/shard.rs:398-405), and slices gathered and laid side by side
+equal the whole product bit for bit, as the reference's gate claims for its chips
+(crates/tt-tests/tests/step14_shard.rs:56-121).  The slice products here are NumPy stand-ins for
+the engine call; the collective and the layout code are the ones the GPU path runs."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from metalium_rs_b200 import sharded
+
+
+def test_partition_is_whole_tiles_in_order():
+    assert sharded.partition(16384, 8) == [(i * 2048, (i + 1) * 2048) for i in range(8)]
+    assert sharded.partition(100, 2) == [(0, 64), (64, 100)]
+    assert sharded.partition(57344, 4)[3] == (43008, 57344)
+    assert sharded.partition(64, 4) == [(0, 32), (32, 64), (64, 64), (64, 64)]  # trailing ranks idle
+    for n, g in ((8192, 2), (28672, 8), (1000, 3)):
+        parts = sharded.partition(n, g)
+        assert parts[0][0] == 0 and parts[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(parts, parts[1:]))
+        assert all(lo % 32 == 0 for lo, _ in parts)
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(7)  # the same A and B on every rank
+        m, k, n = 48, 40, 128
+        a = rng.integers(-7, 8, (m, k)).astype(np.float32)
+        b = rng.integers(-7, 8, (k, n)).astype(np.float32)
+        lo, hi = sharded.partition(n, world)[rank]
+        local = torch.from_numpy(a @ b[:, lo:hi])          # K whole: the same sums as one device
+        staged = sharded.gather_columns(local, world)
+        full = sharded.interleave(staged, n)
+        q.put((rank, bool(np.array_equal(full.numpy(), a @ b)), tuple(staged.shape)))
+        # a rank that fails before the collective is seen by the others as an error, not a hang
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+@pytest.mark.timeout(120)
+def test_two_ranks_gather_the_whole_product_bit_for_bit():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=90) for _ in procs]
+    for p in procs:
+        p.join(30)
+        assert p.exitcode == 0
+    assert sorted(r[0] for r in res) == [0, 1]
+    assert all(r[1] for r in res)
+    assert all(r[2] == (2, 48, 64) for r in res)
