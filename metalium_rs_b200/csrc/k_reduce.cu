@@ -14,6 +14,7 @@
 #include <cooperative_groups.h>
 #include <float.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <mutex>
 #include <string>
@@ -226,14 +227,16 @@ full_sum_stage2(const float* __restrict__ partial, int count, uint64_t n, int me
 __device__ __forceinline__ float nan_max(float a, float b) {
   return (a != a) ? a : ((b != b) ? b : fmaxf(a, b));
 }
+// The maximum ignores NaNs (fmaxf): a NaN in a row reaches every output of the row anyway,
+// through exp(NaN - m) and the sum, which is what a NaN-propagating maximum would give.
 template <int THREADS> __device__ __forceinline__ float block_max(float v, float* sm) {
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = nan_max(v, __shfl_xor_sync(0xffffffffu, v, o));
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   if constexpr (THREADS == 32) return v;
   if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
   __syncthreads();
   float t = sm[0];
-  for (int w = 1; w < THREADS / 32; ++w) t = nan_max(t, sm[w]);
+  for (int w = 1; w < THREADS / 32; ++w) t = fmaxf(t, sm[w]);
   __syncthreads();
   return t;
 }
@@ -272,13 +275,15 @@ softmax_block_kernel(const float* __restrict__ x, const uint32_t* __restrict__ m
       const uint32_t i = threadIdx.x + u * THREADS;
       if (i < n4) {
         float4 t = __ldcs(xr + i);
-        uint4 k = mr ? __ldg(mr + i) : make_uint4(0, 0, 0, 0);
-        t.x = scaled_masked(t.x, k.x, scale, has_scale);
-        t.y = scaled_masked(t.y, k.y, scale, has_scale);
-        t.z = scaled_masked(t.z, k.z, scale, has_scale);
-        t.w = scaled_masked(t.w, k.w, scale, has_scale);
+        if (mr || has_scale) {
+          uint4 k = mr ? __ldg(mr + i) : make_uint4(0, 0, 0, 0);
+          t.x = scaled_masked(t.x, k.x, scale, has_scale);
+          t.y = scaled_masked(t.y, k.y, scale, has_scale);
+          t.z = scaled_masked(t.z, k.z, scale, has_scale);
+          t.w = scaled_masked(t.w, k.w, scale, has_scale);
+        }
         v[u] = t;
-        m = nan_max(m, nan_max(nan_max(t.x, t.y), nan_max(t.z, t.w)));
+        m = fmaxf(m, fmaxf(fmaxf(t.x, t.y), fmaxf(t.z, t.w)));
       }
     }
     m = block_max<THREADS>(m, sm);
@@ -315,12 +320,13 @@ softmax_block_kernel(const float* __restrict__ x, const uint32_t* __restrict__ m
       }
     } else {
       s = (s < FLT_MIN) ? FLT_MIN : s;
+      const float inv = 1.0f / s;  // one division a row, then products: 1.5 u against DIV's 0.5 u
 #pragma unroll
       for (int u = 0; u < VPT; ++u) {
         const uint32_t i = threadIdx.x + u * THREADS;
         if (i < n4) {
           float4 t = v[u];
-          t.x = t.x / s; t.y = t.y / s; t.z = t.z / s; t.w = t.w / s;
+          t.x = t.x * inv; t.y = t.y * inv; t.z = t.z * inv; t.w = t.w * inv;
           __stcs(orow + i, t);
         }
       }
@@ -333,8 +339,8 @@ softmax_block_kernel(const float* __restrict__ x, const uint32_t* __restrict__ m
 // distributed shared memory, combined in rank order so every CTA holds the same bits.
 // Several clusters are resident per SM at different phases, so one row's loads overlap
 // another's exponentials and stores; a single 1024-thread block a row cannot do that.
-template <int VPT>
-__global__ void __launch_bounds__(256, 4)
+template <int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
 softmax_cluster_kernel(const float* __restrict__ x, const uint32_t* __restrict__ mask, uint64_t mask_rows,
                        float scale, int log_form, float* __restrict__ out, uint64_t rows, uint32_t cols) {
   namespace cg = cooperative_groups;
@@ -357,30 +363,32 @@ softmax_cluster_kernel(const float* __restrict__ x, const uint32_t* __restrict__
     float m = -INFINITY;
 #pragma unroll
     for (int u = 0; u < VPT; ++u) {
-      const uint32_t i = first + threadIdx.x + u * 256;
+      const uint32_t i = first + threadIdx.x + u * THREADS;
       if (i < last) {
         float4 t = __ldcs(xr + i);
-        uint4 k = mr ? __ldg(mr + i) : make_uint4(0, 0, 0, 0);
-        t.x = scaled_masked(t.x, k.x, scale, has_scale);
-        t.y = scaled_masked(t.y, k.y, scale, has_scale);
-        t.z = scaled_masked(t.z, k.z, scale, has_scale);
-        t.w = scaled_masked(t.w, k.w, scale, has_scale);
+        if (mr || has_scale) {
+          uint4 k = mr ? __ldg(mr + i) : make_uint4(0, 0, 0, 0);
+          t.x = scaled_masked(t.x, k.x, scale, has_scale);
+          t.y = scaled_masked(t.y, k.y, scale, has_scale);
+          t.z = scaled_masked(t.z, k.z, scale, has_scale);
+          t.w = scaled_masked(t.w, k.w, scale, has_scale);
+        }
         v[u] = t;
-        m = nan_max(m, nan_max(nan_max(t.x, t.y), nan_max(t.z, t.w)));
+        m = fmaxf(m, fmaxf(fmaxf(t.x, t.y), fmaxf(t.z, t.w)));
       }
     }
-    m = block_max<256>(m, sm);
+    m = block_max<THREADS>(m, sm);
     if (csize > 1) {
       if (threadIdx.x == 0) xchg[par][0] = m;
       cluster.sync();
       m = *cluster.map_shared_rank(&xchg[par][0], 0);
-      for (unsigned r = 1; r < csize; ++r) m = nan_max(m, *cluster.map_shared_rank(&xchg[par][0], r));
+      for (unsigned r = 1; r < csize; ++r) m = fmaxf(m, *cluster.map_shared_rank(&xchg[par][0], r));
     }
     m = (m < -FLT_MAX) ? -FLT_MAX : m;
     float s = 0.f;
 #pragma unroll
     for (int u = 0; u < VPT; ++u) {
-      const uint32_t i = first + threadIdx.x + u * 256;
+      const uint32_t i = first + threadIdx.x + u * THREADS;
       if (i < last) {
         float4 t = v[u];
         if (log_form) {
@@ -394,7 +402,7 @@ softmax_cluster_kernel(const float* __restrict__ x, const uint32_t* __restrict__
         }
       }
     }
-    s = block_add<256>(s, sm);
+    s = block_add<THREADS>(s, sm);
     if (csize > 1) {
       if (threadIdx.x == 0) xchg[par][1] = s;
       cluster.sync();
@@ -406,7 +414,7 @@ softmax_cluster_kernel(const float* __restrict__ x, const uint32_t* __restrict__
       const float l = logf(s);
 #pragma unroll
       for (int u = 0; u < VPT; ++u) {
-        const uint32_t i = first + threadIdx.x + u * 256;
+        const uint32_t i = first + threadIdx.x + u * THREADS;
         if (i < last) {
           float4 t = v[u];
           t.x = t.x - l; t.y = t.y - l; t.z = t.z - l; t.w = t.w - l;
@@ -415,12 +423,13 @@ softmax_cluster_kernel(const float* __restrict__ x, const uint32_t* __restrict__
       }
     } else {
       s = (s < FLT_MIN) ? FLT_MIN : s;
+      const float inv = 1.0f / s;
 #pragma unroll
       for (int u = 0; u < VPT; ++u) {
-        const uint32_t i = first + threadIdx.x + u * 256;
+        const uint32_t i = first + threadIdx.x + u * THREADS;
         if (i < last) {
           float4 t = v[u];
-          t.x = t.x / s; t.y = t.y / s; t.z = t.z / s; t.w = t.w / s;
+          t.x = t.x * inv; t.y = t.y * inv; t.z = t.z * inv; t.w = t.w * inv;
           __stcs(orow + i, t);
         }
       }
@@ -441,7 +450,7 @@ softmax_stream_kernel(const float* __restrict__ x, const uint32_t* __restrict__ 
     const uint32_t* mr = mask ? mask + (row % mask_rows) * cols : nullptr;
     float m = -INFINITY;
     for (uint64_t i = threadIdx.x; i < cols; i += 256)
-      m = nan_max(m, scaled_masked(xr[i], mr ? mr[i] : 0u, scale, has_scale));
+      m = fmaxf(m, scaled_masked(xr[i], mr ? mr[i] : 0u, scale, has_scale));
     m = block_max<256>(m, sm);
     m = (m < -FLT_MAX) ? -FLT_MAX : m;
     float s = 0.f;
@@ -667,15 +676,22 @@ cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t m
     else if (n4 <= 256) SM_LAUNCH(128, 2);
     else if (n4 <= 512) SM_LAUNCH(256, 2);
     else if (n4 <= 1024) SM_LAUNCH(256, 4);
-  } else if (al && cols % 4 == 0 && n4 <= 2048ull * 8) {
+  } else if (al && cols % 4 == 0 && n4 > 2048 && n4 <= 8192) {
+    // Measured on a B200: for rows this wide one 1024-thread block a row beats splitting the
+    // row over a cluster (the cluster barriers cost more than the lost overlap).
+    if (n4 <= 4096) SM_LAUNCH(1024, 4);
+    else SM_LAUNCH(1024, 8);
+  } else if (al && cols % 4 == 0 && n4 <= 4096ull * 8) {
+    // n4 in (1024, 2048]: one 256-thread block a row, four resident per SM.
+    // n4 in (8192, 32768]: 2..8 blocks of 512 threads a row, exchanging max and sum through
+    // distributed shared memory.
+    const int threads = n4 <= 2048 ? 256 : 512;
     unsigned csize = 1;
-    while ((n4 + csize - 1) / csize > 2048) csize <<= 1;
-    const uint32_t share = (uint32_t)((n4 + csize - 1) / csize);
-    uint64_t clusters = rows < (148ull * 4) / csize ? rows : (148ull * 4) / csize;
-    if (clusters == 0) clusters = 1;
+    while ((n4 + csize - 1) / csize > (uint64_t)threads * 8) csize <<= 1;
+    uint64_t clusters = rows < (1ull << 20) ? rows : (1ull << 20);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(clusters * csize), 1, 1);
-    cfg.blockDim = dim3(256, 1, 1);
+    cfg.blockDim = dim3(threads, 1, 1);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
@@ -683,8 +699,9 @@ cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t m
     attr[0].val.clusterDim.x = csize; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
     const uint32_t cols32 = (uint32_t)cols;
-    if (share <= 1024) return cudaLaunchKernelEx(&cfg, softmax_cluster_kernel<4>, x, mask, mask_rows, scale, log_form, out, rows, cols32);
-    return cudaLaunchKernelEx(&cfg, softmax_cluster_kernel<8>, x, mask, mask_rows, scale, log_form, out, rows, cols32);
+    if (threads == 256)
+      return cudaLaunchKernelEx(&cfg, softmax_cluster_kernel<256, 8>, x, mask, mask_rows, scale, log_form, out, rows, cols32);
+    return cudaLaunchKernelEx(&cfg, softmax_cluster_kernel<512, 8>, x, mask, mask_rows, scale, log_form, out, rows, cols32);
   } else {
     softmax_stream_kernel<<<(unsigned)grid, 256, 0, s>>>(x, mask, mask_rows, scale, log_form, out, rows, cols);
   }

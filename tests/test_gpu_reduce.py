@@ -127,7 +127,7 @@ def test_full_sum_is_the_same_bits_twice(eng):
         eng.free(i)
 
 
-@pytest.mark.parametrize("shape", [(256, 10), (70, 120), (40, 400), (64, 10), (5, 7), (16, 2048), (8, 4096), (3, 32768), (2, 40000), (9, 1000), (6, 8196), (4, 65536), (2, 70000), (5, 12288)])
+@pytest.mark.parametrize("shape", [(256, 10), (70, 120), (40, 400), (64, 10), (5, 7), (16, 2048), (8, 4096), (3, 32768), (2, 40000), (9, 1000), (6, 8196), (4, 65536), (2, 70000), (5, 12288), (3, 131072), (2, 140000)])
 def test_softmax_rows_within_the_reference_bound(eng, shape):  # step32_burn_softmax.rs:51,94-95
     x = orc.uniform(0x50, 1, shape, -4, 4)
     ix = eng.upload(x, *shape)
