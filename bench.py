@@ -235,7 +235,9 @@ def run_single(args):
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
             "validated": {"samples": 64, "max_err_over_S": worst}}
     if args.extras:
-        line["extras"] = extras(eng)
+        from metalium_rs_b200 import CudaEngine as _E
+        with _E(0) as auto_eng:  # automatic path choice: small and ragged products take the SIMT kernel
+            line["extras"] = extras(auto_eng)
     if not args.no_cpu:
         line["cpu_baseline"] = cpu_gemm_baseline()
     print(json.dumps(line))
@@ -317,7 +319,68 @@ def extras(eng):
     sb = 2 * 4096 * 32768 * 4
     out["suite"]["softmax_4096x32768"] = {"ms": ms, "gbs": sb / ms / 1e6, "frac_of_measured_hbm": sb / ms / 1e6 / hbm}
     eng.free(sx)
+    out["callers"] = callers(eng, timed)
     return out
+
+
+def callers(eng, timed):
+    """The callers either side of the kernels: the MLP training step (launch-bound: reported as
+    latency and launches), the SmolLM2-135M-shape prefill (tokens/s) and the attention products."""
+    from metalium_rs_b200 import I32, workloads as W
+    res = {}
+    rng = np.random.default_rng(0xC0F1)
+    k1, k2 = 1 / np.sqrt(784), 1 / np.sqrt(128)
+    u = lambda shape, k: (rng.random(shape, dtype=np.float32) * 2 - 1) * np.float32(k)
+    mlp = W.MlpStep(eng, u((784, 128), k1), u((128,), k1), u((128, 10), k2), u((10,), k2))
+    x = eng.upload(rng.standard_normal((64, 784), dtype=np.float32), 64, 784)
+    y = eng.upload_bits(rng.integers(0, 10, (64, 1)).astype(np.int32).view(np.uint32), 64, 1, I32)
+    losses = []
+
+    def step():
+        o = mlp.step(x, y, 64)
+        losses.append(o["loss"])
+    l0 = eng.device_traffic().launches
+    step()
+    per = eng.device_traffic().launches - l0
+    ms = timed(step, reps=50, warm=5)
+    first = float(eng.download(losses[0])[0, 0]); last = float(eng.download(losses[-1])[0, 0])
+    for i in losses:
+        eng.free(i)
+    res["mlp_step_64x784x128x10"] = {"ms": ms, "launches_per_step": int(per), "loss_first": first, "loss_last": last}
+
+    cfg = W.LlamaConfig()
+    batch, seq = 8, 512
+    model = W.LlamaPrefill(eng, cfg, W.llama_weights(cfg), batch, seq)
+    ids = eng.upload_bits(rng.integers(0, cfg.vocab, (1, batch * seq)).astype(np.int32).view(np.uint32), 1, batch * seq, I32)
+    outs = []
+
+    def fwd():
+        lg, am = model.forward(ids)
+        outs.append((lg, am))
+    l0 = eng.device_traffic().launches
+    fwd()
+    per = eng.device_traffic().launches - l0
+    ms = timed(fwd, reps=5, warm=2)
+    a0 = eng.download_bits(outs[0][1]).ravel().tolist(); a1 = eng.download_bits(outs[-1][1]).ravel().tolist()
+    for lg, am in outs:
+        eng.free(lg); eng.free(am)
+    fl = model.flops()
+    res["smollm2_135m_prefill_8x512"] = {"ms": ms, "tok_per_s": batch * seq / (ms * 1e-3), "launches": int(per),
+                                         "tflops": fl / ms / 1e9, "argmax_stable": a0 == a1, "next_tokens": a1}
+
+    bh, t, d = 256, 2048, 128
+    bf = lambda: ((rng.standard_normal((bh * t, d), dtype=np.float32)).view(np.uint32) >> 16).astype(np.uint16)
+    q, k, v = (eng.upload_bf16(bf(), bh * t, d) for _ in range(3))
+
+    def att():
+        o = W.attention_products(eng, q, k, v, bh, t, d)
+        eng.free(o)
+    ms = timed(att, reps=3, warm=1)
+    res["attention_16x16x2048x128"] = {"ms": ms, "tflops": 2 * 2.0 * bh * t * t * d / ms / 1e9,
+                                       "materialised_scores_gb": bh * t * t * 4 / 1e9}
+    for i in (q, k, v, x, y, ids):
+        eng.free(i)
+    return res
 
 
 def run_multi(args):

@@ -1,0 +1,241 @@
+"""The callers of the hot path, restated as sequences of `Engine` calls.
+
+Each function issues the ops the reference's Burn models send to the backend, in their
+order, and nothing else: no arithmetic happens on the host.
+  - `MlpStep`: the MNIST-shaped MLP training step (crates/tt-tests/tests/step12_mnist.rs:212-222;
+    op sequence crates/burn-tt/src/ops.rs:5153-5158 (log-softmax), :1001/:1043 (gather and its
+    backward), :5006-5028 (linear backward), :5174 (relu backward)).
+  - `LlamaPrefill`: a decoder prefill with the SmolLM2-135M architecture
+    (crates/tt-models/src/llama.rs:371-507 `Layer::forward`, :798 `forward`, :1055 `head`;
+    crates/tt-models/src/rope.rs:129).
+  - `attention_products`: Q K^T, row softmax, P V on rank-4 views
+    (crates/burn-tt/src/ops.rs:4447 `attention`, the unfused path :4573-4589).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import numpy as np
+
+from . import BF16, BOOL, COLS, F32, I32, SUM, EltwiseOp, kinds
+
+
+def _bf16(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even BF16 bits of an F32 array (host-side weight preparation)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    r = u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))
+    return (r >> np.uint32(16)).astype(np.uint16)
+
+
+# ------------------------------------------------------------------------- config 1
+class MlpStep:
+    """x [n,784] -> Linear(784,h) -> ReLU -> Linear(h,10) -> softmax cross-entropy, backward, SGD.
+    Weights live on the device and are replaced by their updates each step."""
+
+    def __init__(self, eng, w1, b1, w2, b2, lr=0.01, fused_add_relu=True):
+        self.eng, self.lr, self.fused = eng, float(lr), fused_add_relu
+        self.w1 = eng.upload(w1, *w1.shape)
+        self.b1 = eng.upload(b1.reshape(1, -1), 1, b1.size)
+        self.w2 = eng.upload(w2, *w2.shape)
+        self.b2 = eng.upload(b2.reshape(1, -1), 1, b2.size)
+
+    def _el(self, kind, a, b=None, c=None, s=0.0):
+        out, _ = self.eng.eltwise_op(EltwiseOp(kind, s, 0.0), a, b, c)
+        return out
+
+    def step(self, x_buf: int, labels_buf: int, n: int, keep=False) -> Dict[str, int]:
+        """One training step on resident inputs.  Returns buffer ids: `loss` always, and with
+        `keep` the logits and the four gradients (the caller frees what it gets)."""
+        e, K = self.eng, kinds
+        free: List[int] = []
+        pre, _ = e.matmul_dram(x_buf, False, self.w1, False)                       # float_matmul
+        if self.fused:
+            h = self._el(K.ADD_RELU, pre, self.b1)                                 # fusion/eltwise.rs:1-8
+        else:
+            t = self._el(K.ADD, pre, self.b1); h = self._el(K.RELU, t); free.append(t)
+        z0, _ = e.matmul_dram(h, False, self.w2, False)
+        z = self._el(K.ADD, z0, self.b2)
+        logp, _ = e.log_softmax_rows(z)                                            # ops.rs:5153-5158
+        picked, _ = e.pick_columns(logp, labels_buf)                               # ops.rs:1001
+        neg = self._el(K.NEG, picked)
+        loss, _ = e.full_sum(neg, mean=True)                                       # ops.rs:3255
+        # backward
+        zeros, _ = e.zeros_dram((n, 1))
+        gval = self._el(K.ADD_SCALAR, zeros, s=-1.0 / n)                           # d(mean(-picked))
+        zl, dims = e.zeros_dram(e.dims_of(logp)[0])
+        g, _ = e.scatter_add_columns(zl, labels_buf, gval)                         # ops.rs:1043
+        p = self._el(K.EXP, logp)                                                  # log-softmax backward:
+        gs, _ = e.reduce(g, SUM, COLS)                                             #   g - exp(logp) * sum(g)
+        pg = self._el(K.MUL, p, gs)
+        dz = self._el(K.SUB, g, pg)
+        dw2, _ = e.matmul_dram(h, True, dz, False)                                 # x^T g (ops.rs:5006-5016)
+        db2, _ = e.sum_rows(dz)                                                    # in-order (ops.rs:5022-5028)
+        dh, _ = e.matmul_dram(dz, False, self.w2, True)
+        dpre = self._el(K.RELU_BACKWARD, h, dh)                                    # ops.rs:5174
+        dw1, _ = e.matmul_dram(x_buf, True, dpre, False)
+        db1, _ = e.sum_rows(dpre)
+        # SGD: w <- w - lr * dw  (mul_scalar, sub)
+        for name, grad in (("w1", dw1), ("b1", db1), ("w2", dw2), ("b2", db2)):
+            scaled = self._el(K.MUL_SCALAR, grad, s=self.lr)
+            new = self._el(K.SUB, getattr(self, name), scaled)
+            e.free(getattr(self, name)); e.free(scaled)
+            setattr(self, name, new)
+        free += [pre, z0, logp, picked, neg, zeros, gval, zl, g, p, gs, pg, dh, h]
+        out = {"loss": loss}
+        if keep:
+            out.update(logits=z, dw1=dw1, db1=db1, dw2=dw2, db2=db2, dz=dz, dpre=dpre)
+        else:
+            free += [z, dw1, db1, dw2, db2, dz, dpre]
+        for i in free:
+            e.free(i)
+        return out
+
+
+# ------------------------------------------------------------------------- config 4
+@dataclass
+class LlamaConfig:  # crates/tt-models/src/llama.rs:40,60 (SMOLLM2_135M), theta per the benchmark config
+    layers: int = 30
+    hidden: int = 576
+    heads: int = 9
+    kv_heads: int = 3
+    head_dim: int = 64
+    ff: int = 1536
+    vocab: int = 49152
+    eps: float = 1e-5
+    theta: float = 10000.0
+
+
+def llama_weights(cfg: LlamaConfig, seed: int = 0xC0F4, sigma: float = 0.02) -> Dict[str, np.ndarray]:
+    """Random-init weights N(0, sigma) as F32 (norm gains 1), laid out [in, out]."""
+    rng = np.random.default_rng(seed)
+    nrm = lambda *s: (rng.standard_normal(s, dtype=np.float32) * np.float32(sigma))
+    w = {"embed": nrm(cfg.vocab, cfg.hidden), "final_norm": np.ones(cfg.hidden, np.float32)}
+    q, kv = cfg.heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
+    for l in range(cfg.layers):
+        w[f"l{l}.qkv"] = nrm(cfg.hidden, q + 2 * kv)       # Wq | Wk | Wv side by side
+        w[f"l{l}.o"] = nrm(q, cfg.hidden)
+        w[f"l{l}.gate_up"] = nrm(cfg.hidden, 2 * cfg.ff)   # Wgate | Wup side by side
+        w[f"l{l}.down"] = nrm(cfg.ff, cfg.hidden)
+        w[f"l{l}.norm1"] = np.ones(cfg.hidden, np.float32)
+        w[f"l{l}.norm2"] = np.ones(cfg.hidden, np.float32)
+    return w
+
+
+def rope_tables(positions: int, head: int, theta: float):
+    """cos and sin' = [-sin, sin] (crates/tt-models/src/rope.rs:19-60), [positions, head] F32."""
+    i = np.arange(head // 2, dtype=np.float64)
+    freq = (theta ** (-2.0 * i / head)).astype(np.float32)
+    ang = (np.arange(positions, dtype=np.float32)[:, None] * freq[None, :]).astype(np.float32)
+    cos = np.cos(ang.astype(np.float64)).astype(np.float32)
+    sin = np.sin(ang.astype(np.float64)).astype(np.float32)
+    return np.concatenate([cos, cos], 1), np.concatenate([-sin, sin], 1)
+
+
+class LlamaPrefill:
+    """Prefill of `batch` independent causal sequences of `seq` tokens.  Weights are stored BF16;
+    the residual stream is F32; projections read BF16 activations and accumulate in F32."""
+
+    def __init__(self, eng, cfg: LlamaConfig, weights: Dict[str, np.ndarray], batch: int, seq: int):
+        self.eng, self.cfg, self.batch, self.seq = eng, cfg, batch, seq
+        up = lambda a: eng.upload_bf16(_bf16(a), *a.shape)
+        self.w = {}
+        for k, v in weights.items():
+            self.w[k] = up(v.reshape(1, -1) if v.ndim == 1 else v)
+        cos, sin = rope_tables(seq, cfg.head_dim, cfg.theta)
+        self.cos, self.sin = eng.upload(cos, *cos.shape), eng.upload(sin, *sin.shape)
+        mask = np.triu(np.ones((seq, seq), np.uint32), 1)   # 1 above the diagonal: filled with -inf
+        self.mask = eng.upload_bits(mask, seq, seq, BOOL)
+        c = cfg
+        self.q_cols, self.kv_cols = c.heads * c.head_dim, c.kv_heads * c.head_dim
+        group = c.heads // c.kv_heads
+        t = seq
+        hd = c.head_dim
+        # attention block lists (crates/burn-tt/src/ops.rs:3008-3081): item i = (b, h)
+        self.qk_items, self.pv_items, self.merge = [], [], []
+        for b in range(batch):
+            for h in range(c.heads):
+                i = b * c.heads + h
+                kvh = h // group
+                self.qk_items.append((((b * t, h * hd), False), ((b * t, kvh * hd), True)))
+                self.pv_items.append((((i * t, 0), False), ((b * t, self.q_cols + self.kv_cols + kvh * hd), False)))
+                self.merge.append(((i * t, 0), (b * t, h * hd), (t, hd), False))
+        self.last_rows = [(0, b * t + t - 1) for b in range(batch)]
+
+    def forward(self, ids_buf: int, all_positions: bool = False):
+        """ids [1, batch*seq] I32 resident.  Returns (logits buffer [batch or batch*seq, vocab] F32,
+        argmax buffer I32); the caller frees both."""
+        e, c, K = self.eng, self.cfg, kinds
+        n = self.batch * self.seq
+        t, hd = self.seq, c.head_dim
+        el = lambda kind, a, b=None, bf=False: e.eltwise_op_as(EltwiseOp(kind, 0.0, 0.0), a, b, None, bf)[0]
+        emb, _ = e.select_rows(self.w["embed"], ids_buf)                     # ops.rs:4958 embedding
+        x, _ = e.cast_float(emb, False)                                      # residual stream F32
+        e.free(emb)
+        for l in range(c.layers):
+            n1, _ = e.rms_norm_as(x, self.w[f"l{l}.norm1"], c.eps, True)     # llama.rs:151-170
+            qkv, _ = e.matmul_dram_bf16(n1, False, self.w[f"l{l}.qkv"], False)
+            e.free(n1)
+            qr, _ = e.rope_blocks((qkv, (0, 0), (n, self.q_cols)), (self.cos, (0, 0), (t, hd)),
+                                  (self.sin, (0, 0), (t, hd)), hd, True)      # rope.rs:129
+            kr, _ = e.rope_blocks((qkv, (0, self.q_cols), (n, self.kv_cols)), (self.cos, (0, 0), (t, hd)),
+                                  (self.sin, (0, 0), (t, hd)), hd, True)
+            s, _ = e.matmul_dram_batched(qr, kr, self.qk_items, (t, hd, t))  # Q K^T, F32 scores
+            e.free(qr); e.free(kr)
+            p, _ = e.softmax_rows(s, self.mask, 1.0 / float(np.sqrt(hd)))    # scale, causal mask, softmax
+            e.free(s)
+            pb, _ = e.cast_float(p, True)
+            e.free(p)
+            o, _ = e.matmul_dram_batched(pb, qkv, self.pv_items, (t, t, hd), bf16=True)   # P V
+            e.free(pb); e.free(qkv)
+            om, _ = e.copy_blocks(o, self.merge, (n, self.q_cols))           # merge heads
+            e.free(o)
+            att, _ = e.matmul_dram(om, False, self.w[f"l{l}.o"], False)      # o_proj, F32 out
+            e.free(om)
+            x2 = el(K.ADD, x, att)                                           # residual (llama.rs:288)
+            e.free(x); e.free(att)
+            n2, _ = e.rms_norm_as(x2, self.w[f"l{l}.norm2"], c.eps, True)
+            gu, _ = e.matmul_dram_bf16(n2, False, self.w[f"l{l}.gate_up"], False)
+            e.free(n2)
+            act, _ = e.eltwise_blocks_as(EltwiseOp(K.SILU_MUL, 0.0, 0.0), (gu, (0, 0), (n, c.ff)),
+                                         (gu, (0, c.ff), (n, c.ff)), None, True)   # silu(gate) * up (llama.rs:498)
+            e.free(gu)
+            d, _ = e.matmul_dram(act, False, self.w[f"l{l}.down"], False)
+            e.free(act)
+            x = el(K.ADD, x2, d)
+            e.free(x2); e.free(d)
+        if all_positions:
+            last = x
+        else:
+            last, _ = e.gather_rows([x], self.last_rows, c.hidden)           # last position only (llama.rs:1055-1061)
+            e.free(x)
+        fn, _ = e.rms_norm_as(last, self.w["final_norm"], c.eps, True)
+        e.free(last)
+        logits, _ = e.matmul_dram(fn, False, self.w["embed"], True)          # tied head: last . table^T (llama.rs:1090)
+        e.free(fn)
+        am, _ = e.argmax_row(logits)                                         # generate::argmax
+        return logits, am
+
+    def flops(self, all_positions=False) -> float:
+        c, n, t = self.cfg, self.batch * self.seq, self.seq
+        q, kv = self.q_cols, self.kv_cols
+        lin = 2.0 * n * (c.hidden * (q + 2 * kv) + q * c.hidden + c.hidden * 2 * c.ff + c.ff * c.hidden) * c.layers
+        att = 2.0 * 2.0 * self.batch * c.heads * t * t * c.head_dim * c.layers
+        head = 2.0 * (n if all_positions else self.batch) * c.hidden * c.vocab
+        return lin + att + head
+
+
+# ------------------------------------------------------------------------- config 5
+def attention_products(eng, q_buf: int, k_buf: int, v_buf: int, batch_heads: int, t: int, d: int):
+    """Q, K, V stored [batch_heads*t, d] BF16.  S = Q K^T (F32), P = softmax(S / sqrt d) in F32,
+    O = P(BF16) V -> [batch_heads*t, d] BF16.  Returns O's buffer."""
+    qk = [(((i * t, 0), False), ((i * t, 0), True)) for i in range(batch_heads)]
+    pv = [(((i * t, 0), False), ((i * t, 0), False)) for i in range(batch_heads)]
+    s, _ = eng.matmul_dram_batched(q_buf, k_buf, qk, (t, d, t))
+    p, _ = eng.softmax_rows(s, None, 1.0 / float(np.sqrt(d)))
+    eng.free(s)
+    pb, _ = eng.cast_float(p, True)
+    eng.free(p)
+    o, _ = eng.matmul_dram_batched(pb, v_buf, pv, (t, t, d), bf16=True)
+    eng.free(pb)
+    return o
