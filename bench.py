@@ -100,6 +100,7 @@ def cpu_gemm_baseline(target_seconds=12.0):
     """The CPU restatement's F32 product of BF16-rounded operands on all host cores, on a
     bounded sample (the same product at a smaller size), as TFLOP/s."""
     from oracle import oracle as orc
+    orc.clib().orc_set_threads(os.cpu_count() or 1)  # a launcher may have set OMP_NUM_THREADS=1
     cores = orc.clib().orc_threads()
     n = 1024
     a = orc.from_bf16(cheap_bf16((n, n), 1))

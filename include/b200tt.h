@@ -188,6 +188,11 @@ int32_t b200_full_reduce(b200_engine*, const float* values, const uint64_t dims[
 /* `softmax_rows(x, mask, scale)`: mask 0 = none; Bool words, read for rows r % mask_rows. */
 int32_t b200_softmax_rows(b200_engine*, b200_buffer x, b200_buffer mask, float scale,
                           b200_buffer* out, uint64_t out_dims[2]);
+/* `softmax_rows` with its result's type named, as the reference's `_as` methods do
+ * (`rms_norm_as` server.rs:449, `eltwise_op_as` :519): out_bf16 rounds the F32 probabilities
+ * once, bit for bit `softmax_rows` then `cast_float`, with no F32 result written. */
+int32_t b200_softmax_rows_as(b200_engine*, b200_buffer x, b200_buffer mask, float scale, int32_t out_bf16,
+                             b200_buffer* out, uint64_t out_dims[2]);
 /* Burn's `activation::log_softmax` over the last dim (ops.rs:5153-5158). */
 int32_t b200_log_softmax_rows(b200_engine*, b200_buffer x, b200_buffer* out, uint64_t out_dims[2]);
 int32_t b200_rms(b200_engine*, b200_buffer a, float eps, b200_buffer* out, uint64_t out_dims[2]);

@@ -533,8 +533,12 @@ static int run_gemm(b200_engine* e, GemmArgs& g, const GemmBatch* batches_host, 
   const char* why = "";
   const bool want_tc = g.in_bf16 ? e->cfg.bf16_matmul_mode != 1 : e->cfg.f32_matmul_mode == 2;
   if (want_tc && gemm_tc_supported(g, &why)) {
-    e->matmul_path = "tcgen05";
-    return e->launched(launch_gemm_tc(g, batches_host, e->d_err, e->stream), what);
+    const cudaError_t ce = launch_gemm_tc(g, batches_host, e->d_err, e->stream);
+    if (ce != cudaErrorNotSupported) {
+      e->matmul_path = "tcgen05";
+      return e->launched(ce, what);
+    }
+    why = "the driver refused a tensor map for this shape";
   }
   if (g.in_bf16 && e->cfg.bf16_matmul_mode == 2)
     return e->fail(B200_UNSUPPORTED, "%s: the tcgen05 path refuses this product (%s) and the engine is set to use no other", what, why);
@@ -763,8 +767,8 @@ int32_t b200_full_reduce(b200_engine* e, const float* values, const uint64_t dim
   return st;
 }
 
-static int softmax_any(b200_engine* e, b200_buffer x, b200_buffer mask, float scale, int log_form, b200_buffer* out,
-                       uint64_t out_dims[2]) {
+static int softmax_any(b200_engine* e, b200_buffer x, b200_buffer mask, float scale, int log_form, int out_bf16,
+                       b200_buffer* out, uint64_t out_dims[2]) {
   cudaSetDevice(e->device);
   Buf *X = nullptr, *M = nullptr;
   int st = e->need(x, &X, "softmax_rows");
@@ -779,18 +783,22 @@ static int softmax_any(b200_engine* e, b200_buffer x, b200_buffer mask, float sc
   const uint32_t* ms = M ? (const uint32_t*)M->ptr : nullptr;
   const uint64_t mrows = M ? M->rows : 1;
   Buf* O = nullptr;
-  st = e->new_buffer(rows, cols, B200_F32, out, &O);
+  st = e->new_buffer(rows, cols, out_bf16 ? B200_BF16 : B200_F32, out, &O);
   if (st) return st;
-  st = e->launched(launch_softmax_rows(xs, ms, mrows, scale, log_form, (float*)O->ptr, rows, cols, e->stream), "softmax_rows");
+  st = e->launched(launch_softmax_rows(xs, ms, mrows, scale, log_form, O->ptr, out_bf16, rows, cols, e->stream), "softmax_rows");
   if (st) { e->drop(*out); return st; }
   set_dims(out_dims, rows, cols);
   return B200_OK;
 }
 int32_t b200_softmax_rows(b200_engine* e, b200_buffer x, b200_buffer mask, float scale, b200_buffer* out, uint64_t out_dims[2]) {
-  return softmax_any(e, x, mask, scale, 0, out, out_dims);
+  return softmax_any(e, x, mask, scale, 0, 0, out, out_dims);
+}
+int32_t b200_softmax_rows_as(b200_engine* e, b200_buffer x, b200_buffer mask, float scale, int32_t out_bf16, b200_buffer* out,
+                             uint64_t out_dims[2]) {
+  return softmax_any(e, x, mask, scale, 0, out_bf16, out, out_dims);
 }
 int32_t b200_log_softmax_rows(b200_engine* e, b200_buffer x, b200_buffer* out, uint64_t out_dims[2]) {
-  return softmax_any(e, x, 0, 1.0f, 1, out, out_dims);
+  return softmax_any(e, x, 0, 1.0f, 1, 0, out, out_dims);
 }
 
 int32_t b200_rms(b200_engine* e, b200_buffer a, float eps, b200_buffer* out, uint64_t out_dims[2]) {

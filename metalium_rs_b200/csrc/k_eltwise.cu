@@ -86,6 +86,75 @@ __global__ void __launch_bounds__(256) elt_generic(EltwiseArgs g) {
   }
 }
 
+// ---- block / BF16 fast path: eight consecutive columns a thread ---------------------
+// Operands may be blocks of wider buffers (ld > cols), F32 or BF16, and b may be a's shape, one
+// row, whole rows repeated, or one column.  Needs cols % 8 == 0 and 16-byte aligned rows.
+struct Word8 { uint32_t w[8]; };
+
+__device__ __forceinline__ Word8 load8(const Mat& m, uint64_t r, uint32_t c) {
+  Word8 o;
+  const uint64_t rr = (m.rows == 1) ? 0 : (r % m.rows);
+  if (m.cols == 1) {
+    const uint32_t v = m.bf16 ? (uint32_t)reinterpret_cast<const uint16_t*>(m.p)[rr * m.ld] << 16
+                              : reinterpret_cast<const uint32_t*>(m.p)[rr * m.ld];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o.w[i] = v;
+    return o;
+  }
+  const uint64_t off = rr * m.ld + c;
+  if (m.bf16) {
+    const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(m.p) + off);
+    o.w[0] = v.x << 16; o.w[1] = v.x & 0xffff0000u; o.w[2] = v.y << 16; o.w[3] = v.y & 0xffff0000u;
+    o.w[4] = v.z << 16; o.w[5] = v.z & 0xffff0000u; o.w[6] = v.w << 16; o.w[7] = v.w & 0xffff0000u;
+  } else {
+    const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const uint32_t*>(m.p) + off);
+    const uint4 v0 = p[0], v1 = p[1];
+    o.w[0] = v0.x; o.w[1] = v0.y; o.w[2] = v0.z; o.w[3] = v0.w;
+    o.w[4] = v1.x; o.w[5] = v1.y; o.w[6] = v1.z; o.w[7] = v1.w;
+  }
+  return o;
+}
+
+__device__ __forceinline__ void store8(void* out, uint64_t off, int bf16, const Word8& v) {
+  if (bf16) {
+    uint4 o;
+    o.x = (uint32_t)f32_to_bf16_bits(v.w[0]) | ((uint32_t)f32_to_bf16_bits(v.w[1]) << 16);
+    o.y = (uint32_t)f32_to_bf16_bits(v.w[2]) | ((uint32_t)f32_to_bf16_bits(v.w[3]) << 16);
+    o.z = (uint32_t)f32_to_bf16_bits(v.w[4]) | ((uint32_t)f32_to_bf16_bits(v.w[5]) << 16);
+    o.w = (uint32_t)f32_to_bf16_bits(v.w[6]) | ((uint32_t)f32_to_bf16_bits(v.w[7]) << 16);
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + off) = o;
+  } else {
+    uint4* p = reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + off);
+    p[0] = make_uint4(v.w[0], v.w[1], v.w[2], v.w[3]);
+    p[1] = make_uint4(v.w[4], v.w[5], v.w[6], v.w[7]);
+  }
+}
+
+template <uint32_t K>
+__global__ void __launch_bounds__(256) elt_rows8(EltwiseArgs g) {
+  const uint32_t c8 = (uint32_t)(g.cols / 8);
+  const uint64_t n8 = g.rows * c8;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (uint64_t)gridDim.x * blockDim.x) {
+    const uint64_t r = i / c8;
+    const uint32_t c = (uint32_t)(i - r * c8) * 8;
+    const Word8 a = load8(g.a, r, c);
+    Word8 b, cc, o;
+    if (g.b.p) b = load8(g.b, r, c);
+    if (g.c.p) cc = load8(g.c, r, c);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o.w[j] = ev<K>(a.w[j], g.b.p ? b.w[j] : 0u, g.c.p ? cc.w[j] : 0u, g.s1, g.s2, g.err);
+    store8(g.out, r * g.out_ld + c, g.out_bf16, o);
+  }
+}
+
+inline bool mat_ok8(const Mat& m, uint64_t rows, uint64_t cols) {
+  if (!m.p) return true;
+  const uintptr_t a = reinterpret_cast<uintptr_t>(m.p);
+  if (m.cols == 1) return m.rows == rows || m.rows == 1;
+  const uint64_t eb = m.bf16 ? 2 : 4;
+  return m.cols == cols && (a % 16 == 0) && ((m.ld * eb) % 16 == 0) && (m.rows == rows || m.rows == 1 || rows % m.rows == 0);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 template <uint32_t K>
@@ -119,6 +188,14 @@ cudaError_t launch_kind(const EltwiseArgs& g, cudaStream_t stream) {
     }
     return cudaGetLastError();
   }
+  if (g.cols % 8 == 0 && g.a.rows == g.rows && mat_ok8(g.a, g.rows, g.cols) && g.a.cols == g.cols &&
+      mat_ok8(g.b, g.rows, g.cols) && mat_ok8(g.c, g.rows, g.cols) && (!g.c.p || g.c.cols == g.cols) &&
+      (reinterpret_cast<uintptr_t>(g.out) % 16 == 0) && ((g.out_ld * (g.out_bf16 ? 2 : 4)) % 16 == 0) && g.cols / 8 <= 0xffffffffull) {
+    uint64_t blocks = (n / 8 + 255) / 256;
+    if (blocks > 148ull * 32) blocks = 148ull * 32;
+    elt_rows8<K><<<(unsigned)blocks, 256, 0, stream>>>(g);
+    return cudaGetLastError();
+  }
   uint64_t blocks = (n + 255) / 256;
   if (blocks > 148ull * 32) blocks = 148ull * 32;
   elt_generic<K><<<(unsigned)blocks, 256, 0, stream>>>(g);
@@ -148,6 +225,30 @@ rope_kernel(Mat x, Mat cs, Mat sn, uint64_t head, void* out, uint64_t out_ld, in
     const uint64_t o = r * out_ld + c;
     if (out_bf16) reinterpret_cast<uint16_t*>(out)[o] = f32_to_bf16_bits(res);
     else reinterpret_cast<uint32_t*>(out)[o] = res;
+  }
+}
+
+// Eight consecutive columns a thread (they lie in one half of one head when head/2 % 8 == 0).
+__global__ void __launch_bounds__(256)
+rope_kernel8(Mat x, Mat cs, Mat sn, uint32_t head, void* out, uint64_t out_ld, int out_bf16,
+             uint64_t rows, uint32_t cols) {
+  const uint32_t c8 = cols / 8, half = head / 2;
+  const uint64_t n8 = rows * c8;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (uint64_t)gridDim.x * blockDim.x) {
+    const uint64_t r = i / c8;
+    const uint32_t c = (uint32_t)(i - r * c8) * 8;
+    const uint32_t h = c / head, j = c - h * head;
+    const uint32_t cswap = h * head + (j < half ? j + half : j - half);
+    const Word8 xv = load8(x, r, c), xs = load8(x, r, cswap);
+    const Word8 co = load8(cs, r, cs.cols == head ? j : c), si = load8(sn, r, sn.cols == head ? j : c);
+    Word8 o;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float p1 = __uint_as_float(xv.w[q]) * __uint_as_float(co.w[q]);
+      const float p2 = __uint_as_float(xs.w[q]) * __uint_as_float(si.w[q]);
+      o.w[q] = __float_as_uint(p1 + p2);
+    }
+    store8(out, r * out_ld + c, out_bf16, o);
   }
 }
 
@@ -192,6 +293,18 @@ cudaError_t launch_rope(const Mat& x, const Mat& cs, const Mat& sn, uint64_t hea
                         cudaStream_t stream) {
   const uint64_t n = rows * cols;
   if (n == 0) return cudaSuccess;
+  auto ok8 = [&](const Mat& m, uint64_t want_cols) {
+    const uint64_t eb = m.bf16 ? 2 : 4;
+    return m.cols == want_cols && reinterpret_cast<uintptr_t>(m.p) % 16 == 0 && (m.ld * eb) % 16 == 0;
+  };
+  if ((head / 2) % 8 == 0 && cols <= 0xffffffffull && ok8(x, cols) && (ok8(cs, head) || ok8(cs, cols)) &&
+      (ok8(sn, head) || ok8(sn, cols)) && reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
+      (out_ld * (out_bf16 ? 2 : 4)) % 16 == 0) {
+    uint64_t b8 = (n / 8 + 255) / 256;
+    if (b8 > 148ull * 32) b8 = 148ull * 32;
+    rope_kernel8<<<(unsigned)b8, 256, 0, stream>>>(x, cs, sn, (uint32_t)head, out, out_ld, out_bf16, rows, (uint32_t)cols);
+    return cudaGetLastError();
+  }
   uint64_t blocks = (n + 255) / 256;
   if (blocks > 148ull * 32) blocks = 148ull * 32;
   rope_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, cs, sn, head, out, out_ld, out_bf16, rows, cols);

@@ -385,7 +385,10 @@ bool gemm_tc_supported(const GemmArgs& g, const char** why) {
   *why = "";
   if (!g.in_bf16) { *why = "operands are not BF16"; return false; }
   if (!encode_fn()) { *why = "the driver offers no tensor-map encoder"; return false; }
-  if (g.m < 64 || g.n < 64 || g.k < 64) { *why = "a dimension is below 64"; return false; }
+  // A short M is served by a 128-row tile whose rows past M are zero-filled by TMA and masked
+  // in the epilogue -- only when M is A's outer dimension; an inner extent stays >= one box.
+  const bool a_mn = g.batch > 1 ? false : g.a_trans != 0;
+  if (g.n < 64 || g.k < 64 || (g.m < 64 && (a_mn || g.batch > 1))) { *why = "a dimension is below 64"; return false; }
   if (g.lda % 8 || g.ldb % 8) { *why = "a row pitch is not a multiple of 16 bytes"; return false; }
   if (((uintptr_t)g.a | (uintptr_t)g.b) & 15) { *why = "an operand is not 16-byte aligned"; return false; }
   if (g.m > 0x7fffffffull || g.n > 0x7fffffffull || g.k > 0x7fffffffull) { *why = "a dimension exceeds 2^31"; return false; }
@@ -432,8 +435,8 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int
   const uint32_t tiles_n = (uint32_t)((g.n + bn - 1) / bn);
 
   CUtensorMap ma, mb;
-  if (!make_map(&ma, g.a, a_rows, a_cols, g.lda, a_mn ? 64 : BM)) return cudaErrorInvalidValue;
-  if (!make_map(&mb, g.b, b_rows, b_cols, g.ldb, b_mn ? 64 : (uint32_t)bn)) return cudaErrorInvalidValue;
+  if (!make_map(&ma, g.a, a_rows, a_cols, g.lda, a_mn ? 64 : BM)) return cudaErrorNotSupported;
+  if (!make_map(&mb, g.b, b_rows, b_cols, g.ldb, b_mn ? 64 : (uint32_t)bn)) return cudaErrorNotSupported;
 
   TcParams p{};
   p.m = g.m; p.n = g.n; p.k = g.k;

@@ -252,6 +252,22 @@ template <int THREADS> __device__ __forceinline__ float block_add(float v, float
   return t;
 }
 
+// Four results of a row at float4 index i: F32, or rounded once to BF16.
+__device__ __forceinline__ void store4(void* row, uint32_t i, float4 t, int bf16) {
+  if (bf16) {
+    uint2 o;
+    o.x = (uint32_t)f32_to_bf16_bits(__float_as_uint(t.x)) | ((uint32_t)f32_to_bf16_bits(__float_as_uint(t.y)) << 16);
+    o.y = (uint32_t)f32_to_bf16_bits(__float_as_uint(t.z)) | ((uint32_t)f32_to_bf16_bits(__float_as_uint(t.w)) << 16);
+    __stcs(reinterpret_cast<uint2*>(row) + i, o);
+  } else {
+    __stcs(reinterpret_cast<float4*>(row) + i, t);
+  }
+}
+__device__ __forceinline__ void store1(void* row, uint64_t i, float v, int bf16) {
+  if (bf16) reinterpret_cast<uint16_t*>(row)[i] = f32_to_bf16_bits(__float_as_uint(v));
+  else reinterpret_cast<float*>(row)[i] = v;
+}
+
 __device__ __forceinline__ float scaled_masked(float x, uint32_t m, float scale, bool has_scale) {
   const float s = has_scale ? x * scale : x;
   return m ? -INFINITY : s;
@@ -261,7 +277,7 @@ __device__ __forceinline__ float scaled_masked(float x, uint32_t m, float scale,
 template <int THREADS, int VPT>
 __global__ void __launch_bounds__(THREADS)
 softmax_block_kernel(const float* __restrict__ x, const uint32_t* __restrict__ mask, uint64_t mask_rows,
-                     float scale, int log_form, float* __restrict__ out, uint64_t rows, uint32_t cols) {
+                     float scale, int log_form, void* __restrict__ out, int out_bf16, uint64_t rows, uint32_t cols) {
   __shared__ float sm[32];
   const uint32_t n4 = cols / 4;
   const bool has_scale = scale != 1.0f;
@@ -306,7 +322,7 @@ softmax_block_kernel(const float* __restrict__ x, const uint32_t* __restrict__ m
       }
     }
     s = block_add<THREADS>(s, sm);
-    float4* orow = reinterpret_cast<float4*>(out + row * cols);
+    void* orow = reinterpret_cast<char*>(out) + row * cols * (out_bf16 ? 2 : 4);
     if (log_form) {
       const float l = logf(s);
 #pragma unroll
@@ -315,7 +331,7 @@ softmax_block_kernel(const float* __restrict__ x, const uint32_t* __restrict__ m
         if (i < n4) {
           float4 t = v[u];
           t.x = t.x - l; t.y = t.y - l; t.z = t.z - l; t.w = t.w - l;
-          __stcs(orow + i, t);
+          store4(orow, i, t, out_bf16);
         }
       }
     } else {
@@ -327,7 +343,7 @@ softmax_block_kernel(const float* __restrict__ x, const uint32_t* __restrict__ m
         if (i < n4) {
           float4 t = v[u];
           t.x = t.x * inv; t.y = t.y * inv; t.z = t.z * inv; t.w = t.w * inv;
-          __stcs(orow + i, t);
+          store4(orow, i, t, out_bf16);
         }
       }
     }
@@ -342,7 +358,7 @@ softmax_block_kernel(const float* __restrict__ x, const uint32_t* __restrict__ m
 template <int THREADS, int VPT>
 __global__ void __launch_bounds__(THREADS)
 softmax_cluster_kernel(const float* __restrict__ x, const uint32_t* __restrict__ mask, uint64_t mask_rows,
-                       float scale, int log_form, float* __restrict__ out, uint64_t rows, uint32_t cols) {
+                       float scale, int log_form, void* __restrict__ out, int out_bf16, uint64_t rows, uint32_t cols) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned csize = cluster.num_blocks();
@@ -409,7 +425,7 @@ softmax_cluster_kernel(const float* __restrict__ x, const uint32_t* __restrict__
       s = *cluster.map_shared_rank(&xchg[par][1], 0);
       for (unsigned r = 1; r < csize; ++r) s = s + *cluster.map_shared_rank(&xchg[par][1], r);
     }
-    float4* orow = reinterpret_cast<float4*>(out + row * cols);
+    void* orow = reinterpret_cast<char*>(out) + row * cols * (out_bf16 ? 2 : 4);
     if (log_form) {
       const float l = logf(s);
 #pragma unroll
@@ -418,7 +434,7 @@ softmax_cluster_kernel(const float* __restrict__ x, const uint32_t* __restrict__
         if (i < last) {
           float4 t = v[u];
           t.x = t.x - l; t.y = t.y - l; t.z = t.z - l; t.w = t.w - l;
-          __stcs(orow + i, t);
+          store4(orow, i, t, out_bf16);
         }
       }
     } else {
@@ -430,7 +446,7 @@ softmax_cluster_kernel(const float* __restrict__ x, const uint32_t* __restrict__
         if (i < last) {
           float4 t = v[u];
           t.x = t.x * inv; t.y = t.y * inv; t.z = t.z * inv; t.w = t.w * inv;
-          __stcs(orow + i, t);
+          store4(orow, i, t, out_bf16);
         }
       }
     }
@@ -442,7 +458,7 @@ softmax_cluster_kernel(const float* __restrict__ x, const uint32_t* __restrict__
 // mostly from L2).  Rows too short or ragged for the register kernel, or too long.
 __global__ void __launch_bounds__(256)
 softmax_stream_kernel(const float* __restrict__ x, const uint32_t* __restrict__ mask, uint64_t mask_rows,
-                      float scale, int log_form, float* __restrict__ out, uint64_t rows, uint64_t cols) {
+                      float scale, int log_form, void* __restrict__ out, int out_bf16, uint64_t rows, uint64_t cols) {
   __shared__ float sm[32];
   const bool has_scale = scale != 1.0f;
   for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -457,15 +473,15 @@ softmax_stream_kernel(const float* __restrict__ x, const uint32_t* __restrict__ 
     for (uint64_t i = threadIdx.x; i < cols; i += 256)
       s = s + expf(scaled_masked(xr[i], mr ? mr[i] : 0u, scale, has_scale) - m);
     s = block_add<256>(s, sm);
-    float* orow = out + row * cols;
+    void* orow = reinterpret_cast<char*>(out) + row * cols * (out_bf16 ? 2 : 4);
     if (log_form) {
       const float l = logf(s);
       for (uint64_t i = threadIdx.x; i < cols; i += 256)
-        orow[i] = (scaled_masked(xr[i], mr ? mr[i] : 0u, scale, has_scale) - m) - l;
+        store1(orow, i, (scaled_masked(xr[i], mr ? mr[i] : 0u, scale, has_scale) - m) - l, out_bf16);
     } else {
       s = (s < FLT_MIN) ? FLT_MIN : s;
       for (uint64_t i = threadIdx.x; i < cols; i += 256)
-        orow[i] = expf(scaled_masked(xr[i], mr ? mr[i] : 0u, scale, has_scale) - m) / s;
+        store1(orow, i, expf(scaled_masked(xr[i], mr ? mr[i] : 0u, scale, has_scale) - m) / s, out_bf16);
     }
   }
 }
@@ -659,7 +675,7 @@ int32_t b200_full_sum_noalloc(const float* device_values, uint64_t n, int32_t me
 namespace b200 {
 
 cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t mask_rows, float scale,
-                                int log_form, float* out, uint64_t rows, uint64_t cols,
+                                int log_form, void* out, int out_bf16, uint64_t rows, uint64_t cols,
                                 cudaStream_t s) {
   if (rows == 0 || cols == 0) return cudaSuccess;
   const bool al = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) |
@@ -668,7 +684,7 @@ cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t m
   const uint64_t grid = rows < 148ull * 64 ? rows : 148ull * 64;
 #define SM_LAUNCH(T, V)                                                                         \
   softmax_block_kernel<T, V><<<(unsigned)(rows < (148ull * (2048 / T)) ? rows : 148ull * (2048 / T)), \
-                               T, 0, s>>>(x, mask, mask_rows, scale, log_form, out, rows, (uint32_t)cols)
+                               T, 0, s>>>(x, mask, mask_rows, scale, log_form, out, out_bf16, rows, (uint32_t)cols)
   if (al && cols % 4 == 0 && cols >= 128 && n4 <= 1024) {
     if (n4 <= 32) SM_LAUNCH(32, 1);
     else if (n4 <= 64) SM_LAUNCH(64, 1);
@@ -700,10 +716,10 @@ cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t m
     cfg.attrs = attr; cfg.numAttrs = 1;
     const uint32_t cols32 = (uint32_t)cols;
     if (threads == 256)
-      return cudaLaunchKernelEx(&cfg, softmax_cluster_kernel<256, 8>, x, mask, mask_rows, scale, log_form, out, rows, cols32);
-    return cudaLaunchKernelEx(&cfg, softmax_cluster_kernel<512, 8>, x, mask, mask_rows, scale, log_form, out, rows, cols32);
+      return cudaLaunchKernelEx(&cfg, softmax_cluster_kernel<256, 8>, x, mask, mask_rows, scale, log_form, out, out_bf16, rows, cols32);
+    return cudaLaunchKernelEx(&cfg, softmax_cluster_kernel<512, 8>, x, mask, mask_rows, scale, log_form, out, out_bf16, rows, cols32);
   } else {
-    softmax_stream_kernel<<<(unsigned)grid, 256, 0, s>>>(x, mask, mask_rows, scale, log_form, out, rows, cols);
+    softmax_stream_kernel<<<(unsigned)grid, 256, 0, s>>>(x, mask, mask_rows, scale, log_form, out, out_bf16, rows, cols);
   }
 #undef SM_LAUNCH
   return cudaGetLastError();

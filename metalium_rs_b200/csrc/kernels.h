@@ -43,7 +43,7 @@ uint64_t full_sum_scratch_floats();
 cudaError_t launch_full_sum(const float* a, uint64_t n, int mean, float* scratch, float* out,
                             cudaStream_t stream);
 cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t mask_rows, float scale,
-                                int log_form, float* out, uint64_t rows, uint64_t cols,
+                                int log_form, void* out, int out_bf16, uint64_t rows, uint64_t cols,
                                 cudaStream_t stream);
 cudaError_t launch_rms(const float* a, uint64_t rows, uint64_t cols, float eps, float* out,
                        cudaStream_t stream);

@@ -349,6 +349,10 @@ class CudaEngine:
     def softmax_rows(self, x: int, mask: Optional[int], scale: float) -> Out:
         return self._call(self._lib.b200_softmax_rows, C.c_uint64(x), C.c_uint64(mask or 0), C.c_float(scale))
 
+    def softmax_rows_as(self, x: int, mask: Optional[int], scale: float, bf16: bool) -> Out:
+        return self._call(self._lib.b200_softmax_rows_as, C.c_uint64(x), C.c_uint64(mask or 0), C.c_float(scale),
+                          C.c_int32(bf16))
+
     def log_softmax_rows(self, x: int) -> Out:
         return self._call(self._lib.b200_log_softmax_rows, C.c_uint64(x))
 

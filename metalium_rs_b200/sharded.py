@@ -79,7 +79,10 @@ class ShardedMatmul:
         ptr, nbytes = eng.device_ptr(out)
         with torch.cuda.stream(self.stream):
             src = _as_tensor(ptr, (self.m, self.per), self.local.dtype)
-            dist.all_gather_into_tensor(self.staged.view(self.world * self.m, self.per), src)
+            dst = self.staged.view(self.world * self.m, self.per)
+            if self.bf16:  # NCCL has no 16-bit integer type: name the same bits BF16
+                src, dst = src.view(torch.bfloat16), dst.view(torch.bfloat16)
+            dist.all_gather_into_tensor(dst, src)
         eng.free(out)
         full, _ = eng.copy_blocks(self.staged_buf, self.moves, (self.m, self.n))
         return full  # the caller frees it

@@ -182,10 +182,8 @@ class LlamaPrefill:
                                   (self.sin, (0, 0), (t, hd)), hd, True)
             s, _ = e.matmul_dram_batched(qr, kr, self.qk_items, (t, hd, t))  # Q K^T, F32 scores
             e.free(qr); e.free(kr)
-            p, _ = e.softmax_rows(s, self.mask, 1.0 / float(np.sqrt(hd)))    # scale, causal mask, softmax
+            pb, _ = e.softmax_rows_as(s, self.mask, 1.0 / float(np.sqrt(hd)), True)   # scale, causal mask, softmax
             e.free(s)
-            pb, _ = e.cast_float(p, True)
-            e.free(p)
             o, _ = e.matmul_dram_batched(pb, qkv, self.pv_items, (t, t, hd), bf16=True)   # P V
             e.free(pb); e.free(qkv)
             om, _ = e.copy_blocks(o, self.merge, (n, self.q_cols))           # merge heads
@@ -232,10 +230,8 @@ def attention_products(eng, q_buf: int, k_buf: int, v_buf: int, batch_heads: int
     qk = [(((i * t, 0), False), ((i * t, 0), True)) for i in range(batch_heads)]
     pv = [(((i * t, 0), False), ((i * t, 0), False)) for i in range(batch_heads)]
     s, _ = eng.matmul_dram_batched(q_buf, k_buf, qk, (t, d, t))
-    p, _ = eng.softmax_rows(s, None, 1.0 / float(np.sqrt(d)))
+    pb, _ = eng.softmax_rows_as(s, None, 1.0 / float(np.sqrt(d)), True)
     eng.free(s)
-    pb, _ = eng.cast_float(p, True)
-    eng.free(p)
     o, _ = eng.matmul_dram_batched(pb, v_buf, pv, (t, t, d), bf16=True)
     eng.free(pb)
     return o

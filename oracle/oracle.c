@@ -19,6 +19,14 @@
 #include <omp.h>
 #endif
 
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int orc_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();
