@@ -247,3 +247,60 @@ def test_large_unary_and_row_broadcast_fast_path(eng):
         assert np.array_equal(got, want), name
         eng.free(out)
     eng.free(ia); eng.free(ir)
+
+
+@pytest.mark.parametrize("name", ["ADD", "MUL", "SILU_MUL", "SUB", "ADD_RELU", "MUL_ADD"])
+@pytest.mark.parametrize("mix", ["f32", "bf16", "mixed"])
+def test_block_operands_of_either_type(eng, name, mix):
+    # blocks of wider buffers, F32 or BF16 on either side, F32 or BF16 out: the 8-wide path and
+    # the element path must give the same bits as the oracle on the widened values
+    a = orc.uniform(0xB9, 1, (96, 256), -4, 4)
+    b = orc.uniform(0xB9, 2, (64, 384), -4, 4)
+    c = orc.uniform(0xB9, 3, (64, 128), -4, 4)
+    abf, bbf = mix == "bf16", mix in ("bf16", "mixed")
+    ah, bh = orc.to_bf16(a), orc.to_bf16(b)
+    av = orc.from_bf16(ah) if abf else a
+    bv = orc.from_bf16(bh) if bbf else b
+    ia = eng.upload_bf16(ah, 96, 256) if abf else eng.upload(a, 96, 256)
+    ib = eng.upload_bf16(bh, 64, 384) if bbf else eng.upload(b, 64, 384)
+    ic = eng.upload(c, 64, 128)
+    ar = kinds.ARITY[getattr(kinds, name)]
+    for (ac, bc, w) in ((64, 128, 128), (8, 16, 40), (3, 5, 37)):   # aligned, aligned-narrow, ragged
+        blk_a = (ia, (32, ac), (64, w))
+        blk_b = (ib, (0, bc), (64, w))
+        blk_c = (ic, (0, 0), (64, w)) if ar == 3 else None
+        want = orc.eltwise(name, av[32:96, ac:ac + w], bv[:, bc:bc + w], c[:, :w] if ar == 3 else None)
+        for out_bf in (False, True):
+            out, dims = eng.eltwise_blocks_as(EltwiseOp(getattr(kinds, name), 0, 0), blk_a, blk_b, blk_c, out_bf)
+            assert dims == (64, w)
+            if out_bf:
+                got, ref = eng.download_bf16(out), orc.bf16_round_bits(want)
+            else:
+                got, ref = eng.download_bits(out), want
+            if orc.ULP_BOUND.get(name):
+                if out_bf:
+                    assert np.abs(got.astype(np.int32) - ref.astype(np.int32)).max() <= 1
+                else:
+                    assert orc.ulp_error(got, ref) <= orc.ULP_BOUND[name] + 1
+            else:
+                assert np.array_equal(got, ref), (name, mix, w, out_bf)
+            eng.free(out)
+    for i in (ia, ib, ic):
+        eng.free(i)
+
+
+def test_rope_blocks_of_a_wider_bf16_buffer(eng):
+    # q and k as column blocks of one [t, q+k+v] BF16 buffer, tables shorter than the rows (r % t)
+    head, t, batch = 64, 32, 3
+    cos, sin = orc.rope_tables(t, head, 10000.0)
+    x = orc.to_bf16(orc.normal(0xBA, 1, (batch * t, 15 * head)))
+    ix, ic, isn = eng.upload_bf16(x, batch * t, 15 * head), eng.upload(cos, t, head), eng.upload(sin, t, head)
+    xv = orc.from_bf16(x)
+    for c0, heads in ((0, 9), (9 * head, 3)):
+        out, dims = eng.rope_blocks((ix, (0, c0), (batch * t, heads * head)), (ic, (0, 0), (t, head)),
+                                    (isn, (0, 0), (t, head)), head, True)
+        want = orc.rope(xv[:, c0:c0 + heads * head], cos, sin, head)
+        assert np.array_equal(eng.download_bf16(out), orc.to_bf16(want))
+        eng.free(out)
+    for i in (ix, ic, isn):
+        eng.free(i)

@@ -218,3 +218,17 @@ def test_bf16_product_at_4096_by_properties(eng):
     assert np.array_equal(eng.download_bf16(ob), orc.to_bf16(c.astype(np.float32)))
     for i in (ia, ib, out, ob):
         eng.free(i)
+
+
+@pytest.mark.parametrize("m", [1, 8, 33])
+def test_short_m_products_take_the_tensor_cores(eng, m):
+    # a prefill's head: a few rows against a [vocab, hidden] table read transposed
+    a = orc.to_bf16(orc.uniform(0xC0F4, 20, (m, 576), -1, 1))
+    table = orc.to_bf16(orc.normal(0xC0F4, 21, (4096, 576), 0.02))
+    ia, it = eng.upload_bf16(a, m, 576), eng.upload_bf16(table, 4096, 576)
+    out, dims = eng.matmul_dram(ia, False, it, True)
+    assert dims == (m, 4096) and eng.last_matmul_path() == "tcgen05"
+    truth, s = orc.gemm_truth(orc.from_bf16(a), orc.from_bf16(table), False, True)
+    assert orc.gemm_rel_error(eng.download(out), truth, s)[0] <= 1e-6
+    for i in (ia, it, out):
+        eng.free(i)

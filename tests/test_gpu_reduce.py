@@ -234,3 +234,16 @@ def test_argmax_many_rows_and_the_moved_maximum(eng):  # step211_argmax_row.rs:1
     assert int(eng.download_bits(o2)[0, 0]) == H.host_argmax(v) != first
     for i in (ia, out, iv, o2):
         eng.free(i)
+
+
+def test_softmax_rows_as_bf16_is_the_f32_result_narrowed(eng):  # the `_as` pattern: one rounding, no F32 written
+    for shape in [(64, 512), (16, 2048), (4, 8192), (3, 12288), (5, 100)]:
+        x = orc.uniform(0x50, 7, shape, -4, 4)
+        mask = (orc.integers(0x50, 8, (shape[0], shape[1]), 4) == 0).astype(np.uint32)
+        ix, im = eng.upload(x, *shape), eng.upload_bits(mask, *shape, BOOL)
+        f, _ = eng.softmax_rows(ix, im, 0.5)
+        b, dims = eng.softmax_rows_as(ix, im, 0.5, True)
+        assert dims == shape
+        assert np.array_equal(eng.download_bf16(b), orc.to_bf16(eng.download(f))), shape
+        for i in (ix, im, f, b):
+            eng.free(i)
