@@ -348,6 +348,12 @@ def callers(eng, timed):
     for i in losses:
         eng.free(i)
     res["mlp_step_64x784x128x10"] = {"ms": ms, "launches_per_step": int(per), "loss_first": first, "loss_last": last}
+    tm = W.MlpStep(eng, u((784, 128), k1), u((128,), k1), u((128, 10), k2), u((10,), k2), in_place=True)
+    tl = tm.capture(x, y, 64)
+    ms = timed(tm.replay, reps=200, warm=5)
+    res["mlp_step_64x784x128x10"]["traced_ms"] = ms
+    res["mlp_step_64x784x128x10"]["traced_loss_last"] = float(eng.download(tl)[0, 0])
+    eng.release_trace(tm.trace); eng.free(tl)
 
     cfg = W.LlamaConfig()
     batch, seq = 8, 512
@@ -366,8 +372,14 @@ def callers(eng, timed):
     for lg, am in outs:
         eng.free(lg); eng.free(am)
     fl = model.flops()
-    res["smollm2_135m_prefill_8x512"] = {"ms": ms, "tok_per_s": batch * seq / (ms * 1e-3), "launches": int(per),
-                                         "tflops": fl / ms / 1e9, "argmax_stable": a0 == a1, "next_tokens": a1}
+    tlg, tam = model.capture(ids)
+    tms = timed(model.replay, reps=10, warm=2)
+    a2 = eng.download_bits(tam).ravel().tolist()
+    eng.release_trace(model.trace); eng.free(tlg); eng.free(tam)
+    res["smollm2_135m_prefill_8x512"] = {"ms": tms, "tok_per_s": batch * seq / (tms * 1e-3), "launches": int(per),
+                                         "tflops": fl / tms / 1e9, "mode": "traced (CUDA graph replay)",
+                                         "eager_ms": ms, "eager_tok_per_s": batch * seq / (ms * 1e-3),
+                                         "argmax_stable": a0 == a1 == a2, "next_tokens": a1}
 
     bh, t, d = 256, 2048, 128
     bf = lambda: ((rng.standard_normal((bh * t, d), dtype=np.float32)).view(np.uint32) >> 16).astype(np.uint16)

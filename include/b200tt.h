@@ -231,6 +231,17 @@ int32_t b200_copy_blocks(b200_engine*, b200_buffer a, const b200_block_move* mov
 int32_t b200_repack(b200_engine*, b200_buffer a, const uint64_t* row_col_pairs, const uint64_t dims[2],
                     b200_buffer* out, uint64_t out_dims[2]);
 
+/* --- traces: server.rs:591 `begin_trace`, :595 `end_trace`, :650 `run_trace`, :660 `release_trace`.
+ * Ops issued between begin and end are captured into a CUDA graph instead of running; a replay
+ * runs them again on the same buffers.  Inputs are buffers made before the capture (refresh them
+ * with b200_write_* or b200_copy_into), outputs are buffers made during it and still live at
+ * end_trace (read them after each replay).  Run the same ops once before capturing, so every
+ * kernel is loaded.  No upload, download or sync may be issued inside a capture. */
+int32_t b200_begin_trace(b200_engine*);
+int32_t b200_end_trace(b200_engine*, uint64_t* trace);
+int32_t b200_run_trace(b200_engine*, uint64_t trace);
+void    b200_release_trace(b200_engine*, uint64_t trace);
+
 /* --- waits and observability: lib.rs:218 `sync`, server.rs:584,663 --- */
 int32_t b200_sync(b200_engine*);
 void    b200_set_op_label(b200_engine*, const char* label);

@@ -32,6 +32,8 @@ SOURCES = {
     "k_index.cu": [],
     "k_gemm_simt.cu": [],
     "k_gemm_tc.cu": [],
+    "k_gemm_tf32.cu": [],
+    "k_gemm_tc2.cu": [],
 }
 
 

@@ -64,6 +64,23 @@ struct b200_engine {
   std::unordered_map<b200_buffer, Buf> bufs;
   std::multimap<uint64_t, void*> cache;  // free blocks by size
   float* full_scratch = nullptr;
+  // Traces (CUDA graphs): the counterpart of the reference's begin_trace / end_trace / run_trace
+  // (crates/burn-tt/src/server.rs:591-660).  While one is captured, every block the ops take is
+  // owned by the trace: a replay writes the same addresses, so they must not go back to the pool
+  // before the trace is released.
+  struct Trace {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    std::vector<std::pair<void*, uint64_t>> blocks;   // every block the capture took
+    std::vector<void*> pinned;                        // host copies of block lists the graph re-uploads
+    uint64_t launches = 0;
+  };
+  bool capturing = false;
+  Trace cur;                                          // the trace being captured
+  std::multimap<uint64_t, void*> cur_free;            // its blocks free for reuse inside the capture
+  std::unordered_map<void*, uint64_t> cur_owned;      // ptr -> size of blocks the capture owns
+  std::unordered_map<uint64_t, Trace> traces;
+  uint64_t next_trace = 1;
 
   int fail(int code, const char* fmt, ...) {
     char tmp[512];
@@ -103,6 +120,16 @@ struct b200_engine {
       oom[0] = sz; oom[1] = 0; oom[2] = 0;
       return fail(B200_OUT_OF_MEMORY, "out of device memory: need %llu bytes (injected)", (unsigned long long)sz);
     }
+    if (capturing) {
+      auto ft = cur_free.lower_bound(sz);
+      if (ft != cur_free.end() && ft->first <= sz + sz / 4) {
+        *out = ft->second; *got = ft->first;
+        cur_free.erase(ft);
+        traffic.pool_in_use += *got;
+        traffic.pool_high_water = std::max(traffic.pool_high_water, traffic.pool_in_use);
+        return B200_OK;
+      }
+    }
     auto it = cache.lower_bound(sz);
     if (it != cache.end() && it->first <= sz + sz / 4) {
       *out = it->second;
@@ -137,12 +164,23 @@ struct b200_engine {
     }
     traffic.pool_in_use += *got;
     traffic.pool_high_water = std::max(traffic.pool_high_water, traffic.pool_in_use);
+    if (capturing) { cur.blocks.emplace_back(*out, *got); cur_owned.emplace(*out, *got); }
     return B200_OK;
+  }
+  // Whether a block belongs to a trace (captured or being captured): such a block never
+  // returns to the pool while its trace lives.
+  bool trace_owned(void* p) const {
+    if (cur_owned.count(p)) return true;
+    for (auto& kv : traces)
+      for (auto& b : kv.second.blocks) if (b.first == p) return true;
+    return false;
   }
   // The block returns to the cache at once: every user of it was enqueued on the one
   // stream before this call, and so is every later user.
   void release(void* p, uint64_t sz) {
     traffic.pool_in_use -= sz;
+    if (capturing && cur_owned.count(p)) { cur_free.emplace(sz, p); return; }
+    if (!traces.empty() && trace_owned(p)) return;   // its trace keeps it
     cache.emplace(sz, p);
   }
 
@@ -191,6 +229,13 @@ struct b200_engine {
   int to_device(const void* host, uint64_t bytes, void** dev, uint64_t* got) {
     int st = alloc(bytes, dev, got);
     if (st) return st;
+    if (capturing) {
+      void* pin = nullptr;
+      if (cudaMallocHost(&pin, bytes) != cudaSuccess) { cudaGetLastError(); release(*dev, *got); return fail(B200_OUT_OF_MEMORY, "trace: no pinned memory for a block list"); }
+      memcpy(pin, host, bytes);
+      cur.pinned.push_back(pin);
+      host = pin;
+    }
     cudaError_t e = cudaMemcpyAsync(*dev, host, bytes, cudaMemcpyHostToDevice, stream);
     if (e != cudaSuccess) { release(*dev, *got); return cuda_fail(e, "metadata upload"); }
     traffic.bytes_h2d += bytes;
@@ -200,9 +245,11 @@ struct b200_engine {
     if (e == cudaErrorNotSupported) return fail(B200_UNSUPPORTED, "%s: unsupported", what);
     if (e != cudaSuccess) return cuda_fail(e, what);
     traffic.launches += n;
+    if (capturing) cur.launches += n;
     return B200_OK;
   }
   int wait() {
+    if (capturing) return fail(B200_UNSUPPORTED, "a wait (download or sync) inside a trace capture");
     cudaError_t e = cudaMemcpyAsync(h_err, d_err, sizeof(int), cudaMemcpyDeviceToHost, stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) {
@@ -229,6 +276,7 @@ bool host_is_pinned(const void* p) {
 
 int upload_any(b200_engine* e, const void* src, uint64_t rows, uint64_t cols, int elem, b200_buffer* out) {
   cudaSetDevice(e->device);
+  if (e->capturing) return e->fail(B200_UNSUPPORTED, "upload inside a trace capture: upload before begin_trace and refresh with write");
   Buf* b = nullptr;
   int st = e->new_buffer(rows, cols, elem, out, &b);
   if (st) return st;
@@ -247,6 +295,7 @@ int upload_any(b200_engine* e, const void* src, uint64_t rows, uint64_t cols, in
 
 int download_any(b200_engine* e, b200_buffer id, void* dst, uint64_t cap, int want_bytes, const char* what) {
   cudaSetDevice(e->device);
+  if (e->capturing) return e->fail(B200_UNSUPPORTED, "%s inside a trace capture", what);
   Buf* b = nullptr;
   int st = e->need(id, &b, what);
   if (st) return st;
@@ -409,6 +458,19 @@ void b200_engine_destroy(b200_engine* e) {
   if (!e) return;
   cudaSetDevice(e->device);
   cudaStreamSynchronize(e->stream);
+  if (e->capturing) { cudaGraph_t g = nullptr; cudaStreamEndCapture(e->stream, &g); if (g) cudaGraphDestroy(g); cudaGetLastError(); }
+  for (auto& kv : e->traces) {
+    if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+    if (kv.second.graph) cudaGraphDestroy(kv.second.graph);
+    for (void* h : kv.second.pinned) cudaFreeHost(h);
+    for (auto& b : kv.second.blocks) e->cache.emplace(b.second, b.first);  // freed with the cache below
+  }
+  for (auto it = e->bufs.begin(); it != e->bufs.end();) {  // buffers living in trace blocks are freed with them
+    bool owned = false;
+    for (auto& kv : e->traces) for (auto& b : kv.second.blocks) if (b.first == it->second.ptr) owned = true;
+    it = owned ? e->bufs.erase(it) : std::next(it);
+  }
+  e->traces.clear();
   for (auto& kv : e->bufs)
     if (!kv.second.parent && !kv.second.adopted && kv.second.ptr) cudaFree(kv.second.ptr);
   for (auto& kv : e->cache) cudaFree(kv.second);
@@ -513,6 +575,7 @@ int32_t b200_copy_into(b200_engine* e, b200_buffer src, b200_buffer dst) {
 }
 static int write_any(b200_engine* e, b200_buffer id, const void* v, uint64_t n, int eb) {
   cudaSetDevice(e->device);
+  if (e->capturing) return e->fail(B200_UNSUPPORTED, "write inside a trace capture");
   Buf* b = nullptr;
   int st = e->need(id, &b, "write");
   if (st) return st;
@@ -542,6 +605,30 @@ static int run_gemm(b200_engine* e, GemmArgs& g, const GemmBatch* batches_host, 
   }
   if (g.in_bf16 && e->cfg.bf16_matmul_mode == 2)
     return e->fail(B200_UNSUPPORTED, "%s: the tcgen05 path refuses this product (%s) and the engine is set to use no other", what, why);
+  // F32 operands: the split-TF32 tensor-core kernel for products large enough to pay for the
+  // split (automatic from 256^3 up), else FMA.  f32_matmul_mode 1 = FMA only, 2 = tensor only.
+  if (!g.in_bf16 && e->cfg.f32_matmul_mode != 1) {
+    const bool big = g.m >= 256 && g.n >= 256 && g.k >= 256;
+    if ((big || e->cfg.f32_matmul_mode == 2) && gemm_tf32_supported(g, &why)) {
+      const uint64_t a_rows = g.a_trans ? g.k : g.m, b_rows = g.b_trans ? g.n : g.k;
+      const uint64_t na = a_rows * g.lda * 4, nb = b_rows * g.ldb * 4;
+      void* t[4] = {nullptr, nullptr, nullptr, nullptr};
+      uint64_t got[4] = {0, 0, 0, 0};
+      int st = B200_OK;
+      for (int i = 0; i < 4 && !st; ++i) st = e->alloc(i < 2 ? na : nb, &t[i], &got[i]);
+      cudaError_t ce = cudaErrorMemoryAllocation;
+      if (!st) ce = launch_gemm_tf32(g, t[0], t[1], t[2], t[3], e->d_err, e->stream);
+      for (int i = 0; i < 4; ++i) if (t[i]) e->release(t[i], got[i]);
+      if (st) return st;
+      if (ce != cudaErrorNotSupported) {
+        e->matmul_path = "tcgen05-tf32x3";
+        return e->launched(ce, what, 3);
+      }
+      why = "the driver refused a tensor map for this shape";
+    }
+    if (e->cfg.f32_matmul_mode == 2)
+      return e->fail(B200_UNSUPPORTED, "%s: the split-TF32 path refuses this product (%s) and the engine is set to use no other", what, why);
+  }
   e->matmul_path = "simt";
   return e->launched(launch_gemm_simt(g, e->stream), what);
 }
@@ -1165,6 +1252,74 @@ int32_t b200_repack(b200_engine* e, b200_buffer a, const uint64_t* pairs, const 
   }
   set_dims(out_dims, dims[0], dims[1]);
   return B200_OK;
+}
+
+// ---- traces: server.rs:591-660 ---------------------------------------------------
+int32_t b200_begin_trace(b200_engine* e) {
+  cudaSetDevice(e->device);
+  if (e->capturing) return e->fail(B200_UNSUPPORTED, "begin_trace: a capture is already open");
+  int st = e->wait();  // nothing pending, no earlier failure
+  if (st) return st;
+  cudaError_t ce = cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeRelaxed);
+  if (ce != cudaSuccess) return e->cuda_fail(ce, "begin_trace");
+  e->capturing = true;
+  e->cur = b200_engine::Trace();
+  e->cur_free.clear();
+  e->cur_owned.clear();
+  return B200_OK;
+}
+
+int32_t b200_end_trace(b200_engine* e, uint64_t* trace) {
+  cudaSetDevice(e->device);
+  if (!e->capturing) return e->fail(B200_UNSUPPORTED, "end_trace: no capture is open");
+  e->capturing = false;
+  cudaGraph_t g = nullptr;
+  cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
+  if (ce == cudaSuccess) { e->cur.graph = g; ce = cudaGraphInstantiate(&e->cur.exec, g, 0); }
+  if (ce != cudaSuccess) {
+    cudaGetLastError();
+    if (g) cudaGraphDestroy(g);
+    for (void* h : e->cur.pinned) cudaFreeHost(h);
+    // the blocks go back to the pool; buffers made during the failed capture stay valid
+    for (auto& kv : e->cur_free) e->cache.emplace(kv.first, kv.second);
+    e->cur_free.clear(); e->cur_owned.clear();
+    return e->cuda_fail(ce, "end_trace");
+  }
+  e->cur_free.clear();
+  e->cur_owned.clear();
+  *trace = e->next_trace++;
+  e->traces.emplace(*trace, std::move(e->cur));
+  e->cur = b200_engine::Trace();
+  return B200_OK;
+}
+
+int32_t b200_run_trace(b200_engine* e, uint64_t trace) {
+  cudaSetDevice(e->device);
+  if (e->capturing) return e->fail(B200_UNSUPPORTED, "run_trace inside a capture");
+  auto it = e->traces.find(trace);
+  if (it == e->traces.end()) return e->fail(B200_STALE, "run_trace: no trace %llu", (unsigned long long)trace);
+  cudaError_t ce = cudaGraphLaunch(it->second.exec, e->stream);
+  if (ce != cudaSuccess) return e->cuda_fail(ce, "run_trace");
+  e->traffic.launches += it->second.launches;
+  return B200_OK;
+}
+
+void b200_release_trace(b200_engine* e, uint64_t trace) {
+  cudaSetDevice(e->device);
+  auto it = e->traces.find(trace);
+  if (it == e->traces.end()) return;
+  cudaStreamSynchronize(e->stream);
+  b200_engine::Trace t = std::move(it->second);
+  e->traces.erase(it);
+  if (t.exec) cudaGraphExecDestroy(t.exec);
+  if (t.graph) cudaGraphDestroy(t.graph);
+  for (void* h : t.pinned) cudaFreeHost(h);
+  // Blocks no live buffer sits in return to the pool; the rest return when their buffer is freed.
+  for (auto& b : t.blocks) {
+    bool live = false;
+    for (auto& kv : e->bufs) if (kv.second.ptr == b.first && !kv.second.parent) { live = true; break; }
+    if (!live) e->cache.emplace(b.second, b.first);
+  }
 }
 
 // ---- waits and observability ---------------------------------------------------

@@ -1,0 +1,301 @@
+// BF16 product on CTA pairs: tcgen05.mma.cta_group::2, one 256 x 256 output tile a pair.
+// Same contract as k_gemm_tc.cu (`Engine::matmul_dram_bf16`, crates/burn-tt/src/server.rs:191);
+// the engine takes this kernel for one large product and the single-CTA kernel otherwise.
+//
+// The two CTAs of a cluster each hold 128 rows of A and 128 columns of B for a k-block
+// (32 KB a stage instead of 48 KB, so six stages fit and the operand traffic from L2 into an SM
+// drops by a third).  The even CTA (the leader) issues every MMA; the instruction reads both
+// CTAs' shared memory and writes both CTAs' tensor memory (each CTA ends with its own 128 rows
+// of the 256 x 256 tile).  Barriers:
+//   full[s]   lives in the leader; both CTAs' TMA loads complete their bytes on it
+//             (cp.async.bulk.tensor ... .cta_group::2, no multicast);
+//   empty[s]  one in each CTA; the leader's tcgen05.commit arrives on both;
+//   acc_full  one in each CTA, also signalled by the leader's commit;
+//   acc_empty lives in the leader; the eight epilogue warps of the pair arrive on it.
+// Every wait is bounded; on a timeout the engine's error word is set to TIMEOUT and every
+// thread still reaches the closing cluster barrier, after which tensor memory is freed.
+#include <cooperative_groups.h>
+
+#include "tc_common.cuh"
+
+namespace b200 {
+namespace {
+
+using namespace tc;
+
+constexpr int P_BN = 256;     // tile columns of the pair
+constexpr int P_HALF = 128;   // B columns a CTA loads
+constexpr int P_STAGES = 6;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load into this CTA's shared memory; the bytes complete on the barrier at `bar_cluster_addr`
+// (the leader's), which .cta_group::2 allows to lie in the peer CTA.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int32_t c0, int32_t c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrive on the barrier at the same offset in both CTAs of the pair once the MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
+  constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = P_HALF * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + P_STAGES * STAGE_BYTES);
+  uint64_t* empty = full + P_STAGES;
+  uint64_t* acc_full = empty + P_STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();   // 0: leader
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  cluster_sync_all();  // both CTAs' barriers exist before anything remote touches them
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  const uint64_t total_tiles = (uint64_t)p.tiles_m * p.tiles_n;  // tiles of 256 x 256
+  const uint32_t num_kb = (uint32_t)((p.k + BK - 1) / BK);
+  const uint64_t cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---------------- TMA producer (both CTAs) ----------------
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (uint64_t t = cluster_id; t < total_tiles && ok; t += n_clusters) {
+        uint64_t b; uint32_t tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, &b, &tm, &tn);
+        const int32_t m0 = (int32_t)(tm * 256 + rank * BM), n0 = (int32_t)(tn * P_BN + rank * P_HALF);
+        for (uint32_t kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);  // the pair's bytes
+          const uint32_t bar = map_to_rank(smem_u32(&full[stage]), 0);
+          const int32_t k0 = (int32_t)(kb * BK);
+          if constexpr (!A_MN) {
+            tma_load_2d_pair(sa, &map_a, bar, k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * 8192, &map_a, bar, m0 + j * 64, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d_pair(sb, &map_b, bar, k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < P_HALF / 64; ++j) tma_load_2d_pair(sb + j * 8192, &map_b, bar, n0 + j * 64, k0);
+          }
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        atomicCAS(p.err, 0, TIMEOUT_CODE);
+        *abort_flag = 1;
+        const long long t0 = clock64();       // let copies already issued land before the CTA leaves
+        while (clock64() - t0 < 2000000ll) {}
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {  // ---------------- MMA issuer (leader only) ----------------
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                                 ((uint32_t)(P_BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+      uint32_t stage = 0, phase = 0, local = 0;
+      bool ok = true;
+      for (uint64_t t = cluster_id; t < total_tiles && ok; t += n_clusters, ++local) {
+        const uint32_t acc = local & 1, acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t d_tmem = tmem_base + acc * P_BN;
+        for (uint32_t kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t adesc = A_MN ? make_desc(sa + kk * 2048, 8192, 1024) : make_desc(sa + kk * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_desc(sb + kk * 2048, 8192, 1024) : make_desc(sb + kk * 32, 16, 1024);
+            umma_bf16_pair(d_tmem, adesc, bdesc, idesc, (kb | (uint32_t)kk) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[stage]);
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_pair(&acc_full[acc]);
+      }
+      if (!ok) { atomicCAS(p.err, 0, TIMEOUT_CODE); *abort_flag = 1; }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
+    const uint32_t quad = warp & 3;
+    uint32_t local = 0;
+    bool ok = true;
+    for (uint64_t t = cluster_id; t < total_tiles && ok; t += n_clusters, ++local) {
+      uint64_t b; uint32_t tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, &b, &tm, &tn);
+      const uint32_t acc = local & 1, acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint64_t row = (uint64_t)tm * 256 + rank * BM + quad * 32 + lane;
+      const uint64_t n0 = (uint64_t)tn * P_BN;
+      const bool row_ok = row < p.m;
+#pragma unroll 1
+      for (int cb = 0; cb < P_BN / 32; ++cb) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((quad * 32u) << 16) + acc * P_BN + cb * 32, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const uint64_t col = n0 + cb * 32;
+        if (row_ok && col < p.n) {
+          const uint64_t o = row * p.ldc + col;
+          if (p.out_bf16) {
+            uint16_t* dst = (uint16_t*)p.c + o;
+            if (col + 32 <= p.n && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 w;
+                w.x = (uint32_t)f32_to_bf16_bits(v[q * 8 + 0]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 1]) << 16);
+                w.y = (uint32_t)f32_to_bf16_bits(v[q * 8 + 2]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 3]) << 16);
+                w.z = (uint32_t)f32_to_bf16_bits(v[q * 8 + 4]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 5]) << 16);
+                w.w = (uint32_t)f32_to_bf16_bits(v[q * 8 + 6]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 7]) << 16);
+                *reinterpret_cast<uint4*>(dst + q * 8) = w;
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < p.n; ++j) dst[j] = f32_to_bf16_bits(v[j]);
+            }
+          } else {
+            uint32_t* dst = (uint32_t*)p.c + o;
+            if (col + 32 <= p.n && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<uint4*>(dst + q * 4) = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+            } else {
+              for (int j = 0; j < 32 && col + j < p.n; ++j) dst[j] = v[j];
+            }
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(map_to_rank(smem_u32(&acc_empty[acc]), 0));
+    }
+    if (!ok && lane == 0) { atomicCAS(p.err, 0, TIMEOUT_CODE); *abort_flag = 1; }
+  }
+
+  // No CTA may leave (or free tensor memory) while its peer can still read its shared memory,
+  // write its tensor memory or signal its barriers.
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  cluster_sync_all();
+  if (warp == 0) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+}  // namespace
+
+// Whether the pair kernel should take this product: one product whose 256 x 256 tiles fill the
+// clusters at least once.  B200TT_PAIR=0 / 1 overrides (development switch).
+constexpr bool kPairByDefault = false;  // until its parity tests are green on hardware
+
+bool gemm_tc2_wanted(const GemmArgs& g) {
+  static int force = -2;
+  if (force == -2) { const char* e = getenv("B200TT_PAIR"); force = e ? atoi(e) : -1; }
+  if (g.batch > 1 || g.m < 256 || g.n < 256 || g.k < 64) return false;
+  if (force == 0) return false;
+  if (force == 1) return true;
+  return kPairByDefault && ((g.m + 255) / 256) * ((g.n + 255) / 256) >= 64;
+}
+
+cudaError_t launch_gemm_tc2(const GemmArgs& g, int* err_word, cudaStream_t stream) {
+  const bool a_mn = g.a_trans != 0, b_mn = g.b_trans == 0;
+  const uint64_t a_rows = a_mn ? g.k : g.m, a_cols = a_mn ? g.m : g.k;
+  const uint64_t b_rows = b_mn ? g.k : g.n, b_cols = b_mn ? g.n : g.k;
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, g.a, a_rows, a_cols, g.lda, a_mn ? 64 : BM)) return cudaErrorNotSupported;
+  if (!make_map(&mb, g.b, b_rows, b_cols, g.ldb, b_mn ? 64 : P_HALF)) return cudaErrorNotSupported;
+  TcParams p{};
+  p.m = g.m; p.n = g.n; p.k = g.k;
+  p.lda = g.lda; p.ldb = g.ldb; p.ldc = g.ldc;
+  p.tiles_m = (uint32_t)((g.m + 255) / 256);
+  p.tiles_n = (uint32_t)((g.n + P_BN - 1) / P_BN);
+  p.batch = 1; p.batches = nullptr;
+  p.c = g.c; p.out_bf16 = g.out_bf16; p.err = err_word;
+  constexpr size_t smem = (size_t)P_STAGES * (BM * BK * 2 + P_HALF * BK * 2) + 1024 + 256;
+  const uint64_t total = (uint64_t)p.tiles_m * p.tiles_n;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  cudaError_t e = cudaSuccess;
+#define TC2_LAUNCH(AM, BMJ)                                                                           \
+  do {                                                                                                \
+    static int clusters = 0;                                                                          \
+    if (!clusters) {                                                                                  \
+      e = cudaFuncSetAttribute(gemm_tc2_kernel<AM, BMJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return e;                                                                 \
+      cfg.gridDim = dim3(148, 1, 1);                                                                  \
+      int n = 0;                                                                                      \
+      e = cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<AM, BMJ>, &cfg);                         \
+      if (e != cudaSuccess || n <= 0) { cudaGetLastError(); return cudaErrorNotSupported; }           \
+      clusters = n;                                                                                   \
+    }                                                                                                 \
+    const uint64_t use = total < (uint64_t)clusters ? total : (uint64_t)clusters;                     \
+    cfg.gridDim = dim3((unsigned)(2 * use), 1, 1);                                                    \
+    e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<AM, BMJ>, ma, mb, p);                                \
+  } while (0)
+  if (!a_mn && !b_mn) TC2_LAUNCH(false, false);
+  else if (!a_mn && b_mn) TC2_LAUNCH(false, true);
+  else if (a_mn && !b_mn) TC2_LAUNCH(true, false);
+  else TC2_LAUNCH(true, true);
+#undef TC2_LAUNCH
+  return e;
+}
+
+}  // namespace b200

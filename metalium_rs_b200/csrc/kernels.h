@@ -107,6 +107,15 @@ bool gemm_tc_supported(const GemmArgs& g, const char** why);
 cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int* err_word,
                            cudaStream_t stream);
 
+// CTA-pair (cta_group::2) variant of the BF16 tensor-core product, for one large product.
+bool gemm_tc2_wanted(const GemmArgs& g);
+cudaError_t launch_gemm_tc2(const GemmArgs& g, int* err_word, cudaStream_t stream);
+
+// Split-TF32 tensor-core path for F32 operands; the four scratch matrices have the operands' sizes.
+bool gemm_tf32_supported(const GemmArgs& g, const char** why);
+cudaError_t launch_gemm_tf32(const GemmArgs& g, void* a_hi, void* a_lo, void* b_hi, void* b_lo, int* err_word,
+                             cudaStream_t stream);
+
 // Text for `b200_last_error(NULL, ...)`: failures of calls that take no engine.
 void set_global_error(const char* text);
 

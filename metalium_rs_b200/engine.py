@@ -93,6 +93,7 @@ def load_library() -> C.CDLL:
         _lib.b200_set_op_label.restype = None
         _lib.b200_traffic_get.restype = None
         _lib.b200_last_oom.restype = None
+        _lib.b200_release_trace.restype = None
     return _lib
 
 
@@ -428,6 +429,21 @@ class CudaEngine:
         src = np.ascontiguousarray(sources, dtype=np.uint64).reshape(-1)
         assert src.size == 2 * dims[0] * dims[1]
         return self._call(self._lib.b200_repack, C.c_uint64(a), _ptr(src), (C.c_uint64 * 2)(*dims))
+
+    # -- traces (server.rs:591-660) ------------------------------------------------------------
+    def begin_trace(self):
+        self._check(self._lib.b200_begin_trace(self._e))
+
+    def end_trace(self) -> int:
+        t = C.c_uint64()
+        self._check(self._lib.b200_end_trace(self._e, C.byref(t)))
+        return t.value
+
+    def run_trace(self, trace: int):
+        self._check(self._lib.b200_run_trace(self._e, C.c_uint64(trace)))
+
+    def release_trace(self, trace: int):
+        self._lib.b200_release_trace(self._e, C.c_uint64(trace))
 
     # -- waits and observability (lib.rs:218, server.rs:584,663) ---------------------------
     def sync(self):

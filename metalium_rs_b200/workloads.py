@@ -33,8 +33,11 @@ class MlpStep:
     """x [n,784] -> Linear(784,h) -> ReLU -> Linear(h,10) -> softmax cross-entropy, backward, SGD.
     Weights live on the device and are replaced by their updates each step."""
 
-    def __init__(self, eng, w1, b1, w2, b2, lr=0.01, fused_add_relu=True):
-        self.eng, self.lr, self.fused = eng, float(lr), fused_add_relu
+    def __init__(self, eng, w1, b1, w2, b2, lr=0.01, fused_add_relu=True, in_place=False):
+        # in_place: the update is copied over the old weights, so they keep their addresses
+        # (what a captured trace needs to train when it is replayed)
+        self.eng, self.lr, self.fused, self.in_place = eng, float(lr), fused_add_relu, in_place
+        self.trace = None
         self.w1 = eng.upload(w1, *w1.shape)
         self.b1 = eng.upload(b1.reshape(1, -1), 1, b1.size)
         self.w2 = eng.upload(w2, *w2.shape)
@@ -79,8 +82,11 @@ class MlpStep:
         for name, grad in (("w1", dw1), ("b1", db1), ("w2", dw2), ("b2", db2)):
             scaled = self._el(K.MUL_SCALAR, grad, s=self.lr)
             new = self._el(K.SUB, getattr(self, name), scaled)
-            e.free(getattr(self, name)); e.free(scaled)
-            setattr(self, name, new)
+            e.free(scaled)
+            if self.in_place:
+                e.copy_into(new, getattr(self, name)); e.free(new)
+            else:
+                e.free(getattr(self, name)); setattr(self, name, new)
         free += [pre, z0, logp, picked, neg, zeros, gval, zl, g, p, gs, pg, dh, h]
         out = {"loss": loss}
         if keep:
@@ -90,6 +96,22 @@ class MlpStep:
         for i in free:
             e.free(i)
         return out
+
+
+    def capture(self, x_buf: int, labels_buf: int, n: int) -> int:
+        """Run one step eagerly (loads every kernel), then capture the next as a trace
+        (crates/burn-tt/src/trace.rs; server.rs:591-660).  Returns the loss buffer the replays
+        write; `replay()` runs one more training step on whatever x_buf / labels_buf hold."""
+        assert self.in_place, "a replayed step must update the weights where they lie"
+        e = self.eng
+        e.free(self.step(x_buf, labels_buf, n)["loss"])
+        e.begin_trace()
+        loss = self.step(x_buf, labels_buf, n)["loss"]
+        self.trace = e.end_trace()
+        return loss
+
+    def replay(self):
+        self.eng.run_trace(self.trace)
 
 
 # ------------------------------------------------------------------------- config 4
@@ -213,6 +235,20 @@ class LlamaPrefill:
         e.free(fn)
         am, _ = e.argmax_row(logits)                                         # generate::argmax
         return logits, am
+
+    def capture(self, ids_buf: int):
+        """One eager pass, then the forward captured as a trace.  Returns (logits, argmax)
+        buffers that every `replay()` rewrites from the ids then in `ids_buf`."""
+        e = self.eng
+        lg, am = self.forward(ids_buf)
+        e.free(lg); e.free(am)
+        e.begin_trace()
+        out = self.forward(ids_buf)
+        self.trace = e.end_trace()
+        return out
+
+    def replay(self):
+        self.eng.run_trace(self.trace)
 
     def flops(self, all_positions=False) -> float:
         c, n, t = self.cfg, self.batch * self.seq, self.seq

@@ -1,0 +1,64 @@
+"""Writes tests/golden/hot_path.npz: outputs of the CPU oracle on small seeded inputs.
+
+The reference's own golden file (crates/tt-tests/tests/golden/mnist_reduced.txt) pins Tensix
+TF32 bits on MNIST and cannot be reproduced on a GPU, and the reference (Rust) cannot be
+imported, so these vectors are the oracle's: committed so that a later change of the oracle,
+or of the engine, shows up against fixed numbers.  Inputs are regenerated from their seeds by
+the tests; only outputs are stored.
+
+    python tests/golden/make_golden.py
+"""
+import sys
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+from oracle import models as M  # noqa: E402
+from oracle import oracle as orc  # noqa: E402
+
+SEED = 0x601D
+EXACT_KINDS = ["ADD", "SUB", "MUL", "DIV", "RECIP", "SQRT", "RELU", "RELU_BACKWARD", "NEG", "ABS", "ADD_RELU", "MUL_ADD",
+               "CLAMP_MIN", "GT", "FLOOR", "ROUND", "LEAKY_RELU"]
+APPROX_KINDS = ["EXP", "LOG", "SIGMOID", "SILU", "SILU_MUL", "TANH", "GELU", "GELU_TANH", "SUB_EXP"]
+
+
+def inputs():
+    a = orc.uniform(SEED, 1, (24, 40), -4, 4)
+    b = orc.uniform(SEED, 2, (24, 40), 0.25, 4)
+    c = orc.uniform(SEED, 3, (24, 40), -4, 4)
+    return a, b, c
+
+
+def build():
+    a, b, c = inputs()
+    out = {}
+    for k in EXACT_KINDS + APPROX_KINDS:
+        src = b if k in ("LOG", "SQRT", "RECIP") else a
+        out["elt_" + k] = orc.eltwise(k, src, b, c, 0.5, 1.5)
+    out["bf16"] = orc.to_bf16(a)
+    out["sum_rows"] = orc.sum_rows_in_order(a).view(np.uint32)
+    out["max_cols"] = orc.reduce(a, "MAX", 1)
+    out["softmax"] = orc.softmax_rows(a)
+    out["softmax_masked"] = orc.softmax_rows(a, (orc.integers(SEED, 4, (24, 40), 3) == 0).astype(np.uint32), 0.5)
+    out["argmax"] = orc.argmax_rows(a)
+    out["rms_norm"] = orc.rms_norm(a, b[0], 1e-5)
+    cos, sin = orc.rope_tables(24, 8, 10000.0)
+    out["rope"] = orc.rope(a, cos, sin, 8)
+    rng = np.random.default_rng(SEED)
+    ia, ib = rng.integers(-7, 8, (24, 40)).astype(np.float32), rng.integers(-7, 8, (40, 16)).astype(np.float32)
+    out["gemm_int"] = orc.gemm_f32(ia, ib)
+    out["gemm_bf16"] = orc.gemm_bf16(orc.to_bf16(a), orc.to_bf16(b.T.copy()))[0]
+    idx = orc.integers(SEED, 5, (1, 10), 24)
+    out["select_rows"] = orc.select_rows(a, idx).view(np.uint32)
+    x = orc.normal(SEED, 6, (16, 784)); y = orc.integers(SEED, 7, (16, 1), 10)
+    step = M.mlp_step(x, y, *M.mlp_init(seed=SEED))
+    out["mlp_loss"] = np.array([step["loss"]], np.float32)
+    out["mlp_logits"] = step["logits"]
+    return out
+
+
+if __name__ == "__main__":
+    np.savez_compressed(Path(__file__).with_name("hot_path.npz"), **build())
+    print("wrote", Path(__file__).with_name("hot_path.npz"))

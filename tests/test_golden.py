@@ -1,0 +1,89 @@
+"""The committed golden vectors (tests/golden/hot_path.npz, made by tests/golden/make_golden.py):
+the oracle must still reproduce them (no GPU), and the engine must match them through the C ABI."""
+import importlib.util
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from oracle import models as M
+from oracle import oracle as orc
+
+HERE = Path(__file__).resolve().parent
+spec = importlib.util.spec_from_file_location("make_golden", HERE / "golden" / "make_golden.py")
+G = importlib.util.module_from_spec(spec)
+spec.loader.exec_module(G)
+GOLD = np.load(HERE / "golden" / "hot_path.npz")
+
+
+def test_oracle_reproduces_the_golden_vectors():
+    now = G.build()
+    assert sorted(now) == sorted(GOLD.files)
+    for k in GOLD.files:
+        a, b = np.asarray(now[k]), GOLD[k]
+        assert a.shape == b.shape and a.dtype == b.dtype, k
+        same = (a.view(np.uint8) == b.view(np.uint8)).all() if a.dtype.kind != "f" else \
+            np.array_equal(a.view(np.uint32) if a.dtype == np.float32 else a, b.view(np.uint32) if b.dtype == np.float32 else b)
+        assert same, f"{k}: the oracle no longer gives its committed vector"
+
+
+@pytest.mark.gpu
+def test_engine_matches_the_golden_vectors(eng):
+    from metalium_rs_b200 import BOOL, COLS, I32, MAX, ROWS, SUM, EltwiseOp, kinds
+    a, b, c = G.inputs()
+    ia, ib, ic = (eng.upload(x, 24, 40) for x in (a, b, c))
+    for k in G.EXACT_KINDS + G.APPROX_KINDS:
+        src = ib if k in ("LOG", "SQRT", "RECIP") else ia
+        ar = kinds.ARITY[getattr(kinds, k)]
+        out, _ = eng.eltwise_op(EltwiseOp(getattr(kinds, k), 0.5, 1.5), src, ib if ar >= 2 else None, ic if ar == 3 else None)
+        got = eng.download_bits(out)
+        if k in G.EXACT_KINDS:
+            assert np.array_equal(got, GOLD["elt_" + k]), k
+        else:
+            assert orc.ulp_error(got, GOLD["elt_" + k]) <= orc.ULP_BOUND[k] + 1, k
+        eng.free(out)
+    o, _ = eng.cast_float(ia, True)
+    assert np.array_equal(eng.download_bf16(o), GOLD["bf16"]); eng.free(o)
+    o, _ = eng.reduce(ia, SUM, ROWS)
+    assert np.array_equal(eng.download_bits(o), GOLD["sum_rows"]); eng.free(o)
+    o, _ = eng.reduce(ia, MAX, COLS)
+    assert np.array_equal(eng.download_bits(o), GOLD["max_cols"]); eng.free(o)
+    o, _ = eng.softmax_rows(ia, None, 1.0)
+    assert np.max(np.abs(eng.download(o) - GOLD["softmax"]) / GOLD["softmax"]) <= orc.softmax_bound(40); eng.free(o)
+    mask = (orc.integers(G.SEED, 4, (24, 40), 3) == 0).astype(np.uint32)
+    im = eng.upload_bits(mask, 24, 40, BOOL)
+    o, _ = eng.softmax_rows(ia, im, 0.5)
+    got, want = eng.download(o), GOLD["softmax_masked"]
+    assert np.array_equal(got == 0, want == 0)
+    assert np.max(np.abs(got - want)[want > 0] / want[want > 0]) <= orc.softmax_bound(40); eng.free(o)
+    o, _ = eng.argmax_row(ia)
+    assert np.array_equal(eng.download_bits(o).view(np.int32), GOLD["argmax"]); eng.free(o)
+    ig = eng.upload(b[0].reshape(1, -1), 1, 40)
+    o, _ = eng.rms_norm(ia, ig, 1e-5)
+    assert np.max(np.abs(eng.download(o) - GOLD["rms_norm"])) <= 1e-5 * np.abs(GOLD["rms_norm"]).max(); eng.free(o)
+    cos, sin = orc.rope_tables(24, 8, 10000.0)
+    ico, isi = eng.upload(cos, 24, 8), eng.upload(sin, 24, 8)
+    o, _ = eng.rope_blocks((ia, (0, 0), (24, 40)), (ico, (0, 0), (24, 8)), (isi, (0, 0), (24, 8)), 8)
+    assert np.array_equal(eng.download(o).view(np.uint32), GOLD["rope"].view(np.uint32)); eng.free(o)
+    rng = np.random.default_rng(G.SEED)
+    xa, xb = rng.integers(-7, 8, (24, 40)).astype(np.float32), rng.integers(-7, 8, (40, 16)).astype(np.float32)
+    ja, jb = eng.upload(xa, 24, 40), eng.upload(xb, 40, 16)
+    o, _ = eng.matmul_dram(ja, False, jb, False)
+    assert np.array_equal(eng.download(o), GOLD["gemm_int"]); eng.free(o)
+    ha, hb = eng.upload_bf16(orc.to_bf16(a), 24, 40), eng.upload_bf16(orc.to_bf16(b.T.copy()), 40, 24)
+    o, _ = eng.matmul_dram_bf16(ha, False, hb, False)
+    step = np.abs(eng.download_bf16(o).astype(np.int32) - GOLD["gemm_bf16"].astype(np.int32))
+    assert (step <= 1).mean() > 0.99 and (step == 0).mean() > 0.9; eng.free(o)
+    idx = orc.integers(G.SEED, 5, (1, 10), 24)
+    ii = eng.upload_bits(idx.view(np.uint32), 1, 10, I32)
+    o, _ = eng.select_rows(ia, ii)
+    assert np.array_equal(eng.download_bits(o), GOLD["select_rows"]); eng.free(o)
+    from metalium_rs_b200 import workloads as W
+    x = orc.normal(G.SEED, 6, (16, 784)); y = orc.integers(G.SEED, 7, (16, 1), 10)
+    mlp = W.MlpStep(eng, *M.mlp_init(seed=G.SEED))
+    ix, iy = eng.upload(x, 16, 784), eng.upload_bits(y.view(np.uint32), 16, 1, I32)
+    res = mlp.step(ix, iy, 16, keep=True)
+    assert abs(float(eng.download(res["loss"])[0, 0]) - float(GOLD["mlp_loss"][0])) <= 1e-5 * float(GOLD["mlp_loss"][0])
+    assert np.max(np.abs(eng.download(res["logits"]) - GOLD["mlp_logits"])) <= 1e-5
+    for v in list(res.values()) + [ia, ib, ic, im, ig, ico, isi, ja, jb, ha, hb, ii, ix, iy]:
+        eng.free(v)

@@ -232,3 +232,35 @@ def test_short_m_products_take_the_tensor_cores(eng, m):
     assert orc.gemm_rel_error(eng.download(out), truth, s)[0] <= 1e-6
     for i in (ia, it, out):
         eng.free(i)
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("mkn", [(256, 256, 256), (384, 160, 512), (1024, 1024, 1024), (200, 132, 328)])
+def test_f32_products_on_the_split_tf32_tensor_path(lib, mkn, ta, tb):
+    # a = a_hi + a_lo in TF32, three products, FP32 accumulation: F32-grade, not TF32-grade
+    m, k, n = mkn
+    a = orc.uniform(0xC0F2, 11, (k, m) if ta else (m, k), -1, 1)
+    b = orc.uniform(0xC0F2, 12, (n, k) if tb else (k, n), -1, 1)
+    with CudaEngine(0, f32_matmul_mode=2) as e:
+        ia, ib = e.upload(a, *a.shape), e.upload(b, *b.shape)
+        out, dims = e.matmul_dram(ia, ta, ib, tb)
+        assert dims == (m, n) and e.last_matmul_path() == "tcgen05-tf32x3"
+        got = e.download(out)
+    truth, s = orc.gemm_truth(a, b, ta, tb)
+    e_s, _ = orc.gemm_rel_error(got, truth, s)
+    assert e_s <= 2e-6, e_s                        # far inside the contract's 1e-5
+    tf32 = lambda x: (x.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+    lo, _ = orc.gemm_rel_error(orc.gemm_truth(tf32(a), tf32(b), ta, tb)[0], truth, s)
+    assert lo > 10 * e_s                           # negative control: one TF32 product is far worse (step11_burn.rs:197-220)
+
+
+def test_split_tf32_path_is_exact_on_small_integers_and_chosen_automatically(eng):
+    rng = np.random.default_rng(3)
+    a, b = H.small_ints(rng, (512, 320)), H.small_ints(rng, (320, 640))
+    ia, ib = eng.upload(a, 512, 320), eng.upload(b, 320, 640)
+    out, _ = eng.matmul_dram(ia, False, ib, False)
+    assert eng.last_matmul_path() == "tcgen05-tf32x3"
+    assert np.array_equal(eng.download(out), (a.astype(np.int64) @ b.astype(np.int64)).astype(np.float32))
+    small, _ = eng.matmul_dram(ia, True, ia, False)   # [320,512]x[512,320]: still large enough
+    for i in (ia, ib, out, small):
+        eng.free(i)

@@ -119,3 +119,61 @@ def test_attention_products_on_rank4_views(eng):
         assert np.max(np.abs(got[r] - want)) <= 1e-2 * np.max(np.abs(want)), i
     for x in (iq, ik, iv, o):
         eng.free(x)
+
+
+def test_traced_prefill_replays_the_eager_bits(eng):  # server.rs:591-660; trace.rs: replay == eager
+    cfg = small_llama()
+    batch, seq = 2, 128
+    model = W.LlamaPrefill(eng, cfg, W.llama_weights(cfg, seed=7), batch, seq)
+    ids = orc.integers(0xC0F4, 9, (1, batch * seq), cfg.vocab)
+    ids2 = orc.integers(0xC0F4, 10, (1, batch * seq), cfg.vocab)
+    ii = eng.upload_bits(ids.view(np.uint32), 1, batch * seq, I32)
+    i2 = eng.upload_bits(ids2.view(np.uint32), 1, batch * seq, I32)
+    lg, am = model.forward(ii)
+    eager1 = eng.download_bits(lg); eng.free(lg); eng.free(am)
+    lg, am = model.forward(i2)
+    eager2 = eng.download_bits(lg); eng.free(lg); eng.free(am)
+    tl, ta = model.capture(ii)
+    l0 = eng.device_traffic().launches
+    model.replay()
+    per = eng.device_traffic().launches - l0
+    assert per > 40                                   # the replay is counted as the kernels it runs
+    assert np.array_equal(eng.download_bits(tl), eager1)
+    eng.copy_into(i2, ii)                              # new ids into the captured input buffer
+    model.replay()
+    assert np.array_equal(eng.download_bits(tl), eager2)
+    assert np.array_equal(eng.download_bits(ta).view(np.int32).ravel(), eager2.view(np.float32).argmax(1))
+    # other work between replays does not disturb the trace's buffers
+    junk = [eng.upload(np.ones((256, 256), np.float32), 256, 256) for _ in range(8)]
+    for j in junk:
+        eng.free(j)
+    eng.copy_into(i2, ii); model.replay()
+    assert np.array_equal(eng.download_bits(tl), eager2)
+    eng.begin_trace()
+    with pytest.raises(Exception):
+        eng.sync()                                     # a wait inside a capture is refused
+    eng.release_trace(eng.end_trace())
+    eng.release_trace(model.trace)
+    for i in (tl, ta, ii, i2):
+        eng.free(i)
+
+
+def test_traced_mlp_training_matches_eager_training(eng):
+    x = orc.normal(0xC0F1, 0, (64, 784)); labels = orc.integers(0xC0F1, 5, (64, 1), 10)
+    w = M.mlp_init()
+    ix, il = eng.upload(x, 64, 784), eng.upload_bits(labels.view(np.uint32), 64, 1, I32)
+    eager = W.MlpStep(eng, *w, in_place=True)
+    want = []
+    for _ in range(6):
+        o = eager.step(ix, il, 64); want.append(eng.download_bits(o["loss"])[0, 0]); eng.free(o["loss"])
+    traced = W.MlpStep(eng, *w, in_place=True)
+    loss = traced.capture(ix, il, 64)
+    got = []
+    # the capture pass does not execute, so after capture() one step has run
+    for _ in range(5):
+        traced.replay(); got.append(eng.download_bits(loss)[0, 0])
+    assert got == want[1:6]
+    assert want[5].view(np.float32) < want[0].view(np.float32)
+    eng.release_trace(traced.trace)
+    for i in (ix, il, loss):
+        eng.free(i)
