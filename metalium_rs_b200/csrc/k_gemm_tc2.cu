@@ -237,7 +237,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
 // Whether the pair kernel should take this product: one product whose 256 x 256 tiles fill the
 // clusters at least once.  B200TT_PAIR=0 / 1 overrides (development switch).
-constexpr bool kPairByDefault = false;  // until its parity tests are green on hardware
+constexpr bool kPairByDefault = true;
 
 bool gemm_tc2_wanted(const GemmArgs& g) {
   static int force = -2;

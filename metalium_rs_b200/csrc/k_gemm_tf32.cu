@@ -154,12 +154,13 @@ gemm_tf32_kernel(const __grid_constant__ Tf32Maps maps, const TcParams p) {
           const uint32_t sal = sah + A_BYTES, sbh = sal + A_BYTES, sbl = sbh + B_BYTES;
 #pragma unroll
           for (int kk = 0; kk < TBK / 8; ++kk) {
-            // K-major: 32 bytes a step along the row; MN-major: 8 k-rows (1 KB) a step
+            // K-major: 32 bytes a step along the row.  MN-major (128-byte swizzle with 32-byte atoms, four
+            // k-rows an atom, 512 bytes between atoms): 8 k-rows (1 KB) a step
             const uint32_t ao = A_MN ? kk * 1024 : kk * 32, bo = B_MN ? kk * 1024 : kk * 32;
-            const uint64_t ah = A_MN ? make_desc(sah + ao, CHUNK_BYTES, 1024) : make_desc(sah + ao, 16, 1024);
-            const uint64_t al = A_MN ? make_desc(sal + ao, CHUNK_BYTES, 1024) : make_desc(sal + ao, 16, 1024);
-            const uint64_t bh = B_MN ? make_desc(sbh + bo, CHUNK_BYTES, 1024) : make_desc(sbh + bo, 16, 1024);
-            const uint64_t bl = B_MN ? make_desc(sbl + bo, CHUNK_BYTES, 1024) : make_desc(sbl + bo, 16, 1024);
+            const uint64_t ah = A_MN ? make_desc(sah + ao, CHUNK_BYTES, 512, 1) : make_desc(sah + ao, 16, 1024);
+            const uint64_t al = A_MN ? make_desc(sal + ao, CHUNK_BYTES, 512, 1) : make_desc(sal + ao, 16, 1024);
+            const uint64_t bh = B_MN ? make_desc(sbh + bo, CHUNK_BYTES, 512, 1) : make_desc(sbh + bo, 16, 1024);
+            const uint64_t bl = B_MN ? make_desc(sbl + bo, CHUNK_BYTES, 512, 1) : make_desc(sbl + bo, 16, 1024);
             umma_tf32(d_tmem, al, bh, idesc, (kb | (uint32_t)kk) != 0 ? 1u : 0u);  // small terms first
             umma_tf32(d_tmem, ah, bl, idesc, 1u);
             umma_tf32(d_tmem, ah, bh, idesc, 1u);
@@ -252,10 +253,10 @@ cudaError_t launch_gemm_tf32(const GemmArgs& g, void* a_hi, void* a_lo, void* b_
   if (e != cudaSuccess) return e;
 
   Tf32Maps maps;
-  if (!make_map(&maps.a_hi, a_hi, a_rows, a_cols, g.lda, a_mn ? TBK : BM, 4) ||
-      !make_map(&maps.a_lo, a_lo, a_rows, a_cols, g.lda, a_mn ? TBK : BM, 4) ||
-      !make_map(&maps.b_hi, b_hi, b_rows, b_cols, g.ldb, b_mn ? TBK : TBN, 4) ||
-      !make_map(&maps.b_lo, b_lo, b_rows, b_cols, g.ldb, b_mn ? TBK : TBN, 4))
+  if (!make_map(&maps.a_hi, a_hi, a_rows, a_cols, g.lda, a_mn ? TBK : BM, 4, a_mn) ||
+      !make_map(&maps.a_lo, a_lo, a_rows, a_cols, g.lda, a_mn ? TBK : BM, 4, a_mn) ||
+      !make_map(&maps.b_hi, b_hi, b_rows, b_cols, g.ldb, b_mn ? TBK : TBN, 4, b_mn) ||
+      !make_map(&maps.b_lo, b_lo, b_rows, b_cols, g.ldb, b_mn ? TBK : TBN, 4, b_mn))
     return cudaErrorNotSupported;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);

@@ -70,13 +70,15 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
 
 // Shared-memory matrix descriptor (sm_100 UMMA): start address, leading / stride byte
 // offsets (all >> 4), version 1, 128-byte swizzle.
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// layout: 2 = 128-byte swizzle (16-byte atoms), 1 = 128-byte swizzle with 32-byte atoms (the only
+// layout an MN-major 32-bit operand may use).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout = 2) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr >> 4) & 0x3fff);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
   d |= 1ull << 46;  // descriptor version
-  d |= 2ull << 61;  // SWIZZLE_128B
+  d |= (uint64_t)layout << 61;
   return d;
 }
 
@@ -138,7 +140,7 @@ inline EncodeTiledFn encode_fn() {
 // A 2-D tensor map over a stored [rows, cols] matrix of 2-byte (BF16) or 4-byte (F32) elements,
 // box [box_rows, 128 bytes of columns], 128-byte swizzle.
 inline bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
-                     int elem_bytes = 2) {
+                     int elem_bytes = 2, bool atom32 = false) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {cols, rows};
@@ -147,7 +149,7 @@ inline bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
   const cuuint32_t estr[2] = {1, 1};
   return fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

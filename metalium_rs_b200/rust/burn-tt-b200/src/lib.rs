@@ -1,0 +1,299 @@
+//! `impl burn_tt::Engine for CudaEngine`: the B200 engine behind the reference's operator
+//! boundary (crates/burn-tt/src/server.rs:42-786).  Attach it with
+//! `burn_tt::attach(TtDevice::new(0), cuda_factory(0))` (server.rs:2738) or make it the default
+//! with `burn_tt::set_default_engine` (registry.rs:212); nothing above the trait changes.
+//!
+//! Source only: no Rust toolchain exists where this was written, so it has not been compiled.
+//! Every method is one call of include/b200tt.h through `b200-sys`.
+use b200_sys as sys;
+use burn_tt::server::{BlockArg, BufferId, Engine, Serve};
+use burn_tt::TtError;
+use tt_kernels::session::BatchedLayout;
+use tt_kernels::sfpu::reduce::{Axis, ReduceOp};
+use tt_kernels::tensor::{Block, BlockMove, Elem, Eltwise, ReduceThen};
+
+type Made = Result<(BufferId, [usize; 2]), TtError>;
+
+pub struct CudaEngine {
+    raw: *mut sys::b200_engine,
+}
+// Driven by the device's one server thread (server.rs:2801-2820).
+unsafe impl Send for CudaEngine {}
+
+impl Drop for CudaEngine {
+    fn drop(&mut self) {
+        unsafe { sys::b200_engine_destroy(self.raw) }
+    }
+}
+
+fn text(raw: *const sys::b200_engine) -> String {
+    let mut buf = vec![0u8; 1024];
+    let n = unsafe { sys::b200_last_error(raw, buf.as_mut_ptr() as *mut _, buf.len()) };
+    String::from_utf8_lossy(&buf[..n.min(buf.len() - 1)]).into_owned()
+}
+
+impl CudaEngine {
+    pub fn new(ordinal: i32) -> Result<Self, TtError> {
+        let mut raw = std::ptr::null_mut();
+        let cfg = sys::b200_config::default();
+        let st = unsafe { sys::b200_engine_create(ordinal, &cfg, &mut raw) };
+        if st != 0 {
+            return Err(match st {
+                7 => TtError::NoDriver,
+                _ => TtError::Device(text(std::ptr::null())),
+            });
+        }
+        Ok(CudaEngine { raw })
+    }
+
+    /// b200_status -> TtError (crates/burn-tt/src/error.rs:26-67).
+    fn check(&self, st: i32) -> Result<(), TtError> {
+        if st == 0 {
+            return Ok(());
+        }
+        let what = text(self.raw);
+        Err(match st {
+            1 => {
+                let mut o = [0u64; 3];
+                unsafe { sys::b200_last_oom(self.raw, o.as_mut_ptr()) };
+                TtError::OutOfMemory { slots: o[0], free: o[1], largest: o[2] }
+            }
+            2 => TtError::unsupported(what),
+            4 => TtError::Timeout { detail: what },
+            5 => TtError::StaleTensor { id: 0 },
+            _ => TtError::Device(what), // 3 DEVICE, 6 DOMAIN, 7 NO_DEVICE
+        })
+    }
+
+    fn made(&self, st: i32, id: u64, d: [u64; 2]) -> Made {
+        self.check(st)?;
+        Ok((id, [d[0] as usize, d[1] as usize]))
+    }
+
+    fn dims(&self, id: BufferId) -> Result<([usize; 2], i32), TtError> {
+        let (mut d, mut e) = ([0u64; 2], 0i32);
+        if unsafe { sys::b200_dims(self.raw, id, d.as_mut_ptr(), &mut e) } != 0 {
+            return Err(TtError::StaleTensor { id });
+        }
+        Ok(([d[0] as usize, d[1] as usize], e))
+    }
+}
+
+fn elem_code(elem: Elem, bf16: bool) -> i32 {
+    if bf16 {
+        return 3;
+    }
+    match elem {
+        Elem::F32 => 0,
+        Elem::I32 => 1,
+        Elem::Bool => 2,
+        Elem::Packed(_) => 3,
+    }
+}
+fn block(b: &Block) -> sys::b200_block {
+    sys::b200_block { at: [b.at[0] as u64, b.at[1] as u64], transposed: b.transposed as i32, _pad: 0 }
+}
+fn arg(b: &BlockArg) -> sys::b200_block_arg {
+    sys::b200_block_arg { id: b.id, at: [b.at[0] as u64, b.at[1] as u64], dims: [b.dims[0] as u64, b.dims[1] as u64] }
+}
+fn op(o: &Eltwise) -> sys::b200_eltwise_op {
+    sys::b200_eltwise_op { kind: o.kind, scalar: o.scalar, scalar2: o.scalar2 }
+}
+fn reduce_code(o: ReduceOp) -> i32 {
+    match o {
+        ReduceOp::Sum => 0, ReduceOp::Max => 1, ReduceOp::Prod => 2, ReduceOp::All => 3, ReduceOp::Any => 4,
+        ReduceOp::BitOr => 5, ReduceOp::SumI32 => 6, ReduceOp::ProdI32 => 7, ReduceOp::MinI32 => 8, ReduceOp::MaxI32 => 9,
+    }
+}
+
+/// The factory `burn_tt::attach` runs on the server thread.
+pub fn cuda_factory(ordinal: i32) -> impl FnOnce(Serve) -> Result<(), TtError> {
+    move |serve| {
+        let mut engine = CudaEngine::new(ordinal)?;
+        serve.serve(&mut engine)
+    }
+}
+
+macro_rules! produce {
+    ($self:ident, $f:ident ( $($a:expr),* )) => {{
+        let (mut id, mut d) = (0u64, [0u64; 2]);
+        let st = unsafe { sys::$f($self.raw, $($a,)* &mut id, d.as_mut_ptr()) };
+        $self.made(st, id, d)
+    }};
+}
+
+impl Engine for CudaEngine {
+    fn supports_dram(&self) -> bool { true }
+    fn supports_batched_layout(&self) -> bool { true }
+    fn supports_exact_matmul(&self) -> bool { false }
+
+    fn matmul(&mut self, a: &[f32], b: &[f32], mkn: [usize; 3]) -> Result<Vec<f32>, TtError> {
+        let mut out = vec![0f32; mkn[0] * mkn[2]];
+        let d = [mkn[0] as u64, mkn[1] as u64, mkn[2] as u64];
+        let st = unsafe { sys::b200_matmul_host(self.raw, a.as_ptr(), b.as_ptr(), d.as_ptr(), out.as_mut_ptr()) };
+        self.check(st).map(|_| out)
+    }
+    fn upload(&mut self, v: &[f32], rows: usize, cols: usize) -> Result<BufferId, TtError> {
+        let mut id = 0u64;
+        let st = unsafe { sys::b200_upload_f32(self.raw, v.as_ptr(), rows as u64, cols as u64, &mut id) };
+        self.check(st).map(|_| id)
+    }
+    fn upload_bf16(&mut self, v: &[u16], rows: usize, cols: usize) -> Result<BufferId, TtError> {
+        let mut id = 0u64;
+        let st = unsafe { sys::b200_upload_bf16(self.raw, v.as_ptr(), rows as u64, cols as u64, &mut id) };
+        self.check(st).map(|_| id)
+    }
+    fn upload_bits(&mut self, v: &[u32], rows: usize, cols: usize, elem: Elem) -> Result<BufferId, TtError> {
+        let mut id = 0u64;
+        let st = unsafe { sys::b200_upload_bits(self.raw, v.as_ptr(), rows as u64, cols as u64, elem_code(elem, false), &mut id) };
+        self.check(st).map(|_| id)
+    }
+    fn download(&mut self, id: BufferId) -> Result<Vec<f32>, TtError> {
+        let (d, _) = self.dims(id)?;
+        let mut out = vec![0f32; d[0] * d[1]];
+        let st = unsafe { sys::b200_download_f32(self.raw, id, out.as_mut_ptr(), out.len() as u64) };
+        self.check(st).map(|_| out)
+    }
+    fn download_bf16(&mut self, id: BufferId) -> Result<Vec<u16>, TtError> {
+        let (d, _) = self.dims(id)?;
+        let mut out = vec![0u16; d[0] * d[1]];
+        let st = unsafe { sys::b200_download_bf16(self.raw, id, out.as_mut_ptr(), out.len() as u64) };
+        self.check(st).map(|_| out)
+    }
+    fn download_bits(&mut self, id: BufferId) -> Result<Vec<u32>, TtError> {
+        let (d, _) = self.dims(id)?;
+        let mut out = vec![0u32; d[0] * d[1]];
+        let st = unsafe { sys::b200_download_bits(self.raw, id, out.as_mut_ptr(), out.len() as u64) };
+        self.check(st).map(|_| out)
+    }
+    fn free(&mut self, id: BufferId) { unsafe { sys::b200_free(self.raw, id) } }
+    fn zeros_dram(&mut self, dims: [usize; 2], elem: Elem, bf16: bool) -> Made {
+        produce!(self, b200_zeros(dims[0] as u64, dims[1] as u64, elem_code(elem, bf16)))
+    }
+    fn copy_into(&mut self, src: BufferId, dst: BufferId) -> Result<(), TtError> {
+        let st = unsafe { sys::b200_copy_into(self.raw, src, dst) };
+        self.check(st)
+    }
+    fn cast_float(&mut self, a: BufferId, bf16: bool) -> Made { produce!(self, b200_cast_float(a, bf16 as i32)) }
+
+    fn matmul_dram(&mut self, a: BufferId, ta: bool, b: BufferId, tb: bool) -> Made {
+        produce!(self, b200_matmul(a, ta as i32, b, tb as i32, 0))
+    }
+    fn matmul_dram_bf16(&mut self, a: BufferId, ta: bool, b: BufferId, tb: bool) -> Made {
+        produce!(self, b200_matmul(a, ta as i32, b, tb as i32, 1))
+    }
+    fn matmul_dram_batched(&mut self, a: BufferId, b: BufferId, items: &[(Block, Block)], mkn: [usize; 3]) -> Made {
+        self.matmul_dram_batched_layout(a, b, items, mkn, BatchedLayout::STACKED)
+    }
+    fn matmul_dram_batched_layout(&mut self, a: BufferId, b: BufferId, items: &[(Block, Block)], mkn: [usize; 3],
+                                  layout: BatchedLayout) -> Made {
+        let ab: Vec<_> = items.iter().map(|(x, _)| block(x)).collect();
+        let bb: Vec<_> = items.iter().map(|(_, y)| block(y)).collect();
+        let d = [mkn[0] as u64, mkn[1] as u64, mkn[2] as u64];
+        let l = sys::b200_batched_layout { lhs_padded: layout.lhs_padded as i32, stacked: layout.stacked as i32 };
+        // the result takes its operands' type: BF16 operands give a BF16 product (ops.rs:464-503)
+        let bf16 = self.dims(a)?.1 == 3;
+        produce!(self, b200_matmul_batched(a, b, ab.as_ptr(), bb.as_ptr(), items.len() as u64, d.as_ptr(), &l, bf16 as i32))
+    }
+
+    fn eltwise(&mut self, kind: u32, scalar: f32, a: BufferId, b: Option<BufferId>) -> Made {
+        self.eltwise_op_as(Eltwise { kind, scalar, scalar2: 0.0 }, a, b, None, false)
+    }
+    fn eltwise_op(&mut self, o: Eltwise, a: BufferId, b: Option<BufferId>, c: Option<BufferId>) -> Made {
+        self.eltwise_op_as(o, a, b, c, false)
+    }
+    fn eltwise_op_as(&mut self, o: Eltwise, a: BufferId, b: Option<BufferId>, c: Option<BufferId>, bf16: bool) -> Made {
+        let o = op(&o);
+        produce!(self, b200_eltwise(&o, a, b.unwrap_or(0), c.unwrap_or(0), bf16 as i32))
+    }
+    fn eltwise_blocks(&mut self, o: Eltwise, a: BlockArg, b: Option<BlockArg>, c: Option<BlockArg>) -> Made {
+        self.eltwise_blocks_as(o, a, b, c, false)
+    }
+    fn eltwise_blocks_as(&mut self, o: Eltwise, a: BlockArg, b: Option<BlockArg>, c: Option<BlockArg>, bf16: bool) -> Made {
+        let (o, a) = (op(&o), arg(&a));
+        let (b, c) = (b.as_ref().map(arg), c.as_ref().map(arg));
+        let pb = b.as_ref().map_or(std::ptr::null(), |x| x as *const _);
+        let pc = c.as_ref().map_or(std::ptr::null(), |x| x as *const _);
+        produce!(self, b200_eltwise_blocks(&o, &a, pb, pc, bf16 as i32))
+    }
+    fn rope_blocks(&mut self, x: BlockArg, cos: BlockArg, sin: BlockArg, head: usize, bf16: bool) -> Made {
+        let (x, c, s) = (arg(&x), arg(&cos), arg(&sin));
+        produce!(self, b200_rope_blocks(&x, &c, &s, head as u64, bf16 as i32))
+    }
+
+    fn reduce(&mut self, a: BufferId, o: ReduceOp, axis: Axis, then: ReduceThen) -> Made {
+        let (k, bits) = then.unwrap_or((0, 0));
+        produce!(self, b200_reduce(a, reduce_code(o), matches!(axis, Axis::Cols) as i32, k, bits))
+    }
+    fn sum_rows(&mut self, a: BufferId) -> Made { produce!(self, b200_sum_rows(a)) }
+    fn full_reduce(&mut self, values: &[f32], dims: [usize; 2], mean: bool) -> Result<f32, TtError> {
+        let (d, mut out) = ([dims[0] as u64, dims[1] as u64], 0f32);
+        let st = unsafe { sys::b200_full_reduce(self.raw, values.as_ptr(), d.as_ptr(), mean as i32, &mut out) };
+        self.check(st).map(|_| out)
+    }
+    fn softmax_rows(&mut self, x: BufferId, mask: BufferId, scale: f32) -> Made { produce!(self, b200_softmax_rows(x, mask, scale)) }
+    fn rms(&mut self, a: BufferId, eps: f32) -> Made { produce!(self, b200_rms(a, eps)) }
+    fn rms_norm(&mut self, a: BufferId, gamma: Option<BufferId>, eps: f32) -> Made {
+        produce!(self, b200_rms_norm(a, gamma.unwrap_or(0), eps, 0))
+    }
+    fn rms_norm_as(&mut self, a: BufferId, gamma: Option<BufferId>, eps: f32, bf16: bool) -> Made {
+        produce!(self, b200_rms_norm(a, gamma.unwrap_or(0), eps, bf16 as i32))
+    }
+    fn add_rms_norm(&mut self, a: BufferId, b: BufferId, gamma: Option<BufferId>, eps: f32)
+        -> Result<[(BufferId, [usize; 2]); 2], TtError> {
+        let (mut ids, mut d) = ([0u64; 2], [0u64; 2]);
+        let st = unsafe { sys::b200_add_rms_norm(self.raw, a, b, gamma.unwrap_or(0), eps, ids.as_mut_ptr(), d.as_mut_ptr()) };
+        self.check(st)?;
+        let dims = [d[0] as usize, d[1] as usize];
+        Ok([(ids[0], dims), (ids[1], dims)])
+    }
+    fn argmax_row(&mut self, a: BufferId) -> Made { produce!(self, b200_argmax_row(a)) }
+
+    fn select_rows(&mut self, table: BufferId, idx: BufferId) -> Made { produce!(self, b200_select_rows(table, idx)) }
+    fn pick_columns(&mut self, x: BufferId, idx: BufferId) -> Made { produce!(self, b200_pick_columns(x, idx)) }
+    fn select_add_rows(&mut self, t: BufferId, idx: BufferId, v: BufferId) -> Made { produce!(self, b200_select_add_rows(t, idx, v)) }
+    fn gather_indexed(&mut self, x: BufferId, idx: BufferId) -> Made { produce!(self, b200_gather_indexed(x, idx)) }
+    fn scatter_rows(&mut self, t: BufferId, idx: BufferId, v: BufferId, column: bool) -> Made {
+        produce!(self, b200_scatter_rows(t, idx, v, column as i32))
+    }
+    fn rows_add(&mut self, t: BufferId, indices: &[usize], v: BufferId) -> Made {
+        let i: Vec<u64> = indices.iter().map(|&x| x as u64).collect();
+        produce!(self, b200_rows_add(t, i.as_ptr(), i.len() as u64, v))
+    }
+    fn assign_rows(&mut self, t: BufferId, v: BufferId, rows: &[(usize, usize)]) -> Made {
+        let p: Vec<u64> = rows.iter().flat_map(|&(d, s)| [d as u64, s as u64]).collect();
+        produce!(self, b200_assign_rows(t, v, p.as_ptr(), rows.len() as u64))
+    }
+    fn gather_rows(&mut self, sources: &[BufferId], rows: &[(usize, usize)], cols: usize) -> Made {
+        let p: Vec<u64> = rows.iter().flat_map(|&(s, r)| [s as u64, r as u64]).collect();
+        produce!(self, b200_gather_rows(sources.as_ptr(), sources.len() as u64, p.as_ptr(), rows.len() as u64, cols as u64))
+    }
+    fn slice_rows(&mut self, a: BufferId, first: usize, rows: usize) -> Made {
+        produce!(self, b200_slice_rows(a, first as u64, rows as u64))
+    }
+    fn copy_blocks(&mut self, a: BufferId, moves: &[BlockMove], dims: [usize; 2]) -> Made {
+        let m: Vec<_> = moves.iter().map(|m| sys::b200_block_move {
+            from: [m.from[0] as u64, m.from[1] as u64], to: [m.to[0] as u64, m.to[1] as u64],
+            extent: [m.extent[0] as u64, m.extent[1] as u64], transposed: m.transposed as i32, _pad: 0 }).collect();
+        let d = [dims[0] as u64, dims[1] as u64];
+        produce!(self, b200_copy_blocks(a, m.as_ptr(), m.len() as u64, d.as_ptr()))
+    }
+    fn repack(&mut self, a: BufferId, sources: &[[usize; 2]], dims: [usize; 2]) -> Made {
+        let p: Vec<u64> = sources.iter().flat_map(|s| [s[0] as u64, s[1] as u64]).collect();
+        let d = [dims[0] as u64, dims[1] as u64];
+        produce!(self, b200_repack(a, p.as_ptr(), d.as_ptr()))
+    }
+
+    // Traces are CUDA graphs (server.rs:591-660).
+    fn begin_trace(&mut self) -> Result<(), TtError> { let st = unsafe { sys::b200_begin_trace(self.raw) }; self.check(st) }
+    fn end_trace(&mut self) -> Result<u64, TtError> {
+        let mut t = 0u64;
+        let st = unsafe { sys::b200_end_trace(self.raw, &mut t) };
+        self.check(st).map(|_| t)
+    }
+    fn release_trace(&mut self, trace: u64) { unsafe { sys::b200_release_trace(self.raw, trace) } }
+    fn set_op_label(&mut self, label: &'static str) {
+        let c = std::ffi::CString::new(label).unwrap();
+        unsafe { sys::b200_set_op_label(self.raw, c.as_ptr()) }
+    }
+}

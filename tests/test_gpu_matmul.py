@@ -52,7 +52,7 @@ def test_f32_products_hold_f32_accuracy(eng, mkn, ta, tb):
     cpu = orc.gemm_f32(a, b, ta, tb)
     c_s, _ = orc.gemm_rel_error(cpu, truth, s)
     assert e_s <= F32_TOL, (e_s, c_s)
-    assert e_s <= 4 * c_s + 2 ** -22  # never far from the CPU restatement's own rounding
+    assert e_s <= 4 * c_s + 2 ** -20  # never far from the CPU restatement's own rounding (the split path drops a_lo b_lo)
     for i in (ia, ib, out):
         eng.free(i)
 
