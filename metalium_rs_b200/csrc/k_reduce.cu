@@ -538,6 +538,63 @@ rms_norm_kernel(const void* a, int a_bf16, const void* b, int b_bf16, const void
   }
 }
 
+// F32 rows of up to 1024 columns, no residual: a warp a row, the row kept in registers between
+// the sum of squares and the division (one read, one write).  Same roundings as the general kernel.
+template <int V>
+__global__ void __launch_bounds__(256)
+rms_norm_rows_kernel(const float* __restrict__ a, const void* __restrict__ gamma, int g_bf16, float eps,
+                     void* __restrict__ out, int out_bf16, uint64_t rows, uint32_t cols) {
+  const int lane = threadIdx.x & 31;
+  const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+  const uint32_t n4 = cols / 4;
+  const float inv = 1.0f / (float)cols;
+  for (uint64_t row = warp; row < rows; row += nwarps) {
+    const float4* p = reinterpret_cast<const float4*>(a + row * cols);
+    float4 v[V];
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < V; ++u) {
+      const uint32_t i = lane + u * 32;
+      if (i < n4) {
+        v[u] = p[i];
+        ss = ss + ((v[u].x * v[u].x + v[u].y * v[u].y) + (v[u].z * v[u].z + v[u].w * v[u].w));
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss = ss + __shfl_xor_sync(0xffffffffu, ss, o);
+    const float stat = sqrtf(ss * inv + eps);
+    void* orow = reinterpret_cast<char*>(out) + row * cols * (out_bf16 ? 2 : 4);
+#pragma unroll
+    for (int u = 0; u < V; ++u) {
+      const uint32_t i = lane + u * 32;
+      if (i < n4) {
+        float4 t = v[u];
+        t.x = t.x / stat; t.y = t.y / stat; t.z = t.z / stat; t.w = t.w / stat;
+        if (gamma) {
+          float4 g;
+          if (g_bf16) {
+            const uint2 h = reinterpret_cast<const uint2*>(gamma)[i];
+            g.x = __uint_as_float(h.x << 16); g.y = __uint_as_float(h.x & 0xffff0000u);
+            g.z = __uint_as_float(h.y << 16); g.w = __uint_as_float(h.y & 0xffff0000u);
+          } else {
+            g = reinterpret_cast<const float4*>(gamma)[i];
+          }
+          t.x = t.x * g.x; t.y = t.y * g.y; t.z = t.z * g.z; t.w = t.w * g.w;
+        }
+        if (out_bf16) {
+          uint2 o2;
+          o2.x = (uint32_t)f32_to_bf16_bits(__float_as_uint(t.x)) | ((uint32_t)f32_to_bf16_bits(__float_as_uint(t.y)) << 16);
+          o2.y = (uint32_t)f32_to_bf16_bits(__float_as_uint(t.z)) | ((uint32_t)f32_to_bf16_bits(__float_as_uint(t.w)) << 16);
+          reinterpret_cast<uint2*>(orow)[i] = o2;
+        } else {
+          reinterpret_cast<float4*>(orow)[i] = t;
+        }
+      }
+    }
+  }
+}
+
 // ---- argmax ---------------------------------------------------------------------
 struct Best { float v; uint32_t i; };
 __device__ __forceinline__ bool better(float v, uint32_t i, float bv, uint32_t bi) {
@@ -741,6 +798,16 @@ cudaError_t launch_rms_norm(const void* a, int a_bf16, const void* b, int b_bf16
   if (rows == 0) return cudaSuccess;
   uint64_t grid = (rows + 7) / 8;
   if (grid > 148ull * 16) grid = 148ull * 16;
+  if (!a_bf16 && !b && !sum_out && norm_out && cols % 4 == 0 && cols <= 1024 &&
+      ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(norm_out) | reinterpret_cast<uintptr_t>(gamma)) & 15) == 0) {
+    const float* af = (const float*)a;
+    const uint32_t c32 = (uint32_t)cols;
+    const int v = (int)((cols / 4 + 31) / 32);
+#define RN(V) rms_norm_rows_kernel<V><<<(unsigned)grid, 256, 0, s>>>(af, gamma, gamma_bf16, eps, norm_out, norm_bf16, rows, c32)
+    if (v <= 1) RN(1); else if (v <= 2) RN(2); else if (v <= 4) RN(4); else if (v <= 5) RN(5); else RN(8);
+#undef RN
+    return cudaGetLastError();
+  }
   rms_norm_kernel<<<(unsigned)grid, 256, 0, s>>>(a, a_bf16, b, b_bf16, gamma, gamma_bf16, eps, sum_out,
                                                  sum_bf16, norm_out, norm_bf16, nullptr, rows, cols);
   return cudaGetLastError();

@@ -74,14 +74,12 @@ def library_path() -> Path:
     return _LIB_PATH
 
 
-def load_library() -> C.CDLL:
-    """dlopen the engine.  Raises if it was not built: there is no other implementation."""
-    global _lib
-    if _lib is None:
-        if not _LIB_PATH.exists():
-            raise ImportError(f"{_LIB_PATH} is missing: run `python -m metalium_rs_b200.build` "
-                              "(the engine has no CPU or PyTorch fallback)")
-        _lib = C.CDLL(str(_LIB_PATH))
+def _prepare(_lib: C.CDLL) -> C.CDLL:
+    """Declare the return types ctypes would otherwise guess wrong."""
+    if getattr(_lib, "_b200_prepared", False):
+        return _lib
+    _lib._b200_prepared = True
+    if True:
         _lib.b200_last_error.restype = C.c_size_t
         _lib.b200_last_error.argtypes = [C.c_void_p, C.c_char_p, C.c_size_t]
         _lib.b200_stream.restype = C.c_void_p
@@ -94,6 +92,17 @@ def load_library() -> C.CDLL:
         _lib.b200_traffic_get.restype = None
         _lib.b200_last_oom.restype = None
         _lib.b200_release_trace.restype = None
+    return _lib
+
+
+def load_library() -> C.CDLL:
+    """dlopen the engine.  Raises if it was not built: there is no other implementation."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise ImportError(f"{_LIB_PATH} is missing: run `python -m metalium_rs_b200.build` "
+                              "(the engine has no CPU or PyTorch fallback)")
+        _lib = _prepare(C.CDLL(str(_LIB_PATH)))
     return _lib
 
 
@@ -115,8 +124,10 @@ class CudaEngine:
     """One GPU's engine; the B200 counterpart of `KmdEngine` (server.rs:4071)."""
 
     def __init__(self, device: int = 0, *, f32_matmul_mode: int = 0, bf16_matmul_mode: int = 0,
-                 pool_limit_bytes: int = 0, fail_alloc_at: int = 0):
-        self._lib = load_library()
+                 pool_limit_bytes: int = 0, fail_alloc_at: int = 0, lib=None):
+        # `lib`: a library handle to use instead of libb200tt.so -- the test suite passes the
+        # engine's host logic linked against a host-only stand-in for the CUDA runtime.
+        self._lib = _prepare(lib) if lib is not None else load_library()
         self._e = C.c_void_p()
         cfg = Config(f32_matmul_mode, bf16_matmul_mode, pool_limit_bytes, fail_alloc_at, 0)
         st = self._lib.b200_engine_create(C.c_int32(device), C.byref(cfg), C.byref(self._e))

@@ -1,0 +1,52 @@
+// TEST INFRASTRUCTURE: the kernel launch interface (csrc/kernels.h) with every launch a no-op
+// that reports success, and the knobs of the fake runtime.  Linked with engine.cu (compiled as
+// C++) into tests/_build/libb200tt_fake.so; results are never computed, only the host logic runs.
+#include "cuda_runtime.h"
+#include "kernels.h"
+#include "kinds.h"
+
+extern "C" {
+uint64_t fake_cuda_memory_limit = 0;
+uint64_t fake_cuda_memory_in_use = 0;
+int fake_cuda_device_count = 1;
+int fake_cuda_capturing = 0;
+int fake_launch_count = 0;        // launches the engine asked for
+int fake_tc_supported = 1;        // what gemm_tc_supported answers for BF16 operands
+}
+
+namespace b200 {
+#define OK_LAUNCH ++fake_launch_count; return cudaSuccess
+cudaError_t launch_eltwise(const EltwiseArgs&, cudaStream_t) { OK_LAUNCH; }
+bool eltwise_kind_known(uint32_t k) { return kind::arity(k) != 0; }
+cudaError_t launch_rope(const Mat&, const Mat&, const Mat&, uint64_t, void*, uint64_t, int, uint64_t, uint64_t, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_cast(const void*, void*, uint64_t, int, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_reduce(const void*, int, uint64_t, uint64_t, int, int, uint32_t, uint32_t, void*, cudaStream_t) { OK_LAUNCH; }
+uint64_t full_sum_scratch_floats() { return 1184; }
+cudaError_t launch_full_sum(const float*, uint64_t, int, float*, float*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_softmax_rows(const float*, const uint32_t*, uint64_t, float, int, void*, int, uint64_t, uint64_t, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_rms(const float*, uint64_t, uint64_t, float, float*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_rms_norm(const void*, int, const void*, int, const void*, int, float, void*, int, void*, int, uint64_t, uint64_t, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_argmax_rows(const float*, uint64_t, uint64_t, int32_t*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_select_rows(const void*, uint64_t, uint64_t, int, const int32_t*, uint64_t, void*, int*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_pick_columns(const uint32_t*, uint64_t, uint64_t, const int32_t*, uint32_t*, int*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_scatter_add_columns(float*, uint64_t, uint64_t, const int32_t*, const float*, int*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_select_add_rows(float*, uint64_t, uint64_t, const int32_t*, uint64_t, const float*, int*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_scatter_rows(uint32_t*, uint64_t, uint64_t, const int32_t*, uint64_t, const uint32_t*, int*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_gather_indexed(const uint32_t*, uint64_t, uint64_t, const int32_t*, uint64_t, uint32_t*, int*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_gather_row_ptrs(const void* const*, uint64_t, uint64_t, int, void*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_assign_rows(void*, const void*, uint64_t, int, const uint64_t*, uint64_t, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_copy_blocks(const void*, uint64_t, void*, uint64_t, int, const MoveDev*, uint64_t, uint64_t, uint64_t, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_repack(const void*, uint64_t, int, const uint64_t*, uint64_t, void*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_gemm_simt(const GemmArgs&, cudaStream_t) { OK_LAUNCH; }
+bool gemm_tc_supported(const GemmArgs& g, const char** why) {
+  *why = g.in_bf16 ? "the fake runtime was told to refuse" : "operands are not BF16";
+  return g.in_bf16 && fake_tc_supported;
+}
+cudaError_t launch_gemm_tc(const GemmArgs&, const GemmBatch*, int*, cudaStream_t) { OK_LAUNCH; }
+bool gemm_tc2_wanted(const GemmArgs&) { return false; }
+cudaError_t launch_gemm_tc2(const GemmArgs&, int*, cudaStream_t) { OK_LAUNCH; }
+bool gemm_tf32_supported(const GemmArgs& g, const char** why) { *why = "small"; return !g.in_bf16 && g.batch <= 1 && g.m >= 128 && g.n >= 128 && g.k >= 32; }
+cudaError_t launch_gemm_tf32(const GemmArgs&, void*, void*, void*, void*, int*, cudaStream_t) { OK_LAUNCH; }
+}  // namespace b200
+
+extern "C" int32_t b200_full_sum_noalloc(const float*, uint64_t, int32_t, float*, void*) { return 2; }

@@ -1,0 +1,240 @@
+"""The engine's host logic without a GPU: engine.cu compiled with g++ against a host-only
+stand-in for the CUDA runtime (tests/fake_cuda), every kernel launch a no-op.  Checked here:
+result dims of every op (burn-tt fails an op whose dims differ from its own prediction,
+crates/burn-tt/src/server.rs:2963-2972), refusals, buffer-id safety
+(crates/burn-tt/tests/stale_buffer.rs), views, the pool, out-of-memory reports, the path
+choice of products and the trace state machine -- with failures injected on the host only."""
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from metalium_rs_b200 import (BF16, BOOL, COLS, F32, I32, MAX, ROWS, SUM, BatchedLayout, CudaEngine, EltwiseOp, TtError,
+                              kinds)
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def fake():
+    out = ROOT / "tests" / "_build" / "libb200tt_fake.so"
+    out.parent.mkdir(exist_ok=True)
+    srcs = [ROOT / "metalium_rs_b200" / "csrc" / "engine.cu", ROOT / "tests" / "fake_cuda" / "fake_kernels.cpp"]
+    subprocess.run(["g++", "-std=c++17", "-O1", "-fPIC", "-shared", "-x", "c++", "-I", str(ROOT / "tests" / "fake_cuda"),
+                    "-I", str(ROOT / "metalium_rs_b200" / "csrc"), *map(str, srcs), "-o", str(out)], check=True)
+    return C.CDLL(str(out))
+
+
+@pytest.fixture()
+def e(fake):
+    C.c_uint64.in_dll(fake, "fake_cuda_memory_limit").value = 0
+    C.c_int.in_dll(fake, "fake_tc_supported").value = 1
+    eng = CudaEngine(0, lib=fake)
+    yield eng
+    eng.close()
+
+
+def f32(e, r, c):
+    return e.upload(np.arange(r * c, dtype=np.float32).reshape(r, c), r, c)
+
+
+def test_storage_round_trips_and_ids(e):
+    x = np.arange(12, dtype=np.float32).reshape(3, 4)
+    i = e.upload(x, 3, 4)
+    assert np.array_equal(e.download(i), x) and e.dims_of(i) == ((3, 4), F32)
+    j = e.upload(x, 3, 4)
+    assert j != i                                   # ids are unique within an engine
+    e.free(i); e.free(i); e.free(987654)            # unknown ids: no-ops (server.rs:174)
+    with pytest.raises(TtError) as err:
+        e.download(i)
+    assert err.value.status == 5                    # StaleTensor
+    h = e.upload_bf16(np.arange(6, dtype=np.uint16).reshape(2, 3), 2, 3)
+    assert e.dims_of(h) == ((2, 3), BF16)
+    with pytest.raises(TtError):
+        e.download(h)                               # not F32
+    with pytest.raises(TtError):
+        e.upload_bits(np.zeros((1, 1), np.uint32), 1, 1, BF16)
+
+
+def test_result_dims_of_every_op(e):
+    a, b = f32(e, 64, 96), f32(e, 96, 32)
+    assert e.matmul_dram(a, False, b, False)[1] == (64, 32)
+    assert e.matmul_dram(a, True, a, False)[1] == (96, 96)
+    assert e.matmul_dram(b, True, a, True)[1] == (32, 64)
+    with pytest.raises(TtError):
+        e.matmul_dram(a, False, a, False)
+    row, col, blk = f32(e, 1, 96), f32(e, 64, 1), f32(e, 32, 96)
+    for other in (a, row, col, blk):
+        assert e.eltwise_op(EltwiseOp(kinds.ADD, 0, 0), a, other)[1] == (64, 96)
+    assert e.eltwise_op(EltwiseOp(kinds.MUL, 0, 0), row, a)[1] == (64, 96)      # broadcast operand on the left
+    with pytest.raises(TtError):
+        e.eltwise_op(EltwiseOp(kinds.SILU_MUL, 0, 0), a, row)                    # a kind that takes no broadcast
+    assert e.eltwise_op(EltwiseOp(kinds.GT, 0, 0), a, a)[0] and e.dims_of(e.eltwise_op(EltwiseOp(kinds.GT, 0, 0), a, a)[0])[1] == BOOL
+    assert e.dims_of(e.eltwise_op_as(EltwiseOp(kinds.EXP, 0, 0), a, None, None, True)[0])[1] == BF16
+    with pytest.raises(TtError):
+        e.eltwise_op_as(EltwiseOp(kinds.GT, 0, 0), a, a, None, True)             # no BF16 result of a Bool kind
+    assert e.reduce(a, SUM, ROWS)[1] == (1, 96) and e.reduce(a, MAX, COLS)[1] == (64, 1)
+    assert e.sum_rows(a)[1] == (1, 96) and e.full_sum(a)[1] == (1, 1)
+    assert e.softmax_rows(a, None, 1.0)[1] == (64, 96) and e.log_softmax_rows(a)[1] == (64, 96)
+    assert e.rms(a, 1e-5)[1] == (64, 1) and e.rms_norm(a, row, 1e-5)[1] == (64, 96)
+    (s, d1), (n, d2) = e.add_rms_norm(a, a, row, 1e-5)
+    assert d1 == d2 == (64, 96)
+    assert e.argmax_row(a)[1] == (64, 1)
+    idx = e.upload_bits(np.zeros((1, 7), np.uint32), 1, 7, I32)
+    assert e.select_rows(a, idx)[1] == (7, 96)
+    ridx = e.upload_bits(np.zeros((64, 1), np.uint32), 64, 1, I32)
+    assert e.pick_columns(a, ridx)[1] == (64, 1)
+    assert e.scatter_add_columns(a, ridx, col)[1] == (64, 96)
+    v = f32(e, 7, 96)
+    assert e.select_add_rows(a, idx, v)[1] == (64, 96) and e.rows_add(a, [0] * 7, v)[1] == (64, 96)
+    assert e.scatter_rows(a, idx, v, False)[1] == (64, 96)
+    assert e.assign_rows(a, v, [(1, 0), (2, 6)])[1] == (64, 96)
+    with pytest.raises(TtError) as err:
+        e.assign_rows(a, v, [(64, 0)])
+    assert err.value.status == 6                                                # DOMAIN, found on the host
+    assert e.gather_rows([a, v], [(0, 3), (1, 6)], 96)[1] == (2, 96)
+    assert e.slice_rows(a, 32, 16)[1] == (16, 96)
+    with pytest.raises(TtError):
+        e.slice_rows(a, 60, 16)
+    assert e.copy_blocks(a, [((0, 0), (0, 0), (64, 32), False), ((0, 32), (64, 0), (64, 32), False),
+                             ((0, 64), (128, 0), (64, 32), False)], (192, 32))[1] == (192, 32)
+    assert e.copy_blocks(a, [((0, 0), (0, 0), (96, 64), True)], (96, 64))[1] == (96, 64)
+    with pytest.raises(TtError):
+        e.copy_blocks(a, [((0, 0), (0, 0), (64, 32), False)], (192, 32))       # does not cover the output
+    assert e.repack(a, np.zeros((6, 2), np.uint64), (2, 3))[1] == (2, 3)
+    assert e.cast_float(a, True)[1] == (64, 96)
+    x = f32(e, 128, 192)
+    assert e.rope_blocks((x, (0, 0), (128, 128)), (x, (0, 0), (32, 64)), (x, (0, 0), (32, 64)), 64)[1] == (128, 128)
+    with pytest.raises(TtError):
+        e.rope_blocks((x, (0, 0), (128, 100)), (x, (0, 0), (32, 64)), (x, (0, 0), (32, 64)), 64)
+    assert e.eltwise_blocks(EltwiseOp(kinds.MUL, 0, 0), (x, (32, 64), (64, 96)), (x, (0, 0), (64, 96)))[1] == (64, 96)
+    with pytest.raises(TtError):
+        e.eltwise_blocks(EltwiseOp(kinds.MUL, 0, 0), (x, (100, 0), (64, 96)), (x, (0, 0), (64, 96)))
+
+
+def test_batched_product_layouts(e):                                            # server.rs:3749-3754
+    a, b = f32(e, 96, 40), f32(e, 40, 99)
+    items = [(((i * 32, 0), False), ((0, i * 33), False)) for i in range(3)]
+    assert e.matmul_dram_batched(a, b, items, (20, 40, 33))[1] == (60, 33)       # stacked
+    assert e.matmul_dram_batched_layout(a, b, items, (20, 40, 33), BatchedLayout(1, 0))[1] == (96, 33)  # a tile row each
+    with pytest.raises(TtError):
+        e.matmul_dram_batched(a, b, [(((90, 0), False), ((0, 0), False))], (20, 40, 33))   # block outside its buffer
+
+
+def test_product_path_choice(fake, e):
+    a, b = e.upload_bf16(np.zeros((256, 128), np.uint16), 256, 128), e.upload_bf16(np.zeros((128, 256), np.uint16), 128, 256)
+    e.matmul_dram_bf16(a, False, b, False)
+    assert e.last_matmul_path() == "tcgen05"
+    f = f32(e, 256, 256)
+    e.matmul_dram(f, False, f, False)
+    assert e.last_matmul_path() == "tcgen05-tf32x3"
+    s = f32(e, 64, 64)
+    e.matmul_dram(s, False, s, False)
+    assert e.last_matmul_path() == "simt"
+    with pytest.raises(TtError):
+        e.matmul_dram(a, False, f, False)                                       # mixed operand types
+    C.c_int.in_dll(fake, "fake_tc_supported").value = 0
+    e.matmul_dram_bf16(a, False, b, False)
+    assert e.last_matmul_path() == "simt"                                       # automatic mode falls back
+    strict = CudaEngine(0, bf16_matmul_mode=2, lib=fake)
+    x, y = strict.upload_bf16(np.zeros((64, 64), np.uint16), 64, 64), strict.upload_bf16(np.zeros((64, 64), np.uint16), 64, 64)
+    with pytest.raises(TtError) as err:
+        strict.matmul_dram_bf16(x, False, y, False)                             # tensor cores only: refused, never slower silently
+    assert err.value.status == 2
+    strict.close()
+
+
+def test_views_keep_their_parent_alive(e):                                      # server.rs:480-481
+    t0 = e.device_traffic().pool_in_use
+    a = f32(e, 64, 8)
+    v = e.slice_rows(a, 8, 16)[0]
+    e.free(a)
+    with pytest.raises(TtError):
+        e.download(a)                                                           # the id is gone
+    assert np.array_equal(e.download(v), np.arange(64, 192, dtype=np.float32).reshape(16, 8))
+    assert e.device_traffic().pool_in_use > t0                                  # ... but its memory is not
+    e.free(v)
+    assert e.device_traffic().pool_in_use == t0
+
+
+def test_pool_reuse_and_out_of_memory(fake, e):
+    a = f32(e, 256, 256)
+    r0 = e.device_traffic().pool_reserved
+    for _ in range(10):
+        o, _ = e.eltwise_op(EltwiseOp(kinds.RELU, 0, 0), a)
+        e.free(o)
+    assert e.device_traffic().pool_reserved == r0 + 256 * 256 * 4               # one block, reused nine times
+    C.c_uint64.in_dll(fake, "fake_cuda_memory_limit").value = C.c_uint64.in_dll(fake, "fake_cuda_memory_in_use").value + (1 << 20)
+    with pytest.raises(TtError) as err:
+        f32(e, 1024, 1024)                                                      # the driver has no room: reported, not fatal
+    assert err.value.status == 1 and e.last_oom()[0] == 4 << 20
+    C.c_uint64.in_dll(fake, "fake_cuda_memory_limit").value = 0
+    assert f32(e, 1024, 1024)
+    lim = CudaEngine(0, pool_limit_bytes=1 << 20, lib=fake)
+    lim.upload(np.zeros((256, 256), np.float32), 256, 256)
+    with pytest.raises(TtError) as err:
+        lim.upload(np.zeros((512, 512), np.float32), 512, 512)
+    assert err.value.status == 1 and lim.last_oom() == (1 << 20, 768 << 10, 768 << 10)
+    lim.close()
+    nth = CudaEngine(0, fail_alloc_at=2, lib=fake)
+    x = nth.upload(np.zeros((4, 4), np.float32), 4, 4)
+    with pytest.raises(TtError):
+        nth.eltwise_op(EltwiseOp(kinds.RELU, 0, 0), x)                          # the second allocation is told to fail
+    assert nth.eltwise_op(EltwiseOp(kinds.RELU, 0, 0), x)[1] == (4, 4)          # and the engine carries on
+    nth.close()
+
+
+def test_trace_state_machine(fake, e):                                          # server.rs:591-660
+    a = f32(e, 64, 64)
+    with pytest.raises(TtError):
+        e.end_trace()                                                           # nothing open
+    e.begin_trace()
+    with pytest.raises(TtError):
+        e.begin_trace()                                                         # one at a time
+    for call in (lambda: e.sync(), lambda: e.download(a), lambda: f32(e, 2, 2)):
+        with pytest.raises(TtError) as err:
+            call()                                                              # no wait, download or upload inside
+        assert err.value.status == 2
+    o1, _ = e.eltwise_op(EltwiseOp(kinds.RELU, 0, 0), a)
+    t1, _ = e.eltwise_op(EltwiseOp(kinds.EXP, 0, 0), o1)
+    e.free(o1)
+    o2, _ = e.eltwise_op(EltwiseOp(kinds.NEG, 0, 0), t1)                        # may reuse o1's block inside the capture
+    trace = e.end_trace()
+    in_use = e.device_traffic().pool_in_use
+    l0 = e.device_traffic().launches
+    e.run_trace(trace)
+    assert e.device_traffic().launches - l0 == 3                                # a replay counts the kernels it runs
+    junk = [f32(e, 64, 64) for _ in range(4)]                                   # the pool must not hand out the trace's blocks
+    ptrs = {e.device_ptr(j)[0] for j in junk}
+    assert e.device_ptr(o2)[0] not in ptrs and e.device_ptr(t1)[0] not in ptrs
+    e.free(t1)                                                                  # an output freed by the caller stays the trace's
+    more = {e.device_ptr(f32(e, 64, 64))[0] for _ in range(4)}
+    with pytest.raises(TtError):
+        e.run_trace(trace + 7)
+    e.release_trace(trace)
+    e.release_trace(trace)                                                      # twice: a no-op
+    with pytest.raises(TtError):
+        e.run_trace(trace)
+    assert e.download(o2).shape == (64, 64)                                     # a live output outlives its trace
+
+
+def test_errors_carry_the_op_label_and_shapes(e):                               # server.rs:663, 2974-2980
+    e.set_op_label("float_matmul")
+    a = f32(e, 2, 3)
+    with pytest.raises(TtError) as err:
+        e.matmul_dram(a, False, a, False)
+    assert "float_matmul" in str(err.value) and "[2,3] x [2,3]" in str(err.value)
+
+
+def test_no_device_is_reported(fake):
+    C.c_int.in_dll(fake, "fake_cuda_device_count").value = 0
+    try:
+        with pytest.raises(TtError) as err:
+            CudaEngine(0, lib=fake)
+        assert err.value.status == 7
+    finally:
+        C.c_int.in_dll(fake, "fake_cuda_device_count").value = 1
+    with pytest.raises(TtError):
+        CudaEngine(3, lib=fake)                                                 # no such card
