@@ -224,9 +224,13 @@ def run_single(args):
 
     pk, which = peaks()
     peak = float(pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
-    roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel<256,4,K-major A,MN-major B>", "achieved": value, "peak": peak,
-                "unit": UNIT, "frac": value / peak, "peak_source": f"{which} cuBLAS bf16 burst",
-                "frac_of_nominal_2250": value / 2250.0, "traffic": None}
+    # traffic: dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch, from the ncu capture
+    # summarised in profiles/gemm_tc2_bf16_8192.md (1,274.3 MB + 252.4 MB); null at other sizes
+    traffic = 1274306000 + 252358000 if n == N1_SIZE else None
+    roofline = {"bound": "tensor", "kernel": "gemm_tc2_kernel<K-major A, MN-major B> (CTA pairs, 256x256 tiles)",
+                "achieved": value, "peak": peak, "unit": UNIT, "frac": value / peak,
+                "peak_source": f"{which} cuBLAS bf16 burst", "frac_of_nominal_2250": value / 2250.0,
+                "algorithmic_flops_per_launch": flops, "traffic": traffic, "traffic_unit": "bytes per launch"}
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
@@ -396,6 +400,38 @@ def callers(eng, timed):
     return res
 
 
+def run_profile(args):
+    """`--profile NAME`: a short fixed sequence for ncu captures (no JSON line, nothing timed).
+    membound: EXP, MUL by a row, full sum, per-row sum on [8192,8192] F32, three rounds.
+    softmax: three row softmaxes of [1024, 32768].  prefill: two SmolLM2-135M-shape forward passes."""
+    from metalium_rs_b200 import COLS, I32, SUM, CudaEngine, EltwiseOp, build, kinds, workloads as W
+    build.build()
+    rng = np.random.default_rng(3)
+    with CudaEngine(0) as eng:
+        if args.profile == "membound":
+            x = eng.upload(rng.random((8192, 8192), dtype=np.float32) * 3.99 + 0.01, 8192, 8192)
+            row = eng.upload(rng.random((1, 8192), dtype=np.float32) + 0.5, 1, 8192)
+            for _ in range(3):
+                for k, b in ((kinds.EXP, None), (kinds.MUL, row)):
+                    o, _ = eng.eltwise_op(EltwiseOp(k, 0, 0), x, b); eng.free(o)
+                o, _ = eng.full_sum(x); eng.free(o)
+                o, _ = eng.reduce(x, SUM, COLS); eng.free(o)
+        elif args.profile == "softmax":
+            x = eng.upload(rng.random((1024, 32768), dtype=np.float32) * 8 - 4, 1024, 32768)
+            for _ in range(3):
+                o, _ = eng.softmax_rows(x, None, 1.0); eng.free(o)
+        elif args.profile == "prefill":
+            cfg = W.LlamaConfig()
+            m = W.LlamaPrefill(eng, cfg, W.llama_weights(cfg), 8, 512)
+            ids = eng.upload_bits(rng.integers(0, cfg.vocab, (1, 4096)).astype(np.int32).view(np.uint32), 1, 4096, I32)
+            for _ in range(2):
+                lg, am = m.forward(ids); eng.free(lg); eng.free(am)
+        else:
+            raise SystemExit(f"unknown profile {args.profile!r}")
+        eng.sync()
+    print("profile sequence done:", args.profile)
+
+
 def run_multi(args):
     from metalium_rs_b200 import sharded
     sharded.bench_main(args, METRIC, UNIT, NN_SIZE, workload_name, peaks, ClockSampler, cheap_bf16)
@@ -410,10 +446,13 @@ def main():
     ap.add_argument("--extras", action="store_true", help="also time the rest of the sweep and the memory-bound suite")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--profile", default="", help="run a short fixed sequence for an ncu capture: membound | softmax | prefill")
     ap.add_argument("--size", type=int, default=0, help="override the N=1 problem size (profiling on a small case)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.profile:
+        return run_profile(args)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus > 1 or world > 1:
         return run_multi(args)
