@@ -172,7 +172,7 @@ int32_t b200_full_sum(b200_engine*, b200_buffer a, int32_t mean, b200_buffer* ou
  * `device_values` and `device_out` (one float) are the caller's device memory; the call
  * launches on `cuda_stream` (a cudaStream_t; NULL is the default stream) of the current
  * device and returns without waiting.  It calls no cudaMalloc or cudaFree: the per-block
- * partial sums go to a fixed 4,736-byte array inside the library image, which every GPU
+ * partial sums go to a fixed 4,768-byte array inside the library image, which every GPU
  * that loads the library holds until exit.
  *  - n may not exceed 2^31 (B200_UNSUPPORTED, text through b200_last_error(NULL, ..)).
  *  - The first call on each device looks the array's address up; make that call before

@@ -444,6 +444,7 @@ int32_t b200_engine_create(int32_t device_ordinal, const b200_config* cfg, b200_
   if (ce == cudaSuccess) ce = cudaMemsetAsync(e->d_err, 0, 256, e->stream);
   if (ce == cudaSuccess) ce = cudaMallocHost(&e->h_err, sizeof(int));
   if (ce == cudaSuccess) ce = cudaMalloc(&e->full_scratch, full_sum_scratch_floats() * sizeof(float));
+  if (ce == cudaSuccess) ce = cudaMemsetAsync(e->full_scratch, 0, full_sum_scratch_floats() * sizeof(float), e->stream);
   if (ce != cudaSuccess) {
     g_create_error = std::string("engine set-up: ") + cudaGetErrorString(ce);
     delete e;
@@ -839,7 +840,7 @@ int32_t b200_full_sum(b200_engine* e, b200_buffer a, int32_t mean, b200_buffer* 
   Buf* O = nullptr;
   st = e->new_buffer(1, 1, B200_F32, out, &O);
   if (st) return st;
-  st = e->launched(launch_full_sum(src, n, mean, e->full_scratch, (float*)O->ptr, e->stream), "full_sum", 2);
+  st = e->launched(launch_full_sum(src, n, mean, e->full_scratch, (float*)O->ptr, e->stream), "full_sum", 1);
   if (st) { e->drop(*out); return st; }
   set_dims(out_dims, 1, 1);
   return B200_OK;

@@ -185,9 +185,14 @@ __device__ __forceinline__ float block_sum_256(float v, float* sm) {
   return t;  // valid in thread 0
 }
 
+// One launch: every block leaves its partial, and the block that takes the last ticket adds the
+// partials in index order (so the bits do not depend on which block that is) and resets the
+// ticket.  scratch: FULL_BLOCKS partials, then the ticket word, which must be zero at entry.
 __global__ void __launch_bounds__(FULL_THREADS)
-full_sum_stage1(const float* __restrict__ a, uint64_t n, float* __restrict__ partial) {
+full_sum_fused(const float* __restrict__ a, uint64_t n, int mean, float* __restrict__ scratch,
+               float* __restrict__ out) {
   __shared__ float sm[FULL_THREADS / 32];
+  __shared__ int is_last;
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
   const bool vec = (reinterpret_cast<uintptr_t>(a) & 15) == 0;
   const uint64_t n4 = vec ? n / 4 : 0;
@@ -206,21 +211,25 @@ full_sum_stage1(const float* __restrict__ a, uint64_t n, float* __restrict__ par
     const float4 v0 = __ldcs(p + i);
     s0 = s0 + ((v0.x + v0.y) + (v0.z + v0.w));
   }
-  // tail (and the whole array when it is not 16-byte aligned)
   for (uint64_t j = n4 * 4 + (uint64_t)blockIdx.x * FULL_THREADS + threadIdx.x; j < n; j += stride)
     s1 = s1 + a[j];
   const float t = block_sum_256((s0 + s1) + (s2 + s3), sm);
-  if (threadIdx.x == 0) partial[blockIdx.x] = t;
-}
-
-__global__ void __launch_bounds__(FULL_THREADS)
-full_sum_stage2(const float* __restrict__ partial, int count, uint64_t n, int mean,
-                float* __restrict__ out) {
-  __shared__ float sm[FULL_THREADS / 32];
+  unsigned int* ticket = reinterpret_cast<unsigned int*>(scratch + FULL_BLOCKS);
+  if (threadIdx.x == 0) {
+    scratch[blockIdx.x] = t;
+    __threadfence();
+    is_last = (atomicAdd(ticket, 1u) == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
   float s = 0.f;
-  for (int i = threadIdx.x; i < count; i += FULL_THREADS) s = s + partial[i];
-  const float t = block_sum_256(s, sm);
-  if (threadIdx.x == 0) out[0] = mean ? t / (float)n : t;  // sum DIV_SCALAR n (ops.rs:3260-3270)
+  for (int k = threadIdx.x; k < FULL_BLOCKS; k += FULL_THREADS) s = s + __ldcg(scratch + k);
+  const float total = block_sum_256(s, sm);
+  if (threadIdx.x == 0) {
+    out[0] = mean ? total / (float)n : total;  // sum DIV_SCALAR n (ops.rs:3260-3270)
+    *ticket = 0u;
+  }
 }
 
 // ---- softmax rows -----------------------------------------------------------------
@@ -454,6 +463,130 @@ softmax_cluster_kernel(const float* __restrict__ x, const uint32_t* __restrict__
   if (csize > 1) cluster.sync();  // no CTA leaves while a peer may still read its exchange slots
 }
 
+// Rows of 4,097..32,768 columns: several independent workers a block, so an SM has several rows in
+// flight and one row's loads overlap another's exponentials and stores.  A worker is T threads
+// (T = columns / 64); each thread keeps half of its share of the row in registers and half in
+// its own shared-memory slots, filled by cp.async and touched by no other thread, so the only
+// synchronisation is the worker's two reductions (named barriers).  One block an SM, persistent.
+template <int T>
+__global__ void __launch_bounds__(1024, 1)
+softmax_workers_kernel(const float* __restrict__ x, const uint32_t* __restrict__ mask, uint64_t mask_rows,
+                       float scale, int log_form, void* __restrict__ out, int out_bf16, uint64_t rows, uint32_t cols) {
+  constexpr int G = 1024 / T, WARPS = T / 32, VR = 8, VS = 8;
+  extern __shared__ float4 ring[];               // [G][VS][T]
+  __shared__ float red[2][G][WARPS];
+  const int g = threadIdx.x / T, t = threadIdx.x % T, wl = t >> 5;
+  float4* mine = ring + (size_t)g * VS * T;
+  const uint32_t n4 = cols / 4;
+  const bool has_scale = scale != 1.0f;
+  const uint64_t nworkers = (uint64_t)gridDim.x * G;
+  auto worker_reduce = [&](float v, bool is_max, int which) -> float {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float w = __shfl_xor_sync(0xffffffffu, v, o);
+      v = is_max ? fmaxf(v, w) : v + w;
+    }
+    if ((t & 31) == 0) red[which][g][wl] = v;
+    asm volatile("bar.sync %0, %1;" ::"r"(g + 1), "r"(T) : "memory");
+    float r = red[which][g][0];
+#pragma unroll
+    for (int w = 1; w < WARPS; ++w) r = is_max ? fmaxf(r, red[which][g][w]) : r + red[which][g][w];
+    return r;  // red[which] is not rewritten before the worker's next barrier on the other slot
+  };
+  for (uint64_t row = (uint64_t)blockIdx.x * G + g; row < rows; row += nworkers) {
+    const float4* xr = reinterpret_cast<const float4*>(x + row * cols);
+    const uint4* mr = mask ? reinterpret_cast<const uint4*>(mask + (row % mask_rows) * cols) : nullptr;
+    // the shared-memory half first: asynchronous, lands while the register half is loaded
+#pragma unroll
+    for (int u = 0; u < VS; ++u) {
+      const uint32_t i = t + (VR + u) * T;
+      if (i < n4) {
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(mine + u * T + t);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(xr + i) : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    float4 v[VR];
+    float m = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < VR; ++u) {
+      const uint32_t i = t + u * T;
+      if (i < n4) {
+        float4 q = __ldcs(xr + i);
+        if (mr || has_scale) {
+          const uint4 k = mr ? __ldg(mr + i) : make_uint4(0, 0, 0, 0);
+          q.x = scaled_masked(q.x, k.x, scale, has_scale); q.y = scaled_masked(q.y, k.y, scale, has_scale);
+          q.z = scaled_masked(q.z, k.z, scale, has_scale); q.w = scaled_masked(q.w, k.w, scale, has_scale);
+        }
+        v[u] = q;
+        m = fmaxf(m, fmaxf(fmaxf(q.x, q.y), fmaxf(q.z, q.w)));
+      }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int u = 0; u < VS; ++u) {
+      const uint32_t i = t + (VR + u) * T;
+      if (i < n4) {
+        float4 q = mine[u * T + t];
+        if (mr || has_scale) {
+          const uint4 k = mr ? __ldg(mr + i) : make_uint4(0, 0, 0, 0);
+          q.x = scaled_masked(q.x, k.x, scale, has_scale); q.y = scaled_masked(q.y, k.y, scale, has_scale);
+          q.z = scaled_masked(q.z, k.z, scale, has_scale); q.w = scaled_masked(q.w, k.w, scale, has_scale);
+          mine[u * T + t] = q;
+        }
+        m = fmaxf(m, fmaxf(fmaxf(q.x, q.y), fmaxf(q.z, q.w)));
+      }
+    }
+    m = worker_reduce(m, true, 0);
+    m = (m < -FLT_MAX) ? -FLT_MAX : m;
+    float sum = 0.f;
+#pragma unroll
+    for (int u = 0; u < VR; ++u) {
+      const uint32_t i = t + u * T;
+      if (i < n4) {
+        float4 q = v[u];
+        if (log_form) {
+          q.x -= m; q.y -= m; q.z -= m; q.w -= m;
+          sum = sum + ((expf(q.x) + expf(q.y)) + (expf(q.z) + expf(q.w)));
+        } else {
+          q.x = expf(q.x - m); q.y = expf(q.y - m); q.z = expf(q.z - m); q.w = expf(q.w - m);
+          sum = sum + ((q.x + q.y) + (q.z + q.w));
+        }
+        v[u] = q;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < VS; ++u) {
+      const uint32_t i = t + (VR + u) * T;
+      if (i < n4) {
+        float4 q = mine[u * T + t];
+        if (log_form) {
+          q.x -= m; q.y -= m; q.z -= m; q.w -= m;
+          sum = sum + ((expf(q.x) + expf(q.y)) + (expf(q.z) + expf(q.w)));
+        } else {
+          q.x = expf(q.x - m); q.y = expf(q.y - m); q.z = expf(q.z - m); q.w = expf(q.w - m);
+          sum = sum + ((q.x + q.y) + (q.z + q.w));
+        }
+        mine[u * T + t] = q;
+      }
+    }
+    sum = worker_reduce(sum, false, 1);
+    void* orow = reinterpret_cast<char*>(out) + row * cols * (out_bf16 ? 2 : 4);
+    const float l = log_form ? logf(sum) : 0.f;
+    const float inv = 1.0f / ((sum < FLT_MIN) ? FLT_MIN : sum);
+#pragma unroll
+    for (int u = 0; u < VR + VS; ++u) {
+      const uint32_t i = t + u * T;
+      if (i < n4) {
+        float4 q = u < VR ? v[u < VR ? u : 0] : mine[(u - VR) * T + t];
+        if (log_form) { q.x -= l; q.y -= l; q.z -= l; q.w -= l; }
+        else { q.x *= inv; q.y *= inv; q.z *= inv; q.w *= inv; }
+        store4(orow, i, q, out_bf16);
+      }
+    }
+  }
+}
+
 // Any width: a block a row, three passes over global memory (the second and third
 // mostly from L2).  Rows too short or ragged for the register kernel, or too long.
 __global__ void __launch_bounds__(256)
@@ -652,12 +785,11 @@ cudaError_t launch_reduce(const void* a, int a_bf16, uint64_t rows, uint64_t col
   }
 }
 
-uint64_t full_sum_scratch_floats() { return FULL_BLOCKS; }
+uint64_t full_sum_scratch_floats() { return FULL_BLOCKS + 8; }
 
 cudaError_t launch_full_sum(const float* a, uint64_t n, int mean, float* scratch, float* out,
                             cudaStream_t s) {
-  full_sum_stage1<<<FULL_BLOCKS, FULL_THREADS, 0, s>>>(a, n, scratch);
-  full_sum_stage2<<<1, FULL_THREADS, 0, s>>>(scratch, FULL_BLOCKS, n, mean, out);
+  full_sum_fused<<<FULL_BLOCKS, FULL_THREADS, 0, s>>>(a, n, mean, scratch, out);
   return cudaGetLastError();
 }
 
@@ -669,11 +801,11 @@ cudaError_t launch_full_sum(const float* a, uint64_t n, int mean, float* scratch
 // treats any allocation of its own as a leak), or code that runs where allocating would
 // synchronise the device at the wrong moment.  For them the two-stage sum's per-block
 // partials live in a fixed array inside the library image instead of in a buffer the
-// engine allocates.  Every GPU that loads the library holds these 4,736 bytes until exit.
+// engine allocates.  Every GPU that loads the library holds these 4,768 bytes until exit.
 namespace {
 constexpr uint64_t NOALLOC_MAX_ELEMS = 1ull << 31;  // the largest input accepted (8 GiB of F32)
 constexpr int NOALLOC_MAX_DEVICES = 64;
-static __device__ __align__(256) float g_full_sum_partials[b200::FULL_BLOCKS];
+static __device__ __align__(256) float g_full_sum_partials[b200::FULL_BLOCKS + 8];  // partials, then the ticket word
 float* g_partials_addr[NOALLOC_MAX_DEVICES] = {};
 std::mutex g_partials_lock;
 }  // namespace
@@ -716,11 +848,11 @@ int32_t b200_full_sum_noalloc(const float* device_values, uint64_t n, int32_t me
     }
     partials = g_partials_addr[dev];
   }
-  // Stage 1 writes every one of the partials before stage 2 reads them, so nothing has to
-  // start at zero and the last call's contents do not matter.
+  // Every partial is rewritten before it is read, so the last call's partials do not matter.  The
+  // one word that must start at zero is the ticket after them: it is zero when the library is
+  // loaded and the block that finishes a call puts it back to zero.
   cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
-  b200::full_sum_stage1<<<b200::FULL_BLOCKS, b200::FULL_THREADS, 0, s>>>(device_values, n, partials);
-  b200::full_sum_stage2<<<1, b200::FULL_THREADS, 0, s>>>(partials, b200::FULL_BLOCKS, n, mean, device_out);
+  b200::full_sum_fused<<<b200::FULL_BLOCKS, b200::FULL_THREADS, 0, s>>>(device_values, n, mean, partials, device_out);
   e = cudaGetLastError();
   if (e != cudaSuccess) {
     b200::set_global_error((std::string("full_sum_noalloc: launch: ") + cudaGetErrorString(e)).c_str());
@@ -730,6 +862,13 @@ int32_t b200_full_sum_noalloc(const float* device_values, uint64_t n, int32_t me
 }
 
 namespace b200 {
+
+// Development switch: B200TT_SOFTMAX=old keeps the one-block-a-row kernels for wide rows.
+static bool softmax_old_path() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("B200TT_SOFTMAX"); v = (e && e[0] == 'o') ? 1 : 0; }
+  return v == 1;
+}
 
 cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t mask_rows, float scale,
                                 int log_form, void* out, int out_bf16, uint64_t rows, uint64_t cols,
@@ -749,6 +888,27 @@ cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t m
     else if (n4 <= 256) SM_LAUNCH(128, 2);
     else if (n4 <= 512) SM_LAUNCH(256, 2);
     else if (n4 <= 1024) SM_LAUNCH(256, 4);
+  } else if (al && cols % 4 == 0 && n4 > 1024 && n4 <= 8192 && !softmax_old_path()) {
+    // T threads a worker, 16 float4 a thread: the smallest T that covers the row
+    const int threads = n4 <= 2048 ? 128 : (n4 <= 4096 ? 256 : 512);
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const size_t smem = 1024 * 8 * sizeof(float4);
+    const uint64_t workers = 1024 / threads;
+    const unsigned gridw = (unsigned)((rows + workers - 1) / workers < (uint64_t)sms ? (rows + workers - 1) / workers : (uint64_t)sms);
+#define SW(TT)                                                                                                  \
+    do {                                                                                                          \
+      static bool attr = false;                                                                                   \
+      if (!attr) {                                                                                                \
+        cudaError_t e = cudaFuncSetAttribute(softmax_workers_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return e;                                                                           \
+        attr = true;                                                                                              \
+      }                                                                                                           \
+      softmax_workers_kernel<TT><<<gridw, 1024, smem, s>>>(x, mask, mask_rows, scale, log_form, out, out_bf16, rows, (uint32_t)cols); \
+    } while (0)
+    if (threads == 128) SW(128); else if (threads == 256) SW(256); else SW(512);
+#undef SW
   } else if (al && cols % 4 == 0 && n4 > 2048 && n4 <= 8192) {
     // Measured on a B200: for rows this wide one 1024-thread block a row beats splitting the
     // row over a cluster (the cluster barriers cost more than the lost overlap).

@@ -47,10 +47,15 @@ def interleave(staged, n: int):
 
 class ShardedMatmul:
     """C = A B on `world` GPUs, B's columns split.  A [M,K] and the local B slice [K,per] are
-    engine buffers that stay resident; `run()` launches product, all-gather and the strided
-    copy on the engine's stream and returns a new buffer holding the full row-major C."""
+    engine buffers that stay resident; `run()` returns a new buffer holding the full row-major C.
 
-    def __init__(self, eng, rank: int, world: int, m: int, k: int, n: int, a_buf: int, b_slice_buf: int, bf16=True):
+    The product is cut in `panels` row panels.  Each panel's product is launched on the engine's
+    stream and its all-gather is issued asynchronously behind it, so NCCL moves panel p over
+    NVLink while the tensor cores work on panel p+1; one strided copy at the end lays the
+    gathered [panel, rank, rows, per] blocks side by side as the row-major C."""
+
+    def __init__(self, eng, rank: int, world: int, m: int, k: int, n: int, a_buf: int, b_slice_buf: int, bf16=True,
+                 panels: int = 4):
         import torch
         from . import BF16, F32
         self.eng, self.rank, self.world = eng, rank, world
@@ -59,31 +64,40 @@ class ShardedMatmul:
         self.per = self.parts[0][1] - self.parts[0][0]
         if any(hi - lo != self.per for lo, hi in self.parts):
             raise ValueError(f"{n} columns do not split evenly over {world} ranks in whole tiles")
+        while panels > 1 and (m % panels or (m // panels) % 256):
+            panels -= 1
+        self.panels, self.mp = panels, m // panels
         self.a, self.b = a_buf, b_slice_buf
         self.bf16 = bf16
-        dt = torch.int16 if bf16 else torch.float32
+        self.dt = torch.int16 if bf16 else torch.float32
         self.elem = BF16 if bf16 else F32
         dev = torch.device("cuda", torch.cuda.current_device())
-        # torch owns the exchange buffers; the engine adopts them so its kernels write and read them
-        self.local = torch.empty((m, self.per), dtype=dt, device=dev)
-        self.staged = torch.empty((world, m, self.per), dtype=dt, device=dev)
-        self.staged_buf = eng.adopt(self.staged.data_ptr(), world * m, self.per, self.elem)
+        # torch owns the exchange buffer; the engine adopts it so its copy kernel reads it
+        self.staged = torch.empty((panels * world * self.mp, self.per), dtype=self.dt, device=dev)
+        self.staged_buf = eng.adopt(self.staged.data_ptr(), panels * world * self.mp, self.per, self.elem)
         self.stream = torch.cuda.ExternalStream(eng.stream())
-        self.moves = [((r * m, 0), (0, r * self.per), (m, self.per), False) for r in range(world)]
+        self.a_panels = [eng.slice_rows(a_buf, p * self.mp, self.mp)[0] for p in range(panels)] if panels > 1 else [a_buf]
+        self.moves = [(((p * world + r) * self.mp, 0), (p * self.mp, r * self.per), (self.mp, self.per), False)
+                      for p in range(panels) for r in range(world)]
 
     def run(self) -> int:
         import torch
         import torch.distributed as dist
-        eng = self.eng
-        out, _ = (eng.matmul_dram_bf16 if self.bf16 else eng.matmul_dram)(self.a, False, self.b, False)
-        ptr, nbytes = eng.device_ptr(out)
+        eng, g, mp = self.eng, self.world, self.mp
+        mm = eng.matmul_dram_bf16 if self.bf16 else eng.matmul_dram
+        pending = []
         with torch.cuda.stream(self.stream):
-            src = _as_tensor(ptr, (self.m, self.per), self.local.dtype)
-            dst = self.staged.view(self.world * self.m, self.per)
-            if self.bf16:  # NCCL has no 16-bit integer type: name the same bits BF16
-                src, dst = src.view(torch.bfloat16), dst.view(torch.bfloat16)
-            dist.all_gather_into_tensor(dst, src)
-        eng.free(out)
+            for p in range(self.panels):
+                out, _ = mm(self.a_panels[p], False, self.b, False)
+                ptr, _ = eng.device_ptr(out)
+                src = _as_tensor(ptr, (mp, self.per), self.dt)
+                dst = self.staged[p * g * mp:(p + 1) * g * mp]
+                if self.bf16:  # NCCL has no 16-bit integer type: name the same bits BF16
+                    src, dst = src.view(torch.bfloat16), dst.view(torch.bfloat16)
+                pending.append((dist.all_gather_into_tensor(dst, src, async_op=True), out))
+            for work, out in pending:
+                work.wait()      # the engine's stream waits for the gather; the panel may then be reused
+                eng.free(out)
         full, _ = eng.copy_blocks(self.staged_buf, self.moves, (self.m, self.n))
         return full  # the caller frees it
 
@@ -236,7 +250,7 @@ def bench_main(args, metric, unit, size, workload_name, peaks, ClockSampler, che
                 "config": {"workload": workload_name(world) if m == size else f"bf16 gemm {m}^3 column-sharded over {world}",
                            "m": m, "n": n, "k": k, "columns_per_rank": per,
                            "l2": "operands exceed the 126 MB L2; no flush needed",
-                           "collective": "NCCL all-gather of C slices + one strided copy into row-major C"},
+                           "collective": f"{sm.panels} row panels: NCCL all-gather of panel p overlapped with the product of panel p+1, then one strided copy into row-major C"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
                 "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel + ncclAllGather", "achieved": value, "peak": peak,
                              "unit": unit, "frac": value / peak, "peak_source": f"{which} cuBLAS bf16 burst x {world}",
