@@ -231,6 +231,21 @@ int32_t b200_copy_blocks(b200_engine*, b200_buffer a, const b200_block_move* mov
 int32_t b200_repack(b200_engine*, b200_buffer a, const uint64_t* row_col_pairs, const uint64_t dims[2],
                     b200_buffer* out, uint64_t out_dims[2]);
 
+/* --- attention for a few query rows a key/value head, as one op: server.rs:257 `attention_rows`
+ * (kernel contract: crates/tt-kernels/src/attention.rs:360-372).  buffers = [q, k, v, mask]; item i
+ * names the top-left element of head i's blocks: q_i [m, d] (F32), K_i [l, d] and V_i [l, dv]
+ * (both F32 or both BF16, read as they lie), mask the Bool [1, l] of positions not attended, the
+ * same for every row.  dims = [m, d, l, dv].  The result is the F32 [1, n_items * m * dv] row: the
+ * heads' rows stacked in row-major order.  out_i = softmax(scale * q_i K_i^T, masked) V_i with the
+ * composition's steps (product, scale then mask fill, clamped maximum, exp, clamped sum, division,
+ * product).  Refused (UNSUPPORTED) unless 1 <= m <= 32 and d, l, dv are positive multiples of 32
+ * (attention.rs:156-171), the key and value blocks start at a column that is a multiple of 4 in
+ * buffers whose width is one, and every block lies inside its buffer. */
+typedef struct b200_attention_item { uint64_t q[2], k[2], v[2]; } b200_attention_item;
+int32_t b200_attention_rows(b200_engine*, const b200_buffer buffers[4], const b200_attention_item* items,
+                            uint64_t n_items, const uint64_t dims[4], float scale,
+                            b200_buffer* out, uint64_t out_dims[2]);
+
 /* --- traces: server.rs:591 `begin_trace`, :595 `end_trace`, :650 `run_trace`, :660 `release_trace`.
  * Ops issued between begin and end are captured into a CUDA graph instead of running; a replay
  * runs them again on the same buffers.  Inputs are buffers made before the capture (refresh them

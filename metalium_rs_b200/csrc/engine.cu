@@ -1230,6 +1230,67 @@ int32_t b200_copy_blocks(b200_engine* e, b200_buffer a, const b200_block_move* m
   return B200_OK;
 }
 
+int32_t b200_attention_rows(b200_engine* e, const b200_buffer buffers[4], const b200_attention_item* items, uint64_t n_items,
+                            const uint64_t dims[4], float scale, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *Q = nullptr, *K = nullptr, *V = nullptr, *M = nullptr;
+  int st = e->need(buffers[0], &Q, "attention_rows");
+  if (!st) st = e->need(buffers[1], &K, "attention_rows");
+  if (!st) st = e->need(buffers[2], &V, "attention_rows");
+  if (!st) st = e->need(buffers[3], &M, "attention_rows");
+  if (st) return st;
+  const uint64_t m = dims[0], d = dims[1], l = dims[2], dv = dims[3];
+  if (Q->elem != B200_F32) return e->fail(B200_UNSUPPORTED, "attention_rows: queries are F32");
+  if ((K->elem != B200_F32 && K->elem != B200_BF16) || V->elem != K->elem)
+    return e->fail(B200_UNSUPPORTED, "attention_rows: keys and values are both F32 or both BF16");
+  if (M->elem != B200_BOOL) return e->fail(B200_UNSUPPORTED, "attention_rows: the mask is Bool");
+  if (n_items == 0) return e->fail(B200_UNSUPPORTED, "attention_rows: no heads");
+  if (M->rows != 1 || M->cols != l)
+    return e->fail(B200_UNSUPPORTED, "attention_rows: a [%llu, %llu] mask for %llu positions",
+                   (unsigned long long)M->rows, (unsigned long long)M->cols, (unsigned long long)l);
+  if (m < 1 || m > 32 || d == 0 || l == 0 || dv == 0 || d % 32 || l % 32 || dv % 32 || l > (1ull << 30) || d > 8192 || dv > 8192)
+    return e->fail(B200_UNSUPPORTED, "attention_rows: [m, d, l, dv] = [%llu, %llu, %llu, %llu] (1..32 rows, whole tiles along d, l and dv)",
+                   (unsigned long long)m, (unsigned long long)d, (unsigned long long)l, (unsigned long long)dv);
+  if (K->cols % 4 || V->cols % 4) return e->fail(B200_UNSUPPORTED, "attention_rows: key and value buffers are a multiple of 4 columns wide");
+  std::vector<AttnItem> host(n_items);
+  for (uint64_t i = 0; i < n_items; ++i) {
+    const b200_attention_item& it = items[i];
+    if (it.q[0] + m > Q->rows || it.q[1] + d > Q->cols || it.k[0] + l > K->rows || it.k[1] + d > K->cols ||
+        it.v[0] + l > V->rows || it.v[1] + dv > V->cols)
+      return e->fail(B200_UNSUPPORTED, "attention_rows: head %llu's blocks lie outside a tensor", (unsigned long long)i);
+    if (it.k[1] % 4 || it.v[1] % 4)
+      return e->fail(B200_UNSUPPORTED, "attention_rows: head %llu's keys or values start at a column that is not a multiple of 4", (unsigned long long)i);
+    host[i] = AttnItem{it.q[0] * Q->cols + it.q[1], it.k[0] * K->cols + it.k[1], it.v[0] * V->cols + it.v[1]};
+  }
+  int splits = 1, lc = (int)l;
+  attention_rows_plan(n_items, (int)m, (int)l, /*sms: ask the device*/ 0, &splits, &lc);
+  const float* qp = (const float*)Q->ptr; const void* kp = K->ptr; const void* vp = V->ptr; const uint32_t* mp = (const uint32_t*)M->ptr;
+  const uint64_t q_ld = Q->cols, k_ld = K->cols, v_ld = V->cols;
+  const int kv_bf16 = K->elem == B200_BF16;
+  Buf* O = nullptr;
+  st = e->new_buffer(1, n_items * m * dv, B200_F32, out, &O);
+  if (st) return st;
+  float* op = (float*)O->ptr;
+  void* dev = nullptr; uint64_t got = 0;
+  st = e->to_device(host.data(), n_items * sizeof(AttnItem), &dev, &got);
+  if (st) { e->drop(*out); return st; }
+  void* scratch = nullptr; uint64_t sgot = 0;
+  const size_t sfl = attention_rows_scratch_floats(n_items, (int)m, (int)dv, splits);
+  if (sfl) {
+    st = e->alloc(sfl * sizeof(float), &scratch, &sgot);
+    if (st) { e->release(dev, got); e->drop(*out); return st; }
+  }
+  int launches = 0;
+  cudaError_t ce = launch_attention_rows(qp, q_ld, kp, k_ld, vp, v_ld, kv_bf16, mp, (const AttnItem*)dev, n_items, (int)m, (int)d,
+                                         (int)l, (int)dv, scale, splits, lc, (float*)scratch, op, &launches, e->stream);
+  st = e->launched(ce, "attention_rows", launches > 0 ? launches : 1);
+  if (scratch) e->release(scratch, sgot);
+  e->release(dev, got);
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, 1, n_items * m * dv);
+  return B200_OK;
+}
+
 int32_t b200_repack(b200_engine* e, b200_buffer a, const uint64_t* pairs, const uint64_t dims[2], b200_buffer* out, uint64_t out_dims[2]) {
   cudaSetDevice(e->device);
   Buf* A = nullptr;

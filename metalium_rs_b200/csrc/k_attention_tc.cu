@@ -1,0 +1,364 @@
+// Fused attention over whole sequences on the tensor cores: for each (batch, head) block
+//     O = softmax(scale * Q K^T [causal]) V,   Q [sq, d], K [sk, d], V [sk, d]  (BF16), O BF16,
+// with the scores and probabilities never written to memory.  It replaces, for prefill-shaped
+// work, the reference's composed attention (crates/burn-tt/src/ops.rs:4825 `padded_attention`:
+// a batched Q K^T, `SCALE_MASK_FILL`, the row softmax, a batched P V), whose [rows, sk] F32 scores
+// are the largest memory cost of the path.
+//
+// One CTA owns 128 query rows of one block and walks the key tiles (128 keys) twice:
+//   pass 1: S = Q K_j^T on tcgen05 into TMEM, the softmax warps read it and keep the row maximum;
+//   pass 2: S again, P = exp2(S' - max) rounded to BF16 into shared memory (the 128-byte-swizzled
+//           K-major layout the MMA reads), O += P V_j accumulated in TMEM, the row sum kept in
+//           registers; at the end O / sum is written as BF16.
+// With the final maximum known before the first product with V, O is never rescaled; Q K^T is
+// computed twice, which costs tensor-core time the kernel has to spare (the exponentials bound it).
+// Warp 0 lane 0 issues the TMA loads, warp 1 lane 0 the MMAs, warps 2-5 are the softmax (a thread
+// a query row = a TMEM lane).  S is double-buffered in TMEM so the next tile's product runs under
+// this tile's exponentials.  Every wait is bounded; a wait that runs out sets the engine's error
+// word to TIMEOUT and the CTA leaves in order (copies drained, TMEM freed).
+#include <cfloat>
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "tc_common.cuh"
+
+namespace b200 {
+namespace {
+
+using namespace tc;
+
+constexpr uint32_t TILE_BYTES = 128 * 64 * 2;   // a [128 rows, 64 columns] BF16 box
+constexpr uint32_t P_BYTES = 2 * TILE_BYTES;    // [128 rows, 128 keys]
+
+struct AttnTcParams {
+  const AttnBlockDev* items;
+  uint32_t q_tiles, k_tiles;
+  int32_t causal, causal_off;   // a query i sees keys j <= i + causal_off
+  float scale_log2;             // scale * log2(e)
+  uint16_t* out;
+  uint64_t o_ld;
+  int* err;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  return (uint32_t)f32_to_bf16_bits(__float_as_uint(a)) | ((uint32_t)f32_to_bf16_bits(__float_as_uint(b)) << 16);
+}
+
+template <int D>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, const AttnTcParams p) {
+  constexpr int CH = D / 64;                       // 64-column chunks of a row of Q, K or V
+  constexpr int KS = D == 64 ? 3 : 2;              // stages of K and of V
+  constexpr uint32_t OP_BYTES = CH * TILE_BYTES;   // one Q, K or V tile
+  constexpr uint32_t S_COLS = 128, O_COL = 256;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + OP_BYTES;
+  uint8_t* sV = sK + KS * OP_BYTES;
+  uint8_t* sP = sV + KS * OP_BYTES;
+  uint64_t* q_full = (uint64_t*)(sP + P_BYTES);
+  uint64_t* k_full = q_full + 1;
+  uint64_t* k_empty = k_full + KS;
+  uint64_t* v_full = k_empty + KS;
+  uint64_t* v_empty = v_full + KS;
+  uint64_t* s_full = v_empty + KS;
+  uint64_t* s_empty = s_full + 2;
+  uint64_t* p_full = s_empty + 2;
+  uint64_t* p_empty = p_full + 1;
+  uint64_t* o_full = p_empty + 1;
+  uint32_t* tmem_slot = (uint32_t*)(o_full + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < KS; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 128); }
+    mbar_init(p_full, 128);
+    mbar_init(p_empty, 1);
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  // heavy query tiles first: under a causal mask the last tile of a block has the most keys
+  const uint32_t qt = p.q_tiles - 1 - blockIdx.x;
+  const AttnBlockDev it = p.items[blockIdx.y];
+  const int32_t i0 = (int32_t)(qt * 128);
+  uint32_t nk = p.k_tiles;
+  if (p.causal) {
+    const int32_t last = i0 + 127 + p.causal_off;      // the last key any row of this tile sees (>= 0)
+    const uint32_t lim = (uint32_t)(last / 128) + 1;
+    nk = lim < nk ? lim : nk;
+  }
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      bool ok = true;
+      mbar_expect_tx(q_full, OP_BYTES);
+#pragma unroll
+      for (int c = 0; c < CH; ++c) tma_load_2d(sQ + c * TILE_BYTES, &map_q, q_full, it.q_c + c * 64, it.q_r + i0);
+      uint32_t ks = 0, kph = 0, vs = 0, vph = 0;
+      for (int pass = 0; pass < 2 && ok; ++pass) {
+        for (uint32_t j = 0; j < nk; ++j) {
+          if (!mbar_wait(&k_empty[ks], kph ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&k_full[ks], OP_BYTES);
+#pragma unroll
+          for (int c = 0; c < CH; ++c)
+            tma_load_2d(sK + ks * OP_BYTES + c * TILE_BYTES, &map_k, &k_full[ks], it.k_c + c * 64, it.k_r + (int32_t)(j * 128));
+          if (++ks == KS) { ks = 0; kph ^= 1; }
+          if (pass == 1) {
+            if (!mbar_wait(&v_empty[vs], vph ^ 1, abort_flag)) { ok = false; break; }
+            mbar_expect_tx(&v_full[vs], OP_BYTES);
+#pragma unroll
+            for (int c = 0; c < CH; ++c)
+              tma_load_2d(sV + vs * OP_BYTES + c * TILE_BYTES, &map_v, &v_full[vs], it.v_c + c * 64, it.v_r + (int32_t)(j * 128));
+            if (++vs == KS) { vs = 0; vph ^= 1; }
+          }
+        }
+      }
+      if (!ok) {
+        atomicCAS(p.err, 0, TIMEOUT_CODE);
+        *abort_flag = 1;
+      }
+      // Drain: no copy may outlive the CTA.  Stages before the cursor were armed in the current
+      // phase, the rest in the previous one (or never: their barrier is then already past it).
+      {
+        const long long t0 = clock64();
+        while (!mbar_try(q_full, 0)) { if (clock64() - t0 > WAIT_CYCLES) break; }
+      }
+      for (int s = 0; s < KS; ++s) {
+        const uint32_t kp = (s < (int)ks) ? kph : (kph ^ 1);
+        const uint32_t vp = (s < (int)vs) ? vph : (vph ^ 1);
+        const long long t0 = clock64();
+        while (!mbar_try(&k_full[s], kp)) { if (clock64() - t0 > WAIT_CYCLES) break; }
+        while (!mbar_try(&v_full[s], vp)) { if (clock64() - t0 > WAIT_CYCLES) break; }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      // kind::f16: F32 accumulate (bit 4), BF16 A and B (bits 7, 10), B MN-major for P V (bit 16)
+      constexpr uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      uint32_t ks = 0, kph = 0, vs = 0, vph = 0, t = 0;
+      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      auto issue_qk = [&]() -> bool {
+        const uint32_t buf = t & 1, sph = (t >> 1) & 1;
+        if (!mbar_wait(&s_empty[buf], sph ^ 1, abort_flag)) return false;
+        if (!mbar_wait(&k_full[ks], kph, abort_flag)) return false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t k_addr = smem_u32(sK + ks * OP_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < D / UMMA_K; ++kk) {
+          const uint32_t off = (kk / 4) * TILE_BYTES + (kk % 4) * 32;
+          umma_bf16(tmem_base + buf * S_COLS, make_desc(q_addr + off, 16, 1024), make_desc(k_addr + off, 16, 1024), idesc_qk, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(&k_empty[ks]);
+        umma_commit(&s_full[buf]);
+        if (++ks == KS) { ks = 0; kph ^= 1; }
+        ++t;
+        return true;
+      };
+      for (uint32_t j = 0; j < nk && ok; ++j) ok = issue_qk();          // pass 1
+      if (ok) ok = issue_qk();                                           // pass 2, tile 0
+      for (uint32_t j = 0; j < nk && ok; ++j) {
+        if (j + 1 < nk) { ok = issue_qk(); if (!ok) break; }             // the next scores run under these exponentials
+        if (!mbar_wait(p_full, j & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&v_full[vs], vph, abort_flag)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t v_addr = smem_u32(sV + vs * OP_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 128 / UMMA_K; ++kk) {
+          const uint64_t adesc = make_desc(p_addr + (kk / 4) * TILE_BYTES + (kk % 4) * 32, 16, 1024);
+          const uint64_t bdesc = make_desc(v_addr + kk * 2048, TILE_BYTES, 1024);   // 64-column chunks a tile apart
+          umma_bf16(tmem_base + O_COL, adesc, bdesc, idesc_pv, (j | (uint32_t)kk) != 0 ? 1u : 0u);
+        }
+        umma_commit(&v_empty[vs]);
+        umma_commit(p_empty);
+        if (++vs == KS) { vs = 0; vph ^= 1; }
+      }
+      if (ok) umma_commit(o_full);
+      if (!ok) {
+        atomicCAS(p.err, 0, TIMEOUT_CODE);
+        *abort_flag = 1;
+      }
+    }
+  } else {
+    // ---------------- softmax and epilogue (warps 2..5): a thread a query row ----------------
+    const uint32_t quad = warp & 3;
+    const uint32_t row = quad * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16);
+    const int32_t qi = i0 + (int32_t)row;
+    const int32_t last_key = p.causal ? qi + p.causal_off : 0x7fffffff;
+    bool ok = true;
+    uint32_t t = 0;
+    float mx = -INFINITY;
+    for (uint32_t j = 0; j < nk && ok; ++j, ++t) {
+      const uint32_t buf = t & 1, sph = (t >> 1) & 1;
+      if (!mbar_wait(&s_full[buf], sph, abort_flag)) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const bool edge = (int32_t)(j * 128 + 127) > last_key;     // only the diagonal tile needs the mask
+#pragma unroll 1
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t v[32];
+        tmem_ld32(lane_addr + buf * S_COLS + cb * 32, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (edge) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if ((int32_t)(j * 128 + cb * 32 + e) <= last_key) mx = fmaxf(mx, __uint_as_float(v[e]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(&s_empty[buf]);
+    }
+    // the maximum of the scaled scores (scale > 0 keeps the order); a row with no key sees 0
+    float m2 = (mx == -INFINITY) ? 0.f : mx * p.scale_log2;
+    if (p.scale_log2 < 0.f) m2 = 0.f;   // refused on the host; kept finite here
+    float sum = 0.f;
+    for (uint32_t j = 0; j < nk && ok; ++j, ++t) {
+      const uint32_t buf = t & 1, sph = (t >> 1) & 1;
+      if (!mbar_wait(&s_full[buf], sph, abort_flag)) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const bool edge = (int32_t)(j * 128 + 127) > last_key;
+      uint32_t pk[64];
+#pragma unroll
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t v[32];
+        tmem_ld32(lane_addr + buf * S_COLS + cb * 32, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float a = ex2(fmaf(__uint_as_float(v[e]), p.scale_log2, -m2));
+          float b = ex2(fmaf(__uint_as_float(v[e + 1]), p.scale_log2, -m2));
+          if (edge) {
+            if ((int32_t)(j * 128 + cb * 32 + e) > last_key) a = 0.f;
+            if ((int32_t)(j * 128 + cb * 32 + e + 1) > last_key) b = 0.f;
+          }
+          sum += a + b;
+          pk[cb * 16 + e / 2] = pack_bf16(a, b);
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(&s_empty[buf]);
+      // P is single-buffered: the product with V of the tile before must have read it
+      if (!mbar_wait(p_empty, (j & 1) ^ 1, abort_flag)) { ok = false; break; }
+      uint8_t* prow = sP + row * 128;
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const uint32_t off = (u >> 3) * TILE_BYTES + (((u & 7) ^ (row & 7)) << 4);
+        *reinterpret_cast<uint4*>(prow + off) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes, read by the MMA
+      mbar_arrive(p_full);
+    }
+    if (ok && !mbar_wait(o_full, 0, abort_flag)) ok = false;
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float inv = 1.0f / ((sum < FLT_MIN) ? FLT_MIN : sum);
+      uint16_t* dst = p.out + it.o_off + (uint64_t)(i0 + (int32_t)row) * p.o_ld;
+#pragma unroll 1
+      for (int cb = 0; cb < D / 32; ++cb) {
+        uint32_t v[32];
+        tmem_ld32(lane_addr + O_COL + cb * 32, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 w;
+          w.x = pack_bf16(__uint_as_float(v[q4 * 8 + 0]) * inv, __uint_as_float(v[q4 * 8 + 1]) * inv);
+          w.y = pack_bf16(__uint_as_float(v[q4 * 8 + 2]) * inv, __uint_as_float(v[q4 * 8 + 3]) * inv);
+          w.z = pack_bf16(__uint_as_float(v[q4 * 8 + 4]) * inv, __uint_as_float(v[q4 * 8 + 5]) * inv);
+          w.w = pack_bf16(__uint_as_float(v[q4 * 8 + 6]) * inv, __uint_as_float(v[q4 * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(dst + cb * 32 + q4 * 8) = w;
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    if (!ok && lane == 0) {
+      atomicCAS(p.err, 0, TIMEOUT_CODE);
+      *abort_flag = 1;
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+template <int D>
+cudaError_t launch_d(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p,
+                     uint64_t n_items, cudaStream_t stream) {
+  constexpr int CH = D / 64, KS = D == 64 ? 3 : 2;
+  constexpr size_t smem = (size_t)(1 + 2 * KS) * CH * TILE_BYTES + P_BYTES + 256 + 1024;
+  static bool set = false;
+  if (!set) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    set = true;
+  }
+  attention_tc_kernel<D><<<dim3(p.q_tiles, (unsigned)n_items, 1), NUM_THREADS, smem, stream>>>(mq, mk, mv, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool attention_tc_supported(uint64_t sq, uint64_t d, uint64_t sk, uint64_t dv, float scale, int causal, const char** why) {
+  if (!tc::encode_fn()) { *why = "no tensor-map encoder in this driver"; return false; }
+  if (!(d == 64 || d == 128) || dv != d) { *why = "head width 64 or 128, the same for keys and values"; return false; }
+  if (sq == 0 || sk == 0 || sq % 128 || sk % 128) { *why = "sequence lengths are whole tiles of 128"; return false; }
+  if (sq > (1u << 30) || sk > (1u << 30)) { *why = "sequence too long"; return false; }
+  if (!(scale > 0.f)) { *why = "scale must be positive"; return false; }
+  if (causal && sk < sq) { *why = "a causal mask with fewer keys than queries"; return false; }
+  return true;
+}
+
+cudaError_t launch_attention_tc(const void* q, uint64_t q_rows, uint64_t q_cols, const void* k, uint64_t k_rows,
+                                uint64_t k_cols, const void* v, uint64_t v_rows, uint64_t v_cols,
+                                const AttnBlockDev* items, uint64_t n_items, uint64_t sq, uint64_t d, uint64_t sk,
+                                float scale, int causal, void* out, uint64_t o_ld, int* err, cudaStream_t stream) {
+  if (n_items == 0) return cudaSuccess;
+  if (n_items > 65535) return cudaErrorNotSupported;
+  CUtensorMap mq, mk, mv;
+  if (!tc::make_map(&mq, q, q_rows, q_cols, q_cols, 128) || !tc::make_map(&mk, k, k_rows, k_cols, k_cols, 128) ||
+      !tc::make_map(&mv, v, v_rows, v_cols, v_cols, 128))
+    return cudaErrorNotSupported;
+  AttnTcParams p;
+  p.items = items;
+  p.q_tiles = (uint32_t)(sq / 128);
+  p.k_tiles = (uint32_t)(sk / 128);
+  p.causal = causal ? 1 : 0;
+  p.causal_off = (int32_t)(sk - sq);
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.out = (uint16_t*)out;
+  p.o_ld = o_ld;
+  p.err = err;
+  return d == 64 ? launch_d<64>(mq, mk, mv, p, n_items, stream) : launch_d<128>(mq, mk, mv, p, n_items, stream);
+}
+
+}  // namespace b200

@@ -463,20 +463,21 @@ softmax_cluster_kernel(const float* __restrict__ x, const uint32_t* __restrict__
   if (csize > 1) cluster.sync();  // no CTA leaves while a peer may still read its exchange slots
 }
 
-// Rows of 4,097..32,768 columns: several independent workers a block, so an SM has several rows in
-// flight and one row's loads overlap another's exponentials and stores.  A worker is T threads
-// (T = columns / 64); each thread keeps half of its share of the row in registers and half in
-// its own shared-memory slots, filled by cp.async and touched by no other thread, so the only
-// synchronisation is the worker's two reductions (named barriers).  One block an SM, persistent.
+// Rows of 4,097..32,768 columns: a persistent block of 512 threads an SM, split into workers of T
+// threads (T = 128, 256 or 512: the smallest with 16 float4 a thread covering the row).  A worker
+// keeps its row in registers; shared memory holds the NEXT row, fetched by cp.async while this one
+// is reduced, exponentiated and stored, so loads never wait for arithmetic.  Each thread reads and
+// refills only its own shared-memory slots: the only synchronisation is the worker's two
+// reductions (named barriers).
 template <int T>
-__global__ void __launch_bounds__(1024, 1)
+__global__ void __launch_bounds__(512, 1)
 softmax_workers_kernel(const float* __restrict__ x, const uint32_t* __restrict__ mask, uint64_t mask_rows,
                        float scale, int log_form, void* __restrict__ out, int out_bf16, uint64_t rows, uint32_t cols) {
-  constexpr int G = 1024 / T, WARPS = T / 32, VR = 8, VS = 8;
-  extern __shared__ float4 ring[];               // [G][VS][T]
+  constexpr int G = 512 / T, WARPS = T / 32, VPT = 16;
+  extern __shared__ float4 ring[];               // [G][VPT][T]
   __shared__ float red[2][G][WARPS];
   const int g = threadIdx.x / T, t = threadIdx.x % T, wl = t >> 5;
-  float4* mine = ring + (size_t)g * VS * T;
+  float4* mine = ring + (size_t)g * VPT * T + t;
   const uint32_t n4 = cols / 4;
   const bool has_scale = scale != 1.0f;
   const uint64_t nworkers = (uint64_t)gridDim.x * G;
@@ -493,26 +494,29 @@ softmax_workers_kernel(const float* __restrict__ x, const uint32_t* __restrict__
     for (int w = 1; w < WARPS; ++w) r = is_max ? fmaxf(r, red[which][g][w]) : r + red[which][g][w];
     return r;  // red[which] is not rewritten before the worker's next barrier on the other slot
   };
-  for (uint64_t row = (uint64_t)blockIdx.x * G + g; row < rows; row += nworkers) {
-    const float4* xr = reinterpret_cast<const float4*>(x + row * cols);
-    const uint4* mr = mask ? reinterpret_cast<const uint4*>(mask + (row % mask_rows) * cols) : nullptr;
-    // the shared-memory half first: asynchronous, lands while the register half is loaded
+  auto prefetch = [&](uint64_t row) {
+    const float4* xr = reinterpret_cast<const float4*>(x + row * cols) + t;
 #pragma unroll
-    for (int u = 0; u < VS; ++u) {
-      const uint32_t i = t + (VR + u) * T;
-      if (i < n4) {
-        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(mine + u * T + t);
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(xr + i) : "memory");
+    for (int u = 0; u < VPT; ++u) {
+      if (t + u * T < n4) {
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(mine + u * T);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(xr + u * T) : "memory");
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
-    float4 v[VR];
+  };
+  uint64_t row = (uint64_t)blockIdx.x * G + g;
+  if (row < rows) prefetch(row);
+  for (; row < rows; row += nworkers) {
+    const uint4* mr = mask ? reinterpret_cast<const uint4*>(mask + (row % mask_rows) * cols) : nullptr;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    float4 v[VPT];
     float m = -INFINITY;
 #pragma unroll
-    for (int u = 0; u < VR; ++u) {
+    for (int u = 0; u < VPT; ++u) {
       const uint32_t i = t + u * T;
       if (i < n4) {
-        float4 q = __ldcs(xr + i);
+        float4 q = mine[u * T];
         if (mr || has_scale) {
           const uint4 k = mr ? __ldg(mr + i) : make_uint4(0, 0, 0, 0);
           q.x = scaled_masked(q.x, k.x, scale, has_scale); q.y = scaled_masked(q.y, k.y, scale, has_scale);
@@ -522,28 +526,15 @@ softmax_workers_kernel(const float* __restrict__ x, const uint32_t* __restrict__
         m = fmaxf(m, fmaxf(fmaxf(q.x, q.y), fmaxf(q.z, q.w)));
       }
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-#pragma unroll
-    for (int u = 0; u < VS; ++u) {
-      const uint32_t i = t + (VR + u) * T;
-      if (i < n4) {
-        float4 q = mine[u * T + t];
-        if (mr || has_scale) {
-          const uint4 k = mr ? __ldg(mr + i) : make_uint4(0, 0, 0, 0);
-          q.x = scaled_masked(q.x, k.x, scale, has_scale); q.y = scaled_masked(q.y, k.y, scale, has_scale);
-          q.z = scaled_masked(q.z, k.z, scale, has_scale); q.w = scaled_masked(q.w, k.w, scale, has_scale);
-          mine[u * T + t] = q;
-        }
-        m = fmaxf(m, fmaxf(fmaxf(q.x, q.y), fmaxf(q.z, q.w)));
-      }
-    }
+    // every slot of this thread has been read (m depends on all of them): refill them
+    asm volatile("" ::"f"(m) : "memory");
+    if (row + nworkers < rows) prefetch(row + nworkers);
     m = worker_reduce(m, true, 0);
     m = (m < -FLT_MAX) ? -FLT_MAX : m;
     float sum = 0.f;
 #pragma unroll
-    for (int u = 0; u < VR; ++u) {
-      const uint32_t i = t + u * T;
-      if (i < n4) {
+    for (int u = 0; u < VPT; ++u) {
+      if (t + u * T < n4) {
         float4 q = v[u];
         if (log_form) {
           q.x -= m; q.y -= m; q.z -= m; q.w -= m;
@@ -555,30 +546,15 @@ softmax_workers_kernel(const float* __restrict__ x, const uint32_t* __restrict__
         v[u] = q;
       }
     }
-#pragma unroll
-    for (int u = 0; u < VS; ++u) {
-      const uint32_t i = t + (VR + u) * T;
-      if (i < n4) {
-        float4 q = mine[u * T + t];
-        if (log_form) {
-          q.x -= m; q.y -= m; q.z -= m; q.w -= m;
-          sum = sum + ((expf(q.x) + expf(q.y)) + (expf(q.z) + expf(q.w)));
-        } else {
-          q.x = expf(q.x - m); q.y = expf(q.y - m); q.z = expf(q.z - m); q.w = expf(q.w - m);
-          sum = sum + ((q.x + q.y) + (q.z + q.w));
-        }
-        mine[u * T + t] = q;
-      }
-    }
     sum = worker_reduce(sum, false, 1);
     void* orow = reinterpret_cast<char*>(out) + row * cols * (out_bf16 ? 2 : 4);
     const float l = log_form ? logf(sum) : 0.f;
     const float inv = 1.0f / ((sum < FLT_MIN) ? FLT_MIN : sum);
 #pragma unroll
-    for (int u = 0; u < VR + VS; ++u) {
+    for (int u = 0; u < VPT; ++u) {
       const uint32_t i = t + u * T;
       if (i < n4) {
-        float4 q = u < VR ? v[u < VR ? u : 0] : mine[(u - VR) * T + t];
+        float4 q = v[u];
         if (log_form) { q.x -= l; q.y -= l; q.z -= l; q.w -= l; }
         else { q.x *= inv; q.y *= inv; q.z *= inv; q.w *= inv; }
         store4(orow, i, q, out_bf16);
@@ -863,13 +839,6 @@ int32_t b200_full_sum_noalloc(const float* device_values, uint64_t n, int32_t me
 
 namespace b200 {
 
-// Development switch: B200TT_SOFTMAX=old keeps the one-block-a-row kernels for wide rows.
-static bool softmax_old_path() {
-  static int v = -1;
-  if (v < 0) { const char* e = getenv("B200TT_SOFTMAX"); v = (e && e[0] == 'o') ? 1 : 0; }
-  return v == 1;
-}
-
 cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t mask_rows, float scale,
                                 int log_form, void* out, int out_bf16, uint64_t rows, uint64_t cols,
                                 cudaStream_t s) {
@@ -881,21 +850,25 @@ cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t m
 #define SM_LAUNCH(T, V)                                                                         \
   softmax_block_kernel<T, V><<<(unsigned)(rows < (148ull * (2048 / T)) ? rows : 148ull * (2048 / T)), \
                                T, 0, s>>>(x, mask, mask_rows, scale, log_form, out, out_bf16, rows, (uint32_t)cols)
-  if (al && cols % 4 == 0 && cols >= 128 && n4 <= 1024) {
+  // Measured on a B200 (2 x rows x cols x 4 bytes over the launch time, 512 MB of scores): the
+  // workers kernel reaches 5.6-6.0 TB/s from 2,048 to 32,768 columns; a block a row stays ahead
+  // only up to 1,024 columns.
+  const uint64_t workers_from = 256;
+  if (al && cols % 4 == 0 && cols >= 128 && n4 <= workers_from) {
     if (n4 <= 32) SM_LAUNCH(32, 1);
     else if (n4 <= 64) SM_LAUNCH(64, 1);
     else if (n4 <= 128) SM_LAUNCH(128, 1);
     else if (n4 <= 256) SM_LAUNCH(128, 2);
     else if (n4 <= 512) SM_LAUNCH(256, 2);
     else if (n4 <= 1024) SM_LAUNCH(256, 4);
-  } else if (al && cols % 4 == 0 && n4 > 1024 && n4 <= 8192 && !softmax_old_path()) {
+  } else if (al && cols % 4 == 0 && n4 > workers_from && n4 <= 8192) {
     // T threads a worker, 16 float4 a thread: the smallest T that covers the row
-    const int threads = n4 <= 2048 ? 128 : (n4 <= 4096 ? 256 : 512);
+    const int threads = n4 <= 512 ? 32 : (n4 <= 1024 ? 64 : (n4 <= 2048 ? 128 : (n4 <= 4096 ? 256 : 512)));
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const size_t smem = 1024 * 8 * sizeof(float4);
-    const uint64_t workers = 1024 / threads;
+    const size_t smem = 512 * 16 * sizeof(float4);
+    const uint64_t workers = 512 / threads;
     const unsigned gridw = (unsigned)((rows + workers - 1) / workers < (uint64_t)sms ? (rows + workers - 1) / workers : (uint64_t)sms);
 #define SW(TT)                                                                                                  \
     do {                                                                                                          \
@@ -905,20 +878,15 @@ cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t m
         if (e != cudaSuccess) return e;                                                                           \
         attr = true;                                                                                              \
       }                                                                                                           \
-      softmax_workers_kernel<TT><<<gridw, 1024, smem, s>>>(x, mask, mask_rows, scale, log_form, out, out_bf16, rows, (uint32_t)cols); \
+      softmax_workers_kernel<TT><<<gridw, 512, smem, s>>>(x, mask, mask_rows, scale, log_form, out, out_bf16, rows, (uint32_t)cols); \
     } while (0)
-    if (threads == 128) SW(128); else if (threads == 256) SW(256); else SW(512);
+    if (threads == 32) SW(32); else if (threads == 64) SW(64); else if (threads == 128) SW(128);
+    else if (threads == 256) SW(256); else SW(512);
 #undef SW
-  } else if (al && cols % 4 == 0 && n4 > 2048 && n4 <= 8192) {
-    // Measured on a B200: for rows this wide one 1024-thread block a row beats splitting the
-    // row over a cluster (the cluster barriers cost more than the lost overlap).
-    if (n4 <= 4096) SM_LAUNCH(1024, 4);
-    else SM_LAUNCH(1024, 8);
   } else if (al && cols % 4 == 0 && n4 <= 4096ull * 8) {
-    // n4 in (1024, 2048]: one 256-thread block a row, four resident per SM.
     // n4 in (8192, 32768]: 2..8 blocks of 512 threads a row, exchanging max and sum through
     // distributed shared memory.
-    const int threads = n4 <= 2048 ? 256 : 512;
+    const int threads = 512;
     unsigned csize = 1;
     while ((n4 + csize - 1) / csize > (uint64_t)threads * 8) csize <<= 1;
     uint64_t clusters = rows < (1ull << 20) ? rows : (1ull << 20);
@@ -932,8 +900,6 @@ cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t m
     attr[0].val.clusterDim.x = csize; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
     const uint32_t cols32 = (uint32_t)cols;
-    if (threads == 256)
-      return cudaLaunchKernelEx(&cfg, softmax_cluster_kernel<256, 8>, x, mask, mask_rows, scale, log_form, out, out_bf16, rows, cols32);
     return cudaLaunchKernelEx(&cfg, softmax_cluster_kernel<512, 8>, x, mask, mask_rows, scale, log_form, out, out_bf16, rows, cols32);
   } else {
     softmax_stream_kernel<<<(unsigned)grid, 256, 0, s>>>(x, mask, mask_rows, scale, log_form, out, out_bf16, rows, cols);

@@ -75,6 +75,22 @@ cudaError_t launch_gather_row_ptrs(const void* const* row_ptrs, uint64_t n_rows,
 // out[dst_row(i), :] = src[src_row(i), :], pairs (dst, src) on the device.
 cudaError_t launch_assign_rows(void* out, const void* value, uint64_t cols, int elem_bytes,
                                const uint64_t* pairs, uint64_t n, cudaStream_t);
+// attention_rows (k_attention.cu): element offsets of a head's blocks in q, k and v
+struct AttnItem { uint64_t q_off, k_off, v_off; };
+void attention_rows_plan(uint64_t n_items, int m, int l, int sms, int* splits, int* lc);
+size_t attention_rows_scratch_floats(uint64_t n_items, int m, int dv, int splits);
+cudaError_t launch_attention_rows(const float* q, uint64_t q_ld, const void* k, uint64_t k_ld, const void* v,
+                                  uint64_t v_ld, int kv_bf16, const uint32_t* mask, const AttnItem* items,
+                                  uint64_t n_items, int m, int d, int l, int dv, float scale, int splits, int lc,
+                                  float* scratch, float* out, int* launches, cudaStream_t stream);
+// fused attention over whole sequences (k_attention_tc.cu): element coordinates of a block's Q, K
+// and V (row, column) and the element offset of its output
+struct AttnBlockDev { int32_t q_r, q_c, k_r, k_c, v_r, v_c; int32_t pad0, pad1; uint64_t o_off; };
+bool attention_tc_supported(uint64_t sq, uint64_t d, uint64_t sk, uint64_t dv, float scale, int causal, const char** why);
+cudaError_t launch_attention_tc(const void* q, uint64_t q_rows, uint64_t q_cols, const void* k, uint64_t k_rows,
+                                uint64_t k_cols, const void* v, uint64_t v_rows, uint64_t v_cols,
+                                const AttnBlockDev* items, uint64_t n_items, uint64_t sq, uint64_t d, uint64_t sk,
+                                float scale, int causal, void* out, uint64_t o_ld, int* err, cudaStream_t stream);
 struct MoveDev { uint64_t from_r, from_c, to_r, to_c, rows, cols; int32_t transposed; int32_t pad; };
 cudaError_t launch_copy_blocks(const void* src, uint64_t src_ld, void* dst, uint64_t dst_ld,
                                int elem_bytes, const MoveDev* moves_dev, uint64_t n_moves,

@@ -52,6 +52,10 @@ class BlockMove(C.Structure):  # tt-kernels/src/tensor.rs:6659
                 ("transposed", C.c_int32), ("_pad", C.c_int32)]
 
 
+class AttentionItem(C.Structure):  # tt-kernels/src/attention.rs:40
+    _fields_ = [("q", C.c_uint64 * 2), ("k", C.c_uint64 * 2), ("v", C.c_uint64 * 2)]
+
+
 class BlockArg(C.Structure):  # burn-tt/src/server.rs:3449
     _fields_ = [("id", C.c_uint64), ("at", C.c_uint64 * 2), ("dims", C.c_uint64 * 2)]
 
@@ -440,6 +444,17 @@ class CudaEngine:
         src = np.ascontiguousarray(sources, dtype=np.uint64).reshape(-1)
         assert src.size == 2 * dims[0] * dims[1]
         return self._call(self._lib.b200_repack, C.c_uint64(a), _ptr(src), (C.c_uint64 * 2)(*dims))
+
+    def attention_rows(self, buffers, items, dims, scale: float) -> Out:
+        """`attention_rows([q, k, v, mask], items, [m, d, l, dv], scale)` (server.rs:257): each item is
+        the (row, col) of a head's query, key and value blocks; the result is the
+        [1, len(items) * m * dv] row of the heads' rows."""
+        n = len(items)
+        arr = (AttentionItem * max(n, 1))()
+        for i, (q, k, v) in enumerate(items):
+            arr[i] = AttentionItem((C.c_uint64 * 2)(*q), (C.c_uint64 * 2)(*k), (C.c_uint64 * 2)(*v))
+        return self._call(self._lib.b200_attention_rows, (C.c_uint64 * 4)(*buffers), arr, C.c_uint64(n),
+                          (C.c_uint64 * 4)(*dims), C.c_float(scale))
 
     # -- traces (server.rs:591-660) ------------------------------------------------------------
     def begin_trace(self):

@@ -9,6 +9,7 @@ use std::os::raw::{c_char, c_void};
 #[repr(C)] #[derive(Clone, Copy, Default)] pub struct b200_config { pub f32_matmul_mode: i32, pub bf16_matmul_mode: i32, pub pool_limit_bytes: u64, pub fail_alloc_at: i32, pub _pad: i32 }
 #[repr(C)] #[derive(Clone, Copy)] pub struct b200_eltwise_op { pub kind: u32, pub scalar: f32, pub scalar2: f32 }
 #[repr(C)] #[derive(Clone, Copy)] pub struct b200_block { pub at: [u64; 2], pub transposed: i32, pub _pad: i32 }
+#[repr(C)] #[derive(Clone, Copy)] pub struct b200_attention_item { pub q: [u64; 2], pub k: [u64; 2], pub v: [u64; 2] }
 #[repr(C)] #[derive(Clone, Copy)] pub struct b200_block_move { pub from: [u64; 2], pub to: [u64; 2], pub extent: [u64; 2], pub transposed: i32, pub _pad: i32 }
 #[repr(C)] #[derive(Clone, Copy)] pub struct b200_block_arg { pub id: u64, pub at: [u64; 2], pub dims: [u64; 2] }
 #[repr(C)] #[derive(Clone, Copy)] pub struct b200_batched_layout { pub lhs_padded: i32, pub stacked: i32 }
@@ -67,6 +68,7 @@ extern "C" {
     pub fn b200_slice_rows(a0: *mut b200_engine, a: u64, first: u64, rows: u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_copy_blocks(a0: *mut b200_engine, a: u64, moves: *const b200_block_move, n: u64, dims: *const u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_repack(a0: *mut b200_engine, a: u64, row_col_pairs: *const u64, dims: *const u64, out: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_attention_rows(a0: *mut b200_engine, buffers: *const u64, items: *const b200_attention_item, n_items: u64, dims: *const u64, scale: f32, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_begin_trace(a0: *mut b200_engine) -> i32;
     pub fn b200_end_trace(a0: *mut b200_engine, trace: *mut u64) -> i32;
     pub fn b200_run_trace(a0: *mut b200_engine, trace: u64) -> i32;

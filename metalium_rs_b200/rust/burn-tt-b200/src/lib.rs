@@ -278,6 +278,12 @@ impl Engine for CudaEngine {
         let d = [dims[0] as u64, dims[1] as u64];
         produce!(self, b200_copy_blocks(a, m.as_ptr(), m.len() as u64, d.as_ptr()))
     }
+    fn attention_rows(&mut self, buffers: [BufferId; 4], items: &[tt_kernels::attention::Item], dims: [usize; 4], scale: f32) -> Made {
+        let it: Vec<_> = items.iter().map(|i| sys::b200_attention_item {
+            q: [i.q[0] as u64, i.q[1] as u64], k: [i.k[0] as u64, i.k[1] as u64], v: [i.v[0] as u64, i.v[1] as u64] }).collect();
+        let d = [dims[0] as u64, dims[1] as u64, dims[2] as u64, dims[3] as u64];
+        produce!(self, b200_attention_rows(buffers.as_ptr(), it.as_ptr(), it.len() as u64, d.as_ptr(), scale))
+    }
     fn repack(&mut self, a: BufferId, sources: &[[usize; 2]], dims: [usize; 2]) -> Made {
         let p: Vec<u64> = sources.iter().flat_map(|s| [s[0] as u64, s[1] as u64]).collect();
         let d = [dims[0] as u64, dims[1] as u64];

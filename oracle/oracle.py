@@ -461,6 +461,24 @@ def softmax_bound(n: int) -> float:
     return 2 * (2 * 1.3e-7 + (n - 1) * u + 2 * u)
 
 
+def attention_rows(q, k, v, mask, items, dims, scale: float) -> np.ndarray:
+    """`attention_rows` as the composition it stands for (crates/tt-kernels/src/attention.rs:1-18,
+    360-366): per head Q K^T in F32, scale then mask fill, the softmax of `softmax_rows`, and P V in
+    F32.  q, k, v are F32 arrays (BF16 keys and values already widened), mask [l] of 0/1, items
+    ((q_row, q_col), (k_row, k_col), (v_row, v_col)); returns the [1, heads * m * dv] row."""
+    m, d, l, dv = dims
+    rows = []
+    mk = np.ascontiguousarray(mask, dtype=np.uint32).reshape(1, l)
+    for (qa, ka, va) in items:
+        qi = np.ascontiguousarray(q[qa[0]:qa[0] + m, qa[1]:qa[1] + d], dtype=np.float32)
+        ki = np.ascontiguousarray(k[ka[0]:ka[0] + l, ka[1]:ka[1] + d], dtype=np.float32)
+        vi = np.ascontiguousarray(v[va[0]:va[0] + l, va[1]:va[1] + dv], dtype=np.float32)
+        s = gemm_f32(qi, ki, b_t=True)
+        p = softmax_rows(s, mk, scale)
+        rows.append(gemm_f32(p, vi))
+    return np.concatenate(rows, 0).reshape(1, -1)
+
+
 def argmax_rows(a: np.ndarray) -> np.ndarray:
     """First maximum, first NaN wins (crates/tt-tests/tests/step211_argmax_row.rs:8-10)."""
     a = np.ascontiguousarray(a, dtype=np.float32)

@@ -37,6 +37,11 @@ cudaError_t launch_gather_row_ptrs(const void* const*, uint64_t, uint64_t, int, 
 cudaError_t launch_assign_rows(void*, const void*, uint64_t, int, const uint64_t*, uint64_t, cudaStream_t) { OK_LAUNCH; }
 cudaError_t launch_copy_blocks(const void*, uint64_t, void*, uint64_t, int, const MoveDev*, uint64_t, uint64_t, uint64_t, cudaStream_t) { OK_LAUNCH; }
 cudaError_t launch_repack(const void*, uint64_t, int, const uint64_t*, uint64_t, void*, cudaStream_t) { OK_LAUNCH; }
+void attention_rows_plan(uint64_t, int, int l, int, int* splits, int* lc) { *splits = l > 256 ? 2 : 1; *lc = l > 256 ? (l / 2 + 31) / 32 * 32 : l; }
+size_t attention_rows_scratch_floats(uint64_t n, int m, int dv, int splits) { return splits > 1 ? (size_t)n * splits * m * (dv + 2) : 0; }
+cudaError_t launch_attention_rows(const float*, uint64_t, const void*, uint64_t, const void*, uint64_t, int, const uint32_t*,
+                                  const AttnItem*, uint64_t, int, int, int, int, float, int splits, int, float*, float*,
+                                  int* launches, cudaStream_t) { *launches = splits > 1 ? 2 : 1; OK_LAUNCH; }
 cudaError_t launch_gemm_simt(const GemmArgs&, cudaStream_t) { OK_LAUNCH; }
 bool gemm_tc_supported(const GemmArgs& g, const char** why) {
   *why = g.in_bf16 ? "the fake runtime was told to refuse" : "operands are not BF16";

@@ -146,6 +146,30 @@ def test_product_path_choice(fake, e):
     strict.close()
 
 
+def test_attention_rows_dims_and_refusals(e):                                      # tt-kernels/src/attention.rs:156-171, 386-415
+    q, k, v = f32(e, 4, 64), f32(e, 512, 64), f32(e, 512, 32)
+    mask = e.upload_bits(np.zeros((1, 512), np.uint32), 1, 512, BOOL)
+    heads = [((0, 0), (0, 0), (0, 0)), ((2, 0), (0, 0), (0, 0))]
+    before = e.device_traffic().launches
+    out, dims = e.attention_rows([q, k, v, mask], heads, [2, 64, 512, 32], 0.125)
+    assert dims == (1, 2 * 2 * 32) and e.dims_of(out) == ((1, 128), F32)
+    assert e.device_traffic().launches - before == 2          # positions split over blocks, then joined
+    short, _ = e.attention_rows([q, k, v, mask], heads, [2, 64, 512, 32][:1] + [64, 512, 32], 0.125)
+    e.free(short)
+    for dims4 in ([33, 64, 512, 32], [2, 48, 512, 32], [2, 64, 500, 32], [2, 64, 512, 16], [0, 64, 512, 32]):
+        with pytest.raises(TtError) as err:
+            e.attention_rows([q, k, v, mask], heads, dims4, 1.0)
+        assert err.value.status == 2
+    for buffers, items in (([q, k, v, q], heads), ([q, k, v, mask], []), ([q, k, v, mask], [((3, 0), (0, 0), (0, 0))]),
+                           ([q, k, v, mask], [((0, 0), (0, 2), (0, 0))])):
+        with pytest.raises(TtError) as err:
+            e.attention_rows(buffers, items, [2, 64, 512, 32], 1.0)
+        assert err.value.status == 2
+    with pytest.raises(TtError) as err:
+        e.attention_rows([q, 424242, v, mask], heads, [2, 64, 512, 32], 1.0)
+    assert err.value.status == 5
+
+
 def test_views_keep_their_parent_alive(e):                                      # server.rs:480-481
     t0 = e.device_traffic().pool_in_use
     a = f32(e, 64, 8)
