@@ -423,9 +423,17 @@ def callers(eng, timed):
     a2 = eng.download_bits(tam).ravel().tolist()
     eng.release_trace(model.trace); eng.free(tlg); eng.free(tam)
     res["smollm2_135m_prefill_8x512"] = {"ms": tms, "tok_per_s": batch * seq / (tms * 1e-3), "launches": int(per),
-                                         "tflops": fl / tms / 1e9, "mode": "traced (CUDA graph replay)",
+                                         "tflops": fl / tms / 1e9, "mode": "traced (CUDA graph replay), fused attention",
                                          "eager_ms": ms, "eager_tok_per_s": batch * seq / (ms * 1e-3),
                                          "argmax_stable": a0 == a1 == a2, "next_tokens": a1}
+    # the reference-shaped composition of attention (batched Q K^T, softmax, batched P V), traced
+    composed = W.LlamaPrefill(eng, cfg, W.llama_weights(cfg), batch, seq, fused_attention=False)
+    clg, cam = composed.capture(ids)
+    cms = timed(composed.replay, reps=10, warm=2)
+    a3 = eng.download_bits(cam).ravel().tolist()
+    eng.release_trace(composed.trace); eng.free(clg); eng.free(cam)
+    res["smollm2_135m_prefill_8x512"].update({"composed_attention_ms": cms, "composed_tok_per_s": batch * seq / (cms * 1e-3),
+                                              "composed_argmax_agrees": a3 == a2})
 
     bh, t, d = 256, 2048, 128
     bf = lambda: ((rng.standard_normal((bh * t, d), dtype=np.float32)).view(np.uint32) >> 16).astype(np.uint16)
@@ -437,6 +445,13 @@ def callers(eng, timed):
     ms = timed(att, reps=3, warm=1)
     res["attention_16x16x2048x128"] = {"ms": ms, "tflops": 2 * 2.0 * bh * t * t * d / ms / 1e9,
                                        "materialised_scores_gb": bh * t * t * 4 / 1e9}
+    blocks = eng.attention_block_array([((i * t, 0), (i * t, 0), (i * t, 0), (i * t, 0)) for i in range(bh)])
+
+    def att_fused():
+        o = W.attention_fused(eng, q, k, v, bh, t, d, blocks)
+        eng.free(o)
+    fms = timed(att_fused, reps=5, warm=2)
+    res["attention_16x16x2048x128"].update({"fused_ms": fms, "fused_tflops": 2 * 2.0 * bh * t * t * d / fms / 1e9})
     for i in (q, k, v, x, y, ids):
         eng.free(i)
     return res

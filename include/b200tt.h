@@ -246,6 +246,22 @@ int32_t b200_attention_rows(b200_engine*, const b200_buffer buffers[4], const b2
                             uint64_t n_items, const uint64_t dims[4], float scale,
                             b200_buffer* out, uint64_t out_dims[2]);
 
+/* --- attention over whole sequences, fused (an extension beyond the `Engine` trait, as
+ * `b200_softmax_rows_as` is): what burn-tt composes in `padded_attention` (ops.rs:4825-4960: a
+ * batched Q K^T, `SCALE_MASK_FILL` with the causal blocks, the row softmax, a batched P V) as one
+ * kernel, the scores never written.  q, k, v are BF16 buffers; block i names the top-left element
+ * of its Q [sq, d], K [sk, d] and V [sk, dv] blocks and of its [sq, dv] block of the result.
+ * dims = [sq, d, sk, dv].  causal: query row r sees keys 0..r + (sk - sq).  The result is a new
+ * BF16 [result_dims] buffer; elements no block covers are zero.  F32 accumulation, the
+ * probabilities rounded to BF16 before the product with V (as `b200_softmax_rows_as` + the BF16
+ * product do).  Refused (UNSUPPORTED) unless d = dv is 64 or 128, sq and sk are multiples of 128,
+ * scale > 0, sk >= sq when causal, and every column offset and buffer width is a multiple of 8. */
+typedef struct b200_attention_block { uint64_t q[2], k[2], v[2], o[2]; } b200_attention_block;
+int32_t b200_attention_blocks(b200_engine*, b200_buffer q, b200_buffer k, b200_buffer v,
+                              const b200_attention_block* items, uint64_t n_items, const uint64_t dims[4],
+                              float scale, int32_t causal, const uint64_t result_dims[2],
+                              b200_buffer* out, uint64_t out_dims[2]);
+
 /* --- traces: server.rs:591 `begin_trace`, :595 `end_trace`, :650 `run_trace`, :660 `release_trace`.
  * Ops issued between begin and end are captured into a CUDA graph instead of running; a replay
  * runs them again on the same buffers.  Inputs are buffers made before the capture (refresh them

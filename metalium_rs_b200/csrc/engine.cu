@@ -1291,6 +1291,62 @@ int32_t b200_attention_rows(b200_engine* e, const b200_buffer buffers[4], const 
   return B200_OK;
 }
 
+int32_t b200_attention_blocks(b200_engine* e, b200_buffer q, b200_buffer k, b200_buffer v, const b200_attention_block* items,
+                              uint64_t n_items, const uint64_t dims[4], float scale, int32_t causal, const uint64_t result_dims[2],
+                              b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *Q = nullptr, *K = nullptr, *V = nullptr;
+  int st = e->need(q, &Q, "attention_blocks");
+  if (!st) st = e->need(k, &K, "attention_blocks");
+  if (!st) st = e->need(v, &V, "attention_blocks");
+  if (st) return st;
+  const uint64_t sq = dims[0], d = dims[1], sk = dims[2], dv = dims[3];
+  if (Q->elem != B200_BF16 || K->elem != B200_BF16 || V->elem != B200_BF16)
+    return e->fail(B200_UNSUPPORTED, "attention_blocks: queries, keys and values are BF16");
+  if (n_items == 0) return e->fail(B200_UNSUPPORTED, "attention_blocks: no blocks");
+  const char* why = "";
+  if (!attention_tc_supported(sq, d, sk, dv, scale, causal, &why))
+    return e->fail(B200_UNSUPPORTED, "attention_blocks: [sq, d, sk, dv] = [%llu, %llu, %llu, %llu]: %s", (unsigned long long)sq,
+                   (unsigned long long)d, (unsigned long long)sk, (unsigned long long)dv, why);
+  const uint64_t o_rows = result_dims[0], o_cols = result_dims[1];
+  const uint64_t lim = 1ull << 31;
+  if (Q->cols % 8 || K->cols % 8 || V->cols % 8 || o_cols % 8 || o_rows == 0 || o_cols == 0 || Q->rows >= lim || K->rows >= lim ||
+      V->rows >= lim || Q->cols >= lim || K->cols >= lim || V->cols >= lim)
+    return e->fail(B200_UNSUPPORTED, "attention_blocks: buffer widths are multiples of 8 columns (and below 2^31)");
+  std::vector<AttnBlockDev> host(n_items);
+  uint64_t area = 0;
+  for (uint64_t i = 0; i < n_items; ++i) {
+    const b200_attention_block& it = items[i];
+    if (it.q[0] + sq > Q->rows || it.q[1] + d > Q->cols || it.k[0] + sk > K->rows || it.k[1] + d > K->cols ||
+        it.v[0] + sk > V->rows || it.v[1] + dv > V->cols || it.o[0] + sq > o_rows || it.o[1] + dv > o_cols)
+      return e->fail(B200_UNSUPPORTED, "attention_blocks: block %llu lies outside a tensor", (unsigned long long)i);
+    if (it.q[1] % 8 || it.k[1] % 8 || it.v[1] % 8 || it.o[1] % 8)
+      return e->fail(B200_UNSUPPORTED, "attention_blocks: block %llu starts at a column that is not a multiple of 8", (unsigned long long)i);
+    host[i] = AttnBlockDev{(int32_t)it.q[0], (int32_t)it.q[1], (int32_t)it.k[0], (int32_t)it.k[1], (int32_t)it.v[0], (int32_t)it.v[1],
+                           0, 0, it.o[0] * o_cols + it.o[1]};
+    area += sq * dv;
+  }
+  const void *qp = Q->ptr, *kp = K->ptr, *vp = V->ptr;
+  const uint64_t qr = Q->rows, qc = Q->cols, kr = K->rows, kc = K->cols, vr = V->rows, vc = V->cols;
+  Buf* O = nullptr;
+  st = e->new_buffer(o_rows, o_cols, B200_BF16, out, &O);
+  if (st) return st;
+  void* op = O->ptr;
+  if (area != o_rows * o_cols) {
+    cudaError_t ce = cudaMemsetAsync(op, 0, o_rows * o_cols * 2, e->stream);
+    if (ce != cudaSuccess) { e->drop(*out); return e->cuda_fail(ce, "attention_blocks"); }
+  }
+  void* dev = nullptr; uint64_t got = 0;
+  st = e->to_device(host.data(), n_items * sizeof(AttnBlockDev), &dev, &got);
+  if (st) { e->drop(*out); return st; }
+  st = e->launched(launch_attention_tc(qp, qr, qc, kp, kr, kc, vp, vr, vc, (const AttnBlockDev*)dev, n_items, sq, d, sk, scale, causal,
+                                       op, o_cols, e->d_err, e->stream), "attention_blocks");
+  e->release(dev, got);
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, o_rows, o_cols);
+  return B200_OK;
+}
+
 int32_t b200_repack(b200_engine* e, b200_buffer a, const uint64_t* pairs, const uint64_t dims[2], b200_buffer* out, uint64_t out_dims[2]) {
   cudaSetDevice(e->device);
   Buf* A = nullptr;

@@ -12,10 +12,12 @@
 //           registers; at the end O / sum is written as BF16.
 // With the final maximum known before the first product with V, O is never rescaled; Q K^T is
 // computed twice, which costs tensor-core time the kernel has to spare (the exponentials bound it).
-// Warp 0 lane 0 issues the TMA loads, warp 1 lane 0 the MMAs, warps 2-5 are the softmax (a thread
-// a query row = a TMEM lane).  S is double-buffered in TMEM so the next tile's product runs under
-// this tile's exponentials.  Every wait is bounded; a wait that runs out sets the engine's error
-// word to TIMEOUT and the CTA leaves in order (copies drained, TMEM freed).
+// Warp 0 lane 0 issues the TMA loads, warp 1 lane 0 the MMAs, warps 2-9 are the softmax: a query
+// row is a TMEM lane, and two threads share it (warps 2-5 take keys 0-63 of a tile, warps 6-9 keys
+// 64-127; they exchange their maxima after pass 1 and their sums at the end through shared memory).
+// S is double-buffered in TMEM so the next tile's product runs under this tile's exponentials.
+// Every wait is bounded; a wait that runs out sets the engine's error word to TIMEOUT and the CTA
+// leaves in order (copies drained, TMEM freed).
 #include <cfloat>
 #include <cstdint>
 #include <cuda_runtime.h>
@@ -29,6 +31,8 @@ using namespace tc;
 
 constexpr uint32_t TILE_BYTES = 128 * 64 * 2;   // a [128 rows, 64 columns] BF16 box
 constexpr uint32_t P_BYTES = 2 * TILE_BYTES;    // [128 rows, 128 keys]
+constexpr int ATTN_THREADS = 320;               // 10 warps: TMA, MMA, 8 softmax
+constexpr int SOFTMAX_THREADS = 256;
 
 struct AttnTcParams {
   const AttnBlockDev* items;
@@ -45,12 +49,15 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// a in the low half, b in the high half, round to nearest even
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-  return (uint32_t)f32_to_bf16_bits(__float_as_uint(a)) | ((uint32_t)f32_to_bf16_bits(__float_as_uint(b)) << 16);
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(b), "f"(a));
+  return d;
 }
 
 template <int D>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(ATTN_THREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const AttnTcParams p) {
   constexpr int CH = D / 64;                       // 64-column chunks of a row of Q, K or V
@@ -75,13 +82,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   uint64_t* o_full = p_empty + 1;
   uint32_t* tmem_slot = (uint32_t*)(o_full + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  float* xmax = (float*)(sP + P_BYTES + 256);   // [2][128]: the two halves' row maxima
+  float* xsum = xmax + 256;                     // [2][128]: and row sums
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < KS; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 128); }
-    mbar_init(p_full, 128);
+    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], SOFTMAX_THREADS); }
+    mbar_init(p_full, SOFTMAX_THREADS);
     mbar_init(p_empty, 1);
     mbar_init(o_full, 1);
     *abort_flag = 0;
@@ -204,8 +213,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
     }
   } else {
-    // ---------------- softmax and epilogue (warps 2..5): a thread a query row ----------------
-    const uint32_t quad = warp & 3;
+    // ---------------- softmax and epilogue (warps 2..9): two threads a query row ----------------
+    const uint32_t quad = warp & 3;                 // the TMEM lanes this warp may read
+    const uint32_t half = (uint32_t)(warp - 2) >> 2;  // which 64 keys of a tile, which half of O's columns
     const uint32_t row = quad * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16);
     const int32_t qi = i0 + (int32_t)row;
@@ -217,73 +227,77 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const uint32_t buf = t & 1, sph = (t >> 1) & 1;
       if (!mbar_wait(&s_full[buf], sph, abort_flag)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const bool edge = (int32_t)(j * 128 + 127) > last_key;     // only the diagonal tile needs the mask
-#pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
-        uint32_t v[32];
-        tmem_ld32(lane_addr + buf * S_COLS + cb * 32, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (edge) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if ((int32_t)(j * 128 + cb * 32 + e) <= last_key) mx = fmaxf(mx, __uint_as_float(v[e]));
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
-        }
-      }
+      const int32_t key0 = (int32_t)(j * 128 + half * 64);
+      uint32_t v[64];
+      tmem_ld32(lane_addr + buf * S_COLS + half * 64, v);
+      tmem_ld32(lane_addr + buf * S_COLS + half * 64 + 32, v + 32);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(&s_empty[buf]);
+      if (key0 + 63 > last_key) {                    // only the diagonal tile needs the mask
+#pragma unroll
+        for (int e = 0; e < 64; ++e)
+          if (key0 + e <= last_key) mx = fmaxf(mx, __uint_as_float(v[e]));
+      } else {
+#pragma unroll
+        for (int e = 0; e < 64; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+      }
     }
+    xmax[half * 128 + row] = mx;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    mx = fmaxf(xmax[row], xmax[128 + row]);
     // the maximum of the scaled scores (scale > 0 keeps the order); a row with no key sees 0
-    float m2 = (mx == -INFINITY) ? 0.f : mx * p.scale_log2;
-    if (p.scale_log2 < 0.f) m2 = 0.f;   // refused on the host; kept finite here
+    const float m2 = (mx == -INFINITY) ? 0.f : mx * p.scale_log2;
     float sum = 0.f;
     for (uint32_t j = 0; j < nk && ok; ++j, ++t) {
       const uint32_t buf = t & 1, sph = (t >> 1) & 1;
       if (!mbar_wait(&s_full[buf], sph, abort_flag)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const bool edge = (int32_t)(j * 128 + 127) > last_key;
-      uint32_t pk[64];
-#pragma unroll
-      for (int cb = 0; cb < 4; ++cb) {
-        uint32_t v[32];
-        tmem_ld32(lane_addr + buf * S_COLS + cb * 32, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float a = ex2(fmaf(__uint_as_float(v[e]), p.scale_log2, -m2));
-          float b = ex2(fmaf(__uint_as_float(v[e + 1]), p.scale_log2, -m2));
-          if (edge) {
-            if ((int32_t)(j * 128 + cb * 32 + e) > last_key) a = 0.f;
-            if ((int32_t)(j * 128 + cb * 32 + e + 1) > last_key) b = 0.f;
-          }
-          sum += a + b;
-          pk[cb * 16 + e / 2] = pack_bf16(a, b);
-        }
-      }
+      const int32_t key0 = (int32_t)(j * 128 + half * 64);
+      uint32_t v[64];
+      tmem_ld32(lane_addr + buf * S_COLS + half * 64, v);
+      tmem_ld32(lane_addr + buf * S_COLS + half * 64 + 32, v + 32);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(&s_empty[buf]);
+      uint32_t pk[32];
+      const bool edge = key0 + 63 > last_key;
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int e = 0; e < 64; e += 2) {
+        float a = ex2(fmaf(__uint_as_float(v[e]), p.scale_log2, -m2));
+        float b = ex2(fmaf(__uint_as_float(v[e + 1]), p.scale_log2, -m2));
+        if (edge) {
+          if (key0 + e > last_key) a = 0.f;
+          if (key0 + e + 1 > last_key) b = 0.f;
+        }
+        s0 += a;
+        s1 += b;
+        pk[e / 2] = pack_bf16(a, b);
+      }
+      sum += s0 + s1;
       // P is single-buffered: the product with V of the tile before must have read it
       if (!mbar_wait(p_empty, (j & 1) ^ 1, abort_flag)) { ok = false; break; }
-      uint8_t* prow = sP + row * 128;
+      uint8_t* prow = sP + half * TILE_BYTES + row * 128;
 #pragma unroll
-      for (int u = 0; u < 16; ++u) {
-        const uint32_t off = (u >> 3) * TILE_BYTES + (((u & 7) ^ (row & 7)) << 4);
-        *reinterpret_cast<uint4*>(prow + off) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
-      }
+      for (int u = 0; u < 8; ++u)
+        *reinterpret_cast<uint4*>(prow + ((u ^ (row & 7)) << 4)) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes, read by the MMA
       mbar_arrive(p_full);
     }
+    xsum[half * 128 + row] = sum;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    sum = xsum[row] + xsum[128 + row];
     if (ok && !mbar_wait(o_full, 0, abort_flag)) ok = false;
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = 1.0f / ((sum < FLT_MIN) ? FLT_MIN : sum);
-      uint16_t* dst = p.out + it.o_off + (uint64_t)(i0 + (int32_t)row) * p.o_ld;
-#pragma unroll 1
-      for (int cb = 0; cb < D / 32; ++cb) {
+      constexpr int OC = D / 2;                      // this thread's columns of O
+      uint16_t* dst = p.out + it.o_off + (uint64_t)(i0 + (int32_t)row) * p.o_ld + half * OC;
+#pragma unroll
+      for (int cb = 0; cb < OC / 32; ++cb) {
         uint32_t v[32];
-        tmem_ld32(lane_addr + O_COL + cb * 32, v);
+        tmem_ld32(lane_addr + O_COL + half * OC + cb * 32, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
@@ -315,14 +329,14 @@ template <int D>
 cudaError_t launch_d(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p,
                      uint64_t n_items, cudaStream_t stream) {
   constexpr int CH = D / 64, KS = D == 64 ? 3 : 2;
-  constexpr size_t smem = (size_t)(1 + 2 * KS) * CH * TILE_BYTES + P_BYTES + 256 + 1024;
+  constexpr size_t smem = (size_t)(1 + 2 * KS) * CH * TILE_BYTES + P_BYTES + 256 + 2048 + 1024;
   static bool set = false;
   if (!set) {
     cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     set = true;
   }
-  attention_tc_kernel<D><<<dim3(p.q_tiles, (unsigned)n_items, 1), NUM_THREADS, smem, stream>>>(mq, mk, mv, p);
+  attention_tc_kernel<D><<<dim3(p.q_tiles, (unsigned)n_items, 1), ATTN_THREADS, smem, stream>>>(mq, mk, mv, p);
   return cudaGetLastError();
 }
 

@@ -56,6 +56,10 @@ class AttentionItem(C.Structure):  # tt-kernels/src/attention.rs:40
     _fields_ = [("q", C.c_uint64 * 2), ("k", C.c_uint64 * 2), ("v", C.c_uint64 * 2)]
 
 
+class AttentionBlock(C.Structure):  # b200_attention_block
+    _fields_ = [("q", C.c_uint64 * 2), ("k", C.c_uint64 * 2), ("v", C.c_uint64 * 2), ("o", C.c_uint64 * 2)]
+
+
 class BlockArg(C.Structure):  # burn-tt/src/server.rs:3449
     _fields_ = [("id", C.c_uint64), ("at", C.c_uint64 * 2), ("dims", C.c_uint64 * 2)]
 
@@ -455,6 +459,22 @@ class CudaEngine:
             arr[i] = AttentionItem((C.c_uint64 * 2)(*q), (C.c_uint64 * 2)(*k), (C.c_uint64 * 2)(*v))
         return self._call(self._lib.b200_attention_rows, (C.c_uint64 * 4)(*buffers), arr, C.c_uint64(n),
                           (C.c_uint64 * 4)(*dims), C.c_float(scale))
+
+    @staticmethod
+    def attention_block_array(items):
+        """The block list marshalled once, for a caller that issues the same list every step."""
+        arr = (AttentionBlock * max(len(items), 1))()
+        for i, (a, b, c, o) in enumerate(items):
+            arr[i] = AttentionBlock((C.c_uint64 * 2)(*a), (C.c_uint64 * 2)(*b), (C.c_uint64 * 2)(*c), (C.c_uint64 * 2)(*o))
+        return arr
+
+    def attention_blocks(self, q: int, k: int, v: int, items, dims, scale: float, causal: bool, result_dims) -> Out:
+        """Fused attention over whole sequences (what ops.rs:4825 `padded_attention` composes): items are
+        ((q_row, q_col), (k_row, k_col), (v_row, v_col), (o_row, o_col)); dims [sq, d, sk, dv]; BF16 in and out."""
+        arr = items if isinstance(items, C.Array) else self.attention_block_array(items)
+        n = len(items)
+        return self._call(self._lib.b200_attention_blocks, C.c_uint64(q), C.c_uint64(k), C.c_uint64(v), arr, C.c_uint64(n),
+                          (C.c_uint64 * 4)(*dims), C.c_float(scale), C.c_int32(1 if causal else 0), (C.c_uint64 * 2)(*result_dims))
 
     # -- traces (server.rs:591-660) ------------------------------------------------------------
     def begin_trace(self):

@@ -158,8 +158,14 @@ class LlamaPrefill:
     """Prefill of `batch` independent causal sequences of `seq` tokens.  Weights are stored BF16;
     the residual stream is F32; projections read BF16 activations and accumulate in F32."""
 
-    def __init__(self, eng, cfg: LlamaConfig, weights: Dict[str, np.ndarray], batch: int, seq: int):
+    def __init__(self, eng, cfg: LlamaConfig, weights: Dict[str, np.ndarray], batch: int, seq: int, fused_attention=None):
+        """fused_attention: None = the fused kernel where it takes the shape (whole 128-row tiles, heads
+        of 64 or 128), True = require it, False = the composition (batched Q K^T, softmax, batched P V)."""
         self.eng, self.cfg, self.batch, self.seq = eng, cfg, batch, seq
+        takes = seq % 128 == 0 and cfg.head_dim in (64, 128)
+        if fused_attention and not takes:
+            raise ValueError("the fused attention kernel does not take this shape")
+        self.fused = takes if fused_attention is None else bool(fused_attention)
         up = lambda a: eng.upload_bf16(_bf16(a), *a.shape)
         self.w = {}
         for k, v in weights.items():
@@ -174,14 +180,17 @@ class LlamaPrefill:
         t = seq
         hd = c.head_dim
         # attention block lists (crates/burn-tt/src/ops.rs:3008-3081): item i = (b, h)
-        self.qk_items, self.pv_items, self.merge = [], [], []
+        self.qk_items, self.pv_items, self.merge, fused_items = [], [], [], []
         for b in range(batch):
             for h in range(c.heads):
                 i = b * c.heads + h
                 kvh = h // group
+                fused_items.append(((b * t, h * hd), (b * t, kvh * hd), (b * t, self.q_cols + self.kv_cols + kvh * hd),
+                                    (b * t, h * hd)))
                 self.qk_items.append((((b * t, h * hd), False), ((b * t, kvh * hd), True)))
                 self.pv_items.append((((i * t, 0), False), ((b * t, self.q_cols + self.kv_cols + kvh * hd), False)))
                 self.merge.append(((i * t, 0), (b * t, h * hd), (t, hd), False))
+        self.fused_items = eng.attention_block_array(fused_items)
         self.last_rows = [(0, b * t + t - 1) for b in range(batch)]
 
     def forward(self, ids_buf: int, all_positions: bool = False):
@@ -202,14 +211,19 @@ class LlamaPrefill:
                                   (self.sin, (0, 0), (t, hd)), hd, True)      # rope.rs:129
             kr, _ = e.rope_blocks((qkv, (0, self.q_cols), (n, self.kv_cols)), (self.cos, (0, 0), (t, hd)),
                                   (self.sin, (0, 0), (t, hd)), hd, True)
-            s, _ = e.matmul_dram_batched(qr, kr, self.qk_items, (t, hd, t))  # Q K^T, F32 scores
-            e.free(qr); e.free(kr)
-            pb, _ = e.softmax_rows_as(s, self.mask, 1.0 / float(np.sqrt(hd)), True)   # scale, causal mask, softmax
-            e.free(s)
-            o, _ = e.matmul_dram_batched(pb, qkv, self.pv_items, (t, t, hd), bf16=True)   # P V
-            e.free(pb); e.free(qkv)
-            om, _ = e.copy_blocks(o, self.merge, (n, self.q_cols))           # merge heads
-            e.free(o)
+            if self.fused:   # scores, mask, softmax, P V and the merge of heads as one kernel
+                om, _ = e.attention_blocks(qr, kr, qkv, self.fused_items, (t, hd, t, hd), 1.0 / float(np.sqrt(hd)), True,
+                                           (n, self.q_cols))
+                e.free(qr); e.free(kr); e.free(qkv)
+            else:
+                s, _ = e.matmul_dram_batched(qr, kr, self.qk_items, (t, hd, t))  # Q K^T, F32 scores
+                e.free(qr); e.free(kr)
+                pb, _ = e.softmax_rows_as(s, self.mask, 1.0 / float(np.sqrt(hd)), True)   # scale, causal mask, softmax
+                e.free(s)
+                o, _ = e.matmul_dram_batched(pb, qkv, self.pv_items, (t, t, hd), bf16=True)   # P V
+                e.free(pb); e.free(qkv)
+                om, _ = e.copy_blocks(o, self.merge, (n, self.q_cols))           # merge heads
+                e.free(o)
             att, _ = e.matmul_dram(om, False, self.w[f"l{l}.o"], False)      # o_proj, F32 out
             e.free(om)
             x2 = el(K.ADD, x, att)                                           # residual (llama.rs:288)
@@ -271,3 +285,10 @@ def attention_products(eng, q_buf: int, k_buf: int, v_buf: int, batch_heads: int
     o, _ = eng.matmul_dram_batched(pb, v_buf, pv, (t, t, d), bf16=True)
     eng.free(pb)
     return o
+
+
+def attention_fused(eng, q_buf: int, k_buf: int, v_buf: int, batch_heads: int, t: int, d: int, items=None):
+    """The same attention as `attention_products` as one kernel: the scores stay on chip."""
+    if items is None:
+        items = eng.attention_block_array([((i * t, 0), (i * t, 0), (i * t, 0), (i * t, 0)) for i in range(batch_heads)])
+    return eng.attention_blocks(q_buf, k_buf, v_buf, items, (t, d, t, d), 1.0 / float(np.sqrt(d)), False, (batch_heads * t, d))[0]

@@ -42,6 +42,13 @@ size_t attention_rows_scratch_floats(uint64_t n, int m, int dv, int splits) { re
 cudaError_t launch_attention_rows(const float*, uint64_t, const void*, uint64_t, const void*, uint64_t, int, const uint32_t*,
                                   const AttnItem*, uint64_t, int, int, int, int, float, int splits, int, float*, float*,
                                   int* launches, cudaStream_t) { *launches = splits > 1 ? 2 : 1; OK_LAUNCH; }
+bool attention_tc_supported(uint64_t sq, uint64_t d, uint64_t sk, uint64_t dv, float scale, int causal, const char** why) {
+  *why = "the fake runtime follows the kernel's rules";
+  return (d == 64 || d == 128) && dv == d && sq && sk && sq % 128 == 0 && sk % 128 == 0 && scale > 0.f && (!causal || sk >= sq);
+}
+cudaError_t launch_attention_tc(const void*, uint64_t, uint64_t, const void*, uint64_t, uint64_t, const void*, uint64_t, uint64_t,
+                                const AttnBlockDev*, uint64_t, uint64_t, uint64_t, uint64_t, float, int, void*, uint64_t, int*,
+                                cudaStream_t) { OK_LAUNCH; }
 cudaError_t launch_gemm_simt(const GemmArgs&, cudaStream_t) { OK_LAUNCH; }
 bool gemm_tc_supported(const GemmArgs& g, const char** why) {
   *why = g.in_bf16 ? "the fake runtime was told to refuse" : "operands are not BF16";

@@ -1,0 +1,108 @@
+"""Fused attention over whole sequences (`b200_attention_blocks`) against an F64 restatement of the
+composition burn-tt runs (crates/burn-tt/src/ops.rs:4825-4960: batched Q K^T, scale and causal mask
+fill, row softmax, batched P V).  Shapes: the SmolLM2-shaped prefill's heads (grouped-query, Q, K and V
+side by side in one projection buffer) and the [2048, 128] heads of the attention-shaped workload.
+Tolerance: BF16 steps -- the probabilities and the result are each rounded once to 8 bits -- so
+|got - want| <= 2^-7 * sum_j p_j |v_j| + 2^-9 |want| + 1e-6."""
+import numpy as np
+import pytest
+
+from metalium_rs_b200 import UNSUPPORTED, TtError
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _want(q, k, v, scale, causal):
+    sq, sk = q.shape[0], k.shape[0]
+    s = q.astype(np.float64) @ k.astype(np.float64).T * scale
+    if causal:
+        i, j = np.arange(sq)[:, None], np.arange(sk)[None, :]
+        s = np.where(j <= i + (sk - sq), s, -np.inf)
+    p = np.exp(s - s.max(1, keepdims=True))
+    p /= p.sum(1, keepdims=True)
+    return p @ v.astype(np.float64), p @ np.abs(v).astype(np.float64)
+
+
+def _check(got, want, bound_s):
+    err = np.abs(got.astype(np.float64) - want)
+    lim = 2.0 ** -7 * bound_s + 2.0 ** -9 * np.abs(want) + 1e-6
+    assert np.all(err <= lim), (float(err.max()), float((err / lim).max()))
+
+
+@pytest.mark.parametrize("batch,heads,kv_heads,s,d,causal", [
+    (2, 9, 3, 512, 64, True),      # the prefill's attention: 9 query heads on 3 key/value heads
+    (1, 2, 2, 256, 128, False),
+    (1, 4, 1, 384, 128, True),
+    (3, 1, 1, 128, 64, False),     # one tile
+])
+def test_heads_side_by_side_in_one_projection_buffer(eng, batch, heads, kv_heads, s, d, causal):
+    width = (heads + 2 * kv_heads) * d
+    x = orc.to_bf16(orc.normal(0xF1A, 1, (batch * s, width), 1.5))
+    xf = orc.from_bf16(x)
+    ix = eng.upload_bf16(x, batch * s, width)
+    rep = heads // kv_heads
+    items = []
+    for b in range(batch):
+        for h in range(heads):
+            kvh = h // rep
+            items.append(((b * s, h * d), (b * s, (heads + kvh) * d), (b * s, (heads + kv_heads + kvh) * d), (b * s, h * d)))
+    scale = 1.0 / np.sqrt(d)
+    out, dims = eng.attention_blocks(ix, ix, ix, items, [s, d, s, d], scale, causal, [batch * s, heads * d])
+    assert dims == (batch * s, heads * d)
+    got = orc.from_bf16(eng.download_bf16(out))
+    for (qa, ka, va, oa) in items:
+        want, bound = _want(xf[qa[0]:qa[0] + s, qa[1]:qa[1] + d], xf[ka[0]:ka[0] + s, ka[1]:ka[1] + d],
+                            xf[va[0]:va[0] + s, va[1]:va[1] + d], scale, causal)
+        _check(got[oa[0]:oa[0] + s, oa[1]:oa[1] + d], want, bound)
+    eng.free(ix); eng.free(out)
+
+
+def test_more_keys_than_queries_and_future_keys_are_not_seen(eng):
+    sq, sk, d = 128, 384, 64
+    q = orc.to_bf16(orc.normal(0xF1B, 1, (sq, d)))
+    k = orc.to_bf16(orc.normal(0xF1B, 2, (sk, d)))
+    v = orc.to_bf16(orc.normal(0xF1B, 3, (sk, d)))
+    qf, kf, vf = orc.from_bf16(q), orc.from_bf16(k), orc.from_bf16(v)
+    iq, ik, iv = eng.upload_bf16(q, sq, d), eng.upload_bf16(k, sk, d), eng.upload_bf16(v, sk, d)
+    item = [((0, 0), (0, 0), (0, 0), (0, 0))]
+    out, _ = eng.attention_blocks(iq, ik, iv, item, [sq, d, sk, d], 0.2, True, [sq, d])
+    want, bound = _want(qf, kf, vf, 0.2, True)
+    _check(orc.from_bf16(eng.download_bf16(out)), want, bound)
+    eng.free(out)
+    # the last key is seen by the last query alone: make it dominate and look at who moved
+    k2 = kf.copy(); k2[-1] = 40.0 * np.sign(qf[-1])
+    v2 = vf.copy(); v2[-1] = 100.0
+    ik2, iv2 = eng.upload_bf16(orc.to_bf16(k2), sk, d), eng.upload_bf16(orc.to_bf16(v2), sk, d)
+    out2, _ = eng.attention_blocks(iq, ik2, iv2, item, [sq, d, sk, d], 0.2, True, [sq, d])
+    got2 = orc.from_bf16(eng.download_bf16(out2))
+    want2, bound2 = _want(qf, orc.from_bf16(orc.to_bf16(k2)), orc.from_bf16(orc.to_bf16(v2)), 0.2, True)
+    _check(got2, want2, bound2)
+    assert np.all(np.abs(got2[:-1]) < 10.0) and np.all(got2[-1] > 90.0)
+    for i in (iq, ik, iv, ik2, iv2, out2):
+        eng.free(i)
+
+
+def test_uncovered_result_elements_are_zero(eng):
+    s, d = 128, 64
+    x = orc.to_bf16(orc.normal(0xF1C, 1, (s, 3 * d)))
+    ix = eng.upload_bf16(x, s, 3 * d)
+    out, dims = eng.attention_blocks(ix, ix, ix, [((0, 0), (0, d), (0, 2 * d), (128, 64))], [s, d, s, d], 0.125, False, [384, 192])
+    got = eng.download_bf16(out)
+    assert dims == (384, 192)
+    covered = np.zeros((384, 192), bool); covered[128:256, 64:128] = True
+    assert np.all(got[~covered] == 0) and np.any(got[covered] != 0)
+    eng.free(ix); eng.free(out)
+
+
+@pytest.mark.parametrize("dims,scale,causal", [
+    ([128, 32, 128, 32], 1.0, False), ([128, 64, 128, 128], 1.0, False), ([100, 64, 128, 64], 1.0, False),
+    ([128, 64, 200, 64], 1.0, False), ([256, 64, 128, 64], 1.0, True), ([128, 64, 128, 64], 0.0, False),
+])
+def test_shapes_outside_the_kernel_are_refused(eng, dims, scale, causal):
+    sq, d, sk, dv = dims
+    iq = eng.upload_bf16(np.zeros((256, 128), np.uint16), 256, 128)
+    with pytest.raises(TtError) as err:
+        eng.attention_blocks(iq, iq, iq, [((0, 0), (0, 0), (0, 0), (0, 0))], dims, scale, causal, [256, 128])
+    assert err.value.status == UNSUPPORTED
+    eng.free(iq)

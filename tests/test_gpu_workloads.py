@@ -69,14 +69,16 @@ def small_llama():
     return W.LlamaConfig(layers=3, hidden=576, heads=9, kv_heads=3, head_dim=64, ff=1536, vocab=2048)
 
 
-def test_llama_prefill_logits_and_argmax(eng):
+@pytest.mark.parametrize("fused", [False, True])   # the composed attention (ops.rs:4825) and the one-kernel form
+def test_llama_prefill_logits_and_argmax(eng, fused):
     # the SmolLM2-135M layer shape, fewer layers and a smaller vocabulary so the oracle runs in seconds
     cfg = small_llama()
     batch, seq = 2, 128
     w = W.llama_weights(cfg, seed=7)
     wb = {k: orc.from_bf16(orc.to_bf16(v)) for k, v in w.items()}   # the oracle sees the BF16 weights
     ids = orc.integers(0xC0F4, 9, (1, batch * seq), cfg.vocab)
-    model = W.LlamaPrefill(eng, cfg, w, batch, seq)
+    model = W.LlamaPrefill(eng, cfg, w, batch, seq, fused_attention=fused)
+    assert model.fused == fused
     ii = eng.upload_bits(ids.view(np.uint32), 1, batch * seq, I32)
     logits, am = model.forward(ii)
     got = eng.download(logits)
@@ -117,7 +119,14 @@ def test_attention_products_on_rank4_views(eng):
         want = M.attention_item(orc.from_bf16(q[r]), orc.from_bf16(k[r]), orc.from_bf16(v[r]))
         # P is rounded to BF16 before P V and O is BF16: 1e-2 relative to the row's scale
         assert np.max(np.abs(got[r] - want)) <= 1e-2 * np.max(np.abs(want)), i
-    for x in (iq, ik, iv, o):
+    # the one-kernel form of the same attention
+    of = W.attention_fused(eng, iq, ik, iv, bh, t, d)
+    gotf = orc.from_bf16(eng.download_bf16(of)).astype(np.float64)
+    for i in range(bh):
+        r = slice(i * t, (i + 1) * t)
+        want = M.attention_item(orc.from_bf16(q[r]), orc.from_bf16(k[r]), orc.from_bf16(v[r]))
+        assert np.max(np.abs(gotf[r] - want)) <= 1e-2 * np.max(np.abs(want)), i
+    for x in (iq, ik, iv, o, of):
         eng.free(x)
 
 
