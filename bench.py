@@ -460,7 +460,9 @@ def callers(eng, timed):
 def run_profile(args):
     """`--profile NAME`: a short fixed sequence for ncu captures (no JSON line, nothing timed).
     membound: EXP, MUL by a row, full sum, per-row sum on [8192,8192] F32, three rounds.
-    softmax: three row softmaxes of [1024, 32768].  prefill: two SmolLM2-135M-shape forward passes."""
+    softmax: three row softmaxes of [1024, 32768].  prefill: two SmolLM2-135M-shape forward passes.
+    attention: three fused attentions of 64 blocks [1024, 128] (no mask).  decode: three `attention_rows`
+    of 512 heads on 128 key/value heads of [4096, 128] BF16."""
     from metalium_rs_b200 import COLS, I32, SUM, CudaEngine, EltwiseOp, build, kinds, workloads as W
     build.build()
     rng = np.random.default_rng(3)
@@ -483,6 +485,22 @@ def run_profile(args):
             ids = eng.upload_bits(rng.integers(0, cfg.vocab, (1, 4096)).astype(np.int32).view(np.uint32), 1, 4096, I32)
             for _ in range(2):
                 lg, am = m.forward(ids); eng.free(lg); eng.free(am)
+        elif args.profile == "attention":
+            bh, t, d = 64, 1024, 128
+            bits = lambda: (rng.standard_normal((bh * t, d), dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)
+            q, k, v = (eng.upload_bf16(bits(), bh * t, d) for _ in range(3))
+            for _ in range(3):
+                o = W.attention_fused(eng, q, k, v, bh, t, d); eng.free(o)
+        elif args.profile == "decode":
+            from metalium_rs_b200 import BOOL
+            heads, kvh, l, d = 512, 128, 4096, 128
+            q = eng.upload(rng.standard_normal((heads, d), dtype=np.float32), heads, d)
+            kb = (rng.standard_normal((kvh * l, d), dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)
+            k, v = eng.upload_bf16(kb, kvh * l, d), eng.upload_bf16(kb, kvh * l, d)
+            mask = eng.upload_bits(np.zeros(l, np.uint32), 1, l, BOOL)
+            items = eng.attention_item_array([((h, 0), ((h // 4) * l, 0), ((h // 4) * l, 0)) for h in range(heads)])
+            for _ in range(3):
+                o, _ = eng.attention_rows([q, k, v, mask], items, [1, d, l, d], 0.088); eng.free(o)
         else:
             raise SystemExit(f"unknown profile {args.profile!r}")
         eng.sync()
@@ -503,7 +521,7 @@ def main():
     ap.add_argument("--extras", action="store_true", help="also time the rest of the sweep and the memory-bound suite")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
-    ap.add_argument("--profile", default="", help="run a short fixed sequence for an ncu capture: membound | softmax | prefill")
+    ap.add_argument("--profile", default="", help="run a short fixed sequence for an ncu capture: membound | softmax | prefill | attention | decode")
     ap.add_argument("--size", type=int, default=0, help="override the N=1 problem size (profiling on a small case)")
     args = ap.parse_args()
     if args.impl == "reference":

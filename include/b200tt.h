@@ -239,8 +239,9 @@ int32_t b200_repack(b200_engine*, b200_buffer a, const uint64_t* row_col_pairs, 
  * heads' rows stacked in row-major order.  out_i = softmax(scale * q_i K_i^T, masked) V_i with the
  * composition's steps (product, scale then mask fill, clamped maximum, exp, clamped sum, division,
  * product).  Refused (UNSUPPORTED) unless 1 <= m <= 32 and d, l, dv are positive multiples of 32
- * (attention.rs:156-171), the key and value blocks start at a column that is a multiple of 4 in
- * buffers whose width is one, and every block lies inside its buffer. */
+ * (attention.rs:156-171), the key and value blocks start at a column that is a multiple of 4 (F32)
+ * or 8 (BF16) in buffers whose width is one, and every block lies inside its buffer.  Heads that
+ * name the same key and value blocks (grouped-query attention) read them once. */
 typedef struct b200_attention_item { uint64_t q[2], k[2], v[2]; } b200_attention_item;
 int32_t b200_attention_rows(b200_engine*, const b200_buffer buffers[4], const b200_attention_item* items,
                             uint64_t n_items, const uint64_t dims[4], float scale,

@@ -1251,38 +1251,72 @@ int32_t b200_attention_rows(b200_engine* e, const b200_buffer buffers[4], const 
   if (m < 1 || m > 32 || d == 0 || l == 0 || dv == 0 || d % 32 || l % 32 || dv % 32 || l > (1ull << 30) || d > 8192 || dv > 8192)
     return e->fail(B200_UNSUPPORTED, "attention_rows: [m, d, l, dv] = [%llu, %llu, %llu, %llu] (1..32 rows, whole tiles along d, l and dv)",
                    (unsigned long long)m, (unsigned long long)d, (unsigned long long)l, (unsigned long long)dv);
-  if (K->cols % 4 || V->cols % 4) return e->fail(B200_UNSUPPORTED, "attention_rows: key and value buffers are a multiple of 4 columns wide");
-  std::vector<AttnItem> host(n_items);
+  const int kv_bf16 = K->elem == B200_BF16;
+  const uint64_t al = kv_bf16 ? 8 : 4;   // 16-byte pieces of a key or value row
+  if (K->cols % al || V->cols % al)
+    return e->fail(B200_UNSUPPORTED, "attention_rows: key and value buffers are a multiple of %llu columns wide", (unsigned long long)al);
+  // Heads that share a key block and a value block (grouped-query attention) become one job of up
+  // to 8 query rows, in the order the heads came.
+  std::vector<AttnRow> rows;
+  std::vector<AttnJob> jobs;
+  std::map<std::pair<uint64_t, uint64_t>, std::vector<uint32_t>> groups;
+  std::vector<std::pair<uint64_t, uint64_t>> order;
+  rows.reserve(n_items * m);
   for (uint64_t i = 0; i < n_items; ++i) {
     const b200_attention_item& it = items[i];
     if (it.q[0] + m > Q->rows || it.q[1] + d > Q->cols || it.k[0] + l > K->rows || it.k[1] + d > K->cols ||
         it.v[0] + l > V->rows || it.v[1] + dv > V->cols)
       return e->fail(B200_UNSUPPORTED, "attention_rows: head %llu's blocks lie outside a tensor", (unsigned long long)i);
-    if (it.k[1] % 4 || it.v[1] % 4)
-      return e->fail(B200_UNSUPPORTED, "attention_rows: head %llu's keys or values start at a column that is not a multiple of 4", (unsigned long long)i);
-    host[i] = AttnItem{it.q[0] * Q->cols + it.q[1], it.k[0] * K->cols + it.k[1], it.v[0] * V->cols + it.v[1]};
+    if (it.k[1] % al || it.v[1] % al)
+      return e->fail(B200_UNSUPPORTED, "attention_rows: head %llu's keys or values start at a column that is not a multiple of %llu",
+                     (unsigned long long)i, (unsigned long long)al);
+    const std::pair<uint64_t, uint64_t> key(it.k[0] * K->cols + it.k[1], it.v[0] * V->cols + it.v[1]);
+    auto g = groups.find(key);
+    if (g == groups.end()) { g = groups.emplace(key, std::vector<uint32_t>()).first; order.push_back(key); }
+    for (uint64_t r = 0; r < m; ++r) {
+      g->second.push_back((uint32_t)rows.size());
+      rows.push_back(AttnRow{(it.q[0] + r) * Q->cols + it.q[1], (i * m + r) * dv});
+    }
   }
+  std::vector<AttnRow> sorted;
+  sorted.reserve(rows.size());
+  int widest = 1;
+  for (const auto& key : order) {
+    const std::vector<uint32_t>& members = groups[key];
+    for (size_t at = 0; at < members.size(); at += 8) {
+      const int take = (int)std::min<size_t>(8, members.size() - at);
+      jobs.push_back(AttnJob{key.first, key.second, (int32_t)sorted.size(), take});
+      for (int r = 0; r < take; ++r) sorted.push_back(rows[members[at + r]]);
+      widest = std::max(widest, take);
+    }
+  }
+  const uint64_t n_jobs = jobs.size();
+  const int rt = attention_rows_tile(widest);
   int splits = 1, lc = (int)l;
-  attention_rows_plan(n_items, (int)m, (int)l, /*sms: ask the device*/ 0, &splits, &lc);
+  attention_rows_plan(n_jobs, rt, (int)l, /*sms: ask the device*/ 0, &splits, &lc);
   const float* qp = (const float*)Q->ptr; const void* kp = K->ptr; const void* vp = V->ptr; const uint32_t* mp = (const uint32_t*)M->ptr;
-  const uint64_t q_ld = Q->cols, k_ld = K->cols, v_ld = V->cols;
-  const int kv_bf16 = K->elem == B200_BF16;
+  const uint64_t k_ld = K->cols, v_ld = V->cols;
   Buf* O = nullptr;
   st = e->new_buffer(1, n_items * m * dv, B200_F32, out, &O);
   if (st) return st;
   float* op = (float*)O->ptr;
+  std::vector<uint8_t> blob(n_jobs * sizeof(AttnJob) + sorted.size() * sizeof(AttnRow));
+  memcpy(blob.data(), jobs.data(), n_jobs * sizeof(AttnJob));
+  memcpy(blob.data() + n_jobs * sizeof(AttnJob), sorted.data(), sorted.size() * sizeof(AttnRow));
   void* dev = nullptr; uint64_t got = 0;
-  st = e->to_device(host.data(), n_items * sizeof(AttnItem), &dev, &got);
+  st = e->to_device(blob.data(), blob.size(), &dev, &got);
   if (st) { e->drop(*out); return st; }
   void* scratch = nullptr; uint64_t sgot = 0;
-  const size_t sfl = attention_rows_scratch_floats(n_items, (int)m, (int)dv, splits);
+  const size_t sfl = attention_rows_scratch_floats(n_jobs, rt, (int)dv, splits);
   if (sfl) {
     st = e->alloc(sfl * sizeof(float), &scratch, &sgot);
     if (st) { e->release(dev, got); e->drop(*out); return st; }
   }
   int launches = 0;
-  cudaError_t ce = launch_attention_rows(qp, q_ld, kp, k_ld, vp, v_ld, kv_bf16, mp, (const AttnItem*)dev, n_items, (int)m, (int)d,
-                                         (int)l, (int)dv, scale, splits, lc, (float*)scratch, op, &launches, e->stream);
+  const AttnJob* djobs = (const AttnJob*)dev;
+  const AttnRow* drows = (const AttnRow*)((const uint8_t*)dev + n_jobs * sizeof(AttnJob));
+  cudaError_t ce = launch_attention_rows(qp, kp, k_ld, vp, v_ld, kv_bf16, mp, djobs, drows, n_jobs, rt, (int)d, (int)l, (int)dv, scale,
+                                         splits, lc, (float*)scratch, op, &launches, e->stream);
   st = e->launched(ce, "attention_rows", launches > 0 ? launches : 1);
   if (scratch) e->release(scratch, sgot);
   e->release(dev, got);

@@ -61,7 +61,7 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float* sh) {
   return r;
 }
 
-// grid (splits, jobs).  Shared memory: q [RT][d], s [RT][lc], red [slices][RT][dv or less].
+// grid (splits, jobs).  Shared memory: q [RT][d], s [RT][lc], red [slices][dv or less].
 template <typename KV, int RT>
 __global__ void __launch_bounds__(THREADS)
 attention_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, uint64_t k_ld, const KV* __restrict__ v,
@@ -73,7 +73,7 @@ attention_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, uin
   __shared__ float sh[WARPS];
   float* qs = smem;                        // [RT][d]
   float* s = qs + (size_t)RT * d;          // [RT][lc]
-  float* red = s + (size_t)RT * lc;        // [nsl][RT][lanes_c * UN]
+  float* red = s + (size_t)RT * lc;        // [nsl][lanes_c * UN]: one row's slices
   const int job_i = blockIdx.y, split = blockIdx.x, splits = gridDim.x;
   const AttnJob job = jobs[job_i];
   const AttnRow* jr = rows + job.row_start;
@@ -198,23 +198,24 @@ attention_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, uin
           }
         }
       }
-      // join the slices in a fixed order: slot [sl][r][cg][e]
-      __syncthreads();
-      if (active) {
+      // join the slices in a fixed order, a row at a time: slot [sl][cg][e]
 #pragma unroll
-        for (int r = 0; r < RT; ++r)
+      for (int r = 0; r < RT; ++r) {
+        if (r >= nrows) break;               // the same for every thread
+        __syncthreads();
+        if (active) {
 #pragma unroll
-          for (int e = 0; e < UN; ++e) red[((size_t)(sl * RT + r) * lanes_c + cg) * UN + e] = acc[r][e];
-      }
-      __syncthreads();
-      for (int i = tid; i < RT * lanes_c * UN; i += THREADS) {
-        const int r = i / (lanes_c * UN), w = i % (lanes_c * UN);
-        const int col = cb * UN + w;
-        if (r < nrows && col < dv) {
-          float t = 0.f;
-          for (int z = 0; z < nsl; ++z) t += red[(size_t)(z * RT + r) * lanes_c * UN + w];
-          if (splits == 1) out[jr[r].out_off + col] = t;
-          else part_o[(((size_t)job_i * splits + split) * RT + r) * dv + col] = t;
+          for (int e = 0; e < UN; ++e) red[((size_t)sl * lanes_c + cg) * UN + e] = acc[r][e];
+        }
+        __syncthreads();
+        for (int w = tid; w < lanes_c * UN; w += THREADS) {
+          const int col = cb * UN + w;
+          if (col < dv) {
+            float t = 0.f;
+            for (int z = 0; z < nsl; ++z) t += red[(size_t)z * lanes_c * UN + w];
+            if (splits == 1) out[jr[r].out_off + col] = t;
+            else part_o[(((size_t)job_i * splits + split) * RT + r) * dv + col] = t;
+          }
         }
       }
     }
@@ -250,7 +251,7 @@ size_t smem_floats(int rt, int d, int lc, int dv, int kv_bf16) {
   const int cgn = dv / un;
   const int lanes_c = cgn < THREADS ? cgn : THREADS;
   const int nsl = THREADS / lanes_c;
-  return (size_t)rt * d + (size_t)rt * lc + (size_t)nsl * rt * lanes_c * un;
+  return (size_t)rt * d + (size_t)rt * lc + (size_t)nsl * lanes_c * un;
 }
 
 template <typename KV, int RT>
@@ -284,7 +285,8 @@ cudaError_t launch_kv(int rt, const float* q, const KV* k, uint64_t k_ld, const 
 
 int attention_rows_tile(int rows) { return rows <= 1 ? 1 : (rows <= 2 ? 2 : (rows <= 4 ? 4 : 8)); }
 
-// How a job's positions are split: enough blocks for two a SM, chunks of at least 256 positions,
+// How a job's positions are split: chunks of 512 positions or more, as many as give the device
+// about eight blocks an SM (small blocks: several fit an SM and the tail of the grid is short),
 // and a chunk's scores within 64 KB of shared memory.  rt = the rows a job is built for (1, 2, 4, 8).
 void attention_rows_plan(uint64_t n_jobs, int rt, int l, int sms, int* splits, int* lc) {
   if (sms <= 0) {
@@ -294,8 +296,8 @@ void attention_rows_plan(uint64_t n_jobs, int rt, int l, int sms, int* splits, i
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
   const int lc_max = ((64 * 1024 / 4) / rt) / 32 * 32;
-  uint64_t want = (2ull * (uint64_t)sms + n_jobs - 1) / n_jobs;
-  const uint64_t by_len = (uint64_t)(l / 256 > 1 ? l / 256 : 1);
+  uint64_t want = (8ull * (uint64_t)sms + n_jobs - 1) / n_jobs;
+  const uint64_t by_len = (uint64_t)(l / 512 > 1 ? l / 512 : 1);
   if (want > by_len) want = by_len;
   const uint64_t need = ((uint64_t)l + lc_max - 1) / lc_max;
   if (want < need) want = need;

@@ -93,7 +93,7 @@ struct Word8 { uint32_t w[8]; };
 
 __device__ __forceinline__ Word8 load8(const Mat& m, uint64_t r, uint32_t c) {
   Word8 o;
-  const uint64_t rr = (m.rows == 1) ? 0 : (r % m.rows);
+  const uint64_t rr = (m.rows == 1) ? 0 : (r < m.rows ? r : r % m.rows);   // the division only for a repeated block
   if (m.cols == 1) {
     const uint32_t v = m.bf16 ? (uint32_t)reinterpret_cast<const uint16_t*>(m.p)[rr * m.ld] << 16
                               : reinterpret_cast<const uint32_t*>(m.p)[rr * m.ld];
@@ -130,20 +130,30 @@ __device__ __forceinline__ void store8(void* out, uint64_t off, int bf16, const 
   }
 }
 
-template <uint32_t K>
+// Eight columns a thread; two such pieces in flight a thread.  I is the index type: 32-bit
+// arithmetic (no 64-bit division) whenever the piece count fits.
+template <uint32_t K, typename I>
 __global__ void __launch_bounds__(256) elt_rows8(EltwiseArgs g) {
-  const uint32_t c8 = (uint32_t)(g.cols / 8);
-  const uint64_t n8 = g.rows * c8;
-  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (uint64_t)gridDim.x * blockDim.x) {
-    const uint64_t r = i / c8;
-    const uint32_t c = (uint32_t)(i - r * c8) * 8;
-    const Word8 a = load8(g.a, r, c);
-    Word8 b, cc, o;
-    if (g.b.p) b = load8(g.b, r, c);
-    if (g.c.p) cc = load8(g.c, r, c);
+  const I c8 = (I)(g.cols / 8);
+  const I n8 = (I)(g.rows * (g.cols / 8));
+  const I stride = (I)gridDim.x * blockDim.x;
+  for (I i = (I)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += 2 * stride) {
+    const I i2 = i + stride;
+    const bool two = i2 < n8 && i2 > i;   // (i2 > i: no wrap of a 32-bit index)
+    const I r0 = i / c8, r1 = two ? i2 / c8 : r0;
+    const uint32_t c0 = (uint32_t)(i - r0 * c8) * 8, c1 = two ? (uint32_t)(i2 - r1 * c8) * 8 : c0;
+    Word8 a0 = load8(g.a, r0, c0), a1, b0, b1, cc0, cc1, o;
+    if (two) a1 = load8(g.a, r1, c1);
+    if (g.b.p) { b0 = load8(g.b, r0, c0); if (two) b1 = load8(g.b, r1, c1); }
+    if (g.c.p) { cc0 = load8(g.c, r0, c0); if (two) cc1 = load8(g.c, r1, c1); }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o.w[j] = ev<K>(a.w[j], g.b.p ? b.w[j] : 0u, g.c.p ? cc.w[j] : 0u, g.s1, g.s2, g.err);
-    store8(g.out, r * g.out_ld + c, g.out_bf16, o);
+    for (int j = 0; j < 8; ++j) o.w[j] = ev<K>(a0.w[j], g.b.p ? b0.w[j] : 0u, g.c.p ? cc0.w[j] : 0u, g.s1, g.s2, g.err);
+    store8(g.out, (uint64_t)r0 * g.out_ld + c0, g.out_bf16, o);
+    if (two) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o.w[j] = ev<K>(a1.w[j], g.b.p ? b1.w[j] : 0u, g.c.p ? cc1.w[j] : 0u, g.s1, g.s2, g.err);
+      store8(g.out, (uint64_t)r1 * g.out_ld + c1, g.out_bf16, o);
+    }
   }
 }
 
@@ -191,9 +201,11 @@ cudaError_t launch_kind(const EltwiseArgs& g, cudaStream_t stream) {
   if (g.cols % 8 == 0 && g.a.rows == g.rows && mat_ok8(g.a, g.rows, g.cols) && g.a.cols == g.cols &&
       mat_ok8(g.b, g.rows, g.cols) && mat_ok8(g.c, g.rows, g.cols) && (!g.c.p || g.c.cols == g.cols) &&
       (reinterpret_cast<uintptr_t>(g.out) % 16 == 0) && ((g.out_ld * (g.out_bf16 ? 2 : 4)) % 16 == 0) && g.cols / 8 <= 0xffffffffull) {
-    uint64_t blocks = (n / 8 + 255) / 256;
+    uint64_t blocks = (n / 16 + 255) / 256;
+    if (blocks == 0) blocks = 1;
     if (blocks > 148ull * 32) blocks = 148ull * 32;
-    elt_rows8<K><<<(unsigned)blocks, 256, 0, stream>>>(g);
+    if (n / 8 + 2ull * blocks * 256 < 0xffffffffull) elt_rows8<K, uint32_t><<<(unsigned)blocks, 256, 0, stream>>>(g);
+    else elt_rows8<K, uint64_t><<<(unsigned)blocks, 256, 0, stream>>>(g);
     return cudaGetLastError();
   }
   uint64_t blocks = (n + 255) / 256;

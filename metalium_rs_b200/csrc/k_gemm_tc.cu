@@ -295,10 +295,21 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
 
   const uint32_t tiles_m = (uint32_t)((g.m + BM - 1) / BM);
-  // Narrow tiles when wide ones would leave SMs idle or waste most of a tile.
-  const uint64_t wide_tiles = (uint64_t)tiles_m * ((g.n + 255) / 256) * g.batch;
-  const bool narrow = g.n <= 128 || wide_tiles < (uint64_t)sms;
-  const int bn = narrow ? 128 : 256;
+  // Tile width: 128, 192 or 256 columns.  A tile costs a fixed part (pipeline fill, epilogue: about
+  // what sixteen 128-wide k-blocks cost) plus its k-blocks in proportion to its width; the CTAs run
+  // the tiles in waves of one per SM.  Take the width with the least modelled time, so 576 columns
+  // run as three 192-wide tiles in one wave instead of five 128-wide ones in two.
+  const uint64_t num_kb_host = (g.k + BK - 1) / BK;
+  const uint64_t nb = g.batch ? g.batch : 1;
+  int bn = 128;
+  double best = 1e300;
+  for (int cand : {128, 192, 256}) {
+    if (cand > 128 && g.n <= 128) continue;
+    const uint64_t tiles = (uint64_t)tiles_m * ((g.n + cand - 1) / cand) * nb;
+    const uint64_t waves = (tiles + sms - 1) / sms;
+    const double cost = (double)waves * (16.0 + (double)num_kb_host * cand / 128.0);
+    if (cost < best * 0.999) { best = cost; bn = cand; }
+  }
   const uint32_t tiles_n = (uint32_t)((g.n + bn - 1) / bn);
 
   CUtensorMap ma, mb;
@@ -319,6 +330,7 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int
   const uint64_t total = (uint64_t)tiles_m * tiles_n * p.batch;
   const unsigned grid = (unsigned)(total < (uint64_t)sms ? total : (uint64_t)sms);
   if (bn == 256) return launch_variant<256, 4>(ma, mb, p, a_mn, b_mn, grid, stream);
+  if (bn == 192) return launch_variant<192, 5>(ma, mb, p, a_mn, b_mn, grid, stream);
   return launch_variant<128, 6>(ma, mb, p, a_mn, b_mn, grid, stream);
 }
 

@@ -75,14 +75,17 @@ cudaError_t launch_gather_row_ptrs(const void* const* row_ptrs, uint64_t n_rows,
 // out[dst_row(i), :] = src[src_row(i), :], pairs (dst, src) on the device.
 cudaError_t launch_assign_rows(void* out, const void* value, uint64_t cols, int elem_bytes,
                                const uint64_t* pairs, uint64_t n, cudaStream_t);
-// attention_rows (k_attention.cu): element offsets of a head's blocks in q, k and v
-struct AttnItem { uint64_t q_off, k_off, v_off; };
-void attention_rows_plan(uint64_t n_items, int m, int l, int sms, int* splits, int* lc);
-size_t attention_rows_scratch_floats(uint64_t n_items, int m, int dv, int splits);
-cudaError_t launch_attention_rows(const float* q, uint64_t q_ld, const void* k, uint64_t k_ld, const void* v,
-                                  uint64_t v_ld, int kv_bf16, const uint32_t* mask, const AttnItem* items,
-                                  uint64_t n_items, int m, int d, int l, int dv, float scale, int splits, int lc,
-                                  float* scratch, float* out, int* launches, cudaStream_t stream);
+// attention_rows (k_attention.cu).  A job is up to 8 query rows that share a key block and a
+// value block (element offsets); a row is where its query starts in q and its result in out.
+struct AttnJob { uint64_t k_off, v_off; int32_t row_start, nrows; };
+struct AttnRow { uint64_t q_off, out_off; };
+int attention_rows_tile(int rows);   // the rows a job is built for: 1, 2, 4 or 8
+void attention_rows_plan(uint64_t n_jobs, int rt, int l, int sms, int* splits, int* lc);
+size_t attention_rows_scratch_floats(uint64_t n_jobs, int rt, int dv, int splits);
+cudaError_t launch_attention_rows(const float* q, const void* k, uint64_t k_ld, const void* v, uint64_t v_ld, int kv_bf16,
+                                  const uint32_t* mask, const AttnJob* jobs, const AttnRow* rows, uint64_t n_jobs, int rt,
+                                  int d, int l, int dv, float scale, int splits, int lc, float* scratch, float* out,
+                                  int* launches, cudaStream_t stream);
 // fused attention over whole sequences (k_attention_tc.cu): element coordinates of a block's Q, K
 // and V (row, column) and the element offset of its output
 struct AttnBlockDev { int32_t q_r, q_c, k_r, k_c, v_r, v_c; int32_t pad0, pad1; uint64_t o_off; };

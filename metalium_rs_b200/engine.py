@@ -449,15 +449,20 @@ class CudaEngine:
         assert src.size == 2 * dims[0] * dims[1]
         return self._call(self._lib.b200_repack, C.c_uint64(a), _ptr(src), (C.c_uint64 * 2)(*dims))
 
+    @staticmethod
+    def attention_item_array(items):
+        """The head list marshalled once, for a caller that issues the same list every step."""
+        arr = (AttentionItem * max(len(items), 1))()
+        for i, (q, k, v) in enumerate(items):
+            arr[i] = AttentionItem((C.c_uint64 * 2)(*q), (C.c_uint64 * 2)(*k), (C.c_uint64 * 2)(*v))
+        return arr
+
     def attention_rows(self, buffers, items, dims, scale: float) -> Out:
         """`attention_rows([q, k, v, mask], items, [m, d, l, dv], scale)` (server.rs:257): each item is
         the (row, col) of a head's query, key and value blocks; the result is the
         [1, len(items) * m * dv] row of the heads' rows."""
-        n = len(items)
-        arr = (AttentionItem * max(n, 1))()
-        for i, (q, k, v) in enumerate(items):
-            arr[i] = AttentionItem((C.c_uint64 * 2)(*q), (C.c_uint64 * 2)(*k), (C.c_uint64 * 2)(*v))
-        return self._call(self._lib.b200_attention_rows, (C.c_uint64 * 4)(*buffers), arr, C.c_uint64(n),
+        arr = items if isinstance(items, C.Array) else self.attention_item_array(items)
+        return self._call(self._lib.b200_attention_rows, (C.c_uint64 * 4)(*buffers), arr, C.c_uint64(len(items)),
                           (C.c_uint64 * 4)(*dims), C.c_float(scale))
 
     @staticmethod

@@ -12,6 +12,7 @@ int fake_cuda_device_count = 1;
 int fake_cuda_capturing = 0;
 int fake_launch_count = 0;        // launches the engine asked for
 int fake_tc_supported = 1;        // what gemm_tc_supported answers for BF16 operands
+int fake_last_attention_jobs = 0; // jobs of the last attention_rows launch
 }
 
 namespace b200 {
@@ -37,11 +38,12 @@ cudaError_t launch_gather_row_ptrs(const void* const*, uint64_t, uint64_t, int, 
 cudaError_t launch_assign_rows(void*, const void*, uint64_t, int, const uint64_t*, uint64_t, cudaStream_t) { OK_LAUNCH; }
 cudaError_t launch_copy_blocks(const void*, uint64_t, void*, uint64_t, int, const MoveDev*, uint64_t, uint64_t, uint64_t, cudaStream_t) { OK_LAUNCH; }
 cudaError_t launch_repack(const void*, uint64_t, int, const uint64_t*, uint64_t, void*, cudaStream_t) { OK_LAUNCH; }
+int attention_rows_tile(int rows) { return rows <= 1 ? 1 : (rows <= 2 ? 2 : (rows <= 4 ? 4 : 8)); }
 void attention_rows_plan(uint64_t, int, int l, int, int* splits, int* lc) { *splits = l > 256 ? 2 : 1; *lc = l > 256 ? (l / 2 + 31) / 32 * 32 : l; }
-size_t attention_rows_scratch_floats(uint64_t n, int m, int dv, int splits) { return splits > 1 ? (size_t)n * splits * m * (dv + 2) : 0; }
-cudaError_t launch_attention_rows(const float*, uint64_t, const void*, uint64_t, const void*, uint64_t, int, const uint32_t*,
-                                  const AttnItem*, uint64_t, int, int, int, int, float, int splits, int, float*, float*,
-                                  int* launches, cudaStream_t) { *launches = splits > 1 ? 2 : 1; OK_LAUNCH; }
+size_t attention_rows_scratch_floats(uint64_t n, int rt, int dv, int splits) { return splits > 1 ? (size_t)n * splits * rt * (dv + 2) : 0; }
+cudaError_t launch_attention_rows(const float*, const void*, uint64_t, const void*, uint64_t, int, const uint32_t*, const AttnJob*,
+                                  const AttnRow*, uint64_t n_jobs, int, int, int, int, float, int splits, int, float*, float*,
+                                  int* launches, cudaStream_t) { fake_last_attention_jobs = (int)n_jobs; *launches = splits > 1 ? 2 : 1; OK_LAUNCH; }
 bool attention_tc_supported(uint64_t sq, uint64_t d, uint64_t sk, uint64_t dv, float scale, int causal, const char** why) {
   *why = "the fake runtime follows the kernel's rules";
   return (d == 64 || d == 128) && dv == d && sq && sk && sq % 128 == 0 && sk % 128 == 0 && scale > 0.f && (!causal || sk >= sq);

@@ -154,6 +154,7 @@ def test_attention_rows_dims_and_refusals(e):                                   
     out, dims = e.attention_rows([q, k, v, mask], heads, [2, 64, 512, 32], 0.125)
     assert dims == (1, 2 * 2 * 32) and e.dims_of(out) == ((1, 128), F32)
     assert e.device_traffic().launches - before == 2          # positions split over blocks, then joined
+    assert C.c_int.in_dll(e._lib, "fake_last_attention_jobs").value == 1   # both heads share K and V: one job of 4 rows
     short, _ = e.attention_rows([q, k, v, mask], heads, [2, 64, 512, 32][:1] + [64, 512, 32], 0.125)
     e.free(short)
     for dims4 in ([33, 64, 512, 32], [2, 48, 512, 32], [2, 64, 500, 32], [2, 64, 512, 16], [0, 64, 512, 32]):
