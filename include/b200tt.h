@@ -201,6 +201,11 @@ int32_t b200_rms_norm(b200_engine*, b200_buffer a, b200_buffer gamma, float eps,
 /* `add_rms_norm`: s = a + b and s's RMSNorm: (s, norm). */
 int32_t b200_add_rms_norm(b200_engine*, b200_buffer a, b200_buffer b, b200_buffer gamma, float eps,
                           b200_buffer out[2], uint64_t out_dims[2]);
+/* `add_rms_norm` with the norm's type named, as `rms_norm_as` (server.rs:449) names it: norm_bf16
+ * rounds the F32 norm once, bit for bit `add_rms_norm` then `cast_float` of the norm; s stays in
+ * the operands' type. */
+int32_t b200_add_rms_norm_as(b200_engine*, b200_buffer a, b200_buffer b, b200_buffer gamma, float eps,
+                             int32_t norm_bf16, b200_buffer out[2], uint64_t out_dims[2]);
 /* `argmax_row`: a [rows, cols] -> [rows, 1] I32 (the trait passes one row). */
 int32_t b200_argmax_row(b200_engine*, b200_buffer a, b200_buffer* out, uint64_t out_dims[2]);
 

@@ -178,6 +178,7 @@ struct b200_engine {
   // The block returns to the cache at once: every user of it was enqueued on the one
   // stream before this call, and so is every later user.
   void release(void* p, uint64_t sz) {
+    if (sz == 0) return;                 // a kept block list: the engine's, not the pool's
     traffic.pool_in_use -= sz;
     if (capturing && cur_owned.count(p)) { cur_free.emplace(sz, p); return; }
     if (!traces.empty() && trace_owned(p)) return;   // its trace keeps it
@@ -226,7 +227,45 @@ struct b200_engine {
     }
   }
   // Host metadata (block lists, index lists) to a temporary device block.
+  // Block lists (batched products, moves, attention heads) go to the device before their kernel.
+  // A caller issues the same few lists every step, so lists of up to 64 KB are kept on the device
+  // by content: a repeat costs no copy (and adds no copy node to a trace).  A kept list is owned by
+  // the engine: *got comes back 0 and release() of it does nothing.
+  struct MetaEntry { std::vector<uint8_t> bytes; void* dev = nullptr; };
+  std::unordered_multimap<uint64_t, MetaEntry> meta_cache;
+  uint64_t meta_hits = 0;
+  static uint64_t fnv1a(const void* p, uint64_t n) {
+    const uint8_t* b = (const uint8_t*)p;
+    uint64_t h = 1469598103934665603ull;
+    for (uint64_t i = 0; i < n; ++i) { h ^= b[i]; h *= 1099511628211ull; }
+    return h;
+  }
   int to_device(const void* host, uint64_t bytes, void** dev, uint64_t* got) {
+    const bool keepable = bytes > 0 && bytes <= (64u << 10);
+    uint64_t key = 0;
+    if (keepable) {
+      key = fnv1a(host, bytes);
+      auto range = meta_cache.equal_range(key);
+      for (auto it = range.first; it != range.second; ++it)
+        if (it->second.bytes.size() == bytes && memcmp(it->second.bytes.data(), host, bytes) == 0) {
+          *dev = it->second.dev; *got = 0; ++meta_hits;
+          return B200_OK;
+        }
+      if (!capturing && meta_cache.size() < 1024) {
+        void* p = nullptr;
+        if (cudaMalloc(&p, (bytes + 255) & ~255ull) == cudaSuccess) {
+          auto it = meta_cache.emplace(key, MetaEntry());
+          it->second.bytes.assign((const uint8_t*)host, (const uint8_t*)host + bytes);
+          it->second.dev = p;
+          cudaError_t e = cudaMemcpyAsync(p, it->second.bytes.data(), bytes, cudaMemcpyHostToDevice, stream);
+          if (e != cudaSuccess) { cudaFree(p); meta_cache.erase(it); return cuda_fail(e, "metadata upload"); }
+          traffic.bytes_h2d += bytes;
+          *dev = p; *got = 0;
+          return B200_OK;
+        }
+        cudaGetLastError();   // no room for a kept copy: the plain path below
+      }
+    }
     int st = alloc(bytes, dev, got);
     if (st) return st;
     if (capturing) {
@@ -475,6 +514,7 @@ void b200_engine_destroy(b200_engine* e) {
   for (auto& kv : e->bufs)
     if (!kv.second.parent && !kv.second.adopted && kv.second.ptr) cudaFree(kv.second.ptr);
   for (auto& kv : e->cache) cudaFree(kv.second);
+  for (auto& kv : e->meta_cache) cudaFree(kv.second.dev);
   cudaFree(e->d_err);
   cudaFree(e->full_scratch);
   cudaFreeHost(e->h_err);
@@ -931,6 +971,11 @@ int32_t b200_rms_norm(b200_engine* e, b200_buffer a, b200_buffer gamma, float ep
 
 int32_t b200_add_rms_norm(b200_engine* e, b200_buffer a, b200_buffer b, b200_buffer gamma, float eps, b200_buffer out[2],
                           uint64_t out_dims[2]) {
+  return b200_add_rms_norm_as(e, a, b, gamma, eps, 0, out, out_dims);
+}
+
+int32_t b200_add_rms_norm_as(b200_engine* e, b200_buffer a, b200_buffer b, b200_buffer gamma, float eps, int32_t norm_bf16,
+                             b200_buffer out[2], uint64_t out_dims[2]) {
   cudaSetDevice(e->device);
   Buf *A = nullptr, *B = nullptr, *G = nullptr;
   int st = e->need(a, &A, "add_rms_norm");
@@ -949,9 +994,10 @@ int32_t b200_add_rms_norm(b200_engine* e, b200_buffer a, b200_buffer b, b200_buf
   st = e->new_buffer(rows, cols, obf ? B200_BF16 : B200_F32, &out[0], &S);
   if (st) return st;
   void* sp = S->ptr;
-  st = e->new_buffer(rows, cols, obf ? B200_BF16 : B200_F32, &out[1], &N);
+  const int nbf = obf || norm_bf16;   // the norm rounded once to BF16 where asked
+  st = e->new_buffer(rows, cols, nbf ? B200_BF16 : B200_F32, &out[1], &N);
   if (st) { e->drop(out[0]); return st; }
-  st = e->launched(launch_rms_norm(ap, abf, bp, bbf, gp, gbf, eps, sp, obf, N->ptr, obf, rows, cols, e->stream), "add_rms_norm");
+  st = e->launched(launch_rms_norm(ap, abf, bp, bbf, gp, gbf, eps, sp, obf, N->ptr, nbf, rows, cols, e->stream), "add_rms_norm");
   if (st) { e->drop(out[0]); e->drop(out[1]); return st; }
   set_dims(out_dims, rows, cols);
   return B200_OK;

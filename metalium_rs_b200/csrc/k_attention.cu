@@ -17,6 +17,7 @@
 //   rows x V: a thread a 16-byte column group and a slice of positions, rows in registers.
 #include <cfloat>
 #include <cstdint>
+#include <cstdlib>
 #include <cuda_runtime.h>
 
 #include "kernels.h"
@@ -297,7 +298,9 @@ void attention_rows_plan(uint64_t n_jobs, int rt, int l, int sms, int* splits, i
   }
   const int lc_max = ((64 * 1024 / 4) / rt) / 32 * 32;
   uint64_t want = (8ull * (uint64_t)sms + n_jobs - 1) / n_jobs;
-  const uint64_t by_len = (uint64_t)(l / 512 > 1 ? l / 512 : 1);
+  static int chunk = 0;
+  if (!chunk) { const char* e = getenv("B200TT_ATTN_CHUNK"); chunk = e ? atoi(e) : 512; if (chunk < 32) chunk = 512; }
+  const uint64_t by_len = (uint64_t)(l / chunk > 1 ? l / chunk : 1);
   if (want > by_len) want = by_len;
   const uint64_t need = ((uint64_t)l + lc_max - 1) / lc_max;
   if (want < need) want = need;

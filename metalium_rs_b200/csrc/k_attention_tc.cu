@@ -89,8 +89,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < KS; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], SOFTMAX_THREADS); }
-    mbar_init(p_full, SOFTMAX_THREADS);
+    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], SOFTMAX_THREADS / 32); }   // a lane a warp arrives
+    mbar_init(p_full, SOFTMAX_THREADS / 32);
     mbar_init(p_empty, 1);
     mbar_init(o_full, 1);
     *abort_flag = 0;
@@ -106,9 +106,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
-  // heavy query tiles first: under a causal mask the last tile of a block has the most keys
-  const uint32_t qt = p.q_tiles - 1 - blockIdx.x;
-  const AttnBlockDev it = p.items[blockIdx.y];
+  // Heaviest work first: under a causal mask a block's last query tile has the most keys, so the grid
+  // runs every block's last tile, then every block's tile before it, ... (the block index is the
+  // fastest-varying one), and the short tiles fill the SMs the long ones leave.
+  const uint32_t qt = p.q_tiles - 1 - blockIdx.y;
+  const AttnBlockDev it = p.items[blockIdx.x];
   const int32_t i0 = (int32_t)(qt * 128);
   uint32_t nk = p.k_tiles;
   if (p.causal) {
@@ -233,7 +235,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       tmem_ld32(lane_addr + buf * S_COLS + half * 64 + 32, v + 32);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(&s_empty[buf]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[buf]);   // one arrival a warp: 256 arrivals on one barrier serialise
       if (key0 + 63 > last_key) {                    // only the diagonal tile needs the mask
 #pragma unroll
         for (int e = 0; e < 64; ++e)
@@ -259,7 +262,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       tmem_ld32(lane_addr + buf * S_COLS + half * 64 + 32, v + 32);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(&s_empty[buf]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[buf]);   // one arrival a warp: 256 arrivals on one barrier serialise
       uint32_t pk[32];
       const bool edge = key0 + 63 > last_key;
       float s0 = 0.f, s1 = 0.f;
@@ -283,7 +287,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       for (int u = 0; u < 8; ++u)
         *reinterpret_cast<uint4*>(prow + ((u ^ (row & 7)) << 4)) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes, read by the MMA
-      mbar_arrive(p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
     }
     xsum[half * 128 + row] = sum;
     asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -336,7 +341,7 @@ cudaError_t launch_d(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
     if (e != cudaSuccess) return e;
     set = true;
   }
-  attention_tc_kernel<D><<<dim3(p.q_tiles, (unsigned)n_items, 1), ATTN_THREADS, smem, stream>>>(mq, mk, mv, p);
+  attention_tc_kernel<D><<<dim3((unsigned)n_items, p.q_tiles, 1), ATTN_THREADS, smem, stream>>>(mq, mk, mv, p);
   return cudaGetLastError();
 }
 
@@ -357,7 +362,7 @@ cudaError_t launch_attention_tc(const void* q, uint64_t q_rows, uint64_t q_cols,
                                 const AttnBlockDev* items, uint64_t n_items, uint64_t sq, uint64_t d, uint64_t sk,
                                 float scale, int causal, void* out, uint64_t o_ld, int* err, cudaStream_t stream) {
   if (n_items == 0) return cudaSuccess;
-  if (n_items > 65535) return cudaErrorNotSupported;
+  if (n_items > 0x7fffffffull || sq / 128 > 65535) return cudaErrorNotSupported;
   CUtensorMap mq, mk, mv;
   if (!tc::make_map(&mq, q, q_rows, q_cols, q_cols, 128) || !tc::make_map(&mk, k, k_rows, k_cols, k_cols, 128) ||
       !tc::make_map(&mv, v, v_rows, v_cols, v_cols, 128))

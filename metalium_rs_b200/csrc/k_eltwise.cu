@@ -93,7 +93,8 @@ struct Word8 { uint32_t w[8]; };
 
 __device__ __forceinline__ Word8 load8(const Mat& m, uint64_t r, uint32_t c) {
   Word8 o;
-  const uint64_t rr = (m.rows == 1) ? 0 : (r < m.rows ? r : r % m.rows);   // the division only for a repeated block
+  // the division only for a repeated block, and in 32 bits when the numbers fit
+  const uint64_t rr = (m.rows == 1) ? 0 : (r < m.rows ? r : (((r | m.rows) >> 32) == 0 ? (uint64_t)((uint32_t)r % (uint32_t)m.rows) : r % m.rows));
   if (m.cols == 1) {
     const uint32_t v = m.bf16 ? (uint32_t)reinterpret_cast<const uint16_t*>(m.p)[rr * m.ld] << 16
                               : reinterpret_cast<const uint32_t*>(m.p)[rr * m.ld];
@@ -246,8 +247,9 @@ rope_kernel8(Mat x, Mat cs, Mat sn, uint32_t head, void* out, uint64_t out_ld, i
              uint64_t rows, uint32_t cols) {
   const uint32_t c8 = cols / 8, half = head / 2;
   const uint64_t n8 = rows * c8;
+  const bool small = n8 <= 0xffffffffull;     // 32-bit divisions
   for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (uint64_t)gridDim.x * blockDim.x) {
-    const uint64_t r = i / c8;
+    const uint64_t r = small ? (uint64_t)((uint32_t)i / c8) : i / c8;
     const uint32_t c = (uint32_t)(i - r * c8) * 8;
     const uint32_t h = c / head, j = c - h * head;
     const uint32_t cswap = h * head + (j < half ? j + half : j - half);

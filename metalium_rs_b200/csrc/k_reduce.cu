@@ -649,9 +649,11 @@ rms_norm_kernel(const void* a, int a_bf16, const void* b, int b_bf16, const void
 
 // F32 rows of up to 1024 columns, no residual: a warp a row, the row kept in registers between
 // the sum of squares and the division (one read, one write).  Same roundings as the general kernel.
-template <int V>
+// ADD: the row is a + b (one rounding), also written to sum_out.
+template <int V, bool ADD>
 __global__ void __launch_bounds__(256)
-rms_norm_rows_kernel(const float* __restrict__ a, const void* __restrict__ gamma, int g_bf16, float eps,
+rms_norm_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ sum_out,
+                     const void* __restrict__ gamma, int g_bf16, float eps,
                      void* __restrict__ out, int out_bf16, uint64_t rows, uint32_t cols) {
   const int lane = threadIdx.x & 31;
   const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -667,6 +669,11 @@ rms_norm_rows_kernel(const float* __restrict__ a, const void* __restrict__ gamma
       const uint32_t i = lane + u * 32;
       if (i < n4) {
         v[u] = p[i];
+        if constexpr (ADD) {
+          const float4 w = reinterpret_cast<const float4*>(b + row * cols)[i];
+          v[u].x = v[u].x + w.x; v[u].y = v[u].y + w.y; v[u].z = v[u].z + w.z; v[u].w = v[u].w + w.w;
+          reinterpret_cast<float4*>(sum_out + row * cols)[i] = v[u];
+        }
         ss = ss + ((v[u].x * v[u].x + v[u].y * v[u].y) + (v[u].z * v[u].z + v[u].w * v[u].w));
       }
     }
@@ -924,12 +931,21 @@ cudaError_t launch_rms_norm(const void* a, int a_bf16, const void* b, int b_bf16
   if (rows == 0) return cudaSuccess;
   uint64_t grid = (rows + 7) / 8;
   if (grid > 148ull * 16) grid = 148ull * 16;
-  if (!a_bf16 && !b && !sum_out && norm_out && cols % 4 == 0 && cols <= 1024 &&
-      ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(norm_out) | reinterpret_cast<uintptr_t>(gamma)) & 15) == 0) {
+  const bool plain = !b && !sum_out;
+  const bool added = b && !b_bf16 && sum_out && !sum_bf16;
+  if (!a_bf16 && (plain || added) && norm_out && cols % 4 == 0 && cols <= 1024 &&
+      ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(sum_out) |
+        reinterpret_cast<uintptr_t>(norm_out) | reinterpret_cast<uintptr_t>(gamma)) & 15) == 0) {
     const float* af = (const float*)a;
+    const float* bf = (const float*)b;
+    float* sf = (float*)sum_out;
     const uint32_t c32 = (uint32_t)cols;
     const int v = (int)((cols / 4 + 31) / 32);
-#define RN(V) rms_norm_rows_kernel<V><<<(unsigned)grid, 256, 0, s>>>(af, gamma, gamma_bf16, eps, norm_out, norm_bf16, rows, c32)
+#define RN(V)                                                                                                              \
+  do {                                                                                                                     \
+    if (added) rms_norm_rows_kernel<V, true><<<(unsigned)grid, 256, 0, s>>>(af, bf, sf, gamma, gamma_bf16, eps, norm_out, norm_bf16, rows, c32); \
+    else rms_norm_rows_kernel<V, false><<<(unsigned)grid, 256, 0, s>>>(af, nullptr, nullptr, gamma, gamma_bf16, eps, norm_out, norm_bf16, rows, c32); \
+  } while (0)
     if (v <= 1) RN(1); else if (v <= 2) RN(2); else if (v <= 4) RN(4); else if (v <= 5) RN(5); else RN(8);
 #undef RN
     return cudaGetLastError();

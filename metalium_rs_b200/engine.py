@@ -387,10 +387,14 @@ class CudaEngine:
         return self.rms_norm_as(a, gamma, eps, False)
 
     def add_rms_norm(self, a: int, b: int, gamma: Optional[int], eps: float):
+        return self.add_rms_norm_as(a, b, gamma, eps, False)
+
+    def add_rms_norm_as(self, a: int, b: int, gamma: Optional[int], eps: float, bf16: bool):
+        """(s, norm): s = a + b, norm = RMSNorm(s) * gamma, the norm rounded once to BF16 where `bf16`."""
         out = (C.c_uint64 * 2)()
         dims = (C.c_uint64 * 2)()
-        self._check(self._lib.b200_add_rms_norm(self._e, C.c_uint64(a), C.c_uint64(b), C.c_uint64(gamma or 0),
-                                                C.c_float(eps), out, dims))
+        self._check(self._lib.b200_add_rms_norm_as(self._e, C.c_uint64(a), C.c_uint64(b), C.c_uint64(gamma or 0),
+                                                   C.c_float(eps), C.c_int32(1 if bf16 else 0), out, dims))
         d = (dims[0], dims[1])
         return [(out[0], d), (out[1], d)]
 

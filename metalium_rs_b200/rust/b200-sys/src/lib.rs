@@ -55,6 +55,7 @@ extern "C" {
     pub fn b200_rms(a0: *mut b200_engine, a: u64, eps: f32, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_rms_norm(a0: *mut b200_engine, a: u64, gamma: u64, eps: f32, out_bf16: i32, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_add_rms_norm(a0: *mut b200_engine, a: u64, b: u64, gamma: u64, eps: f32, out: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_add_rms_norm_as(a0: *mut b200_engine, a: u64, b: u64, gamma: u64, eps: f32, norm_bf16: i32, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_argmax_row(a0: *mut b200_engine, a: u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_select_rows(a0: *mut b200_engine, table: u64, indices: u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_pick_columns(a0: *mut b200_engine, input: u64, indices: u64, out: *mut u64, out_dims: *mut u64) -> i32;

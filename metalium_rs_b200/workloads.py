@@ -185,9 +185,9 @@ class LlamaPrefill:
             for h in range(c.heads):
                 i = b * c.heads + h
                 kvh = h // group
-                fused_items.append(((b * t, h * hd), (b * t, kvh * hd), (b * t, self.q_cols + self.kv_cols + kvh * hd),
-                                    (b * t, h * hd)))
-                self.qk_items.append((((b * t, h * hd), False), ((b * t, kvh * hd), True)))
+                fused_items.append(((b * t, h * hd), (b * t, self.q_cols + kvh * hd),
+                                    (b * t, self.q_cols + self.kv_cols + kvh * hd), (b * t, h * hd)))
+                self.qk_items.append((((b * t, h * hd), False), ((b * t, self.q_cols + kvh * hd), True)))
                 self.pv_items.append((((i * t, 0), False), ((b * t, self.q_cols + self.kv_cols + kvh * hd), False)))
                 self.merge.append(((i * t, 0), (b * t, h * hd), (t, hd), False))
         self.fused_items = eng.attention_block_array(fused_items)
@@ -203,21 +203,21 @@ class LlamaPrefill:
         emb, _ = e.select_rows(self.w["embed"], ids_buf)                     # ops.rs:4958 embedding
         x, _ = e.cast_float(emb, False)                                      # residual stream F32
         e.free(emb)
+        qk_cols = self.q_cols + self.kv_cols
+        n1, _ = e.rms_norm_as(x, self.w["l0.norm1"], c.eps, True)           # llama.rs:151-170
         for l in range(c.layers):
-            n1, _ = e.rms_norm_as(x, self.w[f"l{l}.norm1"], c.eps, True)     # llama.rs:151-170
             qkv, _ = e.matmul_dram_bf16(n1, False, self.w[f"l{l}.qkv"], False)
             e.free(n1)
-            qr, _ = e.rope_blocks((qkv, (0, 0), (n, self.q_cols)), (self.cos, (0, 0), (t, hd)),
-                                  (self.sin, (0, 0), (t, hd)), hd, True)      # rope.rs:129
-            kr, _ = e.rope_blocks((qkv, (0, self.q_cols), (n, self.kv_cols)), (self.cos, (0, 0), (t, hd)),
+            # RoPE on the query and key heads together: they share the head width and the tables (rope.rs:129)
+            qk, _ = e.rope_blocks((qkv, (0, 0), (n, qk_cols)), (self.cos, (0, 0), (t, hd)),
                                   (self.sin, (0, 0), (t, hd)), hd, True)
             if self.fused:   # scores, mask, softmax, P V and the merge of heads as one kernel
-                om, _ = e.attention_blocks(qr, kr, qkv, self.fused_items, (t, hd, t, hd), 1.0 / float(np.sqrt(hd)), True,
+                om, _ = e.attention_blocks(qk, qk, qkv, self.fused_items, (t, hd, t, hd), 1.0 / float(np.sqrt(hd)), True,
                                            (n, self.q_cols))
-                e.free(qr); e.free(kr); e.free(qkv)
+                e.free(qk); e.free(qkv)
             else:
-                s, _ = e.matmul_dram_batched(qr, kr, self.qk_items, (t, hd, t))  # Q K^T, F32 scores
-                e.free(qr); e.free(kr)
+                s, _ = e.matmul_dram_batched(qk, qk, self.qk_items, (t, hd, t))  # Q K^T, F32 scores
+                e.free(qk)
                 pb, _ = e.softmax_rows_as(s, self.mask, 1.0 / float(np.sqrt(hd)), True)   # scale, causal mask, softmax
                 e.free(s)
                 o, _ = e.matmul_dram_batched(pb, qkv, self.pv_items, (t, t, hd), bf16=True)   # P V
@@ -226,9 +226,9 @@ class LlamaPrefill:
                 e.free(o)
             att, _ = e.matmul_dram(om, False, self.w[f"l{l}.o"], False)      # o_proj, F32 out
             e.free(om)
-            x2 = el(K.ADD, x, att)                                           # residual (llama.rs:288)
+            # residual add and the next norm as one op (`Engine::add_rms_norm`, server.rs:466; llama.rs:288)
+            (x2, _), (n2, _) = e.add_rms_norm_as(x, att, self.w[f"l{l}.norm2"], c.eps, True)
             e.free(x); e.free(att)
-            n2, _ = e.rms_norm_as(x2, self.w[f"l{l}.norm2"], c.eps, True)
             gu, _ = e.matmul_dram_bf16(n2, False, self.w[f"l{l}.gate_up"], False)
             e.free(n2)
             act, _ = e.eltwise_blocks_as(EltwiseOp(K.SILU_MUL, 0.0, 0.0), (gu, (0, 0), (n, c.ff)),
@@ -236,7 +236,10 @@ class LlamaPrefill:
             e.free(gu)
             d, _ = e.matmul_dram(act, False, self.w[f"l{l}.down"], False)
             e.free(act)
-            x = el(K.ADD, x2, d)
+            if l + 1 < c.layers:
+                (x, _), (n1, _) = e.add_rms_norm_as(x2, d, self.w[f"l{l + 1}.norm1"], c.eps, True)
+            else:
+                x = el(K.ADD, x2, d)
             e.free(x2); e.free(d)
         if all_positions:
             last = x

@@ -4,7 +4,7 @@ step32_burn_softmax.rs:47, step230_softmax_rows.rs:123 and step211_argmax_row.rs
 import numpy as np
 import pytest
 
-from metalium_rs_b200 import (ALL, ANY, BITOR, BOOL, COLS, F32, I32, MAX, MAX_I32, MIN_I32, PROD, PROD_I32, ROWS, SUM,
+from metalium_rs_b200 import (ALL, ANY, BF16, BITOR, BOOL, COLS, F32, I32, MAX, MAX_I32, MIN_I32, PROD, PROD_I32, ROWS, SUM,
                               SUM_I32, TtError, kinds)
 from oracle import oracle as orc
 from tests import helpers as H
@@ -206,6 +206,23 @@ def test_add_rms_norm_returns_the_sum_and_its_norm(eng):  # server.rs:466
     wn = orc.rms_norm(ssum, gamma, 1e-5)
     assert np.max(np.abs(eng.download(n) - wn)) <= 1e-5 * np.max(np.abs(wn))
     for i in (ia, ib, ig, s, n):
+        eng.free(i)
+
+
+@pytest.mark.parametrize("shape", [(65, 576), (7, 70), (33, 2052)])   # the register kernel, ragged columns, wide rows
+def test_add_rms_norm_as_is_the_composition_bit_for_bit(eng, shape):  # server.rs:446-463: norm, then cast_float
+    a, b = orc.normal(0x54, 3, shape), orc.normal(0x54, 4, shape)
+    gamma = orc.uniform(0x54, 5, (1, shape[1]), 0.5, 1.5)
+    ia, ib, ig = eng.upload(a, *shape), eng.upload(b, *shape), eng.upload(gamma, 1, shape[1])
+    (s0, _), (n0, _) = eng.add_rms_norm(ia, ib, ig, 1e-5)
+    (s1, _), (n1, d1) = eng.add_rms_norm_as(ia, ib, ig, 1e-5, True)
+    assert d1 == shape and eng.dims_of(n1) == (shape, BF16) and eng.dims_of(s1) == (shape, F32)
+    assert np.array_equal(eng.download_bits(s1), eng.download_bits(s0))
+    assert np.array_equal(eng.download(s1), (a + b).astype(np.float32))
+    cast, _ = eng.cast_float(n0, True)
+    assert np.array_equal(eng.download_bf16(n1), eng.download_bf16(cast))
+    # and the two-op form: ADD, then rms_norm_as
+    for i in (ia, ib, ig, s0, n0, s1, n1, cast):
         eng.free(i)
 
 
