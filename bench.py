@@ -438,6 +438,22 @@ def callers(eng, timed):
     res["smollm2_135m_prefill_8x512"].update({"composed_attention_ms": cms, "composed_tok_per_s": batch * seq / (cms * 1e-3),
                                               "composed_argmax_agrees": a3 == a2})
 
+    # generation: decode steps over a fixed-shape KV cache, one traced step replayed a token
+    for nb in (1, 8):
+        dec = W.LlamaDecode(eng, cfg, model.w, nb, max_len=512, attend=256)
+        start = rng.integers(0, cfg.vocab, nb).astype(np.int32)
+        dec.reset(start)
+        dlg, dam = dec.capture()
+        dec.reset(start)
+        l0 = eng.device_traffic().launches
+        dec.replay()
+        dper = eng.device_traffic().launches - l0
+        dms = timed(dec.replay, reps=64, warm=4)          # positions 1..69 of the 256 attended
+        toks = dec.generated(0, 69)
+        eng.release_trace(dec.trace); eng.free(dlg); eng.free(dam)
+        res[f"smollm2_135m_decode_step_batch{nb}"] = {"ms_per_step": dms, "tok_per_s": nb / (dms * 1e-3), "launches_per_step": int(dper),
+                                                     "mode": "traced (one CUDA graph replay a token, nothing read back between steps)",
+                                                     "attended_positions": 256, "distinct_tokens_generated": int(len(np.unique(toks)))}
     bh, t, d = 256, 2048, 128
     bf = lambda: ((rng.standard_normal((bh * t, d), dtype=np.float32)).view(np.uint32) >> 16).astype(np.uint16)
     q, k, v = (eng.upload_bf16(bf(), bh * t, d) for _ in range(3))
@@ -455,6 +471,26 @@ def callers(eng, timed):
         eng.free(o)
     fms = timed(att_fused, reps=5, warm=2)
     res["attention_16x16x2048x128"].update({"fused_ms": fms, "fused_tflops": 2 * 2.0 * bh * t * t * d / fms / 1e9})
+    # decode attention (`attention_rows`): 256 heads, one query row each, on 256 key/value heads of [4096, 128]
+    from metalium_rs_b200 import BOOL
+    for name, heads, kvh in (("attention_rows_256x4096x128_bf16", 256, 256), ("attention_rows_gqa4_512x4096x128_bf16", 512, 128)):
+        l, dd = 4096, 128
+        kb = ((rng.standard_normal((kvh * l, dd), dtype=np.float32)).view(np.uint32) >> 16).astype(np.uint16)
+        dq = eng.upload(rng.standard_normal((heads, dd), dtype=np.float32), heads, dd)
+        dk, dv_ = eng.upload_bf16(kb, kvh * l, dd), eng.upload_bf16(kb, kvh * l, dd)
+        dm = eng.upload_bits(np.zeros(l, np.uint32), 1, l, BOOL)
+        rep = heads // kvh
+        heads_list = eng.attention_item_array([((h, 0), ((h // rep) * l, 0), ((h // rep) * l, 0)) for h in range(heads)])
+
+        def dec():
+            o, _ = eng.attention_rows([dq, dk, dv_, dm], heads_list, [1, dd, l, dd], 0.088)
+            eng.free(o)
+        dms = timed(dec, reps=10, warm=3)
+        byts = 2 * kvh * l * dd * 2
+        res[name] = {"ms": dms, "gbs_of_k_and_v_once": byts / dms / 1e6,
+                     "frac_of_measured_hbm": byts / dms / 1e6 / float(peaks()[0].get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))}
+        for i in (dq, dk, dv_, dm):
+            eng.free(i)
     for i in (q, k, v, x, y, ids):
         eng.free(i)
     return res

@@ -223,6 +223,15 @@ int32_t b200_assign_rows(b200_engine*, b200_buffer t, b200_buffer value, const u
                          uint64_t n, b200_buffer* out, uint64_t out_dims[2]);
 int32_t b200_scatter_rows(b200_engine*, b200_buffer table, b200_buffer indices, b200_buffer values,
                           int32_t column, b200_buffer* out, uint64_t out_dims[2]);
+/* `scatter_rows_into` (server.rs:389): `scatter_rows` into `table` itself -- a KV cache's step
+ * write.  values is a [n, table cols] block of a buffer of the table's type (F32, I32 or BF16). */
+int32_t b200_scatter_rows_into(b200_engine*, b200_buffer table, b200_buffer indices, const b200_block_arg* values,
+                               int32_t column);
+/* The same words seen as another [rows, cols] (rows * cols unchanged): a view, no copy, the parent
+ * kept alive as `slice_rows` keeps it.  burn-tt reshapes contiguous tensors above the trait
+ * (`views::Strided`); a caller of this ABI needs it to hand `attention_rows`' result row to a
+ * product as [tokens, heads * dv]. */
+int32_t b200_reshape(b200_engine*, b200_buffer a, uint64_t rows, uint64_t cols, b200_buffer* out, uint64_t out_dims[2]);
 int32_t b200_gather_indexed(b200_engine*, b200_buffer input, b200_buffer indices, b200_buffer* out, uint64_t out_dims[2]);
 /* `gather_rows(sources, rows:[(source, row)], cols)` */
 int32_t b200_gather_rows(b200_engine*, const b200_buffer* sources, uint64_t n_sources,

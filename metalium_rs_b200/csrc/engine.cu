@@ -1171,6 +1171,40 @@ int32_t b200_scatter_rows(b200_engine* e, b200_buffer table, b200_buffer indices
   return B200_OK;
 }
 
+int32_t b200_scatter_rows_into(b200_engine* e, b200_buffer table, b200_buffer indices, const b200_block_arg* values, int32_t column) {
+  cudaSetDevice(e->device);
+  Buf *T = nullptr, *I = nullptr, *V = nullptr;
+  int st = e->need(table, &T, "scatter_rows_into");
+  if (!st) st = index_buf(e, indices, &I, "scatter_rows_into");
+  if (!st) st = e->need(values->id, &V, "scatter_rows_into");
+  if (st) return st;
+  const uint64_t n = I->rows * I->cols;
+  if ((column ? I->cols : I->rows) != 1 || V->elem != T->elem || values->dims[0] != n || values->dims[1] != T->cols ||
+      values->at[0] + values->dims[0] > V->rows || values->at[1] + values->dims[1] > V->cols)
+    return e->fail(B200_UNSUPPORTED, "scatter_rows_into: shapes do not meet");
+  const int eb = (int)elem_bytes(T->elem);
+  const char* vp = (const char*)V->ptr + (values->at[0] * V->cols + values->at[1]) * eb;
+  return e->launched(launch_scatter_rows_into(T->ptr, T->rows, T->cols, eb, (const int32_t*)I->ptr, n, vp, V->cols, e->d_err, e->stream),
+                     "scatter_rows_into");
+}
+
+int32_t b200_reshape(b200_engine* e, b200_buffer a, uint64_t rows, uint64_t cols, b200_buffer* out, uint64_t out_dims[2]) {
+  Buf* A = nullptr;
+  int st = e->need(a, &A, "reshape");
+  if (st) return st;
+  if (rows * cols != A->rows * A->cols)
+    return e->fail(B200_UNSUPPORTED, "reshape: [%llu, %llu] as [%llu, %llu]", (unsigned long long)A->rows, (unsigned long long)A->cols,
+                   (unsigned long long)rows, (unsigned long long)cols);
+  Buf v;
+  v.ptr = A->ptr;
+  v.rows = rows; v.cols = cols; v.elem = A->elem; v.parent = a;
+  A->views++;
+  *out = e->next_id++;
+  e->bufs.emplace(*out, v);
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
+}
+
 int32_t b200_gather_indexed(b200_engine* e, b200_buffer input, b200_buffer indices, b200_buffer* out, uint64_t out_dims[2]) {
   cudaSetDevice(e->device);
   Buf *X = nullptr, *I = nullptr;

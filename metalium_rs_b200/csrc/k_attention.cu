@@ -28,18 +28,19 @@ namespace {
 constexpr int THREADS = 256;
 constexpr int WARPS = THREADS / 32;
 
-template <typename KV> struct Unit;   // a 16-byte piece of a row
+// A 16-byte piece of a row: loaded raw (it waits in four registers) and widened where it is used.
+template <typename KV> struct Unit;
 template <> struct Unit<float> {
   static constexpr int N = 4;
-  static __device__ __forceinline__ void load(const float* p, float* f) {
-    const float4 w = __ldg(reinterpret_cast<const float4*>(p));
-    f[0] = w.x; f[1] = w.y; f[2] = w.z; f[3] = w.w;
+  static __device__ __forceinline__ uint4 load(const float* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+  static __device__ __forceinline__ void widen(const uint4& w, float* f) {
+    f[0] = __uint_as_float(w.x); f[1] = __uint_as_float(w.y); f[2] = __uint_as_float(w.z); f[3] = __uint_as_float(w.w);
   }
 };
 template <> struct Unit<uint16_t> {
   static constexpr int N = 8;
-  static __device__ __forceinline__ void load(const uint16_t* p, float* f) {
-    const uint4 w = __ldg(reinterpret_cast<const uint4*>(p));
+  static __device__ __forceinline__ uint4 load(const uint16_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+  static __device__ __forceinline__ void widen(const uint4& w, float* f) {
     f[0] = __uint_as_float(w.x << 16); f[1] = __uint_as_float(w.x & 0xffff0000u);
     f[2] = __uint_as_float(w.y << 16); f[3] = __uint_as_float(w.y & 0xffff0000u);
     f[4] = __uint_as_float(w.z << 16); f[5] = __uint_as_float(w.z & 0xffff0000u);
@@ -64,7 +65,7 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float* sh) {
 
 // grid (splits, jobs).  Shared memory: q [RT][d], s [RT][lc], red [slices][dv or less].
 template <typename KV, int RT>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, RT >= 8 ? 2 : (RT >= 4 ? 3 : 4))
 attention_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, uint64_t k_ld, const KV* __restrict__ v,
                       uint64_t v_ld, const uint32_t* __restrict__ mask, const AttnJob* __restrict__ jobs,
                       const AttnRow* __restrict__ rows, int d, int l, int dv, int lc, float scale,
@@ -100,26 +101,31 @@ attention_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, uin
 #pragma unroll
       for (int r = 0; r < RT; ++r) { acc[r][0] = 0.f; acc[r][1] = 0.f; }
       for (int sb = 0; sb < steps; sb += 4) {
-        float x[4][2 * UN];
+        uint4 raw[4][2];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           if (sb + u < steps) {
-            Unit<KV>::load(kr + (sb + u) * 2 * UN, x[u]);
-            Unit<KV>::load(kr + (sb + u) * 2 * UN + UN, x[u] + UN);
+            raw[u][0] = Unit<KV>::load(kr + (sb + u) * 2 * UN);
+            raw[u][1] = Unit<KV>::load(kr + (sb + u) * 2 * UN + UN);
           }
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           if (sb + u < steps) {
-            const float* qp = qs + (sb + u) * 2 * UN;
 #pragma unroll
-            for (int r = 0; r < RT; ++r) {
+            for (int hf = 0; hf < 2; ++hf) {
+              float x[UN];
+              Unit<KV>::widen(raw[u][hf], x);
+              const float* qp = qs + (sb + u) * 2 * UN + hf * UN;
 #pragma unroll
-              for (int e4 = 0; e4 < 2 * UN; e4 += 4) {
-                const float4 qq = *reinterpret_cast<const float4*>(qp + (size_t)r * d + e4);
-                float& a = acc[r][(e4 >> 2) & 1];
-                a = fmaf(x[u][e4], qq.x, a); a = fmaf(x[u][e4 + 1], qq.y, a);
-                a = fmaf(x[u][e4 + 2], qq.z, a); a = fmaf(x[u][e4 + 3], qq.w, a);
+              for (int r = 0; r < RT; ++r) {
+#pragma unroll
+                for (int e4 = 0; e4 < UN; e4 += 4) {
+                  const float4 qq = *reinterpret_cast<const float4*>(qp + (size_t)r * d + e4);
+                  float& a = acc[r][(UN == 4 ? hf : (e4 >> 2)) & 1];
+                  a = fmaf(x[e4], qq.x, a); a = fmaf(x[e4 + 1], qq.y, a);
+                  a = fmaf(x[e4 + 2], qq.z, a); a = fmaf(x[e4 + 3], qq.w, a);
+                }
               }
             }
           }
@@ -179,21 +185,23 @@ attention_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, uin
       if (mine) {
         const KV* vb = v + job.v_off + (uint64_t)j0 * v_ld + c;
         for (int j = sl; j < n; j += nsl * 4) {
-          float x[4][UN];
+          uint4 raw[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int jj = j + u * nsl;
-            if (jj < n) Unit<KV>::load(vb + (uint64_t)jj * v_ld, x[u]);
+            if (jj < n) raw[u] = Unit<KV>::load(vb + (uint64_t)jj * v_ld);
           }
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int jj = j + u * nsl;
             if (jj < n) {
+              float x[UN];
+              Unit<KV>::widen(raw[u], x);
 #pragma unroll
               for (int r = 0; r < RT; ++r) {
                 const float p = s[(size_t)r * lc + jj];
 #pragma unroll
-                for (int e = 0; e < UN; ++e) acc[r][e] = fmaf(p, x[u][e], acc[r][e]);
+                for (int e = 0; e < UN; ++e) acc[r][e] = fmaf(p, x[e], acc[r][e]);
               }
             }
           }

@@ -36,7 +36,7 @@ constexpr int SOFTMAX_THREADS = 256;
 
 struct AttnTcParams {
   const AttnBlockDev* items;
-  uint32_t q_tiles, k_tiles;
+  uint32_t q_tiles, k_tiles, n_items;
   int32_t causal, causal_off;   // a query i sees keys j <= i + causal_off
   float scale_log2;             // scale * log2(e)
   uint16_t* out;
@@ -109,8 +109,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   // Heaviest work first: under a causal mask a block's last query tile has the most keys, so the grid
   // runs every block's last tile, then every block's tile before it, ... (the block index is the
   // fastest-varying one), and the short tiles fill the SMs the long ones leave.
-  const uint32_t qt = p.q_tiles - 1 - blockIdx.y;
-  const AttnBlockDev it = p.items[blockIdx.x];
+  // Without a mask every tile costs the same and a block's query tiles run side by side, sharing its
+  // K and V in L2.
+  const uint32_t qt = p.causal ? p.q_tiles - 1 - blockIdx.x / p.n_items : blockIdx.x % p.q_tiles;
+  const AttnBlockDev it = p.items[p.causal ? blockIdx.x % p.n_items : blockIdx.x / p.q_tiles];
   const int32_t i0 = (int32_t)(qt * 128);
   uint32_t nk = p.k_tiles;
   if (p.causal) {
@@ -341,7 +343,7 @@ cudaError_t launch_d(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
     if (e != cudaSuccess) return e;
     set = true;
   }
-  attention_tc_kernel<D><<<dim3((unsigned)n_items, p.q_tiles, 1), ATTN_THREADS, smem, stream>>>(mq, mk, mv, p);
+  attention_tc_kernel<D><<<dim3((unsigned)(n_items * p.q_tiles), 1, 1), ATTN_THREADS, smem, stream>>>(mq, mk, mv, p);
   return cudaGetLastError();
 }
 
@@ -362,7 +364,7 @@ cudaError_t launch_attention_tc(const void* q, uint64_t q_rows, uint64_t q_cols,
                                 const AttnBlockDev* items, uint64_t n_items, uint64_t sq, uint64_t d, uint64_t sk,
                                 float scale, int causal, void* out, uint64_t o_ld, int* err, cudaStream_t stream) {
   if (n_items == 0) return cudaSuccess;
-  if (n_items > 0x7fffffffull || sq / 128 > 65535) return cudaErrorNotSupported;
+  if (n_items * (sq / 128) > 0x7fffffffull) return cudaErrorNotSupported;
   CUtensorMap mq, mk, mv;
   if (!tc::make_map(&mq, q, q_rows, q_cols, q_cols, 128) || !tc::make_map(&mk, k, k_rows, k_cols, k_cols, 128) ||
       !tc::make_map(&mv, v, v_rows, v_cols, v_cols, 128))
@@ -371,6 +373,7 @@ cudaError_t launch_attention_tc(const void* q, uint64_t q_rows, uint64_t q_cols,
   p.items = items;
   p.q_tiles = (uint32_t)(sq / 128);
   p.k_tiles = (uint32_t)(sk / 128);
+  p.n_items = (uint32_t)n_items;
   p.causal = causal ? 1 : 0;
   p.causal_off = (int32_t)(sk - sq);
   p.scale_log2 = scale * 1.4426950408889634f;

@@ -86,6 +86,22 @@ scatter_rows_kernel(uint32_t* out, uint64_t t_rows, uint64_t cols, const int32_t
   }
 }
 
+// scatter_rows into the table itself (server.rs:389): table[idx[i], :] = the block's row i, for a
+// table of 16- or 32-bit elements and values that are a block of a wider buffer.  A thread a
+// column, the rows in order, so the last assignment to a row wins whatever the launch.
+template <typename E>
+__global__ void __launch_bounds__(128)
+scatter_rows_into_kernel(E* table, uint64_t t_rows, uint64_t cols, const int32_t* idx, uint64_t n,
+                         const E* values, uint64_t v_ld, int* err) {
+  const uint64_t c = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  for (uint64_t i = 0; i < n; ++i) {
+    const int64_t r = idx[i];
+    if (r < 0 || (uint64_t)r >= t_rows) { if (c == 0) set_err(err, DOMAIN); continue; }
+    table[(uint64_t)r * cols + c] = values[i * v_ld + c];
+  }
+}
+
 // out[r, j] = x[r, idx[r, j]]  (Burn's gather along the last dim)
 __global__ void gather_indexed_kernel(const uint32_t* x, uint64_t rows, uint64_t cols, const int32_t* idx,
                                       uint64_t i_cols, uint32_t* out, int* err) {
@@ -198,6 +214,16 @@ cudaError_t launch_scatter_rows(uint32_t* out, uint64_t t_rows, uint64_t cols, c
                                 uint64_t n, const uint32_t* values, int* err, cudaStream_t s) {
   if (n == 0 || cols == 0) return cudaSuccess;
   scatter_rows_kernel<<<(unsigned)((cols + 127) / 128), 128, 0, s>>>(out, t_rows, cols, idx, n, values, err);
+  return cudaGetLastError();
+}
+cudaError_t launch_scatter_rows_into(void* table, uint64_t t_rows, uint64_t cols, int elem_bytes, const int32_t* idx,
+                                     uint64_t n, const void* values, uint64_t v_ld, int* err, cudaStream_t s) {
+  if (n == 0 || cols == 0) return cudaSuccess;
+  const unsigned grid = (unsigned)((cols + 127) / 128);
+  if (elem_bytes == 2)
+    scatter_rows_into_kernel<uint16_t><<<grid, 128, 0, s>>>((uint16_t*)table, t_rows, cols, idx, n, (const uint16_t*)values, v_ld, err);
+  else
+    scatter_rows_into_kernel<uint32_t><<<grid, 128, 0, s>>>((uint32_t*)table, t_rows, cols, idx, n, (const uint32_t*)values, v_ld, err);
   return cudaGetLastError();
 }
 cudaError_t launch_gather_indexed(const uint32_t* x, uint64_t rows, uint64_t cols, const int32_t* idx,

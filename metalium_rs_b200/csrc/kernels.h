@@ -94,6 +94,8 @@ cudaError_t launch_attention_tc(const void* q, uint64_t q_rows, uint64_t q_cols,
                                 uint64_t k_cols, const void* v, uint64_t v_rows, uint64_t v_cols,
                                 const AttnBlockDev* items, uint64_t n_items, uint64_t sq, uint64_t d, uint64_t sk,
                                 float scale, int causal, void* out, uint64_t o_ld, int* err, cudaStream_t stream);
+cudaError_t launch_scatter_rows_into(void* table, uint64_t t_rows, uint64_t cols, int elem_bytes, const int32_t* idx,
+                                     uint64_t n, const void* values, uint64_t v_ld, int* err, cudaStream_t);
 struct MoveDev { uint64_t from_r, from_c, to_r, to_c, rows, cols; int32_t transposed; int32_t pad; };
 cudaError_t launch_copy_blocks(const void* src, uint64_t src_ld, void* dst, uint64_t dst_ld,
                                int elem_bytes, const MoveDev* moves_dev, uint64_t n_moves,

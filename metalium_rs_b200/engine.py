@@ -427,6 +427,17 @@ class CudaEngine:
         return self._call(self._lib.b200_scatter_rows, C.c_uint64(table), C.c_uint64(indices), C.c_uint64(values),
                           C.c_int32(column))
 
+    def scatter_rows_into(self, table: int, indices: int, values, column: bool = False):
+        """`scatter_rows` into `table` itself (server.rs:389); values = (buffer, (row, col), (rows, cols))."""
+        vid, at, dims = values
+        blk = BlockArg(vid, (C.c_uint64 * 2)(*at), (C.c_uint64 * 2)(*dims))
+        self._check(self._lib.b200_scatter_rows_into(self._e, C.c_uint64(table), C.c_uint64(indices), C.byref(blk),
+                                                     C.c_int32(column)))
+
+    def reshape(self, a: int, rows: int, cols: int) -> Out:
+        """The same words as another [rows, cols]: a view (no copy)."""
+        return self._call(self._lib.b200_reshape, C.c_uint64(a), C.c_uint64(rows), C.c_uint64(cols))
+
     def gather_indexed(self, input: int, indices: int) -> Out:
         return self._call(self._lib.b200_gather_indexed, C.c_uint64(input), C.c_uint64(indices))
 

@@ -256,6 +256,11 @@ impl Engine for CudaEngine {
     fn scatter_rows(&mut self, t: BufferId, idx: BufferId, v: BufferId, column: bool) -> Made {
         produce!(self, b200_scatter_rows(t, idx, v, column as i32))
     }
+    fn scatter_rows_into(&mut self, t: BufferId, idx: BufferId, v: BlockArg, column: bool) -> Result<(), TtError> {
+        let b = sys::b200_block_arg { id: v.id, at: [v.at[0] as u64, v.at[1] as u64], dims: [v.dims[0] as u64, v.dims[1] as u64] };
+        let st = unsafe { sys::b200_scatter_rows_into(self.raw, t, idx, &b, column as i32) };
+        self.check(st)
+    }
     fn rows_add(&mut self, t: BufferId, indices: &[usize], v: BufferId) -> Made {
         let i: Vec<u64> = indices.iter().map(|&x| x as u64).collect();
         produce!(self, b200_rows_add(t, i.as_ptr(), i.len() as u64, v))

@@ -295,3 +295,142 @@ def attention_fused(eng, q_buf: int, k_buf: int, v_buf: int, batch_heads: int, t
     if items is None:
         items = eng.attention_block_array([((i * t, 0), (i * t, 0), (i * t, 0), (i * t, 0)) for i in range(batch_heads)])
     return eng.attention_blocks(q_buf, k_buf, v_buf, items, (t, d, t, d), 1.0 / float(np.sqrt(d)), False, (batch_heads * t, d))[0]
+
+
+# ------------------------------------------------------------------------- generation (decode steps)
+def _int_scalar(v: int) -> float:
+    """An integer kind's scalar travels as the bits of the op's F32 scalar field (tensor.rs:3785)."""
+    return float(np.array([v], dtype=np.int32).view(np.float32)[0])
+
+
+class LlamaDecode:
+    """Token-by-token generation with a fixed-shape key/value cache, as the reference traces it
+    (crates/tt-models/src/kv_cache.rs:1-30, generate.rs:781): `batch` sequences advance in lockstep, one
+    token each a step.  A layer's cache is position-major, [batch * max_len, kv_heads * head_dim] BF16:
+    a step writes its projection's rows as they are (`scatter_rows_into`, server.rs:389) and attention
+    reads each head's column block in place (`attention_rows`, server.rs:257), the positions later than
+    the step's masked.  The position is a device tensor, so one captured step serves every position:
+    the step derives its cache rows, its RoPE rows and its mask from `pos`, and at its end advances
+    `pos`, feeds its argmax back as the next ids and records it in `tokens` -- a generation is then
+    one replay a token with nothing read back until the end.
+
+    `weights_dev`: the device weights of a `LlamaPrefill` (shared, not copied)."""
+
+    def __init__(self, eng, cfg: LlamaConfig, weights_dev: Dict[str, int], batch: int, max_len: int, attend: int = 0):
+        assert max_len % 32 == 0 and cfg.head_dim % 32 == 0
+        self.eng, self.cfg, self.batch, self.max_len = eng, cfg, batch, max_len
+        self.attend = attend or max_len                  # positions attention reads (kv_cache.rs:195-199)
+        assert self.attend % 32 == 0 and self.attend <= max_len
+        self.w = weights_dev
+        c = cfg
+        self.q_cols, self.kv_cols = c.heads * c.head_dim, c.kv_heads * c.head_dim
+        cos, sin = rope_tables(max_len, c.head_dim, c.theta)
+        self.cos, self.sin = eng.upload(cos, *cos.shape), eng.upload(sin, *sin.shape)
+        z = lambda: eng.zeros_dram((batch * max_len, self.kv_cols), bf16=True)[0]
+        self.kc = [z() for _ in range(c.layers)]
+        self.vc = [z() for _ in range(c.layers)]
+        i32 = lambda a, r, k: eng.upload_bits(np.ascontiguousarray(a, dtype=np.int32).view(np.uint32), r, k, I32)
+        self.positions = i32(np.arange(self.attend), 1, self.attend)
+        self.row_base = i32(np.arange(batch) * max_len, 1, batch)
+        self.pos = i32([0], 1, 1)                        # the step's position: a device tensor
+        self.ids = i32(np.zeros(batch), batch, 1)
+        self.tokens = i32(np.zeros((max_len, batch)), max_len, batch)
+        group = c.heads // c.kv_heads
+        hd = c.head_dim
+        self.items = eng.attention_item_array(
+            [((b, h * hd), (b * max_len, (h // group) * hd), (b * max_len, (h // group) * hd))
+             for b in range(batch) for h in range(c.heads)])
+        self.trace = None
+
+    def reset(self, ids: np.ndarray, position: int = 0):
+        """Start (or restart) at `position` with these ids ([batch] I32) as the next input."""
+        e = self.eng
+        fresh = e.upload_bits(np.ascontiguousarray(ids, dtype=np.int32).reshape(self.batch, 1).view(np.uint32), self.batch, 1, I32)
+        p = e.upload_bits(np.array([[position]], np.int32).view(np.uint32), 1, 1, I32)
+        e.copy_into(fresh, self.ids); e.copy_into(p, self.pos)
+        e.free(fresh); e.free(p)
+
+    def set_ids(self, ids: np.ndarray):
+        """Overwrite the next input ids (teacher forcing); the position is untouched."""
+        e = self.eng
+        fresh = e.upload_bits(np.ascontiguousarray(ids, dtype=np.int32).reshape(self.batch, 1).view(np.uint32), self.batch, 1, I32)
+        e.copy_into(fresh, self.ids)
+        e.free(fresh)
+
+    def step(self):
+        """One token a sequence at `pos`.  Returns (logits [batch, vocab] F32, argmax [batch, 1] I32); the
+        caller frees both.  Advances `pos`, feeds the argmax back into `ids` and records it in `tokens`."""
+        e, c, K = self.eng, self.cfg, kinds
+        B, hd = self.batch, c.head_dim
+        op = lambda kind, a, b=None, s1=0.0: e.eltwise_op(EltwiseOp(kind, s1, 0.0), a, b)[0]
+        rows = op(K.INT_ADD, self.row_base, self.pos)                         # each sequence's cache row
+        later = op(K.INT_GT, self.positions, self.pos)                        # kv_cache.rs:216-224 `later`
+        cs, _ = e.select_rows(self.cos, self.pos)                             # the position's RoPE row
+        sn, _ = e.select_rows(self.sin, self.pos)
+        emb, _ = e.select_rows(self.w["embed"], self.ids)
+        x, _ = e.cast_float(emb, False)
+        e.free(emb)
+        n1, _ = e.rms_norm_as(x, self.w["l0.norm1"], c.eps, True)
+        scale = 1.0 / float(np.sqrt(hd))
+        for l in range(c.layers):
+            qkv, _ = e.matmul_dram_bf16(n1, False, self.w[f"l{l}.qkv"], False)
+            e.free(n1)
+            q, _ = e.rope_blocks((qkv, (0, 0), (B, self.q_cols)), (cs, (0, 0), (1, hd)), (sn, (0, 0), (1, hd)), hd, False)
+            k, _ = e.rope_blocks((qkv, (0, self.q_cols), (B, self.kv_cols)), (cs, (0, 0), (1, hd)), (sn, (0, 0), (1, hd)), hd, True)
+            e.scatter_rows_into(self.kc[l], rows, (k, (0, 0), (B, self.kv_cols)))
+            e.scatter_rows_into(self.vc[l], rows, (qkv, (0, self.q_cols + self.kv_cols), (B, self.kv_cols)))
+            e.free(k); e.free(qkv)
+            att, _ = e.attention_rows([q, self.kc[l], self.vc[l], later], self.items, [1, hd, self.attend, hd], scale)
+            e.free(q)
+            rows_view, _ = e.reshape(att, B, self.q_cols)                     # [1, B heads hd] as [B, heads hd]
+            attb, _ = e.cast_float(rows_view, True)
+            e.free(rows_view); e.free(att)
+            o, _ = e.matmul_dram(attb, False, self.w[f"l{l}.o"], False)
+            e.free(attb)
+            (x2, _), (n2, _) = e.add_rms_norm_as(x, o, self.w[f"l{l}.norm2"], c.eps, True)
+            e.free(x); e.free(o)
+            gu, _ = e.matmul_dram_bf16(n2, False, self.w[f"l{l}.gate_up"], False)
+            e.free(n2)
+            act, _ = e.eltwise_blocks_as(EltwiseOp(K.SILU_MUL, 0.0, 0.0), (gu, (0, 0), (B, c.ff)),
+                                         (gu, (0, c.ff), (B, c.ff)), None, True)
+            e.free(gu)
+            d, _ = e.matmul_dram(act, False, self.w[f"l{l}.down"], False)
+            e.free(act)
+            nxt = self.w[f"l{l + 1}.norm1"] if l + 1 < c.layers else self.w["final_norm"]
+            (x, _), (n1, _) = e.add_rms_norm_as(x2, d, nxt, c.eps, True)
+            e.free(x2); e.free(d)
+        e.free(x)
+        logits, _ = e.matmul_dram(n1, False, self.w["embed"], True)          # tied head
+        e.free(n1)
+        am, _ = e.argmax_row(logits)
+        # record, feed back, advance
+        am_row, _ = e.reshape(am, 1, B)
+        e.scatter_rows_into(self.tokens, self.pos, (am_row, (0, 0), (1, B)))
+        e.free(am_row)
+        e.copy_into(am, self.ids)
+        nxt_pos = op(K.INT_ADD_S, self.pos, None, _int_scalar(1))
+        e.copy_into(nxt_pos, self.pos)
+        for i in (nxt_pos, rows, later, cs, sn):
+            e.free(i)
+        return logits, am
+
+    def capture(self):
+        """One eager step (so every kernel is loaded and every block list is on the device), the
+        position put back, then the step captured.  Returns the (logits, argmax) buffers a replay rewrites."""
+        e = self.eng
+        lg, am = self.step()
+        e.free(lg); e.free(am)
+        back = e.eltwise_op(EltwiseOp(kinds.INT_SUB_S, _int_scalar(1), 0.0), self.pos, None)[0]
+        e.copy_into(back, self.pos)
+        e.free(back)
+        e.begin_trace()
+        out = self.step()
+        self.trace = e.end_trace()
+        return out
+
+    def replay(self):
+        self.eng.run_trace(self.trace)
+
+    def generated(self, first: int, count: int) -> np.ndarray:
+        """The tokens recorded at positions first .. first + count - 1: [count, batch] I32."""
+        return self.eng.download_bits(self.tokens).view(np.int32)[first:first + count]

@@ -51,6 +51,7 @@ bool attention_tc_supported(uint64_t sq, uint64_t d, uint64_t sk, uint64_t dv, f
 cudaError_t launch_attention_tc(const void*, uint64_t, uint64_t, const void*, uint64_t, uint64_t, const void*, uint64_t, uint64_t,
                                 const AttnBlockDev*, uint64_t, uint64_t, uint64_t, uint64_t, float, int, void*, uint64_t, int*,
                                 cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_scatter_rows_into(void*, uint64_t, uint64_t, int, const int32_t*, uint64_t, const void*, uint64_t, int*, cudaStream_t) { OK_LAUNCH; }
 cudaError_t launch_gemm_simt(const GemmArgs&, cudaStream_t) { OK_LAUNCH; }
 bool gemm_tc_supported(const GemmArgs& g, const char** why) {
   *why = g.in_bf16 ? "the fake runtime was told to refuse" : "operands are not BF16";

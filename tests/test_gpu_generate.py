@@ -1,0 +1,132 @@
+"""Generation with a fixed-shape key/value cache: `scatter_rows_into` (crates/burn-tt/src/server.rs:389), the
+reshape view, and decode steps (`attention_rows` over the cache) against the prefill of the same tokens
+and against the CPU restatement.  What a cached step must equal is what the reference holds its own to
+(crates/tt-models/src/kv_cache.rs:16-19, `step185_fixed_decode`): the growing-cache arithmetic, a masked
+position adding an exact zero.  Tolerance: the logits' 2e-2 of the prefill test (BF16 weights and
+activations; the two paths round their probabilities differently)."""
+import numpy as np
+import pytest
+
+from metalium_rs_b200 import BF16, F32, I32, TtError, workloads as W
+from oracle import models as M
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _i32(eng, a, r, c):
+    return eng.upload_bits(np.ascontiguousarray(a, dtype=np.int32).view(np.uint32), r, c, I32)
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_scatter_rows_into_writes_the_table_itself(eng, bf16):
+    table = orc.normal(0x6E, 1, (40, 24))
+    values = orc.normal(0x6E, 2, (6, 64))            # the rows written are columns 16..40 of rows 1..5
+    idx = np.array([[3, 39, 0, 3]], np.int32)        # row 3 twice: the later one stays
+    if bf16:
+        tb, vb = orc.to_bf16(table), orc.to_bf16(values)
+        it, iv = eng.upload_bf16(tb, 40, 24), eng.upload_bf16(vb, 6, 64)
+        want = tb.copy()
+        src = vb
+    else:
+        it, iv = eng.upload(table, 40, 24), eng.upload(values, 6, 64)
+        want = table.copy()
+        src = values
+    ii = _i32(eng, idx, 1, 4)
+    eng.scatter_rows_into(it, ii, (iv, (1, 16), (4, 24)))
+    for n, r in enumerate(idx[0]):
+        want[r] = src[1 + n, 16:40]
+    got = eng.download_bf16(it) if bf16 else eng.download(it)
+    assert np.array_equal(got, want)
+    assert eng.dims_of(it) == ((40, 24), BF16 if bf16 else F32)
+    with pytest.raises(TtError):
+        eng.scatter_rows_into(it, ii, (iv, (1, 16), (3, 24)))      # three rows for four indices
+    with pytest.raises(TtError):
+        eng.scatter_rows_into(it, ii, (iv, (4, 16), (4, 24)))      # the block leaves its buffer
+    for i in (it, iv, ii):
+        eng.free(i)
+
+
+def test_scatter_rows_into_reports_a_row_outside_the_table(fresh_eng):
+    e = fresh_eng
+    it, iv = e.upload(np.zeros((4, 8), np.float32), 4, 8), e.upload(np.ones((1, 8), np.float32), 1, 8)
+    ii = _i32(e, [[4]], 1, 1)
+    e.scatter_rows_into(it, ii, (iv, (0, 0), (1, 8)))
+    with pytest.raises(TtError) as err:
+        e.sync()
+    assert err.value.status == 6                     # DOMAIN, at the next wait
+
+
+def test_reshape_is_a_view_of_the_same_words(eng):
+    a = np.arange(48, dtype=np.float32).reshape(4, 12)
+    ia = eng.upload(a, 4, 12)
+    v, dims = eng.reshape(ia, 6, 8)
+    assert dims == (6, 8) and np.array_equal(eng.download(v), a.reshape(6, 8))
+    eng.free(ia)                                     # the view keeps the words alive
+    assert np.array_equal(eng.download(v), a.reshape(6, 8))
+    with pytest.raises(TtError):
+        eng.reshape(v, 5, 8)
+    eng.free(v)
+
+
+def small_llama():
+    return W.LlamaConfig(layers=3, hidden=576, heads=9, kv_heads=3, head_dim=64, ff=1536, vocab=2048)
+
+
+def test_cached_steps_equal_the_prefill_of_the_same_tokens(eng):
+    cfg = small_llama()
+    batch, t = 2, 32
+    w = W.llama_weights(cfg, seed=11)
+    ids = orc.integers(0x6E1, 9, (batch, t), cfg.vocab)
+    pre = W.LlamaPrefill(eng, cfg, w, batch, t)
+    assert not pre.fused                             # 32 tokens: the composed attention
+    ii = _i32(eng, ids.reshape(1, -1), 1, batch * t)
+    la, aa = pre.forward(ii, all_positions=True)
+    want = eng.download(la).reshape(batch, t, cfg.vocab)
+    dec = W.LlamaDecode(eng, cfg, pre.w, batch, max_len=64)
+    dec.reset(ids[:, 0])
+    worst, seen = 0.0, []
+    for step in range(t):
+        dec.set_ids(ids[:, step])
+        lg, am = dec.step()
+        got = eng.download(lg)
+        worst = max(worst, float(np.max(np.abs(got - want[:, step]))))
+        seen.append(eng.download_bits(am).view(np.int32).ravel().copy())
+        assert np.array_equal(seen[-1], got.argmax(1))
+        eng.free(lg); eng.free(am)
+    assert worst <= 2e-2, worst
+    assert np.array_equal(dec.generated(0, t), np.stack(seen))   # every step's choice was recorded at its position
+    # and the CPU restatement at the last position
+    wb = {k: orc.from_bf16(orc.to_bf16(v)) for k, v in w.items()}
+    cpu = M.llama_prefill(cfg, wb, ids.reshape(1, -1), batch, t)
+    assert np.max(np.abs(got - cpu)) <= 2e-2
+    for i in (ii, la, aa):
+        eng.free(i)
+
+
+def test_a_traced_generation_is_the_eager_one(eng):
+    cfg = small_llama()
+    batch, n = 2, 24
+    pre = W.LlamaPrefill(eng, cfg, W.llama_weights(cfg, seed=11), batch, 32)
+    first = np.array([5, 1999], np.int32)
+    eager = W.LlamaDecode(eng, cfg, pre.w, batch, max_len=64)
+    eager.reset(first)
+    toks = []
+    for _ in range(n):
+        lg, am = eager.step()
+        toks.append(eng.download_bits(am).view(np.int32).ravel().copy())
+        eng.free(lg); eng.free(am)
+    toks = np.stack(toks)
+    assert np.array_equal(eager.generated(0, n), toks)
+    traced = W.LlamaDecode(eng, cfg, pre.w, batch, max_len=64)
+    traced.reset(first)
+    lg, am = traced.capture()
+    traced.reset(first)                              # the capture's own eager step wrote position 0
+    l0 = eng.device_traffic().launches
+    for _ in range(n):
+        traced.replay()                              # nothing is read back between steps
+    assert eng.device_traffic().launches - l0 >= n * 12 * cfg.layers
+    assert np.array_equal(traced.generated(0, n), toks)
+    assert np.array_equal(eng.download_bits(am).view(np.int32).ravel(), toks[-1])
+    eng.release_trace(traced.trace)
+    eng.free(lg); eng.free(am)
