@@ -291,6 +291,9 @@ void    b200_release_trace(b200_engine*, uint64_t trace);
 /* --- waits and observability: lib.rs:218 `sync`, server.rs:584,663 --- */
 int32_t b200_sync(b200_engine*);
 void    b200_set_op_label(b200_engine*, const char* label);
+/* The tensor-core products of this engine use at most `sms` SMs from now on (0 = all): a caller that
+ * runs a collective beside a product (the sharded product's all-gather) leaves it SMs to run on. */
+void    b200_set_matmul_sm_limit(b200_engine*, int32_t sms);
 void    b200_traffic_get(const b200_engine*, b200_traffic* out);
 /* Device time of the ops launched between the two marks, in milliseconds
  * (CUDA events on the engine's stream).  `b200_timer_stop` is a wait. */

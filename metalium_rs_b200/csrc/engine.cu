@@ -51,6 +51,7 @@ struct b200_engine {
   cudaStream_t stream = nullptr;
   cudaEvent_t t0 = nullptr, t1 = nullptr;
   int* d_err = nullptr;
+  int matmul_sm_limit = 0;   // b200_set_matmul_sm_limit
   int* h_err = nullptr;  // pinned
   std::string last_error;
   uint64_t oom[3] = {0, 0, 0};
@@ -635,7 +636,13 @@ int32_t b200_write_bf16(b200_engine* e, b200_buffer id, const uint16_t* v, uint6
 // ---- products -------------------------------------------------------------------
 static int run_gemm(b200_engine* e, GemmArgs& g, const GemmBatch* batches_host, const char* what) {
   const char* why = "";
+  g.sm_limit = e->matmul_sm_limit;
   const bool want_tc = g.in_bf16 ? e->cfg.bf16_matmul_mode != 1 : e->cfg.f32_matmul_mode == 2;
+  // A handful of rows (a decode step): stream B once instead of a 128-row tile with a few live rows.
+  if (g.in_bf16 && e->cfg.bf16_matmul_mode == 0 && gemm_skinny_supported(g)) {
+    e->matmul_path = "skinny";
+    return e->launched(launch_gemm_skinny(g, e->stream), what);
+  }
   if (want_tc && gemm_tc_supported(g, &why)) {
     const cudaError_t ce = launch_gemm_tc(g, batches_host, e->d_err, e->stream);
     if (ce != cudaErrorNotSupported) {
@@ -1557,6 +1564,7 @@ void b200_release_trace(b200_engine* e, uint64_t trace) {
 // ---- waits and observability ---------------------------------------------------
 int32_t b200_sync(b200_engine* e) { cudaSetDevice(e->device); return e->wait(); }
 void b200_set_op_label(b200_engine* e, const char* label) { e->label = label ? label : ""; }
+void b200_set_matmul_sm_limit(b200_engine* e, int32_t sms) { e->matmul_sm_limit = sms > 0 ? sms : 0; }
 void b200_traffic_get(const b200_engine* e, b200_traffic* out) { *out = e->traffic; }
 int32_t b200_timer_start(b200_engine* e) {
   cudaSetDevice(e->device);

@@ -293,6 +293,7 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (g.sm_limit > 0 && g.sm_limit < sms) sms = g.sm_limit;
 
   const uint32_t tiles_m = (uint32_t)((g.m + BM - 1) / BM);
   // Tile width: 128, 192 or 256 columns.  A tile costs a fixed part (pipeline fill, epilogue: about

@@ -286,7 +286,8 @@ cudaError_t launch_gemm_tc2(const GemmArgs& g, int* err_word, cudaStream_t strea
       if (e != cudaSuccess || n <= 0) { cudaGetLastError(); return cudaErrorNotSupported; }           \
       clusters = n;                                                                                   \
     }                                                                                                 \
-    const uint64_t use = total < (uint64_t)clusters ? total : (uint64_t)clusters;                     \
+    uint64_t use = total < (uint64_t)clusters ? total : (uint64_t)clusters;                           \
+    if (g.sm_limit > 1 && use > (uint64_t)(g.sm_limit / 2)) use = (uint64_t)(g.sm_limit / 2);        \
     cfg.gridDim = dim3((unsigned)(2 * use), 1, 1);                                                    \
     e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<AM, BMJ>, ma, mb, p);                                \
   } while (0)

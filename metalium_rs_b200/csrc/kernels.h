@@ -118,6 +118,8 @@ struct GemmArgs {
   int a_trans, b_trans;    // stored matrix is the transpose of the logical operand
   uint64_t batch;          // 1, or number of products
   const GemmBatch* batches_dev;  // device array when batch > 1 (or nullptr for batch 1)
+  int sm_limit = 0;        // > 0: the tensor-core product uses at most this many SMs (the rest stay free for a
+                           // collective running beside it)
 };
 // SIMT (FFMA) path: any shape, any transposes, f32 or bf16 operands, f32 accumulate.
 cudaError_t launch_gemm_simt(const GemmArgs& g, cudaStream_t stream);
@@ -127,6 +129,10 @@ struct TcPlan;  // opaque: tensor maps + grid
 bool gemm_tc_supported(const GemmArgs& g, const char** why);
 cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int* err_word,
                            cudaStream_t stream);
+
+// A product of at most 8 rows (a decode step's projections): streams B once on CUDA cores.
+bool gemm_skinny_supported(const GemmArgs& g);
+cudaError_t launch_gemm_skinny(const GemmArgs& g, cudaStream_t stream);
 
 // CTA-pair (cta_group::2) variant of the BF16 tensor-core product, for one large product.
 bool gemm_tc2_wanted(const GemmArgs& g);

@@ -97,6 +97,7 @@ def _prepare(_lib: C.CDLL) -> C.CDLL:
         _lib.b200_engine_destroy.restype = None
         _lib.b200_free.restype = None
         _lib.b200_set_op_label.restype = None
+        _lib.b200_set_matmul_sm_limit.restype = None
         _lib.b200_traffic_get.restype = None
         _lib.b200_last_oom.restype = None
         _lib.b200_release_trace.restype = None
@@ -495,6 +496,10 @@ class CudaEngine:
         n = len(items)
         return self._call(self._lib.b200_attention_blocks, C.c_uint64(q), C.c_uint64(k), C.c_uint64(v), arr, C.c_uint64(n),
                           (C.c_uint64 * 4)(*dims), C.c_float(scale), C.c_int32(1 if causal else 0), (C.c_uint64 * 2)(*result_dims))
+
+    def set_matmul_sm_limit(self, sms: int):
+        """Tensor-core products use at most `sms` SMs (0 = all): room for a collective beside them."""
+        self._lib.b200_set_matmul_sm_limit(self._e, C.c_int32(sms))
 
     # -- traces (server.rs:591-660) ------------------------------------------------------------
     def begin_trace(self):

@@ -55,9 +55,16 @@ class ShardedMatmul:
     gathered [panel, rank, rows, per] blocks side by side as the row-major C."""
 
     def __init__(self, eng, rank: int, world: int, m: int, k: int, n: int, a_buf: int, b_slice_buf: int, bf16=True,
-                 panels: int = 4):
+                 panels: int = 0, comm_sms: int = -1):
+        """panels: row panels (0: B200TT_SHARD_PANELS or 8).  comm_sms: SMs the products leave free for
+        the all-gather running beside them (-1: B200TT_SHARD_COMM_SMS or 0).  Measured on four B200s at
+        16384^3: 8 panels 3,531 TFLOP/s against 3,321 with 4; leaving 16 or 32 SMs free made it slower
+        (3,097 and 3,212) -- NCCL's blocks share the SMs with the persistent product's mostly waiting
+        warps well enough -- so the default keeps every SM on the product."""
         import torch
         from . import BF16, F32
+        panels = panels or int(os.environ.get("B200TT_SHARD_PANELS", "8"))
+        comm_sms = comm_sms if comm_sms >= 0 else int(os.environ.get("B200TT_SHARD_COMM_SMS", "0"))
         self.eng, self.rank, self.world = eng, rank, world
         self.m, self.k, self.n = m, k, n
         self.parts = partition(n, world)
@@ -72,6 +79,8 @@ class ShardedMatmul:
         self.dt = torch.int16 if bf16 else torch.float32
         self.elem = BF16 if bf16 else F32
         dev = torch.device("cuda", torch.cuda.current_device())
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        self.sm_limit = max(2, sms - comm_sms) if (world > 1 and comm_sms > 0) else 0
         # torch owns the exchange buffer; the engine adopts it so its copy kernel reads it
         self.staged = torch.empty((panels * world * self.mp, self.per), dtype=self.dt, device=dev)
         self.staged_buf = eng.adopt(self.staged.data_ptr(), panels * world * self.mp, self.per, self.elem)
@@ -86,6 +95,7 @@ class ShardedMatmul:
         eng, g, mp = self.eng, self.world, self.mp
         mm = eng.matmul_dram_bf16 if self.bf16 else eng.matmul_dram
         pending = []
+        eng.set_matmul_sm_limit(self.sm_limit)
         with torch.cuda.stream(self.stream):
             for p in range(self.panels):
                 out, _ = mm(self.a_panels[p], False, self.b, False)
@@ -98,6 +108,7 @@ class ShardedMatmul:
             for work, out in pending:
                 work.wait()      # the engine's stream waits for the gather; the panel may then be reused
                 eng.free(out)
+        eng.set_matmul_sm_limit(0)
         full, _ = eng.copy_blocks(self.staged_buf, self.moves, (self.m, self.n))
         return full  # the caller frees it
 

@@ -234,6 +234,47 @@ def test_short_m_products_take_the_tensor_cores(eng, m):
         eng.free(i)
 
 
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("kn", [(576, 960), (576, 576), (576, 3072), (1536, 576), (100, 72), (5000, 8)])
+def test_a_handful_of_rows_streams_the_weights_once(eng, m, kn):
+    # a decode step's projections: [m, k] x [k, n], both as stored.  Same claims as the tensor-core path.
+    k, n = kn
+    a = orc.to_bf16(orc.uniform(0xC0F6, 1, (m, k), -1, 1))
+    b = orc.to_bf16(orc.uniform(0xC0F6, 2, (k, n), -1, 1))
+    ia, ib = eng.upload_bf16(a, m, k), eng.upload_bf16(b, k, n)
+    out, dims = eng.matmul_dram_bf16(ia, False, ib, False)
+    assert dims == (m, n) and eng.last_matmul_path() == "skinny"
+    want_bits, truth, s = orc.gemm_bf16(a, b, False, False)
+    got_bits = eng.download_bf16(out)
+    got = orc.from_bf16(got_bits)
+    assert np.all(np.abs(got.astype(np.float64) - truth) <= 2.0 ** -8 * np.abs(truth) + 1e-6 * s)
+    step = np.abs(got_bits.astype(np.int32) - want_bits.astype(np.int32))
+    assert (step <= 1).mean() > 0.999
+    o32, _ = eng.matmul_dram(ia, False, ib, False)
+    assert eng.last_matmul_path() == "skinny"
+    assert orc.gemm_rel_error(eng.download(o32), truth, s)[0] <= 1e-6
+    # nine rows, or a transposed operand, is the tensor cores' again
+    for i in (ia, ib, out, o32):
+        eng.free(i)
+
+
+def test_a_tensor_only_engine_never_takes_the_skinny_kernel(lib):
+    a = orc.to_bf16(orc.uniform(0xC0F6, 3, (4, 576), -1, 1))
+    b = orc.to_bf16(orc.uniform(0xC0F6, 4, (576, 576), -1, 1))
+    with CudaEngine(0, bf16_matmul_mode=2) as e:
+        ia, ib = e.upload_bf16(a, 4, 576), e.upload_bf16(b, 576, 576)
+        out, _ = e.matmul_dram_bf16(ia, False, ib, False)
+        assert e.last_matmul_path() == "tcgen05"
+        tc = e.download_bf16(out)
+    with CudaEngine(0) as e:
+        ia, ib = e.upload_bf16(a, 4, 576), e.upload_bf16(b, 576, 576)
+        out, _ = e.matmul_dram_bf16(ia, False, ib, False)
+        assert e.last_matmul_path() == "skinny"
+        sk = e.download_bf16(out)
+    step = np.abs(tc.astype(np.int32) - sk.astype(np.int32))
+    assert (step <= 1).all() and (step == 0).mean() > 0.98
+
+
 @pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
 @pytest.mark.parametrize("mkn", [(256, 256, 256), (384, 160, 512), (1024, 1024, 1024), (200, 132, 328)])
 def test_f32_products_on_the_split_tf32_tensor_path(lib, mkn, ta, tb):
