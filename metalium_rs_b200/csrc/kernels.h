@@ -130,7 +130,7 @@ bool gemm_tc_supported(const GemmArgs& g, const char** why);
 cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int* err_word,
                            cudaStream_t stream);
 
-// A product of at most 8 rows (a decode step's projections): streams B once on CUDA cores.
+// A product of at most 4 rows (a decode step's projections): streams B once on CUDA cores.
 bool gemm_skinny_supported(const GemmArgs& g);
 cudaError_t launch_gemm_skinny(const GemmArgs& g, cudaStream_t stream);
 

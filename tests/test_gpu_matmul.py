@@ -234,7 +234,7 @@ def test_short_m_products_take_the_tensor_cores(eng, m):
         eng.free(i)
 
 
-@pytest.mark.parametrize("m", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("m", [1, 2, 3, 4])
 @pytest.mark.parametrize("kn", [(576, 960), (576, 576), (576, 3072), (1536, 576), (100, 72), (5000, 8)])
 def test_a_handful_of_rows_streams_the_weights_once(eng, m, kn):
     # a decode step's projections: [m, k] x [k, n], both as stored.  Same claims as the tensor-core path.
@@ -253,7 +253,6 @@ def test_a_handful_of_rows_streams_the_weights_once(eng, m, kn):
     o32, _ = eng.matmul_dram(ia, False, ib, False)
     assert eng.last_matmul_path() == "skinny"
     assert orc.gemm_rel_error(eng.download(o32), truth, s)[0] <= 1e-6
-    # nine rows, or a transposed operand, is the tensor cores' again
     for i in (ia, ib, out, o32):
         eng.free(i)
 
