@@ -129,6 +129,9 @@ int32_t b200_write_bf16(b200_engine*, b200_buffer id, const uint16_t* values, ui
 /* --- products: server.rs:70,178,191,229,245 --- */
 /* `matmul` (host-staged, required by the trait): upload, matmul_dram, download. */
 int32_t b200_matmul_host(b200_engine*, const float* a, const float* b, const uint64_t mkn[3], float* out);
+/* The same for BF16 operands and a BF16 result (F32 accumulate), its copies overlapped with the product in
+ * row panels on two copy streams; returns when `out` is complete.  Pinned host memory gives the overlap. */
+int32_t b200_matmul_host_bf16(b200_engine*, const uint16_t* a, const uint16_t* b, const uint64_t mkn[3], uint16_t* out);
 /* `matmul_dram` / `matmul_dram_bf16`: C = op(A) op(B).  F32 operands give an F32
  * result; with out_bf16 the F32 accumulator is rounded once to BF16.  BF16
  * operands accumulate in F32. */

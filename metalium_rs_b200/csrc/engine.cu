@@ -51,6 +51,7 @@ struct b200_engine {
   cudaStream_t stream = nullptr;
   cudaEvent_t t0 = nullptr, t1 = nullptr;
   int* d_err = nullptr;
+  cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;   // b200_matmul_host_bf16's copy streams
   int matmul_sm_limit = 0;   // b200_set_matmul_sm_limit
   int* h_err = nullptr;  // pinned
   std::string last_error;
@@ -521,6 +522,8 @@ void b200_engine_destroy(b200_engine* e) {
   cudaFreeHost(e->h_err);
   cudaEventDestroy(e->t0);
   cudaEventDestroy(e->t1);
+  if (e->h2d_stream) cudaStreamDestroy(e->h2d_stream);
+  if (e->d2h_stream) cudaStreamDestroy(e->d2h_stream);
   cudaStreamDestroy(e->stream);
   delete e;
 }
@@ -726,6 +729,75 @@ int32_t b200_matmul_host(b200_engine* e, const float* a, const float* b, const u
   if (!st) st = b200_matmul(e, ia, 0, ib, 0, 0, &ic, d);
   if (!st) st = b200_download_f32(e, ic, out, mkn[0] * mkn[2]);
   b200_free(e, ia); b200_free(e, ib); b200_free(e, ic);
+  return st;
+}
+
+// The host-staged product for BF16 operands, with its copies overlapped: B goes up whole, then A
+// goes up, is multiplied and its rows of C come down in row panels, so the upload of panel p+1, the
+// product of panel p and the download of panel p-1 run at once (PCIe carries both directions).  Returns
+// when C is complete in `out`.  Pinned host memory gives the overlap; pageable memory still works.
+int32_t b200_matmul_host_bf16(b200_engine* e, const uint16_t* a, const uint16_t* b, const uint64_t mkn[3], uint16_t* out) {
+  cudaSetDevice(e->device);
+  if (e->capturing) return e->fail(B200_UNSUPPORTED, "matmul_host_bf16 inside a trace capture");
+  const uint64_t m = mkn[0], k = mkn[1], n = mkn[2];
+  if (m == 0 || n == 0) return B200_OK;
+  if (k == 0) { memset(out, 0, m * n * 2); return B200_OK; }
+  if (!e->h2d_stream) {
+    cudaError_t ce = cudaStreamCreateWithFlags(&e->h2d_stream, cudaStreamNonBlocking);
+    if (ce == cudaSuccess) ce = cudaStreamCreateWithFlags(&e->d2h_stream, cudaStreamNonBlocking);
+    if (ce != cudaSuccess) return e->cuda_fail(ce, "matmul_host_bf16: streams");
+  }
+  // panels of about 1024 rows (whole 256-row tiles), at most 64 of them
+  uint64_t rows = 1024;
+  while ((m + rows - 1) / rows > 64) rows *= 2;
+  if (rows > m) rows = m;
+  const uint64_t panels = (m + rows - 1) / rows;
+  void *da = nullptr, *db = nullptr, *dc = nullptr;
+  uint64_t ga = 0, gb = 0, gc = 0;
+  int st = e->alloc(m * k * 2, &da, &ga);
+  if (!st) st = e->alloc(k * n * 2, &db, &gb);
+  if (!st) st = e->alloc(m * n * 2, &dc, &gc);
+  std::vector<cudaEvent_t> ev(2 * panels + 2, nullptr);
+  cudaError_t ce = cudaSuccess;
+  for (auto& x : ev) if (!st && ce == cudaSuccess) ce = cudaEventCreateWithFlags(&x, cudaEventDisableTiming);
+  if (!st && ce != cudaSuccess) st = e->cuda_fail(ce, "matmul_host_bf16: events");
+  if (!st) {
+    cudaEvent_t start = ev[2 * panels], b_up = ev[2 * panels + 1];
+    // the pool's blocks may still be read by work already on the engine's stream
+    cudaEventRecord(start, e->stream);
+    cudaStreamWaitEvent(e->h2d_stream, start, 0);
+    ce = cudaMemcpyAsync(db, b, k * n * 2, cudaMemcpyHostToDevice, e->h2d_stream);
+    cudaEventRecord(b_up, e->h2d_stream);
+    cudaStreamWaitEvent(e->stream, b_up, 0);
+    for (uint64_t p = 0; p < panels && ce == cudaSuccess && !st; ++p) {
+      const uint64_t r0 = p * rows, nr = (r0 + rows <= m) ? rows : m - r0;
+      ce = cudaMemcpyAsync((char*)da + r0 * k * 2, a + r0 * k, nr * k * 2, cudaMemcpyHostToDevice, e->h2d_stream);
+      cudaEventRecord(ev[2 * p], e->h2d_stream);
+      cudaStreamWaitEvent(e->stream, ev[2 * p], 0);
+      GemmArgs g{};
+      g.a = (char*)da + r0 * k * 2; g.b = db; g.c = (char*)dc + r0 * n * 2;
+      g.in_bf16 = 1; g.out_bf16 = 1;
+      g.m = nr; g.n = n; g.k = k;
+      g.lda = k; g.ldb = n; g.ldc = n;
+      g.a_trans = 0; g.b_trans = 0; g.batch = 1; g.batches_dev = nullptr;
+      st = run_gemm(e, g, nullptr, "matmul_host_bf16");
+      if (st) break;
+      cudaEventRecord(ev[2 * p + 1], e->stream);
+      cudaStreamWaitEvent(e->d2h_stream, ev[2 * p + 1], 0);
+      if (ce == cudaSuccess) ce = cudaMemcpyAsync(out + r0 * n, (char*)dc + r0 * n * 2, nr * n * 2, cudaMemcpyDeviceToHost, e->d2h_stream);
+    }
+    if (!st && ce != cudaSuccess) st = e->cuda_fail(ce, "matmul_host_bf16: copy");
+    // everything in flight ends before the blocks go back to the pool
+    cudaStreamSynchronize(e->h2d_stream);
+    cudaStreamSynchronize(e->d2h_stream);
+    const int ws = e->wait();
+    if (!st) st = ws;
+    if (!st) { e->traffic.bytes_h2d += (m * k + k * n) * 2; e->traffic.bytes_d2h += m * n * 2; }
+  }
+  for (auto x : ev) if (x) cudaEventDestroy(x);
+  if (da) e->release(da, ga);
+  if (db) e->release(db, gb);
+  if (dc) e->release(dc, gc);
   return st;
 }
 

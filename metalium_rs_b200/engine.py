@@ -288,6 +288,19 @@ class CudaEngine:
         self._check(self._lib.b200_matmul_host(self._e, _ptr(a), _ptr(b), (C.c_uint64 * 3)(*mkn), _ptr(out)))
         return out
 
+    def matmul_bf16(self, a_bits, b_bits, mkn) -> np.ndarray:
+        """Host-staged BF16 product (bits in, bits out), copies overlapped with the product in row panels."""
+        a = np.ascontiguousarray(a_bits, dtype=np.uint16)
+        b = np.ascontiguousarray(b_bits, dtype=np.uint16)
+        out = np.empty((mkn[0], mkn[2]), dtype=np.uint16)
+        self.matmul_host_bf16_ptr(a.ctypes.data, b.ctypes.data, out.ctypes.data, mkn)
+        return out
+
+    def matmul_host_bf16_ptr(self, a_ptr: int, b_ptr: int, out_ptr: int, mkn):
+        """The same from raw host addresses (pinned memory another library owns)."""
+        self._check(self._lib.b200_matmul_host_bf16(self._e, C.c_void_p(a_ptr), C.c_void_p(b_ptr), (C.c_uint64 * 3)(*mkn),
+                                                    C.c_void_p(out_ptr)))
+
     def matmul_dram(self, a: int, a_transposed: bool, b: int, b_transposed: bool) -> Out:
         return self._call(self._lib.b200_matmul, C.c_uint64(a), C.c_int32(a_transposed), C.c_uint64(b),
                           C.c_int32(b_transposed), C.c_int32(0))

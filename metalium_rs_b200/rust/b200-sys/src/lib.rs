@@ -73,6 +73,7 @@ extern "C" {
     pub fn b200_scatter_rows_into(a0: *mut b200_engine, table: u64, indices: u64, values: *const b200_block_arg, column: i32) -> i32;
     pub fn b200_reshape(a0: *mut b200_engine, a: u64, rows: u64, cols: u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_set_matmul_sm_limit(a0: *mut b200_engine, sms: i32);
+    pub fn b200_matmul_host_bf16(a0: *mut b200_engine, a: *const u16, b: *const u16, mkn: *const u64, out: *mut u16) -> i32;
     pub fn b200_begin_trace(a0: *mut b200_engine) -> i32;
     pub fn b200_end_trace(a0: *mut b200_engine, trace: *mut u64) -> i32;
     pub fn b200_run_trace(a0: *mut b200_engine, trace: u64) -> i32;

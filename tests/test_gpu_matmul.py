@@ -234,6 +234,21 @@ def test_short_m_products_take_the_tensor_cores(eng, m):
         eng.free(i)
 
 
+@pytest.mark.parametrize("mkn", [(2048, 512, 768), (1500, 640, 520), (3000, 256, 256), (64, 64, 64), (5, 576, 960)])
+def test_the_host_staged_bf16_product_is_the_resident_one(eng, mkn):  # server.rs:70 `matmul`, for BF16 operands
+    m, k, n = mkn
+    a = orc.to_bf16(orc.uniform(0xC0F7, 1, (m, k), -1, 1))
+    b = orc.to_bf16(orc.uniform(0xC0F7, 2, (k, n), -1, 1))
+    got = eng.matmul_bf16(a, b, mkn)                      # uploaded, multiplied and downloaded in row panels
+    ia, ib = eng.upload_bf16(a, m, k), eng.upload_bf16(b, k, n)
+    out, _ = eng.matmul_dram_bf16(ia, False, ib, False)
+    assert np.array_equal(got, eng.download_bf16(out))    # K is whole in every panel: the same sums, the same bits
+    _, truth, s = orc.gemm_bf16(a, b, False, False)
+    assert np.all(np.abs(orc.from_bf16(got).astype(np.float64) - truth) <= 2.0 ** -8 * np.abs(truth) + 1e-6 * s)
+    for i in (ia, ib, out):
+        eng.free(i)
+
+
 @pytest.mark.parametrize("m", [1, 2, 3, 4])
 @pytest.mark.parametrize("kn", [(576, 960), (576, 576), (576, 3072), (1536, 576), (100, 72), (5000, 8)])
 def test_a_handful_of_rows_streams_the_weights_once(eng, m, kn):
