@@ -132,6 +132,18 @@ int32_t b200_matmul_host(b200_engine*, const float* a, const float* b, const uin
 /* The same for BF16 operands and a BF16 result (F32 accumulate), its copies overlapped with the product in
  * row panels on two copy streams; returns when `out` is complete.  Pinned host memory gives the overlap. */
 int32_t b200_matmul_host_bf16(b200_engine*, const uint16_t* a, const uint16_t* b, const uint64_t mkn[3], uint16_t* out);
+/* The sharded product's fused step: C = A B (BF16 operands as stored, no transposes) written from the
+ * product's epilogue into columns [col_first, col_first + n) of each of the n_dst matrices dst[i]
+ * ([dst_rows, dst_cols] row-major, of the result's type) -- this GPU's C and, through b200_ipc_open,
+ * every peer's, over NVLink.  No buffer is made.  The caller orders ranks around it (a barrier before a
+ * reader touches C).  Refused unless the tcgen05 path takes the product. */
+int32_t b200_matmul_into(b200_engine*, b200_buffer a, b200_buffer b, void* const* dst, int32_t n_dst,
+                         uint64_t dst_rows, uint64_t dst_cols, uint64_t col_first, int32_t out_bf16);
+/* CUDA IPC for that: a 64-byte handle of a buffer's allocation (not of a view), opened in another process
+ * as a device address valid there, closed before the owner frees the buffer. */
+int32_t b200_ipc_export(b200_engine*, b200_buffer buf, uint8_t handle[64]);
+int32_t b200_ipc_open(b200_engine*, const uint8_t handle[64], void** ptr);
+int32_t b200_ipc_close(b200_engine*, void* ptr);
 /* `matmul_dram` / `matmul_dram_bf16`: C = op(A) op(B).  F32 operands give an F32
  * result; with out_bf16 the F32 accumulator is rounded once to BF16.  BF16
  * operands accumulate in F32. */

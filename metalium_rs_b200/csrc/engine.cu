@@ -732,6 +732,73 @@ int32_t b200_matmul_host(b200_engine* e, const float* a, const float* b, const u
   return st;
 }
 
+// C = A B written into one or more caller-named matrices instead of a new buffer: the sharded
+// product's rank writes its column slice straight into every rank's C (its own and, through
+// addresses opened with b200_ipc_open, its peers' over NVLink) from the product's epilogue.
+int32_t b200_matmul_into(b200_engine* e, b200_buffer a, b200_buffer b, void* const* dst, int32_t n_dst, uint64_t dst_rows,
+                         uint64_t dst_cols, uint64_t col_first, int32_t out_bf16) {
+  cudaSetDevice(e->device);
+  Buf *A = nullptr, *B = nullptr;
+  int st = e->need(a, &A, "matmul_into");
+  if (!st) st = e->need(b, &B, "matmul_into");
+  if (st) return st;
+  if (A->elem != B200_BF16 || B->elem != B200_BF16) return e->fail(B200_UNSUPPORTED, "matmul_into: BF16 operands");
+  const uint64_t m = A->rows, k = A->cols, n = B->cols;
+  if (B->rows != k) return e->fail(B200_UNSUPPORTED, "matmul_into: [%llu,%llu] x [%llu,%llu]", (unsigned long long)m, (unsigned long long)k,
+                                   (unsigned long long)B->rows, (unsigned long long)n);
+  if (n_dst < 1 || n_dst > 8 || !dst) return e->fail(B200_UNSUPPORTED, "matmul_into: 1 to 8 destinations");
+  for (int i = 0; i < n_dst; ++i) if (!dst[i]) return e->fail(B200_UNSUPPORTED, "matmul_into: destination %d is null", i);
+  if (m != dst_rows || col_first + n > dst_cols)
+    return e->fail(B200_UNSUPPORTED, "matmul_into: a [%llu,%llu] product at column %llu of [%llu,%llu]", (unsigned long long)m,
+                   (unsigned long long)n, (unsigned long long)col_first, (unsigned long long)dst_rows, (unsigned long long)dst_cols);
+  if (k == 0 || m == 0 || n == 0) return e->fail(B200_UNSUPPORTED, "matmul_into: an empty product");
+  const uint64_t eb = out_bf16 ? 2 : 4;
+  GemmArgs g{};
+  g.a = A->ptr; g.b = B->ptr;
+  g.c = (char*)dst[0] + col_first * eb;
+  g.n_more = n_dst - 1;
+  for (int i = 1; i < n_dst; ++i) g.c_more[i - 1] = (char*)dst[i] + col_first * eb;
+  g.in_bf16 = 1; g.out_bf16 = out_bf16;
+  g.m = m; g.n = n; g.k = k;
+  g.lda = A->cols; g.ldb = B->cols; g.ldc = dst_cols;
+  g.a_trans = 0; g.b_trans = 0; g.batch = 1; g.batches_dev = nullptr;
+  g.sm_limit = e->matmul_sm_limit;
+  const char* why = "";
+  if (!gemm_tc_supported(g, &why)) return e->fail(B200_UNSUPPORTED, "matmul_into: the tcgen05 path refuses this product (%s)", why);
+  const cudaError_t ce = launch_gemm_tc(g, nullptr, e->d_err, e->stream);
+  if (ce == cudaErrorNotSupported) return e->fail(B200_UNSUPPORTED, "matmul_into: the driver refused a tensor map for this shape");
+  e->matmul_path = "tcgen05";
+  return e->launched(ce, "matmul_into");
+}
+
+// Another process's view of a buffer of this engine (CUDA IPC): export here, open there.
+int32_t b200_ipc_export(b200_engine* e, b200_buffer buf, uint8_t handle[64]) {
+  cudaSetDevice(e->device);
+  Buf* X = nullptr;
+  int st = e->need(buf, &X, "ipc_export");
+  if (st) return st;
+  if (X->parent || X->adopted) return e->fail(B200_UNSUPPORTED, "ipc_export: a view or an adopted buffer has no allocation of its own");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the ABI carries a 64-byte handle");
+  cudaIpcMemHandle_t h;
+  const cudaError_t ce = cudaIpcGetMemHandle(&h, X->ptr);
+  if (ce != cudaSuccess) return e->cuda_fail(ce, "ipc_export");
+  memcpy(handle, &h, 64);
+  return B200_OK;
+}
+int32_t b200_ipc_open(b200_engine* e, const uint8_t handle[64], void** ptr) {
+  cudaSetDevice(e->device);
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  const cudaError_t ce = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  if (ce != cudaSuccess) { cudaGetLastError(); return e->cuda_fail(ce, "ipc_open"); }
+  return B200_OK;
+}
+int32_t b200_ipc_close(b200_engine* e, void* ptr) {
+  cudaSetDevice(e->device);
+  const cudaError_t ce = cudaIpcCloseMemHandle(ptr);
+  return ce == cudaSuccess ? B200_OK : e->cuda_fail(ce, "ipc_close");
+}
+
 // The host-staged product for BF16 operands, with its copies overlapped: B goes up whole, then A
 // goes up, is multiplied and its rows of C come down in row panels, so the upload of panel p+1, the
 // product of panel p and the download of panel p-1 run at once (PCIe carries both directions).  Returns

@@ -37,6 +37,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  uint8_t* epi_stage = smem + STAGES * STAGE_BYTES + 256;   // four warps' staging rows for the epilogue
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -156,44 +157,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint64_t c_off = p.batches ? p.batches[b].c_off : 0;
-      const uint64_t row = (uint64_t)tm * BM + quad * 32 + lane;
       const uint64_t n0 = (uint64_t)tn * BN;
-      const bool row_ok = row < p.m;
-#pragma unroll 1
-      for (int cb = 0; cb < BN / 32; ++cb) {
-        uint32_t v[32];
-        tmem_ld32(tmem_base + ((quad * 32u) << 16) + acc * BN + cb * 32, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const uint64_t col = n0 + cb * 32;
-        if (row_ok && col < p.n) {
-          const uint64_t o = c_off + row * p.ldc + col;
-          if (p.out_bf16) {
-            uint16_t* dst = (uint16_t*)p.c + o;
-            if (col + 32 <= p.n && (((uintptr_t)dst) & 15) == 0) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint4 w;
-                w.x = (uint32_t)f32_to_bf16_bits(v[q * 8 + 0]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 1]) << 16);
-                w.y = (uint32_t)f32_to_bf16_bits(v[q * 8 + 2]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 3]) << 16);
-                w.z = (uint32_t)f32_to_bf16_bits(v[q * 8 + 4]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 5]) << 16);
-                w.w = (uint32_t)f32_to_bf16_bits(v[q * 8 + 6]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 7]) << 16);
-                *reinterpret_cast<uint4*>(dst + q * 8) = w;
-              }
-            } else {
-              for (int j = 0; j < 32 && col + j < p.n; ++j) dst[j] = f32_to_bf16_bits(v[j]);
-            }
-          } else {
-            uint32_t* dst = (uint32_t*)p.c + o;
-            if (col + 32 <= p.n && (((uintptr_t)dst) & 15) == 0) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                *reinterpret_cast<uint4*>(dst + q * 4) = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-            } else {
-              for (int j = 0; j < 32 && col + j < p.n; ++j) dst[j] = v[j];
-            }
-          }
-        }
-      }
+      epilogue_warp<BN>(p, tmem_base + ((quad * 32u) << 16) + acc * BN, c_off, (uint64_t)tm * BM + quad * 32, n0, lane, epi_stage + quad * EPI_WARP_BYTES);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -217,7 +182,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 template <int BN, int STAGES>
 cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, bool a_mn, bool b_mn,
                            unsigned grid, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+  constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256 + EPI_BYTES;
 #define TC_LAUNCH(AM, BMJ)                                                                              \
   do {                                                                                                  \
     static bool attr_set = false;                                                                       \
@@ -324,6 +289,9 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int
   p.batch = g.batch ? g.batch : 1;
   p.batches = g.batch > 1 ? g.batches_dev : nullptr;
   p.c = g.c; p.out_bf16 = g.out_bf16; p.err = err_word;
+  p.n_more = g.n_more;
+  p.staged = epilogue_staged(g.c, g.c_more, g.n_more, g.ldc, g.out_bf16);
+  for (int i = 0; i < 7; ++i) p.c_more[i] = i < g.n_more ? g.c_more[i] : nullptr;
   p.mn_lbo = env_u32("B200TT_MN_LBO", 8192);
   p.mn_sbo = env_u32("B200TT_MN_SBO", 1024);
   if (g.batch == 1 && g.batches_dev) p.batches = g.batches_dev;

@@ -76,6 +76,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  uint8_t* epi_stage = smem + P_STAGES * STAGE_BYTES + 256;   // four warps' staging rows for the epilogue
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();   // 0: leader
@@ -178,44 +179,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const uint32_t acc = local & 1, acc_phase = (local >> 1) & 1;
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint64_t row = (uint64_t)tm * 256 + rank * BM + quad * 32 + lane;
       const uint64_t n0 = (uint64_t)tn * P_BN;
-      const bool row_ok = row < p.m;
-#pragma unroll 1
-      for (int cb = 0; cb < P_BN / 32; ++cb) {
-        uint32_t v[32];
-        tmem_ld32(tmem_base + ((quad * 32u) << 16) + acc * P_BN + cb * 32, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const uint64_t col = n0 + cb * 32;
-        if (row_ok && col < p.n) {
-          const uint64_t o = row * p.ldc + col;
-          if (p.out_bf16) {
-            uint16_t* dst = (uint16_t*)p.c + o;
-            if (col + 32 <= p.n && (((uintptr_t)dst) & 15) == 0) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint4 w;
-                w.x = (uint32_t)f32_to_bf16_bits(v[q * 8 + 0]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 1]) << 16);
-                w.y = (uint32_t)f32_to_bf16_bits(v[q * 8 + 2]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 3]) << 16);
-                w.z = (uint32_t)f32_to_bf16_bits(v[q * 8 + 4]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 5]) << 16);
-                w.w = (uint32_t)f32_to_bf16_bits(v[q * 8 + 6]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 7]) << 16);
-                *reinterpret_cast<uint4*>(dst + q * 8) = w;
-              }
-            } else {
-              for (int j = 0; j < 32 && col + j < p.n; ++j) dst[j] = f32_to_bf16_bits(v[j]);
-            }
-          } else {
-            uint32_t* dst = (uint32_t*)p.c + o;
-            if (col + 32 <= p.n && (((uintptr_t)dst) & 15) == 0) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                *reinterpret_cast<uint4*>(dst + q * 4) = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-            } else {
-              for (int j = 0; j < 32 && col + j < p.n; ++j) dst[j] = v[j];
-            }
-          }
-        }
-      }
+      epilogue_warp<P_BN>(p, tmem_base + ((quad * 32u) << 16) + acc * P_BN, 0, (uint64_t)tm * 256 + rank * BM + quad * 32, n0, lane, epi_stage + quad * EPI_WARP_BYTES);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(map_to_rank(smem_u32(&acc_empty[acc]), 0));
@@ -262,7 +227,10 @@ cudaError_t launch_gemm_tc2(const GemmArgs& g, int* err_word, cudaStream_t strea
   p.tiles_n = (uint32_t)((g.n + P_BN - 1) / P_BN);
   p.batch = 1; p.batches = nullptr;
   p.c = g.c; p.out_bf16 = g.out_bf16; p.err = err_word;
-  constexpr size_t smem = (size_t)P_STAGES * (BM * BK * 2 + P_HALF * BK * 2) + 1024 + 256;
+  p.n_more = g.n_more;
+  p.staged = epilogue_staged(g.c, g.c_more, g.n_more, g.ldc, g.out_bf16);
+  for (int i = 0; i < 7; ++i) p.c_more[i] = i < g.n_more ? g.c_more[i] : nullptr;
+  constexpr size_t smem = (size_t)P_STAGES * (BM * BK * 2 + P_HALF * BK * 2) + 1024 + 256 + EPI_BYTES;
   const uint64_t total = (uint64_t)p.tiles_m * p.tiles_n;
 
   cudaLaunchConfig_t cfg = {};

@@ -118,6 +118,8 @@ struct GemmArgs {
   int a_trans, b_trans;    // stored matrix is the transpose of the logical operand
   uint64_t batch;          // 1, or number of products
   const GemmBatch* batches_dev;  // device array when batch > 1 (or nullptr for batch 1)
+  void* c_more[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  int n_more = 0;          // the tensor-core product also stores C at these addresses (same pitch as c)
   int sm_limit = 0;        // > 0: the tensor-core product uses at most this many SMs (the rest stay free for a
                            // collective running beside it)
 };

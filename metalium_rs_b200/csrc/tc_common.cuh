@@ -25,6 +25,9 @@ struct TcParams {
   uint64_t batch;
   const GemmBatch* batches;  // device, or nullptr
   void* c;
+  void* c_more[7];           // further copies of C with c's pitch (a peer GPU's memory among them), or none
+  int n_more;
+  int staged;                // the epilogue may go through shared memory (pointers and pitch are 16-byte aligned)
   int out_bf16;
   int* err;
   uint32_t mn_lbo, mn_sbo;   // byte offsets of an MN-major operand's descriptor
@@ -103,6 +106,121 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
       : "r"(taddr) : "memory");
 }
 
+// ---- epilogue ---------------------------------------------------------------------------------
+// A warp owns 32 rows of the accumulator (a lane a row).  Stored straight from registers a warp
+// instruction would touch 32 rows with 16 bytes each; a peer GPU's memory takes such stores at a
+// few percent of NVLink's rate.  So 128 bytes of each row are staged in shared memory (EPI_PITCH:
+// 128 + 16 of padding, conflict-free both ways) and written back four rows of 128 contiguous bytes
+// an instruction, to every copy of C.
+constexpr uint32_t EPI_PITCH = 144;
+constexpr uint32_t EPI_WARP_BYTES = 32 * EPI_PITCH;
+constexpr uint32_t EPI_BYTES = 4 * EPI_WARP_BYTES;
+
+__device__ __forceinline__ void epi_store_rows(const uint8_t* stage, const TcParams& p, uint64_t byte_off_row0,
+                                               uint64_t pitch_bytes, uint64_t row0, int lane) {
+  const int sub = lane >> 3, unit = lane & 7;
+  for (int dsti = -1; dsti < p.n_more; ++dsti) {
+    char* base = (char*)(dsti < 0 ? p.c : p.c_more[dsti]) + byte_off_row0 + unit * 16;
+#pragma unroll
+    for (int r = 0; r < 32; r += 4) {
+      const int rr = r + sub;
+      if (row0 + rr < p.m)
+        *reinterpret_cast<uint4*>(base + (uint64_t)rr * pitch_bytes) = *reinterpret_cast<const uint4*>(stage + rr * EPI_PITCH + unit * 16);
+    }
+  }
+}
+
+// 32 columns of this lane's row straight from registers (ragged edges, unaligned pitches).
+__device__ __forceinline__ void epi_store_direct(const TcParams& p, const uint32_t* v, uint64_t o, uint64_t col) {
+  for (int dsti = -1; dsti < p.n_more; ++dsti) {
+    void* const cbase = dsti < 0 ? p.c : p.c_more[dsti];
+    if (p.out_bf16) {
+      uint16_t* dst = (uint16_t*)cbase + o;
+      if (col + 32 <= p.n && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 w;
+          w.x = (uint32_t)f32_to_bf16_bits(v[q * 8 + 0]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 1]) << 16);
+          w.y = (uint32_t)f32_to_bf16_bits(v[q * 8 + 2]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 3]) << 16);
+          w.z = (uint32_t)f32_to_bf16_bits(v[q * 8 + 4]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 5]) << 16);
+          w.w = (uint32_t)f32_to_bf16_bits(v[q * 8 + 6]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 7]) << 16);
+          *reinterpret_cast<uint4*>(dst + q * 8) = w;
+        }
+      } else {
+        for (int j = 0; j < 32 && col + j < p.n; ++j) dst[j] = f32_to_bf16_bits(v[j]);
+      }
+    } else {
+      uint32_t* dst = (uint32_t*)cbase + o;
+      if (col + 32 <= p.n && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<uint4*>(dst + q * 4) = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+      } else {
+        for (int j = 0; j < 32 && col + j < p.n; ++j) dst[j] = v[j];
+      }
+    }
+  }
+}
+
+// One accumulator's 32 rows x BN_ columns (TMEM address `tacc`: this warp's lane quarter, the
+// accumulator's first column) to every copy of C.  row0: the warp's first row; n0: the tile's first
+// column; c_off: the product's element offset in C.  stage: this warp's EPI_WARP_BYTES.
+template <int BN_>
+__device__ __forceinline__ void epilogue_warp(const TcParams& p, uint32_t tacc, uint64_t c_off, uint64_t row0, uint64_t n0,
+                                              int lane, uint8_t* stage) {
+  const uint64_t row = row0 + lane;
+  const bool row_ok = row < p.m;
+  const uint64_t eb = p.out_bf16 ? 2 : 4;
+  const bool staged = p.staged && ((c_off * eb) & 15) == 0;
+  if (p.out_bf16) {
+#pragma unroll 1
+    for (int cb = 0; cb < BN_ / 32; cb += 2) {
+      uint32_t v[64];
+      tmem_ld32(tacc + cb * 32, v);
+      tmem_ld32(tacc + cb * 32 + 32, v + 32);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      const uint64_t col = n0 + cb * 32;
+      if (staged && col + 64 <= p.n) {          // the same for the whole warp
+        uint8_t* mine = stage + lane * EPI_PITCH;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          uint4 w;
+          w.x = (uint32_t)f32_to_bf16_bits(v[q * 8 + 0]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 1]) << 16);
+          w.y = (uint32_t)f32_to_bf16_bits(v[q * 8 + 2]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 3]) << 16);
+          w.z = (uint32_t)f32_to_bf16_bits(v[q * 8 + 4]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 5]) << 16);
+          w.w = (uint32_t)f32_to_bf16_bits(v[q * 8 + 6]) | ((uint32_t)f32_to_bf16_bits(v[q * 8 + 7]) << 16);
+          *reinterpret_cast<uint4*>(mine + q * 16) = w;
+        }
+        __syncwarp();
+        epi_store_rows(stage, p, (c_off + row0 * p.ldc + col) * 2, p.ldc * 2, row0, lane);
+        __syncwarp();
+      } else if (row_ok) {
+        if (col < p.n) epi_store_direct(p, v, c_off + row * p.ldc + col, col);
+        if (col + 32 < p.n) epi_store_direct(p, v + 32, c_off + row * p.ldc + col + 32, col + 32);
+      }
+    }
+  } else {
+#pragma unroll 1
+    for (int cb = 0; cb < BN_ / 32; ++cb) {
+      uint32_t v[32];
+      tmem_ld32(tacc + cb * 32, v);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      const uint64_t col = n0 + cb * 32;
+      if (staged && col + 32 <= p.n) {
+        uint8_t* mine = stage + lane * EPI_PITCH;
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<uint4*>(mine + q * 16) = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+        __syncwarp();
+        epi_store_rows(stage, p, (c_off + row0 * p.ldc + col) * 4, p.ldc * 4, row0, lane);
+        __syncwarp();
+      } else if (row_ok && col < p.n) {
+        epi_store_direct(p, v, c_off + row * p.ldc + col, col);
+      }
+    }
+  }
+}
+
 // Tile order: groups of 16 tile rows walked column by column, so the CTAs running at one
 // time share A rows and B columns in L2.
 __device__ __forceinline__ void tile_coords(uint64_t t, uint32_t tiles_m, uint32_t tiles_n, uint64_t* batch,
@@ -117,6 +235,15 @@ __device__ __forceinline__ void tile_coords(uint64_t t, uint32_t tiles_m, uint32
   const uint32_t in = r - group * G * tiles_n;
   *tm = first + in % rows;
   *tn = in / rows;
+}
+
+// Whether every copy of C can take 16-byte stores at every row start.
+inline int epilogue_staged(const void* c, void* const* c_more, int n_more, uint64_t ldc, int out_bf16) {
+  const char* e = getenv("B200TT_EPILOGUE");
+  if (e && e[0] == 'd') return 0;   // "direct": stores straight from registers
+  uintptr_t bits = (uintptr_t)c | (uintptr_t)(ldc * (out_bf16 ? 2 : 4));
+  for (int i = 0; i < n_more; ++i) bits |= (uintptr_t)c_more[i];
+  return (bits & 15) == 0;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,

@@ -301,6 +301,28 @@ class CudaEngine:
         self._check(self._lib.b200_matmul_host_bf16(self._e, C.c_void_p(a_ptr), C.c_void_p(b_ptr), (C.c_uint64 * 3)(*mkn),
                                                     C.c_void_p(out_ptr)))
 
+    def matmul_into(self, a: int, b: int, dst_ptrs, dst_dims, col_first: int, bf16: bool = True):
+        """C = A B stored from the product's epilogue into columns [col_first, ...) of every matrix in
+        `dst_ptrs` (device addresses: this GPU's or, opened with `ipc_open`, a peer's)."""
+        arr = (C.c_void_p * len(dst_ptrs))(*dst_ptrs)
+        self._check(self._lib.b200_matmul_into(self._e, C.c_uint64(a), C.c_uint64(b), arr, C.c_int32(len(dst_ptrs)),
+                                               C.c_uint64(dst_dims[0]), C.c_uint64(dst_dims[1]), C.c_uint64(col_first),
+                                               C.c_int32(1 if bf16 else 0)))
+
+    def ipc_export(self, buf: int) -> bytes:
+        h = (C.c_uint8 * 64)()
+        self._check(self._lib.b200_ipc_export(self._e, C.c_uint64(buf), h))
+        return bytes(h)
+
+    def ipc_open(self, handle: bytes) -> int:
+        h = (C.c_uint8 * 64)(*handle)
+        p = C.c_void_p()
+        self._check(self._lib.b200_ipc_open(self._e, h, C.byref(p)))
+        return p.value
+
+    def ipc_close(self, ptr: int):
+        self._check(self._lib.b200_ipc_close(self._e, C.c_void_p(ptr)))
+
     def matmul_dram(self, a: int, a_transposed: bool, b: int, b_transposed: bool) -> Out:
         return self._call(self._lib.b200_matmul, C.c_uint64(a), C.c_int32(a_transposed), C.c_uint64(b),
                           C.c_int32(b_transposed), C.c_int32(0))

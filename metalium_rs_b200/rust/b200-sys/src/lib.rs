@@ -74,6 +74,10 @@ extern "C" {
     pub fn b200_reshape(a0: *mut b200_engine, a: u64, rows: u64, cols: u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_set_matmul_sm_limit(a0: *mut b200_engine, sms: i32);
     pub fn b200_matmul_host_bf16(a0: *mut b200_engine, a: *const u16, b: *const u16, mkn: *const u64, out: *mut u16) -> i32;
+    pub fn b200_matmul_into(a0: *mut b200_engine, a: u64, b: u64, dst: *const *mut core::ffi::c_void, n_dst: i32, dst_rows: u64, dst_cols: u64, col_first: u64, out_bf16: i32) -> i32;
+    pub fn b200_ipc_export(a0: *mut b200_engine, buf: u64, handle: *mut u8) -> i32;
+    pub fn b200_ipc_open(a0: *mut b200_engine, handle: *const u8, ptr: *mut *mut core::ffi::c_void) -> i32;
+    pub fn b200_ipc_close(a0: *mut b200_engine, ptr: *mut core::ffi::c_void) -> i32;
     pub fn b200_begin_trace(a0: *mut b200_engine) -> i32;
     pub fn b200_end_trace(a0: *mut b200_engine, trace: *mut u64) -> i32;
     pub fn b200_run_trace(a0: *mut b200_engine, trace: u64) -> i32;

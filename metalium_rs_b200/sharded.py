@@ -110,7 +110,77 @@ class ShardedMatmul:
                 eng.free(out)
         eng.set_matmul_sm_limit(0)
         full, _ = eng.copy_blocks(self.staged_buf, self.moves, (self.m, self.n))
-        return full  # the caller frees it
+        return full  # the caller gives it back with release()
+
+    def release(self, buf: int):
+        self.eng.free(buf)
+
+    def close(self):
+        pass
+
+    describe = "row panels: NCCL all-gather of panel p overlapped with the product of panel p+1, then one strided copy into row-major C"
+
+
+class PeerStoreMatmul:
+    """The same sharded product with the exchange inside the product: every rank keeps a whole C,
+    the ranks exchange CUDA IPC handles of it once, and a rank's product stores each finished tile
+    of its column slice into every rank's C from its epilogue (`b200_matmul_into`: plain stores, its
+    own memory and its peers' over NVLink).  No staging buffer, no collective on the data, no final
+    copy; the ranks meet at a barrier before C is read and before it is written again.
+
+    `run()` returns the buffer that holds C; it belongs to this object (release() does nothing)."""
+
+    def __init__(self, eng, rank: int, world: int, m: int, k: int, n: int, a_buf: int, b_slice_buf: int, bf16=True):
+        import torch
+        import torch.distributed as dist
+        self.eng, self.rank, self.world = eng, rank, world
+        self.m, self.k, self.n = m, k, n
+        self.parts = partition(n, world)
+        self.per = self.parts[0][1] - self.parts[0][0]
+        if any(hi - lo != self.per for lo, hi in self.parts):
+            raise ValueError(f"{n} columns do not split evenly over {world} ranks in whole tiles")
+        if not bf16:
+            raise ValueError("the peer-store product is BF16")
+        self.a, self.b = a_buf, b_slice_buf
+        self.c, _ = eng.zeros_dram((m, n), bf16=True)
+        mine, _ = eng.device_ptr(self.c)
+        handle = eng.ipc_export(self.c)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle)
+        self.peers = {}
+        self.dst = []
+        for r in range(world):
+            if r == rank:
+                self.dst.append(mine)
+            else:
+                self.peers[r] = eng.ipc_open(handles[r])
+                self.dst.append(self.peers[r])
+        # own C first: the epilogue's first store is the local one
+        self.dst = [mine] + [self.dst[r] for r in range(world) if r != rank]
+        self.panels = 1
+        dist.barrier()
+
+    def run(self) -> int:
+        import torch.distributed as dist
+        dist.barrier()                       # nobody still reads the C this step overwrites
+        self.eng.matmul_into(self.a, self.b, self.dst, (self.m, self.n), self.parts[self.rank][0], True)
+        self.eng.sync()                      # this rank's stores have landed, here and on its peers
+        dist.barrier()                       # and so have everyone else's
+        return self.c
+
+    def release(self, buf: int):
+        pass
+
+    def close(self):
+        import torch.distributed as dist
+        dist.barrier()
+        for p in self.peers.values():
+            self.eng.ipc_close(p)
+        self.peers = {}
+        dist.barrier()                       # every mapping is closed before an owner frees its C
+        self.eng.free(self.c)
+
+    describe = "each rank's product stores its tiles into every rank's C from its epilogue (peer stores over NVLink through CUDA IPC mappings); barriers around it, no collective on the data"
 
 
 def _as_tensor(ptr: int, shape, dtype):
@@ -156,10 +226,26 @@ def bench_main(args, metric, unit, size, workload_name, peaks, ClockSampler, che
     a_buf = eng.adopt(a_t.data_ptr(), m, k, BF16)
     b_buf = eng.adopt(b_t.data_ptr(), k, per, BF16)
     torch.cuda.synchronize()
-    sm = ShardedMatmul(eng, rank, world, m, k, n, a_buf, b_buf)
+    # The exchange: peer stores from the product's epilogue, or (B200TT_SHARD=nccl, or where CUDA IPC is
+    # refused) an NCCL all-gather in row panels.
+    sm, how = None, os.environ.get("B200TT_SHARD", "peer")
+    if how != "nccl":
+        try:
+            sm = PeerStoreMatmul(eng, rank, world, m, k, n, a_buf, b_buf)
+        except Exception as ex:   # every rank fails alike (same box, same driver): fall back together
+            if rank == 0:
+                print(f"peer-store product unavailable ({ex}); using the NCCL all-gather", flush=True)
+            sm = None
+    agree = torch.tensor([1.0 if sm is not None else 0.0], device=dev)
+    dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+    if agree.item() < 1.0:
+        if sm is not None:
+            sm.close()
+        sm = ShardedMatmul(eng, rank, world, m, k, n, a_buf, b_buf)
+    fused = isinstance(sm, PeerStoreMatmul)
 
     for _ in range(max(args.warmup, 3)):
-        eng.free(sm.run())
+        sm.release(sm.run())
     full = sm.run()
     eng.sync()
     torch.cuda.synchronize()
@@ -186,7 +272,7 @@ def bench_main(args, metric, unit, size, workload_name, peaks, ClockSampler, che
     eng.sync()
     same = bool(torch.equal(_as_tensor(sp, (m, probe_cols), torch.int16), full_t[:, :probe_cols]))
     eng.free(single)
-    eng.free(full)
+    sm.release(full)
     flags = torch.tensor([0.0, worst], device=dev)
     dist.all_reduce(flags, op=dist.ReduceOp.MAX)
     okt = torch.tensor([1.0 if (ok and same) else 0.0], device=dev)
@@ -205,7 +291,7 @@ def bench_main(args, metric, unit, size, workload_name, peaks, ClockSampler, che
     eng.sync()
     eng.timer_start()
     for _ in range(args.steps):
-        eng.free(sm.run())
+        sm.release(sm.run())
     ms = eng.timer_stop()
     torch.cuda.synchronize()
     clocks = sampler.stop() if sampler else None
@@ -241,7 +327,7 @@ def bench_main(args, metric, unit, size, workload_name, peaks, ClockSampler, che
             eng.write_ptr(b_buf, b_host.data_ptr(), k * per, 2)
             full = sm.run()
             eng.download_into(full, c_host.data_ptr(), m * n, 2)
-            eng.free(full)
+            sm.release(full)
         dt = torch.tensor([(time.perf_counter() - t0) * 1e3 / steps], device=dev)
         dist.all_reduce(dt, op=dist.ReduceOp.MAX)
         e2e_ms = float(dt.item())
@@ -261,9 +347,10 @@ def bench_main(args, metric, unit, size, workload_name, peaks, ClockSampler, che
                 "config": {"workload": workload_name(world) if m == size else f"bf16 gemm {m}^3 column-sharded over {world}",
                            "m": m, "n": n, "k": k, "columns_per_rank": per,
                            "l2": "operands exceed the 126 MB L2; no flush needed",
-                           "collective": f"{sm.panels} row panels: NCCL all-gather of panel p overlapped with the product of panel p+1, then one strided copy into row-major C"},
+                           "collective": (f"{sm.panels} " if not fused else "") + sm.describe},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
-                "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel + ncclAllGather", "achieved": value, "peak": peak,
+                "roofline": {"bound": "tensor", "kernel": "gemm_tc2_kernel with peer stores" if fused else "gemm_tc_kernel + ncclAllGather",
+                             "achieved": value, "peak": peak,
                              "unit": unit, "frac": value / peak, "peak_source": f"{which} cuBLAS bf16 burst x {world}",
                              "traffic": None, "product_only_ms": ms_mm / args.steps,
                              "gather_bytes_per_rank": gather_bytes,
@@ -271,5 +358,6 @@ def bench_main(args, metric, unit, size, workload_name, peaks, ClockSampler, che
                 "validated": {"max_err_over_S": float(flags[1].item()), "sharded_equals_single_gpu_bits": True}}
         print(json.dumps(line))
     dist.barrier()
+    sm.close()
     eng.close()
     dist.destroy_process_group()

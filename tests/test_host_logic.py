@@ -171,6 +171,33 @@ def test_attention_rows_dims_and_refusals(e):                                   
     assert err.value.status == 5
 
 
+def test_matmul_into_and_ipc_handles(e):          # the sharded product's fused step (tt-kernels/src/shard.rs:348-458)
+    a = e.upload_bf16(np.zeros((256, 128), np.uint16), 256, 128)
+    b = e.upload_bf16(np.zeros((128, 64), np.uint16), 128, 64)
+    c, _ = e.zeros_dram((256, 192), bf16=True)
+    mine, _ = e.device_ptr(c)
+    handle = e.ipc_export(c)
+    assert len(handle) == 64
+    peer = e.ipc_open(handle)                     # the stand-in runtime hands the same address back
+    assert peer == mine
+    before = e.device_traffic().launches
+    e.matmul_into(a, b, [mine, peer], (256, 192), 64)
+    assert e.device_traffic().launches - before == 1 and e.last_matmul_path() == "tcgen05"
+    e.ipc_close(peer)
+    for args in (([mine], (256, 192), 160),       # the slice would end past the last column
+                 ([mine], (128, 192), 0),         # C has other rows than the product
+                 ([], (256, 192), 0), ([mine] * 9, (256, 192), 0), ([mine, 0], (256, 192), 0)):
+        with pytest.raises(TtError) as err:
+            e.matmul_into(a, b, *args)
+        assert err.value.status == 2
+    f = f32(e, 256, 128)
+    with pytest.raises(TtError):
+        e.matmul_into(f, b, [mine], (256, 192), 0)          # F32 operands
+    v, _ = e.slice_rows(c, 0, 128)
+    with pytest.raises(TtError):
+        e.ipc_export(v)                                       # a view has no allocation of its own
+
+
 def test_views_keep_their_parent_alive(e):                                      # server.rs:480-481
     t0 = e.device_traffic().pool_in_use
     a = f32(e, 64, 8)
