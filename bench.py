@@ -188,7 +188,7 @@ def run_reference(args):
 def workload_name(n_gpus):
     if n_gpus == 1:
         return f"bf16 gemm {N1_SIZE}^3 (A [M,K], B [K,N] row-major, FP32 accumulate, bf16 out)"
-    return f"bf16 gemm {NN_SIZE}^3 column-sharded over {n_gpus} GPUs, NCCL all-gather of C"
+    return f"bf16 gemm {NN_SIZE}^3 column-sharded over {n_gpus} GPUs, the whole C left on every rank"
 
 
 # ---------------------------------------------------------------------- GPU arm

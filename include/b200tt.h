@@ -139,6 +139,10 @@ int32_t b200_matmul_host_bf16(b200_engine*, const uint16_t* a, const uint16_t* b
  * reader touches C).  Refused unless the tcgen05 path takes the product. */
 int32_t b200_matmul_into(b200_engine*, b200_buffer a, b200_buffer b, void* const* dst, int32_t n_dst,
                          uint64_t dst_rows, uint64_t dst_cols, uint64_t col_first, int32_t out_bf16);
+/* The same for a value no product made (an activation): a block of a buffer stored into columns
+ * [col_first, ...) of every dst[i] -- a rank's column slice of an all-gather, written everywhere by its owner. */
+int32_t b200_store_block_into(b200_engine*, const b200_block_arg* src, void* const* dst, int32_t n_dst,
+                              uint64_t dst_rows, uint64_t dst_cols, uint64_t col_first);
 /* CUDA IPC for that: a 64-byte handle of a buffer's allocation (not of a view), opened in another process
  * as a device address valid there, closed before the owner frees the buffer. */
 int32_t b200_ipc_export(b200_engine*, b200_buffer buf, uint8_t handle[64]);

@@ -86,10 +86,12 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         return OUT
     with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
         objs = list(ex.map(lambda kv: _compile(kv[0], kv[1], stamps[kv[0]]), SOURCES.items()))
-    cmd = [nvcc(), *ARCH, "-shared", "-o", str(OUT), *map(str, objs), "-cudart", "static"]
+    tmp = OUT.with_suffix(".so.tmp")   # linked beside the target, then renamed: a reader never sees half a library
+    cmd = [nvcc(), *ARCH, "-shared", "-o", str(tmp), *map(str, objs), "-cudart", "static"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp, OUT)
     lmark.write_text(link_stamp)
     if verbose:
         print(f"built {OUT}")

@@ -771,6 +771,29 @@ int32_t b200_matmul_into(b200_engine* e, b200_buffer a, b200_buffer b, void* con
   return e->launched(ce, "matmul_into");
 }
 
+// A block of a buffer stored into columns [col_first, ...) of each of the n_dst matrices dst[i]
+// ([dst_rows, dst_cols] of the block's type; this GPU's or a peer's): a rank's column slice of an
+// all-gather, written everywhere by its owner.
+int32_t b200_store_block_into(b200_engine* e, const b200_block_arg* src, void* const* dst, int32_t n_dst, uint64_t dst_rows,
+                              uint64_t dst_cols, uint64_t col_first) {
+  cudaSetDevice(e->device);
+  Buf* S = nullptr;
+  int st = e->need(src->id, &S, "store_block_into");
+  if (st) return st;
+  const uint64_t rows = src->dims[0], cols = src->dims[1];
+  if (src->at[0] + rows > S->rows || src->at[1] + cols > S->cols || rows != dst_rows || col_first + cols > dst_cols)
+    return e->fail(B200_UNSUPPORTED, "store_block_into: shapes do not meet");
+  if (n_dst < 1 || n_dst > 8 || !dst) return e->fail(B200_UNSUPPORTED, "store_block_into: 1 to 8 destinations");
+  for (int i = 0; i < n_dst; ++i) if (!dst[i]) return e->fail(B200_UNSUPPORTED, "store_block_into: destination %d is null", i);
+  const uint64_t eb = elem_bytes(S->elem);
+  const char* sp = (const char*)S->ptr + (src->at[0] * S->cols + src->at[1]) * eb;
+  void* shifted[8];
+  for (int i = 0; i < n_dst; ++i) shifted[i] = (char*)dst[i] + col_first * eb;
+  const cudaError_t ce = launch_store_block_many(sp, S->cols * eb, shifted, n_dst, dst_cols * eb, rows, cols * eb, e->stream);
+  if (ce == cudaErrorNotSupported) return e->fail(B200_UNSUPPORTED, "store_block_into: rows are not whole 16-byte pieces at 16-byte addresses");
+  return e->launched(ce, "store_block_into");
+}
+
 // Another process's view of a buffer of this engine (CUDA IPC): export here, open there.
 int32_t b200_ipc_export(b200_engine* e, b200_buffer buf, uint8_t handle[64]) {
   cudaSetDevice(e->device);

@@ -102,6 +102,21 @@ scatter_rows_into_kernel(E* table, uint64_t t_rows, uint64_t cols, const int32_t
   }
 }
 
+// A [rows, row_bytes] block copied into the same place of up to eight matrices (this GPU's or, through
+// IPC mappings, its peers'): what an all-gather of column slices is when every rank stores its own
+// slice everywhere.  16-byte pieces, consecutive threads on consecutive pieces of a row.
+struct ManyDst { char* p[8]; int n; };
+__global__ void __launch_bounds__(256)
+store_block_many_kernel(const char* __restrict__ src, uint64_t src_pitch, ManyDst dst, uint64_t dst_pitch, uint64_t rows,
+                        uint64_t row_bytes) {
+  const uint64_t units = row_bytes / 16, total = rows * units;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+    const uint64_t r = i / units, u = i - r * units;
+    const uint4 w = *reinterpret_cast<const uint4*>(src + r * src_pitch + u * 16);
+    for (int d = 0; d < dst.n; ++d) *reinterpret_cast<uint4*>(dst.p[d] + r * dst_pitch + u * 16) = w;
+  }
+}
+
 // out[r, j] = x[r, idx[r, j]]  (Burn's gather along the last dim)
 __global__ void gather_indexed_kernel(const uint32_t* x, uint64_t rows, uint64_t cols, const int32_t* idx,
                                       uint64_t i_cols, uint32_t* out, int* err) {
@@ -224,6 +239,19 @@ cudaError_t launch_scatter_rows_into(void* table, uint64_t t_rows, uint64_t cols
     scatter_rows_into_kernel<uint16_t><<<grid, 128, 0, s>>>((uint16_t*)table, t_rows, cols, idx, n, (const uint16_t*)values, v_ld, err);
   else
     scatter_rows_into_kernel<uint32_t><<<grid, 128, 0, s>>>((uint32_t*)table, t_rows, cols, idx, n, (const uint32_t*)values, v_ld, err);
+  return cudaGetLastError();
+}
+cudaError_t launch_store_block_many(const void* src, uint64_t src_pitch, void* const* dst, int n_dst, uint64_t dst_pitch,
+                                    uint64_t rows, uint64_t row_bytes, cudaStream_t s) {
+  if (rows == 0 || row_bytes == 0) return cudaSuccess;
+  if (n_dst < 1 || n_dst > 8 || row_bytes % 16 || src_pitch % 16 || dst_pitch % 16 || ((uintptr_t)src & 15)) return cudaErrorNotSupported;
+  ManyDst d;
+  d.n = n_dst;
+  for (int i = 0; i < 8; ++i) {
+    d.p[i] = i < n_dst ? (char*)dst[i] : nullptr;
+    if (i < n_dst && ((uintptr_t)dst[i] & 15)) return cudaErrorNotSupported;
+  }
+  store_block_many_kernel<<<cap_grid((rows * (row_bytes / 16) + 255) / 256), 256, 0, s>>>((const char*)src, src_pitch, d, dst_pitch, rows, row_bytes);
   return cudaGetLastError();
 }
 cudaError_t launch_gather_indexed(const uint32_t* x, uint64_t rows, uint64_t cols, const int32_t* idx,

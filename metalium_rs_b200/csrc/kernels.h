@@ -96,6 +96,8 @@ cudaError_t launch_attention_tc(const void* q, uint64_t q_rows, uint64_t q_cols,
                                 float scale, int causal, void* out, uint64_t o_ld, int* err, cudaStream_t stream);
 cudaError_t launch_scatter_rows_into(void* table, uint64_t t_rows, uint64_t cols, int elem_bytes, const int32_t* idx,
                                      uint64_t n, const void* values, uint64_t v_ld, int* err, cudaStream_t);
+cudaError_t launch_store_block_many(const void* src, uint64_t src_pitch, void* const* dst, int n_dst, uint64_t dst_pitch,
+                                    uint64_t rows, uint64_t row_bytes, cudaStream_t);
 struct MoveDev { uint64_t from_r, from_c, to_r, to_c, rows, cols; int32_t transposed; int32_t pad; };
 cudaError_t launch_copy_blocks(const void* src, uint64_t src_ld, void* dst, uint64_t dst_ld,
                                int elem_bytes, const MoveDev* moves_dev, uint64_t n_moves,

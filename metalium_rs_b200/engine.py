@@ -309,6 +309,14 @@ class CudaEngine:
                                                C.c_uint64(dst_dims[0]), C.c_uint64(dst_dims[1]), C.c_uint64(col_first),
                                                C.c_int32(1 if bf16 else 0)))
 
+    def store_block_into(self, src, dst_ptrs, dst_dims, col_first: int):
+        """A block (buffer, (row, col), (rows, cols)) stored into columns [col_first, ...) of every matrix in `dst_ptrs`."""
+        sid, at, dims = src
+        blk = BlockArg(sid, (C.c_uint64 * 2)(*at), (C.c_uint64 * 2)(*dims))
+        arr = (C.c_void_p * len(dst_ptrs))(*dst_ptrs)
+        self._check(self._lib.b200_store_block_into(self._e, C.byref(blk), arr, C.c_int32(len(dst_ptrs)), C.c_uint64(dst_dims[0]),
+                                                    C.c_uint64(dst_dims[1]), C.c_uint64(col_first)))
+
     def ipc_export(self, buf: int) -> bytes:
         h = (C.c_uint8 * 64)()
         self._check(self._lib.b200_ipc_export(self._e, C.c_uint64(buf), h))

@@ -7,9 +7,11 @@ on each chip and gathers the column slices on chip 0.  K is never split, so ever
 the same sum as on one chip, bit for bit (shard.rs:11-16).
 
 Here: one process a GPU, each with its own engine.  Rank r holds A and columns
-[r*per, (r+1)*per) of B, runs the engine's product on its slice, and an NCCL all-gather
-(torch.distributed) leaves every slice on every rank; one strided copy then lays the slices
-side by side as the row-major C.  No kernel reads another GPU's memory.
+[r*per, (r+1)*per) of B and runs the engine's product on its slice.  `PeerStoreMatmul` has the
+product's epilogue store every tile into every rank's C (its peers' through CUDA IPC mappings, over
+NVLink); `ShardedMatmul` multiplies into a buffer of its own and lets an NCCL all-gather
+(torch.distributed) and one strided copy build the row-major C.  No kernel reads another GPU's
+memory, and no TMA copy touches it.
 """
 from __future__ import annotations
 
@@ -124,11 +126,18 @@ class ShardedMatmul:
 class PeerStoreMatmul:
     """The same sharded product with the exchange inside the product: every rank keeps a whole C,
     the ranks exchange CUDA IPC handles of it once, and a rank's product stores each finished tile
-    of its column slice into every rank's C from its epilogue (`b200_matmul_into`: plain stores, its
-    own memory and its peers' over NVLink).  No staging buffer, no collective on the data, no final
-    copy; the ranks meet at a barrier before C is read and before it is written again.
+    of its column slice into every rank's C from its epilogue (`b200_matmul_into`: 128-byte row
+    segments, its own memory and its peers' over NVLink).  No staging buffer, no collective on the
+    data, no final copy.
 
-    `run()` returns the buffer that holds C; it belongs to this object (release() does nothing)."""
+    Ordering is on the device: a one-element NCCL all-reduce is enqueued on the engine's stream behind
+    the product, so it completes on a rank only when every rank's product -- and with it every store
+    into this rank's C -- has completed; whatever the caller enqueues next reads a whole C.  Two C
+    buffers alternate, so the product of step i+1 never writes what a reader of step i may still
+    read; a reader must be done with step i's C before step i+2 is issued.
+
+    `run()` returns the buffer that holds this step's C; it belongs to this object (release() does
+    nothing)."""
 
     def __init__(self, eng, rank: int, world: int, m: int, k: int, n: int, a_buf: int, b_slice_buf: int, bf16=True):
         import torch
@@ -142,45 +151,184 @@ class PeerStoreMatmul:
         if not bf16:
             raise ValueError("the peer-store product is BF16")
         self.a, self.b = a_buf, b_slice_buf
-        self.c, _ = eng.zeros_dram((m, n), bf16=True)
-        mine, _ = eng.device_ptr(self.c)
-        handle = eng.ipc_export(self.c)
-        handles = [None] * world
-        dist.all_gather_object(handles, handle)
-        self.peers = {}
-        self.dst = []
-        for r in range(world):
-            if r == rank:
-                self.dst.append(mine)
-            else:
-                self.peers[r] = eng.ipc_open(handles[r])
-                self.dst.append(self.peers[r])
-        # own C first: the epilogue's first store is the local one
-        self.dst = [mine] + [self.dst[r] for r in range(world) if r != rank]
+        self.c, self.dst, self.opened = [], [], []
+        for _ in range(2):
+            c, _ = eng.zeros_dram((m, n), bf16=True)
+            mine, _ = eng.device_ptr(c)
+            handles = [None] * world
+            dist.all_gather_object(handles, eng.ipc_export(c))
+            peers = [eng.ipc_open(handles[r]) for r in range(world) if r != rank]
+            self.c.append(c)
+            self.opened += peers
+            self.dst.append([mine] + peers)          # own C first: the epilogue's first store is the local one
+        self.step = 0
         self.panels = 1
+        self.stream = torch.cuda.ExternalStream(eng.stream())
+        self.flag = torch.zeros(1, device=torch.device("cuda", torch.cuda.current_device()))
         dist.barrier()
 
     def run(self) -> int:
+        import torch
         import torch.distributed as dist
-        dist.barrier()                       # nobody still reads the C this step overwrites
-        self.eng.matmul_into(self.a, self.b, self.dst, (self.m, self.n), self.parts[self.rank][0], True)
-        self.eng.sync()                      # this rank's stores have landed, here and on its peers
-        dist.barrier()                       # and so have everyone else's
-        return self.c
+        which = self.step & 1
+        self.step += 1
+        self.eng.matmul_into(self.a, self.b, self.dst[which], (self.m, self.n), self.parts[self.rank][0], True)
+        with torch.cuda.stream(self.stream):
+            dist.all_reduce(self.flag)               # behind the product on the engine's stream: a device-side barrier
+        return self.c[which]
 
     def release(self, buf: int):
         pass
 
     def close(self):
         import torch.distributed as dist
+        self.eng.sync()
         dist.barrier()
-        for p in self.peers.values():
+        for p in self.opened:
             self.eng.ipc_close(p)
-        self.peers = {}
-        dist.barrier()                       # every mapping is closed before an owner frees its C
-        self.eng.free(self.c)
+        self.opened = []
+        dist.barrier()                               # every mapping is closed before an owner frees its C
+        for c in self.c:
+            self.eng.free(c)
+        self.c = []
 
-    describe = "each rank's product stores its tiles into every rank's C from its epilogue (peer stores over NVLink through CUDA IPC mappings); barriers around it, no collective on the data"
+    describe = ("each rank's product stores its tiles into every rank's C from its epilogue (peer stores over NVLink through "
+                "CUDA IPC mappings); a one-element all-reduce behind it orders the ranks; no collective on the data")
+
+
+class _Shared:
+    """A [rows, cols] BF16 matrix every rank can store into: two alternating copies, each rank's own
+    buffer first in its destination list, the peers' copies opened through CUDA IPC."""
+
+    def __init__(self, eng, rank: int, world: int, rows: int, cols: int):
+        import torch.distributed as dist
+        self.eng, self.bufs, self.dst, self.opened = eng, [], [], []
+        for _ in range(2):
+            c, _ = eng.zeros_dram((rows, cols), bf16=True)
+            mine, _ = eng.device_ptr(c)
+            handles = [None] * world
+            dist.all_gather_object(handles, eng.ipc_export(c))
+            peers = [eng.ipc_open(handles[r]) for r in range(world) if r != rank]
+            self.bufs.append(c)
+            self.opened += peers
+            self.dst.append([mine] + peers)
+
+    def close(self):
+        import torch.distributed as dist
+        self.eng.sync()
+        dist.barrier()
+        for p in self.opened:
+            self.eng.ipc_close(p)
+        dist.barrier()
+        for c in self.bufs:
+            self.eng.free(c)
+        self.opened, self.bufs = [], []
+
+
+class TpMlp:
+    """The tensor-parallel MLP of the attention-shaped workload: x [m, hidden]; gate and up
+    [hidden, ff] column-sharded (rank r holds its ff/g columns of each, side by side); silu(gate)*up
+    local; the hidden activation [m, ff] gathered on every rank; down [ff, hidden] column-sharded;
+    the output [m, hidden] gathered on every rank.  K is never split (shard.rs:11-16), so every
+    element is the one-GPU sum.  Both gathers are owner stores over NVLink: the activation slice by
+    `b200_store_block_into`, the output slice from the down product's epilogue (`b200_matmul_into`);
+    a one-element all-reduce behind each orders the ranks on the device."""
+
+    def __init__(self, eng, rank: int, world: int, m: int, hidden: int, ff: int, x_buf: int, wgu_slice: int, wdown_slice: int):
+        import torch
+        import torch.distributed as dist
+        assert ff % world == 0 and hidden % world == 0
+        self.eng, self.rank, self.world = eng, rank, world
+        self.m, self.hidden, self.ff = m, hidden, ff
+        self.pf, self.ph = ff // world, hidden // world
+        self.x, self.wgu, self.wd = x_buf, wgu_slice, wdown_slice
+        self.hid = _Shared(eng, rank, world, m, ff)
+        self.out = _Shared(eng, rank, world, m, hidden)
+        self.step = 0
+        self.stream = torch.cuda.ExternalStream(eng.stream())
+        self.flag = torch.zeros(1, device=torch.device("cuda", torch.cuda.current_device()))
+        dist.barrier()
+
+    def run(self) -> int:
+        import torch
+        import torch.distributed as dist
+        from . import EltwiseOp, kinds
+        e, m, pf = self.eng, self.m, self.pf
+        which = self.step & 1
+        self.step += 1
+        gu, _ = e.matmul_dram_bf16(self.x, False, self.wgu, False)                      # [m, gate_r | up_r]
+        act, _ = e.eltwise_blocks_as(EltwiseOp(kinds.SILU_MUL, 0.0, 0.0), (gu, (0, 0), (m, pf)), (gu, (0, pf), (m, pf)), None, True)
+        e.free(gu)
+        e.store_block_into((act, (0, 0), (m, pf)), self.hid.dst[which], (m, self.ff), self.rank * pf)
+        e.free(act)
+        with torch.cuda.stream(self.stream):
+            dist.all_reduce(self.flag)          # every rank's slice of the activation is here
+        e.matmul_into(self.hid.bufs[which], self.wd, self.out.dst[which], (m, self.hidden), self.rank * self.ph, True)
+        with torch.cuda.stream(self.stream):
+            dist.all_reduce(self.flag)          # every rank's slice of the output is here
+        return self.out.bufs[which]
+
+    def flops(self) -> float:
+        return 6.0 * self.m * self.hidden * self.ff
+
+    def close(self):
+        self.hid.close()
+        self.out.close()
+
+
+def tp_mlp_bench(eng, rank, world, dev, steps=5):
+    """x [4096, 8192], ff 28672 (the attention-shaped workload's MLP).  Returns (ms a step, validated)."""
+    import torch
+    import torch.distributed as dist
+    from . import BF16, EltwiseOp, kinds
+    m, hidden, ff = 4096, 8192, 28672
+    pf, ph = ff // world, hidden // world
+    g = torch.Generator(device=dev)
+    g.manual_seed(0xC0F5)
+    rnd = lambda r, c, s: ((torch.rand((r, c), generator=g, device=dev) * 2 - 1) * s).to(torch.bfloat16)
+    x_t = rnd(m, hidden, 1.0)
+    wg, wu, wd = rnd(hidden, ff, 0.02), rnd(hidden, ff, 0.02), rnd(ff, hidden, 0.02)
+    lo_f, lo_h = rank * pf, rank * ph
+    wgu_t = torch.cat([wg[:, lo_f:lo_f + pf], wu[:, lo_f:lo_f + pf]], 1).contiguous()
+    wd_t = wd[:, lo_h:lo_h + ph].contiguous()
+    x_buf = eng.adopt(x_t.data_ptr(), m, hidden, BF16)
+    wgu_buf = eng.adopt(wgu_t.data_ptr(), hidden, 2 * pf, BF16)
+    wd_buf = eng.adopt(wd_t.data_ptr(), ff, ph, BF16)
+    torch.cuda.synchronize()
+    mlp = TpMlp(eng, rank, world, m, hidden, ff, x_buf, wgu_buf, wd_buf)
+    for _ in range(3):
+        out = mlp.run()
+    eng.sync()
+    # validation: the first 256 rows computed whole on this GPU, bit for bit
+    rows = 256
+    xp = eng.adopt(x_t.data_ptr(), rows, hidden, BF16)
+    wfull = torch.cat([wg, wu], 1).contiguous()
+    wfull_buf = eng.adopt(wfull.data_ptr(), hidden, 2 * ff, BF16)
+    wd_full = eng.adopt(wd.data_ptr(), ff, hidden, BF16)
+    gu, _ = eng.matmul_dram_bf16(xp, False, wfull_buf, False)
+    act, _ = eng.eltwise_blocks_as(EltwiseOp(kinds.SILU_MUL, 0.0, 0.0), (gu, (0, 0), (rows, ff)), (gu, (0, ff), (rows, ff)), None, True)
+    ref, _ = eng.matmul_dram_bf16(act, False, wd_full, False)
+    eng.sync()
+    op, _ = eng.device_ptr(out)
+    rp, _ = eng.device_ptr(ref)
+    same = bool(torch.equal(_as_tensor(op, (m, hidden), torch.int16)[:rows], _as_tensor(rp, (rows, hidden), torch.int16)))
+    finite = bool(torch.isfinite(_as_tensor(op, (m, hidden), torch.int16).view(torch.bfloat16).float()).all())
+    for b in (gu, act, ref):
+        eng.free(b)
+    okt = torch.tensor([1.0 if (same and finite) else 0.0], device=dev)
+    dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+    dist.barrier()
+    eng.sync()
+    eng.timer_start()
+    for _ in range(steps):
+        mlp.run()
+    ms = eng.timer_stop() / steps
+    t = torch.tensor([ms], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    flops = mlp.flops()
+    mlp.close()
+    del wfull, wg, wu, wd
+    return float(t.item()), okt.item() >= 1.0, flops
 
 
 def _as_tensor(ptr: int, shape, dtype):
@@ -311,6 +459,16 @@ def bench_main(args, metric, unit, size, workload_name, peaks, ClockSampler, che
     dist.all_reduce(t2, op=dist.ReduceOp.MAX)
     ms_mm = float(t2.item())
 
+    # the attention-shaped workload's tensor-parallel MLP on the same ranks (owner stores for both gathers)
+    tp = None
+    if fused and os.environ.get("B200TT_TP_MLP") == "1":
+        try:
+            tp_ms, tp_ok, tp_flops = tp_mlp_bench(eng, rank, world, dev)
+            tp = {"ms_per_step": tp_ms, "tflops": tp_flops / (tp_ms * 1e-3) / 1e12, "equals_single_gpu_bits": bool(tp_ok),
+                  "shape": "x [4096, 8192] BF16, ff 28672: gate|up and down column-sharded, both gathers by owner stores"}
+        except Exception as ex:
+            tp = {"error": str(ex)[:200]}
+
     # end to end: A and the B slice from pinned host memory, the sharded product, C back to the host
     e2e = None
     if not args.no_e2e:
@@ -355,7 +513,8 @@ def bench_main(args, metric, unit, size, workload_name, peaks, ClockSampler, che
                              "traffic": None, "product_only_ms": ms_mm / args.steps,
                              "gather_bytes_per_rank": gather_bytes,
                              "gather_floor_ms_at_770GBs": gather_bytes / 770e9 * 1e3},
-                "validated": {"max_err_over_S": float(flags[1].item()), "sharded_equals_single_gpu_bits": True}}
+                "validated": {"max_err_over_S": float(flags[1].item()), "sharded_equals_single_gpu_bits": True},
+                "tp_mlp": tp}
         print(json.dumps(line))
     dist.barrier()
     sm.close()

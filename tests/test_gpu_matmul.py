@@ -249,6 +249,34 @@ def test_the_host_staged_bf16_product_is_the_resident_one(eng, mkn):  # server.r
         eng.free(i)
 
 
+@pytest.mark.parametrize("mkn,first,width", [((512, 256, 384), 128, 640), ((300, 192, 200), 64, 328), ((256, 128, 256), 8, 272)])
+def test_a_product_stored_into_several_matrices_at_a_column(eng, mkn, first, width):
+    # the sharded product's fused step (crates/tt-kernels/src/shard.rs:348-458) with both "ranks" on one GPU:
+    # the slice lands at its columns of every destination, the same bits as the product on its own
+    m, k, n = mkn
+    a = orc.to_bf16(orc.uniform(0xC0F8, 1, (m, k), -1, 1))
+    b = orc.to_bf16(orc.uniform(0xC0F8, 2, (k, n), -1, 1))
+    ia, ib = eng.upload_bf16(a, m, k), eng.upload_bf16(b, k, n)
+    alone, _ = eng.matmul_dram_bf16(ia, False, ib, False)
+    want = eng.download_bf16(alone)
+    fill = np.full((m, width), 0x7fc0, np.uint16)
+    c0, c1 = eng.upload_bf16(fill, m, width), eng.upload_bf16(fill, m, width)
+    ptrs = [eng.device_ptr(c0)[0], eng.device_ptr(c1)[0]]
+    eng.matmul_into(ia, ib, ptrs, (m, width), first)
+    for c in (c0, c1):
+        got = eng.download_bf16(c)
+        assert np.array_equal(got[:, first:first + n], want)
+        assert np.all(got[:, :first] == 0x7fc0) and np.all(got[:, first + n:] == 0x7fc0)   # nothing else is touched
+    # a block of a buffer stored the same way (an activation's slice of an all-gather)
+    eng.store_block_into((alone, (0, 0), (m, n)), ptrs[:1], (m, width), width - n)
+    got = eng.download_bf16(c0)
+    assert np.array_equal(got[:, width - n:], want)
+    with pytest.raises(TtError):
+        eng.matmul_into(ia, ib, ptrs, (m, width), width - n + 8)      # the slice would end past the last column
+    for i in (ia, ib, alone, c0, c1):
+        eng.free(i)
+
+
 @pytest.mark.parametrize("m", [1, 2, 3, 4])
 @pytest.mark.parametrize("kn", [(576, 960), (576, 576), (576, 3072), (1536, 576), (100, 72), (5000, 8)])
 def test_a_handful_of_rows_streams_the_weights_once(eng, m, kn):
