@@ -461,7 +461,7 @@ def bench_main(args, metric, unit, size, workload_name, peaks, ClockSampler, che
 
     # the attention-shaped workload's tensor-parallel MLP on the same ranks (owner stores for both gathers)
     tp = None
-    if fused and os.environ.get("B200TT_TP_MLP") == "1":
+    if fused and os.environ.get("B200TT_TP_MLP", "1") == "1":
         try:
             tp_ms, tp_ok, tp_flops = tp_mlp_bench(eng, rank, world, dev)
             tp = {"ms_per_step": tp_ms, "tflops": tp_flops / (tp_ms * 1e-3) / 1e12, "equals_single_gpu_bits": bool(tp_ok),
