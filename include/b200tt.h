@@ -132,6 +132,12 @@ int32_t b200_matmul_host(b200_engine*, const float* a, const float* b, const uin
 /* The same for BF16 operands and a BF16 result (F32 accumulate), its copies overlapped with the product in
  * row panels on two copy streams; returns when `out` is complete.  Pinned host memory gives the overlap. */
 int32_t b200_matmul_host_bf16(b200_engine*, const uint16_t* a, const uint16_t* b, const uint64_t mkn[3], uint16_t* out);
+/* A gated MLP's first half as one product (an extension, as `b200_attention_blocks` is): out = silu(A Bg) * (A Bu),
+ * BF16 [m, n / 2], where B [k, n] holds the gate and up weights interleaved in groups of 128 columns (columns
+ * [256t, 256t + 128) are gate columns 128t.., the next 128 the matching up columns; n % 256 == 0).  Bit for bit
+ * `matmul_dram_bf16` on [Bg | Bu] then `SILU_MUL` on its halves (crates/tt-models/src/llama.rs:498), with neither
+ * the [m, n] product nor a second launch.  Refused unless the tcgen05 path takes the product. */
+int32_t b200_matmul_silu_mul(b200_engine*, b200_buffer a, b200_buffer b, b200_buffer* out, uint64_t out_dims[2]);
 /* The sharded product's fused step: C = A B (BF16 operands as stored, no transposes) written from the
  * product's epilogue into columns [col_first, col_first + n) of each of the n_dst matrices dst[i]
  * ([dst_rows, dst_cols] row-major, of the result's type) -- this GPU's C and, through b200_ipc_open,
@@ -243,7 +249,8 @@ int32_t b200_assign_rows(b200_engine*, b200_buffer t, b200_buffer value, const u
 int32_t b200_scatter_rows(b200_engine*, b200_buffer table, b200_buffer indices, b200_buffer values,
                           int32_t column, b200_buffer* out, uint64_t out_dims[2]);
 /* `scatter_rows_into` (server.rs:389): `scatter_rows` into `table` itself -- a KV cache's step
- * write.  values is a [n, table cols] block of a buffer of the table's type (F32, I32 or BF16). */
+ * write.  values is a [n, table cols] block of a buffer of the table's type (F32, I32 or BF16), or of an F32
+ * buffer for a BF16 table: each value is then rounded once, as `cast_float` would round it. */
 int32_t b200_scatter_rows_into(b200_engine*, b200_buffer table, b200_buffer indices, const b200_block_arg* values,
                                int32_t column);
 /* The same words seen as another [rows, cols] (rows * cols unchanged): a view, no copy, the parent
@@ -279,6 +286,11 @@ typedef struct b200_attention_item { uint64_t q[2], k[2], v[2]; } b200_attention
 int32_t b200_attention_rows(b200_engine*, const b200_buffer buffers[4], const b200_attention_item* items,
                             uint64_t n_items, const uint64_t dims[4], float scale,
                             b200_buffer* out, uint64_t out_dims[2]);
+/* The same with the result's type named, as the trait's `_as` methods name it (server.rs:449): out_bf16 rounds
+ * each F32 result once, bit for bit `attention_rows` then `cast_float` (the projection after it reads BF16). */
+int32_t b200_attention_rows_as(b200_engine*, const b200_buffer buffers[4], const b200_attention_item* items,
+                               uint64_t n_items, const uint64_t dims[4], float scale, int32_t out_bf16,
+                               b200_buffer* out, uint64_t out_dims[2]);
 
 /* --- attention over whole sequences, fused (an extension beyond the `Engine` trait, as
  * `b200_softmax_rows_as` is): what burn-tt composes in `padded_attention` (ops.rs:4825-4960: a

@@ -732,6 +732,44 @@ int32_t b200_matmul_host(b200_engine* e, const float* a, const float* b, const u
   return st;
 }
 
+// silu(A Bg) * (A Bu) as one product: B holds the gate and up weights interleaved in groups of 128
+// columns (columns [256t, 256t+128) are gate columns 128t.., the next 128 the matching up columns),
+// so a 256-wide tile of the product holds both and its epilogue stores the activation.  Bit for bit
+// `matmul_dram_bf16` on [Bg | Bu] followed by `SILU_MUL` on its halves (tt-models/src/llama.rs:498).
+int32_t b200_matmul_silu_mul(b200_engine* e, b200_buffer a, b200_buffer b, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *A = nullptr, *B = nullptr;
+  int st = e->need(a, &A, "matmul_silu_mul");
+  if (!st) st = e->need(b, &B, "matmul_silu_mul");
+  if (st) return st;
+  if (A->elem != B200_BF16 || B->elem != B200_BF16) return e->fail(B200_UNSUPPORTED, "matmul_silu_mul: BF16 operands");
+  const uint64_t m = A->rows, k = A->cols, n = B->cols;
+  if (B->rows != k || k == 0 || m == 0 || n == 0 || n % 256)
+    return e->fail(B200_UNSUPPORTED, "matmul_silu_mul: [%llu,%llu] x [%llu,%llu] (the weights come in groups of 256 columns)",
+                   (unsigned long long)m, (unsigned long long)k, (unsigned long long)B->rows, (unsigned long long)n);
+  Buf* C = nullptr;
+  st = e->new_buffer(m, n / 2, B200_BF16, out, &C);
+  if (st) return st;
+  A = e->get(a); B = e->get(b);
+  GemmArgs g{};
+  g.a = A->ptr; g.b = B->ptr; g.c = C->ptr;
+  g.in_bf16 = 1; g.out_bf16 = 1;
+  g.m = m; g.n = n; g.k = k;
+  g.lda = A->cols; g.ldb = B->cols; g.ldc = n / 2;
+  g.a_trans = 0; g.b_trans = 0; g.batch = 1; g.batches_dev = nullptr;
+  g.epi_mode = 1;
+  g.sm_limit = e->matmul_sm_limit;
+  const char* why = "";
+  if (!gemm_tc_supported(g, &why)) { e->drop(*out); return e->fail(B200_UNSUPPORTED, "matmul_silu_mul: the tcgen05 path refuses this product (%s)", why); }
+  const cudaError_t ce = launch_gemm_tc(g, nullptr, e->d_err, e->stream);
+  if (ce == cudaErrorNotSupported) { e->drop(*out); return e->fail(B200_UNSUPPORTED, "matmul_silu_mul: the driver refused a tensor map for this shape"); }
+  e->matmul_path = "tcgen05";
+  st = e->launched(ce, "matmul_silu_mul");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, m, n / 2);
+  return B200_OK;
+}
+
 // C = A B written into one or more caller-named matrices instead of a new buffer: the sharded
 // product's rank writes its column slice straight into every rank's C (its own and, through
 // addresses opened with b200_ipc_open, its peers' over NVLink) from the product's epilogue.
@@ -1348,12 +1386,14 @@ int32_t b200_scatter_rows_into(b200_engine* e, b200_buffer table, b200_buffer in
   if (!st) st = e->need(values->id, &V, "scatter_rows_into");
   if (st) return st;
   const uint64_t n = I->rows * I->cols;
-  if ((column ? I->cols : I->rows) != 1 || V->elem != T->elem || values->dims[0] != n || values->dims[1] != T->cols ||
+  const bool narrow = T->elem == B200_BF16 && V->elem == B200_F32;   // F32 rows rounded once into a BF16 table
+  if ((column ? I->cols : I->rows) != 1 || (V->elem != T->elem && !narrow) || values->dims[0] != n || values->dims[1] != T->cols ||
       values->at[0] + values->dims[0] > V->rows || values->at[1] + values->dims[1] > V->cols)
     return e->fail(B200_UNSUPPORTED, "scatter_rows_into: shapes do not meet");
   const int eb = (int)elem_bytes(T->elem);
-  const char* vp = (const char*)V->ptr + (values->at[0] * V->cols + values->at[1]) * eb;
-  return e->launched(launch_scatter_rows_into(T->ptr, T->rows, T->cols, eb, (const int32_t*)I->ptr, n, vp, V->cols, e->d_err, e->stream),
+  const char* vp = (const char*)V->ptr + (values->at[0] * V->cols + values->at[1]) * elem_bytes(V->elem);
+  return e->launched(launch_scatter_rows_into(T->ptr, T->rows, T->cols, narrow ? -2 : eb, (const int32_t*)I->ptr, n, vp, V->cols, e->d_err,
+                                              e->stream),
                      "scatter_rows_into");
 }
 
@@ -1481,6 +1521,11 @@ int32_t b200_copy_blocks(b200_engine* e, b200_buffer a, const b200_block_move* m
 
 int32_t b200_attention_rows(b200_engine* e, const b200_buffer buffers[4], const b200_attention_item* items, uint64_t n_items,
                             const uint64_t dims[4], float scale, b200_buffer* out, uint64_t out_dims[2]) {
+  return b200_attention_rows_as(e, buffers, items, n_items, dims, scale, 0, out, out_dims);
+}
+
+int32_t b200_attention_rows_as(b200_engine* e, const b200_buffer buffers[4], const b200_attention_item* items, uint64_t n_items,
+                               const uint64_t dims[4], float scale, int32_t out_bf16, b200_buffer* out, uint64_t out_dims[2]) {
   cudaSetDevice(e->device);
   Buf *Q = nullptr, *K = nullptr, *V = nullptr, *M = nullptr;
   int st = e->need(buffers[0], &Q, "attention_rows");
@@ -1546,9 +1591,9 @@ int32_t b200_attention_rows(b200_engine* e, const b200_buffer buffers[4], const 
   const float* qp = (const float*)Q->ptr; const void* kp = K->ptr; const void* vp = V->ptr; const uint32_t* mp = (const uint32_t*)M->ptr;
   const uint64_t k_ld = K->cols, v_ld = V->cols;
   Buf* O = nullptr;
-  st = e->new_buffer(1, n_items * m * dv, B200_F32, out, &O);
+  st = e->new_buffer(1, n_items * m * dv, out_bf16 ? B200_BF16 : B200_F32, out, &O);
   if (st) return st;
-  float* op = (float*)O->ptr;
+  void* op = O->ptr;
   std::vector<uint8_t> blob(n_jobs * sizeof(AttnJob) + sorted.size() * sizeof(AttnRow));
   memcpy(blob.data(), jobs.data(), n_jobs * sizeof(AttnJob));
   memcpy(blob.data() + n_jobs * sizeof(AttnJob), sorted.data(), sorted.size() * sizeof(AttnRow));
@@ -1565,7 +1610,7 @@ int32_t b200_attention_rows(b200_engine* e, const b200_buffer buffers[4], const 
   const AttnJob* djobs = (const AttnJob*)dev;
   const AttnRow* drows = (const AttnRow*)((const uint8_t*)dev + n_jobs * sizeof(AttnJob));
   cudaError_t ce = launch_attention_rows(qp, kp, k_ld, vp, v_ld, kv_bf16, mp, djobs, drows, n_jobs, rt, (int)d, (int)l, (int)dv, scale,
-                                         splits, lc, (float*)scratch, op, &launches, e->stream);
+                                         splits, lc, (float*)scratch, op, out_bf16 ? 1 : 0, &launches, e->stream);
   st = e->launched(ce, "attention_rows", launches > 0 ? launches : 1);
   if (scratch) e->release(scratch, sgot);
   e->release(dev, got);

@@ -20,6 +20,7 @@
 #include <cstdlib>
 #include <cuda_runtime.h>
 
+#include "device_math.cuh"
 #include "kernels.h"
 
 namespace b200 {
@@ -48,6 +49,12 @@ template <> struct Unit<uint16_t> {
   }
 };
 
+// the result element: F32, or rounded once to BF16 (what `cast_float` would make of it)
+__device__ __forceinline__ void put(void* out, int bf16, uint64_t i, float v) {
+  if (bf16) reinterpret_cast<uint16_t*>(out)[i] = f32_to_bf16_bits(__float_as_uint(v));
+  else reinterpret_cast<float*>(out)[i] = v;
+}
+
 __device__ __forceinline__ float block_reduce(float v, bool is_max, float* sh) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -69,7 +76,7 @@ __global__ void __launch_bounds__(THREADS, RT >= 8 ? 2 : (RT >= 4 ? 3 : 4))
 attention_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, uint64_t k_ld, const KV* __restrict__ v,
                       uint64_t v_ld, const uint32_t* __restrict__ mask, const AttnJob* __restrict__ jobs,
                       const AttnRow* __restrict__ rows, int d, int l, int dv, int lc, float scale,
-                      float* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ms) {
+                      void* __restrict__ out, int out_bf16, float* __restrict__ part_o, float* __restrict__ part_ms) {
   constexpr int UN = Unit<KV>::N;
   extern __shared__ float smem[];
   __shared__ float sh[WARPS];
@@ -222,7 +229,7 @@ attention_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, uin
           if (col < dv) {
             float t = 0.f;
             for (int z = 0; z < nsl; ++z) t += red[(size_t)z * lanes_c * UN + w];
-            if (splits == 1) out[jr[r].out_off + col] = t;
+            if (splits == 1) put(out, out_bf16, jr[r].out_off + col, t);
             else part_o[(((size_t)job_i * splits + split) * RT + r) * dv + col] = t;
           }
         }
@@ -235,7 +242,7 @@ attention_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, uin
 // row = sum of rows_s * exp(max_s - M) / L.  grid (rt, jobs), a thread a column.
 __global__ void __launch_bounds__(128)
 attention_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ms, const AttnJob* __restrict__ jobs,
-                      const AttnRow* __restrict__ rows, int splits, int rt, int dv, float* __restrict__ out) {
+                      const AttnRow* __restrict__ rows, int splits, int rt, int dv, void* __restrict__ out, int out_bf16) {
   const size_t job_i = blockIdx.y, r = blockIdx.x;
   const AttnJob job = jobs[job_i];
   if ((int)r >= job.nrows) return;
@@ -246,12 +253,12 @@ attention_join_kernel(const float* __restrict__ part_o, const float* __restrict_
   float den = 0.f;
   for (int z = 0; z < splits; ++z) den += ms0[z * stride + 1] * expf(ms0[z * stride] - mx);
   den = (den < FLT_MIN) ? FLT_MIN : den;
-  float* dst = out + rows[job.row_start + r].out_off;
+  const uint64_t dst = rows[job.row_start + r].out_off;
   for (int c = threadIdx.x; c < dv; c += blockDim.x) {
     float t = 0.f;
     for (int z = 0; z < splits; ++z)
       t += part_o[((job_i * splits + z) * rt + r) * dv + c] * expf(ms0[z * stride] - mx);
-    dst[c] = t / den;
+    put(out, out_bf16, dst + c, t / den);
   }
 }
 
@@ -266,7 +273,7 @@ size_t smem_floats(int rt, int d, int lc, int dv, int kv_bf16) {
 template <typename KV, int RT>
 cudaError_t launch_rt(const float* q, const KV* k, uint64_t k_ld, const KV* v, uint64_t v_ld, const uint32_t* mask,
                       const AttnJob* jobs, const AttnRow* rows, uint64_t n_jobs, int d, int l, int dv, float scale,
-                      int splits, int lc, size_t smem, float* out, float* part_o, float* part_ms, cudaStream_t stream) {
+                      int splits, int lc, size_t smem, void* out, int out_bf16, float* part_o, float* part_ms, cudaStream_t stream) {
   static bool set = false;
   if (!set) {
     cudaError_t e = cudaFuncSetAttribute(attention_rows_kernel<KV, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
@@ -274,15 +281,15 @@ cudaError_t launch_rt(const float* q, const KV* k, uint64_t k_ld, const KV* v, u
     set = true;
   }
   attention_rows_kernel<KV, RT><<<dim3((unsigned)splits, (unsigned)n_jobs, 1), THREADS, smem, stream>>>(
-      q, k, k_ld, v, v_ld, mask, jobs, rows, d, l, dv, lc, scale, out, part_o, part_ms);
+      q, k, k_ld, v, v_ld, mask, jobs, rows, d, l, dv, lc, scale, out, out_bf16, part_o, part_ms);
   return cudaGetLastError();
 }
 
 template <typename KV>
 cudaError_t launch_kv(int rt, const float* q, const KV* k, uint64_t k_ld, const KV* v, uint64_t v_ld, const uint32_t* mask,
                       const AttnJob* jobs, const AttnRow* rows, uint64_t n_jobs, int d, int l, int dv, float scale,
-                      int splits, int lc, size_t smem, float* out, float* part_o, float* part_ms, cudaStream_t stream) {
-#define GO(R) return launch_rt<KV, R>(q, k, k_ld, v, v_ld, mask, jobs, rows, n_jobs, d, l, dv, scale, splits, lc, smem, out, part_o, part_ms, stream)
+                      int splits, int lc, size_t smem, void* out, int out_bf16, float* part_o, float* part_ms, cudaStream_t stream) {
+#define GO(R) return launch_rt<KV, R>(q, k, k_ld, v, v_ld, mask, jobs, rows, n_jobs, d, l, dv, scale, splits, lc, smem, out, out_bf16, part_o, part_ms, stream)
   if (rt <= 1) GO(1);
   if (rt <= 2) GO(2);
   if (rt <= 4) GO(4);
@@ -324,8 +331,8 @@ size_t attention_rows_scratch_floats(uint64_t n_jobs, int rt, int dv, int splits
 
 cudaError_t launch_attention_rows(const float* q, const void* k, uint64_t k_ld, const void* v, uint64_t v_ld, int kv_bf16,
                                   const uint32_t* mask, const AttnJob* jobs, const AttnRow* rows, uint64_t n_jobs, int rt,
-                                  int d, int l, int dv, float scale, int splits, int lc, float* scratch, float* out,
-                                  int* launches, cudaStream_t stream) {
+                                  int d, int l, int dv, float scale, int splits, int lc, float* scratch, void* out,
+                                  int out_bf16, int* launches, cudaStream_t stream) {
   *launches = 0;
   if (n_jobs == 0) return cudaSuccess;
   if (n_jobs > 65535 || rt > 8) return cudaErrorNotSupported;
@@ -336,13 +343,13 @@ cudaError_t launch_attention_rows(const float* q, const void* k, uint64_t k_ld, 
   float* part_ms = scratch ? scratch + (size_t)n_jobs * splits * rt * dv : nullptr;
   cudaError_t e = kv_bf16
       ? launch_kv<uint16_t>(rt, q, (const uint16_t*)k, k_ld, (const uint16_t*)v, v_ld, mask, jobs, rows, n_jobs, d, l, dv, scale,
-                            splits, lc, smem, out, part_o, part_ms, stream)
+                            splits, lc, smem, out, out_bf16, part_o, part_ms, stream)
       : launch_kv<float>(rt, q, (const float*)k, k_ld, (const float*)v, v_ld, mask, jobs, rows, n_jobs, d, l, dv, scale,
-                         splits, lc, smem, out, part_o, part_ms, stream);
+                         splits, lc, smem, out, out_bf16, part_o, part_ms, stream);
   if (e != cudaSuccess) return e;
   *launches = 1;
   if (splits > 1) {
-    attention_join_kernel<<<dim3((unsigned)rt, (unsigned)n_jobs, 1), 128, 0, stream>>>(part_o, part_ms, jobs, rows, splits, rt, dv, out);
+    attention_join_kernel<<<dim3((unsigned)rt, (unsigned)n_jobs, 1), 128, 0, stream>>>(part_o, part_ms, jobs, rows, splits, rt, dv, out, out_bf16);
     e = cudaGetLastError();
     if (e == cudaSuccess) *launches = 2;
   }

@@ -158,7 +158,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint64_t c_off = p.batches ? p.batches[b].c_off : 0;
       const uint64_t n0 = (uint64_t)tn * BN;
-      epilogue_warp<BN>(p, tmem_base + ((quad * 32u) << 16) + acc * BN, c_off, (uint64_t)tm * BM + quad * 32, n0, lane, epi_stage + quad * EPI_WARP_BYTES);
+      if constexpr (BN == 256) {
+        if (p.epi_mode == 1) epilogue_warp_silu_mul(p, tmem_base + ((quad * 32u) << 16) + acc * BN, (uint64_t)tm * BM + quad * 32, tn, lane, epi_stage + quad * EPI_WARP_BYTES);
+        else epilogue_warp<BN>(p, tmem_base + ((quad * 32u) << 16) + acc * BN, c_off, (uint64_t)tm * BM + quad * 32, n0, lane, epi_stage + quad * EPI_WARP_BYTES);
+      } else {
+        epilogue_warp<BN>(p, tmem_base + ((quad * 32u) << 16) + acc * BN, c_off, (uint64_t)tm * BM + quad * 32, n0, lane, epi_stage + quad * EPI_WARP_BYTES);
+      }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -276,6 +281,7 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int
     const double cost = (double)waves * (16.0 + (double)num_kb_host * cand / 128.0);
     if (cost < best * 0.999) { best = cost; bn = cand; }
   }
+  if (g.epi_mode == 1) bn = 256;   // the gated-activation epilogue reads a tile's two 128-column halves
   const uint32_t tiles_n = (uint32_t)((g.n + bn - 1) / bn);
 
   CUtensorMap ma, mb;
@@ -290,6 +296,7 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int
   p.batches = g.batch > 1 ? g.batches_dev : nullptr;
   p.c = g.c; p.out_bf16 = g.out_bf16; p.err = err_word;
   p.n_more = g.n_more;
+  p.epi_mode = g.epi_mode;
   p.staged = epilogue_staged(g.c, g.c_more, g.n_more, g.ldc, g.out_bf16);
   for (int i = 0; i < 7; ++i) p.c_more[i] = i < g.n_more ? g.c_more[i] : nullptr;
   p.mn_lbo = env_u32("B200TT_MN_LBO", 8192);

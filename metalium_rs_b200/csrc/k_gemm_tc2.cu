@@ -180,7 +180,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint64_t n0 = (uint64_t)tn * P_BN;
-      epilogue_warp<P_BN>(p, tmem_base + ((quad * 32u) << 16) + acc * P_BN, 0, (uint64_t)tm * 256 + rank * BM + quad * 32, n0, lane, epi_stage + quad * EPI_WARP_BYTES);
+      if (p.epi_mode == 1) epilogue_warp_silu_mul(p, tmem_base + ((quad * 32u) << 16) + acc * P_BN, (uint64_t)tm * 256 + rank * BM + quad * 32, tn, lane, epi_stage + quad * EPI_WARP_BYTES);
+      else epilogue_warp<P_BN>(p, tmem_base + ((quad * 32u) << 16) + acc * P_BN, 0, (uint64_t)tm * 256 + rank * BM + quad * 32, n0, lane, epi_stage + quad * EPI_WARP_BYTES);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(map_to_rank(smem_u32(&acc_empty[acc]), 0));
@@ -228,6 +229,7 @@ cudaError_t launch_gemm_tc2(const GemmArgs& g, int* err_word, cudaStream_t strea
   p.batch = 1; p.batches = nullptr;
   p.c = g.c; p.out_bf16 = g.out_bf16; p.err = err_word;
   p.n_more = g.n_more;
+  p.epi_mode = g.epi_mode;
   p.staged = epilogue_staged(g.c, g.c_more, g.n_more, g.ldc, g.out_bf16);
   for (int i = 0; i < 7; ++i) p.c_more[i] = i < g.n_more ? g.c_more[i] : nullptr;
   constexpr size_t smem = (size_t)P_STAGES * (BM * BK * 2 + P_HALF * BK * 2) + 1024 + 256 + EPI_BYTES;

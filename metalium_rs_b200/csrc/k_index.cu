@@ -2,6 +2,7 @@
 // crates/tt-kernels/src/session.rs:7978-8396).  A datum's sign of zero, NaN payload and
 // denormal bits survive.  An index outside its table sets the engine's error word to
 // DOMAIN and the access is skipped (crates/burn-tt/src/ops.rs:1177 "checked indices").
+#include "device_math.cuh"
 #include "kernels.h"
 
 namespace b200 {
@@ -114,6 +115,18 @@ store_block_many_kernel(const char* __restrict__ src, uint64_t src_pitch, ManyDs
     const uint64_t r = i / units, u = i - r * units;
     const uint4 w = *reinterpret_cast<const uint4*>(src + r * src_pitch + u * 16);
     for (int d = 0; d < dst.n; ++d) *reinterpret_cast<uint4*>(dst.p[d] + r * dst_pitch + u * 16) = w;
+  }
+}
+
+__global__ void __launch_bounds__(128)
+scatter_rows_narrow_kernel(uint16_t* table, uint64_t t_rows, uint64_t cols, const int32_t* idx, uint64_t n,
+                           const uint32_t* values, uint64_t v_ld, int* err) {
+  const uint64_t c = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  for (uint64_t i = 0; i < n; ++i) {
+    const int64_t r = idx[i];
+    if (r < 0 || (uint64_t)r >= t_rows) { if (c == 0) set_err(err, DOMAIN); continue; }
+    table[(uint64_t)r * cols + c] = f32_to_bf16_bits(values[i * v_ld + c]);
   }
 }
 
@@ -235,7 +248,9 @@ cudaError_t launch_scatter_rows_into(void* table, uint64_t t_rows, uint64_t cols
                                      uint64_t n, const void* values, uint64_t v_ld, int* err, cudaStream_t s) {
   if (n == 0 || cols == 0) return cudaSuccess;
   const unsigned grid = (unsigned)((cols + 127) / 128);
-  if (elem_bytes == 2)
+  if (elem_bytes == -2)   // a BF16 table, F32 values: each rounded once (what `cast_float` would store)
+    scatter_rows_narrow_kernel<<<grid, 128, 0, s>>>((uint16_t*)table, t_rows, cols, idx, n, (const uint32_t*)values, v_ld, err);
+  else if (elem_bytes == 2)
     scatter_rows_into_kernel<uint16_t><<<grid, 128, 0, s>>>((uint16_t*)table, t_rows, cols, idx, n, (const uint16_t*)values, v_ld, err);
   else
     scatter_rows_into_kernel<uint32_t><<<grid, 128, 0, s>>>((uint32_t*)table, t_rows, cols, idx, n, (const uint32_t*)values, v_ld, err);

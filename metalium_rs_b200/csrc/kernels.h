@@ -84,8 +84,8 @@ void attention_rows_plan(uint64_t n_jobs, int rt, int l, int sms, int* splits, i
 size_t attention_rows_scratch_floats(uint64_t n_jobs, int rt, int dv, int splits);
 cudaError_t launch_attention_rows(const float* q, const void* k, uint64_t k_ld, const void* v, uint64_t v_ld, int kv_bf16,
                                   const uint32_t* mask, const AttnJob* jobs, const AttnRow* rows, uint64_t n_jobs, int rt,
-                                  int d, int l, int dv, float scale, int splits, int lc, float* scratch, float* out,
-                                  int* launches, cudaStream_t stream);
+                                  int d, int l, int dv, float scale, int splits, int lc, float* scratch, void* out,
+                                  int out_bf16, int* launches, cudaStream_t stream);
 // fused attention over whole sequences (k_attention_tc.cu): element coordinates of a block's Q, K
 // and V (row, column) and the element offset of its output
 struct AttnBlockDev { int32_t q_r, q_c, k_r, k_c, v_r, v_c; int32_t pad0, pad1; uint64_t o_off; };
@@ -122,6 +122,7 @@ struct GemmArgs {
   const GemmBatch* batches_dev;  // device array when batch > 1 (or nullptr for batch 1)
   void* c_more[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   int n_more = 0;          // the tensor-core product also stores C at these addresses (same pitch as c)
+  int epi_mode = 0;        // 1: the tensor-core epilogue stores silu(gate) * up of each 256-column tile's halves (n % 256 == 0)
   int sm_limit = 0;        // > 0: the tensor-core product uses at most this many SMs (the rest stay free for a
                            // collective running beside it)
 };

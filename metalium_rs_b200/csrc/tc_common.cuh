@@ -27,6 +27,7 @@ struct TcParams {
   void* c;
   void* c_more[7];           // further copies of C with c's pitch (a peer GPU's memory among them), or none
   int n_more;
+  int epi_mode;              // 0: store the product; 1: silu(gate) * up of a tile's two 128-column halves (BN 256)
   int staged;                // the epilogue may go through shared memory (pointers and pitch are 16-byte aligned)
   int out_bf16;
   int* err;
@@ -216,6 +217,53 @@ __device__ __forceinline__ void epilogue_warp(const TcParams& p, uint32_t tacc, 
         __syncwarp();
       } else if (row_ok && col < p.n) {
         epi_store_direct(p, v, c_off + row * p.ldc + col, col);
+      }
+    }
+  }
+}
+
+// The gated-activation epilogue (epi_mode 1): B's columns come in groups of 256, gate columns
+// 128t.. in the first half and the matching up columns in the second, so a 256-wide tile holds
+// both; the tile stores 128 columns of silu(gate) * up.  The steps are the composition's
+// (crates/tt-models/src/llama.rs:498: the BF16 product, then `SILU_MUL`, crates/tt-kernels/src/sfpu/ops.rs:772):
+// each accumulator rounded to BF16 as the product's result would be, g * sigmoid(g) rounded, times u
+// rounded, BF16.  C is [m, n / 2] with pitch ldc.
+__device__ __forceinline__ uint32_t silu_mul_pair(uint32_t g0, uint32_t u0, uint32_t g1, uint32_t u1) {
+  const float a0 = bf16_bits_to_f32(f32_to_bf16_bits(g0)), b0 = bf16_bits_to_f32(f32_to_bf16_bits(u0));
+  const float a1 = bf16_bits_to_f32(f32_to_bf16_bits(g1)), b1 = bf16_bits_to_f32(f32_to_bf16_bits(u1));
+  const float r0 = __fmul_rn(__fmul_rn(a0, sigmoid_flex(a0)), b0);
+  const float r1 = __fmul_rn(__fmul_rn(a1, sigmoid_flex(a1)), b1);
+  return (uint32_t)f32_to_bf16_bits(__float_as_uint(r0)) | ((uint32_t)f32_to_bf16_bits(__float_as_uint(r1)) << 16);
+}
+
+__device__ __forceinline__ void epilogue_warp_silu_mul(const TcParams& p, uint32_t tacc, uint64_t row0, uint64_t tile_n,
+                                                       int lane, uint8_t* stage) {
+  const uint64_t row = row0 + lane;
+  const bool row_ok = row < p.m;
+  const uint64_t out_n = p.n / 2;
+#pragma unroll 1
+  for (int cb = 0; cb < 4; cb += 2) {            // 64 output columns a pass: gate chunks cb, cb+1 and up chunks 4+cb, 4+cb+1
+    uint32_t g[64], u[64];
+    tmem_ld32(tacc + cb * 32, g);
+    tmem_ld32(tacc + cb * 32 + 32, g + 32);
+    tmem_ld32(tacc + 128 + cb * 32, u);
+    tmem_ld32(tacc + 128 + cb * 32 + 32, u + 32);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    const uint64_t col = tile_n * 128 + cb * 32;  // first output column of this pass
+    uint32_t w[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) w[j] = silu_mul_pair(g[2 * j], u[2 * j], g[2 * j + 1], u[2 * j + 1]);
+    if (p.staged && col + 64 <= out_n) {
+      uint8_t* mine = stage + lane * EPI_PITCH;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(mine + q * 16) = make_uint4(w[q * 4], w[q * 4 + 1], w[q * 4 + 2], w[q * 4 + 3]);
+      __syncwarp();
+      epi_store_rows(stage, p, (row0 * p.ldc + col) * 2, p.ldc * 2, row0, lane);
+      __syncwarp();
+    } else if (row_ok) {
+      for (int dsti = -1; dsti < p.n_more; ++dsti) {
+        uint16_t* dst = (uint16_t*)(dsti < 0 ? p.c : p.c_more[dsti]) + row * p.ldc + col;
+        for (int j = 0; j < 64 && col + j < out_n; ++j) dst[j] = (uint16_t)(w[j >> 1] >> ((j & 1) * 16));
       }
     }
   }

@@ -301,6 +301,10 @@ class CudaEngine:
         self._check(self._lib.b200_matmul_host_bf16(self._e, C.c_void_p(a_ptr), C.c_void_p(b_ptr), (C.c_uint64 * 3)(*mkn),
                                                     C.c_void_p(out_ptr)))
 
+    def matmul_silu_mul(self, a: int, b: int) -> Out:
+        """silu(A Bg) * (A Bu) with B's gate and up columns interleaved in groups of 128 (see `interleave_gate_up`)."""
+        return self._call(self._lib.b200_matmul_silu_mul, C.c_uint64(a), C.c_uint64(b))
+
     def matmul_into(self, a: int, b: int, dst_ptrs, dst_dims, col_first: int, bf16: bool = True):
         """C = A B stored from the product's epilogue into columns [col_first, ...) of every matrix in
         `dst_ptrs` (device addresses: this GPU's or, opened with `ipc_open`, a peer's)."""
@@ -520,9 +524,13 @@ class CudaEngine:
         """`attention_rows([q, k, v, mask], items, [m, d, l, dv], scale)` (server.rs:257): each item is
         the (row, col) of a head's query, key and value blocks; the result is the
         [1, len(items) * m * dv] row of the heads' rows."""
+        return self.attention_rows_as(buffers, items, dims, scale, False)
+
+    def attention_rows_as(self, buffers, items, dims, scale: float, bf16: bool) -> Out:
+        """`attention_rows` with its result rounded once to BF16 where `bf16`."""
         arr = items if isinstance(items, C.Array) else self.attention_item_array(items)
-        return self._call(self._lib.b200_attention_rows, (C.c_uint64 * 4)(*buffers), arr, C.c_uint64(len(items)),
-                          (C.c_uint64 * 4)(*dims), C.c_float(scale))
+        return self._call(self._lib.b200_attention_rows_as, (C.c_uint64 * 4)(*buffers), arr, C.c_uint64(len(items)),
+                          (C.c_uint64 * 4)(*dims), C.c_float(scale), C.c_int32(1 if bf16 else 0))
 
     @staticmethod
     def attention_block_array(items):

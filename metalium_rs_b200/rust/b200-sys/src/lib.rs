@@ -9,6 +9,7 @@ use std::os::raw::{c_char, c_void};
 #[repr(C)] #[derive(Clone, Copy, Default)] pub struct b200_config { pub f32_matmul_mode: i32, pub bf16_matmul_mode: i32, pub pool_limit_bytes: u64, pub fail_alloc_at: i32, pub _pad: i32 }
 #[repr(C)] #[derive(Clone, Copy)] pub struct b200_eltwise_op { pub kind: u32, pub scalar: f32, pub scalar2: f32 }
 #[repr(C)] #[derive(Clone, Copy)] pub struct b200_block { pub at: [u64; 2], pub transposed: i32, pub _pad: i32 }
+#[repr(C)] #[derive(Clone, Copy)] pub struct b200_attention_block { pub q: [u64; 2], pub k: [u64; 2], pub v: [u64; 2], pub o: [u64; 2] }
 #[repr(C)] #[derive(Clone, Copy)] pub struct b200_attention_item { pub q: [u64; 2], pub k: [u64; 2], pub v: [u64; 2] }
 #[repr(C)] #[derive(Clone, Copy)] pub struct b200_block_move { pub from: [u64; 2], pub to: [u64; 2], pub extent: [u64; 2], pub transposed: i32, pub _pad: i32 }
 #[repr(C)] #[derive(Clone, Copy)] pub struct b200_block_arg { pub id: u64, pub at: [u64; 2], pub dims: [u64; 2] }
@@ -69,11 +70,14 @@ extern "C" {
     pub fn b200_slice_rows(a0: *mut b200_engine, a: u64, first: u64, rows: u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_copy_blocks(a0: *mut b200_engine, a: u64, moves: *const b200_block_move, n: u64, dims: *const u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_repack(a0: *mut b200_engine, a: u64, row_col_pairs: *const u64, dims: *const u64, out: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_attention_blocks(a0: *mut b200_engine, q: u64, k: u64, v: u64, items: *const b200_attention_block, n_items: u64, dims: *const u64, scale: f32, causal: i32, result_dims: *const u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_attention_rows(a0: *mut b200_engine, buffers: *const u64, items: *const b200_attention_item, n_items: u64, dims: *const u64, scale: f32, out: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_attention_rows_as(a0: *mut b200_engine, buffers: *const u64, items: *const b200_attention_item, n_items: u64, dims: *const u64, scale: f32, out_bf16: i32, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_scatter_rows_into(a0: *mut b200_engine, table: u64, indices: u64, values: *const b200_block_arg, column: i32) -> i32;
     pub fn b200_reshape(a0: *mut b200_engine, a: u64, rows: u64, cols: u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_set_matmul_sm_limit(a0: *mut b200_engine, sms: i32);
     pub fn b200_matmul_host_bf16(a0: *mut b200_engine, a: *const u16, b: *const u16, mkn: *const u64, out: *mut u16) -> i32;
+    pub fn b200_matmul_silu_mul(a0: *mut b200_engine, a: u64, b: u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_matmul_into(a0: *mut b200_engine, a: u64, b: u64, dst: *const *mut core::ffi::c_void, n_dst: i32, dst_rows: u64, dst_cols: u64, col_first: u64, out_bf16: i32) -> i32;
     pub fn b200_store_block_into(a0: *mut b200_engine, src: *const b200_block_arg, dst: *const *mut core::ffi::c_void, n_dst: i32, dst_rows: u64, dst_cols: u64, col_first: u64) -> i32;
     pub fn b200_ipc_export(a0: *mut b200_engine, buf: u64, handle: *mut u8) -> i32;

@@ -144,6 +144,15 @@ def llama_weights(cfg: LlamaConfig, seed: int = 0xC0F4, sigma: float = 0.02) -> 
     return w
 
 
+def interleave_gate_up(w: np.ndarray) -> np.ndarray:
+    """[in, gate | up] -> the layout `matmul_silu_mul` reads: groups of 256 columns, 128 gate columns then the
+    128 matching up columns."""
+    ff = w.shape[1] // 2
+    assert ff % 128 == 0
+    g, u = w[:, :ff].reshape(w.shape[0], ff // 128, 128), w[:, ff:].reshape(w.shape[0], ff // 128, 128)
+    return np.ascontiguousarray(np.concatenate([g, u], axis=2).reshape(w.shape[0], 2 * ff))
+
+
 def rope_tables(positions: int, head: int, theta: float):
     """cos and sin' = [-sin, sin] (crates/tt-models/src/rope.rs:19-60), [positions, head] F32."""
     i = np.arange(head // 2, dtype=np.float64)
@@ -158,10 +167,16 @@ class LlamaPrefill:
     """Prefill of `batch` independent causal sequences of `seq` tokens.  Weights are stored BF16;
     the residual stream is F32; projections read BF16 activations and accumulate in F32."""
 
-    def __init__(self, eng, cfg: LlamaConfig, weights: Dict[str, np.ndarray], batch: int, seq: int, fused_attention=None):
+    def __init__(self, eng, cfg: LlamaConfig, weights: Dict[str, np.ndarray], batch: int, seq: int, fused_attention=None,
+                 fused_mlp=None):
         """fused_attention: None = the fused kernel where it takes the shape (whole 128-row tiles, heads
-        of 64 or 128), True = require it, False = the composition (batched Q K^T, softmax, batched P V)."""
+        of 64 or 128), True = require it, False = the composition (batched Q K^T, softmax, batched P V).
+        fused_mlp: None = silu(gate) * up from the gate|up product's epilogue (`matmul_silu_mul`) where ff is
+        whole groups of 128 columns, False = the product then `SILU_MUL` (the same bits either way)."""
         self.eng, self.cfg, self.batch, self.seq = eng, cfg, batch, seq
+        self.fused_mlp = (cfg.ff % 128 == 0) if fused_mlp is None else bool(fused_mlp)
+        if self.fused_mlp and cfg.ff % 128:
+            raise ValueError("the fused gate|up product needs ff in whole groups of 128 columns")
         takes = seq % 128 == 0 and cfg.head_dim in (64, 128)
         if fused_attention and not takes:
             raise ValueError("the fused attention kernel does not take this shape")
@@ -170,6 +185,8 @@ class LlamaPrefill:
         self.w = {}
         for k, v in weights.items():
             self.w[k] = up(v.reshape(1, -1) if v.ndim == 1 else v)
+            if self.fused_mlp and k.endswith(".gate_up"):
+                self.w[k + ".interleaved"] = up(interleave_gate_up(v))
         cos, sin = rope_tables(seq, cfg.head_dim, cfg.theta)
         self.cos, self.sin = eng.upload(cos, *cos.shape), eng.upload(sin, *sin.shape)
         mask = np.triu(np.ones((seq, seq), np.uint32), 1)   # 1 above the diagonal: filled with -inf
@@ -229,11 +246,15 @@ class LlamaPrefill:
             # residual add and the next norm as one op (`Engine::add_rms_norm`, server.rs:466; llama.rs:288)
             (x2, _), (n2, _) = e.add_rms_norm_as(x, att, self.w[f"l{l}.norm2"], c.eps, True)
             e.free(x); e.free(att)
-            gu, _ = e.matmul_dram_bf16(n2, False, self.w[f"l{l}.gate_up"], False)
-            e.free(n2)
-            act, _ = e.eltwise_blocks_as(EltwiseOp(K.SILU_MUL, 0.0, 0.0), (gu, (0, 0), (n, c.ff)),
-                                         (gu, (0, c.ff), (n, c.ff)), None, True)   # silu(gate) * up (llama.rs:498)
-            e.free(gu)
+            if self.fused_mlp:   # silu(gate) * up stored by the gate|up product's own epilogue
+                act, _ = e.matmul_silu_mul(n2, self.w[f"l{l}.gate_up.interleaved"])
+                e.free(n2)
+            else:
+                gu, _ = e.matmul_dram_bf16(n2, False, self.w[f"l{l}.gate_up"], False)
+                e.free(n2)
+                act, _ = e.eltwise_blocks_as(EltwiseOp(K.SILU_MUL, 0.0, 0.0), (gu, (0, 0), (n, c.ff)),
+                                             (gu, (0, c.ff), (n, c.ff)), None, True)   # silu(gate) * up (llama.rs:498)
+                e.free(gu)
             d, _ = e.matmul_dram(act, False, self.w[f"l{l}.down"], False)
             e.free(act)
             if l + 1 < c.layers:
@@ -372,19 +393,20 @@ class LlamaDecode:
         e.free(emb)
         n1, _ = e.rms_norm_as(x, self.w["l0.norm1"], c.eps, True)
         scale = 1.0 / float(np.sqrt(hd))
+        qk_cols = self.q_cols + self.kv_cols
         for l in range(c.layers):
             qkv, _ = e.matmul_dram_bf16(n1, False, self.w[f"l{l}.qkv"], False)
             e.free(n1)
-            q, _ = e.rope_blocks((qkv, (0, 0), (B, self.q_cols)), (cs, (0, 0), (1, hd)), (sn, (0, 0), (1, hd)), hd, False)
-            k, _ = e.rope_blocks((qkv, (0, self.q_cols), (B, self.kv_cols)), (cs, (0, 0), (1, hd)), (sn, (0, 0), (1, hd)), hd, True)
-            e.scatter_rows_into(self.kc[l], rows, (k, (0, 0), (B, self.kv_cols)))
-            e.scatter_rows_into(self.vc[l], rows, (qkv, (0, self.q_cols + self.kv_cols), (B, self.kv_cols)))
-            e.free(k); e.free(qkv)
-            att, _ = e.attention_rows([q, self.kc[l], self.vc[l], later], self.items, [1, hd, self.attend, hd], scale)
-            e.free(q)
-            rows_view, _ = e.reshape(att, B, self.q_cols)                     # [1, B heads hd] as [B, heads hd]
-            attb, _ = e.cast_float(rows_view, True)
-            e.free(rows_view); e.free(att)
+            # RoPE on the query and key heads together, F32: the queries are read as they are, the keys are
+            # rounded once to BF16 as they are written into the cache
+            qk, _ = e.rope_blocks((qkv, (0, 0), (B, qk_cols)), (cs, (0, 0), (1, hd)), (sn, (0, 0), (1, hd)), hd, False)
+            e.scatter_rows_into(self.kc[l], rows, (qk, (0, self.q_cols), (B, self.kv_cols)))
+            e.scatter_rows_into(self.vc[l], rows, (qkv, (0, qk_cols), (B, self.kv_cols)))
+            e.free(qkv)
+            att, _ = e.attention_rows_as([qk, self.kc[l], self.vc[l], later], self.items, [1, hd, self.attend, hd], scale, True)
+            e.free(qk)
+            attb, _ = e.reshape(att, B, self.q_cols)                          # [1, B heads hd] as [B, heads hd]
+            e.free(att)
             o, _ = e.matmul_dram(attb, False, self.w[f"l{l}.o"], False)
             e.free(attb)
             (x2, _), (n2, _) = e.add_rms_norm_as(x, o, self.w[f"l{l}.norm2"], c.eps, True)

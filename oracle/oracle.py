@@ -479,6 +479,20 @@ def attention_rows(q, k, v, mask, items, dims, scale: float) -> np.ndarray:
     return np.concatenate(rows, 0).reshape(1, -1)
 
 
+def attention_blocks(q, k, v, scale: float, causal: bool):
+    """softmax(scale q k^T [causal]) v for one block in F64: what burn-tt composes in `padded_attention`
+    (crates/burn-tt/src/ops.rs:4825-4960).  Causal: query i sees keys j <= i + (sk - sq).  Returns the result
+    and sum_j p_j |v_j| (the scale of its rounding error)."""
+    sq, sk = q.shape[0], k.shape[0]
+    s = q.astype(np.float64) @ k.astype(np.float64).T * scale
+    if causal:
+        i, j = np.arange(sq)[:, None], np.arange(sk)[None, :]
+        s = np.where(j <= i + (sk - sq), s, -np.inf)
+    p = np.exp(s - s.max(1, keepdims=True))
+    p /= p.sum(1, keepdims=True)
+    return p @ v.astype(np.float64), p @ np.abs(v).astype(np.float64)
+
+
 def argmax_rows(a: np.ndarray) -> np.ndarray:
     """First maximum, first NaN wins (crates/tt-tests/tests/step211_argmax_row.rs:8-10)."""
     a = np.ascontiguousarray(a, dtype=np.float32)

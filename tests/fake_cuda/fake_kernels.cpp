@@ -42,7 +42,7 @@ int attention_rows_tile(int rows) { return rows <= 1 ? 1 : (rows <= 2 ? 2 : (row
 void attention_rows_plan(uint64_t, int, int l, int, int* splits, int* lc) { *splits = l > 256 ? 2 : 1; *lc = l > 256 ? (l / 2 + 31) / 32 * 32 : l; }
 size_t attention_rows_scratch_floats(uint64_t n, int rt, int dv, int splits) { return splits > 1 ? (size_t)n * splits * rt * (dv + 2) : 0; }
 cudaError_t launch_attention_rows(const float*, const void*, uint64_t, const void*, uint64_t, int, const uint32_t*, const AttnJob*,
-                                  const AttnRow*, uint64_t n_jobs, int, int, int, int, float, int splits, int, float*, float*,
+                                  const AttnRow*, uint64_t n_jobs, int, int, int, int, float, int splits, int, float*, void*, int,
                                   int* launches, cudaStream_t) { fake_last_attention_jobs = (int)n_jobs; *launches = splits > 1 ? 2 : 1; OK_LAUNCH; }
 bool attention_tc_supported(uint64_t sq, uint64_t d, uint64_t sk, uint64_t dv, float scale, int causal, const char** why) {
   *why = "the fake runtime follows the kernel's rules";

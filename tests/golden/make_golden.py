@@ -56,7 +56,32 @@ def build():
     step = M.mlp_step(x, y, *M.mlp_init(seed=SEED))
     out["mlp_loss"] = np.array([step["loss"]], np.float32)
     out["mlp_logits"] = step["logits"]
+    # attention for a few query rows a head (decode), its composition in F32
+    q, k, v, mask, items, dims = attention_rows_case()
+    out["attention_rows"] = orc.attention_rows(q, k, v, mask, items, dims, 0.25)
+    # attention over whole sequences (prefill), F64
+    xq, xk, xv = attention_blocks_case()
+    o, s = orc.attention_blocks(orc.from_bf16(xq), orc.from_bf16(xk), orc.from_bf16(xv), 0.125, True)
+    out["attention_blocks"] = o.astype(np.float32)
+    out["attention_blocks_scale"] = s.astype(np.float32)
+    # residual add + RMSNorm
+    out["add_rms_norm"] = orc.rms_norm((a + c).astype(np.float32), b[0], 1e-5)
     return out
+
+
+def attention_rows_case():
+    m, d, l, dv = 2, 32, 64, 32
+    q = orc.normal(SEED, 8, (2 * m, d))
+    k = orc.normal(SEED, 9, (l, d))
+    v = orc.normal(SEED, 10, (l, dv))
+    mask = np.zeros(l, np.uint32)
+    mask[50:] = 1
+    items = [((0, 0), (0, 0), (0, 0)), ((m, 0), (0, 0), (0, 0))]      # two heads on one key/value head
+    return q, k, v, mask, items, [m, d, l, dv]
+
+
+def attention_blocks_case():
+    return tuple(orc.to_bf16(orc.normal(SEED, t, (128, 64))) for t in (11, 12, 13))
 
 
 if __name__ == "__main__":

@@ -60,3 +60,20 @@ def test_kind_numbers_are_the_reference_s():
     assert (kinds.ADD_RELU, kinds.SILU, kinds.SILU_MUL, kinds.SUB_EXP, kinds.MUL_ADD, kinds.SCALE_MASK_FILL) == \
         (0x1F0, 0x1F1, 0x1F2, 0x1F3, 0x1F4, 0x1F5)
     assert kinds.INT_ADD == 0x170 and kinds.INT_LE_S == 0x18D and kinds.ROUND == 0x190
+
+
+def test_the_rust_shim_sources_follow_the_header_and_the_build():
+    # The Rust crates are shipped as source (no cargo here): keep them from drifting.  Every function the
+    # header declares is declared in b200-sys, and its build.rs compiles every CUDA source build.py does.
+    import re
+    from pathlib import Path
+    from metalium_rs_b200 import build
+    root = Path(__file__).resolve().parent.parent
+    header = (root / "include" / "b200tt.h").read_text()
+    declared = set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", header))
+    ffi = (root / "metalium_rs_b200" / "rust" / "b200-sys" / "src" / "lib.rs").read_text()
+    bound = set(re.findall(r"pub fn (b200_[a-z0-9_]+)\(", ffi))
+    assert declared == bound, (sorted(declared - bound), sorted(bound - declared))
+    build_rs = (root / "metalium_rs_b200" / "rust" / "b200-sys" / "build.rs").read_text()
+    for src in build.SOURCES:
+        assert f'"{src}"' in build_rs, src

@@ -85,5 +85,18 @@ def test_engine_matches_the_golden_vectors(eng):
     res = mlp.step(ix, iy, 16, keep=True)
     assert abs(float(eng.download(res["loss"])[0, 0]) - float(GOLD["mlp_loss"][0])) <= 1e-5 * float(GOLD["mlp_loss"][0])
     assert np.max(np.abs(eng.download(res["logits"]) - GOLD["mlp_logits"])) <= 1e-5
-    for v in list(res.values()) + [ia, ib, ic, im, ig, ico, isi, ja, jb, ha, hb, ii, ix, iy]:
+    q, k, v, amask, items, dims = G.attention_rows_case()
+    iq, ik, iv = eng.upload(q, *q.shape), eng.upload(k, *k.shape), eng.upload(v, *v.shape)
+    iam = eng.upload_bits(amask, 1, dims[2], BOOL)
+    o, _ = eng.attention_rows([iq, ik, iv, iam], items, dims, 0.25)
+    assert np.max(np.abs(eng.download(o) - GOLD["attention_rows"])) <= 1e-5 * np.abs(v).max(); eng.free(o)
+    xq, xk, xv = G.attention_blocks_case()
+    jq, jk, jv = (eng.upload_bf16(x, 128, 64) for x in (xq, xk, xv))
+    o, _ = eng.attention_blocks(jq, jk, jv, [((0, 0), (0, 0), (0, 0), (0, 0))], [128, 64, 128, 64], 0.125, True, [128, 64])
+    got = orc.from_bf16(eng.download_bf16(o)).astype(np.float64)
+    want, scale = GOLD["attention_blocks"].astype(np.float64), GOLD["attention_blocks_scale"].astype(np.float64)
+    assert np.all(np.abs(got - want) <= 2.0 ** -7 * scale + 2.0 ** -9 * np.abs(want) + 1e-6); eng.free(o)
+    (s2, _), (n2, _) = eng.add_rms_norm(ia, ic, ig, 1e-5)
+    assert np.max(np.abs(eng.download(n2) - GOLD["add_rms_norm"])) <= 1e-5 * np.abs(GOLD["add_rms_norm"]).max()
+    for v in list(res.values()) + [ia, ib, ic, im, ig, ico, isi, ja, jb, ha, hb, ii, ix, iy, iq, ik, iv, iam, jq, jk, jv, s2, n2]:
         eng.free(v)

@@ -56,6 +56,22 @@ def test_attention_rows_matches_the_composition(eng, heads, kv_heads, m, d, l, d
     assert np.all(np.abs(got - want) <= 1e-5 * vmax + 1e-7), float(np.abs(got - want).max())
 
 
+def test_attention_rows_as_rounds_the_result_once(eng):   # the trait's `_as` convention (server.rs:446-463)
+    heads, m, d, l = 6, 2, 64, 1024
+    q = orc.normal(0xA7C, 1, (heads * m, d))
+    kb, vb = orc.to_bf16(orc.normal(0xA7C, 2, (2 * l, d))), orc.to_bf16(orc.normal(0xA7C, 3, (2 * l, d)))
+    iq, ik, iv = eng.upload(q, *q.shape), eng.upload_bf16(kb, 2 * l, d), eng.upload_bf16(vb, 2 * l, d)
+    im = eng.upload_bits(np.zeros(l, np.uint32), 1, l, BOOL)
+    items = [((h * m, 0), ((h // 3) * l, 0), ((h // 3) * l, 0)) for h in range(heads)]
+    full, _ = eng.attention_rows([iq, ik, iv, im], items, [m, d, l, d], 0.125)
+    cast, _ = eng.cast_float(full, True)
+    narrow, dims = eng.attention_rows_as([iq, ik, iv, im], items, [m, d, l, d], 0.125, True)
+    assert dims == (1, heads * m * d)
+    assert np.array_equal(eng.download_bf16(narrow), eng.download_bf16(cast))
+    for i in (iq, ik, iv, im, full, cast, narrow):
+        eng.free(i)
+
+
 def test_query_rows_may_start_anywhere_in_their_buffer(eng):  # attention.rs:146-149 (`r0`)
     got, want, vmax = _case(eng, 4, 2, 3, 64, 256, 64, False, 0, 0xA78, q_row0=13)
     assert np.all(np.abs(got - want) <= 1e-5 * vmax + 1e-7)

@@ -47,6 +47,21 @@ def test_scatter_rows_into_writes_the_table_itself(eng, bf16):
         eng.free(i)
 
 
+def test_scatter_rows_into_rounds_f32_rows_into_a_bf16_table(eng):   # a BF16 cache fed F32 keys: one rounding
+    table = orc.to_bf16(orc.normal(0x6E2, 1, (16, 24)))
+    values = orc.normal(0x6E2, 2, (3, 40))
+    values[0, 8] = np.float32(1.00390625)            # a tie at the 8th mantissa bit: rounds to even
+    it, iv = eng.upload_bf16(table, 16, 24), eng.upload(values, 3, 40)
+    ii = _i32(eng, [[5, 0, 15]], 1, 3)
+    eng.scatter_rows_into(it, ii, (iv, (0, 8), (3, 24)))
+    want = table.copy()
+    for n, r in enumerate((5, 0, 15)):
+        want[r] = orc.to_bf16(values[n, 8:32])
+    assert np.array_equal(eng.download_bf16(it), want)
+    for i in (it, iv, ii):
+        eng.free(i)
+
+
 def test_scatter_rows_into_reports_a_row_outside_the_table(fresh_eng):
     e = fresh_eng
     it, iv = e.upload(np.zeros((4, 8), np.float32), 4, 8), e.upload(np.ones((1, 8), np.float32), 1, 8)
@@ -125,7 +140,7 @@ def test_a_traced_generation_is_the_eager_one(eng):
     l0 = eng.device_traffic().launches
     for _ in range(n):
         traced.replay()                              # nothing is read back between steps
-    assert eng.device_traffic().launches - l0 >= n * 12 * cfg.layers
+    assert eng.device_traffic().launches - l0 >= n * 10 * cfg.layers
     assert np.array_equal(traced.generated(0, n), toks)
     assert np.array_equal(eng.download_bits(am).view(np.int32).ravel(), toks[-1])
     eng.release_trace(traced.trace)

@@ -277,6 +277,25 @@ def test_a_product_stored_into_several_matrices_at_a_column(eng, mkn, first, wid
         eng.free(i)
 
 
+@pytest.mark.parametrize("mkf", [(4096, 576, 1536), (256, 128, 256), (300, 64, 128), (130, 192, 640)])
+def test_the_gated_product_is_the_product_then_silu_mul_bit_for_bit(eng, mkf):   # tt-models/src/llama.rs:498
+    from metalium_rs_b200 import EltwiseOp, kinds, workloads as W
+    m, k, ff = mkf
+    a = orc.to_bf16(orc.normal(0xC0F9, 1, (m, k), 1.0))
+    w = orc.to_bf16(orc.normal(0xC0F9, 2, (k, 2 * ff), 0.2))              # gate | up side by side
+    ia, iw = eng.upload_bf16(a, m, k), eng.upload_bf16(w, k, 2 * ff)
+    iwi = eng.upload_bf16(W.interleave_gate_up(w), k, 2 * ff)
+    gu, _ = eng.matmul_dram_bf16(ia, False, iw, False)
+    want, _ = eng.eltwise_blocks_as(EltwiseOp(kinds.SILU_MUL, 0.0, 0.0), (gu, (0, 0), (m, ff)), (gu, (0, ff), (m, ff)), None, True)
+    got, dims = eng.matmul_silu_mul(ia, iwi)
+    assert dims == (m, ff) and eng.last_matmul_path() == "tcgen05"
+    assert np.array_equal(eng.download_bf16(got), eng.download_bf16(want))
+    with pytest.raises(TtError):
+        eng.matmul_silu_mul(ia, eng.upload_bf16(w[:, :2 * ff - 8], k, 2 * ff - 8))   # not whole groups of 256 columns
+    for i in (ia, iw, iwi, gu, want, got):
+        eng.free(i)
+
+
 @pytest.mark.parametrize("m", [1, 2, 3, 4])
 @pytest.mark.parametrize("kn", [(576, 960), (576, 576), (576, 3072), (1536, 576), (100, 72), (5000, 8)])
 def test_a_handful_of_rows_streams_the_weights_once(eng, m, kn):

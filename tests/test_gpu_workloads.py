@@ -106,6 +106,23 @@ def test_llama_prefill_logits_and_argmax(eng, fused):
         eng.free(i)
 
 
+def test_the_fused_gate_up_product_leaves_the_prefill_s_bits_alone(eng):
+    cfg = small_llama()
+    batch, seq = 2, 128
+    w = W.llama_weights(cfg, seed=7)
+    ids = orc.integers(0xC0F4, 9, (1, batch * seq), cfg.vocab)
+    ii = eng.upload_bits(ids.view(np.uint32), 1, batch * seq, I32)
+    outs = []
+    for fused in (False, True):
+        model = W.LlamaPrefill(eng, cfg, w, batch, seq, fused_mlp=fused)
+        assert model.fused_mlp == fused
+        lg, am = model.forward(ii)
+        outs.append(eng.download_bits(lg))
+        eng.free(lg); eng.free(am)
+    assert np.array_equal(outs[0], outs[1])
+    eng.free(ii)
+
+
 def test_attention_products_on_rank4_views(eng):
     # config 5's shape scaled down: [2,4,256,128] BF16 ~ N(0,1)
     bh, t, d = 8, 256, 128

@@ -198,6 +198,19 @@ def test_matmul_into_and_ipc_handles(e):          # the sharded product's fused 
         e.ipc_export(v)                                       # a view has no allocation of its own
 
 
+def test_gated_product_dims_and_refusals(e):       # tt-models/src/llama.rs:498 as one product
+    a = e.upload_bf16(np.zeros((64, 128), np.uint16), 64, 128)
+    w = e.upload_bf16(np.zeros((128, 512), np.uint16), 128, 512)
+    out, dims = e.matmul_silu_mul(a, w)
+    assert dims == (64, 256) and e.dims_of(out) == ((64, 256), BF16)
+    for bad in (e.upload_bf16(np.zeros((128, 384), np.uint16), 128, 384),      # not whole groups of 256 columns
+                e.upload_bf16(np.zeros((64, 512), np.uint16), 64, 512),        # inner dimensions differ
+                f32(e, 128, 512)):                                             # F32 weights
+        with pytest.raises(TtError) as err:
+            e.matmul_silu_mul(a, bad)
+        assert err.value.status == 2
+
+
 def test_views_keep_their_parent_alive(e):                                      # server.rs:480-481
     t0 = e.device_traffic().pool_in_use
     a = f32(e, 64, 8)
