@@ -22,6 +22,7 @@
 
 #include "device_math.cuh"
 #include "kernels.h"
+#include "pdl.cuh"
 
 namespace b200 {
 namespace {
@@ -80,6 +81,7 @@ attention_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, uin
   constexpr int UN = Unit<KV>::N;
   extern __shared__ float smem[];
   __shared__ float sh[WARPS];
+  pdl_enter();
   float* qs = smem;                        // [RT][d]
   float* s = qs + (size_t)RT * d;          // [RT][lc]
   float* red = s + (size_t)RT * lc;        // [nsl][lanes_c * UN]: one row's slices
@@ -243,6 +245,7 @@ attention_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, uin
 __global__ void __launch_bounds__(128)
 attention_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ms, const AttnJob* __restrict__ jobs,
                       const AttnRow* __restrict__ rows, int splits, int rt, int dv, void* __restrict__ out, int out_bf16) {
+  pdl_enter();
   const size_t job_i = blockIdx.y, r = blockIdx.x;
   const AttnJob job = jobs[job_i];
   if ((int)r >= job.nrows) return;
@@ -280,8 +283,8 @@ cudaError_t launch_rt(const float* q, const KV* k, uint64_t k_ld, const KV* v, u
     if (e != cudaSuccess) return e;
     set = true;
   }
-  attention_rows_kernel<KV, RT><<<dim3((unsigned)splits, (unsigned)n_jobs, 1), THREADS, smem, stream>>>(
-      q, k, k_ld, v, v_ld, mask, jobs, rows, d, l, dv, lc, scale, out, out_bf16, part_o, part_ms);
+  launch_pdl(attention_rows_kernel<KV, RT>, dim3((unsigned)splits, (unsigned)n_jobs, 1), dim3(THREADS), smem, stream,
+             q, k, k_ld, v, v_ld, mask, jobs, rows, d, l, dv, lc, scale, out, out_bf16, part_o, part_ms);
   return cudaGetLastError();
 }
 
@@ -349,7 +352,8 @@ cudaError_t launch_attention_rows(const float* q, const void* k, uint64_t k_ld, 
   if (e != cudaSuccess) return e;
   *launches = 1;
   if (splits > 1) {
-    attention_join_kernel<<<dim3((unsigned)rt, (unsigned)n_jobs, 1), 128, 0, stream>>>(part_o, part_ms, jobs, rows, splits, rt, dv, out, out_bf16);
+    launch_pdl(attention_join_kernel, dim3((unsigned)rt, (unsigned)n_jobs, 1), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ms,
+               jobs, rows, splits, rt, dv, out, out_bf16);
     e = cudaGetLastError();
     if (e == cudaSuccess) *launches = 2;
   }

@@ -23,6 +23,7 @@
 #include <cuda_runtime.h>
 
 #include "tc_common.cuh"
+#include "pdl.cuh"
 
 namespace b200 {
 namespace {
@@ -105,6 +106,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  // barriers, tensor memory and descriptors are set up: from here on global memory is touched
+  pdl_enter();
 
   // Heaviest work first: under a causal mask a block's last query tile has the most keys, so the grid
   // runs every block's last tile, then every block's tile before it, ... (the block index is the
@@ -343,7 +346,7 @@ cudaError_t launch_d(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
     if (e != cudaSuccess) return e;
     set = true;
   }
-  attention_tc_kernel<D><<<dim3((unsigned)(n_items * p.q_tiles), 1, 1), ATTN_THREADS, smem, stream>>>(mq, mk, mv, p);
+  launch_pdl(attention_tc_kernel<D>, dim3((unsigned)(n_items * p.q_tiles), 1, 1), dim3(ATTN_THREADS), smem, stream, mq, mk, mv, p);
   return cudaGetLastError();
 }
 

@@ -9,6 +9,7 @@
 // roundings (MUL_ADD, HARD_SIGMOID, SILU_MUL ...) keeps them.
 #include "eltwise_ev.cuh"
 #include "kernels.h"
+#include "pdl.cuh"
 
 namespace b200 {
 namespace {
@@ -20,6 +21,7 @@ __global__ void __launch_bounds__(256)
 elt_vec4(const uint4* __restrict__ a, const uint32_t* __restrict__ b, uint4* __restrict__ out,
          uint64_t n4, uint32_t cols4, float s1, float s2, int* err, int streaming) {
   constexpr int U = 4;
+  pdl_enter();
   const uint64_t base = (uint64_t)blockIdx.x * (256 * U) + threadIdx.x;
   uint4 va[U], vb[U];
 #pragma unroll
@@ -135,6 +137,7 @@ __device__ __forceinline__ void store8(void* out, uint64_t off, int bf16, const 
 // arithmetic (no 64-bit division) whenever the piece count fits.
 template <uint32_t K, typename I>
 __global__ void __launch_bounds__(256) elt_rows8(EltwiseArgs g) {
+  pdl_enter();
   const I c8 = (I)(g.cols / 8);
   const I n8 = (I)(g.rows * (g.cols / 8));
   const I stride = (I)gridDim.x * blockDim.x;
@@ -192,10 +195,10 @@ cudaError_t launch_kind(const EltwiseArgs& g, cudaStream_t stream) {
     auto b = reinterpret_cast<const uint32_t*>(g.b.p);
     auto o = reinterpret_cast<uint4*>(g.out);
     switch (bm) {
-      case 0: elt_vec4<K, 0><<<grid, 256, 0, stream>>>(a, b, o, n4, cols4, g.s1, g.s2, g.err, streaming); break;
-      case 1: elt_vec4<K, 1><<<grid, 256, 0, stream>>>(a, b, o, n4, cols4, g.s1, g.s2, g.err, streaming); break;
-      case 2: elt_vec4<K, 2><<<grid, 256, 0, stream>>>(a, b, o, n4, cols4, g.s1, g.s2, g.err, streaming); break;
-      default: elt_vec4<K, 3><<<grid, 256, 0, stream>>>(a, b, o, n4, cols4, g.s1, g.s2, g.err, streaming); break;
+      case 0: launch_pdl(elt_vec4<K, 0>, dim3(grid), dim3(256), 0, stream, a, b, o, n4, cols4, g.s1, g.s2, g.err, streaming); break;
+      case 1: launch_pdl(elt_vec4<K, 1>, dim3(grid), dim3(256), 0, stream, a, b, o, n4, cols4, g.s1, g.s2, g.err, streaming); break;
+      case 2: launch_pdl(elt_vec4<K, 2>, dim3(grid), dim3(256), 0, stream, a, b, o, n4, cols4, g.s1, g.s2, g.err, streaming); break;
+      default: launch_pdl(elt_vec4<K, 3>, dim3(grid), dim3(256), 0, stream, a, b, o, n4, cols4, g.s1, g.s2, g.err, streaming); break;
     }
     return cudaGetLastError();
   }
@@ -205,8 +208,8 @@ cudaError_t launch_kind(const EltwiseArgs& g, cudaStream_t stream) {
     uint64_t blocks = (n / 16 + 255) / 256;
     if (blocks == 0) blocks = 1;
     if (blocks > 148ull * 32) blocks = 148ull * 32;
-    if (n / 8 + 2ull * blocks * 256 < 0xffffffffull) elt_rows8<K, uint32_t><<<(unsigned)blocks, 256, 0, stream>>>(g);
-    else elt_rows8<K, uint64_t><<<(unsigned)blocks, 256, 0, stream>>>(g);
+    if (n / 8 + 2ull * blocks * 256 < 0xffffffffull) launch_pdl(elt_rows8<K, uint32_t>, dim3((unsigned)blocks), dim3(256), 0, stream, g);
+    else launch_pdl(elt_rows8<K, uint64_t>, dim3((unsigned)blocks), dim3(256), 0, stream, g);
     return cudaGetLastError();
   }
   uint64_t blocks = (n + 255) / 256;
@@ -245,6 +248,7 @@ rope_kernel(Mat x, Mat cs, Mat sn, uint64_t head, void* out, uint64_t out_ld, in
 __global__ void __launch_bounds__(256)
 rope_kernel8(Mat x, Mat cs, Mat sn, uint32_t head, void* out, uint64_t out_ld, int out_bf16,
              uint64_t rows, uint32_t cols) {
+  pdl_enter();
   const uint32_t c8 = cols / 8, half = head / 2;
   const uint64_t n8 = rows * c8;
   const bool small = n8 <= 0xffffffffull;     // 32-bit divisions
@@ -316,7 +320,7 @@ cudaError_t launch_rope(const Mat& x, const Mat& cs, const Mat& sn, uint64_t hea
       (out_ld * (out_bf16 ? 2 : 4)) % 16 == 0) {
     uint64_t b8 = (n / 8 + 255) / 256;
     if (b8 > 148ull * 32) b8 = 148ull * 32;
-    rope_kernel8<<<(unsigned)b8, 256, 0, stream>>>(x, cs, sn, (uint32_t)head, out, out_ld, out_bf16, rows, (uint32_t)cols);
+    launch_pdl(rope_kernel8, dim3((unsigned)b8), dim3(256), 0, stream, x, cs, sn, (uint32_t)head, out, out_ld, out_bf16, rows, (uint32_t)cols);
     return cudaGetLastError();
   }
   uint64_t blocks = (n + 255) / 256;

@@ -15,6 +15,7 @@
 
 #include "device_math.cuh"
 #include "kernels.h"
+#include "pdl.cuh"
 
 namespace b200 {
 namespace {
@@ -28,6 +29,7 @@ __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const uint16_t* __restrict__ a, uint64_t lda, const uint16_t* __restrict__ b, uint64_t ldb,
                    void* __restrict__ c, uint64_t ldc, int out_bf16, int m, uint64_t n, int k) {
   extern __shared__ float sm[];
+  pdl_enter();
   float* as = sm;                                   // [MT][k]
   float* red = sm + (size_t)MT * k;                 // [16 warps][MT][64]
   const int tid = threadIdx.x, cg = tid & 7, ks = tid >> 3, warp = tid >> 5, lane = tid & 31;
@@ -122,8 +124,8 @@ cudaError_t launch_gemm_skinny(const GemmArgs& g, cudaStream_t stream) {
       if (e != cudaSuccess) return e;                                                                            \
       set = smem;                                                                                                \
     }                                                                                                            \
-    gemm_skinny_kernel<MT><<<grid, SK_THREADS, smem, stream>>>((const uint16_t*)g.a, g.lda, (const uint16_t*)g.b, g.ldb, g.c, \
-                                                               g.ldc, g.out_bf16, (int)g.m, g.n, (int)g.k);       \
+    launch_pdl(gemm_skinny_kernel<MT>, dim3(grid), dim3(SK_THREADS), smem, stream, (const uint16_t*)g.a, g.lda, (const uint16_t*)g.b, g.ldb, \
+               g.c, g.ldc, g.out_bf16, (int)g.m, g.n, (int)g.k);                                                   \
   } while (0)
   if (mt == 1) GO(1); else if (mt == 2) GO(2); else GO(4);
 #undef GO

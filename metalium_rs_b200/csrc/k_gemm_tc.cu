@@ -18,6 +18,7 @@
 // Every wait on an mbarrier is bounded; a wait that runs out sets the engine's error
 // word to TIMEOUT and the kernel drains and frees its tensor memory before it returns.
 #include "tc_common.cuh"
+#include "pdl.cuh"
 
 namespace b200 {
 namespace {
@@ -55,6 +56,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  // barriers, tensor memory and descriptors are set up: from here on global memory is touched
+  pdl_enter();
 
   const uint64_t total_tiles = (uint64_t)p.tiles_m * p.tiles_n * p.batch;
   const uint32_t num_kb = (uint32_t)((p.k + BK - 1) / BK);
@@ -197,7 +200,7 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const T
       if (e != cudaSuccess) return e;                                                                   \
       attr_set = true;                                                                                  \
     }                                                                                                   \
-    gemm_tc_kernel<BN, STAGES, AM, BMJ><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p);                \
+    launch_pdl(gemm_tc_kernel<BN, STAGES, AM, BMJ>, dim3(grid), dim3(NUM_THREADS), smem, stream, ma, mb, p); \
   } while (0)
   if (!a_mn && !b_mn) TC_LAUNCH(false, false);
   else if (!a_mn && b_mn) TC_LAUNCH(false, true);

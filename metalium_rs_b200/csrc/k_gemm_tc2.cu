@@ -17,6 +17,7 @@
 #include <cooperative_groups.h>
 
 #include "tc_common.cuh"
+#include "pdl.cuh"
 
 namespace b200 {
 namespace {
@@ -96,6 +97,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  // barriers, tensor memory and descriptors are set up: from here on global memory is touched
+  pdl_enter();
 
   const uint64_t total_tiles = (uint64_t)p.tiles_m * p.tiles_n;  // tiles of 256 x 256
   const uint32_t num_kb = (uint32_t)((p.k + BK - 1) / BK);
@@ -239,10 +242,12 @@ cudaError_t launch_gemm_tc2(const GemmArgs& g, int* err_word, cudaStream_t strea
   cfg.blockDim = dim3(NUM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl_enabled() ? 2 : 1;
   cudaError_t e = cudaSuccess;
 #define TC2_LAUNCH(AM, BMJ)                                                                           \
   do {                                                                                                \

@@ -4,6 +4,7 @@
 // DOMAIN and the access is skipped (crates/burn-tt/src/ops.rs:1177 "checked indices").
 #include "device_math.cuh"
 #include "kernels.h"
+#include "pdl.cuh"
 
 namespace b200 {
 namespace {
@@ -94,6 +95,7 @@ template <typename E>
 __global__ void __launch_bounds__(128)
 scatter_rows_into_kernel(E* table, uint64_t t_rows, uint64_t cols, const int32_t* idx, uint64_t n,
                          const E* values, uint64_t v_ld, int* err) {
+  pdl_enter();
   const uint64_t c = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= cols) return;
   for (uint64_t i = 0; i < n; ++i) {
@@ -121,6 +123,7 @@ store_block_many_kernel(const char* __restrict__ src, uint64_t src_pitch, ManyDs
 __global__ void __launch_bounds__(128)
 scatter_rows_narrow_kernel(uint16_t* table, uint64_t t_rows, uint64_t cols, const int32_t* idx, uint64_t n,
                            const uint32_t* values, uint64_t v_ld, int* err) {
+  pdl_enter();
   const uint64_t c = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= cols) return;
   for (uint64_t i = 0; i < n; ++i) {
@@ -249,11 +252,11 @@ cudaError_t launch_scatter_rows_into(void* table, uint64_t t_rows, uint64_t cols
   if (n == 0 || cols == 0) return cudaSuccess;
   const unsigned grid = (unsigned)((cols + 127) / 128);
   if (elem_bytes == -2)   // a BF16 table, F32 values: each rounded once (what `cast_float` would store)
-    scatter_rows_narrow_kernel<<<grid, 128, 0, s>>>((uint16_t*)table, t_rows, cols, idx, n, (const uint32_t*)values, v_ld, err);
+    launch_pdl(scatter_rows_narrow_kernel, dim3(grid), dim3(128), 0, s, (uint16_t*)table, t_rows, cols, idx, n, (const uint32_t*)values, v_ld, err);
   else if (elem_bytes == 2)
-    scatter_rows_into_kernel<uint16_t><<<grid, 128, 0, s>>>((uint16_t*)table, t_rows, cols, idx, n, (const uint16_t*)values, v_ld, err);
+    launch_pdl(scatter_rows_into_kernel<uint16_t>, dim3(grid), dim3(128), 0, s, (uint16_t*)table, t_rows, cols, idx, n, (const uint16_t*)values, v_ld, err);
   else
-    scatter_rows_into_kernel<uint32_t><<<grid, 128, 0, s>>>((uint32_t*)table, t_rows, cols, idx, n, (const uint32_t*)values, v_ld, err);
+    launch_pdl(scatter_rows_into_kernel<uint32_t>, dim3(grid), dim3(128), 0, s, (uint32_t*)table, t_rows, cols, idx, n, (const uint32_t*)values, v_ld, err);
   return cudaGetLastError();
 }
 cudaError_t launch_store_block_many(const void* src, uint64_t src_pitch, void* const* dst, int n_dst, uint64_t dst_pitch,

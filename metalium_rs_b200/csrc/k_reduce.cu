@@ -21,6 +21,7 @@
 
 #include "eltwise_ev.cuh"
 #include "kernels.h"
+#include "pdl.cuh"
 
 namespace b200 {
 namespace {
@@ -655,6 +656,7 @@ __global__ void __launch_bounds__(256)
 rms_norm_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ sum_out,
                      const void* __restrict__ gamma, int g_bf16, float eps,
                      void* __restrict__ out, int out_bf16, uint64_t rows, uint32_t cols) {
+  pdl_enter();
   const int lane = threadIdx.x & 31;
   const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
@@ -943,8 +945,8 @@ cudaError_t launch_rms_norm(const void* a, int a_bf16, const void* b, int b_bf16
     const int v = (int)((cols / 4 + 31) / 32);
 #define RN(V)                                                                                                              \
   do {                                                                                                                     \
-    if (added) rms_norm_rows_kernel<V, true><<<(unsigned)grid, 256, 0, s>>>(af, bf, sf, gamma, gamma_bf16, eps, norm_out, norm_bf16, rows, c32); \
-    else rms_norm_rows_kernel<V, false><<<(unsigned)grid, 256, 0, s>>>(af, nullptr, nullptr, gamma, gamma_bf16, eps, norm_out, norm_bf16, rows, c32); \
+    if (added) launch_pdl(rms_norm_rows_kernel<V, true>, dim3((unsigned)grid), dim3(256), 0, s, af, bf, sf, gamma, gamma_bf16, eps, norm_out, norm_bf16, rows, c32); \
+    else launch_pdl(rms_norm_rows_kernel<V, false>, dim3((unsigned)grid), dim3(256), 0, s, af, (const float*)nullptr, (float*)nullptr, gamma, gamma_bf16, eps, norm_out, norm_bf16, rows, c32); \
   } while (0)
     if (v <= 1) RN(1); else if (v <= 2) RN(2); else if (v <= 4) RN(4); else if (v <= 5) RN(5); else RN(8);
 #undef RN
