@@ -40,6 +40,7 @@ struct AttnTcParams {
   uint32_t q_tiles, k_tiles, n_items;
   int32_t causal, causal_off;   // a query i sees keys j <= i + causal_off
   float scale_log2;             // scale * log2(e)
+  int32_t spin;                 // the S -> P -> O hand-offs wait by polling
   uint16_t* out;
   uint64_t o_ld;
   int* err;
@@ -83,6 +84,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   uint64_t* o_full = p_empty + 1;
   uint32_t* tmem_slot = (uint32_t*)(o_full + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  auto hand_off = [&](uint64_t* bar, uint32_t parity) -> bool {   // a wait on the chain S -> P -> O
+    return p.spin ? mbar_wait_spin(bar, parity, abort_flag) : mbar_wait(bar, parity, abort_flag);
+  };
   float* xmax = (float*)(sP + P_BYTES + 256);   // [2][128]: the two halves' row maxima
   float* xsum = xmax + 256;                     // [2][128]: and row sums
 
@@ -180,7 +184,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
       auto issue_qk = [&]() -> bool {
         const uint32_t buf = t & 1, sph = (t >> 1) & 1;
-        if (!mbar_wait(&s_empty[buf], sph ^ 1, abort_flag)) return false;
+        if (!hand_off(&s_empty[buf], sph ^ 1)) return false;
         if (!mbar_wait(&k_full[ks], kph, abort_flag)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t k_addr = smem_u32(sK + ks * OP_BYTES);
@@ -199,7 +203,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (ok) ok = issue_qk();                                           // pass 2, tile 0
       for (uint32_t j = 0; j < nk && ok; ++j) {
         if (j + 1 < nk) { ok = issue_qk(); if (!ok) break; }             // the next scores run under these exponentials
-        if (!mbar_wait(p_full, j & 1, abort_flag)) { ok = false; break; }
+        if (!hand_off(p_full, j & 1)) { ok = false; break; }
         if (!mbar_wait(&v_full[vs], vph, abort_flag)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t v_addr = smem_u32(sV + vs * OP_BYTES);
@@ -232,7 +236,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     float mx = -INFINITY;
     for (uint32_t j = 0; j < nk && ok; ++j, ++t) {
       const uint32_t buf = t & 1, sph = (t >> 1) & 1;
-      if (!mbar_wait(&s_full[buf], sph, abort_flag)) { ok = false; break; }
+      if (!hand_off(&s_full[buf], sph)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int32_t key0 = (int32_t)(j * 128 + half * 64);
       uint32_t v[64];
@@ -259,7 +263,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     float sum = 0.f;
     for (uint32_t j = 0; j < nk && ok; ++j, ++t) {
       const uint32_t buf = t & 1, sph = (t >> 1) & 1;
-      if (!mbar_wait(&s_full[buf], sph, abort_flag)) { ok = false; break; }
+      if (!hand_off(&s_full[buf], sph)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int32_t key0 = (int32_t)(j * 128 + half * 64);
       uint32_t v[64];
@@ -286,7 +290,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       sum += s0 + s1;
       // P is single-buffered: the product with V of the tile before must have read it
-      if (!mbar_wait(p_empty, (j & 1) ^ 1, abort_flag)) { ok = false; break; }
+      if (!hand_off(p_empty, (j & 1) ^ 1)) { ok = false; break; }
       uint8_t* prow = sP + half * TILE_BYTES + row * 128;
 #pragma unroll
       for (int u = 0; u < 8; ++u)
@@ -380,6 +384,11 @@ cudaError_t launch_attention_tc(const void* q, uint64_t q_rows, uint64_t q_cols,
   p.causal = causal ? 1 : 0;
   p.causal_off = (int32_t)(sk - sq);
   p.scale_log2 = scale * 1.4426950408889634f;
+  {
+    static int spin = -1;
+    if (spin < 0) { const char* e = getenv("B200TT_ATTN_SPIN"); spin = (e && e[0] == '0') ? 0 : 1; }
+    p.spin = spin;
+  }
   p.out = (uint16_t*)out;
   p.o_ld = o_ld;
   p.err = err;
