@@ -271,6 +271,66 @@ int32_t b200_copy_blocks(b200_engine*, b200_buffer a, const b200_block_move* mov
 int32_t b200_repack(b200_engine*, b200_buffer a, const uint64_t* row_col_pairs, const uint64_t dims[2],
                     b200_buffer* out, uint64_t out_dims[2]);
 
+/* `repack_many(inputs, sources:[(input, [row, col])] in output order, dims)` (server.rs:317;
+ * crates/tt-kernels/src/tensor.rs:6791): triples = {input ordinal, row, col} an output element; the inputs
+ * share one element type; rows * cols == n_triples and neither is zero, else UNSUPPORTED; a source outside
+ * its input is DOMAIN. */
+int32_t b200_repack_many(b200_engine*, const b200_buffer* inputs, uint64_t n_inputs, const uint64_t* triples,
+                         uint64_t n_triples, const uint64_t dims[2], b200_buffer* out, uint64_t out_dims[2]);
+/* `select_taps(table, indices [taps, n] I32, zero_row)` (server.rs:309; crates/tt-kernels/src/index.rs:136-160,
+ * crates/tt-kernels/src/session.rs:8068-8084): the result is [n, (taps - 1) * ceil32(cols) + cols]; its row i
+ * holds row indices[t][i] of the table from column t * ceil32(cols) for each tap t, and zeros in the columns
+ * between one tap's end and the next one's start.  With zero_row an index equal to the table's rows reads a
+ * row of zeros.  Any other index outside the table sets DOMAIN on the device. */
+int32_t b200_select_taps(b200_engine*, b200_buffer table, b200_buffer indices, int32_t zero_row, b200_buffer* out,
+                         uint64_t out_dims[2]);
+/* server.rs:137 `cast_block`: `cast_float` of a block of a buffer, a new buffer of the block's dims. */
+int32_t b200_cast_block(b200_engine*, const b200_block_arg* a, int32_t to_bf16, b200_buffer* out, uint64_t out_dims[2]);
+/* server.rs:779 `cast_f16`: F32 -> IEEE binary16 (ties to even, subnormals kept, NaN quiet with its top ten
+ * payload bits) in a two-byte buffer that reads back through `b200_download_bf16`, as the reference keeps FP16
+ * in BF16's raw storage (server.rs:2189-2200); or such a buffer widened, exactly, to F32. */
+int32_t b200_cast_f16(b200_engine*, b200_buffer a, int32_t to_f16, b200_buffer* out, uint64_t out_dims[2]);
+/* server.rs:578 `pow`: x^y as powf; exponent_kind 0 = an F32 buffer of x's shape, 1 = the scalar, 2 = an I32
+ * buffer of x's shape (`PowArg`, server.rs:35-39).  The kinds are POW, POW_S and POW_I of `b200_eltwise`. */
+int32_t b200_pow(b200_engine*, b200_buffer x, int32_t exponent_kind, b200_buffer y, float scalar, b200_buffer* out,
+                 uint64_t out_dims[2]);
+/* server.rs:414 `scan`: inclusive scan down the rows of every column (crates/tt-kernels/src/sfpu/scan.rs:19-41).
+ * F32 Sum and Prod are left folds in row order from +0.0 and 1.0; Min/Max order raw words by `total_cmp`;
+ * MinNan/MaxNan take a NaN, keep the earlier of equal values; the I* ops take and give I32 (wrapping sum and
+ * product, signed min and max).  The input's element type must be the op's. */
+enum b200_scan_op { B200_SCAN_SUM = 0, B200_SCAN_PROD, B200_SCAN_MIN, B200_SCAN_MAX, B200_SCAN_MIN_NAN,
+                    B200_SCAN_MAX_NAN, B200_SCAN_ISUM, B200_SCAN_IPROD, B200_SCAN_IMIN, B200_SCAN_IMAX };
+int32_t b200_scan(b200_engine*, b200_buffer a, int32_t op, b200_buffer* out, uint64_t out_dims[2]);
+/* server.rs:758 `sort_planes` with `Spec{elem, n, descending, indices}` (crates/tt-kernels/src/sfpu/sort.rs:112-122):
+ * `a` is a planes matrix [32 * T, 32 * blocks], T the power of two of 32-position tiles holding n <= 1024
+ * positions, problem q's position e at sort.rs:198's coordinate.  keys (a's shape and type) and, when
+ * `indices` is not NULL, the original positions (I32) hold each problem's first n positions in the stable
+ * order on (key, index): `total_cmp` for F32, two's complement for I32, keys reversed when descending.  What
+ * lies past n is unspecified, as in the reference (sort.rs:699-700). */
+int32_t b200_sort_planes(b200_engine*, b200_buffer a, int32_t elem, uint64_t n, int32_t descending,
+                         b200_buffer* keys, b200_buffer* indices, uint64_t out_dims[2]);
+/* server.rs:768 `random_dram(dims, draw, base)`: a tensor drawn on the device from the seed `base`, with no
+ * upload.  draw (crates/burn-tt/src/random.rs:73-90): 0 Unit [0,1); 1 Uniform(a, b) -> [a, b); 2 Bernoulli(p = a);
+ * 3 Normal(mean a, std b); 4 IntRange(lo, hi) -> [lo, hi), hi - lo <= 2^23; 5 IntWords.  as_int makes Bernoulli
+ * and Normal I32 (the normal truncated toward zero).  A datum depends on (base, draw, position) only.  The
+ * stream is this engine's own: the reference's differs between its simulator and its silicon and is not a
+ * value to match (crates/tt-kernels/src/prng.rs:49-50); the distributions' arithmetic is the reference's. */
+int32_t b200_random(b200_engine*, const uint64_t dims[2], int32_t draw, float a, float b, int32_t lo, int32_t hi,
+                    int32_t as_int, uint64_t base, b200_buffer* out, uint64_t out_dims[2]);
+/* server.rs:118 `pool_bf16(a, windows, divisors, dims)` (crates/tt-kernels/src/fpu.rs:39-132): `a` is BF16; window w
+ * is coords[2 * offsets[w] .. 2 * offsets[w + 1]) as [row, col] pairs; the F32 [dims] result holds at element w (row
+ * major) the window's sum, taken sixteen values a block with the blocks' partial sums added in order, divided by
+ * divisors[w].  Refused as the reference refuses (fpu.rs:48-57): dims[0] * dims[1] != n_windows, no windows, an
+ * empty window, a divisor of 0 or above 2^24; a coordinate outside `a` is DOMAIN. */
+int32_t b200_pool_bf16(b200_engine*, b200_buffer a, const uint64_t* offsets, const uint64_t* coords, const uint64_t* divisors,
+                       uint64_t n_windows, const uint64_t dims[2], b200_buffer* out, uint64_t out_dims[2]);
+/* server.rs:95 `metadata`: operation geometry as a resident buffer of words (an upload whose content the
+ * engine may keep and share). */
+int32_t b200_metadata(b200_engine*, const uint32_t* bits, const uint64_t dims[2], int32_t elem, b200_buffer* out);
+/* server.rs:705 `gddr_free_bytes`: (largest block that can be had now, all free bytes) of device memory,
+ * the pool's idle blocks included. */
+int32_t b200_free_bytes(b200_engine*, uint64_t out[2]);
+
 /* --- attention for a few query rows a key/value head, as one op: server.rs:257 `attention_rows`
  * (kernel contract: crates/tt-kernels/src/attention.rs:360-372).  buffers = [q, k, v, mask]; item i
  * names the top-left element of head i's blocks: q_i [m, d] (F32), K_i [l, d] and V_i [l, dv]

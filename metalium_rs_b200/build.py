@@ -37,6 +37,10 @@ SOURCES = {
     "k_gemm_skinny.cu": [],
     "k_attention.cu": [],
     "k_attention_tc.cu": [],
+    "k_convert.cu": [],
+    "k_pool.cu": ["-fmad=false"],
+    "k_scan_sort.cu": ["-fmad=false"],
+    "k_random.cu": ["-fmad=false"],
 }
 
 

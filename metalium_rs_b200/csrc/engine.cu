@@ -13,6 +13,7 @@
 #include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
+#include <cmath>
 
 #include <algorithm>
 #include <map>
@@ -1697,6 +1698,309 @@ int32_t b200_repack(b200_engine* e, b200_buffer a, const uint64_t* pairs, const 
     if (st) { e->drop(*out); return st; }
   }
   set_dims(out_dims, dims[0], dims[1]);
+  return B200_OK;
+}
+
+// ---- more movement and conversions: server.rs:95,137,309,317,578,705,779 -----------------------------
+int32_t b200_repack_many(b200_engine* e, const b200_buffer* inputs, uint64_t n_inputs, const uint64_t* triples,
+                         uint64_t n_triples, const uint64_t dims[2], b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  if (n_inputs == 0) return e->fail(B200_UNSUPPORTED, "repack_many: no inputs");
+  if (dims[0] == 0 || dims[1] == 0) return e->fail(B200_UNSUPPORTED, "repack_many: an empty result");
+  if (dims[0] * dims[1] != n_triples)     // crates/tt-kernels/src/tensor.rs:6803
+    return e->fail(B200_UNSUPPORTED, "repack_many: %llu sources for a [%llu, %llu] result", (unsigned long long)n_triples,
+                   (unsigned long long)dims[0], (unsigned long long)dims[1]);
+  std::vector<Buf*> src(n_inputs);
+  for (uint64_t i = 0; i < n_inputs; ++i) {
+    int st = e->need(inputs[i], &src[i], "repack_many");
+    if (st) return st;
+    if (src[i]->elem != src[0]->elem) return e->fail(B200_UNSUPPORTED, "repack_many: input %llu is not of the first's element type", (unsigned long long)i);
+  }
+  const int elem = src[0]->elem;
+  const uint64_t eb = elem_bytes(elem), n = dims[0] * dims[1];
+  std::vector<uint64_t> addrs(n);
+  for (uint64_t i = 0; i < n; ++i) {
+    const uint64_t s = triples[3 * i], r = triples[3 * i + 1], c = triples[3 * i + 2];
+    if (s >= n_inputs || r >= src[s]->rows || c >= src[s]->cols)
+      return e->fail(B200_DOMAIN, "repack_many: DOMAIN: source %llu names (%llu, [%llu, %llu])", (unsigned long long)i,
+                     (unsigned long long)s, (unsigned long long)r, (unsigned long long)c);
+    addrs[i] = (uint64_t)(uintptr_t)((const char*)src[s]->ptr + (r * src[s]->cols + c) * eb);
+  }
+  Buf* O = nullptr;
+  int st = e->new_buffer(dims[0], dims[1], elem, out, &O);
+  if (st) return st;
+  void* op = O->ptr;
+  void* dev = nullptr; uint64_t got = 0;
+  st = e->to_device(addrs.data(), n * 8, &dev, &got);
+  if (st) { e->drop(*out); return st; }
+  st = e->launched(launch_gather_addrs((const uint64_t*)dev, n, (int)eb, op, e->stream), "repack_many");
+  e->release(dev, got);
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, dims[0], dims[1]);
+  return B200_OK;
+}
+
+int32_t b200_select_taps(b200_engine* e, b200_buffer table, b200_buffer indices, int32_t zero_row, b200_buffer* out,
+                         uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *T = nullptr, *I = nullptr;
+  int st = e->need(table, &T, "select_taps");
+  if (!st) st = index_buf(e, indices, &I, "select_taps");
+  if (st) return st;
+  const uint64_t taps = I->rows, n = I->cols, cols = T->cols, trows = T->rows;
+  if (taps == 0 || cols == 0) return e->fail(B200_UNSUPPORTED, "select_taps: no taps or an empty table");
+  const uint64_t out_cols = (taps - 1) * ((cols + 31) / 32 * 32) + cols;
+  const int elem = T->elem;
+  const void* tp = T->ptr; const int32_t* ip = (const int32_t*)I->ptr;
+  Buf* O = nullptr;
+  st = e->new_buffer(n, out_cols, elem, out, &O);
+  if (st) return st;
+  st = e->launched(launch_select_taps(tp, trows, cols, (int)elem_bytes(elem), ip, taps, n, zero_row != 0, O->ptr, out_cols, e->d_err,
+                                      e->stream), "select_taps");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, n, out_cols);
+  return B200_OK;
+}
+
+int32_t b200_cast_block(b200_engine* e, const b200_block_arg* a, int32_t to_bf16, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf* A = nullptr;
+  int st = e->need(a->id, &A, "cast_block");
+  if (st) return st;
+  if (A->elem != (to_bf16 ? B200_F32 : B200_BF16)) return e->fail(B200_UNSUPPORTED, "cast_block: source elem %d", A->elem);
+  const uint64_t rows = a->dims[0], cols = a->dims[1];
+  if (a->at[0] + rows > A->rows || a->at[1] + cols > A->cols)
+    return e->fail(B200_UNSUPPORTED, "cast_block: block [%llu, %llu] at [%llu, %llu] leaves its [%llu, %llu] buffer", (unsigned long long)rows,
+                   (unsigned long long)cols, (unsigned long long)a->at[0], (unsigned long long)a->at[1], (unsigned long long)A->rows,
+                   (unsigned long long)A->cols);
+  const uint64_t ld = A->cols;
+  const char* src = (const char*)A->ptr + (a->at[0] * ld + a->at[1]) * elem_bytes(A->elem);
+  Buf* O = nullptr;
+  st = e->new_buffer(rows, cols, to_bf16 ? B200_BF16 : B200_F32, out, &O);
+  if (st) return st;
+  st = e->launched(launch_cast_block(src, ld, O->ptr, rows, cols, to_bf16 != 0, e->stream), "cast_block");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
+}
+
+int32_t b200_cast_f16(b200_engine* e, b200_buffer a, int32_t to_f16, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf* A = nullptr;
+  int st = e->need(a, &A, "cast_f16");
+  if (st) return st;
+  if (A->elem != (to_f16 ? B200_F32 : B200_BF16))
+    return e->fail(B200_UNSUPPORTED, "cast_f16: source elem %d (F32 narrows; two-byte storage widens)", A->elem);
+  const uint64_t rows = A->rows, cols = A->cols;
+  const void* src = A->ptr;
+  Buf* O = nullptr;
+  st = e->new_buffer(rows, cols, to_f16 ? B200_BF16 : B200_F32, out, &O);
+  if (st) return st;
+  st = e->launched(launch_cast_f16(src, O->ptr, rows * cols, to_f16 != 0, e->stream), "cast_f16");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
+}
+
+int32_t b200_pow(b200_engine* e, b200_buffer x, int32_t exponent_kind, b200_buffer y, float scalar, b200_buffer* out,
+                 uint64_t out_dims[2]) {
+  b200_eltwise_op op{};
+  if (exponent_kind == 1) { op.kind = kind::POW_S; op.scalar = scalar; return b200_eltwise(e, &op, x, 0, 0, 0, out, out_dims); }
+  if (exponent_kind != 0 && exponent_kind != 2) return e->fail(B200_UNSUPPORTED, "pow: exponent kind %d", exponent_kind);
+  Buf *X = nullptr, *Y = nullptr;
+  int st = e->need(x, &X, "pow");
+  if (!st) st = e->need(y, &Y, "pow");
+  if (st) return st;
+  if (Y->rows != X->rows || Y->cols != X->cols)     // crates/tt-kernels/src/session.rs:7746-7752
+    return e->fail(B200_UNSUPPORTED, "pow: an exponent [%llu, %llu] for [%llu, %llu]", (unsigned long long)Y->rows, (unsigned long long)Y->cols,
+                   (unsigned long long)X->rows, (unsigned long long)X->cols);
+  if (Y->elem != (exponent_kind == 2 ? B200_I32 : B200_F32)) return e->fail(B200_UNSUPPORTED, "pow: exponent elem %d", Y->elem);
+  op.kind = exponent_kind == 2 ? kind::POW_I : kind::POW;
+  return b200_eltwise(e, &op, x, y, 0, 0, out, out_dims);
+}
+
+int32_t b200_scan(b200_engine* e, b200_buffer a, int32_t op, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf* A = nullptr;
+  int st = e->need(a, &A, "scan");
+  if (st) return st;
+  if (op < B200_SCAN_SUM || op > B200_SCAN_IMAX) return e->fail(B200_UNSUPPORTED, "scan: op %d", op);
+  const int want = op >= B200_SCAN_ISUM ? B200_I32 : B200_F32;     // crates/tt-kernels/src/sfpu/scan.rs:44-49
+  if (A->elem != want) return e->fail(B200_UNSUPPORTED, "scan: op %d takes elem %d, the buffer holds %d", op, want, A->elem);
+  const uint64_t rows = A->rows, cols = A->cols;
+  const uint32_t* src = (const uint32_t*)A->ptr;
+  Buf* O = nullptr;
+  st = e->new_buffer(rows, cols, want, out, &O);
+  if (st) return st;
+  uint32_t* dst = (uint32_t*)O->ptr;
+  const uint64_t chunks = scan_chunks(op, rows, cols);
+  void* carry = nullptr; uint64_t got = 0;
+  if (chunks > 1) {
+    st = e->alloc(chunks * cols * 4, &carry, &got);
+    if (st) { e->drop(*out); return st; }
+  }
+  st = e->launched(launch_scan(src, dst, rows, cols, op, (uint32_t*)carry, e->stream), "scan", chunks > 1 ? 2 : 1);
+  if (carry) e->release(carry, got);
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
+}
+
+int32_t b200_sort_planes(b200_engine* e, b200_buffer a, int32_t elem, uint64_t n, int32_t descending, b200_buffer* keys,
+                         b200_buffer* indices, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf* A = nullptr;
+  int st = e->need(a, &A, "sort_planes");
+  if (st) return st;
+  // crates/tt-kernels/src/sfpu/sort.rs:132-146 (what a sort refuses) and :705-713 (the planes' shape)
+  if (elem != B200_F32 && elem != B200_I32) return e->fail(B200_UNSUPPORTED, "sort of elem %d (F32 and I32 only)", elem);
+  if (n == 0) return e->fail(B200_UNSUPPORTED, "sort of an empty axis");
+  if (n > 1024) return e->fail(B200_UNSUPPORTED, "axis length %llu exceeds the device sort's limit of 1024", (unsigned long long)n);
+  if (A->elem != elem) return e->fail(B200_UNSUPPORTED, "sort_planes: the planes hold elem %d, the sort is of %d", A->elem, elem);
+  uint64_t tiles = 1;
+  while (tiles * 32 < n) tiles <<= 1;
+  if (A->rows != 32 * tiles || A->cols % 32 != 0 || A->cols == 0)
+    return e->fail(B200_UNSUPPORTED, "sort planes [%llu, %llu] for %llu axis positions (want [%llu, a multiple of 32])", (unsigned long long)A->rows,
+                   (unsigned long long)A->cols, (unsigned long long)n, (unsigned long long)(32 * tiles));
+  const uint64_t rows = A->rows, cols = A->cols;
+  const uint32_t* src = (const uint32_t*)A->ptr;
+  Buf *K = nullptr, *I = nullptr;
+  st = e->new_buffer(rows, cols, elem, keys, &K);
+  if (st) return st;
+  uint32_t* kp = (uint32_t*)K->ptr;
+  uint32_t* ip = nullptr;
+  if (indices) {
+    st = e->new_buffer(rows, cols, B200_I32, indices, &I);
+    if (st) { e->drop(*keys); return st; }
+    ip = (uint32_t*)I->ptr;
+  }
+  st = e->launched(launch_sort_planes(src, rows, cols, (uint32_t)n, elem == B200_I32, descending != 0, kp, ip, e->stream), "sort_planes");
+  if (st) { e->drop(*keys); if (indices) e->drop(*indices); return st; }
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
+}
+
+int32_t b200_random(b200_engine* e, const uint64_t dims[2], int32_t draw, float a, float b, int32_t lo, int32_t hi, int32_t as_int,
+                    uint64_t base, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  float p0 = a, p1 = b;
+  int32_t i0 = 0, i1 = 0;
+  int elem = B200_F32;
+  switch (draw) {      // what each draw refuses: crates/tt-kernels/src/prng.rs:462-466, 487-491, 517-521, 574-578
+    case 0: break;
+    case 1: {
+      const float scale = b - a;
+      if (!(std::isfinite(a) && std::isfinite(b) && a < b && std::isfinite(scale) && scale > 0.0f))
+        return e->fail(B200_UNSUPPORTED, "uniform [%g, %g) is not a finite, nonempty interval", a, b);
+      uint32_t bits; memcpy(&bits, &b, 4);                  // the float below hi (prng.rs:322-329)
+      if (b == 0.0f) bits = 0x80000001u; else bits = b > 0.0f ? bits - 1 : bits + 1;
+      i1 = (int32_t)bits;
+      break;
+    }
+    case 2:
+      if (!(a >= 0.0f && a <= 1.0f)) return e->fail(B200_UNSUPPORTED, "Bernoulli probability %g is not in [0, 1]", a);
+      if (as_int) elem = B200_I32;
+      break;
+    case 3:
+      if (!(std::isfinite(a) && std::isfinite(b) && b >= 0.0f)) return e->fail(B200_UNSUPPORTED, "normal(mean %g, std %g) needs finite mean and std >= 0", a, b);
+      if (as_int) elem = B200_I32;
+      break;
+    case 4: {
+      const int64_t range = (int64_t)hi - (int64_t)lo;
+      if (range < 1 || range > (1ll << 23))
+        return e->fail(B200_UNSUPPORTED, "integer uniform [%d, %d): a range of %lld outside 1..=8388608", lo, hi, (long long)range);
+      p0 = (float)range; i0 = lo; elem = B200_I32;
+      break;
+    }
+    case 5: elem = B200_I32; break;
+    default: return e->fail(B200_UNSUPPORTED, "random: draw %d", draw);
+  }
+  Buf* O = nullptr;
+  int st = e->new_buffer(dims[0], dims[1], elem, out, &O);
+  if (st) return st;
+  st = e->launched(launch_random((uint32_t*)O->ptr, dims[0] * dims[1], draw, p0, p1, i0, i1, as_int != 0, base, e->stream), "random");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, dims[0], dims[1]);
+  return B200_OK;
+}
+
+int32_t b200_pool_bf16(b200_engine* e, b200_buffer a, const uint64_t* offsets, const uint64_t* coords, const uint64_t* divisors,
+                       uint64_t n_windows, const uint64_t dims[2], b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf* A = nullptr;
+  int st = e->need(a, &A, "pool_bf16");
+  if (st) return st;
+  if (A->elem != B200_BF16) return e->fail(B200_UNSUPPORTED, "pool_bf16: no BF16 buffer %llu", (unsigned long long)a);
+  if (n_windows == 0 || dims[0] * dims[1] != n_windows) return e->fail(B200_UNSUPPORTED, "pool_bf16: invalid BF16 pool windows (%llu for [%llu, %llu])",
+                                                                       (unsigned long long)n_windows, (unsigned long long)dims[0], (unsigned long long)dims[1]);
+  const uint64_t total = offsets[n_windows];
+  if (total > 0xffffffffull || A->rows * A->cols > 0xffffffffull) return e->fail(B200_UNSUPPORTED, "pool_bf16: more than 2^32 taps or elements");
+  std::vector<uint32_t> meta(n_windows + 1 + total);      // offsets, then the taps' element offsets
+  std::vector<float> div(n_windows);
+  for (uint64_t w = 0; w < n_windows; ++w) {
+    if (offsets[w + 1] <= offsets[w]) return e->fail(B200_UNSUPPORTED, "pool_bf16: window %llu is empty", (unsigned long long)w);
+    if (divisors[w] == 0 || divisors[w] > (1ull << 24)) return e->fail(B200_UNSUPPORTED, "pool_bf16: divisor %llu of window %llu", (unsigned long long)divisors[w], (unsigned long long)w);
+    meta[w] = (uint32_t)offsets[w];
+    div[w] = (float)divisors[w];
+  }
+  meta[n_windows] = (uint32_t)total;
+  for (uint64_t i = 0; i < total; ++i) {
+    const uint64_t r = coords[2 * i], c = coords[2 * i + 1];
+    if (r >= A->rows || c >= A->cols) return e->fail(B200_DOMAIN, "pool_bf16: DOMAIN: tap %llu names [%llu, %llu]", (unsigned long long)i, (unsigned long long)r, (unsigned long long)c);
+    meta[n_windows + 1 + i] = (uint32_t)(r * A->cols + c);
+  }
+  const uint16_t* src = (const uint16_t*)A->ptr;
+  Buf* O = nullptr;
+  st = e->new_buffer(dims[0], dims[1], B200_F32, out, &O);
+  if (st) return st;
+  float* op = (float*)O->ptr;
+  void *dm = nullptr, *dd = nullptr; uint64_t gm = 0, gd = 0;
+  st = e->to_device(meta.data(), meta.size() * 4, &dm, &gm);
+  if (!st) { st = e->to_device(div.data(), div.size() * 4, &dd, &gd); if (st) e->release(dm, gm); }
+  if (st) { e->drop(*out); return st; }
+  st = e->launched(launch_pool_windows(src, (const uint32_t*)dm, (const uint32_t*)dm + n_windows + 1, (const float*)dd, n_windows, op, e->stream), "pool_bf16");
+  e->release(dm, gm); e->release(dd, gd);
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, dims[0], dims[1]);
+  return B200_OK;
+}
+
+int32_t b200_metadata(b200_engine* e, const uint32_t* bits, const uint64_t dims[2], int32_t elem, b200_buffer* out) {
+  if (elem != B200_F32 && elem != B200_I32 && elem != B200_BOOL)
+    return e->fail(B200_UNSUPPORTED, "metadata: elem %d is not a 32-bit element", elem);
+  if (!e->capturing) return upload_any(e, bits, dims[0], dims[1], elem, out);
+  // Inside a capture the words become a copy node from memory the trace owns: every replay writes them again.
+  cudaSetDevice(e->device);
+  Buf* O = nullptr;
+  int st = e->new_buffer(dims[0], dims[1], elem, out, &O);
+  if (st) return st;
+  const uint64_t bytes = dims[0] * dims[1] * 4;
+  if (bytes) {
+    void* pin = nullptr;
+    if (cudaMallocHost(&pin, bytes) != cudaSuccess) { cudaGetLastError(); e->drop(*out); return e->fail(B200_OUT_OF_MEMORY, "trace: no pinned memory for metadata"); }
+    memcpy(pin, bits, bytes);
+    e->cur.pinned.push_back(pin);
+    cudaError_t ce = cudaMemcpyAsync(O->ptr, pin, bytes, cudaMemcpyHostToDevice, e->stream);
+    if (ce != cudaSuccess) { e->drop(*out); return e->cuda_fail(ce, "metadata"); }
+    e->traffic.bytes_h2d += bytes;
+  }
+  return B200_OK;
+}
+
+int32_t b200_free_bytes(b200_engine* e, uint64_t out[2]) {
+  cudaSetDevice(e->device);
+  size_t fr = 0, tot = 0;
+  cudaError_t ce = cudaMemGetInfo(&fr, &tot);
+  if (ce != cudaSuccess) return e->cuda_fail(ce, "free_bytes");
+  uint64_t idle = 0;
+  for (auto& kv : e->cache) idle += kv.first;
+  uint64_t driver = fr;
+  if (e->cfg.pool_limit_bytes) {
+    const uint64_t room = e->cfg.pool_limit_bytes > e->traffic.pool_reserved ? e->cfg.pool_limit_bytes - e->traffic.pool_reserved : 0;
+    driver = std::min<uint64_t>(driver, room);
+  }
+  out[0] = driver + idle;   // idle blocks go back to the driver when a request does not fit them
+  out[1] = driver + idle;
   return B200_OK;
 }
 

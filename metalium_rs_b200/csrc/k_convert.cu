@@ -1,0 +1,113 @@
+// Storage conversions beyond the whole-buffer F32 <-> BF16 cast.
+//
+//  * `cast_block`: `Engine::cast_block` (crates/burn-tt/src/server.rs:137, `Session::cast_block`
+//    crates/tt-kernels/src/session.rs:3732): the F32 <-> BF16 conversion of a block of a buffer into a
+//    new buffer of the block's dims, bit for bit the whole-buffer cast of those elements.
+//  * `cast_f16`: `Engine::cast_f16` (server.rs:779): F32 <-> IEEE binary16 held in two-byte storage.
+//    The rule is the reference's integer programs' (crates/tt-kernels/src/fp16.rs:172-176, 271-275):
+//    narrowing rounds ties to even on the binary16 grid, subnormal results included, |x| >= 65520 and
+//    infinity give infinity, a NaN keeps its sign and its top ten payload bits and is made quiet;
+//    widening is exact, a NaN keeping sign and payload with the quiet bit set.
+//
+// Both are one read and one write an element: HBM-bound, a thread per group of elements, coalesced.
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "device_math.cuh"
+#include "kernels.h"
+#include "pdl.cuh"
+
+namespace b200 {
+namespace {
+
+__device__ __forceinline__ uint16_t f32_to_f16_bits(uint32_t x) {
+  const uint32_t sign = (x >> 16) & 0x8000u, a = x & 0x7fffffffu;
+  if (a > 0x7f800000u) return (uint16_t)(sign | 0x7e00u | ((a >> 13) & 0x3ffu));   // NaN: quiet, payload kept
+  if (a >= 0x477ff000u) return (uint16_t)(sign | 0x7c00u);                          // rounds to 2^16 or beyond
+  if (a >= 0x38800000u) {                                                          // a normal binary16
+    const uint32_t r = a + 0xfffu + ((a >> 13) & 1u);
+    return (uint16_t)(sign | ((r >> 13) - 0x1c000u));
+  }
+  if (a <= 0x33000000u) return (uint16_t)sign;                                     // at most 2^-25: zero (the tie is even)
+  const uint32_t shift = 126u - (a >> 23);                                         // 14 .. 24
+  const uint32_t m = (a & 0x7fffffu) | 0x800000u;
+  const uint32_t lsb = (m >> shift) & 1u;
+  return (uint16_t)(sign | ((m + ((1u << (shift - 1)) - 1u) + lsb) >> shift));     // the 2^-24 grid
+}
+
+__device__ __forceinline__ uint32_t f16_to_f32_bits(uint32_t h) {
+  const uint32_t sign = (h & 0x8000u) << 16, a = h & 0x7fffu;
+  if (a >= 0x7c00u) return sign | 0x7f800000u | ((a & 0x3ffu) << 13) | (a > 0x7c00u ? 0x400000u : 0u);
+  if (a >= 0x400u) return sign | ((a << 13) + 0x38000000u);
+  return sign | __float_as_uint((float)a * 5.9604644775390625e-8f);                 // m * 2^-24, exact
+}
+
+__global__ void __launch_bounds__(256)
+cast_f16_kernel(const void* __restrict__ in, void* __restrict__ out, uint64_t n, int to_f16) {
+  pdl_enter();
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x * 4;
+  for (uint64_t i = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
+    if (to_f16) {
+      const uint32_t* s = reinterpret_cast<const uint32_t*>(in);
+      uint16_t* d = reinterpret_cast<uint16_t*>(out);
+      if (i + 3 < n) {                          // both bases come from the pool: 256-byte aligned
+        const uint4 v = *reinterpret_cast<const uint4*>(s + i);
+        uint2 o;
+        o.x = (uint32_t)f32_to_f16_bits(v.x) | ((uint32_t)f32_to_f16_bits(v.y) << 16);
+        o.y = (uint32_t)f32_to_f16_bits(v.z) | ((uint32_t)f32_to_f16_bits(v.w) << 16);
+        *reinterpret_cast<uint2*>(d + i) = o;
+      } else {
+        for (uint64_t j = i; j < n; ++j) d[j] = f32_to_f16_bits(s[j]);
+      }
+    } else {
+      const uint16_t* s = reinterpret_cast<const uint16_t*>(in);
+      uint32_t* d = reinterpret_cast<uint32_t*>(out);
+      if (i + 3 < n) {
+        const uint2 v = *reinterpret_cast<const uint2*>(s + i);
+        uint4 o;
+        o.x = f16_to_f32_bits(v.x & 0xffffu); o.y = f16_to_f32_bits(v.x >> 16);
+        o.z = f16_to_f32_bits(v.y & 0xffffu); o.w = f16_to_f32_bits(v.y >> 16);
+        *reinterpret_cast<uint4*>(d + i) = o;
+      } else {
+        for (uint64_t j = i; j < n; ++j) d[j] = f16_to_f32_bits(s[j]);
+      }
+    }
+  }
+}
+
+// A block of a wider buffer: rows of `cols` elements, `in_ld` apart; the result is dense.
+__global__ void __launch_bounds__(256)
+cast_block_kernel(const void* __restrict__ in, uint64_t in_ld, void* __restrict__ out, uint64_t rows, uint32_t cols,
+                  int to_bf16) {
+  pdl_enter();
+  const uint64_t n = rows * cols, stride = (uint64_t)gridDim.x * blockDim.x;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const uint64_t r = i / cols; const uint32_t c = (uint32_t)(i - r * cols);
+    if (to_bf16)
+      reinterpret_cast<uint16_t*>(out)[i] = f32_to_bf16_bits(reinterpret_cast<const uint32_t*>(in)[r * in_ld + c]);
+    else
+      reinterpret_cast<uint32_t*>(out)[i] = (uint32_t)reinterpret_cast<const uint16_t*>(in)[r * in_ld + c] << 16;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_cast_f16(const void* in, void* out, uint64_t n, int to_f16, cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  uint64_t blocks = (n / 4 + 255) / 256 + 1;
+  if (blocks > 148ull * 64) blocks = 148ull * 64;
+  launch_pdl(cast_f16_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, in, out, n, to_f16);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_cast_block(const void* in, uint64_t in_ld, void* out, uint64_t rows, uint64_t cols, int to_bf16,
+                              cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return cudaSuccess;
+  if (in_ld == cols) return launch_cast(in, out, rows * cols, to_bf16, stream);   // whole rows: the dense cast
+  uint64_t blocks = (rows * cols + 255) / 256;
+  if (blocks > 148ull * 64) blocks = 148ull * 64;
+  launch_pdl(cast_block_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, in, in_ld, out, rows, (uint32_t)cols, to_bf16);
+  return cudaGetLastError();
+}
+
+}  // namespace b200

@@ -212,6 +212,44 @@ __global__ void repack_kernel(const T* src, uint64_t src_ld, const uint64_t* pai
     out[i] = src[pairs[2 * i] * src_ld + pairs[2 * i + 1]];
 }
 
+// out[i] = the datum at addrs[i]: `Engine::repack_many` (crates/burn-tt/src/server.rs:317,
+// crates/tt-kernels/src/tensor.rs:6791), one source a result element out of several buffers; the host
+// resolves (buffer, row, column) to an address, so the kernel is one gather.
+template <typename T>
+__global__ void gather_addrs_kernel(const uint64_t* __restrict__ addrs, uint64_t n, T* __restrict__ out) {
+  pdl_enter();
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+    out[i] = *reinterpret_cast<const T*>(addrs[i]);
+}
+
+// `Engine::select_taps` (server.rs:309; crates/tt-kernels/src/index.rs:136-160): row i of the result holds,
+// for each tap t, row idx[t][i] of the table from column t * pitch (pitch = the table's columns rounded
+// up to 32; the last tap takes the table's own columns only).  The columns between a tap's end and the
+// next tap's start are zero, and with `zero_row` an index equal to the table's rows reads zeros (a
+// convolution's padding tap).  A warp a (row, tap).
+__global__ void __launch_bounds__(256)
+select_taps_kernel(const char* __restrict__ table, uint64_t t_rows, uint64_t cols, int eb, const int32_t* __restrict__ idx,
+                   uint64_t taps, uint64_t n, int zero_row, char* __restrict__ out, uint64_t out_cols, uint64_t pitch, int* err) {
+  pdl_enter();
+  const int lane = threadIdx.x & 31;
+  const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+  for (uint64_t w = warp; w < n * taps; w += nwarps) {
+    const uint64_t i = w / taps, t = w - i * taps;
+    const int64_t r = idx[t * n + i];
+    char* dst = out + (i * out_cols + t * pitch) * eb;
+    const uint64_t width = (t + 1 < taps ? pitch : cols);          // this tap's columns of the result
+    const bool zero = zero_row && r == (int64_t)t_rows;
+    if (!zero && (r < 0 || (uint64_t)r >= t_rows)) { if (lane == 0) set_err(err, DOMAIN); continue; }
+    if (zero) {
+      for (uint64_t b = lane * 2; b < width * eb; b += 64) *reinterpret_cast<uint16_t*>(dst + b) = 0;
+    } else {
+      copy_row(table + (uint64_t)r * cols * eb, dst, cols * eb, lane, 32);
+      for (uint64_t b = cols * eb + lane * 2; b < width * eb; b += 64) *reinterpret_cast<uint16_t*>(dst + b) = 0;
+    }
+  }
+}
+
 inline unsigned cap_grid(uint64_t blocks) { return (unsigned)(blocks < 148ull * 32 ? (blocks ? blocks : 1) : 148ull * 32); }
 
 }  // namespace
@@ -314,6 +352,21 @@ cudaError_t launch_repack(const void* src, uint64_t src_ld, int elem_bytes, cons
     repack_kernel<uint32_t><<<cap_grid((n + 255) / 256), 256, 0, s>>>((const uint32_t*)src, src_ld, pairs_dev, n, (uint32_t*)out);
   else
     repack_kernel<uint16_t><<<cap_grid((n + 255) / 256), 256, 0, s>>>((const uint16_t*)src, src_ld, pairs_dev, n, (uint16_t*)out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather_addrs(const uint64_t* addrs_dev, uint64_t n, int elem_bytes, void* out, cudaStream_t s) {
+  if (n == 0) return cudaSuccess;
+  if (elem_bytes == 4) launch_pdl(gather_addrs_kernel<uint32_t>, dim3(cap_grid((n + 255) / 256)), dim3(256), 0, s, addrs_dev, n, (uint32_t*)out);
+  else launch_pdl(gather_addrs_kernel<uint16_t>, dim3(cap_grid((n + 255) / 256)), dim3(256), 0, s, addrs_dev, n, (uint16_t*)out);
+  return cudaGetLastError();
+}
+cudaError_t launch_select_taps(const void* table, uint64_t t_rows, uint64_t cols, int elem_bytes, const int32_t* idx,
+                               uint64_t taps, uint64_t n, int zero_row, void* out, uint64_t out_cols, int* err, cudaStream_t s) {
+  if (n == 0 || taps == 0 || cols == 0) return cudaSuccess;
+  const uint64_t pitch = (cols + 31) / 32 * 32;
+  launch_pdl(select_taps_kernel, dim3(cap_grid((n * taps + 7) / 8)), dim3(256), 0, s, (const char*)table, t_rows, cols, elem_bytes,
+             idx, taps, n, zero_row, (char*)out, out_cols, pitch, err);
   return cudaGetLastError();
 }
 

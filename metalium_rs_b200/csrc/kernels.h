@@ -148,6 +148,34 @@ bool gemm_tf32_supported(const GemmArgs& g, const char** why);
 cudaError_t launch_gemm_tf32(const GemmArgs& g, void* a_hi, void* a_lo, void* b_hi, void* b_lo, int* err_word,
                              cudaStream_t stream);
 
+// F32 <-> IEEE binary16 in two-byte storage, and the F32 <-> BF16 cast of a block of a wider buffer.
+cudaError_t launch_cast_f16(const void* in, void* out, uint64_t n, int to_f16, cudaStream_t stream);
+cudaError_t launch_cast_block(const void* in, uint64_t in_ld, void* out, uint64_t rows, uint64_t cols, int to_bf16,
+                              cudaStream_t stream);
+// out[i] = the datum at device address addrs[i] (2- or 4-byte datums).
+cudaError_t launch_gather_addrs(const uint64_t* addrs_dev, uint64_t n, int elem_bytes, void* out, cudaStream_t stream);
+// Rows of a table for each tap of a [taps, n] index matrix, side by side, each tap from a multiple of 32 columns.
+cudaError_t launch_select_taps(const void* table, uint64_t t_rows, uint64_t cols, int elem_bytes, const int32_t* idx,
+                               uint64_t taps, uint64_t n, int zero_row, void* out, uint64_t out_cols, int* err,
+                               cudaStream_t stream);
+// Inclusive scan down rows; `op` in the order Sum, Prod, Min, Max, MinNan, MaxNan, ISum, IProd, IMin, IMax.
+// `scan_chunks` row chunks need a [chunks, cols] word scratch (`carry`); with none the rows stay together.
+uint64_t scan_chunks(int op, uint64_t rows, uint64_t cols);
+cudaError_t launch_scan(const uint32_t* in, uint32_t* out, uint64_t rows, uint64_t cols, int op, uint32_t* carry,
+                        cudaStream_t stream);
+// Sort of every problem of a planes matrix [rows = 32 * a power of two <= 1024, cols % 32 == 0] over its
+// first n positions; `indices` may be null.
+cudaError_t launch_sort_planes(const uint32_t* in, uint64_t rows, uint64_t cols, uint32_t n, int is_i32, int descending,
+                               uint32_t* keys, uint32_t* indices, cudaStream_t stream);
+// A seeded draw of n words; `draw` 0 Unit, 1 Uniform(p0, p1; i1 = bits of the float below p1), 2 Bernoulli(p0),
+// 3 Normal(mean p0, std p1), 4 IntRange(lo i0, range p0), 5 IntWords.
+cudaError_t launch_random(uint32_t* out, uint64_t n, int draw, float p0, float p1, int32_t i0, int32_t i1, int as_int,
+                          uint64_t base, cudaStream_t stream);
+
+// Means over host-built windows of a BF16 matrix: window w is flat[offsets[w] .. offsets[w + 1]) (element offsets).
+cudaError_t launch_pool_windows(const uint16_t* in, const uint32_t* offsets_dev, const uint32_t* flat_dev,
+                                const float* divisors_dev, uint64_t n, float* out, cudaStream_t stream);
+
 // Text for `b200_last_error(NULL, ...)`: failures of calls that take no engine.
 void set_global_error(const char* text);
 

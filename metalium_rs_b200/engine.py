@@ -25,6 +25,9 @@ OK, OUT_OF_MEMORY, UNSUPPORTED, DEVICE, TIMEOUT, STALE, DOMAIN, NO_DEVICE = rang
 F32, I32, BOOL, BF16 = range(4)
 SUM, MAX, PROD, ALL, ANY, BITOR, SUM_I32, PROD_I32, MIN_I32, MAX_I32 = range(10)
 ROWS, COLS = 0, 1
+# crates/tt-kernels/src/sfpu/scan.rs:19-41 `ScanOp`, in its order
+(SCAN_SUM, SCAN_PROD, SCAN_MIN, SCAN_MAX, SCAN_MIN_NAN, SCAN_MAX_NAN, SCAN_ISUM, SCAN_IPROD, SCAN_IMIN,
+ SCAN_IMAX) = range(10)
 
 _STATUS_NAMES = {1: "OutOfMemory", 2: "Unsupported", 3: "Device", 4: "Timeout", 5: "StaleTensor",
                  6: "Device(DOMAIN)", 7: "NoDriver"}
@@ -511,6 +514,86 @@ class CudaEngine:
         src = np.ascontiguousarray(sources, dtype=np.uint64).reshape(-1)
         assert src.size == 2 * dims[0] * dims[1]
         return self._call(self._lib.b200_repack, C.c_uint64(a), _ptr(src), (C.c_uint64 * 2)(*dims))
+
+    def repack_many(self, inputs: Sequence[int], sources, dims) -> Out:
+        """`repack_many(inputs, [(input, [row, col])...], dims)` (server.rs:317): one source a result element."""
+        src = np.ascontiguousarray([(i, r, c) for i, (r, c) in sources], dtype=np.uint64).reshape(-1)
+        ids = (C.c_uint64 * max(len(inputs), 1))(*inputs)
+        return self._call(self._lib.b200_repack_many, ids, C.c_uint64(len(inputs)), _ptr(src), C.c_uint64(len(sources)),
+                          (C.c_uint64 * 2)(*dims))
+
+    def select_taps(self, table: int, indices: int, zero_row: bool) -> Out:
+        return self._call(self._lib.b200_select_taps, C.c_uint64(table), C.c_uint64(indices), C.c_int32(zero_row))
+
+    def cast_block(self, a, bf16: bool) -> Out:
+        blk = _block(a)
+        return self._call(self._lib.b200_cast_block, C.byref(blk), C.c_int32(bf16))
+
+    def cast_f16(self, a: int, to_f16: bool) -> Out:
+        return self._call(self._lib.b200_cast_f16, C.c_uint64(a), C.c_int32(to_f16))
+
+    def pow(self, x: int, y) -> Out:
+        """`pow(x, PowArg)` (server.rs:578): y = ("tensor", id), ("scalar", s) or ("int", id)."""
+        kind, v = y
+        code = {"tensor": 0, "scalar": 1, "int": 2}[kind]
+        return self._call(self._lib.b200_pow, C.c_uint64(x), C.c_int32(code), C.c_uint64(0 if code == 1 else v),
+                          C.c_float(v if code == 1 else 0.0))
+
+    def scan(self, a: int, op: int) -> Out:
+        return self._call(self._lib.b200_scan, C.c_uint64(a), C.c_int32(op))
+
+    def sort_planes(self, a: int, elem: int, n: int, descending: bool, indices: bool):
+        """`sort_planes(a, Spec{elem, n, descending, indices})` (server.rs:758): ((keys, dims), (indices, dims) | None)."""
+        keys, idx = C.c_uint64(), C.c_uint64()
+        dims = (C.c_uint64 * 2)()
+        self._check(self._lib.b200_sort_planes(self._e, C.c_uint64(a), C.c_int32(elem), C.c_uint64(n), C.c_int32(descending),
+                                               C.byref(keys), C.byref(idx) if indices else None, dims))
+        d = (dims[0], dims[1])
+        return (keys.value, d), ((idx.value, d) if indices else None)
+
+    def random_dram(self, dims, draw, base: int) -> Out:
+        """`random_dram(dims, Draw, base)` (server.rs:768).  draw: ("unit",), ("uniform", lo, hi),
+        ("bernoulli", p, int), ("normal", mean, std, int), ("int_range", lo, hi), ("int_words",)."""
+        name, args = draw[0], draw[1:]
+        code = {"unit": 0, "uniform": 1, "bernoulli": 2, "normal": 3, "int_range": 4, "int_words": 5}[name]
+        a = b = 0.0
+        lo = hi = 0
+        as_int = False
+        if name == "uniform":
+            a, b = args
+        elif name == "bernoulli":
+            a, as_int = args
+        elif name == "normal":
+            a, b, as_int = args
+        elif name == "int_range":
+            lo, hi = args
+        return self._call(self._lib.b200_random, (C.c_uint64 * 2)(*dims), C.c_int32(code), C.c_float(a), C.c_float(b),
+                          C.c_int32(lo), C.c_int32(hi), C.c_int32(as_int), C.c_uint64(base & (2**64 - 1)))
+
+    def pool_bf16(self, a: int, windows, divisors, dims) -> Out:
+        """`pool_bf16(a, windows, divisors, dims)` (server.rs:118): windows is a list of lists of [row, col]."""
+        offsets = np.zeros(len(windows) + 1, dtype=np.uint64)
+        offsets[1:] = np.cumsum([len(w) for w in windows])
+        coords = np.ascontiguousarray([rc for w in windows for rc in w], dtype=np.uint64).reshape(-1)
+        if coords.size == 0:
+            coords = np.zeros(2, dtype=np.uint64)
+        div = np.ascontiguousarray(divisors, dtype=np.uint64)
+        assert div.size == len(windows)
+        return self._call(self._lib.b200_pool_bf16, C.c_uint64(a), _ptr(offsets), _ptr(coords), _ptr(div if div.size else np.zeros(1, np.uint64)),
+                          C.c_uint64(len(windows)), (C.c_uint64 * 2)(*dims))
+
+    def metadata(self, bits, dims, elem: int) -> int:
+        a = np.ascontiguousarray(bits).view(np.uint32) if np.asarray(bits).dtype.itemsize == 4 \
+            else np.ascontiguousarray(bits, dtype=np.uint32)
+        assert a.size == dims[0] * dims[1]
+        out = C.c_uint64()
+        self._check(self._lib.b200_metadata(self._e, _ptr(a), (C.c_uint64 * 2)(*dims), C.c_int32(elem), C.byref(out)))
+        return out.value
+
+    def gddr_free_bytes(self) -> Tuple[int, int]:
+        out = (C.c_uint64 * 2)()
+        self._check(self._lib.b200_free_bytes(self._e, out))
+        return out[0], out[1]
 
     @staticmethod
     def attention_item_array(items):

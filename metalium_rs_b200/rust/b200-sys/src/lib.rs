@@ -70,6 +70,17 @@ extern "C" {
     pub fn b200_slice_rows(a0: *mut b200_engine, a: u64, first: u64, rows: u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_copy_blocks(a0: *mut b200_engine, a: u64, moves: *const b200_block_move, n: u64, dims: *const u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_repack(a0: *mut b200_engine, a: u64, row_col_pairs: *const u64, dims: *const u64, out: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_repack_many(a0: *mut b200_engine, inputs: *const u64, n_inputs: u64, triples: *const u64, n_triples: u64, dims: *const u64, out: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_select_taps(a0: *mut b200_engine, table: u64, indices: u64, zero_row: i32, out: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_cast_block(a0: *mut b200_engine, a: *const b200_block_arg, to_bf16: i32, out: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_cast_f16(a0: *mut b200_engine, a: u64, to_f16: i32, out: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_pow(a0: *mut b200_engine, x: u64, exponent_kind: i32, y: u64, scalar: f32, out: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_scan(a0: *mut b200_engine, a: u64, op: i32, out: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_sort_planes(a0: *mut b200_engine, a: u64, elem: i32, n: u64, descending: i32, keys: *mut u64, indices: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_random(a0: *mut b200_engine, dims: *const u64, draw: i32, a: f32, b: f32, lo: i32, hi: i32, as_int: i32, base: u64, out: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_pool_bf16(a0: *mut b200_engine, a: u64, offsets: *const u64, coords: *const u64, divisors: *const u64, n_windows: u64, dims: *const u64, out: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_metadata(a0: *mut b200_engine, bits: *const u32, dims: *const u64, elem: i32, out: *mut u64) -> i32;
+    pub fn b200_free_bytes(a0: *mut b200_engine, out: *mut u64) -> i32;
     pub fn b200_attention_blocks(a0: *mut b200_engine, q: u64, k: u64, v: u64, items: *const b200_attention_block, n_items: u64, dims: *const u64, scale: f32, causal: i32, result_dims: *const u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_attention_rows(a0: *mut b200_engine, buffers: *const u64, items: *const b200_attention_item, n_items: u64, dims: *const u64, scale: f32, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_attention_rows_as(a0: *mut b200_engine, buffers: *const u64, items: *const b200_attention_item, n_items: u64, dims: *const u64, scale: f32, out_bf16: i32, out: *mut u64, out_dims: *mut u64) -> i32;

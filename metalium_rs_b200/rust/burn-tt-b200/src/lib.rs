@@ -6,7 +6,7 @@
 //! Source only: no Rust toolchain exists where this was written, so it has not been compiled.
 //! Every method is one call of include/b200tt.h through `b200-sys`.
 use b200_sys as sys;
-use burn_tt::server::{BlockArg, BufferId, Engine, Serve};
+use burn_tt::server::{BlockArg, BufferId, Engine, PowArg, Serve, SortedBuffers};
 use burn_tt::TtError;
 use tt_kernels::session::BatchedLayout;
 use tt_kernels::sfpu::reduce::{Axis, ReduceOp};
@@ -293,6 +293,72 @@ impl Engine for CudaEngine {
         let p: Vec<u64> = sources.iter().flat_map(|s| [s[0] as u64, s[1] as u64]).collect();
         let d = [dims[0] as u64, dims[1] as u64];
         produce!(self, b200_repack(a, p.as_ptr(), d.as_ptr()))
+    }
+
+    fn repack_many(&mut self, inputs: &[BufferId], sources: &[(usize, [usize; 2])], dims: [usize; 2]) -> Made {
+        let p: Vec<u64> = sources.iter().flat_map(|&(i, at)| [i as u64, at[0] as u64, at[1] as u64]).collect();
+        let d = [dims[0] as u64, dims[1] as u64];
+        produce!(self, b200_repack_many(inputs.as_ptr(), inputs.len() as u64, p.as_ptr(), sources.len() as u64, d.as_ptr()))
+    }
+    fn select_taps(&mut self, table: BufferId, idx: BufferId, zero_row: bool) -> Made {
+        produce!(self, b200_select_taps(table, idx, zero_row as i32))
+    }
+    fn cast_block(&mut self, a: BlockArg, bf16: bool) -> Made {
+        let b = sys::b200_block_arg { id: a.id, at: [a.at[0] as u64, a.at[1] as u64], dims: [a.dims[0] as u64, a.dims[1] as u64] };
+        produce!(self, b200_cast_block(&b, bf16 as i32))
+    }
+    fn cast_f16(&mut self, id: BufferId, to_f16: bool) -> Made { produce!(self, b200_cast_f16(id, to_f16 as i32)) }
+    fn pow(&mut self, x: BufferId, y: PowArg) -> Made {
+        match y {
+            PowArg::Tensor(t) => produce!(self, b200_pow(x, 0, t, 0.0)),
+            PowArg::Scalar(s) => produce!(self, b200_pow(x, 1, 0, s)),
+            PowArg::Int(t) => produce!(self, b200_pow(x, 2, t, 0.0)),
+        }
+    }
+    fn scan(&mut self, a: BufferId, op: tt_kernels::sfpu::scan::ScanOp) -> Made {
+        use tt_kernels::sfpu::scan::ScanOp::*;
+        let code = match op { Sum => 0, Prod => 1, Min => 2, Max => 3, MinNan => 4, MaxNan => 5, ISum => 6, IProd => 7, IMin => 8, IMax => 9 };
+        produce!(self, b200_scan(a, code))
+    }
+    fn sort_planes(&mut self, a: BufferId, spec: tt_kernels::sfpu::sort::Spec) -> Result<SortedBuffers, TtError> {
+        let (mut keys, mut idx, mut d) = (0u64, 0u64, [0u64; 2]);
+        let ip = if spec.indices { &mut idx as *mut u64 } else { std::ptr::null_mut() };
+        let st = unsafe { sys::b200_sort_planes(self.raw, a, elem_code(spec.elem, false), spec.n as u64, spec.descending as i32, &mut keys, ip, d.as_mut_ptr()) };
+        self.check(st)?;
+        let dims = [d[0] as usize, d[1] as usize];
+        Ok(SortedBuffers { keys: (keys, dims), indices: spec.indices.then_some((idx, dims)) })
+    }
+    fn random_dram(&mut self, dims: [usize; 2], draw: burn_tt::random::Draw, base: u64) -> Made {
+        use burn_tt::random::Draw::*;
+        let d = [dims[0] as u64, dims[1] as u64];
+        let (code, a, b, lo, hi, int) = match draw {
+            Unit => (0, 0.0, 0.0, 0, 0, false),
+            Uniform(lo, hi) => (1, lo, hi, 0, 0, false),
+            Bernoulli { p, int } => (2, p, 0.0, 0, 0, int),
+            Normal { mean, std, int } => (3, mean, std, 0, 0, int),
+            IntRange(lo, hi) => (4, 0.0, 0.0, lo, hi, false),
+            IntWords => (5, 0.0, 0.0, 0, 0, false),
+        };
+        produce!(self, b200_random(d.as_ptr(), code, a, b, lo, hi, int as i32, base))
+    }
+    fn pool_bf16(&mut self, a: BufferId, windows: &[Vec<[usize; 2]>], divisors: &[usize], dims: [usize; 2]) -> Made {
+        if divisors.len() != windows.len() { return Err(TtError::unsupported("invalid BF16 pool windows")); }
+        let mut offsets = vec![0u64];
+        for w in windows { offsets.push(offsets.last().unwrap() + w.len() as u64); }
+        let coords: Vec<u64> = windows.iter().flatten().flat_map(|rc| [rc[0] as u64, rc[1] as u64]).collect();
+        let div: Vec<u64> = divisors.iter().map(|&d| d as u64).collect();
+        let d = [dims[0] as u64, dims[1] as u64];
+        produce!(self, b200_pool_bf16(a, offsets.as_ptr(), coords.as_ptr(), div.as_ptr(), windows.len() as u64, d.as_ptr()))
+    }
+    fn metadata(&mut self, bits: &[u32], dims: [usize; 2], elem: Elem) -> Result<BufferId, TtError> {
+        let (mut id, d) = (0u64, [dims[0] as u64, dims[1] as u64]);
+        let st = unsafe { sys::b200_metadata(self.raw, bits.as_ptr(), d.as_ptr(), elem_code(elem, false), &mut id) };
+        self.check(st).map(|_| id)
+    }
+    fn gddr_free_bytes(&mut self) -> Result<(u64, u64), TtError> {
+        let mut out = [0u64; 2];
+        let st = unsafe { sys::b200_free_bytes(self.raw, out.as_mut_ptr()) };
+        self.check(st).map(|_| (out[0], out[1]))
     }
 
     // Traces are CUDA graphs (server.rs:591-660).

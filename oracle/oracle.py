@@ -583,3 +583,214 @@ def scatter_rows(table: np.ndarray, idx: np.ndarray, values: np.ndarray) -> np.n
     for i, r in enumerate(np.asarray(idx).ravel()):
         out[r] = values[i]
     return out
+
+
+# ------------------------------------------------------------------ movement of several sources, taps
+def repack_many(inputs, sources, dims) -> np.ndarray:
+    """crates/tt-kernels/src/tensor.rs:6791: result element i is inputs[s][r, c] for sources[i] = (s, (r, c))."""
+    flat = [inputs[s][r, c] for s, (r, c) in sources]
+    return np.array(flat, dtype=inputs[0].dtype).reshape(dims)
+
+
+def select_taps(table: np.ndarray, idx: np.ndarray, zero_row: bool) -> np.ndarray:
+    """crates/tt-kernels/src/index.rs:136-160 and crates/tt-kernels/src/session.rs:8068-8084: row i holds row
+    idx[t][i] of the table from column t * ceil32(cols); the gap up to the next tap is zero; with zero_row an
+    index equal to the table's rows reads zeros."""
+    taps, n = idx.shape
+    rows, cols = table.shape
+    pitch = (cols + 31) // 32 * 32
+    out = np.zeros((n, (taps - 1) * pitch + cols), dtype=table.dtype)
+    for t in range(taps):
+        for i in range(n):
+            r = int(idx[t, i])
+            if zero_row and r == rows:
+                continue
+            out[i, t * pitch:t * pitch + cols] = table[r]
+    return out
+
+
+# ------------------------------------------------------------------ binary16 storage
+def f16_bits_from_f32_bits(x: np.ndarray) -> np.ndarray:
+    """crates/tt-kernels/src/fp16.rs:172-176: ties to even on the binary16 grid (subnormals included), overflow
+    and infinity to infinity, a NaN made quiet with its sign and top ten payload bits."""
+    x = np.asarray(x, dtype=np.uint32).astype(np.int64)
+    sign, a = (x >> 16) & 0x8000, x & 0x7FFFFFFF
+    normal = ((a + 0xFFF + ((a >> 13) & 1)) >> 13) - 0x1C000
+    shift = np.clip(126 - (a >> 23), 1, 24)
+    m = (a & 0x7FFFFF) | 0x800000
+    sub = (m + (np.int64(1) << (shift - 1)) - 1 + ((m >> shift) & 1)) >> shift
+    h = np.where(a > 0x7F800000, 0x7E00 | ((a >> 13) & 0x3FF),
+                 np.where(a >= 0x477FF000, 0x7C00, np.where(a >= 0x38800000, normal, np.where(a <= 0x33000000, 0, sub))))
+    return (sign | h).astype(np.uint16)
+
+
+def f32_bits_from_f16_bits(h: np.ndarray) -> np.ndarray:
+    """crates/tt-kernels/src/fp16.rs:271-275: exact; a NaN keeps sign and payload and is made quiet."""
+    h = np.asarray(h, dtype=np.uint16).astype(np.int64)
+    sign, a = (h & 0x8000) << 16, h & 0x7FFF
+    special = 0x7F800000 | ((a & 0x3FF) << 13) | np.where(a > 0x7C00, 0x400000, 0)
+    sub = (a.astype(np.float64) * 2.0 ** -24).astype(np.float32).view(np.uint32).astype(np.int64)
+    v = np.where(a >= 0x7C00, special, np.where(a >= 0x400, (a << 13) + 0x38000000, sub))
+    return (sign | v).astype(np.uint32)
+
+
+# ------------------------------------------------------------------ scans down rows
+SCAN_OPS = ("sum", "prod", "min", "max", "min_nan", "max_nan", "isum", "iprod", "imin", "imax")
+_SCAN_IDENTITY = {"sum": 0, "isum": 0, "prod": 0x3F800000, "iprod": 1, "min": 0x7FFFFFFF, "max": 0xFFFFFFFF,
+                  "min_nan": 0x7F800000, "max_nan": 0xFF800000, "imin": 0x7FFFFFFF, "imax": 0x80000000}
+
+
+def _total_key(u):
+    s = u.view(np.int32)
+    return (u ^ ((s >> 31).view(np.uint32) >> u32(1))).view(np.int32)
+
+
+def scan(bits: np.ndarray, op: str) -> np.ndarray:
+    """crates/tt-kernels/src/sfpu/scan.rs:196-231 on words: every column from its first row to its last, from
+    the op's identity.  Rows are the loop; the columns go through numpy together."""
+    bits = np.asarray(bits, dtype=np.uint32)
+    out = np.empty_like(bits)
+    acc = np.full(bits.shape[1], _SCAN_IDENTITY[op], dtype=np.uint32)
+    with np.errstate(all="ignore"):
+        for r in range(bits.shape[0]):
+            x = bits[r]
+            if op == "sum":
+                acc = (x.view(np.float32) + acc.view(np.float32)).astype(np.float32).view(np.uint32)
+            elif op == "prod":
+                acc = (acc.view(np.float32) * x.view(np.float32)).astype(np.float32).view(np.uint32)
+            elif op in ("min", "max"):
+                kx, ka = _total_key(x), _total_key(acc)
+                acc = np.where(kx < ka if op == "min" else kx > ka, x, acc)
+            elif op in ("min_nan", "max_nan"):
+                v, a = x.view(np.float32), acc.view(np.float32)
+                acc = np.where(np.isnan(v) | (v < a if op == "min_nan" else v > a), x, acc)
+            elif op == "isum":
+                acc = (acc.astype(np.uint64) + x).astype(np.uint32)
+            elif op == "iprod":
+                acc = ((acc.astype(np.uint64) * x) & np.uint64(0xFFFFFFFF)).astype(np.uint32)
+            else:
+                sx, sa = x.view(np.int32), acc.view(np.int32)
+                acc = np.where(sx < sa if op == "imin" else sx > sa, x, acc)
+            out[r] = acc
+    return out
+
+
+# ------------------------------------------------------------------ sort of a planes matrix
+def plane_coord(q: int, e: int):
+    """crates/tt-kernels/src/sfpu/sort.rs:198-207."""
+    tr, s = divmod(e, 32)
+    cb, lane = divmod(q, 32)
+    face, group, odd = s // 8, (s // 2) % 4, s % 2
+    j, c = divmod(lane, 8)
+    return 32 * tr + 16 * (face // 2) + 4 * group + j, 32 * cb + 16 * (face % 2) + 2 * c + odd
+
+
+def plane_dims(problems: int, n: int):
+    """sort.rs:223-228."""
+    tiles = 1
+    while tiles * 32 < n:
+        tiles *= 2
+    return 32 * tiles, 32 * ((problems + 31) // 32)
+
+
+def to_planes(values: np.ndarray, fill=0) -> np.ndarray:
+    """[problems, n] words laid out as the planes matrix a sort reads."""
+    problems, n = values.shape
+    out = np.full(plane_dims(problems, n), fill, dtype=values.dtype)
+    for q in range(problems):
+        for e in range(n):
+            out[plane_coord(q, e)] = values[q, e]
+    return out
+
+
+def from_planes(planes: np.ndarray, problems: int, n: int) -> np.ndarray:
+    out = np.empty((problems, n), dtype=planes.dtype)
+    for q in range(problems):
+        for e in range(n):
+            out[q, e] = planes[plane_coord(q, e)]
+    return out
+
+
+def sort_rows(bits: np.ndarray, is_i32: bool, descending: bool):
+    """sort.rs:5-13: the stable order on (key, original index); `total_cmp` for F32 words, two's complement for
+    I32; a descending sort reverses the keys and keeps ties in ascending index.  [problems, n] -> (keys, indices)."""
+    bits = np.asarray(bits, dtype=np.uint32)
+    key = bits.view(np.int32).astype(np.int64) if is_i32 else _total_key(bits).astype(np.int64)
+    if descending:
+        key = -key
+    order = np.argsort(key, axis=1, kind="stable")
+    return np.take_along_axis(bits, order, axis=1), order.astype(np.int32)
+
+
+# ------------------------------------------------------------------ seeded draws on the device
+_ROLES = {"unit": (0, 0), "uniform": (1, 1), "bernoulli": (2, 2), "normal": (3, 4), "int_range": (5, 5), "int_words": (6, 6)}
+
+
+def _mix64(z):
+    with np.errstate(over="ignore"):
+        z = z + _GOLD
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        return z ^ (z >> np.uint64(31))
+
+
+def random_words(base: int, role: int, n: int) -> np.ndarray:
+    """The word of position i in a role: the high half of splitmix64(splitmix64(base ^ role) + i golden), the
+    seed function of crates/tt-kernels/src/prng.rs:34-36 taken an element instead of a tile."""
+    with np.errstate(over="ignore"):
+        seed = _mix64(np.array([(base ^ role) & 0xFFFFFFFFFFFFFFFF], dtype=np.uint64))[0]
+        return (_mix64(seed + np.arange(n, dtype=np.uint64) * _GOLD) >> np.uint64(32)).astype(np.uint32)
+
+
+def random_unit(words: np.ndarray) -> np.ndarray:
+    """prng.rs:41-42: (0x3f800000 | word >> 9) - 1.0, exactly k 2^-23."""
+    return ((words >> u32(9)) | u32(0x3F800000)).view(np.float32) - f32(1.0)
+
+
+def random_draw(dims, draw, base: int) -> np.ndarray:
+    """crates/tt-kernels/src/prng.rs:449-595: each draw as the reference's arithmetic on unit uniforms.  F32
+    results as float32, integer ones as int32."""
+    name, args = draw[0], draw[1:]
+    n = dims[0] * dims[1]
+    ra, rb = _ROLES[name]
+    w = random_words(base, ra, n)
+    u = random_unit(w)
+    if name == "unit":
+        out = u
+    elif name == "uniform":
+        lo, hi = f32(args[0]), f32(args[1])
+        v = (u * f32(hi - lo)).astype(np.float32) + lo
+        top = np.nextafter(hi, f32(-np.inf), dtype=np.float32)
+        out = np.minimum(v.astype(np.float32), top)
+    elif name == "bernoulli":
+        ones = u < f32(args[0])
+        out = ones.astype(np.int32) if args[1] else ones.astype(np.float32)
+    elif name == "normal":
+        u2 = random_unit(random_words(base, rb, n))
+        radius = np.sqrt((f32(-2.0) * np.log((f32(1.0) - u).astype(np.float32)).astype(np.float32)).astype(np.float32))
+        z = (radius * np.cos((f32(2 * np.pi) * u2).astype(np.float32)).astype(np.float32)).astype(np.float32)
+        out = ((z * f32(args[1])).astype(np.float32) + f32(args[0])).astype(np.float32)
+        if args[2]:
+            out = np.trunc(out).astype(np.int64).clip(-2**31, 2**31 - 1).astype(np.int32)
+    elif name == "int_range":
+        lo, hi = args
+        out = (lo + np.trunc((u * f32(hi - lo)).astype(np.float32)).astype(np.int64)).astype(np.int32)
+    else:
+        out = w.view(np.int32)
+    return out.reshape(dims)
+
+
+def pool_bf16(a_bits: np.ndarray, windows, divisors, dims) -> np.ndarray:
+    """crates/tt-kernels/src/fpu.rs:39-132: each window's BF16 values summed sixteen a block in F32, the blocks'
+    partial sums added in order, the total divided by the divisor as F32."""
+    a = from_bf16(a_bits)
+    out = np.empty(len(windows), dtype=np.float32)
+    for w, taps in enumerate(windows):
+        total = None
+        for i0 in range(0, len(taps), 16):
+            part = f32(0.0)
+            for r, c in taps[i0:i0 + 16]:
+                part = f32(part + a[r, c])
+            total = part if total is None else f32(total + part)
+        out[w] = f32(total / f32(divisors[w]))
+    return out.reshape(dims)

@@ -52,6 +52,15 @@ cudaError_t launch_attention_tc(const void*, uint64_t, uint64_t, const void*, ui
                                 const AttnBlockDev*, uint64_t, uint64_t, uint64_t, uint64_t, float, int, void*, uint64_t, int*,
                                 cudaStream_t) { OK_LAUNCH; }
 cudaError_t launch_scatter_rows_into(void*, uint64_t, uint64_t, int, const int32_t*, uint64_t, const void*, uint64_t, int*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_cast_f16(const void*, void*, uint64_t, int, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_cast_block(const void*, uint64_t, void*, uint64_t, uint64_t, int, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_gather_addrs(const uint64_t*, uint64_t, int, void*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_select_taps(const void*, uint64_t, uint64_t, int, const int32_t*, uint64_t, uint64_t, int, void*, uint64_t, int*, cudaStream_t) { OK_LAUNCH; }
+uint64_t scan_chunks(int op, uint64_t rows, uint64_t) { return op >= 2 && rows >= 512 ? 4 : 1; }
+cudaError_t launch_scan(const uint32_t*, uint32_t*, uint64_t, uint64_t, int, uint32_t*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_sort_planes(const uint32_t*, uint64_t, uint64_t, uint32_t, int, int, uint32_t*, uint32_t*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_random(uint32_t*, uint64_t, int, float, float, int32_t, int32_t, int, uint64_t, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_pool_windows(const uint16_t*, const uint32_t*, const uint32_t*, const float*, uint64_t, float*, cudaStream_t) { OK_LAUNCH; }
 cudaError_t launch_gemm_simt(const GemmArgs&, cudaStream_t) { OK_LAUNCH; }
 cudaError_t launch_store_block_many(const void*, uint64_t, void* const*, int, uint64_t, uint64_t, uint64_t, cudaStream_t) { OK_LAUNCH; }
 bool gemm_skinny_supported(const GemmArgs& g) { return g.in_bf16 && g.batch <= 1 && !g.a_trans && !g.b_trans && g.m <= 4 && g.n % 8 == 0; }

@@ -303,3 +303,85 @@ def test_no_device_is_reported(fake):
         C.c_int.in_dll(fake, "fake_cuda_device_count").value = 1
     with pytest.raises(TtError):
         CudaEngine(3, lib=fake)                                                 # no such card
+
+
+def test_movers_casts_scan_sort_and_draws_dims_and_refusals(e):     # server.rs:137,309,317,414,578,758,768,779
+    from metalium_rs_b200 import engine as E
+    a, h = f32(e, 70, 100), e.upload_bf16(np.zeros((70, 100), np.uint16), 70, 100)
+    assert e.cast_block((a, (32, 64), (33, 31)), True)[1] == (33, 31)
+    assert e.cast_block((h, (0, 0), (70, 100)), False)[1] == (70, 100)
+    assert e.cast_f16(a, True)[1] == (70, 100) and e.cast_f16(h, False)[1] == (70, 100)
+    for bad in (lambda: e.cast_block((h, (0, 0), (1, 1)), True), lambda: e.cast_block((a, (69, 0), (2, 1)), True),
+                lambda: e.cast_f16(h, True), lambda: e.cast_f16(a, False)):
+        with pytest.raises(TtError) as err:
+            bad()
+        assert err.value.status == 2
+    b = f32(e, 3, 5)
+    assert e.repack_many([a, b], [(0, (69, 99)), (1, (2, 4))] * 3, (2, 3))[1] == (2, 3)
+    with pytest.raises(TtError) as err:
+        e.repack_many([a, b], [(1, (3, 0))], (1, 1))
+    assert err.value.status == 6                                                   # DOMAIN, found on the host
+    for bad in (lambda: e.repack_many([a, h], [(0, (0, 0))], (1, 1)), lambda: e.repack_many([a], [(0, (0, 0))], (1, 2)),
+                lambda: e.repack_many([], [], (0, 0))):
+        with pytest.raises(TtError) as err:
+            bad()
+        assert err.value.status == 2
+    idx = e.upload_bits(np.zeros((9, 40), np.int32), 9, 40, I32)
+    assert e.select_taps(a, idx, True)[1] == (40, 8 * 128 + 100)                 # index.rs:139-141
+    assert e.select_taps(b, idx, False)[1] == (40, 8 * 32 + 5)
+    with pytest.raises(TtError):
+        e.select_taps(a, a, False)                                                 # indices must be I32
+    i32 = e.upload_bits(np.zeros((70, 100), np.int32), 70, 100, I32)
+    assert e.scan(a, E.SCAN_SUM)[1] == (70, 100) and e.scan(i32, E.SCAN_IMAX)[1] == (70, 100)
+    big = e.upload_bits(np.zeros((600, 4), np.int32), 600, 4, I32)
+    t0 = e.device_traffic().launches
+    e.scan(big, E.SCAN_ISUM)
+    assert e.device_traffic().launches - t0 == 2                                   # row chunks: fold, then scan from the prefix
+    for bad in (lambda: e.scan(a, E.SCAN_ISUM), lambda: e.scan(i32, E.SCAN_MIN_NAN), lambda: e.scan(a, 10)):
+        with pytest.raises(TtError) as err:
+            bad()
+        assert err.value.status == 2
+    planes = f32(e, 64, 96)
+    (k, kd), idx_out = e.sort_planes(planes, F32, 40, True, True)
+    assert kd == (64, 96) and idx_out[1] == (64, 96) and e.dims_of(idx_out[0]) == ((64, 96), I32)
+    assert e.sort_planes(planes, F32, 64, False, False)[1] is None
+    for n, elem in ((0, F32), (1025, F32), (32, F32), (65, F32), (40, I32)):
+        with pytest.raises(TtError) as err:
+            e.sort_planes(planes, elem, n, False, False)
+        assert err.value.status == 2
+    assert e.pow(a, ("scalar", 2.0))[1] == (70, 100) and e.pow(a, ("int", i32))[1] == (70, 100)
+    with pytest.raises(TtError):
+        e.pow(a, ("tensor", b))
+    for draw, elem in ((("unit",), F32), (("uniform", -1.0, 1.0), F32), (("bernoulli", 0.5, True), I32), (("normal", 0.0, 1.0, False), F32),
+                       (("normal", 0.0, 1.0, True), I32), (("int_range", -3, 9), I32), (("int_words",), I32)):
+        out, dims = e.random_dram((5, 7), draw, 42)
+        assert dims == (5, 7) and e.dims_of(out) == ((5, 7), elem)
+    for draw in (("uniform", 1.0, 1.0), ("bernoulli", -0.1, False), ("normal", 0.0, float("nan"), False), ("int_range", 0, 0),
+                 ("int_range", -(1 << 23), 1)):
+        with pytest.raises(TtError) as err:
+            e.random_dram((2, 2), draw, 0)
+        assert err.value.status == 2
+    assert e.pool_bf16(h, [[[0, 0], [1, 1]], [[69, 99]]] * 3, [2, 1] * 3, (2, 3))[1] == (2, 3)
+    assert e.dims_of(e.pool_bf16(h, [[[0, 0]]], [1], (1, 1))[0]) == ((1, 1), F32)
+    for bad, status in ((([[[0, 0]]] * 2, [1, 1], (1, 1)), 2), (([[]], [1], (1, 1)), 2), (([[[0, 0]]], [0], (1, 1)), 2),
+                        (([[[70, 0]]], [1], (1, 1)), 6)):
+        with pytest.raises(TtError) as err:
+            e.pool_bf16(h, *bad)
+        assert err.value.status == status
+    with pytest.raises(TtError):
+        e.pool_bf16(a, [[[0, 0]]], [1], (1, 1))
+    m = e.metadata(np.arange(6, dtype=np.uint32), (2, 3), I32)
+    assert np.array_equal(e.download_bits(m).ravel(), np.arange(6)) and e.dims_of(m) == ((2, 3), I32)
+    largest, total = e.gddr_free_bytes()
+    assert largest <= total
+
+
+def test_metadata_inside_a_trace_is_replayed(fake, e):              # server.rs:95 "replayable mover immediates"
+    a = f32(e, 4, 4)
+    e.begin_trace()
+    m = e.metadata(np.arange(16, dtype=np.uint32), (4, 4), I32)
+    e.eltwise(kinds.RELU, 0.0, a)
+    t = e.end_trace()
+    e.run_trace(t)
+    assert e.dims_of(m) == ((4, 4), I32)
+    e.release_trace(t)

@@ -276,3 +276,73 @@ def test_seeded_generator_first_draws():
     assert orc.integers(0xC0F1, 5, (64,), 10).max() <= 9
     g = orc.normal(0xC0F4, 1, (10000,), 0.02)
     assert abs(g.std() - 0.02) < 1e-3
+
+
+def test_binary16_conversions_are_ieee():   # crates/tt-kernels/src/fp16.rs:172-176, 271-275 against numpy's binary16
+    x = (orc.splitmix64(0xF16, 1, 200000) >> np.uint64(32)).astype(np.uint32)
+    edge = np.array([0, 0x80000000, 0x33000000, 0x33000001, 0x387FE000, 0x387FFFFF, 0x38800000, 0x477FEFFF, 0x477FF000,
+                     0x7F800000, 0xFF800000, 0x33800000, 1], dtype=np.uint32)
+    x = np.concatenate([x, edge])
+    f = x.view(np.float32)
+    ok = ~np.isnan(f)
+    with np.errstate(all="ignore"):
+        want = f[ok].astype(np.float16).view(np.uint16)
+    assert np.array_equal(orc.f16_bits_from_f32_bits(x[ok]), want)
+    h = np.arange(65536, dtype=np.uint32).astype(np.uint16)
+    w = orc.f32_bits_from_f16_bits(h)
+    fin = ~np.isnan(h.view(np.float16))
+    assert np.array_equal(w[fin], h.view(np.float16)[fin].astype(np.float32).view(np.uint32))
+    assert np.array_equal(orc.f16_bits_from_f32_bits(w[fin]), h[fin])              # widening then narrowing is the identity
+    # a NaN keeps its sign and top payload bits and is made quiet
+    assert orc.f16_bits_from_f32_bits(np.array([0xFFC12345, 0x7F800001], np.uint32)).tolist() == [0xFE09, 0x7E00]
+    assert orc.f32_bits_from_f16_bits(np.array([0xFC01, 0x7E00], np.uint16)).tolist() == [0xFFC02000, 0x7FC00000]
+
+
+def test_scans_follow_row_order_from_the_identity():   # crates/tt-kernels/src/sfpu/scan.rs:196-231
+    x = np.array([[1.0, -0.0], [2.0, -0.0], [3.0, 5.0]], dtype=np.float32)
+    assert np.array_equal(orc.scan(x.view(np.uint32), "sum").view(np.float32), [[1, 0], [3, 0], [6, 5]])
+    assert orc.scan(x.view(np.uint32), "sum")[0, 1] == 0                               # +0.0 + -0.0 = +0.0
+    assert orc.scan(x.view(np.uint32), "prod")[1, 1] == 0                              # 1 * -0 * -0 = +0
+    nan, nnan = np.uint32(0x7FC00001), np.uint32(0xFFC00002)
+    col = np.array([[0x40000000], [0x80000000], [0x00000000], [nan], [0x3F800000], [nnan]], dtype=np.uint32)
+    # Flex's cummin: the earlier zero wins a tie; a NaN replaces the accumulator and is only replaced by a NaN
+    assert orc.scan(col, "min_nan").ravel().tolist() == [0x40000000, 0x80000000, 0x80000000, nan, nan, nnan]
+    # raw total order: -NaN < ... < -0 < +0 < ... < +NaN
+    assert orc.scan(col, "min").ravel().tolist() == [0x40000000, 0x80000000, 0x80000000, 0x80000000, 0x80000000, nnan]
+    assert orc.scan(col, "max").ravel().tolist() == [0x40000000, 0x40000000, 0x40000000, nan, nan, nan]
+    i = np.array([[0x7FFFFFFF], [1], [0x80000000]], dtype=np.uint32)
+    assert orc.scan(i, "isum").ravel().tolist() == [0x7FFFFFFF, 0x80000000, 0]        # wrapping
+    assert orc.scan(i, "imin").ravel().tolist() == [0x7FFFFFFF, 1, 0x80000000]
+    assert orc.scan(np.array([[3], [0x80000001], [2]], np.uint32), "iprod").ravel().tolist() == [3, 0x80000003, 6]
+
+
+def test_sort_order_and_the_planes_layout():   # crates/tt-kernels/src/sfpu/sort.rs:5-13, 198-228
+    v = np.array([[0x7FC00000, 0x80000000, 0x00000000, 0xFFC00000, 0x3F800000, 0x3F800000, 0xFF800000]], dtype=np.uint32)
+    k, i = orc.sort_rows(v, False, False)
+    assert k.ravel().tolist() == [0xFFC00000, 0xFF800000, 0x80000000, 0, 0x3F800000, 0x3F800000, 0x7FC00000]
+    assert i.ravel().tolist() == [3, 6, 1, 2, 4, 5, 0]
+    k, i = orc.sort_rows(v, False, True)
+    assert i.ravel().tolist() == [0, 4, 5, 2, 1, 6, 3]                                 # ties still in ascending index
+    k, i = orc.sort_rows(np.array([[5, 0xFFFFFFFF, 5, 0x80000000]], np.uint32), True, False)
+    assert i.ravel().tolist() == [3, 1, 0, 2]
+    assert orc.plane_dims(33, 100) == (128, 64) and orc.plane_dims(1, 1) == (32, 32)
+    seen = {orc.plane_coord(q, e) for q in range(32) for e in range(32)}
+    assert len(seen) == 1024 and max(r for r, _ in seen) == 31 and max(c for _, c in seen) == 31   # a tile: 32 problems x 32 positions
+    assert orc.plane_coord(0, 0) == (0, 0) and orc.plane_coord(1, 0) == (0, 2) and orc.plane_coord(0, 1) == (0, 1)
+    assert orc.plane_coord(8, 0) == (1, 0) and orc.plane_coord(0, 2) == (4, 0) and orc.plane_coord(0, 8) == (0, 16)
+    assert orc.plane_coord(0, 16) == (16, 0) and orc.plane_coord(32, 32) == (32, 32)
+
+
+def test_device_draws_are_the_reference_arithmetic_on_unit_uniforms():   # crates/tt-kernels/src/prng.rs:41-42, 449-595
+    u = orc.random_draw((300, 300), ("unit",), 5)
+    assert u.min() >= 0 and u.max() < 1 and np.array_equal(u * 2.0**23, np.round(u * 2.0**23)) and abs(u.mean() - 0.5) < 5e-3
+    v = orc.random_draw((300, 300), ("uniform", 1.0, 1.0000002), 5)
+    assert v.max() < np.float32(1.0000002) and v.min() >= 1.0
+    r = orc.random_draw((300, 300), ("int_range", -5, 12), 5)
+    assert r.min() == -5 and r.max() == 11 and r.dtype == np.int32
+    z = orc.random_draw((400, 400), ("normal", 2.0, 3.0, False), 5)
+    assert abs(z.mean() - 2.0) < 0.03 and abs(z.std() - 3.0) < 0.03
+    b = orc.random_draw((400, 400), ("bernoulli", 0.3, True), 5)
+    assert abs(b.mean() - 0.3) < 5e-3 and set(np.unique(b)) == {0, 1}
+    assert orc.select_taps(np.arange(6, dtype=np.uint32).reshape(2, 3), np.array([[1, 2], [0, 1]]), True).tolist() == \
+        [[3, 4, 5] + [0] * 29 + [0, 1, 2], [0] * 32 + [3, 4, 5]]
