@@ -156,7 +156,8 @@ int32_t b200_ipc_open(b200_engine*, const uint8_t handle[64], void** ptr);
 int32_t b200_ipc_close(b200_engine*, void* ptr);
 /* `matmul_dram` / `matmul_dram_bf16`: C = op(A) op(B).  F32 operands give an F32
  * result; with out_bf16 the F32 accumulator is rounded once to BF16.  BF16
- * operands accumulate in F32. */
+ * operands accumulate in F32.  One F32 operand against one in BF16 storage (a weight kept by
+ * `cast_bf16_storage`, server.rs:150) is bit for bit the F32 product with the stored operand widened. */
 int32_t b200_matmul(b200_engine*, b200_buffer a, int32_t a_transposed, b200_buffer b, int32_t b_transposed,
                     int32_t out_bf16, b200_buffer* out, uint64_t out_dims[2]);
 /* `matmul_dram_batched(_layout)`: one [m,k]x[k,n] product per (Block,Block) pair,

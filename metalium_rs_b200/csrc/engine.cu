@@ -693,8 +693,19 @@ int32_t b200_matmul(b200_engine* e, b200_buffer a, int32_t ta, b200_buffer b, in
   if (!st) st = e->need(b, &B, "matmul");
   if (st) return st;
   const bool abf = A->elem == B200_BF16, bbf = B->elem == B200_BF16;
-  if ((A->elem != B200_F32 && !abf) || (B->elem != B200_F32 && !bbf) || abf != bbf)
-    return e->fail(B200_UNSUPPORTED, "matmul: operands must both be F32 or both BF16 (got elem %d, %d)", A->elem, B->elem);
+  if ((A->elem != B200_F32 && !abf) || (B->elem != B200_F32 && !bbf))
+    return e->fail(B200_UNSUPPORTED, "matmul: operands must be F32 or BF16 (got elem %d, %d)", A->elem, B->elem);
+  if (abf != bbf) {
+    // An F32 operand against one kept in BF16 storage (`cast_bf16_storage`, crates/burn-tt/src/server.rs:150;
+    // crates/tt-kernels/src/session.rs:3751-3756): bit for bit the F32 product with the stored operand widened,
+    // so it is widened into a block that lives for this product and the F32 path runs.
+    b200_buffer wide = 0; uint64_t wd[2];
+    st = b200_cast_float(e, abf ? a : b, 0, &wide, wd);
+    if (st) return st;
+    st = b200_matmul(e, abf ? wide : a, ta, abf ? b : wide, tb, out_bf16, out, out_dims);
+    e->drop(wide);
+    return st;
+  }
   const uint64_t m = ta ? A->cols : A->rows, k = ta ? A->rows : A->cols;
   const uint64_t k2 = tb ? B->cols : B->rows, n = tb ? B->rows : B->cols;
   if (k != k2)

@@ -529,6 +529,11 @@ class CudaEngine:
         blk = _block(a)
         return self._call(self._lib.b200_cast_block, C.byref(blk), C.c_int32(bf16))
 
+    def cast_bf16_storage(self, a: int, store: bool) -> Out:
+        """`cast_bf16_storage` (server.rs:150): an F32 buffer kept as BF16, which a product reads beside an F32
+        operand, or such a buffer widened back."""
+        return self.cast_float(a, store)
+
     def cast_f16(self, a: int, to_f16: bool) -> Out:
         return self._call(self._lib.b200_cast_f16, C.c_uint64(a), C.c_int32(to_f16))
 
@@ -646,6 +651,29 @@ class CudaEngine:
 
     def run_trace(self, trace: int):
         self._check(self._lib.b200_run_trace(self._e, C.c_uint64(trace)))
+
+    def run_trace_io(self, trace: int, input: int, values, output: int):
+        """The trait's `run_trace(trace, input, values, output)` (server.rs:648-657): overwrite the input, replay,
+        read the output back; returns (output, (write_s, replay_s, read_s))."""
+        run = self.run_generic_trace(trace, [(input, values)], [(output, "f32")])
+        return run[0][0], run[1]
+
+    def run_generic_trace(self, trace: int, inputs, outputs):
+        """`run_generic_trace` (server.rs:746-753, 1205-1238): inputs = [(buffer, array of 32-bit values)], outputs =
+        [(buffer, "f32" | "bits")]; returns ([arrays], (write_s, replay_s, read_s))."""
+        import time
+        self.sync()
+        t0 = time.perf_counter()
+        for buf, values in inputs:
+            a = np.ascontiguousarray(values)
+            assert a.dtype.itemsize == 4
+            self._check(self._lib.b200_write_f32(self._e, C.c_uint64(buf), _ptr(a), C.c_uint64(a.size)))
+        t1 = time.perf_counter()
+        self.run_trace(trace)
+        self.sync()
+        t2 = time.perf_counter()
+        read = [self.download(buf) if kind == "f32" else self.download_bits(buf) for buf, kind in outputs]
+        return read, (t1 - t0, t2 - t1, time.perf_counter() - t2)
 
     def release_trace(self, trace: int):
         self._lib.b200_release_trace(self._e, C.c_uint64(trace))

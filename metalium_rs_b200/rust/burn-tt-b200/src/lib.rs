@@ -6,7 +6,8 @@
 //! Source only: no Rust toolchain exists where this was written, so it has not been compiled.
 //! Every method is one call of include/b200tt.h through `b200-sys`.
 use b200_sys as sys;
-use burn_tt::server::{BlockArg, BufferId, Engine, PowArg, Serve, SortedBuffers};
+use burn_tt::server::{BlockArg, BufferId, Engine, GenericTraceRun, InputPayload, OutputKind, OutputPayload, PowArg, Serve,
+                      SortedBuffers, TraceRun};
 use burn_tt::TtError;
 use tt_kernels::session::BatchedLayout;
 use tt_kernels::sfpu::reduce::{Axis, ReduceOp};
@@ -307,6 +308,9 @@ impl Engine for CudaEngine {
         let b = sys::b200_block_arg { id: a.id, at: [a.at[0] as u64, a.at[1] as u64], dims: [a.dims[0] as u64, a.dims[1] as u64] };
         produce!(self, b200_cast_block(&b, bf16 as i32))
     }
+    // A logical F32 buffer kept as BF16 (half the bytes, read by a product as its B) and back: the storage is
+    // plain BF16 here, and `b200_matmul` takes one F32 and one BF16 operand (server.rs:150-158).
+    fn cast_bf16_storage(&mut self, id: BufferId, store: bool) -> Made { produce!(self, b200_cast_float(id, store as i32)) }
     fn cast_f16(&mut self, id: BufferId, to_f16: bool) -> Made { produce!(self, b200_cast_f16(id, to_f16 as i32)) }
     fn pow(&mut self, x: BufferId, y: PowArg) -> Made {
         match y {
@@ -367,6 +371,47 @@ impl Engine for CudaEngine {
         let mut t = 0u64;
         let st = unsafe { sys::b200_end_trace(self.raw, &mut t) };
         self.check(st).map(|_| t)
+    }
+    // One round trip (server.rs:648-657, 1114-1143): wait for what was queued, write the input, replay to its
+    // end, read the output; the three times are the write's, the replay's and the read's.
+    fn run_trace(&mut self, trace: u64, input: BufferId, values: &[f32], output: BufferId) -> Result<TraceRun, TtError> {
+        use std::time::Instant;
+        let st = unsafe { sys::b200_sync(self.raw) }; self.check(st)?;
+        let t0 = Instant::now();
+        let st = unsafe { sys::b200_write_f32(self.raw, input, values.as_ptr(), values.len() as u64) }; self.check(st)?;
+        let t1 = Instant::now();
+        let st = unsafe { sys::b200_run_trace(self.raw, trace) }; self.check(st)?;
+        let st = unsafe { sys::b200_sync(self.raw) }; self.check(st)?;
+        let t2 = Instant::now();
+        let output = self.download(output)?;
+        Ok(TraceRun { output, write: t1 - t0, replay: t2 - t1, read: t2.elapsed() })
+    }
+    // Several inputs overwritten, the replay, several outputs read (server.rs:746-753, 1205-1238).  A 32-bit
+    // payload of either kind is written as words: `b200_write_f32` copies four-byte elements whatever their type.
+    fn run_generic_trace(&mut self, trace: u64, inputs: &[(BufferId, InputPayload)], outputs: &[(BufferId, OutputKind)])
+                         -> Result<GenericTraceRun, TtError> {
+        use std::time::Instant;
+        let st = unsafe { sys::b200_sync(self.raw) }; self.check(st)?;
+        let t0 = Instant::now();
+        for (id, payload) in inputs {
+            let (p, n) = match payload {
+                InputPayload::F32(v) => (v.as_ptr(), v.len()),
+                InputPayload::Bits(v) => (v.as_ptr() as *const f32, v.len()),
+            };
+            let st = unsafe { sys::b200_write_f32(self.raw, *id, p, n as u64) }; self.check(st)?;
+        }
+        let t1 = Instant::now();
+        let st = unsafe { sys::b200_run_trace(self.raw, trace) }; self.check(st)?;
+        let st = unsafe { sys::b200_sync(self.raw) }; self.check(st)?;
+        let t2 = Instant::now();
+        let mut read = Vec::with_capacity(outputs.len());
+        for (id, kind) in outputs {
+            read.push(match kind {
+                OutputKind::F32 => OutputPayload::F32(self.download(*id)?),
+                OutputKind::Bits => OutputPayload::Bits(self.download_bits(*id)?),
+            });
+        }
+        Ok(GenericTraceRun { outputs: read, write: t1 - t0, replay: t2 - t1, read: t2.elapsed() })
     }
     fn release_trace(&mut self, trace: u64) { unsafe { sys::b200_release_trace(self.raw, trace) } }
     fn set_op_label(&mut self, label: &'static str) {

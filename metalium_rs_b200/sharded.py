@@ -47,6 +47,37 @@ def interleave(staged, n: int):
     return staged.permute(1, 0, 2).reshape(m, world * per)[:, :n].contiguous()
 
 
+class MeshExecution:
+    """Completion evidence of the sharded products, the reference's `FabricExecution`
+    (crates/tt-kernels/src/shard.rs:139-145; `Engine::mesh_execution`, crates/burn-tt/src/server.rs:587):
+    how many products each rank has completed and how much it has handed to its peers.  A rank counts
+    a step once its exchange has been ordered behind the product (the gather waited for, or the
+    all-reduce behind the peer stores enqueued); `report()` synchronises, gathers the ranks' counts and
+    returns them with the transfers and bytes this rank sent."""
+
+    def __init__(self, rank: int, world: int):
+        self.rank, self.world = rank, world
+        self.completed = 0
+        self.transfers = 0
+        self.bytes = 0
+
+    def count(self, transfers: int, nbytes: int):
+        self.completed += 1
+        self.transfers += transfers
+        self.bytes += nbytes
+
+    def report(self, sync=None, group=None) -> dict:
+        import torch.distributed as dist
+        if sync:
+            sync()
+        counts = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(counts, self.completed, group=group)
+        else:
+            counts = [self.completed]
+        return {"completed_matmuls": counts, "acknowledged_transfers": self.transfers, "acknowledged_bytes": self.bytes}
+
+
 class ShardedMatmul:
     """C = A B on `world` GPUs, B's columns split.  A [M,K] and the local B slice [K,per] are
     engine buffers that stay resident; `run()` returns a new buffer holding the full row-major C.
@@ -90,6 +121,7 @@ class ShardedMatmul:
         self.a_panels = [eng.slice_rows(a_buf, p * self.mp, self.mp)[0] for p in range(panels)] if panels > 1 else [a_buf]
         self.moves = [(((p * world + r) * self.mp, 0), (p * self.mp, r * self.per), (self.mp, self.per), False)
                       for p in range(panels) for r in range(world)]
+        self.mesh = MeshExecution(rank, world)
 
     def run(self) -> int:
         import torch
@@ -111,11 +143,15 @@ class ShardedMatmul:
                 work.wait()      # the engine's stream waits for the gather; the panel may then be reused
                 eng.free(out)
         eng.set_matmul_sm_limit(0)
+        self.mesh.count(self.panels, self.m * self.per * (2 if self.bf16 else 4) * (g - 1))
         full, _ = eng.copy_blocks(self.staged_buf, self.moves, (self.m, self.n))
         return full  # the caller gives it back with release()
 
     def release(self, buf: int):
         self.eng.free(buf)
+
+    def mesh_execution(self) -> dict:
+        return self.mesh.report(self.eng.sync)
 
     def close(self):
         pass
@@ -165,6 +201,7 @@ class PeerStoreMatmul:
         self.panels = 1
         self.stream = torch.cuda.ExternalStream(eng.stream())
         self.flag = torch.zeros(1, device=torch.device("cuda", torch.cuda.current_device()))
+        self.mesh = MeshExecution(rank, world)
         dist.barrier()
 
     def run(self) -> int:
@@ -175,10 +212,14 @@ class PeerStoreMatmul:
         self.eng.matmul_into(self.a, self.b, self.dst[which], (self.m, self.n), self.parts[self.rank][0], True)
         with torch.cuda.stream(self.stream):
             dist.all_reduce(self.flag)               # behind the product on the engine's stream: a device-side barrier
+        self.mesh.count(self.world - 1, self.m * self.per * 2 * (self.world - 1))
         return self.c[which]
 
     def release(self, buf: int):
         pass
+
+    def mesh_execution(self) -> dict:
+        return self.mesh.report(self.eng.sync)
 
     def close(self):
         import torch.distributed as dist

@@ -142,3 +142,23 @@ def test_two_engines_are_independent(lib):
         o2, _ = e2.eltwise_op(EltwiseOp(kinds.RELU, 0, 0), i2)
         assert np.array_equal(e1.download(o1), np.maximum(a, 0))
         assert np.array_equal(e2.download(o2), np.maximum(-a, 0))
+
+
+def test_a_generic_trace_run_writes_replays_and_reads(eng):   # server.rs:746-753, 1205-1238; the one-input form :648-657
+    from metalium_rs_b200 import I32, kinds
+    x = np.arange(12, dtype=np.float32).reshape(3, 4)
+    k = np.arange(12, dtype=np.int32).reshape(3, 4)
+    ix, ik = eng.upload(x, 3, 4), eng.upload_bits(k, 3, 4, I32)
+    eng.begin_trace()
+    doubled, _ = eng.eltwise(kinds.MUL_SCALAR, 2.0, ix)
+    shifted, _ = eng.eltwise_op((kinds.INT_ADD_S, np.array([5], np.int32).view(np.float32)[0], 0.0), ik)
+    meta = eng.metadata(np.array([[7, 8]], np.uint32), (1, 2), I32)     # written again by every replay
+    trace = eng.end_trace()
+    (got_f, got_i, got_m), times = eng.run_generic_trace(trace, [(ix, x + 1), (ik, k * 3)], [(doubled, "f32"), (shifted, "bits"), (meta, "bits")])
+    assert np.array_equal(got_f, (x + 1) * 2) and np.array_equal(got_i.view(np.int32), k * 3 + 5) and got_m.tolist() == [[7, 8]]
+    assert len(times) == 3 and all(t >= 0 for t in times)
+    out, _ = eng.run_trace_io(trace, ix, x - 4, doubled)
+    assert np.array_equal(out, (x - 4) * 2)
+    eng.release_trace(trace)
+    for i in (ix, ik, doubled, shifted, meta):
+        eng.free(i)

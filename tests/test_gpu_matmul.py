@@ -366,3 +366,26 @@ def test_split_tf32_path_is_exact_on_small_integers_and_chosen_automatically(eng
     small, _ = eng.matmul_dram(ia, True, ia, False)   # [320,512]x[512,320]: still large enough
     for i in (ia, ib, out, small):
         eng.free(i)
+
+
+@pytest.mark.parametrize("mkn,stored_b,tb", [((64, 784, 128), True, False), ((33, 70, 50), True, True), ((512, 576, 1536), True, False),
+                                              ((48, 96, 40), False, False)])
+def test_a_weight_kept_in_bf16_storage_multiplies_as_its_widened_self(eng, mkn, stored_b, tb):
+    # crates/burn-tt/src/server.rs:150-158, crates/tt-kernels/src/session.rs:3751-3756: bit for bit the F32 product
+    m, k, n = mkn
+    a = orc.uniform(0xB16, 1, (m, k), -1.0, 1.0)
+    b = orc.uniform(0xB16, 2, (n, k) if tb else (k, n), -1.0, 1.0)
+    ia, ib = eng.upload(a, *a.shape), eng.upload(b, *b.shape)
+    which = ib if stored_b else ia
+    stored, sd = eng.cast_bf16_storage(which, True)
+    wide, wd = eng.cast_bf16_storage(stored, False)
+    assert sd == wd
+    if stored_b:
+        mixed, dims = eng.matmul_dram(ia, False, stored, tb)
+        plain, _ = eng.matmul_dram(ia, False, wide, tb)
+    else:
+        mixed, dims = eng.matmul_dram(stored, False, ib, tb)
+        plain, _ = eng.matmul_dram(wide, False, ib, tb)
+    assert dims == (m, n) and np.array_equal(eng.download_bits(mixed), eng.download_bits(plain))
+    for i in (ia, ib, stored, wide, mixed, plain):
+        eng.free(i)

@@ -370,6 +370,9 @@ def test_movers_casts_scan_sort_and_draws_dims_and_refusals(e):     # server.rs:
         assert err.value.status == status
     with pytest.raises(TtError):
         e.pool_bf16(a, [[[0, 0]]], [1], (1, 1))
+    w = e.cast_bf16_storage(f32(e, 100, 40), True)[0]                              # server.rs:150
+    assert e.dims_of(w) == ((100, 40), BF16) and e.matmul_dram(a, False, w, False)[1] == (70, 40)
+    assert e.matmul_dram(w, True, a, True)[1] == (40, 70)
     m = e.metadata(np.arange(6, dtype=np.uint32), (2, 3), I32)
     assert np.array_equal(e.download_bits(m).ravel(), np.arange(6)) and e.dims_of(m) == ((2, 3), I32)
     largest, total = e.gddr_free_bytes()

@@ -39,7 +39,10 @@ def _worker(rank, world, port, q):
         local = torch.from_numpy(a @ b[:, lo:hi])          # K whole: the same sums as one device
         staged = sharded.gather_columns(local, world)
         full = sharded.interleave(staged, n)
-        q.put((rank, bool(np.array_equal(full.numpy(), a @ b)), tuple(staged.shape)))
+        mesh = sharded.MeshExecution(rank, world)           # shard.rs:139-145: completion evidence, gathered over the ranks
+        for _ in range(rank + 2):
+            mesh.count(1, local.numel() * 4 * (world - 1))
+        q.put((rank, bool(np.array_equal(full.numpy(), a @ b)), tuple(staged.shape), mesh.report()))
         # a rank that fails before the collective is seen by the others as an error, not a hang
         dist.barrier()
     finally:
@@ -69,3 +72,6 @@ def test_two_ranks_gather_the_whole_product_bit_for_bit():
     assert sorted(r[0] for r in res) == [0, 1]
     assert all(r[1] for r in res)
     assert all(r[2] == (2, 48, 64) for r in res)
+    for r in res:
+        assert r[3] == {"completed_matmuls": [2, 3], "acknowledged_transfers": r[0] + 2,
+                        "acknowledged_bytes": (r[0] + 2) * 48 * 64 * 4}
