@@ -183,6 +183,16 @@ impl Engine for CudaEngine {
     fn matmul_dram_bf16(&mut self, a: BufferId, ta: bool, b: BufferId, tb: bool) -> Made {
         produce!(self, b200_matmul(a, ta as i32, b, tb as i32, 1))
     }
+    // A fidelity names how many of the Tensix multiplier's passes a product takes (server.rs:203-226); this
+    // engine's products are F32-accurate whatever is asked, which is the highest fidelity's result, and exact on
+    // the integer slices `MatmulMode::Accurate` multiplies at the lowest one.
+    fn matmul_dram_at(&mut self, a: BufferId, ta: bool, b: BufferId, tb: bool, _fidelity: tt_kernels::matmul::Fidelity) -> Made {
+        self.matmul_dram(a, ta, b, tb)
+    }
+    fn matmul_dram_batched_at(&mut self, a: BufferId, b: BufferId, items: &[(Block, Block)], mkn: [usize; 3],
+                              _fidelity: tt_kernels::matmul::Fidelity) -> Made {
+        self.matmul_dram_batched(a, b, items, mkn)
+    }
     fn matmul_dram_batched(&mut self, a: BufferId, b: BufferId, items: &[(Block, Block)], mkn: [usize; 3]) -> Made {
         self.matmul_dram_batched_layout(a, b, items, mkn, BatchedLayout::STACKED)
     }
