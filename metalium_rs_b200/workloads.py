@@ -212,11 +212,21 @@ class LlamaPrefill:
         self.fused_items = eng.attention_block_array(fused_items)
         self.last_rows = [(0, b * t + t - 1) for b in range(batch)]
 
-    def forward(self, ids_buf: int, all_positions: bool = False):
+    def forward(self, ids_buf: int, all_positions: bool = False, cache: "LlamaDecode" = None):
         """ids [1, batch*seq] I32 resident.  Returns (logits buffer [batch or batch*seq, vocab] F32,
-        argmax buffer I32); the caller frees both."""
+        argmax buffer I32); the caller frees both.  With `cache`, every layer's rotated keys and its values are
+        also written into that generation's cache at positions 0 .. seq-1 of each sequence, as the reference's
+        first chunk write does (crates/tt-models/src/kv_cache.rs:231-241, start 0): the bits a token-by-token
+        generation would have left there, so `cache.continue_from(argmax, seq)` goes on from the prompt."""
         e, c, K = self.eng, self.cfg, kinds
         n = self.batch * self.seq
+        if cache is not None:
+            assert cache.batch == self.batch and cache.max_len >= self.seq and cache.cfg is self.cfg
+            key = (cache.max_len,)
+            if getattr(self, "_cache_rows_key", None) != key:
+                rows = (np.arange(self.batch)[:, None] * cache.max_len + np.arange(self.seq)[None, :]).astype(np.int32)
+                self._cache_rows = e.upload_bits(rows.reshape(1, -1).view(np.uint32), 1, n, I32)
+                self._cache_rows_key = key
         t, hd = self.seq, c.head_dim
         el = lambda kind, a, b=None, bf=False: e.eltwise_op_as(EltwiseOp(kind, 0.0, 0.0), a, b, None, bf)[0]
         emb, _ = e.select_rows(self.w["embed"], ids_buf)                     # ops.rs:4958 embedding
@@ -230,6 +240,9 @@ class LlamaPrefill:
             # RoPE on the query and key heads together: they share the head width and the tables (rope.rs:129)
             qk, _ = e.rope_blocks((qkv, (0, 0), (n, qk_cols)), (self.cos, (0, 0), (t, hd)),
                                   (self.sin, (0, 0), (t, hd)), hd, True)
+            if cache is not None:   # the chunk's rows of the cache: keys after RoPE, values as projected
+                e.scatter_rows_into(cache.kc[l], self._cache_rows, (qk, (0, self.q_cols), (n, self.kv_cols)))
+                e.scatter_rows_into(cache.vc[l], self._cache_rows, (qkv, (0, qk_cols), (n, self.kv_cols)))
             if self.fused:   # scores, mask, softmax, P V and the merge of heads as one kernel
                 om, _ = e.attention_blocks(qk, qk, qkv, self.fused_items, (t, hd, t, hd), 1.0 / float(np.sqrt(hd)), True,
                                            (n, self.q_cols))
@@ -372,6 +385,15 @@ class LlamaDecode:
         p = e.upload_bits(np.array([[position]], np.int32).view(np.uint32), 1, 1, I32)
         e.copy_into(fresh, self.ids); e.copy_into(p, self.pos)
         e.free(fresh); e.free(p)
+
+    def continue_from(self, ids_buf: int, position: int):
+        """Go on from a prompt a `LlamaPrefill.forward(..., cache=self)` wrote: `ids_buf` ([batch, 1] I32, the
+        prefill's argmax) becomes the next input and `position` (the prompt's length) the next position.
+        Nothing is read back."""
+        e = self.eng
+        p = e.upload_bits(np.array([[position]], np.int32).view(np.uint32), 1, 1, I32)
+        e.copy_into(ids_buf, self.ids); e.copy_into(p, self.pos)
+        e.free(p)
 
     def set_ids(self, ids: np.ndarray):
         """Overwrite the next input ids (teacher forcing); the position is untouched."""
