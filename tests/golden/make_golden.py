@@ -1,4 +1,4 @@
-"""Writes tests/golden/hot_path.npz: outputs of the CPU oracle on small seeded inputs.
+"""Writes tests/golden/hot_path.npz and more_ops.npz: outputs of the CPU oracle on small seeded inputs.
 
 The reference's own golden file (crates/tt-tests/tests/golden/mnist_reduced.txt) pins Tensix
 TF32 bits on MNIST and cannot be reproduced on a GPU, and the reference (Rust) cannot be
@@ -84,6 +84,48 @@ def attention_blocks_case():
     return tuple(orc.to_bf16(orc.normal(SEED, t, (128, 64))) for t in (11, 12, 13))
 
 
+# ---- the rest of the trait: scans, sort, binary16, taps, pooling windows, draws (tests/golden/more_ops.npz) ----
+SPECIAL = np.array([0x00000000, 0x80000000, 0x7F800000, 0xFF800000, 0x7FC00000, 0xFFC00001, 0x3F800000, 0xBF800000,
+                    0x00000001, 0x7F7FFFFF], dtype=np.uint32)
+
+
+def more_inputs():
+    x = np.round(orc.uniform(SEED, 21, (40, 24), -4, 4)).view(np.uint32).copy()
+    sel = orc.integers(SEED, 22, (40, 24), 7) == 0
+    x[sel] = SPECIAL[orc.integers(SEED, 23, (40, 24), len(SPECIAL))[sel]]
+    xi = (orc.splitmix64(SEED, 24, 40 * 24) >> np.uint64(32)).astype(np.uint32).reshape(40, 24)
+    sums = orc.uniform(SEED, 25, (40, 24), -4, 4).view(np.uint32)
+    table = orc.normal(SEED, 26, (20, 24))
+    taps = orc.integers(SEED, 27, (3, 11), 21).astype(np.int32)
+    windows = [[[r, c], [r + 1, c], [r, c + 1], [r + 1, c + 1]] for r in range(0, 18, 3) for c in range(0, 20, 5)]
+    windows[1] = [[i % 20, (7 * i) % 24] for i in range(37)]           # more than two blocks of sixteen
+    return x, xi, sums, table, taps, windows
+
+
+def build_more():
+    x, xi, sums, table, taps, windows = more_inputs()
+    out = {}
+    for op in orc.SCAN_OPS:
+        src = xi if op.startswith("i") else (sums if op in ("sum", "prod") else x)
+        out["scan_" + op] = orc.scan(src, op)
+    for desc in (False, True):
+        k, i = orc.sort_rows(x[:, :20].T.copy(), False, desc)          # 20 problems of 40 positions
+        out[f"sort_f32_{int(desc)}_keys"], out[f"sort_f32_{int(desc)}_idx"] = k, i
+        k, i = orc.sort_rows(xi[:, :20].T.copy() & np.uint32(0x8000000F), True, desc)
+        out[f"sort_i32_{int(desc)}_keys"], out[f"sort_i32_{int(desc)}_idx"] = k, i
+    out["f16_narrow"] = orc.f16_bits_from_f32_bits(np.concatenate([x.ravel(), sums.ravel(), xi.ravel()]))
+    out["f16_widen"] = orc.f32_bits_from_f16_bits((xi.ravel() >> np.uint32(16)).astype(np.uint16))
+    out["select_taps"] = orc.select_taps(table.view(np.uint32), taps, True)
+    out["pool_bf16"] = orc.pool_bf16(orc.to_bf16(table), windows, [len(w) for w in windows], (6, 4)).view(np.uint32)
+    out["repack_many"] = orc.repack_many([x, xi], [(i % 2, ((5 * i) % 40, (3 * i) % 24)) for i in range(60)], (6, 10))
+    for name, draw in (("unit", ("unit",)), ("uniform", ("uniform", -3.0, 5.5)), ("bernoulli", ("bernoulli", 0.3, True)),
+                       ("int_range", ("int_range", -5, 12)), ("int_words", ("int_words",))):
+        out["draw_" + name] = orc.random_draw((9, 31), draw, 0x5EED)
+    return out
+
+
 if __name__ == "__main__":
     np.savez_compressed(Path(__file__).with_name("hot_path.npz"), **build())
     print("wrote", Path(__file__).with_name("hot_path.npz"))
+    np.savez_compressed(Path(__file__).with_name("more_ops.npz"), **build_more())
+    print("wrote", Path(__file__).with_name("more_ops.npz"))

@@ -100,3 +100,64 @@ def test_engine_matches_the_golden_vectors(eng):
     assert np.max(np.abs(eng.download(n2) - GOLD["add_rms_norm"])) <= 1e-5 * np.abs(GOLD["add_rms_norm"]).max()
     for v in list(res.values()) + [ia, ib, ic, im, ig, ico, isi, ja, jb, ha, hb, ii, ix, iy, iq, ik, iv, iam, jq, jk, jv, s2, n2]:
         eng.free(v)
+
+
+MORE = np.load(HERE / "golden" / "more_ops.npz")
+
+
+def test_oracle_reproduces_the_vectors_of_the_rest_of_the_trait():
+    now = G.build_more()
+    assert sorted(now) == sorted(MORE.files)
+    for k in MORE.files:
+        a, b = np.asarray(now[k]), MORE[k]
+        assert a.shape == b.shape and a.dtype == b.dtype, k
+        assert (np.ascontiguousarray(a).view(np.uint8) == np.ascontiguousarray(b).view(np.uint8)).all(), k
+
+
+@pytest.mark.gpu
+def test_engine_matches_the_vectors_of_the_rest_of_the_trait(eng):
+    from metalium_rs_b200 import F32, I32
+    x, xi, sums, table, taps, windows = G.more_inputs()
+    ix, ixi, isums = eng.upload_bits(x, 40, 24, F32), eng.upload_bits(xi, 40, 24, I32), eng.upload_bits(sums, 40, 24, F32)
+    for code, op in enumerate(orc.SCAN_OPS):
+        src = ixi if op.startswith("i") else (isums if op in ("sum", "prod") else ix)
+        o, _ = eng.scan(src, code)
+        got, want = eng.download_bits(o), MORE["scan_" + op]
+        if op in ("sum", "prod"):      # an arithmetic NaN's payload is not compared
+            g, w = got.view(np.float32), want.view(np.float32)
+            assert np.all((got == want) | (np.isnan(g) & np.isnan(w))), op
+        else:
+            assert np.array_equal(got, want), op
+        eng.free(o)
+    for is_i32, name, src in ((False, "f32", x[:, :20].T.copy()), (True, "i32", xi[:, :20].T.copy() & np.uint32(0x8000000F))):
+        planes = orc.to_planes(src)
+        ip = eng.upload_bits(planes, *planes.shape, I32 if is_i32 else F32)
+        for desc in (False, True):
+            (k, dims), idx = eng.sort_planes(ip, I32 if is_i32 else F32, 40, desc, True)
+            assert np.array_equal(orc.from_planes(eng.download_bits(k), 20, 40), MORE[f"sort_{name}_{int(desc)}_keys"])
+            assert np.array_equal(orc.from_planes(eng.download_bits(idx[0]), 20, 40).view(np.int32), MORE[f"sort_{name}_{int(desc)}_idx"])
+            eng.free(k); eng.free(idx[0])
+        eng.free(ip)
+    words = np.concatenate([x.ravel(), sums.ravel(), xi.ravel()]).reshape(-1, 24)
+    iw = eng.upload_bits(words, *words.shape, F32)
+    o, _ = eng.cast_f16(iw, True)
+    assert np.array_equal(eng.download_bf16(o).ravel(), MORE["f16_narrow"]); eng.free(o); eng.free(iw)
+    halves = (xi >> np.uint32(16)).astype(np.uint16)
+    ih = eng.upload_bf16(halves, 40, 24)
+    o, _ = eng.cast_f16(ih, False)
+    assert np.array_equal(eng.download_bits(o).ravel(), MORE["f16_widen"]); eng.free(o); eng.free(ih)
+    it, itap = eng.upload(table, 20, 24), eng.upload_bits(taps, 3, 11, I32)
+    o, _ = eng.select_taps(it, itap, True)
+    assert np.array_equal(eng.download_bits(o), MORE["select_taps"]); eng.free(o)
+    ib = eng.upload_bf16(orc.to_bf16(table), 20, 24)
+    o, _ = eng.pool_bf16(ib, windows, [len(w) for w in windows], (6, 4))
+    assert np.array_equal(eng.download_bits(o), MORE["pool_bf16"]); eng.free(o)
+    o, _ = eng.repack_many([ix, ixi], [(i % 2, ((5 * i) % 40, (3 * i) % 24)) for i in range(60)], (6, 10))
+    assert np.array_equal(eng.download_bits(o), MORE["repack_many"]); eng.free(o)
+    for name, draw in (("unit", ("unit",)), ("uniform", ("uniform", -3.0, 5.5)), ("bernoulli", ("bernoulli", 0.3, True)),
+                       ("int_range", ("int_range", -5, 12)), ("int_words", ("int_words",))):
+        o, _ = eng.random_dram((9, 31), draw, 0x5EED)
+        assert np.array_equal(eng.download_bits(o), np.ascontiguousarray(MORE["draw_" + name]).view(np.uint32)), name
+        eng.free(o)
+    for i in (ix, ixi, isums, it, itap, ib):
+        eng.free(i)
