@@ -333,6 +333,101 @@ def attention_fused(eng, q_buf: int, k_buf: int, v_buf: int, batch_heads: int, t
     return eng.attention_blocks(q_buf, k_buf, v_buf, items, (t, d, t, d), 1.0 / float(np.sqrt(d)), False, (batch_heads * t, d))[0]
 
 
+# ------------------------------------------------------------------------- convolution and pooling over NHWC tables
+def _tap_at(out: int, tap: int, stride: int, dilation: int, padding: int, length: int):
+    """crates/burn-tt/src/ops/nhwc.rs:159-170: the input coordinate a tap reads, or None in the padding."""
+    i = out * stride + tap * dilation - padding
+    return i if 0 <= i < length else None
+
+
+def conv2d_nhwc(eng, table_buf: int, shape, weight: np.ndarray, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1)):
+    """A 2-D convolution as the reference sends it (crates/burn-tt/src/ops/nhwc.rs:226-292): the activation is its
+    NHWC table [n h w, c] (resident, F32); a [taps, positions] index of table rows that depends on the shapes alone
+    goes up once; `select_taps` makes the patch matrix [positions, (taps-1) ceil32(c) + c] on the device (a padding
+    tap reads the zero row); the weights [o, c, kh, kw] are relaid on the device to [that many rows, o] by
+    `repack_many` from the weight and a zero (rows a tap's channels do not fill are zero); one product, one
+    broadcast add of the bias.  Returns (the [positions, o] result buffer: the next layer's NHWC table, (oh, ow))."""
+    n, c, h, w = shape
+    o, wc, kh, kw = weight.shape
+    assert wc == c
+    oh = (h + 2 * padding[0] - dilation[0] * (kh - 1) - 1) // stride[0] + 1
+    ow = (w + 2 * padding[1] - dilation[1] * (kw - 1) - 1) // stride[1] + 1
+    taps, positions, rows = kh * kw, n * oh * ow, n * h * w
+    idx = np.empty((taps, positions), np.int32)
+    for t in range(taps):
+        ky, kx = divmod(t, kw)
+        for q in range(positions):
+            b, y, xo = q // (oh * ow), q // ow % oh, q % ow
+            iy, ix = _tap_at(y, ky, stride[0], dilation[0], padding[0], h), _tap_at(xo, kx, stride[1], dilation[1], padding[1], w)
+            idx[t, q] = rows if iy is None or ix is None else (b * h + iy) * w + ix
+    ii = eng.upload_bits(idx.view(np.uint32), taps, positions, I32)
+    patches, pd = eng.select_taps(table_buf, ii, any(p > 0 for p in padding))
+    eng.free(ii)
+    pitch = -(-c // 32) * 32
+    k = (taps - 1) * pitch + c
+    assert pd == (positions, k)
+    wm = eng.upload(np.ascontiguousarray(weight, np.float32).reshape(o, c * taps), o, c * taps)    # [o, (c, kh, kw)] as stored
+    zero = eng.zeros_dram((1, 1))[0]
+    sources = []
+    for r in range(k):
+        t, ch = divmod(r, pitch)
+        for oc in range(o):
+            sources.append((0, (oc, ch * taps + t)) if ch < c else (1, (0, 0)))
+    wk, _ = eng.repack_many([wm, zero], sources, (k, o))
+    eng.free(wm); eng.free(zero)
+    out, _ = eng.matmul_dram(patches, False, wk, False)
+    eng.free(patches); eng.free(wk)
+    if bias is not None:
+        ib = eng.upload(np.ascontiguousarray(bias, np.float32).reshape(1, o), 1, o)
+        out2, _ = eng.eltwise_op(EltwiseOp(kinds.ADD, 0.0, 0.0), out, ib)
+        eng.free(out); eng.free(ib)
+        out = out2
+    return out, (oh, ow)
+
+
+def max_pool2d_nhwc(eng, table_buf: int, shape, kernel, stride, padding=(0, 0), dilation=(1, 1)):
+    """`max_pool2d` as one select and a fold over the taps (crates/burn-tt/src/ops/nhwc.rs:296-418): a padding tap
+    reads its window's first valid datum; the taps' column blocks are folded in window order with exact compares
+    and selects -- the first NaN, else the first maximum, bit for bit.  c must be whole tiles of 32 columns.
+    Returns (the [positions, c] result buffer, (oh, ow))."""
+    n, c, h, w = shape
+    assert c % 32 == 0
+    oh = (h + 2 * padding[0] - dilation[0] * (kernel[0] - 1) - 1) // stride[0] + 1
+    ow = (w + 2 * padding[1] - dilation[1] * (kernel[1] - 1) - 1) // stride[1] + 1
+    taps, positions = kernel[0] * kernel[1], n * oh * ow
+    idx = np.zeros((taps, positions), np.int32)
+    for q in range(positions):
+        b, y, xo = q // (oh * ow), q // ow % oh, q % ow
+        at = []
+        for t in range(taps):
+            iy = _tap_at(y, t // kernel[1], stride[0], dilation[0], padding[0], h)
+            ix = _tap_at(xo, t % kernel[1], stride[1], dilation[1], padding[1], w)
+            at.append(None if iy is None or ix is None else (b * h + iy) * w + ix)
+        first = next(a for a in at if a is not None)
+        idx[:, q] = [first if a is None else a for a in at]
+    ii = eng.upload_bits(idx.view(np.uint32), taps, positions, I32)
+    patches, _ = eng.select_taps(table_buf, ii, False)
+    eng.free(ii)
+    K = kinds
+    el = lambda kind, a, b=None, cc=None: eng.eltwise_op(EltwiseOp(kind, 0.0, 0.0), a, b, cc)[0]
+    block = lambda t: eng.copy_blocks(patches, [((0, t * c), (0, 0), (positions, c), False)], (positions, c))[0]
+    best = block(0)
+    nan = el(K.IS_NAN, best)
+    for t in range(1, taps):
+        b = block(t)
+        b_nan = el(K.IS_NAN, b)
+        gt, not_nan = el(K.GT, b, best), el(K.BOOL_NOT, nan)
+        either = el(K.BOOL_OR, gt, b_nan)
+        take = el(K.BOOL_AND, not_nan, either)
+        best2 = el(K.MASK_WHERE, best, take, b)         # `b` where `take`, else the best so far
+        nan2 = el(K.BOOL_OR, nan, b_nan)
+        for i in (b, b_nan, gt, not_nan, either, take, best, nan):
+            eng.free(i)
+        best, nan = best2, nan2
+    eng.free(nan); eng.free(patches)
+    return best, (oh, ow)
+
+
 # ------------------------------------------------------------------------- generation (decode steps)
 def _int_scalar(v: int) -> float:
     """An integer kind's scalar travels as the bits of the op's F32 scalar field (tensor.rs:3785)."""

@@ -794,3 +794,55 @@ def pool_bf16(a_bits: np.ndarray, windows, divisors, dims) -> np.ndarray:
             total = part if total is None else f32(total + part)
         out[w] = f32(total / f32(divisors[w]))
     return out.reshape(dims)
+
+
+# ------------------------------------------------------------------ convolution and max pooling (NCHW in, NCHW out)
+def conv2d(x: np.ndarray, weight: np.ndarray, bias, stride, padding, dilation):
+    """Direct 2-D cross-correlation (Burn's conv2d, groups 1) accumulated in F64: (truth, S) with S the sum of
+    the products' magnitudes, the normalisation of crates/tt-tests/tests/step11_burn.rs:15-17."""
+    n, c, h, w = x.shape
+    o, _, kh, kw = weight.shape
+    oh = (h + 2 * padding[0] - dilation[0] * (kh - 1) - 1) // stride[0] + 1
+    ow = (w + 2 * padding[1] - dilation[1] * (kw - 1) - 1) // stride[1] + 1
+    xp = np.zeros((n, c, h + 2 * padding[0], w + 2 * padding[1]), np.float64)
+    xp[:, :, padding[0]:padding[0] + h, padding[1]:padding[1] + w] = x
+    out = np.zeros((n, o, oh, ow), np.float64)
+    mag = np.zeros((n, o, oh, ow), np.float64)
+    w64 = weight.astype(np.float64)
+    for ky in range(kh):
+        for kx in range(kw):
+            patch = xp[:, :, ky * dilation[0]:ky * dilation[0] + (oh - 1) * stride[0] + 1:stride[0],
+                       kx * dilation[1]:kx * dilation[1] + (ow - 1) * stride[1] + 1:stride[1]]
+            out += np.einsum("nchw,oc->nohw", patch, w64[:, :, ky, kx])
+            mag += np.einsum("nchw,oc->nohw", np.abs(patch), np.abs(w64[:, :, ky, kx]))
+    if bias is not None:
+        out += np.asarray(bias, np.float64).reshape(1, o, 1, 1)
+        mag += np.abs(np.asarray(bias, np.float64)).reshape(1, o, 1, 1)
+    return out, mag
+
+
+def max_pool2d(x_bits: np.ndarray, kernel, stride, padding, dilation) -> np.ndarray:
+    """crates/burn-tt/src/ops/nhwc.rs:12-17, 396-416 on words [n, c, h, w]: over a window's valid taps in window
+    order, the first NaN, else the first maximum (IEEE `>`, so the earlier of +0 and -0 stays)."""
+    n, c, h, w = x_bits.shape
+    oh = (h + 2 * padding[0] - dilation[0] * (kernel[0] - 1) - 1) // stride[0] + 1
+    ow = (w + 2 * padding[1] - dilation[1] * (kernel[1] - 1) - 1) // stride[1] + 1
+    out = np.empty((n, c, oh, ow), np.uint32)
+    for y in range(oh):
+        for xo in range(ow):
+            best = None
+            for ky in range(kernel[0]):
+                for kx in range(kernel[1]):
+                    iy, ix = y * stride[0] + ky * dilation[0] - padding[0], xo * stride[1] + kx * dilation[1] - padding[1]
+                    if not (0 <= iy < h and 0 <= ix < w):
+                        continue
+                    b = x_bits[:, :, iy, ix]
+                    if best is None:
+                        best = b.copy()
+                        continue
+                    bf, cf = b.view(np.float32), best.view(np.float32)
+                    with np.errstate(invalid="ignore"):
+                        take = ~np.isnan(cf) & ((bf > cf) | np.isnan(bf))
+                    best = np.where(take, b, best)
+            out[:, :, y, xo] = best
+    return out

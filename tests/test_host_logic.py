@@ -388,3 +388,15 @@ def test_metadata_inside_a_trace_is_replayed(fake, e):              # server.rs:
     e.run_trace(t)
     assert e.dims_of(m) == ((4, 4), I32)
     e.release_trace(t)
+
+
+def test_convolution_and_pooling_callers_issue_the_reference_sequence(e):   # burn-tt/src/ops/nhwc.rs:226-292, 296-418
+    from metalium_rs_b200 import workloads as W
+    t = f32(e, 2 * 6 * 6, 3)
+    l0 = e.device_traffic().launches
+    out, (oh, ow) = W.conv2d_nhwc(e, t, (2, 3, 6, 6), np.ones((8, 3, 3, 3), np.float32), np.zeros(8, np.float32), (1, 1), (1, 1))
+    assert (oh, ow) == (6, 6) and e.dims_of(out) == ((72, 8), F32)
+    assert e.device_traffic().launches - l0 == 4             # select_taps, repack_many, product, bias add (zeros is a memset)
+    p = f32(e, 1 * 8 * 8, 32)
+    best, (oh, ow) = W.max_pool2d_nhwc(e, p, (1, 32, 8, 8), (2, 2), (2, 2))
+    assert (oh, ow) == (4, 4) and e.dims_of(best) == ((16, 32), F32)

@@ -346,3 +346,18 @@ def test_device_draws_are_the_reference_arithmetic_on_unit_uniforms():   # crate
     assert abs(b.mean() - 0.3) < 5e-3 and set(np.unique(b)) == {0, 1}
     assert orc.select_taps(np.arange(6, dtype=np.uint32).reshape(2, 3), np.array([[1, 2], [0, 1]]), True).tolist() == \
         [[3, 4, 5] + [0] * 29 + [0, 1, 2], [0] * 32 + [3, 4, 5]]
+
+
+def test_convolution_and_pooling_restatements_agree_with_torch_cpu():   # a second, independent check (never the only one)
+    import torch
+    x = orc.normal(1, 1, (2, 5, 9, 8)); w = orc.uniform(1, 2, (4, 5, 3, 2), -1, 1); b = orc.uniform(1, 3, (4,), -1, 1)
+    truth, s = orc.conv2d(x, w, b, (2, 1), (1, 2), (1, 2))
+    ref = torch.nn.functional.conv2d(torch.from_numpy(x).double(), torch.from_numpy(w).double(), torch.from_numpy(b).double(),
+                                     stride=(2, 1), padding=(1, 2), dilation=(1, 2)).numpy()
+    assert truth.shape == ref.shape and np.abs(truth - ref).max() <= 1e-12 and np.all(s >= np.abs(truth) - 1e-12)
+    xb = np.round(orc.uniform(2, 1, (1, 3, 8, 9), -3, 3))
+    m = orc.max_pool2d(xb.view(np.uint32), (3, 2), (2, 1), (1, 0), (1, 2)).view(np.float32)
+    assert np.array_equal(m, torch.nn.functional.max_pool2d(torch.from_numpy(xb), (3, 2), (2, 1), (1, 0), (1, 2)).numpy())
+    nan = np.array([[[[1.0, np.nan], [5.0, np.nan]]]], np.float32)
+    nan.view(np.uint32)[0, 0, 1, 1] = 0xFFC00005
+    assert orc.max_pool2d(nan.view(np.uint32), (2, 2), (1, 1), (0, 0), (1, 1))[0, 0, 0, 0] == 0x7FC00000   # the first NaN
