@@ -428,6 +428,35 @@ def max_pool2d_nhwc(eng, table_buf: int, shape, kernel, stride, padding=(0, 0), 
     return best, (oh, ow)
 
 
+def avg_pool2d_windows(shape, kernel, stride, padding=(0, 0), count_include_pad=True):
+    """The windows and divisors of an average pooling over a BF16 NCHW tensor stored [n c h, w] (the geometry
+    crates/burn-tt/src/ops/pool.rs:254-268 hands to `pool_bf16`): a window lists its valid taps as [row, col] of
+    that matrix; the divisor counts the padding taps too when `count_include_pad`."""
+    n, c, h, w = shape
+    oh = (h + 2 * padding[0] - kernel[0]) // stride[0] + 1
+    ow = (w + 2 * padding[1] - kernel[1]) // stride[1] + 1
+    windows, divisors = [], []
+    for plane in range(n * c):
+        for y in range(oh):
+            for xo in range(ow):
+                taps = [[plane * h + iy, ix] for ky in range(kernel[0]) for kx in range(kernel[1])
+                        for iy, ix in [(y * stride[0] + ky - padding[0], xo * stride[1] + kx - padding[1])]
+                        if 0 <= iy < h and 0 <= ix < w]
+                windows.append(taps)
+                divisors.append(kernel[0] * kernel[1] if count_include_pad else len(taps))
+    return windows, divisors, (n * c * oh, ow)
+
+
+def avg_pool2d_bf16(eng, x_buf: int, shape, kernel, stride, padding=(0, 0), count_include_pad=True) -> int:
+    """`avg_pool2d` of a BF16 tensor (pool.rs:254-275): the window means in F32 by `pool_bf16`, rounded once to
+    BF16.  Returns the [n c oh, ow] BF16 buffer."""
+    windows, divisors, dims = avg_pool2d_windows(shape, kernel, stride, padding, count_include_pad)
+    wide, _ = eng.pool_bf16(x_buf, windows, divisors, dims)
+    out, _ = eng.cast_float(wide, True)
+    eng.free(wide)
+    return out
+
+
 # ------------------------------------------------------------------------- generation (decode steps)
 def _int_scalar(v: int) -> float:
     """An integer kind's scalar travels as the bits of the op's F32 scalar field (tensor.rs:3785)."""

@@ -50,3 +50,21 @@ def test_max_pool2d_is_the_first_nan_else_the_first_maximum(eng, shape, kernel, 
     got = eng.download_bits(out).reshape(shape[0], oh, ow, shape[1]).transpose(0, 3, 1, 2)
     assert np.array_equal(got, want)
     eng.free(t); eng.free(out)
+
+
+@pytest.mark.parametrize("shape,kernel,stride,padding,include", [((2, 3, 8, 8), (2, 2), (2, 2), (0, 0), True),
+                                                                 ((1, 4, 9, 7), (3, 3), (2, 1), (1, 1), False),
+                                                                 ((1, 2, 12, 12), (5, 5), (3, 3), (2, 2), True)])
+def test_avg_pool2d_of_a_bf16_tensor(eng, shape, kernel, stride, padding, include):   # burn-tt/src/ops/pool.rs:254-275
+    import torch
+    x = orc.to_bf16(orc.normal(0xC2, 1, shape))
+    n, c, h, w = shape
+    buf = eng.upload_bf16(x.reshape(n * c * h, w), n * c * h, w)
+    out = W.avg_pool2d_bf16(eng, buf, shape, kernel, stride, padding, include)
+    windows, divisors, dims = W.avg_pool2d_windows(shape, kernel, stride, padding, include)
+    want = orc.to_bf16(orc.pool_bf16(x.reshape(n * c * h, w), windows, divisors, dims))
+    got = eng.download_bf16(out).reshape(dims)
+    assert np.array_equal(got, want)
+    ref = torch.nn.functional.avg_pool2d(torch.from_numpy(orc.from_bf16(x)), kernel, stride, padding, count_include_pad=include).numpy()
+    assert np.max(np.abs(orc.from_bf16(got).reshape(ref.shape) - ref)) <= 2.0 ** -8 * np.abs(ref).max() + 1e-6    # one BF16 rounding
+    eng.free(buf); eng.free(out)
