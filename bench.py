@@ -367,8 +367,52 @@ def extras(eng):
     sb = 2 * 4096 * 32768 * 4
     out["suite"]["softmax_4096x32768"] = {"ms": ms, "gbs": sb / ms / 1e6, "frac_of_measured_hbm": sb / ms / 1e6 / hbm}
     eng.free(sx)
+    out["rest_of_trait"] = rest_of_trait(eng, timed, hbm)
     out["callers"] = callers(eng, timed)
     return out
+
+
+def rest_of_trait(eng, timed, hbm):
+    """Scans, sort, binary16 casts, draws and taps: GB/s of algorithmic bytes (what each op must read and write once)."""
+    from metalium_rs_b200 import F32, I32
+    from metalium_rs_b200 import engine as E
+    rng = np.random.default_rng(5)
+    res = {}
+
+    def one(name, make, nbytes):
+        def f():
+            r = make()
+            for i in (r if isinstance(r, list) else [r]):
+                eng.free(i)
+        ms = timed(f, reps=10)
+        res[name] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm}
+
+    n = 8192
+    x = eng.upload(rng.random((n, n), dtype=np.float32), n, n)
+    nb = n * n * 4
+    one("scan_sum_8192x8192", lambda: eng.scan(x, E.SCAN_SUM)[0], 2 * nb)
+    one("scan_min_nan_8192x8192", lambda: eng.scan(x, E.SCAN_MIN_NAN)[0], 2 * nb)
+    one("cast_f16_narrow_8192x8192", lambda: eng.cast_f16(x, True)[0], nb * 3 // 2)
+    one("cast_block_4096x4096", lambda: eng.cast_block((x, (1024, 2048), (4096, 4096)), True)[0], 4096 * 4096 * 6)
+    one("random_unit_8192x8192", lambda: eng.random_dram((n, n), ("unit",), 1)[0], nb)
+    one("random_normal_8192x8192", lambda: eng.random_dram((n, n), ("normal", 0.0, 1.0, False), 1)[0], nb)
+    eng.free(x)
+    t = eng.upload(rng.random((1 << 20, 64), dtype=np.float32), 1 << 20, 64)
+    one("scan_max_1Mx64_chunked", lambda: eng.scan(t, E.SCAN_MAX)[0], 3 * (1 << 20) * 64 * 4)
+    one("scan_sum_1Mx64_row_order", lambda: eng.scan(t, E.SCAN_SUM)[0], 2 * (1 << 20) * 64 * 4)
+    eng.free(t)
+    p = eng.upload(rng.random((1024, 8192), dtype=np.float32), 1024, 8192)
+
+    def srt():
+        (k, _), i = eng.sort_planes(p, F32, 1024, False, True)
+        return [k, i[0]]
+    one("sort_8192_problems_x_1024", srt, 1024 * 8192 * 4 * 3)
+    eng.free(p)
+    tb = eng.upload_bf16(np.zeros((32768, 64), np.uint16), 32768, 64)
+    idx = eng.upload_bits(rng.integers(0, 32768, (9, 32768)).astype(np.int32).view(np.uint32), 9, 32768, I32)
+    one("select_taps_9x32768x64_bf16", lambda: eng.select_taps(tb, idx, True)[0], 9 * 32768 * 64 * 2 * 2)
+    eng.free(tb); eng.free(idx)
+    return res
 
 
 def callers(eng, timed):
@@ -502,7 +546,8 @@ def run_profile(args):
     membound: EXP, MUL by a row, full sum, per-row sum on [8192,8192] F32, three rounds.
     softmax: three row softmaxes of [1024, 32768].  prefill: two SmolLM2-135M-shape forward passes.
     gemm_small: the four projections of a prefill layer ([4096,576]x[576,960], x[576,576], x[576,3072],
-    [4096,1536]x[1536,576]), three rounds.  attention: three fused attentions of 64 blocks [1024, 128] (no mask).  decode: three `attention_rows`
+    [4096,1536]x[1536,576]), three rounds.  scan_sort: a row-order sum scan and a binary16 cast of [8192,8192] F32 and a
+    sort of 8192 problems of 1024 positions, three rounds.  attention: three fused attentions of 64 blocks [1024, 128] (no mask).  decode: three `attention_rows`
     of 512 heads on 128 key/value heads of [4096, 128] BF16."""
     from metalium_rs_b200 import COLS, I32, SUM, CudaEngine, EltwiseOp, build, kinds, workloads as W
     build.build()
@@ -550,6 +595,15 @@ def run_profile(args):
             items = eng.attention_item_array([((h, 0), ((h // 4) * l, 0), ((h // 4) * l, 0)) for h in range(heads)])
             for _ in range(3):
                 o, _ = eng.attention_rows([q, k, v, mask], items, [1, d, l, d], 0.088); eng.free(o)
+        elif args.profile == "scan_sort":
+            from metalium_rs_b200 import F32
+            from metalium_rs_b200 import engine as E
+            x = eng.upload(rng.random((8192, 8192), dtype=np.float32), 8192, 8192)
+            p = eng.upload(rng.random((1024, 8192), dtype=np.float32), 1024, 8192)
+            for _ in range(3):
+                o, _ = eng.scan(x, E.SCAN_SUM); eng.free(o)
+                o, _ = eng.cast_f16(x, True); eng.free(o)
+                (k, _), i = eng.sort_planes(p, F32, 1024, False, True); eng.free(k); eng.free(i[0])
         else:
             raise SystemExit(f"unknown profile {args.profile!r}")
         eng.sync()
@@ -570,7 +624,7 @@ def main():
     ap.add_argument("--extras", action="store_true", help="also time the rest of the sweep and the memory-bound suite")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
-    ap.add_argument("--profile", default="", help="run a short fixed sequence for an ncu capture: membound | softmax | prefill | gemm_small | attention | decode")
+    ap.add_argument("--profile", default="", help="run a short fixed sequence for an ncu capture: membound | softmax | prefill | gemm_small | attention | decode | scan_sort")
     ap.add_argument("--size", type=int, default=0, help="override the N=1 problem size (profiling on a small case)")
     args = ap.parse_args()
     if args.impl == "reference":
