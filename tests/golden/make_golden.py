@@ -117,7 +117,7 @@ def build_more():
     out["f16_widen"] = orc.f32_bits_from_f16_bits((xi.ravel() >> np.uint32(16)).astype(np.uint16))
     out["select_taps"] = orc.select_taps(table.view(np.uint32), taps, True)
     out["pool_bf16"] = orc.pool_bf16(orc.to_bf16(table), windows, [len(w) for w in windows], (6, 4)).view(np.uint32)
-    out["repack_many"] = orc.repack_many([x, xi], [(i % 2, ((5 * i) % 40, (3 * i) % 24)) for i in range(60)], (6, 10))
+    out["repack_many"] = orc.repack_many([x, sums], [(i % 2, ((5 * i) % 40, (3 * i) % 24)) for i in range(60)], (6, 10))
     for name, draw in (("unit", ("unit",)), ("uniform", ("uniform", -3.0, 5.5)), ("bernoulli", ("bernoulli", 0.3, True)),
                        ("int_range", ("int_range", -5, 12)), ("int_words", ("int_words",))):
         out["draw_" + name] = orc.random_draw((9, 31), draw, 0x5EED)

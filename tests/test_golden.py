@@ -152,7 +152,7 @@ def test_engine_matches_the_vectors_of_the_rest_of_the_trait(eng):
     ib = eng.upload_bf16(orc.to_bf16(table), 20, 24)
     o, _ = eng.pool_bf16(ib, windows, [len(w) for w in windows], (6, 4))
     assert np.array_equal(eng.download_bits(o), MORE["pool_bf16"]); eng.free(o)
-    o, _ = eng.repack_many([ix, ixi], [(i % 2, ((5 * i) % 40, (3 * i) % 24)) for i in range(60)], (6, 10))
+    o, _ = eng.repack_many([ix, isums], [(i % 2, ((5 * i) % 40, (3 * i) % 24)) for i in range(60)], (6, 10))
     assert np.array_equal(eng.download_bits(o), MORE["repack_many"]); eng.free(o)
     for name, draw in (("unit", ("unit",)), ("uniform", ("uniform", -3.0, 5.5)), ("bernoulli", ("bernoulli", 0.3, True)),
                        ("int_range", ("int_range", -5, 12)), ("int_words", ("int_words",))):
