@@ -11,8 +11,9 @@
 // once for all of them.  A job's positions are split over `splits` blocks when there are too few
 // jobs to fill the SMs (each block keeps its own maximum, sum and unnormalised rows, and a second
 // small kernel joins them).  The scores never leave shared memory.
-//   scores: a lane a key -- it walks its key's row in 32-byte steps (whole sectors) against the
-//           query rows broadcast from shared memory; no shuffles;
+//   scores: eight lanes a key, a lane a 16-byte unit (whole 128-byte lines a warp load), the partial sums of
+//           several keys joined by a butterfly of shuffles; for head widths that are not whole groups, a lane
+//           a key walking its row in 32-byte steps against the query rows broadcast from shared memory;
 //   softmax: the whole block a row;
 //   rows x V: a thread a 16-byte column group and a slice of positions, rows in registers.
 #include <cfloat>
@@ -72,7 +73,7 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float* sh) {
 }
 
 // grid (splits, jobs).  Shared memory: q [RT][d], s [RT][lc], red [slices][dv or less].
-template <typename KV, int RT>
+template <typename KV, int RT, bool GROUPED>
 __global__ void __launch_bounds__(THREADS, RT >= 8 ? 2 : (RT >= 4 ? 3 : 4))
 attention_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, uint64_t k_ld, const KV* __restrict__ v,
                       uint64_t v_ld, const uint32_t* __restrict__ mask, const AttnJob* __restrict__ jobs,
@@ -99,6 +100,83 @@ attention_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, uin
   }
   __syncthreads();
 
+  // ---- scores, grouped form: eight lanes a key, a lane a 16-byte unit of it, so a warp's load is four keys'
+  // whole 128-byte lines (a lane a key makes it 32 lines of 32 bytes, and the line lookups then bound the loads).
+  // A lane keeps its partial dot products for KB keys; a butterfly over the group's eight lanes adds them and
+  // leaves key kb's score in lane 8 kb / KB of the group.
+  if constexpr (GROUPED) {
+    constexpr int G = 8, NG = 32 / G, KB = RT >= 2 ? 4 : 8, LD = 4;
+    const int cg = lane & (G - 1), grp = lane / G;
+    const int iters = d / (G * UN);           // d / UN is a multiple of 8 on this path
+    for (int wb = warp * NG * KB; wb < n; wb += WARPS * NG * KB) {     // the same trip count for a warp's lanes
+      const int jb = wb + grp * KB;
+      float acc[RT][KB];
+#pragma unroll
+      for (int r = 0; r < RT; ++r)
+#pragma unroll
+        for (int b = 0; b < KB; ++b) acc[r][b] = 0.f;
+      for (int it = 0; it < iters; ++it) {
+        const int eoff = (cg + it * G) * UN;
+        const float* qp = qs + eoff;
+#pragma unroll
+        for (int b0 = 0; b0 < KB; b0 += LD) {
+          uint4 raw[LD];
+#pragma unroll
+          for (int u = 0; u < LD; ++u) {
+            const int j = jb + b0 + u;
+            raw[u] = Unit<KV>::load(k + job.k_off + (uint64_t)(j0 + (j < n ? j : 0)) * k_ld + eoff);
+          }
+#pragma unroll
+          for (int u = 0; u < LD; ++u) {
+            float x[UN];
+            Unit<KV>::widen(raw[u], x);
+#pragma unroll
+            for (int r = 0; r < RT; ++r) {
+              float a = acc[r][b0 + u];
+#pragma unroll
+              for (int e4 = 0; e4 < UN; e4 += 4) {
+                const float4 qq = *reinterpret_cast<const float4*>(qp + (size_t)r * d + e4);
+                a = fmaf(x[e4], qq.x, a); a = fmaf(x[e4 + 1], qq.y, a);
+                a = fmaf(x[e4 + 2], qq.z, a); a = fmaf(x[e4 + 3], qq.w, a);
+              }
+              acc[r][b0 + u] = a;
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < RT; ++r) {
+        // halving stages: a lane keeps the half of the keys its bit names and takes the partner's sums for them
+        int vals = KB;
+#pragma unroll
+        for (int off = G / 2; off >= 1; off >>= 1) {
+          const bool upper = (cg & off) != 0;
+          if (vals > 1) {
+            const int half = vals / 2;
+#pragma unroll
+            for (int i = 0; i < KB / 2; ++i) {
+              if (i < half) {
+                const float send = upper ? acc[r][i] : acc[r][i + half];
+                const float keep = upper ? acc[r][i + half] : acc[r][i];
+                acc[r][i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+              }
+            }
+            vals = half;
+          } else {
+            acc[r][0] += __shfl_xor_sync(0xffffffffu, acc[r][0], off);
+          }
+        }
+      }
+      // lane cg holds key cg * KB / G (every lane of a run of G / KB lanes the same sum)
+      const int kb = cg / (G / KB);
+      const int j = jb + kb;
+      if ((cg % (G / KB)) == 0 && j < n) {
+        const bool off = mask[j0 + j] != 0;
+#pragma unroll
+        for (int r = 0; r < RT; ++r) s[(size_t)r * lc + j] = off ? -INFINITY : acc[r][0] * scale;
+      }
+    }
+  } else
   // ---- scores: a lane a key; 32 bytes of the key a step, four steps in flight
   {
     const int steps = d / (2 * UN);         // d is a multiple of 32
@@ -273,17 +351,17 @@ size_t smem_floats(int rt, int d, int lc, int dv, int kv_bf16) {
   return (size_t)rt * d + (size_t)rt * lc + (size_t)nsl * lanes_c * un;
 }
 
-template <typename KV, int RT>
+template <typename KV, int RT, bool GROUPED>
 cudaError_t launch_rt(const float* q, const KV* k, uint64_t k_ld, const KV* v, uint64_t v_ld, const uint32_t* mask,
                       const AttnJob* jobs, const AttnRow* rows, uint64_t n_jobs, int d, int l, int dv, float scale,
                       int splits, int lc, size_t smem, void* out, int out_bf16, float* part_o, float* part_ms, cudaStream_t stream) {
   static bool set = false;
   if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(attention_rows_kernel<KV, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(attention_rows_kernel<KV, RT, GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return e;
     set = true;
   }
-  launch_pdl(attention_rows_kernel<KV, RT>, dim3((unsigned)splits, (unsigned)n_jobs, 1), dim3(THREADS), smem, stream,
+  launch_pdl(attention_rows_kernel<KV, RT, GROUPED>, dim3((unsigned)splits, (unsigned)n_jobs, 1), dim3(THREADS), smem, stream,
              q, k, k_ld, v, v_ld, mask, jobs, rows, d, l, dv, lc, scale, out, out_bf16, part_o, part_ms);
   return cudaGetLastError();
 }
@@ -292,7 +370,13 @@ template <typename KV>
 cudaError_t launch_kv(int rt, const float* q, const KV* k, uint64_t k_ld, const KV* v, uint64_t v_ld, const uint32_t* mask,
                       const AttnJob* jobs, const AttnRow* rows, uint64_t n_jobs, int d, int l, int dv, float scale,
                       int splits, int lc, size_t smem, void* out, int out_bf16, float* part_o, float* part_ms, cudaStream_t stream) {
-#define GO(R) return launch_rt<KV, R>(q, k, k_ld, v, v_ld, mask, jobs, rows, n_jobs, d, l, dv, scale, splits, lc, smem, out, out_bf16, part_o, part_ms, stream)
+  // the grouped scores want whole groups of eight 16-byte units a key (d a multiple of 64 for BF16, of 32 for F32);
+  // B200TT_ATTN_SCORES=lane keeps the lane-a-key form for comparison
+  static int lane_form = -1;
+  if (lane_form < 0) { const char* e = getenv("B200TT_ATTN_SCORES"); lane_form = (e && e[0] == 'l') ? 1 : 0; }
+  const bool grouped = !lane_form && (d / Unit<KV>::N) % 8 == 0;
+#define GO(R) return grouped ? launch_rt<KV, R, true>(q, k, k_ld, v, v_ld, mask, jobs, rows, n_jobs, d, l, dv, scale, splits, lc, smem, out, out_bf16, part_o, part_ms, stream) \
+                             : launch_rt<KV, R, false>(q, k, k_ld, v, v_ld, mask, jobs, rows, n_jobs, d, l, dv, scale, splits, lc, smem, out, out_bf16, part_o, part_ms, stream)
   if (rt <= 1) GO(1);
   if (rt <= 2) GO(2);
   if (rt <= 4) GO(4);

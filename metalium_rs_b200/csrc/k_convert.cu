@@ -75,18 +75,41 @@ cast_f16_kernel(const void* __restrict__ in, void* __restrict__ out, uint64_t n,
   }
 }
 
-// A block of a wider buffer: rows of `cols` elements, `in_ld` apart; the result is dense.
+// A block of a wider buffer: rows of `cols` elements, `in_ld` apart; the result is dense.  A warp a row at a
+// time, four elements a lane where the block's rows are whole 16-byte pieces at 16-byte addresses.
 __global__ void __launch_bounds__(256)
 cast_block_kernel(const void* __restrict__ in, uint64_t in_ld, void* __restrict__ out, uint64_t rows, uint32_t cols,
-                  int to_bf16) {
+                  int to_bf16, int vec4) {
   pdl_enter();
-  const uint64_t n = rows * cols, stride = (uint64_t)gridDim.x * blockDim.x;
-  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-    const uint64_t r = i / cols; const uint32_t c = (uint32_t)(i - r * cols);
-    if (to_bf16)
-      reinterpret_cast<uint16_t*>(out)[i] = f32_to_bf16_bits(reinterpret_cast<const uint32_t*>(in)[r * in_ld + c]);
-    else
-      reinterpret_cast<uint32_t*>(out)[i] = (uint32_t)reinterpret_cast<const uint16_t*>(in)[r * in_ld + c] << 16;
+  const int lane = threadIdx.x & 31;
+  const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+  for (uint64_t r = warp; r < rows; r += nwarps) {
+    if (to_bf16) {
+      const uint32_t* s = reinterpret_cast<const uint32_t*>(in) + r * in_ld;
+      uint16_t* d = reinterpret_cast<uint16_t*>(out) + r * cols;
+      if (vec4) {
+        for (uint32_t c = lane * 4; c < cols; c += 128) {
+          const uint4 v = *reinterpret_cast<const uint4*>(s + c);
+          uint2 o;
+          o.x = (uint32_t)f32_to_bf16_bits(v.x) | ((uint32_t)f32_to_bf16_bits(v.y) << 16);
+          o.y = (uint32_t)f32_to_bf16_bits(v.z) | ((uint32_t)f32_to_bf16_bits(v.w) << 16);
+          *reinterpret_cast<uint2*>(d + c) = o;
+        }
+      } else {
+        for (uint32_t c = lane; c < cols; c += 32) d[c] = f32_to_bf16_bits(s[c]);
+      }
+    } else {
+      const uint16_t* s = reinterpret_cast<const uint16_t*>(in) + r * in_ld;
+      uint32_t* d = reinterpret_cast<uint32_t*>(out) + r * cols;
+      if (vec4) {
+        for (uint32_t c = lane * 4; c < cols; c += 128) {
+          const uint2 v = *reinterpret_cast<const uint2*>(s + c);
+          *reinterpret_cast<uint4*>(d + c) = make_uint4(v.x << 16, v.x & 0xffff0000u, v.y << 16, v.y & 0xffff0000u);
+        }
+      } else {
+        for (uint32_t c = lane; c < cols; c += 32) d[c] = (uint32_t)s[c] << 16;
+      }
+    }
   }
 }
 
@@ -104,9 +127,12 @@ cudaError_t launch_cast_block(const void* in, uint64_t in_ld, void* out, uint64_
                               cudaStream_t stream) {
   if (rows == 0 || cols == 0) return cudaSuccess;
   if (in_ld == cols) return launch_cast(in, out, rows * cols, to_bf16, stream);   // whole rows: the dense cast
-  uint64_t blocks = (rows * cols + 255) / 256;
-  if (blocks > 148ull * 64) blocks = 148ull * 64;
-  launch_pdl(cast_block_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, in, in_ld, out, rows, (uint32_t)cols, to_bf16);
+  const uint64_t in_eb = to_bf16 ? 4 : 2;
+  const int vec4 = cols % 4 == 0 && in_ld % 4 == 0 && (reinterpret_cast<uintptr_t>(in) % (4 * in_eb)) == 0 &&
+                   (reinterpret_cast<uintptr_t>(out) % 16) == 0;
+  uint64_t blocks = (rows + 7) / 8;
+  if (blocks > 148ull * 16) blocks = 148ull * 16;
+  launch_pdl(cast_block_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, in, in_ld, out, rows, (uint32_t)cols, to_bf16, vec4);
   return cudaGetLastError();
 }
 

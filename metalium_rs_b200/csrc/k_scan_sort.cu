@@ -19,6 +19,7 @@
 // bitonic network over (ordered key, index) words, which never tie, and writes keys (and indices) back
 // in the same layout.
 #include <cstdint>
+#include <cstdlib>
 #include <cuda_runtime.h>
 
 #include "kernels.h"
@@ -118,28 +119,32 @@ constexpr int SCAN_STAGES = 4;          // tiles a block keeps in shared memory:
 template <int OP, int MODE>
 __global__ void __launch_bounds__(SCAN_THREADS)
 scan_tiled_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, uint64_t rows, uint64_t cols, uint64_t chunk_rows,
-                  int tile_rows, const uint32_t* __restrict__ carry) {
-  extern __shared__ uint32_t tiles[];                      // SCAN_STAGES tiles of [tile_rows][32]
+                  int tile_rows, int strip, const uint32_t* __restrict__ carry) {
+  extern __shared__ uint32_t tiles[];                      // SCAN_STAGES tiles of [tile_rows][strip]
   pdl_enter();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const uint64_t c0 = (uint64_t)blockIdx.x * 32;
+  const int segs = strip / 32;                             // 32-column segments a row of the strip: a scanning warp each
+  const uint64_t c0 = (uint64_t)blockIdx.x * strip;
   const uint64_t chunk = blockIdx.y, r0 = chunk * chunk_rows;
   const uint64_t r1 = r0 + chunk_rows < rows ? r0 + chunk_rows : rows;
-  const bool live = c0 + lane < cols;
+  const bool scans = warp < segs && c0 + warp * 32 + lane < cols;
   uint32_t acc = scan_identity<OP>();
-  if (MODE == 2 && warp == 0 && live)
-    for (uint64_t k = 0; k < chunk; ++k) acc = scan_step<OP>(acc, carry[k * cols + c0 + lane]);
+  if (MODE == 2 && scans)
+    for (uint64_t k = 0; k < chunk; ++k) acc = scan_step<OP>(acc, carry[k * cols + c0 + warp * 32 + lane]);
   const int warps = SCAN_THREADS / 32;
-  const size_t tile_words = (size_t)tile_rows * 32;
+  const size_t tile_words = (size_t)tile_rows * strip;
   const uint64_t n_tiles = (r1 - r0 + tile_rows - 1) / tile_rows;
   // every thread commits one group a tile slot, empty past the last tile, so "all but the newest
   // SCAN_STAGES - 1 groups are complete" always means "tile t has landed"
   auto fetch = [&](uint64_t t) {
-    if (t < n_tiles && live) {
+    if (t < n_tiles) {
       const uint64_t row0 = r0 + t * tile_rows;
       const int n = (int)(r1 - row0 < (uint64_t)tile_rows ? r1 - row0 : tile_rows);
       uint32_t* buf = tiles + (t % SCAN_STAGES) * tile_words;
-      for (int r = warp; r < n; r += warps) cp_async4(buf + r * 32 + lane, in + (row0 + r) * cols + c0 + lane);
+      for (int i = warp; i < n * segs; i += warps) {         // whole 128-byte segments, a row's side by side
+        const int r = i / segs, sg = i - r * segs;
+        if (c0 + sg * 32 + lane < cols) cp_async4(buf + r * strip + sg * 32 + lane, in + (row0 + r) * cols + c0 + sg * 32 + lane);
+      }
     }
     cp_async_commit();
   };
@@ -148,25 +153,28 @@ scan_tiled_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, u
     uint32_t* cur = tiles + (t % SCAN_STAGES) * tile_words;
     const uint64_t row0 = r0 + t * tile_rows;
     const int n = (int)(r1 - row0 < (uint64_t)tile_rows ? r1 - row0 : tile_rows);
-    // the slot this fetch fills held tile t - 1, which every thread stored before the barrier below of the
-    // iteration before (a thread refills only words it stored itself)
+    // the slot this fetch fills held tile t - 1, which every thread stored at the end of the iteration before
+    // (a thread refills only words it stored itself: the two loops deal the segments to the warps alike)
     fetch(t + SCAN_STAGES - 1);
     cp_async_wait<SCAN_STAGES - 1>();
     __syncthreads();
-    if (warp == 0 && live) {
+    if (scans) {
+      uint32_t* col = cur + warp * 32 + lane;
       int r = 0;
       for (; r + 8 <= n; r += 8) {
         uint32_t x[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) x[u] = cur[(r + u) * 32 + lane];
+        for (int u = 0; u < 8; ++u) x[u] = col[(r + u) * strip];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) { acc = scan_step<OP>(acc, x[u]); cur[(r + u) * 32 + lane] = acc; }
+        for (int u = 0; u < 8; ++u) { acc = scan_step<OP>(acc, x[u]); col[(r + u) * strip] = acc; }
       }
-      for (; r < n; ++r) { acc = scan_step<OP>(acc, cur[r * 32 + lane]); cur[r * 32 + lane] = acc; }
+      for (; r < n; ++r) { acc = scan_step<OP>(acc, col[r * strip]); col[r * strip] = acc; }
     }
     __syncthreads();
-    if (live)
-      for (int r = warp; r < n; r += warps) out[(row0 + r) * cols + c0 + lane] = cur[r * 32 + lane];
+    for (int i = warp; i < n * segs; i += warps) {
+      const int r = i / segs, sg = i - r * segs;
+      if (c0 + sg * 32 + lane < cols) out[(row0 + r) * cols + c0 + sg * 32 + lane] = cur[r * strip + sg * 32 + lane];
+    }
   }
 }
 
@@ -175,13 +183,20 @@ cudaError_t scan_go(const uint32_t* in, uint32_t* out, uint64_t rows, uint64_t c
                     uint32_t* carry, cudaStream_t s) {
   const dim3 block(128);
   const unsigned gx = (unsigned)((cols + 127) / 128);
-  const unsigned strips = (unsigned)((cols + 31) / 32);
+  // A block's strip is 32, 64 or 128 columns (one to four scanning warps): wider strips make longer contiguous
+  // reads a row (HBM pages stay open) as long as enough blocks remain to fill the device.
+  static int forced = -1;
+  if (forced < 0) { const char* e = getenv("B200TT_SCAN_STRIP"); forced = e ? atoi(e) : 0; }
+  int strip = 128;
+  while (strip > 32 && ((cols + strip - 1) / strip) * chunks < 64) strip >>= 1;
+  if (forced == 32 || forced == 64 || forced == 128) strip = forced;
+  const unsigned strips = (unsigned)((cols + strip - 1) / strip);
   // every block resident at once: the tiles are as deep as the shared memory of an SM, shared by the blocks that
   // land on it, allows (few blocks: deep tiles, so that what a block has in flight hides the latency)
   const uint64_t per_sm = ((uint64_t)strips * chunks + 147) / 148;
   int tile_rows = 256;
-  while (tile_rows > 16 && per_sm * SCAN_STAGES * tile_rows * 128 > 200 * 1024) tile_rows >>= 1;
-  const size_t smem = (size_t)SCAN_STAGES * tile_rows * 32 * sizeof(uint32_t);
+  while (tile_rows > 16 && per_sm * SCAN_STAGES * tile_rows * strip * 4 > 200 * 1024) tile_rows >>= 1;
+  const size_t smem = (size_t)SCAN_STAGES * tile_rows * strip * sizeof(uint32_t);
   static size_t set0 = 0, set2 = 0;
   if (smem > 48 * 1024) {
     if (chunks <= 1 && smem > set0) {
@@ -196,12 +211,12 @@ cudaError_t scan_go(const uint32_t* in, uint32_t* out, uint64_t rows, uint64_t c
     }
   }
   if (chunks <= 1) {
-    launch_pdl(scan_tiled_kernel<OP, 0>, dim3(strips, 1), dim3(SCAN_THREADS), smem, s, in, out, rows, cols, rows, tile_rows,
+    launch_pdl(scan_tiled_kernel<OP, 0>, dim3(strips, 1), dim3(SCAN_THREADS), smem, s, in, out, rows, cols, rows, tile_rows, strip,
                (const uint32_t*)nullptr);
   } else {
     launch_pdl(scan_kernel<OP, 1>, dim3(gx, (unsigned)chunks), block, 0, s, in, out, rows, cols, chunk_rows, carry);
     launch_pdl(scan_tiled_kernel<OP, 2>, dim3(strips, (unsigned)chunks), dim3(SCAN_THREADS), smem, s, in, out, rows, cols, chunk_rows,
-               tile_rows, (const uint32_t*)carry);
+               tile_rows, strip, (const uint32_t*)carry);
   }
   return cudaGetLastError();
 }
@@ -237,10 +252,11 @@ sort_planes_kernel(const uint32_t* __restrict__ in, uint64_t rows, uint64_t cols
     wires[c * N + e] = ((unsigned long long)u << 32) | e;
   }
   __syncthreads();
+  const uint32_t half_lg = 30 - __clz(N);                  // log2(N / 2)
   for (uint32_t k = 2; k <= N; k <<= 1) {
     for (uint32_t s = k >> 1; s > 0; s >>= 1) {
       for (uint32_t t = tid; t < 4 * N; t += SORT_THREADS) {     // 8 problems x N/2 exchanges
-        const uint32_t prob = t / (N / 2), i = t - prob * (N / 2);
+        const uint32_t prob = t >> half_lg, i = t & (N / 2 - 1);     // N is a power of two
         const uint32_t lo = ((i & ~(s - 1)) << 1) | (i & (s - 1)), hi = lo | s;
         unsigned long long* w = wires + prob * N;
         const unsigned long long a = w[lo], b = w[hi];
