@@ -99,81 +99,176 @@ scan_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, uint64_
   if (MODE == 1) carry[chunk * cols + c] = acc;
 }
 
+// A thread a column with the loads far ahead of the chain: two register buffers of SCAN_DEEP rows, the next one
+// loading while this one is scanned and stored.  Few threads exist (one a column), so each can afford the registers.
+constexpr int SCAN_DEEP = 48;
+
+template <int OP, int MODE>
+__global__ void __launch_bounds__(32)
+scan_deep_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, uint64_t rows, uint64_t cols, uint64_t chunk_rows,
+                 const uint32_t* __restrict__ carry) {
+  pdl_enter();
+  const uint64_t c = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  const uint64_t chunk = blockIdx.y, r0 = chunk * chunk_rows;
+  const uint64_t r1 = r0 + chunk_rows < rows ? r0 + chunk_rows : rows;
+  uint32_t acc = scan_identity<OP>();
+  if (MODE == 2)
+    for (uint64_t k = 0; k < chunk; ++k) acc = scan_step<OP>(acc, carry[k * cols + c]);
+  const uint32_t* p = in + r0 * cols + c;
+  uint32_t* q = out + r0 * cols + c;
+  const uint64_t n = r1 - r0, full = n / SCAN_DEEP;
+  uint32_t a[SCAN_DEEP], b[SCAN_DEEP];
+  if (full) {
+#pragma unroll
+    for (int u = 0; u < SCAN_DEEP; ++u) a[u] = __ldg(p + (uint64_t)u * cols);
+  }
+  for (uint64_t g = 0; g < full; ++g) {
+    const bool more = g + 1 < full;
+    if (more) {
+#pragma unroll
+      for (int u = 0; u < SCAN_DEEP; ++u) b[u] = __ldg(p + (uint64_t)(SCAN_DEEP + u) * cols);
+    }
+#pragma unroll
+    for (int u = 0; u < SCAN_DEEP; ++u) { acc = scan_step<OP>(acc, a[u]); q[(uint64_t)u * cols] = acc; }
+    if (more) {
+#pragma unroll
+      for (int u = 0; u < SCAN_DEEP; ++u) a[u] = b[u];
+    }
+    p += (uint64_t)SCAN_DEEP * cols; q += (uint64_t)SCAN_DEEP * cols;
+  }
+  for (uint64_t r = full * SCAN_DEEP; r < n; ++r) {
+    acc = scan_step<OP>(acc, __ldg(p));
+    *q = acc;
+    p += cols; q += cols;
+  }
+}
+
 // The scanning form for whole launches: a block owns a strip of 32 columns (one 128-byte line a row) and walks
-// its rows in tiles of `tile_rows` rows.  All of its warps bring the next tile into shared memory with
-// cp.async while warp 0 scans the current one in place (a lane a column, the serial chain now an add or a
-// select a row with its operand already on chip), then all warps store the scanned tile in whole lines.  The
-// loads in flight no longer depend on the chain, which is what a thread-a-column loop over global memory
-// cannot give (a [8192, 8192] row-order sum: 1.3 TB/s of bytes moved that way, 3.1 TB/s with two tiles a block).
-constexpr int SCAN_THREADS = 128;
+// its rows in tiles kept in a ring of four shared-memory slots.  Its warps are specialised: warp 0 scans (a lane
+// a column; the serial chain is an add or a select a row with its operand already on chip) and three mover
+// warps, while tile t is scanned, store tile t - 1 and bring tile t + 2 in with cp.async -- sixteen bytes a
+// lane, so one instruction moves four rows of the strip, the addresses advanced by additions only.  One barrier
+// a tile.  What the forms before this one measured on a [8192, 8192] row-order sum: a thread a column over
+// global memory, 1.3 TB/s of bytes moved (only what a thread has in flight is ahead of the chain); all warps
+// fetching, scanning and storing in turn, four bytes a lane, 3.1 TB/s (instruction latencies of the one warp
+// that does everything).
+constexpr int SCAN_SLOTS = 4;
+constexpr int SCAN_MOVERS = 3;           // mover warps a block
+constexpr int SCAN_THREADS = 32 * (1 + SCAN_MOVERS);
 
 __device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-constexpr int SCAN_STAGES = 4;          // tiles a block keeps in shared memory: three in flight behind the one being scanned
-
-template <int OP, int MODE>
+// VEC: the strip's rows are whole 16-byte pieces at 16-byte addresses (cols % 4 == 0, aligned bases).
+template <int OP, int MODE, bool VEC>
 __global__ void __launch_bounds__(SCAN_THREADS)
 scan_tiled_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, uint64_t rows, uint64_t cols, uint64_t chunk_rows,
-                  int tile_rows, int strip, const uint32_t* __restrict__ carry) {
-  extern __shared__ uint32_t tiles[];                      // SCAN_STAGES tiles of [tile_rows][strip]
+                  int tile_rows, const uint32_t* __restrict__ carry) {
+  extern __shared__ __align__(16) uint32_t tiles[];        // SCAN_SLOTS tiles of [tile_rows][32]
   pdl_enter();
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int segs = strip / 32;                             // 32-column segments a row of the strip: a scanning warp each
-  const uint64_t c0 = (uint64_t)blockIdx.x * strip;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint64_t c0 = (uint64_t)blockIdx.x * 32;
   const uint64_t chunk = blockIdx.y, r0 = chunk * chunk_rows;
   const uint64_t r1 = r0 + chunk_rows < rows ? r0 + chunk_rows : rows;
-  const bool scans = warp < segs && c0 + warp * 32 + lane < cols;
-  uint32_t acc = scan_identity<OP>();
-  if (MODE == 2 && scans)
-    for (uint64_t k = 0; k < chunk; ++k) acc = scan_step<OP>(acc, carry[k * cols + c0 + warp * 32 + lane]);
-  const int warps = SCAN_THREADS / 32;
-  const size_t tile_words = (size_t)tile_rows * strip;
-  const uint64_t n_tiles = (r1 - r0 + tile_rows - 1) / tile_rows;
-  // every thread commits one group a tile slot, empty past the last tile, so "all but the newest
-  // SCAN_STAGES - 1 groups are complete" always means "tile t has landed"
-  auto fetch = [&](uint64_t t) {
-    if (t < n_tiles) {
-      const uint64_t row0 = r0 + t * tile_rows;
-      const int n = (int)(r1 - row0 < (uint64_t)tile_rows ? r1 - row0 : tile_rows);
-      uint32_t* buf = tiles + (t % SCAN_STAGES) * tile_words;
-      for (int i = warp; i < n * segs; i += warps) {         // whole 128-byte segments, a row's side by side
-        const int r = i / segs, sg = i - r * segs;
-        if (c0 + sg * 32 + lane < cols) cp_async4(buf + r * strip + sg * 32 + lane, in + (row0 + r) * cols + c0 + sg * 32 + lane);
-      }
-    }
-    cp_async_commit();
+  const int tile_words = tile_rows * 32;
+  const int n_tiles = (int)((r1 - r0 + tile_rows - 1) / tile_rows);
+  auto rows_of = [&](int t) {
+    const uint64_t row0 = r0 + (uint64_t)t * tile_rows;
+    return (int)(r1 - row0 < (uint64_t)tile_rows ? r1 - row0 : tile_rows);
   };
-  for (int t = 0; t < SCAN_STAGES - 1; ++t) fetch(t);
-  for (uint64_t t = 0; t < n_tiles; ++t) {
-    uint32_t* cur = tiles + (t % SCAN_STAGES) * tile_words;
-    const uint64_t row0 = r0 + t * tile_rows;
-    const int n = (int)(r1 - row0 < (uint64_t)tile_rows ? r1 - row0 : tile_rows);
-    // the slot this fetch fills held tile t - 1, which every thread stored at the end of the iteration before
-    // (a thread refills only words it stored itself: the two loops deal the segments to the warps alike)
-    fetch(t + SCAN_STAGES - 1);
-    cp_async_wait<SCAN_STAGES - 1>();
-    __syncthreads();
-    if (scans) {
-      uint32_t* col = cur + warp * 32 + lane;
-      int r = 0;
-      for (; r + 8 <= n; r += 8) {
-        uint32_t x[8];
+  if (warp == 0) {
+    // ---- the scanning warp: tile t between the barriers of iteration t
+    const bool live = c0 + lane < cols;
+    uint32_t acc = scan_identity<OP>();
+    if (MODE == 2 && live)
+      for (uint64_t k = 0; k < chunk; ++k) acc = scan_step<OP>(acc, carry[k * cols + c0 + lane]);
+    __syncthreads();                                       // tile 0 has landed
+    for (int t = 0; t <= n_tiles; ++t) {
+      if (t < n_tiles && live) {
+        uint32_t* col = tiles + (t & (SCAN_SLOTS - 1)) * tile_words + lane;
+        const int n = rows_of(t);
+        int r = 0;
+        if (n >= 8) {                                      // eight rows read ahead of the eight being folded
+          uint32_t x[8], y[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) x[u] = col[(r + u) * strip];
+          for (int u = 0; u < 8; ++u) x[u] = col[u * 32];
+          for (; r + 16 <= n; r += 8) {
 #pragma unroll
-        for (int u = 0; u < 8; ++u) { acc = scan_step<OP>(acc, x[u]); col[(r + u) * strip] = acc; }
+            for (int u = 0; u < 8; ++u) y[u] = col[(8 + u) * 32];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) { acc = scan_step<OP>(acc, x[u]); col[u * 32] = acc; }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) x[u] = y[u];
+            col += 8 * 32;
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) { acc = scan_step<OP>(acc, x[u]); col[u * 32] = acc; }
+          col += 8 * 32;
+          r += 8;
+        }
+        for (; r < n; ++r) { acc = scan_step<OP>(acc, col[0]); col[0] = acc; col += 32; }
       }
-      for (; r < n; ++r) { acc = scan_step<OP>(acc, col[r * strip]); col[r * strip] = acc; }
+      __syncthreads();
     }
-    __syncthreads();
-    for (int i = warp; i < n * segs; i += warps) {
-      const int r = i / segs, sg = i - r * segs;
-      if (c0 + sg * 32 + lane < cols) out[(row0 + r) * cols + c0 + sg * 32 + lane] = cur[r * strip + sg * 32 + lane];
+  } else {
+    // ---- a mover warp: in iteration t it stores tile t - 1, then fetches tile t + 2 into the slot tile t - 2 left
+    // (stored in iteration t - 1, before that iteration's barrier), and waits until tile t + 1 has landed
+    const int mw = warp - 1;
+    // VEC: a lane moves piece `pc` (four columns) of row 4 i + `sub`; else a lane a column of row i
+    const int sub = lane >> 3, pc = (lane & 7) * 4;
+    const bool has = VEC ? c0 + pc < cols : c0 + lane < cols;
+    auto fetch = [&](int t) {
+      if (t < n_tiles && has) {
+        const uint64_t row0 = r0 + (uint64_t)t * tile_rows;
+        const int n = rows_of(t);
+        uint32_t* buf = tiles + (t & (SCAN_SLOTS - 1)) * tile_words;
+        if (VEC) {
+          const uint32_t* src = in + (row0 + 4 * mw + sub) * cols + c0 + pc;
+          uint32_t* dst = buf + (4 * mw + sub) * 32 + pc;
+          for (int r = 4 * mw + sub; r < n; r += 4 * SCAN_MOVERS) {
+            cp_async16(dst, src);
+            src += 4 * SCAN_MOVERS * cols; dst += 4 * SCAN_MOVERS * 32;
+          }
+        } else {
+          const uint32_t* src = in + (row0 + mw) * cols + c0 + lane;
+          uint32_t* dst = buf + mw * 32 + lane;
+          for (int r = mw; r < n; r += SCAN_MOVERS) { cp_async4(dst, src); src += SCAN_MOVERS * cols; dst += SCAN_MOVERS * 32; }
+        }
+      }
+      cp_async_commit();                                   // a group a tile slot, empty past the last tile
+    };
+    fetch(0); fetch(1);
+    cp_async_wait<1>();
+    __syncthreads();                                       // tile 0 has landed
+    for (int t = 0; t <= n_tiles; ++t) {
+      if (t >= 1 && has) {
+        const uint64_t row0 = r0 + (uint64_t)(t - 1) * tile_rows;
+        const int n = rows_of(t - 1);
+        const uint32_t* buf = tiles + ((t - 1) & (SCAN_SLOTS - 1)) * tile_words;
+        if (VEC) {
+          uint32_t* dst = out + (row0 + 4 * mw + sub) * cols + c0 + pc;
+          const uint32_t* src = buf + (4 * mw + sub) * 32 + pc;
+          for (int r = 4 * mw + sub; r < n; r += 4 * SCAN_MOVERS) {
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+            dst += 4 * SCAN_MOVERS * cols; src += 4 * SCAN_MOVERS * 32;
+          }
+        } else {
+          uint32_t* dst = out + (row0 + mw) * cols + c0 + lane;
+          const uint32_t* src = buf + mw * 32 + lane;
+          for (int r = mw; r < n; r += SCAN_MOVERS) { *dst = *src; dst += SCAN_MOVERS * cols; src += SCAN_MOVERS * 32; }
+        }
+      }
+      fetch(t + 2);
+      cp_async_wait<1>();                                  // all but the newest group: tile t + 1 is in
+      __syncthreads();
     }
   }
 }
@@ -183,40 +278,45 @@ cudaError_t scan_go(const uint32_t* in, uint32_t* out, uint64_t rows, uint64_t c
                     uint32_t* carry, cudaStream_t s) {
   const dim3 block(128);
   const unsigned gx = (unsigned)((cols + 127) / 128);
-  // A block's strip is 32, 64 or 128 columns (one to four scanning warps): wider strips make longer contiguous
-  // reads a row (HBM pages stay open) as long as enough blocks remain to fill the device.
-  static int forced = -1;
-  if (forced < 0) { const char* e = getenv("B200TT_SCAN_STRIP"); forced = e ? atoi(e) : 0; }
-  int strip = 128;
-  while (strip > 32 && ((cols + strip - 1) / strip) * chunks < 64) strip >>= 1;
-  if (forced == 32 || forced == 64 || forced == 128) strip = forced;
-  const unsigned strips = (unsigned)((cols + strip - 1) / strip);
+  const unsigned strips = (unsigned)((cols + 31) / 32);
   // every block resident at once: the tiles are as deep as the shared memory of an SM, shared by the blocks that
   // land on it, allows (few blocks: deep tiles, so that what a block has in flight hides the latency)
   const uint64_t per_sm = ((uint64_t)strips * chunks + 147) / 148;
   int tile_rows = 256;
-  while (tile_rows > 16 && per_sm * SCAN_STAGES * tile_rows * strip * 4 > 200 * 1024) tile_rows >>= 1;
-  const size_t smem = (size_t)SCAN_STAGES * tile_rows * strip * sizeof(uint32_t);
-  static size_t set0 = 0, set2 = 0;
+  while (tile_rows > 16 && per_sm * SCAN_SLOTS * tile_rows * 128 > 200 * 1024) tile_rows >>= 1;
+  const size_t smem = (size_t)SCAN_SLOTS * tile_rows * 128;
+  const bool vec = cols % 4 == 0 && reinterpret_cast<uintptr_t>(in) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
   if (smem > 48 * 1024) {
-    if (chunks <= 1 && smem > set0) {
-      cudaError_t e = cudaFuncSetAttribute(scan_tiled_kernel<OP, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static size_t set[4] = {0, 0, 0, 0};
+    const int which = (chunks > 1 ? 2 : 0) + (vec ? 1 : 0);
+    if (smem > set[which]) {
+      cudaError_t e = chunks > 1 ? (vec ? cudaFuncSetAttribute(scan_tiled_kernel<OP, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                                        : cudaFuncSetAttribute(scan_tiled_kernel<OP, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem))
+                                 : (vec ? cudaFuncSetAttribute(scan_tiled_kernel<OP, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                                        : cudaFuncSetAttribute(scan_tiled_kernel<OP, 0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       if (e != cudaSuccess) return e;
-      set0 = smem;
-    }
-    if (chunks > 1 && smem > set2) {
-      cudaError_t e = cudaFuncSetAttribute(scan_tiled_kernel<OP, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return e;
-      set2 = smem;
+      set[which] = smem;
     }
   }
+  static int deep = -1;
+  if (deep < 0) { const char* e = getenv("B200TT_SCAN"); deep = (e && e[0] == 'd') ? 1 : 0; }
+  if (deep) {
+    const unsigned gd = (unsigned)((cols + 31) / 32);
+    if (chunks <= 1) {
+      launch_pdl(scan_deep_kernel<OP, 0>, dim3(gd, 1), dim3(32), 0, s, in, out, rows, cols, rows, (const uint32_t*)nullptr);
+    } else {
+      launch_pdl(scan_kernel<OP, 1>, dim3(gx, (unsigned)chunks), block, 0, s, in, out, rows, cols, chunk_rows, carry);
+      launch_pdl(scan_deep_kernel<OP, 2>, dim3(gd, (unsigned)chunks), dim3(32), 0, s, in, out, rows, cols, chunk_rows, (const uint32_t*)carry);
+    }
+    return cudaGetLastError();
+  }
   if (chunks <= 1) {
-    launch_pdl(scan_tiled_kernel<OP, 0>, dim3(strips, 1), dim3(SCAN_THREADS), smem, s, in, out, rows, cols, rows, tile_rows, strip,
-               (const uint32_t*)nullptr);
+    if (vec) launch_pdl(scan_tiled_kernel<OP, 0, true>, dim3(strips, 1), dim3(SCAN_THREADS), smem, s, in, out, rows, cols, rows, tile_rows, (const uint32_t*)nullptr);
+    else launch_pdl(scan_tiled_kernel<OP, 0, false>, dim3(strips, 1), dim3(SCAN_THREADS), smem, s, in, out, rows, cols, rows, tile_rows, (const uint32_t*)nullptr);
   } else {
     launch_pdl(scan_kernel<OP, 1>, dim3(gx, (unsigned)chunks), block, 0, s, in, out, rows, cols, chunk_rows, carry);
-    launch_pdl(scan_tiled_kernel<OP, 2>, dim3(strips, (unsigned)chunks), dim3(SCAN_THREADS), smem, s, in, out, rows, cols, chunk_rows,
-               tile_rows, strip, (const uint32_t*)carry);
+    if (vec) launch_pdl(scan_tiled_kernel<OP, 2, true>, dim3(strips, (unsigned)chunks), dim3(SCAN_THREADS), smem, s, in, out, rows, cols, chunk_rows, tile_rows, (const uint32_t*)carry);
+    else launch_pdl(scan_tiled_kernel<OP, 2, false>, dim3(strips, (unsigned)chunks), dim3(SCAN_THREADS), smem, s, in, out, rows, cols, chunk_rows, tile_rows, (const uint32_t*)carry);
   }
   return cudaGetLastError();
 }
