@@ -19,7 +19,6 @@
 // bitonic network over (ordered key, index) words, which never tie, and writes keys (and indices) back
 // in the same layout.
 #include <cstdint>
-#include <cstdlib>
 #include <cuda_runtime.h>
 
 #include "kernels.h"
@@ -99,51 +98,6 @@ scan_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, uint64_
   if (MODE == 1) carry[chunk * cols + c] = acc;
 }
 
-// A thread a column with the loads far ahead of the chain: two register buffers of SCAN_DEEP rows, the next one
-// loading while this one is scanned and stored.  Few threads exist (one a column), so each can afford the registers.
-constexpr int SCAN_DEEP = 48;
-
-template <int OP, int MODE>
-__global__ void __launch_bounds__(32)
-scan_deep_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, uint64_t rows, uint64_t cols, uint64_t chunk_rows,
-                 const uint32_t* __restrict__ carry) {
-  pdl_enter();
-  const uint64_t c = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
-  const uint64_t chunk = blockIdx.y, r0 = chunk * chunk_rows;
-  const uint64_t r1 = r0 + chunk_rows < rows ? r0 + chunk_rows : rows;
-  uint32_t acc = scan_identity<OP>();
-  if (MODE == 2)
-    for (uint64_t k = 0; k < chunk; ++k) acc = scan_step<OP>(acc, carry[k * cols + c]);
-  const uint32_t* p = in + r0 * cols + c;
-  uint32_t* q = out + r0 * cols + c;
-  const uint64_t n = r1 - r0, full = n / SCAN_DEEP;
-  uint32_t a[SCAN_DEEP], b[SCAN_DEEP];
-  if (full) {
-#pragma unroll
-    for (int u = 0; u < SCAN_DEEP; ++u) a[u] = __ldg(p + (uint64_t)u * cols);
-  }
-  for (uint64_t g = 0; g < full; ++g) {
-    const bool more = g + 1 < full;
-    if (more) {
-#pragma unroll
-      for (int u = 0; u < SCAN_DEEP; ++u) b[u] = __ldg(p + (uint64_t)(SCAN_DEEP + u) * cols);
-    }
-#pragma unroll
-    for (int u = 0; u < SCAN_DEEP; ++u) { acc = scan_step<OP>(acc, a[u]); q[(uint64_t)u * cols] = acc; }
-    if (more) {
-#pragma unroll
-      for (int u = 0; u < SCAN_DEEP; ++u) a[u] = b[u];
-    }
-    p += (uint64_t)SCAN_DEEP * cols; q += (uint64_t)SCAN_DEEP * cols;
-  }
-  for (uint64_t r = full * SCAN_DEEP; r < n; ++r) {
-    acc = scan_step<OP>(acc, __ldg(p));
-    *q = acc;
-    p += cols; q += cols;
-  }
-}
-
 // The scanning form for whole launches: a block owns a strip of 32 columns (one 128-byte line a row) and walks
 // its rows in tiles kept in a ring of four shared-memory slots.  Its warps are specialised: warp 0 scans (a lane
 // a column; the serial chain is an add or a select a row with its operand already on chip) and three mover
@@ -152,7 +106,7 @@ scan_deep_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, ui
 // a tile.  What the forms before this one measured on a [8192, 8192] row-order sum: a thread a column over
 // global memory, 1.3 TB/s of bytes moved (only what a thread has in flight is ahead of the chain); all warps
 // fetching, scanning and storing in turn, four bytes a lane, 3.1 TB/s (instruction latencies of the one warp
-// that does everything).
+// that does everything); this form, 4.9 TB/s.
 constexpr int SCAN_SLOTS = 4;
 constexpr int SCAN_MOVERS = 3;           // mover warps a block
 constexpr int SCAN_THREADS = 32 * (1 + SCAN_MOVERS);
@@ -298,18 +252,6 @@ cudaError_t scan_go(const uint32_t* in, uint32_t* out, uint64_t rows, uint64_t c
       set[which] = smem;
     }
   }
-  static int deep = -1;
-  if (deep < 0) { const char* e = getenv("B200TT_SCAN"); deep = (e && e[0] == 'd') ? 1 : 0; }
-  if (deep) {
-    const unsigned gd = (unsigned)((cols + 31) / 32);
-    if (chunks <= 1) {
-      launch_pdl(scan_deep_kernel<OP, 0>, dim3(gd, 1), dim3(32), 0, s, in, out, rows, cols, rows, (const uint32_t*)nullptr);
-    } else {
-      launch_pdl(scan_kernel<OP, 1>, dim3(gx, (unsigned)chunks), block, 0, s, in, out, rows, cols, chunk_rows, carry);
-      launch_pdl(scan_deep_kernel<OP, 2>, dim3(gd, (unsigned)chunks), dim3(32), 0, s, in, out, rows, cols, chunk_rows, (const uint32_t*)carry);
-    }
-    return cudaGetLastError();
-  }
   if (chunks <= 1) {
     if (vec) launch_pdl(scan_tiled_kernel<OP, 0, true>, dim3(strips, 1), dim3(SCAN_THREADS), smem, s, in, out, rows, cols, rows, tile_rows, (const uint32_t*)nullptr);
     else launch_pdl(scan_tiled_kernel<OP, 0, false>, dim3(strips, 1), dim3(SCAN_THREADS), smem, s, in, out, rows, cols, rows, tile_rows, (const uint32_t*)nullptr);
@@ -380,10 +322,10 @@ sort_planes_kernel(const uint32_t* __restrict__ in, uint64_t rows, uint64_t cols
 
 uint64_t scan_chunks(int op, uint64_t rows, uint64_t cols) {
   if (op == S_SUM || op == S_PROD) return 1;                 // a left fold in row order: the rows stay together
-  const uint64_t col_blocks = (cols + 127) / 128;
-  if (col_blocks >= 148 * 2 || rows < 512) return 1;
-  uint64_t chunks = (148 * 4 + col_blocks - 1) / col_blocks;
-  if (chunks > rows / 64) chunks = rows / 64;
+  const uint64_t strips = (cols + 31) / 32;                  // blocks of the scanning kernel a chunk
+  if (strips >= 148 || rows < 512) return 1;
+  uint64_t chunks = (148 * 2 + strips - 1) / strips;
+  if (chunks > rows / 256) chunks = rows / 256;
   if (chunks > 256) chunks = 256;
   return chunks < 2 ? 1 : chunks;
 }
