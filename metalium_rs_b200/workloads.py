@@ -212,21 +212,36 @@ class LlamaPrefill:
         self.fused_items = eng.attention_block_array(fused_items)
         self.last_rows = [(0, b * t + t - 1) for b in range(batch)]
 
-    def forward(self, ids_buf: int, all_positions: bool = False, cache: "LlamaDecode" = None):
+    def forward(self, ids_buf: int, all_positions: bool = False, cache: "LlamaDecode" = None, start: int = 0):
         """ids [1, batch*seq] I32 resident.  Returns (logits buffer [batch or batch*seq, vocab] F32,
         argmax buffer I32); the caller frees both.  With `cache`, every layer's rotated keys and its values are
         also written into that generation's cache at positions 0 .. seq-1 of each sequence, as the reference's
         first chunk write does (crates/tt-models/src/kv_cache.rs:231-241, start 0): the bits a token-by-token
-        generation would have left there, so `cache.continue_from(argmax, seq)` goes on from the prompt."""
+        generation would have left there, so `cache.continue_from(argmax, seq)` goes on from the prompt.
+        With `start` > 0 the tokens are a later chunk of the prompt (kv_cache.rs:231-241, 249-296): they take
+        positions start .. start + seq - 1, their keys and values go to those rows of the cache, and every token
+        attends to the cache's positions up to its own -- the chunks before it and its own chunk's earlier tokens
+        -- through the fused attention kernel reading keys and values where the cache holds them (whole 128-row
+        tiles: start and seq multiples of 128)."""
         e, c, K = self.eng, self.cfg, kinds
         n = self.batch * self.seq
+        chunked = start > 0
+        if chunked:
+            if cache is None or not self.fused or start % 128:
+                raise ValueError("a later chunk needs a cache, the fused attention kernel and a start in whole 128-position tiles")
         if cache is not None:
-            assert cache.batch == self.batch and cache.max_len >= self.seq and cache.cfg is self.cfg
-            key = (cache.max_len,)
+            assert cache.batch == self.batch and cache.max_len >= start + self.seq and cache.cfg is self.cfg
+            key = (cache.max_len, start)
             if getattr(self, "_cache_rows_key", None) != key:
-                rows = (np.arange(self.batch)[:, None] * cache.max_len + np.arange(self.seq)[None, :]).astype(np.int32)
+                rows = (np.arange(self.batch)[:, None] * cache.max_len + start + np.arange(self.seq)[None, :]).astype(np.int32)
+                if getattr(self, "_cache_rows", None):
+                    e.free(self._cache_rows)
                 self._cache_rows = e.upload_bits(rows.reshape(1, -1).view(np.uint32), 1, n, I32)
                 self._cache_rows_key = key
+                group, hd_ = self.cfg.heads // self.cfg.kv_heads, self.cfg.head_dim
+                self._cache_items = e.attention_block_array(
+                    [((b * self.seq, h * hd_), (b * cache.max_len, (h // group) * hd_), (b * cache.max_len, (h // group) * hd_),
+                      (b * self.seq, h * hd_)) for b in range(self.batch) for h in range(self.cfg.heads)])
         t, hd = self.seq, c.head_dim
         el = lambda kind, a, b=None, bf=False: e.eltwise_op_as(EltwiseOp(kind, 0.0, 0.0), a, b, None, bf)[0]
         emb, _ = e.select_rows(self.w["embed"], ids_buf)                     # ops.rs:4958 embedding
@@ -238,12 +253,17 @@ class LlamaPrefill:
             qkv, _ = e.matmul_dram_bf16(n1, False, self.w[f"l{l}.qkv"], False)
             e.free(n1)
             # RoPE on the query and key heads together: they share the head width and the tables (rope.rs:129)
-            qk, _ = e.rope_blocks((qkv, (0, 0), (n, qk_cols)), (self.cos, (0, 0), (t, hd)),
-                                  (self.sin, (0, 0), (t, hd)), hd, True)
+            cos_b = (cache.cos, (start, 0), (t, hd)) if chunked else (self.cos, (0, 0), (t, hd))
+            sin_b = (cache.sin, (start, 0), (t, hd)) if chunked else (self.sin, (0, 0), (t, hd))
+            qk, _ = e.rope_blocks((qkv, (0, 0), (n, qk_cols)), cos_b, sin_b, hd, True)
             if cache is not None:   # the chunk's rows of the cache: keys after RoPE, values as projected
                 e.scatter_rows_into(cache.kc[l], self._cache_rows, (qk, (0, self.q_cols), (n, self.kv_cols)))
                 e.scatter_rows_into(cache.vc[l], self._cache_rows, (qkv, (0, qk_cols), (n, self.kv_cols)))
-            if self.fused:   # scores, mask, softmax, P V and the merge of heads as one kernel
+            if chunked:      # keys and values where the cache holds them: positions 0 .. start + t - 1, causal at the end
+                om, _ = e.attention_blocks(qk, cache.kc[l], cache.vc[l], self._cache_items, (t, hd, start + t, hd),
+                                           1.0 / float(np.sqrt(hd)), True, (n, self.q_cols))
+                e.free(qk); e.free(qkv)
+            elif self.fused:   # scores, mask, softmax, P V and the merge of heads as one kernel
                 om, _ = e.attention_blocks(qk, qk, qkv, self.fused_items, (t, hd, t, hd), 1.0 / float(np.sqrt(hd)), True,
                                            (n, self.q_cols))
                 e.free(qk); e.free(qkv)

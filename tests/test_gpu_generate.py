@@ -189,3 +189,37 @@ def test_a_prompt_prefilled_into_the_cache_continues_as_the_stepped_one(eng, t):
             eng.free(i)
     assert worst <= 2e-2, worst
     assert np.array_equal(filled.generated(t, more).shape, (more, batch))
+
+
+def test_a_prompt_prefilled_in_chunks_is_the_prompt_prefilled_at_once(eng):
+    # crates/tt-models/src/kv_cache.rs:231-296: a later chunk writes its rows and attends to the cache up to each
+    # token's own position; the cache and the last logits are those of one prefill of the whole prompt (BF16 rounding:
+    # the chunk's projections run on other tile shapes than the whole prompt's)
+    cfg = small_llama()
+    batch, chunk, max_len = 2, 128, 384
+    w = W.llama_weights(cfg, seed=11)
+    ids = orc.integers(0x6E3, 9, (batch, 2 * chunk), cfg.vocab)
+    whole = W.LlamaPrefill(eng, cfg, w, batch, 2 * chunk)
+    part = W.LlamaPrefill(eng, cfg, w, batch, chunk)
+    a, b = (W.LlamaDecode(eng, cfg, whole.w, batch, max_len=max_len) for _ in range(2))
+    iw = _i32(eng, ids.reshape(1, -1), 1, batch * 2 * chunk)
+    lw, aw = whole.forward(iw, cache=a)
+    outs = []
+    for k in range(2):
+        ic = _i32(eng, ids[:, k * chunk:(k + 1) * chunk].reshape(1, -1), 1, batch * chunk)
+        outs.append(part.forward(ic, cache=b, start=k * chunk))
+        eng.free(ic)
+    lc, ac = outs[-1]
+    assert np.max(np.abs(eng.download(lc) - eng.download(lw))) <= 2e-2
+    for l in range(cfg.layers):
+        for mine, theirs in ((b.kc[l], a.kc[l]), (b.vc[l], a.vc[l])):
+            x = orc.from_bf16(eng.download_bf16(mine)).reshape(batch, max_len, -1)
+            y = orc.from_bf16(eng.download_bf16(theirs)).reshape(batch, max_len, -1)
+            assert not x[:, 2 * chunk:].any() and np.max(np.abs(x - y)) <= 2.0 ** -6 * np.abs(y).max(), l
+    with pytest.raises(ValueError):
+        part.forward(iw, cache=b, start=64)
+    b.continue_from(ac, 2 * chunk)
+    lg, am = b.step()                                  # the generation goes on from the chunked prompt
+    assert np.isfinite(eng.download(lg)).all()
+    for i in (lw, aw, lg, am, iw) + tuple(x for o in outs for x in o):
+        eng.free(i)
