@@ -275,13 +275,22 @@ __device__ __forceinline__ uint32_t unordered(uint32_t u, int is_i32, int descen
   return is_i32 ? (u ^ 0x80000000u) : ((u & 0x80000000u) ? (u & 0x7fffffffu) : ~u);
 }
 
-// grid (column blocks, 4): block (cb, j) sorts problems 32 cb + 8 j + c, c = 0..7, over N = `rows` wires.
+// A wire's place in shared memory: one word of padding every eight, so that a thread reading eight consecutive
+// wires (72 bytes from its neighbour's) meets no bank conflict.
+__device__ __forceinline__ uint32_t wire_at(uint32_t i) { return i + (i >> 3); }
+__device__ __forceinline__ void exchange(unsigned long long& a, unsigned long long& b, bool up) {
+  if ((a > b) == up) { const unsigned long long t = a; a = b; b = t; }
+}
+
+// grid (column blocks, 4): block (cb, j) sorts problems 32 cb + 8 j + c, c = 0..7, over N = `rows` wires.  The
+// network's stages whose partners are less than eight wires apart (the first six stages, and the last three of
+// every later merge) run in registers, eight wires a thread; the others are one pass over shared memory each.
 __global__ void __launch_bounds__(SORT_THREADS)
 sort_planes_kernel(const uint32_t* __restrict__ in, uint64_t rows, uint64_t cols, uint32_t n, int is_i32, int descending,
                    uint32_t* __restrict__ keys, uint32_t* __restrict__ indices) {
-  extern __shared__ unsigned long long wires[];          // [8][N]
+  extern __shared__ unsigned long long wires[];          // [8][N + N / 8]
   pdl_enter();
-  const uint32_t N = (uint32_t)rows, cb = blockIdx.x, j = blockIdx.y, tid = threadIdx.x;
+  const uint32_t N = (uint32_t)rows, NP = N + N / 8, cb = blockIdx.x, j = blockIdx.y, tid = threadIdx.x;
   const uint32_t word = tid & 31;                         // a column of the tile row: (face % 2, c, odd)
   const uint32_t fl = word >> 4, c = (word >> 1) & 7, odd = word & 1;
   // tile rows this block owns: row = 32 tr + 16 fh + 4 g + j
@@ -291,28 +300,60 @@ sort_planes_kernel(const uint32_t* __restrict__ in, uint64_t rows, uint64_t cols
     const uint32_t e = 32 * tr + 8 * (2 * fh + fl) + 2 * g + odd;
     const uint32_t x = in[row * cols + 32ull * cb + word];
     const uint32_t u = e < n ? ordered(x, is_i32, descending) : 0xffffffffu;
-    wires[c * N + e] = ((unsigned long long)u << 32) | e;
+    wires[c * NP + wire_at(e)] = ((unsigned long long)u << 32) | e;
   }
   __syncthreads();
   const uint32_t half_lg = 30 - __clz(N);                  // log2(N / 2)
-  for (uint32_t k = 2; k <= N; k <<= 1) {
-    for (uint32_t s = k >> 1; s > 0; s >>= 1) {
+  const uint32_t group_lg = half_lg - 2;                   // log2(N / 8): groups of eight wires a problem
+  // the stages inside a group of eight: all of k = 2, 4, 8 (`first`), or s = 4, 2, 1 of merge k
+  auto in_registers = [&](uint32_t k, bool first) {
+    for (uint32_t g = tid; g < N; g += SORT_THREADS) {     // 8 problems x N / 8 groups
+      const uint32_t prob = g >> group_lg, base = (g & ((N >> 3) - 1)) << 3;
+      unsigned long long* w = wires + prob * NP + wire_at(base);
+      unsigned long long v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = w[i];
+      if (first) {
+#pragma unroll
+        for (int kk = 2; kk <= 8; kk <<= 1)
+#pragma unroll
+          for (int ss = kk >> 1; ss >= 1; ss >>= 1)
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (!(i & ss)) exchange(v[i], v[i | ss], ((base + i) & kk) == 0);
+      } else {
+        const bool up = (base & k) == 0;
+#pragma unroll
+        for (int ss = 4; ss >= 1; ss >>= 1)
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (!(i & ss)) exchange(v[i], v[i | ss], up);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) w[i] = v[i];
+    }
+    __syncthreads();
+  };
+  in_registers(8, true);
+  for (uint32_t k = 16; k <= N; k <<= 1) {
+    for (uint32_t s = k >> 1; s >= 8; s >>= 1) {
       for (uint32_t t = tid; t < 4 * N; t += SORT_THREADS) {     // 8 problems x N/2 exchanges
         const uint32_t prob = t >> half_lg, i = t & (N / 2 - 1);     // N is a power of two
         const uint32_t lo = ((i & ~(s - 1)) << 1) | (i & (s - 1)), hi = lo | s;
-        unsigned long long* w = wires + prob * N;
-        const unsigned long long a = w[lo], b = w[hi];
+        unsigned long long* w = wires + prob * NP;
+        const unsigned long long a = w[wire_at(lo)], b = w[wire_at(hi)];
         const bool up = (lo & k) == 0;
-        if ((a > b) == up) { w[lo] = b; w[hi] = a; }
+        if ((a > b) == up) { w[wire_at(lo)] = b; w[wire_at(hi)] = a; }
       }
       __syncthreads();
     }
+    in_registers(k, false);
   }
   for (uint32_t rr = tid >> 5; rr < N / 4; rr += SORT_THREADS / 32) {
     const uint32_t tr = rr >> 3, fh = (rr >> 2) & 1, g = rr & 3;
     const uint64_t row = 32ull * tr + 16 * fh + 4 * g + j;
     const uint32_t e = 32 * tr + 8 * (2 * fh + fl) + 2 * g + odd;
-    const unsigned long long w = wires[c * N + e];
+    const unsigned long long w = wires[c * NP + wire_at(e)];
     keys[row * cols + 32ull * cb + word] = unordered((uint32_t)(w >> 32), is_i32, descending);
     if (indices) indices[row * cols + 32ull * cb + word] = (uint32_t)w;
   }
@@ -346,7 +387,7 @@ cudaError_t launch_scan(const uint32_t* in, uint32_t* out, uint64_t rows, uint64
 cudaError_t launch_sort_planes(const uint32_t* in, uint64_t rows, uint64_t cols, uint32_t n, int is_i32, int descending,
                                uint32_t* keys, uint32_t* indices, cudaStream_t s) {
   if (rows == 0 || cols == 0) return cudaSuccess;
-  const size_t smem = (size_t)8 * rows * sizeof(unsigned long long);
+  const size_t smem = (size_t)8 * (rows + rows / 8) * sizeof(unsigned long long);
   static size_t set = 0;
   if (smem > 48 * 1024 && smem > set) {
     cudaError_t e = cudaFuncSetAttribute(sort_planes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
