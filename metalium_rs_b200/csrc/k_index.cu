@@ -229,23 +229,26 @@ __global__ void gather_addrs_kernel(const uint64_t* __restrict__ addrs, uint64_t
 // convolution's padding tap).  A warp a (row, tap).
 __global__ void __launch_bounds__(256)
 select_taps_kernel(const char* __restrict__ table, uint64_t t_rows, uint64_t cols, int eb, const int32_t* __restrict__ idx,
-                   uint64_t taps, uint64_t n, int zero_row, char* __restrict__ out, uint64_t out_cols, uint64_t pitch, int* err) {
+                   uint64_t taps, uint64_t n, int zero_row, char* __restrict__ out, uint64_t out_cols, uint64_t pitch, int lanes_per,
+                   int* err) {
   pdl_enter();
-  const int lane = threadIdx.x & 31;
+  // a (row, tap) takes `lanes_per` lanes (a power of two: enough 16-byte pieces for a tap's columns), so a warp
+  // moves 32 / lanes_per of them at once
+  const int lane = threadIdx.x & 31, sub = lane / lanes_per, ln = lane % lanes_per, per = 32 / lanes_per;
   const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
-  for (uint64_t w = warp; w < n * taps; w += nwarps) {
+  for (uint64_t w = warp * per + sub; w < n * taps; w += nwarps * per) {
     const uint64_t i = w / taps, t = w - i * taps;
     const int64_t r = idx[t * n + i];
     char* dst = out + (i * out_cols + t * pitch) * eb;
     const uint64_t width = (t + 1 < taps ? pitch : cols);          // this tap's columns of the result
     const bool zero = zero_row && r == (int64_t)t_rows;
-    if (!zero && (r < 0 || (uint64_t)r >= t_rows)) { if (lane == 0) set_err(err, DOMAIN); continue; }
+    if (!zero && (r < 0 || (uint64_t)r >= t_rows)) { if (ln == 0) set_err(err, DOMAIN); continue; }
     if (zero) {
-      for (uint64_t b = lane * 2; b < width * eb; b += 64) *reinterpret_cast<uint16_t*>(dst + b) = 0;
+      for (uint64_t b = ln * 2; b < width * eb; b += 2 * lanes_per) *reinterpret_cast<uint16_t*>(dst + b) = 0;
     } else {
-      copy_row(table + (uint64_t)r * cols * eb, dst, cols * eb, lane, 32);
-      for (uint64_t b = cols * eb + lane * 2; b < width * eb; b += 64) *reinterpret_cast<uint16_t*>(dst + b) = 0;
+      copy_row(table + (uint64_t)r * cols * eb, dst, cols * eb, ln, lanes_per);
+      for (uint64_t b = cols * eb + ln * 2; b < width * eb; b += 2 * lanes_per) *reinterpret_cast<uint16_t*>(dst + b) = 0;
     }
   }
 }
@@ -365,8 +368,11 @@ cudaError_t launch_select_taps(const void* table, uint64_t t_rows, uint64_t cols
                                uint64_t taps, uint64_t n, int zero_row, void* out, uint64_t out_cols, int* err, cudaStream_t s) {
   if (n == 0 || taps == 0 || cols == 0) return cudaSuccess;
   const uint64_t pitch = (cols + 31) / 32 * 32;
-  launch_pdl(select_taps_kernel, dim3(cap_grid((n * taps + 7) / 8)), dim3(256), 0, s, (const char*)table, t_rows, cols, elem_bytes,
-             idx, taps, n, zero_row, (char*)out, out_cols, pitch, err);
+  int lanes_per = 1;
+  while (lanes_per < 32 && (uint64_t)lanes_per * 16 < pitch * elem_bytes) lanes_per <<= 1;
+  const uint64_t per_block = 8 * (32 / lanes_per);
+  launch_pdl(select_taps_kernel, dim3(cap_grid((n * taps + per_block - 1) / per_block)), dim3(256), 0, s, (const char*)table, t_rows, cols,
+             elem_bytes, idx, taps, n, zero_row, (char*)out, out_cols, pitch, lanes_per, err);
   return cudaGetLastError();
 }
 

@@ -400,3 +400,27 @@ def test_convolution_and_pooling_callers_issue_the_reference_sequence(e):   # bu
     p = f32(e, 1 * 8 * 8, 32)
     best, (oh, ow) = W.max_pool2d_nhwc(e, p, (1, 32, 8, 8), (2, 2), (2, 2))
     assert (oh, ow) == (4, 4) and e.dims_of(best) == ((16, 32), F32)
+
+
+def test_prompt_chunks_and_the_generation_after_them_issue_consistent_ops(e):   # tt-models/src/kv_cache.rs:231-296
+    from metalium_rs_b200 import workloads as W
+    cfg = W.LlamaConfig(layers=2, hidden=64, heads=2, kv_heads=1, head_dim=64, ff=128, vocab=256)
+    batch, chunk, max_len = 2, 128, 384
+    pre = W.LlamaPrefill(e, cfg, W.llama_weights(cfg, seed=3), batch, chunk)
+    assert pre.fused
+    dec = W.LlamaDecode(e, cfg, pre.w, batch, max_len=max_len)
+    ids = e.upload_bits(np.zeros((1, batch * chunk), np.int32), 1, batch * chunk, I32)
+    for k in range(2):                                   # every op of a chunk passes the engine's bounds and dims checks
+        lg, am = pre.forward(ids, cache=dec, start=k * chunk)
+        assert e.dims_of(lg) == ((batch, cfg.vocab), F32) and e.dims_of(am) == ((batch, 1), I32)
+        if k == 0:
+            e.free(lg); e.free(am)
+    with pytest.raises(ValueError):
+        pre.forward(ids, cache=dec, start=64)            # not whole 128-position tiles
+    with pytest.raises(ValueError):
+        pre.forward(ids, start=128)                      # a later chunk has no cache to attend to
+    with pytest.raises(AssertionError):
+        pre.forward(ids, cache=dec, start=384)           # past the cache
+    dec.continue_from(am, 2 * chunk)
+    lg2, am2 = dec.step()
+    assert e.dims_of(lg2) == ((batch, cfg.vocab), F32)
