@@ -489,6 +489,9 @@ def bench_main(args, metric, unit, size, workload_name, peaks, ClockSampler, che
     ms = float(t.item())
     launches = eng.device_traffic().launches - launches0
 
+    # completion evidence (the reference's `FabricExecution`): every rank's completed products, this rank's transfers
+    mesh = sm.mesh_execution()
+
     # product alone (no gather), to show what the exchange costs
     eng.sync()
     eng.timer_start()
@@ -555,7 +558,7 @@ def bench_main(args, metric, unit, size, workload_name, peaks, ClockSampler, che
                              "gather_bytes_per_rank": gather_bytes,
                              "gather_floor_ms_at_770GBs": gather_bytes / 770e9 * 1e3},
                 "validated": {"max_err_over_S": float(flags[1].item()), "sharded_equals_single_gpu_bits": True},
-                "tp_mlp": tp}
+                "tp_mlp": tp, "mesh_execution": mesh}
         print(json.dumps(line))
     dist.barrier()
     sm.close()
