@@ -5,7 +5,7 @@
  *
  * Every function mirrors one trait method: same argument meaning, same result
  * dims, same refusal behaviour.  A Rust `impl Engine for CudaEngine` binds these
- * one to one (see the `rust/` sources beside the package and INTEGRATION.md).
+ * one to one (the `rust/` sources beside the package hold that binding).
  *
  * Conventions
  *  - Tensors are opaque `b200_buffer` ids numbered by the engine
@@ -91,7 +91,13 @@ typedef struct {
   uint64_t pool_limit_bytes; /* 0 = no limit beyond the device's */
   int32_t fail_alloc_at;     /* host fault hook: the Nth allocation reports OOM; 0 off */
   int32_t _pad;
+  uint64_t wait_limit_cycles; /* how long a kernel of this engine waits on a barrier before it gives up and the
+                               * next wait reports B200_TIMEOUT (tt-device/src/transport.rs:208-217 bounds every
+                               * device wait the same way), in SM clock cycles; 0 = the default, about 2 s */
 } b200_config;
+/* One row of a per-op table (crates/burn-tt/src/report.rs:27-55 `OpStat`, reduced to what a GPU engine can
+ * say): the label an op ran under (`set_op_label`), how often, the kernels it launched, its device time. */
+typedef struct { char op[48]; uint64_t calls; uint64_t launches; double device_ms; } b200_op_stat;
 
 /* --- attach / detach: server.rs:2738 `attach`, :2711 `AttachGuard::drop` --- */
 int32_t b200_engine_create(int32_t device_ordinal, const b200_config* cfg, b200_engine** out);
@@ -203,9 +209,12 @@ int32_t b200_full_sum(b200_engine*, b200_buffer a, int32_t mean, b200_buffer* ou
  *  - n may not exceed 2^31 (B200_UNSUPPORTED, text through b200_last_error(NULL, ..)).
  *  - The first call on each device looks the array's address up; make that call before
  *    any stream capture begins.
- *  - All calls share the array.  Nothing in it needs clearing between calls (every
- *    partial is rewritten before it is read), but two calls that overlap on one GPU --
- *    different streams, or different threads -- race on it: order them.
+ *  - All calls share the array and it keeps the last call's contents.  The partials need no
+ *    clearing (each is rewritten before it is read); the ticket word behind them is cleared on
+ *    `cuda_stream` ahead of every launch, so a call that was cut short leaves nothing behind
+ *    for the next one.  Two calls that overlap on one GPU -- different streams, or different
+ *    threads -- still race on the array and either may give a wrong sum or none: order them.
+ *  - n = 0 gives 0.0 for the sum; the mean of nothing is refused (B200_UNSUPPORTED).
  *  - The result has the same bits as b200_full_sum's on the same values. */
 int32_t b200_full_sum_noalloc(const float* device_values, uint64_t n, int32_t mean, float* device_out,
                               void* cuda_stream);
@@ -379,10 +388,30 @@ int32_t b200_begin_trace(b200_engine*);
 int32_t b200_end_trace(b200_engine*, uint64_t* trace);
 int32_t b200_run_trace(b200_engine*, uint64_t trace);
 void    b200_release_trace(b200_engine*, uint64_t trace);
+/* server.rs:688 `trace_footprint`: the device bytes a trace holds until it is released (the blocks its capture
+ * took; the reference reports stream and program-cache bytes a unit, which a CUDA graph does not have). */
+int32_t b200_trace_footprint(const b200_engine*, uint64_t trace, uint64_t* bytes);
+/* server.rs:664 `trace_ops`: the ops the trace captured, in order, each with its label and its kernels.
+ * Fills at most `capacity` rows; *n is the number of ops. */
+int32_t b200_trace_ops(const b200_engine*, uint64_t trace, b200_op_stat* out, uint64_t capacity, uint64_t* n);
 
 /* --- waits and observability: lib.rs:218 `sync`, server.rs:584,663 --- */
 int32_t b200_sync(b200_engine*);
+/* server.rs:662 `set_op_label`: names the device work queued from here on (the server labels every job before it
+ * runs it, server.rs:2370).  The label prefixes error text, is kept with a capture's ops, and keys the profile. */
 void    b200_set_op_label(b200_engine*, const char* label);
+/* The profile mode (server.rs:672 `profile_mode`, :683 `profile_report`; crates/burn-tt/src/profile.rs:1-48):
+ * between start and stop every `b200_set_op_label` puts an event on the stream, and the device time up to the
+ * next label is charged to that label.  `b200_profile_stop` is a wait; `b200_profile_read` then gives one row a
+ * label in order of first appearance (at most `capacity` rows; *n is the number of labels).  Off by default:
+ * an event a label costs about a microsecond of host time. */
+int32_t b200_profile_start(b200_engine*);
+int32_t b200_profile_stop(b200_engine*);
+int32_t b200_profile_read(const b200_engine*, b200_op_stat* out, uint64_t capacity, uint64_t* n);
+/* Launches one CTA whose bounded wait can never be satisfied, so that the time-out path (error.rs:40 `Timeout`)
+ * runs on a healthy GPU: the wait gives up at `wait_limit_cycles`, the next wait returns B200_TIMEOUT, and the
+ * CUDA context stays usable.  Refused unless the engine was made with a limit of at most 2e9 cycles. */
+int32_t b200_debug_stalled_wait(b200_engine*);
 /* The tensor-core products of this engine use at most `sms` SMs from now on (0 = all): a caller that
  * runs a collective beside a product (the sharded product's all-gather) leaves it SMs to run on. */
 void    b200_set_matmul_sm_limit(b200_engine*, int32_t sms);
@@ -393,7 +422,8 @@ int32_t b200_timer_start(b200_engine*);
 int32_t b200_timer_stop(b200_engine*, float* ms);
 /* The engine's stream as a `cudaStream_t`, for a caller that shares the process. */
 void*   b200_stream(const b200_engine*);
-/* Name of the kernel path the last product took ("tcgen05", "simt", ...). */
+/* Name of the kernel path the last product took: "tcgen05" (one CTA a tile), "tcgen05-pair" (CTA pairs),
+ * "tcgen05-tf32x3", "skinny", "simt". */
 const char* b200_last_matmul_path(const b200_engine*);
 
 #ifdef __cplusplus

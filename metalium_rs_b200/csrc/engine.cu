@@ -17,8 +17,10 @@
 
 #include <algorithm>
 #include <map>
+#include <mutex>
 #include <string>
 #include <unordered_map>
+#include <unordered_set>
 #include <vector>
 
 #include "../../include/b200tt.h"
@@ -29,7 +31,11 @@ using namespace b200;
 
 namespace {
 
+// Text of failures that belong to no engine (a refused create, an engine-less entry point); calls that
+// take no engine may come from any thread, so it is guarded.
+std::mutex g_global_lock;
 std::string g_create_error;
+void set_create_error(const std::string& text) { std::lock_guard<std::mutex> hold(g_global_lock); g_create_error = text; }
 
 struct Buf {
   void* ptr = nullptr;
@@ -52,6 +58,7 @@ struct b200_engine {
   cudaStream_t stream = nullptr;
   cudaEvent_t t0 = nullptr, t1 = nullptr;
   int* d_err = nullptr;
+  long long wait_limit_word = 0;   // host copy of the limit kept behind the device error word
   cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;   // b200_matmul_host_bf16's copy streams
   int matmul_sm_limit = 0;   // b200_set_matmul_sm_limit
   int* h_err = nullptr;  // pinned
@@ -77,6 +84,7 @@ struct b200_engine {
     std::vector<std::pair<void*, uint64_t>> blocks;   // every block the capture took
     std::vector<void*> pinned;                        // host copies of block lists the graph re-uploads
     uint64_t launches = 0;
+    std::vector<std::pair<std::string, uint64_t>> ops;   // the captured ops in order: (label, kernels)
   };
   bool capturing = false;
   Trace cur;                                          // the trace being captured
@@ -84,6 +92,20 @@ struct b200_engine {
   std::unordered_map<void*, uint64_t> cur_owned;      // ptr -> size of blocks the capture owns
   std::unordered_map<uint64_t, Trace> traces;
   uint64_t next_trace = 1;
+  // Per-op device time (the profile mode, crates/burn-tt/src/profile.rs:1-48): while it is on, every
+  // `set_op_label` records an event on the stream, so the device time between two labels is charged to the
+  // first one -- the server labels each job before it runs it (server.rs:2370 `timed_job`).
+  struct Mark { std::string label; cudaEvent_t at = nullptr; uint64_t launches = 0; };
+  bool profiling = false;
+  std::vector<Mark> marks;                 // marks[i] opens op i; the next mark (or `prof_end`) closes it
+  cudaEvent_t prof_end = nullptr;
+  struct Stat { uint64_t calls = 0, launches = 0; double ms = 0; };
+  std::vector<std::pair<std::string, Stat>> prof_table;   // in order of first appearance
+  void drop_marks() {
+    for (auto& m : marks) if (m.at) cudaEventDestroy(m.at);
+    marks.clear();
+    if (prof_end) { cudaEventDestroy(prof_end); prof_end = nullptr; }
+  }
 
   int fail(int code, const char* fmt, ...) {
     char tmp[512];
@@ -147,7 +169,7 @@ struct b200_engine {
       }
       void* p = nullptr;
       cudaError_t e = cudaMalloc(&p, sz);
-      if (e != cudaSuccess) {
+      if (e != cudaSuccess && !capturing) {   // a synchronise would invalidate an open capture: fail at once there
         cudaGetLastError();
         cudaStreamSynchronize(stream);
         release_cache();
@@ -172,19 +194,15 @@ struct b200_engine {
   }
   // Whether a block belongs to a trace (captured or being captured): such a block never
   // returns to the pool while its trace lives.
-  bool trace_owned(void* p) const {
-    if (cur_owned.count(p)) return true;
-    for (auto& kv : traces)
-      for (auto& b : kv.second.blocks) if (b.first == p) return true;
-    return false;
-  }
+  std::unordered_set<void*> trace_ptrs;   // blocks of finished traces still alive
+  bool trace_owned(void* p) const { return cur_owned.count(p) != 0 || trace_ptrs.count(p) != 0; }
   // The block returns to the cache at once: every user of it was enqueued on the one
   // stream before this call, and so is every later user.
   void release(void* p, uint64_t sz) {
     if (sz == 0) return;                 // a kept block list: the engine's, not the pool's
     traffic.pool_in_use -= sz;
     if (capturing && cur_owned.count(p)) { cur_free.emplace(sz, p); return; }
-    if (!traces.empty() && trace_owned(p)) return;   // its trace keeps it
+    if (trace_owned(p)) return;   // its trace keeps it
     cache.emplace(sz, p);
   }
 
@@ -287,7 +305,7 @@ struct b200_engine {
     if (e == cudaErrorNotSupported) return fail(B200_UNSUPPORTED, "%s: unsupported", what);
     if (e != cudaSuccess) return cuda_fail(e, what);
     traffic.launches += n;
-    if (capturing) cur.launches += n;
+    if (capturing) { cur.launches += n; cur.ops.emplace_back(label, (uint64_t)n); }
     return B200_OK;
   }
   int wait() {
@@ -446,7 +464,41 @@ int index_buf(b200_engine* e, b200_buffer id, Buf** b, const char* what) {
 }  // namespace
 
 namespace b200 {
-void set_global_error(const char* text) { g_create_error = text ? text : ""; }
+void set_global_error(const char* text) { set_create_error(text ? text : ""); }
+
+namespace {
+std::mutex g_device_lock;
+std::map<std::pair<int, const void*>, size_t> g_smem_set;     // (device, kernel) -> bytes opted in
+std::map<std::pair<int, const void*>, int> g_device_values;
+}  // namespace
+
+cudaError_t ensure_dynamic_smem(const void* kernel, size_t bytes) {
+  if (bytes <= 48 * 1024) return cudaSuccess;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> hold(g_device_lock);
+  size_t& have = g_smem_set[{dev, kernel}];
+  if (have >= bytes) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess) have = bytes;
+  return e;
+}
+bool device_value_get(const void* key, int* value) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  std::lock_guard<std::mutex> hold(g_device_lock);
+  auto it = g_device_values.find({dev, key});
+  if (it == g_device_values.end()) return false;
+  *value = it->second;
+  return true;
+}
+void device_value_set(const void* key, int value) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  std::lock_guard<std::mutex> hold(g_device_lock);
+  g_device_values[{dev, key}] = value;
+}
 }  // namespace b200
 
 extern "C" {
@@ -457,22 +509,22 @@ int32_t b200_engine_create(int32_t device_ordinal, const b200_config* cfg, b200_
   cudaError_t ce = cudaGetDeviceCount(&count);
   if (ce != cudaSuccess || count == 0) {
     cudaGetLastError();
-    g_create_error = std::string("no CUDA device: ") + (ce != cudaSuccess ? cudaGetErrorString(ce) : "device count is 0");
+    set_create_error(std::string("no CUDA device: ") + (ce != cudaSuccess ? cudaGetErrorString(ce) : "device count is 0"));
     return B200_NO_DEVICE;
   }
   if (device_ordinal < 0 || device_ordinal >= count) {
-    g_create_error = "no such device " + std::to_string(device_ordinal) + " (present: 0.." + std::to_string(count - 1) + ")";
+    set_create_error("no such device " + std::to_string(device_ordinal) + " (present: 0.." + std::to_string(count - 1) + ")");
     return B200_NO_DEVICE;
   }
   cudaDeviceProp prop;
   cudaGetDeviceProperties(&prop, device_ordinal);
   if (prop.major != 10) {
-    g_create_error = std::string("device ") + prop.name + " is sm_" + std::to_string(prop.major) + std::to_string(prop.minor) +
-                     "; this engine's kernels are built for sm_100a only";
+    set_create_error(std::string("device ") + prop.name + " is sm_" + std::to_string(prop.major) + std::to_string(prop.minor) +
+                     "; this engine's kernels are built for sm_100a only");
     return B200_UNSUPPORTED;
   }
   if (cfg && (cfg->f32_matmul_mode < 0 || cfg->f32_matmul_mode > 2 || cfg->bf16_matmul_mode < 0 || cfg->bf16_matmul_mode > 2)) {
-    g_create_error = "config: unknown matmul mode";
+    set_create_error("config: unknown matmul mode");
     return B200_UNSUPPORTED;
   }
   b200_engine* e = new b200_engine();
@@ -484,11 +536,15 @@ int32_t b200_engine_create(int32_t device_ordinal, const b200_config* cfg, b200_
   if (ce == cudaSuccess) ce = cudaEventCreate(&e->t1);
   if (ce == cudaSuccess) ce = cudaMalloc(&e->d_err, 256);
   if (ce == cudaSuccess) ce = cudaMemsetAsync(e->d_err, 0, 256, e->stream);
+  // words 2..3 of the error block: the limit of every bounded device wait, in clock cycles (0: the kernels' default)
+  e->wait_limit_word = cfg ? (long long)cfg->wait_limit_cycles : 0;
+  if (ce == cudaSuccess && e->wait_limit_word > 0)
+    ce = cudaMemcpyAsync((char*)e->d_err + 8, &e->wait_limit_word, sizeof(long long), cudaMemcpyHostToDevice, e->stream);
   if (ce == cudaSuccess) ce = cudaMallocHost(&e->h_err, sizeof(int));
   if (ce == cudaSuccess) ce = cudaMalloc(&e->full_scratch, full_sum_scratch_floats() * sizeof(float));
   if (ce == cudaSuccess) ce = cudaMemsetAsync(e->full_scratch, 0, full_sum_scratch_floats() * sizeof(float), e->stream);
   if (ce != cudaSuccess) {
-    g_create_error = std::string("engine set-up: ") + cudaGetErrorString(ce);
+    set_create_error(std::string("engine set-up: ") + cudaGetErrorString(ce));
     delete e;
     return B200_DEVICE;
   }
@@ -518,6 +574,7 @@ void b200_engine_destroy(b200_engine* e) {
     if (!kv.second.parent && !kv.second.adopted && kv.second.ptr) cudaFree(kv.second.ptr);
   for (auto& kv : e->cache) cudaFree(kv.second);
   for (auto& kv : e->meta_cache) cudaFree(kv.second.dev);
+  e->drop_marks();
   cudaFree(e->d_err);
   cudaFree(e->full_scratch);
   cudaFreeHost(e->h_err);
@@ -534,7 +591,9 @@ int32_t b200_supports_batched_layout(const b200_engine*) { return 1; }
 int32_t b200_supports_exact_matmul(const b200_engine*) { return 0; }
 
 size_t b200_last_error(const b200_engine* e, char* buf, size_t len) {
-  const std::string& s = e ? e->last_error : g_create_error;
+  std::string global;
+  if (!e) { std::lock_guard<std::mutex> hold(g_global_lock); global = g_create_error; }
+  const std::string& s = e ? e->last_error : global;
   if (buf && len) {
     const size_t n = std::min(len - 1, s.size());
     memcpy(buf, s.data(), n);
@@ -648,9 +707,10 @@ static int run_gemm(b200_engine* e, GemmArgs& g, const GemmBatch* batches_host, 
     return e->launched(launch_gemm_skinny(g, e->stream), what);
   }
   if (want_tc && gemm_tc_supported(g, &why)) {
-    const cudaError_t ce = launch_gemm_tc(g, batches_host, e->d_err, e->stream);
+    int pair = 0;
+    const cudaError_t ce = launch_gemm_tc(g, batches_host, e->d_err, e->stream, &pair);
     if (ce != cudaErrorNotSupported) {
-      e->matmul_path = "tcgen05";
+      e->matmul_path = pair ? "tcgen05-pair" : "tcgen05";
       return e->launched(ce, what);
     }
     why = "the driver refused a tensor map for this shape";
@@ -773,9 +833,10 @@ int32_t b200_matmul_silu_mul(b200_engine* e, b200_buffer a, b200_buffer b, b200_
   g.sm_limit = e->matmul_sm_limit;
   const char* why = "";
   if (!gemm_tc_supported(g, &why)) { e->drop(*out); return e->fail(B200_UNSUPPORTED, "matmul_silu_mul: the tcgen05 path refuses this product (%s)", why); }
-  const cudaError_t ce = launch_gemm_tc(g, nullptr, e->d_err, e->stream);
+  int pair = 0;
+  const cudaError_t ce = launch_gemm_tc(g, nullptr, e->d_err, e->stream, &pair);
   if (ce == cudaErrorNotSupported) { e->drop(*out); return e->fail(B200_UNSUPPORTED, "matmul_silu_mul: the driver refused a tensor map for this shape"); }
-  e->matmul_path = "tcgen05";
+  e->matmul_path = pair ? "tcgen05-pair" : "tcgen05";
   st = e->launched(ce, "matmul_silu_mul");
   if (st) { e->drop(*out); return st; }
   set_dims(out_dims, m, n / 2);
@@ -815,9 +876,10 @@ int32_t b200_matmul_into(b200_engine* e, b200_buffer a, b200_buffer b, void* con
   g.sm_limit = e->matmul_sm_limit;
   const char* why = "";
   if (!gemm_tc_supported(g, &why)) return e->fail(B200_UNSUPPORTED, "matmul_into: the tcgen05 path refuses this product (%s)", why);
-  const cudaError_t ce = launch_gemm_tc(g, nullptr, e->d_err, e->stream);
+  int pair = 0;
+  const cudaError_t ce = launch_gemm_tc(g, nullptr, e->d_err, e->stream, &pair);
   if (ce == cudaErrorNotSupported) return e->fail(B200_UNSUPPORTED, "matmul_into: the driver refused a tensor map for this shape");
-  e->matmul_path = "tcgen05";
+  e->matmul_path = pair ? "tcgen05-pair" : "tcgen05";
   return e->launched(ce, "matmul_into");
 }
 
@@ -972,7 +1034,21 @@ int32_t b200_matmul_batched(b200_engine* e, b200_buffer a, b200_buffer b, const 
   if (st) return st;
   A = e->get(a); B = e->get(b);
   if ((!stacked && step != m) || k == 0) cudaMemsetAsync(C->ptr, 0, items * step * n * elem_bytes(C->elem), e->stream);
-  if (items && k) {
+  if (items == 1 && k) {
+    // One item is one plain product on the item's blocks: the block offsets move the operands' bases and the
+    // item's transposed flags are the product's, so every kernel sees what it sees for `matmul_dram` (the
+    // kernels key "batched" on more than one item and would otherwise drop the item's offsets and flags).
+    const uint64_t eb = elem_bytes(A->elem);
+    GemmArgs g{};
+    g.a = (const char*)A->ptr + bt[0].a_off * eb; g.b = (const char*)B->ptr + bt[0].b_off * eb; g.c = C->ptr;
+    g.in_bf16 = abf; g.out_bf16 = out_bf16;
+    g.m = m; g.n = n; g.k = k;
+    g.lda = A->cols; g.ldb = B->cols; g.ldc = n;
+    g.a_trans = bt[0].a_trans; g.b_trans = bt[0].b_trans;
+    g.batch = 1; g.batches_dev = nullptr;
+    st = run_gemm(e, g, nullptr, "matmul_batched");
+    if (st) { e->drop(*out); return st; }
+  } else if (items && k) {
     void* dev = nullptr;
     uint64_t got = 0;
     st = e->to_device(bt.data(), items * sizeof(GemmBatch), &dev, &got);
@@ -1327,14 +1403,33 @@ int32_t b200_select_add_rows(b200_engine* e, b200_buffer t, b200_buffer indices,
 
 int32_t b200_rows_add(b200_engine* e, b200_buffer t, const uint64_t* indices, uint64_t n, b200_buffer value, b200_buffer* out,
                       uint64_t out_dims[2]) {
-  std::vector<uint32_t> idx(n);
-  for (uint64_t i = 0; i < n; ++i) idx[i] = (uint32_t)indices[i];
-  b200_buffer ii = 0;
-  int st = b200_upload_bits(e, idx.data(), 1, n, B200_I32, &ii);
+  // The host's index list goes to the device as a block list does (kept by content, or a copy node of an
+  // open capture), so the call is as capturable as `select_add_rows` itself.
+  cudaSetDevice(e->device);
+  Buf *T = nullptr, *V = nullptr;
+  int st = e->need(t, &T, "rows_add");
+  if (!st) st = e->need(value, &V, "rows_add");
   if (st) return st;
-  st = b200_select_add_rows(e, t, ii, value, out, out_dims);
-  b200_free(e, ii);
-  return st;
+  if (T->elem != B200_F32 || V->elem != B200_F32 || V->rows != n || V->cols != T->cols)
+    return e->fail(B200_UNSUPPORTED, "rows_add: shapes do not meet");
+  const uint64_t rows = T->rows, cols = T->cols;
+  std::vector<int32_t> idx(n);
+  for (uint64_t i = 0; i < n; ++i) idx[i] = indices[i] > 0x7fffffffull ? -1 : (int32_t)indices[i];   // outside every table: DOMAIN
+  Buf* O = nullptr;
+  st = copy_of(e, T, out, &O);
+  if (st) return st;
+  V = e->get(value);
+  if (n) {
+    void* dev = nullptr; uint64_t got = 0;
+    st = e->to_device(idx.data(), n * sizeof(int32_t), &dev, &got);
+    if (st) { e->drop(*out); return st; }
+    st = e->launched(launch_select_add_rows((float*)O->ptr, rows, cols, (const int32_t*)dev, n, (const float*)V->ptr, e->d_err, e->stream),
+                     "rows_add");
+    e->release(dev, got);
+    if (st) { e->drop(*out); return st; }
+  }
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
 }
 
 int32_t b200_assign_rows(b200_engine* e, b200_buffer t, b200_buffer value, const uint64_t* pairs, uint64_t n, b200_buffer* out,
@@ -2049,6 +2144,7 @@ int32_t b200_end_trace(b200_engine* e, uint64_t* trace) {
   e->cur_free.clear();
   e->cur_owned.clear();
   *trace = e->next_trace++;
+  for (auto& b : e->cur.blocks) e->trace_ptrs.insert(b.first);
   e->traces.emplace(*trace, std::move(e->cur));
   e->cur = b200_engine::Trace();
   return B200_OK;
@@ -2076,6 +2172,7 @@ void b200_release_trace(b200_engine* e, uint64_t trace) {
   if (t.graph) cudaGraphDestroy(t.graph);
   for (void* h : t.pinned) cudaFreeHost(h);
   // Blocks no live buffer sits in return to the pool; the rest return when their buffer is freed.
+  for (auto& b : t.blocks) e->trace_ptrs.erase(b.first);
   for (auto& b : t.blocks) {
     bool live = false;
     for (auto& kv : e->bufs) if (kv.second.ptr == b.first && !kv.second.parent) { live = true; break; }
@@ -2085,7 +2182,100 @@ void b200_release_trace(b200_engine* e, uint64_t trace) {
 
 // ---- waits and observability ---------------------------------------------------
 int32_t b200_sync(b200_engine* e) { cudaSetDevice(e->device); return e->wait(); }
-void b200_set_op_label(b200_engine* e, const char* label) { e->label = label ? label : ""; }
+void b200_set_op_label(b200_engine* e, const char* label) {
+  e->label = label ? label : "";
+  if (e->profiling && !e->capturing) {
+    cudaSetDevice(e->device);
+    b200_engine::Mark m;
+    m.label = e->label;
+    m.launches = e->traffic.launches;
+    if (cudaEventCreate(&m.at) == cudaSuccess && cudaEventRecord(m.at, e->stream) == cudaSuccess) e->marks.push_back(m);
+    else { if (m.at) cudaEventDestroy(m.at); cudaGetLastError(); }
+  }
+}
+
+// ---- per-op device time: profile.rs:1-48, report.rs:27-55 -----------------------------
+int32_t b200_profile_start(b200_engine* e) {
+  cudaSetDevice(e->device);
+  if (e->capturing) return e->fail(B200_UNSUPPORTED, "profile_start inside a trace capture");
+  e->drop_marks();
+  e->prof_table.clear();
+  e->profiling = true;
+  return B200_OK;
+}
+int32_t b200_profile_stop(b200_engine* e) {
+  cudaSetDevice(e->device);
+  if (!e->profiling) return e->fail(B200_UNSUPPORTED, "profile_stop: the profile mode is off");
+  if (e->capturing) return e->fail(B200_UNSUPPORTED, "profile_stop inside a trace capture");
+  e->profiling = false;
+  const uint64_t launches_end = e->traffic.launches;
+  cudaError_t ce = cudaEventCreate(&e->prof_end);
+  if (ce == cudaSuccess) ce = cudaEventRecord(e->prof_end, e->stream);
+  if (ce != cudaSuccess) { e->drop_marks(); return e->cuda_fail(ce, "profile_stop"); }
+  const int st = e->wait();
+  if (st) { e->drop_marks(); return st; }
+  for (size_t i = 0; i < e->marks.size(); ++i) {
+    const bool last = i + 1 == e->marks.size();
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, e->marks[i].at, last ? e->prof_end : e->marks[i + 1].at) != cudaSuccess) { cudaGetLastError(); ms = 0.f; }
+    const uint64_t l1 = last ? launches_end : e->marks[i + 1].launches;
+    b200_engine::Stat* stat = nullptr;
+    for (auto& kv : e->prof_table) if (kv.first == e->marks[i].label) { stat = &kv.second; break; }
+    if (!stat) { e->prof_table.emplace_back(e->marks[i].label, b200_engine::Stat()); stat = &e->prof_table.back().second; }
+    stat->calls += 1;
+    stat->launches += l1 - e->marks[i].launches;
+    stat->ms += (double)ms;
+  }
+  e->drop_marks();
+  return B200_OK;
+}
+int32_t b200_profile_read(const b200_engine* e, b200_op_stat* out, uint64_t capacity, uint64_t* n) {
+  if (n) *n = e->prof_table.size();
+  for (uint64_t i = 0; out && i < capacity && i < e->prof_table.size(); ++i) {
+    memset(&out[i], 0, sizeof out[i]);
+    strncpy(out[i].op, e->prof_table[i].first.c_str(), sizeof out[i].op - 1);
+    out[i].calls = e->prof_table[i].second.calls;
+    out[i].launches = e->prof_table[i].second.launches;
+    out[i].device_ms = e->prof_table[i].second.ms;
+  }
+  return B200_OK;
+}
+
+// server.rs:730 `trace_footprint`: the device bytes a trace holds until it is released.
+int32_t b200_trace_footprint(const b200_engine* e, uint64_t trace, uint64_t* bytes) {
+  auto it = e->traces.find(trace);
+  if (it == e->traces.end()) return B200_STALE;
+  uint64_t total = 0;
+  for (auto& b : it->second.blocks) total += b.second;
+  *bytes = total;
+  return B200_OK;
+}
+
+// server.rs:664 `trace_ops`: the ops a trace captured, in capture order, each with the label it ran under
+// and the kernels it launched (`device_ms` is 0: a replay is timed as a whole, under its own label).
+int32_t b200_trace_ops(const b200_engine* e, uint64_t trace, b200_op_stat* out, uint64_t capacity, uint64_t* n) {
+  auto it = e->traces.find(trace);
+  if (it == e->traces.end()) return B200_STALE;
+  const auto& ops = it->second.ops;
+  if (n) *n = ops.size();
+  for (uint64_t i = 0; out && i < capacity && i < ops.size(); ++i) {
+    memset(&out[i], 0, sizeof out[i]);
+    strncpy(out[i].op, ops[i].first.c_str(), sizeof out[i].op - 1);
+    out[i].calls = 1;
+    out[i].launches = ops[i].second;
+  }
+  return B200_OK;
+}
+
+// A bounded device wait that nothing ends, run on purpose: the one failure a kernel of this engine can meet
+// on a healthy GPU.  The wait gives up at the engine's limit, the next wait reports TIMEOUT
+// (crates/burn-tt/src/error.rs:40), the GPU and the CUDA context stay usable.
+int32_t b200_debug_stalled_wait(b200_engine* e) {
+  cudaSetDevice(e->device);
+  if (e->wait_limit_word <= 0 || e->wait_limit_word > 2000000000ll)
+    return e->fail(B200_UNSUPPORTED, "debug_stalled_wait: set b200_config.wait_limit_cycles to at most 2e9 (a second) first");
+  return e->launched(launch_stalled_wait(e->d_err, e->stream), "debug_stalled_wait");
+}
 void b200_set_matmul_sm_limit(b200_engine* e, int32_t sms) { e->matmul_sm_limit = sms > 0 ? sms : 0; }
 void b200_traffic_get(const b200_engine* e, b200_traffic* out) { *out = e->traffic; }
 int32_t b200_timer_start(b200_engine* e) {

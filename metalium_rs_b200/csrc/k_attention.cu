@@ -355,11 +355,9 @@ template <typename KV, int RT, bool GROUPED>
 cudaError_t launch_rt(const float* q, const KV* k, uint64_t k_ld, const KV* v, uint64_t v_ld, const uint32_t* mask,
                       const AttnJob* jobs, const AttnRow* rows, uint64_t n_jobs, int d, int l, int dv, float scale,
                       int splits, int lc, size_t smem, void* out, int out_bf16, float* part_o, float* part_ms, cudaStream_t stream) {
-  static bool set = false;
-  if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(attention_rows_kernel<KV, RT, GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  {
+    const cudaError_t e = ensure_dynamic_smem((const void*)attention_rows_kernel<KV, RT, GROUPED>, 200 * 1024);
     if (e != cudaSuccess) return e;
-    set = true;
   }
   launch_pdl(attention_rows_kernel<KV, RT, GROUPED>, dim3((unsigned)splits, (unsigned)n_jobs, 1), dim3(THREADS), smem, stream,
              q, k, k_ld, v, v_ld, mask, jobs, rows, d, l, dv, lc, scale, out, out_bf16, part_o, part_ms);

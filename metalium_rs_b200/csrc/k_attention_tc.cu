@@ -84,8 +84,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   uint64_t* o_full = p_empty + 1;
   uint32_t* tmem_slot = (uint32_t*)(o_full + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  long long wait_limit = WAIT_CYCLES;   // the engine's limit, read once global memory may be touched
   auto hand_off = [&](uint64_t* bar, uint32_t parity) -> bool {   // a wait on the chain S -> P -> O
-    return p.spin ? mbar_wait_spin(bar, parity, abort_flag) : mbar_wait(bar, parity, abort_flag);
+    return p.spin ? mbar_wait_spin(bar, parity, abort_flag, wait_limit) : mbar_wait(bar, parity, abort_flag, wait_limit);
   };
   float* xmax = (float*)(sP + P_BYTES + 256);   // [2][128]: the two halves' row maxima
   float* xsum = xmax + 256;                     // [2][128]: and row sums
@@ -112,6 +113,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const uint32_t tmem_base = *tmem_slot;
   // barriers, tensor memory and descriptors are set up: from here on global memory is touched
   pdl_enter();
+  wait_limit = wait_limit_of(p.err);
 
   // Heaviest work first: under a causal mask a block's last query tile has the most keys, so the grid
   // runs every block's last tile, then every block's tile before it, ... (the block index is the
@@ -138,14 +140,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       uint32_t ks = 0, kph = 0, vs = 0, vph = 0;
       for (int pass = 0; pass < 2 && ok; ++pass) {
         for (uint32_t j = 0; j < nk; ++j) {
-          if (!mbar_wait(&k_empty[ks], kph ^ 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&k_empty[ks], kph ^ 1, abort_flag, wait_limit)) { ok = false; break; }
           mbar_expect_tx(&k_full[ks], OP_BYTES);
 #pragma unroll
           for (int c = 0; c < CH; ++c)
             tma_load_2d(sK + ks * OP_BYTES + c * TILE_BYTES, &map_k, &k_full[ks], it.k_c + c * 64, it.k_r + (int32_t)(j * 128));
           if (++ks == KS) { ks = 0; kph ^= 1; }
           if (pass == 1) {
-            if (!mbar_wait(&v_empty[vs], vph ^ 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(&v_empty[vs], vph ^ 1, abort_flag, wait_limit)) { ok = false; break; }
             mbar_expect_tx(&v_full[vs], OP_BYTES);
 #pragma unroll
             for (int c = 0; c < CH; ++c)
@@ -162,14 +164,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // phase, the rest in the previous one (or never: their barrier is then already past it).
       {
         const long long t0 = clock64();
-        while (!mbar_try(q_full, 0)) { if (clock64() - t0 > WAIT_CYCLES) break; }
+        while (!mbar_try(q_full, 0)) { if (clock64() - t0 > wait_limit) break; }
       }
       for (int s = 0; s < KS; ++s) {
         const uint32_t kp = (s < (int)ks) ? kph : (kph ^ 1);
         const uint32_t vp = (s < (int)vs) ? vph : (vph ^ 1);
         const long long t0 = clock64();
-        while (!mbar_try(&k_full[s], kp)) { if (clock64() - t0 > WAIT_CYCLES) break; }
-        while (!mbar_try(&v_full[s], vp)) { if (clock64() - t0 > WAIT_CYCLES) break; }
+        while (!mbar_try(&k_full[s], kp)) { if (clock64() - t0 > wait_limit) break; }
+        while (!mbar_try(&v_full[s], vp)) { if (clock64() - t0 > wait_limit) break; }
       }
     }
   } else if (warp == 1) {
@@ -178,14 +180,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // kind::f16: F32 accumulate (bit 4), BF16 A and B (bits 7, 10), B MN-major for P V (bit 16)
       constexpr uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
       constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-      bool ok = mbar_wait(q_full, 0, abort_flag);
+      bool ok = mbar_wait(q_full, 0, abort_flag, wait_limit);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       uint32_t ks = 0, kph = 0, vs = 0, vph = 0, t = 0;
       const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
       auto issue_qk = [&]() -> bool {
         const uint32_t buf = t & 1, sph = (t >> 1) & 1;
         if (!hand_off(&s_empty[buf], sph ^ 1)) return false;
-        if (!mbar_wait(&k_full[ks], kph, abort_flag)) return false;
+        if (!mbar_wait(&k_full[ks], kph, abort_flag, wait_limit)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t k_addr = smem_u32(sK + ks * OP_BYTES);
 #pragma unroll
@@ -204,7 +206,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       for (uint32_t j = 0; j < nk && ok; ++j) {
         if (j + 1 < nk) { ok = issue_qk(); if (!ok) break; }             // the next scores run under these exponentials
         if (!hand_off(p_full, j & 1)) { ok = false; break; }
-        if (!mbar_wait(&v_full[vs], vph, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&v_full[vs], vph, abort_flag, wait_limit)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t v_addr = smem_u32(sV + vs * OP_BYTES);
 #pragma unroll
@@ -302,7 +304,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     xsum[half * 128 + row] = sum;
     asm volatile("bar.sync 1, 256;" ::: "memory");
     sum = xsum[row] + xsum[128 + row];
-    if (ok && !mbar_wait(o_full, 0, abort_flag)) ok = false;
+    if (ok && !mbar_wait(o_full, 0, abort_flag, wait_limit)) ok = false;
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = 1.0f / ((sum < FLT_MIN) ? FLT_MIN : sum);
@@ -344,11 +346,9 @@ cudaError_t launch_d(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
                      uint64_t n_items, cudaStream_t stream) {
   constexpr int CH = D / 64, KS = D == 64 ? 3 : 2;
   constexpr size_t smem = (size_t)(1 + 2 * KS) * CH * TILE_BYTES + P_BYTES + 256 + 2048 + 1024;
-  static bool set = false;
-  if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  {
+    const cudaError_t e = ensure_dynamic_smem((const void*)attention_tc_kernel<D>, smem);
     if (e != cudaSuccess) return e;
-    set = true;
   }
   launch_pdl(attention_tc_kernel<D>, dim3((unsigned)(n_items * p.q_tiles), 1, 1), dim3(ATTN_THREADS), smem, stream, mq, mk, mv, p);
   return cudaGetLastError();

@@ -118,11 +118,9 @@ cudaError_t launch_gemm_skinny(const GemmArgs& g, cudaStream_t stream) {
   const unsigned grid = (unsigned)((g.n + SK_COLS - 1) / SK_COLS);
 #define GO(MT)                                                                                                   \
   do {                                                                                                           \
-    static size_t set = 0;                                                                                       \
-    if (smem > 48 * 1024 && smem > set) {                                                                        \
-      cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    {                                                                                                            \
+      const cudaError_t e = ensure_dynamic_smem((const void*)gemm_skinny_kernel<MT>, smem);                      \
       if (e != cudaSuccess) return e;                                                                            \
-      set = smem;                                                                                                \
     }                                                                                                            \
     launch_pdl(gemm_skinny_kernel<MT>, dim3(grid), dim3(SK_THREADS), smem, stream, (const uint16_t*)g.a, g.lda, (const uint16_t*)g.b, g.ldb, \
                g.c, g.ldc, g.out_bf16, (int)g.m, g.n, (int)g.k);                                                   \

@@ -58,6 +58,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
   // barriers, tensor memory and descriptors are set up: from here on global memory is touched
   pdl_enter();
+  const long long wait_limit = wait_limit_of(p.err);
 
   const uint64_t total_tiles = (uint64_t)p.tiles_m * p.tiles_n * p.batch;
   const uint32_t num_kb = (uint32_t)((p.k + BK - 1) / BK);
@@ -76,7 +77,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int32_t b_r0 = (int32_t)(b_off / p.ldb), b_c0 = (int32_t)(b_off % p.ldb);
         const int32_t m0 = (int32_t)(tm * BM), n0 = (int32_t)(tn * BN);
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, wait_limit)) { ok = false; break; }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           mbar_expect_tx(&full[stage], STAGE_BYTES);
@@ -110,7 +111,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // stages before `stage` were armed in the current phase, the rest in the previous
         const long long t0 = clock64();
         while (!mbar_try(&full[s], ph)) {
-          if (clock64() - t0 > WAIT_CYCLES) break;
+          if (clock64() - t0 > wait_limit) break;
         }
       }
     }
@@ -123,11 +124,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       bool ok = true;
       for (uint64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
         const uint32_t acc = local & 1, acc_phase = (local >> 1) & 1;
-        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, wait_limit)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&full[stage], phase, abort_flag, wait_limit)) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t sb = sa + A_BYTES;
@@ -157,7 +158,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       uint64_t b; uint32_t tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, &b, &tm, &tn);
       const uint32_t acc = local & 1, acc_phase = (local >> 1) & 1;
-      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, wait_limit)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint64_t c_off = p.batches ? p.batches[b].c_off : 0;
       const uint64_t n0 = (uint64_t)tn * BN;
@@ -185,6 +186,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// A wait nothing ends: the barrier expects bytes no copy was issued for.  The same `mbar_wait` the product
+// kernels use runs out at the engine's limit and reports TIMEOUT; the barrier is invalidated before the CTA leaves.
+__global__ void __launch_bounds__(32, 1) stalled_wait_kernel(int* err) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_word;
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_expect_tx(&bar, 16);
+    if (!mbar_wait(&bar, 0, &abort_word, wait_limit_of(err))) atomicCAS(err, 0, TIMEOUT_CODE);
+    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(&bar)) : "memory");
+  }
+}
+
 // ---- host side -----------------------------------------------------------------
 
 template <int BN, int STAGES>
@@ -193,12 +209,9 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const T
   constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256 + EPI_BYTES;
 #define TC_LAUNCH(AM, BMJ)                                                                              \
   do {                                                                                                  \
-    static bool attr_set = false;                                                                       \
-    if (!attr_set) {                                                                                    \
-      cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, AM, BMJ>,                          \
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+    {                                                                                                   \
+      const cudaError_t e = ensure_dynamic_smem((const void*)gemm_tc_kernel<BN, STAGES, AM, BMJ>, smem); \
       if (e != cudaSuccess) return e;                                                                   \
-      attr_set = true;                                                                                  \
     }                                                                                                   \
     launch_pdl(gemm_tc_kernel<BN, STAGES, AM, BMJ>, dim3(grid), dim3(NUM_THREADS), smem, stream, ma, mb, p); \
   } while (0)
@@ -217,6 +230,11 @@ uint32_t env_u32(const char* name, uint32_t dflt) {
 
 }  // namespace
 
+cudaError_t launch_stalled_wait(int* err_word, cudaStream_t stream) {
+  stalled_wait_kernel<<<1, 32, 0, stream>>>(err_word);
+  return cudaGetLastError();
+}
+
 bool gemm_tc_supported(const GemmArgs& g, const char** why) {
   *why = "";
   if (!g.in_bf16) { *why = "operands are not BF16"; return false; }
@@ -232,10 +250,14 @@ bool gemm_tc_supported(const GemmArgs& g, const char** why) {
   return true;
 }
 
-cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int* err_word, cudaStream_t stream) {
+cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int* err_word, cudaStream_t stream, int* pair_taken) {
+  if (pair_taken) *pair_taken = 0;
   if (gemm_tc2_wanted(g)) {
     const cudaError_t e2 = launch_gemm_tc2(g, err_word, stream);
-    if (e2 != cudaErrorNotSupported) return e2;
+    if (e2 != cudaErrorNotSupported) {
+      if (pair_taken) *pair_taken = 1;
+      return e2;
+    }
   }
   bool a_mn = g.a_trans != 0, b_mn = g.b_trans == 0;
   if (g.batch > 1) {

@@ -99,6 +99,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
   // barriers, tensor memory and descriptors are set up: from here on global memory is touched
   pdl_enter();
+  const long long wait_limit = wait_limit_of(p.err);
 
   const uint64_t total_tiles = (uint64_t)p.tiles_m * p.tiles_n;  // tiles of 256 x 256
   const uint32_t num_kb = (uint32_t)((p.k + BK - 1) / BK);
@@ -113,7 +114,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         tile_coords(t, p.tiles_m, p.tiles_n, &b, &tm, &tn);
         const int32_t m0 = (int32_t)(tm * 256 + rank * BM), n0 = (int32_t)(tn * P_BN + rank * P_HALF);
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, wait_limit)) { ok = false; break; }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           if (rank == 0) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);  // the pair's bytes
@@ -149,11 +150,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       bool ok = true;
       for (uint64_t t = cluster_id; t < total_tiles && ok; t += n_clusters, ++local) {
         const uint32_t acc = local & 1, acc_phase = (local >> 1) & 1;
-        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, wait_limit)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d_tmem = tmem_base + acc * P_BN;
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&full[stage], phase, abort_flag, wait_limit)) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t sb = sa + A_BYTES;
@@ -180,7 +181,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       uint64_t b; uint32_t tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, &b, &tm, &tn);
       const uint32_t acc = local & 1, acc_phase = (local >> 1) & 1;
-      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, wait_limit)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint64_t n0 = (uint64_t)tn * P_BN;
       if (p.epi_mode == 1) epilogue_warp_silu_mul(p, tmem_base + ((quad * 32u) << 16) + acc * P_BN, (uint64_t)tm * 256 + rank * BM + quad * 32, tn, lane, epi_stage + quad * EPI_WARP_BYTES);
@@ -251,15 +252,16 @@ cudaError_t launch_gemm_tc2(const GemmArgs& g, int* err_word, cudaStream_t strea
   cudaError_t e = cudaSuccess;
 #define TC2_LAUNCH(AM, BMJ)                                                                           \
   do {                                                                                                \
-    static int clusters = 0;                                                                          \
-    if (!clusters) {                                                                                  \
-      e = cudaFuncSetAttribute(gemm_tc2_kernel<AM, BMJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-      if (e != cudaSuccess) return e;                                                                 \
+    int clusters = 0;   /* clusters of this kernel one device runs at a time: asked once a device */ \
+    e = ensure_dynamic_smem((const void*)gemm_tc2_kernel<AM, BMJ>, smem);                             \
+    if (e != cudaSuccess) return e;                                                                   \
+    if (!device_value_get((const void*)gemm_tc2_kernel<AM, BMJ>, &clusters)) {                        \
       cfg.gridDim = dim3(148, 1, 1);                                                                  \
       int n = 0;                                                                                      \
       e = cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<AM, BMJ>, &cfg);                         \
       if (e != cudaSuccess || n <= 0) { cudaGetLastError(); return cudaErrorNotSupported; }           \
       clusters = n;                                                                                   \
+      device_value_set((const void*)gemm_tc2_kernel<AM, BMJ>, n);                                     \
     }                                                                                                 \
     uint64_t use = total < (uint64_t)clusters ? total : (uint64_t)clusters;                           \
     if (g.sm_limit > 1 && use > (uint64_t)(g.sm_limit / 2)) use = (uint64_t)(g.sm_limit / 2);        \

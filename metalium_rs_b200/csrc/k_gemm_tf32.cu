@@ -85,6 +85,7 @@ gemm_tf32_kernel(const __grid_constant__ Tf32Maps maps, const TcParams p) {
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  const long long wait_limit = wait_limit_of(p.err);
 
   const uint64_t total_tiles = (uint64_t)p.tiles_m * p.tiles_n;
   const uint32_t num_kb = (uint32_t)((p.k + TBK - 1) / TBK);
@@ -98,7 +99,7 @@ gemm_tf32_kernel(const __grid_constant__ Tf32Maps maps, const TcParams p) {
         tile_coords(t, p.tiles_m, p.tiles_n, &b, &tm, &tn);
         const int32_t m0 = (int32_t)(tm * BM), n0 = (int32_t)(tn * TBN);
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, wait_limit)) { ok = false; break; }
           uint8_t* sah = smem + stage * STAGE_BYTES;
           uint8_t* sal = sah + A_BYTES;
           uint8_t* sbh = sal + A_BYTES;
@@ -132,7 +133,7 @@ gemm_tf32_kernel(const __grid_constant__ Tf32Maps maps, const TcParams p) {
       for (int s = 0; s < TSTAGES; ++s) {  // drain: no copy may outlive the CTA
         const uint32_t ph = (s < (int)stage) ? phase : (phase ^ 1);
         const long long t0 = clock64();
-        while (!mbar_try(&full[s], ph)) { if (clock64() - t0 > WAIT_CYCLES) break; }
+        while (!mbar_try(&full[s], ph)) { if (clock64() - t0 > wait_limit) break; }
       }
     }
   } else if (warp == 1) {
@@ -144,11 +145,11 @@ gemm_tf32_kernel(const __grid_constant__ Tf32Maps maps, const TcParams p) {
       bool ok = true;
       for (uint64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
         const uint32_t acc = local & 1, acc_phase = (local >> 1) & 1;
-        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, wait_limit)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d_tmem = tmem_base + acc * TBN;
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&full[stage], phase, abort_flag, wait_limit)) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t sah = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t sal = sah + A_BYTES, sbh = sal + A_BYTES, sbl = sbh + B_BYTES;
@@ -182,7 +183,7 @@ gemm_tf32_kernel(const __grid_constant__ Tf32Maps maps, const TcParams p) {
       uint64_t b; uint32_t tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, &b, &tm, &tn);
       const uint32_t acc = local & 1, acc_phase = (local >> 1) & 1;
-      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, wait_limit)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint64_t row = (uint64_t)tm * BM + quad * 32 + lane;
       const uint64_t n0 = (uint64_t)tn * TBN;
@@ -245,7 +246,8 @@ cudaError_t launch_gemm_tf32(const GemmArgs& g, void* a_hi, void* a_lo, void* b_
   const bool a_mn = g.a_trans != 0, b_mn = g.b_trans == 0;
   const uint64_t a_rows = a_mn ? g.k : g.m, a_cols = a_mn ? g.m : g.k;
   const uint64_t b_rows = b_mn ? g.k : g.n, b_cols = b_mn ? g.n : g.k;
-  const uint64_t na = a_rows * g.lda, nb = b_rows * g.ldb;
+  // the stored operands end at their last row's last column (a block of a wider matrix does not own the rest of that row)
+  const uint64_t na = (a_rows - 1) * g.lda + a_cols, nb = (b_rows - 1) * g.ldb + b_cols;
   auto grid_for = [](uint64_t n) { uint64_t b = (n / 4 + 255) / 256 + 1; return (unsigned)(b < 148ull * 16 ? b : 148ull * 16); };
   split_tf32_kernel<<<grid_for(na), 256, 0, stream>>>((const uint32_t*)g.a, (uint32_t*)a_hi, (uint32_t*)a_lo, na);
   split_tf32_kernel<<<grid_for(nb), 256, 0, stream>>>((const uint32_t*)g.b, (uint32_t*)b_hi, (uint32_t*)b_lo, nb);
@@ -273,12 +275,8 @@ cudaError_t launch_gemm_tf32(const GemmArgs& g, void* a_hi, void* a_lo, void* b_
   constexpr size_t smem = (size_t)TSTAGES * (2 * BM * 128 + 2 * TBN * 128) + 1024 + 256;
 #define TF_LAUNCH(AM, BMJ)                                                                            \
   do {                                                                                                \
-    static bool attr_set = false;                                                                     \
-    if (!attr_set) {                                                                                  \
-      e = cudaFuncSetAttribute(gemm_tf32_kernel<AM, BMJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-      if (e != cudaSuccess) return e;                                                                 \
-      attr_set = true;                                                                                \
-    }                                                                                                 \
+    e = ensure_dynamic_smem((const void*)gemm_tf32_kernel<AM, BMJ>, smem);                            \
+    if (e != cudaSuccess) return e;                                                                   \
     gemm_tf32_kernel<AM, BMJ><<<grid, NUM_THREADS, smem, stream>>>(maps, p);                          \
   } while (0)
   if (!a_mn && !b_mn) TF_LAUNCH(false, false);

@@ -810,6 +810,10 @@ int32_t b200_full_sum_noalloc(const float* device_values, uint64_t n, int32_t me
     b200::set_global_error(msg);
     return 2;
   }
+  if (n == 0 && mean) {   // 0 / 0: refused rather than a NaN handed back without a word
+    b200::set_global_error("full_sum_noalloc: the mean of no elements is undefined");
+    return 2;
+  }
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
@@ -834,9 +838,16 @@ int32_t b200_full_sum_noalloc(const float* device_values, uint64_t n, int32_t me
     partials = g_partials_addr[dev];
   }
   // Every partial is rewritten before it is read, so the last call's partials do not matter.  The
-  // one word that must start at zero is the ticket after them: it is zero when the library is
-  // loaded and the block that finishes a call puts it back to zero.
+  // one word that must start at zero is the ticket after them.  The block that finishes a call puts
+  // it back to zero, but a launch that died half-way, or two calls that overlapped, can leave it
+  // counting; so it is cleared here, on the caller's stream ahead of the kernel (a memset node, no
+  // allocation), and one bad call cannot spoil the ones after it.
   cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+  e = cudaMemsetAsync(partials + b200::FULL_BLOCKS, 0, 8 * sizeof(float), s);
+  if (e != cudaSuccess) {
+    b200::set_global_error((std::string("full_sum_noalloc: clearing the ticket: ") + cudaGetErrorString(e)).c_str());
+    return 3;
+  }
   b200::full_sum_fused<<<b200::FULL_BLOCKS, b200::FULL_THREADS, 0, s>>>(device_values, n, mean, partials, device_out);
   e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -881,11 +892,9 @@ cudaError_t launch_softmax_rows(const float* x, const uint32_t* mask, uint64_t m
     const unsigned gridw = (unsigned)((rows + workers - 1) / workers < (uint64_t)sms ? (rows + workers - 1) / workers : (uint64_t)sms);
 #define SW(TT)                                                                                                  \
     do {                                                                                                          \
-      static bool attr = false;                                                                                   \
-      if (!attr) {                                                                                                \
-        cudaError_t e = cudaFuncSetAttribute(softmax_workers_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      {                                                                                                           \
+        const cudaError_t e = ensure_dynamic_smem((const void*)softmax_workers_kernel<TT>, smem);                 \
         if (e != cudaSuccess) return e;                                                                           \
-        attr = true;                                                                                              \
       }                                                                                                           \
       softmax_workers_kernel<TT><<<gridw, 512, smem, s>>>(x, mask, mask_rows, scale, log_form, out, out_bf16, rows, (uint32_t)cols); \
     } while (0)

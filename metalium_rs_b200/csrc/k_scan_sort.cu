@@ -240,17 +240,11 @@ cudaError_t scan_go(const uint32_t* in, uint32_t* out, uint64_t rows, uint64_t c
   while (tile_rows > 16 && per_sm * SCAN_SLOTS * tile_rows * 128 > 200 * 1024) tile_rows >>= 1;
   const size_t smem = (size_t)SCAN_SLOTS * tile_rows * 128;
   const bool vec = cols % 4 == 0 && reinterpret_cast<uintptr_t>(in) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
-  if (smem > 48 * 1024) {
-    static size_t set[4] = {0, 0, 0, 0};
-    const int which = (chunks > 1 ? 2 : 0) + (vec ? 1 : 0);
-    if (smem > set[which]) {
-      cudaError_t e = chunks > 1 ? (vec ? cudaFuncSetAttribute(scan_tiled_kernel<OP, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                                        : cudaFuncSetAttribute(scan_tiled_kernel<OP, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem))
-                                 : (vec ? cudaFuncSetAttribute(scan_tiled_kernel<OP, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                                        : cudaFuncSetAttribute(scan_tiled_kernel<OP, 0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      if (e != cudaSuccess) return e;
-      set[which] = smem;
-    }
+  {
+    const void* fn = chunks > 1 ? (vec ? (const void*)scan_tiled_kernel<OP, 2, true> : (const void*)scan_tiled_kernel<OP, 2, false>)
+                                : (vec ? (const void*)scan_tiled_kernel<OP, 0, true> : (const void*)scan_tiled_kernel<OP, 0, false>);
+    const cudaError_t e = ensure_dynamic_smem(fn, smem);
+    if (e != cudaSuccess) return e;
   }
   if (chunks <= 1) {
     if (vec) launch_pdl(scan_tiled_kernel<OP, 0, true>, dim3(strips, 1), dim3(SCAN_THREADS), smem, s, in, out, rows, cols, rows, tile_rows, (const uint32_t*)nullptr);
@@ -388,11 +382,9 @@ cudaError_t launch_sort_planes(const uint32_t* in, uint64_t rows, uint64_t cols,
                                uint32_t* keys, uint32_t* indices, cudaStream_t s) {
   if (rows == 0 || cols == 0) return cudaSuccess;
   const size_t smem = (size_t)8 * (rows + rows / 8) * sizeof(unsigned long long);
-  static size_t set = 0;
-  if (smem > 48 * 1024 && smem > set) {
-    cudaError_t e = cudaFuncSetAttribute(sort_planes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  {
+    const cudaError_t e = ensure_dynamic_smem((const void*)sort_planes_kernel, smem);
     if (e != cudaSuccess) return e;
-    set = smem;
   }
   launch_pdl(sort_planes_kernel, dim3((unsigned)(cols / 32), 4), dim3(SORT_THREADS), smem, s, in, rows, cols, n, is_i32, descending,
              keys, indices);

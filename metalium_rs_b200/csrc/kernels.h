@@ -132,8 +132,13 @@ cudaError_t launch_gemm_simt(const GemmArgs& g, cudaStream_t stream);
 // tcgen05 path.  Returns cudaErrorNotSupported when the shape cannot take it.
 struct TcPlan;  // opaque: tensor maps + grid
 bool gemm_tc_supported(const GemmArgs& g, const char** why);
+// `pair_taken` (may be null) is set when the CTA-pair kernel ran the product.
 cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int* err_word,
-                           cudaStream_t stream);
+                           cudaStream_t stream, int* pair_taken = nullptr);
+// One CTA that waits, with the kernels' bounded wait and the engine's limit, on an mbarrier whose bytes
+// never arrive: the wait runs out, the error word becomes TIMEOUT and the kernel returns.  It exists so
+// the time-out path can be exercised without stalling a real product.
+cudaError_t launch_stalled_wait(int* err_word, cudaStream_t stream);
 
 // A product of at most 4 rows (a decode step's projections): streams B once on CUDA cores.
 bool gemm_skinny_supported(const GemmArgs& g);
@@ -178,5 +183,14 @@ cudaError_t launch_pool_windows(const uint16_t* in, const uint32_t* offsets_dev,
 
 // Text for `b200_last_error(NULL, ...)`: failures of calls that take no engine.
 void set_global_error(const char* text);
+
+// Launch set-up that belongs to a device, not to the process.  A kernel's opt-in to more than 48 KB of
+// dynamic shared memory is an attribute of the function ON ONE DEVICE, and engines on different ordinals
+// may live in one process and be driven from different threads: the launchers ask here before every
+// launch, and the attribute is set once per (current device, kernel, largest size asked so far) under a lock.
+cudaError_t ensure_dynamic_smem(const void* kernel, size_t bytes);
+// An integer a launcher works out once per device (an occupancy figure), kept under the same lock.
+bool device_value_get(const void* key, int* value);
+void device_value_set(const void* key, int value);
 
 }  // namespace b200

@@ -16,7 +16,7 @@ constexpr int BK = 64;            // bf16 elements: one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;  // 6 warps
 constexpr int TIMEOUT_CODE = 4;
-constexpr long long WAIT_CYCLES = 4000000000ll;  // ~2 s: far beyond any healthy wait
+constexpr long long WAIT_CYCLES = 4000000000ll;  // ~2 s: far beyond any healthy wait (the default limit)
 
 struct TcParams {
   uint64_t m, n, k;
@@ -54,15 +54,21 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
+// The engine keeps its wait limit (clock cycles, `b200_config.wait_limit_cycles`) in the two words
+// that follow its device error word; a kernel reads it once.  0 or less: the default.
+__device__ __forceinline__ long long wait_limit_of(const int* err) {
+  const long long v = *reinterpret_cast<const volatile long long*>(err + 2);
+  return v > 0 ? v : WAIT_CYCLES;
+}
 // Bounded wait: false when it ran out (the caller abandons its role).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long limit) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
     for (int i = 0; i < 64; ++i)
       if (mbar_try(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > WAIT_CYCLES) return false;
+    if (clock64() - t0 > limit) return false;
   }
 }
 
@@ -77,14 +83,14 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long limit) {
   if (mbar_test(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
     for (int i = 0; i < 256; ++i)
       if (mbar_test(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > WAIT_CYCLES) return false;
+    if (clock64() - t0 > limit) return false;
   }
 }
 
@@ -321,16 +327,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 inline EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  // a function-local static's initialiser runs once, and other threads wait for it: no caller ever
+  // sees the "tried" state without the pointer
+  static const EncodeTiledFn fn = []() -> EncodeTiledFn {
     void* sym = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
         q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)sym;
-  }
+      return (EncodeTiledFn)sym;
+    return nullptr;
+  }();
   return fn;
 }
 

@@ -78,7 +78,11 @@ class Traffic(C.Structure):
 
 class Config(C.Structure):
     _fields_ = [("f32_matmul_mode", C.c_int32), ("bf16_matmul_mode", C.c_int32), ("pool_limit_bytes", C.c_uint64),
-                ("fail_alloc_at", C.c_int32), ("_pad", C.c_int32)]
+                ("fail_alloc_at", C.c_int32), ("_pad", C.c_int32), ("wait_limit_cycles", C.c_uint64)]
+
+
+class OpStat(C.Structure):  # burn-tt/src/report.rs:27 `OpStat`, reduced (b200_op_stat)
+    _fields_ = [("op", C.c_char * 48), ("calls", C.c_uint64), ("launches", C.c_uint64), ("device_ms", C.c_double)]
 
 
 def library_path() -> Path:
@@ -136,12 +140,12 @@ class CudaEngine:
     """One GPU's engine; the B200 counterpart of `KmdEngine` (server.rs:4071)."""
 
     def __init__(self, device: int = 0, *, f32_matmul_mode: int = 0, bf16_matmul_mode: int = 0,
-                 pool_limit_bytes: int = 0, fail_alloc_at: int = 0, lib=None):
+                 pool_limit_bytes: int = 0, fail_alloc_at: int = 0, wait_limit_cycles: int = 0, lib=None):
         # `lib`: a library handle to use instead of libb200tt.so -- the test suite passes the
         # engine's host logic linked against a host-only stand-in for the CUDA runtime.
         self._lib = _prepare(lib) if lib is not None else load_library()
         self._e = C.c_void_p()
-        cfg = Config(f32_matmul_mode, bf16_matmul_mode, pool_limit_bytes, fail_alloc_at, 0)
+        cfg = Config(f32_matmul_mode, bf16_matmul_mode, pool_limit_bytes, fail_alloc_at, 0, wait_limit_cycles)
         st = self._lib.b200_engine_create(C.c_int32(device), C.byref(cfg), C.byref(self._e))
         if st:
             buf = C.create_string_buffer(1024)
@@ -149,6 +153,7 @@ class CudaEngine:
             self._e = None
             raise TtError(st, buf.value.decode())
         self.device = device
+        self.profiling = False
 
     # -- plumbing ------------------------------------------------------------
     def close(self):
@@ -678,6 +683,49 @@ class CudaEngine:
     def release_trace(self, trace: int):
         self._lib.b200_release_trace(self._e, C.c_uint64(trace))
 
+    def trace_footprint(self, trace: int) -> int:
+        """`trace_footprint` (server.rs:688): the device bytes the trace holds until it is released."""
+        n = C.c_uint64()
+        st = self._lib.b200_trace_footprint(self._e, C.c_uint64(trace), C.byref(n))
+        if st:
+            raise TtError(st, f"no trace {trace}")
+        return n.value
+
+    def trace_ops(self, trace: int):
+        """`trace_ops` (server.rs:664): [(label, kernels)] of the captured ops, in capture order."""
+        n = C.c_uint64()
+        st = self._lib.b200_trace_ops(self._e, C.c_uint64(trace), None, C.c_uint64(0), C.byref(n))
+        if st:
+            raise TtError(st, f"no trace {trace}")
+        rows = (OpStat * max(1, n.value))()
+        self._lib.b200_trace_ops(self._e, C.c_uint64(trace), rows, C.c_uint64(n.value), C.byref(n))
+        return [(rows[i].op.decode(), int(rows[i].launches)) for i in range(n.value)]
+
+    # -- the profile mode (server.rs:672 `profile_mode`, :683 `profile_report`) --------------
+    def profile_mode(self, on: bool):
+        """On: from here every `set_op_label` marks the stream.  Off: waits for the device and returns the table
+        `profile_report` gives."""
+        if on:
+            self._check(self._lib.b200_profile_start(self._e))
+            self.profiling = True
+            return None
+        self.profiling = False
+        self._check(self._lib.b200_profile_stop(self._e))
+        return self.profile_report()
+
+    def profile_report(self):
+        """[{op, calls, launches, device_ms}] by label, in order of first appearance."""
+        n = C.c_uint64()
+        self._check(self._lib.b200_profile_read(self._e, None, C.c_uint64(0), C.byref(n)))
+        rows = (OpStat * max(1, n.value))()
+        self._check(self._lib.b200_profile_read(self._e, rows, C.c_uint64(n.value), C.byref(n)))
+        return [{"op": rows[i].op.decode(), "calls": int(rows[i].calls), "launches": int(rows[i].launches),
+                 "device_ms": float(rows[i].device_ms)} for i in range(n.value)]
+
+    def debug_stalled_wait(self):
+        """Runs a bounded device wait that nothing ends (needs `wait_limit_cycles`): the next wait raises Timeout."""
+        self._check(self._lib.b200_debug_stalled_wait(self._e))
+
     # -- waits and observability (lib.rs:218, server.rs:584,663) ---------------------------
     def sync(self):
         self._check(self._lib.b200_sync(self._e))
@@ -707,7 +755,7 @@ class CudaEngine:
         return self._lib.b200_stream(self._e)
 
 
-__all__ = ["CudaEngine", "TtError", "EltwiseOp", "Block", "BlockMove", "BlockArg", "BatchedLayout", "Traffic",
+__all__ = ["CudaEngine", "TtError", "EltwiseOp", "Block", "BlockMove", "BlockArg", "BatchedLayout", "Traffic", "OpStat",
            "load_library", "library_path", "kinds",
            "F32", "I32", "BOOL", "BF16", "SUM", "MAX", "PROD", "ALL", "ANY", "BITOR", "SUM_I32", "PROD_I32",
            "MIN_I32", "MAX_I32", "ROWS", "COLS"]

@@ -1,6 +1,5 @@
 // Builds libb200tt from metalium_rs_b200/csrc with nvcc for sm_100a and links it statically.
-// Source only: no Rust toolchain exists where this was written; `python -m metalium_rs_b200.build`
-// runs the same nvcc command lines.
+// `python -m metalium_rs_b200.build` runs the same nvcc command lines where there is no cargo.
 fn main() {
     let out = std::path::PathBuf::from(std::env::var("OUT_DIR").unwrap());
     let csrc = std::path::Path::new("../../csrc");

@@ -1,12 +1,13 @@
 //! Raw FFI of libb200tt (include/b200tt.h), one declaration per C function.
 //! Generated from the header; the header's comments name the `burn_tt::Engine` method
 //! (crates/burn-tt/src/server.rs) each function stands in for.
-//! Not compiled where it was written (no Rust toolchain there).
+//! Shipped as source: it has not met a Rust compiler.
 #![allow(non_camel_case_types)]
 use std::os::raw::{c_char, c_void};
 
 #[repr(C)] pub struct b200_engine { _private: [u8; 0] }
-#[repr(C)] #[derive(Clone, Copy, Default)] pub struct b200_config { pub f32_matmul_mode: i32, pub bf16_matmul_mode: i32, pub pool_limit_bytes: u64, pub fail_alloc_at: i32, pub _pad: i32 }
+#[repr(C)] #[derive(Clone, Copy, Default)] pub struct b200_config { pub f32_matmul_mode: i32, pub bf16_matmul_mode: i32, pub pool_limit_bytes: u64, pub fail_alloc_at: i32, pub _pad: i32, pub wait_limit_cycles: u64 }
+#[repr(C)] #[derive(Clone, Copy)] pub struct b200_op_stat { pub op: [c_char; 48], pub calls: u64, pub launches: u64, pub device_ms: f64 }
 #[repr(C)] #[derive(Clone, Copy)] pub struct b200_eltwise_op { pub kind: u32, pub scalar: f32, pub scalar2: f32 }
 #[repr(C)] #[derive(Clone, Copy)] pub struct b200_block { pub at: [u64; 2], pub transposed: i32, pub _pad: i32 }
 #[repr(C)] #[derive(Clone, Copy)] pub struct b200_attention_block { pub q: [u64; 2], pub k: [u64; 2], pub v: [u64; 2], pub o: [u64; 2] }
@@ -98,6 +99,12 @@ extern "C" {
     pub fn b200_end_trace(a0: *mut b200_engine, trace: *mut u64) -> i32;
     pub fn b200_run_trace(a0: *mut b200_engine, trace: u64) -> i32;
     pub fn b200_release_trace(a0: *mut b200_engine, trace: u64);
+    pub fn b200_trace_footprint(a0: *const b200_engine, trace: u64, bytes: *mut u64) -> i32;
+    pub fn b200_trace_ops(a0: *const b200_engine, trace: u64, out: *mut b200_op_stat, capacity: u64, n: *mut u64) -> i32;
+    pub fn b200_profile_start(a0: *mut b200_engine) -> i32;
+    pub fn b200_profile_stop(a0: *mut b200_engine) -> i32;
+    pub fn b200_profile_read(a0: *const b200_engine, out: *mut b200_op_stat, capacity: u64, n: *mut u64) -> i32;
+    pub fn b200_debug_stalled_wait(a0: *mut b200_engine) -> i32;
     pub fn b200_sync(a0: *mut b200_engine) -> i32;
     pub fn b200_set_op_label(a0: *mut b200_engine, label: *const c_char);
     pub fn b200_traffic_get(a0: *const b200_engine, out: *mut b200_traffic);

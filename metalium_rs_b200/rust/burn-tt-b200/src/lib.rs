@@ -3,7 +3,8 @@
 //! `burn_tt::attach(TtDevice::new(0), cuda_factory(0))` (server.rs:2738) or make it the default
 //! with `burn_tt::set_default_engine` (registry.rs:212); nothing above the trait changes.
 //!
-//! Source only: no Rust toolchain exists where this was written, so it has not been compiled.
+//! Shipped as source: it has not met a Rust compiler.  A test holds every method of the `impl` below to the
+//! trait's parameter and result types by parsing both.
 //! Every method is one call of include/b200tt.h through `b200-sys`.
 use b200_sys as sys;
 use burn_tt::server::{BlockArg, BufferId, Engine, GenericTraceRun, InputPayload, OutputKind, OutputPayload, PowArg, Serve,
@@ -78,6 +79,48 @@ impl CudaEngine {
         }
         Ok(([d[0] as usize, d[1] as usize], e))
     }
+}
+
+/// What the trait's `trace_footprint`, `trace_ops`, `profile_mode` and `profile_report` (server.rs:664-688) would
+/// carry, in this engine's own terms: those methods return Tensix records (`UnitFootprint`, `OpRecord`,
+/// `Profile`), so they keep the trait's defaults and the figures are offered beside the trait.
+impl CudaEngine {
+    /// Device bytes `trace` holds until it is released.
+    pub fn trace_bytes(&self, trace: u64) -> Result<u64, TtError> {
+        let mut n = 0u64;
+        match unsafe { sys::b200_trace_footprint(self.raw, trace, &mut n) } {
+            0 => Ok(n),
+            _ => Err(TtError::Device(format!("no trace {trace}"))),
+        }
+    }
+    /// The ops `trace` captured, in order: (label, kernels).
+    pub fn trace_labels(&self, trace: u64) -> Result<Vec<(String, u64)>, TtError> {
+        let mut n = 0u64;
+        if unsafe { sys::b200_trace_ops(self.raw, trace, std::ptr::null_mut(), 0, &mut n) } != 0 {
+            return Err(TtError::Device(format!("no trace {trace}")));
+        }
+        let mut rows = vec![unsafe { std::mem::zeroed::<sys::b200_op_stat>() }; n as usize];
+        unsafe { sys::b200_trace_ops(self.raw, trace, rows.as_mut_ptr(), n, &mut n) };
+        Ok(rows.iter().map(|r| (label_of(r), r.launches)).collect())
+    }
+    /// Per-op device time: on, then off with the table (label, calls, kernels, ms).
+    pub fn profile_start(&mut self) -> Result<(), TtError> {
+        let st = unsafe { sys::b200_profile_start(self.raw) };
+        self.check(st)
+    }
+    pub fn profile_stop(&mut self) -> Result<Vec<(String, u64, u64, f64)>, TtError> {
+        let st = unsafe { sys::b200_profile_stop(self.raw) };
+        self.check(st)?;
+        let mut n = 0u64;
+        unsafe { sys::b200_profile_read(self.raw, std::ptr::null_mut(), 0, &mut n) };
+        let mut rows = vec![unsafe { std::mem::zeroed::<sys::b200_op_stat>() }; n as usize];
+        unsafe { sys::b200_profile_read(self.raw, rows.as_mut_ptr(), n, &mut n) };
+        Ok(rows.iter().map(|r| (label_of(r), r.calls, r.launches, r.device_ms)).collect())
+    }
+}
+fn label_of(r: &sys::b200_op_stat) -> String {
+    let bytes: Vec<u8> = r.op.iter().take_while(|c| **c != 0).map(|c| *c as u8).collect();
+    String::from_utf8_lossy(&bytes).into_owned()
 }
 
 fn elem_code(elem: Elem, bf16: bool) -> i32 {

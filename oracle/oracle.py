@@ -2,8 +2,8 @@
 
 A NumPy (plus C, oracle.c) restatement of what the reference's device path is held to by
 its CPU comparison backend.  That backend (burn-flex `=0.21.0`, Cargo.toml:46) and the
-reference itself (Rust; crates.io dependencies not vendored) cannot be built or run where
-this was written, so parity against burn-flex's own output bits is UNPINNED.  What pins
+reference itself (Rust; crates.io dependencies not vendored) need a Rust toolchain and a
+package index to build, so parity against burn-flex's own output bits is UNPINNED.  What pins
 this oracle are the closed-form known-answer cases the reference's tests hold for the
 path (tests/test_oracle_kats.py lists them with file:line).
 

@@ -28,13 +28,21 @@ extern uint64_t fake_cuda_memory_limit;   // bytes cudaMalloc may hand out in to
 extern uint64_t fake_cuda_memory_in_use;
 extern int fake_cuda_device_count;
 extern int fake_cuda_capturing;
+extern int fake_cuda_current_device;
+extern int fake_smem_attr_calls[8];       // cudaFuncSetAttribute calls, by the device that was current
 }
+enum cudaFuncAttribute { cudaFuncAttributeMaxDynamicSharedMemorySize = 8 };
 
 static inline const char* cudaGetErrorString(cudaError_t e) {
   return e == cudaSuccess ? "no error" : (e == cudaErrorMemoryAllocation ? "out of memory" : "fake CUDA error");
 }
 static inline cudaError_t cudaGetLastError() { return cudaSuccess; }
-static inline cudaError_t cudaSetDevice(int) { return cudaSuccess; }
+static inline cudaError_t cudaSetDevice(int d) { fake_cuda_current_device = d; return cudaSuccess; }
+static inline cudaError_t cudaGetDevice(int* d) { *d = fake_cuda_current_device; return cudaSuccess; }
+static inline cudaError_t cudaFuncSetAttribute(const void*, cudaFuncAttribute, int) {
+  if (fake_cuda_current_device >= 0 && fake_cuda_current_device < 8) ++fake_smem_attr_calls[fake_cuda_current_device];
+  return cudaSuccess;
+}
 static inline cudaError_t cudaGetDeviceCount(int* n) { *n = fake_cuda_device_count; return cudaSuccess; }
 static inline cudaError_t cudaGetDeviceProperties(cudaDeviceProp* p, int) {
   strcpy(p->name, "fake B200"); p->major = 10; p->minor = 0; return cudaSuccess;

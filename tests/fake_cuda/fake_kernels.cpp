@@ -10,6 +10,8 @@ uint64_t fake_cuda_memory_limit = 0;
 uint64_t fake_cuda_memory_in_use = 0;
 int fake_cuda_device_count = 1;
 int fake_cuda_capturing = 0;
+int fake_cuda_current_device = 0;
+int fake_smem_attr_calls[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 int fake_launch_count = 0;        // launches the engine asked for
 int fake_tc_supported = 1;        // what gemm_tc_supported answers for BF16 operands
 int fake_last_attention_jobs = 0; // jobs of the last attention_rows launch
@@ -69,7 +71,15 @@ bool gemm_tc_supported(const GemmArgs& g, const char** why) {
   *why = g.in_bf16 ? "the fake runtime was told to refuse" : "operands are not BF16";
   return g.in_bf16 && fake_tc_supported;
 }
-cudaError_t launch_gemm_tc(const GemmArgs&, const GemmBatch*, int*, cudaStream_t) { OK_LAUNCH; }
+// as the real launcher does: the kernel's shared-memory opt-in is asked for on the current device before the launch
+static void fake_tc_kernel() {}
+cudaError_t launch_gemm_tc(const GemmArgs&, const GemmBatch*, int*, cudaStream_t, int* pair) {
+  if (pair) *pair = 0;
+  const cudaError_t e = ensure_dynamic_smem((const void*)fake_tc_kernel, 200 * 1024);
+  if (e != cudaSuccess) return e;
+  OK_LAUNCH;
+}
+cudaError_t launch_stalled_wait(int*, cudaStream_t) { OK_LAUNCH; }
 bool gemm_tc2_wanted(const GemmArgs&) { return false; }
 cudaError_t launch_gemm_tc2(const GemmArgs&, int*, cudaStream_t) { OK_LAUNCH; }
 bool gemm_tf32_supported(const GemmArgs& g, const char** why) { *why = "small"; return !g.in_bf16 && g.batch <= 1 && g.m >= 128 && g.n >= 128 && g.k >= 32; }

@@ -35,7 +35,8 @@ def test_struct_layouts_match_the_header():
     assert ctypes.sizeof(engine.BlockArg) == 40
     assert ctypes.sizeof(engine.BatchedLayout) == 8
     assert ctypes.sizeof(engine.Traffic) == 64
-    assert ctypes.sizeof(engine.Config) == 24
+    assert ctypes.sizeof(engine.Config) == 32
+    assert ctypes.sizeof(engine.OpStat) == 72
 
 
 def test_create_without_a_device_is_refused_not_faked(lib):
@@ -77,3 +78,27 @@ def test_the_rust_shim_sources_follow_the_header_and_the_build():
     build_rs = (root / "metalium_rs_b200" / "rust" / "b200-sys" / "build.rs").read_text()
     for src in build.SOURCES:
         assert f'"{src}"' in build_rs, src
+
+
+def test_the_rust_shim_overrides_only_trait_methods_with_the_trait_s_signatures():
+    # No Rust compiler here, so the shim's `impl Engine for CudaEngine` is held to the trait by text: every method
+    # it defines is a method of `pub trait Engine` (crates/burn-tt/src/server.rs:42-786) with the same parameter
+    # types and result type.  tests/golden/engine_trait.json is the trait's method list (made by
+    # tests/golden/make_trait_signatures.py); where the reference tree is mounted the list is re-derived too.
+    import json
+    from tests.golden.make_trait_signatures import block_after, signatures, trait_signatures
+    trait = json.loads((ROOT / "tests" / "golden" / "engine_trait.json").read_text())
+    reference = Path("/root/reference")
+    if (reference / "crates" / "burn-tt" / "src" / "server.rs").exists():
+        assert trait_signatures(reference) == trait, "engine_trait.json is stale: run tests/golden/make_trait_signatures.py"
+    shim = (ROOT / "metalium_rs_b200" / "rust" / "burn-tt-b200" / "src" / "lib.rs").read_text()
+    impl = signatures(block_after(shim, r"impl Engine for CudaEngine"))
+    alias = {"Made": "Result<(BufferId,[usize;2]),TtError>"}          # the shim's `type Made`
+    assert len(impl) >= 60
+    for name, sig in impl.items():
+        assert name in trait, f"{name} is not a method of the trait"
+        assert sig["params"] == trait[name]["params"], (name, sig["params"], trait[name]["params"])
+        assert alias.get(sig["ret"], sig["ret"]) == trait[name]["ret"], (name, sig["ret"], trait[name]["ret"])
+    # the required method and the capability probes are there (server.rs:53,70,75,240)
+    for name in ("matmul", "supports_dram", "supports_batched_layout", "supports_exact_matmul"):
+        assert name in impl
