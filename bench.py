@@ -5,6 +5,10 @@
 
 N = 1: one step is one 8192^3 BF16 product (FP32 accumulate, BF16 result) on operands
 resident in HBM, launched through `matmul_dram_bf16`; `value` is 2*8192^3*K / device time.
+The same line carries the rest of the metric: `prefill` (the SmolLM2-135M-shape prefill of
+8 x 512 tokens as a replayed trace: tokens/s, launches, a per-op-class table) and `suite` (the
+memory-bound ops on [8192, 8192] F32 and the row softmax on [4096, 32768]: GB/s of algorithmic
+bytes), each with its own `roofline`.
 N > 1 (under torchrun, one rank a GPU): the 16384^3 product split along N with K whole
 (crates/tt-kernels/src/shard.rs:348-458), every rank computing its column slice and an
 NCCL all-gather leaving the full C on every rank; time is the max over ranks.
@@ -138,48 +142,87 @@ def cheap_bf16(shape, seed):
 
 
 # ---------------------------------------------------------------------- CPU baseline
-def cpu_gemm_baseline(target_seconds=12.0):
-    """The CPU restatement's F32 product of BF16-rounded operands on all host cores, on a
-    bounded sample (the same product at a smaller size), as TFLOP/s."""
+CPU_BUDGET_S = 60.0     # a configuration the restatement finishes within this is run whole; beyond it, a smaller sample
+
+
+def _cpu_product(n):
+    """One n^3 F32 product of BF16-rounded operands by the C/OpenMP restatement; seconds."""
     from oracle import oracle as orc
-    orc.clib().orc_set_threads(os.cpu_count() or 1)  # a launcher may have set OMP_NUM_THREADS=1
-    cores = orc.clib().orc_threads()
-    n = 1024
     a = orc.from_bf16(cheap_bf16((n, n), 1))
     b = orc.from_bf16(cheap_bf16((n, n), 2))
     t0 = time.perf_counter()
     orc.gemm_f32(a, b)
-    dt = time.perf_counter() - t0
-    rate = 2.0 * n ** 3 / dt
-    # grow the sample towards the target time (cubic cost), capped at 4096
-    n2 = int(min(4096, max(1024, (rate * target_seconds / 2.0) ** (1.0 / 3.0)) // 256 * 256))
-    if n2 > n:
-        a = orc.from_bf16(cheap_bf16((n2, n2), 1))
-        b = orc.from_bf16(cheap_bf16((n2, n2), 2))
+    return time.perf_counter() - t0
+
+
+def cpu_plan(size):
+    """(threads, n): the size the restatement is timed at -- `size` itself when a 1024^3 probe says it fits the
+    budget, else the largest multiple of 256 that does."""
+    from oracle import oracle as orc
+    orc.clib().orc_set_threads(os.cpu_count() or 1)  # a launcher may have set OMP_NUM_THREADS=1
+    cores = int(orc.clib().orc_threads())
+    _cpu_product(512)                                   # first touch: thread pool, page faults
+    rate = 2.0 * 1024 ** 3 / _cpu_product(1024)
+    fits = int((rate * CPU_BUDGET_S / 2.0) ** (1.0 / 3.0)) // 256 * 256
+    return cores, max(1024, min(size, fits))
+
+
+def torch_cpu_column(n):
+    """The same product by torch on the host cores (oneDNN / MKL, its own threads): a second CPU column, so the
+    restatement's plain loops are not the only CPU figure beside the GPU's."""
+    try:
+        import torch
+        threads = torch.get_num_threads()
+        a = torch.from_numpy((cheap_bf16((n, n), 1).astype(np.uint32) << 16).view(np.float32))
+        b = torch.from_numpy((cheap_bf16((n, n), 2).astype(np.uint32) << 16).view(np.float32))
+        torch.matmul(a[:512, :512], b[:512, :512])
         t0 = time.perf_counter()
-        orc.gemm_f32(a, b)
+        torch.matmul(a, b)
         dt = time.perf_counter() - t0
-        n = n2
-    return {"value": 2.0 * n ** 3 / dt / 1e12, "unit": UNIT, "cores": int(cores), "kind": "port",
-            "sample": f"{n}^3 F32 product of BF16-rounded operands (C/OpenMP restatement), {dt:.2f} s"}
+        return {"value": 2.0 * n ** 3 / dt / 1e12, "unit": UNIT, "threads": int(threads), "sample": f"{n}^3 F32 torch.matmul, {dt:.2f} s"}
+    except Exception as ex:   # a column, not the baseline: its absence is reported, not fatal
+        return {"unavailable": str(ex)[:120]}
+
+
+def cpu_gemm_baseline(size=N1_SIZE, repeats=1, with_torch=True):
+    """The CPU restatement's F32 product of BF16-rounded operands on all host cores: the benchmark's own size when
+    that fits the budget, else a smaller sample named in `sample` and `n`.  Median of `repeats` runs."""
+    cores, n = cpu_plan(size)
+    times = sorted(_cpu_product(n) for _ in range(max(1, repeats)))
+    dt = times[len(times) // 2]
+    out = {"value": 2.0 * n ** 3 / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port", "n": n,
+           "sample": f"{n}^3 F32 product of BF16-rounded operands (C/OpenMP restatement of the comparison backend's "
+                     f"arithmetic; not burn-flex itself), median of {len(times)} run(s), {dt:.2f} s"
+                     + ("" if n == size else f"; the {size}^3 product would not fit {CPU_BUDGET_S:.0f} s")}
+    if with_torch:
+        out["torch_cpu"] = torch_cpu_column(min(n, 4096))
+    return out
 
 
 def run_reference(args):
+    """The CPU arm: the restatement of the reference's comparison backend on the host cores, at the GPU arm's size
+    when that fits the budget (the size actually run is in `config`).  A step is one whole product; as many of the
+    requested steps are run as fit about two and a half minutes, and `steps` says how many that was."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    vals = []
-    base = None
-    for _ in range(max(1, min(args.steps, 3))):
-        base = cpu_gemm_baseline(target_seconds=8.0)
-        vals.append(base["value"])
-    v = float(np.mean(vals))
-    base["value"] = v
-    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+    size = args.size or (N1_SIZE if args.gpus == 1 else NN_SIZE)
+    cores, n = cpu_plan(size)
+    first = _cpu_product(n)
+    steps = max(1, min(args.steps, int(150.0 / max(first, 1e-3))))
+    times = sorted([first] + [_cpu_product(n) for _ in range(steps - 1)])
+    dt = times[len(times) // 2]
+    v = 2.0 * n ** 3 / dt / 1e12
+    base = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "n": n,
+            "sample": f"{n}^3 F32 product of BF16-rounded operands, median of {steps} whole products, {dt:.2f} s each",
+            "torch_cpu": torch_cpu_column(min(n, 4096))}
+    name = workload_name(args.gpus) if n == size else f"bf16 gemm {n}^3 (a sample: the {size}^3 product does not fit {CPU_BUDGET_S:.0f} s of CPU time)"
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+            "steps_requested": args.steps, "warmup": 1, "ms_per_step": dt * 1e3, "higher_is_better": True,
             "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": workload_name(args.gpus), "note": "CPU restatement of the reference's comparison backend "
-                       "(burn-flex is not in the reference tree); bounded sample, see cpu_baseline.sample"},
+            "config": {"workload": name, "m": n, "n": n, "k": n,
+                       "note": "CPU restatement of the reference's comparison backend (burn-flex is not in the reference "
+                               "tree and the reference itself is Rust for Tenstorrent cards); see cpu_baseline.sample"},
             "cpu_baseline": base,
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
@@ -192,6 +235,31 @@ def workload_name(n_gpus):
 
 
 # ---------------------------------------------------------------------- GPU arm
+REPEATS = 9   # the reference's median-of-nine convention (docs/learnings/performance-scoreboard.md:24)
+
+
+def make_timed(eng):
+    """timed(fn, reps, warm, repeats) -> median over `repeats` of (device ms of `reps` back-to-back calls) / reps,
+    CUDA events on the engine's stream, after `warm` untimed calls."""
+    def timed(fn, reps=20, warm=3, repeats=1):
+        for _ in range(warm):
+            fn()
+        eng.sync()
+        got = []
+        for _ in range(max(1, repeats)):
+            eng.timer_start()
+            for _ in range(reps):
+                fn()
+            got.append(eng.timer_stop() / reps)
+        got.sort()
+        return got[len(got) // 2]
+    return timed
+
+
+def bf16_value(bits):
+    return (np.asarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
 def run_single(args):
     import torch
     from metalium_rs_b200 import CudaEngine, build
@@ -212,21 +280,6 @@ def run_single(args):
     for _ in range(max(args.warmup, 3)):
         step()
     eng.sync()
-    # a quick validity check of the timed kernel's output (64 samples against F64 dots)
-    out, _ = eng.matmul_dram(ia, False, ib, False)
-    c = eng.download(out)
-    eng.free(out)
-    af = (a_host.numpy().view(np.uint16).astype(np.uint32) << 16).view(np.float32)
-    bf = (b_host.numpy().view(np.uint16).astype(np.uint32) << 16).view(np.float32)
-    rng = np.random.default_rng(0)
-    worst = 0.0
-    for i, j in zip(rng.integers(0, n, 64), rng.integers(0, n, 64)):
-        t = af[i].astype(np.float64) @ bf[:, j].astype(np.float64)
-        s = np.abs(af[i]).astype(np.float64) @ np.abs(bf[:, j]).astype(np.float64)
-        worst = max(worst, abs(float(c[i, j]) - t) / s)
-    if worst > 1e-5:
-        raise SystemExit(f"bench: the timed kernel's output is wrong (error / S = {worst:.3e})")
-    del c
 
     launches0 = eng.device_traffic().launches
     sampler = ClockSampler(0)
@@ -239,6 +292,32 @@ def run_single(args):
     launches = eng.device_traffic().launches - launches0
     ms_per_step = ms / args.steps
     value = flops / (ms_per_step * 1e-3) / 1e12
+    path = eng.last_matmul_path()
+    # the same region eight more times: the median of nine, beside the one region `value` is taken from
+    rep = [ms_per_step]
+    for _ in range(REPEATS - 1):
+        eng.timer_start()
+        for _ in range(args.steps):
+            step()
+        rep.append(eng.timer_stop() / args.steps)
+    rep.sort()
+
+    # validity: the BF16 result of the very call the loop times, 64 sampled elements against F64 dot products --
+    # within one BF16 step of the truth plus the F32 sum's rounding
+    out, _ = eng.matmul_dram_bf16(ia, False, ib, False)
+    c = eng.download_bf16(out)
+    eng.free(out)
+    af, bf = bf16_value(a_host.numpy().view(np.uint16)), bf16_value(b_host.numpy().view(np.uint16))
+    rng = np.random.default_rng(0)
+    worst = 0.0
+    for i, j in zip(rng.integers(0, n, 64), rng.integers(0, n, 64)):
+        t = af[i].astype(np.float64) @ bf[:, j].astype(np.float64)
+        s = np.abs(af[i]).astype(np.float64) @ np.abs(bf[:, j]).astype(np.float64)
+        got = float(bf16_value(c[i, j]))
+        if abs(got - t) > 2.0 ** -8 * abs(t) + 1e-5 * s:
+            raise SystemExit(f"bench: the timed kernel's output is wrong at ({i}, {j}): {got} against {t}")
+        worst = max(worst, abs(got - t) / s)
+    del c
 
     # end to end through the C ABI with host buffers: one call of the host-staged BF16 product
     # (`b200_matmul_host_bf16`: A and B read from pinned host memory, C written to it, the copies overlapped
@@ -258,56 +337,191 @@ def run_single(args):
         for i, j in zip(rng2.integers(0, n, 16), rng2.integers(0, n, 16)):
             t = af[i].astype(np.float64) @ bf[:, j].astype(np.float64)
             s = np.abs(af[i]).astype(np.float64) @ np.abs(bf[:, j]).astype(np.float64)
-            v = float((np.uint32(got[i, j]) << 16).view(np.float32))
+            v = float(bf16_value(got[i, j]))
             if abs(v - t) > 2.0 ** -8 * abs(t) + 1e-5 * s:
                 raise SystemExit(f"bench: the end-to-end product's output is wrong at ({i}, {j}): {v} against {t}")
         e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": 2 * n * n * 2,
                "d2h_bytes_per_step": n * n * 2, "ms_per_step": e2e_ms,
                "call": "b200_matmul_host_bf16 (pinned host A, B -> pinned host C; wall clock around the call)"}
+    eng.free(ia); eng.free(ib)
+    del af, bf
 
     pk, which = peaks()
     peak = float(pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
-    # traffic: dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch, from the ncu capture
-    # summarised in profiles/gemm_tc2_bf16_8192.md (1,274.3 MB + 252.4 MB); null at other sizes
+    # traffic: dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch of this kernel under ncu (1,274.3 MB
+    # read + 252.4 MB written); it cannot be measured inside a timed run, and is null at other sizes
     traffic = 1274306000 + 252358000 if n == N1_SIZE else None
     roofline = {"bound": "tensor", "kernel": "gemm_tc2_kernel<K-major A, MN-major B> (CTA pairs, 256x256 tiles)",
                 "achieved": value, "peak": peak, "unit": UNIT, "frac": value / peak,
                 "peak_source": f"{which} cuBLAS bf16 burst", "frac_of_nominal_2250": value / 2250.0,
-                "algorithmic_flops_per_launch": flops, "traffic": traffic, "traffic_unit": "bytes per launch"}
+                "algorithmic_flops_per_launch": flops, "traffic": traffic, "traffic_unit": "bytes per launch",
+                "traffic_source": "an ncu capture of one launch of this kernel at this size (not measured in this run)"}
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": workload_name(1) if n == N1_SIZE else f"bf16 gemm {n}^3", "m": n, "n": n, "k": n,
                        "l2": "operands and result (403 MB at 8192^3) exceed the 126 MB L2; no flush needed",
-                       "path": eng.last_matmul_path()},
+                       "path": path},
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
-            "validated": {"samples": 64, "max_err_over_S": worst}}
-    if args.extras:
-        from metalium_rs_b200 import CudaEngine as _E
-        with _E(0) as auto_eng:  # automatic path choice: small and ragged products take the SIMT kernel
-            line["extras"] = extras(auto_eng)
-    if not args.no_cpu:
-        line["cpu_baseline"] = cpu_gemm_baseline()
-    print(json.dumps(line))
+            "repeats": {"n": REPEATS, "steps_each": args.steps, "median_ms_per_step": rep[len(rep) // 2], "min_ms_per_step": rep[0],
+                        "max_ms_per_step": rep[-1], "median_tflops": flops / (rep[len(rep) // 2] * 1e-3) / 1e12},
+            "validated": {"samples": 64, "max_err_over_S": worst, "what": "the BF16 result of the timed call"}}
     eng.close()
+    from metalium_rs_b200 import CudaEngine as _E
+    with _E(0) as auto_eng:  # automatic path choice: small and ragged products take the SIMT kernel
+        timed = make_timed(auto_eng)
+        if not args.no_suite:
+            line["suite"] = suite_leg(auto_eng, timed)
+        if not args.no_prefill:
+            line["prefill"] = prefill_leg(auto_eng, timed)
+        if args.extras:
+            line["extras"] = extras(auto_eng, timed)
+    if not args.no_cpu:
+        line["cpu_baseline"] = cpu_gemm_baseline(n)
+    print(json.dumps(line))
 
 
-def extras(eng):
-    """The other sizes of the sweep and the memory-bound suite, timed the same way."""
+def suite_leg(eng, timed):
+    """The memory-bound suite at its stated sizes: unary and broadcast-row kinds and the sums on [8192, 8192] F32, the
+    row softmax on [4096, 32768].  GB/s of algorithmic bytes (what the op must read and write once), medians of nine
+    repeats of twenty launches; operands (268 MB and up) exceed L2."""
     from metalium_rs_b200 import COLS, SUM, EltwiseOp, kinds
-    pk, _ = peaks()
+    pk, which = peaks()
     hbm = float(pk.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
-    out = {"gemm_bf16": {}, "gemm_f32": {}, "suite": {}}
+    res = {}
+    rows = cols = 8192
+    rng = np.random.default_rng(3)
+    x = eng.upload(rng.random((rows, cols), dtype=np.float32) * 3.99 + 0.01, rows, cols)
+    row = eng.upload(rng.random((1, cols), dtype=np.float32) + 0.5, 1, cols)
+    nbytes = rows * cols * 4
 
-    def timed(fn, reps=20, warm=3):
-        for _ in range(warm):
-            fn()
-        eng.sync()
-        eng.timer_start()
-        for _ in range(reps):
-            fn()
-        return eng.timer_stop() / reps
+    def entry(name, fn, algo_bytes, kernel):
+        ms = timed(fn, reps=20, warm=3, repeats=REPEATS)
+        gbs = algo_bytes / ms / 1e6
+        res[name] = {"ms": ms, "gbs": gbs,
+                     "roofline": {"bound": "hbm", "kernel": kernel, "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
+                                  "peak_source": f"{which} copy bandwidth", "frac_of_nominal_8000": gbs / 8000.0,
+                                  "algorithmic_bytes_per_launch": algo_bytes}}
 
+    for name, k, b in (("exp", kinds.EXP, None), ("log", kinds.LOG, None), ("recip", kinds.RECIP, None),
+                       ("sqrt", kinds.SQRT, None), ("relu", kinds.RELU, None), ("gelu_tanh", kinds.GELU_TANH, None),
+                       ("silu", kinds.SILU, None), ("add_row", kinds.ADD, row), ("mul_row", kinds.MUL, row),
+                       ("div_row", kinds.DIV, row)):
+        def f(k=k, b=b):
+            o, _ = eng.eltwise_op(EltwiseOp(k, 0, 0), x, b)
+            eng.free(o)
+        entry(name, f, 2 * nbytes + (cols * 4 if b else 0), "elt_vec4")
+
+    def fs():
+        o, _ = eng.full_sum(x)
+        eng.free(o)
+    entry("full_sum", fs, nbytes + 4, "full_sum_fused")
+
+    def fr():
+        o, _ = eng.reduce(x, SUM, COLS)
+        eng.free(o)
+    entry("row_sum", fr, nbytes + rows * 4, "reduce_cols_kernel")
+    # spot validity of what was timed: exp and the full sum against NumPy on the same data
+    o, _ = eng.eltwise_op(EltwiseOp(kinds.EXP, 0, 0), x)
+    xe = eng.download(x)[:8]
+    if np.max(np.abs(eng.download(o)[:8] / np.exp(xe.astype(np.float64)) - 1.0)) > 1e-5:
+        raise SystemExit("bench: the timed exp is wrong")
+    eng.free(o)
+    o, _ = eng.full_sum(x)
+    total = float(eng.download(o)[0, 0])
+    eng.free(o)
+    exact = float(eng.download(x).astype(np.float64).sum())
+    if abs(total - exact) > 1e-5 * abs(exact):
+        raise SystemExit(f"bench: the timed full sum is wrong: {total} against {exact}")
+    eng.free(x); eng.free(row)
+    srows, scols = 4096, 32768
+    sx = eng.upload(rng.random((srows, scols), dtype=np.float32) * 8 - 4, srows, scols)
+
+    def fm():
+        o, _ = eng.softmax_rows(sx, None, 1.0)
+        eng.free(o)
+    entry("softmax_4096x32768", fm, 2 * srows * scols * 4, "softmax_workers_kernel<512>")
+    o, _ = eng.softmax_rows(sx, None, 1.0)
+    sums = eng.download(o)[:16].astype(np.float64).sum(1)
+    if np.max(np.abs(sums - 1.0)) > 1e-5:
+        raise SystemExit("bench: the timed softmax's rows do not sum to one")
+    eng.free(o); eng.free(sx)
+    return res
+
+
+OP_CLASSES = {"projections": ("projection qkv", "projection o", "projection gate|up", "projection down"),
+              "attention": ("attention",), "norms": ("norm", "add + norm"), "rope": ("rope",),
+              "element-wise": ("silu_mul",), "head": ("head",), "embedding": ("embedding",)}
+
+
+def prefill_leg(eng, timed):
+    """The SmolLM2-135M-shape prefill: 30 layers, 8 sequences of 512 tokens, BF16 weights N(0, 0.02), last-position
+    logits and their argmax.  Timed as the replay of its trace (the reference's fastest mode); the eager pass gives
+    the launch count and, under the engine's profile mode, device time by op class.  The logits are held to the
+    committed sample of the CPU restatement's (2e-2; the argmax where its margin is clear)."""
+    from metalium_rs_b200 import I32, workloads as W
+    pk, which = peaks()
+    peak = float(pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    cfg = W.LlamaConfig()
+    batch, seq = 8, 512
+    model = W.LlamaPrefill(eng, cfg, W.llama_weights(cfg), batch, seq)
+    ids_host = W.prefill_ids(cfg, batch, seq)
+    ids = eng.upload_bits(ids_host.view(np.uint32), 1, batch * seq, I32)
+    l0 = eng.device_traffic().launches
+    lg, am = model.forward(ids)
+    per = eng.device_traffic().launches - l0
+    eager_logits, eager_am = eng.download(lg), eng.download_bits(am).view(np.int32).ravel()
+    eng.free(lg); eng.free(am)
+
+    def fwd():
+        a, b = model.forward(ids)
+        eng.free(a); eng.free(b)
+    eager_ms = timed(fwd, reps=5, warm=2, repeats=3)
+    # device time by op class: one eager pass with every op under its class's label
+    eng.profile_mode(True)
+    fwd()
+    table = eng.profile_mode(False)
+    by_label = {r["op"]: r for r in table}
+    classes = {}
+    for cls, labels in OP_CLASSES.items():
+        rows = [by_label[x] for x in labels if x in by_label]
+        classes[cls] = {"ms": sum(r["device_ms"] for r in rows), "launches": int(sum(r["launches"] for r in rows))}
+    total = sum(v["ms"] for v in classes.values())
+    for v in classes.values():
+        v["share"] = v["ms"] / total if total else 0.0
+    tlg, tam = model.capture(ids)
+    tms = timed(model.replay, reps=10, warm=2, repeats=REPEATS)
+    traced_logits, traced_am = eng.download(tlg), eng.download_bits(tam).view(np.int32).ravel()
+    footprint = eng.trace_footprint(model.trace)
+    eng.release_trace(model.trace); eng.free(tlg); eng.free(tam); eng.free(ids)
+    if not np.array_equal(traced_logits.view(np.uint32), eager_logits.view(np.uint32)) or not np.array_equal(traced_am, eager_am):
+        raise SystemExit("bench: the replayed prefill's logits differ from the eager pass's")
+    validated = {"replay_equals_eager_bits": True}
+    gold_path = ROOT / "tests" / "golden" / "llama_prefill_8x512.npz"
+    if gold_path.exists():
+        gold = np.load(gold_path)
+        if int(gold["ids_checksum"][0]) == int(ids_host.astype(np.int64).sum()):
+            err = float(np.max(np.abs(np.take_along_axis(traced_logits, gold["columns"].astype(np.int64), 1) - gold["logits"])))
+            clear = gold["margin"] > 4e-2
+            same = bool(np.array_equal(traced_am[clear], gold["argmax"][clear]))
+            if err > 2e-2 or not same:
+                raise SystemExit(f"bench: the prefill's logits are off the CPU restatement's (max abs {err:.3e}, argmax agrees: {same})")
+            validated.update({"max_abs_err_vs_cpu_restatement_sample": err, "argmax_agrees_where_margin_clear": same,
+                              "clear_margins": int(clear.sum())})
+    fl = model.flops()
+    tflops = fl / tms / 1e9
+    return {"tok_per_s": batch * seq / (tms * 1e-3), "ms": tms, "tokens": batch * seq, "launches": int(per),
+            "mode": "traced (CUDA graph replay), fused attention", "eager_ms": eager_ms,
+            "eager_tok_per_s": batch * seq / (eager_ms * 1e-3), "trace_bytes": int(footprint),
+            "next_tokens": traced_am.tolist(), "validated": validated, "op_classes_eager": classes,
+            "roofline": {"bound": "tensor", "kernel": "the prefill's products and fused attention (K = 576 and 1536)", "achieved": tflops,
+                         "peak": peak, "unit": UNIT, "frac": tflops / peak, "peak_source": f"{which} cuBLAS bf16 burst",
+                         "algorithmic_flops_per_step": fl}}
+
+
+def extras(eng, timed):
+    """The other sizes of the sweep, the rest of the trait and the callers, timed the same way."""
+    out = {"gemm_bf16": {}, "gemm_f32": {}}
     for n in (512, 1024, 2048, 4096, 8192):
         ia = eng.upload_bf16(cheap_bf16((n, n), 1), n, n)
         ib = eng.upload_bf16(cheap_bf16((n, n), 2), n, n)
@@ -316,9 +530,9 @@ def extras(eng):
             o, _ = eng.matmul_dram_bf16(ia, False, ib, False)
             eng.free(o)
         ms = timed(f)
-        out["gemm_bf16"][str(n)] = {"ms": ms, "tflops": 2.0 * n ** 3 / ms / 1e9}
+        out["gemm_bf16"][str(n)] = {"ms": ms, "tflops": 2.0 * n ** 3 / ms / 1e9, "path": eng.last_matmul_path()}
         eng.free(ia); eng.free(ib)
-    for n in (512, 1024, 2048, 4096):
+    for n in (512, 1024, 2048, 4096, 8192):
         rng = np.random.default_rng(n)
         ia = eng.upload(rng.random((n, n), dtype=np.float32) * 2 - 1, n, n)
         ib = eng.upload(rng.random((n, n), dtype=np.float32) * 2 - 1, n, n)
@@ -329,44 +543,8 @@ def extras(eng):
         ms = timed(f, reps=5 if n >= 2048 else 20)
         out["gemm_f32"][str(n)] = {"ms": ms, "tflops": 2.0 * n ** 3 / ms / 1e9, "path": eng.last_matmul_path()}
         eng.free(ia); eng.free(ib)
-
-    rows = cols = 8192
-    rng = np.random.default_rng(3)
-    x = eng.upload(rng.random((rows, cols), dtype=np.float32) * 3.99 + 0.01, rows, cols)
-    row = eng.upload(rng.random((1, cols), dtype=np.float32) + 0.5, 1, cols)
-    nbytes = rows * cols * 4
-    for name, k, b in (("exp", kinds.EXP, None), ("log", kinds.LOG, None), ("recip", kinds.RECIP, None),
-                       ("sqrt", kinds.SQRT, None), ("relu", kinds.RELU, None), ("gelu_tanh", kinds.GELU_TANH, None),
-                       ("silu", kinds.SILU, None), ("add_row", kinds.ADD, row), ("mul_row", kinds.MUL, row),
-                       ("div_row", kinds.DIV, row)):
-        def f():
-            o, _ = eng.eltwise_op(EltwiseOp(k, 0, 0), x, b)
-            eng.free(o)
-        ms = timed(f)
-        gbs = 2 * nbytes / ms / 1e6
-        out["suite"][name] = {"ms": ms, "gbs": gbs, "frac_of_measured_hbm": gbs / hbm, "frac_of_nominal_8000": gbs / 8000.0}
-
-    def fs():
-        o, _ = eng.full_sum(x)
-        eng.free(o)
-    ms = timed(fs)
-    out["suite"]["full_sum"] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm}
-
-    def fr():
-        o, _ = eng.reduce(x, SUM, COLS)
-        eng.free(o)
-    ms = timed(fr)
-    out["suite"]["row_sum"] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm}
-    eng.free(x); eng.free(row)
-    sx = eng.upload(rng.random((4096, 32768), dtype=np.float32) * 8 - 4, 4096, 32768)
-
-    def fm():
-        o, _ = eng.softmax_rows(sx, None, 1.0)
-        eng.free(o)
-    ms = timed(fm)
-    sb = 2 * 4096 * 32768 * 4
-    out["suite"]["softmax_4096x32768"] = {"ms": ms, "gbs": sb / ms / 1e6, "frac_of_measured_hbm": sb / ms / 1e6 / hbm}
-    eng.free(sx)
+    pk, _ = peaks()
+    hbm = float(pk.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
     out["rest_of_trait"] = rest_of_trait(eng, timed, hbm)
     out["callers"] = callers(eng, timed)
     return out
@@ -624,6 +802,8 @@ def main():
     ap.add_argument("--extras", action="store_true", help="also time the rest of the sweep and the memory-bound suite")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--no-suite", action="store_true", help="skip the memory-bound suite leg")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill leg")
     ap.add_argument("--profile", default="", help="run a short fixed sequence for an ncu capture: membound | softmax | prefill | gemm_small | attention | decode | scan_sort")
     ap.add_argument("--size", type=int, default=0, help="override the N=1 problem size (profiling on a small case)")
     args = ap.parse_args()

@@ -144,6 +144,11 @@ def llama_weights(cfg: LlamaConfig, seed: int = 0xC0F4, sigma: float = 0.02) -> 
     return w
 
 
+def prefill_ids(cfg: LlamaConfig, batch: int, seq: int, seed: int = 0xC0F4) -> np.ndarray:
+    """Token ids [1, batch * seq] I32, uniform in [0, vocab): the benchmark's synthetic prompt."""
+    return np.random.default_rng(seed ^ 0x1D5).integers(0, cfg.vocab, (1, batch * seq)).astype(np.int32)
+
+
 def interleave_gate_up(w: np.ndarray) -> np.ndarray:
     """[in, gate | up] -> the layout `matmul_silu_mul` reads: groups of 256 columns, 128 gate columns then the
     128 matching up columns."""
@@ -244,21 +249,29 @@ class LlamaPrefill:
                       (b * self.seq, h * hd_)) for b in range(self.batch) for h in range(self.cfg.heads)])
         t, hd = self.seq, c.head_dim
         el = lambda kind, a, b=None, bf=False: e.eltwise_op_as(EltwiseOp(kind, 0.0, 0.0), a, b, None, bf)[0]
+        # while the engine's profile mode is on, each op class runs under its own label (server.rs:2370 labels every job)
+        lab = e.set_op_label if getattr(e, "profiling", False) else (lambda name: None)
+        lab("embedding")
         emb, _ = e.select_rows(self.w["embed"], ids_buf)                     # ops.rs:4958 embedding
         x, _ = e.cast_float(emb, False)                                      # residual stream F32
         e.free(emb)
         qk_cols = self.q_cols + self.kv_cols
+        lab("norm")
         n1, _ = e.rms_norm_as(x, self.w["l0.norm1"], c.eps, True)           # llama.rs:151-170
         for l in range(c.layers):
+            lab("projection qkv")
             qkv, _ = e.matmul_dram_bf16(n1, False, self.w[f"l{l}.qkv"], False)
             e.free(n1)
             # RoPE on the query and key heads together: they share the head width and the tables (rope.rs:129)
             cos_b = (cache.cos, (start, 0), (t, hd)) if chunked else (self.cos, (0, 0), (t, hd))
             sin_b = (cache.sin, (start, 0), (t, hd)) if chunked else (self.sin, (0, 0), (t, hd))
+            lab("rope")
             qk, _ = e.rope_blocks((qkv, (0, 0), (n, qk_cols)), cos_b, sin_b, hd, True)
-            if cache is not None:   # the chunk's rows of the cache: keys after RoPE, values as projected
+            if cache is not None:
+                lab("cache write")   # the chunk's rows of the cache: keys after RoPE, values as projected
                 e.scatter_rows_into(cache.kc[l], self._cache_rows, (qk, (0, self.q_cols), (n, self.kv_cols)))
                 e.scatter_rows_into(cache.vc[l], self._cache_rows, (qkv, (0, qk_cols), (n, self.kv_cols)))
+            lab("attention")
             if chunked:      # keys and values where the cache holds them: positions 0 .. start + t - 1, causal at the end
                 om, _ = e.attention_blocks(qk, cache.kc[l], cache.vc[l], self._cache_items, (t, hd, start + t, hd),
                                            1.0 / float(np.sqrt(hd)), True, (n, self.q_cols))
@@ -276,27 +289,34 @@ class LlamaPrefill:
                 e.free(pb); e.free(qkv)
                 om, _ = e.copy_blocks(o, self.merge, (n, self.q_cols))           # merge heads
                 e.free(o)
+            lab("projection o")
             att, _ = e.matmul_dram(om, False, self.w[f"l{l}.o"], False)      # o_proj, F32 out
             e.free(om)
+            lab("add + norm")
             # residual add and the next norm as one op (`Engine::add_rms_norm`, server.rs:466; llama.rs:288)
             (x2, _), (n2, _) = e.add_rms_norm_as(x, att, self.w[f"l{l}.norm2"], c.eps, True)
             e.free(x); e.free(att)
+            lab("projection gate|up")
             if self.fused_mlp:   # silu(gate) * up stored by the gate|up product's own epilogue
                 act, _ = e.matmul_silu_mul(n2, self.w[f"l{l}.gate_up.interleaved"])
                 e.free(n2)
             else:
                 gu, _ = e.matmul_dram_bf16(n2, False, self.w[f"l{l}.gate_up"], False)
                 e.free(n2)
+                lab("silu_mul")
                 act, _ = e.eltwise_blocks_as(EltwiseOp(K.SILU_MUL, 0.0, 0.0), (gu, (0, 0), (n, c.ff)),
                                              (gu, (0, c.ff), (n, c.ff)), None, True)   # silu(gate) * up (llama.rs:498)
                 e.free(gu)
+            lab("projection down")
             d, _ = e.matmul_dram(act, False, self.w[f"l{l}.down"], False)
             e.free(act)
+            lab("add + norm")
             if l + 1 < c.layers:
                 (x, _), (n1, _) = e.add_rms_norm_as(x2, d, self.w[f"l{l + 1}.norm1"], c.eps, True)
             else:
                 x = el(K.ADD, x2, d)
             e.free(x2); e.free(d)
+        lab("head")
         if all_positions:
             last = x
         else:
@@ -307,6 +327,7 @@ class LlamaPrefill:
         logits, _ = e.matmul_dram(fn, False, self.w["embed"], True)          # tied head: last . table^T (llama.rs:1090)
         e.free(fn)
         am, _ = e.argmax_row(logits)                                         # generate::argmax
+        lab("")
         return logits, am
 
     def capture(self, ids_buf: int):

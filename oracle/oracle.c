@@ -9,7 +9,7 @@
  * baseline leg may load this file's library; the engine never does.
  *
  * IEEE-754 binary32, round to nearest even, denormals kept.  Built with
- * -O2 -fno-fast-math -ffp-contract=off so no product-sum is fused.
+ * -O3 -fno-fast-math -ffp-contract=off so no product-sum is fused and no sum is reassociated.
  */
 #include <math.h>
 #include <stdint.h>
@@ -53,6 +53,59 @@ void orc_bf16_round_n(const uint32_t* in, uint16_t* out, uint64_t n) {
  * multiply and one an add (what a plain CPU loop gives; crates/tt-tests/tests/step11_burn.rs:
  * 15-32 names burn-flex's product as the comparison).  Row-major stored matrices; *_t says
  * the stored matrix is the transpose of the logical operand.  OpenMP over row blocks. */
+/* The F32 product: every element is the left fold over k ascending of separately rounded products and
+ * sums (no fused multiply-add), which is what a plain scalar loop gives.  The loops are blocked for the
+ * caches and four rows share each load of B, but an element's own sequence of additions is untouched,
+ * so the bits are those of the scalar loop whatever the vector width (the clones differ in nothing else). */
+#if defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__)
+#define ORC_CLONES __attribute__((target_clones("avx512f", "avx2", "default")))
+#else
+#define ORC_CLONES
+#endif
+enum { ORC_JB = 512, ORC_KB = 256, ORC_IB = 4 };
+
+ORC_CLONES
+static void orc_gemm_rows(const float* a, uint64_t lda, int a_t, const float* b, uint64_t n, float* c, uint64_t i0,
+                          uint64_t rows, uint64_t k) {
+  for (uint64_t r = 0; r < rows; ++r)
+    for (uint64_t j = 0; j < n; ++j) c[(i0 + r) * n + j] = 0.0f;
+  for (uint64_t j0 = 0; j0 < n; j0 += ORC_JB) {
+    const uint64_t jn = (j0 + ORC_JB <= n ? ORC_JB : n - j0);
+    for (uint64_t p0 = 0; p0 < k; p0 += ORC_KB) {
+      const uint64_t pn = (p0 + ORC_KB <= k ? p0 + ORC_KB : k);
+      if (rows == ORC_IB) {
+        float* c0 = c + (i0 + 0) * n + j0;
+        float* c1 = c + (i0 + 1) * n + j0;
+        float* c2 = c + (i0 + 2) * n + j0;
+        float* c3 = c + (i0 + 3) * n + j0;
+        for (uint64_t p = p0; p < pn; ++p) {
+          const float a0 = a_t ? a[p * lda + i0 + 0] : a[(i0 + 0) * lda + p];
+          const float a1 = a_t ? a[p * lda + i0 + 1] : a[(i0 + 1) * lda + p];
+          const float a2 = a_t ? a[p * lda + i0 + 2] : a[(i0 + 2) * lda + p];
+          const float a3 = a_t ? a[p * lda + i0 + 3] : a[(i0 + 3) * lda + p];
+          const float* bj = b + p * n + j0;
+          for (uint64_t j = 0; j < jn; ++j) {
+            const float bv = bj[j];
+            c0[j] = c0[j] + a0 * bv;
+            c1[j] = c1[j] + a1 * bv;
+            c2[j] = c2[j] + a2 * bv;
+            c3[j] = c3[j] + a3 * bv;
+          }
+        }
+      } else {
+        for (uint64_t r = 0; r < rows; ++r) {
+          float* cr = c + (i0 + r) * n + j0;
+          for (uint64_t p = p0; p < pn; ++p) {
+            const float av = a_t ? a[p * lda + i0 + r] : a[(i0 + r) * lda + p];
+            const float* bj = b + p * n + j0;
+            for (uint64_t j = 0; j < jn; ++j) cr[j] = cr[j] + av * bj[j];
+          }
+        }
+      }
+    }
+  }
+}
+
 void orc_gemm_f32(const float* a, int a_t, const float* b, int b_t, float* c, uint64_t m, uint64_t k, uint64_t n) {
   const uint64_t lda = a_t ? m : k, ldb = b_t ? k : n;
   /* pack B as [k][n] once if transposed, so the inner loop streams */
@@ -63,15 +116,11 @@ void orc_gemm_f32(const float* a, int a_t, const float* b, int b_t, float* c, ui
       for (uint64_t p = 0; p < k; ++p) bp[p * n + j] = b[j * ldb + p];
     b = bp;
   }
+  const int64_t blocks = (int64_t)((m + ORC_IB - 1) / ORC_IB);
 #pragma omp parallel for schedule(dynamic, 4)
-  for (int64_t i = 0; i < (int64_t)m; ++i) {
-    float* ci = c + (uint64_t)i * n;
-    for (uint64_t j = 0; j < n; ++j) ci[j] = 0.0f;
-    for (uint64_t p = 0; p < k; ++p) {
-      const float av = a_t ? a[p * lda + i] : a[(uint64_t)i * lda + p];
-      const float* bj = b + p * n;
-      for (uint64_t j = 0; j < n; ++j) ci[j] = ci[j] + av * bj[j];
-    }
+  for (int64_t ib = 0; ib < blocks; ++ib) {
+    const uint64_t i0 = (uint64_t)ib * ORC_IB;
+    orc_gemm_rows(a, lda, a_t, b, n, c, i0, (i0 + ORC_IB <= m ? ORC_IB : m - i0), k);
   }
   free(bp);
 }
@@ -209,5 +258,66 @@ void orc_map_unary(int which, const float* a, float* out, uint64_t n) {
       default: y = x;
     }
     out[i] = y;
+  }
+}
+
+/* The seeded uniform draw of oracle.py (`uniform`): splitmix64 from seed ^ tag, the top 24 bits as
+ * k 2^-24, then lo + (hi - lo) k with separate F32 roundings.  The same numbers as the NumPy form,
+ * for the tensors of tens of millions of elements the full-size parity tests draw. */
+void orc_uniform(uint64_t seed, uint64_t tag, uint64_t n, float lo, float hi, float* out) {
+  const uint64_t s0 = seed ^ tag;
+  const float span = hi - lo;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < (int64_t)n; ++i) {
+    uint64_t z = s0 + 0x9E3779B97F4A7C15ull * (uint64_t)(i + 1);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z = z ^ (z >> 31);
+    const float u = (float)(z >> 40) / 16777216.0f;
+    const float t = span * u;
+    out[i] = lo + t;
+  }
+}
+
+/* oracle.py `ulp_error`: the largest |got - want| in units of 2^-24 max(|want|, 2^-125); words that are
+ * equal, and two NaNs, count as no error; anything else not finite counts as infinite. */
+double orc_ulp_error(const uint32_t* got, const uint32_t* want, uint64_t n) {
+  double worst = 0.0;
+#pragma omp parallel for schedule(static) reduction(max : worst)
+  for (int64_t i = 0; i < (int64_t)n; ++i) {
+    if (got[i] == want[i]) continue;
+    float gf, wf;
+    memcpy(&gf, &got[i], 4);
+    memcpy(&wf, &want[i], 4);
+    const double g = gf, w = wf;
+    if (isnan(g) && isnan(w)) continue;
+    double scale = fabs(w);
+    if (!(scale > 0x1p-125)) scale = 0x1p-125;     /* also when want is a NaN */
+    double e = fabs(g - w) / (scale * 0x1p-24);
+    if (!isfinite(e)) e = INFINITY;
+    if (e > worst) worst = e;
+  }
+  return worst;
+}
+
+/* The seeded normal draw of oracle.py (`normal`) for large tensors: Box-Muller on draws i and n + i of the
+ * splitmix64 stream, in F64, rounded once to F32.  libm's log and cos may differ from NumPy's in the last
+ * place of an F64, so a value can differ from the NumPy form's by one F32 step; a draw is reproducible
+ * within this form, and nothing compares the two. */
+void orc_normal(uint64_t seed, uint64_t tag, uint64_t n, double sigma, float* out) {
+  const uint64_t s0 = seed ^ tag;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < (int64_t)n; ++i) {
+    uint64_t z[2];
+    for (int h = 0; h < 2; ++h) {
+      uint64_t v = s0 + 0x9E3779B97F4A7C15ull * (uint64_t)(i + 1 + (h ? (int64_t)n : 0));
+      v = (v ^ (v >> 30)) * 0xBF58476D1CE4E5B9ull;
+      v = (v ^ (v >> 27)) * 0x94D049BB133111EBull;
+      z[h] = v ^ (v >> 31);
+    }
+    const double u1 = ((double)(z[0] >> 40) + 1.0) / 16777216.0;
+    const double u2 = (double)(z[1] >> 40) / 16777216.0;
+    const double g = sqrt(-2.0 * log(u1)) * cos(2.0 * 3.14159265358979323846 * u2);
+    out[i] = (float)(g * sigma);
   }
 }

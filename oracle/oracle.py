@@ -47,6 +47,7 @@ def clib() -> C.CDLL:
         lib.orc_full_sum_f64.restype = C.c_double
         lib.orc_bf16_round.restype = C.c_uint16
         lib.orc_argmax.restype = C.c_int32
+        lib.orc_ulp_error.restype = C.c_double
         _clib = lib
     return _clib
 
@@ -72,12 +73,20 @@ def splitmix64(seed: int, tag: int, n: int) -> np.ndarray:
 
 def uniform(seed: int, tag: int, shape, lo: float, hi: float) -> np.ndarray:
     n = int(np.prod(shape))
+    if n >= 1 << 20:   # the C twin of the lines below (the same numbers; tests/test_oracle_kats.py holds them together)
+        out = np.empty(n, dtype=np.float32)
+        clib().orc_uniform(C.c_uint64(seed & 0xFFFFFFFFFFFFFFFF), C.c_uint64(tag), C.c_uint64(n), C.c_float(lo), C.c_float(hi), _p(out))
+        return out.reshape(shape)
     u = (splitmix64(seed, tag, n) >> np.uint64(40)).astype(np.float32) / f32(16777216.0)
     return (f32(lo) + (f32(hi) - f32(lo)) * u).astype(np.float32).reshape(shape)
 
 
 def normal(seed: int, tag: int, shape, sigma: float = 1.0) -> np.ndarray:
     n = int(np.prod(shape))
+    if n >= 1 << 22:   # the C form, for the full-size tensors (see oracle.c: may differ from the lines below by one F32 step)
+        out = np.empty(n, dtype=np.float32)
+        clib().orc_normal(C.c_uint64(seed & 0xFFFFFFFFFFFFFFFF), C.c_uint64(tag), C.c_uint64(n), C.c_double(sigma), _p(out))
+        return out.reshape(shape)
     z = splitmix64(seed, tag, 2 * n)
     u1 = ((z[:n] >> np.uint64(40)).astype(np.float64) + 1.0) / 16777216.0
     u2 = (z[n:] >> np.uint64(40)).astype(np.float64) / 16777216.0
@@ -314,6 +323,10 @@ def eltwise(kind_name: str, a, b=None, c=None, s1: float = 0.0, s2: float = 0.0)
 def ulp_error(got_bits: np.ndarray, want_bits: np.ndarray) -> float:
     """Largest |got - want| in units of 2^-24 |want| (the reference's `u`), NaN == NaN,
     infinities equal when identical."""
+    if got_bits.size >= 1 << 20:   # the C twin of the lines below
+        g32 = np.ascontiguousarray(got_bits).view(np.uint32).ravel()
+        w32 = np.ascontiguousarray(want_bits).view(np.uint32).ravel()
+        return float(clib().orc_ulp_error(_p(g32), _p(w32), C.c_uint64(g32.size)))
     g = got_bits.view(np.float32).astype(np.float64).ravel()
     w = want_bits.view(np.float32).astype(np.float64).ravel()
     same = (got_bits.ravel() == want_bits.ravel()) | (np.isnan(g) & np.isnan(w))

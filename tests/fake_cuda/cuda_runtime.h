@@ -29,6 +29,7 @@ extern uint64_t fake_cuda_memory_in_use;
 extern int fake_cuda_device_count;
 extern int fake_cuda_capturing;
 extern int fake_cuda_current_device;
+extern int fake_sync_in_capture;       // stream synchronisations asked for while a capture was open
 extern int fake_smem_attr_calls[8];       // cudaFuncSetAttribute calls, by the device that was current
 }
 enum cudaFuncAttribute { cudaFuncAttributeMaxDynamicSharedMemorySize = 8 };
@@ -83,7 +84,10 @@ static inline cudaError_t cudaMemsetAsync(void* d, int v, size_t n, cudaStream_t
 }
 static inline cudaError_t cudaStreamCreateWithFlags(cudaStream_t* s, unsigned) { *s = (cudaStream_t)malloc(8); return cudaSuccess; }
 static inline cudaError_t cudaStreamDestroy(cudaStream_t s) { free(s); return cudaSuccess; }
-static inline cudaError_t cudaStreamSynchronize(cudaStream_t) { return fake_cuda_capturing ? cudaErrorInvalidValue : cudaSuccess; }
+static inline cudaError_t cudaStreamSynchronize(cudaStream_t) {
+  if (fake_cuda_capturing) { ++fake_sync_in_capture; return cudaErrorInvalidValue; }   // on a real stream this ends the capture in error
+  return cudaSuccess;
+}
 static inline cudaError_t cudaEventCreate(cudaEvent_t* e) { *e = (cudaEvent_t)malloc(8); return cudaSuccess; }
 static inline cudaError_t cudaEventDestroy(cudaEvent_t e) { free(e); return cudaSuccess; }
 static inline cudaError_t cudaEventRecord(cudaEvent_t, cudaStream_t) { return cudaSuccess; }

@@ -11,6 +11,7 @@ uint64_t fake_cuda_memory_in_use = 0;
 int fake_cuda_device_count = 1;
 int fake_cuda_capturing = 0;
 int fake_cuda_current_device = 0;
+int fake_sync_in_capture = 0;
 int fake_smem_attr_calls[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 int fake_launch_count = 0;        // launches the engine asked for
 int fake_tc_supported = 1;        // what gemm_tc_supported answers for BF16 operands

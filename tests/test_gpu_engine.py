@@ -162,3 +162,102 @@ def test_a_generic_trace_run_writes_replays_and_reads(eng):   # server.rs:746-75
     eng.release_trace(trace)
     for i in (ix, ik, doubled, shifted, meta):
         eng.free(i)
+
+
+def test_a_wait_that_runs_out_is_reported_as_timeout_and_the_gpu_stays_usable(lib):
+    # crates/burn-tt/src/error.rs:40 `Timeout`, crates/tt-device/src/transport.rs:208-217: every device wait is bounded.
+    # Nothing faults here: a kernel waits on a barrier nothing will complete, gives up after the engine's limit
+    # (a million cycles, under a millisecond) and sets the error word; the wait after it reports TIMEOUT.
+    with CudaEngine(0, wait_limit_cycles=1_000_000) as e:
+        a = e.upload(np.ones((4, 4), np.float32), 4, 4)
+        e.sync()
+        e.set_op_label("stalled")
+        e.debug_stalled_wait()
+        with pytest.raises(TtError) as ei:
+            e.sync()
+        assert ei.value.status == 4 and ei.value.variant == "Timeout" and "TIMEOUT" in str(ei.value)
+        with pytest.raises(TtError) as again:                  # the failure is sticky for this engine's waits (server.rs:2392-2405)
+            e.download(a)
+        assert again.value.status == 4
+    with CudaEngine(0) as e:                                   # without a limit the entry point refuses to run
+        with pytest.raises(TtError) as ei:
+            e.debug_stalled_wait()
+        assert ei.value.status == 2
+    # the CUDA context is intact: a new engine multiplies correctly, on the kernels whose waits share that code
+    with CudaEngine(0, bf16_matmul_mode=2, wait_limit_cycles=2_000_000_000) as e:
+        x = orc.to_bf16(orc.uniform(0x71, 1, (256, 128), -1, 1))
+        y = orc.to_bf16(orc.uniform(0x71, 2, (128, 256), -1, 1))
+        out, _ = e.matmul_dram(e.upload_bf16(x, 256, 128), False, e.upload_bf16(y, 128, 256), False)
+        truth, s = orc.gemm_truth(orc.from_bf16(x), orc.from_bf16(y))
+        assert orc.gemm_rel_error(e.download(out), truth, s)[0] <= 1e-6
+
+
+def test_the_profile_mode_charges_device_time_to_labels(eng):  # server.rs:672,683; profile.rs:1-48; report.rs:27-55
+    x = eng.upload(orc.uniform(0x72, 1, (4096, 4096), -1, 1), 4096, 4096)
+    small = eng.upload(orc.uniform(0x72, 2, (8, 8), -1, 1), 8, 8)
+    eng.sync()
+    eng.profile_mode(True)
+    made = []
+    for _ in range(3):
+        eng.set_op_label("exp of 64 MB")
+        made.append(eng.eltwise_op(EltwiseOp(kinds.EXP, 0, 0), x)[0])
+        eng.set_op_label("exp of 256 B")
+        made.append(eng.eltwise_op(EltwiseOp(kinds.EXP, 0, 0), small)[0])
+    eng.set_op_label("")
+    table = {r["op"]: r for r in eng.profile_mode(False)}
+    big, tiny = table["exp of 64 MB"], table["exp of 256 B"]
+    assert big["calls"] == tiny["calls"] == 3 and big["launches"] == tiny["launches"] == 3
+    assert big["device_ms"] > 3 * 0.015                        # 128 MB of traffic a call cannot take under 15 us
+    assert big["device_ms"] > 2 * tiny["device_ms"] > 0.0
+    assert eng.profile_report() == list(eng.profile_report())  # still readable after the mode is off
+    with pytest.raises(TtError):
+        eng.profile_mode(False)                                # not on
+    for i in made + [x, small]:
+        eng.free(i)
+
+
+def test_a_trace_reports_its_ops_and_its_footprint(eng):      # server.rs:664 `trace_ops`, :688 `trace_footprint`
+    x = eng.upload(orc.uniform(0x73, 1, (512, 512), -1, 1), 512, 512)
+    eng.sync()
+    eng.begin_trace()
+    eng.set_op_label("relu")
+    r, _ = eng.eltwise_op(EltwiseOp(kinds.RELU, 0, 0), x)
+    eng.set_op_label("softmax")
+    s, _ = eng.softmax_rows(r, None, 1.0)
+    eng.set_op_label("")
+    t = eng.end_trace()
+    assert eng.trace_ops(t) == [("relu", 1), ("softmax", 1)]
+    assert eng.trace_footprint(t) >= 2 * 512 * 512 * 4        # the two results live in blocks the trace owns
+    eng.run_trace(t)
+    want = orc.softmax_rows(np.maximum(eng.download(x), 0))
+    assert np.max(np.abs(eng.download(s) - want) / want) <= orc.softmax_bound(512)
+    eng.release_trace(t)
+    with pytest.raises(TtError):
+        eng.trace_footprint(t)
+    for i in (x, r, s):
+        eng.free(i)
+
+
+def test_rows_add_inside_a_trace(eng):                         # server.rs:368 `rows_add`: capturable, as `select_add_rows` is
+    t0 = orc.uniform(0x74, 1, (16, 32), -1, 1)
+    v = orc.uniform(0x74, 2, (3, 32), -1, 1)
+    it, iv = eng.upload(t0, 16, 32), eng.upload(v, 3, 32)
+    eager, _ = eng.rows_add(it, [5, 2, 5], iv)
+    want = t0.copy()
+    for i, r in enumerate([5, 2, 5]):
+        want[r] = want[r] + v[i]
+    assert np.array_equal(eng.download(eager), want)
+    eng.begin_trace()
+    out, _ = eng.rows_add(it, [5, 2, 5], iv)
+    tr = eng.end_trace()
+    eng.run_trace(tr)
+    assert np.array_equal(eng.download(out), want)
+    eng.release_trace(tr)
+    with CudaEngine(0) as other:                               # DOMAIN needs an engine of its own (the failure is sticky)
+        ot, ov = other.upload(t0, 16, 32), other.upload(v[:2], 2, 32)
+        other.rows_add(ot, [1, 16], ov)
+        with pytest.raises(TtError) as ei:
+            other.sync()
+        assert ei.value.status == 6
+    for i in (it, iv, eager, out):
+        eng.free(i)

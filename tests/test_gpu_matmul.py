@@ -195,6 +195,74 @@ def test_unstacked_layout_places_each_product_on_a_tile_row(eng):  # server.rs:3
         eng.free(i)
 
 
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("mkn", [(2048, 2048, 2048), (4096, 1024, 2304), (2304, 4096, 2048)])
+def test_the_pair_kernel_with_every_operand_order(eng, mkn, ta, tb):
+    # From 64 tiles of 256 x 256 one product takes the CTA-pair kernel, whose four instantiations differ in the TMA
+    # boxes and the shared-memory descriptors of an MN-major operand (A^T B and A B^T: weight gradients, a tied head;
+    # crates/tt-tests/tests/step11_burn.rs:157-166 gates A B^T).  Too large for the whole F64 product in seconds: the
+    # row-sum identity C 1 = op(A) (op(B) 1) on every row, and 256 sampled elements against F64 dot products.
+    m, k, n = mkn
+    a = orc.to_bf16(orc.uniform(0xC0F2, 21, (k, m) if ta else (m, k), -1, 1))
+    b = orc.to_bf16(orc.uniform(0xC0F2, 22, (n, k) if tb else (k, n), -1, 1))
+    ia, ib = eng.upload_bf16(a, *a.shape), eng.upload_bf16(b, *b.shape)
+    out, dims = eng.matmul_dram(ia, ta, ib, tb)              # F32 result keeps the identity tight
+    assert dims == (m, n) and eng.last_matmul_path() == "tcgen05-pair"
+    c = eng.download(out).astype(np.float64)
+    af, bf = orc.from_bf16(a).astype(np.float64), orc.from_bf16(b).astype(np.float64)
+    la, lb = (af.T if ta else af), (bf.T if tb else bf)      # the logical operands
+    rows = la @ lb.sum(1)
+    s_rows = np.abs(la) @ np.abs(lb).sum(1)
+    assert np.max(np.abs(c.sum(1) - rows) / s_rows) <= 1e-6
+    cols = la.sum(0) @ lb                                     # and 1^T C = (1^T op(A)) op(B): every column
+    s_cols = np.abs(la).sum(0) @ np.abs(lb)
+    assert np.max(np.abs(c.sum(0) - cols) / s_cols) <= 1e-6
+    rng = np.random.default_rng(11)
+    for i, j in zip(rng.integers(0, m, 256), rng.integers(0, n, 256)):
+        t = la[i] @ lb[:, j]
+        s_ = np.abs(la[i]) @ np.abs(lb[:, j])
+        assert abs(c[i, j] - t) <= 1e-6 * s_, (i, j)
+    ob, _ = eng.matmul_dram_bf16(ia, ta, ib, tb)             # the BF16 result is that accumulator rounded once
+    assert eng.last_matmul_path() == "tcgen05-pair"
+    assert np.array_equal(eng.download_bf16(ob), orc.to_bf16(c.astype(np.float32)))
+    for i in (ia, ib, out, ob):
+        eng.free(i)
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+@pytest.mark.parametrize("mkn,a_at,a_t,b_at,b_t", [
+    ((128, 64, 128), (0, 0), False, (0, 0), True),            # one head's Q K^T: item ((0,0),False), ((0,0),True)
+    ((256, 320, 384), (64, 128), False, (32, 256), False),    # blocks at a non-zero row and column
+    ((256, 256, 256), (128, 64), True, (64, 0), True),        # both stored transposed
+    ((2048, 256, 2048), (0, 256), False, (256, 0), True),     # large enough for the pair kernel (BF16)
+    ((96, 72, 80), (8, 16), False, (24, 40), False),          # k not a multiple of 64
+])
+def test_a_batched_call_of_one_item_is_that_item_s_product(eng, bf16, mkn, a_at, a_t, b_at, b_t):
+    # One (Block, Block) pair (server.rs:229): the block offsets and transposed flags of the single item decide
+    # what is multiplied, on every kernel path.
+    m, k, n = mkn
+    ar, ac = (k, m) if a_t else (m, k)
+    br, bc = (n, k) if b_t else (k, n)
+    big_a = orc.uniform(0xC0FA, 1, (a_at[0] + ar + 32, a_at[1] + ac + 64), -1, 1)
+    big_b = orc.uniform(0xC0FA, 2, (b_at[0] + br + 32, b_at[1] + bc + 64), -1, 1)
+    if bf16:
+        big_a, big_b = orc.from_bf16(orc.to_bf16(big_a)), orc.from_bf16(orc.to_bf16(big_b))
+    ia, ib = up(eng, big_a, bf16), up(eng, big_b, bf16)
+    out, dims = eng.matmul_dram_batched(ia, ib, [((a_at, a_t), (b_at, b_t))], mkn, bf16=False)
+    assert dims == (m, n)
+    got = eng.download(out)
+    sa = big_a[a_at[0]:a_at[0] + ar, a_at[1]:a_at[1] + ac]
+    sb = big_b[b_at[0]:b_at[0] + br, b_at[1]:b_at[1] + bc]
+    truth, s_ = orc.gemm_truth(np.ascontiguousarray(sa), np.ascontiguousarray(sb), a_t, b_t)
+    assert orc.gemm_rel_error(got, truth, s_)[0] <= (1e-6 if bf16 else F32_TOL)
+    if bf16 and k % 64 == 0:
+        assert eng.last_matmul_path().startswith("tcgen05")
+    if not bf16 and min(m, k, n) >= 256:
+        assert eng.last_matmul_path() == "tcgen05-tf32x3"
+    for i in (ia, ib, out):
+        eng.free(i)
+
+
 def test_bf16_product_at_4096_by_properties(eng):
     # Too large for the F64 oracle in seconds: check the row-sum identity C 1 = A (B 1) and
     # 64 sampled elements against F64 dot products.
@@ -203,7 +271,7 @@ def test_bf16_product_at_4096_by_properties(eng):
     b = orc.to_bf16(orc.uniform(0xC0F2, 8, (n, n), -1, 1))
     ia, ib = eng.upload_bf16(a, n, n), eng.upload_bf16(b, n, n)
     out, _ = eng.matmul_dram(ia, False, ib, False)  # F32 result keeps the identity tight
-    assert eng.last_matmul_path() == "tcgen05"
+    assert eng.last_matmul_path() == "tcgen05-pair"  # 256 tiles of 256 x 256: the CTA-pair kernel
     c = eng.download(out).astype(np.float64)
     af, bf = orc.from_bf16(a).astype(np.float64), orc.from_bf16(b).astype(np.float64)
     rows = af @ bf.sum(1)
@@ -288,7 +356,7 @@ def test_the_gated_product_is_the_product_then_silu_mul_bit_for_bit(eng, mkf):  
     gu, _ = eng.matmul_dram_bf16(ia, False, iw, False)
     want, _ = eng.eltwise_blocks_as(EltwiseOp(kinds.SILU_MUL, 0.0, 0.0), (gu, (0, 0), (m, ff)), (gu, (0, ff), (m, ff)), None, True)
     got, dims = eng.matmul_silu_mul(ia, iwi)
-    assert dims == (m, ff) and eng.last_matmul_path() == "tcgen05"
+    assert dims == (m, ff) and eng.last_matmul_path() == ("tcgen05-pair" if m >= 4096 else "tcgen05")
     assert np.array_equal(eng.download_bf16(got), eng.download_bf16(want))
     with pytest.raises(TtError):
         eng.matmul_silu_mul(ia, eng.upload_bf16(w[:, :2 * ff - 8], k, 2 * ff - 8))   # not whole groups of 256 columns

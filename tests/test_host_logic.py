@@ -424,3 +424,83 @@ def test_prompt_chunks_and_the_generation_after_them_issue_consistent_ops(e):   
     dec.continue_from(am, 2 * chunk)
     lg2, am2 = dec.step()
     assert e.dims_of(lg2) == ((batch, cfg.vocab), F32)
+
+
+def test_launch_set_up_is_done_on_every_device_an_engine_lives_on(fake):
+    # A kernel's opt-in to large shared memory is an attribute of the function on ONE device: an engine on a second
+    # ordinal of the same process must set it again, once.
+    C.c_int.in_dll(fake, "fake_cuda_device_count").value = 2
+    calls = (C.c_int * 8).in_dll(fake, "fake_smem_attr_calls")
+    try:
+        before = [calls[0], calls[1]]
+        e0, e1 = CudaEngine(0, lib=fake), CudaEngine(1, lib=fake)
+        for eng in (e0, e1, e0, e1):
+            a = eng.upload_bf16(np.zeros((256, 128), np.uint16), 256, 128)
+            b = eng.upload_bf16(np.zeros((128, 256), np.uint16), 128, 256)
+            eng.matmul_dram_bf16(a, False, b, False)
+        assert calls[0] - before[0] <= 1 and calls[1] - before[1] == 1      # device 0 may have been set by an earlier test
+        assert calls[0] >= 1
+        e0.close(); e1.close()
+    finally:
+        C.c_int.in_dll(fake, "fake_cuda_device_count").value = 1
+        C.c_int.in_dll(fake, "fake_cuda_current_device").value = 0
+
+
+def test_a_batched_call_of_one_item_takes_the_plain_product_s_route(fake, e):
+    # One (Block, Block) pair is folded into a plain product on the blocks (offsets into the bases, the item's flags):
+    # an F32 item of 256 and up reaches the split-TF32 path, which refuses batches.
+    f = f32(e, 512, 512)
+    out, dims = e.matmul_dram_batched(f, f, [(((128, 64), False), ((0, 256), True))], (256, 256, 256))
+    assert dims == (256, 256) and e.last_matmul_path() == "tcgen05-tf32x3"
+    out, dims = e.matmul_dram_batched(f, f, [(((0, 0), False), ((0, 0), False)), (((256, 0), False), ((0, 0), False))], (256, 256, 256))
+    assert dims == (512, 256) and e.last_matmul_path() == "simt"                # two F32 items: the batched SIMT kernel
+
+
+def test_out_of_memory_inside_a_capture_does_not_touch_the_stream(fake, e):
+    # the retry path synchronises the stream, which would invalidate an open capture: inside one the failure is immediate
+    a = f32(e, 64, 64)
+    e.begin_trace()
+    syncs = C.c_int.in_dll(fake, "fake_sync_in_capture").value
+    C.c_uint64.in_dll(fake, "fake_cuda_memory_limit").value = C.c_uint64.in_dll(fake, "fake_cuda_memory_in_use").value + 1024
+    with pytest.raises(TtError) as err:
+        e.zeros_dram((2048, 2048))                                              # 16 MB asked with 1 KB of room
+    assert err.value.status == 1
+    assert C.c_int.in_dll(fake, "fake_sync_in_capture").value == syncs          # no synchronise-and-retry
+    C.c_uint64.in_dll(fake, "fake_cuda_memory_limit").value = 0
+    o, _ = e.eltwise_op(EltwiseOp(kinds.RELU, 0, 0), a)                         # the capture is still open and usable
+    t = e.end_trace()
+    e.run_trace(t)
+    e.release_trace(t)
+
+
+def test_rows_add_trace_ops_and_footprint(fake, e):
+    t0, v = f32(e, 16, 32), f32(e, 3, 32)
+    e.begin_trace()
+    e.set_op_label("embedding_backward")
+    out, dims = e.rows_add(t0, [5, 2, 5], v)                                    # an index list inside a capture: a copy node, not an upload
+    assert dims == (16, 32)
+    e.set_op_label("relu")
+    r, _ = e.eltwise_op(EltwiseOp(kinds.RELU, 0, 0), out)
+    tr = e.end_trace()
+    assert e.trace_ops(tr) == [("embedding_backward", 1), ("relu", 1)]
+    assert e.trace_footprint(tr) >= 2 * 16 * 32 * 4
+    e.release_trace(tr)
+    with pytest.raises(TtError):
+        e.trace_ops(tr)
+    with pytest.raises(TtError):
+        e.rows_add(t0, [1, 2], v)                                               # two indices, three value rows
+
+
+def test_profile_mode_state_machine(fake, e):
+    a = f32(e, 8, 8)
+    with pytest.raises(TtError):
+        e.profile_mode(False)                                                   # not on
+    e.profile_mode(True)
+    for label in ("relu", "exp", "relu"):
+        e.set_op_label(label)
+        e.eltwise_op(EltwiseOp(kinds.RELU if label == "relu" else kinds.EXP, 0, 0), a)
+    table = e.profile_mode(False)
+    assert [(r["op"], r["calls"], r["launches"]) for r in table] == [("relu", 2, 2), ("exp", 1, 1)]
+    assert e.profile_report() == table
+    e.set_op_label("after")                                                     # off: labels cost nothing and record nothing
+    assert e.profile_report() == table

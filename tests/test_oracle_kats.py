@@ -361,3 +361,23 @@ def test_convolution_and_pooling_restatements_agree_with_torch_cpu():   # a seco
     nan = np.array([[[[1.0, np.nan], [5.0, np.nan]]]], np.float32)
     nan.view(np.uint32)[0, 0, 1, 1] = 0xFFC00005
     assert orc.max_pool2d(nan.view(np.uint32), (2, 2), (1, 1), (0, 0), (1, 1))[0, 0, 0, 0] == 0x7FC00000   # the first NaN
+
+
+def test_the_c_twins_of_the_draws_and_of_the_ulp_measure_agree_with_numpy():
+    # Large tensors are drawn and compared by C loops (oracle.c) instead of NumPy passes; on a size both forms take,
+    # the same numbers come out.
+    n = (1 << 20) + 7
+    for tag, lo, hi in ((1, -4.0, 4.0), (2, 0.01, 4.0)):
+        c_form = orc.uniform(0xC0F3, tag, (n,), lo, hi)
+        u = (orc.splitmix64(0xC0F3, tag, n) >> np.uint64(40)).astype(np.float32) / np.float32(16777216.0)
+        numpy_form = (np.float32(lo) + (np.float32(hi) - np.float32(lo)) * u).astype(np.float32)
+        assert np.array_equal(c_form, numpy_form)
+    want = orc.eltwise("EXP", c_form)
+    got = want.copy()
+    got[5] += 3
+    got[9] = np.float32(np.nan).view(np.uint32)
+    small = orc.ulp_error(got[:1000], want[:1000])                  # the NumPy form
+    assert small == np.inf and orc.ulp_error(got, want) == np.inf   # a NaN against a number: infinite in both
+    got[9] = want[9]
+    assert abs(orc.ulp_error(got, want) - orc.ulp_error(got[:1000], want[:1000])) < 1e-9
+    assert orc.ulp_error(want, want) == 0.0

@@ -43,7 +43,6 @@ def _worker(rank, world, port, q):
         for _ in range(rank + 2):
             mesh.count(1, local.numel() * 4 * (world - 1))
         q.put((rank, bool(np.array_equal(full.numpy(), a @ b)), tuple(staged.shape), mesh.report()))
-        # a rank that fails before the collective is seen by the others as an error, not a hang
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -75,3 +74,44 @@ def test_two_ranks_gather_the_whole_product_bit_for_bit():
     for r in res:
         assert r[3] == {"completed_matmuls": [2, 3], "acknowledged_transfers": r[0] + 2,
                         "acknowledged_bytes": (r[0] + 2) * 48 * 64 * 4}
+
+
+def _failing_worker(rank, world, port, q):
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=15))
+    dist.barrier()
+    if rank == 1:
+        q.put((1, "raised", 0.0))
+        q.close(); q.join_thread()     # the message is out before the process goes
+        os._exit(3)                    # the rank dies between steps: no collective of its own in flight, no clean-up
+    t0 = time.monotonic()
+    try:
+        sharded.gather_columns(torch.zeros((4, 8)), world)
+        q.put((0, "completed", time.monotonic() - t0))
+    except Exception as ex:            # the survivor's gather ends in an error (a closed connection or the group's timeout)
+        q.put((0, "error: " + type(ex).__name__, time.monotonic() - t0))
+    q.close(); q.join_thread()
+    os._exit(0)
+
+
+@pytest.mark.timeout(120)
+def test_a_rank_that_dies_before_the_gather_is_an_error_on_the_other_not_a_hang():
+    # Failure is made on the host only: rank 1 exits before the all-gather; rank 0's collective must return with an
+    # error inside the process group's timeout (crates/tt-device/src/transport.rs:208-217: every wait is bounded).
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict()
+    for _ in procs:
+        r = q.get(timeout=60)
+        res[r[0]] = r
+    for p in procs:
+        p.join(30)
+    assert res[1][1] == "raised" and procs[1].exitcode == 3
+    assert res[0][1].startswith("error"), res[0]
+    assert res[0][2] < 30.0 and procs[0].exitcode == 0

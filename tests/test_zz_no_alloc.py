@@ -57,3 +57,17 @@ def test_no_alloc_full_sum_refuses_what_is_beyond_its_limit(lib, eng):
     assert _noalloc(lib, eng, ia, 16, False, out_id) == 0
     assert float(eng.download(out_id)[0, 0]) == 16.0
     eng.free(ia); eng.free(out_id)
+
+
+def test_no_alloc_full_sum_of_nothing(lib, eng):
+    ia = eng.upload(np.ones((4, 4), np.float32), 4, 4)
+    out_id = eng.upload(np.full((1, 1), 7.0, np.float32), 1, 1)
+    assert _noalloc(lib, eng, ia, 0, False, out_id) == 0           # the sum of no elements is +0.0
+    assert eng.download_bits(out_id)[0, 0] == 0
+    assert _noalloc(lib, eng, ia, 0, True, out_id) == 2            # their mean is 0 / 0: refused, not a silent NaN
+    buf = C.create_string_buffer(256)
+    lib.b200_last_error(None, buf, 256)
+    assert b"mean of no elements" in buf.value
+    assert _noalloc(lib, eng, ia, 16, True, out_id) == 0            # and the entry point still works after a refusal
+    assert float(eng.download(out_id)[0, 0]) == 1.0
+    eng.free(ia); eng.free(out_id)
