@@ -155,6 +155,16 @@ int32_t b200_matmul_into(b200_engine*, b200_buffer a, b200_buffer b, void* const
  * [col_first, ...) of every dst[i] -- a rank's column slice of an all-gather, written everywhere by its owner. */
 int32_t b200_store_block_into(b200_engine*, const b200_block_arg* src, void* const* dst, int32_t n_dst,
                               uint64_t dst_rows, uint64_t dst_cols, uint64_t col_first);
+/* Both of the above with the exchange done by the NVSwitch: `multicast_dst` is the address of an NVLS multicast
+ * object that maps the destination matrix of every GPU of a group (made by the caller: cuMulticastCreate and its
+ * bindings, or a library that wraps them), and each 16-byte piece is stored there once (`multimem.st`); the switch
+ * delivers it to every GPU bound to the object, this one included.  A rank's outbound bytes are then its slice
+ * once, whatever the number of ranks (crates/tt-kernels/src/shard.rs:348-458 sends the slice to one chip; here every
+ * rank ends with the whole C).  Refused unless the slice is whole 128-byte row segments at 16-byte addresses. */
+int32_t b200_matmul_into_multicast(b200_engine*, b200_buffer a, b200_buffer b, void* multicast_dst, uint64_t dst_rows,
+                                   uint64_t dst_cols, uint64_t col_first, int32_t out_bf16);
+int32_t b200_store_block_into_multicast(b200_engine*, const b200_block_arg* src, void* multicast_dst, uint64_t dst_rows,
+                                        uint64_t dst_cols, uint64_t col_first);
 /* CUDA IPC for that: a 64-byte handle of a buffer's allocation (not of a view), opened in another process
  * as a device address valid there, closed before the owner frees the buffer. */
 int32_t b200_ipc_export(b200_engine*, b200_buffer buf, uint8_t handle[64]);

@@ -5,6 +5,15 @@
 
 namespace b200 {
 
+// Sixteen bytes stored once at a multicast address (an NVLS multicast object that maps the same buffer of every
+// GPU of a group): the NVSwitch delivers the store to every GPU bound to the object, so a rank that owes its
+// tile to g ranks sends it over its links once, not g - 1 times.  A store only: nothing is loaded through the address.
+__device__ __forceinline__ void st_multicast_16(void* addr, uint4 v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(addr), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
 // "positive and not NaN" on raw bits: the test the reference's relu family uses
 // (crates/tt-kernels/src/sfpu/ops.rs:3877-3906): relu(NaN) = 0, relu(-0) = +0.
 __device__ __forceinline__ bool positive_not_nan(uint32_t u) {

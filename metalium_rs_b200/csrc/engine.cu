@@ -846,8 +846,8 @@ int32_t b200_matmul_silu_mul(b200_engine* e, b200_buffer a, b200_buffer b, b200_
 // C = A B written into one or more caller-named matrices instead of a new buffer: the sharded
 // product's rank writes its column slice straight into every rank's C (its own and, through
 // addresses opened with b200_ipc_open, its peers' over NVLink) from the product's epilogue.
-int32_t b200_matmul_into(b200_engine* e, b200_buffer a, b200_buffer b, void* const* dst, int32_t n_dst, uint64_t dst_rows,
-                         uint64_t dst_cols, uint64_t col_first, int32_t out_bf16) {
+static int matmul_into_any(b200_engine* e, b200_buffer a, b200_buffer b, void* const* dst, int32_t n_dst, uint64_t dst_rows,
+                           uint64_t dst_cols, uint64_t col_first, int32_t out_bf16, int multicast) {
   cudaSetDevice(e->device);
   Buf *A = nullptr, *B = nullptr;
   int st = e->need(a, &A, "matmul_into");
@@ -864,6 +864,10 @@ int32_t b200_matmul_into(b200_engine* e, b200_buffer a, b200_buffer b, void* con
                    (unsigned long long)n, (unsigned long long)col_first, (unsigned long long)dst_rows, (unsigned long long)dst_cols);
   if (k == 0 || m == 0 || n == 0) return e->fail(B200_UNSUPPORTED, "matmul_into: an empty product");
   const uint64_t eb = out_bf16 ? 2 : 4;
+  // A multicast address takes whole 16-byte pieces of whole 128-byte row segments only (one multimem.st each): no ragged edge
+  if (multicast && (n_dst != 1 || (n * eb) % 128 || (col_first * eb) % 16 || (dst_cols * eb) % 16 || ((uintptr_t)dst[0] & 15)))
+    return e->fail(B200_UNSUPPORTED, "matmul_into_multicast: %llu columns at column %llu of %llu are not whole 128-byte row segments at 16-byte addresses",
+                   (unsigned long long)n, (unsigned long long)col_first, (unsigned long long)dst_cols);
   GemmArgs g{};
   g.a = A->ptr; g.b = B->ptr;
   g.c = (char*)dst[0] + col_first * eb;
@@ -874,6 +878,7 @@ int32_t b200_matmul_into(b200_engine* e, b200_buffer a, b200_buffer b, void* con
   g.lda = A->cols; g.ldb = B->cols; g.ldc = dst_cols;
   g.a_trans = 0; g.b_trans = 0; g.batch = 1; g.batches_dev = nullptr;
   g.sm_limit = e->matmul_sm_limit;
+  g.multicast = multicast;
   const char* why = "";
   if (!gemm_tc_supported(g, &why)) return e->fail(B200_UNSUPPORTED, "matmul_into: the tcgen05 path refuses this product (%s)", why);
   int pair = 0;
@@ -882,12 +887,25 @@ int32_t b200_matmul_into(b200_engine* e, b200_buffer a, b200_buffer b, void* con
   e->matmul_path = pair ? "tcgen05-pair" : "tcgen05";
   return e->launched(ce, "matmul_into");
 }
+int32_t b200_matmul_into(b200_engine* e, b200_buffer a, b200_buffer b, void* const* dst, int32_t n_dst, uint64_t dst_rows,
+                         uint64_t dst_cols, uint64_t col_first, int32_t out_bf16) {
+  return matmul_into_any(e, a, b, dst, n_dst, dst_rows, dst_cols, col_first, out_bf16, 0);
+}
+// The same product stored ONCE, at a multicast address that maps every rank's C (an NVLS multicast object):
+// the NVSwitch replicates each store to every GPU of the group, so a rank's outbound bytes are its slice, not
+// its slice times the other ranks.
+int32_t b200_matmul_into_multicast(b200_engine* e, b200_buffer a, b200_buffer b, void* multicast_dst, uint64_t dst_rows,
+                                   uint64_t dst_cols, uint64_t col_first, int32_t out_bf16) {
+  void* const one[1] = {multicast_dst};
+  if (!multicast_dst) return e->fail(B200_UNSUPPORTED, "matmul_into_multicast: the destination is null");
+  return matmul_into_any(e, a, b, one, 1, dst_rows, dst_cols, col_first, out_bf16, 1);
+}
 
 // A block of a buffer stored into columns [col_first, ...) of each of the n_dst matrices dst[i]
 // ([dst_rows, dst_cols] of the block's type; this GPU's or a peer's): a rank's column slice of an
 // all-gather, written everywhere by its owner.
-int32_t b200_store_block_into(b200_engine* e, const b200_block_arg* src, void* const* dst, int32_t n_dst, uint64_t dst_rows,
-                              uint64_t dst_cols, uint64_t col_first) {
+static int store_block_any(b200_engine* e, const b200_block_arg* src, void* const* dst, int32_t n_dst, uint64_t dst_rows,
+                           uint64_t dst_cols, uint64_t col_first, int multicast) {
   cudaSetDevice(e->device);
   Buf* S = nullptr;
   int st = e->need(src->id, &S, "store_block_into");
@@ -901,9 +919,19 @@ int32_t b200_store_block_into(b200_engine* e, const b200_block_arg* src, void* c
   const char* sp = (const char*)S->ptr + (src->at[0] * S->cols + src->at[1]) * eb;
   void* shifted[8];
   for (int i = 0; i < n_dst; ++i) shifted[i] = (char*)dst[i] + col_first * eb;
-  const cudaError_t ce = launch_store_block_many(sp, S->cols * eb, shifted, n_dst, dst_cols * eb, rows, cols * eb, e->stream);
+  const cudaError_t ce = launch_store_block_many(sp, S->cols * eb, shifted, n_dst, dst_cols * eb, rows, cols * eb, multicast, e->stream);
   if (ce == cudaErrorNotSupported) return e->fail(B200_UNSUPPORTED, "store_block_into: rows are not whole 16-byte pieces at 16-byte addresses");
   return e->launched(ce, "store_block_into");
+}
+int32_t b200_store_block_into(b200_engine* e, const b200_block_arg* src, void* const* dst, int32_t n_dst, uint64_t dst_rows,
+                              uint64_t dst_cols, uint64_t col_first) {
+  return store_block_any(e, src, dst, n_dst, dst_rows, dst_cols, col_first, 0);
+}
+int32_t b200_store_block_into_multicast(b200_engine* e, const b200_block_arg* src, void* multicast_dst, uint64_t dst_rows,
+                                        uint64_t dst_cols, uint64_t col_first) {
+  void* const one[1] = {multicast_dst};
+  if (!multicast_dst) return e->fail(B200_UNSUPPORTED, "store_block_into_multicast: the destination is null");
+  return store_block_any(e, src, one, 1, dst_rows, dst_cols, col_first, 1);
 }
 
 // Another process's view of a buffer of this engine (CUDA IPC): export here, open there.

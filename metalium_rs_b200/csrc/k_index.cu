@@ -108,7 +108,7 @@ scatter_rows_into_kernel(E* table, uint64_t t_rows, uint64_t cols, const int32_t
 // A [rows, row_bytes] block copied into the same place of up to eight matrices (this GPU's or, through
 // IPC mappings, its peers'): what an all-gather of column slices is when every rank stores its own
 // slice everywhere.  16-byte pieces, consecutive threads on consecutive pieces of a row.
-struct ManyDst { char* p[8]; int n; };
+struct ManyDst { char* p[8]; int n; int multicast; };
 __global__ void __launch_bounds__(256)
 store_block_many_kernel(const char* __restrict__ src, uint64_t src_pitch, ManyDst dst, uint64_t dst_pitch, uint64_t rows,
                         uint64_t row_bytes) {
@@ -116,7 +116,8 @@ store_block_many_kernel(const char* __restrict__ src, uint64_t src_pitch, ManyDs
   for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
     const uint64_t r = i / units, u = i - r * units;
     const uint4 w = *reinterpret_cast<const uint4*>(src + r * src_pitch + u * 16);
-    for (int d = 0; d < dst.n; ++d) *reinterpret_cast<uint4*>(dst.p[d] + r * dst_pitch + u * 16) = w;
+    if (dst.multicast) st_multicast_16(dst.p[0] + r * dst_pitch + u * 16, w);   // one store, delivered to every GPU of the group
+    else for (int d = 0; d < dst.n; ++d) *reinterpret_cast<uint4*>(dst.p[d] + r * dst_pitch + u * 16) = w;
   }
 }
 
@@ -301,11 +302,13 @@ cudaError_t launch_scatter_rows_into(void* table, uint64_t t_rows, uint64_t cols
   return cudaGetLastError();
 }
 cudaError_t launch_store_block_many(const void* src, uint64_t src_pitch, void* const* dst, int n_dst, uint64_t dst_pitch,
-                                    uint64_t rows, uint64_t row_bytes, cudaStream_t s) {
+                                    uint64_t rows, uint64_t row_bytes, int multicast, cudaStream_t s) {
   if (rows == 0 || row_bytes == 0) return cudaSuccess;
   if (n_dst < 1 || n_dst > 8 || row_bytes % 16 || src_pitch % 16 || dst_pitch % 16 || ((uintptr_t)src & 15)) return cudaErrorNotSupported;
+  if (multicast && n_dst != 1) return cudaErrorNotSupported;
   ManyDst d;
   d.n = n_dst;
+  d.multicast = multicast;
   for (int i = 0; i < 8; ++i) {
     d.p[i] = i < n_dst ? (char*)dst[i] : nullptr;
     if (i < n_dst && ((uintptr_t)dst[i] & 15)) return cudaErrorNotSupported;

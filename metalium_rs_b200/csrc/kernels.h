@@ -96,8 +96,9 @@ cudaError_t launch_attention_tc(const void* q, uint64_t q_rows, uint64_t q_cols,
                                 float scale, int causal, void* out, uint64_t o_ld, int* err, cudaStream_t stream);
 cudaError_t launch_scatter_rows_into(void* table, uint64_t t_rows, uint64_t cols, int elem_bytes, const int32_t* idx,
                                      uint64_t n, const void* values, uint64_t v_ld, int* err, cudaStream_t);
+// `multicast`: dst[0] is a multicast address and each piece is stored once with multimem.st (n_dst == 1).
 cudaError_t launch_store_block_many(const void* src, uint64_t src_pitch, void* const* dst, int n_dst, uint64_t dst_pitch,
-                                    uint64_t rows, uint64_t row_bytes, cudaStream_t);
+                                    uint64_t rows, uint64_t row_bytes, int multicast, cudaStream_t);
 struct MoveDev { uint64_t from_r, from_c, to_r, to_c, rows, cols; int32_t transposed; int32_t pad; };
 cudaError_t launch_copy_blocks(const void* src, uint64_t src_ld, void* dst, uint64_t dst_ld,
                                int elem_bytes, const MoveDev* moves_dev, uint64_t n_moves,
@@ -122,6 +123,7 @@ struct GemmArgs {
   const GemmBatch* batches_dev;  // device array when batch > 1 (or nullptr for batch 1)
   void* c_more[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   int n_more = 0;          // the tensor-core product also stores C at these addresses (same pitch as c)
+  int multicast = 0;       // c is a multicast address: every 16-byte piece is stored once with multimem.st (n_more == 0)
   int epi_mode = 0;        // 1: the tensor-core epilogue stores silu(gate) * up of each 256-column tile's halves (n % 256 == 0)
   int sm_limit = 0;        // > 0: the tensor-core product uses at most this many SMs (the rest stay free for a
                            // collective running beside it)

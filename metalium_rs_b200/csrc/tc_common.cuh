@@ -30,6 +30,7 @@ struct TcParams {
   int epi_mode;              // 0: store the product; 1: silu(gate) * up of a tile's two 128-column halves (BN 256)
   int staged;                // the epilogue may go through shared memory (pointers and pitch are 16-byte aligned)
   int out_bf16;
+  int multicast;             // c is a multicast address (stored once with multimem.st, every row piece whole: no ragged edges)
   int* err;
   uint32_t mn_lbo, mn_sbo;   // byte offsets of an MN-major operand's descriptor
 };
@@ -148,6 +149,15 @@ constexpr uint32_t EPI_BYTES = 4 * EPI_WARP_BYTES;
 __device__ __forceinline__ void epi_store_rows(const uint8_t* stage, const TcParams& p, uint64_t byte_off_row0,
                                                uint64_t pitch_bytes, uint64_t row0, int lane) {
   const int sub = lane >> 3, unit = lane & 7;
+  if (p.multicast) {
+    char* base = (char*)p.c + byte_off_row0 + unit * 16;
+#pragma unroll
+    for (int r = 0; r < 32; r += 4) {
+      const int rr = r + sub;
+      if (row0 + rr < p.m) st_multicast_16(base + (uint64_t)rr * pitch_bytes, *reinterpret_cast<const uint4*>(stage + rr * EPI_PITCH + unit * 16));
+    }
+    return;
+  }
   for (int dsti = -1; dsti < p.n_more; ++dsti) {
     char* base = (char*)(dsti < 0 ? p.c : p.c_more[dsti]) + byte_off_row0 + unit * 16;
 #pragma unroll
@@ -161,6 +171,7 @@ __device__ __forceinline__ void epi_store_rows(const uint8_t* stage, const TcPar
 
 // 32 columns of this lane's row straight from registers (ragged edges, unaligned pitches).
 __device__ __forceinline__ void epi_store_direct(const TcParams& p, const uint32_t* v, uint64_t o, uint64_t col) {
+  if (p.multicast) return;   // the host refuses a multicast product with ragged pieces; never a plain store to that address
   for (int dsti = -1; dsti < p.n_more; ++dsti) {
     void* const cbase = dsti < 0 ? p.c : p.c_more[dsti];
     if (p.out_bf16) {

@@ -329,6 +329,17 @@ class CudaEngine:
         self._check(self._lib.b200_store_block_into(self._e, C.byref(blk), arr, C.c_int32(len(dst_ptrs)), C.c_uint64(dst_dims[0]),
                                                     C.c_uint64(dst_dims[1]), C.c_uint64(col_first)))
 
+    def matmul_into_multicast(self, a: int, b: int, multicast_ptr: int, dst_dims, col_first: int, bf16: bool = True):
+        """`matmul_into` with the destination a multicast address that maps every rank's C: each piece is stored once
+        and the NVSwitch delivers it to every GPU of the group."""
+        self._check(self._lib.b200_matmul_into_multicast(self._e, C.c_uint64(a), C.c_uint64(b), C.c_void_p(multicast_ptr),
+                                                         C.c_uint64(dst_dims[0]), C.c_uint64(dst_dims[1]), C.c_uint64(col_first),
+                                                         C.c_int32(int(bf16))))
+
+    def store_block_into_multicast(self, src, multicast_ptr: int, dst_dims, col_first: int):
+        self._check(self._lib.b200_store_block_into_multicast(self._e, C.byref(_block(src)), C.c_void_p(multicast_ptr),
+                                                              C.c_uint64(dst_dims[0]), C.c_uint64(dst_dims[1]), C.c_uint64(col_first)))
+
     def ipc_export(self, buf: int) -> bytes:
         h = (C.c_uint8 * 64)()
         self._check(self._lib.b200_ipc_export(self._e, C.c_uint64(buf), h))

@@ -92,6 +92,8 @@ extern "C" {
     pub fn b200_matmul_silu_mul(a0: *mut b200_engine, a: u64, b: u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_matmul_into(a0: *mut b200_engine, a: u64, b: u64, dst: *const *mut core::ffi::c_void, n_dst: i32, dst_rows: u64, dst_cols: u64, col_first: u64, out_bf16: i32) -> i32;
     pub fn b200_store_block_into(a0: *mut b200_engine, src: *const b200_block_arg, dst: *const *mut core::ffi::c_void, n_dst: i32, dst_rows: u64, dst_cols: u64, col_first: u64) -> i32;
+    pub fn b200_matmul_into_multicast(a0: *mut b200_engine, a: u64, b: u64, multicast_dst: *mut core::ffi::c_void, dst_rows: u64, dst_cols: u64, col_first: u64, out_bf16: i32) -> i32;
+    pub fn b200_store_block_into_multicast(a0: *mut b200_engine, src: *const b200_block_arg, multicast_dst: *mut core::ffi::c_void, dst_rows: u64, dst_cols: u64, col_first: u64) -> i32;
     pub fn b200_ipc_export(a0: *mut b200_engine, buf: u64, handle: *mut u8) -> i32;
     pub fn b200_ipc_open(a0: *mut b200_engine, handle: *const u8, ptr: *mut *mut core::ffi::c_void) -> i32;
     pub fn b200_ipc_close(a0: *mut b200_engine, ptr: *mut core::ffi::c_void) -> i32;

@@ -159,12 +159,90 @@ class ShardedMatmul:
     describe = "row panels: NCCL all-gather of panel p overlapped with the product of panel p+1, then one strided copy into row-major C"
 
 
+class _Shared:
+    """A [rows, cols] BF16 matrix every rank can store into, in two alternating copies.  How a rank reaches the
+    other ranks' copies, best first (`B200TT_EXCHANGE` = multicast | peer | ipc forces one):
+
+      multicast  the copies are symmetric memory bound to one NVLS multicast object (torch.distributed's
+                 symmetric memory does the driver calls); a store to the multicast address is delivered by the
+                 NVSwitch to every rank, so a rank sends each piece once;
+      peer       the same memory, reached through each peer's own address: one store a peer;
+      ipc        pool blocks of the engine exchanged as CUDA IPC handles: one store a peer.
+
+    With plain peer stores the destinations are taken in the order rank + 1, rank + 2, ... so that the ranks do not
+    all store into the same peer at the same moment.  `dst[i]` is the address list for `matmul_into` /
+    `store_block_into` (own copy first); `mc[i]` the multicast address, or 0."""
+
+    def __init__(self, eng, rank: int, world: int, rows: int, cols: int):
+        import torch
+        import torch.distributed as dist
+        self.eng, self.rank, self.world = eng, rank, world
+        self.bufs, self.dst, self.mc, self.opened, self.keep = [], [], [], [], []
+        want = os.environ.get("B200TT_EXCHANGE", "")
+        order = [(rank + i) % world for i in range(1, world)]
+        self.how = "ipc"
+        if want != "ipc":
+            try:
+                import torch.distributed._symmetric_memory as symm
+                from . import BF16
+                dev = torch.device("cuda", torch.cuda.current_device())
+                for _ in range(2):
+                    t = symm.empty((rows, cols), dtype=torch.bfloat16, device=dev)
+                    t.zero_()
+                    h = symm.rendezvous(t, dist.group.WORLD)
+                    ptrs = [int(x) for x in h.buffer_ptrs]
+                    mc = int(h.multicast_ptr) if (want != "peer" and h.has_multicast_support) else 0
+                    self.keep.append((t, h))
+                    self.bufs.append(eng.adopt(t.data_ptr(), rows, cols, BF16))
+                    self.dst.append([ptrs[rank]] + [ptrs[r] for r in order])
+                    self.mc.append(mc)
+                self.how = "multicast" if all(self.mc) else "peer"
+                if not all(self.mc):
+                    self.mc = [0, 0]
+                torch.cuda.synchronize()
+            except Exception as ex:        # no symmetric memory on this box: the IPC form below
+                if want in ("multicast", "peer"):
+                    raise
+                self._why_not = str(ex)[:200]
+                for b in self.bufs:
+                    eng.free(b)
+                self.bufs, self.dst, self.mc, self.keep = [], [], [], []
+        agree = [None] * world
+        dist.all_gather_object(agree, self.how)
+        if len(set(agree)) != 1:           # every rank takes the same form, or all fall back together
+            for b in self.bufs:
+                eng.free(b)
+            self.bufs, self.dst, self.mc, self.keep, self.how = [], [], [], [], "ipc"
+        if self.how == "ipc":
+            for _ in range(2):
+                c, _ = eng.zeros_dram((rows, cols), bf16=True)
+                mine, _ = eng.device_ptr(c)
+                handles = [None] * world
+                dist.all_gather_object(handles, eng.ipc_export(c))
+                peers = [eng.ipc_open(handles[r]) for r in order]
+                self.bufs.append(c)
+                self.opened += peers
+                self.dst.append([mine] + peers)
+                self.mc.append(0)
+
+    def close(self):
+        import torch.distributed as dist
+        self.eng.sync()
+        dist.barrier()
+        for p in self.opened:
+            self.eng.ipc_close(p)
+        dist.barrier()                               # every mapping is closed before an owner frees its copy
+        for c in self.bufs:
+            self.eng.free(c)
+        self.opened, self.bufs, self.keep = [], [], []
+
+
 class PeerStoreMatmul:
-    """The same sharded product with the exchange inside the product: every rank keeps a whole C,
-    the ranks exchange CUDA IPC handles of it once, and a rank's product stores each finished tile
-    of its column slice into every rank's C from its epilogue (`b200_matmul_into`: 128-byte row
-    segments, its own memory and its peers' over NVLink).  No staging buffer, no collective on the
-    data, no final copy.
+    """The same sharded product with the exchange inside the product: every rank keeps a whole C that every
+    rank can store into (`_Shared`), and a rank's product stores each finished tile of its column slice into every
+    rank's C from its epilogue -- once, at the NVLS multicast address (`b200_matmul_into_multicast`: the NVSwitch
+    replicates it), or, where no multicast object can be had, once a rank over NVLink (`b200_matmul_into`).  No
+    staging buffer, no collective on the data, no final copy.
 
     Ordering is on the device: a one-element NCCL all-reduce is enqueued on the engine's stream behind
     the product, so it completes on a rank only when every rank's product -- and with it every store
@@ -187,21 +265,22 @@ class PeerStoreMatmul:
         if not bf16:
             raise ValueError("the peer-store product is BF16")
         self.a, self.b = a_buf, b_slice_buf
-        self.c, self.dst, self.opened = [], [], []
-        for _ in range(2):
-            c, _ = eng.zeros_dram((m, n), bf16=True)
-            mine, _ = eng.device_ptr(c)
-            handles = [None] * world
-            dist.all_gather_object(handles, eng.ipc_export(c))
-            peers = [eng.ipc_open(handles[r]) for r in range(world) if r != rank]
-            self.c.append(c)
-            self.opened += peers
-            self.dst.append([mine] + peers)          # own C first: the epilogue's first store is the local one
+        self.shared = _Shared(eng, rank, world, m, n)
+        self.c = self.shared.bufs
+        if self.shared.how == "multicast" and (self.per * 2) % 128:
+            raise ValueError("a multicast slice must be whole 128-byte row segments")
         self.step = 0
         self.panels = 1
         self.stream = torch.cuda.ExternalStream(eng.stream())
         self.flag = torch.zeros(1, device=torch.device("cuda", torch.cuda.current_device()))
         self.mesh = MeshExecution(rank, world)
+        self.describe = {"multicast": "each rank's product stores its tiles once at an NVLS multicast address from its epilogue "
+                                      "(multimem.st; the NVSwitch delivers them to every rank's C)",
+                         "peer": "each rank's product stores its tiles into every rank's C from its epilogue (peer stores over NVLink "
+                                 "into symmetric memory)",
+                         "ipc": "each rank's product stores its tiles into every rank's C from its epilogue (peer stores over NVLink "
+                                "through CUDA IPC mappings)"}[self.shared.how] + \
+            "; a one-element all-reduce behind it orders the ranks; no collective on the data"
         dist.barrier()
 
     def run(self) -> int:
@@ -209,11 +288,41 @@ class PeerStoreMatmul:
         import torch.distributed as dist
         which = self.step & 1
         self.step += 1
-        self.eng.matmul_into(self.a, self.b, self.dst[which], (self.m, self.n), self.parts[self.rank][0], True)
+        first = self.parts[self.rank][0]
+        if self.shared.mc[which]:
+            self.eng.matmul_into_multicast(self.a, self.b, self.shared.mc[which], (self.m, self.n), first, True)
+        else:
+            self.eng.matmul_into(self.a, self.b, self.shared.dst[which], (self.m, self.n), first, True)
         with torch.cuda.stream(self.stream):
             dist.all_reduce(self.flag)               # behind the product on the engine's stream: a device-side barrier
-        self.mesh.count(self.world - 1, self.m * self.per * 2 * (self.world - 1))
+        sent = 1 if self.shared.mc[which] else self.world - 1
+        self.mesh.count(sent, self.m * self.per * 2 * sent)
         return self.c[which]
+
+    def run_from_host(self, a_rows_host: int, b_slice_host: int, c_rows_host: int) -> None:
+        """One step with host operands and a host result, the work of bringing them in shared by the ranks: this
+        rank uploads ITS row block of A ([m / world, k]) and its column slice of B from pinned host memory, the row
+        blocks are all-gathered over NVLink into every rank's A, the product runs, and this rank downloads ITS row
+        block of C ([m / world, n]) -- so across the ranks A and B go up once and one C comes down
+        (`Fabric::matmul_resident` leaves one C, on chip 0: crates/tt-kernels/src/shard.rs:444-452).  The three
+        arguments are host addresses; returns when this rank's rows of C are in host memory."""
+        import torch
+        import torch.distributed as dist
+        e, g, r = self.eng, self.world, self.rank
+        rows = self.m // g
+        assert self.m % g == 0
+        if not hasattr(self, "_a_rows"):     # views of this rank's row blocks (`slice_rows`: no copy)
+            self._a_rows = e.slice_rows(self.a, r * rows, rows)[0]
+            self._c_rows = [e.slice_rows(c, r * rows, rows)[0] for c in self.c]
+            a_ptr, _ = e.device_ptr(self.a)
+            self._a_t = _as_tensor(a_ptr, (self.m, self.k), torch.int16).view(torch.bfloat16)
+        which = self.step & 1
+        e.write_ptr(self._a_rows, a_rows_host, rows * self.k, 2)
+        e.write_ptr(self.b, b_slice_host, self.k * self.per, 2)
+        with torch.cuda.stream(self.stream):
+            dist.all_gather_into_tensor(self._a_t, self._a_t[r * rows:(r + 1) * rows])   # in place: the row blocks are contiguous
+        self.run()
+        e.download_into(self._c_rows[which], c_rows_host, rows * self.n, 2)
 
     def release(self, buf: int):
         pass
@@ -222,48 +331,11 @@ class PeerStoreMatmul:
         return self.mesh.report(self.eng.sync)
 
     def close(self):
-        import torch.distributed as dist
-        self.eng.sync()
-        dist.barrier()
-        for p in self.opened:
-            self.eng.ipc_close(p)
-        self.opened = []
-        dist.barrier()                               # every mapping is closed before an owner frees its C
-        for c in self.c:
-            self.eng.free(c)
+        if hasattr(self, "_a_rows"):
+            for v in [self._a_rows] + self._c_rows:
+                self.eng.free(v)
+        self.shared.close()
         self.c = []
-
-    describe = ("each rank's product stores its tiles into every rank's C from its epilogue (peer stores over NVLink through "
-                "CUDA IPC mappings); a one-element all-reduce behind it orders the ranks; no collective on the data")
-
-
-class _Shared:
-    """A [rows, cols] BF16 matrix every rank can store into: two alternating copies, each rank's own
-    buffer first in its destination list, the peers' copies opened through CUDA IPC."""
-
-    def __init__(self, eng, rank: int, world: int, rows: int, cols: int):
-        import torch.distributed as dist
-        self.eng, self.bufs, self.dst, self.opened = eng, [], [], []
-        for _ in range(2):
-            c, _ = eng.zeros_dram((rows, cols), bf16=True)
-            mine, _ = eng.device_ptr(c)
-            handles = [None] * world
-            dist.all_gather_object(handles, eng.ipc_export(c))
-            peers = [eng.ipc_open(handles[r]) for r in range(world) if r != rank]
-            self.bufs.append(c)
-            self.opened += peers
-            self.dst.append([mine] + peers)
-
-    def close(self):
-        import torch.distributed as dist
-        self.eng.sync()
-        dist.barrier()
-        for p in self.opened:
-            self.eng.ipc_close(p)
-        dist.barrier()
-        for c in self.bufs:
-            self.eng.free(c)
-        self.opened, self.bufs = [], []
 
 
 class TpMlp:
@@ -300,11 +372,17 @@ class TpMlp:
         gu, _ = e.matmul_dram_bf16(self.x, False, self.wgu, False)                      # [m, gate_r | up_r]
         act, _ = e.eltwise_blocks_as(EltwiseOp(kinds.SILU_MUL, 0.0, 0.0), (gu, (0, 0), (m, pf)), (gu, (0, pf), (m, pf)), None, True)
         e.free(gu)
-        e.store_block_into((act, (0, 0), (m, pf)), self.hid.dst[which], (m, self.ff), self.rank * pf)
+        if self.hid.mc[which]:
+            e.store_block_into_multicast((act, (0, 0), (m, pf)), self.hid.mc[which], (m, self.ff), self.rank * pf)
+        else:
+            e.store_block_into((act, (0, 0), (m, pf)), self.hid.dst[which], (m, self.ff), self.rank * pf)
         e.free(act)
         with torch.cuda.stream(self.stream):
             dist.all_reduce(self.flag)          # every rank's slice of the activation is here
-        e.matmul_into(self.hid.bufs[which], self.wd, self.out.dst[which], (m, self.hidden), self.rank * self.ph, True)
+        if self.out.mc[which]:
+            e.matmul_into_multicast(self.hid.bufs[which], self.wd, self.out.mc[which], (m, self.hidden), self.rank * self.ph, True)
+        else:
+            e.matmul_into(self.hid.bufs[which], self.wd, self.out.dst[which], (m, self.hidden), self.rank * self.ph, True)
         with torch.cuda.stream(self.stream):
             dist.all_reduce(self.flag)          # every rank's slice of the output is here
         return self.out.bufs[which]
@@ -492,13 +570,20 @@ def bench_main(args, metric, unit, size, workload_name, peaks, ClockSampler, che
     # completion evidence (the reference's `FabricExecution`): every rank's completed products, this rank's transfers
     mesh = sm.mesh_execution()
 
-    # product alone (no gather), to show what the exchange costs
+    # product alone (no exchange), to show what the exchange costs.  The two legs run one after the other under a
+    # power cap that moves, so each carries the SM clock sampled while it ran: compare time x median MHz.
+    for _ in range(3):
+        o, _ = eng.matmul_dram_bf16(a_buf, False, b_buf, False)
+        eng.free(o)
+    sampler2 = ClockSampler(local_rank) if rank == 0 else None
+    dist.barrier()
     eng.sync()
     eng.timer_start()
     for _ in range(args.steps):
         o, _ = eng.matmul_dram_bf16(a_buf, False, b_buf, False)
         eng.free(o)
     ms_mm = eng.timer_stop()
+    clocks_mm = sampler2.stop() if sampler2 else None
     t2 = torch.tensor([ms_mm], device=dev)
     dist.all_reduce(t2, op=dist.ReduceOp.MAX)
     ms_mm = float(t2.item())
@@ -509,32 +594,58 @@ def bench_main(args, metric, unit, size, workload_name, peaks, ClockSampler, che
         try:
             tp_ms, tp_ok, tp_flops = tp_mlp_bench(eng, rank, world, dev)
             tp = {"ms_per_step": tp_ms, "tflops": tp_flops / (tp_ms * 1e-3) / 1e12, "equals_single_gpu_bits": bool(tp_ok),
-                  "shape": "x [4096, 8192] BF16, ff 28672: gate|up and down column-sharded, both gathers by owner stores"}
+                  "shape": "x [4096, 8192] BF16, ff 28672: gate|up and down column-sharded, both gathers by owner stores",
+                  "exchange": sm.shared.how}
         except Exception as ex:
             tp = {"error": str(ex)[:200]}
 
     # end to end: A and the B slice from pinned host memory, the sharded product, C back to the host
     e2e = None
     if not args.no_e2e:
-        a_host = a_t.view(torch.int16).cpu().pin_memory()
-        b_host = b_t.view(torch.int16).cpu().pin_memory()
-        c_host = torch.empty((m, n), dtype=torch.int16).pin_memory()
-        steps = 2
         import time
-        dist.barrier()
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            eng.write_ptr(a_buf, a_host.data_ptr(), m * k, 2)
-            eng.write_ptr(b_buf, b_host.data_ptr(), k * per, 2)
-            full = sm.run()
-            eng.download_into(full, c_host.data_ptr(), m * n, 2)
-            sm.release(full)
-        dt = torch.tensor([(time.perf_counter() - t0) * 1e3 / steps], device=dev)
-        dist.all_reduce(dt, op=dist.ReduceOp.MAX)
-        e2e_ms = float(dt.item())
-        e2e = {"value": 2.0 * m * n * k / (e2e_ms * 1e-3) / 1e12, "unit": unit, "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": world * (m * k + k * per) * 2, "d2h_bytes_per_step": world * m * n * 2}
+        steps = 3
+        if fused and m % world == 0:
+            # every rank brings in its row block of A and its column slice of B and takes out its row block of C:
+            # across the ranks the operands go up once and one C comes down
+            rows = m // world
+            a_host = a_t[rank * rows:(rank + 1) * rows].view(torch.int16).cpu().pin_memory()
+            b_host = b_t.view(torch.int16).cpu().pin_memory()
+            c_host = torch.empty((rows, n), dtype=torch.int16).pin_memory()
+            sm.run_from_host(a_host.data_ptr(), b_host.data_ptr(), c_host.data_ptr())      # warm-up
+            dist.barrier()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                sm.run_from_host(a_host.data_ptr(), b_host.data_ptr(), c_host.data_ptr())
+            dt = torch.tensor([(time.perf_counter() - t0) * 1e3 / steps], device=dev)
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+            e2e_ms = float(dt.item())
+            same = torch.equal(c_host, full_t[rank * rows:(rank + 1) * rows].cpu())          # the rows that came down are C's
+            okh = torch.tensor([1.0 if same else 0.0], device=dev)
+            dist.all_reduce(okh, op=dist.ReduceOp.MIN)
+            e2e = {"value": 2.0 * m * n * k / (e2e_ms * 1e-3) / 1e12, "unit": unit, "ms_per_step": e2e_ms,
+                   "h2d_bytes_per_step": (m * k + k * n) * 2, "d2h_bytes_per_step": m * n * 2,
+                   "call": "PeerStoreMatmul.run_from_host: a rank uploads its rows of A and its columns of B, the rows are "
+                           "all-gathered over NVLink, the product runs, the rank downloads its rows of C",
+                   "host_result_equals_device_result": bool(okh.item() >= 1.0)}
+        else:
+            a_host = a_t.view(torch.int16).cpu().pin_memory()
+            b_host = b_t.view(torch.int16).cpu().pin_memory()
+            c_host = torch.empty((m, n), dtype=torch.int16).pin_memory()
+            dist.barrier()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                eng.write_ptr(a_buf, a_host.data_ptr(), m * k, 2)
+                eng.write_ptr(b_buf, b_host.data_ptr(), k * per, 2)
+                full = sm.run()
+                eng.download_into(full, c_host.data_ptr(), m * n, 2)
+                sm.release(full)
+            dt = torch.tensor([(time.perf_counter() - t0) * 1e3 / steps], device=dev)
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+            e2e_ms = float(dt.item())
+            e2e = {"value": 2.0 * m * n * k / (e2e_ms * 1e-3) / 1e12, "unit": unit, "ms_per_step": e2e_ms,
+                   "h2d_bytes_per_step": world * (m * k + k * per) * 2, "d2h_bytes_per_step": world * m * n * 2}
 
     if rank == 0:
         flops = 2.0 * m * n * k
@@ -551,12 +662,17 @@ def bench_main(args, metric, unit, size, workload_name, peaks, ClockSampler, che
                            "l2": "operands exceed the 126 MB L2; no flush needed",
                            "collective": (f"{sm.panels} " if not fused else "") + sm.describe},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
-                "roofline": {"bound": "tensor", "kernel": "gemm_tc2_kernel with peer stores" if fused else "gemm_tc_kernel + ncclAllGather",
+                "roofline": {"bound": "tensor", "kernel": ("gemm_tc2_kernel storing to " + sm.shared.how) if fused else "gemm_tc_kernel + ncclAllGather",
                              "achieved": value, "peak": peak,
                              "unit": unit, "frac": value / peak, "peak_source": f"{which} cuBLAS bf16 burst x {world}",
                              "traffic": None, "product_only_ms": ms_mm / args.steps,
-                             "gather_bytes_per_rank": gather_bytes,
-                             "gather_floor_ms_at_770GBs": gather_bytes / 770e9 * 1e3},
+                             "product_only_clocks": clocks_mm,
+                             "step_ms_x_mhz": (ms_step * clocks["sm_mhz"]) if clocks and clocks.get("sm_mhz") else None,
+                             "product_only_ms_x_mhz": (ms_mm / args.steps * clocks_mm["sm_mhz"]) if clocks_mm and clocks_mm.get("sm_mhz") else None,
+                             "exchange": getattr(getattr(sm, "shared", None), "how", "nccl all-gather"),
+                             "bytes_received_per_rank": gather_bytes,
+                             "bytes_sent_per_rank": (m * per * 2) if getattr(getattr(sm, "shared", None), "how", "") == "multicast" else gather_bytes,
+                             "receive_floor_ms_at_770GBs": gather_bytes / 770e9 * 1e3},
                 "validated": {"max_err_over_S": float(flags[1].item()), "sharded_equals_single_gpu_bits": True},
                 "tp_mlp": tp, "mesh_execution": mesh}
         print(json.dumps(line))

@@ -65,7 +65,7 @@ cudaError_t launch_sort_planes(const uint32_t*, uint64_t, uint64_t, uint32_t, in
 cudaError_t launch_random(uint32_t*, uint64_t, int, float, float, int32_t, int32_t, int, uint64_t, cudaStream_t) { OK_LAUNCH; }
 cudaError_t launch_pool_windows(const uint16_t*, const uint32_t*, const uint32_t*, const float*, uint64_t, float*, cudaStream_t) { OK_LAUNCH; }
 cudaError_t launch_gemm_simt(const GemmArgs&, cudaStream_t) { OK_LAUNCH; }
-cudaError_t launch_store_block_many(const void*, uint64_t, void* const*, int, uint64_t, uint64_t, uint64_t, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_store_block_many(const void*, uint64_t, void* const*, int, uint64_t, uint64_t, uint64_t, int, cudaStream_t) { OK_LAUNCH; }
 bool gemm_skinny_supported(const GemmArgs& g) { return g.in_bf16 && g.batch <= 1 && !g.a_trans && !g.b_trans && g.m <= 4 && g.n % 8 == 0; }
 cudaError_t launch_gemm_skinny(const GemmArgs&, cudaStream_t) { OK_LAUNCH; }
 bool gemm_tc_supported(const GemmArgs& g, const char** why) {
