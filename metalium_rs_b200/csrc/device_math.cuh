@@ -52,10 +52,19 @@ __device__ __forceinline__ float gelu_erf(float x) {
 }
 // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
 // 0.5 (1 + tanh y) = sigmoid(2y), which keeps its relative accuracy for y << 0.
+// The argument t = 2 sqrt(2/pi) (x + 0.044715 x^3) reaches 11 at |x| = 4 and exp(-t) multiplies every relative error of t
+// by t, so an F32 t (three roundings and a rounded constant) would cost some 30 units in the last place of the result.
+// t is therefore formed in F64 and handed to the exponential as an F32 head and tail: exp(-(h + l)) = exp(-h) (1 - l).
 __device__ __forceinline__ float gelu_tanh(float x) {
-  const float x3 = x * x * x;
-  const float inner = 0.7978845608028654f * (x + 0.044715f * x3);
-  return x * sigmoid_flex(2.0f * inner);
+  const double xd = (double)x;
+  const double t = 1.5957691216057308 * xd * (1.0 + 0.044715 * xd * xd);
+  const double a = fabs(t);
+  const float ah = (float)a;
+  const float al = (float)(a - (double)ah);
+  float e = expf(-ah);
+  e = e - e * al;
+  const float d = 1.0f + e;
+  return x * ((t >= 0.0) ? (1.0f / d) : (e / d));
 }
 
 }  // namespace b200

@@ -111,7 +111,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       bool ok = true;
       for (uint64_t t = cluster_id; t < total_tiles && ok; t += n_clusters) {
         uint64_t b; uint32_t tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, &b, &tm, &tn);
+        tile_coords(t, p.tiles_m, p.tiles_n, &b, &tm, &tn, p.group);
         const int32_t m0 = (int32_t)(tm * 256 + rank * BM), n0 = (int32_t)(tn * P_BN + rank * P_HALF);
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, wait_limit)) { ok = false; break; }
@@ -179,7 +179,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     bool ok = true;
     for (uint64_t t = cluster_id; t < total_tiles && ok; t += n_clusters, ++local) {
       uint64_t b; uint32_t tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, &b, &tm, &tn);
+      tile_coords(t, p.tiles_m, p.tiles_n, &b, &tm, &tn, p.group);
       const uint32_t acc = local & 1, acc_phase = (local >> 1) & 1;
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, wait_limit)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -235,6 +235,7 @@ cudaError_t launch_gemm_tc2(const GemmArgs& g, int* err_word, cudaStream_t strea
   p.n_more = g.n_more;
   p.epi_mode = g.epi_mode;
   p.multicast = g.multicast;
+  p.group = tile_group_setting(TILE_GROUP);
   p.staged = epilogue_staged(g.c, g.c_more, g.n_more, g.ldc, g.out_bf16);
   for (int i = 0; i < 7; ++i) p.c_more[i] = i < g.n_more ? g.c_more[i] : nullptr;
   constexpr size_t smem = (size_t)P_STAGES * (BM * BK * 2 + P_HALF * BK * 2) + 1024 + 256 + EPI_BYTES;

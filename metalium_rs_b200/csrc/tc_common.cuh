@@ -33,6 +33,7 @@ struct TcParams {
   int multicast;             // c is a multicast address (stored once with multimem.st, every row piece whole: no ragged edges)
   int* err;
   uint32_t mn_lbo, mn_sbo;   // byte offsets of an MN-major operand's descriptor
+  uint32_t group;            // tile rows walked together (see tile_coords); 0: the default
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -308,20 +309,27 @@ __device__ __forceinline__ void epilogue_warp_silu_mul(const TcParams& p, uint32
   }
 }
 
-// Tile order: groups of 16 tile rows walked column by column, so the CTAs running at one
-// time share A rows and B columns in L2.
+// Tile order: groups of G tile rows walked column by column, so the CTAs running at one
+// time share A rows and B columns in L2, and a group's A rows stay in L2 from one wave of tiles to the next.
+constexpr uint32_t TILE_GROUP = 16;
 __device__ __forceinline__ void tile_coords(uint64_t t, uint32_t tiles_m, uint32_t tiles_n, uint64_t* batch,
-                                            uint32_t* tm, uint32_t* tn) {
+                                            uint32_t* tm, uint32_t* tn, uint32_t G = TILE_GROUP) {
   const uint64_t per = (uint64_t)tiles_m * tiles_n;
   *batch = t / per;
   const uint32_t r = (uint32_t)(t - *batch * per);
-  constexpr uint32_t G = 16;
   const uint32_t group = r / (G * tiles_n);
   const uint32_t first = group * G;
   const uint32_t rows = (tiles_m - first < G) ? (tiles_m - first) : G;
   const uint32_t in = r - group * G * tiles_n;
   *tm = first + in % rows;
   *tn = in / rows;
+}
+
+// The tile-row group of the pair kernel: B200TT_TILE_GROUP overrides (a development switch).
+inline uint32_t tile_group_setting(uint32_t dflt) {
+  const char* e = getenv("B200TT_TILE_GROUP");
+  const long v = e ? atol(e) : 0;
+  return v > 0 ? (uint32_t)v : dflt;
 }
 
 // Whether every copy of C can take 16-byte stores at every row start.
