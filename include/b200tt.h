@@ -53,7 +53,8 @@ enum b200_status {
 };
 
 /* tt-kernels/src/tensor.rs:751 `Elem` (+ Elem::BF16) */
-enum b200_elem { B200_F32 = 0, B200_I32 = 1, B200_BOOL = 2, B200_BF16 = 3 };
+enum b200_elem { B200_F32 = 0, B200_I32 = 1, B200_BOOL = 2, B200_BF16 = 3,
+                 B200_BFP8 = 4 /* Elem::Packed: block-float storage made by b200_cast_bfp, read by a product as its B */ };
 
 /* tt-kernels/src/sfpu/reduce.rs:56 `ReduceOp`, :117 `Axis` */
 enum b200_reduce_op {
@@ -195,6 +196,19 @@ int32_t b200_eltwise_blocks(b200_engine*, const b200_eltwise_op* op, const b200_
                             b200_buffer* out, uint64_t out_dims[2]);
 /* server.rs:128 `cast_float`: F32 <-> BF16. */
 int32_t b200_cast_float(b200_engine*, b200_buffer a, int32_t to_bf16, b200_buffer* out, uint64_t out_dims[2]);
+/* server.rs:141 `cast_bfp(id, format)`: explicit block-float storage (crates/tt-kernels/src/bfp.rs:60-63: sixteen
+ * consecutive values of a row share an 8-bit exponent, a datum is a sign over a 7-bit magnitude).  format 8: an F32 or
+ * BF16 [rows, cols] buffer (cols % 16 == 0) -> a B200_BFP8 buffer of 17 bytes for 16 values; format 0 (the trait's
+ * `None`): a BFP8 buffer widened to F32; format -16: widened to BF16 (exact: every decoded value is a BF16 value).
+ * Decoding is the reference's `bfp8_to_bf16` (crates/tt-isa/src/tile.rs:619-634); encoding rounds |x| 2^(133 - E) to
+ * nearest even under the group's largest exponent E, so a decoded value is within half a step 2^(E - 133) of what was
+ * stored; -0 and values that round to magnitude 0 are stored +0 (the format has no -0), groups below 2^-119 are stored as
+ * zeros, and a group with an infinity or a NaN keeps those and zeroes its finite members.  BFP4 and BFP2 are refused.
+ * `b200_matmul` takes a BFP8 buffer as B (not transposed): bit for bit the product with B widened.  Every other op
+ * refuses a BFP8 buffer. */
+int32_t b200_cast_bfp(b200_engine*, b200_buffer a, int32_t format, b200_buffer* out, uint64_t out_dims[2]);
+/* The stored bytes of a BFP8 buffer: rows * cols datums (row-major) and rows * cols / 16 exponents (row-major). */
+int32_t b200_download_bfp(b200_engine*, b200_buffer id, uint8_t* datums, uint8_t* exponents, uint64_t capacity_datums);
 /* server.rs:566 `rope_blocks` */
 int32_t b200_rope_blocks(b200_engine*, const b200_block_arg* x, const b200_block_arg* cos_,
                          const b200_block_arg* sin_, uint64_t head, int32_t out_bf16,

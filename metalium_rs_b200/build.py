@@ -38,6 +38,7 @@ SOURCES = {
     "k_attention.cu": [],
     "k_attention_tc.cu": [],
     "k_convert.cu": [],
+    "k_bfp.cu": [],
     "k_pool.cu": ["-fmad=false"],
     "k_scan_sort.cu": ["-fmad=false"],
     "k_random.cu": ["-fmad=false"],

@@ -58,7 +58,7 @@ __device__ __forceinline__ float gelu_erf(float x) {
 __device__ __forceinline__ float gelu_tanh(float x) {
   const double xd = (double)x;
   const double t = 1.5957691216057308 * xd * (1.0 + 0.044715 * xd * xd);
-  const double a = fabs(t);
+  const double a = fmin(fabs(t), 128.0);   // exp(-128) is already 0 in F32; the bound keeps the head finite (a NaN t gives 128, x itself carries the NaN)
   const float ah = (float)a;
   const float al = (float)(a - (double)ah);
   float e = expf(-ah);

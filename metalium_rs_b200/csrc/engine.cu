@@ -49,6 +49,11 @@ struct Buf {
 };
 
 inline uint64_t elem_bytes(int elem) { return elem == B200_BF16 ? 2 : 4; }
+// Bytes a [rows, cols] buffer of `elem` holds: a BFP8 matrix is a datum byte an element and an exponent byte
+// for every sixteen of a row (csrc/k_bfp.cu).
+inline uint64_t buffer_bytes(uint64_t rows, uint64_t cols, int elem) {
+  return elem == B200_BFP8 ? rows * cols + rows * cols / 16 : rows * cols * elem_bytes(elem);
+}
 
 }  // namespace
 
@@ -210,7 +215,7 @@ struct b200_engine {
   int new_buffer(uint64_t rows, uint64_t cols, int elem, b200_buffer* id, Buf** out) {
     void* p = nullptr;
     uint64_t got = 0;
-    const uint64_t bytes = rows * cols * elem_bytes(elem);
+    const uint64_t bytes = buffer_bytes(rows, cols, elem);
     int st = alloc(bytes, &p, &got);
     if (st) return st;
     Buf b;
@@ -225,9 +230,14 @@ struct b200_engine {
     if (it == bufs.end() || it->second.freed) return nullptr;
     return &it->second;
   }
-  int need(b200_buffer id, Buf** out, const char* what) {
+  // A BFP8 buffer is read only by the ops that say so (`packed_ok`): every other op sees plain 16- or 32-bit
+  // elements and is refused a packed one here, before it could misread the bytes.
+  int need(b200_buffer id, Buf** out, const char* what, bool packed_ok = false) {
     Buf* b = get(id);
     if (!b) return fail(B200_STALE, "%s: buffer %llu is not live on this engine", what, (unsigned long long)id);
+    if (b->elem == B200_BFP8 && !packed_ok)
+      return fail(B200_UNSUPPORTED, "%s: buffer %llu is BFP8 storage; a product reads it as its B, cast_bfp widens it, nothing else reads it",
+                  what, (unsigned long long)id);
     *out = b;
     return B200_OK;
   }
@@ -750,8 +760,36 @@ int32_t b200_matmul(b200_engine* e, b200_buffer a, int32_t ta, b200_buffer b, in
   cudaSetDevice(e->device);
   Buf *A = nullptr, *B = nullptr;
   int st = e->need(a, &A, "matmul");
-  if (!st) st = e->need(b, &B, "matmul");
+  if (!st) st = e->need(b, &B, "matmul", true);
   if (st) return st;
+  if (B->elem == B200_BFP8) {
+    // A weight kept as BFP8 (crates/burn-tt/src/storage.rs:117-123): a BF16 activation of a few rows reads it where it
+    // lies, decoding in the product's load path; anything else multiplies by the weight widened for the call --
+    // bit for bit the product with the decoded values either way (every decoded value is a BF16 value).
+    if (A->elem != B200_BF16 && A->elem != B200_F32) return e->fail(B200_UNSUPPORTED, "matmul: A must be F32 or BF16 against a BFP8 B");
+    const uint64_t m = ta ? A->cols : A->rows, k = ta ? A->rows : A->cols;
+    if (!ta && !tb && A->elem == B200_BF16 && B->rows == k && k > 0 && gemm_skinny_bfp_supported(m, B->cols, k) &&
+        e->cfg.bf16_matmul_mode == 0) {
+      const uint64_t n = B->cols;
+      Buf* C = nullptr;
+      st = e->new_buffer(m, n, out_bf16 ? B200_BF16 : B200_F32, out, &C);
+      if (st) return st;
+      A = e->get(a); B = e->get(b);
+      const uint8_t* datums = (const uint8_t*)B->ptr;
+      st = e->launched(launch_gemm_skinny_bfp((const uint16_t*)A->ptr, A->cols, datums, datums + B->rows * B->cols, C->ptr, n, out_bf16,
+                                              m, n, k, e->stream), "matmul");
+      if (st) { e->drop(*out); return st; }
+      e->matmul_path = "skinny-bfp8";
+      set_dims(out_dims, m, n);
+      return B200_OK;
+    }
+    b200_buffer wide = 0; uint64_t wd[2];
+    st = b200_cast_bfp(e, b, A->elem == B200_BF16 ? -16 : 0, &wide, wd);
+    if (st) return st;
+    st = b200_matmul(e, a, ta, wide, tb, out_bf16, out, out_dims);
+    e->drop(wide);
+    return st;
+  }
   const bool abf = A->elem == B200_BF16, bbf = B->elem == B200_BF16;
   if ((A->elem != B200_F32 && !abf) || (B->elem != B200_F32 && !bbf))
     return e->fail(B200_UNSUPPORTED, "matmul: operands must be F32 or BF16 (got elem %d, %d)", A->elem, B->elem);
@@ -1137,6 +1175,58 @@ int32_t b200_cast_float(b200_engine* e, b200_buffer a, int32_t to_bf16, b200_buf
   if (st) { e->drop(*out); return st; }
   set_dims(out_dims, rows, cols);
   return B200_OK;
+}
+
+// server.rs:141 `cast_bfp(id, format)`: F32 (or BF16) -> BFP8 storage (`format` 8), or BFP8 widened (`format` 0: to F32,
+// the trait's `None`; -16: to BF16, which holds every decoded value exactly).
+int32_t b200_cast_bfp(b200_engine* e, b200_buffer a, int32_t format, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf* A = nullptr;
+  int st = e->need(a, &A, "cast_bfp", true);
+  if (st) return st;
+  const uint64_t rows = A->rows, cols = A->cols;
+  Buf* O = nullptr;
+  if (format == 8) {
+    if (A->elem != B200_F32 && A->elem != B200_BF16) return e->fail(B200_UNSUPPORTED, "cast_bfp: source elem %d is not F32 or BF16", A->elem);
+    if (cols % 16) return e->fail(B200_UNSUPPORTED, "cast_bfp: %llu columns are not whole groups of sixteen", (unsigned long long)cols);
+    st = e->new_buffer(rows, cols, B200_BFP8, out, &O);
+    if (st) return st;
+    A = e->get(a);
+    uint8_t* datums = (uint8_t*)O->ptr;
+    st = e->launched(launch_bfp8_encode(A->ptr, A->elem == B200_BF16, rows, cols, datums, datums + rows * cols, e->stream), "cast_bfp");
+  } else if (format == 0 || format == -16) {
+    if (A->elem != B200_BFP8) return e->fail(B200_UNSUPPORTED, "cast_bfp: buffer %llu is not BFP8 storage", (unsigned long long)a);
+    st = e->new_buffer(rows, cols, format == 0 ? B200_F32 : B200_BF16, out, &O);
+    if (st) return st;
+    A = e->get(a);
+    const uint8_t* datums = (const uint8_t*)A->ptr;
+    st = e->launched(launch_bfp8_decode(datums, datums + rows * cols, rows, cols, O->ptr, format != 0, e->stream), "cast_bfp");
+  } else {
+    return e->fail(B200_UNSUPPORTED, "cast_bfp: format %d (8 stores BFP8, 0 widens to F32, -16 to BF16; BFP4 and BFP2 are not kept by this engine)", format);
+  }
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, rows, cols);
+  return B200_OK;
+}
+
+// The stored bytes of a BFP8 buffer, as they lie: rows * cols datums, then rows * cols / 16 exponents.
+int32_t b200_download_bfp(b200_engine* e, b200_buffer id, uint8_t* datums, uint8_t* exponents, uint64_t capacity_datums) {
+  cudaSetDevice(e->device);
+  if (e->capturing) return e->fail(B200_UNSUPPORTED, "download_bfp inside a trace capture");
+  Buf* A = nullptr;
+  int st = e->need(id, &A, "download_bfp", true);
+  if (st) return st;
+  if (A->elem != B200_BFP8) return e->fail(B200_UNSUPPORTED, "download_bfp: buffer %llu is not BFP8 storage", (unsigned long long)id);
+  const uint64_t n = A->rows * A->cols;
+  if (capacity_datums < n) return e->fail(B200_UNSUPPORTED, "download_bfp: %llu datums into room for %llu", (unsigned long long)n, (unsigned long long)capacity_datums);
+  if (n) {
+    cudaError_t ce = cudaMemcpyAsync(datums, A->ptr, n, cudaMemcpyDeviceToHost, e->stream);
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(exponents, (const uint8_t*)A->ptr + n, n / 16, cudaMemcpyDeviceToHost, e->stream);
+    if (ce != cudaSuccess) return e->cuda_fail(ce, "download_bfp");
+  }
+  e->traffic.bytes_d2h += n + n / 16;
+  e->traffic.d2h_calls++;
+  return e->wait();
 }
 
 int32_t b200_rope_blocks(b200_engine* e, const b200_block_arg* x, const b200_block_arg* cs, const b200_block_arg* sn,

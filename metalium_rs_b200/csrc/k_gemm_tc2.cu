@@ -235,7 +235,7 @@ cudaError_t launch_gemm_tc2(const GemmArgs& g, int* err_word, cudaStream_t strea
   p.n_more = g.n_more;
   p.epi_mode = g.epi_mode;
   p.multicast = g.multicast;
-  p.group = tile_group_setting(TILE_GROUP);
+  p.group = tile_group_setting(TILE_GROUP_PAIR);
   p.staged = epilogue_staged(g.c, g.c_more, g.n_more, g.ldc, g.out_bf16);
   for (int i = 0; i < 7; ++i) p.c_more[i] = i < g.n_more ? g.c_more[i] : nullptr;
   constexpr size_t smem = (size_t)P_STAGES * (BM * BK * 2 + P_HALF * BK * 2) + 1024 + 256 + EPI_BYTES;

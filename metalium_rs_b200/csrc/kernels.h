@@ -183,6 +183,16 @@ cudaError_t launch_random(uint32_t* out, uint64_t n, int draw, float p0, float p
 cudaError_t launch_pool_windows(const uint16_t* in, const uint32_t* offsets_dev, const uint32_t* flat_dev,
                                 const float* divisors_dev, uint64_t n, float* out, cudaStream_t stream);
 
+// BFP8 storage (k_bfp.cu): [rows, cols] values (cols % 16 == 0) <-> rows * cols datum bytes + rows * cols / 16 exponent bytes.
+cudaError_t launch_bfp8_encode(const void* in, int in_bf16, uint64_t rows, uint64_t cols, uint8_t* datums, uint8_t* exps,
+                               cudaStream_t stream);
+cudaError_t launch_bfp8_decode(const uint8_t* datums, const uint8_t* exps, uint64_t rows, uint64_t cols, void* out, int out_bf16,
+                               cudaStream_t stream);
+// The few-row product with B read as BFP8 (m <= 4, n a multiple of 16, A BF16 as stored, B as stored).
+bool gemm_skinny_bfp_supported(uint64_t m, uint64_t n, uint64_t k);
+cudaError_t launch_gemm_skinny_bfp(const uint16_t* a, uint64_t lda, const uint8_t* datums, const uint8_t* exps, void* c, uint64_t ldc,
+                                   int out_bf16, uint64_t m, uint64_t n, uint64_t k, cudaStream_t stream);
+
 // Text for `b200_last_error(NULL, ...)`: failures of calls that take no engine.
 void set_global_error(const char* text);
 

@@ -311,7 +311,10 @@ __device__ __forceinline__ void epilogue_warp_silu_mul(const TcParams& p, uint32
 
 // Tile order: groups of G tile rows walked column by column, so the CTAs running at one
 // time share A rows and B columns in L2, and a group's A rows stay in L2 from one wave of tiles to the next.
-constexpr uint32_t TILE_GROUP = 16;
+constexpr uint32_t TILE_GROUP = 16;       // the single-CTA kernels' (128-row tiles)
+constexpr uint32_t TILE_GROUP_PAIR = 8;   // the pair kernel's (256-row tiles): 8 x 9 tiles a wave of 74 clusters, and the group's eight
+                                          // A row panels (34 MB at k = 8192) stay in L2 from wave to wave.  Measured at 8192^3, same box:
+                                          // groups of 2 / 4 / 8 / 16 / 32 rows give 1,470 / 1,530 / 1,555 / 1,521 / 1,430 TFLOP/s
 __device__ __forceinline__ void tile_coords(uint64_t t, uint32_t tiles_m, uint32_t tiles_n, uint64_t* batch,
                                             uint32_t* tm, uint32_t* tn, uint32_t G = TILE_GROUP) {
   const uint64_t per = (uint64_t)tiles_m * tiles_n;

@@ -22,7 +22,7 @@ _LIB_PATH = Path(__file__).resolve().parent / "libb200tt.so"
 _lib = None
 
 OK, OUT_OF_MEMORY, UNSUPPORTED, DEVICE, TIMEOUT, STALE, DOMAIN, NO_DEVICE = range(8)
-F32, I32, BOOL, BF16 = range(4)
+F32, I32, BOOL, BF16, BFP8 = range(5)
 SUM, MAX, PROD, ALL, ANY, BITOR, SUM_I32, PROD_I32, MIN_I32, MAX_I32 = range(10)
 ROWS, COLS = 0, 1
 # crates/tt-kernels/src/sfpu/scan.rs:19-41 `ScanOp`, in its order
@@ -409,6 +409,20 @@ class CudaEngine:
     def cast_float(self, a: int, bf16: bool) -> Out:
         return self._call(self._lib.b200_cast_float, C.c_uint64(a), C.c_int32(bf16))
 
+    def cast_bfp(self, a: int, format: Optional[int]) -> Out:
+        """`cast_bfp(id, format)` (server.rs:141): format 8 stores an F32 or BF16 buffer as BFP8; None widens a BFP8
+        buffer to F32 (the trait's `None`); "bf16" widens it to BF16."""
+        code = {8: 8, None: 0, "bf16": -16}[format]
+        return self._call(self._lib.b200_cast_bfp, C.c_uint64(a), C.c_int32(code))
+
+    def download_bfp(self, buf: int):
+        """(datums u8 [rows, cols], exponents u8 [rows, cols / 16]) of a BFP8 buffer, as stored."""
+        (rows, cols), elem = self.dims_of(buf)
+        d = np.empty((rows, cols), dtype=np.uint8)
+        x = np.empty((rows, max(cols // 16, 1)), dtype=np.uint8)
+        self._check(self._lib.b200_download_bfp(self._e, C.c_uint64(buf), _ptr(d), _ptr(x), C.c_uint64(d.size)))
+        return d, x[:, :cols // 16]
+
     def rope_blocks(self, x, cos, sin, head: int, bf16: bool = False) -> Out:
         bx, bc, bs = _block(x), _block(cos), _block(sin)
         return self._call(self._lib.b200_rope_blocks, C.byref(bx), C.byref(bc), C.byref(bs), C.c_uint64(head),
@@ -768,5 +782,5 @@ class CudaEngine:
 
 __all__ = ["CudaEngine", "TtError", "EltwiseOp", "Block", "BlockMove", "BlockArg", "BatchedLayout", "Traffic", "OpStat",
            "load_library", "library_path", "kinds",
-           "F32", "I32", "BOOL", "BF16", "SUM", "MAX", "PROD", "ALL", "ANY", "BITOR", "SUM_I32", "PROD_I32",
+           "F32", "I32", "BOOL", "BF16", "BFP8", "SUM", "MAX", "PROD", "ALL", "ANY", "BITOR", "SUM_I32", "PROD_I32",
            "MIN_I32", "MAX_I32", "ROWS", "COLS"]

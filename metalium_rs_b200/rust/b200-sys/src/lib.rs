@@ -45,6 +45,8 @@ extern "C" {
     pub fn b200_eltwise(a0: *mut b200_engine, op: *const b200_eltwise_op, a: u64, b: u64, c: u64, out_bf16: i32, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_eltwise_blocks(a0: *mut b200_engine, op: *const b200_eltwise_op, a: *const b200_block_arg, b: *const b200_block_arg, c: *const b200_block_arg, out_bf16: i32, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_cast_float(a0: *mut b200_engine, a: u64, to_bf16: i32, out: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_cast_bfp(a0: *mut b200_engine, a: u64, format: i32, out: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_download_bfp(a0: *mut b200_engine, id: u64, datums: *mut u8, exponents: *mut u8, capacity_datums: u64) -> i32;
     pub fn b200_rope_blocks(a0: *mut b200_engine, x: *const b200_block_arg, cos_: *const b200_block_arg, sin_: *const b200_block_arg, head: u64, out_bf16: i32, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_reduce(a0: *mut b200_engine, a: u64, op: i32, axis: i32, then_kind: u32, then_bits: u32, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_sum_rows(a0: *mut b200_engine, a: u64, out: *mut u64, out_dims: *mut u64) -> i32;

@@ -364,6 +364,13 @@ impl Engine for CudaEngine {
     // A logical F32 buffer kept as BF16 (half the bytes, read by a product as its B) and back: the storage is
     // plain BF16 here, and `b200_matmul` takes one F32 and one BF16 operand (server.rs:150-158).
     fn cast_bf16_storage(&mut self, id: BufferId, store: bool) -> Made { produce!(self, b200_cast_float(id, store as i32)) }
+    // Explicit block-float storage (server.rs:141): BFP8 is kept; BFP4 and BFP2 are refused by the engine (format codes
+    // 4 and 2 are not ones it takes).  `None` widens to F32.
+    fn cast_bfp(&mut self, id: BufferId, format: Option<tt_kernels::bfp::BfpFormat>) -> Made {
+        use tt_kernels::bfp::BfpFormat::*;
+        let code = match format { None => 0, Some(Bfp8) => 8, Some(Bfp4) => 4, Some(Bfp2) => 2 };
+        produce!(self, b200_cast_bfp(id, code))
+    }
     fn cast_f16(&mut self, id: BufferId, to_f16: bool) -> Made { produce!(self, b200_cast_f16(id, to_f16 as i32)) }
     fn pow(&mut self, x: BufferId, y: PowArg) -> Made {
         match y {

@@ -866,3 +866,61 @@ def max_pool2d(x_bits: np.ndarray, kernel, stride, padding, dilation) -> np.ndar
                     best = np.where(take, b, best)
             out[:, :, y, xo] = best
     return out
+
+
+# ------------------------------------------------------------------ block-float storage (BFP8)
+def bfp8_decode_bits(datum, exp) -> np.ndarray:
+    """BF16 bits of BFP8 datums under their groups' exponents: crates/tt-isa/src/tile.rs:619-634 (`bfp8_to_bf16`)
+    restated for arrays.  Magnitude 0 is +0, or -infinity under a set sign bit (the format has no -0, tile.rs:606-617);
+    otherwise the 7-bit magnitude is normalised and the exponent reduced by the shift, wrapping as a uint8_t does."""
+    datum = np.asarray(datum, dtype=np.uint8)
+    exp = np.asarray(exp, dtype=np.uint8)
+    sign = (datum >> 7).astype(np.uint16)
+    mag = ((datum.astype(np.uint16) << 1) & 0xFF).astype(np.uint16)
+    lz = np.zeros(mag.shape, np.int32)
+    m = mag.copy()
+    for s in (4, 2, 1):                                     # leading zeros of an 8-bit word, by halving
+        top_clear = (m >> (8 - s)) == 0
+        lz = np.where(top_clear & (m != 0), lz + s, lz)
+        m = np.where(top_clear, (m << s) & 0xFF, m)
+    e = ((exp.astype(np.int32) - lz) & 0xFF).astype(np.uint16)
+    out = (sign << 15) | (e << 7) | (m & 0x7E)
+    return np.where(mag == 0, np.where(sign != 0, np.uint16(0xFF80), np.uint16(0)), out).astype(np.uint16)
+
+
+def bfp8_encode(x: np.ndarray):
+    """x [rows, cols] F32, cols a multiple of 16 -> (datums u8 [rows, cols], exponents u8 [rows, cols / 16]): sixteen
+    consecutive values of a row share an exponent (crates/tt-kernels/src/bfp.rs:60-63).  The reference's encoder is its
+    packer hardware; this is the engine's rule, stated in csrc/k_bfp.cu: the largest F32 exponent of the group, magnitudes
+    |x| 2^(133 - E) rounded to nearest even, one exponent up if a magnitude reaches 128; zero magnitudes stored +0;
+    groups below 2^-119 stored as zeros; a group with an infinity or a NaN keeps those and zeroes the rest."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    r, c = x.shape
+    g = x.reshape(r, c // 16, 16)
+    bits = g.view(np.uint32)
+    ef = ((bits >> 23) & 0xFF).astype(np.int32)
+    nonfinite = ef == 255
+    E = ef.max(axis=2)
+    a = np.abs(g).astype(np.float64)
+
+    def mags(E):
+        with np.errstate(over="ignore", invalid="ignore"):
+            return np.rint(a * np.ldexp(1.0, 133 - E)[..., None])
+    m = mags(E)
+    E = np.where((m >= 128).any(axis=2) & (E < 254), E + 1, E)
+    m = np.minimum(mags(E), 127)
+    tiny = E <= 7
+    m = np.where(tiny[..., None], 0, m)
+    E = np.where(tiny, 0, E)
+    has_nf = nonfinite.any(axis=2)
+    m = np.where(has_nf[..., None], np.where(np.isnan(g), 96, np.where(nonfinite, 64, 0)), m)
+    E = np.where(has_nf, 255, E)
+    m = m.astype(np.uint8)
+    sign = ((bits >> 31).astype(np.uint8) << 7)
+    d = np.where(m == 0, np.uint8(0), sign | m).astype(np.uint8)
+    return d.reshape(r, c), E.astype(np.uint8)
+
+
+def bfp8_decode(datums: np.ndarray, exps: np.ndarray) -> np.ndarray:
+    """The F32 values a stored BFP8 matrix decodes to."""
+    return from_bf16(bfp8_decode_bits(datums, np.repeat(exps, 16, axis=1)))

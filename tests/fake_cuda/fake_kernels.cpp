@@ -81,6 +81,11 @@ cudaError_t launch_gemm_tc(const GemmArgs&, const GemmBatch*, int*, cudaStream_t
   OK_LAUNCH;
 }
 cudaError_t launch_stalled_wait(int*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_bfp8_encode(const void*, int, uint64_t, uint64_t, uint8_t*, uint8_t*, cudaStream_t) { OK_LAUNCH; }
+cudaError_t launch_bfp8_decode(const uint8_t*, const uint8_t*, uint64_t, uint64_t, void*, int, cudaStream_t) { OK_LAUNCH; }
+bool gemm_skinny_bfp_supported(uint64_t m, uint64_t n, uint64_t) { return m >= 1 && m <= 4 && n % 16 == 0; }
+cudaError_t launch_gemm_skinny_bfp(const uint16_t*, uint64_t, const uint8_t*, const uint8_t*, void*, uint64_t, int, uint64_t, uint64_t, uint64_t,
+                                   cudaStream_t) { OK_LAUNCH; }
 bool gemm_tc2_wanted(const GemmArgs&) { return false; }
 cudaError_t launch_gemm_tc2(const GemmArgs&, int*, cudaStream_t) { OK_LAUNCH; }
 bool gemm_tf32_supported(const GemmArgs& g, const char** why) { *why = "small"; return !g.in_bf16 && g.batch <= 1 && g.m >= 128 && g.n >= 128 && g.k >= 32; }

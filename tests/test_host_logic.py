@@ -504,3 +504,24 @@ def test_profile_mode_state_machine(fake, e):
     assert e.profile_report() == table
     e.set_op_label("after")                                                     # off: labels cost nothing and record nothing
     assert e.profile_report() == table
+
+
+def test_bfp8_storage_dims_bytes_and_refusals(e):                  # server.rs:141 `cast_bfp`
+    from metalium_rs_b200 import BFP8
+    w = f32(e, 64, 96)
+    in_use = e.device_traffic().pool_in_use
+    packed, dims = e.cast_bfp(w, 8)
+    assert dims == (64, 96) and e.dims_of(packed) == ((64, 96), BFP8)
+    assert e.device_traffic().pool_in_use - in_use == 8192         # 64 * 96 * 17 / 16 = 6,528 bytes, in a pool block of 8,192
+    assert e.cast_bfp(packed, None)[1] == (64, 96) and e.dims_of(e.cast_bfp(packed, "bf16")[0])[1] == BF16
+    a = e.upload_bf16(np.zeros((2, 64), np.uint16), 2, 64)
+    assert e.matmul_dram_bf16(a, False, packed, False)[1] == (2, 96) and e.last_matmul_path() == "skinny-bfp8"
+    tall = e.upload_bf16(np.zeros((128, 64), np.uint16), 128, 64)
+    assert e.matmul_dram_bf16(tall, False, packed, False)[1] == (128, 96) and e.last_matmul_path() == "tcgen05"   # widened for the call
+    for bad in (lambda: e.cast_bfp(w, None), lambda: e.cast_bfp(packed, 8), lambda: e.cast_bfp(f32(e, 4, 24), 8),
+                lambda: e.download(packed), lambda: e.eltwise_op(EltwiseOp(kinds.EXP, 0, 0), packed),
+                lambda: e.reduce(packed, SUM, ROWS), lambda: e.matmul_dram(packed, False, w, False),
+                lambda: e.slice_rows(packed, 0, 32)):
+        with pytest.raises(TtError) as err:
+            bad()
+        assert err.value.status == 2
