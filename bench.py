@@ -662,8 +662,9 @@ def callers(eng, timed):
                                               "composed_argmax_agrees": a3 == a2})
 
     # generation: decode steps over a fixed-shape KV cache, one traced step replayed a token
-    for nb in (1, 8):
-        dec = W.LlamaDecode(eng, cfg, model.w, nb, max_len=512, attend=256)
+    for nb, fused, storage in ((1, False, "bf16"), (8, False, "bf16"), (1, True, "bf16"), (4, True, "bf16"), (1, True, "bfp8"),
+                               (1, False, "bfp8")):
+        dec = W.LlamaDecode(eng, cfg, model.w, nb, max_len=512, attend=256, fused=fused, weight_storage=storage)
         start = rng.integers(0, cfg.vocab, nb).astype(np.int32)
         dec.reset(start)
         dlg, dam = dec.capture()
@@ -674,7 +675,12 @@ def callers(eng, timed):
         dms = timed(dec.replay, reps=64, warm=4)          # positions 1..69 of the 256 attended
         toks = dec.generated(0, 69)
         eng.release_trace(dec.trace); eng.free(dlg); eng.free(dam)
-        res[f"smollm2_135m_decode_step_batch{nb}"] = {"ms_per_step": dms, "tok_per_s": nb / (dms * 1e-3), "launches_per_step": int(dper),
+        for pk in dec.packed:
+            eng.free(pk)
+        name = f"smollm2_135m_decode_step_batch{nb}" + ("_one_launch" if fused else "") + ("_bfp8" if storage == "bfp8" else "")
+        res[name] = {"ms_per_step": dms, "tok_per_s": nb / (dms * 1e-3), "launches_per_step": int(dper),
+                                                     "layers": "one cooperative launch" if fused else "composed of the trait's ops",
+                                                     "weights": storage,
                                                      "mode": "traced (one CUDA graph replay a token, nothing read back between steps)",
                                                      "attended_positions": 256, "distinct_tokens_generated": int(len(np.unique(toks)))}
     bh, t, d = 256, 2048, 128

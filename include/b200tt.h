@@ -402,6 +402,29 @@ int32_t b200_attention_blocks(b200_engine*, b200_buffer q, b200_buffer k, b200_b
                               float scale, int32_t causal, const uint64_t result_dims[2],
                               b200_buffer* out, uint64_t out_dims[2]);
 
+/* --- one generation step through every layer, as one launch (an extension beside the trait, as
+ * `b200_attention_blocks` is).  The reference's generation replays a trace of its step (crates/tt-models/src/
+ * generate.rs:781); composed from the trait's ops a step is eleven launches a layer whose latencies dwarf the work of
+ * reading a layer's weights once, so the layers' device work is also offered as ONE cooperative kernel (five grid
+ * barriers a layer, every one bounded: B200_TIMEOUT when one runs out).
+ *   x               [rows, hidden] F32: the embedded tokens, one row a sequence (1 <= rows <= 4)
+ *   layer_buffers   8 ids a layer: norm1 gain, Wqkv [hidden, (heads + 2 kv_heads) 64], Wo [heads 64, hidden], norm2 gain,
+ *                   Wgate|Wup [hidden, 2 ff], Wdown [ff, hidden], key cache, value cache ([rows * max_len, kv_heads 64]
+ *                   BF16, position-major as crates/tt-models/src/kv_cache.rs:5-11).  Gains BF16; matrices BF16 or BFP8.
+ *   cos/sin tables  F32 [max_len, 64] (sin as [-sin, sin]: crates/tt-models/src/rope.rs:19-60); position: one I32 on the
+ *                   device, the step's position in every sequence (a position outside the cache is DOMAIN).
+ * Per layer (crates/tt-models/src/llama.rs:371-507): RMSNorm, QKV (rounded to BF16), RoPE in F32, the key (rounded once
+ * to BF16) and value written into the cache at `position`, attention over positions 0..position of the first `attend`
+ * (scale, mask, softmax, P V; a BF16 result), the output projection, the residual add, RMSNorm, gate|up (BF16),
+ * SILU_MUL (BF16), down, the residual add.  The result is the final RMSNorm of the stream as BF16 [rows, hidden]: the
+ * head product's input.  The same steps, roundings included, as the composed sequence of trait ops; sums are taken in
+ * this kernel's own fixed order, so the two agree to F32 rounding, not bit for bit.  Refused unless head_dim is 64,
+ * heads / kv_heads <= 4, hidden and ff are multiples of 64 and attend is a multiple of 64 within max_len. */
+typedef struct { uint32_t layers, hidden, heads, kv_heads, head_dim, ff, max_len, attend; float eps, scale; } b200_decode_shape;
+int32_t b200_decode_layers(b200_engine*, const b200_decode_shape* shape, b200_buffer x, const b200_buffer* layer_buffers,
+                           b200_buffer final_norm, b200_buffer cos_table, b200_buffer sin_table, b200_buffer position,
+                           b200_buffer* out, uint64_t out_dims[2]);
+
 /* --- traces: server.rs:591 `begin_trace`, :595 `end_trace`, :650 `run_trace`, :660 `release_trace`.
  * Ops issued between begin and end are captured into a CUDA graph instead of running; a replay
  * runs them again on the same buffers.  Inputs are buffers made before the capture (refresh them

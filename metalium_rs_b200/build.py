@@ -39,6 +39,7 @@ SOURCES = {
     "k_attention_tc.cu": [],
     "k_convert.cu": [],
     "k_bfp.cu": [],
+    "k_decode.cu": [],
     "k_pool.cu": ["-fmad=false"],
     "k_scan_sort.cu": ["-fmad=false"],
     "k_random.cu": ["-fmad=false"],

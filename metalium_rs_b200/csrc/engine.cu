@@ -2228,6 +2228,84 @@ int32_t b200_free_bytes(b200_engine* e, uint64_t out[2]) {
   return B200_OK;
 }
 
+// ---- one decode step through every layer, as one launch ---------------------------
+// What a generation step (crates/tt-models/src/generate.rs:781) asks of the engine between the embedding and the head,
+// as one cooperative kernel instead of eleven launches a layer (csrc/k_decode.cu).  An extension beside the trait, as
+// `b200_attention_blocks` is: the composed step stays available and the two are held together by a test.
+int32_t b200_decode_layers(b200_engine* e, const b200_decode_shape* shape, b200_buffer x, const b200_buffer* layer_buffers,
+                           b200_buffer final_norm, b200_buffer cos_table, b200_buffer sin_table, b200_buffer position,
+                           b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *X = nullptr, *FN = nullptr, *CS = nullptr, *SN = nullptr, *P = nullptr;
+  int st = e->need(x, &X, "decode_layers");
+  if (!st) st = e->need(final_norm, &FN, "decode_layers");
+  if (!st) st = e->need(cos_table, &CS, "decode_layers");
+  if (!st) st = e->need(sin_table, &SN, "decode_layers");
+  if (!st) st = e->need(position, &P, "decode_layers");
+  if (st) return st;
+  DecodeShape sh{};
+  sh.layers = shape->layers; sh.rows = (uint32_t)X->rows; sh.hidden = shape->hidden; sh.heads = shape->heads;
+  sh.kv_heads = shape->kv_heads; sh.head_dim = shape->head_dim; sh.ff = shape->ff; sh.max_len = shape->max_len;
+  sh.attend = shape->attend; sh.eps = shape->eps; sh.scale = shape->scale;
+  const char* why = "";
+  if (X->rows > 4 || !decode_layers_supported(sh, &why))
+    return e->fail(B200_UNSUPPORTED, "decode_layers: this kernel takes %s", X->rows > 4 ? "one to four sequences a step" : why);
+  const uint64_t H = sh.hidden, QC = (uint64_t)sh.heads * 64, KC = (uint64_t)sh.kv_heads * 64, FF = sh.ff;
+  if (X->elem != B200_F32 || X->cols != H) return e->fail(B200_UNSUPPORTED, "decode_layers: x must be F32 [rows, %llu]", (unsigned long long)H);
+  if (FN->elem != B200_BF16 || FN->rows * FN->cols != H) return e->fail(B200_UNSUPPORTED, "decode_layers: the final gain must be BF16 of %llu values", (unsigned long long)H);
+  if (CS->elem != B200_F32 || SN->elem != B200_F32 || CS->cols != 64 || SN->cols != 64 || CS->rows < sh.max_len || SN->rows < sh.max_len)
+    return e->fail(B200_UNSUPPORTED, "decode_layers: the RoPE tables must be F32 [max_len, 64]");
+  if (P->elem != B200_I32 || P->rows * P->cols != 1) return e->fail(B200_UNSUPPORTED, "decode_layers: the position must be one I32");
+  std::vector<DecodeLayerPtrs> recs(sh.layers);
+  for (uint32_t l = 0; l < sh.layers; ++l) {
+    Buf* b[8];
+    for (int i = 0; i < 8; ++i) {
+      st = e->need(layer_buffers[(size_t)l * 8 + i], &b[i], "decode_layers", true);
+      if (st) return st;
+    }
+    const uint64_t want[6][2] = {{1, H}, {H, QC + 2 * KC}, {QC, H}, {1, H}, {H, 2 * FF}, {FF, H}};
+    for (int i = 0; i < 6; ++i) {
+      const bool gain = i == 0 || i == 3;
+      const bool shape_ok = gain ? b[i]->rows * b[i]->cols == H : (b[i]->rows == want[i][0] && b[i]->cols == want[i][1]);
+      const bool elem_ok = gain ? b[i]->elem == B200_BF16 : (b[i]->elem == B200_BF16 || b[i]->elem == B200_BFP8);
+      if (!shape_ok || !elem_ok)
+        return e->fail(B200_UNSUPPORTED, "decode_layers: layer %u operand %d is [%llu,%llu] elem %d, not [%llu,%llu] %s", l, i,
+                       (unsigned long long)b[i]->rows, (unsigned long long)b[i]->cols, b[i]->elem, (unsigned long long)want[i][0],
+                       (unsigned long long)want[i][1], gain ? "BF16" : "BF16 or BFP8");
+    }
+    for (int i = 6; i < 8; ++i)
+      if (b[i]->elem != B200_BF16 || b[i]->cols != KC || b[i]->rows != (uint64_t)sh.rows * sh.max_len)
+        return e->fail(B200_UNSUPPORTED, "decode_layers: layer %u's cache must be BF16 [%llu, %llu]", l,
+                       (unsigned long long)sh.rows * sh.max_len, (unsigned long long)KC);
+    DecodeLayerPtrs& r = recs[l];
+    r.norm1 = b[0]->ptr; r.qkv = b[1]->ptr; r.o = b[2]->ptr; r.norm2 = b[3]->ptr; r.gate_up = b[4]->ptr; r.down = b[5]->ptr;
+    r.kc = b[6]->ptr; r.vc = b[7]->ptr;
+    r.bfp = (b[1]->elem == B200_BFP8 ? 1u : 0u) | (b[2]->elem == B200_BFP8 ? 2u : 0u) | (b[4]->elem == B200_BFP8 ? 4u : 0u) |
+            (b[5]->elem == B200_BFP8 ? 8u : 0u);
+    r.pad = 0;
+  }
+  const int grid = decode_layers_grid();
+  const DecodeScratch cut = decode_layers_scratch(sh, grid);
+  Buf* O = nullptr;
+  st = e->new_buffer(sh.rows, H, B200_BF16, out, &O);
+  if (st) return st;
+  void *recs_dev = nullptr, *scratch = nullptr;
+  uint64_t got_r = 0, got_s = 0;
+  st = e->to_device(recs.data(), recs.size() * sizeof(DecodeLayerPtrs), &recs_dev, &got_r);
+  if (!st) st = e->alloc(cut.floats * sizeof(float), &scratch, &got_s);
+  if (!st) {
+    X = e->get(x); FN = e->get(final_norm); CS = e->get(cos_table); SN = e->get(sin_table); P = e->get(position); O = e->get(*out);
+    st = e->launched(launch_decode_layers(sh, (const DecodeLayerPtrs*)recs_dev, (const float*)X->ptr, FN->ptr, (const float*)CS->ptr,
+                                          (const float*)SN->ptr, (const int32_t*)P->ptr, (uint16_t*)O->ptr, (float*)scratch, cut, grid,
+                                          e->d_err, e->stream), "decode_layers");
+  }
+  if (scratch) e->release(scratch, got_s);
+  if (recs_dev) e->release(recs_dev, got_r);
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, sh.rows, H);
+  return B200_OK;
+}
+
 // ---- traces: server.rs:591-660 ---------------------------------------------------
 int32_t b200_begin_trace(b200_engine* e) {
   cudaSetDevice(e->device);

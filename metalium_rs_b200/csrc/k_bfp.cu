@@ -29,20 +29,6 @@
 namespace b200 {
 namespace {
 
-// crates/tt-isa/src/tile.rs:619-634, line for line.
-__device__ __forceinline__ uint16_t bfp8_to_bf16_bits(uint32_t datum, uint32_t exp_bits) {
-  const uint32_t sign = datum >> 7;
-  uint32_t mag = (datum << 1) & 0xffu;
-  if (mag == 0) return sign ? 0xff80u : 0u;
-  const uint32_t lz = __clz(mag) - 24;
-  mag = (mag << lz) & 0xffu;
-  const uint32_t e = (exp_bits - lz) & 0xffu;   // `ExpBits -= LZ` on a uint8_t: it wraps
-  return (uint16_t)((sign << 15) | (e << 7) | (mag & 0x7eu));
-}
-__device__ __forceinline__ float bfp8_value(uint32_t datum, uint32_t exp_bits) {
-  return __uint_as_float((uint32_t)bfp8_to_bf16_bits(datum, exp_bits) << 16);
-}
-
 // One thread a group of sixteen values.
 template <bool IN_BF16>
 __global__ void __launch_bounds__(256)

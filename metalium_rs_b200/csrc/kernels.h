@@ -193,6 +193,24 @@ bool gemm_skinny_bfp_supported(uint64_t m, uint64_t n, uint64_t k);
 cudaError_t launch_gemm_skinny_bfp(const uint16_t* a, uint64_t lda, const uint8_t* datums, const uint8_t* exps, void* c, uint64_t ldc,
                                    int out_bf16, uint64_t m, uint64_t n, uint64_t k, cudaStream_t stream);
 
+// One decode step through every layer in one cooperative launch (k_decode.cu).
+struct DecodeShape { uint32_t layers, rows, hidden, heads, kv_heads, head_dim, ff, max_len, attend; float eps, scale; };
+struct DecodeLayerPtrs {          // a layer's operands as device addresses (a device array, one record a layer)
+  const void *norm1, *qkv, *o, *norm2, *gate_up, *down;   // gains BF16 [1, hidden]; matrices [k, n] BF16 or BFP8
+  void *kc, *vc;                                           // the layer's key and value cache, [rows * max_len, kv_heads * 64] BF16
+  uint32_t bfp, pad;                                       // bit 0 qkv, 1 o, 2 gate_up, 3 down: that matrix is BFP8
+};
+struct DecodeScratch {            // how the step's scratch (F32 words) is cut, and how each product's k is sliced
+  uint32_t ks_qkv, sl_qkv, ks_o, sl_o, ks_gu, sl_gu, ks_dn, sl_dn;
+  uint64_t off_qkv, off_att, off_o, off_gu, off_dn, off_bar, floats;
+};
+bool decode_layers_supported(const DecodeShape& shape, const char** why);
+int decode_layers_grid();
+DecodeScratch decode_layers_scratch(const DecodeShape& shape, int grid);
+cudaError_t launch_decode_layers(const DecodeShape& shape, const DecodeLayerPtrs* layers_dev, const float* x0, const void* final_norm,
+                                 const float* cos_t, const float* sin_t, const int32_t* pos, uint16_t* out, float* scratch,
+                                 const DecodeScratch& cut, int grid, int* err, cudaStream_t stream);
+
 // Text for `b200_last_error(NULL, ...)`: failures of calls that take no engine.
 void set_global_error(const char* text);
 

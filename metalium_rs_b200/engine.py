@@ -81,6 +81,11 @@ class Config(C.Structure):
                 ("fail_alloc_at", C.c_int32), ("_pad", C.c_int32), ("wait_limit_cycles", C.c_uint64)]
 
 
+class DecodeShape(C.Structure):  # b200_decode_shape
+    _fields_ = [(n, C.c_uint32) for n in ("layers", "hidden", "heads", "kv_heads", "head_dim", "ff", "max_len", "attend")] + \
+               [("eps", C.c_float), ("scale", C.c_float)]
+
+
 class OpStat(C.Structure):  # burn-tt/src/report.rs:27 `OpStat`, reduced (b200_op_stat)
     _fields_ = [("op", C.c_char * 48), ("calls", C.c_uint64), ("launches", C.c_uint64), ("device_ms", C.c_double)]
 
@@ -665,6 +670,14 @@ class CudaEngine:
         n = len(items)
         return self._call(self._lib.b200_attention_blocks, C.c_uint64(q), C.c_uint64(k), C.c_uint64(v), arr, C.c_uint64(n),
                           (C.c_uint64 * 4)(*dims), C.c_float(scale), C.c_int32(1 if causal else 0), (C.c_uint64 * 2)(*result_dims))
+
+    def decode_layers(self, shape: "DecodeShape", x: int, layer_buffers: Sequence[int], final_norm: int, cos: int, sin: int,
+                      position: int) -> Out:
+        """One generation step through every layer as one launch (`b200_decode_layers`): 8 buffer ids a layer -- norm1, Wqkv,
+        Wo, norm2, Wgate|up, Wdown, key cache, value cache.  Returns the final norm of the stream, BF16 [rows, hidden]."""
+        ids = (C.c_uint64 * len(layer_buffers))(*layer_buffers)
+        return self._call(self._lib.b200_decode_layers, C.byref(shape), C.c_uint64(x), ids, C.c_uint64(final_norm), C.c_uint64(cos),
+                          C.c_uint64(sin), C.c_uint64(position))
 
     def set_matmul_sm_limit(self, sms: int):
         """Tensor-core products use at most `sms` SMs (0 = all): room for a collective beside them."""

@@ -7,6 +7,7 @@ use std::os::raw::{c_char, c_void};
 
 #[repr(C)] pub struct b200_engine { _private: [u8; 0] }
 #[repr(C)] #[derive(Clone, Copy, Default)] pub struct b200_config { pub f32_matmul_mode: i32, pub bf16_matmul_mode: i32, pub pool_limit_bytes: u64, pub fail_alloc_at: i32, pub _pad: i32, pub wait_limit_cycles: u64 }
+#[repr(C)] #[derive(Clone, Copy)] pub struct b200_decode_shape { pub layers: u32, pub hidden: u32, pub heads: u32, pub kv_heads: u32, pub head_dim: u32, pub ff: u32, pub max_len: u32, pub attend: u32, pub eps: f32, pub scale: f32 }
 #[repr(C)] #[derive(Clone, Copy)] pub struct b200_op_stat { pub op: [c_char; 48], pub calls: u64, pub launches: u64, pub device_ms: f64 }
 #[repr(C)] #[derive(Clone, Copy)] pub struct b200_eltwise_op { pub kind: u32, pub scalar: f32, pub scalar2: f32 }
 #[repr(C)] #[derive(Clone, Copy)] pub struct b200_block { pub at: [u64; 2], pub transposed: i32, pub _pad: i32 }
@@ -99,6 +100,7 @@ extern "C" {
     pub fn b200_ipc_export(a0: *mut b200_engine, buf: u64, handle: *mut u8) -> i32;
     pub fn b200_ipc_open(a0: *mut b200_engine, handle: *const u8, ptr: *mut *mut core::ffi::c_void) -> i32;
     pub fn b200_ipc_close(a0: *mut b200_engine, ptr: *mut core::ffi::c_void) -> i32;
+    pub fn b200_decode_layers(a0: *mut b200_engine, shape: *const b200_decode_shape, x: u64, layer_buffers: *const u64, final_norm: u64, cos_table: u64, sin_table: u64, position: u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_begin_trace(a0: *mut b200_engine) -> i32;
     pub fn b200_end_trace(a0: *mut b200_engine, trace: *mut u64) -> i32;
     pub fn b200_run_trace(a0: *mut b200_engine, trace: u64) -> i32;

@@ -517,12 +517,26 @@ class LlamaDecode:
 
     `weights_dev`: the device weights of a `LlamaPrefill` (shared, not copied)."""
 
-    def __init__(self, eng, cfg: LlamaConfig, weights_dev: Dict[str, int], batch: int, max_len: int, attend: int = 0):
+    def __init__(self, eng, cfg: LlamaConfig, weights_dev: Dict[str, int], batch: int, max_len: int, attend: int = 0,
+                 fused: bool = False, weight_storage: str = "bf16"):
+        """fused: the layers of a step as one cooperative launch (`decode_layers`) instead of eleven launches a layer; the
+        same steps and roundings, sums in the kernel's own order.  weight_storage "bfp8": the four projections of every
+        layer kept as BFP8 (`cast_bfp`; crates/burn-tt/src/storage.rs:117-123), read by the products where they lie."""
         assert max_len % 32 == 0 and cfg.head_dim % 32 == 0
         self.eng, self.cfg, self.batch, self.max_len = eng, cfg, batch, max_len
         self.attend = attend or max_len                  # positions attention reads (kv_cache.rs:195-199)
         assert self.attend % 32 == 0 and self.attend <= max_len
-        self.w = weights_dev
+        self.w = dict(weights_dev)
+        self.fused = bool(fused)
+        self.packed = []
+        if weight_storage == "bfp8":
+            for l in range(cfg.layers):
+                for name in ("qkv", "o", "gate_up", "down"):
+                    packed, _ = eng.cast_bfp(self.w[f"l{l}.{name}"], 8)
+                    self.w[f"l{l}.{name}"] = packed
+                    self.packed.append(packed)
+        elif weight_storage != "bf16":
+            raise ValueError("weight_storage is 'bf16' or 'bfp8'")
         c = cfg
         self.q_cols, self.kv_cols = c.heads * c.head_dim, c.kv_heads * c.head_dim
         cos, sin = rope_tables(max_len, c.head_dim, c.theta)
@@ -542,6 +556,13 @@ class LlamaDecode:
             [((b, h * hd), (b * max_len, (h // group) * hd), (b * max_len, (h // group) * hd))
              for b in range(batch) for h in range(c.heads)])
         self.trace = None
+        if self.fused:
+            from .engine import DecodeShape
+            self.shape = DecodeShape(c.layers, c.hidden, c.heads, c.kv_heads, c.head_dim, c.ff, max_len, self.attend, c.eps,
+                                     1.0 / float(np.sqrt(hd)))
+            self.layer_ids = [i for l in range(c.layers)
+                              for i in (self.w[f"l{l}.norm1"], self.w[f"l{l}.qkv"], self.w[f"l{l}.o"], self.w[f"l{l}.norm2"],
+                                        self.w[f"l{l}.gate_up"], self.w[f"l{l}.down"], self.kc[l], self.vc[l])]
 
     def reset(self, ids: np.ndarray, position: int = 0):
         """Start (or restart) at `position` with these ids ([batch] I32) as the next input."""
@@ -573,6 +594,13 @@ class LlamaDecode:
         e, c, K = self.eng, self.cfg, kinds
         B, hd = self.batch, c.head_dim
         op = lambda kind, a, b=None, s1=0.0: e.eltwise_op(EltwiseOp(kind, s1, 0.0), a, b)[0]
+        if self.fused:
+            emb, _ = e.select_rows(self.w["embed"], self.ids)
+            x, _ = e.cast_float(emb, False)
+            e.free(emb)
+            n1, _ = e.decode_layers(self.shape, x, self.layer_ids, self.w["final_norm"], self.cos, self.sin, self.pos)
+            e.free(x)
+            return self._head_and_advance(n1, op)
         rows = op(K.INT_ADD, self.row_base, self.pos)                         # each sequence's cache row
         later = op(K.INT_GT, self.positions, self.pos)                        # kv_cache.rs:216-224 `later`
         cs, _ = e.select_rows(self.cos, self.pos)                             # the position's RoPE row
@@ -611,18 +639,23 @@ class LlamaDecode:
             (x, _), (n1, _) = e.add_rms_norm_as(x2, d, nxt, c.eps, True)
             e.free(x2); e.free(d)
         e.free(x)
+        for i in (rows, later, cs, sn):
+            e.free(i)
+        return self._head_and_advance(n1, op)
+
+    def _head_and_advance(self, n1: int, op):
+        """The tied head on the stream's final norm, its argmax, and the step's bookkeeping: record, feed back, advance."""
+        e, K, B = self.eng, kinds, self.batch
         logits, _ = e.matmul_dram(n1, False, self.w["embed"], True)          # tied head
         e.free(n1)
         am, _ = e.argmax_row(logits)
-        # record, feed back, advance
         am_row, _ = e.reshape(am, 1, B)
         e.scatter_rows_into(self.tokens, self.pos, (am_row, (0, 0), (1, B)))
         e.free(am_row)
         e.copy_into(am, self.ids)
         nxt_pos = op(K.INT_ADD_S, self.pos, None, _int_scalar(1))
         e.copy_into(nxt_pos, self.pos)
-        for i in (nxt_pos, rows, later, cs, sn):
-            e.free(i)
+        e.free(nxt_pos)
         return logits, am
 
     def capture(self):

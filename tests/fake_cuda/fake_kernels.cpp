@@ -83,6 +83,15 @@ cudaError_t launch_gemm_tc(const GemmArgs&, const GemmBatch*, int*, cudaStream_t
 cudaError_t launch_stalled_wait(int*, cudaStream_t) { OK_LAUNCH; }
 cudaError_t launch_bfp8_encode(const void*, int, uint64_t, uint64_t, uint8_t*, uint8_t*, cudaStream_t) { OK_LAUNCH; }
 cudaError_t launch_bfp8_decode(const uint8_t*, const uint8_t*, uint64_t, uint64_t, void*, int, cudaStream_t) { OK_LAUNCH; }
+bool decode_layers_supported(const DecodeShape& s, const char** why) {
+  *why = "heads of 64 columns, one to four sequences, whole 64-column blocks";
+  return s.rows >= 1 && s.rows <= 4 && s.head_dim == 64 && s.kv_heads && s.heads % s.kv_heads == 0 && s.hidden % 64 == 0 && s.ff % 64 == 0 &&
+         s.attend && s.attend % 64 == 0 && s.attend <= s.max_len;
+}
+int decode_layers_grid() { return 64; }
+DecodeScratch decode_layers_scratch(const DecodeShape&, int) { DecodeScratch d{}; d.floats = 1024; return d; }
+cudaError_t launch_decode_layers(const DecodeShape&, const DecodeLayerPtrs*, const float*, const void*, const float*, const float*, const int32_t*,
+                                 uint16_t*, float*, const DecodeScratch&, int, int*, cudaStream_t) { OK_LAUNCH; }
 bool gemm_skinny_bfp_supported(uint64_t m, uint64_t n, uint64_t) { return m >= 1 && m <= 4 && n % 16 == 0; }
 cudaError_t launch_gemm_skinny_bfp(const uint16_t*, uint64_t, const uint8_t*, const uint8_t*, void*, uint64_t, int, uint64_t, uint64_t, uint64_t,
                                    cudaStream_t) { OK_LAUNCH; }

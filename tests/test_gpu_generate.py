@@ -223,3 +223,99 @@ def test_a_prompt_prefilled_in_chunks_is_the_prompt_prefilled_at_once(eng):
     assert np.isfinite(eng.download(lg)).all()
     for i in (lw, aw, lg, am, iw) + tuple(x for o in outs for x in o):
         eng.free(i)
+
+
+@pytest.mark.parametrize("batch", [1, 2, 4])
+@pytest.mark.parametrize("storage", ["bf16", "bfp8"])
+def test_the_one_launch_step_is_the_composed_step(eng, batch, storage):
+    # `decode_layers` (one cooperative launch for every layer of a step) against the step composed of the trait's ops:
+    # the same steps and roundings, sums in another fixed order, so the logits agree to F32 rounding carried through BF16
+    # re-roundings, the cache rows to one BF16 step, and the choices wherever the composed step's margin is clear.  Both
+    # are fed the same tokens.  With BFP8 weights both read the same compressed matrices.
+    cfg = small_llama()
+    max_len, steps = 128, 70                           # past position 64: a second chunk of cache positions is attended
+    pre = W.LlamaPrefill(eng, cfg, W.llama_weights(cfg, seed=11), batch, 32)
+    composed = W.LlamaDecode(eng, cfg, pre.w, batch, max_len=max_len, weight_storage=storage)
+    fused = W.LlamaDecode(eng, cfg, pre.w, batch, max_len=max_len, fused=True, weight_storage=storage)
+    ids = orc.integers(0x6E5, 3, (steps, batch), cfg.vocab)
+    composed.reset(ids[0]); fused.reset(ids[0])
+    l0 = eng.device_traffic().launches
+    worst, disagreements = 0.0, 0
+    for t in range(steps):
+        composed.set_ids(ids[t]); fused.set_ids(ids[t])
+        la, aa = composed.step()
+        before = eng.device_traffic().launches
+        lb, ab = fused.step()
+        fused_launches = eng.device_traffic().launches - before
+        a, b = eng.download(la), eng.download(lb)
+        worst = max(worst, float(np.max(np.abs(a - b))))
+        top2 = np.sort(a, axis=1)[:, -2:]
+        clear = (top2[:, 1] - top2[:, 0]) > 2e-3
+        ca, cb = eng.download_bits(aa).view(np.int32).ravel(), eng.download_bits(ab).view(np.int32).ravel()
+        assert np.array_equal(ca[clear], cb[clear]), t
+        disagreements += int((ca != cb).sum())
+        for i in (la, aa, lb, ab):
+            eng.free(i)
+    assert worst <= 1e-3, worst                        # far inside the 2e-2 the cached steps are held to
+    assert fused_launches <= 12                        # embedding, cast, the layers, head, argmax, bookkeeping
+    for l in range(cfg.layers):
+        for mine, theirs in ((fused.kc[l], composed.kc[l]), (fused.vc[l], composed.vc[l])):
+            x = orc.from_bf16(eng.download_bf16(mine)).reshape(batch, max_len, -1)
+            y = orc.from_bf16(eng.download_bf16(theirs)).reshape(batch, max_len, -1)
+            assert not x[:, steps:].any() and x[:, :steps].any()
+            assert np.max(np.abs(x - y)) <= 2.0 ** -7 * np.abs(y).max(), l
+    assert np.array_equal(fused.generated(0, steps).shape, (steps, batch))
+
+
+def test_a_traced_one_launch_generation_is_its_eager_one(eng):
+    cfg = small_llama()
+    batch, n = 2, 24
+    pre = W.LlamaPrefill(eng, cfg, W.llama_weights(cfg, seed=11), batch, 32)
+    first = np.array([5, 1999], np.int32)
+    eager = W.LlamaDecode(eng, cfg, pre.w, batch, max_len=64, fused=True)
+    eager.reset(first)
+    toks = []
+    for _ in range(n):
+        lg, am = eager.step()
+        toks.append(eng.download_bits(am).view(np.int32).ravel().copy())
+        eng.free(lg); eng.free(am)
+    toks = np.stack(toks)
+    traced = W.LlamaDecode(eng, cfg, pre.w, batch, max_len=64, fused=True)
+    traced.reset(first)
+    lg, am = traced.capture()
+    traced.reset(first)
+    l0 = eng.device_traffic().launches
+    for _ in range(n):
+        traced.replay()
+    assert eng.device_traffic().launches - l0 <= n * 12
+    assert np.array_equal(traced.generated(0, n), toks)    # the same kernel, the same fixed order of sums: the same bits
+    eng.release_trace(traced.trace)
+    eng.free(lg); eng.free(am)
+
+
+def test_one_launch_steps_equal_the_prefill_and_the_cpu_restatement(eng):
+    cfg = small_llama()
+    batch, t = 2, 32
+    w = W.llama_weights(cfg, seed=11)
+    ids = orc.integers(0x6E1, 9, (batch, t), cfg.vocab)
+    pre = W.LlamaPrefill(eng, cfg, w, batch, t)
+    dec = W.LlamaDecode(eng, cfg, pre.w, batch, max_len=64, fused=True)
+    dec.reset(ids[:, 0])
+    for step in range(t):
+        dec.set_ids(ids[:, step])
+        lg, am = dec.step()
+        got = eng.download(lg)
+        eng.free(lg); eng.free(am)
+    wb = {k: orc.from_bf16(orc.to_bf16(v)) for k, v in w.items()}
+    cpu = M.llama_prefill(cfg, wb, ids.reshape(1, -1), batch, t)
+    assert np.max(np.abs(got - cpu)) <= 2e-2
+
+
+def test_the_one_launch_step_refuses_what_it_was_not_written_for(eng):
+    cfg = W.LlamaConfig(layers=1, hidden=128, heads=2, kv_heads=1, head_dim=32, ff=128, vocab=256)
+    pre = W.LlamaPrefill(eng, cfg, W.llama_weights(cfg, seed=3), 1, 32)
+    dec = W.LlamaDecode(eng, cfg, pre.w, 1, max_len=64, fused=True)      # heads of 32 columns
+    dec.reset(np.array([1], np.int32))
+    with pytest.raises(TtError) as ei:
+        dec.step()
+    assert ei.value.status == 2 and "64" in str(ei.value)

@@ -525,3 +525,21 @@ def test_bfp8_storage_dims_bytes_and_refusals(e):                  # server.rs:1
         with pytest.raises(TtError) as err:
             bad()
         assert err.value.status == 2
+
+
+def test_the_one_launch_decode_step_checks_its_operands(e):
+    from metalium_rs_b200 import workloads as W
+    cfg = W.LlamaConfig(layers=2, hidden=128, heads=2, kv_heads=1, head_dim=64, ff=256, vocab=256)
+    pre = W.LlamaPrefill(e, cfg, W.llama_weights(cfg, seed=3), 2, 128)
+    dec = W.LlamaDecode(e, cfg, pre.w, 2, max_len=128, fused=True, weight_storage="bfp8")
+    dec.reset(np.array([1, 2], np.int32))
+    l0 = e.device_traffic().launches
+    lg, am = dec.step()
+    assert e.dims_of(lg) == ((2, cfg.vocab), F32) and e.device_traffic().launches - l0 <= 12
+    bad = list(dec.layer_ids)
+    bad[1], bad[2] = bad[2], bad[1]                                   # Wqkv and Wo exchanged: the shapes do not meet
+    with pytest.raises(TtError) as err:
+        e.decode_layers(dec.shape, e.upload(np.zeros((2, 128), np.float32), 2, 128), bad, dec.w["final_norm"], dec.cos, dec.sin, dec.pos)
+    assert err.value.status == 2 and "layer 0 operand 1" in str(err.value)
+    with pytest.raises(TtError):                                       # five sequences a step
+        e.decode_layers(dec.shape, e.upload(np.zeros((5, 128), np.float32), 5, 128), dec.layer_ids, dec.w["final_norm"], dec.cos, dec.sin, dec.pos)
