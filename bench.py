@@ -732,7 +732,8 @@ def run_profile(args):
     gemm_small: the four projections of a prefill layer ([4096,576]x[576,960], x[576,576], x[576,3072],
     [4096,1536]x[1536,576]), three rounds.  scan_sort: a row-order sum scan and a binary16 cast of [8192,8192] F32 and a
     sort of 8192 problems of 1024 positions, three rounds.  attention: three fused attentions of 64 blocks [1024, 128] (no mask).  decode: three `attention_rows`
-    of 512 heads on 128 key/value heads of [4096, 128] BF16."""
+    of 512 heads on 128 key/value heads of [4096, 128] BF16.  decode_step: three generation steps of the SmolLM2-135M shape at
+    batch 1 with the layers as one launch.  gemm: three 8192^3 BF16 products."""
     from metalium_rs_b200 import COLS, I32, SUM, CudaEngine, EltwiseOp, build, kinds, workloads as W
     build.build()
     rng = np.random.default_rng(3)
@@ -779,6 +780,21 @@ def run_profile(args):
             items = eng.attention_item_array([((h, 0), ((h // 4) * l, 0), ((h // 4) * l, 0)) for h in range(heads)])
             for _ in range(3):
                 o, _ = eng.attention_rows([q, k, v, mask], items, [1, d, l, d], 0.088); eng.free(o)
+        elif args.profile == "decode_step":
+            # three generation steps of the SmolLM2-135M shape at batch 1, the layers as one cooperative launch
+            cfg = W.LlamaConfig()
+            m = W.LlamaPrefill(eng, cfg, W.llama_weights(cfg), 1, 128)
+            dec = W.LlamaDecode(eng, cfg, m.w, 1, max_len=512, attend=256, fused=True)
+            dec.reset(np.array([7], np.int32))
+            for _ in range(3):
+                lg, am = dec.step(); eng.free(lg); eng.free(am)
+        elif args.profile == "gemm":
+            # three 8192^3 BF16 products (the benchmark's kernel)
+            n = args.size or 8192
+            ia = eng.upload_bf16(cheap_bf16((n, n), 11), n, n)
+            ib = eng.upload_bf16(cheap_bf16((n, n), 12), n, n)
+            for _ in range(3):
+                o, _ = eng.matmul_dram_bf16(ia, False, ib, False); eng.free(o)
         elif args.profile == "scan_sort":
             from metalium_rs_b200 import F32
             from metalium_rs_b200 import engine as E
@@ -810,7 +826,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--no-suite", action="store_true", help="skip the memory-bound suite leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill leg")
-    ap.add_argument("--profile", default="", help="run a short fixed sequence for an ncu capture: membound | softmax | prefill | gemm_small | attention | decode | scan_sort")
+    ap.add_argument("--profile", default="", help="run a short fixed sequence for an ncu capture: membound | softmax | prefill | gemm_small | attention | decode | scan_sort | decode_step | gemm")
     ap.add_argument("--size", type=int, default=0, help="override the N=1 problem size (profiling on a small case)")
     args = ap.parse_args()
     if args.impl == "reference":

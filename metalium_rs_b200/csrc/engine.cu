@@ -73,6 +73,7 @@ struct b200_engine {
   std::string sticky_text;
   std::string label;
   const char* matmul_path = "none";
+  const char* decode_form = "none";
   b200_traffic traffic{};
   uint64_t next_id = 1;
   uint64_t alloc_calls = 0;
@@ -2289,18 +2290,26 @@ int32_t b200_decode_layers(b200_engine* e, const b200_decode_shape* shape, b200_
   Buf* O = nullptr;
   st = e->new_buffer(sh.rows, H, B200_BF16, out, &O);
   if (st) return st;
-  void *recs_dev = nullptr, *scratch = nullptr;
-  uint64_t got_r = 0, got_s = 0;
+  void *recs_dev = nullptr, *scratch = nullptr, *maps_dev = nullptr;
+  uint64_t got_r = 0, got_s = 0, got_m = 0;
   st = e->to_device(recs.data(), recs.size() * sizeof(DecodeLayerPtrs), &recs_dev, &got_r);
+  bool any_bfp = false;
+  for (const DecodeLayerPtrs& r : recs) any_bfp = any_bfp || r.bfp != 0;
+  if (!st && decode_layers_cluster_wanted(sh, any_bfp)) {   // the cluster form's descriptors; without an encoder the grid form runs
+    std::vector<uint64_t> maps((decode_layers_maps_bytes(sh) + 7) / 8 + 8);
+    void* aligned = reinterpret_cast<void*>(((uintptr_t)maps.data() + 63) & ~(uintptr_t)63);
+    if (decode_layers_make_maps(sh, recs.data(), aligned)) st = e->to_device(aligned, decode_layers_maps_bytes(sh), &maps_dev, &got_m);
+  }
   if (!st) st = e->alloc(cut.floats * sizeof(float), &scratch, &got_s);
   if (!st) {
     X = e->get(x); FN = e->get(final_norm); CS = e->get(cos_table); SN = e->get(sin_table); P = e->get(position); O = e->get(*out);
     st = e->launched(launch_decode_layers(sh, (const DecodeLayerPtrs*)recs_dev, (const float*)X->ptr, FN->ptr, (const float*)CS->ptr,
                                           (const float*)SN->ptr, (const int32_t*)P->ptr, (uint16_t*)O->ptr, (float*)scratch, cut, grid,
-                                          e->d_err, e->stream), "decode_layers");
+                                          maps_dev, e->d_err, e->stream, &e->decode_form), "decode_layers");
   }
   if (scratch) e->release(scratch, got_s);
   if (recs_dev) e->release(recs_dev, got_r);
+  if (maps_dev) e->release(maps_dev, got_m);
   if (st) { e->drop(*out); return st; }
   set_dims(out_dims, sh.rows, H);
   return B200_OK;
@@ -2488,5 +2497,6 @@ int32_t b200_timer_stop(b200_engine* e, float* ms) {
 }
 void* b200_stream(const b200_engine* e) { return (void*)e->stream; }
 const char* b200_last_matmul_path(const b200_engine* e) { return e->matmul_path; }
+const char* b200_last_decode_form(const b200_engine* e) { return e->decode_form; }
 
 }  // extern "C"

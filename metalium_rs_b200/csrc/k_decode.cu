@@ -1,8 +1,12 @@
 // One token a sequence through every layer of a Llama-architecture decoder in ONE launch: the device side of the
 // reference's traced generation step (crates/tt-models/src/generate.rs:781; layer crates/tt-models/src/llama.rs:371-507;
 // cache crates/tt-models/src/kv_cache.rs:185-330).  The composed step is eleven small launches a layer whose device
-// work (a layer's 9 MB of weights) takes far less time than their launch latencies; here a cooperative grid of
-// persistent blocks walks the layers with five grid-wide barriers a layer instead.
+// work (a layer's 9 MB of weights) takes far less time than their launch latencies; here one launch walks the layers
+// with five barriers a layer instead.  Two forms of the same five phases, chosen at the call
+// (`decode_layers_cluster_wanted`): a cooperative grid of persistent blocks that exchange partial sums through global
+// memory and wait at a counter (described first), and ONE thread-block cluster of sixteen blocks that exchange results
+// through distributed shared memory, wait at the hardware's cluster barrier and stream their weights through a ring of
+// TMA copies (further down).
 //
 // A layer, for `B` <= 4 rows (one token of each sequence), in five phases.  Between phases stand grid barriers; the
 // residual stream lives redundantly in every block's shared memory, so no phase waits for one block to publish it.
@@ -20,15 +24,19 @@
 // After the last layer block 0 adds the last partials and writes the final RMSNorm as BF16: the head product's input.
 //
 // Weights are BF16 or BFP8 (decoded in the load path: csrc/k_bfp.cu), read as stored [k, n]; a thread's load is one
-// 16-byte (8-byte) group of 8 columns.  Every sum has a fixed order, so a step's bits do not depend on the launch.
+// 16-byte (8-byte) group of 8 columns.  What a phase reads that no earlier phase of the step writes -- its first item's
+// weight tile, the cache rows of earlier positions -- is fetched into shared memory (cp.async) BEFORE the barrier the
+// phase waits at, so the fetch runs under the phase before and under the barrier itself.  Every sum has a fixed order, so a step's bits do not depend on the launch.
 // Every spin of the barrier is bounded by the engine's wait limit: when it runs out the error word becomes TIMEOUT,
 // a flag tells the other blocks, and every block returns.
 #include <cooperative_groups.h>
 #include <cstdint>
+#include <cstdlib>
 #include <cuda_runtime.h>
 
 #include "device_math.cuh"
 #include "kernels.h"
+#include "tc_common.cuh"
 
 namespace b200 {
 namespace {
@@ -43,16 +51,42 @@ constexpr long long DEFAULT_WAIT = 4000000000ll;
 __device__ __forceinline__ float bf16_round(float v) { return __uint_as_float((uint32_t)f32_to_bf16_bits(__float_as_uint(v)) << 16); }
 __device__ __forceinline__ float bf16_at(const void* p, uint64_t i) { return __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(p)[i] << 16); }
 
+constexpr int WT_ROWS = 256;       // k-rows of a product item at most (a slice of k)
 struct Shared {
   float* xres;    // [MT][hidden]  the residual stream
   float* vec;     // [MT][vec_cols] a product's A operand
   float* red;     // [8][MT][64]
-  uint32_t* ksm;  // [64][33] a chunk of keys (BF16 pairs), padded
-  uint32_t* vsm;  // [64][33] a chunk of values
+  uint4* ksm;     // [64][8] a chunk of keys: 128-byte rows of BF16, the 16-byte units of row j stored at u ^ (j & 7)
+  uint4* vsm;     // [64][8] a chunk of values, the same layout
   float* qs;      // [4][64] rotated queries of a group
   float* ps;      // [4][64] probabilities
   float* stat;    // [16] small reductions
+  uint8_t* wt;    // a product item's weight tile fetched ahead: [rows][64] BF16, or [rows][64] datums then [rows][4] exponents
 };
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// Fetch ahead the weight tile of a product item: k rows [k0, k0 + len) x columns [c0, c0 + 64) of W [k, n].
+__device__ __forceinline__ void fetch_tile(uint8_t* wt, const void* w, int bfp, uint64_t k_total, uint64_t n, uint32_t k0, uint32_t len,
+                                           uint32_t c0) {
+  if (!bfp) {
+    const uint16_t* src = reinterpret_cast<const uint16_t*>(w) + (uint64_t)k0 * n + c0;
+    for (uint32_t i = threadIdx.x; i < len * 8; i += DT) cp_async16(wt + (size_t)i * 16, src + (uint64_t)(i >> 3) * n + (i & 7) * 8);
+  } else {
+    const uint8_t* datums = reinterpret_cast<const uint8_t*>(w);
+    const uint8_t* src = datums + (uint64_t)k0 * n + c0;
+    const uint8_t* ex = datums + k_total * n + (uint64_t)k0 * (n / 16) + c0 / 16;
+    for (uint32_t i = threadIdx.x; i < len * 4; i += DT) cp_async16(wt + (size_t)i * 16, src + (uint64_t)(i >> 2) * n + (i & 3) * 16);
+    for (uint32_t i = threadIdx.x; i < len; i += DT) cp_async4(wt + (size_t)WT_ROWS * 64 + (size_t)i * 4, ex + (uint64_t)i * (n / 16));
+  }
+}
 
 // Bounded grid barrier: the `index`-th one of the launch.
 __device__ __forceinline__ bool grid_barrier(unsigned* bar, unsigned index, long long limit, int* err, int* ok_word) {
@@ -91,9 +125,11 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 // One product item: C[r, c0 .. c0+64) partial over k rows [k0, k0 + len) of W [k, n]; A's rows are `a` (shared memory,
 // row pitch lda, already offset to k0).  A thread owns 8 columns and every 32nd k-row.
-template <int MT>
+// `emit(r, column, value)` receives the item's results; `wt` holds the item's first `wt_rows` k-rows, fetched ahead (0: none).
+template <int MT, class Emit>
 __device__ __forceinline__ void product_item(const float* a, uint32_t lda, const void* w, int bfp, uint64_t k_total, uint64_t n,
-                                             uint32_t k0, uint32_t len, uint32_t c0, float* out /* [MT][n] */, float* red) {
+                                             uint32_t k0, uint32_t len, uint32_t c0, float* red, const uint8_t* wt, uint32_t wt_rows,
+                                             Emit emit) {
   const int tid = threadIdx.x, cg = tid & 7, kr = tid >> 3, warp = tid >> 5, lane = tid & 31;
   float acc[MT][8];
 #pragma unroll
@@ -101,10 +137,38 @@ __device__ __forceinline__ void product_item(const float* a, uint32_t lda, const
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[r][e] = 0.f;
   const uint64_t col = (uint64_t)c0 + cg * 8;
-  if (col < n) {
+  if (wt_rows > len) wt_rows = len;
+  if (col < n && wt_rows) {
+    // rows fetched ahead into shared memory: the same rows, the same order of additions as the loads from global memory below
+    for (uint32_t kk = kr; kk < wt_rows; kk += 32) {
+      float x[8];
+      if (!bfp) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(wt + ((size_t)kk * 8 + cg) * 16);
+        x[0] = __uint_as_float(raw.x << 16); x[1] = __uint_as_float(raw.x & 0xffff0000u);
+        x[2] = __uint_as_float(raw.y << 16); x[3] = __uint_as_float(raw.y & 0xffff0000u);
+        x[4] = __uint_as_float(raw.z << 16); x[5] = __uint_as_float(raw.z & 0xffff0000u);
+        x[6] = __uint_as_float(raw.w << 16); x[7] = __uint_as_float(raw.w & 0xffff0000u);
+      } else {
+        const uint2 raw = *reinterpret_cast<const uint2*>(wt + (size_t)kk * 64 + cg * 8);
+        const uint32_t ex = wt[(size_t)WT_ROWS * 64 + (size_t)kk * 4 + (cg >> 1)];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          x[e] = bfp8_value((raw.x >> (e * 8)) & 0xffu, ex);
+          x[4 + e] = bfp8_value((raw.y >> (e * 8)) & 0xffu, ex);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < MT; ++r) {
+        const float av = a[(size_t)r * lda + kk];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[r][e] = fmaf(av, x[e], acc[r][e]);
+      }
+    }
+  }
+  if (col < n && wt_rows < len) {                     // wt_rows is a multiple of 32 here: a thread goes on with its next row
     if (!bfp) {
       const uint16_t* bp = reinterpret_cast<const uint16_t*>(w) + (uint64_t)k0 * n + col;
-      for (uint32_t kk0 = kr; kk0 < len; kk0 += 32 * 4) {
+      for (uint32_t kk0 = wt_rows + kr; kk0 < len; kk0 += 32 * 4) {
         uint4 raw[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -134,7 +198,7 @@ __device__ __forceinline__ void product_item(const float* a, uint32_t lda, const
       const uint8_t* exps = datums + k_total * n;
       const uint8_t* bp = datums + (uint64_t)k0 * n + col;
       const uint8_t* ep = exps + (uint64_t)k0 * (n / 16) + col / 16;
-      for (uint32_t kk0 = kr; kk0 < len; kk0 += 32 * 4) {
+      for (uint32_t kk0 = wt_rows + kr; kk0 < len; kk0 += 32 * 4) {
         uint2 raw[4];
         uint32_t ex[4];
 #pragma unroll
@@ -191,7 +255,7 @@ __device__ __forceinline__ void product_item(const float* a, uint32_t lda, const
       float t = 0.f;
 #pragma unroll
       for (int wv = 0; wv < DT / 32; ++wv) t += red[((size_t)wv * MT + r) * DCOLS + cc];
-      out[(uint64_t)r * n + oc] = t;
+      emit(r, (uint32_t)oc, t);
     }
   }
 }
@@ -210,6 +274,24 @@ __device__ __forceinline__ void norm_rows(const float* x, uint32_t cols, const v
     for (uint32_t c = threadIdx.x; c < cols; c += DT) {
       const float t = __fdiv_rn(x[(size_t)r * cols + c], stat);
       vec[(size_t)r * vec_pitch + c] = bf16_round(__fmul_rn(t, bf16_at(gamma, c)));
+    }
+  }
+  __syncthreads();
+}
+
+// The same with the gains already in shared memory as F32 (exact: they are BF16 values).
+template <int MT>
+__device__ __forceinline__ void norm_rows_sm(const float* x, uint32_t cols, const float* gains, float eps, float* vec, uint32_t vec_pitch,
+                                             float* scratch) {
+  const float inv_n = 1.0f / (float)cols;
+  for (int r = 0; r < MT; ++r) {
+    float ss = 0.f;
+    for (uint32_t c = threadIdx.x; c < cols; c += DT) ss = fmaf(x[(size_t)r * cols + c], x[(size_t)r * cols + c], ss);
+    const float total = block_sum(ss, scratch);
+    const float stat = sqrtf(__fadd_rn(__fmul_rn(total, inv_n), eps));
+    for (uint32_t c = threadIdx.x; c < cols; c += DT) {
+      const float t = __fdiv_rn(x[(size_t)r * cols + c], stat);
+      vec[(size_t)r * vec_pitch + c] = bf16_round(__fmul_rn(t, gains[c]));
     }
   }
   __syncthreads();
@@ -239,17 +321,30 @@ struct DecodeParams {
   uint32_t vec_cols;
 };
 
+// Which item of a phase a block takes first, and where its weight tile lies.
+struct Item { uint32_t cb, ks, k0, len; bool any; };
+__device__ __forceinline__ Item first_item(uint32_t col_blocks, uint32_t ks_count, uint32_t slice, uint32_t k) {
+  Item it{};
+  it.any = blockIdx.x < col_blocks * ks_count;
+  it.cb = blockIdx.x % col_blocks;
+  it.ks = blockIdx.x / col_blocks;
+  it.k0 = it.ks * slice;
+  it.len = it.k0 + slice <= k ? slice : k - it.k0;
+  return it;
+}
+
 template <int MT>
 __global__ void __launch_bounds__(DT, 1) decode_layers_kernel(const DecodeParams p) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   __shared__ int ok_word;
   Shared s;
-  s.xres = smem;
+  s.wt = reinterpret_cast<uint8_t*>(smem);                                     // 16-byte aligned pieces first
+  s.ksm = reinterpret_cast<uint4*>(s.wt + WT_ROWS * 64 * 2);
+  s.vsm = s.ksm + DCH * 8;
+  s.xres = reinterpret_cast<float*>(s.vsm + DCH * 8);
   s.vec = s.xres + (size_t)MT * p.hidden;
   s.red = s.vec + (size_t)MT * p.vec_cols;
-  s.ksm = reinterpret_cast<uint32_t*>(s.red + 8 * MT * DCOLS);
-  s.vsm = s.ksm + DCH * 33;
-  s.qs = reinterpret_cast<float*>(s.vsm + DCH * 33);
+  s.qs = s.red + 8 * MT * DCOLS;
   s.ps = s.qs + 4 * HD;
   s.stat = s.ps + 4 * DCH;
 
@@ -266,6 +361,15 @@ __global__ void __launch_bounds__(DT, 1) decode_layers_kernel(const DecodeParams
     return;
   }
   unsigned barrier_index = 0;
+  const uint32_t nb_qkv = NQKV / DCOLS, nb_h = H / DCOLS, nb_gu = 2 * FF / DCOLS;
+  const uint32_t att_items = p.rows * p.kv_heads * chunks;
+
+  // the first layer's QKV tile, fetched under the embedding's norm
+  {
+    const Item it = first_item(nb_qkv, p.ks_qkv, p.sl_qkv, H);
+    if (it.any) fetch_tile(s.wt, p.layers[0].qkv, p.layers[0].bfp & 1, H, NQKV, it.k0, it.len, it.cb * DCOLS);
+    cp_async_commit();
+  }
 
   for (uint32_t l = 0; l < p.n_layers; ++l) {
     const DecodeLayerDev L = p.layers[l];
@@ -284,20 +388,42 @@ __global__ void __launch_bounds__(DT, 1) decode_layers_kernel(const DecodeParams
     }
     __syncthreads();
     norm_rows<MT>(s.xres, H, L.norm1, p.eps, s.vec, p.vec_cols, s.stat);
+    cp_async_wait_all();
+    __syncthreads();
     {
-      const uint32_t nb = NQKV / DCOLS, items = nb * p.ks_qkv;
+      const uint32_t items = nb_qkv * p.ks_qkv;
       for (uint32_t it = blockIdx.x; it < items; it += gridDim.x) {
-        const uint32_t cb = it % nb, ks = it / nb, k0 = ks * p.sl_qkv;
+        const uint32_t cb = it % nb_qkv, ks = it / nb_qkv, k0 = ks * p.sl_qkv;
         const uint32_t len = k0 + p.sl_qkv <= H ? p.sl_qkv : H - k0;
-        product_item<MT>(s.vec + k0, p.vec_cols, L.qkv, L.bfp & 1, H, NQKV, k0, len, cb * DCOLS, p.part_qkv + (size_t)ks * MT * NQKV, s.red);
+        float* out = p.part_qkv + (size_t)ks * MT * NQKV;
+        product_item<MT>(s.vec + k0, p.vec_cols, L.qkv, L.bfp & 1, H, NQKV, k0, len, cb * DCOLS, s.red, s.wt, it == blockIdx.x ? len : 0,
+                         [&](int r, uint32_t c, float t) { out[(size_t)r * NQKV + c] = t; });
       }
+    }
+    __syncthreads();
+    // fetched under phase 2 and its barriers: the output projection's tile; under barrier 1: the cache rows of the
+    // block's first attention item (earlier steps wrote them; the step's own row is patched in after the barrier)
+    {
+      const Item it = first_item(nb_h, p.ks_o, p.sl_o, QC);
+      if (it.any) fetch_tile(s.wt, L.o, (L.bfp >> 1) & 1, QC, H, it.k0, it.len, it.cb * DCOLS);
+      if (blockIdx.x < att_items) {
+        const uint32_t a = blockIdx.x, ch = a % chunks, kvh = (a / chunks) % p.kv_heads, b = a / (chunks * p.kv_heads);
+        if (ch * DCH <= (uint32_t)pos) {
+          const uint64_t row0 = (uint64_t)b * p.max_len + (uint64_t)ch * DCH;
+          for (uint32_t i = tid; i < DCH * 8; i += DT) {
+            const uint32_t j = i >> 3, u = i & 7;
+            cp_async16(s.ksm + j * 8 + (u ^ (j & 7)), reinterpret_cast<const uint16_t*>(L.kc) + (row0 + j) * KC + kvh * HD + u * 8);
+            cp_async16(s.vsm + j * 8 + (u ^ (j & 7)), reinterpret_cast<const uint16_t*>(L.vc) + (row0 + j) * KC + kvh * HD + u * 8);
+          }
+        }
+      }
+      cp_async_commit();
     }
     if (!grid_barrier(p.bar, barrier_index++, limit, p.err, &ok_word)) return;
 
     // ---- phase 2: RoPE, the cache write, attention over chunks of positions ------------------------------------------
     {
-      const uint32_t items = p.rows * p.kv_heads * chunks;
-      for (uint32_t it = blockIdx.x; it < items; it += gridDim.x) {
+      for (uint32_t it = blockIdx.x; it < att_items; it += gridDim.x) {
         const uint32_t ch = it % chunks, kvh = (it / chunks) % p.kv_heads, b = it / (chunks * p.kv_heads);
         float* part = p.part_att + (size_t)it * att_pitch;
         __syncthreads();
@@ -315,34 +441,35 @@ __global__ void __launch_bounds__(DT, 1) decode_layers_kernel(const DecodeParams
         };
         const float* cs = p.cos + (size_t)pos * HD;
         const float* sn = p.sin + (size_t)pos * HD;
-        // rotated queries of the group (F32), and the step's key and value for this head
+        // rotated queries of the group (F32)
         for (uint32_t i = tid; i < group * HD; i += DT) {
           const uint32_t g = i / HD, j = i - g * HD, base = (kvh * group + g) * HD;
           const float x = qkv_at(base + j), xs = qkv_at(base + (j < HD / 2 ? j + HD / 2 : j - HD / 2));
           s.qs[g * HD + j] = __fadd_rn(__fmul_rn(x, cs[j]), __fmul_rn(xs, sn[j]));
         }
-        const bool writer = (uint32_t)pos / DCH == ch;
-        if (writer && tid < HD) {
-          const uint32_t j = tid, kb = QC + kvh * HD, vb = QC + KC + kvh * HD;
-          const float x = qkv_at(kb + j), xs = qkv_at(kb + (j < HD / 2 ? j + HD / 2 : j - HD / 2));
-          const float kr = __fadd_rn(__fmul_rn(x, cs[j]), __fmul_rn(xs, sn[j]));
-          const uint64_t row = (uint64_t)b * p.max_len + (uint32_t)pos;
-          reinterpret_cast<uint16_t*>(L.kc)[row * KC + kvh * HD + j] = f32_to_bf16_bits(__float_as_uint(kr));
-          reinterpret_cast<uint16_t*>(L.vc)[row * KC + kvh * HD + j] = f32_to_bf16_bits(__float_as_uint(qkv_at(vb + j)));
-        }
-        __syncthreads();                               // the step's own row is visible to this block
-        // the chunk's keys and values into shared memory: 64 rows of 128 bytes each
-        {
+        if (it != blockIdx.x) {                        // not the item fetched ahead: the chunk's rows now
           const uint64_t row0 = (uint64_t)b * p.max_len + (uint64_t)ch * DCH;
           for (uint32_t i = tid; i < DCH * 8; i += DT) {
             const uint32_t j = i >> 3, u = i & 7;
-            const uint4 kq = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(L.kc) + (row0 + j) * KC + kvh * HD + u * 8);
-            const uint4 vq = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(L.vc) + (row0 + j) * KC + kvh * HD + u * 8);
-            uint32_t* kd = s.ksm + j * 33 + u * 4;
-            uint32_t* vd = s.vsm + j * 33 + u * 4;
-            kd[0] = kq.x; kd[1] = kq.y; kd[2] = kq.z; kd[3] = kq.w;
-            vd[0] = vq.x; vd[1] = vq.y; vd[2] = vq.z; vd[3] = vq.w;
+            cp_async16(s.ksm + j * 8 + (u ^ (j & 7)), reinterpret_cast<const uint16_t*>(L.kc) + (row0 + j) * KC + kvh * HD + u * 8);
+            cp_async16(s.vsm + j * 8 + (u ^ (j & 7)), reinterpret_cast<const uint16_t*>(L.vc) + (row0 + j) * KC + kvh * HD + u * 8);
           }
+          cp_async_commit();
+        }
+        // NB: the tile of the output projection shares the commit group of the item fetched ahead; waiting for all is right
+        cp_async_wait_all();
+        __syncthreads();
+        // the step's own key (rotated, rounded once to BF16) and value: into the cache, and into the chunk that holds them
+        if ((uint32_t)pos / DCH == ch && tid < HD) {
+          const uint32_t j = tid, kb = QC + kvh * HD, vb = QC + KC + kvh * HD, jr = (uint32_t)pos % DCH;
+          const float x = qkv_at(kb + j), xs = qkv_at(kb + (j < HD / 2 ? j + HD / 2 : j - HD / 2));
+          const uint16_t kbits = f32_to_bf16_bits(__float_as_uint(__fadd_rn(__fmul_rn(x, cs[j]), __fmul_rn(xs, sn[j]))));
+          const uint16_t vbits = f32_to_bf16_bits(__float_as_uint(qkv_at(vb + j)));
+          const uint64_t row = (uint64_t)b * p.max_len + (uint32_t)pos;
+          reinterpret_cast<uint16_t*>(L.kc)[row * KC + kvh * HD + j] = kbits;
+          reinterpret_cast<uint16_t*>(L.vc)[row * KC + kvh * HD + j] = vbits;
+          reinterpret_cast<uint16_t*>(s.ksm + jr * 8 + ((j >> 3) ^ (jr & 7)))[j & 7] = kbits;
+          reinterpret_cast<uint16_t*>(s.vsm + jr * 8 + ((j >> 3) ^ (jr & 7)))[j & 7] = vbits;
         }
         __syncthreads();
         // scores: a thread a (head of the group, position)
@@ -352,13 +479,16 @@ __global__ void __launch_bounds__(DT, 1) decode_layers_kernel(const DecodeParams
           const uint32_t pj = ch * DCH + j;
           if (pj <= (uint32_t)pos) {
             float t = 0.f;
-            const uint32_t* kr = s.ksm + j * 33;
             const float* q = s.qs + g * HD;
-#pragma unroll 8
-            for (int d2 = 0; d2 < HD / 2; ++d2) {
-              const uint32_t w2 = kr[d2];
-              t = fmaf(q[2 * d2], __uint_as_float(w2 << 16), t);
-              t = fmaf(q[2 * d2 + 1], __uint_as_float(w2 & 0xffff0000u), t);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const uint4 kq = s.ksm[j * 8 + (u ^ (j & 7))];
+              const uint32_t w4[4] = {kq.x, kq.y, kq.z, kq.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                t = fmaf(q[u * 8 + 2 * e], __uint_as_float(w4[e] << 16), t);
+                t = fmaf(q[u * 8 + 2 * e + 1], __uint_as_float(w4[e] & 0xffff0000u), t);
+              }
             }
             sc = __fmul_rn(t, p.scale);
           }
@@ -384,8 +514,8 @@ __global__ void __launch_bounds__(DT, 1) decode_layers_kernel(const DecodeParams
           float o = 0.f;
           const float* pr = s.ps + g * DCH;
           for (int jj = 0; jj < DCH; ++jj) {
-            const uint32_t w2 = s.vsm[jj * 33 + (d >> 1)];
-            o = fmaf(pr[jj], __uint_as_float((d & 1) ? (w2 & 0xffff0000u) : (w2 << 16)), o);
+            const uint16_t hv = reinterpret_cast<const uint16_t*>(s.vsm + jj * 8 + ((d >> 3) ^ (jj & 7)))[d & 7];
+            o = fmaf(pr[jj], __uint_as_float((uint32_t)hv << 16), o);
           }
           part[g * (HD + 2) + d] = o;
           if (d == 0) {
@@ -416,14 +546,23 @@ __global__ void __launch_bounds__(DT, 1) decode_layers_kernel(const DecodeParams
       }
       s.vec[(size_t)r * p.vec_cols + c] = v;
     }
+    cp_async_wait_all();
     __syncthreads();
     {
-      const uint32_t nb = H / DCOLS, items = nb * p.ks_o;
+      const uint32_t items = nb_h * p.ks_o;
       for (uint32_t it = blockIdx.x; it < items; it += gridDim.x) {
-        const uint32_t cb = it % nb, ks = it / nb, k0 = ks * p.sl_o;
+        const uint32_t cb = it % nb_h, ks = it / nb_h, k0 = ks * p.sl_o;
         const uint32_t len = k0 + p.sl_o <= QC ? p.sl_o : QC - k0;
-        product_item<MT>(s.vec + k0, p.vec_cols, L.o, (L.bfp >> 1) & 1, QC, H, k0, len, cb * DCOLS, p.part_o + (size_t)ks * MT * H, s.red);
+        float* out = p.part_o + (size_t)ks * MT * H;
+        product_item<MT>(s.vec + k0, p.vec_cols, L.o, (L.bfp >> 1) & 1, QC, H, k0, len, cb * DCOLS, s.red, s.wt, it == blockIdx.x ? len : 0,
+                         [&](int r, uint32_t c, float t) { out[(size_t)r * H + c] = t; });
       }
+    }
+    __syncthreads();
+    {
+      const Item it = first_item(nb_gu, p.ks_gu, p.sl_gu, H);
+      if (it.any) fetch_tile(s.wt, L.gate_up, (L.bfp >> 2) & 1, H, 2 * FF, it.k0, it.len, it.cb * DCOLS);
+      cp_async_commit();
     }
     if (!grid_barrier(p.bar, barrier_index++, limit, p.err, &ok_word)) return;
 
@@ -436,21 +575,31 @@ __global__ void __launch_bounds__(DT, 1) decode_layers_kernel(const DecodeParams
     }
     __syncthreads();
     norm_rows<MT>(s.xres, H, L.norm2, p.eps, s.vec, p.vec_cols, s.stat);
+    cp_async_wait_all();
+    __syncthreads();
     {
-      const uint32_t nb = 2 * FF / DCOLS, items = nb * p.ks_gu;
+      const uint32_t items = nb_gu * p.ks_gu;
       for (uint32_t it = blockIdx.x; it < items; it += gridDim.x) {
-        const uint32_t cb = it % nb, ks = it / nb, k0 = ks * p.sl_gu;
+        const uint32_t cb = it % nb_gu, ks = it / nb_gu, k0 = ks * p.sl_gu;
         const uint32_t len = k0 + p.sl_gu <= H ? p.sl_gu : H - k0;
-        product_item<MT>(s.vec + k0, p.vec_cols, L.gate_up, (L.bfp >> 2) & 1, H, 2 * FF, k0, len, cb * DCOLS, p.part_gu + (size_t)ks * MT * 2 * FF, s.red);
+        float* out = p.part_gu + (size_t)ks * MT * 2 * FF;
+        product_item<MT>(s.vec + k0, p.vec_cols, L.gate_up, (L.bfp >> 2) & 1, H, 2 * FF, k0, len, cb * DCOLS, s.red, s.wt,
+                         it == blockIdx.x ? len : 0, [&](int r, uint32_t c, float t) { out[(size_t)r * 2 * FF + c] = t; });
       }
+    }
+    __syncthreads();
+    {
+      const Item it = first_item(nb_h, p.ks_dn, p.sl_dn, FF);
+      if (it.any) fetch_tile(s.wt, L.down, (L.bfp >> 3) & 1, FF, H, it.k0, it.len, it.cb * DCOLS);
+      cp_async_commit();
     }
     if (!grid_barrier(p.bar, barrier_index++, limit, p.err, &ok_word)) return;
 
     // ---- phase 5: silu(gate) * up for an item's slice of k, the down projection ------------------------------------------
     {
-      const uint32_t nb = H / DCOLS, items = nb * p.ks_dn;
+      const uint32_t items = nb_h * p.ks_dn;
       for (uint32_t it = blockIdx.x; it < items; it += gridDim.x) {
-        const uint32_t cb = it % nb, ks = it / nb, k0 = ks * p.sl_dn;
+        const uint32_t cb = it % nb_h, ks = it / nb_h, k0 = ks * p.sl_dn;
         const uint32_t len = k0 + p.sl_dn <= FF ? p.sl_dn : FF - k0;
         __syncthreads();
         for (uint32_t i = tid; i < (uint32_t)MT * len; i += DT) {
@@ -463,12 +612,22 @@ __global__ void __launch_bounds__(DT, 1) decode_layers_kernel(const DecodeParams
           const float a = bf16_round(gt), bq = bf16_round(up);
           s.vec[(size_t)r * p.vec_cols + kk] = bf16_round(__fmul_rn(__fmul_rn(a, sigmoid_flex(a)), bq));   // SILU_MUL, BF16 result
         }
+        cp_async_wait_all();
         __syncthreads();
-        product_item<MT>(s.vec, p.vec_cols, L.down, (L.bfp >> 3) & 1, FF, H, k0, len, cb * DCOLS, p.part_dn + (size_t)ks * MT * H, s.red);
+        float* out = p.part_dn + (size_t)ks * MT * H;
+        product_item<MT>(s.vec, p.vec_cols, L.down, (L.bfp >> 3) & 1, FF, H, k0, len, cb * DCOLS, s.red, s.wt, it == blockIdx.x ? len : 0,
+                         [&](int r, uint32_t c, float t) { out[(size_t)r * H + c] = t; });
       }
     }
+    __syncthreads();
+    if (l + 1 < p.n_layers) {                          // the next layer's QKV tile, under the barrier
+      const Item it = first_item(nb_qkv, p.ks_qkv, p.sl_qkv, H);
+      if (it.any) fetch_tile(s.wt, p.layers[l + 1].qkv, p.layers[l + 1].bfp & 1, H, NQKV, it.k0, it.len, it.cb * DCOLS);
+    }
+    cp_async_commit();
     if (!grid_barrier(p.bar, barrier_index++, limit, p.err, &ok_word)) return;
   }
+  cp_async_wait_all();
 
   // ---- the stream's last value and its norm: the head product's input -------------------------------------------------------
   if (blockIdx.x == 0) {
@@ -487,16 +646,539 @@ __global__ void __launch_bounds__(DT, 1) decode_layers_kernel(const DecodeParams
   }
 }
 
+// ---- the same step on ONE thread-block cluster --------------------------------------------------------------------------
+// Sixteen (or eight) blocks of one cluster instead of a grid: what a phase hands to the next travels through
+// distributed shared memory (every block stores its results into every block's shared memory), and the phases are
+// separated by the hardware's cluster barrier instead of a counter in global memory -- a few hundred nanoseconds where
+// the grid's barrier and the round trips through L2 for the partial sums cost microseconds.  Only the down projection
+// slices k (its partial sums are added in a fixed order by every block); the other products give a block whole columns.
+//
+// With so few blocks the step is bound by how many bytes of weights a block keeps in flight, so the weights do not wait
+// for the phase that uses them: the tiles a block will multiply by are known from the start (layer after layer, phase
+// after phase, item after item), and a ring of shared-memory slots is kept full of the next chunks of 64 k-rows by
+// TMA (one tiled copy of 64 rows by 64 columns a chunk, completing on the slot's mbarrier), across phases and cluster
+// barriers: loads issued by threads keep some 16 KB a block in flight, far too little for sixteen blocks to draw the
+// device's bandwidth, where the ring holds up to 130 KB a block.  A product waits for its next chunk, multiplies from
+// shared memory, and refills the slot with the chunk that is R chunks ahead.  (A BFP8 matrix's exponents, four bytes
+// a row of a chunk, are too narrow for a tiled copy and come by cp.async into the same slot.)
+namespace cg = cooperative_groups;
+
+struct ClusterParams {
+  const DecodeLayerDev* layers;
+  uint32_t n_layers, rows, hidden, heads, kv_heads, ff, max_len, attend;
+  float eps, scale;
+  const float* x0;
+  const void* final_norm;
+  const float* cos;
+  const float* sin;
+  const int32_t* pos;
+  uint16_t* out;
+  int* err;
+  uint32_t ks_dn, sl_dn, vec_cols, att_items;
+  const CUtensorMap* maps;   // [n_layers][4]: qkv, o, gate|up, down as [k, n] with a box of 64 rows by 64 columns
+};
+
+constexpr int CK_ROWS = 192;                           // k-rows of a chunk: a wait, a barrier and an issue cost some 300 cycles a chunk whatever its size
+constexpr int GN = 4;                                  // gains a thread fetches ahead: the cluster form takes hidden <= GN * 256
+constexpr uint32_t SLOT_BYTES = CK_ROWS * 128 + CK_ROWS * 4;   // rows of 64 BF16 (or 64 datum bytes), then four exponent bytes a row
+static_assert(SLOT_BYTES % 128 == 0 && CK_ROWS % 96 == 0 && CK_ROWS <= 256, "a slot is whole 128-byte lines; a box has at most 256 rows");
+template <int MT> struct RingDepth { static constexpr int value = MT == 1 ? 5 : (MT == 2 ? 4 : 2); };
+
+// The chunks of weights a block multiplies by during ONE layer, in the order it uses them: the same list for every layer,
+// so it is written once (by one thread, into shared memory) and the step's issue path only reads it.
+struct ChunkEnt { uint16_t phase, rows, cb, k0; };     // phase 0 qkv, 1 o, 2 gate|up, 3 down; rows of the chunk; column block; first k-row
+constexpr uint32_t SCHED_MAX = 256;
+
+struct WeightWalk {
+  const ClusterParams* p;
+  const DecodeLayerDev* lay;                           // the layers' records, copied into shared memory
+  const ChunkEnt* tab;
+  uint32_t cnt, ii, il;                                // the list's length; the next chunk to issue: entry ii of layer il
+  bool any_bfp;                                        // some matrix of the step is BFP8: every issue commits a cp.async group
+  // thread 0 writes the list; every thread calls this, the caller's __syncthreads publishes it
+  __device__ void start(const ClusterParams* pp, const DecodeLayerDev* lay_, ChunkEnt* tab_, uint32_t* cnt_sm, uint32_t me, uint32_t C) {
+    p = pp; lay = lay_; tab = tab_; ii = 0; il = 0;
+    if (threadIdx.x == 0) {
+      const uint32_t H = pp->hidden, QC = pp->heads * HD, NQKV = QC + 2 * pp->kv_heads * HD, FF = pp->ff, nb_h = H / DCOLS;
+      uint32_t c = 0;
+      for (uint32_t ph = 0; ph < 4; ++ph) {
+        const uint32_t items = ph == 0 ? NQKV / DCOLS : (ph == 1 ? nb_h : (ph == 2 ? 2 * FF / DCOLS : nb_h * pp->ks_dn));
+        for (uint32_t item = me; item < items; item += C) {
+          const uint32_t kbase = ph == 3 ? (item / nb_h) * pp->sl_dn : 0;
+          const uint32_t total = ph == 0 || ph == 2 ? H : (ph == 1 ? QC : (kbase + pp->sl_dn <= FF ? pp->sl_dn : FF - kbase));
+          const uint32_t cb = ph == 3 ? item % nb_h : item;
+          for (uint32_t k = 0; k < total && c < SCHED_MAX; k += CK_ROWS)
+            tab_[c++] = ChunkEnt{(uint16_t)ph, (uint16_t)(total - k < (uint32_t)CK_ROWS ? total - k : CK_ROWS), (uint16_t)cb, (uint16_t)(kbase + k)};
+        }
+      }
+      *cnt_sm = c;
+    }
+  }
+  // issue the copy of the next chunk into `slot` (called by every thread of the block), then move on; when the walk is
+  // over only an empty cp.async group is committed, so that the groups keep counting chunks
+  __device__ __forceinline__ void issue(uint8_t* slot, uint64_t* bar) {
+    if (il < p->n_layers) {
+      const ChunkEnt e = tab[ii];
+      const int bfp = (lay[il].bfp >> e.phase) & 1;
+      if (threadIdx.x == 0) {
+        tc::mbar_expect_tx(bar, bfp ? CK_ROWS * 64 : CK_ROWS * 128);   // the whole box counts, rows past the matrix filled with zeros
+        tc::tma_load_2d(slot, p->maps + (size_t)il * 4 + e.phase, bar, (int32_t)e.cb * DCOLS, (int32_t)e.k0);
+      }
+      if (bfp && threadIdx.x < e.rows) {
+        const DecodeLayerDev& L = lay[il];
+        const uint32_t H = p->hidden, QC = p->heads * HD, FF = p->ff;
+        const uint32_t n = e.phase == 0 ? QC + 2 * p->kv_heads * HD : (e.phase == 2 ? 2 * FF : H);
+        const uint64_t k_total = e.phase == 0 || e.phase == 2 ? H : (e.phase == 1 ? QC : FF);
+        const uint8_t* w = reinterpret_cast<const uint8_t*>(e.phase == 0 ? L.qkv : (e.phase == 1 ? L.o : (e.phase == 2 ? L.gate_up : L.down)));
+        const uint8_t* ex = w + k_total * n + (uint64_t)e.k0 * (n / 16) + (uint32_t)e.cb * (DCOLS / 16);
+        cp_async4(slot + (size_t)CK_ROWS * 128 + (size_t)threadIdx.x * 4, ex + (uint64_t)threadIdx.x * (n / 16));
+      }
+      if (++ii == cnt) { ii = 0; ++il; }
+    }
+    if (any_bfp) cp_async_commit();
+  }
+};
+
+// mbar_wait's abort flag: a product's wait has no other block to hear from, so the flag is the error word itself (set by
+// any block of the engine's kernels that gave up)
+__device__ __forceinline__ volatile int& dead_flag_of(int* err) { return *reinterpret_cast<volatile int*>(err); }
+template <int N> __device__ __forceinline__ void cp_async_wait_upto() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// One product item fed from the ring: `len` k-rows in chunks of 64, A's rows in shared memory (pitch lda, offset to the item's k0).
+template <int MT, int R, class Emit>
+__device__ __forceinline__ void product_stream(const float* a, uint32_t lda, int bfp, uint32_t len, uint32_t c0, uint64_t n, float* red,
+                                               uint8_t* ring, uint64_t* bars, uint32_t& head, uint32_t& parity, bool& dead, long long limit,
+                                               int* err, WeightWalk& walk, Emit emit) {
+  const int tid = threadIdx.x, cg_ = tid & 7, kr = tid >> 3, warp = tid >> 5, lane = tid & 31;
+  float acc[MT][8];
+#pragma unroll
+  for (int r = 0; r < MT; ++r)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[r][e] = 0.f;
+  for (uint32_t base = 0; base < len; base += CK_ROWS) {
+    // the oldest of the R chunks in flight: its tile (the slot's mbarrier) and, for BFP8, its exponents (the oldest
+    // cp.async group of every thread, then the block's barrier)
+    if (!dead && !tc::mbar_wait(&bars[head], (parity >> head) & 1u, &dead_flag_of(err), limit)) {
+      dead = true;                                     // recorded; the block walks on without waiting, so that the cluster's barriers are still met
+      atomicCAS(err, 0, TIMEOUT_CODE);
+    }
+    parity ^= 1u << head;
+    if (bfp) {
+      cp_async_wait_upto<R - 1>();
+      __syncthreads();
+    }
+    const uint8_t* slot = ring + (size_t)head * SLOT_BYTES;
+    const uint32_t rows = len - base < (uint32_t)CK_ROWS ? len - base : CK_ROWS;
+    // three k-rows a thread at a time, their loads first; a row past the chunk's end counts as zeros
+#pragma unroll
+    for (int h2 = 0; h2 < CK_ROWS / 32; h2 += 3) {
+      float x[3][8], av[3][MT];
+#pragma unroll
+      for (int j = 0; j < 3; ++j) {
+        const uint32_t rr = kr + (h2 + j) * 32;
+        const bool in = rr < rows;
+        if (!bfp) {
+          uint4 raw = make_uint4(0, 0, 0, 0);
+          if (in) raw = *reinterpret_cast<const uint4*>(slot + ((size_t)rr * 8 + cg_) * 16);
+          x[j][0] = __uint_as_float(raw.x << 16); x[j][1] = __uint_as_float(raw.x & 0xffff0000u);
+          x[j][2] = __uint_as_float(raw.y << 16); x[j][3] = __uint_as_float(raw.y & 0xffff0000u);
+          x[j][4] = __uint_as_float(raw.z << 16); x[j][5] = __uint_as_float(raw.z & 0xffff0000u);
+          x[j][6] = __uint_as_float(raw.w << 16); x[j][7] = __uint_as_float(raw.w & 0xffff0000u);
+        } else {
+          uint2 raw = make_uint2(0, 0);
+          uint32_t ex = 0;
+          if (in) {
+            raw = *reinterpret_cast<const uint2*>(slot + (size_t)rr * 64 + cg_ * 8);
+            ex = slot[(size_t)CK_ROWS * 128 + (size_t)rr * 4 + (cg_ >> 1)];
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            x[j][e] = bfp8_value((raw.x >> (e * 8)) & 0xffu, ex);
+            x[j][4 + e] = bfp8_value((raw.y >> (e * 8)) & 0xffu, ex);
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < MT; ++r) av[j][r] = in ? a[(size_t)r * lda + base + rr] : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 3; ++j)                       // ascending k, as before
+#pragma unroll
+        for (int r = 0; r < MT; ++r)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[r][e] = fmaf(av[j][r], x[j][e], acc[r][e]);
+    }
+    __syncthreads();                                   // every thread is done with the slot: refill it
+    walk.issue(ring + (size_t)head * SLOT_BYTES, &bars[head]);
+    head = head + 1 == (uint32_t)R ? 0 : head + 1;
+  }
+#pragma unroll
+  for (int r = 0; r < MT; ++r)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float v = acc[r][e];
+      v += __shfl_xor_sync(0xffffffffu, v, 8);
+      v += __shfl_xor_sync(0xffffffffu, v, 16);
+      acc[r][e] = v;
+    }
+  if (lane < 8) {
+#pragma unroll
+    for (int r = 0; r < MT; ++r)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) red[((size_t)warp * MT + r) * DCOLS + lane * 8 + e] = acc[r][e];
+  }
+  __syncthreads();
+  for (int i = tid; i < MT * DCOLS; i += DT) {
+    const int r = i / DCOLS, cc = i - r * DCOLS;
+    float t = 0.f;
+#pragma unroll
+    for (int wv = 0; wv < DT / 32; ++wv) t += red[((size_t)wv * MT + r) * DCOLS + cc];
+    emit(r, cc, t);                                    // into the block's staging row: the caller sends it on
+  }
+  __syncthreads();                                     // `red` is free for the next item, the staged results are whole
+}
+
+// Send `pieces` 16-byte pieces staged in this block's shared memory to the same place in EVERY block of the cluster
+// (this one included): piece q goes to `dst + where(q)` (in 16-byte units).  A (piece, block) pair a thread, so one
+// product item's results leave in one or a few stores a thread -- a thread that stored sixteen times in a row, once a
+// block, spent some 5,000 cycles an item.
+template <class Where>
+__device__ __forceinline__ void send_to_all(cg::cluster_group& cluster, uint32_t C, uint4* dst, const uint4* staged, uint32_t pieces, Where where) {
+  for (uint32_t idx = threadIdx.x; idx < pieces * C; idx += DT) {
+    const uint32_t q = idx % pieces, d = idx / pieces;
+    cluster.map_shared_rank(dst, d)[where(q)] = staged[q];
+  }
+}
+
+template <int MT>
+__global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterParams p) {
+  constexpr int R = RingDepth<MT>::value;
+  extern __shared__ __align__(16) float smem[];
+  cg::cluster_group cluster = cg::this_cluster();
+  const uint32_t C = cluster.num_blocks(), me = cluster.block_rank();
+  const int tid = threadIdx.x;
+  const uint32_t H = p.hidden, QC = p.heads * HD, KC = p.kv_heads * HD, NQKV = QC + 2 * KC, FF = p.ff;
+  const uint32_t group = p.heads / p.kv_heads, chunks = p.attend / DCH;
+  constexpr uint32_t APH = HD + 4;                    // a head's partial of an attention item: 64 sums, the maximum, the sum, two unused (whole 16-byte pieces)
+  constexpr uint32_t AP = 4 * APH;                    // an attention item's partial
+  // shared memory (the same offsets in every block of the cluster)
+  uint8_t* ring = reinterpret_cast<uint8_t*>(((uintptr_t)smem + 127) & ~(uintptr_t)127);   // a tiled copy lands on 128-byte lines
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)R * SLOT_BYTES);             // [16]
+  uint4* ksm = reinterpret_cast<uint4*>(bars + 16);
+  uint4* vsm = ksm + DCH * 8;
+  float* xres = reinterpret_cast<float*>(vsm + DCH * 8);          // [MT][H]
+  float* vec = xres + (size_t)MT * H;                             // [MT][vec_cols]
+  float* qkv = vec + (size_t)MT * p.vec_cols;                     // [MT][NQKV]   BF16 values, from every block
+  float* att = qkv + (size_t)MT * NQKV;                           // [att_items][AP]
+  float* osum = att + (size_t)p.att_items * AP;                   // [MT][H]
+  float* dn = osum + (size_t)MT * H;                              // [ks_dn][MT][H]
+  float* red = dn + (size_t)p.ks_dn * MT * H;                     // [8][MT][64]
+  float* qs = red + 8 * MT * DCOLS;
+  float* ps = qs + 4 * HD;
+  float* stat = ps + 4 * DCH;
+  float* stage = stat + 16;                                       // [MT][64] a product item's results before they are sent; [AP] an attention item's
+  float* g1 = stage + (MT * DCOLS > (int)AP ? MT * DCOLS : AP);   // [H] the gains of the next first norm
+  float* g2 = g1 + H;                                             // [H] the gains of the next second norm
+  float* cs = g2 + H;                                             // [64] the position's row of the cosine table
+  float* sn = cs + HD;                                            // [64] and of the sine table
+  DecodeLayerDev* lay = reinterpret_cast<DecodeLayerDev*>(sn + HD);   // [n_layers]
+  ChunkEnt* tab = reinterpret_cast<ChunkEnt*>(lay + p.n_layers);  // [SCHED_MAX]
+  uint32_t* tab_len = reinterpret_cast<uint32_t*>(tab + SCHED_MAX);   // [2]
+  uint16_t* gu = reinterpret_cast<uint16_t*>(((uintptr_t)(tab_len + 2) + 15) & ~(uintptr_t)15);   // [MT][2 FF] BF16
+
+  const int32_t pos = *p.pos;
+  if (pos < 0 || (uint32_t)pos >= p.max_len || (uint32_t)pos >= p.attend) {   // every block sees the same position
+    if (tid == 0) atomicCAS(p.err, 0, 6);
+    return;
+  }
+  const uint32_t nb_qkv = NQKV / DCOLS, nb_h = H / DCOLS, nb_gu = 2 * FF / DCOLS;
+  // what every layer needs from global memory and no step changes: read once, so that no phase waits for it
+  for (uint32_t i = tid; i < p.n_layers * (uint32_t)(sizeof(DecodeLayerDev) / 8); i += DT)
+    reinterpret_cast<uint64_t*>(lay)[i] = reinterpret_cast<const uint64_t*>(p.layers)[i];
+  if (tid < HD) { cs[tid] = p.cos[(size_t)pos * HD + tid]; sn[tid] = p.sin[(size_t)pos * HD + tid]; }
+  WeightWalk walk;
+  walk.start(&p, lay, tab, tab_len, me, C);
+  __syncthreads();
+  walk.cnt = *tab_len;
+  {
+    uint32_t any = 0;
+    for (uint32_t l = 0; l < p.n_layers; ++l) any |= lay[l].bfp;
+    walk.any_bfp = any != 0;
+  }
+  for (uint32_t c = tid; c < H; c += DT) g1[c] = bf16_at(lay[0].norm1, c);
+  uint32_t head = 0, parity = 0;
+  bool dead = false;
+  const long long limit = tc::wait_limit_of(p.err);
+  if (tid == 0) {
+    for (int r = 0; r < R; ++r) tc::mbar_init(&bars[r], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  for (int r = 0; r < R; ++r) walk.issue(ring + (size_t)r * SLOT_BYTES, &bars[r]);   // the ring starts full
+
+  for (uint32_t l = 0; l < p.n_layers; ++l) {
+    const DecodeLayerDev L = lay[l];
+    // the gains of this layer's second norm: asked for now, kept in registers, stored after the products
+    float gn[GN];
+#pragma unroll
+    for (int i = 0; i < GN; ++i) gn[i] = tid + i * DT < H ? bf16_at(L.norm2, tid + i * DT) : 0.f;
+    // ---- phase 1 ----
+    for (uint32_t i = tid; i < (uint32_t)MT * H; i += DT) {
+      const uint32_t r = i / H, c = i - r * H;
+      float v;
+      if (l == 0) {
+        v = r < p.rows ? p.x0[(size_t)r * H + c] : 0.f;
+      } else {
+        float d = 0.f;
+        for (uint32_t k = 0; k < p.ks_dn; ++k) d += dn[((size_t)k * MT + r) * H + c];
+        v = __fadd_rn(xres[i], d);
+      }
+      xres[i] = v;
+    }
+    __syncthreads();
+    norm_rows_sm<MT>(xres, H, g1, p.eps, vec, p.vec_cols, stat);
+    for (uint32_t it = me; it < nb_qkv; it += C) {
+      product_stream<MT, R>(vec, p.vec_cols, L.bfp & 1, H, it * DCOLS, NQKV, red, ring, bars, head, parity, dead, limit, p.err, walk,
+                            [&](int r, int cc, float t) { stage[r * DCOLS + cc] = bf16_round(t); });   // the product's BF16 result
+      send_to_all(cluster, C, reinterpret_cast<uint4*>(qkv), reinterpret_cast<const uint4*>(stage), MT * 16,
+                  [&](uint32_t q) { return ((q >> 4) * NQKV + it * DCOLS) / 4 + (q & 15); });
+    }
+#pragma unroll
+    for (int i = 0; i < GN; ++i)
+      if (tid + i * DT < H) g2[tid + i * DT] = gn[i];
+    // the first attention item's cache rows (earlier steps wrote them) are asked for before the barrier
+    uint4 kreg[2], vreg[2];
+    auto load_cache = [&](uint32_t it) {
+      const uint32_t ch = it % chunks, kvh = (it / chunks) % p.kv_heads, b = it / (chunks * p.kv_heads);
+      if (ch * DCH > (uint32_t)pos) return;
+      const uint64_t row0 = (uint64_t)b * p.max_len + (uint64_t)ch * DCH;
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const uint32_t i = tid + h2 * DT, j = i >> 3, u = i & 7;
+        kreg[h2] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(L.kc) + (row0 + j) * KC + kvh * HD + u * 8);
+        vreg[h2] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(L.vc) + (row0 + j) * KC + kvh * HD + u * 8);
+      }
+    };
+    if (me < p.att_items) load_cache(me);
+    cluster.sync();
+
+    // ---- phase 2 ----
+    for (uint32_t it = me; it < p.att_items; it += C) {
+      const uint32_t ch = it % chunks, kvh = (it / chunks) % p.kv_heads, b = it / (chunks * p.kv_heads);
+      __syncthreads();
+      if (it != me) load_cache(it);
+      if (ch * DCH > (uint32_t)pos) {
+        for (uint32_t i = tid; i < AP; i += DT) stage[i] = i % APH == HD ? -INFINITY : 0.f;
+        __syncthreads();
+        send_to_all(cluster, C, reinterpret_cast<uint4*>(att + (size_t)it * AP), reinterpret_cast<const uint4*>(stage), group * (APH / 4),
+                    [&](uint32_t q) { return q; });
+        continue;
+      }
+      const float* qrow = qkv + (size_t)b * NQKV;
+      for (uint32_t i = tid; i < group * HD; i += DT) {
+        const uint32_t g = i / HD, j = i - g * HD, base = (kvh * group + g) * HD;
+        qs[g * HD + j] = __fadd_rn(__fmul_rn(qrow[base + j], cs[j]), __fmul_rn(qrow[base + (j < HD / 2 ? j + HD / 2 : j - HD / 2)], sn[j]));
+      }
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const uint32_t i = tid + h2 * DT, j = i >> 3, u = i & 7;
+        ksm[j * 8 + (u ^ (j & 7))] = kreg[h2];
+        vsm[j * 8 + (u ^ (j & 7))] = vreg[h2];
+      }
+      __syncthreads();
+      if ((uint32_t)pos / DCH == ch && tid < HD) {
+        const uint32_t j = tid, kb = QC + kvh * HD, vb = QC + KC + kvh * HD, jr = (uint32_t)pos % DCH;
+        const float x = qrow[kb + j], xs = qrow[kb + (j < HD / 2 ? j + HD / 2 : j - HD / 2)];
+        const uint16_t kbits = f32_to_bf16_bits(__float_as_uint(__fadd_rn(__fmul_rn(x, cs[j]), __fmul_rn(xs, sn[j]))));
+        const uint16_t vbits = f32_to_bf16_bits(__float_as_uint(qrow[vb + j]));
+        const uint64_t row = (uint64_t)b * p.max_len + (uint32_t)pos;
+        reinterpret_cast<uint16_t*>(L.kc)[row * KC + kvh * HD + j] = kbits;
+        reinterpret_cast<uint16_t*>(L.vc)[row * KC + kvh * HD + j] = vbits;
+        reinterpret_cast<uint16_t*>(ksm + jr * 8 + ((j >> 3) ^ (jr & 7)))[j & 7] = kbits;
+        reinterpret_cast<uint16_t*>(vsm + jr * 8 + ((j >> 3) ^ (jr & 7)))[j & 7] = vbits;
+      }
+      __syncthreads();
+      const uint32_t g = tid / DCH, j = tid - g * DCH;
+      float sc = -INFINITY;
+      if (g < group && ch * DCH + j <= (uint32_t)pos) {
+        float t = 0.f;
+        const float* q = qs + g * HD;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const uint4 kq = ksm[j * 8 + (u ^ (j & 7))];
+          const uint32_t w4[4] = {kq.x, kq.y, kq.z, kq.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            t = fmaf(q[u * 8 + 2 * e], __uint_as_float(w4[e] << 16), t);
+            t = fmaf(q[u * 8 + 2 * e + 1], __uint_as_float(w4[e] & 0xffff0000u), t);
+          }
+        }
+        sc = __fmul_rn(t, p.scale);
+      }
+      float m = sc;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      if ((tid & 31) == 0) stat[tid >> 5] = m;
+      __syncthreads();
+      const float mh = g < group ? fmaxf(fmaxf(stat[2 * g], stat[2 * g + 1]), -3.402823466e38f) : 0.f;
+      const float e = g < group ? expf(sc - mh) : 0.f;
+      if (g < group) ps[g * DCH + j] = e;
+      float sum = e;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      __syncthreads();
+      if ((tid & 31) == 0) stat[8 + (tid >> 5)] = sum;
+      __syncthreads();
+      if (g < group) {
+        const uint32_t d = j;
+        float o = 0.f;
+        const float* pr = ps + g * DCH;
+        for (int jj = 0; jj < DCH; ++jj) {
+          const uint16_t hv = reinterpret_cast<const uint16_t*>(vsm + jj * 8 + ((d >> 3) ^ (jj & 7)))[d & 7];
+          o = fmaf(pr[jj], __uint_as_float((uint32_t)hv << 16), o);
+        }
+        const float lsum = stat[8 + 2 * g] + stat[8 + 2 * g + 1];
+        stage[g * APH + d] = o;
+        if (d == 0) { stage[g * APH + HD] = mh; stage[g * APH + HD + 1] = lsum; }
+      }
+      __syncthreads();
+      send_to_all(cluster, C, reinterpret_cast<uint4*>(att + (size_t)it * AP), reinterpret_cast<const uint4*>(stage), group * (APH / 4),
+                  [&](uint32_t q) { return q; });
+    }
+    cluster.sync();
+
+    // ---- phase 3 ----
+    for (uint32_t i = tid; i < (uint32_t)MT * QC; i += DT) {
+      const uint32_t r = i / QC, c = i - r * QC, h = c / HD, d = c - h * HD, kvh = h / group, g = h - kvh * group;
+      float v = 0.f;
+      if (r < p.rows) {
+        const float* base = att + (size_t)((r * p.kv_heads + kvh) * chunks) * AP + g * APH;
+        float M = -3.402823466e38f;
+        for (uint32_t c2 = 0; c2 < chunks; ++c2) M = fmaxf(M, base[(size_t)c2 * AP + HD]);
+        float Lsum = 0.f, O = 0.f;
+        for (uint32_t c2 = 0; c2 < chunks; ++c2) {
+          const float* q = base + (size_t)c2 * AP;
+          const float wgt = expf(q[HD] - M);
+          Lsum = fmaf(q[HD + 1], wgt, Lsum);
+          O = fmaf(q[d], wgt, O);
+        }
+        v = bf16_round(__fdiv_rn(O, fmaxf(Lsum, 1.175494351e-38f)));
+      }
+      vec[(size_t)r * p.vec_cols + c] = v;
+    }
+    __syncthreads();
+    for (uint32_t it = me; it < nb_h; it += C) {
+      product_stream<MT, R>(vec, p.vec_cols, (L.bfp >> 1) & 1, QC, it * DCOLS, H, red, ring, bars, head, parity, dead, limit, p.err, walk,
+                            [&](int r, int cc, float t) { stage[r * DCOLS + cc] = t; });
+      send_to_all(cluster, C, reinterpret_cast<uint4*>(osum), reinterpret_cast<const uint4*>(stage), MT * 16,
+                  [&](uint32_t q) { return ((q >> 4) * H + it * DCOLS) / 4 + (q & 15); });
+    }
+    cluster.sync();
+
+    // ---- phase 4 ----
+    for (uint32_t i = tid; i < (uint32_t)MT * H; i += DT) xres[i] = __fadd_rn(xres[i], osum[i]);
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < GN; ++i) gn[i] = l + 1 < p.n_layers && tid + i * DT < H ? bf16_at(lay[l + 1].norm1, tid + i * DT) : 0.f;
+    norm_rows_sm<MT>(xres, H, g2, p.eps, vec, p.vec_cols, stat);
+    for (uint32_t it = me; it < nb_gu; it += C) {
+      product_stream<MT, R>(vec, p.vec_cols, (L.bfp >> 2) & 1, H, it * DCOLS, 2 * FF, red, ring, bars, head, parity, dead, limit, p.err, walk, [&](int r, int cc, float t) {
+        reinterpret_cast<uint16_t*>(stage)[r * DCOLS + cc] = f32_to_bf16_bits(__float_as_uint(t));   // the product's BF16 result
+      });
+      send_to_all(cluster, C, reinterpret_cast<uint4*>(gu), reinterpret_cast<const uint4*>(stage), MT * 8,
+                  [&](uint32_t q) { return ((q >> 3) * 2 * FF + it * DCOLS) / 8 + (q & 7); });
+    }
+#pragma unroll
+    for (int i = 0; i < GN; ++i)
+      if (tid + i * DT < H) g1[tid + i * DT] = gn[i];
+
+    cluster.sync();
+
+
+    // ---- phase 5 ----
+    for (uint32_t it = me; it < nb_h * p.ks_dn; it += C) {
+      const uint32_t cb = it % nb_h, ks = it / nb_h, k0 = ks * p.sl_dn;
+      const uint32_t len = k0 + p.sl_dn <= FF ? p.sl_dn : FF - k0;
+      __syncthreads();
+      for (uint32_t i = tid; i < (uint32_t)MT * len; i += DT) {
+        const uint32_t r = i / len, kk = i - r * len;
+        const float a = __uint_as_float((uint32_t)gu[(size_t)r * 2 * FF + k0 + kk] << 16);
+        const float bq = __uint_as_float((uint32_t)gu[(size_t)r * 2 * FF + FF + k0 + kk] << 16);
+        vec[(size_t)r * p.vec_cols + kk] = bf16_round(__fmul_rn(__fmul_rn(a, sigmoid_flex(a)), bq));
+      }
+      __syncthreads();
+      product_stream<MT, R>(vec, p.vec_cols, (L.bfp >> 3) & 1, len, cb * DCOLS, H, red, ring, bars, head, parity, dead, limit, p.err, walk,
+                            [&](int r, int cc, float t) { stage[r * DCOLS + cc] = t; });
+      send_to_all(cluster, C, reinterpret_cast<uint4*>(dn), reinterpret_cast<const uint4*>(stage), MT * 16,
+                  [&](uint32_t q) { return (((size_t)ks * MT + (q >> 4)) * H + cb * DCOLS) / 4 + (q & 15); });
+    }
+    cluster.sync();
+  }
+  cp_async_wait_all();
+  if (me == 0) {
+    for (uint32_t i = tid; i < (uint32_t)MT * H; i += DT) {
+      const uint32_t r = i / H, c = i - r * H;
+      float d = 0.f;
+      for (uint32_t k = 0; k < p.ks_dn; ++k) d += dn[((size_t)k * MT + r) * H + c];
+      xres[i] = __fadd_rn(xres[i], d);
+    }
+    __syncthreads();
+    norm_rows<MT>(xres, H, p.final_norm, p.eps, vec, p.vec_cols, stat);
+    for (uint32_t i = tid; i < p.rows * H; i += DT) {
+      const uint32_t r = i / H, c = i - r * H;
+      p.out[i] = f32_to_bf16_bits(__float_as_uint(vec[(size_t)r * p.vec_cols + c]));
+    }
+  }
+  cluster.sync();   // no block leaves while another may still store into its shared memory
+}
+
+template <int MT>
+cudaError_t launch_cluster(const ClusterParams& p, size_t smem, int* cluster_blocks, cudaStream_t stream) {
+  // the widest cluster the device will schedule: sixteen blocks (beyond the portable eight), else eight
+  cudaError_t e = ensure_dynamic_smem((const void*)decode_cluster_kernel<MT>, smem);
+  if (e != cudaSuccess) return e;
+  int width = 0;
+  if (!device_value_get((const void*)decode_cluster_kernel<MT>, &width)) {
+    width = -1;
+    for (int c : {16, 8}) {
+      if (c > 8 && cudaFuncSetAttribute((const void*)decode_cluster_kernel<MT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+        cudaGetLastError();
+        continue;
+      }
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(c); cfg.blockDim = dim3(DT); cfg.dynamicSmemBytes = smem;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = c; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+      cfg.attrs = at; cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, decode_cluster_kernel<MT>, &cfg) == cudaSuccess && n >= 1) { width = c; break; }
+      cudaGetLastError();
+    }
+    device_value_set((const void*)decode_cluster_kernel<MT>, width);
+  }
+  if (width < 8) return cudaErrorNotSupported;
+  *cluster_blocks = width;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(width); cfg.blockDim = dim3(DT); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = width; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, decode_cluster_kernel<MT>, p);
+}
+
 uint32_t slices_for(uint32_t col_blocks, uint32_t k, uint32_t grid, uint32_t* slice_len) {
-  // as many slices of k as it takes to give every block an item, in slices of whole 32-row steps, at most 8
-  uint32_t ks = (grid + col_blocks - 1) / col_blocks;
+  // Slices of k so that a phase's items (column blocks x slices) come to about one a block: as many slices as fit the
+  // grid, at least as many as keep a slice within the tile fetched ahead, at most 8; slices of whole 32-row steps.
+  uint32_t ks = grid / col_blocks;
   if (ks < 1) ks = 1;
   if (ks > 8) ks = 8;
+  const uint32_t need = (k + WT_ROWS - 1) / WT_ROWS;
+  if (ks < need) ks = need;
   uint32_t len = ((k + ks - 1) / ks + 31) / 32 * 32;
   if (len > k) len = k;
-  ks = (k + len - 1) / len;
   *slice_len = len;
-  return ks;
+  return (k + len - 1) / len;
 }
 
 }  // namespace
@@ -531,17 +1213,106 @@ DecodeScratch decode_layers_scratch(const DecodeShape& sh, int grid) {
   return d;
 }
 
+// The tiled-copy descriptors of the layers' matrices, for the cluster form: four a layer, each over the stored [k, n]
+// (BF16, or a BFP8 matrix's datum bytes) with a box of 64 rows by 64 columns.  False where the driver has no encoder.
+size_t decode_layers_maps_bytes(const DecodeShape& sh) { return (size_t)sh.layers * 4 * sizeof(CUtensorMap); }
+bool decode_layers_make_maps(const DecodeShape& sh, const DecodeLayerPtrs* recs, void* maps_host) {
+  tc::EncodeTiledFn fn = tc::encode_fn();
+  if (!fn) return false;
+  CUtensorMap* maps = reinterpret_cast<CUtensorMap*>(maps_host);
+  const uint64_t H = sh.hidden, QC = (uint64_t)sh.heads * HD, KC = (uint64_t)sh.kv_heads * HD, FF = sh.ff;
+  const uint64_t kn[4][2] = {{H, QC + 2 * KC}, {QC, H}, {H, 2 * FF}, {FF, H}};
+  for (uint32_t l = 0; l < sh.layers; ++l) {
+    const void* w[4] = {recs[l].qkv, recs[l].o, recs[l].gate_up, recs[l].down};
+    for (int i = 0; i < 4; ++i) {
+      const bool bfp = (recs[l].bfp >> i) & 1u;
+      const cuuint64_t dims[2] = {kn[i][1], kn[i][0]};
+      const cuuint64_t strides[1] = {kn[i][1] * (bfp ? 1u : 2u)};
+      const cuuint32_t box[2] = {(cuuint32_t)DCOLS, (cuuint32_t)CK_ROWS};
+      const cuuint32_t estr[2] = {1, 1};
+      if (fn(&maps[(size_t)l * 4 + i], bfp ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(w[i]),
+             dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    }
+  }
+  return true;
+}
+
 int decode_layers_grid() {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  return sms < 64 ? sms : 64;   // the phases have 27 to 96 items; more blocks only lengthen the barriers
+  const char* e = getenv("B200TT_DECODE_GRID");   // a development switch
+  const int want = e ? atoi(e) : 128;            // measured on SmolLM2-135M's shape: 64, 96, 128 blocks give 1.12, 1.05, 0.98 ms a step
+  return want >= 1 && want <= sms ? want : (sms < 128 ? sms : 128);
+}
+
+namespace {
+// What the cluster form needs of a shape: its buffers in a block's shared memory, its per-layer list of chunks within the
+// table, hidden within what a thread fetches ahead.  Fills the shape-derived fields of `c`.
+bool cluster_plan(const DecodeShape& sh, ClusterParams& c, size_t* smem) {
+  const uint32_t MTc = sh.rows <= 1 ? 1 : (sh.rows <= 2 ? 2 : 4);
+  const uint32_t QCc = sh.heads * HD, NQ = QCc + 2 * sh.kv_heads * HD, att_items = sh.rows * sh.kv_heads * (sh.attend / DCH);
+  c.n_layers = sh.layers; c.rows = sh.rows; c.hidden = sh.hidden; c.heads = sh.heads; c.kv_heads = sh.kv_heads; c.ff = sh.ff;
+  c.max_len = sh.max_len; c.attend = sh.attend; c.eps = sh.eps; c.scale = sh.scale;
+  c.ks_dn = (sh.ff + 767) / 768;                       // slices of about 768 rows: eighteen items for SmolLM2's down projection
+  if (c.ks_dn < 1) c.ks_dn = 1;
+  c.sl_dn = ((sh.ff + c.ks_dn - 1) / c.ks_dn + 31) / 32 * 32;
+  c.ks_dn = (sh.ff + c.sl_dn - 1) / c.sl_dn;
+  uint32_t vc = sh.hidden > QCc ? sh.hidden : QCc;
+  if (c.sl_dn > vc) vc = c.sl_dn;
+  c.vec_cols = vc;
+  c.att_items = att_items;
+  const size_t ring_slots = MTc == 1 ? RingDepth<1>::value : (MTc == 2 ? RingDepth<2>::value : RingDepth<4>::value);
+  const size_t stage = (size_t)MTc * DCOLS > 4 * (HD + 4) ? (size_t)MTc * DCOLS : 4 * (HD + 4);
+  *smem = 128 + ring_slots * SLOT_BYTES + 16 * sizeof(uint64_t) + 2 * DCH * 8 * sizeof(uint4) +
+          ((size_t)MTc * sh.hidden * 2 + (size_t)MTc * vc + (size_t)MTc * NQ + (size_t)att_items * 4 * (HD + 4) +
+           (size_t)c.ks_dn * MTc * sh.hidden + 8 * MTc * DCOLS + 4 * HD + 4 * DCH + 16 + stage + 2 * sh.hidden + 2 * HD) * sizeof(float) +
+          (size_t)sh.layers * sizeof(DecodeLayerDev) + SCHED_MAX * sizeof(ChunkEnt) + 8 + 16 + (size_t)MTc * 2 * sh.ff * sizeof(uint16_t);
+  // the longest list of chunks a block of an eight-block cluster walks in a layer (block 0's)
+  auto chunks_of = [&](uint32_t items, uint32_t rows) { return (uint64_t)((items + 7) / 8) * ((rows + CK_ROWS - 1) / CK_ROWS); };
+  const uint64_t sched = chunks_of(NQ / DCOLS, sh.hidden) + chunks_of(sh.hidden / DCOLS, QCc) + chunks_of(2 * sh.ff / DCOLS, sh.hidden) +
+                         chunks_of(sh.hidden / DCOLS * c.ks_dn, c.sl_dn);
+  return *smem <= 224 * 1024 && sh.hidden <= (uint32_t)GN * DT && sched <= SCHED_MAX && sh.ff < 65536 && 2 * sh.ff / DCOLS < 65536;
+}
+}  // namespace
+
+// Which form a step takes.  The cluster form where its plan fits and every matrix is BF16: measured on SmolLM2-135M's shape,
+// one sequence, 0.86 ms a step against the grid's 0.99; with BFP8 weights the sixteen blocks' ALUs decode every datum and
+// the grid's 128 blocks are twice as fast (1.33 against 2.66 ms).  B200TT_DECODE=grid or =cluster forces a form where
+// it can run (a development switch; the tests run both).
+bool decode_layers_cluster_wanted(const DecodeShape& sh, bool any_bfp) {
+  const char* form = getenv("B200TT_DECODE");
+  if (form && form[0] == 'g') return false;
+  if (any_bfp && !(form && form[0] == 'c')) return false;
+  ClusterParams c{};
+  size_t smem = 0;
+  return cluster_plan(sh, c, &smem);
 }
 
 cudaError_t launch_decode_layers(const DecodeShape& sh, const DecodeLayerPtrs* layers_dev, const float* x0, const void* final_norm,
                                  const float* cos_t, const float* sin_t, const int32_t* pos, uint16_t* out, float* scratch,
-                                 const DecodeScratch& d, int grid, int* err, cudaStream_t stream) {
+                                 const DecodeScratch& d, int grid, const void* maps_dev, int* err, cudaStream_t stream, const char** form) {
   static_assert(sizeof(DecodeLayerPtrs) == sizeof(DecodeLayerDev), "the host's layer record is the kernel's");
+  // One cluster when the caller built its descriptors (`decode_layers_cluster_wanted`) and the device schedules one; the
+  // grid form otherwise.
+  ClusterParams c{};
+  size_t smem_c = 0;
+  if (maps_dev && cluster_plan(sh, c, &smem_c)) {
+    const uint32_t MTc = sh.rows <= 1 ? 1 : (sh.rows <= 2 ? 2 : 4);
+    c.layers = reinterpret_cast<const DecodeLayerDev*>(layers_dev);
+    c.x0 = x0; c.final_norm = final_norm; c.cos = cos_t; c.sin = sin_t; c.pos = pos; c.out = out; c.err = err;
+    c.maps = reinterpret_cast<const CUtensorMap*>(maps_dev);
+    int width = 0;
+    cudaError_t ce = MTc == 1 ? launch_cluster<1>(c, smem_c, &width, stream)
+                              : (MTc == 2 ? launch_cluster<2>(c, smem_c, &width, stream) : launch_cluster<4>(c, smem_c, &width, stream));
+    if (ce != cudaErrorNotSupported) {
+      *form = width == 16 ? "cluster16" : "cluster8";
+      return ce;
+    }
+  }
+  *form = "grid";
   DecodeParams p{};
   p.layers = reinterpret_cast<const DecodeLayerDev*>(layers_dev);
   p.n_layers = sh.layers; p.rows = sh.rows; p.hidden = sh.hidden; p.heads = sh.heads; p.kv_heads = sh.kv_heads; p.ff = sh.ff;
@@ -558,8 +1329,8 @@ cudaError_t launch_decode_layers(const DecodeShape& sh, const DecodeLayerPtrs* l
   uint32_t vc = sh.hidden > QC ? sh.hidden : QC;
   if (d.sl_dn > vc) vc = d.sl_dn;
   p.vec_cols = vc;
-  const size_t smem = ((size_t)MT * sh.hidden + (size_t)MT * vc + 8 * MT * DCOLS + 4 * HD + 4 * DCH + 16) * sizeof(float) +
-                      2 * DCH * 33 * sizeof(uint32_t);
+  const size_t smem = (size_t)WT_ROWS * 64 * 2 + 2 * DCH * 8 * sizeof(uint4) +
+                      ((size_t)MT * sh.hidden + (size_t)MT * vc + 8 * MT * DCOLS + 4 * HD + 4 * DCH + 16) * sizeof(float);
   cudaError_t e = cudaMemsetAsync(p.bar, 0, 64 * sizeof(float), stream);   // the barrier's counter and its abort flag start at zero
   if (e != cudaSuccess) return e;
   void* args[] = {(void*)&p};

@@ -209,7 +209,14 @@ int decode_layers_grid();
 DecodeScratch decode_layers_scratch(const DecodeShape& shape, int grid);
 cudaError_t launch_decode_layers(const DecodeShape& shape, const DecodeLayerPtrs* layers_dev, const float* x0, const void* final_norm,
                                  const float* cos_t, const float* sin_t, const int32_t* pos, uint16_t* out, float* scratch,
-                                 const DecodeScratch& cut, int grid, int* err, cudaStream_t stream);
+                                 const DecodeScratch& cut, int grid, const void* maps_dev, int* err, cudaStream_t stream,
+                                 const char** form);   // *form: "cluster16", "cluster8" or "grid", what was launched
+// Whether the step should take the cluster form (then the caller builds the descriptors below and passes them).
+bool decode_layers_cluster_wanted(const DecodeShape& shape, bool any_bfp);
+// The cluster form's tiled-copy descriptors (four a layer), built on the host from the layers' addresses and uploaded
+// beside them; `maps_dev` null sends the step to the grid form.
+size_t decode_layers_maps_bytes(const DecodeShape& shape);
+bool decode_layers_make_maps(const DecodeShape& shape, const DecodeLayerPtrs* layers_host, void* maps_host);
 
 // Text for `b200_last_error(NULL, ...)`: failures of calls that take no engine.
 void set_global_error(const char* text);

@@ -106,6 +106,8 @@ def _prepare(_lib: C.CDLL) -> C.CDLL:
         _lib.b200_stream.argtypes = [C.c_void_p]
         _lib.b200_last_matmul_path.restype = C.c_char_p
         _lib.b200_last_matmul_path.argtypes = [C.c_void_p]
+        _lib.b200_last_decode_form.restype = C.c_char_p
+        _lib.b200_last_decode_form.argtypes = [C.c_void_p]
         _lib.b200_engine_destroy.restype = None
         _lib.b200_free.restype = None
         _lib.b200_set_op_label.restype = None
@@ -384,6 +386,10 @@ class CudaEngine:
 
     def last_matmul_path(self) -> str:
         return self._lib.b200_last_matmul_path(self._e).decode()
+
+    def last_decode_form(self) -> str:
+        """ "cluster16" / "cluster8" / "grid": the form the last `decode_layers` took."""
+        return self._lib.b200_last_decode_form(self._e).decode()
 
     # -- element-wise (server.rs:492-566) --------------------------------------------
     def eltwise_op_as(self, op, a: int, b: Optional[int] = None, c: Optional[int] = None, bf16: bool = False) -> Out:

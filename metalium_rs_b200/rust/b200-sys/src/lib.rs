@@ -118,4 +118,5 @@ extern "C" {
     pub fn b200_timer_stop(a0: *mut b200_engine, ms: *mut f32) -> i32;
     pub fn b200_stream(a0: *const b200_engine) -> *mut c_void;
     pub fn b200_last_matmul_path(a0: *const b200_engine) -> *const c_char;
+    pub fn b200_last_decode_form(a0: *const b200_engine) -> *const c_char;
 }

@@ -1,6 +1,7 @@
 // TEST INFRASTRUCTURE: the kernel launch interface (csrc/kernels.h) with every launch a no-op
 // that reports success, and the knobs of the fake runtime.  Linked with engine.cu (compiled as
 // C++) into tests/_build/libb200tt_fake.so; results are never computed, only the host logic runs.
+#include <cstring>
 #include "cuda_runtime.h"
 #include "kernels.h"
 #include "kinds.h"
@@ -91,7 +92,16 @@ bool decode_layers_supported(const DecodeShape& s, const char** why) {
 int decode_layers_grid() { return 64; }
 DecodeScratch decode_layers_scratch(const DecodeShape&, int) { DecodeScratch d{}; d.floats = 1024; return d; }
 cudaError_t launch_decode_layers(const DecodeShape&, const DecodeLayerPtrs*, const float*, const void*, const float*, const float*, const int32_t*,
-                                 uint16_t*, float*, const DecodeScratch&, int, int*, cudaStream_t) { OK_LAUNCH; }
+                                 uint16_t*, float*, const DecodeScratch&, int, const void* maps, int*, cudaStream_t, const char** form) {
+  *form = maps ? "cluster16" : "grid";
+  OK_LAUNCH;
+}
+bool decode_layers_cluster_wanted(const DecodeShape&, bool any_bfp) { return !any_bfp; }
+size_t decode_layers_maps_bytes(const DecodeShape& s) { return (size_t)s.layers * 4 * 128; }
+bool decode_layers_make_maps(const DecodeShape& s, const DecodeLayerPtrs*, void* maps_host) {
+  memset(maps_host, 0, decode_layers_maps_bytes(s));
+  return true;
+}
 bool gemm_skinny_bfp_supported(uint64_t m, uint64_t n, uint64_t) { return m >= 1 && m <= 4 && n % 16 == 0; }
 cudaError_t launch_gemm_skinny_bfp(const uint16_t*, uint64_t, const uint8_t*, const uint8_t*, void*, uint64_t, int, uint64_t, uint64_t, uint64_t,
                                    cudaStream_t) { OK_LAUNCH; }

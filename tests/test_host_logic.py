@@ -536,6 +536,13 @@ def test_the_one_launch_decode_step_checks_its_operands(e):
     l0 = e.device_traffic().launches
     lg, am = dec.step()
     assert e.dims_of(lg) == ((2, cfg.vocab), F32) and e.device_traffic().launches - l0 <= 12
+    assert e.last_decode_form() == "grid"                             # BFP8 weights: no descriptors are built, the grid form runs
+    plain = W.LlamaDecode(e, cfg, pre.w, 2, max_len=128, fused=True)
+    plain.reset(np.array([1, 2], np.int32))
+    h0 = e.device_traffic().bytes_h2d
+    plain.step()
+    assert e.last_decode_form() == "cluster16"                        # BF16 weights: the descriptors go up beside the layer records
+    assert e.device_traffic().bytes_h2d - h0 >= cfg.layers * 4 * 128
     bad = list(dec.layer_ids)
     bad[1], bad[2] = bad[2], bad[1]                                   # Wqkv and Wo exchanged: the shapes do not meet
     with pytest.raises(TtError) as err:
