@@ -348,9 +348,10 @@ def run_single(args):
 
     pk, which = peaks()
     peak = float(pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
-    # traffic: dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch of this kernel under ncu (1,274.3 MB
-    # read + 252.4 MB written); it cannot be measured inside a timed run, and is null at other sizes
-    traffic = 1274306000 + 252358000 if n == N1_SIZE else None
+    # traffic: dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch of this kernel under ncu (1,071.8 MB
+    # read + 126.5 MB written with tile rows walked in groups of 8; profiles/gemm_tc2_bf16_8192.md); it cannot be
+    # measured inside a timed run, and is null at other sizes
+    traffic = 1071757000 + 126531000 if n == N1_SIZE else None
     roofline = {"bound": "tensor", "kernel": "gemm_tc2_kernel<K-major A, MN-major B> (CTA pairs, 256x256 tiles)",
                 "achieved": value, "peak": peak, "unit": UNIT, "frac": value / peak,
                 "peak_source": f"{which} cuBLAS bf16 burst", "frac_of_nominal_2250": value / 2250.0,
