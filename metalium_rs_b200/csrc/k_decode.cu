@@ -279,9 +279,9 @@ __device__ __forceinline__ void norm_rows(const float* x, uint32_t cols, const v
   __syncthreads();
 }
 
-// The same with the gains already in shared memory as F32 (exact: they are BF16 values).
+// The same with the gains already in shared memory as F32 (exact: they are BF16 values), the result stored as BF16 bits.
 template <int MT>
-__device__ __forceinline__ void norm_rows_sm(const float* x, uint32_t cols, const float* gains, float eps, float* vec, uint32_t vec_pitch,
+__device__ __forceinline__ void norm_rows_sm(const float* x, uint32_t cols, const float* gains, float eps, uint16_t* vec, uint32_t vec_pitch,
                                              float* scratch) {
   const float inv_n = 1.0f / (float)cols;
   for (int r = 0; r < MT; ++r) {
@@ -291,7 +291,7 @@ __device__ __forceinline__ void norm_rows_sm(const float* x, uint32_t cols, cons
     const float stat = sqrtf(__fadd_rn(__fmul_rn(total, inv_n), eps));
     for (uint32_t c = threadIdx.x; c < cols; c += DT) {
       const float t = __fdiv_rn(x[(size_t)r * cols + c], stat);
-      vec[(size_t)r * vec_pitch + c] = bf16_round(__fmul_rn(t, gains[c]));
+      vec[(size_t)r * vec_pitch + c] = f32_to_bf16_bits(__float_as_uint(__fmul_rn(t, gains[c])));
     }
   }
   __syncthreads();
@@ -655,12 +655,12 @@ __global__ void __launch_bounds__(DT, 1) decode_layers_kernel(const DecodeParams
 //
 // With so few blocks the step is bound by how many bytes of weights a block keeps in flight, so the weights do not wait
 // for the phase that uses them: the tiles a block will multiply by are known from the start (layer after layer, phase
-// after phase, item after item), and a ring of shared-memory slots is kept full of the next chunks of 64 k-rows by
-// TMA (one tiled copy of 64 rows by 64 columns a chunk, completing on the slot's mbarrier), across phases and cluster
+// after phase, item after item), and a ring of shared-memory slots is kept full of the next chunks of 192 k-rows by
+// TMA (one tiled copy of 192 rows by 64 columns a chunk, completing on the slot's mbarrier), across phases and cluster
 // barriers: loads issued by threads keep some 16 KB a block in flight, far too little for sixteen blocks to draw the
-// device's bandwidth, where the ring holds up to 130 KB a block.  A product waits for its next chunk, multiplies from
-// shared memory, and refills the slot with the chunk that is R chunks ahead.  (A BFP8 matrix's exponents, four bytes
-// a row of a chunk, are too narrow for a tiled copy and come by cp.async into the same slot.)
+// device's bandwidth, where the ring holds up to 120 KB a block.  A product waits for its next chunk, multiplies from
+// shared memory with tensor-core tiles (`mma.sync`: a warp owns 8 of the item's 64 columns), and refills the slot with
+// the chunk that is R chunks ahead.  The form takes BF16 matrices only.
 namespace cg = cooperative_groups;
 
 struct ClusterParams {
@@ -680,8 +680,8 @@ struct ClusterParams {
 
 constexpr int CK_ROWS = 192;                           // k-rows of a chunk: a wait, a barrier and an issue cost some 300 cycles a chunk whatever its size
 constexpr int GN = 4;                                  // gains a thread fetches ahead: the cluster form takes hidden <= GN * 256
-constexpr uint32_t SLOT_BYTES = CK_ROWS * 128 + CK_ROWS * 4;   // rows of 64 BF16 (or 64 datum bytes), then four exponent bytes a row
-static_assert(SLOT_BYTES % 128 == 0 && CK_ROWS % 96 == 0 && CK_ROWS <= 256, "a slot is whole 128-byte lines; a box has at most 256 rows");
+constexpr uint32_t SLOT_BYTES = CK_ROWS * 128;         // rows of 64 BF16, 128-byte swizzled as the copy writes them
+static_assert(SLOT_BYTES % 1024 == 0 && CK_ROWS % 32 == 0 && CK_ROWS <= 256, "a swizzled slot starts on 1,024 bytes; a box has at most 256 rows");
 template <int MT> struct RingDepth { static constexpr int value = MT == 1 ? 5 : (MT == 2 ? 4 : 2); };
 
 // The chunks of weights a block multiplies by during ONE layer, in the order it uses them: the same list for every layer,
@@ -691,13 +691,11 @@ constexpr uint32_t SCHED_MAX = 256;
 
 struct WeightWalk {
   const ClusterParams* p;
-  const DecodeLayerDev* lay;                           // the layers' records, copied into shared memory
   const ChunkEnt* tab;
   uint32_t cnt, ii, il;                                // the list's length; the next chunk to issue: entry ii of layer il
-  bool any_bfp;                                        // some matrix of the step is BFP8: every issue commits a cp.async group
   // thread 0 writes the list; every thread calls this, the caller's __syncthreads publishes it
-  __device__ void start(const ClusterParams* pp, const DecodeLayerDev* lay_, ChunkEnt* tab_, uint32_t* cnt_sm, uint32_t me, uint32_t C) {
-    p = pp; lay = lay_; tab = tab_; ii = 0; il = 0;
+  __device__ void start(const ClusterParams* pp, ChunkEnt* tab_, uint32_t* cnt_sm, uint32_t me, uint32_t C) {
+    p = pp; tab = tab_; ii = 0; il = 0;
     if (threadIdx.x == 0) {
       const uint32_t H = pp->hidden, QC = pp->heads * HD, NQKV = QC + 2 * pp->kv_heads * HD, FF = pp->ff, nb_h = H / DCOLS;
       uint32_t c = 0;
@@ -714,127 +712,77 @@ struct WeightWalk {
       *cnt_sm = c;
     }
   }
-  // issue the copy of the next chunk into `slot` (called by every thread of the block), then move on; when the walk is
-  // over only an empty cp.async group is committed, so that the groups keep counting chunks
+  // issue the copy of the next chunk into `slot` (called by every thread of the block; thread 0 issues), then move on
   __device__ __forceinline__ void issue(uint8_t* slot, uint64_t* bar) {
     if (il < p->n_layers) {
-      const ChunkEnt e = tab[ii];
-      const int bfp = (lay[il].bfp >> e.phase) & 1;
       if (threadIdx.x == 0) {
-        tc::mbar_expect_tx(bar, bfp ? CK_ROWS * 64 : CK_ROWS * 128);   // the whole box counts, rows past the matrix filled with zeros
+        const ChunkEnt e = tab[ii];
+        tc::mbar_expect_tx(bar, SLOT_BYTES);           // the whole box counts, rows past the matrix filled with zeros
         tc::tma_load_2d(slot, p->maps + (size_t)il * 4 + e.phase, bar, (int32_t)e.cb * DCOLS, (int32_t)e.k0);
-      }
-      if (bfp && threadIdx.x < e.rows) {
-        const DecodeLayerDev& L = lay[il];
-        const uint32_t H = p->hidden, QC = p->heads * HD, FF = p->ff;
-        const uint32_t n = e.phase == 0 ? QC + 2 * p->kv_heads * HD : (e.phase == 2 ? 2 * FF : H);
-        const uint64_t k_total = e.phase == 0 || e.phase == 2 ? H : (e.phase == 1 ? QC : FF);
-        const uint8_t* w = reinterpret_cast<const uint8_t*>(e.phase == 0 ? L.qkv : (e.phase == 1 ? L.o : (e.phase == 2 ? L.gate_up : L.down)));
-        const uint8_t* ex = w + k_total * n + (uint64_t)e.k0 * (n / 16) + (uint32_t)e.cb * (DCOLS / 16);
-        cp_async4(slot + (size_t)CK_ROWS * 128 + (size_t)threadIdx.x * 4, ex + (uint64_t)threadIdx.x * (n / 16));
       }
       if (++ii == cnt) { ii = 0; ++il; }
     }
-    if (any_bfp) cp_async_commit();
   }
 };
 
 // mbar_wait's abort flag: a product's wait has no other block to hear from, so the flag is the error word itself (set by
 // any block of the engine's kernels that gave up)
 __device__ __forceinline__ volatile int& dead_flag_of(int* err) { return *reinterpret_cast<volatile int*>(err); }
-template <int N> __device__ __forceinline__ void cp_async_wait_upto() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
-// One product item fed from the ring: `len` k-rows in chunks of 64, A's rows in shared memory (pitch lda, offset to the item's k0).
+// One product item fed from the ring: `len` k-rows in chunks of CK_ROWS, A's rows as BF16 in shared memory (pitch lda
+// elements, offset to the item's first k-row).  The eight warps split the item's 64 columns: a warp owns 8 of them and all of
+// k, so its accumulator (one m16n8 tile of `mma.sync`, rows past MT fed zeros) is the item's result for those columns and
+// no sum crosses warps.  B comes from the slot by `ldmatrix.trans` (the slot is [k][64 columns], 128-byte swizzled as the
+// copy wrote it: a warp's 16-byte unit of row k sits at unit ^ (k & 7), so eight rows of one matrix meet eight bank groups).
+// With 16 blocks a step the CUDA cores were the products' bound (unpacking and 8 FMA a 16-byte load: 17 k of a block's
+// 48 k warp instructions a layer); a sixteenth of a tensor tile is used and it is still an order less issue.
 template <int MT, int R, class Emit>
-__device__ __forceinline__ void product_stream(const float* a, uint32_t lda, int bfp, uint32_t len, uint32_t c0, uint64_t n, float* red,
-                                               uint8_t* ring, uint64_t* bars, uint32_t& head, uint32_t& parity, bool& dead, long long limit,
-                                               int* err, WeightWalk& walk, Emit emit) {
-  const int tid = threadIdx.x, cg_ = tid & 7, kr = tid >> 3, warp = tid >> 5, lane = tid & 31;
-  float acc[MT][8];
-#pragma unroll
-  for (int r = 0; r < MT; ++r)
-#pragma unroll
-    for (int e = 0; e < 8; ++e) acc[r][e] = 0.f;
+__device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, uint32_t len, uint8_t* ring, uint64_t* bars, uint32_t& head,
+                                               uint32_t& parity, bool& dead, long long limit, int* err, WeightWalk& walk, Emit emit) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  float c[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint16_t* arow = a + (size_t)(g < MT ? g : 0) * lda;
   for (uint32_t base = 0; base < len; base += CK_ROWS) {
-    // the oldest of the R chunks in flight: its tile (the slot's mbarrier) and, for BFP8, its exponents (the oldest
-    // cp.async group of every thread, then the block's barrier)
+    // the oldest of the R chunks in flight: its tile has landed when the slot's mbarrier flips
     if (!dead && !tc::mbar_wait(&bars[head], (parity >> head) & 1u, &dead_flag_of(err), limit)) {
       dead = true;                                     // recorded; the block walks on without waiting, so that the cluster's barriers are still met
       atomicCAS(err, 0, TIMEOUT_CODE);
     }
     parity ^= 1u << head;
-    if (bfp) {
-      cp_async_wait_upto<R - 1>();
-      __syncthreads();
-    }
-    const uint8_t* slot = ring + (size_t)head * SLOT_BYTES;
-    const uint32_t rows = len - base < (uint32_t)CK_ROWS ? len - base : CK_ROWS;
-    // three k-rows a thread at a time, their loads first; a row past the chunk's end counts as zeros
+    const uint32_t slot = tc::smem_u32(ring + (size_t)head * SLOT_BYTES);
 #pragma unroll
-    for (int h2 = 0; h2 < CK_ROWS / 32; h2 += 3) {
-      float x[3][8], av[3][MT];
-#pragma unroll
-      for (int j = 0; j < 3; ++j) {
-        const uint32_t rr = kr + (h2 + j) * 32;
-        const bool in = rr < rows;
-        if (!bfp) {
-          uint4 raw = make_uint4(0, 0, 0, 0);
-          if (in) raw = *reinterpret_cast<const uint4*>(slot + ((size_t)rr * 8 + cg_) * 16);
-          x[j][0] = __uint_as_float(raw.x << 16); x[j][1] = __uint_as_float(raw.x & 0xffff0000u);
-          x[j][2] = __uint_as_float(raw.y << 16); x[j][3] = __uint_as_float(raw.y & 0xffff0000u);
-          x[j][4] = __uint_as_float(raw.z << 16); x[j][5] = __uint_as_float(raw.z & 0xffff0000u);
-          x[j][6] = __uint_as_float(raw.w << 16); x[j][7] = __uint_as_float(raw.w & 0xffff0000u);
-        } else {
-          uint2 raw = make_uint2(0, 0);
-          uint32_t ex = 0;
-          if (in) {
-            raw = *reinterpret_cast<const uint2*>(slot + (size_t)rr * 64 + cg_ * 8);
-            ex = slot[(size_t)CK_ROWS * 128 + (size_t)rr * 4 + (cg_ >> 1)];
-          }
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            x[j][e] = bfp8_value((raw.x >> (e * 8)) & 0xffu, ex);
-            x[j][4 + e] = bfp8_value((raw.y >> (e * 8)) & 0xffu, ex);
-          }
-        }
-#pragma unroll
-        for (int r = 0; r < MT; ++r) av[j][r] = in ? a[(size_t)r * lda + base + rr] : 0.f;
+    for (int ks = 0; ks < CK_ROWS / 16; ks += 2) {     // two k-steps of 16 rows a load of four 8x8 matrices
+      const uint32_t k = ks * 16 + lane;               // this lane names row k of the slot
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4_trans(slot + k * 128 + (((uint32_t)warp ^ (k & 7)) << 4), b0, b1, b2, b3);
+      const uint32_t kk = base + ks * 16 + 2 * t;       // this thread's A columns: kk, kk+1, kk+8, kk+9 and the same + 16
+      uint32_t a0 = 0, a2 = 0, a4 = 0, a6 = 0;
+      if (g < MT) {                                     // a row past the item's k counts as zeros (the slot may hold the next slice there)
+        if (kk < len) a0 = *reinterpret_cast<const uint32_t*>(arow + kk);
+        if (kk + 8 < len) a2 = *reinterpret_cast<const uint32_t*>(arow + kk + 8);
+        if (kk + 16 < len) a4 = *reinterpret_cast<const uint32_t*>(arow + kk + 16);
+        if (kk + 24 < len) a6 = *reinterpret_cast<const uint32_t*>(arow + kk + 24);
       }
-#pragma unroll
-      for (int j = 0; j < 3; ++j)                       // ascending k, as before
-#pragma unroll
-        for (int r = 0; r < MT; ++r)
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[r][e] = fmaf(av[j][r], x[j][e], acc[r][e]);
+      mma_bf16_16816(c, a0, 0u, a2, 0u, b0, b1);
+      mma_bf16_16816(c, a4, 0u, a6, 0u, b2, b3);
     }
-    __syncthreads();                                   // every thread is done with the slot: refill it
+    __syncthreads();                                   // every warp is done with the slot: refill it
     walk.issue(ring + (size_t)head * SLOT_BYTES, &bars[head]);
     head = head + 1 == (uint32_t)R ? 0 : head + 1;
   }
-#pragma unroll
-  for (int r = 0; r < MT; ++r)
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      float v = acc[r][e];
-      v += __shfl_xor_sync(0xffffffffu, v, 8);
-      v += __shfl_xor_sync(0xffffffffu, v, 16);
-      acc[r][e] = v;
-    }
-  if (lane < 8) {
-#pragma unroll
-    for (int r = 0; r < MT; ++r)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) red[((size_t)warp * MT + r) * DCOLS + lane * 8 + e] = acc[r][e];
+  if (g < MT) {
+    emit(g, warp * 8 + 2 * t, c[0]);                   // into the block's staging row: the caller sends it on
+    emit(g, warp * 8 + 2 * t + 1, c[1]);
   }
-  __syncthreads();
-  for (int i = tid; i < MT * DCOLS; i += DT) {
-    const int r = i / DCOLS, cc = i - r * DCOLS;
-    float t = 0.f;
-#pragma unroll
-    for (int wv = 0; wv < DT / 32; ++wv) t += red[((size_t)wv * MT + r) * DCOLS + cc];
-    emit(r, cc, t);                                    // into the block's staging row: the caller sends it on
-  }
-  __syncthreads();                                     // `red` is free for the next item, the staged results are whole
+  __syncthreads();                                     // the staged results are whole
 }
 
 // Send `pieces` 16-byte pieces staged in this block's shared memory to the same place in EVERY block of the cluster
@@ -861,18 +809,16 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
   constexpr uint32_t APH = HD + 4;                    // a head's partial of an attention item: 64 sums, the maximum, the sum, two unused (whole 16-byte pieces)
   constexpr uint32_t AP = 4 * APH;                    // an attention item's partial
   // shared memory (the same offsets in every block of the cluster)
-  uint8_t* ring = reinterpret_cast<uint8_t*>(((uintptr_t)smem + 127) & ~(uintptr_t)127);   // a tiled copy lands on 128-byte lines
+  uint8_t* ring = reinterpret_cast<uint8_t*>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);   // a swizzled tile starts on 1,024 bytes
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)R * SLOT_BYTES);             // [16]
   uint4* ksm = reinterpret_cast<uint4*>(bars + 16);
   uint4* vsm = ksm + DCH * 8;
   float* xres = reinterpret_cast<float*>(vsm + DCH * 8);          // [MT][H]
-  float* vec = xres + (size_t)MT * H;                             // [MT][vec_cols]
-  float* qkv = vec + (size_t)MT * p.vec_cols;                     // [MT][NQKV]   BF16 values, from every block
+  float* qkv = xres + (size_t)MT * H;                             // [MT][NQKV]   BF16 values, from every block
   float* att = qkv + (size_t)MT * NQKV;                           // [att_items][AP]
   float* osum = att + (size_t)p.att_items * AP;                   // [MT][H]
   float* dn = osum + (size_t)MT * H;                              // [ks_dn][MT][H]
-  float* red = dn + (size_t)p.ks_dn * MT * H;                     // [8][MT][64]
-  float* qs = red + 8 * MT * DCOLS;
+  float* qs = dn + (size_t)p.ks_dn * MT * H;
   float* ps = qs + 4 * HD;
   float* stat = ps + 4 * DCH;
   float* stage = stat + 16;                                       // [MT][64] a product item's results before they are sent; [AP] an attention item's
@@ -884,6 +830,7 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
   ChunkEnt* tab = reinterpret_cast<ChunkEnt*>(lay + p.n_layers);  // [SCHED_MAX]
   uint32_t* tab_len = reinterpret_cast<uint32_t*>(tab + SCHED_MAX);   // [2]
   uint16_t* gu = reinterpret_cast<uint16_t*>(((uintptr_t)(tab_len + 2) + 15) & ~(uintptr_t)15);   // [MT][2 FF] BF16
+  uint16_t* vec = gu + (size_t)MT * 2 * FF;                       // [MT][vec_cols] BF16: a product's A operand
 
   const int32_t pos = *p.pos;
   if (pos < 0 || (uint32_t)pos >= p.max_len || (uint32_t)pos >= p.attend) {   // every block sees the same position
@@ -896,14 +843,9 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
     reinterpret_cast<uint64_t*>(lay)[i] = reinterpret_cast<const uint64_t*>(p.layers)[i];
   if (tid < HD) { cs[tid] = p.cos[(size_t)pos * HD + tid]; sn[tid] = p.sin[(size_t)pos * HD + tid]; }
   WeightWalk walk;
-  walk.start(&p, lay, tab, tab_len, me, C);
+  walk.start(&p, tab, tab_len, me, C);
   __syncthreads();
   walk.cnt = *tab_len;
-  {
-    uint32_t any = 0;
-    for (uint32_t l = 0; l < p.n_layers; ++l) any |= lay[l].bfp;
-    walk.any_bfp = any != 0;
-  }
   for (uint32_t c = tid; c < H; c += DT) g1[c] = bf16_at(lay[0].norm1, c);
   uint32_t head = 0, parity = 0;
   bool dead = false;
@@ -937,7 +879,7 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
     __syncthreads();
     norm_rows_sm<MT>(xres, H, g1, p.eps, vec, p.vec_cols, stat);
     for (uint32_t it = me; it < nb_qkv; it += C) {
-      product_stream<MT, R>(vec, p.vec_cols, L.bfp & 1, H, it * DCOLS, NQKV, red, ring, bars, head, parity, dead, limit, p.err, walk,
+      product_stream<MT, R>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk,
                             [&](int r, int cc, float t) { stage[r * DCOLS + cc] = bf16_round(t); });   // the product's BF16 result
       send_to_all(cluster, C, reinterpret_cast<uint4*>(qkv), reinterpret_cast<const uint4*>(stage), MT * 16,
                   [&](uint32_t q) { return ((q >> 4) * NQKV + it * DCOLS) / 4 + (q & 15); });
@@ -1061,13 +1003,13 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
           Lsum = fmaf(q[HD + 1], wgt, Lsum);
           O = fmaf(q[d], wgt, O);
         }
-        v = bf16_round(__fdiv_rn(O, fmaxf(Lsum, 1.175494351e-38f)));
+        v = __fdiv_rn(O, fmaxf(Lsum, 1.175494351e-38f));
       }
-      vec[(size_t)r * p.vec_cols + c] = v;
+      vec[(size_t)r * p.vec_cols + c] = f32_to_bf16_bits(__float_as_uint(v));
     }
     __syncthreads();
     for (uint32_t it = me; it < nb_h; it += C) {
-      product_stream<MT, R>(vec, p.vec_cols, (L.bfp >> 1) & 1, QC, it * DCOLS, H, red, ring, bars, head, parity, dead, limit, p.err, walk,
+      product_stream<MT, R>(vec, p.vec_cols, QC, ring, bars, head, parity, dead, limit, p.err, walk,
                             [&](int r, int cc, float t) { stage[r * DCOLS + cc] = t; });
       send_to_all(cluster, C, reinterpret_cast<uint4*>(osum), reinterpret_cast<const uint4*>(stage), MT * 16,
                   [&](uint32_t q) { return ((q >> 4) * H + it * DCOLS) / 4 + (q & 15); });
@@ -1081,7 +1023,7 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
     for (int i = 0; i < GN; ++i) gn[i] = l + 1 < p.n_layers && tid + i * DT < H ? bf16_at(lay[l + 1].norm1, tid + i * DT) : 0.f;
     norm_rows_sm<MT>(xres, H, g2, p.eps, vec, p.vec_cols, stat);
     for (uint32_t it = me; it < nb_gu; it += C) {
-      product_stream<MT, R>(vec, p.vec_cols, (L.bfp >> 2) & 1, H, it * DCOLS, 2 * FF, red, ring, bars, head, parity, dead, limit, p.err, walk, [&](int r, int cc, float t) {
+      product_stream<MT, R>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk, [&](int r, int cc, float t) {
         reinterpret_cast<uint16_t*>(stage)[r * DCOLS + cc] = f32_to_bf16_bits(__float_as_uint(t));   // the product's BF16 result
       });
       send_to_all(cluster, C, reinterpret_cast<uint4*>(gu), reinterpret_cast<const uint4*>(stage), MT * 8,
@@ -1103,17 +1045,16 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
         const uint32_t r = i / len, kk = i - r * len;
         const float a = __uint_as_float((uint32_t)gu[(size_t)r * 2 * FF + k0 + kk] << 16);
         const float bq = __uint_as_float((uint32_t)gu[(size_t)r * 2 * FF + FF + k0 + kk] << 16);
-        vec[(size_t)r * p.vec_cols + kk] = bf16_round(__fmul_rn(__fmul_rn(a, sigmoid_flex(a)), bq));
+        vec[(size_t)r * p.vec_cols + kk] = f32_to_bf16_bits(__float_as_uint(__fmul_rn(__fmul_rn(a, sigmoid_flex(a)), bq)));
       }
       __syncthreads();
-      product_stream<MT, R>(vec, p.vec_cols, (L.bfp >> 3) & 1, len, cb * DCOLS, H, red, ring, bars, head, parity, dead, limit, p.err, walk,
+      product_stream<MT, R>(vec, p.vec_cols, len, ring, bars, head, parity, dead, limit, p.err, walk,
                             [&](int r, int cc, float t) { stage[r * DCOLS + cc] = t; });
       send_to_all(cluster, C, reinterpret_cast<uint4*>(dn), reinterpret_cast<const uint4*>(stage), MT * 16,
                   [&](uint32_t q) { return (((size_t)ks * MT + (q >> 4)) * H + cb * DCOLS) / 4 + (q & 15); });
     }
     cluster.sync();
   }
-  cp_async_wait_all();
   if (me == 0) {
     for (uint32_t i = tid; i < (uint32_t)MT * H; i += DT) {
       const uint32_t r = i / H, c = i - r * H;
@@ -1122,11 +1063,8 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
       xres[i] = __fadd_rn(xres[i], d);
     }
     __syncthreads();
-    norm_rows<MT>(xres, H, p.final_norm, p.eps, vec, p.vec_cols, stat);
-    for (uint32_t i = tid; i < p.rows * H; i += DT) {
-      const uint32_t r = i / H, c = i - r * H;
-      p.out[i] = f32_to_bf16_bits(__float_as_uint(vec[(size_t)r * p.vec_cols + c]));
-    }
+    norm_rows<MT>(xres, H, p.final_norm, p.eps, osum, H, stat);   // `osum` is free: the norm's BF16 values as F32
+    for (uint32_t i = tid; i < p.rows * H; i += DT) p.out[i] = f32_to_bf16_bits(__float_as_uint(osum[i]));
   }
   cluster.sync();   // no block leaves while another may still store into its shared memory
 }
@@ -1214,7 +1152,7 @@ DecodeScratch decode_layers_scratch(const DecodeShape& sh, int grid) {
 }
 
 // The tiled-copy descriptors of the layers' matrices, for the cluster form: four a layer, each over the stored [k, n]
-// (BF16, or a BFP8 matrix's datum bytes) with a box of 64 rows by 64 columns.  False where the driver has no encoder.
+// (BF16) with a box of CK_ROWS rows by 64 columns, 128-byte swizzled.  False where the driver has no encoder.
 size_t decode_layers_maps_bytes(const DecodeShape& sh) { return (size_t)sh.layers * 4 * sizeof(CUtensorMap); }
 bool decode_layers_make_maps(const DecodeShape& sh, const DecodeLayerPtrs* recs, void* maps_host) {
   tc::EncodeTiledFn fn = tc::encode_fn();
@@ -1225,13 +1163,13 @@ bool decode_layers_make_maps(const DecodeShape& sh, const DecodeLayerPtrs* recs,
   for (uint32_t l = 0; l < sh.layers; ++l) {
     const void* w[4] = {recs[l].qkv, recs[l].o, recs[l].gate_up, recs[l].down};
     for (int i = 0; i < 4; ++i) {
-      const bool bfp = (recs[l].bfp >> i) & 1u;
+      if ((recs[l].bfp >> i) & 1u) return false;        // the cluster form multiplies BF16 tiles where they land
       const cuuint64_t dims[2] = {kn[i][1], kn[i][0]};
-      const cuuint64_t strides[1] = {kn[i][1] * (bfp ? 1u : 2u)};
+      const cuuint64_t strides[1] = {kn[i][1] * 2u};
       const cuuint32_t box[2] = {(cuuint32_t)DCOLS, (cuuint32_t)CK_ROWS};
       const cuuint32_t estr[2] = {1, 1};
-      if (fn(&maps[(size_t)l * 4 + i], bfp ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(w[i]),
-             dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      if (fn(&maps[(size_t)l * 4 + i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(w[i]),
+             dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
     }
@@ -1262,14 +1200,16 @@ bool cluster_plan(const DecodeShape& sh, ClusterParams& c, size_t* smem) {
   c.ks_dn = (sh.ff + c.sl_dn - 1) / c.sl_dn;
   uint32_t vc = sh.hidden > QCc ? sh.hidden : QCc;
   if (c.sl_dn > vc) vc = c.sl_dn;
+  vc = (vc + 7) / 8 * 8;
   c.vec_cols = vc;
   c.att_items = att_items;
   const size_t ring_slots = MTc == 1 ? RingDepth<1>::value : (MTc == 2 ? RingDepth<2>::value : RingDepth<4>::value);
   const size_t stage = (size_t)MTc * DCOLS > 4 * (HD + 4) ? (size_t)MTc * DCOLS : 4 * (HD + 4);
-  *smem = 128 + ring_slots * SLOT_BYTES + 16 * sizeof(uint64_t) + 2 * DCH * 8 * sizeof(uint4) +
-          ((size_t)MTc * sh.hidden * 2 + (size_t)MTc * vc + (size_t)MTc * NQ + (size_t)att_items * 4 * (HD + 4) +
-           (size_t)c.ks_dn * MTc * sh.hidden + 8 * MTc * DCOLS + 4 * HD + 4 * DCH + 16 + stage + 2 * sh.hidden + 2 * HD) * sizeof(float) +
-          (size_t)sh.layers * sizeof(DecodeLayerDev) + SCHED_MAX * sizeof(ChunkEnt) + 8 + 16 + (size_t)MTc * 2 * sh.ff * sizeof(uint16_t);
+  *smem = 1024 + ring_slots * SLOT_BYTES + 16 * sizeof(uint64_t) + 2 * DCH * 8 * sizeof(uint4) +
+          ((size_t)MTc * sh.hidden * 2 + (size_t)MTc * NQ + (size_t)att_items * 4 * (HD + 4) +
+           (size_t)c.ks_dn * MTc * sh.hidden + 4 * HD + 4 * DCH + 16 + stage + 2 * sh.hidden + 2 * HD) * sizeof(float) +
+          (size_t)sh.layers * sizeof(DecodeLayerDev) + SCHED_MAX * sizeof(ChunkEnt) + 8 + 16 +
+          ((size_t)MTc * 2 * sh.ff + (size_t)MTc * vc) * sizeof(uint16_t);
   // the longest list of chunks a block of an eight-block cluster walks in a layer (block 0's)
   auto chunks_of = [&](uint32_t items, uint32_t rows) { return (uint64_t)((items + 7) / 8) * ((rows + CK_ROWS - 1) / CK_ROWS); };
   const uint64_t sched = chunks_of(NQ / DCOLS, sh.hidden) + chunks_of(sh.hidden / DCOLS, QCc) + chunks_of(2 * sh.ff / DCOLS, sh.hidden) +
@@ -1278,14 +1218,13 @@ bool cluster_plan(const DecodeShape& sh, ClusterParams& c, size_t* smem) {
 }
 }  // namespace
 
-// Which form a step takes.  The cluster form where its plan fits and every matrix is BF16: measured on SmolLM2-135M's shape,
-// one sequence, 0.86 ms a step against the grid's 0.99; with BFP8 weights the sixteen blocks' ALUs decode every datum and
-// the grid's 128 blocks are twice as fast (1.33 against 2.66 ms).  B200TT_DECODE=grid or =cluster forces a form where
-// it can run (a development switch; the tests run both).
+// Which form a step takes.  The cluster form where its plan fits and every matrix is BF16 (its products are tensor-core
+// tiles of BF16 as the copies land them); with BFP8 weights every datum is decoded on the ALUs, and the grid's 128 blocks
+// do that twice as fast as sixteen (measured 1.33 against 2.66 ms a step).  B200TT_DECODE=grid forces the grid form (a
+// development switch; the tests run both).
 bool decode_layers_cluster_wanted(const DecodeShape& sh, bool any_bfp) {
   const char* form = getenv("B200TT_DECODE");
-  if (form && form[0] == 'g') return false;
-  if (any_bfp && !(form && form[0] == 'c')) return false;
+  if ((form && form[0] == 'g') || any_bfp) return false;
   ClusterParams c{};
   size_t smem = 0;
   return cluster_plan(sh, c, &smem);

@@ -265,7 +265,8 @@ def test_the_one_launch_step_is_the_composed_step(eng, batch, storage, form, mon
     # element is held to the 2e-2 the cached steps are held to, and the typical one to a fraction of it
     assert worst <= 2e-2 and total / steps <= 1.5e-3, (worst, total / steps)
     assert fused_launches <= 12                        # embedding, cast, the layers, head, argmax, bookkeeping
-    assert eng.last_decode_form().startswith(form)     # "cluster16" / "cluster8" / "grid"
+    # "cluster16" / "cluster8" / "grid"; BFP8 matrices always take the grid form (the cluster form multiplies BF16 tiles)
+    assert eng.last_decode_form().startswith("grid" if storage == "bfp8" else form)
     for l in range(cfg.layers):
         for mine, theirs in ((fused.kc[l], composed.kc[l]), (fused.vc[l], composed.vc[l])):
             x = orc.from_bf16(eng.download_bf16(mine)).reshape(batch, max_len, -1)
