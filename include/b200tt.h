@@ -394,8 +394,10 @@ int32_t b200_attention_rows_as(b200_engine*, const b200_buffer buffers[4], const
  * dims = [sq, d, sk, dv].  causal: query row r sees keys 0..r + (sk - sq).  The result is a new
  * BF16 [result_dims] buffer; elements no block covers are zero.  F32 accumulation, the
  * probabilities rounded to BF16 before the product with V (as `b200_softmax_rows_as` + the BF16
- * product do).  Refused (UNSUPPORTED) unless d = dv is 64 or 128, sq and sk are multiples of 128,
- * scale > 0, sk >= sq when causal, and every column offset and buffer width is a multiple of 8. */
+ * product do).  sq and sk are any positive lengths (ragged heads are what ops.rs:4838-4842 pads): a tail tile reads
+ * the rows that follow its block in the buffer (zeros past the buffer's end) and keeps them out of every maximum and
+ * sum; value rows read that way are weighted by exact zeros, so they must be finite.  Refused (UNSUPPORTED) unless
+ * d = dv is 64 or 128, scale > 0, sk >= sq when causal, and every column offset and buffer width is a multiple of 8. */
 typedef struct b200_attention_block { uint64_t q[2], k[2], v[2], o[2]; } b200_attention_block;
 int32_t b200_attention_blocks(b200_engine*, b200_buffer q, b200_buffer k, b200_buffer v,
                               const b200_attention_block* items, uint64_t n_items, const uint64_t dims[4],

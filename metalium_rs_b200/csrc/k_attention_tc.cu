@@ -18,6 +18,10 @@
 // S is double-buffered in TMEM so the next tile's product runs under this tile's exponentials.
 // Every wait is bounded; a wait that runs out sets the engine's error word to TIMEOUT and the CTA
 // leaves in order (copies drained, TMEM freed).
+// sq and sk need not be whole tiles (the reference pads ragged heads, ops.rs:4838-4842): the last query tile's rows
+// past sq are computed and not stored, the last key tile's keys past sk are masked by index like the keys a causal
+// row may not see.  The rows a tail tile reads past its block are whatever follows in the buffer (zeros past its end):
+// scores of such keys never enter a maximum or a sum, and such value rows are weighted by exact zeros.
 #include <cfloat>
 #include <cstdint>
 #include <cuda_runtime.h>
@@ -38,6 +42,7 @@ constexpr int SOFTMAX_THREADS = 256;
 struct AttnTcParams {
   const AttnBlockDev* items;
   uint32_t q_tiles, k_tiles, n_items;
+  uint32_t sq, sk;              // rows of a block's Q and of its K and V (the last tiles may be partial)
   int32_t causal, causal_off;   // a query i sees keys j <= i + causal_off
   float scale_log2;             // scale * log2(e)
   int32_t spin;                 // the S -> P -> O hand-offs wait by polling
@@ -232,7 +237,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const uint32_t row = quad * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16);
     const int32_t qi = i0 + (int32_t)row;
-    const int32_t last_key = p.causal ? qi + p.causal_off : 0x7fffffff;
+    const int32_t seen = p.causal ? qi + p.causal_off : 0x7fffffff;
+    const int32_t last_key = seen < (int32_t)p.sk - 1 ? seen : (int32_t)p.sk - 1;   // no key past the block's
     bool ok = true;
     uint32_t t = 0;
     float mx = -INFINITY;
@@ -307,6 +313,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (ok && !mbar_wait(o_full, 0, abort_flag, wait_limit)) ok = false;
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const bool stored = qi < (int32_t)p.sq;          // a row past the block's queries is read with its warp (the
+                                                       // tensor-memory loads are warp-wide) and not stored
       const float inv = 1.0f / ((sum < FLT_MIN) ? FLT_MIN : sum);
       constexpr int OC = D / 2;                      // this thread's columns of O
       uint16_t* dst = p.out + it.o_off + (uint64_t)(i0 + (int32_t)row) * p.o_ld + half * OC;
@@ -322,7 +330,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           w.y = pack_bf16(__uint_as_float(v[q4 * 8 + 2]) * inv, __uint_as_float(v[q4 * 8 + 3]) * inv);
           w.z = pack_bf16(__uint_as_float(v[q4 * 8 + 4]) * inv, __uint_as_float(v[q4 * 8 + 5]) * inv);
           w.w = pack_bf16(__uint_as_float(v[q4 * 8 + 6]) * inv, __uint_as_float(v[q4 * 8 + 7]) * inv);
-          *reinterpret_cast<uint4*>(dst + cb * 32 + q4 * 8) = w;
+          if (stored) *reinterpret_cast<uint4*>(dst + cb * 32 + q4 * 8) = w;
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -359,7 +367,7 @@ cudaError_t launch_d(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
 bool attention_tc_supported(uint64_t sq, uint64_t d, uint64_t sk, uint64_t dv, float scale, int causal, const char** why) {
   if (!tc::encode_fn()) { *why = "no tensor-map encoder in this driver"; return false; }
   if (!(d == 64 || d == 128) || dv != d) { *why = "head width 64 or 128, the same for keys and values"; return false; }
-  if (sq == 0 || sk == 0 || sq % 128 || sk % 128) { *why = "sequence lengths are whole tiles of 128"; return false; }
+  if (sq == 0 || sk == 0) { *why = "no queries or no keys"; return false; }
   if (sq > (1u << 30) || sk > (1u << 30)) { *why = "sequence too long"; return false; }
   if (!(scale > 0.f)) { *why = "scale must be positive"; return false; }
   if (causal && sk < sq) { *why = "a causal mask with fewer keys than queries"; return false; }
@@ -371,15 +379,17 @@ cudaError_t launch_attention_tc(const void* q, uint64_t q_rows, uint64_t q_cols,
                                 const AttnBlockDev* items, uint64_t n_items, uint64_t sq, uint64_t d, uint64_t sk,
                                 float scale, int causal, void* out, uint64_t o_ld, int* err, cudaStream_t stream) {
   if (n_items == 0) return cudaSuccess;
-  if (n_items * (sq / 128) > 0x7fffffffull) return cudaErrorNotSupported;
+  if (n_items * ((sq + 127) / 128) > 0x7fffffffull) return cudaErrorNotSupported;
   CUtensorMap mq, mk, mv;
   if (!tc::make_map(&mq, q, q_rows, q_cols, q_cols, 128) || !tc::make_map(&mk, k, k_rows, k_cols, k_cols, 128) ||
       !tc::make_map(&mv, v, v_rows, v_cols, v_cols, 128))
     return cudaErrorNotSupported;
   AttnTcParams p;
   p.items = items;
-  p.q_tiles = (uint32_t)(sq / 128);
-  p.k_tiles = (uint32_t)(sk / 128);
+  p.q_tiles = (uint32_t)((sq + 127) / 128);
+  p.k_tiles = (uint32_t)((sk + 127) / 128);
+  p.sq = (uint32_t)sq;
+  p.sk = (uint32_t)sk;
   p.n_items = (uint32_t)n_items;
   p.causal = causal ? 1 : 0;
   p.causal_off = (int32_t)(sk - sq);

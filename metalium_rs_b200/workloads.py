@@ -184,10 +184,11 @@ class LlamaPrefill:
         self.fused_mlp = bool(fused_mlp)
         if self.fused_mlp and cfg.ff % 128:
             raise ValueError("the fused gate|up product needs ff in whole groups of 128 columns")
-        takes = seq % 128 == 0 and cfg.head_dim in (64, 128)
+        takes = cfg.head_dim in (64, 128)                    # any length: a tail tile is masked by index
         if fused_attention and not takes:
             raise ValueError("the fused attention kernel does not take this shape")
-        self.fused = takes if fused_attention is None else bool(fused_attention)
+        # by default the one-kernel form from a tile of tokens up (below that the composed form's scores are small)
+        self.fused = (takes and seq >= 128) if fused_attention is None else bool(fused_attention)
         up = lambda a: eng.upload_bf16(_bf16(a), *a.shape)
         self.w = {}
         for k, v in weights.items():

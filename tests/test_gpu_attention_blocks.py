@@ -75,6 +75,35 @@ def test_more_keys_than_queries_and_future_keys_are_not_seen(eng):
         eng.free(i)
 
 
+@pytest.mark.parametrize("blocks,sq,sk,d,causal", [
+    (3, 100, 100, 64, True),       # a prompt of 100 tokens: one partial tile
+    (2, 500, 500, 64, True),       # the 500-token prompt of ops.rs:4838's padding: three whole tiles and a tail
+    (2, 77, 333, 128, False),      # ragged on both sides
+    (2, 129, 257, 64, True),       # one row and one key past a tile
+    (1, 1, 1, 64, False), (1, 200, 129, 128, False),
+])
+def test_heads_whose_lengths_are_not_whole_tiles(eng, blocks, sq, sk, d, causal):
+    # the blocks lie one after another in their buffers, so a tail tile reads the next block's rows (the last block's
+    # tail reads past the buffer): none of that may reach a result, and rows past sq must not be written
+    q = orc.to_bf16(orc.normal(0xF1D, 1, (blocks * sq, d), 1.5))
+    k = orc.to_bf16(orc.normal(0xF1D, 2, (blocks * sk, d), 1.5))
+    v = orc.to_bf16(orc.normal(0xF1D, 3, (blocks * sk, d), 1.5))
+    qf, kf, vf = orc.from_bf16(q), orc.from_bf16(k), orc.from_bf16(v)
+    iq, ik, iv = eng.upload_bf16(q, blocks * sq, d), eng.upload_bf16(k, blocks * sk, d), eng.upload_bf16(v, blocks * sk, d)
+    pad = 64                                           # rows of the result no block covers: they stay zero
+    items = [((b * sq, 0), (b * sk, 0), (b * sk, 0), (b * (sq + pad), 0)) for b in range(blocks)]
+    scale = 1.0 / np.sqrt(d)
+    out, dims = eng.attention_blocks(iq, ik, iv, items, [sq, d, sk, d], scale, causal, [blocks * (sq + pad), d])
+    got = orc.from_bf16(eng.download_bf16(out))
+    for b in range(blocks):
+        want, bound = _want(qf[b * sq:(b + 1) * sq], kf[b * sk:(b + 1) * sk], vf[b * sk:(b + 1) * sk], scale, causal)
+        r0 = b * (sq + pad)
+        _check(got[r0:r0 + sq], want, bound)
+        assert not got[r0 + sq:r0 + sq + pad].any(), b    # a partial query tile wrote nothing past its block
+    for i in (iq, ik, iv, out):
+        eng.free(i)
+
+
 def test_uncovered_result_elements_are_zero(eng):
     s, d = 128, 64
     x = orc.to_bf16(orc.normal(0xF1C, 1, (s, 3 * d)))
@@ -88,8 +117,8 @@ def test_uncovered_result_elements_are_zero(eng):
 
 
 @pytest.mark.parametrize("dims,scale,causal", [
-    ([128, 32, 128, 32], 1.0, False), ([128, 64, 128, 128], 1.0, False), ([100, 64, 128, 64], 1.0, False),
-    ([128, 64, 200, 64], 1.0, False), ([256, 64, 128, 64], 1.0, True), ([128, 64, 128, 64], 0.0, False),
+    ([128, 32, 128, 32], 1.0, False), ([128, 64, 128, 128], 1.0, False), ([0, 64, 128, 64], 1.0, False),
+    ([256, 64, 128, 64], 1.0, True), ([128, 64, 128, 64], 0.0, False),
 ])
 def test_shapes_outside_the_kernel_are_refused(eng, dims, scale, causal):
     sq, d, sk, dv = dims

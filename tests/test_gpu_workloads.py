@@ -69,6 +69,29 @@ def small_llama():
     return W.LlamaConfig(layers=3, hidden=576, heads=9, kv_heads=3, head_dim=64, ff=1536, vocab=2048)
 
 
+def test_llama_prefill_of_a_prompt_that_is_not_whole_tiles(eng):
+    # 200 tokens a sequence: the fused attention kernel masks its second tile's tail by index, where the reference pads
+    # (crates/burn-tt/src/ops.rs:4838-4842); both forms against the restatement, and against each other
+    cfg = small_llama()
+    batch, seq = 2, 200
+    w = W.llama_weights(cfg, seed=7)
+    wb = {k: orc.from_bf16(orc.to_bf16(v)) for k, v in w.items()}
+    ids = orc.integers(0xC0F4, 11, (1, batch * seq), cfg.vocab)
+    want = M.llama_prefill(cfg, wb, ids, batch, seq)
+    ii = eng.upload_bits(ids.view(np.uint32), 1, batch * seq, I32)
+    got = {}
+    for fused in (True, False):
+        model = W.LlamaPrefill(eng, cfg, w, batch, seq, fused_attention=fused)
+        assert model.fused == fused
+        logits, am = model.forward(ii)
+        got[fused] = eng.download(logits)
+        assert np.max(np.abs(got[fused] - want)) <= 2e-2, fused
+        eng.free(logits); eng.free(am)
+    assert W.LlamaPrefill(eng, cfg, w, batch, seq).fused      # and it is the default from a tile of tokens up
+    assert np.max(np.abs(got[True] - got[False])) <= 2e-2
+    eng.free(ii)
+
+
 @pytest.mark.parametrize("fused", [False, True])   # the composed attention (ops.rs:4825) and the one-kernel form
 def test_llama_prefill_logits_and_argmax(eng, fused):
     # the SmolLM2-135M layer shape, fewer layers and a smaller vocabulary so the oracle runs in seconds
