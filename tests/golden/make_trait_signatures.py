@@ -102,7 +102,9 @@ def trait_signatures(reference_root: Path) -> dict:
 
 
 if __name__ == "__main__":
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_trait_signatures.py <root of the metalium-rs tree>")
+    root = Path(sys.argv[1])
     sig = trait_signatures(root)
     (HERE / "engine_trait.json").write_text(json.dumps(sig, indent=1, sort_keys=True) + "\n")
     print(f"{len(sig)} methods written")
