@@ -748,7 +748,7 @@ template <int MT, int R, class Emit>
 __device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, uint32_t len, uint8_t* ring, uint64_t* bars, uint32_t& head,
                                                uint32_t& parity, bool& dead, long long limit, int* err, WeightWalk& walk, Emit emit) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  float c[4] = {0.f, 0.f, 0.f, 0.f};
+  float c[4][4] = {};
   const uint16_t* arow = a + (size_t)(g < MT ? g : 0) * lda;
   for (uint32_t base = 0; base < len; base += CK_ROWS) {
     // the oldest of the R chunks in flight: its tile has landed when the slot's mbarrier flips
@@ -758,29 +758,30 @@ __device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, 
     }
     parity ^= 1u << head;
     const uint32_t slot = tc::smem_u32(ring + (size_t)head * SLOT_BYTES);
+    // every load of the chunk first (six loads of four 8x8 matrices, the A columns beside them), then twelve MMAs into
+    // four accumulators in turn: one accumulator would chain the twelve, ~35 cycles each
+    uint32_t bq[CK_ROWS / 32][4], aq[CK_ROWS / 32][4];
 #pragma unroll
-    for (int ks = 0; ks < CK_ROWS / 16; ks += 2) {     // two k-steps of 16 rows a load of four 8x8 matrices
-      const uint32_t k = ks * 16 + lane;               // this lane names row k of the slot
-      uint32_t b0, b1, b2, b3;
-      ldmatrix_x4_trans(slot + k * 128 + (((uint32_t)warp ^ (k & 7)) << 4), b0, b1, b2, b3);
-      const uint32_t kk = base + ks * 16 + 2 * t;       // this thread's A columns: kk, kk+1, kk+8, kk+9 and the same + 16
-      uint32_t a0 = 0, a2 = 0, a4 = 0, a6 = 0;
-      if (g < MT) {                                     // a row past the item's k counts as zeros (the slot may hold the next slice there)
-        if (kk < len) a0 = *reinterpret_cast<const uint32_t*>(arow + kk);
-        if (kk + 8 < len) a2 = *reinterpret_cast<const uint32_t*>(arow + kk + 8);
-        if (kk + 16 < len) a4 = *reinterpret_cast<const uint32_t*>(arow + kk + 16);
-        if (kk + 24 < len) a6 = *reinterpret_cast<const uint32_t*>(arow + kk + 24);
-      }
-      mma_bf16_16816(c, a0, 0u, a2, 0u, b0, b1);
-      mma_bf16_16816(c, a4, 0u, a6, 0u, b2, b3);
+    for (int i = 0; i < CK_ROWS / 32; ++i) {
+      const uint32_t k = i * 32 + lane;                // this lane names row k of the slot
+      ldmatrix_x4_trans(slot + k * 128 + (((uint32_t)warp ^ (k & 7)) << 4), bq[i][0], bq[i][1], bq[i][2], bq[i][3]);
+      const uint32_t kk = base + i * 32 + 2 * t;        // this thread's A columns: kk, kk+1, kk+8, kk+9 and the same + 16
+#pragma unroll
+      for (int j = 0; j < 4; ++j)                       // a row past the item's k counts as zeros (the slot may hold the next slice there)
+        aq[i][j] = (g < MT && kk + 8 * j < len) ? *reinterpret_cast<const uint32_t*>(arow + kk + 8 * j) : 0u;
+    }
+#pragma unroll
+    for (int i = 0; i < CK_ROWS / 32; ++i) {
+      mma_bf16_16816(c[(2 * i) & 3], aq[i][0], 0u, aq[i][1], 0u, bq[i][0], bq[i][1]);
+      mma_bf16_16816(c[(2 * i + 1) & 3], aq[i][2], 0u, aq[i][3], 0u, bq[i][2], bq[i][3]);
     }
     __syncthreads();                                   // every warp is done with the slot: refill it
     walk.issue(ring + (size_t)head * SLOT_BYTES, &bars[head]);
     head = head + 1 == (uint32_t)R ? 0 : head + 1;
   }
-  if (g < MT) {
-    emit(g, warp * 8 + 2 * t, c[0]);                   // into the block's staging row: the caller sends it on
-    emit(g, warp * 8 + 2 * t + 1, c[1]);
+  if (g < MT) {                                        // the four partial sums in a fixed order
+    emit(g, warp * 8 + 2 * t, (c[0][0] + c[1][0]) + (c[2][0] + c[3][0]));   // into the block's staging row: the caller sends it on
+    emit(g, warp * 8 + 2 * t + 1, (c[0][1] + c[1][1]) + (c[2][1] + c[3][1]));
   }
   __syncthreads();                                     // the staged results are whole
 }
