@@ -145,6 +145,15 @@ int32_t b200_matmul_host_bf16(b200_engine*, const uint16_t* a, const uint16_t* b
  * `matmul_dram_bf16` on [Bg | Bu] then `SILU_MUL` on its halves (crates/tt-models/src/llama.rs:498), with neither
  * the [m, n] product nor a second launch.  Refused unless the tcgen05 path takes the product. */
 int32_t b200_matmul_silu_mul(b200_engine*, b200_buffer a, b200_buffer b, b200_buffer* out, uint64_t out_dims[2]);
+/* A fused QKV projection with RoPE in the product's epilogue (an extension, as `b200_matmul_silu_mul` is): out =
+ * A B as BF16 [m, n] with the heads of 64 columns that lie below `rope_cols` rotated, fl(fl(x cos) + fl(swap(x) sin))
+ * on the product's BF16 result, rounded once more to BF16 -- bit for bit `matmul_dram_bf16` then `rope_blocks`
+ * (server.rs:566) with a BF16 result on columns [0, rope_cols) (crates/tt-models/src/llama.rs:404-433,
+ * crates/tt-models/src/rope.rs:19-60).  cos_ and sin_ are F32 [r, 64] blocks (sin as [-sin, sin]); product row i
+ * uses table row i % r.  Refused unless rope_cols is a multiple of 64 within n, r divides m, the tables' rows start
+ * at 16-byte addresses, and the tcgen05 path takes the product. */
+int32_t b200_matmul_rope(b200_engine*, b200_buffer a, b200_buffer b, const b200_block_arg* cos_, const b200_block_arg* sin_,
+                         uint64_t rope_cols, b200_buffer* out, uint64_t out_dims[2]);
 /* The sharded product's fused step: C = A B (BF16 operands as stored, no transposes) written from the
  * product's epilogue into columns [col_first, col_first + n) of each of the n_dst matrices dst[i]
  * ([dst_rows, dst_cols] row-major, of the result's type) -- this GPU's C and, through b200_ipc_open,

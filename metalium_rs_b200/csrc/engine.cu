@@ -882,6 +882,58 @@ int32_t b200_matmul_silu_mul(b200_engine* e, b200_buffer a, b200_buffer b, b200_
   return B200_OK;
 }
 
+// The fused QKV projection with RoPE applied in the product's epilogue to the heads below `rope_cols` (the query and
+// key heads; the value heads pass through): bit for bit `matmul_dram_bf16` then `rope_blocks` with a BF16 result on
+// those columns (crates/tt-models/src/llama.rs:404-433), without the second launch or its pass over the projection.
+int32_t b200_matmul_rope(b200_engine* e, b200_buffer a, b200_buffer b, const b200_block_arg* cs, const b200_block_arg* sn,
+                         uint64_t rope_cols, b200_buffer* out, uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *A = nullptr, *B = nullptr;
+  int st = e->need(a, &A, "matmul_rope");
+  if (!st) st = e->need(b, &B, "matmul_rope");
+  if (st) return st;
+  Mat mc, ms;
+  st = mat_of_block(e, cs, &mc, "matmul_rope");
+  if (!st) st = mat_of_block(e, sn, &ms, "matmul_rope");
+  if (st) return st;
+  A = e->get(a); B = e->get(b);
+  if (A->elem != B200_BF16 || B->elem != B200_BF16) return e->fail(B200_UNSUPPORTED, "matmul_rope: BF16 operands");
+  const uint64_t m = A->rows, k = A->cols, n = B->cols;
+  if (B->rows != k || k == 0 || m == 0 || n == 0 || rope_cols == 0 || rope_cols % 64 || rope_cols > n)
+    return e->fail(B200_UNSUPPORTED, "matmul_rope: [%llu,%llu] x [%llu,%llu] with RoPE on %llu columns (heads of 64 within the product)",
+                   (unsigned long long)m, (unsigned long long)k, (unsigned long long)B->rows, (unsigned long long)n, (unsigned long long)rope_cols);
+  auto table_ok = [&](const Mat& t) {
+    return !t.bf16 && t.cols == 64 && t.rows > 0 && m % t.rows == 0 && t.ld % 4 == 0 && ((uintptr_t)t.p & 15) == 0 && t.ld < (1ull << 31) &&
+           t.rows < (1ull << 31);
+  };
+  if (!table_ok(mc) || !table_ok(ms) || mc.rows != ms.rows || mc.ld != ms.ld)
+    return e->fail(B200_UNSUPPORTED, "matmul_rope: the tables are F32 [r, 64] blocks at 16-byte rows, r dividing the product's rows");
+  Buf* C = nullptr;
+  st = e->new_buffer(m, n, B200_BF16, out, &C);
+  if (st) return st;
+  A = e->get(a); B = e->get(b);
+  GemmArgs g{};
+  g.a = A->ptr; g.b = B->ptr; g.c = C->ptr;
+  g.in_bf16 = 1; g.out_bf16 = 1;
+  g.m = m; g.n = n; g.k = k;
+  g.lda = A->cols; g.ldb = B->cols; g.ldc = n;
+  g.a_trans = 0; g.b_trans = 0; g.batch = 1; g.batches_dev = nullptr;
+  g.epi_mode = 2;
+  g.rope_cos = (const float*)mc.p; g.rope_sin = (const float*)ms.p;
+  g.rope_rows = (uint32_t)mc.rows; g.rope_ld = (uint32_t)mc.ld; g.rope_cols = (uint32_t)rope_cols;
+  g.sm_limit = e->matmul_sm_limit;
+  const char* why = "";
+  if (n >= (1ull << 31) || !gemm_tc_supported(g, &why)) { e->drop(*out); return e->fail(B200_UNSUPPORTED, "matmul_rope: the tcgen05 path refuses this product (%s)", why); }
+  int pair = 0;
+  const cudaError_t ce = launch_gemm_tc(g, nullptr, e->d_err, e->stream, &pair);
+  if (ce == cudaErrorNotSupported) { e->drop(*out); return e->fail(B200_UNSUPPORTED, "matmul_rope: the driver refused a tensor map for this shape"); }
+  e->matmul_path = pair ? "tcgen05-pair" : "tcgen05";
+  st = e->launched(ce, "matmul_rope");
+  if (st) { e->drop(*out); return st; }
+  set_dims(out_dims, m, n);
+  return B200_OK;
+}
+
 // C = A B written into one or more caller-named matrices instead of a new buffer: the sharded
 // product's rank writes its column slice straight into every rank's C (its own and, through
 // addresses opened with b200_ipc_open, its peers' over NVLink) from the product's epilogue.

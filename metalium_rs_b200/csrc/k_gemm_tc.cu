@@ -322,6 +322,7 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int
   p.c = g.c; p.out_bf16 = g.out_bf16; p.err = err_word;
   p.n_more = g.n_more;
   p.epi_mode = g.epi_mode;
+  p.rope_cos = g.rope_cos; p.rope_sin = g.rope_sin; p.rope_rows = g.rope_rows; p.rope_ld = g.rope_ld; p.rope_cols = g.rope_cols;
   p.multicast = g.multicast;
   p.staged = epilogue_staged(g.c, g.c_more, g.n_more, g.ldc, g.out_bf16);
   for (int i = 0; i < 7; ++i) p.c_more[i] = i < g.n_more ? g.c_more[i] : nullptr;

@@ -26,7 +26,7 @@ using namespace tc;
 
 constexpr int P_BN = 256;     // tile columns of the pair
 constexpr int P_HALF = 128;   // B columns a CTA loads
-constexpr int P_STAGES = 6;
+constexpr int P_STAGES = 6;       // with four epilogue warps a CTA; five with eight (their staging rows take a stage's room)
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -65,9 +65,12 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                ::"r"(smem_u32(bar)), "h"(mask) : "memory");
 }
 
-template <bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// EW: epilogue warps a CTA.  Four for a plain product; eight for the gated epilogue (`epi_mode` 1), whose activation
+// is too much arithmetic for four warps to finish under the next tile's mainloop when k is short.
+template <bool A_MN, bool B_MN, int EW = 4>
+__global__ void __launch_bounds__(64 + EW * 32, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
+  constexpr int P_STAGES = EW == 8 ? 5 : 6;
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = P_HALF * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -83,7 +86,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const uint32_t rank = cluster_rank();   // 0: leader
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 2 * EW); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -173,8 +176,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       if (!ok) { atomicCAS(p.err, 0, TIMEOUT_CODE); *abort_flag = 1; }
     }
   } else {
-    // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
-    const uint32_t quad = warp & 3;
+    // ---------------- epilogue (warps 2.. of both CTAs; a warp reads the tensor-memory lanes of its quadrant) ----------------
+    const uint32_t quad = warp & 3, ew = (uint32_t)warp - 2;
     uint32_t local = 0;
     bool ok = true;
     for (uint64_t t = cluster_id; t < total_tiles && ok; t += n_clusters, ++local) {
@@ -184,8 +187,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, wait_limit)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint64_t n0 = (uint64_t)tn * P_BN;
-      if (p.epi_mode == 1) epilogue_warp_silu_mul(p, tmem_base + ((quad * 32u) << 16) + acc * P_BN, (uint64_t)tm * 256 + rank * BM + quad * 32, tn, lane, epi_stage + quad * EPI_WARP_BYTES);
-      else epilogue_warp<P_BN>(p, tmem_base + ((quad * 32u) << 16) + acc * P_BN, 0, (uint64_t)tm * 256 + rank * BM + quad * 32, n0, lane, epi_stage + quad * EPI_WARP_BYTES);
+      if constexpr (EW == 8) {   // the gated epilogue on eight warps: warps 2..5 take the first 64 output columns, 6..9 the others
+        silu_mul_pass(p, tmem_base + ((quad * 32u) << 16) + acc * P_BN, (uint64_t)tm * 256 + rank * BM + quad * 32, tn, lane,
+                      epi_stage + ew * EPI_WARP_BYTES, (int)(ew >> 2) * 2);
+      } else {
+        if (p.epi_mode == 1) epilogue_warp_silu_mul(p, tmem_base + ((quad * 32u) << 16) + acc * P_BN, (uint64_t)tm * 256 + rank * BM + quad * 32, tn, lane, epi_stage + ew * EPI_WARP_BYTES);
+        else epilogue_warp<P_BN>(p, tmem_base + ((quad * 32u) << 16) + acc * P_BN, 0, (uint64_t)tm * 256 + rank * BM + quad * 32, n0, lane, epi_stage + ew * EPI_WARP_BYTES);
+      }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(map_to_rank(smem_u32(&acc_empty[acc]), 0));
@@ -234,15 +242,20 @@ cudaError_t launch_gemm_tc2(const GemmArgs& g, int* err_word, cudaStream_t strea
   p.c = g.c; p.out_bf16 = g.out_bf16; p.err = err_word;
   p.n_more = g.n_more;
   p.epi_mode = g.epi_mode;
+  p.rope_cos = g.rope_cos; p.rope_sin = g.rope_sin; p.rope_rows = g.rope_rows; p.rope_ld = g.rope_ld; p.rope_cols = g.rope_cols;
   p.multicast = g.multicast;
   p.group = tile_group_setting(TILE_GROUP_PAIR);
   p.staged = epilogue_staged(g.c, g.c_more, g.n_more, g.ldc, g.out_bf16);
   for (int i = 0; i < 7; ++i) p.c_more[i] = i < g.n_more ? g.c_more[i] : nullptr;
-  constexpr size_t smem = (size_t)P_STAGES * (BM * BK * 2 + P_HALF * BK * 2) + 1024 + 256 + EPI_BYTES;
+  // the gated epilogue takes eight epilogue warps a CTA and five stages (B200TT_SILU_WARPS=4: the four-warp form, for comparison)
+  static const bool eight = []() { const char* e = getenv("B200TT_SILU_WARPS"); return !(e && e[0] == '4'); }();
+  const bool ew8 = g.epi_mode == 1 && eight;
+  const size_t smem = ew8 ? (size_t)5 * (BM * BK * 2 + P_HALF * BK * 2) + 1024 + 256 + 2 * EPI_BYTES
+                          : (size_t)P_STAGES * (BM * BK * 2 + P_HALF * BK * 2) + 1024 + 256 + EPI_BYTES;
   const uint64_t total = (uint64_t)p.tiles_m * p.tiles_n;
 
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.blockDim = dim3(ew8 ? 64 + 8 * 32 : NUM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -252,28 +265,35 @@ cudaError_t launch_gemm_tc2(const GemmArgs& g, int* err_word, cudaStream_t strea
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr; cfg.numAttrs = pdl_enabled() ? 2 : 1;
   cudaError_t e = cudaSuccess;
-#define TC2_LAUNCH(AM, BMJ)                                                                           \
+#define TC2_LAUNCH(AM, BMJ, EWJ)                                                                      \
   do {                                                                                                \
     int clusters = 0;   /* clusters of this kernel one device runs at a time: asked once a device */ \
-    e = ensure_dynamic_smem((const void*)gemm_tc2_kernel<AM, BMJ>, smem);                             \
+    e = ensure_dynamic_smem((const void*)gemm_tc2_kernel<AM, BMJ, EWJ>, smem);                        \
     if (e != cudaSuccess) return e;                                                                   \
-    if (!device_value_get((const void*)gemm_tc2_kernel<AM, BMJ>, &clusters)) {                        \
+    if (!device_value_get((const void*)gemm_tc2_kernel<AM, BMJ, EWJ>, &clusters)) {                   \
       cfg.gridDim = dim3(148, 1, 1);                                                                  \
       int n = 0;                                                                                      \
-      e = cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<AM, BMJ>, &cfg);                         \
+      e = cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<AM, BMJ, EWJ>, &cfg);                    \
       if (e != cudaSuccess || n <= 0) { cudaGetLastError(); return cudaErrorNotSupported; }           \
       clusters = n;                                                                                   \
-      device_value_set((const void*)gemm_tc2_kernel<AM, BMJ>, n);                                     \
+      device_value_set((const void*)gemm_tc2_kernel<AM, BMJ, EWJ>, n);                                \
     }                                                                                                 \
     uint64_t use = total < (uint64_t)clusters ? total : (uint64_t)clusters;                           \
     if (g.sm_limit > 1 && use > (uint64_t)(g.sm_limit / 2)) use = (uint64_t)(g.sm_limit / 2);        \
     cfg.gridDim = dim3((unsigned)(2 * use), 1, 1);                                                    \
-    e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<AM, BMJ>, ma, mb, p);                                \
+    e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<AM, BMJ, EWJ>, ma, mb, p);                           \
   } while (0)
-  if (!a_mn && !b_mn) TC2_LAUNCH(false, false);
-  else if (!a_mn && b_mn) TC2_LAUNCH(false, true);
-  else if (a_mn && !b_mn) TC2_LAUNCH(true, false);
-  else TC2_LAUNCH(true, true);
+  if (ew8) {
+    if (!a_mn && !b_mn) TC2_LAUNCH(false, false, 8);
+    else if (!a_mn && b_mn) TC2_LAUNCH(false, true, 8);
+    else if (a_mn && !b_mn) TC2_LAUNCH(true, false, 8);
+    else TC2_LAUNCH(true, true, 8);
+  } else {
+    if (!a_mn && !b_mn) TC2_LAUNCH(false, false, 4);
+    else if (!a_mn && b_mn) TC2_LAUNCH(false, true, 4);
+    else if (a_mn && !b_mn) TC2_LAUNCH(true, false, 4);
+    else TC2_LAUNCH(true, true, 4);
+  }
 #undef TC2_LAUNCH
   return e;
 }

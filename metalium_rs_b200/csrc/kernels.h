@@ -125,6 +125,10 @@ struct GemmArgs {
   int n_more = 0;          // the tensor-core product also stores C at these addresses (same pitch as c)
   int multicast = 0;       // c is a multicast address: every 16-byte piece is stored once with multimem.st (n_more == 0)
   int epi_mode = 0;        // 1: the tensor-core epilogue stores silu(gate) * up of each 256-column tile's halves (n % 256 == 0)
+                           // 2: BF16 result with RoPE applied to the heads of 64 columns that lie below rope_cols
+  const float* rope_cos = nullptr;   // [rope_rows, 64] F32 (pitch rope_ld floats): row r of the product uses table row r % rope_rows
+  const float* rope_sin = nullptr;   // the same shape, [-sin, sin]
+  uint32_t rope_rows = 0, rope_ld = 0, rope_cols = 0;
   int sm_limit = 0;        // > 0: the tensor-core product uses at most this many SMs (the rest stay free for a
                            // collective running beside it)
 };

@@ -27,7 +27,11 @@ struct TcParams {
   void* c;
   void* c_more[7];           // further copies of C with c's pitch (a peer GPU's memory among them), or none
   int n_more;
-  int epi_mode;              // 0: store the product; 1: silu(gate) * up of a tile's two 128-column halves (BN 256)
+  int epi_mode;              // 0: store the product; 1: silu(gate) * up of a tile's two 128-column halves (BN 256);
+                             // 2: RoPE on the 64-column heads below rope_cols (BF16 result)
+  const float* rope_cos;     // [rope_rows, 64] F32, pitch rope_ld: product row r uses table row r % rope_rows
+  const float* rope_sin;     // [-sin, sin]
+  uint32_t rope_rows, rope_ld, rope_cols;
   int staged;                // the epilogue may go through shared memory (pointers and pitch are 16-byte aligned)
   int out_bf16;
   int multicast;             // c is a multicast address (stored once with multimem.st, every row piece whole: no ragged edges)
@@ -221,6 +225,27 @@ __device__ __forceinline__ void epilogue_warp(const TcParams& p, uint32_t tacc, 
       tmem_ld32(tacc + cb * 32 + 32, v + 32);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       const uint64_t col = n0 + cb * 32;
+      if (p.epi_mode == 2 && col + 64 <= p.rope_cols) {   // the same for the whole warp: these 64 columns are one head
+        // the composition's steps (crates/tt-models/src/rope.rs:19-60 through `rope_blocks`, crates/tt-kernels/src/tensor.rs:5545-5552):
+        // the product rounded to BF16 as its result would be, then fl(fl(x cos) + fl(swap(x) sin)) with swap(j) = j +- 32;
+        // the store below rounds that once more to BF16, as `rope_blocks` with a BF16 result does
+        const uint64_t tr = (row_ok ? row : 0) % p.rope_rows;
+        const float4* co = reinterpret_cast<const float4*>(p.rope_cos + tr * p.rope_ld);
+        const float4* si = reinterpret_cast<const float4*>(p.rope_sin + tr * p.rope_ld);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 c_lo = co[q], c_hi = co[q + 8], s_lo = si[q], s_hi = si[q + 8];
+          const float cl[4] = {c_lo.x, c_lo.y, c_lo.z, c_lo.w}, ch[4] = {c_hi.x, c_hi.y, c_hi.z, c_hi.w};
+          const float sl[4] = {s_lo.x, s_lo.y, s_lo.z, s_lo.w}, sh[4] = {s_hi.x, s_hi.y, s_hi.z, s_hi.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = q * 4 + e;
+            const float x0 = bf16_bits_to_f32(f32_to_bf16_bits(v[j])), x1 = bf16_bits_to_f32(f32_to_bf16_bits(v[j + 32]));
+            v[j] = __float_as_uint(__fadd_rn(__fmul_rn(x0, cl[e]), __fmul_rn(x1, sl[e])));
+            v[j + 32] = __float_as_uint(__fadd_rn(__fmul_rn(x1, ch[e]), __fmul_rn(x0, sh[e])));
+          }
+        }
+      }
       if (staged && col + 64 <= p.n) {          // the same for the whole warp
         uint8_t* mine = stage + lane * EPI_PITCH;
 #pragma unroll
@@ -276,13 +301,13 @@ __device__ __forceinline__ uint32_t silu_mul_pair(uint32_t g0, uint32_t u0, uint
   return (uint32_t)f32_to_bf16_bits(__float_as_uint(r0)) | ((uint32_t)f32_to_bf16_bits(__float_as_uint(r1)) << 16);
 }
 
-__device__ __forceinline__ void epilogue_warp_silu_mul(const TcParams& p, uint32_t tacc, uint64_t row0, uint64_t tile_n,
-                                                       int lane, uint8_t* stage) {
+// One pass of the gated epilogue: 64 output columns, from gate chunks cb, cb+1 and up chunks 4+cb, 4+cb+1 (cb 0 or 2).
+__device__ __forceinline__ void silu_mul_pass(const TcParams& p, uint32_t tacc, uint64_t row0, uint64_t tile_n, int lane,
+                                              uint8_t* stage, int cb) {
   const uint64_t row = row0 + lane;
   const bool row_ok = row < p.m;
   const uint64_t out_n = p.n / 2;
-#pragma unroll 1
-  for (int cb = 0; cb < 4; cb += 2) {            // 64 output columns a pass: gate chunks cb, cb+1 and up chunks 4+cb, 4+cb+1
+  {
     uint32_t g[64], u[64];
     tmem_ld32(tacc + cb * 32, g);
     tmem_ld32(tacc + cb * 32 + 32, g + 32);
@@ -307,6 +332,13 @@ __device__ __forceinline__ void epilogue_warp_silu_mul(const TcParams& p, uint32
       }
     }
   }
+}
+// Four epilogue warps a CTA: a warp takes both passes of its 32 rows.  Eight: two warps share the rows, a pass each
+// (the activation's exponentials and divisions on four warps outlast a tile of nine k-blocks; on eight they do not).
+__device__ __forceinline__ void epilogue_warp_silu_mul(const TcParams& p, uint32_t tacc, uint64_t row0, uint64_t tile_n,
+                                                       int lane, uint8_t* stage) {
+#pragma unroll 1
+  for (int cb = 0; cb < 4; cb += 2) silu_mul_pass(p, tacc, row0, tile_n, lane, stage, cb);
 }
 
 // Tile order: groups of G tile rows walked column by column, so the CTAs running at one

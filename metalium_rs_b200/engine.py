@@ -320,6 +320,11 @@ class CudaEngine:
         """silu(A Bg) * (A Bu) with B's gate and up columns interleaved in groups of 128 (see `interleave_gate_up`)."""
         return self._call(self._lib.b200_matmul_silu_mul, C.c_uint64(a), C.c_uint64(b))
 
+    def matmul_rope(self, a: int, b: int, cos, sin, rope_cols: int) -> Out:
+        """A B as BF16 with RoPE applied, in the product's epilogue, to the heads of 64 columns below `rope_cols`."""
+        bc, bs = _block(cos), _block(sin)
+        return self._call(self._lib.b200_matmul_rope, C.c_uint64(a), C.c_uint64(b), C.byref(bc), C.byref(bs), C.c_uint64(rope_cols))
+
     def matmul_into(self, a: int, b: int, dst_ptrs, dst_dims, col_first: int, bf16: bool = True):
         """C = A B stored from the product's epilogue into columns [col_first, ...) of every matrix in
         `dst_ptrs` (device addresses: this GPU's or, opened with `ipc_open`, a peer's)."""

@@ -16,6 +16,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Optional
 
+import os
+
 import numpy as np
 
 from . import BF16, BOOL, COLS, F32, I32, SUM, EltwiseOp, kinds
@@ -176,12 +178,16 @@ class LlamaPrefill:
                  fused_mlp=None):
         """fused_attention: None = the fused kernel where it takes the shape (whole 128-row tiles, heads
         of 64 or 128), True = require it, False = the composition (batched Q K^T, softmax, batched P V).
-        fused_mlp: True = silu(gate) * up from the gate|up product's epilogue (`matmul_silu_mul`), None or
-        False = the product then `SILU_MUL`.  The same bits either way; the two-launch form is the default
-        because it is the faster one here (the activation's exponentials on four epilogue warps a CTA take
-        longer than the tile's product: 3.91 against 3.65 ms for the 8 x 512 prefill)."""
+        fused_mlp: True = silu(gate) * up from the gate|up product's epilogue (`matmul_silu_mul`), False = the
+        product then `SILU_MUL`, None = the fused form where ff is whole groups of 128 columns.  The same bits
+        either way.  On eight epilogue warps a CTA the fused form is the faster one (8 x 512 prefill: 3.63 ms
+        against 3.80; on four warps the activation's exponentials outlasted the tile's product: 3.98)."""
         self.eng, self.cfg, self.batch, self.seq = eng, cfg, batch, seq
-        self.fused_mlp = bool(fused_mlp)
+        self.fused_mlp = (cfg.ff % 128 == 0) if fused_mlp is None else bool(fused_mlp)
+        # RoPE in the QKV projection's epilogue (`matmul_rope`, heads 64 wide) only on request (B200TT_FUSED_ROPE=1): the
+        # same bits, but this projection is ONE wave of tiles, so its epilogue hides under nothing and the rotation there
+        # (a row's table entries fetched by the row's own thread) costs more than the separate launch: 3.83 against 3.66 ms
+        self.fused_rope = cfg.head_dim == 64 and os.environ.get("B200TT_FUSED_ROPE", "0") == "1"
         if self.fused_mlp and cfg.ff % 128:
             raise ValueError("the fused gate|up product needs ff in whole groups of 128 columns")
         takes = cfg.head_dim in (64, 128)                    # any length: a tail tile is masked by index
@@ -261,13 +267,18 @@ class LlamaPrefill:
         n1, _ = e.rms_norm_as(x, self.w["l0.norm1"], c.eps, True)           # llama.rs:151-170
         for l in range(c.layers):
             lab("projection qkv")
-            qkv, _ = e.matmul_dram_bf16(n1, False, self.w[f"l{l}.qkv"], False)
-            e.free(n1)
             # RoPE on the query and key heads together: they share the head width and the tables (rope.rs:129)
             cos_b = (cache.cos, (start, 0), (t, hd)) if chunked else (self.cos, (0, 0), (t, hd))
             sin_b = (cache.sin, (start, 0), (t, hd)) if chunked else (self.sin, (0, 0), (t, hd))
-            lab("rope")
-            qk, _ = e.rope_blocks((qkv, (0, 0), (n, qk_cols)), cos_b, sin_b, hd, True)
+            if self.fused_rope:   # the rotation in the projection's own epilogue: the same bits, one launch less
+                qkv, _ = e.matmul_rope(n1, self.w[f"l{l}.qkv"], cos_b, sin_b, qk_cols)
+                e.free(n1)
+                qk = qkv          # the rotated query and key heads are the buffer's first columns
+            else:
+                qkv, _ = e.matmul_dram_bf16(n1, False, self.w[f"l{l}.qkv"], False)
+                e.free(n1)
+                lab("rope")
+                qk, _ = e.rope_blocks((qkv, (0, 0), (n, qk_cols)), cos_b, sin_b, hd, True)
             if cache is not None:
                 lab("cache write")   # the chunk's rows of the cache: keys after RoPE, values as projected
                 e.scatter_rows_into(cache.kc[l], self._cache_rows, (qk, (0, self.q_cols), (n, self.kv_cols)))
@@ -276,14 +287,19 @@ class LlamaPrefill:
             if chunked:      # keys and values where the cache holds them: positions 0 .. start + t - 1, causal at the end
                 om, _ = e.attention_blocks(qk, cache.kc[l], cache.vc[l], self._cache_items, (t, hd, start + t, hd),
                                            1.0 / float(np.sqrt(hd)), True, (n, self.q_cols))
-                e.free(qk); e.free(qkv)
+                if qk != qkv:
+                    e.free(qk)
+                e.free(qkv)
             elif self.fused:   # scores, mask, softmax, P V and the merge of heads as one kernel
                 om, _ = e.attention_blocks(qk, qk, qkv, self.fused_items, (t, hd, t, hd), 1.0 / float(np.sqrt(hd)), True,
                                            (n, self.q_cols))
-                e.free(qk); e.free(qkv)
+                if qk != qkv:
+                    e.free(qk)
+                e.free(qkv)
             else:
                 s, _ = e.matmul_dram_batched(qk, qk, self.qk_items, (t, hd, t))  # Q K^T, F32 scores
-                e.free(qk)
+                if qk != qkv:
+                    e.free(qk)
                 pb, _ = e.softmax_rows_as(s, self.mask, 1.0 / float(np.sqrt(hd)), True)   # scale, causal mask, softmax
                 e.free(s)
                 o, _ = e.matmul_dram_batched(pb, qkv, self.pv_items, (t, t, hd), bf16=True)   # P V

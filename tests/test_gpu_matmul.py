@@ -364,6 +364,34 @@ def test_the_gated_product_is_the_product_then_silu_mul_bit_for_bit(eng, mkf):  
         eng.free(i)
 
 
+@pytest.mark.parametrize("mknr", [(4096, 576, 960, 768, 512),    # the prefill's fused QKV projection: the CTA-pair kernel
+                                  (256, 576, 960, 768, 128),     # the single-CTA kernel, tiles that end inside the key heads
+                                  (384, 128, 192, 192, 384),     # every column rotated, a table row a product row
+                                  (130, 64, 320, 64, 65)])       # one head rotated, rows that are not whole tiles
+def test_the_projection_with_rope_is_the_product_then_rope_blocks_bit_for_bit(eng, mknr):   # tt-models/src/llama.rs:404-433
+    from metalium_rs_b200 import workloads as W
+    m, k, n, rope_cols, r = mknr
+    a = orc.to_bf16(orc.normal(0xC0FA, 1, (m, k), 1.0))
+    w = orc.to_bf16(orc.normal(0xC0FA, 2, (k, n), 0.2))
+    cos, sin = W.rope_tables(r, 64, 10000.0)
+    ia, iw = eng.upload_bf16(a, m, k), eng.upload_bf16(w, k, n)
+    ic, isn = eng.upload(cos, r, 64), eng.upload(sin, r, 64)
+    plain, _ = eng.matmul_dram_bf16(ia, False, iw, False)
+    rot, _ = eng.rope_blocks((plain, (0, 0), (m, rope_cols)), (ic, (0, 0), (r, 64)), (isn, (0, 0), (r, 64)), 64, True)
+    got, dims = eng.matmul_rope(ia, iw, (ic, (0, 0), (r, 64)), (isn, (0, 0), (r, 64)), rope_cols)
+    assert dims == (m, n) and eng.last_matmul_path() == ("tcgen05-pair" if m >= 4096 else "tcgen05")
+    g = eng.download_bf16(got)
+    assert np.array_equal(g[:, :rope_cols], eng.download_bf16(rot))              # the rotated heads
+    assert np.array_equal(g[:, rope_cols:], eng.download_bf16(plain)[:, rope_cols:])   # the rest as the product leaves them
+    for bad in (rope_cols + 8, n + 64):
+        with pytest.raises(TtError):
+            eng.matmul_rope(ia, iw, (ic, (0, 0), (r, 64)), (isn, (0, 0), (r, 64)), bad)
+    with pytest.raises(TtError):                                                  # a table whose rows do not divide the product's
+        eng.matmul_rope(ia, iw, (ic, (0, 0), (r - 1, 64)), (isn, (0, 0), (r - 1, 64)), rope_cols)
+    for i in (ia, iw, ic, isn, plain, rot, got):
+        eng.free(i)
+
+
 @pytest.mark.parametrize("m", [1, 2, 3, 4])
 @pytest.mark.parametrize("kn", [(576, 960), (576, 576), (576, 3072), (1536, 576), (100, 72), (5000, 8)])
 def test_a_handful_of_rows_streams_the_weights_once(eng, m, kn):
