@@ -5,17 +5,21 @@
 // a batched Q K^T, `SCALE_MASK_FILL`, the row softmax, a batched P V), whose [rows, sk] F32 scores
 // are the largest memory cost of the path.
 //
-// One CTA owns 128 query rows of one block and walks the key tiles (128 keys) twice:
-//   pass 1: S = Q K_j^T on tcgen05 into TMEM, the softmax warps read it and keep the row maximum;
-//   pass 2: S again, P = exp2(S' - max) rounded to BF16 into shared memory (the 128-byte-swizzled
-//           K-major layout the MMA reads), O += P V_j accumulated in TMEM, the row sum kept in
-//           registers; at the end O / sum is written as BF16.
-// With the final maximum known before the first product with V, O is never rescaled; Q K^T is
-// computed twice, which costs tensor-core time the kernel has to spare (the exponentials bound it).
-// Warp 0 lane 0 issues the TMA loads, warp 1 lane 0 the MMAs, warps 2-9 are the softmax: a query
-// row is a TMEM lane, and two threads share it (warps 2-5 take keys 0-63 of a tile, warps 6-9 keys
-// 64-127; they exchange their maxima after pass 1 and their sums at the end through shared memory).
-// S is double-buffered in TMEM so the next tile's product runs under this tile's exponentials.
+// One CTA owns 128 query rows of one block and walks the key tiles (128 keys) ONCE, with a running reference for
+// the softmax: S = Q K_j^T on tcgen05 into TMEM; a softmax warp reads its 32 rows (a thread a query row, all 128 keys
+// of the tile), P = exp2(S' - ref) rounded to BF16 into shared memory (the 128-byte-swizzled K-major layout the MMA
+// reads), O += P V_j accumulated in TMEM, the row sum kept in registers; at the end O / sum is written as BF16.
+// The reference is the largest scaled score seen so far, but it is only moved -- and O and the sum rescaled by
+// exp2(old - new) -- when a tile's maximum exceeds it by more than 8 (a factor 256: P then stays within BF16's and
+// the sum within F32's range), so after the first tiles O is almost never touched; the result is exact whatever the
+// reference, since O and the sum carry the same one.  (The kernel once took two passes, the first only for the row
+// maxima: Q K^T twice, 1.5x the tensor-core work of this form.)
+// Warp 0 lane 0 issues the TMA loads, warp 1 lane 0 the MMAs, warps 2-9 are the softmax: a query row is a TMEM lane,
+// a warp reads the lanes of its quadrant, and two threads share a row (keys 0-63 and 64-127 of a tile; they exchange
+// their halves' maxima through shared memory every tile and their sums at the end).  S is double-buffered in TMEM so the next tile's product runs under this
+// tile's exponentials.  The rescale of O (tcgen05.ld, multiply, tcgen05.st by the row's thread) happens between the
+// product with V of the tile before (waited for through that tile's p_empty) and the signal that lets the next one start.
+// P is double-buffered in shared memory, so a tile's exponentials run while the tile before is multiplied by V.
 // Every wait is bounded; a wait that runs out sets the engine's error word to TIMEOUT and the CTA
 // leaves in order (copies drained, TMEM freed).
 // sq and sk need not be whole tiles (the reference pads ragged heads, ops.rs:4838-4842): the last query tile's rows
@@ -38,6 +42,19 @@ constexpr uint32_t TILE_BYTES = 128 * 64 * 2;   // a [128 rows, 64 columns] BF16
 constexpr uint32_t P_BYTES = 2 * TILE_BYTES;    // [128 rows, 128 keys]
 constexpr int ATTN_THREADS = 320;               // 10 warps: TMA, MMA, 8 softmax
 constexpr int SOFTMAX_THREADS = 256;
+constexpr float REF_STEP = 8.0f;                // the reference moves when a tile's maximum exceeds it by more than this (log2 units)
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
 
 struct AttnTcParams {
   const AttnBlockDev* items;
@@ -77,7 +94,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   uint8_t* sK = sQ + OP_BYTES;
   uint8_t* sV = sK + KS * OP_BYTES;
   uint8_t* sP = sV + KS * OP_BYTES;
-  uint64_t* q_full = (uint64_t*)(sP + P_BYTES);
+  uint64_t* q_full = (uint64_t*)(sP + 2 * P_BYTES);   // P is double-buffered: a tile's probabilities are written while the tile before is multiplied
   uint64_t* k_full = q_full + 1;
   uint64_t* k_empty = k_full + KS;
   uint64_t* v_full = k_empty + KS;
@@ -85,24 +102,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   uint64_t* s_full = v_empty + KS;
   uint64_t* s_empty = s_full + 2;
   uint64_t* p_full = s_empty + 2;
-  uint64_t* p_empty = p_full + 1;
-  uint64_t* o_full = p_empty + 1;
+  uint64_t* p_empty = p_full + 2;
+  uint64_t* o_full = p_empty + 2;
   uint32_t* tmem_slot = (uint32_t*)(o_full + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  float* xmax = (float*)(sP + 2 * P_BYTES + 256);   // [2 halves][128 rows]: the halves' maxima of a tile; at the end their row sums
   long long wait_limit = WAIT_CYCLES;   // the engine's limit, read once global memory may be touched
   auto hand_off = [&](uint64_t* bar, uint32_t parity) -> bool {   // a wait on the chain S -> P -> O
     return p.spin ? mbar_wait_spin(bar, parity, abort_flag, wait_limit) : mbar_wait(bar, parity, abort_flag, wait_limit);
   };
-  float* xmax = (float*)(sP + P_BYTES + 256);   // [2][128]: the two halves' row maxima
-  float* xsum = xmax + 256;                     // [2][128]: and row sums
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < KS; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], SOFTMAX_THREADS / 32); }   // a lane a warp arrives
-    mbar_init(p_full, SOFTMAX_THREADS / 32);
-    mbar_init(p_empty, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(&p_full[b], SOFTMAX_THREADS / 32); mbar_init(&p_empty[b], 1); }
     mbar_init(o_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -143,23 +158,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
       for (int c = 0; c < CH; ++c) tma_load_2d(sQ + c * TILE_BYTES, &map_q, q_full, it.q_c + c * 64, it.q_r + i0);
       uint32_t ks = 0, kph = 0, vs = 0, vph = 0;
-      for (int pass = 0; pass < 2 && ok; ++pass) {
-        for (uint32_t j = 0; j < nk; ++j) {
-          if (!mbar_wait(&k_empty[ks], kph ^ 1, abort_flag, wait_limit)) { ok = false; break; }
-          mbar_expect_tx(&k_full[ks], OP_BYTES);
+      for (uint32_t j = 0; j < nk; ++j) {
+        if (!mbar_wait(&k_empty[ks], kph ^ 1, abort_flag, wait_limit)) { ok = false; break; }
+        mbar_expect_tx(&k_full[ks], OP_BYTES);
 #pragma unroll
-          for (int c = 0; c < CH; ++c)
-            tma_load_2d(sK + ks * OP_BYTES + c * TILE_BYTES, &map_k, &k_full[ks], it.k_c + c * 64, it.k_r + (int32_t)(j * 128));
-          if (++ks == KS) { ks = 0; kph ^= 1; }
-          if (pass == 1) {
-            if (!mbar_wait(&v_empty[vs], vph ^ 1, abort_flag, wait_limit)) { ok = false; break; }
-            mbar_expect_tx(&v_full[vs], OP_BYTES);
+        for (int c = 0; c < CH; ++c)
+          tma_load_2d(sK + ks * OP_BYTES + c * TILE_BYTES, &map_k, &k_full[ks], it.k_c + c * 64, it.k_r + (int32_t)(j * 128));
+        if (++ks == KS) { ks = 0; kph ^= 1; }
+        if (!mbar_wait(&v_empty[vs], vph ^ 1, abort_flag, wait_limit)) { ok = false; break; }
+        mbar_expect_tx(&v_full[vs], OP_BYTES);
 #pragma unroll
-            for (int c = 0; c < CH; ++c)
-              tma_load_2d(sV + vs * OP_BYTES + c * TILE_BYTES, &map_v, &v_full[vs], it.v_c + c * 64, it.v_r + (int32_t)(j * 128));
-            if (++vs == KS) { vs = 0; vph ^= 1; }
-          }
-        }
+        for (int c = 0; c < CH; ++c)
+          tma_load_2d(sV + vs * OP_BYTES + c * TILE_BYTES, &map_v, &v_full[vs], it.v_c + c * 64, it.v_r + (int32_t)(j * 128));
+        if (++vs == KS) { vs = 0; vph ^= 1; }
       }
       if (!ok) {
         atomicCAS(p.err, 0, TIMEOUT_CODE);
@@ -206,22 +217,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ++t;
         return true;
       };
-      for (uint32_t j = 0; j < nk && ok; ++j) ok = issue_qk();          // pass 1
-      if (ok) ok = issue_qk();                                           // pass 2, tile 0
+      if (ok) ok = issue_qk();                                           // tile 0's scores
       for (uint32_t j = 0; j < nk && ok; ++j) {
         if (j + 1 < nk) { ok = issue_qk(); if (!ok) break; }             // the next scores run under these exponentials
-        if (!hand_off(p_full, j & 1)) { ok = false; break; }
+        const uint32_t pb = j & 1, pph = (j >> 1) & 1;
+        if (!hand_off(&p_full[pb], pph)) { ok = false; break; }
         if (!mbar_wait(&v_full[vs], vph, abort_flag, wait_limit)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t v_addr = smem_u32(sV + vs * OP_BYTES);
 #pragma unroll
         for (int kk = 0; kk < 128 / UMMA_K; ++kk) {
-          const uint64_t adesc = make_desc(p_addr + (kk / 4) * TILE_BYTES + (kk % 4) * 32, 16, 1024);
+          const uint64_t adesc = make_desc(p_addr + pb * P_BYTES + (kk / 4) * TILE_BYTES + (kk % 4) * 32, 16, 1024);
           const uint64_t bdesc = make_desc(v_addr + kk * 2048, TILE_BYTES, 1024);   // 64-column chunks a tile apart
           umma_bf16(tmem_base + O_COL, adesc, bdesc, idesc_pv, (j | (uint32_t)kk) != 0 ? 1u : 0u);
         }
         umma_commit(&v_empty[vs]);
-        umma_commit(p_empty);
+        umma_commit(&p_empty[pb]);
         if (++vs == KS) { vs = 0; vph ^= 1; }
       }
       if (ok) umma_commit(o_full);
@@ -232,29 +243,35 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
   } else {
     // ---------------- softmax and epilogue (warps 2..9): two threads a query row ----------------
-    const uint32_t quad = warp & 3;                 // the TMEM lanes this warp may read
-    const uint32_t half = (uint32_t)(warp - 2) >> 2;  // which 64 keys of a tile, which half of O's columns
+    // A warp reads the TMEM lanes of its quadrant; warps 2-5 take keys 0-63 of a tile and the first half of O's
+    // columns, warps 6-9 keys 64-127 and the second half.  The two threads of a row exchange their halves' maxima
+    // through shared memory every tile (one named barrier), so both move the row's reference alike.
+    const uint32_t quad = warp & 3;
+    const uint32_t half = (uint32_t)(warp - 2) >> 2;
     const uint32_t row = quad * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16);
     const int32_t qi = i0 + (int32_t)row;
     const int32_t seen = p.causal ? qi + p.causal_off : 0x7fffffff;
     const int32_t last_key = seen < (int32_t)p.sk - 1 ? seen : (int32_t)p.sk - 1;   // no key past the block's
+    constexpr int OC = D / 2;                       // this thread's columns of O
     bool ok = true;
-    uint32_t t = 0;
-    float mx = -INFINITY;
-    for (uint32_t j = 0; j < nk && ok; ++j, ++t) {
-      const uint32_t buf = t & 1, sph = (t >> 1) & 1;
+    float ref = -INFINITY;                          // the row's reference: a scaled score (log2 units), -inf until a key is seen
+    float sum = 0.f;                                // this thread's keys only
+    for (uint32_t j = 0; j < nk && ok; ++j) {
+      const uint32_t buf = j & 1, sph = (j >> 1) & 1;
       if (!hand_off(&s_full[buf], sph)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int32_t key0 = (int32_t)(j * 128 + half * 64);
+      const bool edge = key0 + 63 > last_key;        // only a diagonal or tail tile needs the mask
       uint32_t v[64];
       tmem_ld32(lane_addr + buf * S_COLS + half * 64, v);
       tmem_ld32(lane_addr + buf * S_COLS + half * 64 + 32, v + 32);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[buf]);   // one arrival a warp: 256 arrivals on one barrier serialise
-      if (key0 + 63 > last_key) {                    // only the diagonal tile needs the mask
+      if (lane == 0) mbar_arrive(&s_empty[buf]);     // one arrival a warp: the scores are in registers
+      float mx = -INFINITY;
+      if (edge) {
 #pragma unroll
         for (int e = 0; e < 64; ++e)
           if (key0 + e <= last_key) mx = fmaxf(mx, __uint_as_float(v[e]));
@@ -262,27 +279,34 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
         for (int e = 0; e < 64; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
       }
-    }
-    xmax[half * 128 + row] = mx;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    mx = fmaxf(xmax[row], xmax[128 + row]);
-    // the maximum of the scaled scores (scale > 0 keeps the order); a row with no key sees 0
-    const float m2 = (mx == -INFINITY) ? 0.f : mx * p.scale_log2;
-    float sum = 0.f;
-    for (uint32_t j = 0; j < nk && ok; ++j, ++t) {
-      const uint32_t buf = t & 1, sph = (t >> 1) & 1;
-      if (!hand_off(&s_full[buf], sph)) { ok = false; break; }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int32_t key0 = (int32_t)(j * 128 + half * 64);
-      uint32_t v[64];
-      tmem_ld32(lane_addr + buf * S_COLS + half * 64, v);
-      tmem_ld32(lane_addr + buf * S_COLS + half * 64 + 32, v + 32);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[buf]);   // one arrival a warp: 256 arrivals on one barrier serialise
+      xmax[half * 128 + row] = mx;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      mx = fmaxf(xmax[row], xmax[128 + row]);
+      asm volatile("bar.sync 1, 256;" ::: "memory");   // every thread has read before the next tile (or the sums) overwrite
+      // move the reference only when the tile exceeds it by more than REF_STEP (always at the row's first key)
+      const float t2 = mx * p.scale_log2;            // scale > 0 keeps the order; -inf when the tile holds no key of this row
+      const bool grow = t2 > ref + REF_STEP;         // (-inf + 8 is -inf: the first key always moves it)
+      const float alpha = grow ? ex2(ref - t2) : 1.0f;   // 0 when ref was -inf
+      if (grow) ref = t2;
+      const float m2 = (ref == -INFINITY) ? 0.f : ref;
+      const uint32_t pb = j & 1, pph = (j >> 1) & 1;
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {  // the whole warp takes the (warp-wide) loads and stores; a row that did not move multiplies by 1
+        // O is being accumulated: the product with V of the tile before must be done (its commit on that tile's p_empty)
+        if (!hand_off(&p_empty[pb ^ 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+        for (int cb = 0; cb < OC / 32; ++cb) {
+          uint32_t o[32];
+          tmem_ld32(lane_addr + O_COL + half * OC + cb * 32, o);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+          tmem_st32(lane_addr + O_COL + half * OC + cb * 32, o);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      }
       uint32_t pk[32];
-      const bool edge = key0 + 63 > last_key;
       float s0 = 0.f, s1 = 0.f;
 #pragma unroll
       for (int e = 0; e < 64; e += 2) {
@@ -296,27 +320,26 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         s1 += b;
         pk[e / 2] = pack_bf16(a, b);
       }
-      sum += s0 + s1;
-      // P is single-buffered: the product with V of the tile before must have read it
-      if (!hand_off(p_empty, (j & 1) ^ 1)) { ok = false; break; }
-      uint8_t* prow = sP + half * TILE_BYTES + row * 128;
+      sum = fmaf(sum, alpha, s0 + s1);
+      // this tile's P buffer: the product with V of the tile two before must have read it
+      if (!hand_off(&p_empty[pb], pph ^ 1)) { ok = false; break; }
+      uint8_t* prow = sP + pb * P_BYTES + half * TILE_BYTES + row * 128;
 #pragma unroll
       for (int u = 0; u < 8; ++u)
         *reinterpret_cast<uint4*>(prow + ((u ^ (row & 7)) << 4)) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes, read by the MMA
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(&p_full[pb]);
     }
-    xsum[half * 128 + row] = sum;
+    xmax[half * 128 + row] = sum;
     asm volatile("bar.sync 1, 256;" ::: "memory");
-    sum = xsum[row] + xsum[128 + row];
+    sum = xmax[row] + xmax[128 + row];
     if (ok && !mbar_wait(o_full, 0, abort_flag, wait_limit)) ok = false;
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool stored = qi < (int32_t)p.sq;          // a row past the block's queries is read with its warp (the
                                                        // tensor-memory loads are warp-wide) and not stored
       const float inv = 1.0f / ((sum < FLT_MIN) ? FLT_MIN : sum);
-      constexpr int OC = D / 2;                      // this thread's columns of O
       uint16_t* dst = p.out + it.o_off + (uint64_t)(i0 + (int32_t)row) * p.o_ld + half * OC;
 #pragma unroll
       for (int cb = 0; cb < OC / 32; ++cb) {
@@ -353,7 +376,7 @@ template <int D>
 cudaError_t launch_d(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p,
                      uint64_t n_items, cudaStream_t stream) {
   constexpr int CH = D / 64, KS = D == 64 ? 3 : 2;
-  constexpr size_t smem = (size_t)(1 + 2 * KS) * CH * TILE_BYTES + P_BYTES + 256 + 2048 + 1024;
+  constexpr size_t smem = (size_t)(1 + 2 * KS) * CH * TILE_BYTES + 2 * P_BYTES + 256 + 1024 + 1024;
   {
     const cudaError_t e = ensure_dynamic_smem((const void*)attention_tc_kernel<D>, smem);
     if (e != cudaSuccess) return e;
