@@ -655,10 +655,11 @@ __global__ void __launch_bounds__(DT, 1) decode_layers_kernel(const DecodeParams
 //
 // With so few blocks the step is bound by how many bytes of weights a block keeps in flight, so the weights do not wait
 // for the phase that uses them: the tiles a block will multiply by are known from the start (layer after layer, phase
-// after phase, item after item), and a ring of shared-memory slots is kept full of the next chunks of 192 k-rows by
-// TMA (one tiled copy of 192 rows by 64 columns a chunk, completing on the slot's mbarrier), across phases and cluster
+// after phase, item after item), and a ring of shared-memory slots is kept full of the next chunks by TMA (tiled copies
+// of 192 k-rows by 64 columns -- one a chunk, or three for one sequence, where a chunk is a whole 576-row item --
+// completing on the slot's mbarrier), across phases and cluster
 // barriers: loads issued by threads keep some 16 KB a block in flight, far too little for sixteen blocks to draw the
-// device's bandwidth, where the ring holds up to 120 KB a block.  A product waits for its next chunk, multiplies from
+// device's bandwidth, where the ring holds up to 144 KB a block.  A product waits for its next chunk, multiplies from
 // shared memory with tensor-core tiles (`mma.sync`: a warp owns 8 of the item's 64 columns), and refills the slot with
 // the chunk that is R chunks ahead.  The form takes BF16 matrices only.
 namespace cg = cooperative_groups;
@@ -678,11 +679,16 @@ struct ClusterParams {
   const CUtensorMap* maps;   // [n_layers][4]: qkv, o, gate|up, down as [k, n] with a box of 64 rows by 64 columns
 };
 
-constexpr int CK_ROWS = 192;                           // k-rows of a chunk: a wait, a barrier and an issue cost some 300 cycles a chunk whatever its size
+constexpr int CK_ROWS = 192;                           // k-rows of a tiled copy's box (at most 256)
 constexpr int GN = 4;                                  // gains a thread fetches ahead: the cluster form takes hidden <= GN * 256
-constexpr uint32_t SLOT_BYTES = CK_ROWS * 128;         // rows of 64 BF16, 128-byte swizzled as the copy writes them
-static_assert(SLOT_BYTES % 1024 == 0 && CK_ROWS % 32 == 0 && CK_ROWS <= 256, "a swizzled slot starts on 1,024 bytes; a box has at most 256 rows");
-template <int MT> struct RingDepth { static constexpr int value = MT == 1 ? 5 : (MT == 2 ? 4 : 2); };
+constexpr uint32_t BOX_BYTES = CK_ROWS * 128;          // rows of 64 BF16, 128-byte swizzled as the copy writes them
+static_assert(BOX_BYTES % 1024 == 0 && CK_ROWS % 32 == 0 && CK_ROWS <= 256, "a swizzled box starts on 1,024 bytes and has at most 256 rows");
+// A chunk -- what one wait, one block barrier and one issue move -- is up to NB boxes on one mbarrier: a wait, a barrier and
+// an issue cost some 500 cycles a chunk whatever its size, so one sequence (whose other buffers are small) takes a whole
+// 576-row item as one chunk in a ring of two; the wider steps keep single boxes.
+template <int MT> struct ChunkBoxes { static constexpr int value = MT == 1 ? 3 : 1; };
+template <int MT> struct RingDepth { static constexpr int value = MT == 1 ? 2 : (MT == 2 ? 4 : 2); };
+inline uint32_t chunk_rows_of(uint32_t mt) { return (mt == 1 ? 3u : 1u) * CK_ROWS; }
 
 // The chunks of weights a block multiplies by during ONE layer, in the order it uses them: the same list for every layer,
 // so it is written once (by one thread, into shared memory) and the step's issue path only reads it.
@@ -693,9 +699,10 @@ struct WeightWalk {
   const ClusterParams* p;
   const ChunkEnt* tab;
   uint32_t cnt, ii, il;                                // the list's length; the next chunk to issue: entry ii of layer il
+  uint32_t slot_bytes;
   // thread 0 writes the list; every thread calls this, the caller's __syncthreads publishes it
-  __device__ void start(const ClusterParams* pp, ChunkEnt* tab_, uint32_t* cnt_sm, uint32_t me, uint32_t C) {
-    p = pp; tab = tab_; ii = 0; il = 0;
+  __device__ void start(const ClusterParams* pp, ChunkEnt* tab_, uint32_t* cnt_sm, uint32_t me, uint32_t C, uint32_t chunk_rows) {
+    p = pp; tab = tab_; ii = 0; il = 0; slot_bytes = chunk_rows * 128;
     if (threadIdx.x == 0) {
       const uint32_t H = pp->hidden, QC = pp->heads * HD, NQKV = QC + 2 * pp->kv_heads * HD, FF = pp->ff, nb_h = H / DCOLS;
       uint32_t c = 0;
@@ -705,8 +712,8 @@ struct WeightWalk {
           const uint32_t kbase = ph == 3 ? (item / nb_h) * pp->sl_dn : 0;
           const uint32_t total = ph == 0 || ph == 2 ? H : (ph == 1 ? QC : (kbase + pp->sl_dn <= FF ? pp->sl_dn : FF - kbase));
           const uint32_t cb = ph == 3 ? item % nb_h : item;
-          for (uint32_t k = 0; k < total && c < SCHED_MAX; k += CK_ROWS)
-            tab_[c++] = ChunkEnt{(uint16_t)ph, (uint16_t)(total - k < (uint32_t)CK_ROWS ? total - k : CK_ROWS), (uint16_t)cb, (uint16_t)(kbase + k)};
+          for (uint32_t k = 0; k < total && c < SCHED_MAX; k += chunk_rows)
+            tab_[c++] = ChunkEnt{(uint16_t)ph, (uint16_t)(total - k < chunk_rows ? total - k : chunk_rows), (uint16_t)cb, (uint16_t)(kbase + k)};
         }
       }
       *cnt_sm = c;
@@ -717,8 +724,10 @@ struct WeightWalk {
     if (il < p->n_layers) {
       if (threadIdx.x == 0) {
         const ChunkEnt e = tab[ii];
-        tc::mbar_expect_tx(bar, SLOT_BYTES);           // the whole box counts, rows past the matrix filled with zeros
-        tc::tma_load_2d(slot, p->maps + (size_t)il * 4 + e.phase, bar, (int32_t)e.cb * DCOLS, (int32_t)e.k0);
+        const uint32_t boxes = ((uint32_t)e.rows + CK_ROWS - 1) / CK_ROWS;
+        tc::mbar_expect_tx(bar, boxes * BOX_BYTES);    // whole boxes count, rows past the matrix filled with zeros
+        for (uint32_t b = 0; b < boxes; ++b)
+          tc::tma_load_2d(slot + (size_t)b * BOX_BYTES, p->maps + (size_t)il * 4 + e.phase, bar, (int32_t)e.cb * DCOLS, (int32_t)(e.k0 + b * CK_ROWS));
       }
       if (++ii == cnt) { ii = 0; ++il; }
     }
@@ -737,7 +746,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// One product item fed from the ring: `len` k-rows in chunks of CK_ROWS, A's rows as BF16 in shared memory (pitch lda
+// One product item fed from the ring: `len` k-rows in chunks of up to ChunkBoxes<MT> boxes of CK_ROWS, A's rows as BF16 in shared memory (pitch lda
 // elements, offset to the item's first k-row).  The eight warps split the item's 64 columns: a warp owns 8 of them and all of
 // k, so its accumulator (one m16n8 tile of `mma.sync`, rows past MT fed zeros) is the item's result for those columns and
 // no sum crosses warps.  B comes from the slot by `ldmatrix.trans` (the slot is [k][64 columns], 128-byte swizzled as the
@@ -750,15 +759,20 @@ __device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   float c[4][4] = {};
   const uint16_t* arow = a + (size_t)(g < MT ? g : 0) * lda;
-  for (uint32_t base = 0; base < len; base += CK_ROWS) {
+  constexpr uint32_t CHUNK_ROWS = ChunkBoxes<MT>::value * CK_ROWS, SLOT_BYTES = ChunkBoxes<MT>::value * BOX_BYTES;
+  for (uint32_t cbase = 0; cbase < len; cbase += CHUNK_ROWS) {
     // the oldest of the R chunks in flight: its tile has landed when the slot's mbarrier flips
     if (!dead && !tc::mbar_wait(&bars[head], (parity >> head) & 1u, &dead_flag_of(err), limit)) {
       dead = true;                                     // recorded; the block walks on without waiting, so that the cluster's barriers are still met
       atomicCAS(err, 0, TIMEOUT_CODE);
     }
     parity ^= 1u << head;
-    const uint32_t slot = tc::smem_u32(ring + (size_t)head * SLOT_BYTES);
-    // every load of the chunk first (six loads of four 8x8 matrices, the A columns beside them), then twelve MMAs into
+    const uint32_t boxes = len - cbase < CHUNK_ROWS ? (len - cbase + CK_ROWS - 1) / CK_ROWS : ChunkBoxes<MT>::value;
+#pragma unroll 1
+    for (uint32_t bx = 0; bx < boxes; ++bx) {
+    const uint32_t base = cbase + bx * CK_ROWS;
+    const uint32_t slot = tc::smem_u32(ring + (size_t)head * SLOT_BYTES + (size_t)bx * BOX_BYTES);
+    // every load of the box first (six loads of four 8x8 matrices, the A columns beside them), then twelve MMAs into
     // four accumulators in turn: one accumulator would chain the twelve, ~35 cycles each
     uint32_t bq[CK_ROWS / 32][4], aq[CK_ROWS / 32][4];
 #pragma unroll
@@ -774,6 +788,7 @@ __device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, 
     for (int i = 0; i < CK_ROWS / 32; ++i) {
       mma_bf16_16816(c[(2 * i) & 3], aq[i][0], 0u, aq[i][1], 0u, bq[i][0], bq[i][1]);
       mma_bf16_16816(c[(2 * i + 1) & 3], aq[i][2], 0u, aq[i][3], 0u, bq[i][2], bq[i][3]);
+    }
     }
     __syncthreads();                                   // every warp is done with the slot: refill it
     walk.issue(ring + (size_t)head * SLOT_BYTES, &bars[head]);
@@ -801,6 +816,7 @@ __device__ __forceinline__ void send_to_all(cg::cluster_group& cluster, uint32_t
 template <int MT>
 __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterParams p) {
   constexpr int R = RingDepth<MT>::value;
+  constexpr uint32_t SLOT_BYTES = ChunkBoxes<MT>::value * BOX_BYTES;
   extern __shared__ __align__(16) float smem[];
   cg::cluster_group cluster = cg::this_cluster();
   const uint32_t C = cluster.num_blocks(), me = cluster.block_rank();
@@ -844,7 +860,7 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
     reinterpret_cast<uint64_t*>(lay)[i] = reinterpret_cast<const uint64_t*>(p.layers)[i];
   if (tid < HD) { cs[tid] = p.cos[(size_t)pos * HD + tid]; sn[tid] = p.sin[(size_t)pos * HD + tid]; }
   WeightWalk walk;
-  walk.start(&p, tab, tab_len, me, C);
+  walk.start(&p, tab, tab_len, me, C, ChunkBoxes<MT>::value * CK_ROWS);
   __syncthreads();
   walk.cnt = *tab_len;
   for (uint32_t c = tid; c < H; c += DT) g1[c] = bf16_at(lay[0].norm1, c);
@@ -1195,7 +1211,9 @@ bool cluster_plan(const DecodeShape& sh, ClusterParams& c, size_t* smem) {
   const uint32_t QCc = sh.heads * HD, NQ = QCc + 2 * sh.kv_heads * HD, att_items = sh.rows * sh.kv_heads * (sh.attend / DCH);
   c.n_layers = sh.layers; c.rows = sh.rows; c.hidden = sh.hidden; c.heads = sh.heads; c.kv_heads = sh.kv_heads; c.ff = sh.ff;
   c.max_len = sh.max_len; c.attend = sh.attend; c.eps = sh.eps; c.scale = sh.scale;
-  c.ks_dn = (sh.ff + 767) / 768;                       // slices of about 768 rows: eighteen items for SmolLM2's down projection
+  // the down projection's k in slices of about a chunk's rows (one sequence: 576, three slices and 27 items for SmolLM2-135M; else 768)
+  const uint32_t want_rows = MTc == 1 ? 576u : 768u;
+  c.ks_dn = (sh.ff + want_rows - 1) / want_rows;
   if (c.ks_dn < 1) c.ks_dn = 1;
   c.sl_dn = ((sh.ff + c.ks_dn - 1) / c.ks_dn + 31) / 32 * 32;
   c.ks_dn = (sh.ff + c.sl_dn - 1) / c.sl_dn;
@@ -1205,6 +1223,8 @@ bool cluster_plan(const DecodeShape& sh, ClusterParams& c, size_t* smem) {
   c.vec_cols = vc;
   c.att_items = att_items;
   const size_t ring_slots = MTc == 1 ? RingDepth<1>::value : (MTc == 2 ? RingDepth<2>::value : RingDepth<4>::value);
+  const uint32_t chunk_rows = chunk_rows_of(MTc);
+  const size_t SLOT_BYTES = (size_t)chunk_rows * 128;
   const size_t stage = (size_t)MTc * DCOLS > 4 * (HD + 4) ? (size_t)MTc * DCOLS : 4 * (HD + 4);
   *smem = 1024 + ring_slots * SLOT_BYTES + 16 * sizeof(uint64_t) + 2 * DCH * 8 * sizeof(uint4) +
           ((size_t)MTc * sh.hidden * 2 + (size_t)MTc * NQ + (size_t)att_items * 4 * (HD + 4) +
@@ -1212,7 +1232,7 @@ bool cluster_plan(const DecodeShape& sh, ClusterParams& c, size_t* smem) {
           (size_t)sh.layers * sizeof(DecodeLayerDev) + SCHED_MAX * sizeof(ChunkEnt) + 8 + 16 +
           ((size_t)MTc * 2 * sh.ff + (size_t)MTc * vc) * sizeof(uint16_t);
   // the longest list of chunks a block of an eight-block cluster walks in a layer (block 0's)
-  auto chunks_of = [&](uint32_t items, uint32_t rows) { return (uint64_t)((items + 7) / 8) * ((rows + CK_ROWS - 1) / CK_ROWS); };
+  auto chunks_of = [&](uint32_t items, uint32_t rows) { return (uint64_t)((items + 7) / 8) * ((rows + chunk_rows - 1) / chunk_rows); };
   const uint64_t sched = chunks_of(NQ / DCOLS, sh.hidden) + chunks_of(sh.hidden / DCOLS, QCc) + chunks_of(2 * sh.ff / DCOLS, sh.hidden) +
                          chunks_of(sh.hidden / DCOLS * c.ks_dn, c.sl_dn);
   return *smem <= 224 * 1024 && sh.hidden <= (uint32_t)GN * DT && sched <= SCHED_MAX && sh.ff < 65536 && 2 * sh.ff / DCOLS < 65536;
