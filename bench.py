@@ -593,6 +593,9 @@ def rest_of_trait(eng, timed, hbm):
     one("scan_sum_8192x8192", lambda: eng.scan(x, E.SCAN_SUM)[0], 2 * nb)
     one("scan_min_nan_8192x8192", lambda: eng.scan(x, E.SCAN_MIN_NAN)[0], 2 * nb)
     one("cast_f16_narrow_8192x8192", lambda: eng.cast_f16(x, True)[0], nb * 3 // 2)
+    h16, _ = eng.cast_f16(x, True)
+    one("cast_f16_widen_8192x8192", lambda: eng.cast_f16(h16, False)[0], nb * 3 // 2)
+    eng.free(h16)
     one("cast_block_4096x4096", lambda: eng.cast_block((x, (1024, 2048), (4096, 4096)), True)[0], 4096 * 4096 * 6)
     one("random_unit_8192x8192", lambda: eng.random_dram((n, n), ("unit",), 1)[0], nb)
     one("random_normal_8192x8192", lambda: eng.random_dram((n, n), ("normal", 0.0, 1.0, False), 1)[0], nb)
