@@ -104,6 +104,35 @@ def test_heads_whose_lengths_are_not_whole_tiles(eng, blocks, sq, sk, d, causal)
         eng.free(i)
 
 
+@pytest.mark.parametrize("d,causal", [(64, False), (128, False), (64, True)])
+def test_scores_that_keep_growing_along_the_keys(eng, d, causal):
+    # The kernel walks the keys once with a running reference that it moves -- rescaling the accumulated result and the
+    # sum -- only when a tile's scores exceed it by 2^8.  Random scores move it in the first tiles only; here the scores
+    # of a row grow steadily with the key's position (to ~170 in log2 units: some twenty moves, in every tile for the
+    # steepest rows), and shrink again in the second block, where the reference must stay.
+    sq, sk = 256, 1024
+    rng = np.random.default_rng(0xF1E)
+    e = np.full(d, 1.0 / np.sqrt(d))
+    steep = rng.uniform(0.05, 1.5, (sq, 1))
+    q = orc.to_bf16((np.sqrt(d) * steep * e + 0.05 * rng.standard_normal((sq, d))).astype(np.float32))
+    ramp = np.linspace(0.0, 1.0, sk)[:, None]
+    k_up = (80.0 * ramp * e + 0.05 * rng.standard_normal((sk, d))).astype(np.float32)
+    k_down = (80.0 * (1.0 - ramp) * e + 0.05 * rng.standard_normal((sk, d))).astype(np.float32)
+    k = orc.to_bf16(np.concatenate([k_up, k_down]))
+    v = orc.to_bf16(orc.normal(0xF1E, 3, (2 * sk, d)))
+    qf, kf, vf = orc.from_bf16(q), orc.from_bf16(k), orc.from_bf16(v)
+    iq, ik, iv = eng.upload_bf16(q, sq, d), eng.upload_bf16(k, 2 * sk, d), eng.upload_bf16(v, 2 * sk, d)
+    items = [((0, 0), (0, 0), (0, 0), (0, 0)), ((0, 0), (sk, 0), (sk, 0), (sq, 0))]
+    scale = 1.0 / np.sqrt(d)
+    out, _ = eng.attention_blocks(iq, ik, iv, items, [sq, d, sk, d], scale, causal, [2 * sq, d])
+    got = orc.from_bf16(eng.download_bf16(out))
+    for b in range(2):
+        want, bound = _want(qf, kf[b * sk:(b + 1) * sk], vf[b * sk:(b + 1) * sk], scale, causal)
+        _check(got[b * sq:(b + 1) * sq], want, bound)
+    for i in (iq, ik, iv, out):
+        eng.free(i)
+
+
 def test_uncovered_result_elements_are_zero(eng):
     s, d = 128, 64
     x = orc.to_bf16(orc.normal(0xF1C, 1, (s, 3 * d)))
