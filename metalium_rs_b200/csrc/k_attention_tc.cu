@@ -270,15 +270,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[buf]);     // one arrival a warp: the scores are in registers
-      float mx = -INFINITY;
-      if (edge) {
+      if (edge) {                                    // a key this row does not see scores -inf: no maximum, and exp2 makes it 0
 #pragma unroll
         for (int e = 0; e < 64; ++e)
-          if (key0 + e <= last_key) mx = fmaxf(mx, __uint_as_float(v[e]));
-      } else {
-#pragma unroll
-        for (int e = 0; e < 64; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+          if (key0 + e > last_key) v[e] = 0xff800000u;
       }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;   // four chains instead of one of 64
+#pragma unroll
+      for (int e = 0; e < 64; e += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(v[e]));
+        mx1 = fmaxf(mx1, __uint_as_float(v[e + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(v[e + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(v[e + 3]));
+      }
+      float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       xmax[half * 128 + row] = mx;
       asm volatile("bar.sync 1, 256;" ::: "memory");
       mx = fmaxf(xmax[row], xmax[128 + row]);
@@ -310,12 +315,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       float s0 = 0.f, s1 = 0.f;
 #pragma unroll
       for (int e = 0; e < 64; e += 2) {
-        float a = ex2(fmaf(__uint_as_float(v[e]), p.scale_log2, -m2));
-        float b = ex2(fmaf(__uint_as_float(v[e + 1]), p.scale_log2, -m2));
-        if (edge) {
-          if (key0 + e > last_key) a = 0.f;
-          if (key0 + e + 1 > last_key) b = 0.f;
-        }
+        const float a = ex2(fmaf(__uint_as_float(v[e]), p.scale_log2, -m2));
+        const float b = ex2(fmaf(__uint_as_float(v[e + 1]), p.scale_log2, -m2));
         s0 += a;
         s1 += b;
         pk[e / 2] = pack_bf16(a, b);
