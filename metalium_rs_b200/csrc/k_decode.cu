@@ -279,21 +279,28 @@ __device__ __forceinline__ void norm_rows(const float* x, uint32_t cols, const v
   __syncthreads();
 }
 
-// The same with the gains already in shared memory as F32 (exact: they are BF16 values), the result stored as BF16 bits.
+// The same with the gains already in shared memory as F32 (exact: they are BF16 values), the result stored as BF16 bits,
+// and the rows taken side by side: 8 / MT warps a row, a warp's partial sum of squares in `scratch`, a row's partials added
+// in warp order by every thread of the row -- two block barriers whatever MT (a row after the other cost two each).
 template <int MT>
 __device__ __forceinline__ void norm_rows_sm(const float* x, uint32_t cols, const float* gains, float eps, uint16_t* vec, uint32_t vec_pitch,
                                              float* scratch) {
-  const float inv_n = 1.0f / (float)cols;
-  for (int r = 0; r < MT; ++r) {
-    float ss = 0.f;
-    for (uint32_t c = threadIdx.x; c < cols; c += DT) ss = fmaf(x[(size_t)r * cols + c], x[(size_t)r * cols + c], ss);
-    const float total = block_sum(ss, scratch);
-    const float stat = sqrtf(__fadd_rn(__fmul_rn(total, inv_n), eps));
-    for (uint32_t c = threadIdx.x; c < cols; c += DT) {
-      const float t = __fdiv_rn(x[(size_t)r * cols + c], stat);
-      vec[(size_t)r * vec_pitch + c] = f32_to_bf16_bits(__float_as_uint(__fmul_rn(t, gains[c])));
-    }
-  }
+  constexpr int W = (DT / 32) / MT;                    // warps a row
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = warp / W, sub = warp - r * W;
+  const float* xr = x + (size_t)r * cols;
+  float ss = 0.f;
+  for (uint32_t c = sub * 32 + lane; c < cols; c += W * 32) ss = fmaf(xr[c], xr[c], ss);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  __syncthreads();                                     // `scratch` is free
+  if (lane == 0) scratch[warp] = ss;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int w = 0; w < W; ++w) total += scratch[r * W + w];
+  const float stat = sqrtf(__fadd_rn(__fmul_rn(total, 1.0f / (float)cols), eps));
+  for (uint32_t c = sub * 32 + lane; c < cols; c += W * 32)
+    vec[(size_t)r * vec_pitch + c] = f32_to_bf16_bits(__float_as_uint(__fmul_rn(__fdiv_rn(xr[c], stat), gains[c])));
   __syncthreads();
 }
 
