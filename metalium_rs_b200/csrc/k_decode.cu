@@ -1013,21 +1013,32 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
     cluster.sync();
 
     // ---- phase 3 ----
+    // a (row, head)'s chunk weights exp(m_c - M) and its sum, once (a thread a pair), in the down projection's idle buffer;
+    // then every output element is four multiply-adds and a division instead of eight exponentials
+    float* mw = dn;                                    // [MT * heads][chunks + 1]
+    for (uint32_t i = tid; i < (uint32_t)MT * p.heads; i += DT) {
+      const uint32_t r = i / p.heads, h = i - r * p.heads, kvh = h / group, g = h - kvh * group;
+      const float* base = att + (size_t)((r * p.kv_heads + kvh) * chunks) * AP + g * APH;
+      float M = -3.402823466e38f;
+      for (uint32_t c2 = 0; c2 < chunks; ++c2) M = fmaxf(M, base[(size_t)c2 * AP + HD]);
+      float Lsum = 0.f;
+      for (uint32_t c2 = 0; c2 < chunks; ++c2) {
+        const float wgt = expf(base[(size_t)c2 * AP + HD] - M);
+        mw[(size_t)i * (chunks + 1) + c2] = wgt;
+        Lsum = fmaf(base[(size_t)c2 * AP + HD + 1], wgt, Lsum);
+      }
+      mw[(size_t)i * (chunks + 1) + chunks] = fmaxf(Lsum, 1.175494351e-38f);
+    }
+    __syncthreads();
     for (uint32_t i = tid; i < (uint32_t)MT * QC; i += DT) {
       const uint32_t r = i / QC, c = i - r * QC, h = c / HD, d = c - h * HD, kvh = h / group, g = h - kvh * group;
       float v = 0.f;
       if (r < p.rows) {
         const float* base = att + (size_t)((r * p.kv_heads + kvh) * chunks) * AP + g * APH;
-        float M = -3.402823466e38f;
-        for (uint32_t c2 = 0; c2 < chunks; ++c2) M = fmaxf(M, base[(size_t)c2 * AP + HD]);
-        float Lsum = 0.f, O = 0.f;
-        for (uint32_t c2 = 0; c2 < chunks; ++c2) {
-          const float* q = base + (size_t)c2 * AP;
-          const float wgt = expf(q[HD] - M);
-          Lsum = fmaf(q[HD + 1], wgt, Lsum);
-          O = fmaf(q[d], wgt, O);
-        }
-        v = __fdiv_rn(O, fmaxf(Lsum, 1.175494351e-38f));
+        const float* w = mw + (size_t)(r * p.heads + h) * (chunks + 1);
+        float O = 0.f;
+        for (uint32_t c2 = 0; c2 < chunks; ++c2) O = fmaf(base[(size_t)c2 * AP + d], w[c2], O);
+        v = __fdiv_rn(O, w[chunks]);
       }
       vec[(size_t)r * p.vec_cols + c] = f32_to_bf16_bits(__float_as_uint(v));
     }
@@ -1242,7 +1253,9 @@ bool cluster_plan(const DecodeShape& sh, ClusterParams& c, size_t* smem) {
   auto chunks_of = [&](uint32_t items, uint32_t rows) { return (uint64_t)((items + 7) / 8) * ((rows + chunk_rows - 1) / chunk_rows); };
   const uint64_t sched = chunks_of(NQ / DCOLS, sh.hidden) + chunks_of(sh.hidden / DCOLS, QCc) + chunks_of(2 * sh.ff / DCOLS, sh.hidden) +
                          chunks_of(sh.hidden / DCOLS * c.ks_dn, c.sl_dn);
-  return *smem <= 224 * 1024 && sh.hidden <= (uint32_t)GN * DT && sched <= SCHED_MAX && sh.ff < 65536 && 2 * sh.ff / DCOLS < 65536;
+  const uint64_t merge_words = (uint64_t)sh.heads * (sh.attend / DCH + 1);   // a row's chunk weights wait in the down projection's buffer
+  return *smem <= 224 * 1024 && sh.hidden <= (uint32_t)GN * DT && sched <= SCHED_MAX && sh.ff < 65536 && 2 * sh.ff / DCOLS < 65536 &&
+         merge_words <= (uint64_t)c.ks_dn * sh.hidden;
 }
 }  // namespace
 
