@@ -260,6 +260,34 @@ def bf16_value(bits):
     return (np.asarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
 
 
+def sustained_leg(eng, a_ptr, b_ptr, n, flops, ms_guess):
+    """The same product for about a second and a half, clocks sampled throughout: under the 1 kW cap the SM clock
+    settles well below its maximum, and ms x MHz says whether the rate follows the clock (the kernel's tensor pipe is
+    busy 91 % of the elapsed cycles in the ncu capture, whatever the clock).  Run last, so that the legs timed before it
+    do not start on a GPU it has just heated."""
+    ia = eng.upload_ptr(a_ptr, n, n, 3)
+    ib = eng.upload_ptr(b_ptr, n, n, 3)
+
+    def step():
+        out, _ = eng.matmul_dram_bf16(ia, False, ib, False)
+        eng.free(out)
+    for _ in range(3):
+        step()
+    eng.sync()
+    k_sus = int(1500.0 / ms_guess)
+    s2 = ClockSampler(0)
+    eng.timer_start()
+    for _ in range(k_sus):
+        step()
+    sus_ms = eng.timer_stop() / k_sus
+    c2 = s2.stop()
+    eng.free(ia); eng.free(ib)
+    return {"steps": k_sus, "ms_per_step": sus_ms, "tflops": flops / (sus_ms * 1e-3) / 1e12, "clocks": c2,
+            "ms_x_mhz": sus_ms * c2["sm_mhz"] if c2.get("sm_mhz") else None,
+            "implied_sm_mhz_at_0.914_tensor_pipe": flops / (sus_ms * 1e-3) / (0.914 * 148 * 8192) / 1e6,
+            "path": eng.last_matmul_path()}
+
+
 def run_single(args):
     import torch
     from metalium_rs_b200 import CudaEngine, build
@@ -301,22 +329,6 @@ def run_single(args):
             step()
         rep.append(eng.timer_stop() / args.steps)
     rep.sort()
-
-    # the same product for about a second and a half, clocks sampled throughout: under the 1 kW cap the SM clock
-    # settles well below its maximum, and ms x MHz says whether the rate follows the clock (the kernel's tensor pipe
-    # is busy 91 % of the elapsed cycles in the ncu capture, whatever the clock)
-    sustained = None
-    if n == N1_SIZE and not args.no_e2e:
-        k_sus = int(1500.0 / ms_per_step)
-        s2 = ClockSampler(0)
-        eng.timer_start()
-        for _ in range(k_sus):
-            step()
-        sus_ms = eng.timer_stop() / k_sus
-        c2 = s2.stop()
-        sustained = {"steps": k_sus, "ms_per_step": sus_ms, "tflops": flops / (sus_ms * 1e-3) / 1e12, "clocks": c2,
-                     "ms_x_mhz": sus_ms * c2["sm_mhz"] if c2.get("sm_mhz") else None,
-                     "implied_sm_mhz_at_0.914_tensor_pipe": flops / (sus_ms * 1e-3) / (0.914 * 148 * 8192) / 1e6}
 
     # validity: the BF16 result of the very call the loop times, 64 sampled elements against F64 dot products --
     # within one BF16 step of the truth plus the F32 sum's rounding
@@ -383,11 +395,6 @@ def run_single(args):
             "repeats": {"n": REPEATS, "steps_each": args.steps, "median_ms_per_step": rep[len(rep) // 2], "min_ms_per_step": rep[0],
                         "max_ms_per_step": rep[-1], "median_tflops": flops / (rep[len(rep) // 2] * 1e-3) / 1e12},
             "validated": {"samples": 64, "max_err_over_S": worst, "what": "the BF16 result of the timed call"}}
-    if sustained:
-        pk_s = float(pk.get("bf16_tflops_sustained", 0) or 0)
-        sustained["frac_of_measured_sustained"] = sustained["tflops"] / pk_s if pk_s else None
-        sustained["burst_implied_sm_mhz_at_0.914_tensor_pipe"] = value * 1e12 / (0.914 * 148 * 8192) / 1e6
-        line["sustained"] = sustained
     eng.close()
     from metalium_rs_b200 import CudaEngine as _E
     with _E(0) as auto_eng:  # automatic path choice: small and ragged products take the SIMT kernel
@@ -398,6 +405,12 @@ def run_single(args):
             line["prefill"] = prefill_leg(auto_eng, timed)
         if args.extras:
             line["extras"] = extras(auto_eng, timed)
+        if n == N1_SIZE and not args.no_e2e:
+            sus = sustained_leg(auto_eng, a_host.data_ptr(), b_host.data_ptr(), n, flops, ms_per_step)
+            pk_s = float(pk.get("bf16_tflops_sustained", 0) or 0)
+            sus["frac_of_measured_sustained"] = sus["tflops"] / pk_s if pk_s else None
+            sus["burst_implied_sm_mhz_at_0.914_tensor_pipe"] = value * 1e12 / (0.914 * 148 * 8192) / 1e6
+            line["sustained"] = sus
     if not args.no_cpu:
         line["cpu_baseline"] = cpu_gemm_baseline(n)
     print(json.dumps(line))
