@@ -211,6 +211,27 @@ def test_gated_product_dims_and_refusals(e):       # tt-models/src/llama.rs:498 
         assert err.value.status == 2
 
 
+def test_projection_with_rope_dims_and_refusals(e):   # tt-models/src/llama.rs:404-433 as one product
+    a = e.upload_bf16(np.zeros((128, 64), np.uint16), 128, 64)
+    w = e.upload_bf16(np.zeros((64, 320), np.uint16), 64, 320)
+    cos, sin = f32(e, 64, 64), f32(e, 64, 64)
+    tab = lambda t, r=64: (t, (0, 0), (r, 64))
+    launches = e.device_traffic().launches
+    out, dims = e.matmul_rope(a, w, tab(cos), tab(sin), 192)
+    assert dims == (128, 320) and e.dims_of(out) == ((128, 320), BF16) and e.device_traffic().launches - launches == 1
+    for bad_cols in (0, 100, 384):                                              # none, not whole heads of 64, past the product
+        with pytest.raises(TtError) as err:
+            e.matmul_rope(a, w, tab(cos), tab(sin), bad_cols)
+        assert err.value.status == 2
+    with pytest.raises(TtError):                                                # 48 table rows do not divide 128 product rows
+        e.matmul_rope(a, w, tab(cos, 48), tab(sin, 48), 192)
+    with pytest.raises(TtError):                                                # F32 weights
+        e.matmul_rope(a, f32(e, 64, 320), tab(cos), tab(sin), 192)
+    wide = f32(e, 64, 96)
+    with pytest.raises(TtError):                                                # a table block 32 columns wide
+        e.matmul_rope(a, w, (wide, (0, 0), (64, 32)), tab(sin), 192)
+
+
 def test_views_keep_their_parent_alive(e):                                      # server.rs:480-481
     t0 = e.device_traffic().pool_in_use
     a = f32(e, 64, 8)
