@@ -753,20 +753,29 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// One product item fed from the ring: `len` k-rows in chunks of up to ChunkBoxes<MT> boxes of CK_ROWS, A's rows as BF16 in shared memory (pitch lda
-// elements, offset to the item's first k-row).  The eight warps split the item's 64 columns: a warp owns 8 of them and all of
-// k, so its accumulator (one m16n8 tile of `mma.sync`, rows past MT fed zeros) is the item's result for those columns and
-// no sum crosses warps.  B comes from the slot by `ldmatrix.trans` (the slot is [k][64 columns], 128-byte swizzled as the
-// copy wrote it: a warp's 16-byte unit of row k sits at unit ^ (k & 7), so eight rows of one matrix meet eight bank groups).
+// One product item fed from the ring: `len` k-rows in chunks of up to ChunkBoxes<MT> boxes of CK_ROWS, A's rows as BF16 in
+// shared memory (pitch lda elements, offset to the item's first k-row).  The product is taken transposed on the tensor
+// cores, C^T = W^T x^T, so that the 16-row side of `mma.sync.m16n8k16` holds sixteen of the item's 64 columns and the
+// 8-column side the step's rows (MT of them fed, the rest zeros): a warp owns sixteen columns and half of a box's
+// k-steps (warps 0-3 the first six, warps 4-7 the last six), six MMAs a box where the other orientation -- eight columns
+// and all of k a warp -- took twelve; the two halves of k meet in shared memory, added in a fixed order.  The weights'
+// fragment comes by `ldmatrix.trans` (the slot is [k][64 columns], 128-byte swizzled as the copy wrote it: the 16-byte
+// unit of row k sits at unit ^ (k & 7), so eight rows of one matrix meet eight bank groups).
 // With 16 blocks a step the CUDA cores were the products' bound (unpacking and 8 FMA a 16-byte load: 17 k of a block's
-// 48 k warp instructions a layer); a sixteenth of a tensor tile is used and it is still an order less issue.
+// 48 k warp instructions a layer); an eighth of a tensor tile is used and it is still an order less issue.
 template <int MT, int R, class Emit>
 __device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, uint32_t len, uint8_t* ring, uint64_t* bars, uint32_t& head,
-                                               uint32_t& parity, bool& dead, long long limit, int* err, WeightWalk& walk, Emit emit) {
+                                               uint32_t& parity, bool& dead, long long limit, int* err, WeightWalk& walk, float* halves,
+                                               Emit emit) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  float c[4][4] = {};
+  const uint32_t mblk = warp & 3, khalf = warp >> 2;
+  float c[2][4] = {};
   const uint16_t* arow = a + (size_t)(g < MT ? g : 0) * lda;
+  // this lane's row and 16-byte unit inside a k-step's sixteen rows, for the load of four 8x8 matrices:
+  // matrices 0, 1: rows 0-7, the block's first and second eight columns; 2, 3: rows 8-15
+  const uint32_t lrow = (uint32_t)(lane & 7) + ((lane >> 4) << 3), lunit = mblk * 2 + ((lane >> 3) & 1);
   constexpr uint32_t CHUNK_ROWS = ChunkBoxes<MT>::value * CK_ROWS, SLOT_BYTES = ChunkBoxes<MT>::value * BOX_BYTES;
+  constexpr int HALF_STEPS = CK_ROWS / 32;             // k-steps of 16 rows a warp takes of a box
   for (uint32_t cbase = 0; cbase < len; cbase += CHUNK_ROWS) {
     // the oldest of the R chunks in flight: its tile has landed when the slot's mbarrier flips
     if (!dead && !tc::mbar_wait(&bars[head], (parity >> head) & 1u, &dead_flag_of(err), limit)) {
@@ -777,33 +786,36 @@ __device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, 
     const uint32_t boxes = len - cbase < CHUNK_ROWS ? (len - cbase + CK_ROWS - 1) / CK_ROWS : ChunkBoxes<MT>::value;
 #pragma unroll 1
     for (uint32_t bx = 0; bx < boxes; ++bx) {
-    const uint32_t base = cbase + bx * CK_ROWS;
-    const uint32_t slot = tc::smem_u32(ring + (size_t)head * SLOT_BYTES + (size_t)bx * BOX_BYTES);
-    // every load of the box first (six loads of four 8x8 matrices, the A columns beside them), then twelve MMAs into
-    // four accumulators in turn: one accumulator would chain the twelve, ~35 cycles each
-    uint32_t bq[CK_ROWS / 32][4], aq[CK_ROWS / 32][4];
+      const uint32_t base = cbase + bx * CK_ROWS + khalf * (CK_ROWS / 2);     // this warp's first k-row of the box, in the item
+      const uint32_t slot = tc::smem_u32(ring + (size_t)head * SLOT_BYTES + (size_t)bx * BOX_BYTES) + khalf * (CK_ROWS / 2) * 128;
+      // every load first (six loads of four 8x8 matrices, the rows' values beside them), then six MMAs into two accumulators in turn
+      uint32_t wq[HALF_STEPS][4], xq[HALF_STEPS][2];
 #pragma unroll
-    for (int i = 0; i < CK_ROWS / 32; ++i) {
-      const uint32_t k = i * 32 + lane;                // this lane names row k of the slot
-      ldmatrix_x4_trans(slot + k * 128 + (((uint32_t)warp ^ (k & 7)) << 4), bq[i][0], bq[i][1], bq[i][2], bq[i][3]);
-      const uint32_t kk = base + i * 32 + 2 * t;        // this thread's A columns: kk, kk+1, kk+8, kk+9 and the same + 16
+      for (int i = 0; i < HALF_STEPS; ++i) {
+        const uint32_t k = i * 16 + lrow;              // row of the warp's half of the box
+        ldmatrix_x4_trans(slot + k * 128 + ((lunit ^ (k & 7)) << 4), wq[i][0], wq[i][1], wq[i][2], wq[i][3]);
+        const uint32_t kk = base + i * 16 + 2 * t;      // this thread's k columns of the rows' fragment: kk, kk+1 and kk+8, kk+9
+        xq[i][0] = (g < MT && kk < len) ? *reinterpret_cast<const uint32_t*>(arow + kk) : 0u;       // a row past the item's k counts as zeros
+        xq[i][1] = (g < MT && kk + 8 < len) ? *reinterpret_cast<const uint32_t*>(arow + kk + 8) : 0u;
+      }
 #pragma unroll
-      for (int j = 0; j < 4; ++j)                       // a row past the item's k counts as zeros (the slot may hold the next slice there)
-        aq[i][j] = (g < MT && kk + 8 * j < len) ? *reinterpret_cast<const uint32_t*>(arow + kk + 8 * j) : 0u;
-    }
-#pragma unroll
-    for (int i = 0; i < CK_ROWS / 32; ++i) {
-      mma_bf16_16816(c[(2 * i) & 3], aq[i][0], 0u, aq[i][1], 0u, bq[i][0], bq[i][1]);
-      mma_bf16_16816(c[(2 * i + 1) & 3], aq[i][2], 0u, aq[i][3], 0u, bq[i][2], bq[i][3]);
-    }
+      for (int i = 0; i < HALF_STEPS; ++i) mma_bf16_16816(c[i & 1], wq[i][0], wq[i][1], wq[i][2], wq[i][3], xq[i][0], xq[i][1]);
     }
     __syncthreads();                                   // every warp is done with the slot: refill it
     walk.issue(ring + (size_t)head * SLOT_BYTES, &bars[head]);
     head = head + 1 == (uint32_t)R ? 0 : head + 1;
   }
-  if (g < MT) {                                        // the four partial sums in a fixed order
-    emit(g, warp * 8 + 2 * t, (c[0][0] + c[1][0]) + (c[2][0] + c[3][0]));   // into the block's staging row: the caller sends it on
-    emit(g, warp * 8 + 2 * t + 1, (c[0][1] + c[1][1]) + (c[2][1] + c[3][1]));
+  // a thread holds columns mblk * 16 + g (and + 8) of rows 2t, 2t + 1 for its half of k: halves[khalf][row][column]
+  {
+    const uint32_t col = mblk * 16 + g;
+    const float lo0 = c[0][0] + c[1][0], lo1 = c[0][1] + c[1][1], hi0 = c[0][2] + c[1][2], hi1 = c[0][3] + c[1][3];
+    if (2 * t < MT) { halves[(khalf * MT + 2 * t) * DCOLS + col] = lo0; halves[(khalf * MT + 2 * t) * DCOLS + col + 8] = hi0; }
+    if (2 * t + 1 < MT) { halves[(khalf * MT + 2 * t + 1) * DCOLS + col] = lo1; halves[(khalf * MT + 2 * t + 1) * DCOLS + col + 8] = hi1; }
+  }
+  __syncthreads();
+  for (int i = tid; i < MT * DCOLS; i += DT) {
+    const int r = i / DCOLS, cc = i - r * DCOLS;
+    emit(r, cc, halves[r * DCOLS + cc] + halves[(MT + r) * DCOLS + cc]);   // into the block's staging row: the caller sends it on
   }
   __syncthreads();                                     // the staged results are whole
 }
@@ -846,7 +858,8 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
   float* ps = qs + 4 * HD;
   float* stat = ps + 4 * DCH;
   float* stage = stat + 16;                                       // [MT][64] a product item's results before they are sent; [AP] an attention item's
-  float* g1 = stage + (MT * DCOLS > (int)AP ? MT * DCOLS : AP);   // [H] the gains of the next first norm
+  float* halves = stage + (MT * DCOLS > (int)AP ? MT * DCOLS : AP);   // [2][MT][64] a product item's sums over the two halves of k
+  float* g1 = halves + 2 * MT * DCOLS;                            // [H] the gains of the next first norm
   float* g2 = g1 + H;                                             // [H] the gains of the next second norm
   float* cs = g2 + H;                                             // [64] the position's row of the cosine table
   float* sn = cs + HD;                                            // [64] and of the sine table
@@ -903,7 +916,7 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
     __syncthreads();
     norm_rows_sm<MT>(xres, H, g1, p.eps, vec, p.vec_cols, stat);
     for (uint32_t it = me; it < nb_qkv; it += C) {
-      product_stream<MT, R>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk,
+      product_stream<MT, R>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk, halves,
                             [&](int r, int cc, float t) { stage[r * DCOLS + cc] = bf16_round(t); });   // the product's BF16 result
       send_to_all(cluster, C, reinterpret_cast<uint4*>(qkv), reinterpret_cast<const uint4*>(stage), MT * 16,
                   [&](uint32_t q) { return ((q >> 4) * NQKV + it * DCOLS) / 4 + (q & 15); });
@@ -1049,7 +1062,7 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
     }
     __syncthreads();
     for (uint32_t it = me; it < nb_h; it += C) {
-      product_stream<MT, R>(vec, p.vec_cols, QC, ring, bars, head, parity, dead, limit, p.err, walk,
+      product_stream<MT, R>(vec, p.vec_cols, QC, ring, bars, head, parity, dead, limit, p.err, walk, halves,
                             [&](int r, int cc, float t) { stage[r * DCOLS + cc] = t; });
       send_to_all(cluster, C, reinterpret_cast<uint4*>(osum), reinterpret_cast<const uint4*>(stage), MT * 16,
                   [&](uint32_t q) { return ((q >> 4) * H + it * DCOLS) / 4 + (q & 15); });
@@ -1063,7 +1076,7 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
     for (int i = 0; i < GN; ++i) gn[i] = l + 1 < p.n_layers && tid + i * DT < H ? bf16_at(lay[l + 1].norm1, tid + i * DT) : 0.f;
     norm_rows_sm<MT>(xres, H, g2, p.eps, vec, p.vec_cols, stat);
     for (uint32_t it = me; it < nb_gu; it += C) {
-      product_stream<MT, R>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk, [&](int r, int cc, float t) {
+      product_stream<MT, R>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk, halves, [&](int r, int cc, float t) {
         reinterpret_cast<uint16_t*>(stage)[r * DCOLS + cc] = f32_to_bf16_bits(__float_as_uint(t));   // the product's BF16 result
       });
       send_to_all(cluster, C, reinterpret_cast<uint4*>(gu), reinterpret_cast<const uint4*>(stage), MT * 8,
@@ -1088,7 +1101,7 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
         vec[(size_t)r * p.vec_cols + kk] = f32_to_bf16_bits(__float_as_uint(__fmul_rn(__fmul_rn(a, sigmoid_flex(a)), bq)));
       }
       __syncthreads();
-      product_stream<MT, R>(vec, p.vec_cols, len, ring, bars, head, parity, dead, limit, p.err, walk,
+      product_stream<MT, R>(vec, p.vec_cols, len, ring, bars, head, parity, dead, limit, p.err, walk, halves,
                             [&](int r, int cc, float t) { stage[r * DCOLS + cc] = t; });
       send_to_all(cluster, C, reinterpret_cast<uint4*>(dn), reinterpret_cast<const uint4*>(stage), MT * 16,
                   [&](uint32_t q) { return (((size_t)ks * MT + (q >> 4)) * H + cb * DCOLS) / 4 + (q & 15); });
@@ -1251,7 +1264,7 @@ bool cluster_plan(const DecodeShape& sh, ClusterParams& c, size_t* smem) {
   const size_t stage = (size_t)MTc * DCOLS > 4 * (HD + 4) ? (size_t)MTc * DCOLS : 4 * (HD + 4);
   *smem = 1024 + ring_slots * SLOT_BYTES + 16 * sizeof(uint64_t) + 2 * DCH * 8 * sizeof(uint4) +
           ((size_t)MTc * sh.hidden * 2 + (size_t)MTc * NQ + (size_t)att_items * 4 * (HD + 4) +
-           (size_t)c.ks_dn * MTc * sh.hidden + 4 * HD + 4 * DCH + 16 + stage + 2 * sh.hidden + 2 * HD) * sizeof(float) +
+           (size_t)c.ks_dn * MTc * sh.hidden + 4 * HD + 4 * DCH + 16 + stage + 2 * MTc * DCOLS + 2 * sh.hidden + 2 * HD) * sizeof(float) +
           (size_t)sh.layers * sizeof(DecodeLayerDev) + SCHED_MAX * sizeof(ChunkEnt) + 8 + 16 +
           ((size_t)MTc * 2 * sh.ff + (size_t)MTc * vc) * sizeof(uint16_t);
   // the longest list of chunks a block of an eight-block cluster walks in a layer (block 0's)
