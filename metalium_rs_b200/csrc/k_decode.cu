@@ -662,9 +662,9 @@ __global__ void __launch_bounds__(DT, 1) decode_layers_kernel(const DecodeParams
 //
 // With so few blocks the step is bound by how many bytes of weights a block keeps in flight, so the weights do not wait
 // for the phase that uses them: the tiles a block will multiply by are known from the start (layer after layer, phase
-// after phase, item after item), and a ring of shared-memory slots is kept full of the next chunks by TMA (tiled copies
-// of 192 k-rows by 64 columns -- one a chunk, or three for one sequence, where a chunk is a whole 576-row item --
-// completing on the slot's mbarrier), across phases and cluster
+// after phase, item after item), and a ring of shared-memory slots is kept full of the next chunks by TMA (one tiled copy
+// a chunk -- 192 k-rows by 64 columns, or 576 for one sequence, where a chunk is a whole item -- completing on the slot's
+// mbarrier), across phases and cluster
 // barriers: loads issued by threads keep some 16 KB a block in flight, far too little for sixteen blocks to draw the
 // device's bandwidth, where the ring holds up to 144 KB a block.  A product waits for its next chunk, multiplies from
 // shared memory with tensor-core tiles (`mma.sync`: a warp owns 8 of the item's 64 columns), and refills the slot with
@@ -730,11 +730,13 @@ struct WeightWalk {
   __device__ __forceinline__ void issue(uint8_t* slot, uint64_t* bar) {
     if (il < p->n_layers) {
       if (threadIdx.x == 0) {
+        // one copy a chunk: the matrices are described as [k / 64][64][n], so a box of (chunk rows / 64) x 64 x 64 is the
+        // chunk's rows in order (at most 256 a dimension); the whole box counts, rows past the matrix filled with zeros
         const ChunkEnt e = tab[ii];
-        const uint32_t boxes = ((uint32_t)e.rows + CK_ROWS - 1) / CK_ROWS;
-        tc::mbar_expect_tx(bar, boxes * BOX_BYTES);    // whole boxes count, rows past the matrix filled with zeros
-        for (uint32_t b = 0; b < boxes; ++b)
-          tc::tma_load_2d(slot + (size_t)b * BOX_BYTES, p->maps + (size_t)il * 4 + e.phase, bar, (int32_t)e.cb * DCOLS, (int32_t)(e.k0 + b * CK_ROWS));
+        tc::mbar_expect_tx(bar, slot_bytes);
+        asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                     ::"r"(tc::smem_u32(slot)), "l"(p->maps + (size_t)il * 4 + e.phase), "r"(tc::smem_u32(bar)), "r"((int32_t)e.cb * DCOLS),
+                       "r"(0), "r"((int32_t)(e.k0 / 64)) : "memory");
       }
       if (++ii == cnt) { ii = 0; ++il; }
     }
@@ -1205,9 +1207,10 @@ DecodeScratch decode_layers_scratch(const DecodeShape& sh, int grid) {
 }
 
 // The tiled-copy descriptors of the layers' matrices, for the cluster form: four a layer, each over the stored [k, n]
-// (BF16) with a box of CK_ROWS rows by 64 columns, 128-byte swizzled.  False where the driver has no encoder.
+// (BF16) as [k / 64][64][n] with a box of a chunk's rows by 64 columns, 128-byte swizzled.  False where the driver has no encoder.
 size_t decode_layers_maps_bytes(const DecodeShape& sh) { return (size_t)sh.layers * 4 * sizeof(CUtensorMap); }
 bool decode_layers_make_maps(const DecodeShape& sh, const DecodeLayerPtrs* recs, void* maps_host) {
+  const uint32_t MTm = sh.rows <= 1 ? 1 : (sh.rows <= 2 ? 2 : 4);
   tc::EncodeTiledFn fn = tc::encode_fn();
   if (!fn) return false;
   CUtensorMap* maps = reinterpret_cast<CUtensorMap*>(maps_host);
@@ -1217,11 +1220,13 @@ bool decode_layers_make_maps(const DecodeShape& sh, const DecodeLayerPtrs* recs,
     const void* w[4] = {recs[l].qkv, recs[l].o, recs[l].gate_up, recs[l].down};
     for (int i = 0; i < 4; ++i) {
       if ((recs[l].bfp >> i) & 1u) return false;        // the cluster form multiplies BF16 tiles where they land
-      const cuuint64_t dims[2] = {kn[i][1], kn[i][0]};
-      const cuuint64_t strides[1] = {kn[i][1] * 2u};
-      const cuuint32_t box[2] = {(cuuint32_t)DCOLS, (cuuint32_t)CK_ROWS};
-      const cuuint32_t estr[2] = {1, 1};
-      if (fn(&maps[(size_t)l * 4 + i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(w[i]),
+      // [k, n] seen as [k / 64][64][n]: a box of (a chunk's rows / 64) x 64 rows x 64 columns lands as the chunk's rows in order
+      const cuuint64_t dims[3] = {kn[i][1], 64, (kn[i][0] + 63) / 64};
+      const cuuint64_t strides[2] = {kn[i][1] * 2u, kn[i][1] * 2u * 64u};
+      const cuuint32_t box[3] = {(cuuint32_t)DCOLS, 64u, (cuuint32_t)(chunk_rows_of(MTm) / 64)};
+      const cuuint32_t estr[3] = {1, 1, 1};
+      if (kn[i][0] % 64) return false;
+      if (fn(&maps[(size_t)l * 4 + i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(w[i]),
              dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
@@ -1251,7 +1256,7 @@ bool cluster_plan(const DecodeShape& sh, ClusterParams& c, size_t* smem) {
   const uint32_t want_rows = MTc == 1 ? 576u : 768u;
   c.ks_dn = (sh.ff + want_rows - 1) / want_rows;
   if (c.ks_dn < 1) c.ks_dn = 1;
-  c.sl_dn = ((sh.ff + c.ks_dn - 1) / c.ks_dn + 31) / 32 * 32;
+  c.sl_dn = ((sh.ff + c.ks_dn - 1) / c.ks_dn + 63) / 64 * 64;   // a slice starts at a multiple of 64 rows: the copies address k in 64s
   c.ks_dn = (sh.ff + c.sl_dn - 1) / c.sl_dn;
   uint32_t vc = sh.hidden > QCc ? sh.hidden : QCc;
   if (c.sl_dn > vc) vc = c.sl_dn;
