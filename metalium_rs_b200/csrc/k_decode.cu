@@ -904,7 +904,7 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
     for (int i = 0; i < GN; ++i) gn[i] = tid + i * DT < H ? bf16_at(L.norm2, tid + i * DT) : 0.f;
     // ---- phase 1 ----
     for (uint32_t i = tid; i < (uint32_t)MT * H; i += DT) {
-      const uint32_t r = i / H, c = i - r * H;
+      const uint32_t r = MT == 1 ? 0u : i / H, c = i - r * H;              // (one sequence: no division)
       float v;
       if (l == 0) {
         v = r < p.rows ? p.x0[(size_t)r * H + c] : 0.f;
@@ -1036,8 +1036,9 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
     // a (row, head)'s chunk weights exp(m_c - M) and its sum, once (a thread a pair), in the down projection's idle buffer;
     // then every output element is four multiply-adds and a division instead of eight exponentials
     float* mw = dn;                                    // [MT * heads][chunks + 1]
+    uint32_t* mbase = reinterpret_cast<uint32_t*>(mw + (size_t)MT * p.heads * (chunks + 1));   // [MT * heads]
     for (uint32_t i = tid; i < (uint32_t)MT * p.heads; i += DT) {
-      const uint32_t r = i / p.heads, h = i - r * p.heads, kvh = h / group, g = h - kvh * group;
+      const uint32_t r = MT == 1 ? 0u : i / p.heads, h = i - r * p.heads, kvh = h / group, g = h - kvh * group;
       const float* base = att + (size_t)((r * p.kv_heads + kvh) * chunks) * AP + g * APH;
       float M = -3.402823466e38f;
       for (uint32_t c2 = 0; c2 < chunks; ++c2) M = fmaxf(M, base[(size_t)c2 * AP + HD]);
@@ -1048,13 +1049,14 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
         Lsum = fmaf(base[(size_t)c2 * AP + HD + 1], wgt, Lsum);
       }
       mw[(size_t)i * (chunks + 1) + chunks] = fmaxf(Lsum, 1.175494351e-38f);
+      mbase[i] = (uint32_t)((size_t)((r * p.kv_heads + kvh) * chunks) * AP + g * APH);   // where the head's partials start
     }
     __syncthreads();
     for (uint32_t i = tid; i < (uint32_t)MT * QC; i += DT) {
-      const uint32_t r = i / QC, c = i - r * QC, h = c / HD, d = c - h * HD, kvh = h / group, g = h - kvh * group;
+      const uint32_t r = MT == 1 ? 0u : i / QC, c = i - r * QC, h = c / HD, d = c - h * HD;
       float v = 0.f;
       if (r < p.rows) {
-        const float* base = att + (size_t)((r * p.kv_heads + kvh) * chunks) * AP + g * APH;
+        const float* base = att + mbase[r * p.heads + h];
         const float* w = mw + (size_t)(r * p.heads + h) * (chunks + 1);
         float O = 0.f;
         for (uint32_t c2 = 0; c2 < chunks; ++c2) O = fmaf(base[(size_t)c2 * AP + d], w[c2], O);
@@ -1097,7 +1099,7 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
       const uint32_t len = k0 + p.sl_dn <= FF ? p.sl_dn : FF - k0;
       __syncthreads();
       for (uint32_t i = tid; i < (uint32_t)MT * len; i += DT) {
-        const uint32_t r = i / len, kk = i - r * len;
+        const uint32_t r = MT == 1 ? 0u : i / len, kk = i - r * len;
         const float a = __uint_as_float((uint32_t)gu[(size_t)r * 2 * FF + k0 + kk] << 16);
         const float bq = __uint_as_float((uint32_t)gu[(size_t)r * 2 * FF + FF + k0 + kk] << 16);
         vec[(size_t)r * p.vec_cols + kk] = f32_to_bf16_bits(__float_as_uint(__fmul_rn(__fmul_rn(a, sigmoid_flex(a)), bq)));
@@ -1112,7 +1114,7 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
   }
   if (me == 0) {
     for (uint32_t i = tid; i < (uint32_t)MT * H; i += DT) {
-      const uint32_t r = i / H, c = i - r * H;
+      const uint32_t r = MT == 1 ? 0u : i / H, c = i - r * H;
       float d = 0.f;
       for (uint32_t k = 0; k < p.ks_dn; ++k) d += dn[((size_t)k * MT + r) * H + c];
       xres[i] = __fadd_rn(xres[i], d);
@@ -1276,7 +1278,7 @@ bool cluster_plan(const DecodeShape& sh, ClusterParams& c, size_t* smem) {
   auto chunks_of = [&](uint32_t items, uint32_t rows) { return (uint64_t)((items + 7) / 8) * ((rows + chunk_rows - 1) / chunk_rows); };
   const uint64_t sched = chunks_of(NQ / DCOLS, sh.hidden) + chunks_of(sh.hidden / DCOLS, QCc) + chunks_of(2 * sh.ff / DCOLS, sh.hidden) +
                          chunks_of(sh.hidden / DCOLS * c.ks_dn, c.sl_dn);
-  const uint64_t merge_words = (uint64_t)sh.heads * (sh.attend / DCH + 1);   // a row's chunk weights wait in the down projection's buffer
+  const uint64_t merge_words = (uint64_t)sh.heads * (sh.attend / DCH + 2);   // a row's chunk weights (and where its partials start) wait in the down projection's buffer
   return *smem <= 224 * 1024 && sh.hidden <= (uint32_t)GN * DT && sched <= SCHED_MAX && sh.ff < 65536 && 2 * sh.ff / DCOLS < 65536 &&
          merge_words <= (uint64_t)c.ks_dn * sh.hidden;
 }
