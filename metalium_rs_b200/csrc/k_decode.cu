@@ -655,10 +655,11 @@ __global__ void __launch_bounds__(DT, 1) decode_layers_kernel(const DecodeParams
 
 // ---- the same step on ONE thread-block cluster --------------------------------------------------------------------------
 // Sixteen (or eight) blocks of one cluster instead of a grid: what a phase hands to the next travels through
-// distributed shared memory (every block stores its results into every block's shared memory), and the phases are
-// separated by the hardware's cluster barrier instead of a counter in global memory -- a few hundred nanoseconds where
-// the grid's barrier and the round trips through L2 for the partial sums cost microseconds.  Only the down projection
-// slices k (its partial sums are added in a fixed order by every block); the other products give a block whole columns.
+// distributed shared memory -- a block stages its results and the copy engine delivers them into every block's shared
+// memory, completing as transaction bytes on the receiver's mbarrier of the phase -- so a block waits for the bytes it
+// expects instead of at a counter in global memory after round trips through L2 for the partial sums.  Only the down
+// projection slices k (its partial sums are added in a fixed order by every block); the other products give a block
+// whole columns.
 //
 // With so few blocks the step is bound by how many bytes of weights a block keeps in flight, so the weights do not wait
 // for the phase that uses them: the tiles a block will multiply by are known from the start (layer after layer, phase
@@ -683,6 +684,7 @@ struct ClusterParams {
   uint16_t* out;
   int* err;
   uint32_t ks_dn, sl_dn, vec_cols, att_items;
+  uint32_t min_width;        // the narrowest cluster the shared-memory plan holds the staging slots of (8 or 16 blocks)
   const CUtensorMap* maps;   // [n_layers][4]: qkv, o, gate|up, down as [k, n] with a box of 64 rows by 64 columns
 };
 
@@ -819,19 +821,20 @@ __device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, 
     const int r = i / DCOLS, cc = i - r * DCOLS;
     emit(r, cc, halves[r * DCOLS + cc] + halves[(MT + r) * DCOLS + cc]);   // into the block's staging row: the caller sends it on
   }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // written by threads, read by the copy engine
   __syncthreads();                                     // the staged results are whole
 }
 
-// Send `pieces` 16-byte pieces staged in this block's shared memory to the same place in EVERY block of the cluster
-// (this one included): piece q goes to `dst + where(q)` (in 16-byte units).  A (piece, block) pair a thread, so one
-// product item's results leave in one or a few stores a thread -- a thread that stored sixteen times in a row, once a
-// block, spent some 5,000 cycles an item.
-template <class Where>
-__device__ __forceinline__ void send_to_all(cg::cluster_group& cluster, uint32_t C, uint4* dst, const uint4* staged, uint32_t pieces, Where where) {
-  for (uint32_t idx = threadIdx.x; idx < pieces * C; idx += DT) {
-    const uint32_t q = idx % pieces, d = idx / pieces;
-    cluster.map_shared_rank(dst, d)[where(q)] = staged[q];
-  }
+// The same delivery by the copy engine: `bytes` staged in this block's shared memory go to the same offset `dst` in the
+// shared memory of block `rank`, and complete (as transaction bytes) on that block's mbarrier `bar` -- the receiver waits
+// for the bytes it expects of a phase on its own barrier instead of the whole cluster meeting at a barrier whose release
+// must first see every store into sixteen shared memories land.
+__device__ __forceinline__ void copy_to_block(void* dst, const void* staged, uint32_t bytes, uint64_t* bar, uint32_t rank) {
+  uint32_t rd, rb;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rd) : "r"(tc::smem_u32(dst)), "r"(rank));
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rb) : "r"(tc::smem_u32(bar)), "r"(rank));
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(rd), "r"(tc::smem_u32(staged)), "r"(bytes), "r"(rb) : "memory");
 }
 
 template <int MT>
@@ -859,9 +862,16 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
   float* qs = dn + (size_t)p.ks_dn * MT * H;
   float* ps = qs + 4 * HD;
   float* stat = ps + 4 * DCH;
-  float* stage = stat + 16;                                       // [MT][64] a product item's results before they are sent; [AP] an attention item's
-  float* halves = stage + (MT * DCOLS > (int)AP ? MT * DCOLS : AP);   // [2][MT][64] a product item's sums over the two halves of k
-  float* g1 = halves + 2 * MT * DCOLS;                            // [H] the gains of the next first norm
+  float* halves = stat + 16;                                      // [2][MT][64] a product item's sums over the two halves of k
+  // what the block's items of a phase hand to the copy engine, a slot an item: the engine reads a slot after the block
+  // has moved on, and the slot is written again a layer later, when every receiver has long waited for its bytes
+  const uint32_t nb_qkv = NQKV / DCOLS, nb_h = H / DCOLS, nb_gu = 2 * FF / DCOLS, nb_dn = nb_h * p.ks_dn;
+  float* sq = halves + 2 * MT * DCOLS;                            // [items a block of phase 1][MT][64]
+  float* sa = sq + (size_t)((nb_qkv + C - 1) / C) * MT * DCOLS;   // [... of phase 2][AP]
+  float* so = sa + (size_t)((p.att_items + C - 1) / C) * AP;      // [... of phase 3][MT][64]
+  float* sg = so + (size_t)((nb_h + C - 1) / C) * MT * DCOLS;     // [... of phase 4][MT][64] BF16
+  float* sd = sg + (size_t)((nb_gu + C - 1) / C) * MT * DCOLS / 2;   // [... of phase 5][MT][64]
+  float* g1 = sd + (size_t)((nb_dn + C - 1) / C) * MT * DCOLS;    // [H] the gains of the next first norm
   float* g2 = g1 + H;                                             // [H] the gains of the next second norm
   float* cs = g2 + H;                                             // [64] the position's row of the cosine table
   float* sn = cs + HD;                                            // [64] and of the sine table
@@ -876,7 +886,6 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
     if (tid == 0) atomicCAS(p.err, 0, 6);
     return;
   }
-  const uint32_t nb_qkv = NQKV / DCOLS, nb_h = H / DCOLS, nb_gu = 2 * FF / DCOLS;
   // what every layer needs from global memory and no step changes: read once, so that no phase waits for it
   for (uint32_t i = tid; i < p.n_layers * (uint32_t)(sizeof(DecodeLayerDev) / 8); i += DT)
     reinterpret_cast<uint64_t*>(lay)[i] = reinterpret_cast<const uint64_t*>(p.layers)[i];
@@ -889,15 +898,33 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
   uint32_t head = 0, parity = 0;
   bool dead = false;
   const long long limit = tc::wait_limit_of(p.err);
+  // The phases hand their results on by copies that complete, as transaction bytes, on the RECEIVER's mbarrier of the
+  // phase: a block waits for the bytes it expects of a phase instead of the cluster meeting at a barrier (whose release
+  // must first see every store into sixteen shared memories land: 8,000 of a layer's 42,000 cycles).  Nothing else
+  // orders the blocks, and nothing else has to: every block has items in the gate|up and down phases, so no block can be
+  // a layer ahead of another -- a buffer is read before the phase that refills it a layer later can have started
+  // anywhere, and a barrier is armed for its next use before a byte of that use can have been sent.
+  uint64_t* xb = &bars[8];                            // [5]
+  const uint32_t expect[5] = {nb_qkv * MT * DCOLS * 4, p.att_items * group * APH * 4, nb_h * MT * DCOLS * 4, nb_gu * MT * DCOLS * 2,
+                              nb_dn * MT * DCOLS * 4};
   if (tid == 0) {
     for (int r = 0; r < R; ++r) tc::mbar_init(&bars[r], 1);
+    for (int k = 0; k < 5; ++k) tc::mbar_init(&xb[k], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int k = 0; k < 5; ++k) tc::mbar_expect_tx(&xb[k], expect[k]);   // layer 0's
   }
   __syncthreads();
+  cluster.sync();                                      // every block's barriers exist before a copy may name them
   for (int r = 0; r < R; ++r) walk.issue(ring + (size_t)r * SLOT_BYTES, &bars[r]);   // the ring starts full
 
   for (uint32_t l = 0; l < p.n_layers; ++l) {
     const DecodeLayerDev L = lay[l];
+    // wait for the bytes this block expects of phase k of this layer, then arm the barrier for the next layer's
+    auto arrived = [&](int k) {
+      if (!dead && !tc::mbar_wait(&xb[k], l & 1u, &dead_flag_of(p.err), limit)) { dead = true; atomicCAS(p.err, 0, TIMEOUT_CODE); }
+      __syncthreads();                                 // every thread is past the wait
+      if (tid == 0 && l + 1 < p.n_layers) tc::mbar_expect_tx(&xb[k], expect[k]);
+    };
     // the gains of this layer's second norm: asked for now, kept in registers, stored after the products
     float gn[GN];
 #pragma unroll
@@ -918,10 +945,13 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
     __syncthreads();
     norm_rows_sm<MT>(xres, H, g1, p.eps, vec, p.vec_cols, stat);
     for (uint32_t it = me; it < nb_qkv; it += C) {
+      float* slot = sq + (size_t)((it - me) / C) * MT * DCOLS;
       product_stream<MT, R>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk, halves,
-                            [&](int r, int cc, float t) { stage[r * DCOLS + cc] = bf16_round(t); });   // the product's BF16 result
-      send_to_all(cluster, C, reinterpret_cast<uint4*>(qkv), reinterpret_cast<const uint4*>(stage), MT * 16,
-                  [&](uint32_t q) { return ((q >> 4) * NQKV + it * DCOLS) / 4 + (q & 15); });
+                            [&](int r, int cc, float t) { slot[r * DCOLS + cc] = bf16_round(t); });   // the product's BF16 result
+      if ((uint32_t)tid < C * MT) {                    // a (block, row) pair a thread: 256 bytes each
+        const uint32_t d = (uint32_t)tid / MT, r = (uint32_t)tid - d * MT;
+        copy_to_block(qkv + (size_t)r * NQKV + it * DCOLS, slot + r * DCOLS, DCOLS * 4, &xb[0], d);
+      }
     }
 #pragma unroll
     for (int i = 0; i < GN; ++i)
@@ -940,18 +970,19 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
       }
     };
     if (me < p.att_items) load_cache(me);
-    cluster.sync();
+    arrived(0);                                        // every block's QKV results have landed here
 
     // ---- phase 2 ----
     for (uint32_t it = me; it < p.att_items; it += C) {
       const uint32_t ch = it % chunks, kvh = (it / chunks) % p.kv_heads, b = it / (chunks * p.kv_heads);
+      float* stage = sa + (size_t)((it - me) / C) * AP;
       __syncthreads();
       if (it != me) load_cache(it);
       if (ch * DCH > (uint32_t)pos) {
         for (uint32_t i = tid; i < AP; i += DT) stage[i] = i % APH == HD ? -INFINITY : 0.f;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncthreads();
-        send_to_all(cluster, C, reinterpret_cast<uint4*>(att + (size_t)it * AP), reinterpret_cast<const uint4*>(stage), group * (APH / 4),
-                    [&](uint32_t q) { return q; });
+        if ((uint32_t)tid < C) copy_to_block(att + (size_t)it * AP, stage, group * APH * 4, &xb[1], (uint32_t)tid);
         continue;
       }
       const float* qrow = qkv + (size_t)b * NQKV;
@@ -1026,11 +1057,11 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
         stage[g * APH + d] = o;
         if (d == 0) { stage[g * APH + HD] = mh; stage[g * APH + HD + 1] = lsum; }
       }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncthreads();
-      send_to_all(cluster, C, reinterpret_cast<uint4*>(att + (size_t)it * AP), reinterpret_cast<const uint4*>(stage), group * (APH / 4),
-                  [&](uint32_t q) { return q; });
+      if ((uint32_t)tid < C) copy_to_block(att + (size_t)it * AP, stage, group * APH * 4, &xb[1], (uint32_t)tid);
     }
-    cluster.sync();
+    arrived(1);                                        // every chunk's partial has landed here
 
     // ---- phase 3 ----
     // a (row, head)'s chunk weights exp(m_c - M) and its sum, once (a thread a pair), in the down projection's idle buffer;
@@ -1066,12 +1097,15 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
     }
     __syncthreads();
     for (uint32_t it = me; it < nb_h; it += C) {
+      float* slot = so + (size_t)((it - me) / C) * MT * DCOLS;
       product_stream<MT, R>(vec, p.vec_cols, QC, ring, bars, head, parity, dead, limit, p.err, walk, halves,
-                            [&](int r, int cc, float t) { stage[r * DCOLS + cc] = t; });
-      send_to_all(cluster, C, reinterpret_cast<uint4*>(osum), reinterpret_cast<const uint4*>(stage), MT * 16,
-                  [&](uint32_t q) { return ((q >> 4) * H + it * DCOLS) / 4 + (q & 15); });
+                            [&](int r, int cc, float t) { slot[r * DCOLS + cc] = t; });
+      if ((uint32_t)tid < C * MT) {
+        const uint32_t d = (uint32_t)tid / MT, r = (uint32_t)tid - d * MT;
+        copy_to_block(osum + (size_t)r * H + it * DCOLS, slot + r * DCOLS, DCOLS * 4, &xb[2], d);
+      }
     }
-    cluster.sync();
+    arrived(2);                                        // the attention output's projection, whole
 
     // ---- phase 4 ----
     for (uint32_t i = tid; i < (uint32_t)MT * H; i += DT) xres[i] = __fadd_rn(xres[i], osum[i]);
@@ -1080,21 +1114,22 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
     for (int i = 0; i < GN; ++i) gn[i] = l + 1 < p.n_layers && tid + i * DT < H ? bf16_at(lay[l + 1].norm1, tid + i * DT) : 0.f;
     norm_rows_sm<MT>(xres, H, g2, p.eps, vec, p.vec_cols, stat);
     for (uint32_t it = me; it < nb_gu; it += C) {
+      uint16_t* slot = reinterpret_cast<uint16_t*>(sg) + (size_t)((it - me) / C) * MT * DCOLS;
       product_stream<MT, R>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk, halves, [&](int r, int cc, float t) {
-        reinterpret_cast<uint16_t*>(stage)[r * DCOLS + cc] = f32_to_bf16_bits(__float_as_uint(t));   // the product's BF16 result
+        slot[r * DCOLS + cc] = f32_to_bf16_bits(__float_as_uint(t));   // the product's BF16 result
       });
-      send_to_all(cluster, C, reinterpret_cast<uint4*>(gu), reinterpret_cast<const uint4*>(stage), MT * 8,
-                  [&](uint32_t q) { return ((q >> 3) * 2 * FF + it * DCOLS) / 8 + (q & 7); });
+      if ((uint32_t)tid < C * MT) {
+        const uint32_t d = (uint32_t)tid / MT, r = (uint32_t)tid - d * MT;
+        copy_to_block(gu + (size_t)r * 2 * FF + it * DCOLS, slot + r * DCOLS, DCOLS * 2, &xb[3], d);
+      }
     }
 #pragma unroll
     for (int i = 0; i < GN; ++i)
       if (tid + i * DT < H) g1[tid + i * DT] = gn[i];
-
-    cluster.sync();
-
+    arrived(3);                                        // gate|up, whole
 
     // ---- phase 5 ----
-    for (uint32_t it = me; it < nb_h * p.ks_dn; it += C) {
+    for (uint32_t it = me; it < nb_dn; it += C) {
       const uint32_t cb = it % nb_h, ks = it / nb_h, k0 = ks * p.sl_dn;
       const uint32_t len = k0 + p.sl_dn <= FF ? p.sl_dn : FF - k0;
       __syncthreads();
@@ -1105,12 +1140,15 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
         vec[(size_t)r * p.vec_cols + kk] = f32_to_bf16_bits(__float_as_uint(__fmul_rn(__fmul_rn(a, sigmoid_flex(a)), bq)));
       }
       __syncthreads();
+      float* slot = sd + (size_t)((it - me) / C) * MT * DCOLS;
       product_stream<MT, R>(vec, p.vec_cols, len, ring, bars, head, parity, dead, limit, p.err, walk, halves,
-                            [&](int r, int cc, float t) { stage[r * DCOLS + cc] = t; });
-      send_to_all(cluster, C, reinterpret_cast<uint4*>(dn), reinterpret_cast<const uint4*>(stage), MT * 16,
-                  [&](uint32_t q) { return (((size_t)ks * MT + (q >> 4)) * H + cb * DCOLS) / 4 + (q & 15); });
+                            [&](int r, int cc, float t) { slot[r * DCOLS + cc] = t; });
+      if ((uint32_t)tid < C * MT) {
+        const uint32_t d = (uint32_t)tid / MT, r = (uint32_t)tid - d * MT;
+        copy_to_block(dn + ((size_t)ks * MT + r) * H + cb * DCOLS, slot + r * DCOLS, DCOLS * 4, &xb[4], d);
+      }
     }
-    cluster.sync();
+    arrived(4);                                        // the down projection's partial sums, all of them
   }
   if (me == 0) {
     for (uint32_t i = tid; i < (uint32_t)MT * H; i += DT) {
@@ -1135,6 +1173,7 @@ cudaError_t launch_cluster(const ClusterParams& p, size_t smem, int* cluster_blo
   if (!device_value_get((const void*)decode_cluster_kernel<MT>, &width)) {
     width = -1;
     for (int c : {16, 8}) {
+      if ((uint32_t)c < p.min_width) continue;
       if (c > 8 && cudaFuncSetAttribute((const void*)decode_cluster_kernel<MT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
         cudaGetLastError();
         continue;
@@ -1151,7 +1190,7 @@ cudaError_t launch_cluster(const ClusterParams& p, size_t smem, int* cluster_blo
     }
     device_value_set((const void*)decode_cluster_kernel<MT>, width);
   }
-  if (width < 8) return cudaErrorNotSupported;
+  if (width < 8 || (uint32_t)width < p.min_width) return cudaErrorNotSupported;
   *cluster_blocks = width;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(width); cfg.blockDim = dim3(DT); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
@@ -1268,19 +1307,27 @@ bool cluster_plan(const DecodeShape& sh, ClusterParams& c, size_t* smem) {
   const size_t ring_slots = MTc == 1 ? RingDepth<1>::value : (MTc == 2 ? RingDepth<2>::value : RingDepth<4>::value);
   const uint32_t chunk_rows = chunk_rows_of(MTc);
   const size_t SLOT_BYTES = (size_t)chunk_rows * 128;
-  const size_t stage = (size_t)MTc * DCOLS > 4 * (HD + 4) ? (size_t)MTc * DCOLS : 4 * (HD + 4);
-  *smem = 1024 + ring_slots * SLOT_BYTES + 16 * sizeof(uint64_t) + 2 * DCH * 8 * sizeof(uint4) +
-          ((size_t)MTc * sh.hidden * 2 + (size_t)MTc * NQ + (size_t)att_items * 4 * (HD + 4) +
-           (size_t)c.ks_dn * MTc * sh.hidden + 4 * HD + 4 * DCH + 16 + stage + 2 * MTc * DCOLS + 2 * sh.hidden + 2 * HD) * sizeof(float) +
-          (size_t)sh.layers * sizeof(DecodeLayerDev) + SCHED_MAX * sizeof(ChunkEnt) + 8 + 16 +
-          ((size_t)MTc * 2 * sh.ff + (size_t)MTc * vc) * sizeof(uint16_t);
+  // the items' staging slots, sized for a cluster of eight blocks where that fits, else of sixteen
+  const uint64_t nbq = NQ / DCOLS, nbh = sh.hidden / DCOLS, nbg = 2 * sh.ff / DCOLS, nbd = nbh * c.ks_dn;
+  for (uint32_t width : {8u, 16u}) {
+    auto per = [&](uint64_t items) { return (items + width - 1) / width; };
+    const size_t stage = (per(nbq) + per(nbh) + per(nbd)) * MTc * DCOLS + per(att_items) * 4 * (HD + 4) + per(nbg) * MTc * DCOLS / 2;
+    *smem = 1024 + ring_slots * SLOT_BYTES + 16 * sizeof(uint64_t) + 2 * DCH * 8 * sizeof(uint4) +
+            ((size_t)MTc * sh.hidden * 2 + (size_t)MTc * NQ + (size_t)att_items * 4 * (HD + 4) +
+             (size_t)c.ks_dn * MTc * sh.hidden + 4 * HD + 4 * DCH + 16 + stage + 2 * MTc * DCOLS + 2 * sh.hidden + 2 * HD) * sizeof(float) +
+            (size_t)sh.layers * sizeof(DecodeLayerDev) + SCHED_MAX * sizeof(ChunkEnt) + 8 + 16 +
+            ((size_t)MTc * 2 * sh.ff + (size_t)MTc * vc) * sizeof(uint16_t);
+    c.min_width = width;
+    if (*smem <= 224 * 1024) break;
+  }
   // the longest list of chunks a block of an eight-block cluster walks in a layer (block 0's)
   auto chunks_of = [&](uint32_t items, uint32_t rows) { return (uint64_t)((items + 7) / 8) * ((rows + chunk_rows - 1) / chunk_rows); };
   const uint64_t sched = chunks_of(NQ / DCOLS, sh.hidden) + chunks_of(sh.hidden / DCOLS, QCc) + chunks_of(2 * sh.ff / DCOLS, sh.hidden) +
                          chunks_of(sh.hidden / DCOLS * c.ks_dn, c.sl_dn);
   const uint64_t merge_words = (uint64_t)sh.heads * (sh.attend / DCH + 2);   // a row's chunk weights (and where its partials start) wait in the down projection's buffer
   return *smem <= 224 * 1024 && sh.hidden <= (uint32_t)GN * DT && sched <= SCHED_MAX && sh.ff < 65536 && 2 * sh.ff / DCOLS < 65536 &&
-         merge_words <= (uint64_t)c.ks_dn * sh.hidden;
+         merge_words <= (uint64_t)c.ks_dn * sh.hidden &&
+         nbg >= 16 && nbd >= 16;                         // every block has gate|up and down items: what orders the blocks (see the kernel)
 }
 }  // namespace
 
