@@ -686,6 +686,12 @@ struct ClusterParams {
   uint32_t ks_dn, sl_dn, vec_cols, att_items;
   uint32_t min_width;        // the narrowest cluster the shared-memory plan holds the staging slots of (8 or 16 blocks)
   const CUtensorMap* maps;   // [n_layers][4]: qkv, o, gate|up, down as [k, n] with a box of 64 rows by 64 columns
+  // the several-cluster form only
+  uint32_t tp;               // clusters a step: each takes 1/tp of the heads and of ff
+  uint32_t pbytes[4];        // bytes one tiled copy of a chunk lands, by matrix (the box of that matrix's descriptors)
+  float* part_o;             // [tp][MT][hidden]: a cluster's share of the attention output's projection
+  float* part_dn;            // [tp * ks_dn][MT][hidden]: and of the down projection, a slice of k each
+  unsigned* gbar;            // the count of blocks that reached a meeting (zero at launch)
 };
 
 constexpr int CK_ROWS = 192;                           // k-rows of a tiled copy's box (at most 256)
@@ -704,14 +710,35 @@ inline uint32_t chunk_rows_of(uint32_t mt) { return (mt == 1 ? 3u : 1u) * CK_ROW
 struct ChunkEnt { uint16_t phase, rows, cb, k0; };     // phase 0 qkv, 1 o, 2 gate|up, 3 down; rows of the chunk; column block; first k-row
 constexpr uint32_t SCHED_MAX = 256;
 
+// The several-cluster form's cut of a layer: cluster `cgi` of `tp` takes heads / tp query heads with their key/value
+// heads (the QKV columns of those heads, their attention, the rows of the output projection they feed) and ff / tp of the
+// MLP (those gate and up columns, the rows of the down projection they feed).  Item j of a phase goes to the block whose
+// rank is (j + the phase's offset) mod the cluster's width, so that the phases with fewer items than blocks do not all
+// land on the first blocks.
+struct TpCut {
+  uint32_t cgi, heads, kv_heads, hq, hk, QCl, KCl, NQl, FFl, nfl, ffb, n_q, n_att, nb_h, n_gu, n_dn, off_att, off_o, off_dn;
+  __device__ TpCut(const ClusterParams& p, uint32_t cgi_) {
+    cgi = cgi_; heads = p.heads; kv_heads = p.kv_heads;
+    hq = p.heads / p.tp; hk = p.kv_heads / p.tp; QCl = hq * HD; KCl = hk * HD; NQl = QCl + 2 * KCl;
+    FFl = p.ff / p.tp; nfl = FFl / DCOLS; ffb = p.ff / DCOLS;
+    n_q = hq + 2 * hk; n_att = p.rows * hk * (p.attend / DCH); nb_h = p.hidden / DCOLS; n_gu = 2 * nfl; n_dn = nb_h * p.ks_dn;
+    off_att = n_q; off_o = off_att + n_att; off_dn = off_o + nb_h;
+  }
+  // the column block (of 64) of the stored matrix that local item j multiplies by
+  __device__ uint32_t qkv_cb(uint32_t j) const {
+    return j < hq ? cgi * hq + j : (j < hq + hk ? heads + cgi * hk + (j - hq) : heads + kv_heads + cgi * hk + (j - hq - hk));
+  }
+  __device__ uint32_t gu_cb(uint32_t j) const { return j < nfl ? cgi * nfl + j : ffb + cgi * nfl + (j - nfl); }
+  __device__ static uint32_t first(uint32_t me, uint32_t C, uint32_t off) { return (me + C - off % C) % C; }
+};
+
 struct WeightWalk {
   const ClusterParams* p;
   const ChunkEnt* tab;
   uint32_t cnt, ii, il;                                // the list's length; the next chunk to issue: entry ii of layer il
-  uint32_t slot_bytes;
   // thread 0 writes the list; every thread calls this, the caller's __syncthreads publishes it
   __device__ void start(const ClusterParams* pp, ChunkEnt* tab_, uint32_t* cnt_sm, uint32_t me, uint32_t C, uint32_t chunk_rows) {
-    p = pp; tab = tab_; ii = 0; il = 0; slot_bytes = chunk_rows * 128;
+    p = pp; tab = tab_; ii = 0; il = 0;
     if (threadIdx.x == 0) {
       const uint32_t H = pp->hidden, QC = pp->heads * HD, NQKV = QC + 2 * pp->kv_heads * HD, FF = pp->ff, nb_h = H / DCOLS;
       uint32_t c = 0;
@@ -728,14 +755,34 @@ struct WeightWalk {
       *cnt_sm = c;
     }
   }
+  // the same list for a block of the several-cluster form: its cluster's share, in the order of the phases
+  __device__ void start_tp(const ClusterParams* pp, ChunkEnt* tab_, uint32_t* cnt_sm, uint32_t me, uint32_t C, const TpCut& cut,
+                           uint32_t chunk_rows) {
+    p = pp; tab = tab_; ii = 0; il = 0;
+    if (threadIdx.x == 0) {
+      uint32_t c = 0;
+      auto put = [&](uint32_t ph, uint32_t cb, uint32_t k0, uint32_t total) {
+        for (uint32_t k = 0; k < total && c < SCHED_MAX; k += chunk_rows)
+          tab_[c++] = ChunkEnt{(uint16_t)ph, (uint16_t)(total - k < chunk_rows ? total - k : chunk_rows), (uint16_t)cb, (uint16_t)(k0 + k)};
+      };
+      for (uint32_t j = TpCut::first(me, C, 0); j < cut.n_q; j += C) put(0, cut.qkv_cb(j), 0, pp->hidden);
+      for (uint32_t j = TpCut::first(me, C, cut.off_o); j < cut.nb_h; j += C) put(1, j, cut.cgi * cut.QCl, cut.QCl);
+      for (uint32_t j = TpCut::first(me, C, 0); j < cut.n_gu; j += C) put(2, cut.gu_cb(j), 0, pp->hidden);
+      for (uint32_t j = TpCut::first(me, C, cut.off_dn); j < cut.n_dn; j += C) {
+        const uint32_t ks = j / cut.nb_h, k0 = ks * pp->sl_dn;
+        put(3, j % cut.nb_h, cut.cgi * cut.FFl + k0, k0 + pp->sl_dn <= cut.FFl ? pp->sl_dn : cut.FFl - k0);
+      }
+      *cnt_sm = c;
+    }
+  }
   // issue the copy of the next chunk into `slot` (called by every thread of the block; thread 0 issues), then move on
   __device__ __forceinline__ void issue(uint8_t* slot, uint64_t* bar) {
-    if (il < p->n_layers) {
+    if (cnt != 0 && il < p->n_layers) {
       if (threadIdx.x == 0) {
         // one copy a chunk: the matrices are described as [k / 64][64][n], so a box of (chunk rows / 64) x 64 x 64 is the
         // chunk's rows in order (at most 256 a dimension); the whole box counts, rows past the matrix filled with zeros
         const ChunkEnt e = tab[ii];
-        tc::mbar_expect_tx(bar, slot_bytes);
+        tc::mbar_expect_tx(bar, p->pbytes[e.phase]);   // what the matrix's descriptor brings
         asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                      ::"r"(tc::smem_u32(slot)), "l"(p->maps + (size_t)il * 4 + e.phase), "r"(tc::smem_u32(bar)), "r"((int32_t)e.cb * DCOLS),
                        "r"(0), "r"((int32_t)(e.k0 / 64)) : "memory");
@@ -803,7 +850,8 @@ __device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, 
         xq[i][1] = (g < MT && kk + 8 < len) ? *reinterpret_cast<const uint32_t*>(arow + kk + 8) : 0u;
       }
 #pragma unroll
-      for (int i = 0; i < HALF_STEPS; ++i) mma_bf16_16816(c[i & 1], wq[i][0], wq[i][1], wq[i][2], wq[i][3], xq[i][0], xq[i][1]);
+      for (int i = 0; i < HALF_STEPS; ++i)               // (a step past the item's k is no product: its slot rows may be another chunk's)
+        if (base + i * 16 < len) mma_bf16_16816(c[i & 1], wq[i][0], wq[i][1], wq[i][2], wq[i][3], xq[i][0], xq[i][1]);
     }
     __syncthreads();                                   // every warp is done with the slot: refill it
     walk.issue(ring + (size_t)head * SLOT_BYTES, &bars[head]);
@@ -1164,6 +1212,367 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
   cluster.sync();   // no block leaves while another may still store into its shared memory
 }
 
+
+// ---- The several-cluster form ----
+// One cluster draws its weights through one GPC's port to the L2 (measured: some 450 bytes a clock for the sixteen blocks
+// together, whether the weights come from DRAM or sit in the L2), so a step's 213 MB of BF16 weights cost a cluster
+// 0.27 ms whatever else it does.  Here `tp` clusters share a step the way tensor-parallel ranks share a layer: cluster c
+// takes heads / tp of the query heads with their key/value heads and ff / tp of the MLP.  QKV, the attention and its merge,
+// gate|up and the activation stay inside a cluster (results handed on by copies onto the receivers' transaction
+// barriers, as in the one-cluster form); the output projection and the down projection give one partial sum a cluster,
+// which go to global memory, and every block of every cluster meets -- a counter in global memory, every wait bounded --
+// before it adds them up in a fixed order.  Two meetings a layer order everything else: a buffer a phase refills was read
+// before the meeting in between.
+// x[i] += parts[0][i] + parts[1][i] + ... (in that order) for i < n, the partial sums read from global memory (through the
+// L2: other blocks wrote them).  Every load of up to four elements a thread is issued before the first sum, so a pass
+// costs one trip to the L2 instead of one a partial sum and element.
+__device__ __forceinline__ void add_parts(float* x, uint32_t n, const float* parts, uint32_t nparts, size_t stride) {
+  constexpr int E = 4, KMAX = 8;
+  for (uint32_t base = 0; base < n; base += E * DT) {
+    float d[E] = {0.f, 0.f, 0.f, 0.f};
+    for (uint32_t k0 = 0; k0 < nparts; k0 += KMAX) {
+      float v[KMAX][E];
+#pragma unroll
+      for (int k = 0; k < KMAX; ++k)
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const uint32_t i = base + e * DT + threadIdx.x;
+          v[k][e] = (k0 + k < nparts && i < n) ? __ldcg(parts + (size_t)(k0 + k) * stride + i) : 0.f;
+        }
+#pragma unroll
+      for (int k = 0; k < KMAX; ++k)
+#pragma unroll
+        for (int e = 0; e < E; ++e)
+          if (k0 + k < nparts) d[e] += v[k][e];
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      const uint32_t i = base + e * DT + threadIdx.x;
+      if (i < n) x[i] = __fadd_rn(x[i], d[e]);
+    }
+  }
+}
+
+__device__ __forceinline__ void tp_meet(unsigned* ctr, unsigned target, bool& dead, uint32_t* dead_sm, long long limit, int* err) {
+  __syncthreads();                                     // the block's stores are issued
+  if (threadIdx.x == 0) {
+    // (the release is cumulative: it covers the stores of the block's other threads, which the barrier above ordered before it)
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
+    if (!dead) {
+      const long long t0 = clock64();
+      for (;;) {
+        unsigned v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+        if (v >= target) break;
+        if (dead_flag_of(err) != 0 || clock64() - t0 > limit) {   // another block gave up, or this wait ran out
+          atomicCAS(err, 0, TIMEOUT_CODE);
+          *dead_sm = 1;
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (*dead_sm) dead = true;                           // the block walks on without waiting, so that the others' meetings are still met
+}
+
+template <int MT>
+__global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p) {
+  constexpr int R = RingDepth<MT>::value;
+  constexpr uint32_t SLOT_BYTES = ChunkBoxes<MT>::value * BOX_BYTES;
+  extern __shared__ __align__(16) float smem[];
+  cg::cluster_group cluster = cg::this_cluster();
+  const uint32_t C = cluster.num_blocks(), me = cluster.block_rank(), cgi = blockIdx.x / C, nblocks = gridDim.x;
+  const int tid = threadIdx.x;
+  const TpCut cut(p, cgi);
+  const uint32_t H = p.hidden, KC = p.kv_heads * HD, QCl = cut.QCl, KCl = cut.KCl, NQl = cut.NQl, FFl = cut.FFl;
+  const uint32_t group = p.heads / p.kv_heads, chunks = p.attend / DCH, att_l = cut.n_att, nparts_dn = p.tp * p.ks_dn;
+  constexpr uint32_t APH = HD + 4, AP = 4 * APH;      // as in the one-cluster form
+  auto per = [&](uint32_t items) { return (items + C - 1) / C; };
+  // shared memory (the same offsets in every block of a cluster); every piece is a whole number of 16 bytes
+  uint8_t* ring = reinterpret_cast<uint8_t*>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)R * SLOT_BYTES);             // [16]
+  uint4* ksm = reinterpret_cast<uint4*>(bars + 16);
+  uint4* vsm = ksm + DCH * 8;
+  float* xres = reinterpret_cast<float*>(vsm + DCH * 8);          // [MT][H]
+  float* qkv = xres + (size_t)MT * H;                             // [MT][NQl]: the cluster's heads, q | k | v
+  float* att = qkv + (size_t)MT * NQl;                            // [att_l][AP]
+  float* osum = att + (size_t)att_l * AP;                         // [MT][H]: the last norm's values
+  float* mw = osum + (size_t)MT * H;                              // [MT * hq][chunks + 1] and [MT * hq] offsets
+  float* qs = mw + (((size_t)MT * cut.hq * (chunks + 2) + 3) & ~(size_t)3);
+  float* ps = qs + 4 * HD;
+  float* stat = ps + 4 * DCH;
+  float* halves = stat + 16;                                      // [2][MT][64]
+  float* sq = halves + 2 * MT * DCOLS;                            // staging, a slot an item of the block: QKV
+  float* sa = sq + (size_t)per(cut.n_q) * MT * DCOLS;             // attention partials
+  float* sg = sa + (size_t)per(att_l) * AP;                       // gate|up, BF16
+  float* g1 = sg + (size_t)per(cut.n_gu) * MT * DCOLS / 2;
+  float* g2 = g1 + H;
+  float* cs = g2 + H;
+  float* sn = cs + HD;
+  DecodeLayerDev* lay = reinterpret_cast<DecodeLayerDev*>(sn + HD);   // [n_layers]
+  ChunkEnt* tab = reinterpret_cast<ChunkEnt*>(lay + p.n_layers);  // [SCHED_MAX]
+  uint32_t* tab_len = reinterpret_cast<uint32_t*>(tab + SCHED_MAX);   // [2]: the list's length; a meeting's wait ran out
+  uint16_t* gu = reinterpret_cast<uint16_t*>(((uintptr_t)(tab_len + 2) + 15) & ~(uintptr_t)15);   // [MT][2 FFl] BF16: gate | up of the cluster's slice
+  uint16_t* vec = gu + (size_t)MT * 2 * FFl;                      // [MT][vec_cols] BF16: a product's A operand
+
+  const int32_t pos = *p.pos;
+  if (pos < 0 || (uint32_t)pos >= p.max_len || (uint32_t)pos >= p.attend) {   // every block sees the same position
+    if (tid == 0) atomicCAS(p.err, 0, 6);
+    return;
+  }
+  for (uint32_t i = tid; i < p.n_layers * (uint32_t)(sizeof(DecodeLayerDev) / 8); i += DT)
+    reinterpret_cast<uint64_t*>(lay)[i] = reinterpret_cast<const uint64_t*>(p.layers)[i];
+  if (tid < HD) { cs[tid] = p.cos[(size_t)pos * HD + tid]; sn[tid] = p.sin[(size_t)pos * HD + tid]; }
+  if (tid == 0) tab_len[1] = 0;
+  WeightWalk walk;
+  walk.start_tp(&p, tab, tab_len, me, C, cut, ChunkBoxes<MT>::value * CK_ROWS);
+  __syncthreads();
+  walk.cnt = *tab_len;
+  for (uint32_t c = tid; c < H; c += DT) g1[c] = bf16_at(lay[0].norm1, c);
+  uint32_t head = 0, parity = 0;
+  bool dead = false;
+  const long long limit = tc::wait_limit_of(p.err);
+  uint64_t* xb = &bars[8];                            // [3]: QKV, attention partials, gate|up
+  const uint32_t expect[3] = {cut.n_q * MT * DCOLS * 4, att_l * group * APH * 4, cut.n_gu * MT * DCOLS * 2};
+  if (tid == 0) {
+    for (int r = 0; r < R; ++r) tc::mbar_init(&bars[r], 1);
+    for (int k = 0; k < 3; ++k) tc::mbar_init(&xb[k], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int k = 0; k < 3; ++k) tc::mbar_expect_tx(&xb[k], expect[k]);   // layer 0's
+  }
+  __syncthreads();
+  cluster.sync();                                      // every block's barriers exist before a copy may name them
+  for (int r = 0; r < R; ++r) walk.issue(ring + (size_t)r * SLOT_BYTES, &bars[r]);
+
+  for (uint32_t l = 0; l < p.n_layers; ++l) {
+    const DecodeLayerDev L = lay[l];
+    auto arrived = [&](int k) {
+      if (!dead && !tc::mbar_wait(&xb[k], l & 1u, &dead_flag_of(p.err), limit)) { dead = true; atomicCAS(p.err, 0, TIMEOUT_CODE); }
+      __syncthreads();
+      if (tid == 0 && l + 1 < p.n_layers) tc::mbar_expect_tx(&xb[k], expect[k]);
+    };
+    float gn[GN];
+#pragma unroll
+    for (int i = 0; i < GN; ++i) gn[i] = tid + i * DT < H ? bf16_at(L.norm2, tid + i * DT) : 0.f;
+    // ---- phase 1: the residual (the clusters' down partials of the layer before, in a fixed order), norm, QKV of the cluster's heads ----
+    if (l == 0) {
+      for (uint32_t i = tid; i < (uint32_t)MT * H; i += DT) xres[i] = i < p.rows * H ? p.x0[i] : 0.f;
+    } else {
+      add_parts(xres, MT * H, p.part_dn, nparts_dn, (size_t)MT * H);
+    }
+    __syncthreads();
+    norm_rows_sm<MT>(xres, H, g1, p.eps, vec, p.vec_cols, stat);
+    {
+      const uint32_t j0 = TpCut::first(me, C, 0);
+      for (uint32_t j = j0; j < cut.n_q; j += C) {
+        float* slot = sq + (size_t)((j - j0) / C) * MT * DCOLS;
+        product_stream<MT, R>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk, halves,
+                              [&](int r, int cc, float t) { slot[r * DCOLS + cc] = bf16_round(t); });
+        if ((uint32_t)tid < C * MT) {
+          const uint32_t d = (uint32_t)tid / MT, r = (uint32_t)tid - d * MT;
+          copy_to_block(qkv + (size_t)r * NQl + j * DCOLS, slot + r * DCOLS, DCOLS * 4, &xb[0], d);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < GN; ++i)
+      if (tid + i * DT < H) g2[tid + i * DT] = gn[i];
+    uint4 kreg[2], vreg[2];
+    auto load_cache = [&](uint32_t it) {
+      const uint32_t ch = it % chunks, kvh = cgi * cut.hk + (it / chunks) % cut.hk, b = it / (chunks * cut.hk);
+      if (ch * DCH > (uint32_t)pos) return;
+      const uint64_t row0 = (uint64_t)b * p.max_len + (uint64_t)ch * DCH;
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const uint32_t i = tid + h2 * DT, j = i >> 3, u = i & 7;
+        kreg[h2] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(L.kc) + (row0 + j) * KC + kvh * HD + u * 8);
+        vreg[h2] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(L.vc) + (row0 + j) * KC + kvh * HD + u * 8);
+      }
+    };
+    const uint32_t it0 = TpCut::first(me, C, cut.off_att);
+    if (it0 < att_l) load_cache(it0);
+    arrived(0);
+
+    // ---- phase 2: the attention of the cluster's heads, an item a (sequence, key/value head, 64 positions) ----
+    for (uint32_t it = it0; it < att_l; it += C) {
+      const uint32_t ch = it % chunks, kvl = (it / chunks) % cut.hk, kvh = cgi * cut.hk + kvl, b = it / (chunks * cut.hk);
+      float* stage = sa + (size_t)((it - it0) / C) * AP;
+      __syncthreads();
+      if (it != it0) load_cache(it);
+      if (ch * DCH > (uint32_t)pos) {
+        for (uint32_t i = tid; i < AP; i += DT) stage[i] = i % APH == HD ? -INFINITY : 0.f;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+        if ((uint32_t)tid < C) copy_to_block(att + (size_t)it * AP, stage, group * APH * 4, &xb[1], (uint32_t)tid);
+        continue;
+      }
+      const float* qrow = qkv + (size_t)b * NQl;
+      for (uint32_t i = tid; i < group * HD; i += DT) {
+        const uint32_t g = i / HD, j = i - g * HD, base = (kvl * group + g) * HD;
+        qs[g * HD + j] = __fadd_rn(__fmul_rn(qrow[base + j], cs[j]), __fmul_rn(qrow[base + (j < HD / 2 ? j + HD / 2 : j - HD / 2)], sn[j]));
+      }
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const uint32_t i = tid + h2 * DT, j = i >> 3, u = i & 7;
+        ksm[j * 8 + (u ^ (j & 7))] = kreg[h2];
+        vsm[j * 8 + (u ^ (j & 7))] = vreg[h2];
+      }
+      __syncthreads();
+      if ((uint32_t)pos / DCH == ch && tid < HD) {
+        const uint32_t j = tid, kb = QCl + kvl * HD, vb = QCl + KCl + kvl * HD, jr = (uint32_t)pos % DCH;
+        const float x = qrow[kb + j], xs = qrow[kb + (j < HD / 2 ? j + HD / 2 : j - HD / 2)];
+        const uint16_t kbits = f32_to_bf16_bits(__float_as_uint(__fadd_rn(__fmul_rn(x, cs[j]), __fmul_rn(xs, sn[j]))));
+        const uint16_t vbits = f32_to_bf16_bits(__float_as_uint(qrow[vb + j]));
+        const uint64_t row = (uint64_t)b * p.max_len + (uint32_t)pos;
+        reinterpret_cast<uint16_t*>(L.kc)[row * KC + kvh * HD + j] = kbits;
+        reinterpret_cast<uint16_t*>(L.vc)[row * KC + kvh * HD + j] = vbits;
+        reinterpret_cast<uint16_t*>(ksm + jr * 8 + ((j >> 3) ^ (jr & 7)))[j & 7] = kbits;
+        reinterpret_cast<uint16_t*>(vsm + jr * 8 + ((j >> 3) ^ (jr & 7)))[j & 7] = vbits;
+      }
+      __syncthreads();
+      const uint32_t g = tid / DCH, j = tid - g * DCH;
+      float sc = -INFINITY;
+      if (g < group && ch * DCH + j <= (uint32_t)pos) {
+        float t4[4] = {0.f, 0.f, 0.f, 0.f};
+        const float* q = qs + g * HD;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const uint4 kq = ksm[j * 8 + (u ^ (j & 7))];
+          const uint32_t w4[4] = {kq.x, kq.y, kq.z, kq.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            t4[e] = fmaf(q[u * 8 + 2 * e], __uint_as_float(w4[e] << 16), t4[e]);
+            t4[e] = fmaf(q[u * 8 + 2 * e + 1], __uint_as_float(w4[e] & 0xffff0000u), t4[e]);
+          }
+        }
+        sc = __fmul_rn((t4[0] + t4[1]) + (t4[2] + t4[3]), p.scale);
+      }
+      float m = sc;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      if ((tid & 31) == 0) stat[tid >> 5] = m;
+      __syncthreads();
+      const float mh = g < group ? fmaxf(fmaxf(stat[2 * g], stat[2 * g + 1]), -3.402823466e38f) : 0.f;
+      const float e = g < group ? expf(sc - mh) : 0.f;
+      if (g < group) ps[g * DCH + j] = e;
+      float sum = e;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      __syncthreads();
+      if ((tid & 31) == 0) stat[8 + (tid >> 5)] = sum;
+      __syncthreads();
+      if (g < group) {
+        const uint32_t d = j;
+        float o4[4] = {0.f, 0.f, 0.f, 0.f};
+        const float* pr = ps + g * DCH;
+#pragma unroll 4
+        for (int jj = 0; jj < DCH; jj += 4) {
+#pragma unroll
+          for (int e2 = 0; e2 < 4; ++e2) {
+            const uint16_t hv = reinterpret_cast<const uint16_t*>(vsm + (jj + e2) * 8 + ((d >> 3) ^ ((jj + e2) & 7)))[d & 7];
+            o4[e2] = fmaf(pr[jj + e2], __uint_as_float((uint32_t)hv << 16), o4[e2]);
+          }
+        }
+        const float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+        const float lsum = stat[8 + 2 * g] + stat[8 + 2 * g + 1];
+        stage[g * APH + d] = o;
+        if (d == 0) { stage[g * APH + HD] = mh; stage[g * APH + HD + 1] = lsum; }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncthreads();
+      if ((uint32_t)tid < C) copy_to_block(att + (size_t)it * AP, stage, group * APH * 4, &xb[1], (uint32_t)tid);
+    }
+    arrived(1);
+
+    // ---- phase 3: the merge of the cluster's heads, and their rows of the output projection: a partial sum a cluster ----
+    uint32_t* mbase = reinterpret_cast<uint32_t*>(mw + (size_t)MT * cut.hq * (chunks + 1));   // [MT * hq]
+    for (uint32_t i = tid; i < (uint32_t)MT * cut.hq; i += DT) {
+      const uint32_t r = MT == 1 ? 0u : i / cut.hq, h = i - r * cut.hq, kvl = h / group, g = h - kvl * group;
+      const float* base = att + (size_t)((r * cut.hk + kvl) * chunks) * AP + g * APH;
+      float M = -3.402823466e38f;
+      for (uint32_t c2 = 0; c2 < chunks; ++c2) M = fmaxf(M, base[(size_t)c2 * AP + HD]);
+      float Lsum = 0.f;
+      for (uint32_t c2 = 0; c2 < chunks; ++c2) {
+        const float wgt = expf(base[(size_t)c2 * AP + HD] - M);
+        mw[(size_t)i * (chunks + 1) + c2] = wgt;
+        Lsum = fmaf(base[(size_t)c2 * AP + HD + 1], wgt, Lsum);
+      }
+      mw[(size_t)i * (chunks + 1) + chunks] = fmaxf(Lsum, 1.175494351e-38f);
+      mbase[i] = (uint32_t)((size_t)((r * cut.hk + kvl) * chunks) * AP + g * APH);
+    }
+    __syncthreads();
+    for (uint32_t i = tid; i < (uint32_t)MT * QCl; i += DT) {
+      const uint32_t r = MT == 1 ? 0u : i / QCl, c = i - r * QCl, h = c / HD, d = c - h * HD;
+      float v = 0.f;
+      if (r < p.rows) {
+        const float* base = att + mbase[r * cut.hq + h];
+        const float* w = mw + (size_t)(r * cut.hq + h) * (chunks + 1);
+        float O = 0.f;
+        for (uint32_t c2 = 0; c2 < chunks; ++c2) O = fmaf(base[(size_t)c2 * AP + d], w[c2], O);
+        v = __fdiv_rn(O, w[chunks]);
+      }
+      vec[(size_t)r * p.vec_cols + c] = f32_to_bf16_bits(__float_as_uint(v));
+    }
+    __syncthreads();
+    for (uint32_t j = TpCut::first(me, C, cut.off_o); j < cut.nb_h; j += C) {
+      float* dst = p.part_o + (size_t)cgi * MT * H + j * DCOLS;
+      product_stream<MT, R>(vec, p.vec_cols, QCl, ring, bars, head, parity, dead, limit, p.err, walk, halves,
+                            [&](int r, int cc, float t) { dst[(size_t)r * H + cc] = t; });
+    }
+    tp_meet(p.gbar, (2 * l + 1) * nblocks, dead, &tab_len[1], limit, p.err);   // every cluster's partial is in global memory
+
+    // ---- phase 4: the residual, norm, the cluster's gate and up columns ----
+    add_parts(xres, MT * H, p.part_o, p.tp, (size_t)MT * H);
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < GN; ++i) gn[i] = l + 1 < p.n_layers && tid + i * DT < H ? bf16_at(lay[l + 1].norm1, tid + i * DT) : 0.f;
+    norm_rows_sm<MT>(xres, H, g2, p.eps, vec, p.vec_cols, stat);
+    {
+      const uint32_t j0 = TpCut::first(me, C, 0);
+      for (uint32_t j = j0; j < cut.n_gu; j += C) {
+        uint16_t* slot = reinterpret_cast<uint16_t*>(sg) + (size_t)((j - j0) / C) * MT * DCOLS;
+        product_stream<MT, R>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk, halves, [&](int r, int cc, float t) {
+          slot[r * DCOLS + cc] = f32_to_bf16_bits(__float_as_uint(t));
+        });
+        if ((uint32_t)tid < C * MT) {
+          const uint32_t d = (uint32_t)tid / MT, r = (uint32_t)tid - d * MT;
+          copy_to_block(gu + (size_t)r * 2 * FFl + j * DCOLS, slot + r * DCOLS, DCOLS * 2, &xb[2], d);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < GN; ++i)
+      if (tid + i * DT < H) g1[tid + i * DT] = gn[i];
+    arrived(2);
+
+    // ---- phase 5: the activation of the cluster's slice of ff and its rows of the down projection: a partial a (cluster, slice) ----
+    for (uint32_t j = TpCut::first(me, C, cut.off_dn); j < cut.n_dn; j += C) {
+      const uint32_t cb = j % cut.nb_h, ks = j / cut.nb_h, k0 = ks * p.sl_dn;
+      const uint32_t len = k0 + p.sl_dn <= FFl ? p.sl_dn : FFl - k0;
+      __syncthreads();
+      for (uint32_t i = tid; i < (uint32_t)MT * len; i += DT) {
+        const uint32_t r = MT == 1 ? 0u : i / len, kk = i - r * len;
+        const float a = __uint_as_float((uint32_t)gu[(size_t)r * 2 * FFl + k0 + kk] << 16);
+        const float bq = __uint_as_float((uint32_t)gu[(size_t)r * 2 * FFl + FFl + k0 + kk] << 16);
+        vec[(size_t)r * p.vec_cols + kk] = f32_to_bf16_bits(__float_as_uint(__fmul_rn(__fmul_rn(a, sigmoid_flex(a)), bq)));
+      }
+      __syncthreads();
+      float* dst = p.part_dn + ((size_t)cgi * p.ks_dn + ks) * MT * H + cb * DCOLS;
+      product_stream<MT, R>(vec, p.vec_cols, len, ring, bars, head, parity, dead, limit, p.err, walk, halves,
+                            [&](int r, int cc, float t) { dst[(size_t)r * H + cc] = t; });
+    }
+    tp_meet(p.gbar, (2 * l + 2) * nblocks, dead, &tab_len[1], limit, p.err);
+  }
+  if (blockIdx.x == 0) {
+    add_parts(xres, MT * H, p.part_dn, nparts_dn, (size_t)MT * H);
+    __syncthreads();
+    norm_rows<MT>(xres, H, p.final_norm, p.eps, osum, H, stat);
+    for (uint32_t i = tid; i < p.rows * H; i += DT) p.out[i] = f32_to_bf16_bits(__float_as_uint(osum[i]));
+  }
+  cluster.sync();   // no block leaves while another may still store into its shared memory
+}
+
 template <int MT>
 cudaError_t launch_cluster(const ClusterParams& p, size_t smem, int* cluster_blocks, cudaStream_t stream) {
   // the widest cluster the device will schedule: sixteen blocks (beyond the portable eight), else eight
@@ -1201,6 +1610,46 @@ cudaError_t launch_cluster(const ClusterParams& p, size_t smem, int* cluster_blo
   return cudaLaunchKernelEx(&cfg, decode_cluster_kernel<MT>, p);
 }
 
+// The several-cluster form's launch: `p.tp` clusters of the widest width the device holds all at once (every block meets
+// every other twice a layer, so the launch is made only where the occupancy figure says they are resident together;
+// the meetings' waits are bounded all the same).
+template <int MT>
+cudaError_t launch_tp(const ClusterParams& p, size_t smem, int* cluster_blocks, cudaStream_t stream) {
+  cudaError_t e = ensure_dynamic_smem((const void*)decode_tp_kernel<MT>, smem);
+  if (e != cudaSuccess) return e;
+  int found = 0;                                       // width * 256 + clusters the device holds at once
+  if (!device_value_get((const void*)decode_tp_kernel<MT>, &found)) {
+    found = 0;
+    for (int c : {16, 8}) {
+      if ((uint32_t)c < p.min_width) continue;
+      if (c > 8 && cudaFuncSetAttribute((const void*)decode_tp_kernel<MT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+        cudaGetLastError();
+        continue;
+      }
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(c * p.tp); cfg.blockDim = dim3(DT); cfg.dynamicSmemBytes = smem;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = c; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+      cfg.attrs = at; cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, decode_tp_kernel<MT>, &cfg) == cudaSuccess && n >= (int)p.tp) { found = c * 256 + (n > 255 ? 255 : n); break; }
+      cudaGetLastError();
+    }
+    device_value_set((const void*)decode_tp_kernel<MT>, found);
+  }
+  const int width = found / 256, held = found % 256;
+  if (width < 8 || (uint32_t)width < p.min_width || held < (int)p.tp) return cudaErrorNotSupported;
+  *cluster_blocks = width;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(width * p.tp); cfg.blockDim = dim3(DT); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = width; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, decode_tp_kernel<MT>, p);
+}
+
 uint32_t slices_for(uint32_t col_blocks, uint32_t k, uint32_t grid, uint32_t* slice_len) {
   // Slices of k so that a phase's items (column blocks x slices) come to about one a block: as many slices as fit the
   // grid, at least as many as keep a slice within the tile fetched ahead, at most 8; slices of whole 32-row steps.
@@ -1216,74 +1665,6 @@ uint32_t slices_for(uint32_t col_blocks, uint32_t k, uint32_t grid, uint32_t* sl
 }
 
 }  // namespace
-
-bool decode_layers_supported(const DecodeShape& sh, const char** why) {
-  *why = "";
-  if (sh.rows < 1 || sh.rows > 4) { *why = "one to four sequences a step"; return false; }
-  if (sh.head_dim != HD) { *why = "heads of 64 columns"; return false; }
-  if (sh.heads == 0 || sh.kv_heads == 0 || sh.heads % sh.kv_heads || sh.heads / sh.kv_heads > 4) { *why = "one to four query heads a key/value head"; return false; }
-  if (sh.hidden % 64 || sh.ff % 64 || sh.hidden == 0 || sh.ff == 0) { *why = "hidden and ff in whole 64-column blocks"; return false; }
-  if (sh.attend == 0 || sh.attend % DCH || sh.attend > sh.max_len) { *why = "attended positions in whole chunks of 64 inside the cache"; return false; }
-  return true;
-}
-
-DecodeScratch decode_layers_scratch(const DecodeShape& sh, int grid) {
-  DecodeScratch d{};
-  const uint32_t MT = sh.rows <= 1 ? 1 : (sh.rows <= 2 ? 2 : 4);
-  const uint32_t QC = sh.heads * HD, KC = sh.kv_heads * HD, NQKV = QC + 2 * KC;
-  d.ks_qkv = slices_for(NQKV / DCOLS, sh.hidden, grid, &d.sl_qkv);
-  d.ks_o = slices_for(sh.hidden / DCOLS, QC, grid, &d.sl_o);
-  d.ks_gu = slices_for(2 * sh.ff / DCOLS, sh.hidden, grid, &d.sl_gu);
-  d.ks_dn = slices_for(sh.hidden / DCOLS, sh.ff, grid, &d.sl_dn);
-  uint64_t off = 0;
-  auto take = [&](uint64_t floats) { const uint64_t at = off; off += (floats + 63) / 64 * 64; return at; };
-  d.off_qkv = take((uint64_t)d.ks_qkv * MT * NQKV);
-  d.off_att = take((uint64_t)sh.rows * sh.kv_heads * (sh.attend / DCH) * 4 * (HD + 2));
-  d.off_o = take((uint64_t)d.ks_o * MT * sh.hidden);
-  d.off_gu = take((uint64_t)d.ks_gu * MT * 2 * sh.ff);
-  d.off_dn = take((uint64_t)d.ks_dn * MT * sh.hidden);
-  d.off_bar = take(64);
-  d.floats = off;
-  return d;
-}
-
-// The tiled-copy descriptors of the layers' matrices, for the cluster form: four a layer, each over the stored [k, n]
-// (BF16) as [k / 64][64][n] with a box of a chunk's rows by 64 columns, 128-byte swizzled.  False where the driver has no encoder.
-size_t decode_layers_maps_bytes(const DecodeShape& sh) { return (size_t)sh.layers * 4 * sizeof(CUtensorMap); }
-bool decode_layers_make_maps(const DecodeShape& sh, const DecodeLayerPtrs* recs, void* maps_host) {
-  const uint32_t MTm = sh.rows <= 1 ? 1 : (sh.rows <= 2 ? 2 : 4);
-  tc::EncodeTiledFn fn = tc::encode_fn();
-  if (!fn) return false;
-  CUtensorMap* maps = reinterpret_cast<CUtensorMap*>(maps_host);
-  const uint64_t H = sh.hidden, QC = (uint64_t)sh.heads * HD, KC = (uint64_t)sh.kv_heads * HD, FF = sh.ff;
-  const uint64_t kn[4][2] = {{H, QC + 2 * KC}, {QC, H}, {H, 2 * FF}, {FF, H}};
-  for (uint32_t l = 0; l < sh.layers; ++l) {
-    const void* w[4] = {recs[l].qkv, recs[l].o, recs[l].gate_up, recs[l].down};
-    for (int i = 0; i < 4; ++i) {
-      if ((recs[l].bfp >> i) & 1u) return false;        // the cluster form multiplies BF16 tiles where they land
-      // [k, n] seen as [k / 64][64][n]: a box of (a chunk's rows / 64) x 64 rows x 64 columns lands as the chunk's rows in order
-      const cuuint64_t dims[3] = {kn[i][1], 64, (kn[i][0] + 63) / 64};
-      const cuuint64_t strides[2] = {kn[i][1] * 2u, kn[i][1] * 2u * 64u};
-      const cuuint32_t box[3] = {(cuuint32_t)DCOLS, 64u, (cuuint32_t)(chunk_rows_of(MTm) / 64)};
-      const cuuint32_t estr[3] = {1, 1, 1};
-      if (kn[i][0] % 64) return false;
-      if (fn(&maps[(size_t)l * 4 + i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(w[i]),
-             dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return false;
-    }
-  }
-  return true;
-}
-
-int decode_layers_grid() {
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const char* e = getenv("B200TT_DECODE_GRID");   // a development switch
-  const int want = e ? atoi(e) : 128;            // measured on SmolLM2-135M's shape: 64, 96, 128 blocks give 1.12, 1.05, 0.98 ms a step
-  return want >= 1 && want <= sms ? want : (sms < 128 ? sms : 128);
-}
 
 namespace {
 // What the cluster form needs of a shape: its buffers in a block's shared memory, its per-layer list of chunks within the
@@ -1304,6 +1685,7 @@ bool cluster_plan(const DecodeShape& sh, ClusterParams& c, size_t* smem) {
   vc = (vc + 7) / 8 * 8;
   c.vec_cols = vc;
   c.att_items = att_items;
+  for (int i = 0; i < 4; ++i) c.pbytes[i] = chunk_rows_of(MTc) * 128;
   const size_t ring_slots = MTc == 1 ? RingDepth<1>::value : (MTc == 2 ? RingDepth<2>::value : RingDepth<4>::value);
   const uint32_t chunk_rows = chunk_rows_of(MTc);
   const size_t SLOT_BYTES = (size_t)chunk_rows * 128;
@@ -1329,18 +1711,151 @@ bool cluster_plan(const DecodeShape& sh, ClusterParams& c, size_t* smem) {
          merge_words <= (uint64_t)c.ks_dn * sh.hidden &&
          nbg >= 16 && nbd >= 16;                         // every block has gate|up and down items: what orders the blocks (see the kernel)
 }
+
+// The several-cluster form's plan: how many clusters share a step (the most of 4, 3, 2 that cut the heads, the key/value
+// heads and ff's 64-column blocks evenly), the down projection's slices of a cluster's share of ff, the rows a chunk's copy
+// brings of each matrix, and a block's shared memory.  False where no cut or no plan fits.
+struct TpPlan { uint32_t G, ks, sl, vc, att_items, min_width, cr[4]; size_t smem; };
+bool tp_plan(const DecodeShape& sh, TpPlan* t) {
+  const uint32_t MTc = sh.rows <= 1 ? 1 : (sh.rows <= 2 ? 2 : 4);
+  const char* e = getenv("B200TT_DECODE_TP");          // a development switch: that many clusters, or none (1)
+  const uint32_t forced = e ? (uint32_t)atoi(e) : 0;
+  uint32_t G = 0;
+  for (uint32_t g : {4u, 3u, 2u}) {
+    if (forced && g != forced) continue;
+    if (sh.heads % g == 0 && sh.kv_heads % g == 0 && sh.ff % (DCOLS * g) == 0) { G = g; break; }
+  }
+  if (!G || sh.hidden % DCOLS) return false;
+  const uint32_t hq = sh.heads / G, hk = sh.kv_heads / G, QCl = hq * HD, NQl = QCl + 2 * hk * HD, FFl = sh.ff / G, chunks = sh.attend / DCH;
+  const uint32_t att_l = sh.rows * hk * chunks;
+  const uint32_t want_rows = MTc == 1 ? 576u : 768u;
+  uint32_t ks = (FFl + want_rows - 1) / want_rows;
+  if (ks < 1) ks = 1;
+  const uint32_t sl = ((FFl + ks - 1) / ks + 63) / 64 * 64;
+  ks = (FFl + sl - 1) / sl;
+  uint32_t vc = sh.hidden > QCl ? sh.hidden : QCl;
+  if (sl > vc) vc = sl;
+  vc = (vc + 7) / 8 * 8;
+  const uint32_t chunk_rows = chunk_rows_of(MTc);
+  const uint32_t rows_of[4] = {sh.hidden, QCl, sh.hidden, sl};
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t r64 = (rows_of[i] + 63) / 64 * 64;
+    t->cr[i] = r64 < chunk_rows ? r64 : chunk_rows;
+  }
+  t->G = G; t->ks = ks; t->sl = sl; t->vc = vc; t->att_items = att_l;
+  const size_t ring_slots = MTc == 1 ? RingDepth<1>::value : (MTc == 2 ? RingDepth<2>::value : RingDepth<4>::value);
+  const size_t SLOT_BYTES = (size_t)chunk_rows * 128;
+  const uint64_t n_q = hq + 2 * hk, nb_h = sh.hidden / DCOLS, n_gu = 2 * FFl / DCOLS, n_dn = nb_h * ks;
+  constexpr uint64_t AP = 4 * (HD + 4);
+  for (uint32_t width : {8u, 16u}) {
+    auto per = [&](uint64_t items) { return (items + width - 1) / width; };
+    const size_t stage = per(n_q) * MTc * DCOLS + per(att_l) * AP + per(n_gu) * MTc * DCOLS / 2;
+    t->smem = 1024 + ring_slots * SLOT_BYTES + 16 * sizeof(uint64_t) + 2 * DCH * 8 * sizeof(uint4) +
+              ((size_t)MTc * sh.hidden * 2 + (size_t)MTc * NQl + (size_t)att_l * AP + (((size_t)MTc * hq * (chunks + 2) + 3) & ~(size_t)3) +
+               4 * HD + 4 * DCH + 16 + 2 * MTc * DCOLS + stage + 2 * sh.hidden + 2 * HD) * sizeof(float) +
+              (size_t)sh.layers * sizeof(DecodeLayerDev) + SCHED_MAX * sizeof(ChunkEnt) + 8 + 16 +
+              ((size_t)MTc * 2 * FFl + (size_t)MTc * vc) * sizeof(uint16_t);
+    t->min_width = width;
+    if (t->smem <= 224 * 1024) break;
+  }
+  auto chunks_of = [&](uint64_t items, uint32_t rows) { return (uint64_t)((items + 7) / 8) * ((rows + chunk_rows - 1) / chunk_rows); };
+  const uint64_t sched = chunks_of(n_q, sh.hidden) + chunks_of(nb_h, QCl) + chunks_of(n_gu, sh.hidden) + chunks_of(n_dn, sl);
+  return t->smem <= 224 * 1024 && sh.hidden <= (uint32_t)GN * DT && sched <= SCHED_MAX && sh.ff < 65536 && 2 * sh.ff / DCOLS < 65536;
+}
+
+// Which form a step of BF16 matrices takes: 2 several clusters, 1 one cluster, 0 the grid.  B200TT_DECODE=grid and
+// B200TT_DECODE=one force the grid and the one-cluster form (development switches; the tests run all three).
+int cluster_form_of(const DecodeShape& sh, TpPlan* t) {
+  const char* form = getenv("B200TT_DECODE");
+  if (form && form[0] == 'g') return 0;
+  if (!(form && form[0] == 'o') && tp_plan(sh, t)) return 2;
+  ClusterParams c{};
+  size_t smem = 0;
+  return cluster_plan(sh, c, &smem) ? 1 : 0;
+}
 }  // namespace
+
+bool decode_layers_supported(const DecodeShape& sh, const char** why) {
+  *why = "";
+  if (sh.rows < 1 || sh.rows > 4) { *why = "one to four sequences a step"; return false; }
+  if (sh.head_dim != HD) { *why = "heads of 64 columns"; return false; }
+  if (sh.heads == 0 || sh.kv_heads == 0 || sh.heads % sh.kv_heads || sh.heads / sh.kv_heads > 4) { *why = "one to four query heads a key/value head"; return false; }
+  if (sh.hidden % 64 || sh.ff % 64 || sh.hidden == 0 || sh.ff == 0) { *why = "hidden and ff in whole 64-column blocks"; return false; }
+  if (sh.attend == 0 || sh.attend % DCH || sh.attend > sh.max_len) { *why = "attended positions in whole chunks of 64 inside the cache"; return false; }
+  return true;
+}
+
+DecodeScratch decode_layers_scratch(const DecodeShape& sh, int grid) {
+  DecodeScratch d{};
+  const uint32_t MT = sh.rows <= 1 ? 1 : (sh.rows <= 2 ? 2 : 4);
+  const uint32_t QC = sh.heads * HD, KC = sh.kv_heads * HD, NQKV = QC + 2 * KC;
+  d.ks_qkv = slices_for(NQKV / DCOLS, sh.hidden, grid, &d.sl_qkv);
+  d.ks_o = slices_for(sh.hidden / DCOLS, QC, grid, &d.sl_o);
+  d.ks_gu = slices_for(2 * sh.ff / DCOLS, sh.hidden, grid, &d.sl_gu);
+  d.ks_dn = slices_for(sh.hidden / DCOLS, sh.ff, grid, &d.sl_dn);
+  uint64_t off = 0;
+  auto take = [&](uint64_t floats) { const uint64_t at = off; off += (floats + 63) / 64 * 64; return at; };
+  d.off_qkv = take((uint64_t)d.ks_qkv * MT * NQKV);
+  d.off_att = take((uint64_t)sh.rows * sh.kv_heads * (sh.attend / DCH) * 4 * (HD + 2));
+  TpPlan t{};                                          // the several-cluster form keeps a partial a cluster (and slice) in the same places
+  const bool tp = tp_plan(sh, &t);
+  const uint32_t parts_o = tp && t.G > d.ks_o ? t.G : d.ks_o, parts_dn = tp && t.G * t.ks > d.ks_dn ? t.G * t.ks : d.ks_dn;
+  d.off_o = take((uint64_t)parts_o * MT * sh.hidden);
+  d.off_gu = take((uint64_t)d.ks_gu * MT * 2 * sh.ff);
+  d.off_dn = take((uint64_t)parts_dn * MT * sh.hidden);
+  d.off_bar = take(64);
+  d.floats = off;
+  return d;
+}
+
+// The tiled-copy descriptors of the layers' matrices, for the cluster form: four a layer, each over the stored [k, n]
+// (BF16) as [k / 64][64][n] with a box of a chunk's rows by 64 columns, 128-byte swizzled.  False where the driver has no encoder.
+size_t decode_layers_maps_bytes(const DecodeShape& sh) { return (size_t)sh.layers * 4 * sizeof(CUtensorMap); }
+bool decode_layers_make_maps(const DecodeShape& sh, const DecodeLayerPtrs* recs, void* maps_host) {
+  const uint32_t MTm = sh.rows <= 1 ? 1 : (sh.rows <= 2 ? 2 : 4);
+  TpPlan t{};
+  const int form = cluster_form_of(sh, &t);            // the several-cluster form's chunks are as deep as its items' k
+  tc::EncodeTiledFn fn = tc::encode_fn();
+  if (!fn) return false;
+  CUtensorMap* maps = reinterpret_cast<CUtensorMap*>(maps_host);
+  const uint64_t H = sh.hidden, QC = (uint64_t)sh.heads * HD, KC = (uint64_t)sh.kv_heads * HD, FF = sh.ff;
+  const uint64_t kn[4][2] = {{H, QC + 2 * KC}, {QC, H}, {H, 2 * FF}, {FF, H}};
+  for (uint32_t l = 0; l < sh.layers; ++l) {
+    const void* w[4] = {recs[l].qkv, recs[l].o, recs[l].gate_up, recs[l].down};
+    for (int i = 0; i < 4; ++i) {
+      if ((recs[l].bfp >> i) & 1u) return false;        // the cluster form multiplies BF16 tiles where they land
+      // [k, n] seen as [k / 64][64][n]: a box of (a chunk's rows / 64) x 64 rows x 64 columns lands as the chunk's rows in order
+      const cuuint64_t dims[3] = {kn[i][1], 64, (kn[i][0] + 63) / 64};
+      const cuuint64_t strides[2] = {kn[i][1] * 2u, kn[i][1] * 2u * 64u};
+      const cuuint32_t box[3] = {(cuuint32_t)DCOLS, 64u, (cuuint32_t)((form == 2 ? t.cr[i] : chunk_rows_of(MTm)) / 64)};
+      const cuuint32_t estr[3] = {1, 1, 1};
+      if (kn[i][0] % 64) return false;
+      if (fn(&maps[(size_t)l * 4 + i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(w[i]),
+             dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    }
+  }
+  return true;
+}
+
+int decode_layers_grid() {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const char* e = getenv("B200TT_DECODE_GRID");   // a development switch
+  const int want = e ? atoi(e) : 128;            // measured on SmolLM2-135M's shape: 64, 96, 128 blocks give 1.12, 1.05, 0.98 ms a step
+  return want >= 1 && want <= sms ? want : (sms < 128 ? sms : 128);
+}
+
 
 // Which form a step takes.  The cluster form where its plan fits and every matrix is BF16 (its products are tensor-core
 // tiles of BF16 as the copies land them); with BFP8 weights every datum is decoded on the ALUs, and the grid's 128 blocks
 // do that twice as fast as sixteen (measured 1.33 against 2.66 ms a step).  B200TT_DECODE=grid forces the grid form (a
 // development switch; the tests run both).
 bool decode_layers_cluster_wanted(const DecodeShape& sh, bool any_bfp) {
-  const char* form = getenv("B200TT_DECODE");
-  if ((form && form[0] == 'g') || any_bfp) return false;
-  ClusterParams c{};
-  size_t smem = 0;
-  return cluster_plan(sh, c, &smem);
+  TpPlan t{};
+  return !any_bfp && cluster_form_of(sh, &t) != 0;
 }
 
 cudaError_t launch_decode_layers(const DecodeShape& sh, const DecodeLayerPtrs* layers_dev, const float* x0, const void* final_norm,
@@ -1351,7 +1866,30 @@ cudaError_t launch_decode_layers(const DecodeShape& sh, const DecodeLayerPtrs* l
   // grid form otherwise.
   ClusterParams c{};
   size_t smem_c = 0;
-  if (maps_dev && cluster_plan(sh, c, &smem_c)) {
+  TpPlan t{};
+  const int want = maps_dev ? cluster_form_of(sh, &t) : 0;
+  if (want == 2) {
+    const uint32_t MTc = sh.rows <= 1 ? 1 : (sh.rows <= 2 ? 2 : 4);
+    c.n_layers = sh.layers; c.rows = sh.rows; c.hidden = sh.hidden; c.heads = sh.heads; c.kv_heads = sh.kv_heads; c.ff = sh.ff;
+    c.max_len = sh.max_len; c.attend = sh.attend; c.eps = sh.eps; c.scale = sh.scale;
+    c.ks_dn = t.ks; c.sl_dn = t.sl; c.vec_cols = t.vc; c.att_items = t.att_items; c.min_width = t.min_width; c.tp = t.G;
+    for (int i = 0; i < 4; ++i) c.pbytes[i] = t.cr[i] * 128;
+    c.layers = reinterpret_cast<const DecodeLayerDev*>(layers_dev);
+    c.x0 = x0; c.final_norm = final_norm; c.cos = cos_t; c.sin = sin_t; c.pos = pos; c.out = out; c.err = err;
+    c.maps = reinterpret_cast<const CUtensorMap*>(maps_dev);
+    c.part_o = scratch + d.off_o; c.part_dn = scratch + d.off_dn; c.gbar = reinterpret_cast<unsigned*>(scratch + d.off_bar);
+    cudaError_t ce = cudaMemsetAsync(c.gbar, 0, 64 * sizeof(float), stream);   // the meetings' counter starts at zero
+    if (ce != cudaSuccess) return ce;
+    int width = 0;
+    ce = MTc == 1 ? launch_tp<1>(c, t.smem, &width, stream) : (MTc == 2 ? launch_tp<2>(c, t.smem, &width, stream) : launch_tp<4>(c, t.smem, &width, stream));
+    if (ce != cudaErrorNotSupported) {
+      static const char* const names[2][3] = {{"cluster8x2", "cluster8x3", "cluster8x4"}, {"cluster16x2", "cluster16x3", "cluster16x4"}};
+      *form = names[width == 16][t.G - 2];
+      return ce;
+    }
+    // (the descriptors were built for this form's chunks: the one-cluster form cannot use them, the grid form needs none)
+  }
+  if (want == 1 && cluster_plan(sh, c, &smem_c)) {
     const uint32_t MTc = sh.rows <= 1 ? 1 : (sh.rows <= 2 ? 2 : 4);
     c.layers = reinterpret_cast<const DecodeLayerDev*>(layers_dev);
     c.x0 = x0; c.final_norm = final_norm; c.cos = cos_t; c.sin = sin_t; c.pos = pos; c.out = out; c.err = err;

@@ -227,10 +227,10 @@ def test_a_prompt_prefilled_in_chunks_is_the_prompt_prefilled_at_once(eng):
 
 @pytest.mark.parametrize("batch", [1, 2, 4])
 @pytest.mark.parametrize("storage", ["bf16", "bfp8"])
-@pytest.mark.parametrize("form", ["cluster", "grid"])
+@pytest.mark.parametrize("form", ["cluster", "one", "grid"])
 def test_the_one_launch_step_is_the_composed_step(eng, batch, storage, form, monkeypatch):
-    # `decode_layers` (one launch for every layer of a step, as one thread-block cluster or as a cooperative grid: the
-    # switch is read at every call) against the step composed of the trait's ops:
+    # `decode_layers` (one launch for every layer of a step: as several thread-block clusters that share the heads and ff,
+    # as one cluster, or as a cooperative grid: the switch is read at every call) against the step composed of the trait's ops:
     # the same steps and roundings, sums in another fixed order, so the two agree as two correct BF16 evaluations do
     # (see the tolerance below), the cache rows to one BF16 step, and the choices wherever the composed step's margin is
     # clear.  Both are fed the same tokens.  With BFP8 weights both read the same compressed matrices.
@@ -265,8 +265,15 @@ def test_the_one_launch_step_is_the_composed_step(eng, batch, storage, form, mon
     # element is held to the 2e-2 the cached steps are held to, and the typical one to a fraction of it
     assert worst <= 2e-2 and total / steps <= 1.5e-3, (worst, total / steps)
     assert fused_launches <= 12                        # embedding, cast, the layers, head, argmax, bookkeeping
-    # "cluster16" / "cluster8" / "grid"; BFP8 matrices always take the grid form (the cluster form multiplies BF16 tiles)
-    assert eng.last_decode_form().startswith("grid" if storage == "bfp8" else form)
+    # "cluster16x3" (three clusters of sixteen blocks: this shape's nine heads over three key/value heads) / "cluster16" /
+    # "grid"; BFP8 matrices always take the grid form (the cluster forms multiply BF16 tiles)
+    took = eng.last_decode_form()
+    if storage == "bfp8" or form == "grid":
+        assert took == "grid"
+    elif form == "one":
+        assert took in ("cluster16", "cluster8")
+    else:
+        assert took in ("cluster16x3", "cluster8x3")
     for l in range(cfg.layers):
         for mine, theirs in ((fused.kc[l], composed.kc[l]), (fused.vc[l], composed.vc[l])):
             x = orc.from_bf16(eng.download_bf16(mine)).reshape(batch, max_len, -1)
