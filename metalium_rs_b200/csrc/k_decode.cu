@@ -689,9 +689,10 @@ struct ClusterParams {
   // the several-cluster form only
   uint32_t tp;               // clusters a step: each takes 1/tp of the heads and of ff
   uint32_t pbytes[4];        // bytes one tiled copy of a chunk lands, by matrix (the box of that matrix's descriptors)
-  float* part_o;             // [tp][MT][hidden]: a cluster's share of the attention output's projection
-  float* part_dn;            // [tp * ks_dn][MT][hidden]: and of the down projection, a slice of k each
-  unsigned* gbar;            // the count of blocks that reached a meeting (zero at launch)
+  // a cluster's partial sums, in global memory, every element an 8-byte word {value, layer + 1}, two copies used by
+  // the layers in turn, all words zero at launch
+  unsigned long long* part_o;    // [2][tp][MT][hidden]: a cluster's share of the attention output's projection
+  unsigned long long* part_dn;   // [2][tp * ks_dn][MT][hidden]: and of the down projection, a slice of k each
 };
 
 constexpr int CK_ROWS = 192;                           // k-rows of a tiled copy's box (at most 256)
@@ -1214,36 +1215,58 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
 
 
 // ---- The several-cluster form ----
-// One cluster draws its weights through one GPC's port to the L2 (measured: some 450 bytes a clock for the sixteen blocks
-// together, whether the weights come from DRAM or sit in the L2), so a step's 213 MB of BF16 weights cost a cluster
-// 0.27 ms whatever else it does.  Here `tp` clusters share a step the way tensor-parallel ranks share a layer: cluster c
-// takes heads / tp of the query heads with their key/value heads and ff / tp of the MLP.  QKV, the attention and its merge,
-// gate|up and the activation stay inside a cluster (results handed on by copies onto the receivers' transaction
-// barriers, as in the one-cluster form); the output projection and the down projection give one partial sum a cluster,
-// which go to global memory, and every block of every cluster meets -- a counter in global memory, every wait bounded --
-// before it adds them up in a fixed order.  Two meetings a layer order everything else: a buffer a phase refills was read
-// before the meeting in between.
-// x[i] += parts[0][i] + parts[1][i] + ... (in that order) for i < n, the partial sums read from global memory (through the
-// L2: other blocks wrote them).  Every load of up to four elements a thread is issued before the first sum, so a pass
-// costs one trip to the L2 instead of one a partial sum and element.
-__device__ __forceinline__ void add_parts(float* x, uint32_t n, const float* parts, uint32_t nparts, size_t stride) {
-  constexpr int E = 4, KMAX = 8;
+// One cluster draws its weights through one GPC's port to the L2, so sixteen blocks stream a step's 213 MB of BF16 weights
+// no faster than some 0.3 ms whatever else they do, and a phase with fewer items than blocks leaves blocks idle.  Here `tp`
+// clusters share a step the way tensor-parallel ranks share a layer: cluster c takes heads / tp of the query heads with their
+// key/value heads and ff / tp of the MLP.  QKV, the attention and its merge, gate|up and the activation stay inside a
+// cluster (results handed on by copies onto the receivers' transaction barriers, as in the one-cluster form); the output
+// projection and the down projection give one partial sum a cluster (and slice of k), which every block of every cluster
+// needs.  Those go through global memory, and a trip to the L2 and back costs some 2,000 cycles here (the two dies), so an
+// exchange is ONE trip after the data is there: an element travels as an 8-byte word {value, layer + 1}, stored and loaded
+// whole, and a reader polls the very words it needs until each carries the layer's tag -- no counter to wait for and then
+// the data to fetch, no fence.  What orders the blocks is the data itself: every block has a gate|up item and a down item
+// (the plan sees to it), so the down partials of layer l are whole only after every block has read what layer l sent it and
+// armed its barriers for l + 1, and nothing of layer l + 1 is sent before some block has the down partials of layer l; the
+// partials' two copies are used by the layers in turn, since a block with nothing to do but gate|up and down may read
+// layer l's down partials while another cluster already writes layer l + 1's.  Every poll is bounded.
+__device__ __forceinline__ void st_tagged(unsigned long long* dst, float v, uint32_t tag) {
+  const unsigned long long w = ((unsigned long long)tag << 32) | __float_as_uint(v);
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(dst), "l"(w) : "memory");
+}
+// x[i] += parts[0][i] + parts[1][i] + ... (in that order) for i < n, once every word carries `tag`.  A thread asks for all
+// the words of up to four of its elements at once, so a pass costs one trip to the L2 once the data is there.
+__device__ __forceinline__ void add_parts_tagged(float* x, uint32_t n, const unsigned long long* parts, uint32_t nparts, size_t stride,
+                                                 uint32_t tag, bool& dead, long long limit, int* err) {
+  constexpr int E = 4, KMAX = 4;
   for (uint32_t base = 0; base < n; base += E * DT) {
     float d[E] = {0.f, 0.f, 0.f, 0.f};
     for (uint32_t k0 = 0; k0 < nparts; k0 += KMAX) {
-      float v[KMAX][E];
+      unsigned long long w[KMAX][E];
+      long long t0 = 0;
+      for (uint32_t spins = 0;; ++spins) {
+        bool ok = true;
 #pragma unroll
-      for (int k = 0; k < KMAX; ++k)
+        for (int k = 0; k < KMAX; ++k)
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
-          const uint32_t i = base + e * DT + threadIdx.x;
-          v[k][e] = (k0 + k < nparts && i < n) ? __ldcg(parts + (size_t)(k0 + k) * stride + i) : 0.f;
+          for (int e = 0; e < E; ++e) {                 // no load is conditional (an index past the end reads the last word again)
+            const uint32_t i = base + e * DT + threadIdx.x, kk = k0 + k < nparts ? k0 + k : nparts - 1;
+            asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w[k][e]) : "l"(parts + (size_t)kk * stride + (i < n ? i : n - 1)) : "memory");
+          }
+#pragma unroll
+        for (int k = 0; k < KMAX; ++k)
+#pragma unroll
+          for (int e = 0; e < E; ++e) ok = ok && (uint32_t)(w[k][e] >> 32) == tag;
+        if (ok || dead) break;
+        if ((spins & 15u) == 15u) {                     // the wait is bounded: by the engine's limit, and by another block's giving up
+          if (t0 == 0) t0 = clock64();
+          if (dead_flag_of(err) != 0 || clock64() - t0 > limit) { atomicCAS(err, 0, TIMEOUT_CODE); dead = true; }
         }
+      }
 #pragma unroll
       for (int k = 0; k < KMAX; ++k)
 #pragma unroll
         for (int e = 0; e < E; ++e)
-          if (k0 + k < nparts) d[e] += v[k][e];
+          if (k0 + k < nparts) d[e] += __uint_as_float((uint32_t)w[k][e]);
     }
 #pragma unroll
     for (int e = 0; e < E; ++e) {
@@ -1253,36 +1276,13 @@ __device__ __forceinline__ void add_parts(float* x, uint32_t n, const float* par
   }
 }
 
-__device__ __forceinline__ void tp_meet(unsigned* ctr, unsigned target, bool& dead, uint32_t* dead_sm, long long limit, int* err) {
-  __syncthreads();                                     // the block's stores are issued
-  if (threadIdx.x == 0) {
-    // (the release is cumulative: it covers the stores of the block's other threads, which the barrier above ordered before it)
-    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
-    if (!dead) {
-      const long long t0 = clock64();
-      for (;;) {
-        unsigned v;
-        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
-        if (v >= target) break;
-        if (dead_flag_of(err) != 0 || clock64() - t0 > limit) {   // another block gave up, or this wait ran out
-          atomicCAS(err, 0, TIMEOUT_CODE);
-          *dead_sm = 1;
-          break;
-        }
-      }
-    }
-  }
-  __syncthreads();
-  if (*dead_sm) dead = true;                           // the block walks on without waiting, so that the others' meetings are still met
-}
-
 template <int MT>
 __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p) {
   constexpr int R = RingDepth<MT>::value;
   constexpr uint32_t SLOT_BYTES = ChunkBoxes<MT>::value * BOX_BYTES;
   extern __shared__ __align__(16) float smem[];
   cg::cluster_group cluster = cg::this_cluster();
-  const uint32_t C = cluster.num_blocks(), me = cluster.block_rank(), cgi = blockIdx.x / C, nblocks = gridDim.x;
+  const uint32_t C = cluster.num_blocks(), me = cluster.block_rank(), cgi = blockIdx.x / C;
   const int tid = threadIdx.x;
   const TpCut cut(p, cgi);
   const uint32_t H = p.hidden, KC = p.kv_heads * HD, QCl = cut.QCl, KCl = cut.KCl, NQl = cut.NQl, FFl = cut.FFl;
@@ -1312,7 +1312,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
   float* sn = cs + HD;
   DecodeLayerDev* lay = reinterpret_cast<DecodeLayerDev*>(sn + HD);   // [n_layers]
   ChunkEnt* tab = reinterpret_cast<ChunkEnt*>(lay + p.n_layers);  // [SCHED_MAX]
-  uint32_t* tab_len = reinterpret_cast<uint32_t*>(tab + SCHED_MAX);   // [2]: the list's length; a meeting's wait ran out
+  uint32_t* tab_len = reinterpret_cast<uint32_t*>(tab + SCHED_MAX);   // [2]
   uint16_t* gu = reinterpret_cast<uint16_t*>(((uintptr_t)(tab_len + 2) + 15) & ~(uintptr_t)15);   // [MT][2 FFl] BF16: gate | up of the cluster's slice
   uint16_t* vec = gu + (size_t)MT * 2 * FFl;                      // [MT][vec_cols] BF16: a product's A operand
 
@@ -1324,7 +1324,6 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
   for (uint32_t i = tid; i < p.n_layers * (uint32_t)(sizeof(DecodeLayerDev) / 8); i += DT)
     reinterpret_cast<uint64_t*>(lay)[i] = reinterpret_cast<const uint64_t*>(p.layers)[i];
   if (tid < HD) { cs[tid] = p.cos[(size_t)pos * HD + tid]; sn[tid] = p.sin[(size_t)pos * HD + tid]; }
-  if (tid == 0) tab_len[1] = 0;
   WeightWalk walk;
   walk.start_tp(&p, tab, tab_len, me, C, cut, ChunkBoxes<MT>::value * CK_ROWS);
   __syncthreads();
@@ -1359,7 +1358,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
     if (l == 0) {
       for (uint32_t i = tid; i < (uint32_t)MT * H; i += DT) xres[i] = i < p.rows * H ? p.x0[i] : 0.f;
     } else {
-      add_parts(xres, MT * H, p.part_dn, nparts_dn, (size_t)MT * H);
+      add_parts_tagged(xres, MT * H, p.part_dn + (size_t)((l - 1) & 1u) * nparts_dn * MT * H, nparts_dn, (size_t)MT * H, l, dead, limit, p.err);
     }
     __syncthreads();
     norm_rows_sm<MT>(xres, H, g1, p.eps, vec, p.vec_cols, stat);
@@ -1516,14 +1515,13 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
     }
     __syncthreads();
     for (uint32_t j = TpCut::first(me, C, cut.off_o); j < cut.nb_h; j += C) {
-      float* dst = p.part_o + (size_t)cgi * MT * H + j * DCOLS;
+      unsigned long long* dst = p.part_o + ((size_t)(l & 1u) * p.tp + cgi) * MT * H + j * DCOLS;
       product_stream<MT, R>(vec, p.vec_cols, QCl, ring, bars, head, parity, dead, limit, p.err, walk, halves,
-                            [&](int r, int cc, float t) { dst[(size_t)r * H + cc] = t; });
+                            [&](int r, int cc, float t) { st_tagged(dst + (size_t)r * H + cc, t, l + 1); });
     }
-    tp_meet(p.gbar, (2 * l + 1) * nblocks, dead, &tab_len[1], limit, p.err);   // every cluster's partial is in global memory
 
     // ---- phase 4: the residual, norm, the cluster's gate and up columns ----
-    add_parts(xres, MT * H, p.part_o, p.tp, (size_t)MT * H);
+    add_parts_tagged(xres, MT * H, p.part_o + (size_t)(l & 1u) * p.tp * MT * H, p.tp, (size_t)MT * H, l + 1, dead, limit, p.err);
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < GN; ++i) gn[i] = l + 1 < p.n_layers && tid + i * DT < H ? bf16_at(lay[l + 1].norm1, tid + i * DT) : 0.f;
@@ -1558,14 +1556,14 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
         vec[(size_t)r * p.vec_cols + kk] = f32_to_bf16_bits(__float_as_uint(__fmul_rn(__fmul_rn(a, sigmoid_flex(a)), bq)));
       }
       __syncthreads();
-      float* dst = p.part_dn + ((size_t)cgi * p.ks_dn + ks) * MT * H + cb * DCOLS;
+      unsigned long long* dst = p.part_dn + ((size_t)(l & 1u) * nparts_dn + (size_t)cgi * p.ks_dn + ks) * MT * H + cb * DCOLS;
       product_stream<MT, R>(vec, p.vec_cols, len, ring, bars, head, parity, dead, limit, p.err, walk, halves,
-                            [&](int r, int cc, float t) { dst[(size_t)r * H + cc] = t; });
+                            [&](int r, int cc, float t) { st_tagged(dst + (size_t)r * H + cc, t, l + 1); });
     }
-    tp_meet(p.gbar, (2 * l + 2) * nblocks, dead, &tab_len[1], limit, p.err);
   }
   if (blockIdx.x == 0) {
-    add_parts(xres, MT * H, p.part_dn, nparts_dn, (size_t)MT * H);
+    add_parts_tagged(xres, MT * H, p.part_dn + (size_t)((p.n_layers - 1) & 1u) * nparts_dn * MT * H, nparts_dn, (size_t)MT * H, p.n_layers,
+                     dead, limit, p.err);
     __syncthreads();
     norm_rows<MT>(xres, H, p.final_norm, p.eps, osum, H, stat);
     for (uint32_t i = tid; i < p.rows * H; i += DT) p.out[i] = f32_to_bf16_bits(__float_as_uint(osum[i]));
@@ -1729,8 +1727,11 @@ bool tp_plan(const DecodeShape& sh, TpPlan* t) {
   const uint32_t hq = sh.heads / G, hk = sh.kv_heads / G, QCl = hq * HD, NQl = QCl + 2 * hk * HD, FFl = sh.ff / G, chunks = sh.attend / DCH;
   const uint32_t att_l = sh.rows * hk * chunks;
   const uint32_t want_rows = MTc == 1 ? 576u : 768u;
+  // the slices of a cluster's share of ff: about a chunk's rows, and at least so many that every block of a cluster of
+  // sixteen has a down item (what orders the blocks, see the kernel)
   uint32_t ks = (FFl + want_rows - 1) / want_rows;
-  if (ks < 1) ks = 1;
+  const uint32_t per_block = (16 + sh.hidden / DCOLS - 1) / (sh.hidden / DCOLS);
+  if (ks < per_block) ks = per_block;
   const uint32_t sl = ((FFl + ks - 1) / ks + 63) / 64 * 64;
   ks = (FFl + sl - 1) / sl;
   uint32_t vc = sh.hidden > QCl ? sh.hidden : QCl;
@@ -1760,7 +1761,8 @@ bool tp_plan(const DecodeShape& sh, TpPlan* t) {
   }
   auto chunks_of = [&](uint64_t items, uint32_t rows) { return (uint64_t)((items + 7) / 8) * ((rows + chunk_rows - 1) / chunk_rows); };
   const uint64_t sched = chunks_of(n_q, sh.hidden) + chunks_of(nb_h, QCl) + chunks_of(n_gu, sh.hidden) + chunks_of(n_dn, sl);
-  return t->smem <= 224 * 1024 && sh.hidden <= (uint32_t)GN * DT && sched <= SCHED_MAX && sh.ff < 65536 && 2 * sh.ff / DCOLS < 65536;
+  return t->smem <= 224 * 1024 && sh.hidden <= (uint32_t)GN * DT && sched <= SCHED_MAX && sh.ff < 65536 && 2 * sh.ff / DCOLS < 65536 &&
+         n_gu >= 16 && n_dn >= 16;                       // every block has gate|up and down items: what orders the blocks (see the kernel)
 }
 
 // Which form a step of BF16 matrices takes: 2 several clusters, 1 one cluster, 0 the grid.  B200TT_DECODE=grid and
@@ -1797,13 +1799,13 @@ DecodeScratch decode_layers_scratch(const DecodeShape& sh, int grid) {
   auto take = [&](uint64_t floats) { const uint64_t at = off; off += (floats + 63) / 64 * 64; return at; };
   d.off_qkv = take((uint64_t)d.ks_qkv * MT * NQKV);
   d.off_att = take((uint64_t)sh.rows * sh.kv_heads * (sh.attend / DCH) * 4 * (HD + 2));
-  TpPlan t{};                                          // the several-cluster form keeps a partial a cluster (and slice) in the same places
-  const bool tp = tp_plan(sh, &t);
-  const uint32_t parts_o = tp && t.G > d.ks_o ? t.G : d.ks_o, parts_dn = tp && t.G * t.ks > d.ks_dn ? t.G * t.ks : d.ks_dn;
-  d.off_o = take((uint64_t)parts_o * MT * sh.hidden);
+  d.off_o = take((uint64_t)d.ks_o * MT * sh.hidden);
   d.off_gu = take((uint64_t)d.ks_gu * MT * 2 * sh.ff);
-  d.off_dn = take((uint64_t)parts_dn * MT * sh.hidden);
+  d.off_dn = take((uint64_t)d.ks_dn * MT * sh.hidden);
   d.off_bar = take(64);
+  TpPlan t{};                                          // the several-cluster form's partial sums: 8-byte words, two copies of each
+  d.tp_floats = tp_plan(sh, &t) ? 2 * ((uint64_t)2 * t.G * MT * sh.hidden + (uint64_t)2 * t.G * t.ks * MT * sh.hidden) : 0;
+  d.off_tp = take(d.tp_floats);
   d.floats = off;
   return d;
 }
@@ -1877,8 +1879,12 @@ cudaError_t launch_decode_layers(const DecodeShape& sh, const DecodeLayerPtrs* l
     c.layers = reinterpret_cast<const DecodeLayerDev*>(layers_dev);
     c.x0 = x0; c.final_norm = final_norm; c.cos = cos_t; c.sin = sin_t; c.pos = pos; c.out = out; c.err = err;
     c.maps = reinterpret_cast<const CUtensorMap*>(maps_dev);
-    c.part_o = scratch + d.off_o; c.part_dn = scratch + d.off_dn; c.gbar = reinterpret_cast<unsigned*>(scratch + d.off_bar);
-    cudaError_t ce = cudaMemsetAsync(c.gbar, 0, 64 * sizeof(float), stream);   // the meetings' counter starts at zero
+    // the partials' words (two copies of each) follow the grid form's scratch; a word's tag is the layer's, so all start at zero
+    const size_t words_o = (size_t)2 * t.G * MTc * sh.hidden, words_dn = (size_t)2 * t.G * t.ks * MTc * sh.hidden;
+    if (d.tp_floats < 2 * (words_o + words_dn)) return cudaErrorInvalidValue;
+    c.part_o = reinterpret_cast<unsigned long long*>(scratch + d.off_tp);
+    c.part_dn = c.part_o + words_o;
+    cudaError_t ce = cudaMemsetAsync(c.part_o, 0, (words_o + words_dn) * sizeof(unsigned long long), stream);
     if (ce != cudaSuccess) return ce;
     int width = 0;
     ce = MTc == 1 ? launch_tp<1>(c, t.smem, &width, stream) : (MTc == 2 ? launch_tp<2>(c, t.smem, &width, stream) : launch_tp<4>(c, t.smem, &width, stream));

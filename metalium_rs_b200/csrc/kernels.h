@@ -207,6 +207,7 @@ struct DecodeLayerPtrs {          // a layer's operands as device addresses (a d
 struct DecodeScratch {            // how the step's scratch (F32 words) is cut, and how each product's k is sliced
   uint32_t ks_qkv, sl_qkv, ks_o, sl_o, ks_gu, sl_gu, ks_dn, sl_dn;
   uint64_t off_qkv, off_att, off_o, off_gu, off_dn, off_bar, floats;
+  uint64_t off_tp, tp_floats;       // the several-cluster form's partial sums (F32 words; the region starts on 256 bytes)
 };
 bool decode_layers_supported(const DecodeShape& shape, const char** why);
 int decode_layers_grid();
