@@ -693,6 +693,7 @@ struct ClusterParams {
   // the layers in turn, all words zero at launch
   unsigned long long* part_o;    // [2][tp][MT][hidden]: a cluster's share of the attention output's projection
   unsigned long long* part_dn;   // [2][tp * ks_dn][MT][hidden]: and of the down projection, a slice of k each
+  unsigned long long* done;      // [2][blocks]: a block's word {0, layer + 1}: it has finished the layer
 };
 
 constexpr int CK_ROWS = 192;                           // k-rows of a tiled copy's box (at most 256)
@@ -1224,11 +1225,11 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
 // needs.  Those go through global memory, and a trip to the L2 and back costs some 2,000 cycles here (the two dies), so an
 // exchange is ONE trip after the data is there: an element travels as an 8-byte word {value, layer + 1}, stored and loaded
 // whole, and a reader polls the very words it needs until each carries the layer's tag -- no counter to wait for and then
-// the data to fetch, no fence.  What orders the blocks is the data itself: every block has a gate|up item and a down item
-// (the plan sees to it), so the down partials of layer l are whole only after every block has read what layer l sent it and
-// armed its barriers for l + 1, and nothing of layer l + 1 is sent before some block has the down partials of layer l; the
-// partials' two copies are used by the layers in turn, since a block with nothing to do but gate|up and down may read
-// layer l's down partials while another cluster already writes layer l + 1's.  Every poll is bounded.
+// the data to fetch, no fence.  What orders the blocks is one more such word a block: at the end of a layer a block stores
+// {0, layer + 1} in its own place, and the poll that opens the next layer (for the down partials) also waits for every
+// block's word -- so nothing of layer l + 1 is sent anywhere before every block has read what layer l sent it and armed
+// its barriers for l + 1.  The words' two copies are used by the layers in turn: a block may still poll layer l's while
+// a faster one stores layer l + 1's.  Every poll is bounded.
 __device__ __forceinline__ void st_tagged(unsigned long long* dst, float v, uint32_t tag) {
   const unsigned long long w = ((unsigned long long)tag << 32) | __float_as_uint(v);
   asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(dst), "l"(w) : "memory");
@@ -1236,7 +1237,8 @@ __device__ __forceinline__ void st_tagged(unsigned long long* dst, float v, uint
 // x[i] += parts[0][i] + parts[1][i] + ... (in that order) for i < n, once every word carries `tag`.  A thread asks for all
 // the words of up to four of its elements at once, so a pass costs one trip to the L2 once the data is there.
 __device__ __forceinline__ void add_parts_tagged(float* x, uint32_t n, const unsigned long long* parts, uint32_t nparts, size_t stride,
-                                                 uint32_t tag, bool& dead, long long limit, int* err) {
+                                                 uint32_t tag, bool& dead, long long limit, int* err,
+                                                 const unsigned long long* also = nullptr) {   // one more word this thread waits for
   constexpr int E = 4, KMAX = 4;
   for (uint32_t base = 0; base < n; base += E * DT) {
     float d[E] = {0.f, 0.f, 0.f, 0.f};
@@ -1252,6 +1254,11 @@ __device__ __forceinline__ void add_parts_tagged(float* x, uint32_t n, const uns
             const uint32_t i = base + e * DT + threadIdx.x, kk = k0 + k < nparts ? k0 + k : nparts - 1;
             asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w[k][e]) : "l"(parts + (size_t)kk * stride + (i < n ? i : n - 1)) : "memory");
           }
+        if (also) {
+          unsigned long long t;
+          asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(t) : "l"(also) : "memory");
+          ok = (uint32_t)(t >> 32) == tag;
+        }
 #pragma unroll
         for (int k = 0; k < KMAX; ++k)
 #pragma unroll
@@ -1358,7 +1365,9 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
     if (l == 0) {
       for (uint32_t i = tid; i < (uint32_t)MT * H; i += DT) xres[i] = i < p.rows * H ? p.x0[i] : 0.f;
     } else {
-      add_parts_tagged(xres, MT * H, p.part_dn + (size_t)((l - 1) & 1u) * nparts_dn * MT * H, nparts_dn, (size_t)MT * H, l, dead, limit, p.err);
+      // (thread t also waits for block t's word: every block has finished layer l - 1)
+      add_parts_tagged(xres, MT * H, p.part_dn + (size_t)((l - 1) & 1u) * nparts_dn * MT * H, nparts_dn, (size_t)MT * H, l, dead, limit, p.err,
+                       (uint32_t)tid < gridDim.x ? p.done + (size_t)((l - 1) & 1u) * gridDim.x + tid : nullptr);
     }
     __syncthreads();
     norm_rows_sm<MT>(xres, H, g1, p.eps, vec, p.vec_cols, stat);
@@ -1560,6 +1569,8 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
       product_stream<MT, R>(vec, p.vec_cols, len, ring, bars, head, parity, dead, limit, p.err, walk, halves,
                             [&](int r, int cc, float t) { st_tagged(dst + (size_t)r * H + cc, t, l + 1); });
     }
+    // every thread of the block is past its last read of what the layer sent it (each path here ends in a block barrier)
+    if (tid == 0) st_tagged(p.done + (size_t)(l & 1u) * gridDim.x + blockIdx.x, 0.f, l + 1);
   }
   if (blockIdx.x == 0) {
     add_parts_tagged(xres, MT * H, p.part_dn + (size_t)((p.n_layers - 1) & 1u) * nparts_dn * MT * H, nparts_dn, (size_t)MT * H, p.n_layers,
@@ -1727,11 +1738,8 @@ bool tp_plan(const DecodeShape& sh, TpPlan* t) {
   const uint32_t hq = sh.heads / G, hk = sh.kv_heads / G, QCl = hq * HD, NQl = QCl + 2 * hk * HD, FFl = sh.ff / G, chunks = sh.attend / DCH;
   const uint32_t att_l = sh.rows * hk * chunks;
   const uint32_t want_rows = MTc == 1 ? 576u : 768u;
-  // the slices of a cluster's share of ff: about a chunk's rows, and at least so many that every block of a cluster of
-  // sixteen has a down item (what orders the blocks, see the kernel)
   uint32_t ks = (FFl + want_rows - 1) / want_rows;
-  const uint32_t per_block = (16 + sh.hidden / DCOLS - 1) / (sh.hidden / DCOLS);
-  if (ks < per_block) ks = per_block;
+  if (ks < 1) ks = 1;
   const uint32_t sl = ((FFl + ks - 1) / ks + 63) / 64 * 64;
   ks = (FFl + sl - 1) / sl;
   uint32_t vc = sh.hidden > QCl ? sh.hidden : QCl;
@@ -1762,7 +1770,7 @@ bool tp_plan(const DecodeShape& sh, TpPlan* t) {
   auto chunks_of = [&](uint64_t items, uint32_t rows) { return (uint64_t)((items + 7) / 8) * ((rows + chunk_rows - 1) / chunk_rows); };
   const uint64_t sched = chunks_of(n_q, sh.hidden) + chunks_of(nb_h, QCl) + chunks_of(n_gu, sh.hidden) + chunks_of(n_dn, sl);
   return t->smem <= 224 * 1024 && sh.hidden <= (uint32_t)GN * DT && sched <= SCHED_MAX && sh.ff < 65536 && 2 * sh.ff / DCOLS < 65536 &&
-         n_gu >= 16 && n_dn >= 16;                       // every block has gate|up and down items: what orders the blocks (see the kernel)
+         16 * G <= (uint32_t)DT;                         // a thread a block waits for that block's word
 }
 
 // Which form a step of BF16 matrices takes: 2 several clusters, 1 one cluster, 0 the grid.  B200TT_DECODE=grid and
@@ -1804,7 +1812,7 @@ DecodeScratch decode_layers_scratch(const DecodeShape& sh, int grid) {
   d.off_dn = take((uint64_t)d.ks_dn * MT * sh.hidden);
   d.off_bar = take(64);
   TpPlan t{};                                          // the several-cluster form's partial sums: 8-byte words, two copies of each
-  d.tp_floats = tp_plan(sh, &t) ? 2 * ((uint64_t)2 * t.G * MT * sh.hidden + (uint64_t)2 * t.G * t.ks * MT * sh.hidden) : 0;
+  d.tp_floats = tp_plan(sh, &t) ? 2 * ((uint64_t)2 * t.G * MT * sh.hidden + (uint64_t)2 * t.G * t.ks * MT * sh.hidden + 2 * 16 * t.G) : 0;
   d.off_tp = take(d.tp_floats);
   d.floats = off;
   return d;
@@ -1881,10 +1889,12 @@ cudaError_t launch_decode_layers(const DecodeShape& sh, const DecodeLayerPtrs* l
     c.maps = reinterpret_cast<const CUtensorMap*>(maps_dev);
     // the partials' words (two copies of each) follow the grid form's scratch; a word's tag is the layer's, so all start at zero
     const size_t words_o = (size_t)2 * t.G * MTc * sh.hidden, words_dn = (size_t)2 * t.G * t.ks * MTc * sh.hidden;
-    if (d.tp_floats < 2 * (words_o + words_dn)) return cudaErrorInvalidValue;
+    const size_t words_done = (size_t)2 * 16 * t.G;
+    if (d.tp_floats < 2 * (words_o + words_dn + words_done)) return cudaErrorInvalidValue;
     c.part_o = reinterpret_cast<unsigned long long*>(scratch + d.off_tp);
     c.part_dn = c.part_o + words_o;
-    cudaError_t ce = cudaMemsetAsync(c.part_o, 0, (words_o + words_dn) * sizeof(unsigned long long), stream);
+    c.done = c.part_dn + words_dn;
+    cudaError_t ce = cudaMemsetAsync(c.part_o, 0, (words_o + words_dn + words_done) * sizeof(unsigned long long), stream);
     if (ce != cudaSuccess) return ce;
     int width = 0;
     ce = MTc == 1 ? launch_tp<1>(c, t.smem, &width, stream) : (MTc == 2 ? launch_tp<2>(c, t.smem, &width, stream) : launch_tp<4>(c, t.smem, &width, stream));
