@@ -672,6 +672,13 @@ __global__ void __launch_bounds__(DT, 1) decode_layers_kernel(const DecodeParams
 // the chunk that is R chunks ahead.  The form takes BF16 matrices only.
 namespace cg = cooperative_groups;
 
+// The several-cluster form's cut of a layer, worked out on the host (a division in the kernel is a hundred cycles, and
+// under its register pressure the compiler repeats one wherever its result is used): a cluster takes hq query heads with
+// their hk key/value heads and FFl of ff.
+struct TpShape {
+  uint32_t hq, hk, QCl, KCl, NQl, FFl, nfl, ffb, n_q, n_qs, n_att, nb_h, n_gu, n_dn, off_att, off_o, off_dn, group;
+};
+
 struct ClusterParams {
   const DecodeLayerDev* layers;
   uint32_t n_layers, rows, hidden, heads, kv_heads, ff, max_len, attend;
@@ -693,6 +700,8 @@ struct ClusterParams {
   // the layers in turn, all words zero at launch
   unsigned long long* part_o;    // [2][tp][MT][hidden]: a cluster's share of the attention output's projection
   unsigned long long* part_dn;   // [2][tp * ks_dn][MT][hidden]: and of the down projection, a slice of k each
+  uint32_t ks_q, sl_q;           // the QKV product's k in ks_q slices of sl_q rows: an item a (column block, slice)
+  TpShape cut;
   unsigned long long* done;      // [2][blocks]: a block's word {0, layer + 1}: it has finished the layer
 };
 
@@ -717,21 +726,15 @@ constexpr uint32_t SCHED_MAX = 256;
 // MLP (those gate and up columns, the rows of the down projection they feed).  Item j of a phase goes to the block whose
 // rank is (j + the phase's offset) mod the cluster's width, so that the phases with fewer items than blocks do not all
 // land on the first blocks.
-struct TpCut {
-  uint32_t cgi, heads, kv_heads, hq, hk, QCl, KCl, NQl, FFl, nfl, ffb, n_q, n_att, nb_h, n_gu, n_dn, off_att, off_o, off_dn;
-  __device__ TpCut(const ClusterParams& p, uint32_t cgi_) {
-    cgi = cgi_; heads = p.heads; kv_heads = p.kv_heads;
-    hq = p.heads / p.tp; hk = p.kv_heads / p.tp; QCl = hq * HD; KCl = hk * HD; NQl = QCl + 2 * KCl;
-    FFl = p.ff / p.tp; nfl = FFl / DCOLS; ffb = p.ff / DCOLS;
-    n_q = hq + 2 * hk; n_att = p.rows * hk * (p.attend / DCH); nb_h = p.hidden / DCOLS; n_gu = 2 * nfl; n_dn = nb_h * p.ks_dn;
-    off_att = n_q; off_o = off_att + n_att; off_dn = off_o + nb_h;
-  }
+struct TpCut : TpShape {
+  uint32_t cgi, heads, kv_heads;
+  __device__ TpCut(const ClusterParams& p, uint32_t cgi_) : TpShape(p.cut) { cgi = cgi_; heads = p.heads; kv_heads = p.kv_heads; }
   // the column block (of 64) of the stored matrix that local item j multiplies by
   __device__ uint32_t qkv_cb(uint32_t j) const {
     return j < hq ? cgi * hq + j : (j < hq + hk ? heads + cgi * hk + (j - hq) : heads + kv_heads + cgi * hk + (j - hq - hk));
   }
   __device__ uint32_t gu_cb(uint32_t j) const { return j < nfl ? cgi * nfl + j : ffb + cgi * nfl + (j - nfl); }
-  __device__ static uint32_t first(uint32_t me, uint32_t C, uint32_t off) { return (me + C - off % C) % C; }
+  __device__ static uint32_t first(uint32_t me, uint32_t C, uint32_t off) { return (me + C - (off & (C - 1))) & (C - 1); }   // C is 8 or 16
 };
 
 struct WeightWalk {
@@ -767,7 +770,10 @@ struct WeightWalk {
         for (uint32_t k = 0; k < total && c < SCHED_MAX; k += chunk_rows)
           tab_[c++] = ChunkEnt{(uint16_t)ph, (uint16_t)(total - k < chunk_rows ? total - k : chunk_rows), (uint16_t)cb, (uint16_t)(k0 + k)};
       };
-      for (uint32_t j = TpCut::first(me, C, 0); j < cut.n_q; j += C) put(0, cut.qkv_cb(j), 0, pp->hidden);
+      for (uint32_t j = TpCut::first(me, C, 0); j < cut.n_qs; j += C) {
+        const uint32_t k0 = (j / cut.n_q) * pp->sl_q;
+        put(0, cut.qkv_cb(j % cut.n_q), k0, k0 + pp->sl_q <= pp->hidden ? pp->sl_q : pp->hidden - k0);
+      }
       for (uint32_t j = TpCut::first(me, C, cut.off_o); j < cut.nb_h; j += C) put(1, j, cut.cgi * cut.QCl, cut.QCl);
       for (uint32_t j = TpCut::first(me, C, 0); j < cut.n_gu; j += C) put(2, cut.gu_cb(j), 0, pp->hidden);
       for (uint32_t j = TpCut::first(me, C, cut.off_dn); j < cut.n_dn; j += C) {
@@ -837,7 +843,7 @@ __device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, 
     }
     parity ^= 1u << head;
     const uint32_t boxes = len - cbase < CHUNK_ROWS ? (len - cbase + CK_ROWS - 1) / CK_ROWS : ChunkBoxes<MT>::value;
-#pragma unroll 1
+#pragma unroll
     for (uint32_t bx = 0; bx < boxes; ++bx) {
       const uint32_t base = cbase + bx * CK_ROWS + khalf * (CK_ROWS / 2);     // this warp's first k-row of the box, in the item
       const uint32_t slot = tc::smem_u32(ring + (size_t)head * SLOT_BYTES + (size_t)bx * BOX_BYTES) + khalf * (CK_ROWS / 2) * 128;
@@ -1289,13 +1295,13 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
   constexpr uint32_t SLOT_BYTES = ChunkBoxes<MT>::value * BOX_BYTES;
   extern __shared__ __align__(16) float smem[];
   cg::cluster_group cluster = cg::this_cluster();
-  const uint32_t C = cluster.num_blocks(), me = cluster.block_rank(), cgi = blockIdx.x / C;
+  const uint32_t C = cluster.num_blocks(), me = cluster.block_rank(), lgC = 31 - __clz(C), cgi = blockIdx.x >> lgC;   // C is 8 or 16
   const int tid = threadIdx.x;
   const TpCut cut(p, cgi);
   const uint32_t H = p.hidden, KC = p.kv_heads * HD, QCl = cut.QCl, KCl = cut.KCl, NQl = cut.NQl, FFl = cut.FFl;
-  const uint32_t group = p.heads / p.kv_heads, chunks = p.attend / DCH, att_l = cut.n_att, nparts_dn = p.tp * p.ks_dn;
+  const uint32_t group = cut.group, chunks = p.attend / DCH, att_l = cut.n_att, nparts_dn = p.tp * p.ks_dn;
   constexpr uint32_t APH = HD + 4, AP = 4 * APH;      // as in the one-cluster form
-  auto per = [&](uint32_t items) { return (items + C - 1) / C; };
+  auto per = [&](uint32_t items) { return (items + C - 1) >> lgC; };
   // shared memory (the same offsets in every block of a cluster); every piece is a whole number of 16 bytes
   uint8_t* ring = reinterpret_cast<uint8_t*>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)R * SLOT_BYTES);             // [16]
@@ -1303,7 +1309,8 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
   uint4* vsm = ksm + DCH * 8;
   float* xres = reinterpret_cast<float*>(vsm + DCH * 8);          // [MT][H]
   float* qkv = xres + (size_t)MT * H;                             // [MT][NQl]: the cluster's heads, q | k | v
-  float* att = qkv + (size_t)MT * NQl;                            // [att_l][AP]
+  float* qkvp = qkv + (size_t)MT * NQl;                           // [ks_q][MT][NQl]: their sums over the slices of k, from every block
+  float* att = qkvp + (size_t)p.ks_q * MT * NQl;                  // [att_l][AP]
   float* osum = att + (size_t)att_l * AP;                         // [MT][H]: the last norm's values
   float* mw = osum + (size_t)MT * H;                              // [MT * hq][chunks + 1] and [MT * hq] offsets
   float* qs = mw + (((size_t)MT * cut.hq * (chunks + 2) + 3) & ~(size_t)3);
@@ -1311,7 +1318,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
   float* stat = ps + 4 * DCH;
   float* halves = stat + 16;                                      // [2][MT][64]
   float* sq = halves + 2 * MT * DCOLS;                            // staging, a slot an item of the block: QKV
-  float* sa = sq + (size_t)per(cut.n_q) * MT * DCOLS;             // attention partials
+  float* sa = sq + (size_t)per(cut.n_qs) * MT * DCOLS;            // attention partials
   float* sg = sa + (size_t)per(att_l) * AP;                       // gate|up, BF16
   float* g1 = sg + (size_t)per(cut.n_gu) * MT * DCOLS / 2;
   float* g2 = g1 + H;
@@ -1320,7 +1327,12 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
   DecodeLayerDev* lay = reinterpret_cast<DecodeLayerDev*>(sn + HD);   // [n_layers]
   ChunkEnt* tab = reinterpret_cast<ChunkEnt*>(lay + p.n_layers);  // [SCHED_MAX]
   uint32_t* tab_len = reinterpret_cast<uint32_t*>(tab + SCHED_MAX);   // [2]
-  uint16_t* gu = reinterpret_cast<uint16_t*>(((uintptr_t)(tab_len + 2) + 15) & ~(uintptr_t)15);   // [MT][2 FFl] BF16: gate | up of the cluster's slice
+  // the block's items of the phases whose items take divisions to name, worked out once: {column block or chunk, slice or
+  // key/value head, first k-row or sequence, rows}
+  uint4* it_q = reinterpret_cast<uint4*>(((uintptr_t)(tab_len + 2) + 15) & ~(uintptr_t)15);   // QKV
+  uint4* it_a = it_q + per(cut.n_qs);                             // attention
+  uint4* it_d = it_a + per(att_l);                                // down
+  uint16_t* gu = reinterpret_cast<uint16_t*>(it_d + per(cut.n_dn));   // [MT][2 FFl] BF16: gate | up of the cluster's slice
   uint16_t* vec = gu + (size_t)MT * 2 * FFl;                      // [MT][vec_cols] BF16: a product's A operand
 
   const int32_t pos = *p.pos;
@@ -1333,6 +1345,20 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
   if (tid < HD) { cs[tid] = p.cos[(size_t)pos * HD + tid]; sn[tid] = p.sin[(size_t)pos * HD + tid]; }
   WeightWalk walk;
   walk.start_tp(&p, tab, tab_len, me, C, cut, ChunkBoxes<MT>::value * CK_ROWS);
+  const uint32_t j0q = TpCut::first(me, C, 0), it0 = TpCut::first(me, C, cut.off_att), j0o = TpCut::first(me, C, cut.off_o),
+                 j0d = TpCut::first(me, C, cut.off_dn);
+  for (uint32_t i = tid, j = j0q + tid * C; j < cut.n_qs; i += DT, j += DT * C) {
+    const uint32_t ks = j / cut.n_q, k0 = ks * p.sl_q;
+    it_q[i] = make_uint4(j - ks * cut.n_q, ks, k0, k0 + p.sl_q <= H ? p.sl_q : H - k0);
+  }
+  for (uint32_t i = tid, it = it0 + tid * C; it < att_l; i += DT, it += DT * C) {
+    const uint32_t q = it / chunks, b = q / cut.hk;
+    it_a[i] = make_uint4(it - q * chunks, q - b * cut.hk, b, 0);
+  }
+  for (uint32_t i = tid, j = j0d + tid * C; j < cut.n_dn; i += DT, j += DT * C) {
+    const uint32_t ks = j / cut.nb_h, k0 = ks * p.sl_dn;
+    it_d[i] = make_uint4(j - ks * cut.nb_h, ks, k0, k0 + p.sl_dn <= FFl ? p.sl_dn : FFl - k0);
+  }
   __syncthreads();
   walk.cnt = *tab_len;
   for (uint32_t c = tid; c < H; c += DT) g1[c] = bf16_at(lay[0].norm1, c);
@@ -1340,7 +1366,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
   bool dead = false;
   const long long limit = tc::wait_limit_of(p.err);
   uint64_t* xb = &bars[8];                            // [3]: QKV, attention partials, gate|up
-  const uint32_t expect[3] = {cut.n_q * MT * DCOLS * 4, att_l * group * APH * 4, cut.n_gu * MT * DCOLS * 2};
+  const uint32_t expect[3] = {cut.n_qs * MT * DCOLS * 4, att_l * group * APH * 4, cut.n_gu * MT * DCOLS * 2};
   if (tid == 0) {
     for (int r = 0; r < R; ++r) tc::mbar_init(&bars[r], 1);
     for (int k = 0; k < 3; ++k) tc::mbar_init(&xb[k], 1);
@@ -1372,14 +1398,16 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
     __syncthreads();
     norm_rows_sm<MT>(xres, H, g1, p.eps, vec, p.vec_cols, stat);
     {
-      const uint32_t j0 = TpCut::first(me, C, 0);
-      for (uint32_t j = j0; j < cut.n_q; j += C) {
-        float* slot = sq + (size_t)((j - j0) / C) * MT * DCOLS;
-        product_stream<MT, R>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk, halves,
-                              [&](int r, int cc, float t) { slot[r * DCOLS + cc] = bf16_round(t); });
+      for (uint32_t j = j0q, idx = 0; j < cut.n_qs; j += C, ++idx) {   // an item a (column block, slice of k): the slices' sums meet at the receivers
+        const uint4 e = it_q[idx];
+        const uint32_t jc = e.x, ks = e.y, k0 = e.z, len = e.w;
+        float* slot = sq + (size_t)idx * MT * DCOLS;
+        const bool whole = p.ks_q == 1;                  // one slice: the sender rounds, the receivers take the values as they come
+        product_stream<MT, R>(vec + k0, p.vec_cols, len, ring, bars, head, parity, dead, limit, p.err, walk, halves,
+                              [&](int r, int cc, float t) { slot[r * DCOLS + cc] = whole ? bf16_round(t) : t; });
         if ((uint32_t)tid < C * MT) {
           const uint32_t d = (uint32_t)tid / MT, r = (uint32_t)tid - d * MT;
-          copy_to_block(qkv + (size_t)r * NQl + j * DCOLS, slot + r * DCOLS, DCOLS * 4, &xb[0], d);
+          copy_to_block((whole ? qkv : qkvp + (size_t)ks * MT * NQl) + (size_t)r * NQl + jc * DCOLS, slot + r * DCOLS, DCOLS * 4, &xb[0], d);
         }
       }
     }
@@ -1387,8 +1415,9 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
     for (int i = 0; i < GN; ++i)
       if (tid + i * DT < H) g2[tid + i * DT] = gn[i];
     uint4 kreg[2], vreg[2];
-    auto load_cache = [&](uint32_t it) {
-      const uint32_t ch = it % chunks, kvh = cgi * cut.hk + (it / chunks) % cut.hk, b = it / (chunks * cut.hk);
+    auto load_cache = [&](uint32_t idx) {
+      const uint4 e = it_a[idx];
+      const uint32_t ch = e.x, kvh = cgi * cut.hk + e.y, b = e.z;
       if (ch * DCH > (uint32_t)pos) return;
       const uint64_t row0 = (uint64_t)b * p.max_len + (uint64_t)ch * DCH;
 #pragma unroll
@@ -1398,16 +1427,22 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
         vreg[h2] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(L.vc) + (row0 + j) * KC + kvh * HD + u * 8);
       }
     };
-    const uint32_t it0 = TpCut::first(me, C, cut.off_att);
-    if (it0 < att_l) load_cache(it0);
+    if (it0 < att_l) load_cache(0);
     arrived(0);
 
     // ---- phase 2: the attention of the cluster's heads, an item a (sequence, key/value head, 64 positions) ----
-    for (uint32_t it = it0; it < att_l; it += C) {
-      const uint32_t ch = it % chunks, kvl = (it / chunks) % cut.hk, kvh = cgi * cut.hk + kvl, b = it / (chunks * cut.hk);
-      float* stage = sa + (size_t)((it - it0) / C) * AP;
+    if (it0 < att_l && p.ks_q > 1)                     // the product's BF16 result: the slices' sums in order, rounded once
+      for (uint32_t i = tid; i < (uint32_t)MT * NQl; i += DT) {
+        float t = qkvp[i];
+        for (uint32_t k = 1; k < p.ks_q; ++k) t += qkvp[(size_t)k * MT * NQl + i];
+        qkv[i] = bf16_round(t);
+      }
+    for (uint32_t it = it0, idx = 0; it < att_l; it += C, ++idx) {
+      const uint4 e4 = it_a[idx];
+      const uint32_t ch = e4.x, kvl = e4.y, kvh = cgi * cut.hk + kvl, b = e4.z;
+      float* stage = sa + (size_t)idx * AP;
       __syncthreads();
-      if (it != it0) load_cache(it);
+      if (idx != 0) load_cache(idx);
       if (ch * DCH > (uint32_t)pos) {
         for (uint32_t i = tid; i < AP; i += DT) stage[i] = i % APH == HD ? -INFINITY : 0.f;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1448,10 +1483,12 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
         for (int u = 0; u < 8; ++u) {
           const uint4 kq = ksm[j * 8 + (u ^ (j & 7))];
           const uint32_t w4[4] = {kq.x, kq.y, kq.z, kq.w};
+          const float4 qa = *reinterpret_cast<const float4*>(q + u * 8), qb = *reinterpret_cast<const float4*>(q + u * 8 + 4);
+          const float q8[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            t4[e] = fmaf(q[u * 8 + 2 * e], __uint_as_float(w4[e] << 16), t4[e]);
-            t4[e] = fmaf(q[u * 8 + 2 * e + 1], __uint_as_float(w4[e] & 0xffff0000u), t4[e]);
+            t4[e] = fmaf(q8[2 * e], __uint_as_float(w4[e] << 16), t4[e]);
+            t4[e] = fmaf(q8[2 * e + 1], __uint_as_float(w4[e] & 0xffff0000u), t4[e]);
           }
         }
         sc = __fmul_rn((t4[0] + t4[1]) + (t4[2] + t4[3]), p.scale);
@@ -1470,22 +1507,35 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
       __syncthreads();
       if ((tid & 31) == 0) stat[8 + (tid >> 5)] = sum;
       __syncthreads();
+      // P.V: a head's two warps take half of the positions each, a lane two columns (one 4-byte load a position: a row of V
+      // is the warp's 128 bytes), the probabilities by 16-byte loads; the halves meet in the query's idle buffer.  A load a
+      // position and column, as before, kept the load pipe busy for most of the phase.
       if (g < group) {
-        const uint32_t d = j;
-        float o4[4] = {0.f, 0.f, 0.f, 0.f};
-        const float* pr = ps + g * DCH;
-#pragma unroll 4
-        for (int jj = 0; jj < DCH; jj += 4) {
+        const uint32_t half = (j >> 5) & 1u, dp = j & 31u;
+        float oa[2] = {0.f, 0.f}, ob[2] = {0.f, 0.f};    // two chains a column, joined in a fixed order
+        const float* pr = ps + g * DCH + half * 32;
+#pragma unroll 2
+        for (int jj = 0; jj < 32; jj += 4) {
+          const float4 p4 = *reinterpret_cast<const float4*>(pr + jj);
+          const float pe[4] = {p4.x, p4.y, p4.z, p4.w};
 #pragma unroll
           for (int e2 = 0; e2 < 4; ++e2) {
-            const uint16_t hv = reinterpret_cast<const uint16_t*>(vsm + (jj + e2) * 8 + ((d >> 3) ^ ((jj + e2) & 7)))[d & 7];
-            o4[e2] = fmaf(pr[jj + e2], __uint_as_float((uint32_t)hv << 16), o4[e2]);
+            const uint32_t row = half * 32 + jj + e2;
+            const uint32_t w2 = reinterpret_cast<const uint32_t*>(vsm + row * 8 + ((dp >> 2) ^ (row & 7)))[dp & 3];
+            oa[e2 & 1] = fmaf(pe[e2], __uint_as_float(w2 << 16), oa[e2 & 1]);
+            ob[e2 & 1] = fmaf(pe[e2], __uint_as_float(w2 & 0xffff0000u), ob[e2 & 1]);
           }
         }
-        const float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
-        const float lsum = stat[8 + 2 * g] + stat[8 + 2 * g + 1];
-        stage[g * APH + d] = o;
-        if (d == 0) { stage[g * APH + HD] = mh; stage[g * APH + HD + 1] = lsum; }
+        const float o_lo = oa[0] + oa[1], o_hi = ob[0] + ob[1];
+        if (half) { qs[g * HD + 2 * dp] = o_lo; qs[g * HD + 2 * dp + 1] = o_hi; }
+        __syncthreads();
+        if (!half) {
+          stage[g * APH + 2 * dp] = o_lo + qs[g * HD + 2 * dp];
+          stage[g * APH + 2 * dp + 1] = o_hi + qs[g * HD + 2 * dp + 1];
+          if (dp == 0) { stage[g * APH + HD] = mh; stage[g * APH + HD + 1] = stat[8 + 2 * g] + stat[8 + 2 * g + 1]; }
+        }
+      } else {
+        __syncthreads();
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncthreads();
@@ -1523,22 +1573,26 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
       vec[(size_t)r * p.vec_cols + c] = f32_to_bf16_bits(__float_as_uint(v));
     }
     __syncthreads();
-    for (uint32_t j = TpCut::first(me, C, cut.off_o); j < cut.nb_h; j += C) {
+    for (uint32_t j = j0o; j < cut.nb_h; j += C) {
       unsigned long long* dst = p.part_o + ((size_t)(l & 1u) * p.tp + cgi) * MT * H + j * DCOLS;
       product_stream<MT, R>(vec, p.vec_cols, QCl, ring, bars, head, parity, dead, limit, p.err, walk, halves,
                             [&](int r, int cc, float t) { st_tagged(dst + (size_t)r * H + cc, t, l + 1); });
     }
 
     // ---- phase 4: the residual, norm, the cluster's gate and up columns ----
+    // (the next layer's first gains are asked for before the poll, whose wait hides their trip)
+    uint16_t gnb[GN];
+#pragma unroll
+    for (int i = 0; i < GN; ++i)
+      gnb[i] = l + 1 < p.n_layers && tid + i * DT < H ? reinterpret_cast<const uint16_t*>(lay[l + 1].norm1)[tid + i * DT] : (uint16_t)0;
     add_parts_tagged(xres, MT * H, p.part_o + (size_t)(l & 1u) * p.tp * MT * H, p.tp, (size_t)MT * H, l + 1, dead, limit, p.err);
     __syncthreads();
 #pragma unroll
-    for (int i = 0; i < GN; ++i) gn[i] = l + 1 < p.n_layers && tid + i * DT < H ? bf16_at(lay[l + 1].norm1, tid + i * DT) : 0.f;
+    for (int i = 0; i < GN; ++i) gn[i] = __uint_as_float((uint32_t)gnb[i] << 16);
     norm_rows_sm<MT>(xres, H, g2, p.eps, vec, p.vec_cols, stat);
     {
-      const uint32_t j0 = TpCut::first(me, C, 0);
-      for (uint32_t j = j0; j < cut.n_gu; j += C) {
-        uint16_t* slot = reinterpret_cast<uint16_t*>(sg) + (size_t)((j - j0) / C) * MT * DCOLS;
+      for (uint32_t j = j0q, idx = 0; j < cut.n_gu; j += C, ++idx) {
+        uint16_t* slot = reinterpret_cast<uint16_t*>(sg) + (size_t)idx * MT * DCOLS;
         product_stream<MT, R>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk, halves, [&](int r, int cc, float t) {
           slot[r * DCOLS + cc] = f32_to_bf16_bits(__float_as_uint(t));
         });
@@ -1554,9 +1608,9 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
     arrived(2);
 
     // ---- phase 5: the activation of the cluster's slice of ff and its rows of the down projection: a partial a (cluster, slice) ----
-    for (uint32_t j = TpCut::first(me, C, cut.off_dn); j < cut.n_dn; j += C) {
-      const uint32_t cb = j % cut.nb_h, ks = j / cut.nb_h, k0 = ks * p.sl_dn;
-      const uint32_t len = k0 + p.sl_dn <= FFl ? p.sl_dn : FFl - k0;
+    for (uint32_t j = j0d, idx = 0; j < cut.n_dn; j += C, ++idx) {
+      const uint4 e = it_d[idx];
+      const uint32_t cb = e.x, ks = e.y, k0 = e.z, len = e.w;
       __syncthreads();
       for (uint32_t i = tid; i < (uint32_t)MT * len; i += DT) {
         const uint32_t r = MT == 1 ? 0u : i / len, kk = i - r * len;
@@ -1724,7 +1778,7 @@ bool cluster_plan(const DecodeShape& sh, ClusterParams& c, size_t* smem) {
 // The several-cluster form's plan: how many clusters share a step (the most of 4, 3, 2 that cut the heads, the key/value
 // heads and ff's 64-column blocks evenly), the down projection's slices of a cluster's share of ff, the rows a chunk's copy
 // brings of each matrix, and a block's shared memory.  False where no cut or no plan fits.
-struct TpPlan { uint32_t G, ks, sl, vc, att_items, min_width, cr[4]; size_t smem; };
+struct TpPlan { uint32_t G, ks, sl, ks_q, sl_q, vc, att_items, min_width, cr[4]; size_t smem; };
 bool tp_plan(const DecodeShape& sh, TpPlan* t) {
   const uint32_t MTc = sh.rows <= 1 ? 1 : (sh.rows <= 2 ? 2 : 4);
   const char* e = getenv("B200TT_DECODE_TP");          // a development switch: that many clusters, or none (1)
@@ -1746,7 +1800,16 @@ bool tp_plan(const DecodeShape& sh, TpPlan* t) {
   if (sl > vc) vc = sl;
   vc = (vc + 7) / 8 * 8;
   const uint32_t chunk_rows = chunk_rows_of(MTc);
-  const uint32_t rows_of[4] = {sh.hidden, QCl, sh.hidden, sl};
+  // the QKV product's k in slices of whole boxes, as many as spread a cluster's few column blocks over sixteen blocks
+  uint32_t ks_q = 16 / (hq + 2 * hk);
+  const uint32_t boxes_q = (sh.hidden + CK_ROWS - 1) / CK_ROWS;
+  if (ks_q > boxes_q) ks_q = boxes_q;
+  if (MTc == 1) ks_q = 1;                              // one sequence takes a 576-row item as one chunk: slices did not pay (0.50 against 0.49 ms)
+  if (ks_q < 1) ks_q = 1;
+  const uint32_t sl_q = (boxes_q + ks_q - 1) / ks_q * CK_ROWS;
+  ks_q = (sh.hidden + sl_q - 1) / sl_q;
+  t->ks_q = ks_q; t->sl_q = sl_q;
+  const uint32_t rows_of[4] = {sl_q < sh.hidden ? sl_q : sh.hidden, QCl, sh.hidden, sl};
   for (int i = 0; i < 4; ++i) {
     const uint32_t r64 = (rows_of[i] + 63) / 64 * 64;
     t->cr[i] = r64 < chunk_rows ? r64 : chunk_rows;
@@ -1754,21 +1817,22 @@ bool tp_plan(const DecodeShape& sh, TpPlan* t) {
   t->G = G; t->ks = ks; t->sl = sl; t->vc = vc; t->att_items = att_l;
   const size_t ring_slots = MTc == 1 ? RingDepth<1>::value : (MTc == 2 ? RingDepth<2>::value : RingDepth<4>::value);
   const size_t SLOT_BYTES = (size_t)chunk_rows * 128;
-  const uint64_t n_q = hq + 2 * hk, nb_h = sh.hidden / DCOLS, n_gu = 2 * FFl / DCOLS, n_dn = nb_h * ks;
+  const uint64_t n_q = (uint64_t)(hq + 2 * hk) * ks_q, nb_h = sh.hidden / DCOLS, n_gu = 2 * FFl / DCOLS, n_dn = nb_h * ks;
   constexpr uint64_t AP = 4 * (HD + 4);
   for (uint32_t width : {8u, 16u}) {
     auto per = [&](uint64_t items) { return (items + width - 1) / width; };
     const size_t stage = per(n_q) * MTc * DCOLS + per(att_l) * AP + per(n_gu) * MTc * DCOLS / 2;
     t->smem = 1024 + ring_slots * SLOT_BYTES + 16 * sizeof(uint64_t) + 2 * DCH * 8 * sizeof(uint4) +
-              ((size_t)MTc * sh.hidden * 2 + (size_t)MTc * NQl + (size_t)att_l * AP + (((size_t)MTc * hq * (chunks + 2) + 3) & ~(size_t)3) +
+              ((size_t)MTc * sh.hidden * 2 + (size_t)(1 + ks_q) * MTc * NQl + (size_t)att_l * AP + (((size_t)MTc * hq * (chunks + 2) + 3) & ~(size_t)3) +
                4 * HD + 4 * DCH + 16 + 2 * MTc * DCOLS + stage + 2 * sh.hidden + 2 * HD) * sizeof(float) +
               (size_t)sh.layers * sizeof(DecodeLayerDev) + SCHED_MAX * sizeof(ChunkEnt) + 8 + 16 +
+              (per(n_q) + per(att_l) + per(n_dn)) * sizeof(uint4) +
               ((size_t)MTc * 2 * FFl + (size_t)MTc * vc) * sizeof(uint16_t);
     t->min_width = width;
     if (t->smem <= 224 * 1024) break;
   }
   auto chunks_of = [&](uint64_t items, uint32_t rows) { return (uint64_t)((items + 7) / 8) * ((rows + chunk_rows - 1) / chunk_rows); };
-  const uint64_t sched = chunks_of(n_q, sh.hidden) + chunks_of(nb_h, QCl) + chunks_of(n_gu, sh.hidden) + chunks_of(n_dn, sl);
+  const uint64_t sched = chunks_of(n_q, rows_of[0]) + chunks_of(nb_h, QCl) + chunks_of(n_gu, sh.hidden) + chunks_of(n_dn, sl);
   return t->smem <= 224 * 1024 && sh.hidden <= (uint32_t)GN * DT && sched <= SCHED_MAX && sh.ff < 65536 && 2 * sh.ff / DCOLS < 65536 &&
          16 * G <= (uint32_t)DT;                         // a thread a block waits for that block's word
 }
@@ -1882,7 +1946,15 @@ cudaError_t launch_decode_layers(const DecodeShape& sh, const DecodeLayerPtrs* l
     const uint32_t MTc = sh.rows <= 1 ? 1 : (sh.rows <= 2 ? 2 : 4);
     c.n_layers = sh.layers; c.rows = sh.rows; c.hidden = sh.hidden; c.heads = sh.heads; c.kv_heads = sh.kv_heads; c.ff = sh.ff;
     c.max_len = sh.max_len; c.attend = sh.attend; c.eps = sh.eps; c.scale = sh.scale;
-    c.ks_dn = t.ks; c.sl_dn = t.sl; c.vec_cols = t.vc; c.att_items = t.att_items; c.min_width = t.min_width; c.tp = t.G;
+    c.ks_dn = t.ks; c.sl_dn = t.sl; c.vec_cols = t.vc; c.att_items = t.att_items; c.min_width = t.min_width; c.tp = t.G; c.ks_q = t.ks_q; c.sl_q = t.sl_q;
+    {
+      TpShape& u = c.cut;
+      u.hq = sh.heads / t.G; u.hk = sh.kv_heads / t.G; u.QCl = u.hq * HD; u.KCl = u.hk * HD; u.NQl = u.QCl + 2 * u.KCl;
+      u.FFl = sh.ff / t.G; u.nfl = u.FFl / DCOLS; u.ffb = sh.ff / DCOLS;
+      u.n_q = u.hq + 2 * u.hk; u.n_qs = u.n_q * t.ks_q; u.n_att = sh.rows * u.hk * (sh.attend / DCH); u.nb_h = sh.hidden / DCOLS;
+      u.n_gu = 2 * u.nfl; u.n_dn = u.nb_h * t.ks;
+      u.off_att = u.n_qs; u.off_o = u.off_att + u.n_att; u.off_dn = u.off_o + u.nb_h; u.group = sh.heads / sh.kv_heads;
+    }
     for (int i = 0; i < 4; ++i) c.pbytes[i] = t.cr[i] * 128;
     c.layers = reinterpret_cast<const DecodeLayerDev*>(layers_dev);
     c.x0 = x0; c.final_norm = final_norm; c.cos = cos_t; c.sin = sin_t; c.pos = pos; c.out = out; c.err = err;
