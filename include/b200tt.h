@@ -483,8 +483,9 @@ void*   b200_stream(const b200_engine*);
 /* Name of the kernel path the last product took: "tcgen05" (one CTA a tile), "tcgen05-pair" (CTA pairs),
  * "tcgen05-tf32x3", "skinny", "simt". */
 const char* b200_last_matmul_path(const b200_engine*);
-/* Name of the form the last `b200_decode_layers` took: "cluster16" or "cluster8" (one thread-block cluster of that
- * many blocks), "grid" (a cooperative grid), "none" before the first. */
+/* Name of the form the last `b200_decode_layers` took: "cluster16x3" and the like (that many clusters -- 2 to 4 -- of
+ * 16 or 8 blocks, sharing a layer's heads and ff), "cluster16" or "cluster8" (one thread-block cluster of that many
+ * blocks), "grid" (a cooperative grid), "none" before the first. */
 const char* b200_last_decode_form(const b200_engine*);
 
 #ifdef __cplusplus

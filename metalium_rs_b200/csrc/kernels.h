@@ -215,7 +215,7 @@ DecodeScratch decode_layers_scratch(const DecodeShape& shape, int grid);
 cudaError_t launch_decode_layers(const DecodeShape& shape, const DecodeLayerPtrs* layers_dev, const float* x0, const void* final_norm,
                                  const float* cos_t, const float* sin_t, const int32_t* pos, uint16_t* out, float* scratch,
                                  const DecodeScratch& cut, int grid, const void* maps_dev, int* err, cudaStream_t stream,
-                                 const char** form);   // *form: "cluster16", "cluster8" or "grid", what was launched
+                                 const char** form);   // *form: "cluster16x3" (several clusters), "cluster16", "cluster8" or "grid", what was launched
 // Whether the step should take the cluster form (then the caller builds the descriptors below and passes them).
 bool decode_layers_cluster_wanted(const DecodeShape& shape, bool any_bfp);
 // The cluster form's tiled-copy descriptors (four a layer), built on the host from the layers' addresses and uploaded

@@ -393,7 +393,7 @@ class CudaEngine:
         return self._lib.b200_last_matmul_path(self._e).decode()
 
     def last_decode_form(self) -> str:
-        """ "cluster16" / "cluster8" / "grid": the form the last `decode_layers` took."""
+        """ "cluster16x3" (and the like) / "cluster16" / "cluster8" / "grid": the form the last `decode_layers` took."""
         return self._lib.b200_last_decode_form(self._e).decode()
 
     # -- element-wise (server.rs:492-566) --------------------------------------------
