@@ -283,6 +283,52 @@ def test_the_one_launch_step_is_the_composed_step(eng, batch, storage, form, mon
     assert np.array_equal(fused.generated(0, steps).shape, (steps, batch))
 
 
+@pytest.mark.parametrize("heads,kv_heads,ff,tp,batch", [
+    (8, 4, 1024, 0, 2),       # four clusters: two query heads on one key/value head each
+    (8, 4, 1024, 2, 1),       # two clusters: four query heads on two key/value heads each
+    (4, 4, 768, 0, 4),        # four clusters, a query head a key/value head
+    (6, 2, 1024, 0, 2),       # two clusters (neither 4 nor 3 divides): three query heads a key/value head
+    (9, 3, 1536, 0, 3),       # three sequences in a four-row step
+])
+def test_the_several_cluster_step_over_other_cuts(eng, heads, kv_heads, ff, tp, batch, monkeypatch):
+    # The several-cluster form cuts the heads, the key/value heads and ff by the number of clusters: the cuts the
+    # SmolLM2-135M shape does not reach (more than one key/value head a cluster, one query head a key/value head, two and
+    # four clusters), against the composed step as above.
+    monkeypatch.delenv("B200TT_DECODE", raising=False)
+    if tp:
+        monkeypatch.setenv("B200TT_DECODE_TP", str(tp))
+    cfg = W.LlamaConfig(layers=2, hidden=heads * 64, heads=heads, kv_heads=kv_heads, head_dim=64, ff=ff, vocab=1024)
+    max_len, steps = 128, 70
+    pre = W.LlamaPrefill(eng, cfg, W.llama_weights(cfg, seed=5), batch, 32)
+    composed = W.LlamaDecode(eng, cfg, pre.w, batch, max_len=max_len)
+    fused = W.LlamaDecode(eng, cfg, pre.w, batch, max_len=max_len, fused=True)
+    ids = orc.integers(0x6E9, 4, (steps, batch), cfg.vocab)
+    composed.reset(ids[0]); fused.reset(ids[0])
+    worst, total = 0.0, 0.0
+    for t in range(steps):
+        composed.set_ids(ids[t]); fused.set_ids(ids[t])
+        la, aa = composed.step()
+        lb, ab = fused.step()
+        a, b = eng.download(la), eng.download(lb)
+        worst = max(worst, float(np.max(np.abs(a - b))))
+        total += float(np.mean(np.abs(a - b)))
+        top2 = np.sort(a, axis=1)[:, -2:]
+        clear = (top2[:, 1] - top2[:, 0]) > 4e-2
+        ca, cb = eng.download_bits(aa).view(np.int32).ravel(), eng.download_bits(ab).view(np.int32).ravel()
+        assert np.array_equal(ca[clear], cb[clear]), t
+        for i in (la, aa, lb, ab):
+            eng.free(i)
+    assert worst <= 2e-2 and total / steps <= 1.5e-3, (worst, total / steps)
+    want = tp if tp else next(g for g in (4, 3, 2) if heads % g == 0 and kv_heads % g == 0 and ff % (64 * g) == 0)
+    assert eng.last_decode_form() in (f"cluster16x{want}", f"cluster8x{want}")
+    for l in range(cfg.layers):
+        for mine, theirs in ((fused.kc[l], composed.kc[l]), (fused.vc[l], composed.vc[l])):
+            x = orc.from_bf16(eng.download_bf16(mine)).reshape(batch, max_len, -1)
+            y = orc.from_bf16(eng.download_bf16(theirs)).reshape(batch, max_len, -1)
+            assert not x[:, steps:].any() and x[:, :steps].any()
+            assert np.max(np.abs(x - y)) <= 2.0 ** -6 * np.abs(y).max(), l
+
+
 def test_a_traced_one_launch_generation_is_its_eager_one(eng):
     cfg = small_llama()
     batch, n = 2, 24
