@@ -289,6 +289,7 @@ __device__ __forceinline__ void norm_rows_sm(const float* x, uint32_t cols, cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = warp / W, sub = warp - r * W;
   const float* xr = x + (size_t)r * cols;
   float ss = 0.f;
+#pragma unroll 1                                       // (the form's code is fetched anew every layer: short beats unrolled)
   for (uint32_t c = sub * 32 + lane; c < cols; c += W * 32) ss = fmaf(xr[c], xr[c], ss);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -299,6 +300,7 @@ __device__ __forceinline__ void norm_rows_sm(const float* x, uint32_t cols, cons
 #pragma unroll
   for (int w = 0; w < W; ++w) total += scratch[r * W + w];
   const float stat = sqrtf(__fadd_rn(__fmul_rn(total, 1.0f / (float)cols), eps));
+#pragma unroll 1
   for (uint32_t c = sub * 32 + lane; c < cols; c += W * 32)
     vec[(size_t)r * vec_pitch + c] = f32_to_bf16_bits(__float_as_uint(__fmul_rn(__fdiv_rn(xr[c], stat), gains[c])));
   __syncthreads();
@@ -903,6 +905,8 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
   const int tid = threadIdx.x;
   const uint32_t H = p.hidden, QC = p.heads * HD, KC = p.kv_heads * HD, NQKV = QC + 2 * KC, FF = p.ff;
   const uint32_t group = p.heads / p.kv_heads, chunks = p.attend / DCH;
+  // a bulk copy's issue costs its warp some 70 cycles, so an item's copies (one a block and row) are spread over the eight warps
+  const uint32_t cpw = (C * MT + DT / 32 - 1) / (DT / 32), cpa = (C + DT / 32 - 1) / (DT / 32);
   constexpr uint32_t APH = HD + 4;                    // a head's partial of an attention item: 64 sums, the maximum, the sum, two unused (whole 16-byte pieces)
   constexpr uint32_t AP = 4 * APH;                    // an attention item's partial
   // shared memory (the same offsets in every block of the cluster)
@@ -1004,8 +1008,8 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
       float* slot = sq + (size_t)((it - me) / C) * MT * DCOLS;
       product_stream<MT, R>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk, halves,
                             [&](int r, int cc, float t) { slot[r * DCOLS + cc] = bf16_round(t); });   // the product's BF16 result
-      if ((uint32_t)tid < C * MT) {                    // a (block, row) pair a thread: 256 bytes each
-        const uint32_t d = (uint32_t)tid / MT, r = (uint32_t)tid - d * MT;
+      if (const uint32_t ci = (uint32_t)(tid >> 5) * cpw + (tid & 31); (uint32_t)(tid & 31) < cpw && ci < C * MT) {   // a (block, row) pair a thread: 256 bytes each
+        const uint32_t d = ci / MT, r = ci - d * MT;
         copy_to_block(qkv + (size_t)r * NQKV + it * DCOLS, slot + r * DCOLS, DCOLS * 4, &xb[0], d);
       }
     }
@@ -1038,7 +1042,8 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
         for (uint32_t i = tid; i < AP; i += DT) stage[i] = i % APH == HD ? -INFINITY : 0.f;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncthreads();
-        if ((uint32_t)tid < C) copy_to_block(att + (size_t)it * AP, stage, group * APH * 4, &xb[1], (uint32_t)tid);
+        if (const uint32_t ci = (uint32_t)(tid >> 5) * cpa + (tid & 31); (uint32_t)(tid & 31) < cpa && ci < C)
+          copy_to_block(att + (size_t)it * AP, stage, group * APH * 4, &xb[1], ci);
         continue;
       }
       const float* qrow = qkv + (size_t)b * NQKV;
@@ -1115,7 +1120,8 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncthreads();
-      if ((uint32_t)tid < C) copy_to_block(att + (size_t)it * AP, stage, group * APH * 4, &xb[1], (uint32_t)tid);
+      if (const uint32_t ci = (uint32_t)(tid >> 5) * cpa + (tid & 31); (uint32_t)(tid & 31) < cpa && ci < C)
+          copy_to_block(att + (size_t)it * AP, stage, group * APH * 4, &xb[1], ci);
     }
     arrived(1);                                        // every chunk's partial has landed here
 
@@ -1156,8 +1162,8 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
       float* slot = so + (size_t)((it - me) / C) * MT * DCOLS;
       product_stream<MT, R>(vec, p.vec_cols, QC, ring, bars, head, parity, dead, limit, p.err, walk, halves,
                             [&](int r, int cc, float t) { slot[r * DCOLS + cc] = t; });
-      if ((uint32_t)tid < C * MT) {
-        const uint32_t d = (uint32_t)tid / MT, r = (uint32_t)tid - d * MT;
+      if (const uint32_t ci = (uint32_t)(tid >> 5) * cpw + (tid & 31); (uint32_t)(tid & 31) < cpw && ci < C * MT) {
+        const uint32_t d = ci / MT, r = ci - d * MT;
         copy_to_block(osum + (size_t)r * H + it * DCOLS, slot + r * DCOLS, DCOLS * 4, &xb[2], d);
       }
     }
@@ -1174,8 +1180,8 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
       product_stream<MT, R>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk, halves, [&](int r, int cc, float t) {
         slot[r * DCOLS + cc] = f32_to_bf16_bits(__float_as_uint(t));   // the product's BF16 result
       });
-      if ((uint32_t)tid < C * MT) {
-        const uint32_t d = (uint32_t)tid / MT, r = (uint32_t)tid - d * MT;
+      if (const uint32_t ci = (uint32_t)(tid >> 5) * cpw + (tid & 31); (uint32_t)(tid & 31) < cpw && ci < C * MT) {
+        const uint32_t d = ci / MT, r = ci - d * MT;
         copy_to_block(gu + (size_t)r * 2 * FF + it * DCOLS, slot + r * DCOLS, DCOLS * 2, &xb[3], d);
       }
     }
@@ -1199,8 +1205,8 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
       float* slot = sd + (size_t)((it - me) / C) * MT * DCOLS;
       product_stream<MT, R>(vec, p.vec_cols, len, ring, bars, head, parity, dead, limit, p.err, walk, halves,
                             [&](int r, int cc, float t) { slot[r * DCOLS + cc] = t; });
-      if ((uint32_t)tid < C * MT) {
-        const uint32_t d = (uint32_t)tid / MT, r = (uint32_t)tid - d * MT;
+      if (const uint32_t ci = (uint32_t)(tid >> 5) * cpw + (tid & 31); (uint32_t)(tid & 31) < cpw && ci < C * MT) {
+        const uint32_t d = ci / MT, r = ci - d * MT;
         copy_to_block(dn + ((size_t)ks * MT + r) * H + cb * DCOLS, slot + r * DCOLS, DCOLS * 4, &xb[4], d);
       }
     }
@@ -1302,6 +1308,8 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
   const uint32_t group = cut.group, chunks = p.attend / DCH, att_l = cut.n_att, nparts_dn = p.tp * p.ks_dn;
   constexpr uint32_t APH = HD + 4, AP = 4 * APH;      // as in the one-cluster form
   auto per = [&](uint32_t items) { return (items + C - 1) >> lgC; };
+  // a bulk copy's issue costs its warp some 70 cycles, so an item's copies (one a block and row) are spread over the eight warps
+  const uint32_t cpw = (C * MT + DT / 32 - 1) / (DT / 32), cpa = (C + DT / 32 - 1) / (DT / 32);
   // shared memory (the same offsets in every block of a cluster); every piece is a whole number of 16 bytes
   uint8_t* ring = reinterpret_cast<uint8_t*>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)R * SLOT_BYTES);             // [16]
@@ -1405,8 +1413,8 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
         const bool whole = p.ks_q == 1;                  // one slice: the sender rounds, the receivers take the values as they come
         product_stream<MT, R>(vec + k0, p.vec_cols, len, ring, bars, head, parity, dead, limit, p.err, walk, halves,
                               [&](int r, int cc, float t) { slot[r * DCOLS + cc] = whole ? bf16_round(t) : t; });
-        if ((uint32_t)tid < C * MT) {
-          const uint32_t d = (uint32_t)tid / MT, r = (uint32_t)tid - d * MT;
+        if (const uint32_t ci = (uint32_t)(tid >> 5) * cpw + (tid & 31); (uint32_t)(tid & 31) < cpw && ci < C * MT) {
+          const uint32_t d = ci / MT, r = ci - d * MT;
           copy_to_block((whole ? qkv : qkvp + (size_t)ks * MT * NQl) + (size_t)r * NQl + jc * DCOLS, slot + r * DCOLS, DCOLS * 4, &xb[0], d);
         }
       }
@@ -1447,7 +1455,8 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
         for (uint32_t i = tid; i < AP; i += DT) stage[i] = i % APH == HD ? -INFINITY : 0.f;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncthreads();
-        if ((uint32_t)tid < C) copy_to_block(att + (size_t)it * AP, stage, group * APH * 4, &xb[1], (uint32_t)tid);
+        if (const uint32_t ci = (uint32_t)(tid >> 5) * cpa + (tid & 31); (uint32_t)(tid & 31) < cpa && ci < C)
+          copy_to_block(att + (size_t)it * AP, stage, group * APH * 4, &xb[1], ci);
         continue;
       }
       const float* qrow = qkv + (size_t)b * NQl;
@@ -1539,7 +1548,8 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncthreads();
-      if ((uint32_t)tid < C) copy_to_block(att + (size_t)it * AP, stage, group * APH * 4, &xb[1], (uint32_t)tid);
+      if (const uint32_t ci = (uint32_t)(tid >> 5) * cpa + (tid & 31); (uint32_t)(tid & 31) < cpa && ci < C)
+        copy_to_block(att + (size_t)it * AP, stage, group * APH * 4, &xb[1], ci);
     }
     arrived(1);
 
@@ -1596,8 +1606,8 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
         product_stream<MT, R>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk, halves, [&](int r, int cc, float t) {
           slot[r * DCOLS + cc] = f32_to_bf16_bits(__float_as_uint(t));
         });
-        if ((uint32_t)tid < C * MT) {
-          const uint32_t d = (uint32_t)tid / MT, r = (uint32_t)tid - d * MT;
+        if (const uint32_t ci = (uint32_t)(tid >> 5) * cpw + (tid & 31); (uint32_t)(tid & 31) < cpw && ci < C * MT) {
+          const uint32_t d = ci / MT, r = ci - d * MT;
           copy_to_block(gu + (size_t)r * 2 * FFl + j * DCOLS, slot + r * DCOLS, DCOLS * 2, &xb[2], d);
         }
       }
