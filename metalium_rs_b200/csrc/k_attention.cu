@@ -386,9 +386,13 @@ cudaError_t launch_kv(int rt, const float* q, const KV* k, uint64_t k_ld, const 
 
 int attention_rows_tile(int rows) { return rows <= 1 ? 1 : (rows <= 2 ? 2 : (rows <= 4 ? 4 : 8)); }
 
-// How a job's positions are split: chunks of 512 positions or more, as many as give the device
-// about eight blocks an SM (small blocks: several fit an SM and the tail of the grid is short),
-// and a chunk's scores within 64 KB of shared memory.  rt = the rows a job is built for (1, 2, 4, 8).
+// How a job's positions are split over blocks.  The kernel reads K and V once, so the step's time is the time of the
+// longest chain of blocks an SM runs: with R blocks resident on the device at once (the kernel's blocks an SM by its row
+// tile, fewer where a chunk's scores fill shared memory), s splits make ceil(jobs * s / R) rounds of blocks of l / s
+// positions (plus a block's fixed part, taken as 96 positions).  The split count with the least rounds x length wins:
+// 256 jobs of 4096 positions took 1,280 blocks in three rounds (114 us) where 1,024 in two take 99; 64 grouped jobs took
+// 512 blocks in two rounds (62 us) where 384 in one take 44.  A chunk is at least `B200TT_ATTN_CHUNK` positions
+// (default 256) and its scores stay within 64 KB of shared memory.  rt = the rows a job is built for (1, 2, 4, 8).
 void attention_rows_plan(uint64_t n_jobs, int rt, int l, int sms, int* splits, int* lc) {
   if (sms <= 0) {
     int dev = 0;
@@ -397,14 +401,27 @@ void attention_rows_plan(uint64_t n_jobs, int rt, int l, int sms, int* splits, i
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
   const int lc_max = ((64 * 1024 / 4) / rt) / 32 * 32;
-  uint64_t want = (8ull * (uint64_t)sms + n_jobs - 1) / n_jobs;
   static int chunk = 0;
-  if (!chunk) { const char* e = getenv("B200TT_ATTN_CHUNK"); chunk = e ? atoi(e) : 512; if (chunk < 32) chunk = 512; }
-  const uint64_t by_len = (uint64_t)(l / chunk > 1 ? l / chunk : 1);
-  if (want > by_len) want = by_len;
-  const uint64_t need = ((uint64_t)l + lc_max - 1) / lc_max;
-  if (want < need) want = need;
-  int c = (int)((l + want - 1) / want);
+  if (!chunk) { const char* e = getenv("B200TT_ATTN_CHUNK"); chunk = e ? atoi(e) : 256; if (chunk < 32) chunk = 256; }
+  const uint64_t need = ((uint64_t)l + lc_max - 1) / lc_max;          // fewest splits: a chunk's scores fit
+  uint64_t most = (uint64_t)(l / chunk > 1 ? l / chunk : 1);            // most splits: a chunk is not too short
+  if (most < need) most = need;
+  if (most > 64) most = 64;
+  const int by_bounds = rt >= 8 ? 2 : (rt >= 4 ? 3 : 4);                // the kernel's launch bounds
+  uint64_t best = need, best_cost = ~0ull;
+  for (uint64_t s = need; s <= most; ++s) {
+    int c = (int)((l + s - 1) / s);
+    c = (c + 31) / 32 * 32;
+    const uint64_t real = ((uint64_t)l + c - 1) / c;                    // the splits that chunk length makes
+    const uint64_t smem = (uint64_t)rt * (128 + c) * 4 + 8 * 1024;       // about a block's shared memory (heads of 128 columns)
+    uint64_t occ = (220ull * 1024) / smem;
+    if (occ > (uint64_t)by_bounds) occ = by_bounds;
+    if (occ < 1) occ = 1;
+    const uint64_t resident = occ * (uint64_t)sms, blocks = n_jobs * real;
+    const uint64_t cost = ((blocks + resident - 1) / resident) * (uint64_t)(c + 96);
+    if (cost < best_cost) { best_cost = cost; best = s; }
+  }
+  int c = (int)((l + best - 1) / best);
   c = (c + 31) / 32 * 32;
   *lc = c;
   *splits = (l + c - 1) / c;
