@@ -6,7 +6,8 @@
 N = 1: one step is one 8192^3 BF16 product (FP32 accumulate, BF16 result) on operands
 resident in HBM, launched through `matmul_dram_bf16`; `value` is 2*8192^3*K / device time.
 The same line carries the rest of the metric: `prefill` (the SmolLM2-135M-shape prefill of
-8 x 512 tokens as a replayed trace: tokens/s, launches, a per-op-class table) and `suite` (the
+8 x 512 tokens as a replayed trace: tokens/s, launches, a per-op-class table; under `decode_step` the
+generation step that follows it, ms a token at 1 and 4 sequences) and `suite` (the
 memory-bound ops on [8192, 8192] F32 and the row softmax on [4096, 32768]: GB/s of algorithmic
 bytes), each with its own `roofline`.
 N > 1 (under torchrun, one rank a GPU): the 16384^3 product split along N with K whole
@@ -550,7 +551,24 @@ def prefill_leg(eng, timed):
                               "clear_margins": int(clear.sum())})
     fl = model.flops()
     tflops = fl / tms / 1e9
-    return {"tok_per_s": batch * seq / (tms * 1e-3), "ms": tms, "tokens": batch * seq, "launches": int(per),
+    # the step after the prefill (the reference's traced generation step): one token a sequence over a fixed-shape cache,
+    # the 30 layers as one launch, replayed as a trace; 64 steps from position 1 of 256 attended
+    decode = {}
+    rng = np.random.default_rng(0xDEC0)
+    for nb in (1, 4):
+        dec = W.LlamaDecode(eng, cfg, model.w, nb, max_len=512, attend=256, fused=True)
+        start = rng.integers(0, cfg.vocab, nb).astype(np.int32)
+        dec.reset(start)
+        dlg, dam = dec.capture()
+        dec.reset(start)
+        l0 = eng.device_traffic().launches
+        dec.replay()
+        dper = eng.device_traffic().launches - l0
+        dms = timed(dec.replay, reps=64, warm=4)
+        decode[f"batch{nb}"] = {"ms_per_step": dms, "tok_per_s": nb / (dms * 1e-3), "launches_per_step": int(dper),
+                                "form": eng.last_decode_form(), "distinct_tokens_generated": int(len(np.unique(dec.generated(0, 69))))}
+        eng.release_trace(dec.trace); eng.free(dlg); eng.free(dam)
+    return {"tok_per_s": batch * seq / (tms * 1e-3), "ms": tms, "tokens": batch * seq, "launches": int(per), "decode_step": decode,
             "mode": "traced (CUDA graph replay), fused attention", "eager_ms": eager_ms,
             "eager_tok_per_s": batch * seq / (eager_ms * 1e-3), "trace_bytes": int(footprint),
             "next_tokens": traced_am.tolist(), "validated": validated, "op_classes_eager": classes,
