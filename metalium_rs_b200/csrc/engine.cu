@@ -2337,6 +2337,11 @@ int32_t b200_decode_layers(b200_engine* e, const b200_decode_shape* shape, b200_
             (b[5]->elem == B200_BFP8 ? 8u : 0u);
     r.pad = 0;
   }
+  {
+    bool any = false, all = true;
+    for (const DecodeLayerPtrs& r : recs) { any = any || r.bfp != 0; all = all && r.bfp == 15u; }
+    sh.weights = !any ? 0u : (all ? 1u : 2u);
+  }
   const int grid = decode_layers_grid();
   const DecodeScratch cut = decode_layers_scratch(sh, grid);
   Buf* O = nullptr;

@@ -703,6 +703,11 @@ struct ClusterParams {
   unsigned long long* part_o;    // [2][tp][MT][hidden]: a cluster's share of the attention output's projection
   unsigned long long* part_dn;   // [2][tp * ks_dn][MT][hidden]: and of the down projection, a slice of k each
   uint32_t ks_q, sl_q;           // the QKV product's k in ks_q slices of sl_q rows: an item a (column block, slice)
+  // BFP8 matrices (every matrix of every layer, or none): a chunk lands as its datum bytes [rows][64] by one tiled copy and
+  // its exponent bytes [rows][4] by 4-byte copies a thread, and is decoded into BF16 before the tensor-core tiles read it
+  uint32_t bfp;
+  uint32_t crows[4];             // rows a chunk's copy brings, by matrix
+  uint32_t kn[4][2];             // the matrices' [k, n]
   TpShape cut;
   unsigned long long* done;      // [2][blocks]: a block's word {0, layer + 1}: it has finished the layer
 };
@@ -743,9 +748,11 @@ struct WeightWalk {
   const ClusterParams* p;
   const ChunkEnt* tab;
   uint32_t cnt, ii, il;                                // the list's length; the next chunk to issue: entry ii of layer il
+  uint32_t ic;                                         // the entry being multiplied (the list repeats every layer)
+  const DecodeLayerDev* lay;                           // the layers' records in shared memory (the BFP8 form reads the matrices' addresses)
   // thread 0 writes the list; every thread calls this, the caller's __syncthreads publishes it
   __device__ void start(const ClusterParams* pp, ChunkEnt* tab_, uint32_t* cnt_sm, uint32_t me, uint32_t C, uint32_t chunk_rows) {
-    p = pp; tab = tab_; ii = 0; il = 0;
+    p = pp; tab = tab_; ii = 0; il = 0; ic = 0; lay = nullptr;
     if (threadIdx.x == 0) {
       const uint32_t H = pp->hidden, QC = pp->heads * HD, NQKV = QC + 2 * pp->kv_heads * HD, FF = pp->ff, nb_h = H / DCOLS;
       uint32_t c = 0;
@@ -765,7 +772,7 @@ struct WeightWalk {
   // the same list for a block of the several-cluster form: its cluster's share, in the order of the phases
   __device__ void start_tp(const ClusterParams* pp, ChunkEnt* tab_, uint32_t* cnt_sm, uint32_t me, uint32_t C, const TpCut& cut,
                            uint32_t chunk_rows) {
-    p = pp; tab = tab_; ii = 0; il = 0;
+    p = pp; tab = tab_; ii = 0; il = 0; ic = 0; lay = nullptr;
     if (threadIdx.x == 0) {
       uint32_t c = 0;
       auto put = [&](uint32_t ph, uint32_t cb, uint32_t k0, uint32_t total) {
@@ -785,9 +792,21 @@ struct WeightWalk {
       *cnt_sm = c;
     }
   }
+  __device__ __forceinline__ void consumed() { if (++ic == cnt) ic = 0; }
   // issue the copy of the next chunk into `slot` (called by every thread of the block; thread 0 issues), then move on
   __device__ __forceinline__ void issue(uint8_t* slot, uint64_t* bar) {
     if (cnt != 0 && il < p->n_layers) {
+      if (p->bfp) {
+        // the chunk's exponent bytes: four a row (the item's 64 columns are four groups of sixteen), a 4-byte copy a row,
+        // whose completion arrives on the slot's barrier with the tiled copy's bytes (the barrier counts every thread)
+        const ChunkEnt e = tab[ii];
+        const uint32_t rows = p->crows[e.phase], K = p->kn[e.phase][0], N = p->kn[e.phase][1];
+        const DecodeLayerDev& L = lay[il];
+        const uint8_t* w = reinterpret_cast<const uint8_t*>(e.phase == 0 ? L.qkv : (e.phase == 1 ? L.o : (e.phase == 2 ? L.gate_up : L.down)));
+        const uint8_t* ex = w + (size_t)K * N + (size_t)e.k0 * (N / 16) + (size_t)e.cb * 4;
+        for (uint32_t r = threadIdx.x; r < rows && e.k0 + r < K; r += DT) cp_async4(slot + (size_t)rows * 64 + r * 4, ex + (size_t)r * (N / 16));
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(tc::smem_u32(bar)) : "memory");
+      }
       if (threadIdx.x == 0) {
         // one copy a chunk: the matrices are described as [k / 64][64][n], so a box of (chunk rows / 64) x 64 x 64 is the
         // chunk's rows in order (at most 256 a dimension); the whole box counts, rows past the matrix filled with zeros
@@ -824,10 +843,44 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 // unit of row k sits at unit ^ (k & 7), so eight rows of one matrix meet eight bank groups).
 // With 16 blocks a step the CUDA cores were the products' bound (unpacking and 8 FMA a 16-byte load: 17 k of a block's
 // 48 k warp instructions a layer); an eighth of a tensor tile is used and it is still an order less issue.
-template <int MT, int R, class Emit>
+// BFP8 chunks: eight datums of a row (one 16-byte piece of the BF16 tile) a thread at a time.  A datum is a sign over a
+// 7-bit magnitude m, its value m 2^(E - 133) under the group's exponent byte E (crates/tt-isa/src/tile.rs:619-634).  Two
+// datums a step on the BF16 pipe: the magnitudes set into the mantissas of two 128.0 give 128 + m exactly, less 128.0 is m,
+// times 2^(E - 133) is the value (a power of two: exact), and the sign bits go on top -- the decoder's bits for every
+// finite group.  An exponent of 255 (a group that keeps an infinity or a NaN), an exponent below 7 (stored as zeros) and a
+// datum 0x80 (the decoder's -infinity) take the decoder itself.
+__device__ __forceinline__ uint32_t bfp8_pair(uint32_t two, uint32_t scale2) {
+  uint32_t m = (two & 0x007f007fu) | 0x43004300u, r;
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(m), "r"(0x43004300u));
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(r), "r"(scale2));
+  return r ^ ((two << 8) & 0x80008000u);
+}
+__device__ __forceinline__ uint4 bfp8_unit(uint2 raw, uint32_t E) {
+  const uint32_t x = raw.x ^ 0x80808080u, y = raw.y ^ 0x80808080u;
+  const uint32_t has80 = (((x - 0x01010101u) & ~x) | ((y - 0x01010101u) & ~y)) & 0x80808080u;
+  uint4 o;
+  if (E == 255u || E < 7u || has80) {
+    uint32_t w[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t src = q < 2 ? raw.x : raw.y, sh = (q & 1) * 16;
+      w[q] = (uint32_t)bfp8_to_bf16_bits((src >> sh) & 0xffu, E) | ((uint32_t)bfp8_to_bf16_bits((src >> (sh + 8)) & 0xffu, E) << 16);
+    }
+    o = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+    const uint32_t s1 = (E - 6u) << 7, s2 = s1 | (s1 << 16);
+    o.x = bfp8_pair(__byte_perm(raw.x, 0, 0x4140), s2);
+    o.y = bfp8_pair(__byte_perm(raw.x, 0, 0x4342), s2);
+    o.z = bfp8_pair(__byte_perm(raw.y, 0, 0x4140), s2);
+    o.w = bfp8_pair(__byte_perm(raw.y, 0, 0x4342), s2);
+  }
+  return o;
+}
+
+template <int MT, int R, bool BFP = false, class Emit>
 __device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, uint32_t len, uint8_t* ring, uint64_t* bars, uint32_t& head,
                                                uint32_t& parity, bool& dead, long long limit, int* err, WeightWalk& walk, float* halves,
-                                               Emit emit) {
+                                               Emit emit, uint8_t* wbuf = nullptr) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const uint32_t mblk = warp & 3, khalf = warp >> 2;
   float c[2][4] = {};
@@ -835,7 +888,9 @@ __device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, 
   // this lane's row and 16-byte unit inside a k-step's sixteen rows, for the load of four 8x8 matrices:
   // matrices 0, 1: rows 0-7, the block's first and second eight columns; 2, 3: rows 8-15
   const uint32_t lrow = (uint32_t)(lane & 7) + ((lane >> 4) << 3), lunit = mblk * 2 + ((lane >> 3) & 1);
-  constexpr uint32_t CHUNK_ROWS = ChunkBoxes<MT>::value * CK_ROWS, SLOT_BYTES = ChunkBoxes<MT>::value * BOX_BYTES;
+  constexpr uint32_t CHUNK_ROWS = ChunkBoxes<MT>::value * CK_ROWS;
+  // a slot holds a chunk as the copies land it: BF16 tiles, or datum bytes [rows][64] and exponent bytes [rows][4]
+  constexpr uint32_t SLOT_BYTES = BFP ? (CHUNK_ROWS * 68 + 1023) / 1024 * 1024 : ChunkBoxes<MT>::value * BOX_BYTES;
   constexpr int HALF_STEPS = CK_ROWS / 32;             // k-steps of 16 rows a warp takes of a box
   for (uint32_t cbase = 0; cbase < len; cbase += CHUNK_ROWS) {
     // the oldest of the R chunks in flight: its tile has landed when the slot's mbarrier flips
@@ -845,10 +900,26 @@ __device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, 
     }
     parity ^= 1u << head;
     const uint32_t boxes = len - cbase < CHUNK_ROWS ? (len - cbase + CK_ROWS - 1) / CK_ROWS : ChunkBoxes<MT>::value;
+    if (BFP) {
+      // decode the chunk into the BF16 tile the loads below expect (row k's 16-byte piece u at piece u ^ (k & 7), as the
+      // BF16 form's copies write it), then give the slot back: its next chunk travels while this one is multiplied
+      const uint8_t* raw = ring + (size_t)head * SLOT_BYTES;
+      const uint32_t crows = walk.p->crows[walk.tab[walk.ic].phase];            // rows the slot's copy brought
+      const uint32_t rows = len - cbase < crows ? (len - cbase + 15) / 16 * 16 : crows;
+      for (uint32_t u = tid; u < rows * 8; u += DT) {
+        const uint32_t r = u >> 3, c8 = u & 7;
+        const uint2 d8 = *reinterpret_cast<const uint2*>(raw + (size_t)r * 64 + c8 * 8);
+        const uint32_t E = raw[(size_t)crows * 64 + r * 4 + (c8 >> 1)];
+        *reinterpret_cast<uint4*>(wbuf + (size_t)r * 128 + ((c8 ^ (r & 7)) << 4)) = bfp8_unit(d8, E);
+      }
+      __syncthreads();                                 // the tile is whole, the slot is read
+      walk.issue(ring + (size_t)head * SLOT_BYTES, &bars[head]);
+    }
 #pragma unroll
     for (uint32_t bx = 0; bx < boxes; ++bx) {
       const uint32_t base = cbase + bx * CK_ROWS + khalf * (CK_ROWS / 2);     // this warp's first k-row of the box, in the item
-      const uint32_t slot = tc::smem_u32(ring + (size_t)head * SLOT_BYTES + (size_t)bx * BOX_BYTES) + khalf * (CK_ROWS / 2) * 128;
+      const uint32_t slot = tc::smem_u32(BFP ? wbuf + (size_t)bx * BOX_BYTES : ring + (size_t)head * SLOT_BYTES + (size_t)bx * BOX_BYTES) +
+                            khalf * (CK_ROWS / 2) * 128;
       // every load first (six loads of four 8x8 matrices, the rows' values beside them), then six MMAs into two accumulators in turn
       uint32_t wq[HALF_STEPS][4], xq[HALF_STEPS][2];
 #pragma unroll
@@ -863,8 +934,9 @@ __device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, 
       for (int i = 0; i < HALF_STEPS; ++i)               // (a step past the item's k is no product: its slot rows may be another chunk's)
         if (base + i * 16 < len) mma_bf16_16816(c[i & 1], wq[i][0], wq[i][1], wq[i][2], wq[i][3], xq[i][0], xq[i][1]);
     }
-    __syncthreads();                                   // every warp is done with the slot: refill it
-    walk.issue(ring + (size_t)head * SLOT_BYTES, &bars[head]);
+    __syncthreads();                                   // every warp is done with the slot (with the decoded tile): refill it
+    if (!BFP) walk.issue(ring + (size_t)head * SLOT_BYTES, &bars[head]);
+    walk.consumed();
     head = head + 1 == (uint32_t)R ? 0 : head + 1;
   }
   // a thread holds columns mblk * 16 + g (and + 8) of rows 2t, 2t + 1 for its half of k: halves[khalf][row][column]
@@ -1295,10 +1367,12 @@ __device__ __forceinline__ void add_parts_tagged(float* x, uint32_t n, const uns
   }
 }
 
-template <int MT>
+template <int MT, bool BFP>
 __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p) {
   constexpr int R = RingDepth<MT>::value;
-  constexpr uint32_t SLOT_BYTES = ChunkBoxes<MT>::value * BOX_BYTES;
+  constexpr uint32_t CHUNK_ROWS = ChunkBoxes<MT>::value * CK_ROWS;
+  constexpr uint32_t SLOT_BYTES = BFP ? (CHUNK_ROWS * 68 + 1023) / 1024 * 1024 : ChunkBoxes<MT>::value * BOX_BYTES;   // as `product_stream` has it
+  constexpr uint32_t WBUF_BYTES = BFP ? CHUNK_ROWS * 128 : 0;   // the BF16 tile a BFP8 chunk is decoded into
   extern __shared__ __align__(16) float smem[];
   cg::cluster_group cluster = cg::this_cluster();
   const uint32_t C = cluster.num_blocks(), me = cluster.block_rank(), lgC = 31 - __clz(C), cgi = blockIdx.x >> lgC;   // C is 8 or 16
@@ -1312,7 +1386,8 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
   const uint32_t cpw = (C * MT + DT / 32 - 1) / (DT / 32), cpa = (C + DT / 32 - 1) / (DT / 32);
   // shared memory (the same offsets in every block of a cluster); every piece is a whole number of 16 bytes
   uint8_t* ring = reinterpret_cast<uint8_t*>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)R * SLOT_BYTES);             // [16]
+  uint8_t* wbuf = ring + (size_t)R * SLOT_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(wbuf + WBUF_BYTES);                         // [16]
   uint4* ksm = reinterpret_cast<uint4*>(bars + 16);
   uint4* vsm = ksm + DCH * 8;
   float* xres = reinterpret_cast<float*>(vsm + DCH * 8);          // [MT][H]
@@ -1369,6 +1444,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
   }
   __syncthreads();
   walk.cnt = *tab_len;
+  walk.lay = lay;
   for (uint32_t c = tid; c < H; c += DT) g1[c] = bf16_at(lay[0].norm1, c);
   uint32_t head = 0, parity = 0;
   bool dead = false;
@@ -1376,7 +1452,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
   uint64_t* xb = &bars[8];                            // [3]: QKV, attention partials, gate|up
   const uint32_t expect[3] = {cut.n_qs * MT * DCOLS * 4, att_l * group * APH * 4, cut.n_gu * MT * DCOLS * 2};
   if (tid == 0) {
-    for (int r = 0; r < R; ++r) tc::mbar_init(&bars[r], 1);
+    for (int r = 0; r < R; ++r) tc::mbar_init(&bars[r], BFP ? 1 + DT : 1);   // (a BFP8 chunk's exponent bytes: every thread's copies arrive)
     for (int k = 0; k < 3; ++k) tc::mbar_init(&xb[k], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     for (int k = 0; k < 3; ++k) tc::mbar_expect_tx(&xb[k], expect[k]);   // layer 0's
@@ -1411,8 +1487,8 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
         const uint32_t jc = e.x, ks = e.y, k0 = e.z, len = e.w;
         float* slot = sq + (size_t)idx * MT * DCOLS;
         const bool whole = p.ks_q == 1;                  // one slice: the sender rounds, the receivers take the values as they come
-        product_stream<MT, R>(vec + k0, p.vec_cols, len, ring, bars, head, parity, dead, limit, p.err, walk, halves,
-                              [&](int r, int cc, float t) { slot[r * DCOLS + cc] = whole ? bf16_round(t) : t; });
+        product_stream<MT, R, BFP>(vec + k0, p.vec_cols, len, ring, bars, head, parity, dead, limit, p.err, walk, halves,
+                              [&](int r, int cc, float t) { slot[r * DCOLS + cc] = whole ? bf16_round(t) : t; }, wbuf);
         if (const uint32_t ci = (uint32_t)(tid >> 5) * cpw + (tid & 31); (uint32_t)(tid & 31) < cpw && ci < C * MT) {
           const uint32_t d = ci / MT, r = ci - d * MT;
           copy_to_block((whole ? qkv : qkvp + (size_t)ks * MT * NQl) + (size_t)r * NQl + jc * DCOLS, slot + r * DCOLS, DCOLS * 4, &xb[0], d);
@@ -1585,8 +1661,8 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
     __syncthreads();
     for (uint32_t j = j0o; j < cut.nb_h; j += C) {
       unsigned long long* dst = p.part_o + ((size_t)(l & 1u) * p.tp + cgi) * MT * H + j * DCOLS;
-      product_stream<MT, R>(vec, p.vec_cols, QCl, ring, bars, head, parity, dead, limit, p.err, walk, halves,
-                            [&](int r, int cc, float t) { st_tagged(dst + (size_t)r * H + cc, t, l + 1); });
+      product_stream<MT, R, BFP>(vec, p.vec_cols, QCl, ring, bars, head, parity, dead, limit, p.err, walk, halves,
+                            [&](int r, int cc, float t) { st_tagged(dst + (size_t)r * H + cc, t, l + 1); }, wbuf);
     }
 
     // ---- phase 4: the residual, norm, the cluster's gate and up columns ----
@@ -1603,9 +1679,9 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
     {
       for (uint32_t j = j0q, idx = 0; j < cut.n_gu; j += C, ++idx) {
         uint16_t* slot = reinterpret_cast<uint16_t*>(sg) + (size_t)idx * MT * DCOLS;
-        product_stream<MT, R>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk, halves, [&](int r, int cc, float t) {
+        product_stream<MT, R, BFP>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk, halves, [&](int r, int cc, float t) {
           slot[r * DCOLS + cc] = f32_to_bf16_bits(__float_as_uint(t));
-        });
+        }, wbuf);
         if (const uint32_t ci = (uint32_t)(tid >> 5) * cpw + (tid & 31); (uint32_t)(tid & 31) < cpw && ci < C * MT) {
           const uint32_t d = ci / MT, r = ci - d * MT;
           copy_to_block(gu + (size_t)r * 2 * FFl + j * DCOLS, slot + r * DCOLS, DCOLS * 2, &xb[2], d);
@@ -1630,8 +1706,8 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
       }
       __syncthreads();
       unsigned long long* dst = p.part_dn + ((size_t)(l & 1u) * nparts_dn + (size_t)cgi * p.ks_dn + ks) * MT * H + cb * DCOLS;
-      product_stream<MT, R>(vec, p.vec_cols, len, ring, bars, head, parity, dead, limit, p.err, walk, halves,
-                            [&](int r, int cc, float t) { st_tagged(dst + (size_t)r * H + cc, t, l + 1); });
+      product_stream<MT, R, BFP>(vec, p.vec_cols, len, ring, bars, head, parity, dead, limit, p.err, walk, halves,
+                            [&](int r, int cc, float t) { st_tagged(dst + (size_t)r * H + cc, t, l + 1); }, wbuf);
     }
     // every thread of the block is past its last read of what the layer sent it (each path here ends in a block barrier)
     if (tid == 0) st_tagged(p.done + (size_t)(l & 1u) * gridDim.x + blockIdx.x, 0.f, l + 1);
@@ -1686,16 +1762,16 @@ cudaError_t launch_cluster(const ClusterParams& p, size_t smem, int* cluster_blo
 // The several-cluster form's launch: `p.tp` clusters of the widest width the device holds all at once (every block meets
 // every other twice a layer, so the launch is made only where the occupancy figure says they are resident together;
 // the meetings' waits are bounded all the same).
-template <int MT>
+template <int MT, bool BFP>
 cudaError_t launch_tp(const ClusterParams& p, size_t smem, int* cluster_blocks, cudaStream_t stream) {
-  cudaError_t e = ensure_dynamic_smem((const void*)decode_tp_kernel<MT>, smem);
+  cudaError_t e = ensure_dynamic_smem((const void*)decode_tp_kernel<MT, BFP>, smem);
   if (e != cudaSuccess) return e;
   int found = 0;                                       // width * 256 + clusters the device holds at once
-  if (!device_value_get((const void*)decode_tp_kernel<MT>, &found)) {
+  if (!device_value_get((const void*)decode_tp_kernel<MT, BFP>, &found)) {
     found = 0;
     for (int c : {16, 8}) {
       if ((uint32_t)c < p.min_width) continue;
-      if (c > 8 && cudaFuncSetAttribute((const void*)decode_tp_kernel<MT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+      if (c > 8 && cudaFuncSetAttribute((const void*)decode_tp_kernel<MT, BFP>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
         cudaGetLastError();
         continue;
       }
@@ -1706,10 +1782,10 @@ cudaError_t launch_tp(const ClusterParams& p, size_t smem, int* cluster_blocks, 
       at[0].val.clusterDim.x = c; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
       cfg.attrs = at; cfg.numAttrs = 1;
       int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, decode_tp_kernel<MT>, &cfg) == cudaSuccess && n >= (int)p.tp) { found = c * 256 + (n > 255 ? 255 : n); break; }
+      if (cudaOccupancyMaxActiveClusters(&n, decode_tp_kernel<MT, BFP>, &cfg) == cudaSuccess && n >= (int)p.tp) { found = c * 256 + (n > 255 ? 255 : n); break; }
       cudaGetLastError();
     }
-    device_value_set((const void*)decode_tp_kernel<MT>, found);
+    device_value_set((const void*)decode_tp_kernel<MT, BFP>, found);
   }
   const int width = found / 256, held = found % 256;
   if (width < 8 || (uint32_t)width < p.min_width || held < (int)p.tp) return cudaErrorNotSupported;
@@ -1720,7 +1796,7 @@ cudaError_t launch_tp(const ClusterParams& p, size_t smem, int* cluster_blocks, 
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = width; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, decode_tp_kernel<MT>, p);
+  return cudaLaunchKernelEx(&cfg, decode_tp_kernel<MT, BFP>, p);
 }
 
 uint32_t slices_for(uint32_t col_blocks, uint32_t k, uint32_t grid, uint32_t* slice_len) {
@@ -1826,7 +1902,8 @@ bool tp_plan(const DecodeShape& sh, TpPlan* t) {
   }
   t->G = G; t->ks = ks; t->sl = sl; t->vc = vc; t->att_items = att_l;
   const size_t ring_slots = MTc == 1 ? RingDepth<1>::value : (MTc == 2 ? RingDepth<2>::value : RingDepth<4>::value);
-  const size_t SLOT_BYTES = (size_t)chunk_rows * 128;
+  const bool bfp = sh.weights == 1;                    // datum and exponent bytes in the slots, and the BF16 tile a chunk is decoded into
+  const size_t SLOT_BYTES = bfp ? ((size_t)chunk_rows * 68 + 1023) / 1024 * 1024 + (size_t)chunk_rows * 128 / ring_slots : (size_t)chunk_rows * 128;
   const uint64_t n_q = (uint64_t)(hq + 2 * hk) * ks_q, nb_h = sh.hidden / DCOLS, n_gu = 2 * FFl / DCOLS, n_dn = nb_h * ks;
   constexpr uint64_t AP = 4 * (HD + 4);
   for (uint32_t width : {8u, 16u}) {
@@ -1851,8 +1928,9 @@ bool tp_plan(const DecodeShape& sh, TpPlan* t) {
 // B200TT_DECODE=one force the grid and the one-cluster form (development switches; the tests run all three).
 int cluster_form_of(const DecodeShape& sh, TpPlan* t) {
   const char* form = getenv("B200TT_DECODE");
-  if (form && form[0] == 'g') return 0;
+  if ((form && form[0] == 'g') || sh.weights == 2) return 0;   // (BF16 and BFP8 matrices mixed: the grid form takes each as it is)
   if (!(form && form[0] == 'o') && tp_plan(sh, t)) return 2;
+  if (sh.weights != 0) return 0;                       // the one-cluster form multiplies BF16 tiles where they land
   ClusterParams c{};
   size_t smem = 0;
   return cluster_plan(sh, c, &smem) ? 1 : 0;
@@ -1907,16 +1985,18 @@ bool decode_layers_make_maps(const DecodeShape& sh, const DecodeLayerPtrs* recs,
   for (uint32_t l = 0; l < sh.layers; ++l) {
     const void* w[4] = {recs[l].qkv, recs[l].o, recs[l].gate_up, recs[l].down};
     for (int i = 0; i < 4; ++i) {
-      if ((recs[l].bfp >> i) & 1u) return false;        // the cluster form multiplies BF16 tiles where they land
+      const bool bfp = (recs[l].bfp >> i) & 1u;
+      if (bfp != (sh.weights == 1) || (bfp && form != 2)) return false;   // every matrix as the shape says; BFP8 only in the several-cluster form
+      if (kn[i][0] % 64) return false;
+      const uint64_t eb = bfp ? 1 : 2;                 // BFP8: the datum bytes [k, n] (the exponent bytes behind them travel by plain copies)
       // [k, n] seen as [k / 64][64][n]: a box of (a chunk's rows / 64) x 64 rows x 64 columns lands as the chunk's rows in order
       const cuuint64_t dims[3] = {kn[i][1], 64, (kn[i][0] + 63) / 64};
-      const cuuint64_t strides[2] = {kn[i][1] * 2u, kn[i][1] * 2u * 64u};
+      const cuuint64_t strides[2] = {kn[i][1] * eb, kn[i][1] * eb * 64u};
       const cuuint32_t box[3] = {(cuuint32_t)DCOLS, 64u, (cuuint32_t)((form == 2 ? t.cr[i] : chunk_rows_of(MTm)) / 64)};
       const cuuint32_t estr[3] = {1, 1, 1};
-      if (kn[i][0] % 64) return false;
-      if (fn(&maps[(size_t)l * 4 + i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(w[i]),
-             dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      if (fn(&maps[(size_t)l * 4 + i], bfp ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(w[i]),
+             dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, bfp ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
     }
   }
@@ -1939,7 +2019,7 @@ int decode_layers_grid() {
 // development switch; the tests run both).
 bool decode_layers_cluster_wanted(const DecodeShape& sh, bool any_bfp) {
   TpPlan t{};
-  return !any_bfp && cluster_form_of(sh, &t) != 0;
+  return (!any_bfp || sh.weights == 1) && cluster_form_of(sh, &t) != 0;
 }
 
 cudaError_t launch_decode_layers(const DecodeShape& sh, const DecodeLayerPtrs* layers_dev, const float* x0, const void* final_norm,
@@ -1965,7 +2045,14 @@ cudaError_t launch_decode_layers(const DecodeShape& sh, const DecodeLayerPtrs* l
       u.n_gu = 2 * u.nfl; u.n_dn = u.nb_h * t.ks;
       u.off_att = u.n_qs; u.off_o = u.off_att + u.n_att; u.off_dn = u.off_o + u.nb_h; u.group = sh.heads / sh.kv_heads;
     }
-    for (int i = 0; i < 4; ++i) c.pbytes[i] = t.cr[i] * 128;
+    const bool bfp = sh.weights == 1;
+    c.bfp = bfp ? 1u : 0u;
+    for (int i = 0; i < 4; ++i) { c.crows[i] = t.cr[i]; c.pbytes[i] = t.cr[i] * (bfp ? 64 : 128); }
+    {
+      const uint32_t QCg = sh.heads * HD, NQg = QCg + 2 * sh.kv_heads * HD;
+      const uint32_t kn[4][2] = {{sh.hidden, NQg}, {QCg, sh.hidden}, {sh.hidden, 2 * sh.ff}, {sh.ff, sh.hidden}};
+      for (int i = 0; i < 4; ++i) { c.kn[i][0] = kn[i][0]; c.kn[i][1] = kn[i][1]; }
+    }
     c.layers = reinterpret_cast<const DecodeLayerDev*>(layers_dev);
     c.x0 = x0; c.final_norm = final_norm; c.cos = cos_t; c.sin = sin_t; c.pos = pos; c.out = out; c.err = err;
     c.maps = reinterpret_cast<const CUtensorMap*>(maps_dev);
@@ -1979,7 +2066,12 @@ cudaError_t launch_decode_layers(const DecodeShape& sh, const DecodeLayerPtrs* l
     cudaError_t ce = cudaMemsetAsync(c.part_o, 0, (words_o + words_dn + words_done) * sizeof(unsigned long long), stream);
     if (ce != cudaSuccess) return ce;
     int width = 0;
-    ce = MTc == 1 ? launch_tp<1>(c, t.smem, &width, stream) : (MTc == 2 ? launch_tp<2>(c, t.smem, &width, stream) : launch_tp<4>(c, t.smem, &width, stream));
+    if (bfp)
+      ce = MTc == 1 ? launch_tp<1, true>(c, t.smem, &width, stream)
+                    : (MTc == 2 ? launch_tp<2, true>(c, t.smem, &width, stream) : launch_tp<4, true>(c, t.smem, &width, stream));
+    else
+      ce = MTc == 1 ? launch_tp<1, false>(c, t.smem, &width, stream)
+                    : (MTc == 2 ? launch_tp<2, false>(c, t.smem, &width, stream) : launch_tp<4, false>(c, t.smem, &width, stream));
     if (ce != cudaErrorNotSupported) {
       static const char* const names[2][3] = {{"cluster8x2", "cluster8x3", "cluster8x4"}, {"cluster16x2", "cluster16x3", "cluster16x4"}};
       *form = names[width == 16][t.G - 2];

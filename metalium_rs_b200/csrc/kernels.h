@@ -198,7 +198,11 @@ cudaError_t launch_gemm_skinny_bfp(const uint16_t* a, uint64_t lda, const uint8_
                                    int out_bf16, uint64_t m, uint64_t n, uint64_t k, cudaStream_t stream);
 
 // One decode step through every layer in one cooperative launch (k_decode.cu).
-struct DecodeShape { uint32_t layers, rows, hidden, heads, kv_heads, head_dim, ff, max_len, attend; float eps, scale; };
+struct DecodeShape {
+  uint32_t layers, rows, hidden, heads, kv_heads, head_dim, ff, max_len, attend;
+  float eps, scale;
+  uint32_t weights;   // the layers' matrices: 0 every one BF16, 1 every one BFP8, 2 some of each
+};
 struct DecodeLayerPtrs {          // a layer's operands as device addresses (a device array, one record a layer)
   const void *norm1, *qkv, *o, *norm2, *gate_up, *down;   // gains BF16 [1, hidden]; matrices [k, n] BF16 or BFP8
   void *kc, *vc;                                           // the layer's key and value cache, [rows * max_len, kv_heads * 64] BF16
