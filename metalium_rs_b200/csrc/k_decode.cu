@@ -798,7 +798,7 @@ struct WeightWalk {
     if (cnt != 0 && il < p->n_layers) {
       if (p->bfp) {
         // the chunk's exponent bytes: four a row (the item's 64 columns are four groups of sixteen), a 4-byte copy a row,
-        // whose completion arrives on the slot's barrier with the tiled copy's bytes (the barrier counts every thread)
+        // whose completion arrives on the slot's barrier with the tiled copy's bytes (the barrier counts every thread: one warp issuing a chunk's 576 copies held the block up for ~1,000 cycles)
         const ChunkEnt e = tab[ii];
         const uint32_t rows = p->crows[e.phase], K = p->kn[e.phase][0], N = p->kn[e.phase][1];
         const DecodeLayerDev& L = lay[il];
@@ -849,31 +849,33 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 // times 2^(E - 133) is the value (a power of two: exact), and the sign bits go on top -- the decoder's bits for every
 // finite group.  An exponent of 255 (a group that keeps an infinity or a NaN), an exponent below 7 (stored as zeros) and a
 // datum 0x80 (the decoder's -infinity) take the decoder itself.
-__device__ __forceinline__ uint32_t bfp8_pair(uint32_t two, uint32_t scale2) {
-  uint32_t m = (two & 0x007f007fu) | 0x43004300u, r;
-  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(m), "r"(0x43004300u));
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(r), "r"(scale2));
-  return r ^ ((two << 8) & 0x80008000u);
+__device__ __forceinline__ uint32_t bfp8_pair(uint32_t two, uint32_t scale2, uint32_t off2) {
+  // `two`: a datum in both bytes of each half.  (128 + m) s - 128 s in one rounding: every term a BF16 value, the result exact
+  uint32_t r;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"((two & 0x007f007fu) | 0x43004300u), "r"(scale2), "r"(off2));
+  return r ^ (two & 0x80008000u);
 }
-__device__ __forceinline__ uint4 bfp8_unit(uint2 raw, uint32_t E) {
+__device__ __forceinline__ bool bfp8_slow(uint2 raw, uint32_t E) {
   const uint32_t x = raw.x ^ 0x80808080u, y = raw.y ^ 0x80808080u;
-  const uint32_t has80 = (((x - 0x01010101u) & ~x) | ((y - 0x01010101u) & ~y)) & 0x80808080u;
-  uint4 o;
-  if (E == 255u || E < 7u || has80) {
-    uint32_t w[4];
+  return E >= 254u || E < 7u || ((((x - 0x01010101u) & ~x) | ((y - 0x01010101u) & ~y)) & 0x80808080u) != 0;   // (254: 128 s would overflow)
+}
+__device__ __forceinline__ uint4 bfp8_unit_slow(uint2 raw, uint32_t E) {
+  uint32_t w[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const uint32_t src = q < 2 ? raw.x : raw.y, sh = (q & 1) * 16;
-      w[q] = (uint32_t)bfp8_to_bf16_bits((src >> sh) & 0xffu, E) | ((uint32_t)bfp8_to_bf16_bits((src >> (sh + 8)) & 0xffu, E) << 16);
-    }
-    o = make_uint4(w[0], w[1], w[2], w[3]);
-  } else {
-    const uint32_t s1 = (E - 6u) << 7, s2 = s1 | (s1 << 16);
-    o.x = bfp8_pair(__byte_perm(raw.x, 0, 0x4140), s2);
-    o.y = bfp8_pair(__byte_perm(raw.x, 0, 0x4342), s2);
-    o.z = bfp8_pair(__byte_perm(raw.y, 0, 0x4140), s2);
-    o.w = bfp8_pair(__byte_perm(raw.y, 0, 0x4342), s2);
+  for (int q = 0; q < 4; ++q) {
+    const uint32_t src = q < 2 ? raw.x : raw.y, sh = (q & 1) * 16;
+    w[q] = (uint32_t)bfp8_to_bf16_bits((src >> sh) & 0xffu, E) | ((uint32_t)bfp8_to_bf16_bits((src >> (sh + 8)) & 0xffu, E) << 16);
   }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ uint4 bfp8_unit_fast(uint2 raw, uint32_t E) {
+  const uint32_t s1 = (E - 6u) << 7, s2 = s1 | (s1 << 16);             // 2^(E - 133) twice
+  const uint32_t o1 = ((E + 1u) << 7) | 0x8000u, o2 = o1 | (o1 << 16);  // -128 of them
+  uint4 o;
+  o.x = bfp8_pair(__byte_perm(raw.x, 0, 0x1100), s2, o2);
+  o.y = bfp8_pair(__byte_perm(raw.x, 0, 0x3322), s2, o2);
+  o.z = bfp8_pair(__byte_perm(raw.y, 0, 0x1100), s2, o2);
+  o.w = bfp8_pair(__byte_perm(raw.y, 0, 0x3322), s2, o2);
   return o;
 }
 
@@ -906,11 +908,24 @@ __device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, 
       const uint8_t* raw = ring + (size_t)head * SLOT_BYTES;
       const uint32_t crows = walk.p->crows[walk.tab[walk.ic].phase];            // rows the slot's copy brought
       const uint32_t rows = len - cbase < crows ? (len - cbase + 15) / 16 * 16 : crows;
-      for (uint32_t u = tid; u < rows * 8; u += DT) {
-        const uint32_t r = u >> 3, c8 = u & 7;
-        const uint2 d8 = *reinterpret_cast<const uint2*>(raw + (size_t)r * 64 + c8 * 8);
-        const uint32_t E = raw[(size_t)crows * 64 + r * 4 + (c8 >> 1)];
-        *reinterpret_cast<uint4*>(wbuf + (size_t)r * 128 + ((c8 ^ (r & 7)) << 4)) = bfp8_unit(d8, E);
+      // (two pieces a step, 32 rows apart: their chains interleave; rows is a multiple of 16 and a step covers 32 rows)
+      const uint32_t c8 = tid & 7, r0 = tid >> 3;
+      const uint32_t sraw = tc::smem_u32(raw) + c8 * 8, sex = tc::smem_u32(raw) + crows * 64 + (c8 >> 1), sout = tc::smem_u32(wbuf);
+      for (uint32_t r = r0; r < rows; r += 64) {
+        const bool two = r + 32 < rows;
+        const uint32_t rb = two ? r + 32 : r;
+        uint2 da, db;
+        uint32_t Ea, Eb;
+        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(da.x), "=r"(da.y) : "r"(sraw + r * 64));
+        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(db.x), "=r"(db.y) : "r"(sraw + rb * 64));
+        asm volatile("ld.shared.u8 %0, [%1];" : "=r"(Ea) : "r"(sex + r * 4));
+        asm volatile("ld.shared.u8 %0, [%1];" : "=r"(Eb) : "r"(sex + rb * 4));
+        uint4 oa, ob;
+        if (bfp8_slow(da, Ea) || bfp8_slow(db, Eb)) { oa = bfp8_unit_slow(da, Ea); ob = bfp8_unit_slow(db, Eb); }
+        else { oa = bfp8_unit_fast(da, Ea); ob = bfp8_unit_fast(db, Eb); }
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sout + r * 128 + ((c8 ^ (r & 7)) << 4)), "r"(oa.x), "r"(oa.y), "r"(oa.z), "r"(oa.w) : "memory");
+        if (two)
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sout + rb * 128 + ((c8 ^ (rb & 7)) << 4)), "r"(ob.x), "r"(ob.y), "r"(ob.z), "r"(ob.w) : "memory");
       }
       __syncthreads();                                 // the tile is whole, the slot is read
       walk.issue(ring + (size_t)head * SLOT_BYTES, &bars[head]);
