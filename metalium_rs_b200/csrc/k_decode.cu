@@ -748,11 +748,11 @@ struct WeightWalk {
   const ClusterParams* p;
   const ChunkEnt* tab;
   uint32_t cnt, ii, il;                                // the list's length; the next chunk to issue: entry ii of layer il
-  uint32_t ic;                                         // the entry being multiplied (the list repeats every layer)
+  uint32_t ic, lc;                                     // the entry being multiplied, of layer lc (the list repeats every layer)
   const DecodeLayerDev* lay;                           // the layers' records in shared memory (the BFP8 form reads the matrices' addresses)
   // thread 0 writes the list; every thread calls this, the caller's __syncthreads publishes it
   __device__ void start(const ClusterParams* pp, ChunkEnt* tab_, uint32_t* cnt_sm, uint32_t me, uint32_t C, uint32_t chunk_rows) {
-    p = pp; tab = tab_; ii = 0; il = 0; ic = 0; lay = nullptr;
+    p = pp; tab = tab_; ii = 0; il = 0; ic = 0; lc = 0; lay = nullptr;
     if (threadIdx.x == 0) {
       const uint32_t H = pp->hidden, QC = pp->heads * HD, NQKV = QC + 2 * pp->kv_heads * HD, FF = pp->ff, nb_h = H / DCOLS;
       uint32_t c = 0;
@@ -772,7 +772,7 @@ struct WeightWalk {
   // the same list for a block of the several-cluster form: its cluster's share, in the order of the phases
   __device__ void start_tp(const ClusterParams* pp, ChunkEnt* tab_, uint32_t* cnt_sm, uint32_t me, uint32_t C, const TpCut& cut,
                            uint32_t chunk_rows) {
-    p = pp; tab = tab_; ii = 0; il = 0; ic = 0; lay = nullptr;
+    p = pp; tab = tab_; ii = 0; il = 0; ic = 0; lc = 0; lay = nullptr;
     if (threadIdx.x == 0) {
       uint32_t c = 0;
       auto put = [&](uint32_t ph, uint32_t cb, uint32_t k0, uint32_t total) {
@@ -792,7 +792,7 @@ struct WeightWalk {
       *cnt_sm = c;
     }
   }
-  __device__ __forceinline__ void consumed() { if (++ic == cnt) ic = 0; }
+  __device__ __forceinline__ void consumed() { if (++ic == cnt) { ic = 0; ++lc; } }
   // issue the copy of the next chunk into `slot` (called by every thread of the block; thread 0 issues), then move on
   __device__ __forceinline__ void issue(uint8_t* slot, uint64_t* bar) {
     if (cnt != 0 && il < p->n_layers) {
@@ -879,10 +879,55 @@ __device__ __forceinline__ uint4 bfp8_unit_fast(uint2 raw, uint32_t E) {
   return o;
 }
 
+// A landed BFP8 chunk (datum bytes [crows][64], then exponent bytes [crows][4]) into the BF16 tile the tensor-core loads
+// expect: row k's 16-byte piece u at piece u ^ (k & 7), as the BF16 form's copies write it.  Every thread; two pieces a
+// step, 32 rows apart, so that their chains interleave (`rows` is a multiple of 16).
+__device__ __forceinline__ void decode_chunk(const uint8_t* raw, uint32_t crows, uint32_t rows, uint8_t* wbuf) {
+  const uint32_t tid = threadIdx.x, c8 = tid & 7, r0 = tid >> 3;
+  const uint32_t sraw = tc::smem_u32(raw) + c8 * 8, sex = tc::smem_u32(raw) + crows * 64 + (c8 >> 1), sout = tc::smem_u32(wbuf);
+  for (uint32_t r = r0; r < rows; r += 64) {
+    const bool two = r + 32 < rows;
+    const uint32_t rb = two ? r + 32 : r;
+    uint2 da, db;
+    uint32_t Ea, Eb;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(da.x), "=r"(da.y) : "r"(sraw + r * 64));
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(db.x), "=r"(db.y) : "r"(sraw + rb * 64));
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(Ea) : "r"(sex + r * 4));
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(Eb) : "r"(sex + rb * 4));
+    uint4 oa, ob;
+    if (bfp8_slow(da, Ea) || bfp8_slow(db, Eb)) { oa = bfp8_unit_slow(da, Ea); ob = bfp8_unit_slow(db, Eb); }
+    else { oa = bfp8_unit_fast(da, Ea); ob = bfp8_unit_fast(db, Eb); }
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sout + r * 128 + ((c8 ^ (r & 7)) << 4)), "r"(oa.x), "r"(oa.y), "r"(oa.z), "r"(oa.w) : "memory");
+    if (two)
+      asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sout + rb * 128 + ((c8 ^ (rb & 7)) << 4)), "r"(ob.x), "r"(ob.y), "r"(ob.z), "r"(ob.w) : "memory");
+  }
+}
+
+// The BFP8 form's next chunk taken ahead of its product: waited for, decoded into the (free) BF16 tile, its slot given
+// back.  A block calls this when a phase's items are done and sent, before it waits for the other blocks: the decode
+// (some 3,000 cycles a 576-row chunk) then runs in time the block would have spent waiting.  `ahead` tells the product
+// that its first chunk is already in the tile.
+template <int MT, int R>
+__device__ __forceinline__ void decode_ahead(uint8_t* ring, uint64_t* bars, uint32_t head, uint32_t& parity, bool& dead, long long limit,
+                                             int* err, WeightWalk& walk, uint8_t* wbuf, bool& ahead) {
+  constexpr uint32_t SLOT_BYTES = (ChunkBoxes<MT>::value * CK_ROWS * 68 + 1023) / 1024 * 1024;
+  if (ahead || walk.cnt == 0 || walk.lc >= walk.p->n_layers) return;
+  if (!dead && !tc::mbar_wait(&bars[head], (parity >> head) & 1u, &dead_flag_of(err), limit)) {
+    dead = true;
+    atomicCAS(err, 0, TIMEOUT_CODE);
+  }
+  parity ^= 1u << head;
+  const ChunkEnt e = walk.tab[walk.ic];
+  decode_chunk(ring + (size_t)head * SLOT_BYTES, walk.p->crows[e.phase], ((uint32_t)e.rows + 15) / 16 * 16, wbuf);
+  __syncthreads();                                     // the tile is whole, the slot is read
+  walk.issue(ring + (size_t)head * SLOT_BYTES, &bars[head]);
+  ahead = true;
+}
+
 template <int MT, int R, bool BFP = false, class Emit>
 __device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, uint32_t len, uint8_t* ring, uint64_t* bars, uint32_t& head,
                                                uint32_t& parity, bool& dead, long long limit, int* err, WeightWalk& walk, float* halves,
-                                               Emit emit, uint8_t* wbuf = nullptr) {
+                                               Emit emit, uint8_t* wbuf = nullptr, bool* ahead = nullptr) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const uint32_t mblk = warp & 3, khalf = warp >> 2;
   float c[2][4] = {};
@@ -895,40 +940,23 @@ __device__ __forceinline__ void product_stream(const uint16_t* a, uint32_t lda, 
   constexpr uint32_t SLOT_BYTES = BFP ? (CHUNK_ROWS * 68 + 1023) / 1024 * 1024 : ChunkBoxes<MT>::value * BOX_BYTES;
   constexpr int HALF_STEPS = CK_ROWS / 32;             // k-steps of 16 rows a warp takes of a box
   for (uint32_t cbase = 0; cbase < len; cbase += CHUNK_ROWS) {
-    // the oldest of the R chunks in flight: its tile has landed when the slot's mbarrier flips
-    if (!dead && !tc::mbar_wait(&bars[head], (parity >> head) & 1u, &dead_flag_of(err), limit)) {
-      dead = true;                                     // recorded; the block walks on without waiting, so that the cluster's barriers are still met
-      atomicCAS(err, 0, TIMEOUT_CODE);
-    }
-    parity ^= 1u << head;
     const uint32_t boxes = len - cbase < CHUNK_ROWS ? (len - cbase + CK_ROWS - 1) / CK_ROWS : ChunkBoxes<MT>::value;
-    if (BFP) {
-      // decode the chunk into the BF16 tile the loads below expect (row k's 16-byte piece u at piece u ^ (k & 7), as the
-      // BF16 form's copies write it), then give the slot back: its next chunk travels while this one is multiplied
-      const uint8_t* raw = ring + (size_t)head * SLOT_BYTES;
-      const uint32_t crows = walk.p->crows[walk.tab[walk.ic].phase];            // rows the slot's copy brought
-      const uint32_t rows = len - cbase < crows ? (len - cbase + 15) / 16 * 16 : crows;
-      // (two pieces a step, 32 rows apart: their chains interleave; rows is a multiple of 16 and a step covers 32 rows)
-      const uint32_t c8 = tid & 7, r0 = tid >> 3;
-      const uint32_t sraw = tc::smem_u32(raw) + c8 * 8, sex = tc::smem_u32(raw) + crows * 64 + (c8 >> 1), sout = tc::smem_u32(wbuf);
-      for (uint32_t r = r0; r < rows; r += 64) {
-        const bool two = r + 32 < rows;
-        const uint32_t rb = two ? r + 32 : r;
-        uint2 da, db;
-        uint32_t Ea, Eb;
-        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(da.x), "=r"(da.y) : "r"(sraw + r * 64));
-        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(db.x), "=r"(db.y) : "r"(sraw + rb * 64));
-        asm volatile("ld.shared.u8 %0, [%1];" : "=r"(Ea) : "r"(sex + r * 4));
-        asm volatile("ld.shared.u8 %0, [%1];" : "=r"(Eb) : "r"(sex + rb * 4));
-        uint4 oa, ob;
-        if (bfp8_slow(da, Ea) || bfp8_slow(db, Eb)) { oa = bfp8_unit_slow(da, Ea); ob = bfp8_unit_slow(db, Eb); }
-        else { oa = bfp8_unit_fast(da, Ea); ob = bfp8_unit_fast(db, Eb); }
-        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sout + r * 128 + ((c8 ^ (r & 7)) << 4)), "r"(oa.x), "r"(oa.y), "r"(oa.z), "r"(oa.w) : "memory");
-        if (two)
-          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sout + rb * 128 + ((c8 ^ (rb & 7)) << 4)), "r"(ob.x), "r"(ob.y), "r"(ob.z), "r"(ob.w) : "memory");
+    if (BFP && *ahead) {
+      *ahead = false;                                  // `decode_ahead` waited for this chunk, decoded it and gave its slot back
+    } else {
+      // the oldest of the R chunks in flight: its tile has landed when the slot's mbarrier flips
+      if (!dead && !tc::mbar_wait(&bars[head], (parity >> head) & 1u, &dead_flag_of(err), limit)) {
+        dead = true;                                   // recorded; the block walks on without waiting, so that the cluster's barriers are still met
+        atomicCAS(err, 0, TIMEOUT_CODE);
       }
-      __syncthreads();                                 // the tile is whole, the slot is read
-      walk.issue(ring + (size_t)head * SLOT_BYTES, &bars[head]);
+      parity ^= 1u << head;
+      if (BFP) {
+        // decode the chunk into the BF16 tile, then give the slot back: its next chunk travels while this one is multiplied
+        const uint32_t crows = walk.p->crows[walk.tab[walk.ic].phase];          // rows the slot's copy brought
+        decode_chunk(ring + (size_t)head * SLOT_BYTES, crows, len - cbase < crows ? (len - cbase + 15) / 16 * 16 : crows, wbuf);
+        __syncthreads();                               // the tile is whole, the slot is read
+        walk.issue(ring + (size_t)head * SLOT_BYTES, &bars[head]);
+      }
     }
 #pragma unroll
     for (uint32_t bx = 0; bx < boxes; ++bx) {
@@ -1462,7 +1490,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
   walk.lay = lay;
   for (uint32_t c = tid; c < H; c += DT) g1[c] = bf16_at(lay[0].norm1, c);
   uint32_t head = 0, parity = 0;
-  bool dead = false;
+  bool dead = false, ahead = false;                    // (BFP8: the next chunk is already decoded into the tile)
   const long long limit = tc::wait_limit_of(p.err);
   uint64_t* xb = &bars[8];                            // [3]: QKV, attention partials, gate|up
   const uint32_t expect[3] = {cut.n_qs * MT * DCOLS * 4, att_l * group * APH * 4, cut.n_gu * MT * DCOLS * 2};
@@ -1503,7 +1531,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
         float* slot = sq + (size_t)idx * MT * DCOLS;
         const bool whole = p.ks_q == 1;                  // one slice: the sender rounds, the receivers take the values as they come
         product_stream<MT, R, BFP>(vec + k0, p.vec_cols, len, ring, bars, head, parity, dead, limit, p.err, walk, halves,
-                              [&](int r, int cc, float t) { slot[r * DCOLS + cc] = whole ? bf16_round(t) : t; }, wbuf);
+                              [&](int r, int cc, float t) { slot[r * DCOLS + cc] = whole ? bf16_round(t) : t; }, wbuf, &ahead);
         if (const uint32_t ci = (uint32_t)(tid >> 5) * cpw + (tid & 31); (uint32_t)(tid & 31) < cpw && ci < C * MT) {
           const uint32_t d = ci / MT, r = ci - d * MT;
           copy_to_block((whole ? qkv : qkvp + (size_t)ks * MT * NQl) + (size_t)r * NQl + jc * DCOLS, slot + r * DCOLS, DCOLS * 4, &xb[0], d);
@@ -1527,6 +1555,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
       }
     };
     if (it0 < att_l) load_cache(0);
+    if constexpr (BFP) decode_ahead<MT, R>(ring, bars, head, parity, dead, limit, p.err, walk, wbuf, ahead);
     arrived(0);
 
     // ---- phase 2: the attention of the cluster's heads, an item a (sequence, key/value head, 64 positions) ----
@@ -1642,6 +1671,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
       if (const uint32_t ci = (uint32_t)(tid >> 5) * cpa + (tid & 31); (uint32_t)(tid & 31) < cpa && ci < C)
         copy_to_block(att + (size_t)it * AP, stage, group * APH * 4, &xb[1], ci);
     }
+    if constexpr (BFP) decode_ahead<MT, R>(ring, bars, head, parity, dead, limit, p.err, walk, wbuf, ahead);
     arrived(1);
 
     // ---- phase 3: the merge of the cluster's heads, and their rows of the output projection: a partial sum a cluster ----
@@ -1677,10 +1707,11 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
     for (uint32_t j = j0o; j < cut.nb_h; j += C) {
       unsigned long long* dst = p.part_o + ((size_t)(l & 1u) * p.tp + cgi) * MT * H + j * DCOLS;
       product_stream<MT, R, BFP>(vec, p.vec_cols, QCl, ring, bars, head, parity, dead, limit, p.err, walk, halves,
-                            [&](int r, int cc, float t) { st_tagged(dst + (size_t)r * H + cc, t, l + 1); }, wbuf);
+                            [&](int r, int cc, float t) { st_tagged(dst + (size_t)r * H + cc, t, l + 1); }, wbuf, &ahead);
     }
 
     // ---- phase 4: the residual, norm, the cluster's gate and up columns ----
+    if constexpr (BFP) decode_ahead<MT, R>(ring, bars, head, parity, dead, limit, p.err, walk, wbuf, ahead);
     // (the next layer's first gains are asked for before the poll, whose wait hides their trip)
     uint16_t gnb[GN];
 #pragma unroll
@@ -1696,7 +1727,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
         uint16_t* slot = reinterpret_cast<uint16_t*>(sg) + (size_t)idx * MT * DCOLS;
         product_stream<MT, R, BFP>(vec, p.vec_cols, H, ring, bars, head, parity, dead, limit, p.err, walk, halves, [&](int r, int cc, float t) {
           slot[r * DCOLS + cc] = f32_to_bf16_bits(__float_as_uint(t));
-        }, wbuf);
+        }, wbuf, &ahead);
         if (const uint32_t ci = (uint32_t)(tid >> 5) * cpw + (tid & 31); (uint32_t)(tid & 31) < cpw && ci < C * MT) {
           const uint32_t d = ci / MT, r = ci - d * MT;
           copy_to_block(gu + (size_t)r * 2 * FFl + j * DCOLS, slot + r * DCOLS, DCOLS * 2, &xb[2], d);
@@ -1706,6 +1737,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
 #pragma unroll
     for (int i = 0; i < GN; ++i)
       if (tid + i * DT < H) g1[tid + i * DT] = gn[i];
+    if constexpr (BFP) decode_ahead<MT, R>(ring, bars, head, parity, dead, limit, p.err, walk, wbuf, ahead);
     arrived(2);
 
     // ---- phase 5: the activation of the cluster's slice of ff and its rows of the down projection: a partial a (cluster, slice) ----
@@ -1722,10 +1754,11 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
       __syncthreads();
       unsigned long long* dst = p.part_dn + ((size_t)(l & 1u) * nparts_dn + (size_t)cgi * p.ks_dn + ks) * MT * H + cb * DCOLS;
       product_stream<MT, R, BFP>(vec, p.vec_cols, len, ring, bars, head, parity, dead, limit, p.err, walk, halves,
-                            [&](int r, int cc, float t) { st_tagged(dst + (size_t)r * H + cc, t, l + 1); }, wbuf);
+                            [&](int r, int cc, float t) { st_tagged(dst + (size_t)r * H + cc, t, l + 1); }, wbuf, &ahead);
     }
     // every thread of the block is past its last read of what the layer sent it (each path here ends in a block barrier)
     if (tid == 0) st_tagged(p.done + (size_t)(l & 1u) * gridDim.x + blockIdx.x, 0.f, l + 1);
+    if constexpr (BFP) decode_ahead<MT, R>(ring, bars, head, parity, dead, limit, p.err, walk, wbuf, ahead);
   }
   if (blockIdx.x == 0) {
     add_parts_tagged(xres, MT * H, p.part_dn + (size_t)((p.n_layers - 1) & 1u) * nparts_dn * MT * H, nparts_dn, (size_t)MT * H, p.n_layers,
