@@ -880,26 +880,37 @@ __device__ __forceinline__ uint4 bfp8_unit_fast(uint2 raw, uint32_t E) {
 }
 
 // A landed BFP8 chunk (datum bytes [crows][64], then exponent bytes [crows][4]) into the BF16 tile the tensor-core loads
-// expect: row k's 16-byte piece u at piece u ^ (k & 7), as the BF16 form's copies write it.  Every thread; two pieces a
+// expect: row k's 16-byte piece u at piece u ^ (k & 7), as the BF16 form's copies write it.  Every thread; four pieces a
 // step, 32 rows apart, so that their chains interleave (`rows` is a multiple of 16).
 __device__ __forceinline__ void decode_chunk(const uint8_t* raw, uint32_t crows, uint32_t rows, uint8_t* wbuf) {
+  constexpr int NP = 4;                                // pieces a step, 32 rows apart
   const uint32_t tid = threadIdx.x, c8 = tid & 7, r0 = tid >> 3;
   const uint32_t sraw = tc::smem_u32(raw) + c8 * 8, sex = tc::smem_u32(raw) + crows * 64 + (c8 >> 1), sout = tc::smem_u32(wbuf);
-  for (uint32_t r = r0; r < rows; r += 64) {
-    const bool two = r + 32 < rows;
-    const uint32_t rb = two ? r + 32 : r;
-    uint2 da, db;
-    uint32_t Ea, Eb;
-    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(da.x), "=r"(da.y) : "r"(sraw + r * 64));
-    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(db.x), "=r"(db.y) : "r"(sraw + rb * 64));
-    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(Ea) : "r"(sex + r * 4));
-    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(Eb) : "r"(sex + rb * 4));
-    uint4 oa, ob;
-    if (bfp8_slow(da, Ea) || bfp8_slow(db, Eb)) { oa = bfp8_unit_slow(da, Ea); ob = bfp8_unit_slow(db, Eb); }
-    else { oa = bfp8_unit_fast(da, Ea); ob = bfp8_unit_fast(db, Eb); }
-    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sout + r * 128 + ((c8 ^ (r & 7)) << 4)), "r"(oa.x), "r"(oa.y), "r"(oa.z), "r"(oa.w) : "memory");
-    if (two)
-      asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sout + rb * 128 + ((c8 ^ (rb & 7)) << 4)), "r"(ob.x), "r"(ob.y), "r"(ob.z), "r"(ob.w) : "memory");
+  for (uint32_t r = r0; r < rows; r += 32 * NP) {
+    uint2 d[NP];
+    uint32_t E[NP], rr[NP];
+    bool slow = false;
+#pragma unroll
+    for (int q = 0; q < NP; ++q) {
+      rr[q] = r + 32 * q < rows ? r + 32 * q : r;     // (a piece past the chunk decodes the first again and is not stored)
+      asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(d[q].x), "=r"(d[q].y) : "r"(sraw + rr[q] * 64));
+      asm volatile("ld.shared.u8 %0, [%1];" : "=r"(E[q]) : "r"(sex + rr[q] * 4));
+    }
+#pragma unroll
+    for (int q = 0; q < NP; ++q) slow = slow || bfp8_slow(d[q], E[q]);
+    uint4 o[NP];
+    if (slow) {
+#pragma unroll
+      for (int q = 0; q < NP; ++q) o[q] = bfp8_unit_slow(d[q], E[q]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < NP; ++q) o[q] = bfp8_unit_fast(d[q], E[q]);
+    }
+#pragma unroll
+    for (int q = 0; q < NP; ++q)
+      if (q == 0 || r + 32 * q < rows)
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sout + rr[q] * 128 + ((c8 ^ (rr[q] & 7)) << 4)), "r"(o[q].x), "r"(o[q].y),
+                     "r"(o[q].z), "r"(o[q].w) : "memory");
   }
 }
 
