@@ -555,8 +555,8 @@ def prefill_leg(eng, timed):
     # the 30 layers as one launch, replayed as a trace; 64 steps from position 1 of 256 attended
     decode = {}
     rng = np.random.default_rng(0xDEC0)
-    for nb in (1, 4):
-        dec = W.LlamaDecode(eng, cfg, model.w, nb, max_len=512, attend=256, fused=True)
+    for nb, storage in ((1, "bf16"), (4, "bf16"), (1, "bfp8")):
+        dec = W.LlamaDecode(eng, cfg, model.w, nb, max_len=512, attend=256, fused=True, weight_storage=storage)
         start = rng.integers(0, cfg.vocab, nb).astype(np.int32)
         dec.reset(start)
         dlg, dam = dec.capture()
@@ -565,9 +565,12 @@ def prefill_leg(eng, timed):
         dec.replay()
         dper = eng.device_traffic().launches - l0
         dms = timed(dec.replay, reps=64, warm=4)
-        decode[f"batch{nb}"] = {"ms_per_step": dms, "tok_per_s": nb / (dms * 1e-3), "launches_per_step": int(dper),
-                                "form": eng.last_decode_form(), "distinct_tokens_generated": int(len(np.unique(dec.generated(0, 69))))}
+        decode[f"batch{nb}" + ("_bfp8" if storage == "bfp8" else "")] = {
+            "ms_per_step": dms, "tok_per_s": nb / (dms * 1e-3), "launches_per_step": int(dper), "weights": storage,
+            "form": eng.last_decode_form(), "distinct_tokens_generated": int(len(np.unique(dec.generated(0, 69))))}
         eng.release_trace(dec.trace); eng.free(dlg); eng.free(dam)
+        for pk in dec.packed:
+            eng.free(pk)
     return {"tok_per_s": batch * seq / (tms * 1e-3), "ms": tms, "tokens": batch * seq, "launches": int(per), "decode_step": decode,
             "mode": "traced (CUDA graph replay), fused attention", "eager_ms": eager_ms,
             "eager_tok_per_s": batch * seq / (eager_ms * 1e-3), "trace_bytes": int(footprint),
