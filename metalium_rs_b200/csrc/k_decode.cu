@@ -289,7 +289,7 @@ __device__ __forceinline__ void norm_rows_sm(const float* x, uint32_t cols, cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = warp / W, sub = warp - r * W;
   const float* xr = x + (size_t)r * cols;
   float ss = 0.f;
-#pragma unroll 1                                       // (the form's code is fetched anew every layer: short beats unrolled)
+#pragma unroll (MT == 1 ? 1 : 4)                       // (one row: eight warps share it, and short code beats unrolled; several: a thread has nine divisions in a row)
   for (uint32_t c = sub * 32 + lane; c < cols; c += W * 32) ss = fmaf(xr[c], xr[c], ss);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -300,7 +300,7 @@ __device__ __forceinline__ void norm_rows_sm(const float* x, uint32_t cols, cons
 #pragma unroll
   for (int w = 0; w < W; ++w) total += scratch[r * W + w];
   const float stat = sqrtf(__fadd_rn(__fmul_rn(total, 1.0f / (float)cols), eps));
-#pragma unroll 1
+#pragma unroll (MT == 1 ? 1 : 4)
   for (uint32_t c = sub * 32 + lane; c < cols; c += W * 32)
     vec[(size_t)r * vec_pitch + c] = f32_to_bf16_bits(__float_as_uint(__fmul_rn(__fdiv_rn(xr[c], stat), gains[c])));
   __syncthreads();
@@ -1374,12 +1374,15 @@ __device__ __forceinline__ void st_tagged(unsigned long long* dst, float v, uint
 }
 // x[i] += parts[0][i] + parts[1][i] + ... (in that order) for i < n, once every word carries `tag`.  A thread asks for all
 // the words of up to four of its elements at once, so a pass costs one trip to the L2 once the data is there.
+template <int E>                                       // elements a thread asks for at once: a trip to the L2 a batch
 __device__ __forceinline__ void add_parts_tagged(float* x, uint32_t n, const unsigned long long* parts, uint32_t nparts, size_t stride,
                                                  uint32_t tag, bool& dead, long long limit, int* err,
                                                  const unsigned long long* also = nullptr) {   // one more word this thread waits for
-  constexpr int E = 4, KMAX = 4;
+  constexpr int KMAX = 4;
   for (uint32_t base = 0; base < n; base += E * DT) {
-    float d[E] = {0.f, 0.f, 0.f, 0.f};
+    float d[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) d[e] = 0.f;
     for (uint32_t k0 = 0; k0 < nparts; k0 += KMAX) {
       unsigned long long w[KMAX][E];
       long long t0 = 0;
@@ -1435,6 +1438,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
   const uint32_t H = p.hidden, KC = p.kv_heads * HD, QCl = cut.QCl, KCl = cut.KCl, NQl = cut.NQl, FFl = cut.FFl;
   const uint32_t group = cut.group, chunks = p.attend / DCH, att_l = cut.n_att, nparts_dn = p.tp * p.ks_dn;
   constexpr uint32_t APH = HD + 4, AP = 4 * APH;      // as in the one-cluster form
+  constexpr int PE = MT == 1 ? 4 : (MT == 2 ? 5 : 9);   // elements of the residual a thread fetches at once (hidden 576: all of them)
   auto per = [&](uint32_t items) { return (items + C - 1) >> lgC; };
   // a bulk copy's issue costs its warp some 70 cycles, so an item's copies (one a block and row) are spread over the eight warps
   const uint32_t cpw = (C * MT + DT / 32 - 1) / (DT / 32), cpa = (C + DT / 32 - 1) / (DT / 32);
@@ -1530,7 +1534,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
       for (uint32_t i = tid; i < (uint32_t)MT * H; i += DT) xres[i] = i < p.rows * H ? p.x0[i] : 0.f;
     } else {
       // (thread t also waits for block t's word: every block has finished layer l - 1)
-      add_parts_tagged(xres, MT * H, p.part_dn + (size_t)((l - 1) & 1u) * nparts_dn * MT * H, nparts_dn, (size_t)MT * H, l, dead, limit, p.err,
+      add_parts_tagged<PE>(xres, MT * H, p.part_dn + (size_t)((l - 1) & 1u) * nparts_dn * MT * H, nparts_dn, (size_t)MT * H, l, dead, limit, p.err,
                        (uint32_t)tid < gridDim.x ? p.done + (size_t)((l - 1) & 1u) * gridDim.x + tid : nullptr);
     }
     __syncthreads();
@@ -1728,7 +1732,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
 #pragma unroll
     for (int i = 0; i < GN; ++i)
       gnb[i] = l + 1 < p.n_layers && tid + i * DT < H ? reinterpret_cast<const uint16_t*>(lay[l + 1].norm1)[tid + i * DT] : (uint16_t)0;
-    add_parts_tagged(xres, MT * H, p.part_o + (size_t)(l & 1u) * p.tp * MT * H, p.tp, (size_t)MT * H, l + 1, dead, limit, p.err);
+    add_parts_tagged<PE>(xres, MT * H, p.part_o + (size_t)(l & 1u) * p.tp * MT * H, p.tp, (size_t)MT * H, l + 1, dead, limit, p.err);
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < GN; ++i) gn[i] = __uint_as_float((uint32_t)gnb[i] << 16);
@@ -1772,7 +1776,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
     if constexpr (BFP) decode_ahead<MT, R>(ring, bars, head, parity, dead, limit, p.err, walk, wbuf, ahead);
   }
   if (blockIdx.x == 0) {
-    add_parts_tagged(xres, MT * H, p.part_dn + (size_t)((p.n_layers - 1) & 1u) * nparts_dn * MT * H, nparts_dn, (size_t)MT * H, p.n_layers,
+    add_parts_tagged<PE>(xres, MT * H, p.part_dn + (size_t)((p.n_layers - 1) & 1u) * nparts_dn * MT * H, nparts_dn, (size_t)MT * H, p.n_layers,
                      dead, limit, p.err);
     __syncthreads();
     norm_rows<MT>(xres, H, p.final_norm, p.eps, osum, H, stat);
