@@ -710,6 +710,7 @@ struct ClusterParams {
   uint32_t kn[4][2];             // the matrices' [k, n]
   TpShape cut;
   unsigned long long* done;      // [2][blocks]: a block's word {0, layer + 1}: it has finished the layer
+  uint32_t skip_done;            // a test's hook: that block never stores its word, so the others' polls run out (no block: ~0)
 };
 
 constexpr int CK_ROWS = 192;                           // k-rows of a tiled copy's box (at most 256)
@@ -1019,6 +1020,26 @@ __device__ __forceinline__ void copy_to_block(void* dst, const void* staged, uin
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rb) : "r"(tc::smem_u32(bar)), "r"(rank));
   asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(rd), "r"(tc::smem_u32(staged)), "r"(bytes), "r"(rb) : "memory");
+}
+
+// Before a block leaves: no copy may still be on its way into the block's shared memory.  After a normal step every
+// chunk that was asked for was waited for, and this returns at once; a block that gave up its waits (a timeout anywhere in
+// the step) walked on without them, so the last copy armed on each slot may still be in flight: it is waited for here,
+// bounded.  Slot r's last armed phase is the one before the parity the block would wait for next.
+__device__ __forceinline__ void drain_ring(uint64_t* bars, int slots, uint32_t parity, long long limit) {
+  const long long t0 = clock64();
+  for (int r = 0; r < slots; ++r)
+    while (!tc::mbar_try(&bars[r], ((parity >> r) & 1u) ^ 1u))
+      if (clock64() - t0 > limit) return;
+}
+// The same for what the other blocks of the cluster send into this block: a thread that gave up a wait waits (bounded) for
+// the last layer's phase of each of the block's receiving barriers before the block may leave.
+__device__ __forceinline__ void drain_received(uint64_t* xb, int n, uint32_t last_layer, bool dead, long long limit) {
+  if (!dead) return;                                   // every phase was waited for where it was used
+  const long long t0 = clock64();
+  for (int k = 0; k < n; ++k)
+    while (!tc::mbar_try(&xb[k], last_layer & 1u))
+      if (clock64() - t0 > limit) return;
 }
 
 template <int MT>
@@ -1349,6 +1370,8 @@ __global__ void __launch_bounds__(DT, 1) decode_cluster_kernel(const ClusterPara
     norm_rows<MT>(xres, H, p.final_norm, p.eps, osum, H, stat);   // `osum` is free: the norm's BF16 values as F32
     for (uint32_t i = tid; i < p.rows * H; i += DT) p.out[i] = f32_to_bf16_bits(__float_as_uint(osum[i]));
   }
+  drain_ring(bars, R, parity, limit);
+  drain_received(xb, 5, p.n_layers - 1, dead, limit);
   cluster.sync();   // no block leaves while another may still store into its shared memory
 }
 
@@ -1772,7 +1795,7 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
                             [&](int r, int cc, float t) { st_tagged(dst + (size_t)r * H + cc, t, l + 1); }, wbuf, &ahead);
     }
     // every thread of the block is past its last read of what the layer sent it (each path here ends in a block barrier)
-    if (tid == 0) st_tagged(p.done + (size_t)(l & 1u) * gridDim.x + blockIdx.x, 0.f, l + 1);
+    if (tid == 0 && blockIdx.x != p.skip_done) st_tagged(p.done + (size_t)(l & 1u) * gridDim.x + blockIdx.x, 0.f, l + 1);
     if constexpr (BFP) decode_ahead<MT, R>(ring, bars, head, parity, dead, limit, p.err, walk, wbuf, ahead);
   }
   if (blockIdx.x == 0) {
@@ -1782,6 +1805,8 @@ __global__ void __launch_bounds__(DT, 1) decode_tp_kernel(const ClusterParams p)
     norm_rows<MT>(xres, H, p.final_norm, p.eps, osum, H, stat);
     for (uint32_t i = tid; i < p.rows * H; i += DT) p.out[i] = f32_to_bf16_bits(__float_as_uint(osum[i]));
   }
+  drain_ring(bars, R, parity, limit);
+  drain_received(xb, 3, p.n_layers - 1, dead, limit);
   cluster.sync();   // no block leaves while another may still store into its shared memory
 }
 
@@ -2110,6 +2135,8 @@ cudaError_t launch_decode_layers(const DecodeShape& sh, const DecodeLayerPtrs* l
     }
     const bool bfp = sh.weights == 1;
     c.bfp = bfp ? 1u : 0u;
+    const char* skip = getenv("B200TT_DEBUG_DECODE_SKIP_DONE");   // a test's hook (see `skip_done`)
+    c.skip_done = skip ? (uint32_t)atoi(skip) : ~0u;
     for (int i = 0; i < 4; ++i) { c.crows[i] = t.cr[i]; c.pbytes[i] = t.cr[i] * (bfp ? 64 : 128); }
     {
       const uint32_t QCg = sh.heads * HD, NQg = QCg + 2 * sh.kv_heads * HD;

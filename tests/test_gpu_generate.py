@@ -329,6 +329,40 @@ def test_the_several_cluster_step_over_other_cuts(eng, heads, kv_heads, ff, tp, 
             assert np.max(np.abs(x - y)) <= 2.0 ** -6 * np.abs(y).max(), l
 
 
+def test_a_block_that_never_reports_runs_the_other_blocks_polls_out(monkeypatch):
+    # The several-cluster step's blocks wait for one another's words in global memory, every wait bounded by the engine's
+    # limit.  A test's hook keeps one block from ever storing its end-of-layer word (a flag that nothing sets): the polls
+    # for it run out after the limit (here 2e6 cycles, a millisecond), the step reports TIMEOUT at the next wait instead
+    # of hanging, every block still leaves (no copy in flight into its shared memory), and the context stays usable:
+    # a new engine's step is the composed step's.
+    from metalium_rs_b200 import CudaEngine
+    cfg = small_llama()
+    ids = np.array([7], np.int32)
+    monkeypatch.delenv("B200TT_DECODE", raising=False)
+    with CudaEngine(0, wait_limit_cycles=2_000_000) as e:
+        pre = W.LlamaPrefill(e, cfg, W.llama_weights(cfg, seed=11), 1, 32)
+        dec = W.LlamaDecode(e, cfg, pre.w, 1, max_len=64, fused=True)
+        dec.reset(ids)
+        lg, am = dec.step()                            # a whole step first: the form is the several-cluster one and it works
+        e.sync()
+        assert e.last_decode_form() in ("cluster16x3", "cluster8x3") and np.isfinite(e.download(lg)).all()
+        monkeypatch.setenv("B200TT_DEBUG_DECODE_SKIP_DONE", "5")
+        dec.step()
+        with pytest.raises(TtError) as ei:
+            e.sync()
+        assert ei.value.status == 4 and ei.value.variant == "Timeout"
+    monkeypatch.delenv("B200TT_DEBUG_DECODE_SKIP_DONE")
+    with CudaEngine(0) as e:
+        pre = W.LlamaPrefill(e, cfg, W.llama_weights(cfg, seed=11), 1, 32)
+        composed = W.LlamaDecode(e, cfg, pre.w, 1, max_len=64)
+        fused = W.LlamaDecode(e, cfg, pre.w, 1, max_len=64, fused=True)
+        composed.reset(ids); fused.reset(ids)
+        for _ in range(3):
+            la, _a = composed.step()
+            lb, _b = fused.step()
+        assert np.max(np.abs(e.download(la) - e.download(lb))) <= 2e-2
+
+
 def test_a_traced_one_launch_generation_is_its_eager_one(eng):
     cfg = small_llama()
     batch, n = 2, 24
