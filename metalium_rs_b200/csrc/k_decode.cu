@@ -2,11 +2,12 @@
 // reference's traced generation step (crates/tt-models/src/generate.rs:781; layer crates/tt-models/src/llama.rs:371-507;
 // cache crates/tt-models/src/kv_cache.rs:185-330).  The composed step is eleven small launches a layer whose device
 // work (a layer's 9 MB of weights) takes far less time than their launch latencies; here one launch walks the layers
-// with five barriers a layer instead.  Two forms of the same five phases, chosen at the call
-// (`decode_layers_cluster_wanted`): a cooperative grid of persistent blocks that exchange partial sums through global
-// memory and wait at a counter (described first), and ONE thread-block cluster of sixteen blocks that exchange results
-// through distributed shared memory, wait at the hardware's cluster barrier and stream their weights through a ring of
-// TMA copies (further down).
+// with five exchanges a layer instead.  Three forms of the same five phases, chosen at the call (`cluster_form_of`):
+// a cooperative grid of persistent blocks that exchange partial sums through global memory and wait at a counter
+// (described first); ONE thread-block cluster of sixteen blocks that hand results on through distributed shared memory,
+// by copies that complete on the receivers' transaction barriers, and stream their weights through a ring of TMA copies
+// (further down); and two to four such clusters that share a layer's heads and ff the way tensor-parallel ranks do and
+// exchange their partial sums as tagged words in global memory (last; the form a step takes where the shape divides).
 //
 // A layer, for `B` <= 4 rows (one token of each sequence), in five phases.  Between phases stand grid barriers; the
 // residual stream lives redundantly in every block's shared memory, so no phase waits for one block to publish it.
