@@ -283,14 +283,16 @@ def test_the_one_launch_step_is_the_composed_step(eng, batch, storage, form, mon
     assert np.array_equal(fused.generated(0, steps).shape, (steps, batch))
 
 
-@pytest.mark.parametrize("heads,kv_heads,ff,tp,batch", [
-    (8, 4, 1024, 0, 2),       # four clusters: two query heads on one key/value head each
-    (8, 4, 1024, 2, 1),       # two clusters: four query heads on two key/value heads each
-    (4, 4, 768, 0, 4),        # four clusters, a query head a key/value head
-    (6, 2, 1024, 0, 2),       # two clusters (neither 4 nor 3 divides): three query heads a key/value head
-    (9, 3, 1536, 0, 3),       # three sequences in a four-row step
+@pytest.mark.parametrize("heads,kv_heads,ff,tp,batch,max_len", [
+    (8, 4, 1024, 0, 2, 128),      # four clusters: two query heads on one key/value head each
+    (8, 4, 1024, 2, 1, 128),      # two clusters: four query heads on two key/value heads each
+    (4, 4, 768, 0, 4, 128),       # four clusters, a query head a key/value head
+    (6, 2, 1024, 0, 2, 128),      # two clusters (neither 4 nor 3 divides): three query heads a key/value head
+    (9, 3, 1536, 0, 3, 128),      # three sequences in a four-row step
+    (9, 3, 1536, 0, 4, 1024),     # sixteen chunks of positions a head: four attention items a block, most of them past the step
+    (8, 4, 1024, 2, 2, 512),      # two key/value heads a cluster over eight chunks: two items a block
 ])
-def test_the_several_cluster_step_over_other_cuts(eng, heads, kv_heads, ff, tp, batch, monkeypatch):
+def test_the_several_cluster_step_over_other_cuts(eng, heads, kv_heads, ff, tp, batch, max_len, monkeypatch):
     # The several-cluster form cuts the heads, the key/value heads and ff by the number of clusters: the cuts the
     # SmolLM2-135M shape does not reach (more than one key/value head a cluster, one query head a key/value head, two and
     # four clusters), against the composed step as above.
@@ -298,7 +300,7 @@ def test_the_several_cluster_step_over_other_cuts(eng, heads, kv_heads, ff, tp, 
     if tp:
         monkeypatch.setenv("B200TT_DECODE_TP", str(tp))
     cfg = W.LlamaConfig(layers=2, hidden=heads * 64, heads=heads, kv_heads=kv_heads, head_dim=64, ff=ff, vocab=1024)
-    max_len, steps = 128, 70
+    steps = 70
     pre = W.LlamaPrefill(eng, cfg, W.llama_weights(cfg, seed=5), batch, 32)
     composed = W.LlamaDecode(eng, cfg, pre.w, batch, max_len=max_len)
     fused = W.LlamaDecode(eng, cfg, pre.w, batch, max_len=max_len, fused=True)
