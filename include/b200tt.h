@@ -154,6 +154,15 @@ int32_t b200_matmul_silu_mul(b200_engine*, b200_buffer a, b200_buffer b, b200_bu
  * at 16-byte addresses, and the tcgen05 path takes the product. */
 int32_t b200_matmul_rope(b200_engine*, b200_buffer a, b200_buffer b, const b200_block_arg* cos_, const b200_block_arg* sin_,
                          uint64_t rope_cols, b200_buffer* out, uint64_t out_dims[2]);
+/* A projection into the residual stream and its norm as one product (an extension, as `b200_matmul_silu_mul` is):
+ * out[0] = resid + A B (F32 [m, n]) and out[1] = RMSNorm(out[0]) * gains rounded once to BF16 -- `matmul_dram` then
+ * `add_rms_norm_as(resid, product, gains, eps, 1)` (crates/tt-models/src/llama.rs:371-507) without the product's round
+ * trip through memory or the second launch.  out[0] is that composition's bit for bit; out[1] sums the squares in
+ * another fixed order (192 columns a CTA of a cluster, the CTAs in order), so it agrees with the composed norm to a
+ * unit in the last place of the statistic.  A [m, k] and B [k, n] BF16, resid F32 [m, n], gains BF16 of n values;
+ * refused unless n is one to eight tiles of 192 columns, m >= 64, k >= 64 and the driver makes the descriptors. */
+int32_t b200_matmul_add_rms_norm(b200_engine*, b200_buffer a, b200_buffer b, b200_buffer resid, b200_buffer gains, float eps,
+                                 b200_buffer out[2], uint64_t out_dims[2]);
 /* The sharded product's fused step: C = A B (BF16 operands as stored, no transposes) written from the
  * product's epilogue into columns [col_first, col_first + n) of each of the n_dst matrices dst[i]
  * ([dst_rows, dst_cols] row-major, of the result's type) -- this GPU's C and, through b200_ipc_open,

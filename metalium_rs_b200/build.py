@@ -34,6 +34,7 @@ SOURCES = {
     "k_gemm_tc.cu": [],
     "k_gemm_tf32.cu": [],
     "k_gemm_tc2.cu": [],
+    "k_gemm_addnorm.cu": ["-fmad=false"],
     "k_gemm_skinny.cu": [],
     "k_attention.cu": [],
     "k_attention_tc.cu": [],

@@ -934,6 +934,42 @@ int32_t b200_matmul_rope(b200_engine* e, b200_buffer a, b200_buffer b, const b20
   return B200_OK;
 }
 
+int32_t b200_matmul_add_rms_norm(b200_engine* e, b200_buffer a, b200_buffer b, b200_buffer resid, b200_buffer gains, float eps,
+                                 b200_buffer out[2], uint64_t out_dims[2]) {
+  cudaSetDevice(e->device);
+  Buf *A = nullptr, *B = nullptr, *R = nullptr, *G = nullptr;
+  int st = e->need(a, &A, "matmul_add_rms_norm");
+  if (!st) st = e->need(b, &B, "matmul_add_rms_norm");
+  if (!st) st = e->need(resid, &R, "matmul_add_rms_norm");
+  if (!st) st = e->need(gains, &G, "matmul_add_rms_norm");
+  if (st) return st;
+  if (A->elem != B200_BF16 || B->elem != B200_BF16 || R->elem != B200_F32 || G->elem != B200_BF16)
+    return e->fail(B200_UNSUPPORTED, "matmul_add_rms_norm: BF16 operands and gains, an F32 residual");
+  const uint64_t m = A->rows, k = A->cols, n = B->cols;
+  if (B->rows != k || R->rows != m || R->cols != n || G->rows * G->cols != n)
+    return e->fail(B200_UNSUPPORTED, "matmul_add_rms_norm: [%llu,%llu] x [%llu,%llu] + [%llu,%llu] with %llu gains: the shapes do not meet",
+                   (unsigned long long)m, (unsigned long long)k, (unsigned long long)B->rows, (unsigned long long)n,
+                   (unsigned long long)R->rows, (unsigned long long)R->cols, (unsigned long long)(G->rows * G->cols));
+  const char* why = "";
+  if (!gemm_addnorm_supported(m, n, k, &why)) return e->fail(B200_UNSUPPORTED, "matmul_add_rms_norm: %s", why);
+  Buf *S = nullptr, *N = nullptr;
+  st = e->new_buffer(m, n, B200_F32, &out[0], &S);
+  if (st) return st;
+  st = e->new_buffer(m, n, B200_BF16, &out[1], &N);
+  if (st) { e->drop(out[0]); return st; }
+  A = e->get(a); B = e->get(b); R = e->get(resid); G = e->get(gains); S = e->get(out[0]);
+  const cudaError_t ce = launch_gemm_addnorm(A->ptr, B->ptr, (const float*)R->ptr, G->ptr, eps, (float*)S->ptr, N->ptr, m, n, k, e->d_err, e->stream);
+  if (ce == cudaErrorNotSupported) {
+    e->drop(out[0]); e->drop(out[1]);
+    return e->fail(B200_UNSUPPORTED, "matmul_add_rms_norm: the driver refused a tensor map for this shape");
+  }
+  e->matmul_path = "tcgen05-addnorm";
+  st = e->launched(ce, "matmul_add_rms_norm");
+  if (st) { e->drop(out[0]); e->drop(out[1]); return st; }
+  set_dims(out_dims, m, n);
+  return B200_OK;
+}
+
 // C = A B written into one or more caller-named matrices instead of a new buffer: the sharded
 // product's rank writes its column slice straight into every rank's C (its own and, through
 // addresses opened with b200_ipc_open, its peers' over NVLink) from the product's epilogue.

@@ -139,6 +139,11 @@ cudaError_t launch_gemm_simt(const GemmArgs& g, cudaStream_t stream);
 struct TcPlan;  // opaque: tensor maps + grid
 bool gemm_tc_supported(const GemmArgs& g, const char** why);
 // `pair_taken` (may be null) is set when the CTA-pair kernel ran the product.
+// sum = resid + A B (F32) and norm = RMSNorm(sum) * gains (BF16) as one kernel (k_gemm_addnorm.cu): A [m, k] BF16,
+// B [k, n] BF16, resid [m, n] F32, gains [n] BF16; n is one to eight tiles of 192 columns.
+bool gemm_addnorm_supported(uint64_t m, uint64_t n, uint64_t k, const char** why);
+cudaError_t launch_gemm_addnorm(const void* a, const void* b, const float* resid, const void* gains, float eps, float* sum_out,
+                                void* norm_out, uint64_t m, uint64_t n, uint64_t k, int* err_word, cudaStream_t stream);
 cudaError_t launch_gemm_tc(const GemmArgs& g, const GemmBatch* batches_host, int* err_word,
                            cudaStream_t stream, int* pair_taken = nullptr);
 // One CTA that waits, with the kernels' bounded wait and the engine's limit, on an mbarrier whose bytes

@@ -325,6 +325,15 @@ class CudaEngine:
         bc, bs = _block(cos), _block(sin)
         return self._call(self._lib.b200_matmul_rope, C.c_uint64(a), C.c_uint64(b), C.byref(bc), C.byref(bs), C.c_uint64(rope_cols))
 
+    def matmul_add_rms_norm(self, a: int, b: int, resid: int, gains: int, eps: float):
+        """(s, norm): s = resid + A B (F32), norm = RMSNorm(s) * gains as BF16, one kernel (see `b200_matmul_add_rms_norm`)."""
+        out = (C.c_uint64 * 2)()
+        dims = (C.c_uint64 * 2)()
+        self._check(self._lib.b200_matmul_add_rms_norm(self._e, C.c_uint64(a), C.c_uint64(b), C.c_uint64(resid), C.c_uint64(gains),
+                                                       C.c_float(eps), out, dims))
+        d = (dims[0], dims[1])
+        return [(out[0], d), (out[1], d)]
+
     def matmul_into(self, a: int, b: int, dst_ptrs, dst_dims, col_first: int, bf16: bool = True):
         """C = A B stored from the product's epilogue into columns [col_first, ...) of every matrix in
         `dst_ptrs` (device addresses: this GPU's or, opened with `ipc_open`, a peer's)."""

@@ -4,7 +4,7 @@ fn main() {
     let out = std::path::PathBuf::from(std::env::var("OUT_DIR").unwrap());
     let csrc = std::path::Path::new("../../csrc");
     let units = [("engine.cu", false), ("k_eltwise.cu", true), ("k_reduce.cu", true), ("k_index.cu", false),
-                 ("k_gemm_simt.cu", false), ("k_gemm_tc.cu", false), ("k_gemm_tc2.cu", false), ("k_gemm_tf32.cu", false),
+                 ("k_gemm_simt.cu", false), ("k_gemm_tc.cu", false), ("k_gemm_tc2.cu", false), ("k_gemm_addnorm.cu", true), ("k_gemm_tf32.cu", false),
                  ("k_gemm_skinny.cu", false), ("k_attention.cu", false), ("k_attention_tc.cu", false),
                  ("k_convert.cu", false), ("k_bfp.cu", false), ("k_decode.cu", false), ("k_pool.cu", true), ("k_scan_sort.cu", true), ("k_random.cu", true)];
     let mut objs = vec![];

@@ -93,6 +93,7 @@ extern "C" {
     pub fn b200_set_matmul_sm_limit(a0: *mut b200_engine, sms: i32);
     pub fn b200_matmul_host_bf16(a0: *mut b200_engine, a: *const u16, b: *const u16, mkn: *const u64, out: *mut u16) -> i32;
     pub fn b200_matmul_silu_mul(a0: *mut b200_engine, a: u64, b: u64, out: *mut u64, out_dims: *mut u64) -> i32;
+    pub fn b200_matmul_add_rms_norm(a0: *mut b200_engine, a: u64, b: u64, resid: u64, gains: u64, eps: f32, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_matmul_rope(a0: *mut b200_engine, a: u64, b: u64, cos_: *const b200_block_arg, sin_: *const b200_block_arg, rope_cols: u64, out: *mut u64, out_dims: *mut u64) -> i32;
     pub fn b200_matmul_into(a0: *mut b200_engine, a: u64, b: u64, dst: *const *mut core::ffi::c_void, n_dst: i32, dst_rows: u64, dst_cols: u64, col_first: u64, out_bf16: i32) -> i32;
     pub fn b200_store_block_into(a0: *mut b200_engine, src: *const b200_block_arg, dst: *const *mut core::ffi::c_void, n_dst: i32, dst_rows: u64, dst_cols: u64, col_first: u64) -> i32;

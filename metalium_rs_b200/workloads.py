@@ -188,6 +188,14 @@ class LlamaPrefill:
         # same bits, but this projection is ONE wave of tiles, so its epilogue hides under nothing and the rotation there
         # (a row's table entries fetched by the row's own thread) costs more than the separate launch: 3.83 against 3.66 ms
         self.fused_rope = cfg.head_dim == 64 and os.environ.get("B200TT_FUSED_ROPE", "0") == "1"
+        # the output and down projections straight into the residual stream and its norm (`matmul_add_rms_norm`: one
+        # launch where the composition takes two) only on request (B200TT_FUSED_NORM=1), where hidden is one to eight
+        # tiles of 192 columns and there are at least 64 tokens.  The sums are the composition's bits, the norm's
+        # statistic is added in another fixed order.  Measured it loses: these products are ONE wave of tiles, so the
+        # norm in their epilogue hides under nothing and runs on the 96 SMs that hold a tile where the norm's own launch
+        # fills the device (17.3 against 15.5 us for the pair, 8 x 512 prefill 3.80 against 3.66 ms).
+        self.fused_norm = (cfg.hidden % 192 == 0 and cfg.hidden // 192 <= 8 and batch * seq >= 64 and
+                           os.environ.get("B200TT_FUSED_NORM", "0") == "1")
         if self.fused_mlp and cfg.ff % 128:
             raise ValueError("the fused gate|up product needs ff in whole groups of 128 columns")
         takes = cfg.head_dim in (64, 128)                    # any length: a tail tile is masked by index
@@ -307,12 +315,16 @@ class LlamaPrefill:
                 om, _ = e.copy_blocks(o, self.merge, (n, self.q_cols))           # merge heads
                 e.free(o)
             lab("projection o")
-            att, _ = e.matmul_dram(om, False, self.w[f"l{l}.o"], False)      # o_proj, F32 out
-            e.free(om)
-            lab("add + norm")
-            # residual add and the next norm as one op (`Engine::add_rms_norm`, server.rs:466; llama.rs:288)
-            (x2, _), (n2, _) = e.add_rms_norm_as(x, att, self.w[f"l{l}.norm2"], c.eps, True)
-            e.free(x); e.free(att)
+            if self.fused_norm:   # o_proj, the residual add and the next norm as one launch
+                (x2, _), (n2, _) = e.matmul_add_rms_norm(om, self.w[f"l{l}.o"], x, self.w[f"l{l}.norm2"], c.eps)
+                e.free(om); e.free(x)
+            else:
+                att, _ = e.matmul_dram(om, False, self.w[f"l{l}.o"], False)      # o_proj, F32 out
+                e.free(om)
+                lab("add + norm")
+                # residual add and the next norm as one op (`Engine::add_rms_norm`, server.rs:466; llama.rs:288)
+                (x2, _), (n2, _) = e.add_rms_norm_as(x, att, self.w[f"l{l}.norm2"], c.eps, True)
+                e.free(x); e.free(att)
             lab("projection gate|up")
             if self.fused_mlp:   # silu(gate) * up stored by the gate|up product's own epilogue
                 act, _ = e.matmul_silu_mul(n2, self.w[f"l{l}.gate_up.interleaved"])
@@ -325,14 +337,18 @@ class LlamaPrefill:
                                              (gu, (0, c.ff), (n, c.ff)), None, True)   # silu(gate) * up (llama.rs:498)
                 e.free(gu)
             lab("projection down")
-            d, _ = e.matmul_dram(act, False, self.w[f"l{l}.down"], False)
-            e.free(act)
-            lab("add + norm")
-            if l + 1 < c.layers:
-                (x, _), (n1, _) = e.add_rms_norm_as(x2, d, self.w[f"l{l + 1}.norm1"], c.eps, True)
+            if self.fused_norm and l + 1 < c.layers:
+                (x, _), (n1, _) = e.matmul_add_rms_norm(act, self.w[f"l{l}.down"], x2, self.w[f"l{l + 1}.norm1"], c.eps)
+                e.free(act); e.free(x2)
             else:
-                x = el(K.ADD, x2, d)
-            e.free(x2); e.free(d)
+                d, _ = e.matmul_dram(act, False, self.w[f"l{l}.down"], False)
+                e.free(act)
+                lab("add + norm")
+                if l + 1 < c.layers:
+                    (x, _), (n1, _) = e.add_rms_norm_as(x2, d, self.w[f"l{l + 1}.norm1"], c.eps, True)
+                else:
+                    x = el(K.ADD, x2, d)
+                e.free(x2); e.free(d)
         lab("head")
         if all_positions:
             last = x

@@ -81,6 +81,12 @@ cudaError_t launch_gemm_tc(const GemmArgs&, const GemmBatch*, int*, cudaStream_t
   if (e != cudaSuccess) return e;
   OK_LAUNCH;
 }
+bool gemm_addnorm_supported(uint64_t m, uint64_t n, uint64_t k, const char** why) {
+  *why = "the row is one to eight tiles of 192 columns";
+  return n % 192 == 0 && n / 192 <= 8 && m >= 64 && k >= 64 && k % 8 == 0;
+}
+cudaError_t launch_gemm_addnorm(const void*, const void*, const float*, const void*, float, float*, void*, uint64_t, uint64_t, uint64_t, int*,
+                                cudaStream_t) { OK_LAUNCH; }
 cudaError_t launch_stalled_wait(int*, cudaStream_t) { OK_LAUNCH; }
 cudaError_t launch_bfp8_encode(const void*, int, uint64_t, uint64_t, uint8_t*, uint8_t*, cudaStream_t) { OK_LAUNCH; }
 cudaError_t launch_bfp8_decode(const uint8_t*, const uint8_t*, uint64_t, uint64_t, void*, int, cudaStream_t) { OK_LAUNCH; }

@@ -392,6 +392,44 @@ def test_the_projection_with_rope_is_the_product_then_rope_blocks_bit_for_bit(en
         eng.free(i)
 
 
+@pytest.mark.parametrize("mkn", [(4096, 576, 576),      # the prefill's output projection: three CTAs a row panel
+                                 (4096, 1536, 576),     # its down projection
+                                 (200, 576, 576),       # rows that are not whole tiles
+                                 (256, 512, 768),       # four CTAs a panel
+                                 (128, 64, 192),        # one CTA a panel, one k-block
+                                 (300, 320, 1536)])     # eight CTAs a panel
+def test_the_projection_into_the_residual_and_its_norm(eng, mkn):   # tt-models/src/llama.rs:371-507
+    # `matmul_add_rms_norm` against the composition it replaces: `matmul_dram` (F32 product of BF16 operands), then
+    # `add_rms_norm_as(resid, product, gains, eps, bf16)`.  The sum is that composition's bit for bit (the same product,
+    # one F32 addition).  The norm's statistic is summed in another fixed order, so a quotient may round the other way:
+    # held to one BF16 step, with nearly every element equal.
+    m, k, n = mkn
+    a = orc.to_bf16(orc.normal(0xADD0, 1, (m, k), 1.0))
+    w = orc.to_bf16(orc.normal(0xADD0, 2, (k, n), 0.05))
+    resid = orc.normal(0xADD0, 3, (m, n), 1.0).astype(np.float32)
+    gains = orc.to_bf16(1.0 + orc.normal(0xADD0, 4, (1, n), 0.1))
+    ia, iw, ir, ig = eng.upload_bf16(a, m, k), eng.upload_bf16(w, k, n), eng.upload(resid, m, n), eng.upload_bf16(gains, 1, n)
+    prod, _ = eng.matmul_dram(ia, False, iw, False)
+    (s_want, _), (n_want, _) = eng.add_rms_norm_as(ir, prod, ig, 1e-5, True)
+    (s_got, d0), (n_got, d1) = eng.matmul_add_rms_norm(ia, iw, ir, ig, 1e-5)
+    assert d0 == d1 == (m, n) and eng.last_matmul_path() == "tcgen05-addnorm"
+    assert np.array_equal(eng.download(s_got).view(np.uint32), eng.download(s_want).view(np.uint32))
+    got, want = eng.download_bf16(n_got).astype(np.int32), eng.download_bf16(n_want).astype(np.int32)
+    step = np.abs(got - want)
+    assert step.max() <= 1 and (step == 0).mean() > 0.99, (int(step.max()), float((step == 0).mean()))
+    # against F64: the norm of the F32 sum, to BF16's half step and the F32 statistic's rounding
+    s64 = eng.download(s_got).astype(np.float64)
+    ref = s64 / np.sqrt((s64 * s64).mean(axis=1, keepdims=True) + 1e-5) * orc.from_bf16(gains).astype(np.float64)
+    assert np.all(np.abs(orc.from_bf16(eng.download_bf16(n_got)).astype(np.float64) - ref) <= 2.0 ** -8 * np.abs(ref) + 1e-6)
+    for bad in (lambda: eng.matmul_add_rms_norm(ia, iw, ir, iw, 1e-5),          # gains of the wrong length
+                lambda: eng.matmul_add_rms_norm(ia, iw, prod, ia, 1e-5),
+                lambda: eng.matmul_add_rms_norm(iw, ia, ir, ig, 1e-5)):         # shapes that do not meet
+        with pytest.raises(TtError):
+            bad()
+    for i in (ia, iw, ir, ig, prod, s_want, n_want, s_got, n_got):
+        eng.free(i)
+
+
 @pytest.mark.parametrize("m", [1, 2, 3, 4])
 @pytest.mark.parametrize("kn", [(576, 960), (576, 576), (576, 3072), (1536, 576), (100, 72), (5000, 8)])
 def test_a_handful_of_rows_streams_the_weights_once(eng, m, kn):

@@ -232,6 +232,26 @@ def test_projection_with_rope_dims_and_refusals(e):   # tt-models/src/llama.rs:4
         e.matmul_rope(a, w, (wide, (0, 0), (64, 32)), tab(sin), 192)
 
 
+def test_projection_into_the_residual_and_its_norm_dims_and_refusals(e):   # tt-models/src/llama.rs:371-507 as one product
+    a = e.upload_bf16(np.zeros((128, 64), np.uint16), 128, 64)
+    w = e.upload_bf16(np.zeros((64, 576), np.uint16), 64, 576)
+    resid = f32(e, 128, 576)
+    gains = e.upload_bf16(np.zeros((1, 576), np.uint16), 1, 576)
+    launches = e.device_traffic().launches
+    (s, d0), (n, d1) = e.matmul_add_rms_norm(a, w, resid, gains, 1e-5)
+    assert d0 == d1 == (128, 576) and e.dims_of(s) == ((128, 576), F32) and e.dims_of(n) == ((128, 576), BF16)
+    assert e.device_traffic().launches - launches == 1 and e.last_matmul_path() == "tcgen05-addnorm"
+    for bad in (lambda: e.matmul_add_rms_norm(a, w, f32(e, 128, 512), gains, 1e-5),                     # a residual of another shape
+                lambda: e.matmul_add_rms_norm(a, w, resid, e.upload_bf16(np.zeros((1, 64), np.uint16), 1, 64), 1e-5),   # too few gains
+                lambda: e.matmul_add_rms_norm(a, w, resid, f32(e, 1, 576), 1e-5),                       # F32 gains
+                lambda: e.matmul_add_rms_norm(a, f32(e, 64, 576), resid, gains, 1e-5),                  # F32 weights
+                lambda: e.matmul_add_rms_norm(a, e.upload_bf16(np.zeros((64, 320), np.uint16), 64, 320), f32(e, 128, 320),
+                                              e.upload_bf16(np.zeros((1, 320), np.uint16), 1, 320), 1e-5)):   # 320 columns: not tiles of 192
+        with pytest.raises(TtError) as err:
+            bad()
+        assert err.value.status == 2
+
+
 def test_views_keep_their_parent_alive(e):                                      # server.rs:480-481
     t0 = e.device_traffic().pool_in_use
     a = f32(e, 64, 8)
