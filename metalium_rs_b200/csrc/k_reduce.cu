@@ -728,9 +728,20 @@ argmax_rows_kernel(const float* __restrict__ a, uint64_t rows, uint64_t cols, in
     const float* p = a + row * cols;
     float bv = -INFINITY;
     uint32_t bi = 0xffffffffu;
-    for (uint64_t i = threadIdx.x; i < cols; i += blockDim.x) {
-      const float v = p[i];
-      if (better(v, (uint32_t)i, bv, bi)) { bv = v; bi = (uint32_t)i; }
+    // eight of a thread's values asked for before the first is compared: one block reads a row, so a load a compare
+    // made a 49,152-column row (a decode step's logits) 48 trips to memory one after the other
+    for (uint64_t base = threadIdx.x; base < cols; base += 8ull * blockDim.x) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const uint64_t i = base + (uint64_t)u * blockDim.x;
+        v[u] = i < cols ? p[i] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const uint64_t i = base + (uint64_t)u * blockDim.x;
+        if (i < cols && better(v[u], (uint32_t)i, bv, bi)) { bv = v[u]; bi = (uint32_t)i; }
+      }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -747,6 +758,69 @@ argmax_rows_kernel(const float* __restrict__ a, uint64_t rows, uint64_t cols, in
       out[row] = (int32_t)bi;
     }
     __syncthreads();
+  }
+}
+
+// A few long rows (a decode step's logits: one to four rows of 49,152): one block a row read the row at a single SM's rate
+// (10.5 us for 196 KB).  Here the eight blocks of a thread-block cluster take an eighth of the row each, hand their best
+// (value, index) to the first block's shared memory and meet at the cluster barrier (every block arrives whatever it
+// found, so it cannot stall); the first block joins them in rank order.  `better` orders by value, then index, so the
+// result does not depend on how the row was cut.
+constexpr int ARGMAX_CLUSTER = 8;
+__global__ void __launch_bounds__(512)
+argmax_rows_cluster_kernel(const float* __restrict__ a, uint64_t rows, uint64_t cols, int32_t* __restrict__ out) {
+  __shared__ float sv[32];
+  __shared__ uint32_t si[32];
+  __shared__ float pv[ARGMAX_CLUSTER];
+  __shared__ uint32_t pi[ARGMAX_CLUSTER];
+  uint32_t rank, csize;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(csize));
+  const uint64_t row = blockIdx.x / csize;
+  const uint64_t seg = ((cols + csize - 1) / csize + 3) / 4 * 4, c0 = rank * seg, c1 = c0 + seg < cols ? c0 + seg : cols;
+  const float* p = a + row * cols;
+  float bv = -INFINITY;
+  uint32_t bi = 0xffffffffu;
+  for (uint64_t base = c0 + threadIdx.x; base < c1; base += 8ull * blockDim.x) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const uint64_t i = base + (uint64_t)u * blockDim.x;
+      v[u] = i < c1 ? p[i] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const uint64_t i = base + (uint64_t)u * blockDim.x;
+      if (i < c1 && better(v[u], (uint32_t)i, bv, bi)) { bv = v[u]; bi = (uint32_t)i; }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int nw = (blockDim.x + 31) / 32;
+    for (int w = 1; w < nw; ++w)
+      if (better(sv[w], si[w], bv, bi)) { bv = sv[w]; bi = si[w]; }
+    // this block's best into the first block's shared memory
+    uint32_t rv, ri;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rv) : "r"((uint32_t)__cvta_generic_to_shared(&pv[rank])), "r"(0));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ri) : "r"((uint32_t)__cvta_generic_to_shared(&pi[rank])), "r"(0));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(rv), "f"(bv) : "memory");
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(ri), "r"(bi) : "memory");
+  }
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (rank == 0 && threadIdx.x == 0 && row < rows) {
+    float fv = pv[0];
+    uint32_t fi = pi[0];
+    for (uint32_t r = 1; r < csize; ++r)
+      if (better(pv[r], pi[r], fv, fi)) { fv = pv[r]; fi = pi[r]; }
+    out[row] = (int32_t)fi;
   }
 }
 
@@ -969,7 +1043,17 @@ cudaError_t launch_rms_norm(const void* a, int a_bf16, const void* b, int b_bf16
 cudaError_t launch_argmax_rows(const float* a, uint64_t rows, uint64_t cols, int32_t* out,
                                cudaStream_t s) {
   if (rows == 0) return cudaSuccess;
-  const unsigned threads = cols >= 4096 ? 1024 : (cols >= 512 ? 256 : 64);
+  if (rows <= 64 && cols >= 16384 && cols < (1ull << 32)) {   // a few long rows: a cluster of eight blocks a row
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)rows * ARGMAX_CLUSTER); cfg.blockDim = dim3(512); cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = ARGMAX_CLUSTER; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, argmax_rows_cluster_kernel, a, rows, cols, out);
+  }
+  // sixteen and more values a thread: a block of 1,024 threads over a 4,096-column row spent its time being scheduled
+  const unsigned threads = cols >= 32768 ? 1024 : (cols >= 8192 ? 512 : (cols >= 2048 ? 256 : (cols >= 512 ? 128 : 64)));
   argmax_rows_kernel<<<(unsigned)(rows < 65535 ? rows : 65535), threads, 0, s>>>(a, rows, cols, out);
   return cudaGetLastError();
 }
