@@ -102,9 +102,92 @@ gemm_skinny_kernel(const uint16_t* __restrict__ a, uint64_t lda, const uint16_t*
   }
 }
 
+// The same against a B stored [n, k] (`matmul_dram(a, false, b, true)`: a tied language-model head, logits = x table^T,
+// crates/tt-models/src/llama.rs:1090): every output is the dot product of a row of A with a contiguous row of B, so a
+// warp takes rows of B four at a time, a lane the 16-byte units lane, lane + 32, ... of each (whole 128-byte lines a
+// load), A in shared memory as F32, and a butterfly of shuffles joins the lanes' sums.  The 128-row tensor-core tile read
+// SmolLM2-135M's 57 MB table at 3.6 TB/s (15.8 us); one row here 5.7 TB/s (10.0 us).  With four and eight rows of A this
+// kernel is bound by its reads of A from shared memory (22.7 and 37.6 us), so it takes one or two rows and the tile the rest.
+constexpr int SKT_THREADS = 256;
+constexpr int SKT_ROWS = 4;                  // rows of B a warp has in flight
+
+template <int MT>
+__global__ void __launch_bounds__(SKT_THREADS)
+gemm_skinny_t_kernel(const uint16_t* __restrict__ a, uint64_t lda, const uint16_t* __restrict__ b, uint64_t ldb,
+                     void* __restrict__ c, uint64_t ldc, int out_bf16, int m, uint64_t n, int k, uint32_t rows_a_warp) {
+  extern __shared__ float sm[];
+  pdl_enter();
+  float* as = sm;                                   // [MT][k]
+  const int tid = threadIdx.x, lane = tid & 31;
+  for (int i = tid; i < MT * k; i += SKT_THREADS) {
+    const int r = i / k, e = i - r * k;
+    as[i] = r < m ? __uint_as_float((uint32_t)a[(uint64_t)r * lda + e] << 16) : 0.f;
+  }
+  __syncthreads();
+  const uint64_t warp = ((uint64_t)blockIdx.x * SKT_THREADS + tid) >> 5;
+  const uint64_t v0 = warp * rows_a_warp, v1 = v0 + rows_a_warp < n ? v0 + rows_a_warp : n;
+  const int units = k / 8;                          // k is a multiple of 8
+  for (uint64_t v = v0; v < v1; v += SKT_ROWS) {
+    float acc[SKT_ROWS][MT];
+#pragma unroll
+    for (int q = 0; q < SKT_ROWS; ++q)
+#pragma unroll
+      for (int r = 0; r < MT; ++r) acc[q][r] = 0.f;
+    for (int u = lane; u < units; u += 32) {
+      uint4 raw[SKT_ROWS];
+#pragma unroll
+      for (int q = 0; q < SKT_ROWS; ++q) {
+        const uint64_t row = v + q < v1 ? v + q : v1 - 1;          // (a row past the warp's share reads its last again)
+        raw[q] = __ldg(reinterpret_cast<const uint4*>(b + row * ldb) + u);
+      }
+      float4 xa[MT], xb[MT];
+#pragma unroll
+      for (int r = 0; r < MT; ++r) {
+        xa[r] = *reinterpret_cast<const float4*>(as + (size_t)r * k + u * 8);
+        xb[r] = *reinterpret_cast<const float4*>(as + (size_t)r * k + u * 8 + 4);
+      }
+#pragma unroll
+      for (int q = 0; q < SKT_ROWS; ++q) {
+        const float w0 = __uint_as_float(raw[q].x << 16), w1 = __uint_as_float(raw[q].x & 0xffff0000u);
+        const float w2 = __uint_as_float(raw[q].y << 16), w3 = __uint_as_float(raw[q].y & 0xffff0000u);
+        const float w4 = __uint_as_float(raw[q].z << 16), w5 = __uint_as_float(raw[q].z & 0xffff0000u);
+        const float w6 = __uint_as_float(raw[q].w << 16), w7 = __uint_as_float(raw[q].w & 0xffff0000u);
+#pragma unroll
+        for (int r = 0; r < MT; ++r) {
+          float t = acc[q][r];
+          t = fmaf(xa[r].x, w0, t); t = fmaf(xa[r].y, w1, t); t = fmaf(xa[r].z, w2, t); t = fmaf(xa[r].w, w3, t);
+          t = fmaf(xb[r].x, w4, t); t = fmaf(xb[r].y, w5, t); t = fmaf(xb[r].z, w6, t); t = fmaf(xb[r].w, w7, t);
+          acc[q][r] = t;
+        }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < SKT_ROWS; ++q)
+#pragma unroll
+      for (int r = 0; r < MT; ++r) {
+        float t = acc[q][r];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        acc[q][r] = t;
+      }
+    // lane q * MT + r stores output (row r of A, row v + q of B)
+#pragma unroll
+    for (int q = 0; q < SKT_ROWS; ++q)
+#pragma unroll
+      for (int r = 0; r < MT; ++r)
+        if (lane == q * MT + r && r < m && v + q < v1) {
+          if (out_bf16) reinterpret_cast<uint16_t*>(c)[(uint64_t)r * ldc + v + q] = f32_to_bf16_bits(__float_as_uint(acc[q][r]));
+          else reinterpret_cast<float*>(c)[(uint64_t)r * ldc + v + q] = acc[q][r];
+        }
+  }
+}
+
 }  // namespace
 
 bool gemm_skinny_supported(const GemmArgs& g) {
+  if (g.in_bf16 && g.batch <= 1 && !g.batches_dev && !g.a_trans && g.b_trans && g.m >= 1 && g.m <= 2 && g.n >= 1024 &&
+      g.k >= 8 && g.k % 8 == 0 && g.ldb % 8 == 0 && (((uintptr_t)g.b) & 15) == 0 && !g.n_more && !g.multicast && g.epi_mode == 0)
+    return (uint64_t)8 * g.k * sizeof(float) <= 96 * 1024;   // B stored [n, k]: the transposed kernel, A in shared memory
   if (!(g.in_bf16 && g.batch <= 1 && !g.batches_dev && !g.a_trans && !g.b_trans && g.m >= 1 && g.m <= 4 && g.n >= 8 &&
         g.n % 8 == 0 && g.ldb % 8 == 0 && g.k >= 1 && (((uintptr_t)g.b) & 15) == 0))
     return false;
@@ -113,6 +196,31 @@ bool gemm_skinny_supported(const GemmArgs& g) {
 }
 
 cudaError_t launch_gemm_skinny(const GemmArgs& g, cudaStream_t stream) {
+  if (g.b_trans) {
+    const int mt = g.m <= 1 ? 1 : (g.m <= 2 ? 2 : (g.m <= 4 ? 4 : 8));
+    const size_t smem = (size_t)mt * g.k * sizeof(float);
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    // about four blocks an SM, every warp whole groups of SKT_ROWS rows of B
+    const uint64_t warps_wanted = (uint64_t)sms * 4 * (SKT_THREADS / 32);
+    uint64_t per = (g.n + warps_wanted - 1) / warps_wanted;
+    per = (per + SKT_ROWS - 1) / SKT_ROWS * SKT_ROWS;
+    const uint64_t warps = (g.n + per - 1) / per;
+    const unsigned grid = (unsigned)((warps + SKT_THREADS / 32 - 1) / (SKT_THREADS / 32));
+#define GOT(MT)                                                                                                  \
+  do {                                                                                                           \
+    {                                                                                                            \
+      const cudaError_t e = ensure_dynamic_smem((const void*)gemm_skinny_t_kernel<MT>, smem);                    \
+      if (e != cudaSuccess) return e;                                                                            \
+    }                                                                                                            \
+    launch_pdl(gemm_skinny_t_kernel<MT>, dim3(grid), dim3(SKT_THREADS), smem, stream, (const uint16_t*)g.a, g.lda, (const uint16_t*)g.b, g.ldb, \
+               g.c, g.ldc, g.out_bf16, (int)g.m, g.n, (int)g.k, (uint32_t)per);                                   \
+  } while (0)
+    if (mt == 1) GOT(1); else if (mt == 2) GOT(2); else if (mt == 4) GOT(4); else GOT(8);
+#undef GOT
+    return cudaGetLastError();
+  }
   const int mt = g.m <= 1 ? 1 : (g.m <= 2 ? 2 : (g.m <= 4 ? 4 : 8));
   const size_t smem = ((size_t)mt * g.k + (size_t)(SK_THREADS / 32) * mt * SK_COLS) * sizeof(float);
   const unsigned grid = (unsigned)((g.n + SK_COLS - 1) / SK_COLS);

@@ -288,7 +288,7 @@ def test_bf16_product_at_4096_by_properties(eng):
         eng.free(i)
 
 
-@pytest.mark.parametrize("m", [1, 8, 33])
+@pytest.mark.parametrize("m", [3, 8, 33])
 def test_short_m_products_take_the_tensor_cores(eng, m):
     # a prefill's head: a few rows against a [vocab, hidden] table read transposed
     a = orc.to_bf16(orc.uniform(0xC0F4, 20, (m, 576), -1, 1))
@@ -449,6 +449,29 @@ def test_a_handful_of_rows_streams_the_weights_once(eng, m, kn):
     o32, _ = eng.matmul_dram(ia, False, ib, False)
     assert eng.last_matmul_path() == "skinny"
     assert orc.gemm_rel_error(eng.download(o32), truth, s)[0] <= 1e-6
+    for i in (ia, ib, out, o32):
+        eng.free(i)
+
+
+@pytest.mark.parametrize("m", [1, 2])
+@pytest.mark.parametrize("kn", [(576, 49152), (576, 2048), (64, 1024), (1536, 4100)])
+def test_one_or_two_rows_against_a_table_stored_by_rows(eng, m, kn):   # tt-models/src/llama.rs:1090: the tied head
+    # logits = x table^T: [m, k] x ([n, k])^T with B as stored.  The same claims as above; past two rows, or a short
+    # table, the tensor-core tile takes it.
+    k, n = kn
+    a = orc.to_bf16(orc.uniform(0xC0F8, 1, (m, k), -1, 1))
+    b = orc.to_bf16(orc.uniform(0xC0F8, 2, (n, k), -1, 1))
+    ia, ib = eng.upload_bf16(a, m, k), eng.upload_bf16(b, n, k)
+    o32, dims = eng.matmul_dram(ia, False, ib, True)
+    assert dims == (m, n) and eng.last_matmul_path() == "skinny"
+    af, bf = orc.from_bf16(a).astype(np.float64), orc.from_bf16(b).astype(np.float64)
+    truth = af @ bf.T
+    s = np.abs(af) @ np.abs(bf).T
+    assert np.all(np.abs(eng.download(o32).astype(np.float64) - truth) <= 1e-6 * s)
+    out, _ = eng.matmul_dram_bf16(ia, False, ib, True)
+    assert eng.last_matmul_path() == "skinny"
+    got = orc.from_bf16(eng.download_bf16(out)).astype(np.float64)
+    assert np.all(np.abs(got - truth) <= 2.0 ** -8 * np.abs(truth) + 1e-6 * s)
     for i in (ia, ib, out, o32):
         eng.free(i)
 
