@@ -270,6 +270,58 @@ rope_kernel8(Mat x, Mat cs, Mat sn, uint32_t head, void* out, uint64_t out_ld, i
   }
 }
 
+// RoPE on heads of 64 columns of a BF16 matrix with F32 tables of 64 columns (a Llama layer's query and key heads,
+// crates/tt-models/src/rope.rs:19-60): a warp a row.  A lane takes four consecutive columns j of the low half of a head and
+// the four at j + 32, of one head in four, so a warp's load is four heads' two 64-byte halves; the row's table entries for
+// those columns wait in registers for all of the row's heads (the general kernel fetches them again for every eight
+// outputs: a 4096 x 768 block moved 38 MB through the load pipe for 12.6 MB of heads).  The steps are the general
+// kernel's: fl(fl(x cos) + fl(x' sin)) with x' the element 32 columns across, rounded once to BF16.
+__device__ __forceinline__ uint2 rope_bf16x4(float t0, float t1, float t2, float t3) {
+  // `f32_to_bf16_bits` of four values: the hardware's conversion is that rounding for every number that is zero or at
+  // least 2^-126 in magnitude; the others, and NaNs, take the integer rule
+  const uint32_t a0 = __float_as_uint(t0) & 0x7fffffffu, a1 = __float_as_uint(t1) & 0x7fffffffu;
+  const uint32_t a2 = __float_as_uint(t2) & 0x7fffffffu, a3 = __float_as_uint(t3) & 0x7fffffffu;
+  const uint32_t lo = min(min(a0 - 1u, a1 - 1u), min(a2 - 1u, a3 - 1u)), hi = max(max(a0, a1), max(a2, a3));
+  uint2 o;
+  if (lo < 0x007fffffu || hi > 0x7f800000u) {
+    o.x = (uint32_t)f32_to_bf16_bits(__float_as_uint(t0)) | ((uint32_t)f32_to_bf16_bits(__float_as_uint(t1)) << 16);
+    o.y = (uint32_t)f32_to_bf16_bits(__float_as_uint(t2)) | ((uint32_t)f32_to_bf16_bits(__float_as_uint(t3)) << 16);
+  } else {
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o.x) : "f"(t1), "f"(t0));
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o.y) : "f"(t3), "f"(t2));
+  }
+  return o;
+}
+__global__ void __launch_bounds__(256)
+rope_rows64_kernel(const uint16_t* __restrict__ x, uint64_t x_ld, const float* __restrict__ cs, uint64_t cs_ld,
+                   const float* __restrict__ sn, uint64_t sn_ld, uint64_t table_rows, uint16_t* __restrict__ out, uint64_t out_ld,
+                   uint64_t rows, uint32_t heads) {
+  pdl_enter();
+  const int lane = threadIdx.x & 31;
+  const uint32_t j0 = (lane & 7) * 4, hg = lane >> 3;
+  const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+  for (uint64_t r = warp; r < rows; r += nwarps) {
+    const uint64_t tr = r < table_rows ? r : r % table_rows;
+    const float4 cl = *reinterpret_cast<const float4*>(cs + tr * cs_ld + j0), ch = *reinterpret_cast<const float4*>(cs + tr * cs_ld + 32 + j0);
+    const float4 sl = *reinterpret_cast<const float4*>(sn + tr * sn_ld + j0), sh = *reinterpret_cast<const float4*>(sn + tr * sn_ld + 32 + j0);
+    const uint16_t* xr = x + r * x_ld;
+    uint16_t* orow = out + r * out_ld;
+    for (uint32_t h = hg; h < heads; h += 4) {
+      const uint2 lo = *reinterpret_cast<const uint2*>(xr + h * 64 + j0), hi = *reinterpret_cast<const uint2*>(xr + h * 64 + 32 + j0);
+      const float a0 = __uint_as_float(lo.x << 16), a1 = __uint_as_float(lo.x & 0xffff0000u);
+      const float a2 = __uint_as_float(lo.y << 16), a3 = __uint_as_float(lo.y & 0xffff0000u);
+      const float b0 = __uint_as_float(hi.x << 16), b1 = __uint_as_float(hi.x & 0xffff0000u);
+      const float b2 = __uint_as_float(hi.y << 16), b3 = __uint_as_float(hi.y & 0xffff0000u);
+      *reinterpret_cast<uint2*>(orow + h * 64 + j0) =
+          rope_bf16x4(__fadd_rn(__fmul_rn(a0, cl.x), __fmul_rn(b0, sl.x)), __fadd_rn(__fmul_rn(a1, cl.y), __fmul_rn(b1, sl.y)),
+                      __fadd_rn(__fmul_rn(a2, cl.z), __fmul_rn(b2, sl.z)), __fadd_rn(__fmul_rn(a3, cl.w), __fmul_rn(b3, sl.w)));
+      *reinterpret_cast<uint2*>(orow + h * 64 + 32 + j0) =
+          rope_bf16x4(__fadd_rn(__fmul_rn(b0, ch.x), __fmul_rn(a0, sh.x)), __fadd_rn(__fmul_rn(b1, ch.y), __fmul_rn(a1, sh.y)),
+                      __fadd_rn(__fmul_rn(b2, ch.z), __fmul_rn(a2, sh.z)), __fadd_rn(__fmul_rn(b3, ch.w), __fmul_rn(a3, sh.w)));
+    }
+  }
+}
+
 // ---- casts ---------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 cast_to_bf16(const uint32_t* __restrict__ in, uint16_t* __restrict__ out, uint64_t n) {
@@ -315,6 +367,19 @@ cudaError_t launch_rope(const Mat& x, const Mat& cs, const Mat& sn, uint64_t hea
     const uint64_t eb = m.bf16 ? 2 : 4;
     return m.cols == want_cols && reinterpret_cast<uintptr_t>(m.p) % 16 == 0 && (m.ld * eb) % 16 == 0;
   };
+  // heads of 64 columns, BF16 in and out, F32 tables a head wide: a warp a row, the row's table entries kept for all its heads
+  static int rows_form = -1;
+  if (rows_form < 0) { const char* e = getenv("B200TT_ROPE_ROWS"); rows_form = (e && e[0] == '0') ? 0 : 1; }   // a development switch
+  if (rows_form && head == 64 && x.bf16 && out_bf16 && !cs.bf16 && !sn.bf16 && cs.cols == 64 && sn.cols == 64 && cs.rows == sn.rows && cs.rows > 0 &&
+      cols % 64 == 0 && cols / 64 < (1ull << 31) && x.cols == cols && x.rows == rows && x.ld % 4 == 0 && out_ld % 4 == 0 && cs.ld % 4 == 0 &&
+      sn.ld % 4 == 0 && reinterpret_cast<uintptr_t>(x.p) % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 8 == 0 &&
+      reinterpret_cast<uintptr_t>(cs.p) % 16 == 0 && reinterpret_cast<uintptr_t>(sn.p) % 16 == 0) {
+    uint64_t blocks = (rows + 7) / 8;
+    if (blocks > 148ull * 32) blocks = 148ull * 32;
+    launch_pdl(rope_rows64_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (const uint16_t*)x.p, x.ld, (const float*)cs.p, cs.ld,
+               (const float*)sn.p, sn.ld, cs.rows, (uint16_t*)out, out_ld, rows, (uint32_t)(cols / 64));
+    return cudaGetLastError();
+  }
   if ((head / 2) % 8 == 0 && cols <= 0xffffffffull && ok8(x, cols) && (ok8(cs, head) || ok8(cs, cols)) &&
       (ok8(sn, head) || ok8(sn, cols)) && reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
       (out_ld * (out_bf16 ? 2 : 4)) % 16 == 0) {

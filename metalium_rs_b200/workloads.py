@@ -189,13 +189,14 @@ class LlamaPrefill:
         # (a row's table entries fetched by the row's own thread) costs more than the separate launch: 3.83 against 3.66 ms
         self.fused_rope = cfg.head_dim == 64 and os.environ.get("B200TT_FUSED_ROPE", "0") == "1"
         # the output and down projections straight into the residual stream and its norm (`matmul_add_rms_norm`: one
-        # launch where the composition takes two) only on request (B200TT_FUSED_NORM=1), where hidden is one to eight
-        # tiles of 192 columns and there are at least 64 tokens.  The sums are the composition's bits, the norm's
-        # statistic is added in another fixed order.  Measured it loses: these products are ONE wave of tiles, so the
-        # norm in their epilogue hides under nothing and runs on the 96 SMs that hold a tile where the norm's own launch
-        # fills the device (17.3 against 15.5 us for the pair, 8 x 512 prefill 3.80 against 3.66 ms).
+        # launch where the composition takes two), where hidden is one to eight tiles of 192 columns and there are at
+        # least 64 tokens (B200TT_FUSED_NORM=0: the composition).  The sums are the composition's bits, the norm's
+        # statistic is added in another fixed order.  Timed alone, back to back, the fused launch is the slower one
+        # (17.2 against 15.5 us for the pair: the norm in a one-wave product's epilogue hides under nothing); inside the
+        # layer's chain of launches it saves a launch, its gap and a round trip of the product: 8 x 512 prefill 3.42
+        # against 3.67 ms on the same box.
         self.fused_norm = (cfg.hidden % 192 == 0 and cfg.hidden // 192 <= 8 and batch * seq >= 64 and
-                           os.environ.get("B200TT_FUSED_NORM", "0") == "1")
+                           os.environ.get("B200TT_FUSED_NORM", "1") != "0")
         if self.fused_mlp and cfg.ff % 128:
             raise ValueError("the fused gate|up product needs ff in whole groups of 128 columns")
         takes = cfg.head_dim in (64, 128)                    # any length: a tail tile is masked by index

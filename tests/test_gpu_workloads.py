@@ -186,7 +186,7 @@ def test_traced_prefill_replays_the_eager_bits(eng):  # server.rs:591-660; trace
     l0 = eng.device_traffic().launches
     model.replay()
     per = eng.device_traffic().launches - l0
-    assert per >= 9 * cfg.layers                      # the replay is counted as the kernels it runs
+    assert per >= 6 * cfg.layers                      # the replay is counted as the kernels it runs (six a layer)
     assert np.array_equal(eng.download_bits(tl), eager1)
     eng.copy_into(i2, ii)                              # new ids into the captured input buffer
     model.replay()
